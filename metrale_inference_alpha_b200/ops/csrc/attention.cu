@@ -1,0 +1,900 @@
+// Paged attention for GQA models on sm_100a.
+//
+//   mb_qk_norm_rope_kvwrite  per-head RMSNorm (optional) + NeoX RoPE (optional, partial
+//                            rotary) on q and k, then K/V rows scattered into the paged
+//                            cache by slot id, bf16 or e4m3 with a per-tensor scale.
+//   mb_paged_attention       one kernel family for decode (1 query token), speculative
+//                            verify (a few query tokens) and chunked prefill (many):
+//                              * "split-KV" kernel: a CTA owns one (kv head, sequence,
+//                                512-token partition); its 4 warps each take 16 of every
+//                                64 cached tokens, all G*q_len query rows ride in the
+//                                m16 rows of the tensor-core tiles, warps merge through
+//                                shared memory, partitions merge in a second kernel.
+//                                The partition size is fixed, so the result for one
+//                                sequence never depends on what else is in the batch.
+//                              * "split-Q" kernel (prefill): a CTA owns 64 query rows of
+//                                one (q head, sequence), 16 per warp, and walks the
+//                                causal range of cached tokens FlashAttention-2 style.
+// Cache layout (both K and V): [num_blocks, block_size, kv_heads, head_dim].
+// e4m3 cache rows are widened to f16 while being staged into shared memory with an
+// integer bit trick (exact, 2^-8 scale folded into the softmax/output scales); bf16
+// caches are staged as they are. The contraction is mma.sync m16n8k16 (these kernels
+// are bandwidth-bound on the KV stream; the query side has at most 64 rows).
+//
+// Reference behaviour covered: kernels/gb10/common/fused_k_norm_rope_cache.cu,
+// reshape_and_cache.cu, rope.cu, paged_decode_attn{,_fp8,_bf16_gqa,_fp8_gqa}.cu
+// (+ split-K reduce), prefill_paged_compute.cuh and attn_prefill_paged{,_fp8,_batched}.cu.
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------ rope + kv write
+struct RopeKvParams {
+  int M, Hq, Hkv, D, rot;
+  const __nv_bfloat16* qkv;      // [M, qkv_ld]: q heads, then k heads, then v heads
+  long long qkv_ld;
+  int q_head_stride;             // D, or 2*D when an output gate is interleaved per head
+  int k_off, v_off;              // element offsets of k / v inside a row
+  const int* positions;          // [M]
+  const long long* slots;        // [M] flat slot = block * block_size + offset; <0 skips
+  const __nv_bfloat16* q_norm_w; // [D] or null
+  const __nv_bfloat16* k_norm_w;
+  int norm_plus_one;
+  float eps;
+  const float* cos_tab;          // [max_pos, rot/2] or null (no rope)
+  const float* sin_tab;
+  int max_pos;
+  __nv_bfloat16* q_out;          // [M, Hq, D]
+  void* k_cache;
+  void* v_cache;
+  int cache_fp8;
+  const float* k_scale;          // per-tensor dequant multipliers (fp8 cache)
+  const float* v_scale;
+  long long num_slots;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKvParams p) {
+  const int m = blockIdx.x;
+  const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int Htot = p.Hq + 2 * p.Hkv;
+  if (head >= Htot) return;
+  const int D = p.D;
+  const int per = D / 32;  // <= 8
+  const __nv_bfloat16* src;
+  int kind;  // 0 q, 1 k, 2 v
+  int h;
+  if (head < p.Hq) { kind = 0; h = head; src = p.qkv + (size_t)m * p.qkv_ld + (size_t)h * p.q_head_stride; }
+  else if (head < p.Hq + p.Hkv) { kind = 1; h = head - p.Hq; src = p.qkv + (size_t)m * p.qkv_ld + p.k_off + (size_t)h * D; }
+  else { kind = 2; h = head - p.Hq - p.Hkv; src = p.qkv + (size_t)m * p.qkv_ld + p.v_off + (size_t)h * D; }
+
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = j < per ? __bfloat162float(src[lane + 32 * j]) : 0.f;
+
+  if (kind != 2) {
+    const __nv_bfloat16* nw = kind == 0 ? p.q_norm_w : p.k_norm_w;
+    if (nw) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+      ss = mb::warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)D + p.eps);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < per) {
+          float w = __bfloat162float(nw[lane + 32 * j]);
+          if (p.norm_plus_one) w += 1.f;
+          // the normalised value passes through bf16 like an unfused norm kernel's output
+          v[j] = __bfloat162float(__float2bfloat16(v[j] * inv * w));
+        }
+    }
+    if (p.cos_tab) {
+      int pos = p.positions[m];
+      if (pos < 0 || pos >= p.max_pos) {
+        if (lane == 0 && p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
+        pos = 0;
+      }
+      const int half = p.rot / 2;       // multiple of 32
+      const int hj = half / 32;         // register distance between pair members
+      const float* c = p.cos_tab + (size_t)pos * half;
+      const float* s = p.sin_tab + (size_t)pos * half;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (j < hj) {
+          const int i = lane + 32 * j;
+          const float x1 = v[j], x2 = v[j + hj];
+          const float cs = c[i], sn = s[i];
+          v[j] = x1 * cs - x2 * sn;
+          v[j + hj] = x2 * cs + x1 * sn;
+        }
+    }
+  }
+
+  if (kind == 0) {
+    __nv_bfloat16* dst = p.q_out + ((size_t)m * p.Hq + h) * D;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < per) dst[lane + 32 * j] = __float2bfloat16(v[j]);
+    return;
+  }
+  const long long slot = p.slots[m];
+  if (slot < 0) return;
+  if (slot >= p.num_slots) {
+    if (lane == 0 && p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
+    return;
+  }
+  const size_t off = ((size_t)slot * p.Hkv + h) * D;
+  if (p.cache_fp8) {
+    const float sc = kind == 1 ? *p.k_scale : *p.v_scale;
+    const float inv = 1.f / sc;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(kind == 1 ? p.k_cache : p.v_cache) + off;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < per) dst[lane + 32 * j] = mb::float_to_e4m3(v[j] * inv);
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(kind == 1 ? p.k_cache : p.v_cache) + off;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < per) dst[lane + 32 * j] = __float2bfloat16(v[j]);
+  }
+}
+
+// ------------------------------------------------------------------ mma helpers
+template <bool F16>
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  if constexpr (F16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+__device__ __forceinline__ void ldsm4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (F16) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+// two e4m3 bytes (low 16 bits of x) -> f16x2 holding value * 2^-8 (exact, incl. denormals)
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2_scaled(uint32_t x) {
+  const uint32_t w = __byte_perm(x, 0, 0x1404);  // b0 -> bits 15:8, b1 -> bits 31:24
+  return (w & 0x80008000u) | ((w & 0x7F007F00u) >> 1);
+}
+// Shared-memory tile of 16-bit elements, rows of D elements, 16-byte chunks XOR-swizzled by
+// (row & 7) so ldmatrix row fetches spread over all banks.
+template <int D>
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+  return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
+}
+
+struct AttnParams {
+  const __nv_bfloat16* q;   // [rows, Hq, D]
+  const void* k_cache;
+  const void* v_cache;
+  const int* block_table;   // [num_seqs, max_blocks]
+  int max_blocks;
+  const int* q_start;       // [num_seqs] first query row of the sequence
+  const int* q_len;         // [num_seqs]
+  const int* ctx_len;       // [num_seqs] cached tokens including this step's
+  int Hq, Hkv, block_size;
+  long long num_blocks;
+  float scale;              // softmax scale
+  const float* k_scale;
+  const float* v_scale;
+  __nv_bfloat16* out;       // [rows, Hq, D]
+  float* part_o;            // [rows, Hq, parts, D]
+  float* part_ml;           // [rows, Hq, parts, 2]
+  int parts, part_tokens;
+  int window;               // sliding window (0 = none)
+  uint32_t* status;
+};
+
+// Stage a [64 x D] tile of cache rows for one kv head into shared memory.
+//   e4m3 cache: fetch() issues the global loads into registers, commit() widens to f16
+//               and stores into the tile (register prefetch across the compute phase);
+//   bf16 cache: fetch() issues cp.async straight into the tile, commit() waits for them.
+template <int D, bool FP8>
+struct TileLoader {
+  static constexpr int kChunkElems = FP8 ? 16 : 8;           // elements per 16-byte load
+  static constexpr int kChunksPerRow = D / kChunkElems;
+  static constexpr int kTotal = 64 * kChunksPerRow;
+  static constexpr int kPerThread = kTotal / 128;
+  uint4 regs[FP8 ? kPerThread : 1];
+  __device__ __forceinline__ void fetch(const AttnParams& p, const void* cache, const int* bt,
+                                        int kv_head, int tok0, int tok_end, int tid,
+                                        uint32_t smem_tile) {
+    const int esize = FP8 ? 1 : 2;
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int idx = tid + i * 128;
+      const int r = idx / kChunksPerRow, c = idx - r * kChunksPerRow;
+      const int tok = tok0 + r;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(cache);
+      bool valid = tok < tok_end;
+      if (valid) {
+        long long blk = bt[tok / p.block_size];
+        if (blk < 0 || blk >= p.num_blocks) {
+          if (p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
+          valid = false;
+        } else {
+          src += (((size_t)blk * p.block_size + (tok % p.block_size)) * p.Hkv + kv_head) * D * esize +
+                 (size_t)c * 16;
+        }
+      }
+      if constexpr (FP8) {
+        regs[i] = valid ? __ldg(reinterpret_cast<const uint4*>(src)) : make_uint4(0, 0, 0, 0);
+      } else {
+        const uint32_t dst = smem_tile + tile_off<D>(r, c);
+        const int sz = valid ? 16 : 0;                        // 0 -> zero fill
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz)
+                     : "memory");
+      }
+    }
+    if constexpr (!FP8) asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  __device__ __forceinline__ void commit(uint32_t smem_tile, int tid) {
+    if constexpr (!FP8) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      return;
+    } else {
+#pragma unroll
+      for (int i = 0; i < kPerThread; ++i) {
+        const int idx = tid + i * 128;
+        const int r = idx / kChunksPerRow, c = idx - r * kChunksPerRow;
+        const uint4 v = regs[i];
+        uint4 lo, hi;
+        lo.x = e4m3x2_to_f16x2_scaled(v.x);
+        lo.y = e4m3x2_to_f16x2_scaled(v.x >> 16);
+        lo.z = e4m3x2_to_f16x2_scaled(v.y);
+        lo.w = e4m3x2_to_f16x2_scaled(v.y >> 16);
+        hi.x = e4m3x2_to_f16x2_scaled(v.z);
+        hi.y = e4m3x2_to_f16x2_scaled(v.z >> 16);
+        hi.z = e4m3x2_to_f16x2_scaled(v.w);
+        hi.w = e4m3x2_to_f16x2_scaled(v.w >> 16);
+        const uint32_t a0 = smem_tile + tile_off<D>(r, 2 * c);
+        const uint32_t a1 = smem_tile + tile_off<D>(r, 2 * c + 1);
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(lo.x), "r"(lo.y),
+                     "r"(lo.z), "r"(lo.w) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a1), "r"(hi.x), "r"(hi.y),
+                     "r"(hi.z), "r"(hi.w) : "memory");
+      }
+    }
+  }
+};
+
+// ------------------------------------------------------------------ split-KV kernel
+// grid (Hkv, num_seqs, parts), 128 threads. MT = number of m16 query-row tiles.
+template <int D, bool FP8, int MT>
+__global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
+  constexpr bool F16 = FP8;
+  constexpr int kTile = 64;
+  constexpr int kTileBytes = kTile * D * 2;
+  extern __shared__ __align__(128) uint8_t smem_attn[];
+  const uint32_t sbase = mb::smem_u32(smem_attn);
+  const uint32_t sQ = sbase;                                   // MT*16 rows
+  const uint32_t sK = sbase + MT * 16 * D * 2;                 // 2 buffers
+  const uint32_t sV = sK + 2 * kTileBytes;                     // 2 buffers
+  const int kvh = blockIdx.x, seq = blockIdx.y, part = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.Hq / p.Hkv;
+  const int qlen = p.q_len[seq], ctx = p.ctx_len[seq], qs = p.q_start[seq];
+  const int R = G * qlen;                                      // valid query rows
+  if (qlen <= 0) return;
+  int tok_begin = part * p.part_tokens;
+  int tok_end = min(ctx, tok_begin + p.part_tokens);
+  if (p.window > 0) tok_begin = max(tok_begin, ctx - qlen + 1 - p.window);
+  const bool empty = tok_begin >= tok_end;
+  const int* bt = p.block_table + (size_t)seq * p.max_blocks;
+
+  if (!empty) {
+    // Q rows -> shared (row r = query token r / G, head r % G), widened/copied as 16-bit
+    for (int idx = tid; idx < MT * 16 * (D / 8); idx += 128) {
+      const int r = idx / (D / 8), c = idx - r * (D / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < R) {
+        const int t = r / G, g = r - t * G;
+        v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + t) * p.Hq + kvh * G + g) * D + c * 8);
+        if constexpr (F16) {
+          const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+          uint4 o;
+          uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(b[i]);
+            oo[i] = pack2<true>(f.x, f.y);
+          }
+          v = o;
+        }
+      }
+      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + tile_off<D>(r, c)), "r"(v.x),
+                   "r"(v.y), "r"(v.z), "r"(v.w));
+    }
+  }
+
+  float o_acc[MT][D / 8][4];
+  float m_run[MT][2], l_run[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    m_run[mt][0] = m_run[mt][1] = -INFINITY;
+    l_run[mt][0] = l_run[mt][1] = 0.f;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o_acc[mt][n][i] = 0.f;
+  }
+  // scores are scaled into the log2 domain once
+  const float kmul = FP8 ? (*p.k_scale) * 256.f : 1.f;
+  const float sc_log2 = p.scale * kmul * 1.44269504088896f;
+
+  if (!empty) {
+    TileLoader<D, FP8> ldK, ldV;
+    const int ntiles = (tok_end - tok_begin + kTile - 1) / kTile;
+    ldK.fetch(p, p.k_cache, bt, kvh, tok_begin, tok_end, tid, sK);
+    ldV.fetch(p, p.v_cache, bt, kvh, tok_begin, tok_end, tid, sV);
+    for (int it = 0; it < ntiles; ++it) {
+      const int buf = it & 1;
+      ldK.commit(sK + buf * kTileBytes, tid);
+      ldV.commit(sV + buf * kTileBytes, tid);
+      __syncthreads();
+      if (it + 1 < ntiles) {
+        ldK.fetch(p, p.k_cache, bt, kvh, tok_begin + (it + 1) * kTile, tok_end, tid,
+                  sK + (buf ^ 1) * kTileBytes);
+        ldV.fetch(p, p.v_cache, bt, kvh, tok_begin + (it + 1) * kTile, tok_end, tid,
+                  sV + (buf ^ 1) * kTileBytes);
+      }
+      const int tok0 = tok_begin + it * kTile + warp * 16;     // this warp's 16 tokens
+      if (tok0 < tok_end) {
+        const uint32_t kT = sK + buf * kTileBytes, vT = sV + buf * kTileBytes;
+        // S = Q K^T : [MT*16 x 16]
+        float s[MT][2][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[mt][n][i] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          uint32_t b[4];
+          {
+            // matrices: (tok 0-7, k lo) (tok 0-7, k hi) (tok 8-15, k lo) (tok 8-15, k hi)
+            const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+            const int chunk = ks * 2 + ((lane >> 3) & 1);
+            ldsm4(b, kT + tile_off<D>(row, chunk));
+          }
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            uint32_t a[4];
+            const int row = mt * 16 + (lane & 15);
+            const int chunk = ks * 2 + (lane >> 4);
+            ldsm4(a, sQ + tile_off<D>(row, chunk));
+            mma16816<F16>(s[mt][0], a, b[0], b[1]);
+            mma16816<F16>(s[mt][1], a, b[2], b[3]);
+          }
+        }
+        // online softmax over this warp's 16 tokens
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+          for (int hr = 0; hr < 2; ++hr) {                      // rows g and g + 8
+            const int r = mt * 16 + (lane >> 2) + hr * 8;
+            const int tq = r / G;
+            const int limit = ctx - qlen + tq + 1;              // causal: tokens < limit
+            const int wlo = p.window > 0 ? limit - p.window : 0;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const int tok = tok0 + n * 8 + (lane & 3) * 2 + i;
+                float v = s[mt][n][hr * 2 + i] * sc_log2;
+                if (tok >= limit || tok >= tok_end || tok < wlo || r >= R) v = -INFINITY;
+                s[mt][n][hr * 2 + i] = v;
+                mx = fmaxf(mx, v);
+              }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[mt][hr], mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = exp2f(m_run[mt][hr] - m_use);   // 0 when m_run = -inf
+            float rs = 0.f;
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const float pv = exp2f(s[mt][n][hr * 2 + i] - m_use);
+                s[mt][n][hr * 2 + i] = pv;
+                rs += pv;
+              }
+            l_run[mt][hr] = l_run[mt][hr] * alpha + rs;
+            m_run[mt][hr] = m_new;
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n) {
+              o_acc[mt][n][hr * 2] *= alpha;
+              o_acc[mt][n][hr * 2 + 1] *= alpha;
+            }
+          }
+        }
+        // O += P V  (k = 16 tokens)
+        uint32_t pa[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          pa[mt][0] = pack2<F16>(s[mt][0][0], s[mt][0][1]);
+          pa[mt][1] = pack2<F16>(s[mt][0][2], s[mt][0][3]);
+          pa[mt][2] = pack2<F16>(s[mt][1][0], s[mt][1][1]);
+          pa[mt][3] = pack2<F16>(s[mt][1][2], s[mt][1][3]);
+        }
+#pragma unroll
+        for (int n2 = 0; n2 < D / 16; ++n2) {
+          uint32_t b[4];
+          {
+            // matrices: (tok 0-7, dims lo) (tok 8-15, dims lo) (tok 0-7, dims hi) (tok 8-15, dims hi)
+            const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            const int chunk = n2 * 2 + (lane >> 4);
+            ldsm4t(b, vT + tile_off<D>(row, chunk));
+          }
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma16816<F16>(o_acc[mt][n2 * 2], pa[mt], b[0], b[1]);
+            mma16816<F16>(o_acc[mt][n2 * 2 + 1], pa[mt], b[2], b[3]);
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+
+  // ---- merge the 4 warps through shared memory (tile buffers are free now)
+  // layout: ml[warp][row][2], o[warp][row][D]
+  float* s_ml = reinterpret_cast<float*>(smem_attn + MT * 16 * D * 2);
+  float* s_o = s_ml + 4 * MT * 16 * 2;
+  const float vmul = FP8 ? (*p.v_scale) * 256.f : 1.f;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int r = mt * 16 + (lane >> 2) + hr * 8;
+      float l = l_run[mt][hr];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if ((lane & 3) == 0) {
+        s_ml[(warp * MT * 16 + r) * 2] = m_run[mt][hr];
+        s_ml[(warp * MT * 16 + r) * 2 + 1] = l;
+      }
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        float* dst = s_o + ((size_t)(warp * MT * 16 + r)) * D + n * 8 + (lane & 3) * 2;
+        dst[0] = o_acc[mt][n][hr * 2];
+        dst[1] = o_acc[mt][n][hr * 2 + 1];
+      }
+    }
+  __syncthreads();
+  for (int idx = tid; idx < R * (D / 4); idx += 128) {
+    const int r = idx / (D / 4), c4 = idx - r * (D / 4);
+    float mw[4], lw[4];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      mw[w] = s_ml[(w * MT * 16 + r) * 2];
+      lw[w] = s_ml[(w * MT * 16 + r) * 2 + 1];
+      mx = fmaxf(mx, mw[w]);
+    }
+    float l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = mw[w] == -INFINITY ? 0.f : exp2f(mw[w] - mx);
+      l += lw[w] * f;
+      const float4 ov = *reinterpret_cast<const float4*>(s_o + ((size_t)(w * MT * 16 + r)) * D + c4 * 4);
+      acc.x += ov.x * f; acc.y += ov.y * f; acc.z += ov.z * f; acc.w += ov.w * f;
+    }
+    const float inv = l > 0.f ? vmul / l : 0.f;
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    const int t = r / G, g = r - t * G;
+    const size_t orow = (size_t)(qs + t) * p.Hq + kvh * G + g;
+    if (p.parts == 1) {
+      __nv_bfloat16* dst = p.out + orow * D + c4 * 4;
+      *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x, acc.y);
+      *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z, acc.w);
+    } else {
+      *reinterpret_cast<float4*>(p.part_o + (orow * p.parts + part) * D + c4 * 4) = acc;
+      if (c4 == 0) {
+        p.part_ml[(orow * p.parts + part) * 2] = mx;          // log2-domain max
+        p.part_ml[(orow * p.parts + part) * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// Merge partitions: out = sum_p w_p * o_p, w_p = l_p 2^(m_p - m) / sum(...)
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                  __nv_bfloat16* __restrict__ out, int parts, int D) {
+  const size_t row = blockIdx.x;  // (query row, head)
+  float mx = -INFINITY;
+  for (int s = 0; s < parts; ++s) mx = fmaxf(mx, part_ml[(row * parts + s) * 2]);
+  float denom = 0.f;
+  for (int s = 0; s < parts; ++s) {
+    const float m = part_ml[(row * parts + s) * 2], l = part_ml[(row * parts + s) * 2 + 1];
+    denom += (m == -INFINITY) ? 0.f : l * exp2f(m - mx);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < parts; ++s) {
+      const float m = part_ml[(row * parts + s) * 2], l = part_ml[(row * parts + s) * 2 + 1];
+      if (m == -INFINITY || l <= 0.f) continue;
+      acc += part_o[(row * parts + s) * D + d] * (l * exp2f(m - mx));
+    }
+    out[row * D + d] = __float2bfloat16(denom > 0.f ? acc / denom : 0.f);
+  }
+}
+
+// ------------------------------------------------------------------ split-Q (prefill) kernel
+// grid (ceil(max_q_len / 64), Hq, num_seqs), 128 threads; warp w owns query rows 16w..16w+15.
+template <int D, bool FP8>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
+  constexpr bool F16 = FP8;
+  constexpr int kTile = 64;
+  constexpr int kTileBytes = kTile * D * 2;
+  extern __shared__ __align__(128) uint8_t smem_attn[];
+  const uint32_t sbase = mb::smem_u32(smem_attn);
+  const uint32_t sQ = sbase;
+  const uint32_t sK = sbase + kTileBytes;
+  const uint32_t sV = sK + 2 * kTileBytes;
+  const int qt = blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.Hq / p.Hkv, kvh = head / G;
+  const int qlen = p.q_len[seq], ctx = p.ctx_len[seq], qs = p.q_start[seq];
+  const int q0 = qt * 64;
+  if (q0 >= qlen) return;
+  const int* bt = p.block_table + (size_t)seq * p.max_blocks;
+  const int past = ctx - qlen;                                 // tokens cached before this chunk
+  const int tok_end = min(ctx, past + q0 + 64);                // causal upper bound for the tile
+  int tok_begin = 0;
+  if (p.window > 0) tok_begin = max(0, past + q0 + 1 - p.window);
+  tok_begin &= ~63;
+
+  for (int idx = tid; idx < 64 * (D / 8); idx += 128) {
+    const int r = idx / (D / 8), c = idx - r * (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (q0 + r < qlen) {
+      v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + q0 + r) * p.Hq + head) * D + c * 8);
+      if constexpr (F16) {
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+        uint4 o;
+        uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(b[i]);
+          oo[i] = pack2<true>(f.x, f.y);
+        }
+        v = o;
+      }
+    }
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + tile_off<D>(r, c)), "r"(v.x),
+                 "r"(v.y), "r"(v.z), "r"(v.w));
+  }
+
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o_acc[n][i] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float kmul = FP8 ? (*p.k_scale) * 256.f : 1.f;
+  const float sc_log2 = p.scale * kmul * 1.44269504088896f;
+
+  TileLoader<D, FP8> ldK, ldV;
+  const int ntiles = (tok_end - tok_begin + kTile - 1) / kTile;
+  ldK.fetch(p, p.k_cache, bt, kvh, tok_begin, tok_end, tid, sK);
+  ldV.fetch(p, p.v_cache, bt, kvh, tok_begin, tok_end, tid, sV);
+  for (int it = 0; it < ntiles; ++it) {
+    const int buf = it & 1;
+    ldK.commit(sK + buf * kTileBytes, tid);
+    ldV.commit(sV + buf * kTileBytes, tid);
+    __syncthreads();
+    if (it + 1 < ntiles) {
+      ldK.fetch(p, p.k_cache, bt, kvh, tok_begin + (it + 1) * kTile, tok_end, tid,
+                sK + (buf ^ 1) * kTileBytes);
+      ldV.fetch(p, p.v_cache, bt, kvh, tok_begin + (it + 1) * kTile, tok_end, tid,
+                sV + (buf ^ 1) * kTileBytes);
+    }
+    const uint32_t kT = sK + buf * kTileBytes, vT = sV + buf * kTileBytes;
+    const int tile_tok0 = tok_begin + it * kTile;
+    // S[16 x 64] for this warp
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a[4];
+      ldsm4(a, sQ + tile_off<D>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        uint32_t b[4];
+        const int row = nb * 16 + (lane & 7) + ((lane >> 4) << 3);
+        ldsm4(b, kT + tile_off<D>(row, ks * 2 + ((lane >> 3) & 1)));
+        mma16816<F16>(s[nb * 2], a, b[0], b[1]);
+        mma16816<F16>(s[nb * 2 + 1], a, b[2], b[3]);
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int qr = q0 + warp * 16 + (lane >> 2) + hr * 8;    // query index inside the chunk
+      const int limit = past + qr + 1;
+      const int wlo = p.window > 0 ? limit - p.window : 0;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int tok = tile_tok0 + n * 8 + (lane & 3) * 2 + i;
+          float v = s[n][hr * 2 + i] * sc_log2;
+          if (tok >= limit || tok >= tok_end || tok < wlo || qr >= qlen) v = -INFINITY;
+          s[n][hr * 2 + i] = v;
+          mx = fmaxf(mx, v);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[hr], mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      alpha[hr] = exp2f(m_run[hr] - m_use);
+      float rs = 0.f;
+#pragma unroll
+      for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float pv = exp2f(s[n][hr * 2 + i] - m_use);
+          s[n][hr * 2 + i] = pv;
+          rs += pv;
+        }
+      l_run[hr] = l_run[hr] * alpha[hr] + rs;
+      m_run[hr] = m_new;
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      o_acc[n][0] *= alpha[0]; o_acc[n][1] *= alpha[0];
+      o_acc[n][2] *= alpha[1]; o_acc[n][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kb = 0; kb < 4; ++kb) {                            // 16 tokens per k step
+      uint32_t pa[4];
+      pa[0] = pack2<F16>(s[kb * 2][0], s[kb * 2][1]);
+      pa[1] = pack2<F16>(s[kb * 2][2], s[kb * 2][3]);
+      pa[2] = pack2<F16>(s[kb * 2 + 1][0], s[kb * 2 + 1][1]);
+      pa[3] = pack2<F16>(s[kb * 2 + 1][2], s[kb * 2 + 1][3]);
+#pragma unroll
+      for (int n2 = 0; n2 < D / 16; ++n2) {
+        uint32_t b[4];
+        const int row = kb * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        ldsm4t(b, vT + tile_off<D>(row, n2 * 2 + (lane >> 4)));
+        mma16816<F16>(o_acc[n2 * 2], pa, b[0], b[1]);
+        mma16816<F16>(o_acc[n2 * 2 + 1], pa, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  const float vmul = FP8 ? (*p.v_scale) * 256.f : 1.f;
+#pragma unroll
+  for (int hr = 0; hr < 2; ++hr) {
+    float l = l_run[hr];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int qr = q0 + warp * 16 + (lane >> 2) + hr * 8;
+    if (qr >= qlen) continue;
+    const float inv = l > 0.f ? vmul / l : 0.f;
+    __nv_bfloat16* dst = p.out + ((size_t)(qs + qr) * p.Hq + head) * D + (lane & 3) * 2;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+      *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) =
+          __floats2bfloat162_rn(o_acc[n][hr * 2] * inv, o_acc[n][hr * 2 + 1] * inv);
+  }
+}
+
+template <int D, bool FP8, int MT>
+int launch_splitkv(const AttnParams& p, int num_seqs, cudaStream_t stream) {
+  constexpr int kTileBytes = 64 * D * 2;
+  constexpr int kMerge = 4 * MT * 16 * 2 * 4 + 4 * MT * 16 * D * 4;
+  constexpr int kLoop = 4 * kTileBytes;
+  constexpr int smem = MT * 16 * D * 2 + (kMerge > kLoop ? kMerge : kLoop);
+  auto kern = attn_splitkv_kernel<D, FP8, MT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<dim3(p.Hkv, num_seqs, p.parts), 128, smem, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+template <int D, bool FP8>
+int launch_prefill(const AttnParams& p, int num_seqs, int max_q_len, cudaStream_t stream) {
+  constexpr int smem = 5 * 64 * D * 2;
+  auto kern = attn_prefill_kernel<D, FP8>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<dim3((max_q_len + 63) / 64, p.Hq, num_seqs), 128, smem, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+template <int D, bool FP8>
+int dispatch_mt(int mt, const AttnParams& p, int num_seqs, cudaStream_t stream) {
+  if (mt == 1) return launch_splitkv<D, FP8, 1>(p, num_seqs, stream);
+  // two m16 row tiles keep 2 * D / 2 accumulator registers per thread: fits up to D = 128
+  if constexpr (D <= 128) {
+    if (mt == 2) return launch_splitkv<D, FP8, 2>(p, num_seqs, stream);
+  }
+  return MB_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+extern "C" {
+
+struct MbRopeKvArgs {
+  int M, Hq, Hkv, D, rot;
+  const void* qkv;
+  long long qkv_ld;
+  int q_head_stride, k_off, v_off;
+  const int* positions;
+  const long long* slots;
+  const void* q_norm_w;
+  const void* k_norm_w;
+  int norm_plus_one;
+  float eps;
+  const float* cos_tab;
+  const float* sin_tab;
+  int max_pos;
+  void* q_out;
+  void* k_cache;
+  void* v_cache;
+  int cache_fp8;
+  const float* k_scale;
+  const float* v_scale;
+  long long num_slots;
+  uint32_t* status;
+};
+
+int mb_qk_norm_rope_kvwrite(const MbRopeKvArgs* a, cudaStream_t stream) {
+  if (!a || a->M <= 0 || !a->qkv || !a->q_out || !a->slots) return MB_ERR_BAD_ARG;
+  if (a->D % 32 || a->D > 256) return MB_ERR_UNSUPPORTED;
+  if (a->cos_tab && (a->rot % 64 || a->rot > a->D || !a->positions)) return MB_ERR_UNSUPPORTED;
+  if (a->cache_fp8 && (!a->k_scale || !a->v_scale)) return MB_ERR_BAD_ARG;
+  RopeKvParams p{};
+  p.M = a->M; p.Hq = a->Hq; p.Hkv = a->Hkv; p.D = a->D; p.rot = a->rot;
+  p.qkv = reinterpret_cast<const __nv_bfloat16*>(a->qkv); p.qkv_ld = a->qkv_ld;
+  p.q_head_stride = a->q_head_stride; p.k_off = a->k_off; p.v_off = a->v_off;
+  p.positions = a->positions; p.slots = a->slots;
+  p.q_norm_w = reinterpret_cast<const __nv_bfloat16*>(a->q_norm_w);
+  p.k_norm_w = reinterpret_cast<const __nv_bfloat16*>(a->k_norm_w);
+  p.norm_plus_one = a->norm_plus_one; p.eps = a->eps;
+  p.cos_tab = a->cos_tab; p.sin_tab = a->sin_tab; p.max_pos = a->max_pos;
+  p.q_out = reinterpret_cast<__nv_bfloat16*>(a->q_out);
+  p.k_cache = a->k_cache; p.v_cache = a->v_cache; p.cache_fp8 = a->cache_fp8;
+  p.k_scale = a->k_scale; p.v_scale = a->v_scale; p.num_slots = a->num_slots;
+  p.status = a->status;
+  const int Htot = a->Hq + 2 * a->Hkv;
+  rope_kv_kernel<<<dim3(a->M, (Htot + 3) / 4), 128, 0, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+struct MbAttnArgs {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const int* block_table;
+  int max_blocks;
+  const int* q_start;
+  const int* q_len;
+  const int* ctx_len;
+  int num_seqs, max_q_len, max_ctx;
+  int Hq, Hkv, D, block_size;
+  long long num_blocks;
+  float scale;
+  int cache_fp8;
+  const float* k_scale;
+  const float* v_scale;
+  void* out;
+  void* ws;                // split-KV partials
+  size_t ws_bytes;
+  int total_rows;          // query rows (for workspace sizing)
+  int part_tokens;         // 0 = default 512
+  int window;
+  int force_mode;          // 0 auto, 1 split-KV, 2 split-Q
+  uint32_t* status;
+};
+
+// workspace bytes for the split-KV path
+size_t mb_attn_ws_bytes(int total_rows, int Hq, int D, int max_ctx, int part_tokens) {
+  const int pt = part_tokens > 0 ? part_tokens : 512;
+  const int parts = (max_ctx + pt - 1) / pt;
+  if (parts <= 1) return 0;
+  return (size_t)total_rows * Hq * parts * (D + 2) * sizeof(float);
+}
+
+int mb_paged_attention(const MbAttnArgs* a, cudaStream_t stream) {
+  if (!a || !a->q || !a->k_cache || !a->v_cache || !a->block_table || !a->out) return MB_ERR_BAD_ARG;
+  if (a->num_seqs <= 0 || a->Hkv <= 0 || a->Hq % a->Hkv) return MB_ERR_BAD_ARG;
+  if (a->cache_fp8 && (!a->k_scale || !a->v_scale)) return MB_ERR_BAD_ARG;
+  AttnParams p{};
+  p.q = reinterpret_cast<const __nv_bfloat16*>(a->q);
+  p.k_cache = a->k_cache; p.v_cache = a->v_cache;
+  p.block_table = a->block_table; p.max_blocks = a->max_blocks;
+  p.q_start = a->q_start; p.q_len = a->q_len; p.ctx_len = a->ctx_len;
+  p.Hq = a->Hq; p.Hkv = a->Hkv; p.block_size = a->block_size; p.num_blocks = a->num_blocks;
+  p.scale = a->scale; p.k_scale = a->k_scale; p.v_scale = a->v_scale;
+  p.out = reinterpret_cast<__nv_bfloat16*>(a->out);
+  p.window = a->window; p.status = a->status;
+  const int G = a->Hq / a->Hkv;
+  const int rows = G * a->max_q_len;
+  int mode = a->force_mode;
+  if (mode == 0) mode = rows <= 32 ? 1 : 2;
+  const bool fp8 = a->cache_fp8 != 0;
+  if (mode == 1) {
+    if (rows > 32) return MB_ERR_UNSUPPORTED;
+    const int mt = rows <= 16 ? 1 : 2;
+    p.part_tokens = a->part_tokens > 0 ? a->part_tokens : 512;
+    p.parts = (a->max_ctx + p.part_tokens - 1) / p.part_tokens;
+    if (p.parts < 1) p.parts = 1;
+    if (p.parts > 1) {
+      const size_t need = (size_t)a->total_rows * a->Hq * p.parts * (a->D + 2) * sizeof(float);
+      if (!a->ws || a->ws_bytes < need) return MB_ERR_TOO_LARGE;
+      p.part_o = reinterpret_cast<float*>(a->ws);
+      p.part_ml = p.part_o + (size_t)a->total_rows * a->Hq * p.parts * a->D;
+    }
+    int rc;
+    if (a->D == 128) rc = fp8 ? dispatch_mt<128, true>(mt, p, a->num_seqs, stream)
+                              : dispatch_mt<128, false>(mt, p, a->num_seqs, stream);
+    else if (a->D == 64) rc = fp8 ? dispatch_mt<64, true>(mt, p, a->num_seqs, stream)
+                                  : dispatch_mt<64, false>(mt, p, a->num_seqs, stream);
+    else if (a->D == 256) rc = fp8 ? dispatch_mt<256, true>(mt, p, a->num_seqs, stream)
+                                   : dispatch_mt<256, false>(mt, p, a->num_seqs, stream);
+    else return MB_ERR_UNSUPPORTED;
+    if (rc) return rc;
+    if (p.parts > 1) {
+      attn_merge_kernel<<<a->total_rows * a->Hq, 128, 0, stream>>>(p.part_o, p.part_ml, p.out,
+                                                                  p.parts, a->D);
+      return (int)cudaGetLastError();
+    }
+    return 0;
+  }
+  p.parts = 1;
+  if (a->D == 128) return fp8 ? launch_prefill<128, true>(p, a->num_seqs, a->max_q_len, stream)
+                              : launch_prefill<128, false>(p, a->num_seqs, a->max_q_len, stream);
+  if (a->D == 64) return fp8 ? launch_prefill<64, true>(p, a->num_seqs, a->max_q_len, stream)
+                             : launch_prefill<64, false>(p, a->num_seqs, a->max_q_len, stream);
+  if (a->D == 256) return fp8 ? launch_prefill<256, true>(p, a->num_seqs, a->max_q_len, stream)
+                              : launch_prefill<256, false>(p, a->num_seqs, a->max_q_len, stream);
+  return MB_ERR_UNSUPPORTED;
+}
+
+}  // extern "C"

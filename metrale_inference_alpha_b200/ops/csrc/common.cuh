@@ -1,0 +1,332 @@
+// Shared device helpers for the sm_100a kernel library: PTX wrappers for
+// mbarrier, TMA (cp.async.bulk[.tensor]), tcgen05 (TMEM alloc, UMMA, commit,
+// ld, cp), bounded waits and the status word every kernel reports through.
+//
+// Conventions used by every kernel in this library
+//   * launchers are `extern "C"`, take raw device pointers + a cudaStream_t
+//     and return 0 or a negative MB_ERR_* / positive cudaError code;
+//   * every spin on an mbarrier or on a flag is bounded by a clock budget;
+//     on expiry the kernel writes a non-zero code into the caller-provided
+//     status word, drains, frees TMEM and returns (no trap, no endless loop);
+//   * all TMA loads are plain (no cluster multicast anywhere in the library).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cstdint>
+
+#define MB_OK 0
+#define MB_ERR_BAD_ARG (-1)
+#define MB_ERR_UNSUPPORTED (-2)
+#define MB_ERR_TOO_LARGE (-3)
+#define MB_ERR_DRIVER (-4)
+
+// device status codes (written to *status by kernels)
+#define MB_ST_OK 0u
+#define MB_ST_TIMEOUT_TMA 0x100u
+#define MB_ST_TIMEOUT_MMA 0x200u
+#define MB_ST_TIMEOUT_EPI 0x300u
+#define MB_ST_TIMEOUT_PEER 0x400u
+#define MB_ST_BOUNDS 0x500u
+
+// ~1 s at 2 GHz: long enough for any legitimate wait, short enough to give a
+// shared GPU back.
+#ifndef MB_WAIT_CYCLES
+#define MB_WAIT_CYCLES (2000000000ll)
+#endif
+
+namespace mb {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n.reg .b32 rx;\n.reg .pred px;\n"
+      "elect.sync rx|px, 0xffffffff;\n"
+      "selp.b32 %0, 1, 0, px;\n}\n"
+      : "+r"(pred));
+  return pred != 0;
+}
+
+// ---------------------------------------------------------------- mbarrier
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false (and records `code`) when the budget runs out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status,
+                                          uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > MB_WAIT_CYCLES) {
+      if (status) atomicCAS(status, 0u, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------- TMA
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0,
+                                            int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0,
+                                            int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// untiled bulk copy: both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// ---------------------------------------------------------------- tcgen05
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are exactly one
+// 128-byte swizzle span (row pitch 128 B, 8-row groups 1024 B apart). The tile
+// base must be 1024-byte aligned; advancing along K inside the span is done by
+// adding the byte offset (>>4) to the start-address field.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // start address
+  d |= (uint64_t)1 << 16;                            // LBO (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                  // SBO: 8 rows * 128 B
+  d |= (uint64_t)1 << 46;                            // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+  return d;
+}
+// MN-major tile with 128-byte swizzle: the contiguous (MN) direction is stored in
+// 128-byte spans, 8 K-rows per 1024-byte group. `lbo_bytes` is the distance between
+// consecutive 128-byte spans along MN, SBO the distance between 8-row groups along K.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t saddr, uint32_t lbo_bytes,
+                                                       uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Un-swizzled descriptor used by tcgen05.cp for scale-factor tiles:
+// 8x128-bit atoms, SBO = 128 B between atoms along rows.
+__device__ __forceinline__ uint64_t umma_desc_sf(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(128 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+// Instruction descriptor, kind::f16 / kind::f8f6f4 (dense, fp32 accumulate).
+// fmt: kind::f16 0=f16 1=bf16 ; kind::f8f6f4 0=e4m3 1=e5m2 5=e2m1.
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, uint32_t b_fmt, uint32_t M,
+                                                  uint32_t N, uint32_t a_mn_major = 0,
+                                                  uint32_t b_mn_major = 0) {
+  return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) |
+         ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+// Instruction descriptor, block-scaled kinds. mxf4nvf4: fmt 1 = e2m1, scale_fmt 0 = ue4m3.
+__host__ __device__ constexpr uint32_t umma_idesc_bs(uint32_t a_fmt, uint32_t b_fmt, uint32_t M,
+                                                     uint32_t N, uint32_t scale_fmt,
+                                                     uint32_t a_sf_id = 0, uint32_t b_sf_id = 0) {
+  return (b_sf_id << 4) | (a_fmt << 7) | (b_fmt << 10) | ((N >> 3) << 17) | (scale_fmt << 23) |
+         ((M >> 4) << 24) | (a_sf_id << 29);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f8f6f4(uint32_t d_tmem, uint64_t a, uint64_t b,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_nvfp4(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                           uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X"
+      " [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::"r"(d_tmem),
+      "l"(a), "l"(b), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// smem -> TMEM copy of one 32-row x 128-bit block, replicated to the 4 lane quadrants.
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
+  uint32_t r[8];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// ---------------------------------------------------------------- numerics
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum for blockDim.x <= 1024 (scratch: 32 floats of shared memory).
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) scratch[w] = v;
+  __syncthreads();
+  float t = (l < nw) ? scratch[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) scratch[w] = v;
+  __syncthreads();
+  float t = (l < nw) ? scratch[l] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t b) {
+  __nv_fp8_e4m3 t;
+  t.__x = b;
+  return static_cast<float>(t);
+}
+__device__ __forceinline__ uint8_t float_to_e4m3(float f) {
+  return __nv_cvt_float_to_fp8(f, __NV_SATFINITE, __NV_E4M3);
+}
+// E2M1 magnitude code (3 bits) for |x| with round-to-nearest-even on the
+// {0,.5,1,1.5,2,3,4,6} grid, saturating at 6.
+__device__ __forceinline__ uint32_t e2m1_code(float x) {
+  const float a = fabsf(x);
+  uint32_t c;
+  if (a <= 0.25f) c = 0;
+  else if (a < 0.75f) c = 1;
+  else if (a <= 1.25f) c = 2;
+  else if (a < 1.75f) c = 3;
+  else if (a <= 2.5f) c = 4;
+  else if (a < 3.5f) c = 5;
+  else if (a <= 5.0f) c = 6;
+  else c = 7;
+  return c | (x < 0.f ? 8u : 0u);
+}
+__device__ __forceinline__ float e2m1_value(uint32_t code) {
+  const float lut[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  const float m = lut[code & 7];
+  return (code & 8) ? -m : m;
+}
+
+// Byte offset of scale factor (row r, k-group kk in 0..3) inside one 512-byte
+// 128-row x 4 tile in the layout tcgen05.cp (32x128b.warpx4) consumes.
+__host__ __device__ __forceinline__ uint32_t sf_tile_offset(uint32_t r, uint32_t kk) {
+  return (r & 31u) * 16u + ((r >> 5) & 3u) * 4u + kk;
+}
+
+}  // namespace mb

@@ -1,0 +1,491 @@
+// Weight-stationary ("swap-AB") linear layer for sm_100a:
+//     out[m, n] = epilogue( sum_k X[m, k] * W[n, k] )
+// The weight tile is the UMMA "A" operand (M = 128 output features per CTA) and
+// the activation tile is the "B" operand (UMMA N = TN tokens, 16..256), so decode
+// batches of 1..128 tokens waste no tensor work and each CTA streams a
+// [128 x K] slab of weights exactly once through a TMA -> shared -> tcgen05.mma
+// pipeline with the fp32 accumulator in TMEM.
+//
+// Operand kinds
+//   KIND_BF16   W, X bf16                    tcgen05.mma kind::f16
+//   KIND_FP8    W, X e4m3; per-row weight scale and per-token activation scale
+//               applied in the epilogue      tcgen05.mma kind::f8f6f4
+//   KIND_NVFP4  W, X packed e2m1 (two per byte, even k in the low nibble) with
+//               per-16 ue4m3 scale factors staged smem -> TMEM by tcgen05.cp and
+//               an fp32 global scale (x per-token activation scale) in the
+//               epilogue                     kind::mxf4nvf4.block_scale.scale_vec::4X
+//   KIND_FP8_BLOCK  W e4m3 with one fp32 scale per 128x128 block, X e4m3 with one
+//               scale per token per 128-wide k group: each 128-deep k block is
+//               accumulated into one of two TMEM buffers and promoted into fp32
+//               registers by the epilogue warps with both scales applied.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (one TMEM lane quadrant each).
+//
+// Small-N layers (o_proj, down_proj) use split-K over blockIdx.z: every split
+// writes an fp32 partial tile to a caller-provided workspace, bumps a per-tile
+// counter, and the last arriver sums the partials in split order (deterministic)
+// and runs the epilogue; it also re-zeroes the counter so no memset is needed
+// between launches.
+//
+// Reference behaviour covered: the projection GEMM/GEMV tiers of
+// kernels/gb10/common/{dense_gemm_bf16,dense_gemv_bf16*,w4a16_gemm,w4a16_gemv,
+// w8a16_gemm*,w8a8_gemv,fp8_gemm_t_blockscaled}.cu and the W4A4 path of
+// kernels/gb10/qwen3.6-27b/nvfp4/nvfp4_mmq.cu (compiled out for sm_100a there).
+#include "common.cuh"
+#include "tensormap.h"
+
+namespace {
+
+enum { KIND_BF16 = 0, KIND_FP8 = 1, KIND_NVFP4 = 2, KIND_FP8_BLOCK = 3 };
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
+
+struct GemmParams {
+  int M, N, K, ldo;
+  void* out;
+  const __nv_bfloat16* residual;
+  const float* w_scale;   // KIND_FP8: [N]; KIND_FP8_BLOCK: [ceil(N/128), ceil(K/128)]
+  const float* a_scale;   // KIND_FP8 / NVFP4: [M] or null; KIND_FP8_BLOCK: [ceil(K/128), a_ld]
+  int a_ld;
+  float alpha;
+  const uint8_t* sfa;     // NVFP4 tiled scale factors of W: [ceil(N/128)][k64 groups][512]
+  const uint8_t* sfb;     // NVFP4 tiled scale factors of X: [ceil(M/128)][k64 groups][512]
+  int sf_k64;             // number of 64-element k groups allocated per 128-row block
+  float* ws;
+  uint32_t* cnt;
+  int splits, kb_per_split, num_kb;
+  int epilogue, out_f32;
+  uint32_t* status;
+};
+
+constexpr int kTileN = 128;  // output features per CTA (UMMA M)
+
+template <int KIND, int TN>
+struct Cfg {
+  static constexpr int kABytes = kTileN * 128;
+  static constexpr int kBBytes = TN * 128;
+  static constexpr int kSfBytes = (KIND == KIND_NVFP4) ? 2048 : 0;
+  static constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;
+  static constexpr int kBudget = 200 * 1024;
+  static constexpr int kStagesRaw = kBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kAccCols = (KIND == KIND_FP8_BLOCK) ? 2 * TN : TN;
+  static constexpr int kNeedCols = kAccCols + (KIND == KIND_NVFP4 ? 32 : 0);
+  static constexpr int kTmemCols =
+      kNeedCols <= 32 ? 32 : kNeedCols <= 64 ? 64 : kNeedCols <= 128 ? 128 : kNeedCols <= 256 ? 256 : 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+};
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int KIND, int TN>
+__global__ void __launch_bounds__(192, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmParams p) {
+  using C = Cfg<KIND, TN>;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int is_last_s;
+
+  const int warp = threadIdx.x >> 5;
+  const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mb::mbar_init(&full_bar[s], 1);
+      mb::mbar_init(&empty_bar[s], 1);
+    }
+    mb::mbar_init(&acc_full[0], 1);
+    mb::mbar_init(&acc_full[1], 1);
+    mb::mbar_init(&acc_empty[0], 128);
+    mb::mbar_init(&acc_empty[1], 128);
+    mb::mbar_fence_init();
+    mb::tma_prefetch_desc(&tmA);
+    mb::tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) mb::tmem_alloc(&tmem_base_s, C::kTmemCols);
+  mb::tc_fence_before();
+  __syncthreads();
+  mb::tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+
+  auto sA = [&](int s) { return smem + s * C::kStageBytes; };
+  auto sB = [&](int s) { return smem + s * C::kStageBytes + C::kABytes; };
+  auto sSFA = [&](int s) { return smem + s * C::kStageBytes + C::kABytes + C::kBBytes; };
+  auto sSFB = [&](int s) {
+    return smem + s * C::kStageBytes + C::kABytes + C::kBBytes + C::kSfBytes;
+  };
+  // inner TMA coordinate advance per k block, in tensor-map elements
+  constexpr int kCoordStep = (KIND == KIND_BF16) ? 64 : 128;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (mb::elect_one()) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % kStages;
+        const uint32_t ph = (i / kStages) & 1;
+        if (!mb::mbar_wait(&empty_bar[s], ph ^ 1, p.status, MB_ST_TIMEOUT_TMA)) break;
+        mb::mbar_expect_tx(&full_bar[s], C::kStageBytes);
+        const int kb = kb0 + i;
+        mb::tma_load_2d(sA(s), &tmA, &full_bar[s], kb * kCoordStep, tile_n * kTileN);
+        mb::tma_load_2d(sB(s), &tmB, &full_bar[s], kb * kCoordStep, tile_m * TN);
+        if constexpr (KIND == KIND_NVFP4) {
+          const size_t a_off = ((size_t)tile_n * p.sf_k64 + (size_t)kb * 4) * 512;
+          const size_t b_off = ((size_t)((tile_m * TN) / 128) * p.sf_k64 + (size_t)kb * 4) * 512;
+          mb::bulk_load(sSFA(s), p.sfa + a_off, 2048, &full_bar[s]);
+          mb::bulk_load(sSFB(s), p.sfb + b_off, 2048, &full_bar[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (mb::elect_one()) {
+      uint32_t idesc;
+      if constexpr (KIND == KIND_BF16) idesc = mb::umma_idesc(1, 1, kTileN, TN);
+      else if constexpr (KIND == KIND_NVFP4) idesc = mb::umma_idesc_bs(1, 1, kTileN, TN, 0);
+      else idesc = mb::umma_idesc(0, 0, kTileN, TN);
+      constexpr uint32_t kSfaCol = TN, kSfbCol = TN + 16;
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % kStages;
+        const uint32_t ph = (i / kStages) & 1;
+        uint32_t acc = tmem;
+        if constexpr (KIND == KIND_FP8_BLOCK) {
+          const int buf = i & 1;
+          const uint32_t aph = (i >> 1) & 1;
+          ok = mb::mbar_wait(&acc_empty[buf], aph ^ 1, p.status, MB_ST_TIMEOUT_MMA);
+          if (!ok) break;
+          acc = tmem + buf * TN;
+        }
+        ok = mb::mbar_wait(&full_bar[s], ph, p.status, MB_ST_TIMEOUT_MMA);
+        if (!ok) break;
+        mb::tc_fence_after();
+        const uint32_t a_base = mb::smem_u32(sA(s)), b_base = mb::smem_u32(sB(s));
+        if constexpr (KIND == KIND_NVFP4) {
+          const uint32_t sfa = mb::smem_u32(sSFA(s)), sfb = mb::smem_u32(sSFB(s));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            mb::tmem_cp_sf(tmem + kSfaCol + j * 4, mb::umma_desc_sf(sfa + j * 512));
+            mb::tmem_cp_sf(tmem + kSfbCol + j * 4, mb::umma_desc_sf(sfb + j * 512));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint64_t da = mb::umma_desc_sw128(a_base + j * 32);
+          const uint64_t db = mb::umma_desc_sw128(b_base + j * 32);
+          if constexpr (KIND == KIND_BF16) {
+            mb::umma_f16(acc, da, db, idesc, (i | j) != 0);
+          } else if constexpr (KIND == KIND_FP8) {
+            mb::umma_f8f6f4(acc, da, db, idesc, (i | j) != 0);
+          } else if constexpr (KIND == KIND_FP8_BLOCK) {
+            mb::umma_f8f6f4(acc, da, db, idesc, j != 0);
+          } else {
+            mb::umma_nvfp4(acc, da, db, idesc, tmem + kSfaCol + j * 4, tmem + kSfbCol + j * 4,
+                           (i | j) != 0);
+          }
+        }
+        mb::tc_commit(&empty_bar[s]);
+        if constexpr (KIND == KIND_FP8_BLOCK) mb::tc_commit(&acc_full[i & 1]);
+      }
+      if constexpr (KIND != KIND_FP8_BLOCK) mb::tc_commit(&acc_full[0]);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    const int lane = threadIdx.x & 31;
+    const int n = tile_n * kTileN + q * 32 + lane;
+    const int m0 = tile_m * TN;
+    const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+    bool ok = true;
+
+    auto finish = [&](float* v, int c) {
+      // v[j] = accumulator for (n, m0 + c*16 + j), all splits summed, block scales applied
+      float wsc = p.alpha;
+      if constexpr (KIND == KIND_FP8) {
+        if (p.w_scale && n < p.N) wsc *= p.w_scale[n];
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int m = m0 + c * 16 + j;
+        float val = v[j] * wsc;
+        if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
+          if (p.a_scale && m < p.M) val *= p.a_scale[m];
+        }
+        if (p.epilogue == EPI_SWIGLU) {
+          const float other = __shfl_xor_sync(0xffffffffu, val, 1);
+          if (!(lane & 1) && m < p.M && n < p.N) {
+            const float r = mb::silu(val) * other;
+            reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] =
+                __float2bfloat16(r);
+          }
+        } else if (m < p.M && n < p.N) {
+          const size_t o = (size_t)m * p.ldo + n;
+          if (p.residual) val += __bfloat162float(p.residual[o]);
+          if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = val;
+          else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16(val);
+        }
+      }
+    };
+
+    if constexpr (KIND == KIND_FP8_BLOCK) {
+      float accr[TN];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) accr[j] = 0.f;
+      const int kgroups = (p.K + 127) / 128;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int buf = i & 1;
+        const uint32_t aph = (i >> 1) & 1;
+        ok = mb::mbar_wait(&acc_full[buf], aph, p.status, MB_ST_TIMEOUT_EPI);
+        if (!ok) break;
+        mb::tc_fence_after();
+        const int kb = kb0 + i;
+        const float wsc = p.w_scale[(size_t)tile_n * kgroups + kb];
+        const float* as = p.a_scale + (size_t)kb * p.a_ld + m0;
+#pragma unroll
+        for (int c = 0; c < TN / 16; ++c) {
+          float v[16];
+          mb::tmem_ld16(lane_addr + buf * TN + c * 16, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) accr[c * 16 + j] += v[j] * (wsc * as[c * 16 + j]);
+        }
+        mb::tc_fence_before();
+        mb::mbar_arrive(&acc_empty[buf]);
+      }
+      if (ok) {
+        if (p.splits == 1) {
+#pragma unroll
+          for (int c = 0; c < TN / 16; ++c) finish(&accr[c * 16], c);
+        } else {
+          const size_t tile_lin = (size_t)tile_m * gridDim.x + tile_n;
+          float* wsp = p.ws + (tile_lin * p.splits + split) * (size_t)(TN * kTileN);
+#pragma unroll
+          for (int j = 0; j < TN; ++j) wsp[j * kTileN + q * 32 + lane] = accr[j];
+        }
+      }
+    } else {
+      ok = mb::mbar_wait(&acc_full[0], 0, p.status, MB_ST_TIMEOUT_EPI);
+      if (ok) {
+        mb::tc_fence_after();
+        if (p.splits == 1) {
+#pragma unroll 1
+          for (int c = 0; c < TN / 16; ++c) {
+            float v[16];
+            mb::tmem_ld16(lane_addr + c * 16, v);
+            finish(v, c);
+          }
+        } else {
+          const size_t tile_lin = (size_t)tile_m * gridDim.x + tile_n;
+          float* wsp = p.ws + (tile_lin * p.splits + split) * (size_t)(TN * kTileN);
+#pragma unroll 1
+          for (int c = 0; c < TN / 16; ++c) {
+            float v[16];
+            mb::tmem_ld16(lane_addr + c * 16, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) wsp[(c * 16 + j) * kTileN + q * 32 + lane] = v[j];
+          }
+        }
+      }
+    }
+    if (p.splits > 1) {
+      // last-arriver reduction, summed in split order so the result does not
+      // depend on which CTA finishes last
+      const size_t tile_lin = (size_t)tile_m * gridDim.x + tile_n;
+      __threadfence();
+      epi_bar_sync();
+      if (threadIdx.x == 64) {
+        const uint32_t prev = atomicAdd(&p.cnt[tile_lin], 1u);
+        const int last = (prev == (uint32_t)p.splits - 1);
+        if (last) p.cnt[tile_lin] = 0;
+        is_last_s = last;
+      }
+      epi_bar_sync();
+      if (is_last_s && ok) {
+        __threadfence();
+        const float* base = p.ws + tile_lin * p.splits * (size_t)(TN * kTileN);
+#pragma unroll 1
+        for (int c = 0; c < TN / 16; ++c) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          for (int s = 0; s < p.splits; ++s) {
+            const float* wsp = base + (size_t)s * (TN * kTileN);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              v[j] += __ldcg(&wsp[(c * 16 + j) * kTileN + q * 32 + lane]);
+          }
+          finish(v, c);
+        }
+      }
+    }
+    mb::tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    mb::tc_fence_after();
+    mb::tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+template <int KIND, int TN>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, dim3 grid,
+           cudaStream_t stream) {
+  using C = Cfg<KIND, TN>;
+  static bool configured = false;
+  auto kern = gemm_kernel<KIND, TN>;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<grid, 192, C::kSmemBytes, stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}
+
+template <int KIND>
+int dispatch_tn(int tn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                dim3 grid, cudaStream_t stream) {
+  switch (tn) {
+    case 16: return launch<KIND, 16>(tmA, tmB, p, grid, stream);
+    case 32: return launch<KIND, 32>(tmA, tmB, p, grid, stream);
+    case 64: return launch<KIND, 64>(tmA, tmB, p, grid, stream);
+    case 128: return launch<KIND, 128>(tmA, tmB, p, grid, stream);
+    default: break;
+  }
+  if constexpr (KIND == KIND_BF16 || KIND == KIND_FP8) {
+    if (tn == 256) return launch<KIND, 256>(tmA, tmB, p, grid, stream);
+  }
+  return MB_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Bytes of split-K workspace needed for (M, N, K, kind) under the default
+// heuristics; the first `mb_gemm_counter_bytes` bytes of the workspace hold the
+// per-tile arrival counters and must be zero before the first launch.
+size_t mb_gemm_counter_bytes() { return 64 * 1024; }
+
+struct MbGemmArgs {
+  int kind, M, N, K, ldo, a_ld;
+  const void* W;
+  const void* X;
+  void* out;
+  const void* residual;
+  const float* w_scale;
+  const float* a_scale;
+  float alpha;
+  const void* sfa;
+  const void* sfb;
+  int sf_k64;
+  int epilogue, out_f32;
+  void* ws;
+  size_t ws_bytes;
+  uint32_t* status;
+  int force_tn, force_splits, sm_count;
+};
+
+int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
+  if (!a || !a->W || !a->X || !a->out || a->M <= 0 || a->N <= 0 || a->K <= 0) return MB_ERR_BAD_ARG;
+  const int kind = a->kind;
+  int kelems, elem_bits;
+  CUtensorMapDataType dt;
+  switch (kind) {
+    case KIND_BF16: kelems = 64; elem_bits = 16; dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+    case KIND_FP8:
+    case KIND_FP8_BLOCK: kelems = 128; elem_bits = 8; dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    case KIND_NVFP4: kelems = 256; elem_bits = 4; dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    default: return MB_ERR_UNSUPPORTED;
+  }
+  const size_t row_bytes = (size_t)a->K * elem_bits / 8;
+  if (row_bytes % 16) return MB_ERR_BAD_ARG;           // TMA global stride rule
+  if (kind == KIND_NVFP4 && (!a->sfa || !a->sfb)) return MB_ERR_BAD_ARG;
+  if (kind == KIND_FP8_BLOCK && (!a->w_scale || !a->a_scale)) return MB_ERR_BAD_ARG;
+  if (a->epilogue == EPI_SWIGLU && (a->out_f32 || a->residual)) return MB_ERR_BAD_ARG;
+  const int num_kb = (a->K + kelems - 1) / kelems;
+  if (kind == KIND_NVFP4 && a->sf_k64 < num_kb * 4) return MB_ERR_BAD_ARG;
+
+  int tn = a->force_tn;
+  const int tn_cap = (kind == KIND_BF16 || kind == KIND_FP8) ? 256 : 128;
+  if (tn <= 0) {
+    tn = 16;
+    while (tn < a->M && tn < tn_cap) tn <<= 1;
+  }
+  if (kind == KIND_FP8_BLOCK && tn > 64) tn = 64;       // register-resident promotion
+  const int tiles_n = (a->N + kTileN - 1) / kTileN;
+  const int tiles_m = (a->M + tn - 1) / tn;
+  if (kind == KIND_FP8_BLOCK && a->a_ld < tiles_m * tn) return MB_ERR_BAD_ARG;
+  // scale-factor tiles are 128 rows: several token tiles only line up at TN = 128
+  if (kind == KIND_NVFP4 && tiles_m > 1 && tn != 128) return MB_ERR_BAD_ARG;
+  const int tiles = tiles_n * tiles_m;
+  const int sms = a->sm_count > 0 ? a->sm_count : 148;
+  int splits = a->force_splits;
+  if (splits <= 0) {
+    splits = 1;
+    if (tiles < sms && a->ws) {
+      splits = sms / tiles;
+      const int max_by_k = num_kb / 4 > 0 ? num_kb / 4 : 1;
+      if (splits > max_by_k) splits = max_by_k;
+      if (splits < 1) splits = 1;
+    }
+  }
+  if (splits > num_kb) splits = num_kb;
+  int kb_per = (num_kb + splits - 1) / splits;
+  splits = (num_kb + kb_per - 1) / kb_per;              // no empty split
+
+  GemmParams p{};
+  p.M = a->M; p.N = a->N; p.K = a->K; p.ldo = a->ldo;
+  p.out = a->out;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
+  p.w_scale = a->w_scale; p.a_scale = a->a_scale; p.a_ld = a->a_ld;
+  p.alpha = a->alpha;
+  p.sfa = reinterpret_cast<const uint8_t*>(a->sfa);
+  p.sfb = reinterpret_cast<const uint8_t*>(a->sfb);
+  p.sf_k64 = a->sf_k64;
+  p.splits = splits; p.kb_per_split = kb_per; p.num_kb = num_kb;
+  p.epilogue = a->epilogue; p.out_f32 = a->out_f32;
+  p.status = a->status;
+  if (splits > 1) {
+    const size_t cbytes = mb_gemm_counter_bytes();
+    const size_t need = cbytes + (size_t)tiles * splits * tn * kTileN * sizeof(float);
+    if (!a->ws || a->ws_bytes < need || (size_t)tiles * 4 > cbytes) return MB_ERR_TOO_LARGE;
+    p.cnt = reinterpret_cast<uint32_t*>(a->ws);
+    p.ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a->ws) + cbytes);
+  }
+
+  CUtensorMap tmA, tmB;
+  const uint64_t inner = (uint64_t)row_bytes * 8 / (elem_bits == 4 ? 8 : elem_bits);
+  const uint32_t box_inner = (elem_bits == 16) ? 64 : 128;
+  int rc = mbh::encode_2d(&tmA, dt, a->W, inner, (uint64_t)a->N, row_bytes, box_inner, kTileN);
+  if (rc) return rc;
+  rc = mbh::encode_2d(&tmB, dt, a->X, inner, (uint64_t)a->M, row_bytes, box_inner, (uint32_t)tn);
+  if (rc) return rc;
+
+  dim3 grid(tiles_n, tiles_m, splits);
+  switch (kind) {
+    case KIND_BF16: return dispatch_tn<KIND_BF16>(tn, tmA, tmB, p, grid, stream);
+    case KIND_FP8: return dispatch_tn<KIND_FP8>(tn, tmA, tmB, p, grid, stream);
+    case KIND_NVFP4: return dispatch_tn<KIND_NVFP4>(tn, tmA, tmB, p, grid, stream);
+    case KIND_FP8_BLOCK:
+      switch (tn) {
+        case 16: return launch<KIND_FP8_BLOCK, 16>(tmA, tmB, p, grid, stream);
+        case 32: return launch<KIND_FP8_BLOCK, 32>(tmA, tmB, p, grid, stream);
+        case 64: return launch<KIND_FP8_BLOCK, 64>(tmA, tmB, p, grid, stream);
+        default: return MB_ERR_UNSUPPORTED;
+      }
+  }
+  return MB_ERR_UNSUPPORTED;
+}
+
+}  // extern "C"

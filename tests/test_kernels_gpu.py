@@ -1,0 +1,322 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 reference of the same op.
+The reference consumes the *same quantised operands*, so tolerances only cover accumulation
+order and the final bf16 rounding."""
+import math
+
+import pytest
+import torch
+
+from metrale_inference_alpha_b200 import ops
+from metrale_inference_alpha_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(got, want, rtol=2e-2, atol=2e-2):
+    got, want = got.float().cpu(), want.float().cpu()
+    err = (got - want).abs()
+    tol = atol + rtol * want.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{bad}/{got.numel()} off; max err {err.max():.4g} (ref max {want.abs().max():.4g})"
+
+
+def _mk(M, N, K, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g) * 0.05
+    return x, w
+
+
+def _run_linear(fmt, M, N, K, **kw):
+    x, w = _mk(M, N, K)
+    qw_cpu = ops.make_weight(w, fmt)
+    act_cpu = ops.encode_act_ref(x, ops.ACT_FOR_WEIGHT[fmt])
+    want = act_cpu.data @ qw_cpu.dequant().t()
+    qw = qw_cpu.to(DEV)
+    act = ops.quantize_act(x.to(DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[fmt])
+    # the oracle quantises the bf16-rounded activations exactly like the kernel did
+    act_cpu = ops.encode_act_ref(x.to(torch.bfloat16).float(), ops.ACT_FOR_WEIGHT[fmt])
+    want = act_cpu.data @ qw_cpu.dequant().t()
+    got = ops.linear(act, qw, out_f32=True, **kw)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    _close(got, want, rtol=1e-2, atol=1e-2 * want.abs().max().item())
+    return got, want
+
+
+@pytest.mark.parametrize("M", [1, 16, 77, 128, 300])
+def test_gemm_bf16(M):
+    _run_linear("bf16", M, 384, 512)
+
+
+def test_gemm_bf16_ragged_n_and_splitk():
+    _run_linear("bf16", 40, 200, 1024)                 # N not a multiple of 128
+    _run_linear("bf16", 40, 256, 2048, force_splits=4)
+    _run_linear("bf16", 130, 256, 2048, force_splits=3)
+
+
+@pytest.mark.parametrize("M", [1, 33, 128, 260])
+def test_gemm_fp8_row(M):
+    _run_linear("fp8_row", M, 256, 1024)
+
+
+@pytest.mark.parametrize("M", [1, 20, 64, 150])
+def test_gemm_fp8_block(M):
+    _run_linear("fp8_block", M, 384, 1024)
+    _run_linear("fp8_block", M, 256, 2048, force_splits=2)
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 64, 128, 200])
+def test_gemm_nvfp4(M):
+    _run_linear("nvfp4", M, 256, 1024)
+
+
+def test_gemm_nvfp4_splitk_and_tn():
+    _run_linear("nvfp4", 24, 384, 2048, force_splits=4)
+    _run_linear("nvfp4", 24, 128, 512, force_tn=128)
+    _run_linear("nvfp4", 128, 5120, 1024)
+
+
+def test_gemm_swiglu_and_residual():
+    M, I, K = 50, 192, 512
+    x, wg = _mk(M, I, K, 1)
+    _, wu = _mk(M, I, K, 2)
+    w = ops.interleave_gate_up(wg, wu)
+    for fmt in ("bf16", "nvfp4", "fp8_row"):
+        qw_cpu = ops.make_weight(w, fmt)
+        xb = x.to(torch.bfloat16)
+        a_cpu = ops.encode_act_ref(xb.float(), ops.ACT_FOR_WEIGHT[fmt])
+        want = ops.linear(a_cpu, qw_cpu, swiglu=True, out_f32=True)
+        a = ops.quantize_act(xb.to(DEV), ops.ACT_FOR_WEIGHT[fmt])
+        got = ops.linear(a, qw_cpu.to(DEV), swiglu=True)
+        _close(got, want, rtol=2e-2, atol=2e-2 * want.abs().max().item())
+    res = torch.randn(M, 2 * I).to(torch.bfloat16)
+    qw_cpu = ops.make_weight(w, "bf16")
+    a_cpu = ops.encode_act_ref(x.to(torch.bfloat16).float(), "bf16")
+    want = ops.linear(a_cpu, qw_cpu, residual=res, out_f32=True)
+    got = ops.linear(ops.quantize_act(x.to(torch.bfloat16).to(DEV), "bf16"), qw_cpu.to(DEV),
+                     residual=res.to(DEV))
+    _close(got, want, rtol=2e-2, atol=2e-2 * want.abs().max().item())
+    ops.check_status(DEV)
+
+
+def test_sf_repack_matches_reference_layout():
+    sf = torch.randint(0, 120, (300, 40), dtype=torch.uint8)
+    w = ops.QuantWeight("nvfp4", 300, 640, torch.zeros(300, 320, dtype=torch.uint8), sf, 1.0).to(DEV)
+    want = ref.sf_to_tiled(sf, w.sf_k64).flatten()
+    assert torch.equal(w.sf_tiled.cpu(), want)
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "fp8_row", "fp8_g128", "nvfp4"])
+def test_rowop_rmsnorm_quant(fmt):
+    M, K = 37, 1024
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    r = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(K, generator=g) * 0.1).to(torch.bfloat16)
+    a_ref, res_ref = ops.row_op(x, fmt, ops.IN_RMSNORM, residual=r, write_residual=True, w=w,
+                                plus_one=True, eps=1e-6, also_bf16=True)
+    a, res = ops.row_op(x.to(DEV), fmt, ops.IN_RMSNORM, residual=r.to(DEV), write_residual=True,
+                        w=w.to(DEV), plus_one=True, eps=1e-6, also_bf16=True)
+    assert torch.equal(res.cpu(), res_ref)
+    _close(a.bf16, a_ref.bf16, rtol=1e-2, atol=1e-2)
+    # decode the kernel's encoding and compare with the oracle's dequantised matrix
+    if fmt == "bf16":
+        deq = a.data.float().cpu()
+    elif fmt == "fp8_row":
+        deq = ref.from_e4m3(a.data.cpu()) * a.scale.cpu()[:, None]
+    elif fmt == "fp8_g128":
+        deq = ref.from_e4m3(a.data.cpu()) * a.scale.cpu()[:, :M].t().repeat_interleave(128, 1)[:, :K]
+    else:
+        sf = ref.tiled_to_sf(a.sf.cpu().view(-1, a.sf_k64, 512), M, K // 16)
+        deq = ref.dequantize_nvfp4(a.data.cpu(), sf, a.scale.cpu())
+    # quantisation bins can flip on 1-ulp differences of the normalised value: allow one step
+    step = a_ref.data.abs().amax(dim=1, keepdim=True) * (0.3 if fmt == "nvfp4" else 0.08)
+    assert ((deq - a_ref.data).abs() <= step + 1e-3).all()
+    assert ((deq - a_ref.data).abs() > 1e-3).float().mean() < 0.02
+
+
+def test_rowop_activations():
+    M, K = 19, 512
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(M, 2 * K, generator=g).to(torch.bfloat16)
+    for mode, kk in ((ops.IN_SILU_MUL, K), (ops.IN_RELU2, 2 * K)):
+        want, _ = ops.row_op(x, "bf16", mode, K=kk)
+        got, _ = ops.row_op(x.to(DEV), "bf16", mode, K=kk)
+        _close(got.data, want.data, 1e-2, 1e-2)
+    # sigmoid gate interleaved per head: [Q_h | G_h] with head_dim 64
+    H, D = 4, 64
+    attn = torch.randn(M, H * D, generator=g).to(torch.bfloat16)
+    qg = torch.randn(M, H * 2 * D + 100, generator=g).to(torch.bfloat16)
+    kw = dict(gate=qg, head_dim=D, gate_head_stride=2 * D, gate_head_off=D)
+    want, _ = ops.row_op(attn, "bf16", ops.IN_SIGMOID_GATE, **kw)
+    kw["gate"] = qg.to(DEV)
+    got, _ = ops.row_op(attn.to(DEV), "bf16", ops.IN_SIGMOID_GATE, **kw)
+    _close(got.data, want.data, 1e-2, 1e-2)
+    # gated rmsnorm over groups with an fp32 input
+    xf = torch.randn(M, K, generator=g)
+    z = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(128, generator=g).abs().to(torch.bfloat16).repeat(K // 128)
+    want, _ = ops.row_op(xf, "bf16", ops.IN_GATED_RMSNORM, gate=z, w=w, group=128)
+    got, _ = ops.row_op(xf.to(DEV), "bf16", ops.IN_GATED_RMSNORM, gate=z.to(DEV), w=w.to(DEV), group=128)
+    _close(got.data, want.data, 1e-2, 1e-2)
+
+
+def _cache(nb, bs, Hkv, D, fp8):
+    dt = torch.uint8 if fp8 else torch.bfloat16
+    return torch.zeros(nb, bs, Hkv, D, dtype=dt), torch.zeros(nb, bs, Hkv, D, dtype=dt)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("D,rot", [(128, 128), (64, 64), (256, 64)])
+def test_rope_kvwrite(fp8, D, rot):
+    M, Hq, Hkv, bs, nb = 23, 8, 2, 16, 12
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(M, (Hq + 2 * Hkv) * D, generator=g).to(torch.bfloat16)
+    pos = torch.randint(0, 500, (M,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(nb * bs, generator=g)[:M].to(torch.int64)
+    slots[3] = -1
+    qn = (torch.randn(D, generator=g) * 0.1).to(torch.bfloat16)
+    kn = (torch.randn(D, generator=g) * 0.1).to(torch.bfloat16)
+    cos, sin = ref.rope_tables(512, rot, 1e6)
+    ks, vs = torch.tensor([0.02]), torch.tensor([0.015])
+    kc, vc = _cache(nb, bs, Hkv, D, fp8)
+    q_ref = ops.qk_norm_rope_kvwrite(qkv, Hq=Hq, Hkv=Hkv, D=D, positions=pos, slots=slots, k_cache=kc,
+                                     v_cache=vc, q_norm_w=qn, k_norm_w=kn, plus_one=True, cos=cos,
+                                     sin=sin, k_scale=ks, v_scale=vs)
+    kcg, vcg = kc.clone().zero_().to(DEV), vc.clone().zero_().to(DEV)
+    q = ops.qk_norm_rope_kvwrite(qkv.to(DEV), Hq=Hq, Hkv=Hkv, D=D, positions=pos.to(DEV),
+                                 slots=slots.to(DEV), k_cache=kcg, v_cache=vcg, q_norm_w=qn.to(DEV),
+                                 k_norm_w=kn.to(DEV), plus_one=True, cos=cos.to(DEV), sin=sin.to(DEV),
+                                 k_scale=ks.to(DEV), v_scale=vs.to(DEV))
+    _close(q, q_ref, 2e-2, 2e-2)
+    if fp8:
+        _close(ref.from_e4m3(kcg.cpu()), ref.from_e4m3(kc), 0.13, 1.0)   # one e4m3 step
+        assert (kcg.cpu() != kc).float().mean() < 0.02
+        assert torch.equal(vcg.cpu(), vc)
+    else:
+        _close(kcg, kc, 2e-2, 2e-2)
+        assert torch.equal(vcg.cpu(), vc)
+    ops.check_status(DEV)
+
+
+def _attn_case(fp8, D, Hq, Hkv, q_lens, ctx_lens, window=0, force_mode=0, seed=6):
+    bs = 16
+    g = torch.Generator().manual_seed(seed)
+    S = len(q_lens)
+    max_blocks = (max(ctx_lens) + bs - 1) // bs
+    nb = S * max_blocks + 3
+    perm = torch.randperm(nb, generator=g)
+    bt = torch.full((S, max_blocks), -1, dtype=torch.int32)
+    used = 0
+    for s in range(S):
+        n = (ctx_lens[s] + bs - 1) // bs
+        bt[s, :n] = perm[used:used + n].to(torch.int32)
+        used += n
+    if fp8:
+        kc = torch.randint(0, 256, (nb, bs, Hkv, D), generator=g, dtype=torch.uint8)
+        vc = torch.randint(0, 256, (nb, bs, Hkv, D), generator=g, dtype=torch.uint8)
+        kc[(kc & 0x7F) == 0x7F] = 0x30   # no NaN codes
+        vc[(vc & 0x7F) == 0x7F] = 0x30
+        kc = (kc & 0xBF) | 0x20          # keep magnitudes moderate
+        vc = (vc & 0xBF) | 0x20
+        ks, vs = torch.tensor([0.05]), torch.tensor([0.03])
+    else:
+        kc = torch.randn(nb, bs, Hkv, D, generator=g).to(torch.bfloat16)
+        vc = torch.randn(nb, bs, Hkv, D, generator=g).to(torch.bfloat16)
+        ks = vs = None
+    T = sum(q_lens)
+    q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+    q_len = torch.tensor(q_lens, dtype=torch.int32)
+    q_start = torch.cumsum(q_len, 0, dtype=torch.int32) - q_len
+    ctx = torch.tensor(ctx_lens, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(D)
+    want = ref.paged_attention(q, kc, vc, bt.clamp(min=0), q_start, q_len, ctx, scale, ks, vs, window)
+    dv = lambda t: None if t is None else t.to(DEV)
+    got = ops.paged_attention(dv(q), dv(kc), dv(vc), dv(bt.clamp(min=0)), dv(q_start), dv(q_len), dv(ctx),
+                              max_q_len=max(q_lens), max_ctx=max(ctx_lens), scale=scale, k_scale=dv(ks),
+                              v_scale=dv(vs), window=window, force_mode=force_mode)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    _close(got, want, 2e-2, 2e-2 * max(1.0, want.abs().max().item()))
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_attention_decode_gqa5_d128(fp8):
+    _attn_case(fp8, 128, 40, 8, [1, 1, 1, 1], [1, 17, 640, 1153])
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_attention_verify_rows(fp8):
+    _attn_case(fp8, 128, 40, 8, [5, 5, 3], [133, 700, 64])       # 25 rows: two m16 tiles
+    _attn_case(fp8, 64, 4, 2, [1, 4, 2], [33, 100, 2])
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_attention_decode_d256(fp8):
+    _attn_case(fp8, 256, 16, 2, [1, 1], [90, 600])
+    _attn_case(fp8, 256, 16, 2, [4, 1], [90, 600])                # falls back to row-wise sequences
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_attention_prefill(fp8, D):
+    Hq, Hkv = (8, 2) if D != 64 else (4, 2)
+    _attn_case(fp8, D, Hq, Hkv, [128, 70, 200], [128, 170, 200])   # fresh, chunked-after-cache, fresh
+
+
+def test_attention_sliding_window():
+    _attn_case(False, 128, 8, 2, [1, 1], [300, 900], window=128)
+    _attn_case(False, 128, 8, 2, [100], [400], window=64)
+
+
+def test_argmax_and_logprob():
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(9, 151936, generator=g).to(torch.bfloat16)
+    x[2, 5] = x[2, 77] = 50.0                                       # tie -> lower index
+    ids_ref, lp_ref = ops.argmax(x, logprob=True, mask_ids=(3, -1))
+    ids, lp = ops.argmax(x.to(DEV), logprob=True, mask_ids=(3, -1))
+    assert torch.equal(ids.cpu(), ids_ref)
+    _close(lp, lp_ref, 1e-3, 1e-3)
+    xf = torch.randn(4, 4096, generator=g)
+    assert torch.equal(ops.argmax(xf.to(DEV)).cpu(), ops.argmax(xf))
+
+
+def test_sample_matches_reference_draws():
+    g = torch.Generator().manual_seed(8)
+    M, V = 12, 4096
+    x = torch.randn(M, V, generator=g) * 3
+    temp = torch.tensor([0.0, 1.0, 0.7, 1.3] * 3)
+    top_k = torch.tensor([0, 0, 50, 5] * 3, dtype=torch.int32)
+    top_p = torch.tensor([1.0, 0.9, 1.0, 0.8] * 3)
+    min_p = torch.tensor([0.0, 0.0, 0.05, 0.0] * 3)
+    seed = torch.arange(M, dtype=torch.int64) + 42
+    step = torch.arange(M, dtype=torch.int64)
+    ids_ref, lp_ref = ops.sample(x, temp, top_k, top_p, min_p, seed, step)
+    d = lambda t: t.to(DEV)
+    ids, lp = ops.sample(d(x), d(temp), d(top_k), d(top_p), d(min_p), d(seed), d(step))
+    ids = ids.cpu()
+    # every draw must land inside the reference keep-set; exact equality except when the
+    # uniform draw falls within float noise of a cumulative boundary
+    for r in range(M):
+        if temp[r] <= 0:
+            assert ids[r] == ids_ref[r]
+        else:
+            keep = ops.sample_keep_mask(x[r], float(temp[r]), int(top_k[r]), float(top_p[r]), float(min_p[r]))
+            assert keep[ids[r]]
+    assert (ids == ids_ref).float().mean() >= 0.75
+    same = ids == ids_ref
+    _close(lp.cpu()[same], lp_ref[same], 1e-3, 1e-3)
+
+
+def test_embed_and_bounds_status():
+    table = torch.randn(100, 64).to(torch.bfloat16).to(DEV)
+    ids = torch.tensor([0, 99, 5], dtype=torch.int32, device=DEV)
+    assert torch.equal(ops.embed(ids, table), table[ids.long()])
+    bad = torch.tensor([0, 100], dtype=torch.int32, device=DEV)
+    out = ops.embed(bad, table)
+    assert out[1].abs().sum() == 0
+    with pytest.raises(Exception):
+        ops.check_status(DEV)
+    assert ops.check_status(DEV) == 0
