@@ -209,8 +209,8 @@ def kv_cache_write(k_cache, v_cache, k, v, slots, k_scale=None, v_scale=None):
     ok = slots >= 0
     idx = slots[ok].long()
     if k_cache.dtype == torch.uint8:
-        kf[idx] = to_e4m3(k.float()[ok] / k_scale)
-        vf[idx] = to_e4m3(v.float()[ok] / v_scale)
+        kf[idx] = to_e4m3(k.float()[ok] * (1.0 / k_scale))
+        vf[idx] = to_e4m3(v.float()[ok] * (1.0 / v_scale))
     else:
         kf[idx] = k[ok].to(k_cache.dtype)
         vf[idx] = v[ok].to(v_cache.dtype)

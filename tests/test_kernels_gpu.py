@@ -194,7 +194,8 @@ def test_rope_kvwrite(fp8, D, rot):
     if fp8:
         _close(ref.from_e4m3(kcg.cpu()), ref.from_e4m3(kc), 0.13, 1.0)   # one e4m3 step
         assert (kcg.cpu() != kc).float().mean() < 0.02
-        assert torch.equal(vcg.cpu(), vc)
+        _close(ref.from_e4m3(vcg.cpu()), ref.from_e4m3(vc), 0.13, 1.0)
+        assert (vcg.cpu() != vc).float().mean() < 0.02
     else:
         _close(kcg, kc, 2e-2, 2e-2)
         assert torch.equal(vcg.cpu(), vc)
