@@ -1,0 +1,277 @@
+#!/usr/bin/env python
+"""Headline benchmark: aggregate decode tokens/s of the dense ~27B NVFP4 model (fp8 KV) at
+concurrency C (default 128, the top rung of the reference's ISL128/OSL1024 ladder) on N GPUs
+of one node (tensor parallel over NVLink).
+
+    python bench.py --gpus 1 --steps 64 --warmup 8
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 64 --warmup 8
+
+Workload (reference ladder semantics): C requests arrive at once, prompts are 128 uniform
+random token ids (seed 42), temperature 0, context 2048, batch cap 128, OSL 1024. Weights are
+random N(0, 0.02) quantised to NVFP4 (e2m1 + per-16 e4m3 scales + fp32 global scale), bf16
+embeddings / lm_head; there is no network for a real checkpoint.
+
+Two numbers are measured on the same sequences around the middle of the 1024-token
+generation (context ~640, reached by untimed fast-forward decode steps):
+  value  K decode steps replayed as CUDA graphs from device-resident metadata, timed with
+         CUDA events (kernel-only view).
+  e2e    K ticks of the public engine API (`LLMEngine.step()`): scheduler planning, metadata
+         staged in pinned host memory and copied host->device every step, graph replay,
+         on-device token selection, device->host read of the new token ids.
+Both are the max over ranks. One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+BASELINE_TOKS = {1: 23.59, 2: 41.02, 4: 74.21, 8: 125.95, 16: 203.36, 32: 291.01, 64: 386.63, 128: 478.11}
+SMI_FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+def reference_arm(args) -> int:
+    """The reference is a Rust workspace (no setup.py / pyproject, needs cargo + crates.io +
+    CUDA 13.0): `pip install --no-index ... /root/reference` reports "not installable"."""
+    line = {"impl": "reference",
+            "unavailable": "reference is a Cargo workspace (Rust 1.93.1 + CUDA 13.0 + ~400 crates); "
+                           "pip reports 'neither setup.py nor pyproject.toml found'; no cargo/rustc offline"}
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(line), flush=True)
+    return 0
+
+
+class ClockSampler:
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.path = f"/tmp/bench_clocks_{os.getpid()}.csv"
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={SMI_FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=self.f,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1])); mx.append(float(p[2])); power.append(float(p[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, p[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                       samples=len(sm), power_w_max=max(power))
+        return out
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--concurrency", type=int, default=128)
+    ap.add_argument("--model", default="dense-27b-nvfp4")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the line invalid)")
+    ap.add_argument("--isl", type=int, default=128)
+    ap.add_argument("--osl", type=int, default=1024)
+    ap.add_argument("--no-fast-forward", action="store_true")
+    ap.add_argument("--no-fused", action="store_true", help="NCCL(+library-free GEMM) baseline collectives")
+    ap.add_argument("--ladder", action="store_true", help="also print one line per concurrency rung")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    tp = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+        from metrale_inference_alpha_b200.parallel.tp import NcclTpContext
+        tp = NcclTpContext(rank, world, dev, fused=not args.no_fused)
+
+    from metrale_inference_alpha_b200 import ops
+    from metrale_inference_alpha_b200.config.model_config import preset
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+
+    cfg = preset(args.model)
+    if args.layers:
+        cfg = cfg.scaled(num_layers=args.layers, layer_types=cfg.layer_types[:args.layers],
+                         ffn_types=cfg.ffn_types[:args.layers])
+    ctx_len = 2048
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def run_rung(C: int, steps: int, warmup: int, eng=None):
+        if eng is None:
+            eng = LLMEngine(EngineArgs(model=cfg, device=dev, max_num_seqs=128, max_model_len=ctx_len,
+                                       max_prefill_tokens=8192, enable_prefix_caching=True,
+                                       gpu_memory_utilization=0.85, tp_size=world, seed=0), tp=tp)
+        g = torch.Generator().manual_seed(42)
+        prompts = [torch.randint(0, cfg.vocab_size, (args.isl,), generator=g).tolist() for _ in range(C)]
+        sp = SamplingParams(max_tokens=args.osl, temperature=0.0, ignore_eos=True)
+        barrier()
+        t_arrive = time.perf_counter()
+        for p in prompts:
+            eng.add_request(p, sp)
+        ttfts = {}
+        while eng.scheduler.waiting or eng.scheduler.prefilling:
+            for o in eng.step():
+                if o.ttft_ms is not None and o.request_id not in ttfts:
+                    ttfts[o.request_id] = (time.perf_counter() - t_arrive) * 1e3
+        torch.cuda.synchronize()
+        # fast-forward (untimed) so the timed window sits around the middle of the generation
+        target_ctx = args.isl + args.osl // 2
+        ff = 0 if args.no_fast_forward else max(0, target_ctx - steps - warmup - args.isl - 1)
+        ff = min(ff, args.osl - 2 * steps - warmup - 8)
+        for _ in range(max(0, ff)):
+            eng.step()
+        for _ in range(warmup):
+            eng.step()
+        sampler = ClockSampler(local)
+        # ---- e2e: public API ticks, host->device metadata + device->host token ids each step
+        barrier()
+        h0, d0 = eng.runner.h2d_bytes, eng.runner.d2h_bytes
+        sampler.start()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        tokens_before = eng.scheduler.stats["decode_tokens"]
+        e0.record()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            eng.step()
+        e1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        barrier()
+        e2e_s = max_over_ranks(max(wall, e0.elapsed_time(e1) / 1e3))
+        e2e_tokens = eng.scheduler.stats["decode_tokens"] - tokens_before
+        h2d = (eng.runner.h2d_bytes - h0) / steps
+        d2h = (eng.runner.d2h_bytes - d0) / steps
+        # ---- kernel-only: replay the decode graph of this rung from device-resident metadata
+        plan = eng.scheduler.plan()
+        rung = eng.runner._rung(len(plan.items))
+        key = (rung, True, False)
+        eng.runner._stage(plan, pad_seqs=rung)
+        graph = eng.runner.graphs[key][0]
+        launches_per_step = eng.runner.graphs[key][1]
+        for _ in range(3):
+            graph.replay()
+        barrier()
+        k0 = torch.cuda.Event(enable_timing=True); k1 = torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for _ in range(steps):
+            graph.replay()
+        k1.record()
+        torch.cuda.synchronize()
+        barrier()
+        clocks = sampler.stop()
+        dev_s = max_over_ranks(k0.elapsed_time(k1) / 1e3)
+        # hand the planned step back to the scheduler so its bookkeeping stays consistent
+        res = eng.runner.execute(plan)
+        eng.scheduler.apply(plan, res)
+        ctx_mid = int(sum(len(s.tokens) for s in eng.scheduler.running) / max(1, len(eng.scheduler.running)))
+        for s in list(eng.scheduler.running):
+            eng.abort(s.req.request_id)
+        tt = sorted(ttfts.values())
+        return dict(C=C, tok_s=C * steps / dev_s, ms_per_step=dev_s / steps * 1e3,
+                    e2e_tok_s=e2e_tokens / e2e_s, e2e_ms_per_step=e2e_s / steps * 1e3, h2d=h2d, d2h=d2h,
+                    launches=launches_per_step * steps, clocks=clocks, ctx=ctx_mid, ff=ff,
+                    ttft_p50_ms=tt[len(tt) // 2] if tt else None, eng=eng)
+
+    C = args.concurrency
+    r = run_rung(C, args.steps, args.warmup)
+    eng = r.pop("eng")
+    line = {
+        "metric": "aggregate decode tok/s at C=%d (ISL128/OSL1024), dense 27B NVFP4, fp8 KV" % C,
+        "value": round(r["tok_s"], 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": round(r["tok_s"] / BASELINE_TOKS.get(C, BASELINE_TOKS[128]), 3),
+        "dtype": "nvfp4 weights x nvfp4 activations (fp32 accumulate), bf16 lm_head, fp8 KV",
+        "data": "synthetic: random-init N(0,0.02) weights in NVFP4 checkpoint layout, uniform-random prompts (seed 42)",
+        "config": {"model": cfg.name, "layers": cfg.num_layers, "hidden": cfg.hidden_size,
+                   "global_batch": C, "seq_len": args.isl, "osl": args.osl, "context": ctx_len,
+                   "mean_ctx_in_timed_window": r["ctx"], "fast_forward_steps": r["ff"],
+                   "parallelism": f"tp{world}", "l2": "inputs larger than L2 (weights %.1f GB + KV per step)" % (eng.weights.nbytes() / 1e9),
+                   "fused_collectives": bool(tp is not None and getattr(tp, "fused", False)),
+                   "speculative": "off (MTP gate: random-init drafts never accepted)"},
+        "e2e": {"value": round(r["e2e_tok_s"], 2), "unit": "tokens/s", "ms_per_step": round(r["e2e_ms_per_step"], 4),
+                "h2d_bytes_per_step": int(r["h2d"]), "d2h_bytes_per_step": int(r["d2h"])},
+        "gpu_launches": int(r["launches"]),
+        "clocks": r["clocks"],
+        "ttft_p50_ms": None if r["ttft_p50_ms"] is None else round(r["ttft_p50_ms"], 1),
+        "impl": "ours",
+    }
+    if args.layers:
+        line["invalid"] = "debug run with fewer layers"
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if args.ladder:
+        for c in (1, 2, 4, 8, 16, 32, 64):
+            rr = run_rung(c, max(16, args.steps // 2), args.warmup, eng)
+            rr.pop("eng")
+            if rank == 0:
+                print(json.dumps({"ladder_rung": c, "tok_s": round(rr["tok_s"], 2),
+                                  "e2e_tok_s": round(rr["e2e_tok_s"], 2), "ms_per_step": round(rr["ms_per_step"], 4),
+                                  "ttft_p50_ms": rr["ttft_p50_ms"], "vs_baseline": round(rr["tok_s"] / BASELINE_TOKS[c], 2)}),
+                      flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

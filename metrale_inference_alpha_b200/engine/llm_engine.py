@@ -1,0 +1,203 @@
+"""The public engine API: build a model from a preset / checkpoint, add requests, step.
+
+``LLMEngine.step()`` is one scheduler tick: plan -> execute on the device -> (draft) -> apply.
+``generate()`` is the offline convenience loop over ``step()``. The HTTP server drives the
+same object from its scheduler thread. Role of the reference's boot phases 1-9
+(``crates/server/src/main_modules/serve_load``) and of ``metrale_scheduler::run``.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, List, Optional, Sequence as Seq, Union
+
+import torch
+
+from ..cache import RadixTree
+from ..config.model_config import ModelConfig, preset as cfg_preset
+from ..models.decoder import TpContext
+from ..sampling.params import SamplingParams
+from ..scheduler.core import SchedulerCore
+from ..scheduler.policy import SchedulerConfig
+from ..scheduler.types import FatalDeviceError, Request, RequestOutput, StepPlan
+from ..speculative import KLadder, MtpGate, NgramProposer, SpecStats
+from ..utils.fault import FaultLatch
+from ..weights.loader import load_weights
+from ..weights.source import SafetensorsSource, TensorSource
+from .runner import ModelRunner, plan_kv_blocks
+
+
+@dataclass
+class EngineArgs:
+    model: Union[str, ModelConfig] = "tiny-dense"     # preset name, checkpoint dir, or a config
+    device: str = "cpu"
+    seed: int = 0
+    max_num_seqs: int = 128
+    max_model_len: int = 2048
+    max_prefill_tokens: int = 8192
+    block_size: int = 16
+    gpu_memory_utilization: float = 0.90
+    num_kv_blocks: Optional[int] = None
+    enable_prefix_caching: bool = True
+    scheduler: str = "fifo"
+    tbt_deadline_ms: float = 100.0
+    use_cuda_graphs: bool = True
+    speculative: str = "none"                          # none | mtp | ngram
+    num_drafts: int = 3
+    mtp_gate: bool = True
+    kv_poison: bool = False
+    tp_size: int = 1
+    ep_size: int = 1
+    request_timeout_s: float = 300.0
+    eos_token_id: Optional[int] = None
+    fused_collectives: bool = True
+
+
+class LLMEngine:
+    def __init__(self, args: EngineArgs, tp: Optional[TpContext] = None, source: Optional[TensorSource] = None):
+        self.args = args
+        self.device = torch.device(args.device)
+        self.tp = tp or TpContext()
+        cfg = args.model
+        if isinstance(cfg, str):
+            import os
+            if os.path.isdir(cfg):
+                from ..weights.checkpoint import open_checkpoint
+                cfg, source = open_checkpoint(cfg, device=args.device)
+            else:
+                cfg = cfg_preset(cfg)
+        self.cfg: ModelConfig = cfg
+        self.fault = FaultLatch()
+        t0 = time.time()
+        self.weights = load_weights(cfg, source, device=args.device, tp_rank=self.tp.rank,
+                                    tp_size=self.tp.size if args.ep_size == 1 or args.tp_size > 1 else 1,
+                                    ep_rank=getattr(self.tp, "ep_rank", 0), ep_size=args.ep_size, seed=args.seed)
+        self.load_seconds = time.time() - t0
+        self.sched_cfg = SchedulerConfig(
+            max_num_seqs=args.max_num_seqs, max_prefill_tokens=args.max_prefill_tokens,
+            max_model_len=min(args.max_model_len, cfg.max_position), block_size=args.block_size,
+            policy=args.scheduler, tbt_deadline_ms=args.tbt_deadline_ms,
+            enable_prefix_caching=args.enable_prefix_caching, request_timeout_s=args.request_timeout_s)
+        blocks = args.num_kv_blocks or plan_kv_blocks(cfg, self.weights, args.device, args.block_size,
+                                                      args.gpu_memory_utilization)
+        # never more than every sequence at full length needs (plus headroom for the prefix cache)
+        cap = (self.sched_cfg.max_model_len // args.block_size + 1) * args.max_num_seqs * 2 + 64
+        blocks = min(blocks, cap)
+        self.runner = ModelRunner(cfg, self.weights, args.device, blocks, self.sched_cfg, self.tp,
+                                  use_graphs=args.use_cuda_graphs, kv_poison=args.kv_poison)
+        needs_snap = self.runner.pool is not None
+        self.prefix = None
+        if args.enable_prefix_caching:
+            self.prefix = RadixTree(self.runner.kv.allocator, args.block_size, needs_snapshot=needs_snap,
+                                    on_snapshot_evict=(self.runner.pool.release_snapshot if needs_snap else None))
+        self.scheduler = SchedulerCore(self.sched_cfg, self.runner.kv.allocator, self.prefix, self.runner.pool)
+        self._ids = itertools.count(1)
+        self.spec_mode = args.speculative
+        if self.spec_mode == "mtp" and self.weights.mtp is None:
+            self.spec_mode = "none"
+        self.ladder = KLadder(max_k=args.num_drafts)
+        self.gate = MtpGate(enabled=(self.spec_mode != "none" and args.mtp_gate))
+        self.ngram = NgramProposer()
+        self.spec_stats = SpecStats()
+        self.step_count = 0
+        self.tokenizer = None
+        self.stop_strings_active = False
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_ids: Seq[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, adapter: Optional[str] = None) -> str:
+        if self.fault.is_set():
+            raise FatalDeviceError(self.fault.reason())
+        rid = request_id or f"req-{next(self._ids)}"
+        req = Request(rid, list(prompt_ids), params or SamplingParams(), adapter=adapter,
+                      eos_token_id=self.args.eos_token_id)
+        self.scheduler.add_request(req)
+        return rid
+
+    def abort(self, request_id: str) -> bool:
+        return self.scheduler.abort(request_id)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ one tick
+    def step(self) -> List[RequestOutput]:
+        if self.fault.is_set():
+            raise FatalDeviceError(self.fault.reason())
+        sch = self.scheduler
+        plan = sch.plan()
+        if plan is None:
+            return sch.drain_finished()
+        speculate = False
+        if self.spec_mode != "none" and plan.kind in ("decode", "verify"):
+            speculate = self.gate.next_step() == MtpGate.MEASURE_VERIFY or not self.gate.enabled
+            if not speculate and plan.kind == "verify":
+                # the gate turned speculation off: drop pending drafts
+                for it in plan.items:
+                    it.tokens, it.verify = it.tokens[:1], 0
+                plan = StepPlan("decode", plan.items)
+        t0 = time.perf_counter()
+        try:
+            result = self.runner.execute(plan)
+        except FatalDeviceError as e:
+            self.fault.set(str(e))
+            raise
+        except RuntimeError as e:
+            if "CUDA" in str(e) or "device status" in str(e):
+                self.fault.set(str(e))
+                raise FatalDeviceError(str(e)) from e
+            raise
+        before = {it.seq.seq_id: len(it.seq.tokens) for it in plan.items}
+        drafts = None
+        outs = sch.apply(plan, result, None)
+        if speculate:
+            k = self.ladder.drafts_for(len(plan.items))
+            if k > 0:
+                accepted = [len(it.seq.tokens) - before[it.seq.seq_id] for it in plan.items]
+                if self.spec_mode == "mtp":
+                    drafts = self.runner.propose(plan, result, accepted, k)
+                else:
+                    drafts = [self.ngram.propose(it.seq.tokens, k) if not it.seq.is_finished() else []
+                              for it in plan.items]
+                for it, d in zip(plan.items, drafts):
+                    if not it.seq.is_finished():
+                        room = it.seq.req.params.max_tokens - it.seq.num_output - 1
+                        it.seq.drafts = list(d[:max(0, room)])
+        dt = time.perf_counter() - t0
+        if plan.kind in ("decode", "verify"):
+            emitted = sum(len(it.seq.tokens) - before[it.seq.seq_id] for it in plan.items)
+            self.gate.record(emitted, dt)
+            self.spec_stats.steps += 1
+            self.spec_stats.emitted += emitted
+            self.spec_stats.drafted += sum(it.verify for it in plan.items)
+            self.spec_stats.accepted += sum(getattr(it.seq, "last_accept", 0) for it in plan.items)
+        self.step_count += 1
+        return outs
+
+    # ------------------------------------------------------------------ offline loop
+    def generate(self, prompts: Iterable[Seq[int]], params: Union[SamplingParams, Seq[SamplingParams], None] = None
+                 ) -> List[RequestOutput]:
+        prompts = list(prompts)
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        done: Dict[str, RequestOutput] = {}
+        while len(done) < len(ids):
+            outs = self.step()
+            for o in outs:
+                if o.finished:
+                    done[o.request_id] = o
+            if not outs and not self.has_work():
+                break
+        return [done[i] for i in ids if i in done]
+
+    def stats(self) -> dict:
+        s = self.scheduler.snapshot()
+        s.update({"steps": self.step_count, "graph_replays": self.runner.graph_replays,
+                  "h2d_bytes": self.runner.h2d_bytes, "d2h_bytes": self.runner.d2h_bytes,
+                  "spec_accept_len": self.spec_stats.accept_len, "gate_mode": self.gate.mode,
+                  "kv_blocks": self.runner.kv.num_blocks, "weights_bytes": self.weights.nbytes()})
+        if self.prefix:
+            s["prefix_cache"] = self.prefix.stats()
+        return s

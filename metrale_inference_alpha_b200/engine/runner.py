@@ -1,0 +1,356 @@
+"""Executes step plans on one device: stages the step's metadata through pinned host memory
+into fixed device buffers, runs the decoder (a CUDA graph per batch rung for decode, eager for
+prefill / verify), selects tokens on the device and reads back 4 bytes per sampled row.
+
+Role of the reference's ``TransformerModel`` forward entry points
+(``crates/model-engine/src/model/trait_impl/decode_a2.rs``: rung padding, fixed-address
+metadata, graph cache; ``prefill_b.rs``: chunked prefill; ``verify_e.rs``: batched verify;
+``meta_argmax.rs``: device argmax + 4*n-byte readback) and of ``factory/build.rs`` (KV budget).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache import KvCacheConfig, PagedKvCache, StatePool
+from ..config.model_config import ModelConfig
+from ..models.decoder import Decoder, LayerCaches, TpContext
+from ..scheduler.policy import SchedulerConfig
+from ..scheduler.types import StepPlan, StepResult
+from ..weights.loader import ModelW
+from .batch import ForwardBatch
+
+
+def state_shapes(cfg: ModelConfig, w: ModelW):
+    """(conv window, ssm matrix) shapes of every recurrent layer, from the loaded (sharded) weights."""
+    out = []
+    for lw in w.layers:
+        if lw.kind == "gdn":
+            m = lw.mixer
+            C = 2 * m.k_heads * cfg.gdn_k_dim + m.v_heads * cfg.gdn_v_dim
+            out.append(((C, cfg.conv_kernel - 1), (m.v_heads, cfg.gdn_k_dim, cfg.gdn_v_dim)))
+        elif lw.kind == "mamba2":
+            m = lw.mixer
+            C = m.heads * cfg.mamba_head_dim + 2 * m.groups * cfg.mamba_state
+            out.append(((C, cfg.conv_kernel - 1), (m.heads, cfg.mamba_head_dim, cfg.mamba_state)))
+    return out
+
+
+def kv_config(cfg: ModelConfig, w: ModelW, block_size: int, mtp: bool = False) -> KvCacheConfig:
+    if cfg.arch == "deepseek_mla":
+        return KvCacheConfig(1 if mtp else len(cfg.attention_layers()), 1, cfg.kv_lora_rank + cfg.qk_rope_dim,
+                             block_size, cfg.kv_dtype if cfg.kv_dtype == "bf16" else "bf16", has_v=False)
+    kvh = cfg.num_kv_heads
+    for lw in ([w.mtp.layer] if (mtp and w.mtp) else w.layers):
+        if lw.kind == "attention":
+            kvh = lw.mixer.kv_heads
+            break
+    return KvCacheConfig(1 if mtp else max(1, len(cfg.attention_layers())), kvh, cfg.head_dim, block_size,
+                         cfg.kv_dtype)
+
+
+class _Stager:
+    """One pinned int32 buffer + one device int32 buffer; a step's integer metadata crosses
+    PCIe in a single async copy of just the bytes in use. The field layout is a function of
+    (token capacity, sequence capacity), so a CUDA-graph rung always sees the same addresses."""
+
+    FIELDS = ("slots", "tokens", "pos", "q_start", "q_len", "ctx", "state", "lrows", "bt")
+
+    def __init__(self, max_tokens: int, max_seqs: int, max_blocks: int, device):
+        self.max_tokens, self.max_seqs, self.max_blocks = max_tokens, max_seqs, max_blocks
+        self.device = torch.device(device)
+        self.total = self._layout(max_tokens, max_seqs)[1]
+        pin = self.device.type == "cuda"
+        self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=pin)
+        self.np = self.host.numpy()
+        self.dev = torch.zeros(self.total, dtype=torch.int32, device=self.device)
+        self.bytes_per_copy = 0
+        self.off = {}
+        self.used = 0
+
+    def _layout(self, T: int, S: int):
+        off, o = {}, 0
+        # slot_mapping and logit rows are int64: they come first / stay 8-byte aligned
+        for name, n in (("slots", 2 * T), ("lrows", 2 * T), ("tokens", T), ("pos", T), ("q_start", S),
+                        ("q_len", S), ("ctx", S), ("state", S), ("bt", S * self.max_blocks)):
+            off[name] = (o, n)
+            o += n + (n & 1)
+        return off, o
+
+    def begin(self, T_cap: int, S_cap: int) -> None:
+        assert T_cap <= self.max_tokens and S_cap <= self.max_seqs, (T_cap, S_cap)
+        self.off, self.used = self._layout(T_cap, S_cap)
+        self.S_cap = S_cap
+
+    def view(self, buf, name, n=None):
+        o, cap = self.off[name]
+        return buf[o:o + (cap if n is None else n)]
+
+    def upload(self) -> None:
+        self.dev[:self.used].copy_(self.host[:self.used], non_blocking=True)
+        self.bytes_per_copy = self.used * 4
+
+
+class ModelRunner:
+    def __init__(self, cfg: ModelConfig, weights: ModelW, device="cpu", num_blocks: int = 256,
+                 sched: Optional[SchedulerConfig] = None, tp: Optional[TpContext] = None,
+                 use_graphs: bool = True, max_state_slots: Optional[int] = None, num_snapshots: int = 16,
+                 mtp_drafts: int = 0, kv_poison: bool = False):
+        self.cfg, self.w, self.device = cfg, weights, torch.device(device)
+        self.sched = sched or SchedulerConfig()
+        self.tp = tp or TpContext()
+        bs = self.sched.block_size
+        self.block_size = bs
+        self.kv = PagedKvCache(kv_config(cfg, weights, bs), num_blocks, device, poison=kv_poison)
+        self.mtp_kv = None
+        if weights.mtp is not None:
+            self.mtp_kv = PagedKvCache(kv_config(cfg, weights, bs, mtp=True), num_blocks, device)
+        shapes = state_shapes(cfg, weights)
+        self.pool = None
+        if shapes:
+            slots = (max_state_slots or self.sched.max_num_seqs) + 1
+            self.pool = StatePool(shapes, slots, num_snapshots, device)
+        self.caches = LayerCaches(cfg, kv=self.kv, state=self.pool, mtp_kv=self.mtp_kv)
+        self.decoder = Decoder(cfg, weights, self.tp, device)
+        self.max_blocks = (self.sched.max_model_len + bs - 1) // bs
+        self.max_seqs = max(self.sched.batch_rungs[-1], self.sched.max_num_seqs)
+        max_tokens = max(self.sched.max_prefill_tokens + self.max_seqs, self.max_seqs * 8)
+        self.stage = _Stager(max_tokens, self.max_seqs, self.max_blocks, device)
+        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self.graphs: Dict[Tuple, object] = {}
+        self.mtp_drafts = mtp_drafts if weights.mtp is not None else 0
+        S = self.max_seqs
+        dev = self.device
+        # sampling parameters, fixed addresses
+        self.s_temp = torch.zeros(S, dtype=torch.float32, device=dev)
+        self.s_topk = torch.zeros(S, dtype=torch.int32, device=dev)
+        self.s_topp = torch.ones(S, dtype=torch.float32, device=dev)
+        self.s_minp = torch.zeros(S, dtype=torch.float32, device=dev)
+        self.s_seed = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.s_step = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.out_ids = torch.zeros(max_tokens, dtype=torch.int32, device=dev)
+        self.out_lp = torch.zeros(max_tokens, dtype=torch.float32, device=dev)
+        pin = dev.type == "cuda"
+        self.host_ids = torch.zeros(max_tokens, dtype=torch.int32, pin_memory=pin)
+        self.host_lp = torch.zeros(max_tokens, dtype=torch.float32, pin_memory=pin)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.last_hidden = None
+        self.graph_replays = 0
+        self.logit_processor = None    # fn(seq, row_logits fp32 [V]) -> row_logits, host-logits path
+
+    # ------------------------------------------------------------------ batch staging
+    def _stage(self, plan: StepPlan, pad_seqs: int = 0, logits_all_verify: bool = True) -> ForwardBatch:
+        st, bs = self.stage, self.block_size
+        n_rows = sum(len(i.tokens) for i in plan.items)
+        n_seqs = max(len(plan.items), pad_seqs)
+        pad_rows = max(0, pad_seqs - len(plan.items))
+        if pad_seqs:
+            st.begin(n_rows + pad_rows, n_seqs)               # graph rung: exact, fixed layout
+        else:
+            st.begin(min(st.max_tokens, (n_rows + 63) // 64 * 64), min(st.max_seqs, (n_seqs + 7) // 8 * 8))
+        npv = lambda name: st.view(st.np, name)
+        tokens, pos, qs, ql, ctx, state, bt = (npv(n) for n in ("tokens", "pos", "q_start", "q_len", "ctx", "state", "bt"))
+        slots = npv("slots").view(np.int64)
+        lrows = npv("lrows").view(np.int64)
+        bt2 = bt.reshape(st.S_cap, st.max_blocks)
+        row = 0
+        nl = 0
+        max_q = 1
+        max_ctx = 1
+        for s, it in enumerate(plan.items):
+            n = len(it.tokens)
+            p0 = it.start_pos
+            tokens[row:row + n] = it.tokens
+            pos[row:row + n] = np.arange(p0, p0 + n, dtype=np.int32)
+            blocks = it.seq.blocks
+            nb = len(blocks)
+            bt2[s, :nb] = blocks
+            pp = np.arange(p0, p0 + n)
+            barr = np.asarray(blocks, dtype=np.int64)
+            slots[row:row + n] = barr[pp // bs] * bs + pp % bs
+            qs[s], ql[s], ctx[s], state[s] = row, n, p0 + n, it.seq.state_slot
+            if it.sample:
+                k = it.verify if logits_all_verify else 0
+                lrows[nl:nl + k + 1] = np.arange(row + n - 1 - k, row + n)
+                nl += k + 1
+            row += n
+            max_q, max_ctx = max(max_q, n), max(max_ctx, p0 + n)
+        S = len(plan.items)
+        while S < pad_seqs:                                   # null rows up to the graph rung
+            tokens[row], pos[row], slots[row] = 0, 0, -1
+            qs[S], ql[S], ctx[S], state[S] = row, 1, 1, 0
+            bt2[S, 0] = 0
+            lrows[nl] = row
+            nl += 1
+            row += 1
+            S += 1
+        st.upload()
+        self.h2d_bytes += st.bytes_per_copy
+        dv = lambda name, n: st.view(st.dev, name, n)
+        b = ForwardBatch(
+            token_ids=dv("tokens", row), positions=dv("pos", row),
+            slot_mapping=dv("slots", 2 * row).view(torch.int64),
+            q_start=dv("q_start", S), q_len=dv("q_len", S), ctx_len=dv("ctx", S),
+            block_table=dv("bt", None).view(st.S_cap, st.max_blocks)[:S],
+            logit_rows=dv("lrows", 2 * nl).view(torch.int64),
+            max_q_len=max_q, max_ctx=max_ctx, state_slots=dv("state", S), num_tokens=row, num_seqs=S)
+        return b
+
+    def _set_sampling(self, plan: StepPlan) -> bool:
+        """Upload per-row sampling parameters; returns True when every row is greedy."""
+        all_greedy = all(i.seq.req.params.greedy for i in plan.items)
+        if all_greedy:
+            return True
+        n = len(plan.items)
+        P = [i.seq.req.params for i in plan.items]
+        dev = self.device
+        self.s_temp[:n] = torch.tensor([p.temperature for p in P], dtype=torch.float32).to(dev, non_blocking=True)
+        self.s_topk[:n] = torch.tensor([p.top_k for p in P], dtype=torch.int32).to(dev, non_blocking=True)
+        self.s_topp[:n] = torch.tensor([p.top_p for p in P], dtype=torch.float32).to(dev, non_blocking=True)
+        self.s_minp[:n] = torch.tensor([p.min_p for p in P], dtype=torch.float32).to(dev, non_blocking=True)
+        seeds = [(p.seed if p.seed is not None else i.seq.seq_id * 1000003) & ((1 << 62) - 1)
+                 for p, i in zip(P, plan.items)]
+        self.s_seed[:n] = torch.tensor(seeds, dtype=torch.int64).to(dev, non_blocking=True)
+        self.s_step[:n] = torch.tensor([i.seq.sample_step for i in plan.items], dtype=torch.int64).to(dev, non_blocking=True)
+        self.h2d_bytes += n * 32
+        return False
+
+    # ------------------------------------------------------------------ forward variants
+    def _forward_select(self, batch: ForwardBatch, greedy: bool, want_lp: bool, n_rows: int):
+        """decoder forward + on-device token selection into self.out_ids[:n_rows]."""
+        logits, hidden = self.decoder.forward(batch, self.caches, out_f32=not greedy)
+        self.last_hidden = hidden
+        if greedy:
+            if want_lp:
+                _, lp = ops.argmax(logits, logprob=True, out=self.out_ids[:n_rows])
+                self.out_lp[:n_rows].copy_(lp)
+            else:
+                ops.argmax(logits, out=self.out_ids[:n_rows])
+        else:
+            ids, lp = ops.sample(logits, self.s_temp[:n_rows], self.s_topk[:n_rows], self.s_topp[:n_rows],
+                                 self.s_minp[:n_rows], self.s_seed[:n_rows], self.s_step[:n_rows])
+            self.out_ids[:n_rows].copy_(ids)
+            self.out_lp[:n_rows].copy_(lp)
+        return logits
+
+    def _rung(self, n: int) -> int:
+        for r in self.sched.batch_rungs:
+            if n <= r:
+                return r
+        return n
+
+    def _decode_graph(self, plan: StepPlan, greedy: bool, want_lp: bool):
+        """Replay (capturing on first use) the CUDA graph for this batch rung."""
+        n = len(plan.items)
+        rung = self._rung(n)
+        key = (rung, greedy, want_lp)
+        if key not in self.graphs:
+            # warm-up + capture on an all-null batch (rows that write nothing and touch only
+            # the scratch state slot), so capturing never advances a live sequence
+            null = self._stage(StepPlan("decode", []), pad_seqs=rung)
+            null.max_ctx, null.max_q_len = self.sched.max_model_len, 1   # fixed launch geometry
+            self._forward_select(null, greedy, want_lp, rung)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            count0 = ops.launch_count
+            with torch.cuda.graph(g):
+                self._forward_select(null, greedy, want_lp, rung)
+            self.graphs[key] = (g, ops.launch_count - count0, self.last_hidden)
+        self._stage(plan, pad_seqs=rung)
+        g, launches, hidden = self.graphs[key]
+        g.replay()
+        ops.launch_count += launches
+        self.graph_replays += 1
+        self.last_hidden = hidden
+        return rung
+
+    # ------------------------------------------------------------------ entry point
+    def execute(self, plan: StepPlan) -> StepResult:
+        dev_cuda = self.device.type == "cuda"
+        t0 = time.perf_counter()
+        host_logits = any(i.seq.req.params.needs_host_logits or i.seq.req.params.has_penalties
+                          for i in plan.items if i.sample)
+        want_lp = any(i.seq.req.params.logprobs for i in plan.items)
+        greedy = self._set_sampling(plan) if not host_logits else True
+        n_sample_rows = sum((i.verify + 1) for i in plan.items if i.sample)
+        if n_sample_rows == 0:
+            batch = self._stage(plan)
+            self.decoder.backbone(batch, self.caches)
+            return StepResult([[] for _ in plan.items], device_ms=(time.perf_counter() - t0) * 1e3)
+        if host_logits:
+            return self._execute_host_logits(plan, t0)
+        is_plain_decode = plan.kind == "decode" and all(len(i.tokens) == 1 for i in plan.items)
+        if is_plain_decode and self.use_graphs and (greedy or True):
+            self._decode_graph(plan, greedy, want_lp)
+        else:
+            batch = self._stage(plan)
+            if not greedy and n_sample_rows != len(plan.items):
+                greedy = True                                   # verify rows are always argmax
+            self._forward_select(batch, greedy, want_lp, n_sample_rows)
+        self.host_ids[:n_sample_rows].copy_(self.out_ids[:n_sample_rows], non_blocking=True)
+        if want_lp or not greedy:
+            self.host_lp[:n_sample_rows].copy_(self.out_lp[:n_sample_rows], non_blocking=True)
+            self.d2h_bytes += 4 * n_sample_rows
+        self.d2h_bytes += 4 * n_sample_rows
+        if dev_cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+        ids = self.host_ids[:n_sample_rows].tolist()
+        lps = self.host_lp[:n_sample_rows].tolist() if (want_lp or not greedy) else None
+        toks, lpo, r = [], [], 0
+        for it in plan.items:
+            if not it.sample:
+                toks.append([]); lpo.append([])
+                continue
+            k = it.verify + 1
+            toks.append(ids[r:r + k])
+            lpo.append(lps[r:r + k] if lps else [])
+            it.seq.sample_step += 1
+            r += k
+        return StepResult(toks, lpo if lps else None, hidden=self.last_hidden,
+                          device_ms=(time.perf_counter() - t0) * 1e3)
+
+    def _execute_host_logits(self, plan: StepPlan, t0: float) -> StepResult:
+        """Full-logits path: penalties, logit bias, grammar masks, top-n-sigma, top log-probs."""
+        from ..sampling.host import sample_rows
+        batch = self._stage(plan)
+        logits, hidden = self.decoder.forward(batch, self.caches, out_f32=True)
+        self.last_hidden = hidden
+        toks, lps = sample_rows(self, plan, logits)
+        self.d2h_bytes += logits.numel() * 4
+        return StepResult(toks, lps, hidden=hidden, device_ms=(time.perf_counter() - t0) * 1e3)
+
+    # ------------------------------------------------------------------ MTP drafting
+    def propose(self, plan: StepPlan, result: StepResult, accepted: List[int], k: int) -> List[List[int]]:
+        """Draft k tokens per sequence with the MTP head, autoregressively: step j feeds the
+        previous token and the previous hidden state (target hidden for j = 0)."""
+        if self.w.mtp is None or k <= 0:
+            return [[] for _ in plan.items]
+        from ..speculative.mtp import mtp_propose
+        return mtp_propose(self, plan, result, accepted, k)
+
+    # ------------------------------------------------------------------ helpers
+    def kv_bytes(self) -> int:
+        return self.kv.bytes() + (self.mtp_kv.bytes() if self.mtp_kv else 0)
+
+
+def plan_kv_blocks(cfg: ModelConfig, w: ModelW, device, block_size: int, utilization: float = 0.9,
+                   reserve_bytes: int = 6 << 30, max_blocks: Optional[int] = None) -> int:
+    """KV budget: what is left of `utilization` x device memory after the weights and a
+    reserve for activations / workspaces / graphs (role of factory/build.rs KV sizing)."""
+    dev = torch.device(device)
+    kc = kv_config(cfg, w, block_size)
+    per_block = kc.block_bytes()
+    if w.mtp is not None:
+        per_block += kv_config(cfg, w, block_size, mtp=True).block_bytes()
+    if dev.type != "cuda":
+        return max_blocks or 512
+    free, total = torch.cuda.mem_get_info(dev)
+    budget = min(free, int(total * utilization) - (total - free)) - reserve_bytes
+    n = max(16, budget // max(1, per_block))
+    return min(n, max_blocks) if max_blocks else n

@@ -1,0 +1,180 @@
+"""The decoder graph: one class assembles every served architecture from per-layer blocks
+(attention | gated-delta-net | Mamba2 | MLA mixer, then dense | MoE | no FFN), following the
+op order of the reference's circuits (``kernels/circuits/dense_gqa.toml:65-212``,
+``blocks/qwen3_hybrid.toml``, ``qwen3_6_moe.toml``, ``nemotron_h.toml``).
+
+The residual stream `x` is bf16 ``[T, hidden]``. Every sub-block is
+``x = x + proj(mixer(norm(x)))`` with the residual add fused into the projection GEMM's
+epilogue and the norm fused with the activation quantiser of the GEMM that consumes it, so a
+dense layer is ten launches. The same code runs on CPU tensors (fp32 restatement of each op:
+the oracle) and on CUDA tensors (sm_100a kernels).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import torch
+
+from .. import ops
+from ..config.model_config import ModelConfig
+from ..engine.batch import ForwardBatch
+from ..ops import ACT_FOR_WEIGHT, Act
+from ..ops import reference as ref
+from ..weights.loader import AttnW, FfnW, LayerW, ModelW
+
+
+class LayerCaches:
+    """Per-layer handles into the paged KV cache and the recurrent-state pool."""
+
+    def __init__(self, cfg: ModelConfig, kv=None, state=None, mtp_kv=None):
+        self.kv, self.state, self.mtp_kv = kv, state, mtp_kv
+        self.kv_index, self.state_index = {}, {}
+        a = s = 0
+        for i, t in enumerate(cfg.layer_types):
+            if t in ("attention", "mla"):
+                self.kv_index[i] = a
+                a += 1
+            else:
+                self.state_index[i] = s
+                s += 1
+
+
+class TpContext:
+    """How partial sums are combined across tensor-parallel ranks. The single-rank context
+    is a no-op (role of the reference's ``SingleGpuBackend``)."""
+    size = 1
+    rank = 0
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        return t
+
+    def all_gather_last(self, t: torch.Tensor) -> torch.Tensor:
+        return t
+
+    def linear_reduce(self, act: Act, w, residual=None) -> torch.Tensor:
+        """Row-parallel projection + sum over ranks + residual."""
+        return ops.linear(act, w, residual=residual)
+
+
+class Decoder:
+    def __init__(self, cfg: ModelConfig, weights: ModelW, tp: Optional[TpContext] = None, device="cpu"):
+        self.cfg, self.w, self.tp = cfg, weights, tp or TpContext()
+        self.device = torch.device(device)
+        rot = cfg.rotary_dim
+        self.cos = self.sin = None
+        if rot > 0:
+            self.cos, self.sin = ref.rope_tables(cfg.max_position, rot, cfg.rope_theta, device=self.device)
+        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+
+    # ------------------------------------------------------------------ helpers
+    def _norm_act(self, x, w, fmt: str, also_bf16: bool = False) -> Act:
+        return ops.row_op(x, fmt, ops.IN_RMSNORM, w=w, plus_one=self.cfg.norm_plus_one,
+                          eps=self.cfg.rms_eps, also_bf16=also_bf16)[0]
+
+    @staticmethod
+    def _as_act(t: torch.Tensor, fmt: str) -> Act:
+        if fmt == "bf16" and t.is_cuda:
+            return Act("bf16", t.shape[0], t.shape[1], t, bf16=t)
+        return ops.quantize_act(t, fmt)
+
+    # ------------------------------------------------------------------ blocks
+    def attention_block(self, x, lw: LayerW, batch: ForwardBatch, kc, vc, ks, vs):
+        c, w = self.cfg, lw.mixer
+        D = c.head_dim
+        a = self._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.qkv.fmt])
+        qkv = ops.linear(a, w.qkv)
+        qhs = 2 * D if c.attn_output_gate else D
+        q = ops.qk_norm_rope_kvwrite(
+            qkv, Hq=w.heads, Hkv=w.kv_heads, D=D, positions=batch.positions, slots=batch.slot_mapping,
+            k_cache=kc, v_cache=vc, q_norm_w=w.q_norm, k_norm_w=w.k_norm, plus_one=c.norm_plus_one,
+            eps=c.rms_eps, cos=self.cos, sin=self.sin, q_head_stride=qhs, k_scale=ks, v_scale=vs)
+        o = ops.paged_attention(q, kc, vc, batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
+                                max_q_len=batch.max_q_len, max_ctx=batch.max_ctx, scale=self.scale,
+                                k_scale=ks, v_scale=vs, window=c.sliding_window)
+        o = o.view(o.shape[0], w.heads * D)
+        fmt = ACT_FOR_WEIGHT[w.o.fmt]
+        if c.attn_output_gate:
+            oa = ops.row_op(o, fmt, ops.IN_SIGMOID_GATE, gate=qkv, head_dim=D, gate_head_stride=2 * D,
+                            gate_head_off=D)[0]
+        else:
+            oa = self._as_act(o, fmt)
+        return self.tp.linear_reduce(oa, w.o, residual=x)
+
+    def dense_ffn(self, a: Act, w: FfnW, residual) -> torch.Tensor:
+        c = self.cfg
+        fmt_d = ACT_FOR_WEIGHT[w.down.fmt]
+        if c.ffn_act == "relu2":
+            up = ops.linear(a, w.gate_up)
+            h = ops.row_op(up, fmt_d, ops.IN_RELU2)[0]
+        elif w.interleaved:
+            h = self._as_act(ops.linear(a, w.gate_up, swiglu=True), fmt_d)
+        else:
+            gu = ops.linear(a, w.gate_up)
+            h = ops.row_op(gu, fmt_d, ops.IN_SILU_MUL)[0]
+        return self.tp.linear_reduce(h, w.down, residual=residual)
+
+    def ffn_block(self, x, lw: LayerW):
+        if lw.ffn_kind == "none":
+            return x
+        if lw.ffn_kind == "dense":
+            a = self._norm_act(x, lw.ln2, ACT_FOR_WEIGHT[lw.ffn.gate_up.fmt])
+            return self.dense_ffn(a, lw.ffn, x)
+        from .moe import moe_block
+        return moe_block(self, x, lw)
+
+    def layer(self, i: int, x, lw: LayerW, batch: ForwardBatch, caches: LayerCaches, kv=None, kv_idx=None):
+        if lw.kind == "attention":
+            kv = kv or caches.kv
+            j = caches.kv_index[i] if kv_idx is None else kv_idx
+            x = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j])
+        elif lw.kind == "gdn":
+            from .recurrent import gdn_block
+            x = gdn_block(self, x, lw, batch, caches.state, caches.state_index[i])
+        elif lw.kind == "mamba2":
+            from .recurrent import mamba2_block
+            x = mamba2_block(self, x, lw, batch, caches.state, caches.state_index[i])
+        elif lw.kind == "mla":
+            from .mla import mla_block
+            kv = kv or caches.kv
+            j = caches.kv_index[i] if kv_idx is None else kv_idx
+            x = mla_block(self, x, lw, batch, kv, j)
+        return self.ffn_block(x, lw)
+
+    # ------------------------------------------------------------------ full forward
+    def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
+        return ops.embed(token_ids, self.w.embed)
+
+    def backbone(self, batch: ForwardBatch, caches: LayerCaches) -> torch.Tensor:
+        """Token ids -> final residual stream [T, hidden] (before the final norm)."""
+        x = self.embed(batch.token_ids)
+        for i, lw in enumerate(self.w.layers):
+            x = self.layer(i, x, lw, batch, caches)
+        return x
+
+    def logits(self, hidden_rows: torch.Tensor, final_norm=None, out_f32: bool = False) -> torch.Tensor:
+        """Final norm + (vocab-parallel) lm_head on the selected rows."""
+        a = self._norm_act(hidden_rows, self.w.final_norm if final_norm is None else final_norm, "bf16")
+        lg = ops.linear(a, self.w.lm_head, out_f32=out_f32)
+        return self.tp.all_gather_last(lg)
+
+    def forward(self, batch: ForwardBatch, caches: LayerCaches, out_f32: bool = False
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Returns (logits [R, vocab], hidden [R, hidden]) for batch.logit_rows."""
+        x = self.backbone(batch, caches)
+        rows = x.index_select(0, batch.logit_rows) if batch.logit_rows.numel() != x.shape[0] else x
+        return self.logits(rows, out_f32=out_f32), rows
+
+    # ------------------------------------------------------------------ MTP draft head
+    def mtp_forward(self, token_ids, hidden, batch: ForwardBatch, caches: LayerCaches) -> Tuple[torch.Tensor, torch.Tensor]:
+        """One multi-token-prediction step: embed(next token) || target hidden -> two norms ->
+        concat -> fc -> one decoder layer over the head's own KV cache -> norm -> lm_head
+        (kernels/circuits/blocks/qwen3_hybrid.toml:285-340). Returns (logits, hidden)."""
+        m, c = self.w.mtp, self.cfg
+        e = self._norm_act(self.embed(token_ids), m.norm_emb, "bf16").bf16
+        h = self._norm_act(hidden, m.norm_hid, "bf16").bf16
+        cat = torch.cat([e, h], dim=-1).contiguous()
+        x = ops.linear(self._as_act(cat, "bf16"), m.fc)
+        x = self.layer(c.num_layers, x, m.layer, batch, caches, kv=caches.mtp_kv, kv_idx=0)
+        rows = x.index_select(0, batch.logit_rows) if batch.logit_rows.numel() != x.shape[0] else x
+        return self.logits(rows, final_norm=m.final_norm), rows

@@ -1,0 +1,68 @@
+"""Multi-head latent attention block (DeepSeek-V3 shape) in absorbed form.
+
+The paged cache stores one row per token: ``[kv_lora latent (RMS-normed) | rope key]``
+(kv_lora + rope dims, a single "kv head"). Queries are projected into latent space with
+W_uk, attention runs as multi-query attention over the latent rows, and W_uv maps the
+latent-space output back to per-head values before o_proj.
+Reference behaviour: ``kernels/gb10/deepseek-v4-flash/nvfp4/mla_absorbed.cu``
+(``mla_batched_gemv``, ``mla_cache_assemble``), ``paged_decode_attn_mla.cu``.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import ops
+from ..ops import ACT_FOR_WEIGHT
+from ..ops import reference as ref
+
+
+def mla_block(dec, x, lw, batch, kv, j: int):
+    c, w = dec.cfg, lw.mixer
+    H, nope, rope, vd, L = w.heads, c.qk_nope_dim, c.qk_rope_dim, c.v_head_dim, c.kv_lora_rank
+    T = x.shape[0]
+    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.kv_a.fmt])
+    if w.q_a is not None:
+        qa = ops.linear(a, w.q_a)
+        qn = ops.row_op(qa, ACT_FOR_WEIGHT[w.q_b.fmt], ops.IN_RMSNORM, w=w.q_a_norm, eps=c.rms_eps)[0]
+        q = ops.linear(qn, w.q_b)
+    else:
+        q = ops.linear(a, w.q_b)
+    q = q.view(T, H, nope + rope).float()
+    ckv = ops.linear(a, w.kv_a).float()                                # [T, L + rope]
+    lat = ref.rms_norm(ckv[:, :L], w.kv_a_norm, c.rms_eps)
+    k_rope = ref.apply_rope_neox(ckv[:, None, L:], batch.positions, dec.cos, dec.sin)[:, 0]
+    q_rope = ref.apply_rope_neox(q[..., nope:], batch.positions, dec.cos, dec.sin)
+    row = torch.cat([lat, k_rope], -1).to(kv.k[j].dtype)               # cache row
+    flat = kv.k[j].view(-1, L + rope)
+    ok = batch.slot_mapping >= 0
+    flat[batch.slot_mapping[ok]] = row[ok]
+    q_lat = torch.einsum("thn,hnl->thl", q[..., :nope], w.w_uk.float())   # absorb W_uk
+    qq = torch.cat([q_lat, q_rope], -1).to(torch.bfloat16)             # [T, H, L + rope]
+    scale = 1.0 / math.sqrt(nope + rope)
+    o_lat = mla_attention(qq, kv.k[j], batch, scale, L)                # [T, H, L] fp32
+    o = torch.einsum("thl,hvl->thv", o_lat, w.w_uv.float()).reshape(T, H * vd)
+    oa = ops.quantize_act(o.to(torch.bfloat16), ACT_FOR_WEIGHT[w.o.fmt])
+    return dec.tp.linear_reduce(oa, w.o, residual=x)
+
+
+def mla_attention(q, cache, batch, scale: float, L: int) -> torch.Tensor:
+    """Multi-query attention over latent rows: keys are the full row, values its first L dims."""
+    T, H, D = q.shape
+    nb, bs, _, _ = cache.shape
+    out = torch.zeros(T, H, L, dtype=torch.float32, device=q.device)
+    qs, ql, cl = batch.q_start.tolist(), batch.q_len.tolist(), batch.ctx_len.tolist()
+    for s in range(len(ql)):
+        n, ctx = ql[s], cl[s]
+        if n <= 0:
+            continue
+        nblk = (ctx + bs - 1) // bs
+        rows = cache[batch.block_table[s, :nblk].long()].reshape(nblk * bs, D)[:ctx].float()
+        qq = q[qs[s]:qs[s] + n].float()
+        sc = torch.einsum("qhd,kd->hqk", qq, rows) * scale
+        pq = torch.arange(ctx - n, ctx, device=q.device)[:, None]
+        pk = torch.arange(ctx, device=q.device)[None, :]
+        sc = sc.masked_fill(~(pk <= pq)[None], float("-inf"))
+        out[qs[s]:qs[s] + n] = torch.einsum("hqk,kl->qhl", torch.softmax(sc, -1), rows[:, :L])
+    return out

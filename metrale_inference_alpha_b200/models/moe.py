@@ -1,0 +1,78 @@
+"""MoE FFN block: norm -> router -> top-k -> routed experts (+ shared expert, optional
+sigmoid gate) -> blend -> residual (``kernels/circuits/qwen3_6_moe.toml:43-125``; sigmoid
+group-limited routing for DeepSeek-V3-shaped models).
+
+Expert parallelism: every rank routes all tokens; on the plain path a rank runs only its
+local experts and the partial outputs are summed over ranks (the reference's masked-local +
+all-reduce scheme, ``model-layers/src/layers/moe/forward/ep_reduce.rs:21-52``). The fused
+dispatch/combine path over NVLink peer memory lives in ``parallel/ep.py``.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import ACT_FOR_WEIGHT, moe as moe_ops
+
+
+def moe_block(dec, x, lw):
+    c, w = dec.cfg, lw.ffn
+    fmt = ACT_FOR_WEIGHT[(w.experts[0].gate_up if w.experts else w.shared.gate_up).fmt]
+    a = dec._norm_act(x, lw.ln2, fmt, also_bf16=True)
+    hb = a.bf16
+    logits = ops.linear(dec._as_act(hb, "bf16"), w.router, out_f32=True)
+    weights, idx = moe_ops.route(logits, c, w.bias)
+    T = x.shape[0]
+    ep = getattr(dec.tp, "ep", None)
+    if ep is not None and x.is_cuda:
+        routed = ep.dispatch_compute_combine(dec, a, weights, idx, w)
+    else:
+        routed = routed_experts(dec, a, weights, idx, w)
+    y = routed
+    if w.shared is not None:
+        sh = shared_expert(dec, a, w)
+        if w.shared_gate is not None:
+            g = ops.linear(dec._as_act(hb, "bf16"), w.shared_gate, out_f32=True)
+            sh = sh.float() * torch.sigmoid(g)
+        y = y.float() + sh.float()
+    y = dec.tp.all_reduce(y.to(torch.bfloat16)) if (dec.tp.size > 1) else y
+    return (x.float() + y.float()).to(torch.bfloat16)
+
+
+def shared_expert(dec, a, w):
+    f = w.shared
+    fmt_d = ACT_FOR_WEIGHT[f.down.fmt]
+    if dec.cfg.ffn_act == "relu2":
+        h = ops.row_op(ops.linear(a, f.gate_up), fmt_d, ops.IN_RELU2)[0]
+    elif f.interleaved:
+        h = dec._as_act(ops.linear(a, f.gate_up, swiglu=True), fmt_d)
+    else:
+        h = ops.row_op(ops.linear(a, f.gate_up), fmt_d, ops.IN_SILU_MUL)[0]
+    return ops.linear(h, f.down)
+
+
+def routed_experts(dec, a, weights, idx, w):
+    """Sum over the local experts of weight * expert(x); fp32 [T, hidden]."""
+    if a.data.is_cuda and w.grouped is not None:
+        from ..ops.moe_cuda import grouped_ffn
+        return grouped_ffn(dec.cfg, a, weights, idx, w)
+    T = a.M
+    H = dec.cfg.hidden_size
+    out = torch.zeros(T, H, dtype=torch.float32, device=a.data.device)
+    lo = w.expert_lo
+    for j, f in enumerate(w.experts):
+        e = lo + j
+        tok, slot = torch.nonzero(idx == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        sub = ops.Act(a.fmt, tok.numel(), a.K, a.data[tok])
+        fmt_d = ACT_FOR_WEIGHT[f.down.fmt]
+        if dec.cfg.ffn_act == "relu2":
+            h = ops.row_op(ops.linear(sub, f.gate_up), fmt_d, ops.IN_RELU2)[0]
+        elif f.interleaved:
+            h = ops.quantize_act(ops.linear(sub, f.gate_up, swiglu=True), fmt_d)
+        else:
+            h = ops.row_op(ops.linear(sub, f.gate_up), fmt_d, ops.IN_SILU_MUL)[0]
+        y = ops.linear(h, f.down, out_f32=True)
+        out.index_add_(0, tok, y * weights[tok, slot][:, None])
+    return out

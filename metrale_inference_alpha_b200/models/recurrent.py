@@ -1,0 +1,59 @@
+"""Recurrent mixers: gated-delta-net (Qwen3.5 / 3.6 linear attention) and Mamba2 (Nemotron-H).
+
+Both keep an fp32 state per sequence in the state pool (a conv window + a matrix) and
+process a batch whose sequences contribute any number of tokens (decode 1, verify k+1,
+prefill chunk n). On CUDA the conv, gate, recurrence and scan steps are the kernels in
+``ops/csrc/recurrent.cu`` (one launch for all sequences); on CPU they are the reference loops.
+Op order: ``kernels/circuits/blocks/qwen3_hybrid.toml:52-130`` and
+``kernels/circuits/nemotron_h.toml:81-173``.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import ACT_FOR_WEIGHT
+from ..ops import recurrent as rops
+
+
+def gdn_block(dec, x, lw, batch, pool, sidx: int):
+    c, w = dec.cfg, lw.mixer
+    kd, vd, kh, vh = c.gdn_k_dim, c.gdn_v_dim, w.k_heads, w.v_heads
+    QK, V = kh * kd, vh * vd
+    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.in_qkvz.fmt], also_bf16=True)
+    qkvz = ops.linear(a, w.in_qkvz)                                   # [T, 2QK + 2V]
+    ba = ops.linear(dec._as_act(a.bf16, "bf16"), w.in_ba, out_f32=True)   # [T, 2 vh] = b | a
+    conv_out = rops.causal_conv1d(qkvz, 2 * QK + V, w.conv_w, None, pool.conv[sidx], batch, activation=True)
+    core = rops.gdn_recurrence(conv_out, ba, w.A_log, w.dt_bias, pool.ssm[sidx], batch,
+                               k_heads=kh, v_heads=vh, k_dim=kd, v_dim=vd)          # [T, V] fp32
+    z = qkvz[:, 2 * QK + V:]
+    y = ops.row_op(core, ACT_FOR_WEIGHT[w.out.fmt], ops.IN_GATED_RMSNORM, gate=z, w=_tile(w.norm_w, vh),
+                   group=vd, eps=c.rms_eps)[0]
+    return dec.tp.linear_reduce(y, w.out, residual=x)
+
+
+_tile_cache = {}
+
+
+def _tile(w: torch.Tensor, n: int) -> torch.Tensor:
+    key = (w.data_ptr(), n)
+    if key not in _tile_cache:
+        _tile_cache[key] = w.repeat(n).contiguous()
+    return _tile_cache[key]
+
+
+def mamba2_block(dec, x, lw, batch, pool, sidx: int):
+    c, w = dec.cfg, lw.mixer
+    H, G, P, N = w.heads, w.groups, c.mamba_head_dim, c.mamba_state
+    inner, GN = H * P, G * N
+    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.in_proj.fmt])
+    zxbcdt = ops.linear(a, w.in_proj)                                 # [T, 2 inner + 2GN + H]
+    xbc = rops.causal_conv1d(zxbcdt[:, inner:], inner + 2 * GN, w.conv_w, w.conv_b, pool.conv[sidx], batch,
+                             activation=True)
+    dt = zxbcdt[:, 2 * inner + 2 * GN:]
+    y = rops.mamba2_scan(xbc, dt, w.A_log, w.D, w.dt_bias, pool.ssm[sidx], batch, heads=H, groups=G,
+                         head_dim=P, state=N)                          # [T, inner] fp32
+    z = zxbcdt[:, :inner]
+    ya = ops.row_op(y, ACT_FOR_WEIGHT[w.out.fmt], ops.IN_GATED_RMSNORM, gate=z, w=w.norm_w,
+                    group=inner // max(1, G), eps=c.rms_eps)[0]
+    return dec.tp.linear_reduce(ya, w.out, residual=x)

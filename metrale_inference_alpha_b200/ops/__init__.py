@@ -93,6 +93,7 @@ class QuantWeight:
     data: torch.Tensor
     scale: Optional[torch.Tensor] = None
     gscale: float = 1.0
+    row_gscale: Optional[torch.Tensor] = None   # nvfp4: per-row global scale (fused q|k|v, gate|up)
     sf_tiled: Optional[torch.Tensor] = None
     sf_k64: int = 0
     _deq: Optional[torch.Tensor] = None
@@ -108,13 +109,16 @@ class QuantWeight:
             d = ref.dequantize_fp8_block128(self.data, self.scale.float())
         else:
             d = ref.dequantize_nvfp4(self.data, self.scale, self.gscale)
+            if self.row_gscale is not None:
+                d = d * self.row_gscale.float()[:, None]
         if not self.data.is_cuda:
             self._deq = d
         return d
 
     def to(self, device) -> "QuantWeight":
         w = QuantWeight(self.fmt, self.N, self.K, self.data.to(device),
-                        None if self.scale is None else self.scale.to(device), self.gscale)
+                        None if self.scale is None else self.scale.to(device), self.gscale,
+                        None if self.row_gscale is None else self.row_gscale.to(device))
         if w.fmt == "nvfp4" and w.data.is_cuda:
             w.prepare_cuda()
         return w
@@ -333,12 +337,46 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
         a.sfa, a.sfb, a.sf_k64 = _ptr(w.sf_tiled), _ptr(act.sf), w.sf_k64
         assert act.sf_k64 == w.sf_k64
         a.a_scale = _ptr(act.scale)
+        a.w_scale = _ptr(w.row_gscale)
         a.alpha = w.gscale
     a.epilogue, a.out_f32 = int(swiglu), int(out_f32)
     a.ws, a.ws_bytes, a.status = _ptr(rt.ws), rt.ws_bytes, _ptr(rt.status)
     a.force_tn, a.force_splits, a.sm_count = force_tn, force_splits, rt.sm_count
     _native.check(L.mb_gemm(C.byref(a), _stream()), f"gemm[{w.fmt} M={M} N={N} K={w.K}]")
     _count()
+    return out
+
+
+def concat_weights(ws) -> QuantWeight:
+    """Stack linear layers that share an input along N (q|k|v, gate|up). NVFP4 parts keep
+    their own fp32 global scale as a per-row scale."""
+    fmt, K = ws[0].fmt, ws[0].K
+    assert all(w.fmt == fmt and w.K == K for w in ws)
+    data = torch.cat([w.data for w in ws], 0)
+    N = sum(w.N for w in ws)
+    if fmt == "bf16":
+        return QuantWeight(fmt, N, K, data)
+    if fmt == "fp8_block":
+        assert all(w.N % 128 == 0 for w in ws[:-1]), "block-scaled parts must be 128-row aligned"
+    scale = torch.cat([w.scale for w in ws], 0)
+    out = QuantWeight(fmt, N, K, data, scale)
+    if fmt == "nvfp4":
+        out.row_gscale = torch.cat([torch.full((w.N,), w.gscale, dtype=torch.float32, device=data.device)
+                                    if w.row_gscale is None else w.row_gscale * w.gscale for w in ws])
+        out.gscale = 1.0
+    return out
+
+
+def permute_rows(w: QuantWeight, perm: torch.Tensor) -> QuantWeight:
+    """Reorder output features (used to interleave gate/up rows for the SwiGLU epilogue)."""
+    assert w.fmt != "fp8_block" or True
+    out = QuantWeight(w.fmt, w.N, w.K, w.data[perm].contiguous(), None, w.gscale)
+    if w.fmt in ("fp8_row", "nvfp4"):
+        out.scale = w.scale[perm].contiguous()
+    elif w.fmt == "fp8_block":
+        raise ValueError("row permutation would break 128x128 scale blocks")
+    if w.row_gscale is not None:
+        out.row_gscale = w.row_gscale[perm].contiguous()
     return out
 
 
@@ -370,6 +408,10 @@ def argmax(logits: torch.Tensor, *, logprob: bool = False, mask_ids: Tuple[int, 
             if m >= 0:
                 x[:, m] = float("-inf")
         ids = x.argmax(dim=-1).to(torch.int32)
+        if out is not None:
+            out.copy_(ids)
+        if feed is not None:
+            feed.copy_(ids)
         lp = None
         if logprob:
             lp = -(torch.logsumexp(logits.float(), -1) - x.max(-1).values)

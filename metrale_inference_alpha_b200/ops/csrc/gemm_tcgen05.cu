@@ -44,7 +44,7 @@ struct GemmParams {
   int M, N, K, ldo;
   void* out;
   const __nv_bfloat16* residual;
-  const float* w_scale;   // KIND_FP8: [N]; KIND_FP8_BLOCK: [ceil(N/128), ceil(K/128)]
+  const float* w_scale;   // KIND_FP8: [N]; KIND_NVFP4: optional per-row global scale [N]; KIND_FP8_BLOCK: [ceil(N/128), ceil(K/128)]
   const float* a_scale;   // KIND_FP8 / NVFP4: [M] or null; KIND_FP8_BLOCK: [ceil(K/128), a_ld]
   int a_ld;
   float alpha;
@@ -211,7 +211,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     auto finish = [&](float* v, int c) {
       // v[j] = accumulator for (n, m0 + c*16 + j), all splits summed, block scales applied
       float wsc = p.alpha;
-      if constexpr (KIND == KIND_FP8) {
+      if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
         if (p.w_scale && n < p.N) wsc *= p.w_scale[n];
       }
 #pragma unroll

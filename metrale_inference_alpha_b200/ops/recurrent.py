@@ -1,0 +1,92 @@
+"""Recurrent-state ops over a ragged batch: causal conv1d with a carried window,
+gated-delta-net recurrence, Mamba2 selective scan. CUDA tensors run the kernels in
+``csrc/recurrent.cu``; CPU tensors run the reference loops (the oracle).
+
+State tensors are indexed by ``batch.state_slots[s]``; a sequence whose first row is at
+position 0 starts from a zero state.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _native, reference as ref
+from . import _count, _ptr, _stream
+
+
+def _seq_rows(batch):
+    qs, ql = batch.q_start.tolist(), batch.q_len.tolist()
+    slots = batch.state_slots.tolist()
+    pos0 = [int(batch.positions[qs[s]]) if ql[s] > 0 else 0 for s in range(len(ql))]
+    return qs, ql, slots, pos0
+
+
+def causal_conv1d(x: torch.Tensor, channels: int, w: torch.Tensor, bias, state: torch.Tensor, batch,
+                  activation: bool = True) -> torch.Tensor:
+    """x [T, >=channels] (first `channels` columns are convolved), w [C, taps] (tap 0 oldest),
+    state [slots, C, taps-1] fp32. Returns fp32 [T, C]; updates the window in place."""
+    if x.is_cuda and _native.available() and hasattr(_native.lib(), "mb_causal_conv1d"):
+        return _conv_cuda(x, channels, w, bias, state, batch, activation)
+    T = x.shape[0]
+    out = torch.empty(T, channels, dtype=torch.float32, device=x.device)
+    qs, ql, slots, pos0 = _seq_rows(batch)
+    for s in range(len(ql)):
+        if slots[s] == 0 and False:
+            continue
+        st = state[slots[s]:slots[s] + 1]
+        if pos0[s] == 0:
+            st = torch.zeros_like(st)
+        for t in range(qs[s], qs[s] + ql[s]):
+            y, st = ref.causal_conv1d_update(st, x[t:t + 1, :channels], w, bias, activation)
+            out[t] = y[0]
+        state[slots[s]] = st[0]
+    return out
+
+
+def gdn_recurrence(conv_out, ba, A_log, dt_bias, state, batch, *, k_heads, v_heads, k_dim, v_dim):
+    """conv_out [T, 2 QK + V] fp32 (q | k | v after conv + SiLU), ba [T, 2 v_heads] fp32
+    (b | a). Applies l2-norm to q and k per head, computes decay/beta, runs the delta rule.
+    state [slots, v_heads, k_dim, v_dim] fp32. Returns fp32 [T, v_heads * v_dim]."""
+    if conv_out.is_cuda and _native.available() and hasattr(_native.lib(), "mb_gdn_recurrence"):
+        return _gdn_cuda(conv_out, ba, A_log, dt_bias, state, batch, k_heads, v_heads, k_dim, v_dim)
+    T = conv_out.shape[0]
+    QK, V = k_heads * k_dim, v_heads * v_dim
+    out = torch.empty(T, V, dtype=torch.float32, device=conv_out.device)
+    qs, ql, slots, pos0 = _seq_rows(batch)
+    decay, beta = ref.gdn_gates(ba[:, v_heads:], ba[:, :v_heads], A_log, dt_bias)
+    for s in range(len(ql)):
+        h = state[slots[s]:slots[s] + 1].clone()
+        if pos0[s] == 0:
+            h.zero_()
+        for t in range(qs[s], qs[s] + ql[s]):
+            q = ref.l2_norm(conv_out[t, :QK].view(1, k_heads, k_dim))
+            k = ref.l2_norm(conv_out[t, QK:2 * QK].view(1, k_heads, k_dim))
+            v = conv_out[t, 2 * QK:2 * QK + V].view(1, v_heads, v_dim)
+            o, h = ref.gdn_recurrence_step(h, q, k, v, decay[t:t + 1], beta[t:t + 1])
+            out[t] = o.reshape(-1)
+        state[slots[s]] = h[0]
+    return out
+
+
+def mamba2_scan(xbc, dt, A_log, D, dt_bias, ssm_state, batch, *, heads, groups, head_dim, state):
+    """xbc [T, inner + 2 G N] fp32 (x | B | C after conv + SiLU), dt [T, heads] (raw).
+    ssm_state [slots, heads, head_dim, state] fp32. Returns fp32 [T, heads * head_dim]."""
+    if xbc.is_cuda and _native.available() and hasattr(_native.lib(), "mb_mamba2_scan"):
+        return _mamba_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups, head_dim, state)
+    T = xbc.shape[0]
+    inner, GN = heads * head_dim, groups * state
+    out = torch.empty(T, inner, dtype=torch.float32, device=xbc.device)
+    qs, ql, slots, pos0 = _seq_rows(batch)
+    for s in range(len(ql)):
+        h = ssm_state[slots[s]:slots[s] + 1].clone()
+        if pos0[s] == 0:
+            h.zero_()
+        for t in range(qs[s], qs[s] + ql[s]):
+            x = xbc[t, :inner].view(1, heads, head_dim)
+            B = xbc[t, inner:inner + GN].view(1, groups, state)
+            Cm = xbc[t, inner + GN:inner + 2 * GN].view(1, groups, state)
+            y, h = ref.mamba2_step(h, x, dt[t:t + 1].float(), A_log, B, Cm, D, dt_bias)
+            out[t] = y.reshape(-1)
+        ssm_state[slots[s]] = h[0]
+    return out

@@ -1,0 +1,56 @@
+"""Per-request sampling parameters (the OpenAI / Anthropic request fields that reach the
+sampler). Role of ``crates/sampling/src/lib.rs:54-103`` (``SamplingParams``)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+
+@dataclass
+class SamplingParams:
+    max_tokens: int = 256
+    min_tokens: int = 0
+    temperature: float = 0.0            # 0 -> greedy
+    top_k: int = 0
+    top_p: float = 1.0
+    min_p: float = 0.0
+    top_n_sigma: float = 0.0
+    repetition_penalty: float = 1.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    logit_bias: Dict[int, float] = field(default_factory=dict)
+    seed: Optional[int] = None
+    stop: List[str] = field(default_factory=list)
+    stop_token_ids: List[int] = field(default_factory=list)
+    ignore_eos: bool = False
+    logprobs: bool = False
+    top_logprobs: int = 0
+    n: int = 1
+    timeout_s: float = 0.0
+    grammar: Optional[object] = None    # constrained decoding matcher (server/grammar.py)
+
+    @property
+    def greedy(self) -> bool:
+        return not self.temperature > 0.0
+
+    @property
+    def needs_host_logits(self) -> bool:
+        """True when plain device argmax / device sampling cannot serve the request."""
+        return bool(self.logit_bias) or self.top_n_sigma > 0 or self.grammar is not None or self.top_logprobs > 0
+
+    @property
+    def has_penalties(self) -> bool:
+        return (self.repetition_penalty != 1.0 or self.presence_penalty != 0.0
+                or self.frequency_penalty != 0.0)
+
+    def validate(self) -> None:
+        if self.max_tokens < 1:
+            raise ValueError("max_tokens must be >= 1")
+        if self.temperature < 0:
+            raise ValueError("temperature must be >= 0")
+        if not 0 < self.top_p <= 1:
+            raise ValueError("top_p must be in (0, 1]")
+        if not 0 <= self.min_p <= 1:
+            raise ValueError("min_p must be in [0, 1]")
+        if self.repetition_penalty <= 0:
+            raise ValueError("repetition_penalty must be > 0")

@@ -1,0 +1,25 @@
+"""Prompt-lookup (n-gram) drafter: find the most recent earlier occurrence of the last n
+tokens and propose what followed it. Needs no model.
+(``crates/speculative/src/ngram.rs:46-70``.)"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+
+class NgramProposer:
+    def __init__(self, max_n: int = 4, min_n: int = 2, window: int = 4096):
+        self.max_n, self.min_n, self.window = max_n, min_n, window
+
+    def propose(self, tokens: Sequence[int], k: int) -> List[int]:
+        L = len(tokens)
+        if k <= 0 or L < self.min_n + 1:
+            return []
+        lo = max(0, L - self.window)
+        for n in range(min(self.max_n, L - 1), self.min_n - 1, -1):
+            tail = list(tokens[L - n:])
+            for start in range(L - n - 1, lo - 1, -1):      # most recent match first
+                if list(tokens[start:start + n]) == tail:
+                    cont = list(tokens[start + n:start + n + k])
+                    if cont:
+                        return cont
+        return []

@@ -1,0 +1,20 @@
+"""Open a checkpoint directory: HF ``config.json`` (or the engine's own ``engine_config.json``
+written by ``write_checkpoint``) + safetensors shards -> (ModelConfig, TensorSource)."""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+from ..config.model_config import ModelConfig, from_hf_config
+from .source import SafetensorsSource
+
+
+def open_checkpoint(path, device="cpu"):
+    p = Path(path)
+    src = SafetensorsSource(p, device=device)
+    eng = p / "engine_config.json"
+    if eng.exists():
+        cfg = ModelConfig.from_json(eng.read_text())
+    else:
+        cfg = from_hf_config(json.loads((p / "config.json").read_text()), name=p.name)
+    return cfg, src
