@@ -303,7 +303,7 @@ def quantize_act(x: torch.Tensor, fmt: str) -> Act:
 # ----------------------------------------------------------------------------- linear
 def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
            swiglu: bool = False, out_f32: bool = False, out: Optional[torch.Tensor] = None,
-           force_tn: int = 0, force_splits: int = 0) -> torch.Tensor:
+           force_tn: int = 0, force_splits: int = 0, dbg: int = 0, grouped=None, trace=None) -> torch.Tensor:
     """out[m, n] = sum_k act[m, k] * w[n, k] (+ residual); with `swiglu`, w holds gate/up rows
     interleaved (2j, 2j+1) and the result is silu(gate) * up of width N/2."""
     assert act.K == w.K, (act.K, w.K)
@@ -319,6 +319,8 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
     L = _native.lib()
     rt = runtime(act.data.device)
     n_out = N // 2 if swiglu else N
+    if grouped is not None:
+        n_out = grouped[3] // 2 if swiglu else grouped[3]
     if out is None:
         out = torch.empty(M, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16,
                           device=act.data.device)
@@ -341,7 +343,12 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
         a.alpha = w.gscale
     a.epilogue, a.out_f32 = int(swiglu), int(out_f32)
     a.ws, a.ws_bytes, a.status = _ptr(rt.ws), rt.ws_bytes, _ptr(rt.status)
-    a.force_tn, a.force_splits, a.sm_count = force_tn, force_splits, rt.sm_count
+    a.force_tn, a.force_splits, a.sm_count, a.dbg = force_tn, force_splits, rt.sm_count, dbg
+    a.trace = _ptr(trace)
+    if grouped is not None:
+        # (tile_expert, tile_row0, tile_nrows, n_per_expert, max_tiles, tile_rows)
+        a.tile_expert, a.tile_row0, a.tile_nrows = _ptr(grouped[0]), _ptr(grouped[1]), _ptr(grouped[2])
+        a.n_per_expert, a.max_tiles, a.force_tn = grouped[3], grouped[4], grouped[5]
     _native.check(L.mb_gemm(C.byref(a), _stream()), f"gemm[{w.fmt} M={M} N={N} K={w.K}]")
     _count()
     return out

@@ -287,53 +287,131 @@ struct TileLoader {
 
 // ------------------------------------------------------------------ split-KV kernel
 // grid (Hkv, num_seqs, parts), 128 threads. MT = number of m16 query-row tiles.
+//
+// K and V tiles of 64 cached tokens stream into shared memory *as stored* (e4m3 bytes or
+// bf16) through a multi-stage cp.async pipeline; nothing is staged in registers. For an e4m3
+// cache the tensor-core fragments are widened to f16 when they are loaded:
+//   * Q.K^T: ldmatrix on the raw bytes hands thread (g, t) four consecutive dims
+//     4t..4t+3 of token g per 16-dim k step; the contraction index may be permuted freely as
+//     long as both operands agree, so the Q fragments (kept in registers for the whole
+//     kernel) are loaded with the same 4t.. ordering and no shuffle is needed.
+//   * P.V: ldmatrix.trans on byte pairs hands thread (g, t) tokens 2t, 2t+1 of dims 2g and
+//     2g+1; the even dims feed one n8 tile and the odd dims another, which only relabels
+//     output columns (undone when O is written).
+template <int ROWB>
+__device__ __forceinline__ uint32_t raw_off(int row, int chunk) {
+  return (uint32_t)(row * ROWB + ((chunk ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ uint32_t e4m3_pair_to_f16x2(uint32_t x, uint32_t sel) {
+  const uint32_t w = __byte_perm(x, 0, sel);          // bytes -> bits 15:8 and 31:24
+  return (w & 0x80008000u) | ((w & 0x7F007F00u) >> 1);
+}
+
+template <int D, bool FP8, int MT>
+struct SplitKvCfg {
+  static constexpr int kRowB = FP8 ? D : 2 * D;                // bytes per cached row in smem
+  static constexpr int kTileB = 64 * kRowB;                    // one K (or V) tile
+  static constexpr int kStages = FP8 ? 4 : 3;
+  static constexpr int kPipeB = kStages * 2 * kTileB;
+  static constexpr int kMergeB = 4 * MT * 16 * 2 * 4 + 4 * MT * 16 * D * 4;
+  static constexpr int kSmem = kPipeB > kMergeB ? kPipeB : kMergeB;
+};
+
 template <int D, bool FP8, int MT>
 __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
+  using C = SplitKvCfg<D, FP8, MT>;
   constexpr bool F16 = FP8;
   constexpr int kTile = 64;
-  constexpr int kTileBytes = kTile * D * 2;
+  constexpr int kRowB = C::kRowB, kTileB = C::kTileB, kStages = C::kStages;
+  constexpr int kChunks = kRowB / 16;                          // 16-byte chunks per row
   extern __shared__ __align__(128) uint8_t smem_attn[];
   const uint32_t sbase = mb::smem_u32(smem_attn);
-  const uint32_t sQ = sbase;                                   // MT*16 rows
-  const uint32_t sK = sbase + MT * 16 * D * 2;                 // 2 buffers
-  const uint32_t sV = sK + 2 * kTileBytes;                     // 2 buffers
   const int kvh = blockIdx.x, seq = blockIdx.y, part = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
   const int G = p.Hq / p.Hkv;
   const int qlen = p.q_len[seq], ctx = p.ctx_len[seq], qs = p.q_start[seq];
-  const int R = G * qlen;                                      // valid query rows
+  const int R = G * qlen;
   if (qlen <= 0) return;
   int tok_begin = part * p.part_tokens;
-  int tok_end = min(ctx, tok_begin + p.part_tokens);
-  if (p.window > 0) tok_begin = max(tok_begin, ctx - qlen + 1 - p.window);
+  const int tok_end = min(ctx, tok_begin + p.part_tokens);
+  if (p.window > 0) tok_begin = max(tok_begin, (ctx - qlen + 1 - p.window) & ~63);
+  if (tok_begin < 0) tok_begin = 0;
   const bool empty = tok_begin >= tok_end;
   const int* bt = p.block_table + (size_t)seq * p.max_blocks;
+  const int ntiles = empty ? 0 : (tok_end - tok_begin + kTile - 1) / kTile;
 
-  if (!empty) {
-    // Q rows -> shared (row r = query token r / G, head r % G), widened/copied as 16-bit
-    for (int idx = tid; idx < MT * 16 * (D / 8); idx += 128) {
-      const int r = idx / (D / 8), c = idx - r * (D / 8);
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < R) {
-        const int t = r / G, g = r - t * G;
-        v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + t) * p.Hq + kvh * G + g) * D + c * 8);
-        if constexpr (F16) {
-          const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
-          uint4 o;
-          uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+  auto issue_tile = [&](int it) {
+    const int stage = it % kStages;
+    const uint32_t sK = sbase + stage * 2 * kTileB, sV = sK + kTileB;
+    const int tok0 = tok_begin + it * kTile;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(b[i]);
-            oo[i] = pack2<true>(f.x, f.y);
-          }
-          v = o;
+    for (int i = 0; i < (64 * kChunks) / 128; ++i) {
+      const int idx = tid + i * 128;
+      const int r = idx / kChunks, c = idx - r * kChunks;
+      const int tok = tok0 + r;
+      const uint8_t* srcK = reinterpret_cast<const uint8_t*>(p.k_cache);
+      const uint8_t* srcV = reinterpret_cast<const uint8_t*>(p.v_cache);
+      int sz = 0;
+      if (tok < tok_end) {
+        const long long blk = bt[tok / p.block_size];
+        if (blk < 0 || blk >= p.num_blocks) {
+          if (p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
+        } else {
+          const size_t off = (((size_t)blk * p.block_size + (tok % p.block_size)) * p.Hkv + kvh) * kRowB +
+                             (size_t)c * 16;
+          srcK += off;
+          srcV += off;
+          sz = 16;
         }
       }
-      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + tile_off<D>(r, c)), "r"(v.x),
-                   "r"(v.y), "r"(v.z), "r"(v.w));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sK + raw_off<kRowB>(r, c)),
+                   "l"(srcK), "r"(sz) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sV + raw_off<kRowB>(r, c)),
+                   "l"(srcV), "r"(sz) : "memory");
+    }
+  };
+
+  // prologue: fill the pipeline, then load the Q fragments while the copies fly
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (s < ntiles) issue_tile(s);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  uint32_t qf[MT][D / 16][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int r = mt * 16 + g + hr * 8;
+      const __nv_bfloat16* qrow = nullptr;
+      if (r < R) {
+        const int tq = r / G, hh = r - tq * G;
+        qrow = p.q + ((size_t)(qs + tq) * p.Hq + kvh * G + hh) * D;
+      }
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t lo = 0, hi = 0;
+        if (qrow) {
+          if constexpr (FP8) {
+            const uint2 v = *reinterpret_cast<const uint2*>(qrow + ks * 16 + 4 * t);
+            const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+            const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+            lo = pack2<true>(f0.x, f0.y);
+            hi = pack2<true>(f1.x, f1.y);
+          } else {
+            lo = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t);
+            hi = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t + 8);
+          }
+        }
+        qf[mt][ks][hr] = lo;          // a0 (row g) / a1 (row g + 8)
+        qf[mt][ks][2 + hr] = hi;      // a2 / a3
+      }
     }
   }
 
+  // O accumulators: o_acc[mt][n][4]; for an e4m3 cache n = 2 * (16-dim group) + parity
   float o_acc[MT][D / 8][4];
   float m_run[MT][2], l_run[MT][2];
 #pragma unroll
@@ -345,150 +423,177 @@ __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) o_acc[mt][n][i] = 0.f;
   }
-  // scores are scaled into the log2 domain once
   const float kmul = FP8 ? (*p.k_scale) * 256.f : 1.f;
   const float sc_log2 = p.scale * kmul * 1.44269504088896f;
 
-  if (!empty) {
-    TileLoader<D, FP8> ldK, ldV;
-    const int ntiles = (tok_end - tok_begin + kTile - 1) / kTile;
-    ldK.fetch(p, p.k_cache, bt, kvh, tok_begin, tok_end, tid, sK);
-    ldV.fetch(p, p.v_cache, bt, kvh, tok_begin, tok_end, tid, sV);
-    for (int it = 0; it < ntiles; ++it) {
-      const int buf = it & 1;
-      ldK.commit(sK + buf * kTileBytes, tid);
-      ldV.commit(sV + buf * kTileBytes, tid);
-      __syncthreads();
-      if (it + 1 < ntiles) {
-        ldK.fetch(p, p.k_cache, bt, kvh, tok_begin + (it + 1) * kTile, tok_end, tid,
-                  sK + (buf ^ 1) * kTileBytes);
-        ldV.fetch(p, p.v_cache, bt, kvh, tok_begin + (it + 1) * kTile, tok_end, tid,
-                  sV + (buf ^ 1) * kTileBytes);
-      }
-      const int tok0 = tok_begin + it * kTile + warp * 16;     // this warp's 16 tokens
-      if (tok0 < tok_end) {
-        const uint32_t kT = sK + buf * kTileBytes, vT = sV + buf * kTileBytes;
-        // S = Q K^T : [MT*16 x 16]
-        float s[MT][2][4];
+  for (int it = 0; it < ntiles; ++it) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 2) : "memory");
+    __syncthreads();
+    if (it + kStages - 1 < ntiles) issue_tile(it + kStages - 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int stage = it % kStages;
+    const uint32_t kT = sbase + stage * 2 * kTileB, vT = kT + kTileB;
+    const int tok0 = tok_begin + it * kTile + warp * 16;
+    if (tok0 >= tok_end) continue;
+    float s[MT][2][4];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-          for (int n = 0; n < 2; ++n)
+      for (int n = 0; n < 2; ++n)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) s[mt][n][i] = 0.f;
+        for (int i = 0; i < 4; ++i) s[mt][n][i] = 0.f;
+    if constexpr (FP8) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          uint32_t b[4];
-          {
-            // matrices: (tok 0-7, k lo) (tok 0-7, k hi) (tok 8-15, k lo) (tok 8-15, k hi)
-            const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
-            const int chunk = ks * 2 + ((lane >> 3) & 1);
-            ldsm4(b, kT + tile_off<D>(row, chunk));
-          }
+      for (int kg = 0; kg < D / 32; ++kg) {              // 32 dims = 2 k steps per ldmatrix.x4
+        uint32_t r[4];
+        // matrices: (tok 0-7, bytes lo) (tok 0-7, bytes hi) (tok 8-15, lo) (tok 8-15, hi)
+        const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+        ldsm4(r, kT + raw_off<kRowB>(row, kg * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {                     // k step 2 kg + h
+          const uint32_t b00 = e4m3_pair_to_f16x2(r[h], 0x1404), b01 = e4m3_pair_to_f16x2(r[h], 0x3424);
+          const uint32_t b10 = e4m3_pair_to_f16x2(r[2 + h], 0x1404), b11 = e4m3_pair_to_f16x2(r[2 + h], 0x3424);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            uint32_t a[4];
-            const int row = mt * 16 + (lane & 15);
-            const int chunk = ks * 2 + (lane >> 4);
-            ldsm4(a, sQ + tile_off<D>(row, chunk));
-            mma16816<F16>(s[mt][0], a, b[0], b[1]);
-            mma16816<F16>(s[mt][1], a, b[2], b[3]);
-          }
-        }
-        // online softmax over this warp's 16 tokens
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-          for (int hr = 0; hr < 2; ++hr) {                      // rows g and g + 8
-            const int r = mt * 16 + (lane >> 2) + hr * 8;
-            const int tq = r / G;
-            const int limit = ctx - qlen + tq + 1;              // causal: tokens < limit
-            const int wlo = p.window > 0 ? limit - p.window : 0;
-            float mx = -INFINITY;
-#pragma unroll
-            for (int n = 0; n < 2; ++n)
-#pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                const int tok = tok0 + n * 8 + (lane & 3) * 2 + i;
-                float v = s[mt][n][hr * 2 + i] * sc_log2;
-                if (tok >= limit || tok >= tok_end || tok < wlo || r >= R) v = -INFINITY;
-                s[mt][n][hr * 2 + i] = v;
-                mx = fmaxf(mx, v);
-              }
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m_run[mt][hr], mx);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = exp2f(m_run[mt][hr] - m_use);   // 0 when m_run = -inf
-            float rs = 0.f;
-#pragma unroll
-            for (int n = 0; n < 2; ++n)
-#pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                const float pv = exp2f(s[mt][n][hr * 2 + i] - m_use);
-                s[mt][n][hr * 2 + i] = pv;
-                rs += pv;
-              }
-            l_run[mt][hr] = l_run[mt][hr] * alpha + rs;
-            m_run[mt][hr] = m_new;
-#pragma unroll
-            for (int n = 0; n < D / 8; ++n) {
-              o_acc[mt][n][hr * 2] *= alpha;
-              o_acc[mt][n][hr * 2 + 1] *= alpha;
-            }
-          }
-        }
-        // O += P V  (k = 16 tokens)
-        uint32_t pa[MT][4];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          pa[mt][0] = pack2<F16>(s[mt][0][0], s[mt][0][1]);
-          pa[mt][1] = pack2<F16>(s[mt][0][2], s[mt][0][3]);
-          pa[mt][2] = pack2<F16>(s[mt][1][0], s[mt][1][1]);
-          pa[mt][3] = pack2<F16>(s[mt][1][2], s[mt][1][3]);
-        }
-#pragma unroll
-        for (int n2 = 0; n2 < D / 16; ++n2) {
-          uint32_t b[4];
-          {
-            // matrices: (tok 0-7, dims lo) (tok 8-15, dims lo) (tok 0-7, dims hi) (tok 8-15, dims hi)
-            const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-            const int chunk = n2 * 2 + (lane >> 4);
-            ldsm4t(b, vT + tile_off<D>(row, chunk));
-          }
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            mma16816<F16>(o_acc[mt][n2 * 2], pa[mt], b[0], b[1]);
-            mma16816<F16>(o_acc[mt][n2 * 2 + 1], pa[mt], b[2], b[3]);
+            mma16816<true>(s[mt][0], qf[mt][kg * 2 + h], b00, b01);
+            mma16816<true>(s[mt][1], qf[mt][kg * 2 + h], b10, b11);
           }
         }
       }
-      __syncthreads();
+    } else {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t b[4];
+        const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+        ldsm4(b, kT + raw_off<kRowB>(row, ks * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma16816<false>(s[mt][0], qf[mt][ks], b[0], b[1]);
+          mma16816<false>(s[mt][1], qf[mt][ks], b[2], b[3]);
+        }
+      }
+    }
+    // online softmax over this warp's 16 tokens
+    uint32_t pa[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {
+        const int r = mt * 16 + g + hr * 8;
+        const int tq = r / G;
+        const int limit = ctx - qlen + tq + 1;
+        const int wlo = p.window > 0 ? limit - p.window : 0;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int tok = tok0 + n * 8 + t * 2 + i;
+            float v = s[mt][n][hr * 2 + i] * sc_log2;
+            if (tok >= limit || tok >= tok_end || tok < wlo || r >= R) v = -INFINITY;
+            s[mt][n][hr * 2 + i] = v;
+            mx = fmaxf(mx, v);
+          }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[mt][hr], mx);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = exp2f(m_run[mt][hr] - m_use);
+        float rs = 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const float pv = exp2f(s[mt][n][hr * 2 + i] - m_use);
+            s[mt][n][hr * 2 + i] = pv;
+            rs += pv;
+          }
+        l_run[mt][hr] = l_run[mt][hr] * alpha + rs;
+        m_run[mt][hr] = m_new;
+        if (alpha != 1.f) {
+#pragma unroll
+          for (int n = 0; n < D / 8; ++n) {
+            o_acc[mt][n][hr * 2] *= alpha;
+            o_acc[mt][n][hr * 2 + 1] *= alpha;
+          }
+        }
+      }
+      pa[mt][0] = pack2<F16>(s[mt][0][0], s[mt][0][1]);
+      pa[mt][1] = pack2<F16>(s[mt][0][2], s[mt][0][3]);
+      pa[mt][2] = pack2<F16>(s[mt][1][0], s[mt][1][1]);
+      pa[mt][3] = pack2<F16>(s[mt][1][2], s[mt][1][3]);
+    }
+    // O += P V
+    if constexpr (FP8) {
+#pragma unroll
+      for (int d2 = 0; d2 < D / 32; ++d2) {               // two 16-dim groups per ldmatrix.x4.trans
+        uint32_t r[4];
+        // matrices: (tok 0-7, grp 2 d2) (tok 8-15, grp 2 d2) (tok 0-7, grp 2 d2 + 1) (tok 8-15, ...)
+        const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        ldsm4t(r, vT + raw_off<kRowB>(row, d2 * 2 + (lane >> 4)));
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int dg = d2 * 2 + h;
+          const uint32_t e0 = e4m3_pair_to_f16x2(r[2 * h], 0x2404), e1 = e4m3_pair_to_f16x2(r[2 * h + 1], 0x2404);
+          const uint32_t o0 = e4m3_pair_to_f16x2(r[2 * h], 0x3414), o1 = e4m3_pair_to_f16x2(r[2 * h + 1], 0x3414);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma16816<true>(o_acc[mt][dg * 2], pa[mt], e0, e1);        // even dims of the group
+            mma16816<true>(o_acc[mt][dg * 2 + 1], pa[mt], o0, o1);    // odd dims
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n2 = 0; n2 < D / 16; ++n2) {
+        uint32_t b[4];
+        const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        ldsm4t(b, vT + raw_off<kRowB>(row, n2 * 2 + (lane >> 4)));
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma16816<false>(o_acc[mt][n2 * 2], pa[mt], b[0], b[1]);
+          mma16816<false>(o_acc[mt][n2 * 2 + 1], pa[mt], b[2], b[3]);
+        }
+      }
     }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
 
-  // ---- merge the 4 warps through shared memory (tile buffers are free now)
-  // layout: ml[warp][row][2], o[warp][row][D]
-  float* s_ml = reinterpret_cast<float*>(smem_attn + MT * 16 * D * 2);
+  // ---- merge the 4 warps through shared memory (the pipeline buffers are free now)
+  float* s_ml = reinterpret_cast<float*>(smem_attn);
   float* s_o = s_ml + 4 * MT * 16 * 2;
   const float vmul = FP8 ? (*p.v_scale) * 256.f : 1.f;
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int hr = 0; hr < 2; ++hr) {
-      const int r = mt * 16 + (lane >> 2) + hr * 8;
+      const int r = mt * 16 + g + hr * 8;
       float l = l_run[mt][hr];
       l += __shfl_xor_sync(0xffffffffu, l, 1);
       l += __shfl_xor_sync(0xffffffffu, l, 2);
-      if ((lane & 3) == 0) {
+      if (t == 0) {
         s_ml[(warp * MT * 16 + r) * 2] = m_run[mt][hr];
         s_ml[(warp * MT * 16 + r) * 2 + 1] = l;
       }
+      float* orow = s_o + ((size_t)(warp * MT * 16 + r)) * D;
+      if constexpr (FP8) {
 #pragma unroll
-      for (int n = 0; n < D / 8; ++n) {
-        float* dst = s_o + ((size_t)(warp * MT * 16 + r)) * D + n * 8 + (lane & 3) * 2;
-        dst[0] = o_acc[mt][n][hr * 2];
-        dst[1] = o_acc[mt][n][hr * 2 + 1];
+        for (int dg = 0; dg < D / 16; ++dg) {
+          // even tile cols (2t, 2t+1) -> dims 4t, 4t+2 ; odd tile -> dims 4t+1, 4t+3
+          float4 v4;
+          v4.x = o_acc[mt][dg * 2][hr * 2];
+          v4.y = o_acc[mt][dg * 2 + 1][hr * 2];
+          v4.z = o_acc[mt][dg * 2][hr * 2 + 1];
+          v4.w = o_acc[mt][dg * 2 + 1][hr * 2 + 1];
+          *reinterpret_cast<float4*>(orow + dg * 16 + 4 * t) = v4;
+        }
+      } else {
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+          orow[n * 8 + t * 2] = o_acc[mt][n][hr * 2];
+          orow[n * 8 + t * 2 + 1] = o_acc[mt][n][hr * 2 + 1];
+        }
       }
     }
   __syncthreads();
@@ -513,8 +618,8 @@ __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
     }
     const float inv = l > 0.f ? vmul / l : 0.f;
     acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-    const int t = r / G, g = r - t * G;
-    const size_t orow = (size_t)(qs + t) * p.Hq + kvh * G + g;
+    const int tq = r / G, hh = r - tq * G;
+    const size_t orow = (size_t)(qs + tq) * p.Hq + kvh * G + hh;
     if (p.parts == 1) {
       __nv_bfloat16* dst = p.out + orow * D + c4 * 4;
       *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x, acc.y);
@@ -718,10 +823,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
 
 template <int D, bool FP8, int MT>
 int launch_splitkv(const AttnParams& p, int num_seqs, cudaStream_t stream) {
-  constexpr int kTileBytes = 64 * D * 2;
-  constexpr int kMerge = 4 * MT * 16 * 2 * 4 + 4 * MT * 16 * D * 4;
-  constexpr int kLoop = 4 * kTileBytes;
-  constexpr int smem = MT * 16 * D * 2 + (kMerge > kLoop ? kMerge : kLoop);
+  constexpr int smem = SplitKvCfg<D, FP8, MT>::kSmem;
   auto kern = attn_splitkv_kernel<D, FP8, MT>;
   static bool configured = false;
   if (!configured) {

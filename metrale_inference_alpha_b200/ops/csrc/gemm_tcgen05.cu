@@ -56,6 +56,13 @@ struct GemmParams {
   int splits, kb_per_split, num_kb;
   int epilogue, out_f32;
   uint32_t* status;
+  // grouped (MoE) mode: blockIdx.y indexes a tile work-list; W is [experts * n_per_expert, K]
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* tile_nrows;
+  int n_per_expert;
+  long long* trace;   // optional per-phase cycle stamps of CTA (0,0,0) and the last CTA in x
+  int dbg;   // timing experiments only: 1 skip SF copies, 2 skip epilogue stores, 4 skip MMAs, 8 skip SF loads
 };
 
 constexpr int kTileN = 128;  // output features per CTA (UMMA M)
@@ -70,11 +77,17 @@ struct Cfg {
   static constexpr int kStagesRaw = kBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = (KIND == KIND_FP8_BLOCK) ? 2 * TN : TN;
-  static constexpr int kNeedCols = kAccCols + (KIND == KIND_NVFP4 ? 32 : 0);
+  static constexpr int kNeedCols = kAccCols + (KIND == KIND_NVFP4 ? 64 : 0);   // 2 x (SFA 16 + SFB 16)
   static constexpr int kTmemCols =
       kNeedCols <= 32 ? 32 : kNeedCols <= 64 ? 64 : kNeedCols <= 128 ? 128 : kNeedCols <= 256 ? 256 : 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
 };
+
+#define MB_STAMP(i)                                                                              \
+  do {                                                                                           \
+    if (p.trace && blockIdx.y == 0 && blockIdx.z == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) \
+      p.trace[(blockIdx.x == 0 ? 0 : 8) + (i)] = clock64();                                     \
+  } while (0)
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -93,13 +106,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int is_last_s;
+  __shared__ float s_ascale[TN];
 
   const int warp = threadIdx.x >> 5;
   const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
+  int m_row0 = tile_m * TN, m_end = p.M, expert = 0, n_limit = p.N;
+  if (p.tile_expert) {
+    expert = p.tile_expert[tile_m];
+    if (expert < 0) return;                       // unused work-list entry (uniform for the CTA)
+    m_row0 = p.tile_row0[tile_m];
+    m_end = m_row0 + p.tile_nrows[tile_m];
+    n_limit = p.n_per_expert;
+  }
+  const int w_row0 = expert * p.n_per_expert + tile_n * kTileN;   // n_per_expert = 0 when not grouped
   const int kb0 = split * p.kb_per_split;
   const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
   const int nkb = kb1 - kb0;
 
+  if (threadIdx.x == 0) MB_STAMP(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mb::mbar_init(&full_bar[s], 1);
@@ -118,6 +142,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __syncthreads();
   mb::tc_fence_after();
   const uint32_t tmem = tmem_base_s;
+  if (threadIdx.x == 0) MB_STAMP(1);
 
   auto sA = [&](int s) { return smem + s * C::kStageBytes; };
   auto sB = [&](int s) { return smem + s * C::kStageBytes + C::kABytes; };
@@ -135,16 +160,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int s = i % kStages;
         const uint32_t ph = (i / kStages) & 1;
         if (!mb::mbar_wait(&empty_bar[s], ph ^ 1, p.status, MB_ST_TIMEOUT_TMA)) break;
-        mb::mbar_expect_tx(&full_bar[s], C::kStageBytes);
+        const bool sf_load = (KIND == KIND_NVFP4) && !(p.dbg & 8);
+        mb::mbar_expect_tx(&full_bar[s], C::kStageBytes - (KIND == KIND_NVFP4 && !sf_load ? 4096 : 0));
         const int kb = kb0 + i;
-        mb::tma_load_2d(sA(s), &tmA, &full_bar[s], kb * kCoordStep, tile_n * kTileN);
-        mb::tma_load_2d(sB(s), &tmB, &full_bar[s], kb * kCoordStep, tile_m * TN);
-        if constexpr (KIND == KIND_NVFP4) {
+        mb::tma_load_2d(sA(s), &tmA, &full_bar[s], kb * kCoordStep, w_row0);
+        mb::tma_load_2d(sB(s), &tmB, &full_bar[s], kb * kCoordStep, m_row0);
+        if (sf_load) {
           const size_t a_off = ((size_t)tile_n * p.sf_k64 + (size_t)kb * 4) * 512;
           const size_t b_off = ((size_t)((tile_m * TN) / 128) * p.sf_k64 + (size_t)kb * 4) * 512;
           mb::bulk_load(sSFA(s), p.sfa + a_off, 2048, &full_bar[s]);
           mb::bulk_load(sSFB(s), p.sfb + b_off, 2048, &full_bar[s]);
         }
+        if (i == 0) MB_STAMP(2);
       }
     }
   } else if (warp == 1) {
@@ -154,7 +181,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if constexpr (KIND == KIND_BF16) idesc = mb::umma_idesc(1, 1, kTileN, TN);
       else if constexpr (KIND == KIND_NVFP4) idesc = mb::umma_idesc_bs(1, 1, kTileN, TN, 0);
       else idesc = mb::umma_idesc(0, 0, kTileN, TN);
-      constexpr uint32_t kSfaCol = TN, kSfbCol = TN + 16;
+      // scale factors alternate between two TMEM column sets so the copies of k block i + 1
+      // do not wait for the MMAs of k block i to release the columns
+      constexpr uint32_t kSfBase = TN;
       bool ok = true;
       for (int i = 0; i < nkb && ok; ++i) {
         const int s = i % kStages;
@@ -170,15 +199,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         ok = mb::mbar_wait(&full_bar[s], ph, p.status, MB_ST_TIMEOUT_MMA);
         if (!ok) break;
         mb::tc_fence_after();
+        if (i == 0) MB_STAMP(3);
         const uint32_t a_base = mb::smem_u32(sA(s)), b_base = mb::smem_u32(sB(s));
+        const uint32_t kSfaCol = kSfBase + (i & 1) * 32, kSfbCol = kSfaCol + 16;
         if constexpr (KIND == KIND_NVFP4) {
-          const uint32_t sfa = mb::smem_u32(sSFA(s)), sfb = mb::smem_u32(sSFB(s));
+          if (!(p.dbg & 1)) {
+            const uint32_t sfa = mb::smem_u32(sSFA(s)), sfb = mb::smem_u32(sSFB(s));
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            mb::tmem_cp_sf(tmem + kSfaCol + j * 4, mb::umma_desc_sf(sfa + j * 512));
-            mb::tmem_cp_sf(tmem + kSfbCol + j * 4, mb::umma_desc_sf(sfb + j * 512));
+            for (int j = 0; j < 4; ++j) {
+              mb::tmem_cp_sf(tmem + kSfaCol + j * 4, mb::umma_desc_sf(sfa + j * 512));
+              mb::tmem_cp_sf(tmem + kSfbCol + j * 4, mb::umma_desc_sf(sfb + j * 512));
+            }
           }
         }
+        if (!(p.dbg & 4)) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const uint64_t da = mb::umma_desc_sw128(a_base + j * 32);
@@ -194,48 +228,50 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                            (i | j) != 0);
           }
         }
+        }
         mb::tc_commit(&empty_bar[s]);
         if constexpr (KIND == KIND_FP8_BLOCK) mb::tc_commit(&acc_full[i & 1]);
       }
       if constexpr (KIND != KIND_FP8_BLOCK) mb::tc_commit(&acc_full[0]);
+      MB_STAMP(4);
     }
   } else {
     // ------------------------------------------------------------ epilogue
+    // (a) TMEM -> registers -> fp32 staging tile [m][n] in the (by then idle) pipeline
+    //     buffers, or -> the split-K workspace; (b) barrier; (c) all 128 threads walk the
+    //     tile row by row with 16-byte accesses: scales, SwiGLU, residual, store.
     const int q = warp & 3;
     const int lane = threadIdx.x & 31;
-    const int n = tile_n * kTileN + q * 32 + lane;
-    const int m0 = tile_m * TN;
+    const int et = threadIdx.x - 64;                       // 0..127
+    const int m0 = m_row0;
     const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+    float* s_tile = reinterpret_cast<float*>(smem);
     bool ok = true;
-
-    auto finish = [&](float* v, int c) {
-      // v[j] = accumulator for (n, m0 + c*16 + j), all splits summed, block scales applied
+    const bool swiglu = p.epilogue == EPI_SWIGLU;
+    // per-token scales of this tile, staged while the main loop runs
+    for (int j = et; j < TN; j += 128) {
+      float sc = 1.f;
+      if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
+        if (p.a_scale && m0 + j < m_end) sc = __ldg(&p.a_scale[m0 + j]);
+      }
+      s_ascale[j] = sc;
+    }
+    // this thread's fixed column group in phase (c): 8 columns (16 with SwiGLU)
+    const int cpt = swiglu ? 16 : 8;
+    const int tpr = kTileN / cpt;                          // threads per row
+    const int col0 = (et % tpr) * cpt;
+    float wcol[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
       float wsc = p.alpha;
       if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
-        if (p.w_scale && n < p.N) wsc *= p.w_scale[n];
+        const int n = tile_n * kTileN + col0 + i;
+        if (i < cpt && p.w_scale && n < n_limit) wsc *= __ldg(&p.w_scale[(size_t)expert * p.n_per_expert + n]);
       }
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int m = m0 + c * 16 + j;
-        float val = v[j] * wsc;
-        if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
-          if (p.a_scale && m < p.M) val *= p.a_scale[m];
-        }
-        if (p.epilogue == EPI_SWIGLU) {
-          const float other = __shfl_xor_sync(0xffffffffu, val, 1);
-          if (!(lane & 1) && m < p.M && n < p.N) {
-            const float r = mb::silu(val) * other;
-            reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] =
-                __float2bfloat16(r);
-          }
-        } else if (m < p.M && n < p.N) {
-          const size_t o = (size_t)m * p.ldo + n;
-          if (p.residual) val += __bfloat162float(p.residual[o]);
-          if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = val;
-          else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16(val);
-        }
-      }
-    };
+      wcol[i] = wsc;
+    }
+    const size_t tile_lin = (size_t)tile_m * gridDim.x + tile_n;
+    float* wsp = p.splits > 1 ? p.ws + (tile_lin * p.splits + split) * (size_t)(TN * kTileN) : s_tile;
 
     if constexpr (KIND == KIND_FP8_BLOCK) {
       float accr[TN];
@@ -249,57 +285,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!ok) break;
         mb::tc_fence_after();
         const int kb = kb0 + i;
-        const float wsc = p.w_scale[(size_t)tile_n * kgroups + kb];
+        const float wsc = __ldg(&p.w_scale[((size_t)expert * (p.n_per_expert / kTileN) + tile_n) * kgroups + kb]);
         const float* as = p.a_scale + (size_t)kb * p.a_ld + m0;
 #pragma unroll
         for (int c = 0; c < TN / 16; ++c) {
           float v[16];
           mb::tmem_ld16(lane_addr + buf * TN + c * 16, v);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) accr[c * 16 + j] += v[j] * (wsc * as[c * 16 + j]);
+          for (int j = 0; j < 16; ++j) accr[c * 16 + j] += v[j] * (wsc * __ldg(&as[c * 16 + j]));
         }
         mb::tc_fence_before();
         mb::mbar_arrive(&acc_empty[buf]);
       }
+      if (threadIdx.x == 64) MB_STAMP(5);
+      // the last k block's MMAs are complete (acc_full observed), so the stage buffers are idle
       if (ok) {
-        if (p.splits == 1) {
 #pragma unroll
-          for (int c = 0; c < TN / 16; ++c) finish(&accr[c * 16], c);
-        } else {
-          const size_t tile_lin = (size_t)tile_m * gridDim.x + tile_n;
-          float* wsp = p.ws + (tile_lin * p.splits + split) * (size_t)(TN * kTileN);
-#pragma unroll
-          for (int j = 0; j < TN; ++j) wsp[j * kTileN + q * 32 + lane] = accr[j];
-        }
+        for (int j = 0; j < TN; ++j) wsp[j * kTileN + q * 32 + lane] = accr[j];
       }
     } else {
       ok = mb::mbar_wait(&acc_full[0], 0, p.status, MB_ST_TIMEOUT_EPI);
+      if (threadIdx.x == 64) MB_STAMP(5);
       if (ok) {
         mb::tc_fence_after();
-        if (p.splits == 1) {
-#pragma unroll 1
-          for (int c = 0; c < TN / 16; ++c) {
-            float v[16];
-            mb::tmem_ld16(lane_addr + c * 16, v);
-            finish(v, c);
-          }
-        } else {
-          const size_t tile_lin = (size_t)tile_m * gridDim.x + tile_n;
-          float* wsp = p.ws + (tile_lin * p.splits + split) * (size_t)(TN * kTileN);
-#pragma unroll 1
-          for (int c = 0; c < TN / 16; ++c) {
-            float v[16];
-            mb::tmem_ld16(lane_addr + c * 16, v);
+#pragma unroll 2
+        for (int c = 0; c < TN / 16; ++c) {
+          float v[16];
+          mb::tmem_ld16(lane_addr + c * 16, v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) wsp[(c * 16 + j) * kTileN + q * 32 + lane] = v[j];
-          }
+          for (int j = 0; j < 16; ++j) wsp[(c * 16 + j) * kTileN + q * 32 + lane] = v[j];
         }
       }
     }
+    int nsrc = 1;                                          // tiles to sum in phase (c)
+    const float* src = s_tile;
+    bool do_store = ok;
     if (p.splits > 1) {
-      // last-arriver reduction, summed in split order so the result does not
-      // depend on which CTA finishes last
-      const size_t tile_lin = (size_t)tile_m * gridDim.x + tile_n;
+      // last-arriver reduction, summed in split order so the result does not depend on
+      // which CTA finishes last
       __threadfence();
       epi_bar_sync();
       if (threadIdx.x == 64) {
@@ -309,27 +332,86 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         is_last_s = last;
       }
       epi_bar_sync();
-      if (is_last_s && ok) {
-        __threadfence();
-        const float* base = p.ws + tile_lin * p.splits * (size_t)(TN * kTileN);
-#pragma unroll 1
-        for (int c = 0; c < TN / 16; ++c) {
-          float v[16];
+      do_store = do_store && is_last_s;
+      if (do_store) __threadfence();
+      nsrc = p.splits;
+      src = p.ws + tile_lin * p.splits * (size_t)(TN * kTileN);
+    } else {
+      epi_bar_sync();
+    }
+    if (do_store && !(p.dbg & 2)) {
+      const int rpp = 128 / tpr;                           // rows per pass
+      const int n_out0 = swiglu ? (tile_n * kTileN + col0) / 2 : tile_n * kTileN + col0;
+      const int n_out_limit = swiglu ? n_limit / 2 : n_limit;
+      const bool vec_ok = (p.ldo % 8 == 0) && (n_out0 + 8 <= n_out_limit) &&
+                          ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.residual)) & 15) == 0;
+#pragma unroll 2
+      for (int mr = et / tpr; mr < TN; mr += rpp) {
+        const int m = m0 + mr;
+        if (m >= m_end) break;
+        float x[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          for (int s = 0; s < p.splits; ++s) {
-            const float* wsp = base + (size_t)s * (TN * kTileN);
+        for (int i = 0; i < 16; ++i) x[i] = 0.f;
+        for (int s = 0; s < nsrc; ++s) {
+          const float* row = src + (size_t)s * (TN * kTileN) + mr * kTileN + col0;
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              v[j] += __ldcg(&wsp[(c * 16 + j) * kTileN + q * 32 + lane]);
+          for (int i4 = 0; i4 < 4; ++i4) {
+            if (i4 * 4 < cpt) {
+              const float4 f = nsrc > 1 ? __ldcg(reinterpret_cast<const float4*>(row) + i4)
+                                        : *(reinterpret_cast<const float4*>(row) + i4);
+              x[i4 * 4] += f.x; x[i4 * 4 + 1] += f.y; x[i4 * 4 + 2] += f.z; x[i4 * 4 + 3] += f.w;
+            }
           }
-          finish(v, c);
+        }
+        const float as = s_ascale[mr];
+        float y[8];
+        if (swiglu) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) y[i] = mb::silu(x[2 * i] * wcol[2 * i] * as) * (x[2 * i + 1] * wcol[2 * i + 1] * as);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) y[i] = x[i] * wcol[i] * as;
+        }
+        const size_t o = (size_t)m * p.ldo + n_out0;
+        if (vec_ok) {
+          if (p.residual) {
+            const uint4 r = __ldg(reinterpret_cast<const uint4*>(p.residual + o));
+            const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(rb[i]);
+              y[2 * i] += f.x; y[2 * i + 1] += f.y;
+            }
+          }
+          if (p.out_f32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
+            dst[0] = make_float4(y[0], y[1], y[2], y[3]);
+            dst[1] = make_float4(y[4], y[5], y[6], y[7]);
+          } else {
+            uint4 pk;
+            __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pb[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (n_out0 + i < n_out_limit) {
+              float val = y[i];
+              if (p.residual) val += __bfloat162float(p.residual[o + i]);
+              if (p.out_f32) reinterpret_cast<float*>(p.out)[o + i] = val;
+              else reinterpret_cast<__nv_bfloat16*>(p.out)[o + i] = __float2bfloat16(val);
+            }
+          }
         }
       }
     }
+    if (threadIdx.x == 64) MB_STAMP(6);
     mb::tc_fence_before();
   }
   __syncthreads();
+  if (threadIdx.x == 0) MB_STAMP(7);
   if (warp == 1) {
     mb::tc_fence_after();
     mb::tmem_dealloc(tmem, C::kTmemCols);
@@ -394,6 +476,12 @@ struct MbGemmArgs {
   size_t ws_bytes;
   uint32_t* status;
   int force_tn, force_splits, sm_count;
+  int dbg;
+  long long* trace;
+  const int* tile_expert;   // grouped mode (all four set together)
+  const int* tile_row0;
+  const int* tile_nrows;
+  int n_per_expert, max_tiles;
 };
 
 int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
@@ -423,9 +511,17 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
     while (tn < a->M && tn < tn_cap) tn <<= 1;
   }
   if (kind == KIND_FP8_BLOCK && tn > 64) tn = 64;       // register-resident promotion
-  const int tiles_n = (a->N + kTileN - 1) / kTileN;
-  const int tiles_m = (a->M + tn - 1) / tn;
-  if (kind == KIND_FP8_BLOCK && a->a_ld < tiles_m * tn) return MB_ERR_BAD_ARG;
+  const bool grouped = a->tile_expert != nullptr;
+  if (grouped) {
+    if (!a->tile_row0 || !a->tile_nrows || a->n_per_expert <= 0 || a->n_per_expert % kTileN ||
+        a->max_tiles <= 0 || kind == KIND_NVFP4)
+      return MB_ERR_UNSUPPORTED;
+    if (tn > 64) tn = 64;
+  }
+  const int tiles_n = grouped ? a->n_per_expert / kTileN : (a->N + kTileN - 1) / kTileN;
+  const int tiles_m = grouped ? a->max_tiles : (a->M + tn - 1) / tn;
+  if (kind == KIND_FP8_BLOCK && !grouped && a->a_ld < tiles_m * tn) return MB_ERR_BAD_ARG;
+  if (kind == KIND_FP8_BLOCK && grouped && a->a_ld < a->M + tn) return MB_ERR_BAD_ARG;
   // scale-factor tiles are 128 rows: several token tiles only line up at TN = 128
   if (kind == KIND_NVFP4 && tiles_m > 1 && tn != 128) return MB_ERR_BAD_ARG;
   const int tiles = tiles_n * tiles_m;
@@ -456,6 +552,10 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   p.splits = splits; p.kb_per_split = kb_per; p.num_kb = num_kb;
   p.epilogue = a->epilogue; p.out_f32 = a->out_f32;
   p.status = a->status;
+  p.dbg = a->dbg;
+  p.trace = a->trace;
+  p.tile_expert = a->tile_expert; p.tile_row0 = a->tile_row0; p.tile_nrows = a->tile_nrows;
+  p.n_per_expert = grouped ? a->n_per_expert : 0;
   if (splits > 1) {
     const size_t cbytes = mb_gemm_counter_bytes();
     const size_t need = cbytes + (size_t)tiles * splits * tn * kTileN * sizeof(float);

@@ -1,0 +1,287 @@
+// Mixture-of-experts support kernels (the expert FFN itself is the grouped mode of the
+// tcgen05 GEMM in gemm_tcgen05.cu).
+//
+//   mb_moe_route    one warp per token over <= 512 expert logits: softmax top-k, or sigmoid
+//                   scores + selection bias with group-limited selection (keep the
+//                   `topk_group` groups with the largest sum of their two best biased scores,
+//                   then top-k inside them). Ties resolve to the lower expert id. Weights are
+//                   the un-biased scores, optionally sum-normalised and scaled.
+//   mb_moe_sort     counting sort of the (token, slot) pairs by *local* expert: per-expert row
+//                   ranges, the pair -> row map, and a tile work-list of (expert, first row,
+//                   rows) entries for the grouped GEMM. Pairs routed to experts outside
+//                   [expert_lo, expert_lo + num_local) are dropped (expert parallelism).
+//   mb_moe_gather   expert-sorted copy of activation rows (+ per-row / per-group scales).
+//   mb_moe_combine  out[t] = sum_j w[t, j] * y[row(t, j)] (+ optional addend), fp32 math.
+//
+// Reference behaviour covered: kernels/gb10/common/moe_topk.cu, moe_topk_sigmoid.cu (no
+// group limit there), moe_permute.cu (sort_by_expert, build_tile_worklist, permute_tokens,
+// unpermute_reduce), moe_unpermute_blend.cu.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxPerLane = 16;  // 512 experts / 32 lanes
+
+__global__ void __launch_bounds__(128)
+route_kernel(const float* __restrict__ logits, long long ld, int T, int E, int K, int mode,
+             const float* __restrict__ bias, int n_group, int topk_group, int renorm, float scaling,
+             float* __restrict__ out_w, int* __restrict__ out_id) {
+  const int tok = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (tok >= T) return;
+  const float* x = logits + (size_t)tok * ld;
+  float score[kMaxPerLane], sel[kMaxPerLane];
+  const int per = (E + 31) / 32;
+  // expert e = j * 32 + lane (interleaved so warp reductions see a whole 32-expert stripe)
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kMaxPerLane; ++j) {
+    const int e = j * 32 + lane;
+    score[j] = (j < per && e < E) ? x[e] : -INFINITY;
+    mx = fmaxf(mx, score[j]);
+  }
+  if (mode == 0) {  // softmax
+    mx = mb::warp_max(mx);
+    float se = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      score[j] = score[j] == -INFINITY ? 0.f : __expf(score[j] - mx);
+      se += score[j];
+    }
+    se = mb::warp_sum(se);
+    const float inv = 1.f / se;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = j * 32 + lane;
+      score[j] *= inv;
+      sel[j] = (j < per && e < E) ? score[j] : -INFINITY;
+    }
+  } else {          // sigmoid + selection bias
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = j * 32 + lane;
+      const bool ok = j < per && e < E;
+      score[j] = ok ? 1.f / (1.f + __expf(-score[j])) : 0.f;
+      sel[j] = ok ? score[j] + (bias ? bias[e] : 0.f) : -INFINITY;
+    }
+    if (n_group > 1) {
+      // group g owns experts [g * gs, (g + 1) * gs); score = sum of its two best sel values
+      const int gs = E / n_group;
+      float gscore_mine = -INFINITY;  // lane g (< n_group) keeps group g's score
+      for (int g = 0; g < n_group; ++g) {
+        float b1 = -INFINITY, b2 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; ++j) {
+          const int e = j * 32 + lane;
+          if (j < per && e >= g * gs && e < (g + 1) * gs) {
+            const float v = sel[j];
+            if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) { b2 = v; }
+          }
+        }
+        // merge (b1, b2) pairs across lanes
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float o1 = __shfl_xor_sync(0xffffffffu, b1, o), o2 = __shfl_xor_sync(0xffffffffu, b2, o);
+          const float n1 = fmaxf(b1, o1);
+          const float n2 = fmaxf(fminf(b1, o1), fmaxf(b2, o2));
+          b1 = n1; b2 = n2;
+        }
+        if (lane == g) gscore_mine = b1 + b2;
+      }
+      // pick topk_group groups (ties -> lower group id); keep-mask as a bit set
+      uint32_t keep = 0;
+      for (int r = 0; r < topk_group; ++r) {
+        float v = (lane < n_group && !((keep >> lane) & 1)) ? gscore_mine : -INFINITY;
+        int idx = lane;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+          if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+        }
+        keep |= 1u << idx;
+      }
+#pragma unroll
+      for (int j = 0; j < kMaxPerLane; ++j) {
+        const int e = j * 32 + lane;
+        if (j < per && e < E && !((keep >> (e / gs)) & 1)) sel[j] = -INFINITY;
+      }
+    }
+  }
+  // iterative top-k over sel; weights come from score
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_id = 0;
+  for (int r = 0; r < K; ++r) {
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = j * 32 + lane;
+      if (j < per && e < E && (sel[j] > v || (sel[j] == v && e < idx))) { v = sel[j]; idx = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    // owner lane reports the weight and retires the expert
+    float w = 0.f;
+    if ((idx & 31) == lane) {
+      const int j = idx >> 5;
+#pragma unroll
+      for (int jj = 0; jj < kMaxPerLane; ++jj)
+        if (jj == j) { w = score[jj]; sel[jj] = -INFINITY; }
+    }
+    w = __shfl_sync(0xffffffffu, w, idx & 31);
+    wsum += w;
+    if (lane == r) { my_w = w; my_id = idx; }
+  }
+  if (lane < K) {
+    float w = my_w;
+    if (renorm) w = w / (wsum + (mode == 0 ? 0.f : 1e-20f));
+    out_w[(size_t)tok * K + lane] = w * scaling;
+    out_id[(size_t)tok * K + lane] = my_id;
+  }
+}
+
+// ------------------------------------------------------------------ sort (single CTA)
+// pairs = T * K. counts/offsets in shared memory; stable order is not required (rows of one
+// expert are independent), determinism is: positions are assigned by pair index order.
+__global__ void __launch_bounds__(1024)
+sort_kernel(const int* __restrict__ ids, int pairs, int expert_lo, int num_local, int tile_rows,
+            int* __restrict__ pair_row, int* __restrict__ row_pair, int* __restrict__ expert_off,
+            int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ tile_nrows,
+            int max_tiles, int* __restrict__ total_rows) {
+  extern __shared__ int sm_i[];
+  int* cnt = sm_i;                       // [num_local]
+  int* off = sm_i + num_local;           // [num_local + 1]
+  const int tid = threadIdx.x, nt = blockDim.x;
+  for (int e = tid; e < num_local; e += nt) cnt[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < pairs; i += nt) {
+    const int e = ids[i] - expert_lo;
+    if (e >= 0 && e < num_local) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int acc = 0, tiles = 0;
+    for (int e = 0; e < num_local; ++e) {
+      off[e] = acc;
+      const int c = cnt[e];
+      for (int r = 0; r < c && tiles < max_tiles; r += tile_rows) {
+        tile_expert[tiles] = e;
+        tile_row0[tiles] = acc + r;
+        tile_nrows[tiles] = min(tile_rows, c - r);
+        ++tiles;
+      }
+      acc += c;
+    }
+    off[num_local] = acc;
+    for (int i = tiles; i < max_tiles; ++i) { tile_expert[i] = -1; tile_row0[i] = 0; tile_nrows[i] = 0; }
+    *total_rows = acc;
+  }
+  __syncthreads();
+  for (int e = tid; e <= num_local; e += nt) expert_off[e] = off[e];
+  // deterministic placement: each expert's pairs keep their pair-index order. One thread per
+  // expert walks the pair list (pairs <= a few thousand at decode; prefill uses more CTAs of
+  // the same kernel on token ranges through the host wrapper).
+  for (int e = tid; e < num_local; e += nt) {
+    int pos = off[e];
+    if (cnt[e] == 0) continue;
+    for (int i = 0; i < pairs; ++i) {
+      if (ids[i] - expert_lo == e) {
+        pair_row[i] = pos;
+        row_pair[pos] = i;
+        ++pos;
+      }
+    }
+  }
+  for (int i = tid; i < pairs; i += nt) {
+    const int e = ids[i] - expert_lo;
+    if (e < 0 || e >= num_local) pair_row[i] = -1;
+  }
+}
+
+// ------------------------------------------------------------------ gather / combine
+// dst row r = src row (row_pair[r] / K); 16-byte vectors; rows beyond *total_rows are skipped.
+__global__ void gather_kernel(const uint8_t* __restrict__ src, long long src_ld, uint8_t* __restrict__ dst,
+                              long long dst_ld, int row_bytes, const int* __restrict__ row_pair, int K,
+                              const int* __restrict__ total_rows, int max_rows,
+                              const float* __restrict__ src_scale, float* __restrict__ dst_scale,
+                              int scale_groups, int src_scale_ld, int dst_scale_ld) {
+  const int r = blockIdx.x;
+  if (r >= *total_rows || r >= max_rows) return;
+  const int tok = row_pair[r] / K;
+  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)tok * src_ld);
+  uint4* d = reinterpret_cast<uint4*>(dst + (size_t)r * dst_ld);
+  for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) d[i] = s[i];
+  if (src_scale) {
+    // scales stored [group][row]
+    for (int gI = threadIdx.x; gI < scale_groups; gI += blockDim.x)
+      dst_scale[(size_t)gI * dst_scale_ld + r] = src_scale[(size_t)gI * src_scale_ld + tok];
+  }
+}
+
+__global__ void combine_kernel(const float* __restrict__ y, long long y_ld, const int* __restrict__ pair_row,
+                               const float* __restrict__ w, int K, int H, const float* __restrict__ addend,
+                               float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16) {
+  const int tok = blockIdx.x;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float acc = addend ? addend[(size_t)tok * H + h] : 0.f;
+    for (int j = 0; j < K; ++j) {
+      const int r = pair_row[(size_t)tok * K + j];
+      if (r >= 0) acc += w[(size_t)tok * K + j] * y[(size_t)r * y_ld + h];
+    }
+    if (out_f32) out_f32[(size_t)tok * H + h] = acc;
+    if (out_bf16) out_bf16[(size_t)tok * H + h] = __float2bfloat16(acc);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int mb_moe_route(const float* logits, long long ld, int T, int E, int K, int mode, const float* bias,
+                 int n_group, int topk_group, int renorm, float scaling, float* out_w, int* out_id,
+                 cudaStream_t stream) {
+  if (!logits || !out_w || !out_id || T <= 0 || E <= 0 || E > 512 || K <= 0 || K > 32 || K > E)
+    return MB_ERR_BAD_ARG;
+  if (n_group > 1 && (E % n_group || n_group > 32 || topk_group > n_group)) return MB_ERR_BAD_ARG;
+  route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(logits, ld, T, E, K, mode, bias, n_group, topk_group,
+                                               renorm, scaling, out_w, out_id);
+  return (int)cudaGetLastError();
+}
+
+int mb_moe_sort(const int* ids, int pairs, int expert_lo, int num_local, int tile_rows, int* pair_row,
+                int* row_pair, int* expert_off, int* tile_expert, int* tile_row0, int* tile_nrows,
+                int max_tiles, int* total_rows, cudaStream_t stream) {
+  if (!ids || pairs <= 0 || num_local <= 0 || num_local > 1024 || tile_rows <= 0) return MB_ERR_BAD_ARG;
+  const size_t smem = (2 * (size_t)num_local + 1) * sizeof(int);
+  sort_kernel<<<1, 1024, smem, stream>>>(ids, pairs, expert_lo, num_local, tile_rows, pair_row, row_pair,
+                                         expert_off, tile_expert, tile_row0, tile_nrows, max_tiles, total_rows);
+  return (int)cudaGetLastError();
+}
+
+int mb_moe_gather(const void* src, long long src_ld, void* dst, long long dst_ld, int row_bytes,
+                  const int* row_pair, int K, const int* total_rows, int max_rows, const float* src_scale,
+                  float* dst_scale, int scale_groups, int src_scale_ld, int dst_scale_ld,
+                  cudaStream_t stream) {
+  if (!src || !dst || row_bytes % 16 || max_rows <= 0) return MB_ERR_BAD_ARG;
+  gather_kernel<<<max_rows, 128, 0, stream>>>(reinterpret_cast<const uint8_t*>(src), src_ld,
+                                              reinterpret_cast<uint8_t*>(dst), dst_ld, row_bytes, row_pair, K,
+                                              total_rows, max_rows, src_scale, dst_scale, scale_groups,
+                                              src_scale_ld, dst_scale_ld);
+  return (int)cudaGetLastError();
+}
+
+int mb_moe_combine(const float* y, long long y_ld, const int* pair_row, const float* w, int T, int K, int H,
+                   const float* addend, float* out_f32, void* out_bf16, cudaStream_t stream) {
+  if (!y || !pair_row || !w || T <= 0) return MB_ERR_BAD_ARG;
+  combine_kernel<<<T, 256, 0, stream>>>(y, y_ld, pair_row, w, K, H, addend, out_f32,
+                                        reinterpret_cast<__nv_bfloat16*>(out_bf16));
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

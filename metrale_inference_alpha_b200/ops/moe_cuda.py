@@ -1,0 +1,116 @@
+"""CUDA path of the MoE ops: device routing, expert sort + tile work-list, gathered
+activations, grouped tcgen05 GEMMs, weighted combine. No host synchronisation anywhere, so a
+MoE layer can sit inside a CUDA graph."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import Act, ACT_FOR_WEIGHT, IN_RELU2, IN_SILU_MUL, _count, _native, _ptr, _stream, linear, row_op
+
+c = C
+_native.register_optional("mb_moe_route", [c.c_void_p, c.c_longlong, c.c_int, c.c_int, c.c_int, c.c_int, c.c_void_p,
+                                          c.c_int, c.c_int, c.c_int, c.c_float, c.c_void_p, c.c_void_p, c.c_void_p])
+_native.register_optional("mb_moe_sort", [c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int] + [c.c_void_p] * 6 +
+                          [c.c_int, c.c_void_p, c.c_void_p])
+_native.register_optional("mb_moe_gather", [c.c_void_p, c.c_longlong, c.c_void_p, c.c_longlong, c.c_int, c.c_void_p,
+                                           c.c_int, c.c_void_p, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int,
+                                           c.c_int, c.c_void_p])
+_native.register_optional("mb_moe_combine", [c.c_void_p, c.c_longlong, c.c_void_p, c.c_void_p, c.c_int, c.c_int,
+                                            c.c_int, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p])
+
+
+def route_cuda(logits: torch.Tensor, cfg, bias=None):
+    T, E = logits.shape
+    K = cfg.experts_per_token
+    w = torch.empty(T, K, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(T, K, dtype=torch.int32, device=logits.device)
+    mode = 0 if cfg.router == "softmax" else 1
+    rc = _native.lib().mb_moe_route(_ptr(logits), logits.stride(0), T, E, K, mode, _ptr(bias),
+                                    cfg.router_n_group if mode else 1, cfg.router_topk_group if mode else 1,
+                                    int(cfg.router_renormalize), float(cfg.router_scaling if mode else 1.0),
+                                    _ptr(w), _ptr(idx), _stream())
+    _native.check(rc, "moe_route")
+    _count()
+    return w, idx
+
+
+class SortedPairs:
+    """Device-side result of sorting (token, slot) pairs by local expert."""
+
+    def __init__(self, idx: torch.Tensor, expert_lo: int, num_local: int, tile_rows: int):
+        dev = idx.device
+        T, K = idx.shape
+        self.T, self.K, self.pairs = T, K, T * K
+        self.tile_rows = tile_rows
+        self.max_tiles = (self.pairs + tile_rows - 1) // tile_rows + num_local
+        i32 = lambda n: torch.empty(n, dtype=torch.int32, device=dev)
+        self.pair_row, self.row_pair = i32(self.pairs), i32(self.pairs)
+        self.expert_off = i32(num_local + 1)
+        self.tile_expert, self.tile_row0, self.tile_nrows = i32(self.max_tiles), i32(self.max_tiles), i32(self.max_tiles)
+        self.total_rows = i32(1)
+        rc = _native.lib().mb_moe_sort(_ptr(idx), self.pairs, expert_lo, num_local, tile_rows, _ptr(self.pair_row),
+                                       _ptr(self.row_pair), _ptr(self.expert_off), _ptr(self.tile_expert),
+                                       _ptr(self.tile_row0), _ptr(self.tile_nrows), self.max_tiles,
+                                       _ptr(self.total_rows), _stream())
+        _native.check(rc, "moe_sort")
+        _count()
+
+
+def gather_act(a: Act, sp: SortedPairs) -> Act:
+    """Expert-sorted copy of the activation rows (and their scales)."""
+    dev = a.data.device
+    rows = sp.pairs
+    alloc = rows + 64                                   # the last tile may read past the end
+    row_bytes = a.data.shape[1] * a.data.element_size()
+    out = Act(a.fmt, rows, a.K, torch.empty(alloc, a.data.shape[1], dtype=a.data.dtype, device=dev))
+    src_scale = dst_scale = None
+    groups = s_ld = d_ld = 0
+    if a.fmt == "fp8_g128":
+        groups, s_ld, d_ld = a.scale.shape[0], a.scale.stride(0), alloc
+        out.scale = torch.ones(groups, alloc, dtype=torch.float32, device=dev)
+        src_scale, dst_scale = a.scale, out.scale
+    elif a.fmt == "fp8_row":
+        groups, s_ld, d_ld = 1, a.scale.numel(), alloc
+        out.scale = torch.ones(alloc, dtype=torch.float32, device=dev)
+        src_scale, dst_scale = a.scale, out.scale
+    elif a.fmt == "nvfp4":
+        raise NotImplementedError("grouped NVFP4 experts need 128-row aligned scale-factor tiles")
+    rc = _native.lib().mb_moe_gather(_ptr(a.data), a.data.stride(0) * a.data.element_size(), _ptr(out.data),
+                                     out.data.stride(0) * out.data.element_size(), row_bytes, _ptr(sp.row_pair),
+                                     sp.K, _ptr(sp.total_rows), rows, _ptr(src_scale), _ptr(dst_scale), groups,
+                                     s_ld, d_ld, _stream())
+    _native.check(rc, "moe_gather")
+    _count(2 if src_scale is not None else 1)
+    return out
+
+
+def grouped_ffn(cfg, a: Act, weights: torch.Tensor, idx: torch.Tensor, w) -> torch.Tensor:
+    """Routed experts for all tokens: fp32 [T, hidden] = sum_j weight_j * expert_j(x)."""
+    ge = w.grouped
+    T = a.M
+    per_expert = max(1, (T * cfg.experts_per_token) // max(1, ge.num))
+    tile_rows = 16 if per_expert <= 16 else (32 if per_expert <= 32 else 64)
+    sp = SortedPairs(idx, w.expert_lo, ge.num, tile_rows)
+    xa = gather_act(a, sp)
+    g = lambda n: (sp.tile_expert, sp.tile_row0, sp.tile_nrows, n, sp.max_tiles, tile_rows)
+    fmt_d = ACT_FOR_WEIGHT[ge.down.fmt]
+    if cfg.ffn_act == "relu2":
+        h = row_op(linear(xa, ge.gate_up, grouped=g(ge.n_gate_up)), fmt_d, IN_RELU2)[0]
+    elif ge.interleaved:
+        act = linear(xa, ge.gate_up, swiglu=True, grouped=g(ge.n_gate_up))
+        h = row_op(act, fmt_d)[0]
+    else:
+        h = row_op(linear(xa, ge.gate_up, grouped=g(ge.n_gate_up)), fmt_d, IN_SILU_MUL)[0]
+    if h.fmt == "fp8_g128" and h.scale.shape[1] < h.M + 64:
+        pad = torch.ones(h.scale.shape[0], h.M + 64, dtype=torch.float32, device=h.scale.device)
+        pad[:, :h.scale.shape[1]] = h.scale
+        h.scale = pad
+    y = linear(h, ge.down, out_f32=True, grouped=g(ge.n_down))
+    out = torch.empty(T, ge.n_down, dtype=torch.float32, device=y.device)
+    rc = _native.lib().mb_moe_combine(_ptr(y), y.stride(0), _ptr(sp.pair_row), _ptr(weights), T, sp.K, ge.n_down,
+                                      None, _ptr(out), None, _stream())
+    _native.check(rc, "moe_combine")
+    _count()
+    return out

@@ -90,3 +90,57 @@ def mamba2_scan(xbc, dt, A_log, D, dt_bias, ssm_state, batch, *, heads, groups, 
             out[t] = y.reshape(-1)
         ssm_state[slots[s]] = h[0]
     return out
+
+
+# ----------------------------------------------------------------------------- CUDA launchers
+_c = C
+_native.register_optional("mb_causal_conv1d", [_c.c_void_p, _c.c_longlong, _c.c_int, _c.c_int, _c.c_void_p,
+                                              _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                              _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
+                                              _c.c_void_p, _c.c_void_p])
+_native.register_optional("mb_gdn_recurrence", [_c.c_void_p] * 6 + [_c.c_int] * 4 + [_c.c_void_p] * 4 +
+                          [_c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p])
+_native.register_optional("mb_mamba2_scan", [_c.c_void_p, _c.c_void_p, _c.c_longlong] + [_c.c_void_p] * 5 +
+                          [_c.c_int] * 4 + [_c.c_void_p] * 4 + [_c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p])
+
+
+def _status(dev):
+    from . import runtime
+    return runtime(dev).status
+
+
+def _conv_cuda(x, channels, w, bias, state, batch, activation):
+    T = x.shape[0]
+    out = torch.empty(T, channels, dtype=torch.float32, device=x.device)
+    rc = _native.lib().mb_causal_conv1d(
+        _ptr(x), x.stride(0), channels, w.shape[1], _ptr(w), _ptr(bias), _ptr(state), _ptr(out),
+        _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions), _ptr(batch.state_slots),
+        batch.q_len.numel(), state.shape[0], int(activation), _ptr(_status(x.device)), _stream())
+    _native.check(rc, "causal_conv1d")
+    _count()
+    return out
+
+
+def _gdn_cuda(conv_out, ba, A_log, dt_bias, state, batch, k_heads, v_heads, k_dim, v_dim):
+    T = conv_out.shape[0]
+    out = torch.empty(T, v_heads * v_dim, dtype=torch.float32, device=conv_out.device)
+    rc = _native.lib().mb_gdn_recurrence(
+        _ptr(conv_out), _ptr(ba), _ptr(A_log), _ptr(dt_bias), _ptr(state), _ptr(out), k_heads, v_heads,
+        k_dim, v_dim, _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions),
+        _ptr(batch.state_slots), batch.q_len.numel(), state.shape[0], _ptr(_status(conv_out.device)), _stream())
+    _native.check(rc, "gdn_recurrence")
+    _count()
+    return out
+
+
+def _mamba_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups, head_dim, state):
+    T = xbc.shape[0]
+    out = torch.empty(T, heads * head_dim, dtype=torch.float32, device=xbc.device)
+    assert dt.dtype == torch.bfloat16
+    rc = _native.lib().mb_mamba2_scan(
+        _ptr(xbc), _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(D), _ptr(dt_bias), _ptr(ssm_state), _ptr(out),
+        heads, groups, head_dim, state, _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions),
+        _ptr(batch.state_slots), batch.q_len.numel(), ssm_state.shape[0], _ptr(_status(xbc.device)), _stream())
+    _native.check(rc, "mamba2_scan")
+    _count()
+    return out

@@ -1,0 +1,135 @@
+"""Tensor-parallel execution context: how a rank combines partial results with its peers.
+
+``NcclTpContext`` is both the baseline (plain NCCL all-reduce / all-gather after the local
+GEMM, the reference's scheme: one bf16 all-reduce after o_proj, after the FFN / MoE output and
+on the vocab-parallel logits, ``crates/comm/src/nccl_backend.rs``) and the home of the fused
+paths: when ``fused`` is on, row-parallel projections run ``parallel.fused.gemm_allreduce``
+(GEMM whose epilogue reduces through NVLink peer memory / NVLS multimem), and the lm_head
+exchanges per-rank (max, argmax) pairs instead of all-reducing logits.
+
+Health: every collective is followed by an async-error check when ``check_health`` is set;
+a failed or timed-out collective poisons the context (all later calls raise) and the engine
+latches the fault (role of ``collective_wait.rs`` and ``NcclBackend::is_healthy``).
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..models.decoder import TpContext
+from ..ops import Act
+
+
+class CommPoisoned(RuntimeError):
+    pass
+
+
+class NcclTpContext(TpContext):
+    def __init__(self, rank: int, size: int, device, fused: bool = True, group=None,
+                 diagnostics: Optional[bool] = None):
+        self.rank, self.size = rank, size
+        self.device = torch.device(device)
+        self.group = group
+        self.fused = False
+        self.poisoned: Optional[str] = None
+        self.seq = 0
+        self.diagnostics = (os.environ.get("METRALE_COMM_DIAGNOSTICS") == "1") if diagnostics is None else diagnostics
+        self.bytes_reduced = 0
+        self.fused_impl = None
+        if fused and size > 1 and self.device.type == "cuda":
+            try:
+                from .fused import FusedCollectives
+                self.fused_impl = FusedCollectives(rank, size, self.device, group)
+                self.fused = True
+            except Exception as e:                      # symmetric memory unavailable: keep NCCL
+                if rank == 0:
+                    print(f"[tp] fused collectives unavailable ({type(e).__name__}: {e}); using NCCL", flush=True)
+
+    # ------------------------------------------------------------------ plumbing
+    def _pre(self, what: str, t: torch.Tensor) -> None:
+        if self.poisoned:
+            raise CommPoisoned(self.poisoned)
+        self.seq += 1
+        if self.diagnostics:
+            print(f"[comm r{self.rank}] #{self.seq} {what} {tuple(t.shape)} {t.dtype}", flush=True)
+
+    def poison(self, reason: str) -> None:
+        if not self.poisoned:
+            self.poisoned = reason
+
+    def is_healthy(self) -> bool:
+        return self.poisoned is None
+
+    # ------------------------------------------------------------------ collectives
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.size == 1:
+            return t
+        self._pre("all_reduce", t)
+        try:
+            dist.all_reduce(t, group=self.group)
+        except RuntimeError as e:
+            self.poison(f"all_reduce failed: {e}")
+            raise
+        self.bytes_reduced += t.numel() * t.element_size()
+        return t
+
+    def all_gather_last(self, t: torch.Tensor) -> torch.Tensor:
+        """Concatenate per-rank column shards (vocab-parallel logits)."""
+        if self.size == 1:
+            return t
+        self._pre("all_gather", t)
+        parts = [torch.empty_like(t) for _ in range(self.size)]
+        try:
+            dist.all_gather(parts, t.contiguous(), group=self.group)
+        except RuntimeError as e:
+            self.poison(f"all_gather failed: {e}")
+            raise
+        return torch.cat(parts, dim=-1)
+
+    def broadcast(self, t: torch.Tensor, root: int = 0) -> torch.Tensor:
+        if self.size > 1:
+            self._pre("broadcast", t)
+            dist.broadcast(t, root, group=self.group)
+        return t
+
+    def barrier(self) -> None:
+        if self.size > 1:
+            dist.barrier(group=self.group)
+
+    def linear_reduce(self, act: Act, w, residual=None) -> torch.Tensor:
+        """Row-parallel projection: sum of the ranks' partial products, plus the residual once."""
+        if self.size == 1:
+            return ops.linear(act, w, residual=residual)
+        if self.fused and act.data.is_cuda:
+            return self.fused_impl.gemm_allreduce(act, w, residual)
+        y = ops.linear(act, w, residual=residual if self.rank == 0 else None)
+        return self.all_reduce(y)
+
+
+class GlooTpContext(NcclTpContext):
+    """Same protocol over gloo for CPU ranks (multi-process tests of the host-side logic)."""
+
+    def __init__(self, rank: int, size: int, group=None):
+        super().__init__(rank, size, "cpu", fused=False, group=group)
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.size == 1:
+            return t
+        self._pre("all_reduce", t)
+        x = t.float() if t.dtype == torch.bfloat16 else t
+        dist.all_reduce(x, group=self.group)
+        if x is not t:
+            t.copy_(x.to(t.dtype))
+        return t
+
+    def all_gather_last(self, t: torch.Tensor) -> torch.Tensor:
+        if self.size == 1:
+            return t
+        x = t.float().contiguous() if t.dtype == torch.bfloat16 else t.contiguous()
+        parts = [torch.empty_like(x) for _ in range(self.size)]
+        dist.all_gather(parts, x, group=self.group)
+        return torch.cat(parts, dim=-1).to(t.dtype)

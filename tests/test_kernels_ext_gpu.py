@@ -1,0 +1,132 @@
+"""Recurrent-state and MoE kernels against their fp32 PyTorch references."""
+import pytest
+import torch
+
+from metrale_inference_alpha_b200 import ops
+from metrale_inference_alpha_b200.config.model_config import preset
+from metrale_inference_alpha_b200.engine.batch import ForwardBatch
+from metrale_inference_alpha_b200.ops import moe as moe_ops
+from metrale_inference_alpha_b200.ops import recurrent as rops
+from metrale_inference_alpha_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(got, want, rtol=2e-3, atol=2e-3):
+    got, want = got.float().cpu(), want.float().cpu()
+    err = (got - want).abs()
+    assert (err <= atol + rtol * want.abs()).all(), f"max err {err.max():.4g} (ref max {want.abs().max():.4g})"
+
+
+def _batch(dev):
+    # three sequences: fresh prefill (7 tokens), continuing decode (1 token at position 5), verify (3 at pos 9)
+    seqs = [dict(tokens=[1] * 7, start_pos=0, blocks=[1], state_slot=1),
+            dict(tokens=[2], start_pos=5, blocks=[2], state_slot=2),
+            dict(tokens=[3] * 3, start_pos=9, blocks=[3], state_slot=3)]
+    return ForwardBatch.build(seqs, 16, device=dev)
+
+
+def test_causal_conv1d_matches_reference():
+    g = torch.Generator().manual_seed(0)
+    C, taps, T = 200, 4, 11
+    x = torch.randn(T, C + 24, generator=g).to(torch.bfloat16)
+    w = torch.randn(C, taps, generator=g)
+    b = torch.randn(C, generator=g)
+    st = torch.randn(5, C, taps - 1, generator=g)
+    st_ref = st.clone()
+    want = rops.causal_conv1d(x, C, w, b, st_ref, _batch("cpu"))
+    st_dev = st.to(DEV)
+    got = rops.causal_conv1d(x.to(DEV), C, w.to(DEV), b.to(DEV), st_dev, _batch(DEV))
+    _close(got, want)
+    _close(st_dev, st_ref)
+
+
+@pytest.mark.parametrize("dk", [32, 128])
+def test_gdn_recurrence_matches_reference(dk):
+    g = torch.Generator().manual_seed(1)
+    kh, vh, T = 2, 4, 11
+    QK, V = kh * dk, vh * dk
+    conv = torch.randn(T, 2 * QK + V, generator=g)
+    ba = torch.randn(T, 2 * vh, generator=g)
+    A_log, dtb = torch.randn(vh, generator=g) * 0.3, torch.randn(vh, generator=g) * 0.1
+    st = torch.randn(5, vh, dk, dk, generator=g) * 0.1
+    st_ref = st.clone()
+    want = rops.gdn_recurrence(conv, ba, A_log, dtb, st_ref, _batch("cpu"), k_heads=kh, v_heads=vh, k_dim=dk, v_dim=dk)
+    st_dev = st.to(DEV)
+    got = rops.gdn_recurrence(conv.to(DEV), ba.to(DEV), A_log.to(DEV), dtb.to(DEV), st_dev, _batch(DEV),
+                              k_heads=kh, v_heads=vh, k_dim=dk, v_dim=dk)
+    _close(got, want, 5e-3, 5e-3)
+    _close(st_dev, st_ref, 5e-3, 5e-3)
+
+
+@pytest.mark.parametrize("N,P", [(16, 32), (128, 64)])
+def test_mamba2_scan_matches_reference(N, P):
+    g = torch.Generator().manual_seed(2)
+    H, G, T = 8, 2, 11
+    inner, GN = H * P, G * N
+    xbc = torch.randn(T, inner + 2 * GN, generator=g)
+    dt = torch.randn(T, H + 8, generator=g).to(torch.bfloat16)
+    A_log, D, dtb = torch.randn(H, generator=g) * 0.3, torch.randn(H, generator=g), torch.randn(H, generator=g) * 0.1
+    st = torch.randn(5, H, P, N, generator=g) * 0.1
+    st_ref = st.clone()
+    kw = dict(heads=H, groups=G, head_dim=P, state=N)
+    want = rops.mamba2_scan(xbc, dt[:, :H], A_log, D, dtb, st_ref, _batch("cpu"), **kw)
+    st_dev = st.to(DEV)
+    got = rops.mamba2_scan(xbc.to(DEV), dt.to(DEV)[:, :H], A_log.to(DEV), D.to(DEV), dtb.to(DEV), st_dev,
+                           _batch(DEV), **kw)
+    _close(got, want, 5e-3, 5e-3)
+    _close(st_dev, st_ref, 5e-3, 5e-3)
+
+
+def test_router_softmax_and_group_limited():
+    g = torch.Generator().manual_seed(3)
+    T, E = 37, 256
+    logits = torch.randn(T, E, generator=g)
+    cfg = preset("qwen-hybrid-moe-35b-fp8")
+    w_ref, i_ref = moe_ops.route(logits, cfg)
+    w, i = moe_ops.route(logits.to(DEV), cfg)
+    assert torch.equal(i.cpu(), i_ref)
+    _close(w, w_ref, 1e-4, 1e-6)
+    cfg = preset("deepseek-v3-671b-fp8")
+    bias = torch.randn(E, generator=g) * 0.1
+    w_ref, i_ref = moe_ops.route(logits, cfg, bias)
+    w, i = moe_ops.route(logits.to(DEV), cfg, bias.to(DEV))
+    assert torch.equal(i.cpu().sort(-1).values, i_ref.sort(-1).values)
+    _close(w.cpu().sort(-1).values, w_ref.sort(-1).values, 1e-4, 1e-6)
+
+
+@pytest.mark.parametrize("fmt", ["fp8_block", "fp8_row", "bf16"])
+def test_grouped_expert_ffn_matches_loop(fmt):
+    from metrale_inference_alpha_b200.models.decoder import Decoder
+    from metrale_inference_alpha_b200.models.moe import routed_experts
+    from metrale_inference_alpha_b200.weights.loader import FfnW, MoeW
+    g = torch.Generator().manual_seed(4)
+    T, H, I, E, K = 29, 256, 128, 8, 2
+    cfg = preset("qwen-hybrid-moe-35b-fp8", num_layers=1, hidden_size=H, num_experts=E, experts_per_token=K,
+                 moe_intermediate_size=I, weight_format=fmt, vocab_size=512)
+    experts = []
+    for e in range(E):
+        gate, up = torch.randn(I, H, generator=g) * 0.05, torch.randn(I, H, generator=g) * 0.05
+        down = torch.randn(H, I, generator=g) * 0.05
+        if fmt == "fp8_block":
+            gu, inter = ops.make_weight(torch.cat([gate, up]), fmt), False
+        else:
+            gu, inter = ops.make_weight(ops.interleave_gate_up(gate, up), fmt), True
+        experts.append(FfnW(gu, ops.make_weight(down, fmt), interleaved=inter))
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    wts = torch.rand(T, K, generator=g)
+
+    class _D:
+        pass
+    d = _D(); d.cfg = cfg
+    a_ref = ops.quantize_act(x, ops.ACT_FOR_WEIGHT[fmt])
+    want = routed_experts(d, a_ref, wts, idx, MoeW(experts=experts))
+    dev_experts = [FfnW(e.gate_up.to(DEV), e.down.to(DEV), e.interleaved) for e in experts]
+    mw = MoeW(experts=dev_experts, grouped=moe_ops.stack_experts(dev_experts))
+    a = ops.quantize_act(x.to(DEV), ops.ACT_FOR_WEIGHT[fmt])
+    got = routed_experts(d, a, wts.to(DEV), idx.to(DEV), mw)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    _close(got, want, 3e-2, 3e-2 * want.abs().max().item())
