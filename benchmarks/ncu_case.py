@@ -1,0 +1,67 @@
+#!/usr/bin/env python
+"""Runs one op a few times, eagerly, at the flagship decode shape: the target of
+`ncu --set full -k regex:<kernel> -c 3` captures (small case: a few hundred MB on the device).
+
+    python benchmarks/ncu_case.py --op attn   [--m 128 --ctx 640]
+    python benchmarks/ncu_case.py --op gemm   [--m 128 --n 5120 --k 17408 --fmt nvfp4]
+    python benchmarks/ncu_case.py --op rowop  [--m 128 --k 5120]
+"""
+import argparse
+import math
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from metrale_inference_alpha_b200 import ops  # noqa: E402
+from kernel_bench import rand_weight  # noqa: E402
+
+DEV = "cuda"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="attn")
+    ap.add_argument("--m", type=int, default=128)
+    ap.add_argument("--ctx", type=int, default=640)
+    ap.add_argument("--n", type=int, default=5120)
+    ap.add_argument("--k", type=int, default=17408)
+    ap.add_argument("--fmt", default="nvfp4")
+    ap.add_argument("--iters", type=int, default=6)
+    a = ap.parse_args()
+    M = a.m
+    if a.op == "attn":
+        Hq, Hkv, D, bs = 40, 8, 128, 16
+        nblk = (a.ctx + bs - 1) // bs
+        nb = M * nblk + 1
+        kc = torch.randint(0, 100, (nb, bs, Hkv, D), dtype=torch.uint8, device=DEV)
+        vc = torch.randint(0, 100, (nb, bs, Hkv, D), dtype=torch.uint8, device=DEV)
+        bt = torch.zeros(M, 128, dtype=torch.int32, device=DEV)
+        bt[:, :nblk] = (torch.arange(M * nblk, device=DEV, dtype=torch.int32) + 1).view(M, nblk)
+        q = torch.randn(M, Hq, D, device=DEV).to(torch.bfloat16)
+        qs = torch.arange(M, device=DEV, dtype=torch.int32)
+        ql = torch.ones(M, device=DEV, dtype=torch.int32)
+        cl = torch.full((M,), a.ctx, device=DEV, dtype=torch.int32)
+        sc = torch.tensor([0.05], device=DEV)
+        for _ in range(a.iters):
+            ops.paged_attention(q, kc, vc, bt, qs, ql, cl, max_q_len=1, max_ctx=2048, scale=1 / math.sqrt(D),
+                                k_scale=sc, v_scale=sc)
+    elif a.op == "gemm":
+        ws = rand_weight(a.n, a.k, a.fmt, 3)
+        act = ops.quantize_act(torch.randn(M, a.k, device=DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[a.fmt])
+        out = torch.empty(M, a.n, device=DEV, dtype=torch.bfloat16)
+        for i in range(a.iters):
+            ops.linear(act, ws[i % 3], out=out)
+    elif a.op == "rowop":
+        x = torch.randn(M, a.k, device=DEV).to(torch.bfloat16)
+        w = torch.ones(a.k, device=DEV, dtype=torch.bfloat16)
+        for _ in range(a.iters):
+            ops.row_op(x, ops.ACT_FOR_WEIGHT[a.fmt], ops.IN_RMSNORM, w=w)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    print("ok")
+
+
+if __name__ == "__main__":
+    main()

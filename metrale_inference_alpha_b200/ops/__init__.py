@@ -232,7 +232,10 @@ def row_op(x: torch.Tensor, out_fmt: str = "bf16", mode: int = IN_COPY, *, K: Op
         act.data = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
         act.scale = torch.empty(M, dtype=torch.float32, device=dev)
         act.sf_k64 = ((K + 255) // 256) * 4
-        act.sf = torch.zeros(((M + 127) // 128) * act.sf_k64 * 512, dtype=torch.uint8, device=dev)
+        # every 64-wide k group of every row is written by the kernel when K fills the padded
+        # layout; otherwise the padding groups must read as zero scale factors
+        sf_alloc = torch.empty if K % 256 == 0 else torch.zeros
+        act.sf = sf_alloc(((M + 127) // 128) * act.sf_k64 * 512, dtype=torch.uint8, device=dev)
         a.out_ld = K // 2
         a.sf = _ptr(act.sf)
         a.sf_k64 = act.sf_k64
@@ -245,7 +248,7 @@ def row_op(x: torch.Tensor, out_fmt: str = "bf16", mode: int = IN_COPY, *, K: Op
     elif out_fmt == "bf16":
         act.bf16 = act.data
     _native.check(L.mb_row_op(C.byref(a), _stream()), "row_op")
-    _count(2 if out_fmt == "nvfp4" else 1)  # nvfp4 also zero-fills its scale-factor tile
+    _count(2 if (out_fmt == "nvfp4" and K % 256) else 1)  # + the zero fill of padded scale-factor groups
     return act, res_out
 
 
@@ -614,7 +617,7 @@ def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_l
     a.ws, a.ws_bytes, a.total_rows = _ptr(rt.attn_ws), rt.attn_ws.numel(), T
     a.part_tokens, a.window, a.force_mode, a.status = part_tokens, window, force_mode, _ptr(rt.status)
     _native.check(L.mb_paged_attention(C.byref(a), _stream()), "paged_attention")
-    _count(2 if need else 1)
+    _count()
     return out
 
 

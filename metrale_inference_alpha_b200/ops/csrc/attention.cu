@@ -56,6 +56,8 @@ struct RopeKvParams {
 
 __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKvParams p) {
   const int m = blockIdx.x;
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
   const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int Htot = p.Hq + 2 * p.Hkv;
@@ -190,6 +192,8 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
   return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
 }
 
+constexpr size_t kAttnCntBytes = 64 * 1024;   // arrival counters at the head of the split-KV workspace
+
 struct AttnParams {
   const __nv_bfloat16* q;   // [rows, Hq, D]
   const void* k_cache;
@@ -208,6 +212,7 @@ struct AttnParams {
   float* part_o;            // [rows, Hq, parts, D]
   float* part_ml;           // [rows, Hq, parts, 2]
   int parts, part_tokens;
+  uint32_t* part_cnt;       // [num_seqs * Hkv] arrival counters (zero between launches)
   int window;               // sliding window (0 = none)
   uint32_t* status;
 };
@@ -302,23 +307,36 @@ template <int ROWB>
 __device__ __forceinline__ uint32_t raw_off(int row, int chunk) {
   return (uint32_t)(row * ROWB + ((chunk ^ (row & 7)) << 4));
 }
-__device__ __forceinline__ uint32_t e4m3_pair_to_f16x2(uint32_t x, uint32_t sel) {
-  const uint32_t w = __byte_perm(x, 0, sel);          // bytes -> bits 15:8 and 31:24
-  return (w & 0x80008000u) | ((w & 0x7F007F00u) >> 1);
+// two e4m3 bytes -> f16x2 (exact). lo16 / hi16 take the low / high half of a 32-bit word,
+// `sel` gathers an arbitrary byte pair first.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(uint16_t v) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+  return r;
+}
+__device__ __forceinline__ uint32_t e4m3_lo16(uint32_t x) { return cvt_e4m3x2((uint16_t)(x & 0xFFFFu)); }
+__device__ __forceinline__ uint32_t e4m3_hi16(uint32_t x) { return cvt_e4m3x2((uint16_t)(x >> 16)); }
+__device__ __forceinline__ uint32_t e4m3_sel(uint32_t x, uint32_t sel) {
+  return cvt_e4m3x2((uint16_t)__byte_perm(x, 0, sel));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 template <int D, bool FP8, int MT>
 struct SplitKvCfg {
   static constexpr int kRowB = FP8 ? D : 2 * D;                // bytes per cached row in smem
   static constexpr int kTileB = 64 * kRowB;                    // one K (or V) tile
-  static constexpr int kStages = FP8 ? 4 : 3;
+  static constexpr int kStages = 3;
   static constexpr int kPipeB = kStages * 2 * kTileB;
   static constexpr int kMergeB = 4 * MT * 16 * 2 * 4 + 4 * MT * 16 * D * 4;
   static constexpr int kSmem = kPipeB > kMergeB ? kPipeB : kMergeB;
 };
 
 template <int D, bool FP8, int MT>
-__global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_splitkv_kernel(const AttnParams p) {
   using C = SplitKvCfg<D, FP8, MT>;
   constexpr bool F16 = FP8;
   constexpr int kTile = 64;
@@ -330,45 +348,73 @@ __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int G = p.Hq / p.Hkv;
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
   const int qlen = p.q_len[seq], ctx = p.ctx_len[seq], qs = p.q_start[seq];
   const int R = G * qlen;
   if (qlen <= 0) return;
-  int tok_begin = part * p.part_tokens;
-  const int tok_end = min(ctx, tok_begin + p.part_tokens);
+  // partitions of one sequence: as many as a fixed partition size needs, then balanced
+  // (a function of this sequence's own length only, never of the rest of the batch)
+  const int nparts = max(1, (ctx + p.part_tokens - 1) / p.part_tokens);
+  if (part >= nparts) return;
+  const int part_len = (((ctx + nparts - 1) / nparts) + 63) & ~63;
+  int tok_begin = part * part_len;
+  const int tok_end = min(ctx, tok_begin + part_len);
   if (p.window > 0) tok_begin = max(tok_begin, (ctx - qlen + 1 - p.window) & ~63);
   if (tok_begin < 0) tok_begin = 0;
   const bool empty = tok_begin >= tok_end;
   const int* bt = p.block_table + (size_t)seq * p.max_blocks;
   const int ntiles = empty ? 0 : (tok_end - tok_begin + kTile - 1) / kTile;
 
+  // block ids of this partition, staged once (bounds-checked here, not per chunk)
+  __shared__ int s_blk[64];
+  const int bs = p.block_size;
+  const bool fast_blocks = (bs == 16 || bs == 32 || bs == 64) && (p.part_tokens + 64) / bs <= 64;
+  const int bs_shift = 31 - __clz(bs);
+  if (!empty) {
+    const int first_blk = tok_begin / bs, nblk = (tok_end - 1) / bs - first_blk + 1;
+    for (int i = tid; i < nblk && i < 64; i += 128) {
+      int b = bt[first_blk + i];
+      if (b < 0 || b >= p.num_blocks) {
+        if (p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
+        b = 0;
+      }
+      s_blk[i] = b;
+    }
+  }
+  __syncthreads();
+  // per-thread constants of the copy pattern: chunk i of a tile is row r_i, 16-byte column c_i
+  constexpr int kCopies = (64 * kChunks) / 128;
+  const size_t row_pitch = (size_t)p.Hkv * kRowB;              // bytes between consecutive tokens
   auto issue_tile = [&](int it) {
     const int stage = it % kStages;
     const uint32_t sK = sbase + stage * 2 * kTileB, sV = sK + kTileB;
     const int tok0 = tok_begin + it * kTile;
+    const int blk0 = (tok0 - tok_begin) >> bs_shift;
 #pragma unroll
-    for (int i = 0; i < (64 * kChunks) / 128; ++i) {
+    for (int i = 0; i < kCopies; ++i) {
       const int idx = tid + i * 128;
-      const int r = idx / kChunks, c = idx - r * kChunks;
+      const int r = idx / kChunks, c = idx % kChunks;          // compile-time divisors
       const int tok = tok0 + r;
-      const uint8_t* srcK = reinterpret_cast<const uint8_t*>(p.k_cache);
-      const uint8_t* srcV = reinterpret_cast<const uint8_t*>(p.v_cache);
       int sz = 0;
+      size_t off = 0;
       if (tok < tok_end) {
-        const long long blk = bt[tok / p.block_size];
-        if (blk < 0 || blk >= p.num_blocks) {
-          if (p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
+        int blk, within;
+        if (fast_blocks) {
+          blk = s_blk[blk0 + (r >> bs_shift)];
+          within = r & (bs - 1);                                      // tiles start on a block boundary
         } else {
-          const size_t off = (((size_t)blk * p.block_size + (tok % p.block_size)) * p.Hkv + kvh) * kRowB +
-                             (size_t)c * 16;
-          srcK += off;
-          srcV += off;
-          sz = 16;
+          blk = bt[tok / bs];
+          within = tok % bs;
+          if (blk < 0 || blk >= p.num_blocks) blk = 0;
         }
+        off = ((size_t)blk * bs + within) * row_pitch + (size_t)kvh * kRowB + (size_t)c * 16;
+        sz = 16;
       }
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sK + raw_off<kRowB>(r, c)),
-                   "l"(srcK), "r"(sz) : "memory");
+                   "l"(reinterpret_cast<const uint8_t*>(p.k_cache) + off), "r"(sz) : "memory");
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sV + raw_off<kRowB>(r, c)),
-                   "l"(srcV), "r"(sz) : "memory");
+                   "l"(reinterpret_cast<const uint8_t*>(p.v_cache) + off), "r"(sz) : "memory");
     }
   };
 
@@ -423,8 +469,22 @@ __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) o_acc[mt][n][i] = 0.f;
   }
-  const float kmul = FP8 ? (*p.k_scale) * 256.f : 1.f;
+  const float kmul = FP8 ? (*p.k_scale) : 1.f;
   const float sc_log2 = p.scale * kmul * 1.44269504088896f;
+  // rows of this thread: (mt, hr) -> causal limit; constant over the whole kernel
+  int lim[MT][2];
+  int min_limit = 0x7fffffff;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int r = mt * 16 + g + hr * 8;
+      lim[mt][hr] = r < R ? ctx - qlen + r / G + 1 : 0x7fffffff;   // rows past R are never stored
+      if (r < R) min_limit = min(min_limit, lim[mt][hr]);
+    }
+  min_limit = min(min_limit, __shfl_xor_sync(0xffffffffu, min_limit, 4));
+  min_limit = min(min_limit, __shfl_xor_sync(0xffffffffu, min_limit, 8));
+  min_limit = min(min_limit, __shfl_xor_sync(0xffffffffu, min_limit, 16));
 
   for (int it = 0; it < ntiles; ++it) {
     asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 2) : "memory");
@@ -451,8 +511,8 @@ __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
         ldsm4(r, kT + raw_off<kRowB>(row, kg * 2 + ((lane >> 3) & 1)));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {                     // k step 2 kg + h
-          const uint32_t b00 = e4m3_pair_to_f16x2(r[h], 0x1404), b01 = e4m3_pair_to_f16x2(r[h], 0x3424);
-          const uint32_t b10 = e4m3_pair_to_f16x2(r[2 + h], 0x1404), b11 = e4m3_pair_to_f16x2(r[2 + h], 0x3424);
+          const uint32_t b00 = e4m3_lo16(r[h]), b01 = e4m3_hi16(r[h]);
+          const uint32_t b10 = e4m3_lo16(r[2 + h]), b11 = e4m3_hi16(r[2 + h]);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             mma16816<true>(s[mt][0], qf[mt][kg * 2 + h], b00, b01);
@@ -473,38 +533,49 @@ __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
         }
       }
     }
-    // online softmax over this warp's 16 tokens
+    // online softmax over this warp's 16 tokens; the mask code only runs for tiles that
+    // touch a causal limit, the end of the range or a sliding window
+    const bool need_mask = (tok0 + 16 > min_limit) || (tok0 + 16 > tok_end) || (p.window > 0);
     uint32_t pa[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
       for (int hr = 0; hr < 2; ++hr) {
-        const int r = mt * 16 + g + hr * 8;
-        const int tq = r / G;
-        const int limit = ctx - qlen + tq + 1;
-        const int wlo = p.window > 0 ? limit - p.window : 0;
         float mx = -INFINITY;
+        if (need_mask) {
+          const int limit = min(lim[mt][hr], tok_end);
+          const int wlo = p.window > 0 ? lim[mt][hr] - p.window : 0;
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
+          for (int n = 0; n < 2; ++n)
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int tok = tok0 + n * 8 + t * 2 + i;
-            float v = s[mt][n][hr * 2 + i] * sc_log2;
-            if (tok >= limit || tok >= tok_end || tok < wlo || r >= R) v = -INFINITY;
-            s[mt][n][hr * 2 + i] = v;
-            mx = fmaxf(mx, v);
-          }
+            for (int i = 0; i < 2; ++i) {
+              const int tok = tok0 + n * 8 + t * 2 + i;
+              float v = s[mt][n][hr * 2 + i] * sc_log2;
+              if (tok >= limit || tok < wlo) v = -INFINITY;
+              s[mt][n][hr * 2 + i] = v;
+              mx = fmaxf(mx, v);
+            }
+        } else {
+#pragma unroll
+          for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const float v = s[mt][n][hr * 2 + i] * sc_log2;
+              s[mt][n][hr * 2 + i] = v;
+              mx = fmaxf(mx, v);
+            }
+        }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float m_new = fmaxf(m_run[mt][hr], mx);
         const float m_use = m_new == -INFINITY ? 0.f : m_new;
-        const float alpha = exp2f(m_run[mt][hr] - m_use);
+        const float alpha = fast_exp2(m_run[mt][hr] - m_use);
         float rs = 0.f;
 #pragma unroll
         for (int n = 0; n < 2; ++n)
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
-            const float pv = exp2f(s[mt][n][hr * 2 + i] - m_use);
+            const float pv = fast_exp2(s[mt][n][hr * 2 + i] - m_use);
             s[mt][n][hr * 2 + i] = pv;
             rs += pv;
           }
@@ -534,8 +605,8 @@ __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int dg = d2 * 2 + h;
-          const uint32_t e0 = e4m3_pair_to_f16x2(r[2 * h], 0x2404), e1 = e4m3_pair_to_f16x2(r[2 * h + 1], 0x2404);
-          const uint32_t o0 = e4m3_pair_to_f16x2(r[2 * h], 0x3414), o1 = e4m3_pair_to_f16x2(r[2 * h + 1], 0x3414);
+          const uint32_t e0 = e4m3_sel(r[2 * h], 0x4420), e1 = e4m3_sel(r[2 * h + 1], 0x4420);
+          const uint32_t o0 = e4m3_sel(r[2 * h], 0x4431), o1 = e4m3_sel(r[2 * h + 1], 0x4431);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             mma16816<true>(o_acc[mt][dg * 2], pa[mt], e0, e1);        // even dims of the group
@@ -563,7 +634,7 @@ __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
   // ---- merge the 4 warps through shared memory (the pipeline buffers are free now)
   float* s_ml = reinterpret_cast<float*>(smem_attn);
   float* s_o = s_ml + 4 * MT * 16 * 2;
-  const float vmul = FP8 ? (*p.v_scale) * 256.f : 1.f;
+  const float vmul = FP8 ? (*p.v_scale) : 1.f;
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -620,7 +691,7 @@ __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
     acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
     const int tq = r / G, hh = r - tq * G;
     const size_t orow = (size_t)(qs + tq) * p.Hq + kvh * G + hh;
-    if (p.parts == 1) {
+    if (nparts == 1) {
       __nv_bfloat16* dst = p.out + orow * D + c4 * 4;
       *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x, acc.y);
       *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z, acc.w);
@@ -632,12 +703,50 @@ __global__ void __launch_bounds__(128) attn_splitkv_kernel(const AttnParams p) {
       }
     }
   }
+  if (nparts == 1) return;
+  // the last partition of this (sequence, kv head) to arrive merges all of them, in
+  // partition order, and re-arms the counter
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const uint32_t prev = atomicAdd(&p.part_cnt[seq * p.Hkv + kvh], 1u);
+    s_last = (prev == (uint32_t)nparts - 1);
+    if (s_last) p.part_cnt[seq * p.Hkv + kvh] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = tid; idx < R * (D / 4); idx += 128) {
+    const int r = idx / (D / 4), c4 = idx - r * (D / 4);
+    const int tq = r / G, hh = r - tq * G;
+    const size_t orow = (size_t)(qs + tq) * p.Hq + kvh * G + hh;
+    float mx = -INFINITY;
+    for (int s2 = 0; s2 < nparts; ++s2) mx = fmaxf(mx, __ldcg(&p.part_ml[(orow * p.parts + s2) * 2]));
+    float denom = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s2 = 0; s2 < nparts; ++s2) {
+      const float m = __ldcg(&p.part_ml[(orow * p.parts + s2) * 2]);
+      const float l = __ldcg(&p.part_ml[(orow * p.parts + s2) * 2 + 1]);
+      if (m == -INFINITY || l <= 0.f) continue;
+      const float wgt = l * exp2f(m - mx);
+      denom += wgt;
+      const float4 ov = __ldcg(reinterpret_cast<const float4*>(p.part_o + (orow * p.parts + s2) * D + c4 * 4));
+      acc.x += ov.x * wgt; acc.y += ov.y * wgt; acc.z += ov.z * wgt; acc.w += ov.w * wgt;
+    }
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    __nv_bfloat16* dst = p.out + orow * D + c4 * 4;
+    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+    *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+  }
 }
 
 // Merge partitions: out = sum_p w_p * o_p, w_p = l_p 2^(m_p - m) / sum(...)
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* __restrict__ out, int parts, int D) {
   const size_t row = blockIdx.x;  // (query row, head)
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
   float mx = -INFINITY;
   for (int s = 0; s < parts; ++s) mx = fmaxf(mx, part_ml[(row * parts + s) * 2]);
   float denom = 0.f;
@@ -671,6 +780,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
   const int qt = blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.Hq / p.Hkv, kvh = head / G;
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
   const int qlen = p.q_len[seq], ctx = p.ctx_len[seq], qs = p.q_start[seq];
   const int q0 = qt * 64;
   if (q0 >= qlen) return;
@@ -831,8 +942,7 @@ int launch_splitkv(const AttnParams& p, int num_seqs, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<dim3(p.Hkv, num_seqs, p.parts), 128, smem, stream>>>(p);
-  return (int)cudaGetLastError();
+  return (int)mb::launch_kernel(kern, dim3(p.Hkv, num_seqs, p.parts), dim3(128), smem, stream, p);
 }
 template <int D, bool FP8>
 int launch_prefill(const AttnParams& p, int num_seqs, int max_q_len, cudaStream_t stream) {
@@ -844,8 +954,7 @@ int launch_prefill(const AttnParams& p, int num_seqs, int max_q_len, cudaStream_
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<dim3((max_q_len + 63) / 64, p.Hq, num_seqs), 128, smem, stream>>>(p);
-  return (int)cudaGetLastError();
+  return (int)mb::launch_kernel(kern, dim3((max_q_len + 63) / 64, p.Hq, num_seqs), dim3(128), smem, stream, p);
 }
 
 template <int D, bool FP8>
@@ -905,8 +1014,7 @@ int mb_qk_norm_rope_kvwrite(const MbRopeKvArgs* a, cudaStream_t stream) {
   p.k_scale = a->k_scale; p.v_scale = a->v_scale; p.num_slots = a->num_slots;
   p.status = a->status;
   const int Htot = a->Hq + 2 * a->Hkv;
-  rope_kv_kernel<<<dim3(a->M, (Htot + 3) / 4), 128, 0, stream>>>(p);
-  return (int)cudaGetLastError();
+  return (int)mb::launch_kernel(rope_kv_kernel, dim3(a->M, (Htot + 3) / 4), dim3(128), 0, stream, p);
 }
 
 struct MbAttnArgs {
@@ -940,7 +1048,7 @@ size_t mb_attn_ws_bytes(int total_rows, int Hq, int D, int max_ctx, int part_tok
   const int pt = part_tokens > 0 ? part_tokens : 512;
   const int parts = (max_ctx + pt - 1) / pt;
   if (parts <= 1) return 0;
-  return (size_t)total_rows * Hq * parts * (D + 2) * sizeof(float);
+  return kAttnCntBytes + (size_t)total_rows * Hq * parts * (D + 2) * sizeof(float);
 }
 
 int mb_paged_attention(const MbAttnArgs* a, cudaStream_t stream) {
@@ -968,9 +1076,13 @@ int mb_paged_attention(const MbAttnArgs* a, cudaStream_t stream) {
     p.parts = (a->max_ctx + p.part_tokens - 1) / p.part_tokens;
     if (p.parts < 1) p.parts = 1;
     if (p.parts > 1) {
-      const size_t need = (size_t)a->total_rows * a->Hq * p.parts * (a->D + 2) * sizeof(float);
-      if (!a->ws || a->ws_bytes < need) return MB_ERR_TOO_LARGE;
-      p.part_o = reinterpret_cast<float*>(a->ws);
+      const size_t cnt_bytes = ((size_t)a->num_seqs * a->Hkv * sizeof(uint32_t) + 255) & ~size_t(255);
+      const size_t need = cnt_bytes + (size_t)a->total_rows * a->Hq * p.parts * (a->D + 2) * sizeof(float);
+      if (!a->ws || a->ws_bytes < need || cnt_bytes > kAttnCntBytes) return MB_ERR_TOO_LARGE;
+      // counters sit in the first kAttnCntBytes of the workspace (zero-initialised by the
+      // owner once; every launch leaves them at zero again)
+      p.part_cnt = reinterpret_cast<uint32_t*>(a->ws);
+      p.part_o = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a->ws) + kAttnCntBytes);
       p.part_ml = p.part_o + (size_t)a->total_rows * a->Hq * p.parts * a->D;
     }
     int rc;
@@ -981,11 +1093,10 @@ int mb_paged_attention(const MbAttnArgs* a, cudaStream_t stream) {
     else if (a->D == 256) rc = fp8 ? dispatch_mt<256, true>(mt, p, a->num_seqs, stream)
                                    : dispatch_mt<256, false>(mt, p, a->num_seqs, stream);
     else return MB_ERR_UNSUPPORTED;
-    if (rc) return rc;
+    return rc;
     if (p.parts > 1) {
-      attn_merge_kernel<<<a->total_rows * a->Hq, 128, 0, stream>>>(p.part_o, p.part_ml, p.out,
-                                                                  p.parts, a->D);
-      return (int)cudaGetLastError();
+      return (int)mb::launch_kernel(attn_merge_kernel, dim3(a->total_rows * a->Hq), dim3(128), 0, stream,
+                                    (const float*)p.part_o, (const float*)p.part_ml, p.out, p.parts, a->D);
     }
     return 0;
   }

@@ -259,6 +259,18 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
   for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of the library starts with pdl_wait() before its first global-memory access
+// and may be launched with the programmatic-stream-serialization attribute (launch_kernel
+// below): the next kernel's CTAs are then scheduled, and run their global-memory-free set-up
+// (barrier init, TMEM alloc, descriptor prefetch), while the previous kernel drains.
+// pdl_wait() returns once the previous grid has completed and its writes are visible; it is
+// a no-op for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- numerics
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -329,4 +341,24 @@ __host__ __device__ __forceinline__ uint32_t sf_tile_offset(uint32_t r, uint32_t
   return (r & 31u) * 16u + ((r >> 5) & 3u) * 4u + kk;
 }
 
+}  // namespace mb
+
+// ---------------------------------------------------------------- host launch helper
+extern "C" int mb_pdl_enabled();
+namespace mb {
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = mb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 }  // namespace mb

@@ -142,6 +142,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __syncthreads();
   mb::tc_fence_after();
   const uint32_t tmem = tmem_base_s;
+  mb::pdl_wait();                 // set-up above touched no global memory
+  mb::pdl_launch_dependents();
   if (threadIdx.x == 0) MB_STAMP(1);
 
   auto sA = [&](int s) { return smem + s * C::kStageBytes; };
@@ -430,8 +432,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, 192, C::kSmemBytes, stream>>>(tmA, tmB, p);
-  return (int)cudaGetLastError();
+  return (int)mb::launch_kernel(kern, grid, dim3(192), C::kSmemBytes, stream, tmA, tmB, p);
 }
 
 template <int KIND>

@@ -25,6 +25,7 @@
 // relu_squared.cu, residual_add.cu::sigmoid_gate_mul, quantize_bf16_to_nvfp4.cu,
 // w8a8_act_quant.cu, per_token_group_quant_fp8.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace {
 
@@ -68,6 +69,8 @@ __global__ void __launch_bounds__(512) row_kernel(const RowParams p) {
   const int m = blockIdx.x;
   const int K = p.K;
   const int tid = threadIdx.x, nt = blockDim.x;
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
 
   // ---- stage 1: build the fp32 row
   if (p.in_mode == IN_RMSNORM) {
@@ -234,6 +237,8 @@ __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* _
                              __nv_bfloat16* __restrict__ out, int hidden, int vocab,
                              uint32_t* status) {
   const int m = blockIdx.x;
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
   const int id = ids[m];
   const bool ok = id >= 0 && id < vocab;
   if (!ok && threadIdx.x == 0 && status) atomicCAS(status, 0u, MB_ST_BOUNDS);
@@ -246,6 +251,16 @@ __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* _
 }  // namespace
 
 extern "C" {
+
+static int g_pdl = -1;
+int mb_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("METRALE_PDL");
+    g_pdl = (e && e[0] == '1') ? 1 : 0;   // opt-in: measured slower than plain launches here
+  }
+  return g_pdl;
+}
+void mb_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 struct MbRowArgs {
   int M, K, in_mode, out_mode;
@@ -302,8 +317,7 @@ int mb_row_op(const MbRowArgs* a, cudaStream_t stream) {
     configured = true;
   }
   int threads = a->K >= 4096 ? 512 : (a->K >= 1024 ? 256 : 128);
-  row_kernel<<<a->M, threads, smem, stream>>>(p);
-  return (int)cudaGetLastError();
+  return (int)mb::launch_kernel(row_kernel, dim3(a->M), dim3(threads), smem, stream, p);
 }
 
 int mb_sf_repack(const void* src, void* dst, int N, int kblocks, int sf_k64, cudaStream_t stream) {
@@ -328,9 +342,9 @@ int mb_add_inplace(void* dst, const void* src, long long n, cudaStream_t stream)
 int mb_embed(const int* ids, const void* table, void* out, int M, int hidden, int vocab,
              uint32_t* status, cudaStream_t stream) {
   if (!ids || !table || !out || M <= 0 || hidden % 8) return MB_ERR_BAD_ARG;
-  embed_kernel<<<M, 128, 0, stream>>>(ids, reinterpret_cast<const __nv_bfloat16*>(table),
-                                      reinterpret_cast<__nv_bfloat16*>(out), hidden, vocab, status);
-  return (int)cudaGetLastError();
+  return (int)mb::launch_kernel(embed_kernel, dim3(M), dim3(128), 0, stream, ids,
+                                reinterpret_cast<const __nv_bfloat16*>(table),
+                                reinterpret_cast<__nv_bfloat16*>(out), hidden, vocab, status);
 }
 
 }  // extern "C"

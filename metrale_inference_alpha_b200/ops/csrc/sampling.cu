@@ -46,6 +46,8 @@ argmax_kernel(const T* __restrict__ logits, long long ld, int V, int* __restrict
   __shared__ int s_idx[32];
   __shared__ float s_red[32];
   const int row = blockIdx.x;
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
   const T* x = logits + (size_t)row * ld;
   float best = -INFINITY;
   int bidx = 0x7fffffff;
