@@ -306,7 +306,7 @@ def quantize_act(x: torch.Tensor, fmt: str) -> Act:
 # ----------------------------------------------------------------------------- linear
 def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
            swiglu: bool = False, out_f32: bool = False, out: Optional[torch.Tensor] = None,
-           force_tn: int = 0, force_splits: int = 0, dbg: int = 0, grouped=None, trace=None) -> torch.Tensor:
+           force_tn: int = 0, force_splits: int = 0, dbg: int = 0, grouped=None, trace=None, no_cluster: bool = False) -> torch.Tensor:
     """out[m, n] = sum_k act[m, k] * w[n, k] (+ residual); with `swiglu`, w holds gate/up rows
     interleaved (2j, 2j+1) and the result is silu(gate) * up of width N/2."""
     assert act.K == w.K, (act.K, w.K)
@@ -348,6 +348,7 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
     a.ws, a.ws_bytes, a.status = _ptr(rt.ws), rt.ws_bytes, _ptr(rt.status)
     a.force_tn, a.force_splits, a.sm_count, a.dbg = force_tn, force_splits, rt.sm_count, dbg
     a.trace = _ptr(trace)
+    a.no_cluster = int(no_cluster)
     if grouped is not None:
         # (tile_expert, tile_row0, tile_nrows, n_per_expert, max_tiles, tile_rows)
         a.tile_expert, a.tile_row0, a.tile_nrows = _ptr(grouped[0]), _ptr(grouped[1]), _ptr(grouped[2])

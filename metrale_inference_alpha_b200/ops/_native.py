@@ -25,7 +25,7 @@ class GemmArgs(C.Structure):
         ("sfa", c_void_p), ("sfb", c_void_p), ("sf_k64", c_int),
         ("epilogue", c_int), ("out_f32", c_int),
         ("ws", c_void_p), ("ws_bytes", c_size_t), ("status", c_void_p),
-        ("force_tn", c_int), ("force_splits", c_int), ("sm_count", c_int), ("dbg", c_int), ("trace", c_void_p),
+        ("force_tn", c_int), ("force_splits", c_int), ("sm_count", c_int), ("dbg", c_int), ("trace", c_void_p), ("no_cluster", c_int),
         ("tile_expert", c_void_p), ("tile_row0", c_void_p), ("tile_nrows", c_void_p),
         ("n_per_expert", c_int), ("max_tiles", c_int),
     ]

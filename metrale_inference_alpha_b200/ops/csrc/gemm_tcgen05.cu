@@ -61,6 +61,7 @@ struct GemmParams {
   const int* tile_row0;
   const int* tile_nrows;
   int n_per_expert;
+  int cluster;        // splits form a thread-block cluster; partial tiles are reduced over DSMEM
   long long* trace;   // optional per-phase cycle stamps of CTA (0,0,0) and the last CTA in x
   int dbg;   // timing experiments only: 1 skip SF copies, 2 skip epilogue stores, 4 skip MMAs, 8 skip SF loads
 };
@@ -85,8 +86,8 @@ struct Cfg {
 
 #define MB_STAMP(i)                                                                              \
   do {                                                                                           \
-    if (p.trace && blockIdx.y == 0 && blockIdx.z == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) \
-      p.trace[(blockIdx.x == 0 ? 0 : 8) + (i)] = clock64();                                     \
+    if (p.trace && blockIdx.y == 0 && blockIdx.x == 0 && (blockIdx.z == 0 || blockIdx.z == gridDim.z - 1)) \
+      p.trace[(blockIdx.z == 0 ? 0 : 12) + (i)] = clock64();                                     \
   } while (0)
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -176,6 +177,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (i == 0) MB_STAMP(2);
       }
     }
+    __syncwarp();
+    if (p.cluster) { mb::cluster_sync_all(); mb::cluster_sync_all(); }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (mb::elect_one()) {
@@ -237,6 +240,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if constexpr (KIND != KIND_FP8_BLOCK) mb::tc_commit(&acc_full[0]);
       MB_STAMP(4);
     }
+    __syncwarp();
+    if (p.cluster) { mb::cluster_sync_all(); mb::cluster_sync_all(); }
   } else {
     // ------------------------------------------------------------ epilogue
     // (a) TMEM -> registers -> fp32 staging tile [m][n] in the (by then idle) pipeline
@@ -273,7 +278,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       wcol[i] = wsc;
     }
     const size_t tile_lin = (size_t)tile_m * gridDim.x + tile_n;
-    float* wsp = p.splits > 1 ? p.ws + (tile_lin * p.splits + split) * (size_t)(TN * kTileN) : s_tile;
+    float* wsp = (p.splits > 1 && !p.cluster) ? p.ws + (tile_lin * p.splits + split) * (size_t)(TN * kTileN) : s_tile;
 
     if constexpr (KIND == KIND_FP8_BLOCK) {
       float accr[TN];
@@ -322,9 +327,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int nsrc = 1;                                          // tiles to sum in phase (c)
     const float* src = s_tile;
     bool do_store = ok;
-    if (p.splits > 1) {
+    int row_lo = 0, row_hi = TN;                           // rows this CTA finishes
+    if (p.splits > 1 && p.cluster) {
+      // every CTA of the cluster holds its partial tile in shared memory at the same offset;
+      // each one finishes a contiguous share of the rows, summing the peers' tiles in split
+      // order through distributed shared memory
+      epi_bar_sync();
+      mb::cluster_sync_all();
+      nsrc = p.splits;
+      const int share = (((TN + p.splits - 1) / p.splits) + 7) & ~7;
+      row_lo = split * share;
+      row_hi = min(TN, row_lo + share);
+    } else if (p.splits > 1) {
       // last-arriver reduction, summed in split order so the result does not depend on
       // which CTA finishes last
+      if (threadIdx.x == 64) MB_STAMP(8);
       __threadfence();
       epi_bar_sync();
       if (threadIdx.x == 64) {
@@ -334,8 +351,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         is_last_s = last;
       }
       epi_bar_sync();
+      if (threadIdx.x == 64) MB_STAMP(9);
       do_store = do_store && is_last_s;
       if (do_store) __threadfence();
+      if (threadIdx.x == 64) MB_STAMP(10);
       nsrc = p.splits;
       src = p.ws + tile_lin * p.splits * (size_t)(TN * kTileN);
     } else {
@@ -347,24 +366,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int n_out_limit = swiglu ? n_limit / 2 : n_limit;
       const bool vec_ok = (p.ldo % 8 == 0) && (n_out0 + 8 <= n_out_limit) &&
                           ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.residual)) & 15) == 0;
-#pragma unroll 2
-      for (int mr = et / tpr; mr < TN; mr += rpp) {
+      const int rows_valid = min(row_hi, m_end - m0);
+      const int nf4 = cpt / 4;                             // float4 per row for this thread
+      // scale + (SwiGLU) + residual + store of one row held in x[]
+      auto emit = [&](int mr, const float* x) {
         const int m = m0 + mr;
-        if (m >= m_end) break;
-        float x[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = 0.f;
-        for (int s = 0; s < nsrc; ++s) {
-          const float* row = src + (size_t)s * (TN * kTileN) + mr * kTileN + col0;
-#pragma unroll
-          for (int i4 = 0; i4 < 4; ++i4) {
-            if (i4 * 4 < cpt) {
-              const float4 f = nsrc > 1 ? __ldcg(reinterpret_cast<const float4*>(row) + i4)
-                                        : *(reinterpret_cast<const float4*>(row) + i4);
-              x[i4 * 4] += f.x; x[i4 * 4 + 1] += f.y; x[i4 * 4 + 2] += f.z; x[i4 * 4 + 3] += f.w;
-            }
-          }
-        }
         const float as = s_ascale[mr];
         float y[8];
         if (swiglu) {
@@ -407,8 +413,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
         }
+      };
+      if (nsrc == 1) {
+        // staged tile in shared memory
+        for (int mr = row_lo + et / tpr; mr < rows_valid; mr += rpp) {
+          float x[16];
+          const float4* row = reinterpret_cast<const float4*>(s_tile + mr * kTileN + col0);
+#pragma unroll
+          for (int i4 = 0; i4 < 4; ++i4) {
+            const float4 f = i4 < nf4 ? row[i4] : make_float4(0.f, 0.f, 0.f, 0.f);
+            x[i4 * 4] = f.x; x[i4 * 4 + 1] = f.y; x[i4 * 4 + 2] = f.z; x[i4 * 4 + 3] = f.w;
+          }
+          emit(mr, x);
+        }
+      } else {
+        // split-K: partial tiles in the workspace (L2). Two rows x all splits are requested
+        // before the first use so the loads overlap; summed in split order.
+        constexpr int kMaxBatch = 4;                       // splits handled per load batch
+        for (int mr = row_lo + et / tpr; mr < rows_valid; mr += 2 * rpp) {
+          const int mr1 = mr + rpp;
+          const bool has1 = mr1 < rows_valid;
+          float x0[16], x1[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { x0[i] = 0.f; x1[i] = 0.f; }
+          for (int s0 = 0; s0 < nsrc; s0 += kMaxBatch) {
+            float4 f0[kMaxBatch][4], f1[kMaxBatch][4];
+#pragma unroll
+            for (int sb = 0; sb < kMaxBatch; ++sb) {
+              const bool on = s0 + sb < nsrc;
+              const float* base = src + (size_t)(on ? s0 + sb : 0) * (TN * kTileN) + col0;
+              const uint32_t peer = p.cluster ? mb::dsmem_addr(mb::smem_u32(s_tile + col0), on ? s0 + sb : 0) : 0u;
+#pragma unroll
+              for (int i4 = 0; i4 < 4; ++i4) {
+                const bool ld = on && i4 < nf4;
+                const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (p.cluster) {
+                  f0[sb][i4] = ld ? mb::dsmem_ld_f4(peer + (mr * kTileN + i4 * 4) * 4) : z4;
+                  f1[sb][i4] = (ld && has1) ? mb::dsmem_ld_f4(peer + (mr1 * kTileN + i4 * 4) * 4) : z4;
+                } else {
+                  f0[sb][i4] = ld ? __ldcg(reinterpret_cast<const float4*>(base + mr * kTileN) + i4) : z4;
+                  f1[sb][i4] = (ld && has1) ? __ldcg(reinterpret_cast<const float4*>(base + mr1 * kTileN) + i4) : z4;
+                }
+              }
+            }
+#pragma unroll
+            for (int sb = 0; sb < kMaxBatch; ++sb)
+#pragma unroll
+              for (int i4 = 0; i4 < 4; ++i4) {
+                x0[i4 * 4] += f0[sb][i4].x; x0[i4 * 4 + 1] += f0[sb][i4].y;
+                x0[i4 * 4 + 2] += f0[sb][i4].z; x0[i4 * 4 + 3] += f0[sb][i4].w;
+                x1[i4 * 4] += f1[sb][i4].x; x1[i4 * 4 + 1] += f1[sb][i4].y;
+                x1[i4 * 4 + 2] += f1[sb][i4].z; x1[i4 * 4 + 3] += f1[sb][i4].w;
+              }
+          }
+          emit(mr, x0);
+          if (has1) emit(mr1, x1);
+        }
       }
     }
+    if (p.splits > 1 && p.cluster) mb::cluster_sync_all();   // peers may still be reading this CTA's tile
     if (threadIdx.x == 64) MB_STAMP(6);
     mb::tc_fence_before();
   }
@@ -423,6 +486,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 template <int KIND, int TN>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, dim3 grid,
            cudaStream_t stream) {
+  const int cluster_z = p.cluster ? p.splits : 1;
   using C = Cfg<KIND, TN>;
   static bool configured = false;
   auto kern = gemm_kernel<KIND, TN>;
@@ -432,7 +496,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return (int)mb::launch_kernel(kern, grid, dim3(192), C::kSmemBytes, stream, tmA, tmB, p);
+  return (int)mb::launch_kernel_cluster(kern, grid, dim3(192), C::kSmemBytes, stream, cluster_z, tmA, tmB, p);
 }
 
 template <int KIND>
@@ -479,6 +543,7 @@ struct MbGemmArgs {
   int force_tn, force_splits, sm_count;
   int dbg;
   long long* trace;
+  int no_cluster;           // keep split-K on the workspace path
   const int* tile_expert;   // grouped mode (all four set together)
   const int* tile_row0;
   const int* tile_nrows;
@@ -557,7 +622,8 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   p.trace = a->trace;
   p.tile_expert = a->tile_expert; p.tile_row0 = a->tile_row0; p.tile_nrows = a->tile_nrows;
   p.n_per_expert = grouped ? a->n_per_expert : 0;
-  if (splits > 1) {
+  p.cluster = (splits > 1 && splits <= 8 && !a->no_cluster) ? 1 : 0;
+  if (splits > 1 && !p.cluster) {
     const size_t cbytes = mb_gemm_counter_bytes();
     const size_t need = cbytes + (size_t)tiles * splits * tn * kTileN * sizeof(float);
     if (!a->ws || a->ws_bytes < need || (size_t)tiles * 4 > cbytes) return MB_ERR_TOO_LARGE;

@@ -206,6 +206,173 @@ __global__ void __launch_bounds__(512) row_kernel(const RowParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Fast path for the hot recipes (copy / RMSNorm / SiLU-mul from bf16 rows): every thread owns
+// whole 16-element blocks in registers (BPT of them), all global traffic is 16-byte vectors,
+// and the row statistics (sum of squares and max |x * w|) share ONE block reduction, so the
+// kernel is load -> reduce -> store. amax(y) is taken as max|x w| * inv_rms.
+template <int BPT>
+__global__ void __launch_bounds__(1024) row_kernel_v2(const RowParams p) {
+  __shared__ float red[64];
+  const int m = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+  const int K = p.K, nblk = K >> 4;
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
+  float x[BPT][16];
+  float ss = 0.f, mx = 0.f;
+  const bool norm = p.in_mode == IN_RMSNORM;
+#pragma unroll
+  for (int j = 0; j < BPT; ++j) {
+    const int b = tid + j * nt;
+    if (b < nblk) {
+      const __nv_bfloat16* src = p.x + (size_t)m * p.x_ld + b * 16;
+      uint4 v0 = __ldg(reinterpret_cast<const uint4*>(src));
+      uint4 v1 = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+      const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0);
+      const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = __bfloat1622float2(h0[i]), c = __bfloat1622float2(h1[i]);
+        x[j][2 * i] = a.x; x[j][2 * i + 1] = a.y; x[j][8 + 2 * i] = c.x; x[j][8 + 2 * i + 1] = c.y;
+      }
+      if (p.in_mode == IN_SILU_MUL) {
+        const __nv_bfloat16* up = src + K;
+        uint4 u0 = __ldg(reinterpret_cast<const uint4*>(up));
+        uint4 u1 = __ldg(reinterpret_cast<const uint4*>(up) + 1);
+        const __nv_bfloat162* g0 = reinterpret_cast<const __nv_bfloat162*>(&u0);
+        const __nv_bfloat162* g1 = reinterpret_cast<const __nv_bfloat162*>(&u1);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 a = __bfloat1622float2(g0[i]), c = __bfloat1622float2(g1[i]);
+          x[j][2 * i] = mb::silu(x[j][2 * i]) * a.x; x[j][2 * i + 1] = mb::silu(x[j][2 * i + 1]) * a.y;
+          x[j][8 + 2 * i] = mb::silu(x[j][8 + 2 * i]) * c.x; x[j][8 + 2 * i + 1] = mb::silu(x[j][8 + 2 * i + 1]) * c.y;
+        }
+      }
+      if (norm) {
+        float w[16];
+        if (p.w) {
+          uint4 w0 = __ldg(reinterpret_cast<const uint4*>(p.w + b * 16));
+          uint4 w1 = __ldg(reinterpret_cast<const uint4*>(p.w + b * 16) + 1);
+          const __nv_bfloat162* q0 = reinterpret_cast<const __nv_bfloat162*>(&w0);
+          const __nv_bfloat162* q1 = reinterpret_cast<const __nv_bfloat162*>(&w1);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 a = __bfloat1622float2(q0[i]), c = __bfloat1622float2(q1[i]);
+            w[2 * i] = a.x; w[2 * i + 1] = a.y; w[8 + 2 * i] = c.x; w[8 + 2 * i + 1] = c.y;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) w[i] = 1.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          ss += x[j][i] * x[j][i];
+          x[j][i] *= p.w_plus_one ? (w[i] + 1.f) : w[i];      // x now holds x * w
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) mx = fmaxf(mx, fabsf(x[j][i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) x[j][i] = 0.f;
+    }
+  }
+  // one block reduction for (sum of squares, max)
+  const bool need_red = norm || p.out_mode == OUT_FP8_ROW || p.out_mode == OUT_NVFP4;
+  float inv = 1.f, amax = mx;
+  if (need_red) {
+    ss = mb::warp_sum(ss);
+    mx = mb::warp_max(mx);
+    const int w = tid >> 5, l = tid & 31, nw = (nt + 31) >> 5;
+    if (l == 0) { red[w] = ss; red[32 + w] = mx; }
+    __syncthreads();
+    float a = l < nw ? red[l] : 0.f, c = l < nw ? red[32 + l] : 0.f;
+    a = mb::warp_sum(a);
+    c = mb::warp_max(c);
+    if (norm) inv = rsqrtf(a / (float)K + p.eps);
+    amax = c * inv;
+  }
+  float gs = 1.f, row_inv = 1.f;
+  if (p.out_mode == OUT_FP8_ROW) {
+    gs = amax > 0.f ? amax / 448.f : 1.f;
+    row_inv = 1.f / gs;
+    if (tid == 0) p.scale[m] = gs;
+  } else if (p.out_mode == OUT_NVFP4) {
+    gs = amax > 0.f ? amax / (6.f * 448.f) : 1.f;
+    if (tid == 0) p.scale[m] = gs;
+  }
+#pragma unroll
+  for (int j = 0; j < BPT; ++j) {
+    const int b = tid + j * nt;
+    const bool valid = b < nblk;                       // no early exit: the group shuffles below need whole warps
+    float y[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) y[i] = x[j][i] * inv;
+    if (valid && (p.out_bf16 || p.out_mode == OUT_BF16)) {
+      uint4 o0, o1;
+      __nv_bfloat162* q0 = reinterpret_cast<__nv_bfloat162*>(&o0);
+      __nv_bfloat162* q1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        q0[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+        q1[i] = __floats2bfloat162_rn(y[8 + 2 * i], y[8 + 2 * i + 1]);
+      }
+      if (p.out_bf16) {
+        uint4* d = reinterpret_cast<uint4*>(p.out_bf16 + (size_t)m * p.out_bf16_ld + b * 16);
+        d[0] = o0; d[1] = o1;
+      }
+      if (p.out_mode == OUT_BF16) {
+        uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.out_ld + b * 16);
+        d[0] = o0; d[1] = o1;
+      }
+    }
+    if (p.out_mode == OUT_FP8_ROW || p.out_mode == OUT_FP8_G128) {
+      float sc_inv = row_inv;
+      if (p.out_mode == OUT_FP8_G128) {
+        float bm = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) bm = fmaxf(bm, fabsf(y[i]));
+        // a 128-channel group is 8 consecutive blocks = 8 consecutive lanes
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
+        const float sc = bm > 0.f ? bm / 448.f : 1.f;
+        sc_inv = 1.f / sc;
+        if (valid && (b & 7) == 0) p.scale[(size_t)(b >> 3) * p.scale_ld + m] = sc;
+      }
+      uint32_t w4[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        w4[i] = (uint32_t)mb::float_to_e4m3(y[4 * i] * sc_inv) | ((uint32_t)mb::float_to_e4m3(y[4 * i + 1] * sc_inv) << 8) |
+                ((uint32_t)mb::float_to_e4m3(y[4 * i + 2] * sc_inv) << 16) | ((uint32_t)mb::float_to_e4m3(y[4 * i + 3] * sc_inv) << 24);
+      }
+      if (valid)
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.out) + (size_t)m * p.out_ld + b * 16) =
+            make_uint4(w4[0], w4[1], w4[2], w4[3]);
+    } else if (valid && p.out_mode == OUT_NVFP4) {
+      float bmax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(y[i]));
+      const uint8_t sfc = mb::float_to_e4m3(bmax / (6.f * gs));
+      const float sff = mb::e4m3_to_float(sfc);
+      const float qi = sff > 0.f ? 1.f / (sff * gs) : 0.f;
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) lo |= mb::e2m1_code(y[i] * qi) << (4 * i);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) hi |= mb::e2m1_code(y[8 + i] * qi) << (4 * i);
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(p.out) + (size_t)m * p.out_ld + b * 8) = make_uint2(lo, hi);
+      uint8_t* sf_blk = p.sf + (size_t)(m >> 7) * p.sf_k64 * 512;
+      sf_blk[(size_t)(b >> 2) * 512 + mb::sf_tile_offset(m & 127, b & 3)] = sfc;
+    }
+  }
+}
+
+template <int BPT>
+int launch_row_v2(const RowParams& p, int threads, cudaStream_t stream) {
+  return (int)mb::launch_kernel(row_kernel_v2<BPT>, dim3(p.M), dim3(threads), 0, stream, p);
+}
+
 // Repack row-major ue4m3 scale factors [N, K/16] into the tiled layout
 // [ceil(N/128)][sf_k64][512] (zero padded).
 __global__ void sf_repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N,
@@ -308,6 +475,27 @@ int mb_row_op(const MbRowArgs* a, cudaStream_t stream) {
   p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(a->out_bf16); p.out_bf16_ld = a->out_bf16_ld;
   p.scale = a->scale; p.scale_ld = a->scale_ld;
   p.sf = reinterpret_cast<uint8_t*>(a->sf); p.sf_k64 = a->sf_k64;
+  {
+    // fast path eligibility: bf16 input, whole 16-element blocks, 16-byte aligned vectors
+    const bool modes = p.in_mode == IN_COPY || p.in_mode == IN_RMSNORM || p.in_mode == IN_SILU_MUL;
+    const uintptr_t al = reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out) |
+                         reinterpret_cast<uintptr_t>(p.out_bf16) | reinterpret_cast<uintptr_t>(p.w);
+    const bool ld_ok = p.x_ld % 8 == 0 && p.out_ld % 8 == 0 && p.out_bf16_ld % 8 == 0;
+    const int nblk = a->K / 16;
+    if (modes && !p.xf32 && !p.residual && !p.residual_out && a->K % 16 == 0 && !(al & 15) && ld_ok &&
+        (p.out_mode != OUT_FP8_G128 || a->K % 128 == 0) && nblk <= 4096) {
+      const int bpt = (nblk + 511) / 512;
+      int threads = ((nblk + bpt - 1) / bpt + 31) / 32 * 32;
+      if (p.out_mode == OUT_FP8_G128) threads = (threads + 7) / 8 * 8;
+      switch (bpt) {
+        case 1: return launch_row_v2<1>(p, threads, stream);
+        case 2: return launch_row_v2<2>(p, threads, stream);
+        case 3: return launch_row_v2<3>(p, threads, stream);
+        case 4: return launch_row_v2<4>(p, threads, stream);
+        default: break;
+      }
+    }
+  }
   const size_t smem = (size_t)a->K * sizeof(float);
   static bool configured = false;
   if (!configured) {

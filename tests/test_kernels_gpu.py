@@ -72,6 +72,14 @@ def test_gemm_nvfp4(M):
     _run_linear("nvfp4", M, 256, 1024)
 
 
+def test_gemm_splitk_workspace_path_matches_cluster_path():
+    for fmt in ("nvfp4", "bf16", "fp8_block"):
+        _run_linear(fmt, 24, 384, 2048, force_splits=4, no_cluster=True)
+        _run_linear(fmt, 100, 256, 4096, force_splits=3, no_cluster=True)
+        _run_linear(fmt, 100, 256, 4096, force_splits=3)
+        _run_linear(fmt, 128, 512, 4096, force_splits=8)
+
+
 def test_gemm_nvfp4_splitk_and_tn():
     _run_linear("nvfp4", 24, 384, 2048, force_splits=4)
     _run_linear("nvfp4", 24, 128, 512, force_tn=128)
@@ -109,17 +117,19 @@ def test_sf_repack_matches_reference_layout():
 
 
 @pytest.mark.parametrize("fmt", ["bf16", "fp8_row", "fp8_g128", "nvfp4"])
-def test_rowop_rmsnorm_quant(fmt):
-    M, K = 37, 1024
+@pytest.mark.parametrize("K,with_res", [(1024, True), (1024, False), (17408, False), (5120, False)])
+def test_rowop_rmsnorm_quant(fmt, K, with_res):
+    M = 37
     g = torch.Generator().manual_seed(3)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
-    r = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    r = torch.randn(M, K, generator=g).to(torch.bfloat16) if with_res else None
     w = (torch.randn(K, generator=g) * 0.1).to(torch.bfloat16)
-    a_ref, res_ref = ops.row_op(x, fmt, ops.IN_RMSNORM, residual=r, write_residual=True, w=w,
+    a_ref, res_ref = ops.row_op(x, fmt, ops.IN_RMSNORM, residual=r, write_residual=with_res, w=w,
                                 plus_one=True, eps=1e-6, also_bf16=True)
-    a, res = ops.row_op(x.to(DEV), fmt, ops.IN_RMSNORM, residual=r.to(DEV), write_residual=True,
-                        w=w.to(DEV), plus_one=True, eps=1e-6, also_bf16=True)
-    assert torch.equal(res.cpu(), res_ref)
+    a, res = ops.row_op(x.to(DEV), fmt, ops.IN_RMSNORM, residual=None if r is None else r.to(DEV),
+                        write_residual=with_res, w=w.to(DEV), plus_one=True, eps=1e-6, also_bf16=True)
+    if with_res:
+        assert torch.equal(res.cpu(), res_ref)
     _close(a.bf16, a_ref.bf16, rtol=1e-2, atol=1e-2)
     # decode the kernel's encoding and compare with the oracle's dequantised matrix
     if fmt == "bf16":
@@ -145,6 +155,13 @@ def test_rowop_activations():
         want, _ = ops.row_op(x, "bf16", mode, K=kk)
         got, _ = ops.row_op(x.to(DEV), "bf16", mode, K=kk)
         _close(got.data, want.data, 1e-2, 1e-2)
+    for fmt in ("nvfp4", "fp8_g128", "fp8_row"):
+        want, _ = ops.row_op(x, fmt, ops.IN_SILU_MUL, K=K, also_bf16=True)
+        got, _ = ops.row_op(x.to(DEV), fmt, ops.IN_SILU_MUL, K=K, also_bf16=True)
+        _close(got.bf16, want.bf16, 1e-2, 1e-2)
+        wfmt = {"nvfp4": "nvfp4", "fp8_g128": "fp8_block", "fp8_row": "fp8_row"}[fmt]
+        got_lin = ops.linear(got, ops.make_weight(torch.eye(K)[:128], wfmt).to(DEV), out_f32=True)
+        _close(got_lin, want.data[:, :128], 0.3, 0.3 * want.data.abs().max().item())
     # sigmoid gate interleaved per head: [Q_h | G_h] with head_dim 64
     H, D = 4, 64
     attn = torch.randn(M, H * D, generator=g).to(torch.bfloat16)
