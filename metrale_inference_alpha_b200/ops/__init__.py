@@ -306,7 +306,7 @@ def quantize_act(x: torch.Tensor, fmt: str) -> Act:
 # ----------------------------------------------------------------------------- linear
 def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
            swiglu: bool = False, out_f32: bool = False, out: Optional[torch.Tensor] = None,
-           force_tn: int = 0, force_splits: int = 0, dbg: int = 0, grouped=None, trace=None, no_cluster: bool = False) -> torch.Tensor:
+           force_tn: int = 0, force_splits: int = 0, dbg: int = 0, grouped=None, trace=None, no_cluster: bool = False, tp=None) -> torch.Tensor:
     """out[m, n] = sum_k act[m, k] * w[n, k] (+ residual); with `swiglu`, w holds gate/up rows
     interleaved (2j, 2j+1) and the result is silu(gate) * up of width N/2."""
     assert act.K == w.K, (act.K, w.K)
@@ -349,6 +349,13 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
     a.force_tn, a.force_splits, a.sm_count, a.dbg = force_tn, force_splits, rt.sm_count, dbg
     a.trace = _ptr(trace)
     a.no_cluster = int(no_cluster)
+    if tp is not None:
+        # fused all-reduce: tp = dict(size, rank, m_cap, u_cap, recv[], out[], flags[], done[], par)
+        a.tp_size, a.tp_rank, a.tp_m_cap, a.tp_u_cap = tp["size"], tp["rank"], tp["m_cap"], tp["u_cap"]
+        for r in range(tp["size"]):
+            a.tp_recv[r], a.tp_out[r] = tp["recv"][r], tp["out"][r]
+            a.tp_flags[r], a.tp_done[r] = tp["flags"][r], tp["done"][r]
+        a.tp_par = tp["par"]
     if grouped is not None:
         # (tile_expert, tile_row0, tile_nrows, n_per_expert, max_tiles, tile_rows)
         a.tile_expert, a.tile_row0, a.tile_nrows = _ptr(grouped[0]), _ptr(grouped[1]), _ptr(grouped[2])

@@ -26,6 +26,9 @@ class GemmArgs(C.Structure):
         ("epilogue", c_int), ("out_f32", c_int),
         ("ws", c_void_p), ("ws_bytes", c_size_t), ("status", c_void_p),
         ("force_tn", c_int), ("force_splits", c_int), ("sm_count", c_int), ("dbg", c_int), ("trace", c_void_p), ("no_cluster", c_int),
+        ("tp_size", c_int), ("tp_rank", c_int), ("tp_m_cap", c_int), ("tp_u_cap", c_int),
+        ("tp_recv", c_void_p * 8), ("tp_out", c_void_p * 8), ("tp_flags", c_void_p * 8), ("tp_done", c_void_p * 8),
+        ("tp_par", c_void_p),
         ("tile_expert", c_void_p), ("tile_row0", c_void_p), ("tile_nrows", c_void_p),
         ("n_per_expert", c_int), ("max_tiles", c_int),
     ]

@@ -291,6 +291,28 @@ __device__ __forceinline__ float4 dsmem_ld_f4(uint32_t addr) {
   return v;
 }
 
+// ---------------------------------------------------------------- system-scope signalling (peer GPUs)
+__device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded spin until *p >= want. Returns false (and records MB_ST_TIMEOUT_PEER) on expiry.
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* p, uint32_t want, uint32_t* status) {
+  const long long t0 = clock64();
+  while (ld_acquire_sys(p) < want) {
+    if (clock64() - t0 > MB_WAIT_CYCLES) {
+      if (status) atomicCAS(status, 0u, MB_ST_TIMEOUT_PEER);
+      return false;
+    }
+    __nanosleep(64);
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------- numerics
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

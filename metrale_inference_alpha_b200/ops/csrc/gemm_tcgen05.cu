@@ -61,6 +61,13 @@ struct GemmParams {
   const int* tile_row0;
   const int* tile_nrows;
   int n_per_expert;
+  // tensor-parallel fused all-reduce (row-parallel GEMM): see the epilogue
+  int tp_size, tp_rank, tp_m_cap, tp_u_cap;
+  __nv_bfloat16* tp_recv[8];    // per rank: [2 parity][tp source][m_cap][ldo] bf16 landing zones
+  __nv_bfloat16* tp_out[8];     // unused by the one-hop protocol (kept for layout stability)
+  uint32_t* tp_flags[8];        // per rank: [2 parity][u_cap] arrivals per unit
+  uint32_t* tp_done[8];         // per rank: CTA completion counter of the running call
+  const uint32_t* tp_par;       // this rank's current parity (flipped by the last CTA of a call)
   int cluster;        // splits form a thread-block cluster; partial tiles are reduced over DSMEM
   long long* trace;   // optional per-phase cycle stamps of CTA (0,0,0) and the last CTA in x
   int dbg;   // timing experiments only: 1 skip SF copies, 2 skip epilogue stores, 4 skip MMAs, 8 skip SF loads
@@ -74,6 +81,9 @@ struct Cfg {
   static constexpr int kBBytes = TN * 128;
   static constexpr int kSfBytes = (KIND == KIND_NVFP4) ? 2048 : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;
+  // one CTA per SM with a deep pipeline: two co-resident CTAs with half the stages measured
+  // slower on the decode shapes (fewer bytes in flight per CTA on the split-K GEMMs)
+  static constexpr int kCtasPerSm = 1;
   static constexpr int kBudget = 200 * 1024;
   static constexpr int kStagesRaw = kBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
@@ -93,7 +103,7 @@ struct Cfg {
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int KIND, int TN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, Cfg<KIND, TN>::kCtasPerSm)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const GemmParams p) {
   using C = Cfg<KIND, TN>;
@@ -368,6 +378,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                           ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.residual)) & 15) == 0;
       const int rows_valid = min(row_hi, m_end - m0);
       const int nf4 = cpt / 4;                             // float4 per row for this thread
+      const int tp_unit = (int)tile_lin * (p.cluster ? p.splits : 1) + (p.cluster ? split : 0);
+      const uint32_t tp_par = p.tp_size > 1 ? (*reinterpret_cast<const volatile uint32_t*>(p.tp_par) & 1u) : 0u;
       // scale + (SwiGLU) + residual + store of one row held in x[]
       auto emit = [&](int mr, const float* x) {
         const int m = m0 + mr;
@@ -381,6 +393,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           for (int i = 0; i < 8; ++i) y[i] = x[i] * wcol[i] * as;
         }
         const size_t o = (size_t)m * p.ldo + n_out0;
+        if (p.tp_size > 1) {
+          // stage 1 of the fused all-reduce: this rank's bf16 partial goes straight into every
+          // rank's landing zone [parity][source rank] (peer stores over NVLink)
+          uint4 pk;
+          __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) pb[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+          const size_t slot = (((size_t)tp_par * p.tp_size + p.tp_rank) * p.tp_m_cap + m) * p.ldo + n_out0;
+#pragma unroll 1
+          for (int r = 0; r < p.tp_size; ++r) *reinterpret_cast<uint4*>(p.tp_recv[r] + slot) = pk;
+          return;
+        }
         if (vec_ok) {
           if (p.residual) {
             const uint4 r = __ldg(reinterpret_cast<const uint4*>(p.residual + o));
@@ -470,6 +494,75 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (has1) emit(mr1, x1);
         }
       }
+      if (p.tp_size > 1) {
+        // ---- fused all-reduce, one NVLink hop. Every rank runs the same grid, so unit u (an
+        // output tile share) exists on every rank. Publish: system-scope fence, then a release
+        // increment of unit u's arrival flag on every rank. Consume: wait (bounded) until all
+        // ranks have arrived here, sum the landing-zone rows in rank order, add the residual,
+        // store the bf16 result locally, re-arm the flag. Landing zones and flags are
+        // double-buffered by a per-rank parity that the last CTA of the kernel flips.
+        __threadfence_system();
+        epi_bar_sync();
+        if (threadIdx.x == 64) {
+          for (int r = 0; r < p.tp_size; ++r)
+            mb::red_add_release_sys(p.tp_flags[r] + (size_t)tp_par * p.tp_u_cap + tp_unit, 1u);
+        }
+        uint32_t* my_flag = p.tp_flags[p.tp_rank] + (size_t)tp_par * p.tp_u_cap + tp_unit;
+        if (threadIdx.x == 64) is_last_s = mb::wait_flag_sys(my_flag, (uint32_t)p.tp_size, p.status) ? 1 : 0;
+        epi_bar_sync();
+        if (is_last_s) {
+          const __nv_bfloat16* zone = p.tp_recv[p.tp_rank] + (size_t)tp_par * p.tp_size * p.tp_m_cap * p.ldo;
+          for (int mr = row_lo + et / tpr; mr < rows_valid; mr += rpp) {
+            const int m = m0 + mr;
+            const size_t o = (size_t)m * p.ldo + n_out0;
+            uint4 v[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (r < p.tp_size)
+                v[r] = __ldcg(reinterpret_cast<const uint4*>(zone + ((size_t)r * p.tp_m_cap + m) * p.ldo + n_out0));
+            float acc[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              if (r < p.tp_size) {
+                const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&v[r]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 f = __bfloat1622float2(vb[i]);
+                  acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+                }
+              }
+            }
+            if (p.residual) {
+              const uint4 rr = __ldg(reinterpret_cast<const uint4*>(p.residual + o));
+              const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(rb[i]);
+                acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+              }
+            }
+            uint4 pk;
+            __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pb[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
+          }
+        }
+        epi_bar_sync();
+        if (threadIdx.x == 64) {
+          *my_flag = 0;
+          __threadfence();
+          // the last CTA of the grid to get here flips the parity for the next call
+          const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
+          const uint32_t prev = atomicAdd(p.tp_done[p.tp_rank], 1u);
+          if (prev == total - 1) {
+            *p.tp_done[p.tp_rank] = 0;
+            *const_cast<uint32_t*>(p.tp_par) = tp_par ^ 1u;
+          }
+        }
+      }
     }
     if (p.splits > 1 && p.cluster) mb::cluster_sync_all();   // peers may still be reading this CTA's tile
     if (threadIdx.x == 64) MB_STAMP(6);
@@ -481,6 +574,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     mb::tc_fence_after();
     mb::tmem_dealloc(tmem, C::kTmemCols);
   }
+}
+
+// Waits (bounded) until every unit of the fused all-reduce has been finished by its owner,
+// re-arms the counter and flips this rank's parity for the next call.
+__global__ void tp_finish_kernel(uint32_t* done, uint32_t* par, uint32_t units, uint32_t* status) {
+  if (threadIdx.x != 0) return;
+  const uint32_t pcur = *par & 1u;
+  mb::wait_flag_sys(done + pcur, units, status);
+  done[pcur] = 0;
+  *par = pcur ^ 1u;
+  __threadfence_system();
 }
 
 template <int KIND, int TN>
@@ -544,6 +648,13 @@ struct MbGemmArgs {
   int dbg;
   long long* trace;
   int no_cluster;           // keep split-K on the workspace path
+  // fused tensor-parallel all-reduce (0 = off)
+  int tp_size, tp_rank, tp_m_cap, tp_u_cap;
+  void* tp_recv[8];
+  void* tp_out[8];
+  void* tp_flags[8];
+  void* tp_done[8];
+  void* tp_par;
   const int* tile_expert;   // grouped mode (all four set together)
   const int* tile_row0;
   const int* tile_nrows;
@@ -623,6 +734,20 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   p.tile_expert = a->tile_expert; p.tile_row0 = a->tile_row0; p.tile_nrows = a->tile_nrows;
   p.n_per_expert = grouped ? a->n_per_expert : 0;
   p.cluster = (splits > 1 && splits <= 8 && !a->no_cluster) ? 1 : 0;
+  if (a->tp_size > 1) {
+    if (a->tp_size > 8 || a->epilogue != EPI_PLAIN || a->out_f32 || grouped || a->N % kTileN || a->ldo % 8 ||
+        a->M > a->tp_m_cap || (splits > 1 && !p.cluster) || !a->tp_par)
+      return MB_ERR_UNSUPPORTED;
+    if (tiles * splits > a->tp_u_cap) return MB_ERR_TOO_LARGE;
+    p.tp_size = a->tp_size; p.tp_rank = a->tp_rank; p.tp_m_cap = a->tp_m_cap; p.tp_u_cap = a->tp_u_cap;
+    for (int r = 0; r < a->tp_size; ++r) {
+      p.tp_recv[r] = reinterpret_cast<__nv_bfloat16*>(a->tp_recv[r]);
+      p.tp_out[r] = reinterpret_cast<__nv_bfloat16*>(a->tp_out[r]);
+      p.tp_flags[r] = reinterpret_cast<uint32_t*>(a->tp_flags[r]);
+      p.tp_done[r] = reinterpret_cast<uint32_t*>(a->tp_done[r]);
+    }
+    p.tp_par = reinterpret_cast<const uint32_t*>(a->tp_par);
+  }
   if (splits > 1 && !p.cluster) {
     const size_t cbytes = mb_gemm_counter_bytes();
     const size_t need = cbytes + (size_t)tiles * splits * tn * kTileN * sizeof(float);
@@ -640,19 +765,21 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   if (rc) return rc;
 
   dim3 grid(tiles_n, tiles_m, splits);
+  rc = MB_ERR_UNSUPPORTED;
   switch (kind) {
-    case KIND_BF16: return dispatch_tn<KIND_BF16>(tn, tmA, tmB, p, grid, stream);
-    case KIND_FP8: return dispatch_tn<KIND_FP8>(tn, tmA, tmB, p, grid, stream);
-    case KIND_NVFP4: return dispatch_tn<KIND_NVFP4>(tn, tmA, tmB, p, grid, stream);
+    case KIND_BF16: rc = dispatch_tn<KIND_BF16>(tn, tmA, tmB, p, grid, stream); break;
+    case KIND_FP8: rc = dispatch_tn<KIND_FP8>(tn, tmA, tmB, p, grid, stream); break;
+    case KIND_NVFP4: rc = dispatch_tn<KIND_NVFP4>(tn, tmA, tmB, p, grid, stream); break;
     case KIND_FP8_BLOCK:
       switch (tn) {
-        case 16: return launch<KIND_FP8_BLOCK, 16>(tmA, tmB, p, grid, stream);
-        case 32: return launch<KIND_FP8_BLOCK, 32>(tmA, tmB, p, grid, stream);
-        case 64: return launch<KIND_FP8_BLOCK, 64>(tmA, tmB, p, grid, stream);
-        default: return MB_ERR_UNSUPPORTED;
+        case 16: rc = launch<KIND_FP8_BLOCK, 16>(tmA, tmB, p, grid, stream); break;
+        case 32: rc = launch<KIND_FP8_BLOCK, 32>(tmA, tmB, p, grid, stream); break;
+        case 64: rc = launch<KIND_FP8_BLOCK, 64>(tmA, tmB, p, grid, stream); break;
+        default: rc = MB_ERR_UNSUPPORTED;
       }
+      break;
   }
-  return MB_ERR_UNSUPPORTED;
+  return rc;
 }
 
 }  // extern "C"
