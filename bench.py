@@ -269,7 +269,13 @@ def main() -> int:
                                   "ttft_p50_ms": rr["ttft_p50_ms"], "vs_baseline": round(rr["tok_s"] / BASELINE_TOKS[c], 2)}),
                       flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # NCCL communicators captured into CUDA graphs do not tear down reliably at interpreter
+        # exit; every rank has printed / reduced what it needs, so leave without destructors
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 
