@@ -34,6 +34,7 @@
 // kernels/gb10/qwen3.6-27b/nvfp4/nvfp4_mmq.cu (compiled out for sm_100a there).
 #include "common.cuh"
 #include "tensormap.h"
+#include "noalloc.h"
 
 namespace {
 
@@ -783,3 +784,46 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in noalloc.h).
+//
+// Some callers may not allocate device memory at all: code running between
+// cudaStreamBeginCapture and cudaStreamEndCapture, plugins that live inside another
+// framework's memory plan, and real-time loops that must not touch the allocator. The
+// split-K GEMM normally gets its partial-tile workspace from the caller; this variant
+// keeps that workspace in a file-scope device array instead, so the only pointers the
+// caller supplies are operands and outputs.
+//
+// The array's name is only a host-side handle: the device address is obtained once per
+// device with cudaGetSymbolAddress (with that device current) on the first call made on
+// that device, which also zeroes the arrival counters. That first call should therefore be
+// made before any stream capture starts. Every call on a device shares the one array and
+// it keeps the previous call's partial tiles; the counters re-arm themselves, nothing else
+// needs clearing. Two calls that overlap on the GPU (different streams) would race on the
+// array: serialise them. Problem sizes whose workspace exceeds MB_NOALLOC_SCRATCH_BYTES are
+// refused with MB_ERR_TOO_LARGE. No cudaMalloc / cudaFree / allocating library call is made.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[MB_NOALLOC_SCRATCH_BYTES];
+
+extern "C" int mb_gemm_noalloc(const MbGemmArgs* a, cudaStream_t stream) {
+  if (!a) return MB_ERR_BAD_ARG;
+  static void* dev_ptr[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return MB_ERR_UNSUPPORTED;
+  if (!dev_ptr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemsetAsync(ptr, 0, mb_gemm_counter_bytes(), stream);   // arrival counters start at zero
+    if (e != cudaSuccess) return (int)e;
+    dev_ptr[dev] = ptr;
+  }
+  MbGemmArgs b = *a;
+  b.ws = dev_ptr[dev];
+  b.ws_bytes = MB_NOALLOC_SCRATCH_BYTES;
+  b.no_cluster = 1;            // this variant is the workspace path by definition
+  b.tp_size = 0;
+  return mb_gemm(&b, stream);  // refuses with MB_ERR_TOO_LARGE when the workspace would not fit
+}
