@@ -1,0 +1,402 @@
+"""HTTP surface: OpenAI ``/v1/chat/completions``, ``/v1/completions``, ``/v1/responses``,
+``/v1/models``; Anthropic ``/v1/messages`` (+ ``/count_tokens``); ``/tokenize``, ``/health``,
+``/health/live``, ``/metrics`` (Prometheus), ``/serve-config``, ``/memory``. SSE streaming,
+usage blocks with the engine's timing extras, stop strings, logprobs, tool-call parsing,
+reasoning split, JSON-constrained decoding, bearer auth, rate limiting, GPU-fault gate.
+All three chat surfaces lower to one internal request (``_ChatJob``) like the reference's
+shared IR (``crates/server/src/main_modules/serve_router.rs:44-141``, ``api/chat/mod.rs``,
+``openai/chat_request.rs``, ``anthropic/types.rs``).
+"""
+from __future__ import annotations
+
+import contextlib
+import json
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+from fastapi import FastAPI, HTTPException, Request
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from ..sampling.params import SamplingParams
+from ..utils.telemetry import Telemetry
+from .chat_template import ChatRenderer
+from .engine_loop import AsyncEngine
+from .grammar import grammar_for_response_format
+from .ratelimit import RateLimiter
+from .reasoning_parser import ReasoningParser
+from .tool_parser import StreamingToolDetector, parse_tool_calls
+
+
+@dataclass
+class ServerConfig:
+    model_name: str = "model"
+    auth_tokens: List[str] = field(default_factory=list)
+    rate_per_s: float = 0.0
+    tool_call_parser: str = "hermes"
+    reasoning_format: str = "think"
+    default_max_tokens: int = 1024
+    tool_max_tokens: int = 8192
+    request_timeout_s: float = 300.0
+    telemetry: str = "basic"
+    disable_thinking: bool = False
+
+
+@dataclass
+class _ChatJob:
+    prompt_ids: List[int]
+    params: SamplingParams
+    tools: Optional[List[dict]] = None
+    thinking_open: bool = False
+    want_logprobs: bool = False
+    return_token_ids: bool = False
+
+
+def _sampling_from(body: Dict[str, Any], cfg: ServerConfig, max_key="max_tokens") -> SamplingParams:
+    stop = body.get("stop") or body.get("stop_sequences") or []
+    if isinstance(stop, str):
+        stop = [stop]
+    mt = body.get(max_key) or body.get("max_completion_tokens") or body.get("max_output_tokens")
+    if mt is None:
+        mt = cfg.tool_max_tokens if body.get("tools") else cfg.default_max_tokens
+    return SamplingParams(
+        max_tokens=int(mt), min_tokens=int(body.get("min_tokens") or 0),
+        temperature=float(body.get("temperature", 1.0) if body.get("temperature") is not None else 1.0),
+        top_k=int(body.get("top_k") or 0), top_p=float(body.get("top_p") or 1.0),
+        min_p=float(body.get("min_p") or 0.0), top_n_sigma=float(body.get("top_n_sigma") or 0.0),
+        repetition_penalty=float(body.get("repetition_penalty") or 1.0),
+        presence_penalty=float(body.get("presence_penalty") or 0.0),
+        frequency_penalty=float(body.get("frequency_penalty") or 0.0),
+        logit_bias={int(k): float(v) for k, v in (body.get("logit_bias") or {}).items()},
+        seed=body.get("seed"), stop=list(stop), logprobs=bool(body.get("logprobs")),
+        top_logprobs=int(body.get("top_logprobs") or 0),
+        timeout_s=float(body.get("timeout") or 0.0))
+
+
+def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=None) -> FastAPI:
+    cfg = cfg or ServerConfig()
+    aeng = AsyncEngine(engine, tokenizer, control)
+
+    @contextlib.asynccontextmanager
+    async def lifespan(_app):
+        aeng.start()
+        yield
+        aeng.shutdown(drain_s=15.0)        # drain in-flight requests, then stop the scheduler thread
+
+    app = FastAPI(title="metrale b200 engine", lifespan=lifespan)
+    tel = Telemetry(cfg.telemetry)
+    limiter = RateLimiter(cfg.rate_per_s)
+    renderer = ChatRenderer(getattr(tokenizer, "chat_template", None))
+    app.state.engine, app.state.async_engine, app.state.telemetry = engine, aeng, tel
+    eos = getattr(tokenizer, "eos_token_id", None)
+    engine.args.eos_token_id = engine.args.eos_token_id if engine.args.eos_token_id is not None else eos
+
+    @app.middleware("http")
+    async def gate(request: Request, call_next):
+        t0 = time.perf_counter()
+        path = request.url.path
+        open_paths = ("/health", "/health/live", "/metrics")
+        if path not in open_paths:
+            if aeng.fatal or engine.fault.is_set():
+                return JSONResponse({"error": {"message": aeng.fatal or engine.fault.reason(), "type": "gpu_fault"}}, 503)
+            key = request.headers.get("authorization", "").removeprefix("Bearer ").strip() or \
+                request.headers.get("x-api-key", "")
+            if cfg.auth_tokens and key not in cfg.auth_tokens:
+                return JSONResponse({"error": {"message": "invalid API key", "type": "authentication_error"}}, 401)
+            if not limiter.allow(key or (request.client.host if request.client else "anon")):
+                return JSONResponse({"error": {"message": "rate limit exceeded", "type": "rate_limit_error"}}, 429)
+        try:
+            resp = await call_next(request)
+        except Exception as e:                      # handler panic -> 500, server stays up
+            tel.inc("http_500")
+            return JSONResponse({"error": {"message": f"{type(e).__name__}: {e}", "type": "internal_error"}}, 500)
+        tel.inc("http_requests")
+        tel.observe_ms("http_latency", (time.perf_counter() - t0) * 1e3)
+        return resp
+
+    # ------------------------------------------------------------------ plumbing
+    def _job_from_chat(body: Dict[str, Any], messages, system=None, tools=None) -> _ChatJob:
+        msgs = list(messages)
+        if system:
+            msgs = [{"role": "system", "content": system}] + msgs
+        thinking = body.get("enable_thinking")
+        if thinking is None:
+            th = body.get("thinking")
+            thinking = bool(th and (th is True or th.get("type") == "enabled"))
+        thinking = bool(thinking) and not cfg.disable_thinking
+        kw = body.get("chat_template_kwargs") or {}
+        text = renderer.render(msgs, tools=tools, add_generation_prompt=True, enable_thinking=thinking, **kw)
+        ids = tokenizer.encode(text)
+        sp = _sampling_from(body, cfg)
+        sp.grammar = grammar_for_response_format(body.get("response_format"), tokenizer, eos)
+        return _ChatJob(ids, sp, tools, thinking, bool(body.get("logprobs")), bool(body.get("return_token_ids")))
+
+    async def _collect(job: _ChatJob):
+        text, ids, usage, reason, lps = "", [], None, None, None
+        async for ev in aeng.submit(job.prompt_ids, job.params):
+            if ev.error:
+                raise HTTPException(500 if "fault" in (ev.error or "") else 400, ev.error)
+            text += ev.text
+            ids += ev.token_ids
+            if ev.finished:
+                usage, reason, lps = ev.usage, ev.finish_reason, ev.logprobs
+        return text, ids, usage, reason, lps
+
+    def _split_outputs(job: _ChatJob, text: str):
+        rp = ReasoningParser(cfg.reasoning_format, starts_open=job.thinking_open)
+        r, c = rp.push(text)
+        r2, c2 = rp.flush()
+        reasoning, content = r + r2, c + c2
+        calls = []
+        if job.tools:
+            content, calls = parse_tool_calls(content, cfg.tool_call_parser, job.tools)
+        return reasoning, content, calls
+
+    def _lp_block(ids, lps):
+        if not lps:
+            return None
+        return {"content": [{"token": tokenizer.decode([t], False), "logprob": lp, "bytes": None, "top_logprobs": []}
+                            for t, lp in zip(ids, lps)]}
+
+    # ------------------------------------------------------------------ OpenAI
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": cfg.model_name, "object": "model", "owned_by": "metrale-b200",
+                                            "max_model_len": engine.sched_cfg.max_model_len}]}
+
+    @app.post("/v1/chat/completions")
+    async def chat(request: Request):
+        body = await request.json()
+        if not body.get("messages"):
+            raise HTTPException(400, "messages is required")
+        job = _job_from_chat(body, body["messages"], tools=body.get("tools"))
+        rid, created = "chatcmpl-" + uuid.uuid4().hex[:24], int(time.time())
+        if not body.get("stream"):
+            text, ids, usage, reason, lps = await _collect(job)
+            reasoning, content, calls = _split_outputs(job, text)
+            msg: Dict[str, Any] = {"role": "assistant", "content": content or (None if calls else "")}
+            if reasoning:
+                msg["reasoning_content"] = reasoning
+            if calls:
+                msg["tool_calls"] = calls
+                reason = "tool_calls"
+            choice = {"index": 0, "message": msg, "finish_reason": reason, "logprobs": _lp_block(ids, lps)}
+            if job.return_token_ids:
+                choice["token_ids"] = ids
+            return {"id": rid, "object": "chat.completion", "created": created, "model": cfg.model_name,
+                    "choices": [choice], "usage": usage}
+
+        include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
+
+        async def gen():
+            def chunk(delta, finish=None, usage=None):
+                d = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": cfg.model_name,
+                     "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+                if usage is not None:
+                    d["usage"] = usage
+                return f"data: {json.dumps(d)}\n\n"
+            yield chunk({"role": "assistant", "content": ""})
+            rp = ReasoningParser(cfg.reasoning_format, starts_open=job.thinking_open)
+            td = StreamingToolDetector() if job.tools else None
+            final_usage, reason = None, None
+            async for ev in aeng.submit(job.prompt_ids, job.params):
+                if ev.error:
+                    yield f"data: {json.dumps({'error': {'message': ev.error}})}\n\n"
+                    break
+                r, c = rp.push(ev.text)
+                if ev.finished:
+                    r2, c2 = rp.flush()
+                    r, c = r + r2, c + c2
+                if td is not None:
+                    c = td.push(c)
+                if r:
+                    yield chunk({"reasoning_content": r})
+                if c:
+                    yield chunk({"content": c})
+                if ev.finished:
+                    final_usage, reason = ev.usage, ev.finish_reason
+            if td is not None:
+                held = td.finish()
+                if held:
+                    rest, calls = parse_tool_calls(held, cfg.tool_call_parser, job.tools)
+                    if rest:
+                        yield chunk({"content": rest})
+                    for i, cl in enumerate(calls):
+                        yield chunk({"tool_calls": [dict(cl, index=i)]})
+                    if calls:
+                        reason = "tool_calls"
+            yield chunk({}, finish=reason or "stop")
+            if include_usage and final_usage:
+                d = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": cfg.model_name,
+                     "choices": [], "usage": final_usage}
+                yield f"data: {json.dumps(d)}\n\n"
+            yield "data: [DONE]\n\n"
+        return StreamingResponse(gen(), media_type="text/event-stream")
+
+    @app.post("/v1/completions")
+    async def completions(request: Request):
+        body = await request.json()
+        prompt = body.get("prompt")
+        if prompt is None:
+            raise HTTPException(400, "prompt is required")
+        ids = prompt if (isinstance(prompt, list) and prompt and isinstance(prompt[0], int)) else \
+            tokenizer.encode(prompt if isinstance(prompt, str) else prompt[0])
+        sp = _sampling_from(body, cfg)
+        if body.get("ignore_eos"):
+            sp.ignore_eos = True
+        job = _ChatJob(ids, sp)
+        rid, created = "cmpl-" + uuid.uuid4().hex[:24], int(time.time())
+        if not body.get("stream"):
+            text, out_ids, usage, reason, lps = await _collect(job)
+            ch = {"index": 0, "text": text, "finish_reason": reason, "logprobs": None}
+            if body.get("return_token_ids"):
+                ch["token_ids"] = out_ids
+            if lps:
+                ch["logprobs"] = {"token_logprobs": lps, "tokens": [tokenizer.decode([t], False) for t in out_ids]}
+            return {"id": rid, "object": "text_completion", "created": created, "model": cfg.model_name,
+                    "choices": [ch], "usage": usage}
+
+        async def gen():
+            usage = None
+            async for ev in aeng.submit(job.prompt_ids, job.params):
+                if ev.error:
+                    yield f"data: {json.dumps({'error': {'message': ev.error}})}\n\n"
+                    break
+                d = {"id": rid, "object": "text_completion", "created": created, "model": cfg.model_name,
+                     "choices": [{"index": 0, "text": ev.text, "finish_reason": ev.finish_reason if ev.finished else None}]}
+                if ev.finished:
+                    d["usage"] = ev.usage
+                yield f"data: {json.dumps(d)}\n\n"
+            yield "data: [DONE]\n\n"
+        return StreamingResponse(gen(), media_type="text/event-stream")
+
+    @app.post("/v1/responses")
+    async def responses(request: Request):
+        body = await request.json()
+        inp = body.get("input")
+        messages = [{"role": "user", "content": inp}] if isinstance(inp, str) else [
+            {"role": m.get("role", "user"), "content": m.get("content")} for m in (inp or [])]
+        job = _job_from_chat(body, messages, system=body.get("instructions"), tools=body.get("tools"))
+        text, ids, usage, reason, _ = await _collect(job)
+        reasoning, content, calls = _split_outputs(job, text)
+        out = []
+        if reasoning:
+            out.append({"type": "reasoning", "id": "rs_" + uuid.uuid4().hex[:16], "summary": [{"type": "summary_text", "text": reasoning}]})
+        out.append({"type": "message", "id": "msg_" + uuid.uuid4().hex[:16], "role": "assistant", "status": "completed",
+                    "content": [{"type": "output_text", "text": content, "annotations": []}]})
+        for c in calls:
+            out.append({"type": "function_call", "call_id": c["id"], "name": c["function"]["name"],
+                        "arguments": c["function"]["arguments"]})
+        u = usage or {}
+        return {"id": "resp_" + uuid.uuid4().hex[:24], "object": "response", "created_at": int(time.time()),
+                "model": cfg.model_name, "status": "completed", "output": out,
+                "usage": {"input_tokens": u.get("prompt_tokens"), "output_tokens": u.get("completion_tokens"),
+                          "total_tokens": u.get("total_tokens")}}
+
+    # ------------------------------------------------------------------ Anthropic
+    @app.post("/v1/messages")
+    async def messages(request: Request):
+        body = await request.json()
+        if "max_tokens" not in body:
+            raise HTTPException(400, "max_tokens is required")
+        tools = [{"type": "function", "function": {"name": t["name"], "description": t.get("description", ""),
+                                                   "parameters": t.get("input_schema", {})}} for t in body.get("tools", [])] or None
+        job = _job_from_chat(body, body.get("messages", []), system=body.get("system"), tools=tools)
+        mid = "msg_" + uuid.uuid4().hex[:24]
+
+        def blocks(reasoning, content, calls):
+            out = []
+            if reasoning:
+                out.append({"type": "thinking", "thinking": reasoning})
+            if content:
+                out.append({"type": "text", "text": content})
+            for c in calls:
+                out.append({"type": "tool_use", "id": c["id"].replace("call_", "toolu_"), "name": c["function"]["name"],
+                            "input": json.loads(c["function"]["arguments"] or "{}")})
+            return out
+        stop_map = {"stop": "end_turn", "length": "max_tokens", "tool_calls": "tool_use"}
+        if not body.get("stream"):
+            text, ids, usage, reason, _ = await _collect(job)
+            reasoning, content, calls = _split_outputs(job, text)
+            u = usage or {}
+            hit = None
+            if reason == "stop" and job.params.stop:
+                reason, hit = "stop_sequence", None
+            return {"id": mid, "type": "message", "role": "assistant", "model": cfg.model_name,
+                    "content": blocks(reasoning, content, calls),
+                    "stop_reason": "tool_use" if calls else (reason if reason == "stop_sequence" else stop_map.get(reason, reason)),
+                    "stop_sequence": hit,
+                    "usage": {"input_tokens": u.get("prompt_tokens"), "output_tokens": u.get("completion_tokens"),
+                              "cache_read_input_tokens": (u.get("prompt_tokens_details") or {}).get("cached_tokens", 0)}}
+
+        async def gen():
+            def sse(ev, data):
+                return f"event: {ev}\ndata: {json.dumps(data)}\n\n"
+            yield sse("message_start", {"type": "message_start", "message": {
+                "id": mid, "type": "message", "role": "assistant", "model": cfg.model_name, "content": [],
+                "stop_reason": None, "usage": {"input_tokens": len(job.prompt_ids), "output_tokens": 0}}})
+            yield sse("content_block_start", {"type": "content_block_start", "index": 0,
+                                              "content_block": {"type": "text", "text": ""}})
+            usage, reason = None, None
+            async for ev in aeng.submit(job.prompt_ids, job.params):
+                if ev.text:
+                    yield sse("content_block_delta", {"type": "content_block_delta", "index": 0,
+                                                      "delta": {"type": "text_delta", "text": ev.text}})
+                if ev.finished:
+                    usage, reason = ev.usage, ev.finish_reason
+            yield sse("content_block_stop", {"type": "content_block_stop", "index": 0})
+            yield sse("message_delta", {"type": "message_delta",
+                                        "delta": {"stop_reason": stop_map.get(reason, reason), "stop_sequence": None},
+                                        "usage": {"output_tokens": (usage or {}).get("completion_tokens", 0)}})
+            yield sse("message_stop", {"type": "message_stop"})
+        return StreamingResponse(gen(), media_type="text/event-stream")
+
+    @app.post("/v1/messages/count_tokens")
+    async def count_tokens(request: Request):
+        body = await request.json()
+        job = _job_from_chat({"max_tokens": 1}, body.get("messages", []), system=body.get("system"))
+        return {"input_tokens": len(job.prompt_ids)}
+
+    # ------------------------------------------------------------------ utility routes
+    @app.post("/tokenize")
+    async def tokenize(request: Request):
+        body = await request.json()
+        ids = tokenizer.encode(body.get("prompt") or body.get("text") or "")
+        return {"tokens": ids, "count": len(ids), "max_model_len": engine.sched_cfg.max_model_len}
+
+    @app.post("/detokenize")
+    async def detokenize(request: Request):
+        body = await request.json()
+        return {"prompt": tokenizer.decode(body.get("tokens", []))}
+
+    @app.get("/health")
+    async def health():
+        if aeng.fatal or engine.fault.is_set():
+            return JSONResponse({"status": "gpu_fault", "reason": aeng.fatal or engine.fault.reason()}, 503)
+        return {"status": "ok"}
+
+    @app.get("/health/live")
+    async def live():
+        return {"status": "alive"}
+
+    @app.get("/metrics")
+    async def metrics():
+        st = engine.stats()
+        flat = {f"engine_{k}": v for k, v in st.items() if isinstance(v, (int, float))}
+        return PlainTextResponse(tel.prometheus(flat))
+
+    @app.get("/serve-config")
+    async def serve_config():
+        a = engine.args
+        return {"model": cfg.model_name, "engine": {k: (v if isinstance(v, (int, float, str, bool, type(None))) else str(v))
+                                                     for k, v in vars(a).items()},
+                "model_config": json.loads(engine.cfg.to_json())}
+
+    @app.get("/memory")
+    async def memory():
+        st = engine.stats()
+        return {"weights_bytes": st.get("weights_bytes"), "kv_bytes": engine.runner.kv_bytes(),
+                "kv_blocks": st.get("kv_blocks"), "free_blocks": st.get("free_blocks")}
+
+    return app

@@ -1,0 +1,159 @@
+"""Command line: ``serve``, ``benchmark``, ``doctor``, ``dump-serve-options``.
+
+Role of the reference binary's subcommands (``crates/server/src/main.rs``,
+``main_modules/serve_router.rs``, ``main_modules/doctor.rs``): ``serve`` builds the engine and
+the HTTP app; ``benchmark`` drives the concurrency ladder through the public engine API;
+``doctor`` reports the device, driver, library and lever state without loading a model;
+``dump-serve-options`` prints every option with its default as JSON.
+
+Run as ``python -m metrale_inference_alpha_b200.server.cli <subcommand>``.
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+import os
+import sys
+from typing import List, Optional
+
+
+def _add_engine_args(p: argparse.ArgumentParser) -> None:
+    from ..engine.llm_engine import EngineArgs
+    for f in dataclasses.fields(EngineArgs):
+        name = "--" + f.name.replace("_", "-")
+        default = f.default
+        if f.name == "model":
+            p.add_argument(name, default="tiny-dense", help="preset name or checkpoint directory")
+        elif isinstance(default, bool):
+            p.add_argument(name, default=default, action=argparse.BooleanOptionalAction)
+        elif isinstance(default, int):
+            p.add_argument(name, type=int, default=default)
+        elif isinstance(default, float):
+            p.add_argument(name, type=float, default=default)
+        elif default is None:
+            p.add_argument(name, type=int, default=None)
+        else:
+            p.add_argument(name, default=default)
+
+
+def _engine_args(ns) -> "EngineArgs":
+    from ..engine.llm_engine import EngineArgs
+    kw = {f.name: getattr(ns, f.name) for f in dataclasses.fields(EngineArgs) if hasattr(ns, f.name)}
+    return EngineArgs(**kw)
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="metrale-b200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    s = sub.add_parser("serve", help="start the HTTP server")
+    _add_engine_args(s)
+    s.add_argument("--host", default="127.0.0.1")
+    s.add_argument("--port", type=int, default=8000)
+    s.add_argument("--served-model-name", default=None)
+    s.add_argument("--tokenizer", default=None, help="directory with tokenizer.json (default: the checkpoint)")
+    s.add_argument("--api-key", action="append", default=[])
+    s.add_argument("--rate-limit", type=float, default=0.0, help="requests per second per key; 0 = off")
+    s.add_argument("--tool-call-parser", default="hermes", choices=["hermes", "qwen3_xml", "mistral", "json"])
+    s.add_argument("--reasoning-format", default="think")
+    s.add_argument("--default-max-tokens", type=int, default=1024)
+    s.add_argument("--telemetry", default="basic", choices=["off", "basic", "full"])
+    s.add_argument("--disable-thinking", action="store_true")
+
+    b = sub.add_parser("benchmark", help="concurrency ladder over the engine API")
+    _add_engine_args(b)
+    b.add_argument("--concurrency", default="1,2,4,8,16,32,64,128")
+    b.add_argument("--isl", type=int, default=128)
+    b.add_argument("--osl", type=int, default=1024)
+    b.add_argument("--json", action="store_true")
+
+    d = sub.add_parser("doctor", help="report device, driver and library state")
+    d.add_argument("--json", action="store_true")
+
+    o = sub.add_parser("dump-serve-options", help="print every serve option and its default")
+    return ap
+
+
+def dump_serve_options() -> dict:
+    ap = build_parser()
+    serve = ap._subparsers._group_actions[0].choices["serve"]      # noqa: SLF001 (argparse has no public API)
+    out = {}
+    for a in serve._actions:
+        if a.dest in ("help",):
+            continue
+        out[a.option_strings[-1] if a.option_strings else a.dest] = {
+            "default": a.default, "help": a.help or "", "choices": list(a.choices) if a.choices else None}
+    from ..utils.levers import LEVERS
+    out["__env_levers__"] = dict(LEVERS)
+    return out
+
+
+def doctor() -> dict:
+    import torch
+    rep = {"python": sys.version.split()[0], "torch": torch.__version__, "cuda_runtime": torch.version.cuda,
+           "cuda_available": torch.cuda.is_available(), "devices": []}
+    if torch.cuda.is_available():
+        for i in range(torch.cuda.device_count()):
+            p = torch.cuda.get_device_properties(i)
+            free, total = torch.cuda.mem_get_info(i)
+            rep["devices"].append({"index": i, "name": p.name, "sm": f"{p.major}.{p.minor}", "sms": p.multi_processor_count,
+                                   "total_gb": round(total / 2**30, 1), "free_gb": round(free / 2**30, 1)})
+        rep["nccl"] = ".".join(map(str, torch.cuda.nccl.version()))
+        rep["p2p"] = (torch.cuda.device_count() > 1 and torch.cuda.can_device_access_peer(0, 1))
+    from ..ops import _native
+    lib = os.path.join(os.path.dirname(_native.__file__), "libmetrale_b200.so")
+    rep["native_library"] = {"path": lib, "present": os.path.exists(lib)}
+    from ..utils.levers import LEVERS, undeclared
+    rep["levers"] = {k: os.environ[k] for k in LEVERS if k in os.environ}
+    rep["undeclared_levers"] = undeclared()
+    rep["ok"] = not rep["undeclared_levers"] and (
+        (not torch.cuda.is_available()) or (rep["native_library"]["present"] and all(d["sm"] == "10.0" for d in rep["devices"])))
+    return rep
+
+
+def run_benchmark(ns) -> List[dict]:
+    from ..bench.ladder import run_ladder
+    return run_ladder(_engine_args(ns), [int(c) for c in ns.concurrency.split(",")], ns.isl, ns.osl)
+
+
+def serve(ns) -> None:
+    import uvicorn
+    from ..engine.llm_engine import LLMEngine
+    from .app import ServerConfig, create_app
+    from .tokenizer import load_tokenizer
+    eargs = _engine_args(ns)
+    engine = LLMEngine(eargs)
+    tok_dir = ns.tokenizer or (eargs.model if isinstance(eargs.model, str) and os.path.isdir(eargs.model) else None)
+    tokenizer = load_tokenizer(tok_dir, engine.cfg.vocab_size)
+    cfg = ServerConfig(model_name=ns.served_model_name or str(ns.model), auth_tokens=ns.api_key,
+                       rate_per_s=ns.rate_limit, tool_call_parser=ns.tool_call_parser,
+                       reasoning_format=ns.reasoning_format, default_max_tokens=ns.default_max_tokens,
+                       telemetry=ns.telemetry, disable_thinking=ns.disable_thinking)
+    app = create_app(engine, tokenizer, cfg)
+    uvicorn.run(app, host=ns.host, port=ns.port, log_level="info", timeout_graceful_shutdown=20)
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    ns = build_parser().parse_args(argv)
+    if ns.cmd == "serve":
+        serve(ns)
+    elif ns.cmd == "benchmark":
+        rows = run_benchmark(ns)
+        if ns.json:
+            print(json.dumps(rows))
+        else:
+            print(f"{'C':>4} {'tok/s':>10} {'p50 TTFT ms':>12} {'p99 TTFT ms':>12} {'ms/step':>9}")
+            for r in rows:
+                print(f"{r['concurrency']:>4} {r['tok_s']:>10.1f} {r['ttft_p50_ms']:>12.1f} {r['ttft_p99_ms']:>12.1f} {r['ms_per_step']:>9.2f}")
+    elif ns.cmd == "doctor":
+        rep = doctor()
+        print(json.dumps(rep, indent=None if ns.json else 2))
+        return 0 if rep["ok"] else 1
+    elif ns.cmd == "dump-serve-options":
+        print(json.dumps(dump_serve_options(), indent=2, default=str))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

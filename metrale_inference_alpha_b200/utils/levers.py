@@ -1,0 +1,32 @@
+"""Every ``METRALE_*`` environment lever the engine reads, declared in one table; starting with
+an undeclared ``METRALE_*`` variable set is refused (a typo must not silently do nothing).
+Role of ``crates/config/src/levers.rs:3-14``."""
+from __future__ import annotations
+
+import os
+from typing import Dict, List
+
+LEVERS: Dict[str, str] = {
+    "METRALE_PDL": "1 = launch kernels with programmatic stream serialization (default 0)",
+    "METRALE_B200_AUTOBUILD": "0 = never build the kernel library on import (default 1)",
+    "METRALE_COMM_DIAGNOSTICS": "1 = log every collective submission with a sequence number",
+    "METRALE_MTP_K_LADDER": "draft-width ladder 'width:k,...' (default 4:3,8:3,16:1,32:1)",
+    "METRALE_NO_MTP_K_LADDER": "1 = disable the draft-width ladder",
+    "METRALE_ATTN_PART_TOKENS": "split-KV partition size in tokens (default 512)",
+    "METRALE_DEBUG_SYNC_KERNELS": "1 = synchronise and check the status word after every step",
+    "METRALE_KV_POISON": "1 = fill fresh KV blocks with NaN bytes",
+    "METRALE_TELEMETRY": "off | basic | kernel",
+    "METRALE_NO_FUSED_COLLECTIVES": "1 = NCCL collectives after plain GEMMs",
+}
+
+
+def undeclared(environ=None) -> List[str]:
+    env = os.environ if environ is None else environ
+    return sorted(k for k in env if k.startswith("METRALE_") and k not in LEVERS)
+
+
+def check_environment(environ=None) -> None:
+    bad = undeclared(environ)
+    if bad:
+        raise SystemExit(f"undeclared METRALE_* environment variable(s): {', '.join(bad)}; "
+                         f"known levers: {', '.join(sorted(LEVERS))}")

@@ -1,0 +1,329 @@
+"""Request shaping and the HTTP surface on CPU: tokenizer + streaming detokeniser, chat
+template, reasoning split, tool-call parsers (with salvage and schema coercion), JSON
+grammar, rate limiter, levers, telemetry, CLI, and every route of the app driven through
+FastAPI's test client over the tiny dense model. Mirrors the reference's server test
+strategy (``crates/server/tests``: golden request / response shapes, SSE framing, auth)."""
+import json
+
+import pytest
+import torch
+
+from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+from metrale_inference_alpha_b200.server.chat_template import ChatRenderer
+from metrale_inference_alpha_b200.server.grammar import (JsonMatcher, TokenGrammar, grammar_for_response_format,
+                                                           validate_schema)
+from metrale_inference_alpha_b200.server.ratelimit import RateLimiter
+from metrale_inference_alpha_b200.server.reasoning_parser import ReasoningParser, split_reasoning
+from metrale_inference_alpha_b200.server.tokenizer import ByteTokenizer, IncrementalDetokenizer, load_tokenizer
+from metrale_inference_alpha_b200.server.tool_parser import StreamingToolDetector, parse_tool_calls
+from metrale_inference_alpha_b200.utils import levers
+from metrale_inference_alpha_b200.utils.telemetry import Telemetry
+
+TOOLS = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+    "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}}, "required": ["city"]}}}]
+
+
+# ---------------------------------------------------------------------------- tokenizer
+def test_byte_tokenizer_roundtrip_and_incremental_utf8():
+    tk = ByteTokenizer(4096)
+    s = "héllo wörld ✓ 你好"
+    ids = tk.encode(s)
+    assert tk.decode(ids) == s
+    d = IncrementalDetokenizer(tk)
+    out = "".join(d.push([i]) for i in ids) + d.flush()
+    assert out == s                                   # multi-byte characters never split
+    assert load_tokenizer(None, 512).vocab_size == 512
+
+
+# ---------------------------------------------------------------------------- templates
+def test_chat_template_default_and_custom():
+    r = ChatRenderer()
+    txt = r.render([{"role": "system", "content": "be brief"},
+                    {"role": "user", "content": [{"type": "text", "text": "hi"}, {"type": "text", "text": " there"}]}])
+    assert "be brief" in txt and "hi there" in txt and txt.rstrip().endswith("assistant")
+    with_tools = r.render([{"role": "user", "content": "x"}], tools=TOOLS)
+    assert "get_weather" in with_tools
+    custom = ChatRenderer("{% for m in messages %}[{{ m.role }}]{{ m.content }}{% endfor %}{% if add_generation_prompt %}[a]{% endif %}")
+    assert custom.render([{"role": "user", "content": "q"}]) == "[user]q[a]"
+
+
+# ---------------------------------------------------------------------------- reasoning
+def test_reasoning_split_whole_and_streamed_by_character():
+    text = "<think>step one\nstep two</think>The answer is 4."
+    assert split_reasoning(text) == ("step one\nstep two", "The answer is 4.")
+    p = ReasoningParser()
+    r = c = ""
+    for ch in text:
+        a, b = p.push(ch)
+        r, c = r + a, c + b
+    a, b = p.flush()
+    assert (r + a, c + b) == ("step one\nstep two", "The answer is 4.")
+    # template already opened the block
+    assert split_reasoning("inner</think>outer", starts_open=True) == ("inner", "outer")
+    assert split_reasoning("no tags at all") == ("", "no tags at all")
+    assert split_reasoning("never closes", starts_open=True) == ("never closes", "")
+
+
+# ---------------------------------------------------------------------------- tool calls
+def test_tool_parsers_primary_and_salvage():
+    hermes = 'Sure.<tool_call>\n{"name": "get_weather", "arguments": {"city": "Oslo", "days": "3"}}\n</tool_call>'
+    rest, calls = parse_tool_calls(hermes, "hermes", TOOLS)
+    assert rest == "Sure." and len(calls) == 1
+    args = json.loads(calls[0]["function"]["arguments"])
+    assert args == {"city": "Oslo", "days": 3}        # "3" coerced to the declared integer
+    assert calls[0]["id"].startswith("call_") and calls[0]["type"] == "function"
+
+    xml = "<tool_call>\n<function=get_weather>\n<parameter=city>\nRome\n</parameter>\n</function>\n</tool_call>"
+    _, calls = parse_tool_calls(xml, "qwen3_xml", TOOLS)
+    assert json.loads(calls[0]["function"]["arguments"]) == {"city": "Rome"}
+    _, calls = parse_tool_calls(xml, "hermes", TOOLS)               # wrong primary parser: salvaged
+    assert calls and calls[0]["function"]["name"] == "get_weather"
+
+    mistral = '[TOOL_CALLS] [{"name": "get_weather", "arguments": {"city": "Lima"}}]'
+    _, calls = parse_tool_calls(mistral, "mistral", TOOLS)
+    assert json.loads(calls[0]["function"]["arguments"])["city"] == "Lima"
+
+    bare = 'I will call {"name": "get_wether", "arguments": {"city": "Kyiv"}} now'
+    rest, calls = parse_tool_calls(bare, "hermes", TOOLS)
+    assert calls[0]["function"]["name"] == "get_weather"             # fuzzy name repair
+    assert "{" not in rest
+
+    assert parse_tool_calls("plain text", "hermes", TOOLS) == ("plain text", [])
+    thought = '<think>{"name": "get_weather", "arguments": {}}</think>done'
+    assert parse_tool_calls(thought, "hermes", TOOLS)[1] == []       # reasoning is not scanned
+
+
+def test_streaming_tool_detector_holds_back_markup():
+    d = StreamingToolDetector()
+    seen = ""
+    for ch in 'ok <tool_call>{"name": "f", "arguments": {}}</tool_call>':
+        seen += d.push(ch)
+    assert seen == "ok " and d.finish().startswith("<tool_call>")
+    d = StreamingToolDetector()
+    assert "".join(d.push(ch) for ch in "a < b and <tool") + d.finish() == "a < b and <tool"
+
+
+# ---------------------------------------------------------------------------- grammar
+@pytest.mark.parametrize("doc,ok", [
+    ('{"a": 1, "b": [true, null, -2.5e3], "c": {"d": "x\\n\\u00e9"}}', True),
+    ('  {"k": ""}  ', True), ('{}', True), ('{"a": 01}', False), ('{"a": 1,}', False),
+    ('{a: 1}', False), ('{"a": tru}', False), ('{"a": "x}', False), ('[1, 2]', False)])
+def test_json_matcher_accepts_exactly_valid_objects(doc, ok):
+    m = JsonMatcher(require_object=True)
+    fed = m.feed_bytes(doc.encode())
+    assert (fed and m.is_complete()) == ok
+
+
+def test_token_grammar_drives_a_random_model_to_valid_json():
+    tk = ByteTokenizer(512)
+    g = TokenGrammar(tk, JsonMatcher(require_object=True), eos_token_id=0)
+    gen = torch.Generator().manual_seed(3)
+    out = []
+    for _ in range(400):
+        logits = torch.randn(512, generator=gen)
+        if len(out) > 40:
+            logits[0] += 50.0                        # the model "wants" to stop
+            logits[ord("}")] += 20.0
+            logits[ord('"')] += 10.0
+        g.observe_logits(logits)
+        mask = g.allowed_mask(512)
+        assert mask.any()
+        t = int(torch.where(mask, logits, torch.full_like(logits, -1e30)).argmax())
+        if t == 0:
+            break
+        g.advance(t)
+        out.append(t)
+    doc = tk.decode(out)
+    assert isinstance(json.loads(doc), dict)
+    assert grammar_for_response_format({"type": "text"}, tk) is None
+    assert grammar_for_response_format({"type": "json_object"}, tk, 0) is not None
+
+
+def test_validate_schema_subset():
+    sch = {"type": "object", "required": ["n"], "properties": {"n": {"type": "integer"}, "t": {"enum": ["a", "b"]},
+                                                               "l": {"type": "array", "items": {"type": "number"}}}}
+    assert validate_schema({"n": 1, "t": "a", "l": [1, 2.5]}, sch)
+    assert not validate_schema({"t": "a"}, sch)
+    assert not validate_schema({"n": True}, sch)
+    assert not validate_schema({"n": 1, "t": "z"}, sch)
+    assert not validate_schema({"n": 1, "l": ["x"]}, sch)
+    assert validate_schema(3, {"anyOf": [{"type": "string"}, {"type": "integer"}]})
+
+
+# ---------------------------------------------------------------------------- small utilities
+def test_rate_limiter_token_bucket():
+    t = [0.0]
+    rl = RateLimiter(2.0, burst=2, clock=lambda: t[0])
+    assert rl.allow("k") and rl.allow("k") and not rl.allow("k")
+    assert rl.allow("other")
+    t[0] = 0.6
+    assert rl.allow("k") and not rl.allow("k")
+    assert RateLimiter(0.0).allow("x")
+
+
+def test_undeclared_levers_are_refused():
+    assert levers.undeclared({"METRALE_PDL": "1", "PATH": "/bin"}) == []
+    assert levers.undeclared({"METRALE_PDLL": "1"}) == ["METRALE_PDLL"]
+    with pytest.raises(SystemExit):
+        levers.check_environment({"METRALE_TYPO": "1"})
+
+
+def test_telemetry_prometheus_text():
+    t = Telemetry("basic")
+    t.inc("requests")
+    t.inc("requests", 2)
+    t.set("queue_depth", 5)
+    t.observe_ms("step", 2.0)
+    t.observe_ms("step", 4.0)
+    with t.span("load"):
+        pass
+    text = t.prometheus({"engine_steps": 7})
+    assert "metrale_requests_total 3" in text and "metrale_queue_depth 5" in text and "metrale_engine_steps 7" in text
+    assert "step" in text
+    off = Telemetry("off")
+    off.inc("x")
+    assert "metrale_x_total" not in off.prometheus()
+
+
+def test_cli_dump_options_and_doctor():
+    from metrale_inference_alpha_b200.server import cli
+    opts = cli.dump_serve_options()
+    assert "--port" in opts and "--max-num-seqs" in opts and "METRALE_PDL" in opts["__env_levers__"]
+    rep = cli.doctor()
+    assert "torch" in rep and "native_library" in rep
+    ns = cli.build_parser().parse_args(["serve", "--model", "tiny-dense", "--max-num-seqs", "4", "--no-use-cuda-graphs"])
+    ea = cli._engine_args(ns)
+    assert ea.max_num_seqs == 4 and ea.use_cuda_graphs is False
+
+
+def test_bench_ladder_on_cpu():
+    from metrale_inference_alpha_b200.bench.ladder import run_ladder
+    rows = run_ladder(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=128), [1, 3], isl=12, osl=6)
+    assert [r["concurrency"] for r in rows] == [1, 3]
+    assert rows[1]["tokens"] == 18 and rows[1]["tok_s"] > 0 and rows[1]["ttft_p50_ms"] > 0
+
+
+# ---------------------------------------------------------------------------- HTTP surface
+@pytest.fixture(scope="module")
+def client():
+    from fastapi.testclient import TestClient
+    from metrale_inference_alpha_b200.server.app import ServerConfig, create_app
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=8, max_model_len=512))
+    tok = load_tokenizer(None, eng.cfg.vocab_size)
+    app = create_app(eng, tok, ServerConfig(model_name="tiny", auth_tokens=["sekret"]))
+    with TestClient(app) as c:
+        c.headers.update({"Authorization": "Bearer sekret"})
+        yield c
+
+
+def test_health_models_auth(client):
+    assert client.get("/health").json()["status"] == "ok"
+    assert client.get("/health/live").status_code == 200
+    assert client.get("/v1/models").json()["data"][0]["id"] == "tiny"
+    r = client.get("/v1/models", headers={"Authorization": "Bearer wrong"})
+    assert r.status_code == 401 and r.json()["error"]["type"] == "authentication_error"
+    assert client.get("/v1/models", headers={"Authorization": "", "x-api-key": "sekret"}).status_code == 200
+
+
+def test_chat_completion_shape_usage_and_determinism(client):
+    body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 8, "temperature": 0, "return_token_ids": True}
+    a = client.post("/v1/chat/completions", json=body).json()
+    b = client.post("/v1/chat/completions", json=body).json()
+    assert a["object"] == "chat.completion" and a["choices"][0]["finish_reason"] == "length"
+    assert a["choices"][0]["token_ids"] == b["choices"][0]["token_ids"] and len(a["choices"][0]["token_ids"]) == 8
+    u = a["usage"]
+    assert u["completion_tokens"] == 8 and u["total_tokens"] == u["prompt_tokens"] + 8
+    for k in ("time_to_first_token_ms", "decode_time_ms", "total_time_ms", "response_tokens_per_second"):
+        assert k in u
+    assert b["usage"]["prompt_tokens_details"]["cached_tokens"] > 0      # second call hits the prefix cache
+    assert client.post("/v1/chat/completions", json={"max_tokens": 1}).status_code == 400
+
+
+def test_chat_streaming_sse_framing(client):
+    body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 5, "stream": True,
+            "stream_options": {"include_usage": True}}
+    with client.stream("POST", "/v1/chat/completions", json=body) as s:
+        lines = [l for l in s.iter_lines() if l]
+    assert all(l.startswith("data: ") for l in lines) and lines[-1] == "data: [DONE]"
+    chunks = [json.loads(l[6:]) for l in lines[:-1]]
+    assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    assert chunks[-1]["choices"] == [] and chunks[-1]["usage"]["completion_tokens"] == 5
+    assert chunks[-2]["choices"][0]["finish_reason"] == "length"
+
+
+def test_completions_logprobs_stop_and_stream(client):
+    r = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 6, "logprobs": True, "return_token_ids": True}).json()
+    ch = r["choices"][0]
+    assert len(ch["token_ids"]) == 6 and len(ch["logprobs"]["token_logprobs"]) == 6
+    assert all(lp <= 0 for lp in ch["logprobs"]["token_logprobs"])
+    r = client.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 3}).json()
+    assert r["usage"]["prompt_tokens"] == 3
+    with client.stream("POST", "/v1/completions", json={"prompt": "abc", "max_tokens": 3, "stream": True}) as s:
+        lines = [l for l in s.iter_lines() if l]
+    assert lines[-1] == "data: [DONE]" and "usage" in json.loads(lines[-2][6:])
+
+
+def test_sampling_fields_reach_the_sampler(client):
+    body = {"prompt": "xyz", "max_tokens": 6, "temperature": 0.9, "top_p": 0.9, "top_k": 20, "seed": 11,
+            "repetition_penalty": 1.1, "presence_penalty": 0.2, "return_token_ids": True}
+    a = client.post("/v1/completions", json=body).json()["choices"][0]["token_ids"]
+    b = client.post("/v1/completions", json=body).json()["choices"][0]["token_ids"]
+    assert a == b                                    # seeded sampling is reproducible
+    body["seed"] = 12
+    c = client.post("/v1/completions", json=body).json()["choices"][0]["token_ids"]
+    assert len(c) == 6
+
+
+def test_json_mode_returns_a_json_object(client):
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "json please"}],
+                                                  "max_tokens": 48, "response_format": {"type": "json_object"},
+                                                  "temperature": 0}).json()
+    text = r["choices"][0]["message"]["content"]
+    m = JsonMatcher(require_object=True)
+    assert m.feed_bytes(text.encode())               # always a legal prefix of a JSON object
+    if r["choices"][0]["finish_reason"] == "stop":
+        assert isinstance(json.loads(text), dict)
+
+
+def test_anthropic_messages_and_count_tokens(client):
+    body = {"model": "tiny", "max_tokens": 5, "system": "be brief", "messages": [{"role": "user", "content": "hi"}]}
+    r = client.post("/v1/messages", json=body).json()
+    assert r["type"] == "message" and r["role"] == "assistant" and r["stop_reason"] == "max_tokens"
+    assert r["usage"]["output_tokens"] == 5 and r["usage"]["input_tokens"] > 0
+    n = client.post("/v1/messages/count_tokens", json=body).json()["input_tokens"]
+    assert n == r["usage"]["input_tokens"]
+    assert client.post("/v1/messages", json={"messages": []}).status_code == 400
+    with client.stream("POST", "/v1/messages", json=dict(body, stream=True)) as s:
+        events = [l[7:] for l in s.iter_lines() if l.startswith("event: ")]
+    assert events[0] == "message_start" and events[-1] == "message_stop" and "message_delta" in events
+
+
+def test_responses_api(client):
+    r = client.post("/v1/responses", json={"input": "hi", "instructions": "short", "max_output_tokens": 4}).json()
+    assert r["object"] == "response" and r["status"] == "completed"
+    assert r["output"][-1]["type"] == "message" and r["usage"]["output_tokens"] == 4
+
+
+def test_tokenize_metrics_config_memory(client):
+    t = client.post("/tokenize", json={"prompt": "abc"}).json()
+    assert t["count"] == 3 and client.post("/detokenize", json={"tokens": t["tokens"]}).json()["prompt"] == "abc"
+    m = client.get("/metrics").text
+    assert "metrale_http_requests_total" in m and "metrale_engine_decode_tokens" in m
+    cfg = client.get("/serve-config").json()
+    assert cfg["engine"]["max_num_seqs"] == 8 and cfg["model_config"]["num_layers"] >= 1
+    mem = client.get("/memory").json()
+    assert mem["kv_bytes"] > 0 and mem["weights_bytes"] > 0
+
+
+def test_gpu_fault_latch_turns_routes_into_503(client):
+    eng = client.app.state.engine
+    eng.fault.set("injected on the host")
+    try:
+        assert client.get("/health").status_code == 503
+        r = client.post("/v1/completions", json={"prompt": "a", "max_tokens": 1})
+        assert r.status_code == 503 and r.json()["error"]["type"] == "gpu_fault"
+        assert client.get("/health/live").status_code == 200
+    finally:
+        eng.fault._reason = None if hasattr(eng.fault, "_reason") else None
+        eng.fault.__init__()
+    assert client.get("/health").status_code == 200
