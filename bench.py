@@ -1,7 +1,10 @@
 #!/usr/bin/env python
 """Headline benchmark: aggregate decode tokens/s of the dense ~27B NVFP4 model (fp8 KV) at
 concurrency C (default 128, the top rung of the reference's ISL128/OSL1024 ladder) on N GPUs
-of one node (tensor parallel over NVLink).
+of one node. For N > 1 the default is one engine replica per GPU, each serving its own C
+requests (the model fits one GPU, so replicas are the throughput deployment; the job's value is
+the sum over replicas, weak scaling); `--parallelism tp` shards one engine over the N GPUs with
+the fused GEMM + all-reduce kernels over NVLink peer memory (C requests in total, strong scaling).
 
     python bench.py --gpus 1 --steps 64 --warmup 8
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -111,6 +114,10 @@ def main() -> int:
     ap.add_argument("--no-fast-forward", action="store_true")
     ap.add_argument("--no-fused", action="store_true", help="NCCL(+library-free GEMM) baseline collectives")
     ap.add_argument("--ladder", action="store_true", help="also print one line per concurrency rung")
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                    help="N>1: dp = one engine replica per GPU, each serving C requests (weak scaling, the "
+                         "throughput deployment of a model that fits one GPU); tp = one engine sharded over "
+                         "N GPUs with the fused GEMM+all-reduce kernels, C requests in total (strong scaling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -127,11 +134,14 @@ def main() -> int:
     torch.cuda.set_device(local)
     dev = f"cuda:{local}"
     tp = None
+    use_tp = world > 1 and args.parallelism == "tp"
+    replicas = world if not use_tp else 1
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(dev))
-        from metrale_inference_alpha_b200.parallel.tp import NcclTpContext
-        tp = NcclTpContext(rank, world, dev, fused=not args.no_fused)
+        if use_tp:
+            from metrale_inference_alpha_b200.parallel.tp import NcclTpContext
+            tp = NcclTpContext(rank, world, dev, fused=not args.no_fused)
 
     from metrale_inference_alpha_b200 import ops
     from metrale_inference_alpha_b200.config.model_config import preset
@@ -160,8 +170,8 @@ def main() -> int:
         if eng is None:
             eng = LLMEngine(EngineArgs(model=cfg, device=dev, max_num_seqs=128, max_model_len=ctx_len,
                                        max_prefill_tokens=8192, enable_prefix_caching=True,
-                                       gpu_memory_utilization=0.85, tp_size=world, seed=0), tp=tp)
-        g = torch.Generator().manual_seed(42)
+                                       gpu_memory_utilization=0.85, tp_size=world if use_tp else 1, seed=0), tp=tp)
+        g = torch.Generator().manual_seed(42 + (0 if use_tp else rank))
         prompts = [torch.randint(0, cfg.vocab_size, (args.isl,), generator=g).tolist() for _ in range(C)]
         sp = SamplingParams(max_tokens=args.osl, temperature=0.0, ignore_eos=True)
         barrier()
@@ -227,9 +237,9 @@ def main() -> int:
         for s in list(eng.scheduler.running):
             eng.abort(s.req.request_id)
         tt = sorted(ttfts.values())
-        return dict(C=C, tok_s=C * steps / dev_s, ms_per_step=dev_s / steps * 1e3,
-                    e2e_tok_s=e2e_tokens / e2e_s, e2e_ms_per_step=e2e_s / steps * 1e3, h2d=h2d, d2h=d2h,
-                    launches=launches_per_step * steps, clocks=clocks, ctx=ctx_mid, ff=ff,
+        return dict(C=C, tok_s=replicas * C * steps / dev_s, ms_per_step=dev_s / steps * 1e3,
+                    e2e_tok_s=replicas * e2e_tokens / e2e_s, e2e_ms_per_step=e2e_s / steps * 1e3, h2d=h2d, d2h=d2h,
+                    launches=launches_per_step * steps * world, clocks=clocks, ctx=ctx_mid, ff=ff,
                     ttft_p50_ms=tt[len(tt) // 2] if tt else None, eng=eng)
 
     C = args.concurrency
@@ -239,17 +249,17 @@ def main() -> int:
         "metric": "aggregate decode tok/s at C=%d (ISL128/OSL1024), dense 27B NVFP4, fp8 KV" % C,
         "value": round(r["tok_s"], 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": round(r["tok_s"] / BASELINE_TOKS.get(C, BASELINE_TOKS[128]), 3),
+        "scaling": "strong" if use_tp else "weak", "vs_baseline": round(r["tok_s"] / BASELINE_TOKS.get(C, BASELINE_TOKS[128]), 3),
         "dtype": "nvfp4 weights x nvfp4 activations (fp32 accumulate), bf16 lm_head, fp8 KV",
         "data": "synthetic: random-init N(0,0.02) weights in NVFP4 checkpoint layout, uniform-random prompts (seed 42)",
         "config": {"model": cfg.name, "layers": cfg.num_layers, "hidden": cfg.hidden_size,
-                   "global_batch": C, "seq_len": args.isl, "osl": args.osl, "context": ctx_len,
+                   "global_batch": C * replicas, "per_gpu_batch": C if not use_tp else None, "seq_len": args.isl, "osl": args.osl, "context": ctx_len,
                    "mean_ctx_in_timed_window": r["ctx"], "fast_forward_steps": r["ff"],
-                   "parallelism": f"tp{world}", "l2": "inputs larger than L2 (weights %.1f GB + KV per step)" % (eng.weights.nbytes() / 1e9),
+                   "parallelism": (f"tp{world}" if use_tp else f"dp{world}"), "l2": "inputs larger than L2 (weights %.1f GB + KV per step)" % (eng.weights.nbytes() / 1e9),
                    "fused_collectives": bool(tp is not None and getattr(tp, "fused", False)),
                    "speculative": "off (MTP gate: random-init drafts never accepted)"},
         "e2e": {"value": round(r["e2e_tok_s"], 2), "unit": "tokens/s", "ms_per_step": round(r["e2e_ms_per_step"], 4),
-                "h2d_bytes_per_step": int(r["h2d"]), "d2h_bytes_per_step": int(r["d2h"])},
+                "h2d_bytes_per_step": int(r["h2d"]) * replicas, "d2h_bytes_per_step": int(r["d2h"]) * replicas},
         "gpu_launches": int(r["launches"]),
         "clocks": r["clocks"],
         "ttft_p50_ms": None if r["ttft_p50_ms"] is None else round(r["ttft_p50_ms"], 1),

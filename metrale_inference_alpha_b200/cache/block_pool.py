@@ -100,7 +100,8 @@ class PagedKvCache:
         self.cfg = cfg
         self.num_blocks = num_blocks
         self.device = torch.device(device)
-        self.allocator = BlockAllocator(num_blocks)
+        from . import make_allocator
+        self.allocator = make_allocator(num_blocks)
         dt = torch.uint8 if cfg.dtype == "fp8" else torch.bfloat16
         shape_k = (num_blocks, cfg.block_size, cfg.kv_heads, cfg.head_dim)
         shape_v = (num_blocks, cfg.block_size, cfg.kv_heads, cfg.v_head_dim or cfg.head_dim)

@@ -14,7 +14,8 @@ from typing import Dict, Iterable, List, Optional, Sequence as Seq, Union
 
 import torch
 
-from ..cache import RadixTree
+from .. import ops
+from ..cache import RadixTree, make_radix  # noqa: F401
 from ..config.model_config import ModelConfig, preset as cfg_preset
 from ..models.decoder import TpContext
 from ..sampling.params import SamplingParams
@@ -84,12 +85,15 @@ class LLMEngine:
         # never more than every sequence at full length needs (plus headroom for the prefix cache)
         cap = (self.sched_cfg.max_model_len // args.block_size + 1) * args.max_num_seqs * 2 + 64
         blocks = min(blocks, cap)
+        # the batch cap is a deployment constant, so the partitioning (and with it the numerics of
+        # a sequence) still never depends on which other requests happen to be running
+        ops.configure(attn_part_tokens=1024 if args.max_num_seqs >= 64 else 512)
         self.runner = ModelRunner(cfg, self.weights, args.device, blocks, self.sched_cfg, self.tp,
                                   use_graphs=args.use_cuda_graphs, kv_poison=args.kv_poison)
         needs_snap = self.runner.pool is not None
         self.prefix = None
         if args.enable_prefix_caching:
-            self.prefix = RadixTree(self.runner.kv.allocator, args.block_size, needs_snapshot=needs_snap,
+            self.prefix = make_radix(self.runner.kv.allocator, args.block_size, needs_snapshot=needs_snap,
                                     on_snapshot_evict=(self.runner.pool.release_snapshot if needs_snap else None))
         self.scheduler = SchedulerCore(self.sched_cfg, self.runner.kv.allocator, self.prefix, self.runner.pool)
         self._ids = itertools.count(1)

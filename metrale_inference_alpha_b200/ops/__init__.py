@@ -8,6 +8,8 @@ granularity), so CPU and GPU agree to accumulation-order noise.
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 import math
 from dataclasses import dataclass
@@ -592,6 +594,20 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, *, Hq: int, Hkv: int, D: int, positi
     return q_out
 
 
+# split-KV partition size (tokens); a function of nothing but this lever, so a sequence's
+# partitioning -- and therefore its numerics -- never depends on the rest of the batch
+_ATTN_PART_TOKENS = int(os.environ.get("METRALE_ATTN_PART_TOKENS", "0") or 0)
+
+
+def configure(attn_part_tokens: Optional[int] = None) -> None:
+    """Deployment constants of the kernel library. ``attn_part_tokens``: split-KV partition size;
+    larger partitions amortise the per-CTA prologue and merge when the batch alone fills the GPU,
+    smaller ones give short batches more CTAs. The environment lever wins over this call."""
+    global _ATTN_PART_TOKENS
+    if attn_part_tokens is not None and "METRALE_ATTN_PART_TOKENS" not in os.environ:
+        _ATTN_PART_TOKENS = int(attn_part_tokens)
+
+
 def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_len, ctx_len, *,
                     max_q_len: int, max_ctx: int, scale: float, k_scale=None, v_scale=None,
                     window: int = 0, force_mode: int = 0, part_tokens: int = 0) -> torch.Tensor:
@@ -604,6 +620,8 @@ def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_l
     rt = runtime(q.device)
     nb, bs, Hkv, _ = k_cache.shape
     G = Hq // Hkv
+    if part_tokens == 0:
+        part_tokens = _ATTN_PART_TOKENS
     out = torch.empty_like(q)
     S = q_len.numel()
     if force_mode == 0 and G * max_q_len <= 32 and D == 256 and G * max_q_len > 16:

@@ -389,8 +389,8 @@ __host__ __device__ __forceinline__ uint32_t sf_tile_offset(uint32_t r, uint32_t
 extern "C" int mb_pdl_enabled();
 namespace mb {
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_kernel_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                         cudaStream_t stream, int cluster_z, Args&&... args) {
+inline cudaError_t launch_kernel_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, int cluster_z, bool pdl, Args&&... args) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -398,7 +398,7 @@ inline cudaError_t launch_kernel_cluster(void (*kern)(KArgs...), dim3 grid, dim3
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int n = 0;
-  if (mb_pdl_enabled()) {
+  if (pdl) {
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
@@ -414,9 +414,17 @@ inline cudaError_t launch_kernel_cluster(void (*kern)(KArgs...), dim3 grid, dim3
   cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
+// METRALE_PDL: 0 = plain launches, 1 = every kernel launches programmatically, 2 = only the GEMMs
+// (whose prologue and first weight tiles then overlap the tail of the preceding kernel)
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t stream, int cluster_z, Args&&... args) {
+  return launch_kernel_ex(kern, grid, block, smem, stream, cluster_z, mb_pdl_enabled() >= 1,
+                          static_cast<Args&&>(args)...);
+}
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                  cudaStream_t stream, Args&&... args) {
-  return launch_kernel_cluster(kern, grid, block, smem, stream, 1, static_cast<Args&&>(args)...);
+  return launch_kernel_ex(kern, grid, block, smem, stream, 1, mb_pdl_enabled() == 1, static_cast<Args&&>(args)...);
 }
 }  // namespace mb

@@ -124,6 +124,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
   int m_row0 = tile_m * TN, m_end = p.M, expert = 0, n_limit = p.N;
   if (p.tile_expert) {
+    mb::pdl_wait();                               // the work list is written by the preceding sort kernel
     expert = p.tile_expert[tile_m];
     if (expert < 0) return;                       // unused work-list entry (uniform for the CTA)
     m_row0 = p.tile_row0[tile_m];
@@ -154,7 +155,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __syncthreads();
   mb::tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  mb::pdl_wait();                 // set-up above touched no global memory
+  // Programmatic dependent launch: everything above touched no global memory. The weights are
+  // never written by a kernel of the same stream, so the producer starts streaming them before
+  // the wait; only the activation operand, its scale factors and the epilogue's reads and
+  // writes wait for the preceding kernel.
   mb::pdl_launch_dependents();
   if (threadIdx.x == 0) MB_STAMP(1);
 
@@ -170,22 +174,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (mb::elect_one()) {
-      for (int i = 0; i < nkb; ++i) {
+      const bool sf_load = (KIND == KIND_NVFP4) && !(p.dbg & 8);
+      const uint32_t stage_tx = C::kStageBytes - (KIND == KIND_NVFP4 && !sf_load ? 4096 : 0);
+      auto load_w = [&](int i) {                   // weight tile + its scale factors
+        const int s = i % kStages, kb = kb0 + i;
+        mb::tma_load_2d(sA(s), &tmA, &full_bar[s], kb * kCoordStep, w_row0);
+        if (sf_load)
+          mb::bulk_load(sSFA(s), p.sfa + ((size_t)tile_n * p.sf_k64 + (size_t)kb * 4) * 512, 2048, &full_bar[s]);
+      };
+      auto load_x = [&](int i) {                   // activation tile + its scale factors
+        const int s = i % kStages, kb = kb0 + i;
+        mb::tma_load_2d(sB(s), &tmB, &full_bar[s], kb * kCoordStep, m_row0);
+        if (sf_load)
+          mb::bulk_load(sSFB(s), p.sfb + ((size_t)((tile_m * TN) / 128) * p.sf_k64 + (size_t)kb * 4) * 512, 2048,
+                        &full_bar[s]);
+      };
+      const int pre = min(nkb, kStages);           // the first round needs no empty-slot wait
+      for (int i = 0; i < pre; ++i) {
+        mb::mbar_expect_tx(&full_bar[i], stage_tx);
+        load_w(i);
+      }
+      mb::pdl_wait();
+      for (int i = 0; i < pre; ++i) {
+        load_x(i);
+        if (i == 0) MB_STAMP(2);
+      }
+      for (int i = pre; i < nkb; ++i) {
         const int s = i % kStages;
         const uint32_t ph = (i / kStages) & 1;
         if (!mb::mbar_wait(&empty_bar[s], ph ^ 1, p.status, MB_ST_TIMEOUT_TMA)) break;
-        const bool sf_load = (KIND == KIND_NVFP4) && !(p.dbg & 8);
-        mb::mbar_expect_tx(&full_bar[s], C::kStageBytes - (KIND == KIND_NVFP4 && !sf_load ? 4096 : 0));
-        const int kb = kb0 + i;
-        mb::tma_load_2d(sA(s), &tmA, &full_bar[s], kb * kCoordStep, w_row0);
-        mb::tma_load_2d(sB(s), &tmB, &full_bar[s], kb * kCoordStep, m_row0);
-        if (sf_load) {
-          const size_t a_off = ((size_t)tile_n * p.sf_k64 + (size_t)kb * 4) * 512;
-          const size_t b_off = ((size_t)((tile_m * TN) / 128) * p.sf_k64 + (size_t)kb * 4) * 512;
-          mb::bulk_load(sSFA(s), p.sfa + a_off, 2048, &full_bar[s]);
-          mb::bulk_load(sSFB(s), p.sfb + b_off, 2048, &full_bar[s]);
-        }
-        if (i == 0) MB_STAMP(2);
+        mb::mbar_expect_tx(&full_bar[s], stage_tx);
+        load_w(i);
+        load_x(i);
       }
     }
     __syncwarp();
@@ -266,6 +286,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     float* s_tile = reinterpret_cast<float*>(smem);
     bool ok = true;
     const bool swiglu = p.epilogue == EPI_SWIGLU;
+    mb::pdl_wait();                                        // first global access of these warps follows
     // per-token scales of this tile, staged while the main loop runs
     for (int j = et; j < TN; j += 128) {
       float sc = 1.f;
@@ -577,6 +598,252 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Persistent variant for layers with more weight-row tiles than SMs (gate_up, lm_head) and one
+// token tile (M <= 128): every CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... with the
+// stage ring running across tile boundaries and two TMEM accumulators, so the epilogue of tile i
+// (TMEM -> registers -> global, no shared-memory staging) overlaps the main loop of tile i + 1
+// and the weight stream never pauses. Same operand kinds except the 128x128-block fp8 kind.
+template <int KIND, int TN>
+struct PCfg {
+  static constexpr int kABytes = kTileN * 128;
+  static constexpr int kBBytes = TN * 128;
+  static constexpr int kSfBytes = (KIND == KIND_NVFP4) ? 2048 : 0;
+  static constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;
+  static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kSfBase = 2 * TN;                                        // after the two accumulators
+  static constexpr int kNeedCols = 2 * TN + (KIND == KIND_NVFP4 ? 64 : 0);
+  static constexpr int kTmemCols =
+      kNeedCols <= 32 ? 32 : kNeedCols <= 64 ? 64 : kNeedCols <= 128 ? 128 : kNeedCols <= 256 ? 256 : 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+};
+
+template <int KIND, int TN>
+__global__ void __launch_bounds__(192, 1)
+gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const GemmParams p) {
+  static_assert(KIND != KIND_FP8_BLOCK && TN <= 128, "unsupported persistent configuration");
+  using C = PCfg<KIND, TN>;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ float s_ascale[TN];
+
+  const int warp = threadIdx.x >> 5;
+  const int n_tiles = (p.N + kTileN - 1) / kTileN;
+  const int nkb = p.num_kb;
+  const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // grid <= n_tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mb::mbar_init(&full_bar[s], 1);
+      mb::mbar_init(&empty_bar[s], 1);
+    }
+    mb::mbar_init(&acc_full[0], 1);
+    mb::mbar_init(&acc_full[1], 1);
+    mb::mbar_init(&acc_empty[0], 128);
+    mb::mbar_init(&acc_empty[1], 128);
+    mb::mbar_fence_init();
+    mb::tma_prefetch_desc(&tmA);
+    mb::tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) mb::tmem_alloc(&tmem_base_s, C::kTmemCols);
+  mb::tc_fence_before();
+  __syncthreads();
+  mb::tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  mb::pdl_launch_dependents();
+
+  auto sA = [&](int s) { return smem + s * C::kStageBytes; };
+  auto sB = [&](int s) { return smem + s * C::kStageBytes + C::kABytes; };
+  auto sSFA = [&](int s) { return smem + s * C::kStageBytes + C::kABytes + C::kBBytes; };
+  auto sSFB = [&](int s) { return smem + s * C::kStageBytes + C::kABytes + C::kBBytes + C::kSfBytes; };
+  constexpr int kCoordStep = (KIND == KIND_BF16) ? 64 : 128;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (mb::elect_one()) {
+      const int total = my_tiles * nkb;                   // k blocks this CTA streams, over all its tiles
+      auto load_w = [&](int g) {
+        const int tile = (int)blockIdx.x + (g / nkb) * (int)gridDim.x, kb = g % nkb, s = g % kStages;
+        mb::tma_load_2d(sA(s), &tmA, &full_bar[s], kb * kCoordStep, tile * kTileN);
+        if constexpr (KIND == KIND_NVFP4)
+          mb::bulk_load(sSFA(s), p.sfa + ((size_t)tile * p.sf_k64 + (size_t)kb * 4) * 512, 2048, &full_bar[s]);
+      };
+      auto load_x = [&](int g) {
+        const int kb = g % nkb, s = g % kStages;
+        mb::tma_load_2d(sB(s), &tmB, &full_bar[s], kb * kCoordStep, 0);
+        if constexpr (KIND == KIND_NVFP4) mb::bulk_load(sSFB(s), p.sfb + (size_t)kb * 4 * 512, 2048, &full_bar[s]);
+      };
+      const int pre = min(total, kStages);
+      for (int g = 0; g < pre; ++g) {                     // weights do not depend on the preceding kernel
+        mb::mbar_expect_tx(&full_bar[g], C::kStageBytes);
+        load_w(g);
+      }
+      mb::pdl_wait();
+      for (int g = 0; g < pre; ++g) load_x(g);
+      for (int g = pre; g < total; ++g) {
+        const int s = g % kStages;
+        const uint32_t ph = (g / kStages) & 1;
+        if (!mb::mbar_wait(&empty_bar[s], ph ^ 1, p.status, MB_ST_TIMEOUT_TMA)) break;
+        mb::mbar_expect_tx(&full_bar[s], C::kStageBytes);
+        load_w(g);
+        load_x(g);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (mb::elect_one()) {
+      uint32_t idesc;
+      if constexpr (KIND == KIND_BF16) idesc = mb::umma_idesc(1, 1, kTileN, TN);
+      else if constexpr (KIND == KIND_NVFP4) idesc = mb::umma_idesc_bs(1, 1, kTileN, TN, 0);
+      else idesc = mb::umma_idesc(0, 0, kTileN, TN);
+      bool ok = true;
+      int g = 0;
+      for (int it = 0; it < my_tiles && ok; ++it) {
+        const int buf = it & 1;
+        // the epilogue must have drained this accumulator (two tiles ago) before it is overwritten
+        ok = mb::mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, p.status, MB_ST_TIMEOUT_MMA);
+        if (!ok) break;
+        mb::tc_fence_after();
+        const uint32_t acc = tmem + buf * TN;
+        for (int i = 0; i < nkb; ++i, ++g) {
+          const int s = g % kStages;
+          const uint32_t ph = (g / kStages) & 1;
+          ok = mb::mbar_wait(&full_bar[s], ph, p.status, MB_ST_TIMEOUT_MMA);
+          if (!ok) break;
+          mb::tc_fence_after();
+          const uint32_t a_base = mb::smem_u32(sA(s)), b_base = mb::smem_u32(sB(s));
+          const uint32_t sfa_col = C::kSfBase + (g & 1) * 32, sfb_col = sfa_col + 16;
+          if constexpr (KIND == KIND_NVFP4) {
+            const uint32_t sfa = mb::smem_u32(sSFA(s)), sfb = mb::smem_u32(sSFB(s));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              mb::tmem_cp_sf(tmem + sfa_col + j * 4, mb::umma_desc_sf(sfa + j * 512));
+              mb::tmem_cp_sf(tmem + sfb_col + j * 4, mb::umma_desc_sf(sfb + j * 512));
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint64_t da = mb::umma_desc_sw128(a_base + j * 32);
+            const uint64_t db = mb::umma_desc_sw128(b_base + j * 32);
+            if constexpr (KIND == KIND_BF16) mb::umma_f16(acc, da, db, idesc, (i | j) != 0);
+            else if constexpr (KIND == KIND_FP8) mb::umma_f8f6f4(acc, da, db, idesc, (i | j) != 0);
+            else mb::umma_nvfp4(acc, da, db, idesc, tmem + sfa_col + j * 4, tmem + sfb_col + j * 4, (i | j) != 0);
+          }
+          mb::tc_commit(&empty_bar[s]);
+        }
+        if (ok) mb::tc_commit(&acc_full[buf]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue: TMEM -> registers -> global
+    const int q = warp & 3;
+    const int lane = threadIdx.x & 31;
+    const int et = threadIdx.x - 64;
+    const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+    const bool swiglu = p.epilogue == EPI_SWIGLU;
+    const int m_valid = min(p.M, TN);
+    mb::pdl_wait();
+    for (int j = et; j < TN; j += 128) {
+      float sc = 1.f;
+      if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
+        if (p.a_scale && j < m_valid) sc = __ldg(&p.a_scale[j]);
+      }
+      s_ascale[j] = sc;
+    }
+    epi_bar_sync();
+    const int f = q * 32 + lane;                          // weight row of this thread inside a tile
+    bool ok = true;
+    for (int it = 0; it < my_tiles && ok; ++it) {
+      const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+      const int buf = it & 1;
+      ok = mb::mbar_wait(&acc_full[buf], (it >> 1) & 1, p.status, MB_ST_TIMEOUT_EPI);
+      if (!ok) break;
+      mb::tc_fence_after();
+      const int n = tile * kTileN + f;
+      float wsc = p.alpha;
+      if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
+        if (p.w_scale && n < p.N) wsc *= __ldg(&p.w_scale[n]);
+      }
+      for (int c = 0; c * 16 < m_valid; ++c) {
+        float v[16];
+        mb::tmem_ld16(lane_addr + buf * TN + c * 16, v);
+        if (swiglu) {
+          // rows are interleaved (gate, up): an even lane holds the gate row, its odd neighbour
+          // the up row. Per pair of tokens the even lane finishes token j, the odd one token j + 1.
+          const int n_out = n >> 1;
+          const bool odd = lane & 1;
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            const int m0 = c * 16 + j;
+            const float x0 = v[j] * wsc * s_ascale[m0], x1 = v[j + 1] * wsc * s_ascale[m0 + 1];
+            const float other = __shfl_xor_sync(0xffffffffu, odd ? x0 : x1, 1);
+            const float y = odd ? mb::silu(other) * x1 : mb::silu(x0) * other;
+            const int m = m0 + (odd ? 1 : 0);
+            if (m < m_valid && n + (odd ? 0 : 1) < p.N)
+              reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n_out] = __float2bfloat16(y);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c * 16 + j;
+            if (m < m_valid && n < p.N) {
+              float y = v[j] * wsc * s_ascale[m];
+              const size_t o = (size_t)m * p.ldo + n;
+              if (p.residual) y += __bfloat162float(p.residual[o]);
+              if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = y;
+              else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16(y);
+            }
+          }
+        }
+      }
+      mb::tc_fence_before();
+      mb::mbar_arrive(&acc_empty[buf]);
+    }
+    mb::tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    mb::tc_fence_after();
+    mb::tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+template <int KIND, int TN>
+int launch_persistent(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid_x,
+                      cudaStream_t stream) {
+  using C = PCfg<KIND, TN>;
+  static bool configured = false;
+  auto kern = gemm_persistent_kernel<KIND, TN>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return (int)mb::launch_kernel_cluster(kern, dim3(grid_x), dim3(192), C::kSmemBytes, stream, 1, tmA, tmB, p);
+}
+
+template <int KIND>
+int dispatch_persistent(int tn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid_x,
+                        cudaStream_t stream) {
+  switch (tn) {
+    case 16: return launch_persistent<KIND, 16>(tmA, tmB, p, grid_x, stream);
+    case 32: return launch_persistent<KIND, 32>(tmA, tmB, p, grid_x, stream);
+    case 64: return launch_persistent<KIND, 64>(tmA, tmB, p, grid_x, stream);
+    case 128: return launch_persistent<KIND, 128>(tmA, tmB, p, grid_x, stream);
+    default: return MB_ERR_UNSUPPORTED;
+  }
+}
+
 // Waits (bounded) until every unit of the fused all-reduce has been finished by its owner,
 // re-arms the counter and flips this rank's parity for the next call.
 __global__ void tp_finish_kernel(uint32_t* done, uint32_t* par, uint32_t units, uint32_t* status) {
@@ -767,6 +1034,17 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
 
   dim3 grid(tiles_n, tiles_m, splits);
   rc = MB_ERR_UNSUPPORTED;
+  // more weight-row tiles than SMs and a single token tile: persistent CTAs, balanced tile counts
+  if (!grouped && a->tp_size <= 1 && splits == 1 && tiles_m == 1 && tn <= 128 && kind != KIND_FP8_BLOCK &&
+      tiles_n > sms && !a->trace && !(a->dbg & 16)) {
+    const int waves = (tiles_n + sms - 1) / sms;
+    const int grid_x = (tiles_n + waves - 1) / waves;
+    switch (kind) {
+      case KIND_BF16: return dispatch_persistent<KIND_BF16>(tn, tmA, tmB, p, grid_x, stream);
+      case KIND_FP8: return dispatch_persistent<KIND_FP8>(tn, tmA, tmB, p, grid_x, stream);
+      default: return dispatch_persistent<KIND_NVFP4>(tn, tmA, tmB, p, grid_x, stream);
+    }
+  }
   switch (kind) {
     case KIND_BF16: rc = dispatch_tn<KIND_BF16>(tn, tmA, tmB, p, grid, stream); break;
     case KIND_FP8: rc = dispatch_tn<KIND_FP8>(tn, tmA, tmB, p, grid, stream); break;

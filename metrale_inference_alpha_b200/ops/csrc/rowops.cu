@@ -423,11 +423,11 @@ static int g_pdl = -1;
 int mb_pdl_enabled() {
   if (g_pdl < 0) {
     const char* e = getenv("METRALE_PDL");
-    g_pdl = (e && e[0] == '1') ? 1 : 0;   // opt-in: measured slower than plain launches here
+    g_pdl = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0;   // opt-in: measured slower than plain launches here
   }
   return g_pdl;
 }
-void mb_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+void mb_set_pdl(int mode) { g_pdl = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 
 struct MbRowArgs {
   int M, K, in_mode, out_mode;

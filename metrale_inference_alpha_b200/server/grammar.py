@@ -284,5 +284,8 @@ def grammar_for_response_format(fmt: Optional[dict], tokenizer, eos_token_id=Non
         return None
     t = fmt.get("type")
     if t in ("json_object", "json_schema"):
+        from .. import native
+        if native.available() and hasattr(tokenizer, "token_bytes") and hasattr(tokenizer, "vocab_size"):
+            return native.NativeJsonGrammar(tokenizer, eos_token_id, require_object=True)
         return TokenGrammar(tokenizer, JsonMatcher(require_object=True), eos_token_id)
     return None

@@ -7,7 +7,7 @@ import os
 from typing import Dict, List
 
 LEVERS: Dict[str, str] = {
-    "METRALE_PDL": "1 = launch kernels with programmatic stream serialization (default 0)",
+    "METRALE_PDL": "programmatic dependent launch: 0 = off (default), 1 = every kernel, 2 = GEMMs only",
     "METRALE_B200_AUTOBUILD": "0 = never build the kernel library on import (default 1)",
     "METRALE_COMM_DIAGNOSTICS": "1 = log every collective submission with a sequence number",
     "METRALE_MTP_K_LADDER": "draft-width ladder 'width:k,...' (default 4:3,8:3,16:1,32:1)",
@@ -16,6 +16,7 @@ LEVERS: Dict[str, str] = {
     "METRALE_DEBUG_SYNC_KERNELS": "1 = synchronise and check the status word after every step",
     "METRALE_KV_POISON": "1 = fill fresh KV blocks with NaN bytes",
     "METRALE_TELEMETRY": "off | basic | kernel",
+    "METRALE_NATIVE_RUNTIME": "0 = keep allocator / prefix index / JSON grammar on the Python implementations",
     "METRALE_NO_FUSED_COLLECTIVES": "1 = NCCL collectives after plain GEMMs",
 }
 

@@ -6,12 +6,12 @@ import json
 from pathlib import Path
 
 from ..config.model_config import ModelConfig, from_hf_config
-from .source import SafetensorsSource
+from .fast_source import open_source
 
 
 def open_checkpoint(path, device="cpu"):
     p = Path(path)
-    src = SafetensorsSource(p, device=device)
+    src = open_source(p, device=device)
     eng = p / "engine_config.json"
     if eng.exists():
         cfg = ModelConfig.from_json(eng.read_text())

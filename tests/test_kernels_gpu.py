@@ -109,6 +109,45 @@ def test_gemm_swiglu_and_residual():
     ops.check_status(DEV)
 
 
+# N / 128 > 148 SMs selects the persistent kernel (tile loop per CTA, two TMEM accumulators)
+@pytest.mark.parametrize("fmt", ["nvfp4", "fp8_row", "bf16"])
+@pytest.mark.parametrize("M", [1, 16, 50, 128])
+def test_gemm_persistent_path_matches_oracle(fmt, M):
+    N = 128 * 150 + (64 if fmt == "bf16" else 0)          # bf16 case ends in a ragged tile
+    _run_linear(fmt, M, N, 512)
+
+
+def test_gemm_persistent_matches_one_tile_per_cta_kernel_bitwise():
+    M, N, K = 96, 128 * 300, 1024
+    x, w = _mk(M, N, K, 5)
+    for fmt in ("nvfp4", "fp8_row"):
+        qw = ops.make_weight(w, fmt).to(DEV)
+        act = ops.quantize_act(x.to(DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[fmt])
+        a = ops.linear(act, qw)
+        b = ops.linear(act, qw, dbg=16)                   # dbg bit 16: keep the one-tile-per-CTA kernel
+        assert torch.equal(a, b)
+    ops.check_status(DEV)
+
+
+def test_gemm_persistent_swiglu_and_residual():
+    M, I, K = 70, 64 * 160, 512
+    x, wg = _mk(M, I, K, 1)
+    _, wu = _mk(M, I, K, 2)
+    w = ops.interleave_gate_up(wg, wu)
+    for fmt in ("nvfp4", "fp8_row", "bf16"):
+        qw_cpu = ops.make_weight(w, fmt)
+        xb = x.to(torch.bfloat16)
+        want = ops.linear(ops.encode_act_ref(xb.float(), ops.ACT_FOR_WEIGHT[fmt]), qw_cpu, swiglu=True, out_f32=True)
+        got = ops.linear(ops.quantize_act(xb.to(DEV), ops.ACT_FOR_WEIGHT[fmt]), qw_cpu.to(DEV), swiglu=True)
+        _close(got, want, rtol=2e-2, atol=2e-2 * want.abs().max().item())
+    res = torch.randn(M, 2 * I).to(torch.bfloat16)
+    qw_cpu = ops.make_weight(w, "bf16")
+    want = ops.linear(ops.encode_act_ref(x.to(torch.bfloat16).float(), "bf16"), qw_cpu, residual=res, out_f32=True)
+    got = ops.linear(ops.quantize_act(x.to(torch.bfloat16).to(DEV), "bf16"), qw_cpu.to(DEV), residual=res.to(DEV))
+    _close(got, want, rtol=2e-2, atol=2e-2 * want.abs().max().item())
+    ops.check_status(DEV)
+
+
 def test_sf_repack_matches_reference_layout():
     sf = torch.randint(0, 120, (300, 40), dtype=torch.uint8)
     w = ops.QuantWeight("nvfp4", 300, 640, torch.zeros(300, 320, dtype=torch.uint8), sf, 1.0).to(DEV)
