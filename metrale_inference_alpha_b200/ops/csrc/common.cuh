@@ -282,6 +282,9 @@ __device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t ran
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
   return r;
 }
+__device__ __forceinline__ void dsmem_st_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 __device__ __forceinline__ float4 dsmem_ld_f4(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
@@ -346,7 +349,8 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return t;
 }
 
-__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+// x * sigmoid(x) with the approximate divide (ex2.approx + rcp.approx): ~2 ulp, 6 instructions
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 __device__ __forceinline__ float e4m3_to_float(uint8_t b) {
   __nv_fp8_e4m3 t;

@@ -619,8 +619,10 @@ struct PCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
 };
 
+constexpr int kPersistThreads = 320;   // producer warp + MMA warp + 8 epilogue warps
+
 template <int KIND, int TN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kPersistThreads, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const GemmParams p) {
   static_assert(KIND != KIND_FP8_BLOCK && TN <= 128, "unsupported persistent configuration");
@@ -633,7 +635,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_s;
-  __shared__ float s_ascale[TN];
+  __shared__ __align__(8) float s_ascale[TN];
 
   const int warp = threadIdx.x >> 5;
   const int n_tiles = (p.N + kTileN - 1) / kTileN;
@@ -647,8 +649,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
     mb::mbar_init(&acc_full[0], 1);
     mb::mbar_init(&acc_full[1], 1);
-    mb::mbar_init(&acc_empty[0], 128);
-    mb::mbar_init(&acc_empty[1], 128);
+    mb::mbar_init(&acc_empty[0], kPersistThreads - 64);
+    mb::mbar_init(&acc_empty[1], kPersistThreads - 64);
     mb::mbar_fence_init();
     mb::tma_prefetch_desc(&tmA);
     mb::tma_prefetch_desc(&tmB);
@@ -688,13 +690,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       }
       mb::pdl_wait();
       for (int g = 0; g < pre; ++g) load_x(g);
+      const bool skip_x = p.dbg & 32;                     // timing experiments: stale activation tiles
       for (int g = pre; g < total; ++g) {
         const int s = g % kStages;
         const uint32_t ph = (g / kStages) & 1;
         if (!mb::mbar_wait(&empty_bar[s], ph ^ 1, p.status, MB_ST_TIMEOUT_TMA)) break;
-        mb::mbar_expect_tx(&full_bar[s], C::kStageBytes);
+        mb::mbar_expect_tx(&full_bar[s], C::kStageBytes - (skip_x ? C::kBBytes + C::kSfBytes : 0));
         load_w(g);
-        load_x(g);
+        if (!skip_x) load_x(g);
       }
     }
     __syncwarp();
@@ -730,6 +733,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
               mb::tmem_cp_sf(tmem + sfb_col + j * 4, mb::umma_desc_sf(sfb + j * 512));
             }
           }
+          if (!(p.dbg & 4)) {                             // timing experiments: no MMAs
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint64_t da = mb::umma_desc_sw128(a_base + j * 32);
@@ -737,6 +741,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             if constexpr (KIND == KIND_BF16) mb::umma_f16(acc, da, db, idesc, (i | j) != 0);
             else if constexpr (KIND == KIND_FP8) mb::umma_f8f6f4(acc, da, db, idesc, (i | j) != 0);
             else mb::umma_nvfp4(acc, da, db, idesc, tmem + sfa_col + j * 4, tmem + sfb_col + j * 4, (i | j) != 0);
+          }
           }
           mb::tc_commit(&empty_bar[s]);
         }
@@ -746,21 +751,25 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue: TMEM -> registers -> global
+    // eight warps: two per TMEM lane quadrant (a warp may only read the quadrant warp_id % 4),
+    // each taking every other 16-token chunk, so that the exposed epilogue of a CTA's last tile
+    // is half as long
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int lane = threadIdx.x & 31;
     const int et = threadIdx.x - 64;
     const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
     const bool swiglu = p.epilogue == EPI_SWIGLU;
     const int m_valid = min(p.M, TN);
     mb::pdl_wait();
-    for (int j = et; j < TN; j += 128) {
+    for (int j = et; j < TN; j += kPersistThreads - 64) {
       float sc = 1.f;
       if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
         if (p.a_scale && j < m_valid) sc = __ldg(&p.a_scale[j]);
       }
       s_ascale[j] = sc;
     }
-    epi_bar_sync();
+    asm volatile("bar.sync 1, %0;" ::"n"(kPersistThreads - 64) : "memory");
     const int f = q * 32 + lane;                          // weight row of this thread inside a tile
     bool ok = true;
     for (int it = 0; it < my_tiles && ok; ++it) {
@@ -774,23 +783,26 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
         if (p.w_scale && n < p.N) wsc *= __ldg(&p.w_scale[n]);
       }
-      for (int c = 0; c * 16 < m_valid; ++c) {
+      for (int c = half; c * 16 < m_valid && !(p.dbg & 2); c += 2) {   // dbg 2: timing experiments, no epilogue
         float v[16];
         mb::tmem_ld16(lane_addr + buf * TN + c * 16, v);
         if (swiglu) {
           // rows are interleaved (gate, up): an even lane holds the gate row, its odd neighbour
-          // the up row. Per pair of tokens the even lane finishes token j, the odd one token j + 1.
-          const int n_out = n >> 1;
+          // the up row. Per pair of tokens the even lane finishes token j, the odd one token
+          // j + 1 (branch-free: both lanes run the same instruction stream).
           const bool odd = lane & 1;
+          const bool n_ok = odd ? (n < p.N) : (n + 1 < p.N);
+          __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(p.out) + (n >> 1);
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
             const int m0 = c * 16 + j;
-            const float x0 = v[j] * wsc * s_ascale[m0], x1 = v[j + 1] * wsc * s_ascale[m0 + 1];
+            const float2 as = *reinterpret_cast<const float2*>(&s_ascale[m0]);
+            const float x0 = v[j] * (wsc * as.x), x1 = v[j + 1] * (wsc * as.y);
             const float other = __shfl_xor_sync(0xffffffffu, odd ? x0 : x1, 1);
-            const float y = odd ? mb::silu(other) * x1 : mb::silu(x0) * other;
+            const float gate = odd ? other : x0, up = odd ? x1 : other;
+            const float y = mb::silu(gate) * up;
             const int m = m0 + (odd ? 1 : 0);
-            if (m < m_valid && n + (odd ? 0 : 1) < p.N)
-              reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n_out] = __float2bfloat16(y);
+            if (n_ok && m < m_valid) outp[(size_t)m * p.ldo] = __float2bfloat16(y);
           }
         } else {
 #pragma unroll
@@ -829,7 +841,7 @@ int launch_persistent(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return (int)mb::launch_kernel_cluster(kern, dim3(grid_x), dim3(192), C::kSmemBytes, stream, 1, tmA, tmB, p);
+  return (int)mb::launch_kernel_cluster(kern, dim3(grid_x), dim3(kPersistThreads), C::kSmemBytes, stream, 1, tmA, tmB, p);
 }
 
 template <int KIND>
