@@ -4,6 +4,8 @@ The paged cache stores one row per token: ``[kv_lora latent (RMS-normed) | rope 
 (kv_lora + rope dims, a single "kv head"). Queries are projected into latent space with
 W_uk, attention runs as multi-query attention over the latent rows, and W_uv maps the
 latent-space output back to per-head values before o_proj.
+On a GPU the attention itself runs in ``ops/csrc/mla.cu`` (one CTA per 16 query rows, the cached
+tile feeding both products); this file keeps the fp32 restatement used on CPU and as the oracle.
 Reference behaviour: ``kernels/gb10/deepseek-v4-flash/nvfp4/mla_absorbed.cu``
 (``mla_batched_gemv``, ``mla_cache_assemble``), ``paged_decode_attn_mla.cu``.
 """
@@ -14,7 +16,7 @@ import math
 import torch
 
 from .. import ops
-from ..ops import ACT_FOR_WEIGHT
+from ..ops import ACT_FOR_WEIGHT, mla_cuda
 from ..ops import reference as ref
 
 
@@ -41,7 +43,11 @@ def mla_block(dec, x, lw, batch, kv, j: int):
     q_lat = torch.einsum("thn,hnl->thl", q[..., :nope], w.w_uk.float())   # absorb W_uk
     qq = torch.cat([q_lat, q_rope], -1).to(torch.bfloat16)             # [T, H, L + rope]
     scale = 1.0 / math.sqrt(nope + rope)
-    o_lat = mla_attention(qq, kv.k[j], batch, scale, L)                # [T, H, L] fp32
+    if mla_cuda.supported(qq, kv.k[j]) and L == mla_cuda.LATENT:
+        o_lat = mla_cuda.mla_attention(qq, kv.k[j], batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
+                                       max_q_len=batch.max_q_len, max_ctx=max(batch.max_ctx, 1), scale=scale)
+    else:
+        o_lat = mla_attention(qq, kv.k[j], batch, scale, L)            # [T, H, L] fp32
     o = torch.einsum("thl,hvl->thv", o_lat, w.w_uv.float()).reshape(T, H * vd)
     oa = ops.quantize_act(o.to(torch.bfloat16), ACT_FOR_WEIGHT[w.o.fmt])
     return dec.tp.linear_reduce(oa, w.o, residual=x)

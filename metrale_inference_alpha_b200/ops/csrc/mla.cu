@@ -1,0 +1,370 @@
+// Absorbed multi-head latent attention (DeepSeek-V2/V3 shape) over the paged latent cache.
+//
+// Cache row per token: [kv_lora = 512 latent dims (RMS-normed) | 64 rope key dims], bf16, a single
+// shared "kv head". Queries arrive already absorbed (q_nope * W_uk | rope(q_rope)), 576 dims per
+// head. Scores use the whole 576-dim row, values are its first 512 dims, so this is multi-query
+// attention in which K and V are the same bytes: a tile of cached rows is staged in shared memory
+// once and feeds both products.
+//
+// grid (ceil(H * max_q_len / 16), num_seqs, parts), 128 threads. A CTA owns 16 query rows
+// (row r of a sequence = query token r / H, head r % H) and one partition of the context.
+// Per 64-token tile (cp.async, two stages):
+//   S   warp w: S[16 rows x 16 tokens] for tokens 16w..16w+15, 36 k steps of mma.sync m16n8k16
+//       (Q fragments by ldmatrix from shared memory: 576 dims do not fit registers);
+//   softmax over the tile with the row maximum shared by the four warps (shared memory), P -> bf16
+//       in shared memory;
+//   O   warp w: O[16 rows x 128 latent dims 128w..] += P[16 x 64] * V[64 x 128] (ldmatrix.trans).
+// Partitions are merged by mla_merge_kernel. Rows of 1152 bytes are XOR-swizzled in 16-byte
+// chunks so that ldmatrix sees no bank conflicts.
+//
+// Reference behaviour: kernels/gb10/deepseek-v4-flash/nvfp4/{paged_decode_attn_mla.cu,
+// mla_paged_decode_fp8.cu, mla_absorbed.cu} (CUDA-core per-head loops there).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kD = 576, kL = 512, kRowB = kD * 2, kChunks = kRowB / 16, kTile = 64;
+constexpr int kTileB = kTile * kRowB;
+constexpr int kQB = 16 * kRowB;
+constexpr int kSmem = 2 * kTileB + kQB + 16 * 128 /*P*/ + 4 * 16 * 4 /*max*/ + 4 * 16 * 4 /*l*/;
+
+struct MlaParams {
+  const __nv_bfloat16* q;       // [rows, H, 576]
+  const __nv_bfloat16* cache;   // [num_blocks, block_size, 1, 576]
+  const int* block_table;
+  int max_blocks;
+  const int* q_start;
+  const int* q_len;
+  const int* ctx_len;
+  int H, block_size;
+  long long num_blocks;
+  float scale;
+  float* out;                   // [rows, H, 512] fp32
+  float* part_o;                // [rows * H, parts, 512]
+  float* part_ml;               // [rows * H, parts, 2]
+  int parts, part_tokens;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+  return (uint32_t)(row * kRowB + ((chunk ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ void ldsm4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(128, 1) mla_decode_kernel(const MlaParams p) {
+  extern __shared__ __align__(128) uint8_t smem_mla[];
+  const uint32_t sbase = mb::smem_u32(smem_mla);
+  const uint32_t sQ = sbase + 2 * kTileB, sP = sQ + kQB;
+  float* s_max = reinterpret_cast<float*>(smem_mla + 2 * kTileB + kQB + 16 * 128);
+  float* s_l = s_max + 64;
+  const int rg = blockIdx.x, seq = blockIdx.y, part = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
+  const int qlen = p.q_len[seq], ctx = p.ctx_len[seq], qs = p.q_start[seq];
+  const int R = p.H * qlen;
+  if (qlen <= 0 || rg * 16 >= R) return;
+  const int nparts = max(1, (ctx + p.part_tokens - 1) / p.part_tokens);
+  if (part >= nparts) return;
+  const int part_len = (((ctx + nparts - 1) / nparts) + 63) & ~63;
+  const int tok_begin = part * part_len;
+  const int tok_end = min(ctx, tok_begin + part_len);
+  const int ntiles = tok_begin < tok_end ? (tok_end - tok_begin + kTile - 1) / kTile : 0;
+  const int* bt = p.block_table + (size_t)seq * p.max_blocks;
+
+  auto issue_tile = [&](int it) {
+    const uint32_t dst = sbase + (it & 1) * kTileB;
+    const int tok0 = tok_begin + it * kTile;
+    for (int idx = tid; idx < kTile * kChunks; idx += 128) {
+      const int r = idx / kChunks, c = idx - r * kChunks;
+      const int tok = tok0 + r;
+      int sz = 0;
+      size_t off = 0;
+      if (tok < tok_end) {
+        long long blk = bt[tok / p.block_size];
+        if (blk < 0 || blk >= p.num_blocks) {
+          if (p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
+          blk = 0;
+        }
+        off = ((size_t)blk * p.block_size + tok % p.block_size) * kRowB + (size_t)c * 16;
+        sz = 16;
+      }
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + swz(r, c)),
+                   "l"(reinterpret_cast<const uint8_t*>(p.cache) + off), "r"(sz) : "memory");
+    }
+  };
+  if (ntiles > 0) issue_tile(0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  // Q rows of this group -> shared memory (zero rows past R)
+  for (int idx = tid; idx < 16 * kChunks; idx += 128) {
+    const int r = idx / kChunks, c = idx - r * kChunks;
+    const int row = rg * 16 + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < R) {
+      const int tq = row / p.H, hh = row - tq * p.H;
+      v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.q) +
+                                          ((size_t)(qs + tq) * p.H + hh) * kRowB + (size_t)c * 16);
+    }
+    *reinterpret_cast<uint4*>(smem_mla + 2 * kTileB + swz(r, c)) = v;
+  }
+
+  float o_acc[16][4];
+#pragma unroll
+  for (int n = 0; n < 16; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o_acc[n][i] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  int lim[2];
+#pragma unroll
+  for (int hr = 0; hr < 2; ++hr) {
+    const int row = rg * 16 + g + hr * 8;
+    lim[hr] = row < R ? ctx - qlen + row / p.H + 1 : 0;      // rows past R see nothing
+  }
+  const float sc_log2 = p.scale * 1.44269504088896f;
+
+  for (int it = 0; it < ntiles; ++it) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (it + 1 < ntiles) issue_tile(it + 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const uint32_t kT = sbase + (it & 1) * kTileB;
+    const int tok0 = tok_begin + it * kTile + warp * 16;
+
+    // ---- S = Q K^T for this warp's 16 tokens
+    float s[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
+#pragma unroll 4
+    for (int ks = 0; ks < kD / 16; ++ks) {
+      uint32_t a[4], b[4];
+      ldsm4(a, sQ + swz((lane & 7) + (((lane >> 3) & 1) << 3), ks * 2 + (lane >> 4)));
+      ldsm4(b, kT + swz(warp * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+      mma_bf16(s[0], a, b[0], b[1]);
+      mma_bf16(s[1], a, b[2], b[3]);
+    }
+    // ---- tile softmax; the row maximum is shared by the four warps
+    float mx[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int limit = min(lim[hr], tok_end);
+      float m = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int tok = tok0 + n * 8 + t * 2 + i;
+          float v = s[n][hr * 2 + i] * sc_log2;
+          if (tok >= limit) v = -INFINITY;
+          s[n][hr * 2 + i] = v;
+          m = fmaxf(m, v);
+        }
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+      mx[hr] = m;
+      if (t == 0) s_max[warp * 16 + g + hr * 8] = m;
+    }
+    __syncthreads();
+    float alpha[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int r = g + hr * 8;
+      const float tm = fmaxf(fmaxf(s_max[r], s_max[16 + r]), fmaxf(s_max[32 + r], s_max[48 + r]));
+      const float m_new = fmaxf(m_run[hr], tm);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      alpha[hr] = ex2(m_run[hr] - m_use);
+      float rs = 0.f;
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float pv = ex2(s[n][hr * 2 + i] - m_use);
+          s[n][hr * 2 + i] = pv;
+          rs += pv;
+        }
+      l_run[hr] = l_run[hr] * alpha[hr] + rs;       // this warp's tokens only; summed at the end
+      m_run[hr] = m_new;
+    }
+    // P (bf16) -> shared memory [16 rows][64 tokens], 128-byte rows, swizzled
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr)
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const int r = g + hr * 8;
+        const int col = warp * 16 + n * 8 + t * 2;                 // token column
+        const uint32_t addr = sP + r * 128 + ((((col >> 3) ^ (r & 7)) << 4) | ((col & 7) << 1));
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack_bf16(s[n][hr * 2], s[n][hr * 2 + 1])) : "memory");
+      }
+    __syncthreads();
+    // ---- O[:, 128 warp ..] = alpha * O + P V
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      o_acc[n][0] *= alpha[0]; o_acc[n][1] *= alpha[0];
+      o_acc[n][2] *= alpha[1]; o_acc[n][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t a[4];
+      {
+        const int r = (lane & 7) + (((lane >> 3) & 1) << 3);
+        const int ch = kk * 2 + (lane >> 4);
+        ldsm4(a, sP + r * 128 + ((ch ^ (r & 7)) << 4));
+      }
+#pragma unroll
+      for (int n2 = 0; n2 < 8; ++n2) {
+        uint32_t b[4];
+        ldsm4t(b, kT + swz(kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), warp * 16 + n2 * 2 + (lane >> 4)));
+        mma_bf16(o_acc[n2 * 2], a, b[0], b[1]);
+        mma_bf16(o_acc[n2 * 2 + 1], a, b[2], b[3]);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  // ---- row sums over the four warps, normalise, write
+#pragma unroll
+  for (int hr = 0; hr < 2; ++hr) {
+    float l = l_run[hr];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (t == 0) s_l[warp * 16 + g + hr * 8] = l;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int hr = 0; hr < 2; ++hr) {
+    const int r = g + hr * 8;
+    const int row = rg * 16 + r;
+    if (row >= R) continue;
+    const float l = s_l[r] + s_l[16 + r] + s_l[32 + r] + s_l[48 + r];
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const int tq = row / p.H, hh = row - tq * p.H;
+    const size_t grow = (size_t)(qs + tq) * p.H + hh;
+    float* dst = nparts == 1 ? p.out + grow * kL : p.part_o + (grow * p.parts + part) * kL;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      const float2 v = make_float2(o_acc[n][hr * 2] * inv, o_acc[n][hr * 2 + 1] * inv);
+      *reinterpret_cast<float2*>(dst + warp * 128 + n * 8 + t * 2) = v;
+    }
+    if (nparts > 1 && warp == 0 && t == 0) {
+      p.part_ml[(grow * p.parts + part) * 2] = m_run[hr];
+      p.part_ml[(grow * p.parts + part) * 2 + 1] = l;
+    }
+  }
+}
+
+// one CTA per (query row, head): weights l_i * 2^(m_i - M), in partition order
+__global__ void mla_merge_kernel(const MlaParams p, const int* row_seq) {
+  const int grow = blockIdx.x;                      // (token row) * H + head
+  const int seq = row_seq[grow / p.H];
+  mb::pdl_wait();
+  const int ctx = p.ctx_len[seq];
+  const int nparts = max(1, (ctx + p.part_tokens - 1) / p.part_tokens);
+  if (nparts == 1) return;                          // the decode kernel wrote the row directly
+  float M = -INFINITY;
+  for (int s = 0; s < nparts; ++s) M = fmaxf(M, p.part_ml[((size_t)grow * p.parts + s) * 2]);
+  float wsum = 0.f;
+  for (int s = 0; s < nparts; ++s) {
+    const float m = p.part_ml[((size_t)grow * p.parts + s) * 2], l = p.part_ml[((size_t)grow * p.parts + s) * 2 + 1];
+    wsum += m == -INFINITY ? 0.f : l * exp2f(m - M);
+  }
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  for (int d = threadIdx.x; d < kL; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < nparts; ++s) {
+      const float m = p.part_ml[((size_t)grow * p.parts + s) * 2], l = p.part_ml[((size_t)grow * p.parts + s) * 2 + 1];
+      const float w = m == -INFINITY ? 0.f : l * exp2f(m - M) * inv;
+      acc += w * p.part_o[((size_t)grow * p.parts + s) * kL + d];
+    }
+    p.out[(size_t)grow * kL + d] = acc;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+struct MbMlaArgs {
+  const void* q;
+  const void* cache;
+  const int* block_table;
+  int max_blocks;
+  const int* q_start;
+  const int* q_len;
+  const int* ctx_len;
+  const int* row_seq;        // [total_rows] sequence index of every query row (merge kernel)
+  int num_seqs, max_q_len, max_ctx, total_rows;
+  int H, block_size;
+  long long num_blocks;
+  float scale;
+  float* out;
+  void* ws;
+  size_t ws_bytes;
+  int part_tokens;           // 0 = default 1024
+  uint32_t* status;
+};
+
+size_t mb_mla_ws_bytes(int total_rows, int H, int max_ctx, int part_tokens) {
+  const int pt = part_tokens > 0 ? part_tokens : 1024;
+  const size_t parts = (size_t)(max_ctx + pt - 1) / pt;
+  return parts <= 1 ? 0 : (size_t)total_rows * H * parts * (kL + 2) * sizeof(float);
+}
+
+int mb_mla_attention(const MbMlaArgs* a, cudaStream_t stream) {
+  if (!a || !a->q || !a->cache || !a->out || a->num_seqs <= 0 || a->H <= 0 || a->max_q_len <= 0) return MB_ERR_BAD_ARG;
+  MlaParams p{};
+  p.q = reinterpret_cast<const __nv_bfloat16*>(a->q);
+  p.cache = reinterpret_cast<const __nv_bfloat16*>(a->cache);
+  p.block_table = a->block_table; p.max_blocks = a->max_blocks;
+  p.q_start = a->q_start; p.q_len = a->q_len; p.ctx_len = a->ctx_len;
+  p.H = a->H; p.block_size = a->block_size; p.num_blocks = a->num_blocks;
+  p.scale = a->scale; p.out = a->out; p.status = a->status;
+  p.part_tokens = a->part_tokens > 0 ? a->part_tokens : 1024;
+  p.parts = (a->max_ctx + p.part_tokens - 1) / p.part_tokens;
+  if (p.parts < 1) p.parts = 1;
+  if (p.parts > 1) {
+    const size_t need = mb_mla_ws_bytes(a->total_rows, a->H, a->max_ctx, p.part_tokens);
+    if (!a->ws || a->ws_bytes < need || !a->row_seq) return MB_ERR_TOO_LARGE;
+    p.part_o = reinterpret_cast<float*>(a->ws);
+    p.part_ml = p.part_o + (size_t)a->total_rows * a->H * p.parts * kL;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int groups = (a->H * a->max_q_len + 15) / 16;
+  cudaError_t e = mb::launch_kernel(mla_decode_kernel, dim3(groups, a->num_seqs, p.parts), dim3(128), (size_t)kSmem, stream, p);
+  if (e != cudaSuccess) return (int)e;
+  if (p.parts > 1) {
+    e = mb::launch_kernel(mla_merge_kernel, dim3(a->total_rows * a->H), dim3(128), (size_t)0, stream, p, a->row_seq);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,66 @@
+"""Binding of the absorbed-MLA paged attention kernel (``csrc/mla.cu``): multi-query attention of
+``[T, H, 576]`` absorbed queries over the latent cache ``[blocks, block, 1, 576]`` (bf16), values =
+the first 512 dims of each cached row. On CPU tensors the fp32 restatement in ``models/mla.py`` runs."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _native
+
+c_void_p, c_int, c_ll, c_float, c_size_t = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_size_t
+
+
+class MlaArgs(C.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("cache", c_void_p), ("block_table", c_void_p), ("max_blocks", c_int),
+        ("q_start", c_void_p), ("q_len", c_void_p), ("ctx_len", c_void_p), ("row_seq", c_void_p),
+        ("num_seqs", c_int), ("max_q_len", c_int), ("max_ctx", c_int), ("total_rows", c_int),
+        ("H", c_int), ("block_size", c_int), ("num_blocks", c_ll), ("scale", c_float),
+        ("out", c_void_p), ("ws", c_void_p), ("ws_bytes", c_size_t), ("part_tokens", c_int), ("status", c_void_p),
+    ]
+
+
+_native.register_optional("mb_mla_attention", [C.POINTER(MlaArgs), c_void_p])
+
+LATENT, ROW = 512, 576
+
+
+def supported(q: torch.Tensor, cache: torch.Tensor) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and q.shape[-1] == ROW
+            and cache.shape[-1] == ROW and cache.shape[2] == 1)
+
+
+def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_table, q_start, q_len, ctx_len, *, max_q_len: int,
+                  max_ctx: int, scale: float, row_seq=None, part_tokens: int = 0) -> torch.Tensor:
+    """q [T, H, 576] bf16 -> [T, H, 512] fp32."""
+    from . import _count, _ptr, _stream, runtime
+    L = _native.lib()
+    if not hasattr(L, "mb_mla_attention"):
+        raise RuntimeError("kernel library was built without mla.cu")
+    L.mb_mla_ws_bytes.argtypes = [c_int, c_int, c_int, c_int]
+    L.mb_mla_ws_bytes.restype = c_size_t
+    T, H, _ = q.shape
+    q = q.contiguous()
+    rt = runtime(q.device)
+    out = torch.empty(T, H, LATENT, dtype=torch.float32, device=q.device)
+    need = L.mb_mla_ws_bytes(T, H, max_ctx, part_tokens)
+    if need:
+        rt.ensure_attn_ws(need)
+        if row_seq is None:                       # row -> sequence map for the merge pass
+            row_seq = torch.repeat_interleave(torch.arange(q_len.numel(), device=q.device, dtype=torch.int32),
+                                              q_len.clamp(min=0).long(), output_size=None)
+            if row_seq.numel() < T:
+                row_seq = torch.cat([row_seq, row_seq.new_zeros(T - row_seq.numel())])
+            row_seq = row_seq.to(torch.int32).contiguous()
+    a = MlaArgs()
+    a.q, a.cache, a.block_table, a.max_blocks = _ptr(q), _ptr(cache), _ptr(block_table), block_table.stride(0)
+    a.q_start, a.q_len, a.ctx_len, a.row_seq = _ptr(q_start), _ptr(q_len), _ptr(ctx_len), _ptr(row_seq)
+    a.num_seqs, a.max_q_len, a.max_ctx, a.total_rows = q_len.numel(), max_q_len, max_ctx, T
+    a.H, a.block_size, a.num_blocks, a.scale = H, cache.shape[1], cache.shape[0], scale
+    a.out, a.part_tokens, a.status = _ptr(out), part_tokens, _ptr(rt.status)
+    a.ws, a.ws_bytes = (_ptr(rt.attn_ws), rt.attn_ws.numel()) if need else (None, 0)
+    _native.check(L.mb_mla_attention(C.byref(a), _stream()), "mla_attention")
+    _count()
+    return out

@@ -130,3 +130,42 @@ def test_grouped_expert_ffn_matches_loop(fmt):
     torch.cuda.synchronize()
     ops.check_status(DEV)
     _close(got, want, 3e-2, 3e-2 * want.abs().max().item())
+
+
+# ---------------------------------------------------------------------------- absorbed MLA attention
+@pytest.mark.parametrize("H,q_lens,ctx_lens,part_tokens", [
+    (16, [1, 1, 1], [5, 130, 64], 0),             # decode, ragged contexts, one row group per sequence
+    (128, [1, 1], [700, 33], 0),                  # DeepSeek-V3 head count: 8 row groups
+    (8, [4, 1, 7], [40, 9, 200], 0),              # verify / chunked rows: causal limits inside a group
+    (16, [1, 2], [300, 257], 128),                # three partitions + merge kernel
+])
+def test_mla_attention_matches_fp32_oracle(H, q_lens, ctx_lens, part_tokens):
+    from types import SimpleNamespace
+    from metrale_inference_alpha_b200.models.mla import mla_attention as mla_ref
+    from metrale_inference_alpha_b200.ops import mla_cuda
+    g = torch.Generator().manual_seed(11)
+    bs, D, L = 16, 576, 512
+    S = len(q_lens)
+    nblk = [(c + bs - 1) // bs for c in ctx_lens]
+    nb = sum(nblk) + 1
+    cache = (torch.randn(nb, bs, 1, D, generator=g) * 0.5).to(torch.bfloat16)
+    bt = torch.zeros(S, max(nblk) + 2, dtype=torch.int32)
+    perm = (torch.randperm(nb - 1, generator=g) + 1).tolist()
+    k = 0
+    for s in range(S):
+        for b in range(nblk[s]):
+            bt[s, b] = perm[k]
+            k += 1
+    T = sum(q_lens)
+    q = (torch.randn(T, H, D, generator=g) * 0.5).to(torch.bfloat16)
+    qs = torch.tensor([sum(q_lens[:i]) for i in range(S)], dtype=torch.int32)
+    ql, cl = torch.tensor(q_lens, dtype=torch.int32), torch.tensor(ctx_lens, dtype=torch.int32)
+    batch = SimpleNamespace(q_start=qs, q_len=ql, ctx_len=cl, block_table=bt)
+    scale = 1.0 / (192 ** 0.5)
+    want = mla_ref(q, cache, batch, scale, L)
+    got = mla_cuda.mla_attention(q.to(DEV), cache.to(DEV), bt.to(DEV), qs.to(DEV), ql.to(DEV), cl.to(DEV),
+                                 max_q_len=max(q_lens), max_ctx=max(ctx_lens), scale=scale, part_tokens=part_tokens)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    err = (got.cpu() - want).abs().max().item()
+    assert err < 2e-2 * max(1.0, want.abs().max().item()), err
