@@ -35,6 +35,8 @@ class ForwardBatch:
     host_q_len: Optional[List[int]] = None
     # hidden rows to return for the MTP head (same indexing as logit_rows)
     want_hidden: bool = False
+    # LoRA: adapter slot of every token row (-1 = base model); None when no row has an adapter
+    adapter_rows: Optional[torch.Tensor] = None
 
     @property
     def device(self):

@@ -53,6 +53,9 @@ class EngineArgs:
     request_timeout_s: float = 300.0
     eos_token_id: Optional[int] = None
     fused_collectives: bool = True
+    preempt_mode: str = "recompute"                    # recompute | swap (KV + state to host memory / swap files)
+    swap_space_bytes: int = 8 << 30
+    swap_dir: Optional[str] = None
 
 
 class LLMEngine:
@@ -95,7 +98,13 @@ class LLMEngine:
         if args.enable_prefix_caching:
             self.prefix = make_radix(self.runner.kv.allocator, args.block_size, needs_snapshot=needs_snap,
                                     on_snapshot_evict=(self.runner.pool.release_snapshot if needs_snap else None))
-        self.scheduler = SchedulerCore(self.sched_cfg, self.runner.kv.allocator, self.prefix, self.runner.pool)
+        self.spill = None
+        if args.preempt_mode == "swap":
+            from ..cache.kv_spill import KvSpillManager
+            self.sched_cfg.preempt_mode = "swap"
+            self.spill = KvSpillManager(self.runner.kv, self.runner.pool, args.swap_space_bytes, args.swap_dir)
+        self.scheduler = SchedulerCore(self.sched_cfg, self.runner.kv.allocator, self.prefix, self.runner.pool,
+                                       spill=self.spill)
         self._ids = itertools.count(1)
         self.spec_mode = args.speculative
         if self.spec_mode == "mtp" and self.weights.mtp is None:
@@ -108,13 +117,40 @@ class LLMEngine:
         self.tokenizer = None
         self.stop_strings_active = False
 
+    # ------------------------------------------------------------------ LoRA adapters
+    def load_adapter(self, name: str, source, max_adapters: int = 8, max_rank: int = 16) -> int:
+        """Make a LoRA adapter available to ``add_request(..., adapter=name)``. ``source`` is a PEFT
+        checkpoint directory or a ``lora.LoraAdapter``. Returns the device slot."""
+        from ..lora import LoraAdapter, LoraManager
+        if self.tp.size > 1:
+            raise NotImplementedError("LoRA adapters are served on single-rank engines")
+        dec, c = self.runner.decoder, self.cfg
+        if dec.lora is None:
+            D = c.head_dim
+            dims = {"q": (c.hidden_size, c.num_heads * D), "k": (c.hidden_size, c.num_kv_heads * D),
+                    "v": (c.hidden_size, c.num_kv_heads * D), "o": (c.num_heads * D, c.hidden_size),
+                    "down": (c.intermediate_size, c.hidden_size)}
+            dec.lora = LoraManager(c.num_layers, dims, max_adapters, max_rank, device=self.device,
+                                   max_rows=max(self.sched_cfg.max_prefill_tokens, self.sched_cfg.max_num_seqs * 8))
+        ad = source if isinstance(source, LoraAdapter) else LoraAdapter.from_dir(name, source)
+        ad.name = name
+        return dec.lora.load(ad)
+
+    def unload_adapter(self, name: str) -> None:
+        if self.runner.decoder.lora is not None:
+            self.runner.decoder.lora.unload(name)
+
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_ids: Seq[int], params: Optional[SamplingParams] = None,
                     request_id: Optional[str] = None, adapter: Optional[str] = None) -> str:
         if self.fault.is_set():
             raise FatalDeviceError(self.fault.reason())
         rid = request_id or f"req-{next(self._ids)}"
-        req = Request(rid, list(prompt_ids), params or SamplingParams(), adapter=adapter,
+        params = params or SamplingParams()
+        adapter = adapter or params.adapter
+        if adapter and (self.runner.decoder.lora is None or adapter not in self.runner.decoder.lora.slots):
+            raise ValueError(f"unknown LoRA adapter {adapter!r}")
+        req = Request(rid, list(prompt_ids), params, adapter=adapter,
                       eos_token_id=self.args.eos_token_id)
         self.scheduler.add_request(req)
         return rid

@@ -202,6 +202,25 @@ class ModelRunner:
             max_q_len=max_q, max_ctx=max_ctx, state_slots=dv("state", S), num_tokens=row, num_seqs=S)
         return b
 
+    def _adapter_rows(self, plan: StepPlan) -> Optional[torch.Tensor]:
+        """Adapter slot of every token row of the step, or None when no sequence uses an adapter."""
+        lora = self.decoder.lora
+        if lora is None or not any(i.seq.req.adapter for i in plan.items):
+            return None
+        rows: List[int] = []
+        for it in plan.items:
+            rows += [lora.slot_of(it.seq.req.adapter)] * len(it.tokens)
+        cap = (len(rows) + 63) // 64 * 64
+        rows += [-1] * (cap - len(rows))
+        t = torch.tensor(rows, dtype=torch.int32)
+        self.h2d_bytes += t.numel() * 4
+        return t.to(self.device, non_blocking=True)
+
+    def _stage_with_adapters(self, plan: StepPlan) -> ForwardBatch:
+        batch = self._stage(plan)
+        batch.adapter_rows = self._adapter_rows(plan)
+        return batch
+
     def _set_sampling(self, plan: StepPlan) -> bool:
         """Upload per-row sampling parameters; returns True when every row is greedy."""
         all_greedy = all(i.seq.req.params.greedy for i in plan.items)
@@ -280,16 +299,17 @@ class ModelRunner:
         greedy = self._set_sampling(plan) if not host_logits else True
         n_sample_rows = sum((i.verify + 1) for i in plan.items if i.sample)
         if n_sample_rows == 0:
-            batch = self._stage(plan)
+            batch = self._stage_with_adapters(plan)
             self.decoder.backbone(batch, self.caches)
             return StepResult([[] for _ in plan.items], device_ms=(time.perf_counter() - t0) * 1e3)
         if host_logits:
             return self._execute_host_logits(plan, t0)
         is_plain_decode = plan.kind == "decode" and all(len(i.tokens) == 1 for i in plan.items)
-        if is_plain_decode and self.use_graphs and (greedy or True):
+        uses_adapter = self.decoder.lora is not None and any(i.seq.req.adapter for i in plan.items)
+        if is_plain_decode and self.use_graphs and not uses_adapter:
             self._decode_graph(plan, greedy, want_lp)
         else:
-            batch = self._stage(plan)
+            batch = self._stage_with_adapters(plan)     # steps with adapter rows run eagerly
             if not greedy and n_sample_rows != len(plan.items):
                 greedy = True                                   # verify rows are always argmax
             self._forward_select(batch, greedy, want_lp, n_sample_rows)
@@ -318,7 +338,7 @@ class ModelRunner:
     def _execute_host_logits(self, plan: StepPlan, t0: float) -> StepResult:
         """Full-logits path: penalties, logit bias, grammar masks, top-n-sigma, top log-probs."""
         from ..sampling.host import sample_rows
-        batch = self._stage(plan)
+        batch = self._stage_with_adapters(plan)
         logits, hidden = self.decoder.forward(batch, self.caches, out_f32=True)
         self.last_hidden = hidden
         toks, lps = sample_rows(self, plan, logits)

@@ -66,6 +66,7 @@ class Decoder:
         if rot > 0:
             self.cos, self.sin = ref.rope_tables(cfg.max_position, rot, cfg.rope_theta, device=self.device)
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.lora = None                   # lora.LoraManager when adapters are served
 
     # ------------------------------------------------------------------ helpers
     def _norm_act(self, x, w, fmt: str, also_bf16: bool = False) -> Act:
@@ -79,12 +80,25 @@ class Decoder:
         return ops.quantize_act(t, fmt)
 
     # ------------------------------------------------------------------ blocks
-    def attention_block(self, x, lw: LayerW, batch: ForwardBatch, kc, vc, ks, vs):
+    def _lora_for(self, batch: ForwardBatch, li: int):
+        if self.lora is None or li < 0 or getattr(batch, "adapter_rows", None) is None:
+            return None
+        return self.lora
+
+    def attention_block(self, x, lw: LayerW, batch: ForwardBatch, kc, vc, ks, vs, li: int = -1):
         c, w = self.cfg, lw.mixer
         D = c.head_dim
-        a = self._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.qkv.fmt])
+        lora = self._lora_for(batch, li)
+        a = self._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.qkv.fmt], also_bf16=lora is not None)
         qkv = ops.linear(a, w.qkv)
         qhs = 2 * D if c.attn_output_gate else D
+        if lora is not None:
+            # adapter deltas go straight into the fused q|k|v output, before norm / rope / cache write
+            xb = a.bf16 if getattr(a, "bf16", None) is not None else a.data
+            if not c.attn_output_gate:
+                lora.apply(qkv, xb, li, "q", batch.adapter_rows, 0)
+            lora.apply(qkv, xb, li, "k", batch.adapter_rows, w.heads * qhs)
+            lora.apply(qkv, xb, li, "v", batch.adapter_rows, w.heads * qhs + w.kv_heads * D)
         q = ops.qk_norm_rope_kvwrite(
             qkv, Hq=w.heads, Hkv=w.kv_heads, D=D, positions=batch.positions, slots=batch.slot_mapping,
             k_cache=kc, v_cache=vc, q_norm_w=w.q_norm, k_norm_w=w.k_norm, plus_one=c.norm_plus_one,
@@ -99,27 +113,38 @@ class Decoder:
                             gate_head_off=D)[0]
         else:
             oa = self._as_act(o, fmt)
-        return self.tp.linear_reduce(oa, w.o, residual=x)
+        y = self.tp.linear_reduce(oa, w.o, residual=x)
+        if lora is not None and not c.attn_output_gate:
+            lora.apply(y, o, li, "o", batch.adapter_rows)
+        return y
 
-    def dense_ffn(self, a: Act, w: FfnW, residual) -> torch.Tensor:
+    def dense_ffn(self, a: Act, w: FfnW, residual, lora=None, li: int = -1, rows=None) -> torch.Tensor:
         c = self.cfg
         fmt_d = ACT_FOR_WEIGHT[w.down.fmt]
+        hb = None
         if c.ffn_act == "relu2":
             up = ops.linear(a, w.gate_up)
-            h = ops.row_op(up, fmt_d, ops.IN_RELU2)[0]
+            h = ops.row_op(up, fmt_d, ops.IN_RELU2, also_bf16=lora is not None)[0]
         elif w.interleaved:
-            h = self._as_act(ops.linear(a, w.gate_up, swiglu=True), fmt_d)
+            hb = ops.linear(a, w.gate_up, swiglu=True)
+            h = self._as_act(hb, fmt_d)
         else:
             gu = ops.linear(a, w.gate_up)
-            h = ops.row_op(gu, fmt_d, ops.IN_SILU_MUL)[0]
-        return self.tp.linear_reduce(h, w.down, residual=residual)
+            h = ops.row_op(gu, fmt_d, ops.IN_SILU_MUL, also_bf16=lora is not None)[0]
+        y = self.tp.linear_reduce(h, w.down, residual=residual)
+        if lora is not None:
+            if hb is None:
+                hb = h.bf16 if getattr(h, "bf16", None) is not None else h.data
+            lora.apply(y, hb, li, "down", rows)
+        return y
 
-    def ffn_block(self, x, lw: LayerW):
+    def ffn_block(self, x, lw: LayerW, batch: Optional[ForwardBatch] = None, li: int = -1):
         if lw.ffn_kind == "none":
             return x
         if lw.ffn_kind == "dense":
             a = self._norm_act(x, lw.ln2, ACT_FOR_WEIGHT[lw.ffn.gate_up.fmt])
-            return self.dense_ffn(a, lw.ffn, x)
+            lora = self._lora_for(batch, li) if batch is not None else None
+            return self.dense_ffn(a, lw.ffn, x, lora, li, batch.adapter_rows if lora is not None else None)
         from .moe import moe_block
         return moe_block(self, x, lw)
 
@@ -127,7 +152,7 @@ class Decoder:
         if lw.kind == "attention":
             kv = kv or caches.kv
             j = caches.kv_index[i] if kv_idx is None else kv_idx
-            x = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j])
+            x = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i)
         elif lw.kind == "gdn":
             from .recurrent import gdn_block
             x = gdn_block(self, x, lw, batch, caches.state, caches.state_index[i])
@@ -139,7 +164,7 @@ class Decoder:
             kv = kv or caches.kv
             j = caches.kv_index[i] if kv_idx is None else kv_idx
             x = mla_block(self, x, lw, batch, kv, j)
-        return self.ffn_block(x, lw)
+        return self.ffn_block(x, lw, batch, i)
 
     # ------------------------------------------------------------------ full forward
     def embed(self, token_ids: torch.Tensor) -> torch.Tensor:

@@ -28,6 +28,7 @@ class SamplingParams:
     n: int = 1
     timeout_s: float = 0.0
     grammar: Optional[object] = None    # constrained decoding matcher (server/grammar.py)
+    adapter: Optional[str] = None       # LoRA adapter name (engine.load_adapter)
 
     @property
     def greedy(self) -> bool:

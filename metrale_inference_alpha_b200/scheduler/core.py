@@ -322,6 +322,10 @@ class SchedulerCore:
                 lst.remove(seq)
         if seq in self.waiting:
             self.waiting.remove(seq)
+        if seq in self.swapped:
+            self.swapped.remove(seq)
+            if self.spill is not None and hasattr(self.spill, "drop"):
+                self.spill.drop(seq)
         if publish and self.prefix is not None and seq.blocks:
             n_full = min(seq.num_computed, len(seq.tokens)) // self.cfg.block_size
             if n_full:
@@ -336,7 +340,7 @@ class SchedulerCore:
         self._finished_now.append(seq)
 
     def _check_timeouts(self, now: float) -> None:
-        for seq in list(self.waiting) + list(self.prefilling) + list(self.running):
+        for seq in list(self.waiting) + list(self.prefilling) + list(self.running) + list(self.swapped):
             limit = seq.req.params.timeout_s or self.cfg.request_timeout_s
             if limit and now - seq.req.arrival > limit:
                 self.stats["timeouts"] += 1

@@ -118,6 +118,12 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
     # ------------------------------------------------------------------ plumbing
     def _job_from_chat(body: Dict[str, Any], messages, system=None, tools=None) -> _ChatJob:
         msgs = list(messages)
+        choice = body.get("tool_choice")
+        if choice == "none":
+            tools = None
+        elif isinstance(choice, dict) and tools:
+            want = (choice.get("function") or {}).get("name") or choice.get("name")
+            tools = [t for t in tools if t.get("function", {}).get("name") == want] or tools
         if system:
             msgs = [{"role": "system", "content": system}] + msgs
         thinking = body.get("enable_thinking")
@@ -130,6 +136,7 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         ids = tokenizer.encode(text)
         sp = _sampling_from(body, cfg)
         sp.grammar = grammar_for_response_format(body.get("response_format"), tokenizer, eos)
+        sp.adapter = body.get("adapter")
         return _ChatJob(ids, sp, tools, thinking, bool(body.get("logprobs")), bool(body.get("return_token_ids")))
 
     async def _collect(job: _ChatJob):
@@ -243,6 +250,7 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         ids = prompt if (isinstance(prompt, list) and prompt and isinstance(prompt[0], int)) else \
             tokenizer.encode(prompt if isinstance(prompt, str) else prompt[0])
         sp = _sampling_from(body, cfg)
+        sp.adapter = body.get("adapter")
         if body.get("ignore_eos"):
             sp.ignore_eos = True
         job = _ChatJob(ids, sp)

@@ -50,16 +50,23 @@ def build_parser() -> argparse.ArgumentParser:
     s = sub.add_parser("serve", help="start the HTTP server")
     _add_engine_args(s)
     s.add_argument("--host", default="127.0.0.1")
-    s.add_argument("--port", type=int, default=8000)
+    s.add_argument("--port", type=int, default=8888)
     s.add_argument("--served-model-name", default=None)
     s.add_argument("--tokenizer", default=None, help="directory with tokenizer.json (default: the checkpoint)")
     s.add_argument("--api-key", action="append", default=[])
     s.add_argument("--rate-limit", type=float, default=0.0, help="requests per second per key; 0 = off")
-    s.add_argument("--tool-call-parser", default="hermes", choices=["hermes", "qwen3_xml", "mistral", "json"])
+    s.add_argument("--tool-call-parser", default="hermes", choices=["hermes", "qwen3_xml", "qwen3_coder", "mistral", "gemma4", "minimax_xml", "deepseek_v4_dsml",
+                            "poolside_v1", "bare_json", "json"])
     s.add_argument("--reasoning-format", default="think")
     s.add_argument("--default-max-tokens", type=int, default=1024)
     s.add_argument("--telemetry", default="basic", choices=["off", "basic", "full"])
     s.add_argument("--disable-thinking", action="store_true")
+    s.add_argument("--tool-max-tokens", type=int, default=8192)
+    s.add_argument("--lora-adapter", action="append", default=[], metavar="NAME=DIR", help="PEFT adapter to serve")
+    s.add_argument("--max-loras", type=int, default=8)
+    s.add_argument("--max-lora-rank", type=int, default=16)
+    s.add_argument("--swap-space-gb", type=float, default=0.0,
+                   help="> 0: preempted sequences are swapped to host memory (then swap files) instead of recomputed")
 
     b = sub.add_parser("benchmark", help="concurrency ladder over the engine API")
     _add_engine_args(b)
@@ -123,12 +130,18 @@ def serve(ns) -> None:
     from .app import ServerConfig, create_app
     from .tokenizer import load_tokenizer
     eargs = _engine_args(ns)
+    if ns.swap_space_gb > 0:
+        eargs.preempt_mode, eargs.swap_space_bytes = "swap", int(ns.swap_space_gb * (1 << 30))
     engine = LLMEngine(eargs)
+    for spec in ns.lora_adapter:
+        name, _, path = spec.partition("=")
+        engine.load_adapter(name, path, ns.max_loras, ns.max_lora_rank)
     tok_dir = ns.tokenizer or (eargs.model if isinstance(eargs.model, str) and os.path.isdir(eargs.model) else None)
     tokenizer = load_tokenizer(tok_dir, engine.cfg.vocab_size)
     cfg = ServerConfig(model_name=ns.served_model_name or str(ns.model), auth_tokens=ns.api_key,
                        rate_per_s=ns.rate_limit, tool_call_parser=ns.tool_call_parser,
                        reasoning_format=ns.reasoning_format, default_max_tokens=ns.default_max_tokens,
+                       tool_max_tokens=ns.tool_max_tokens,
                        telemetry=ns.telemetry, disable_thinking=ns.disable_thinking)
     app = create_app(engine, tokenizer, cfg)
     uvicorn.run(app, host=ns.host, port=ns.port, log_level="info", timeout_graceful_shutdown=20)

@@ -7,7 +7,7 @@ from __future__ import annotations
 from typing import Tuple
 
 FORMATS = {"think": ("<think>", "</think>"), "mistral": ("[THINK]", "[/THINK]"),
-           "gemma": ("<|channel>", "<channel|>")}
+           "gemma": ("<|channel>", "<channel|>"), "gemma4": ("<|channel>", "<channel|>")}
 
 
 class ReasoningParser:

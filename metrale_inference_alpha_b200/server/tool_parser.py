@@ -83,11 +83,133 @@ def parse_bare_json(text: str) -> Tuple[str, List[dict]]:
     return text.strip(), calls
 
 
+def _loose_value(v: str):
+    """A parameter body: JSON when it parses, else the raw text."""
+    v = v.strip()
+    try:
+        return json.loads(v)
+    except Exception:
+        return v
+
+
+def parse_minimax_xml(text: str) -> Tuple[str, List[dict]]:
+    """``<minimax:tool_call><invoke name="f"><parameter name="k">v</parameter></invoke></minimax:tool_call>``"""
+    calls, keep, pos = [], [], 0
+    for m in re.finditer(r"<minimax:tool_call>(.*?)(?:</minimax:tool_call>|$)", text, re.S):
+        found = False
+        for inv in re.finditer(r'<invoke name="([^"]+)">(.*?)</invoke>', m.group(1), re.S):
+            args = {k: v.strip("\n") for k, v in re.findall(r'<parameter name="([^"]+)">(.*?)</parameter>', inv.group(2), re.S)}
+            calls.append(_call(inv.group(1), args))
+            found = True
+        if found:
+            keep.append(text[pos:m.start()])
+            pos = m.end()
+    keep.append(text[pos:])
+    return "".join(keep).strip(), calls
+
+
+def parse_gemma4(text: str) -> Tuple[str, List[dict]]:
+    """``<|tool_call>call:fn_name{key:val,...}<tool_call|>``; values are JSON scalars / strings,
+    bare words are taken as strings."""
+    calls, keep, pos = [], [], 0
+    for m in re.finditer(r"<\|tool_call>\s*call:([\w.\-]+)\s*\{(.*?)\}\s*<tool_call\|>", text, re.S):
+        body, args, ok = m.group(2), {}, True
+        depth, cur, parts, in_str = 0, "", [], False
+        for ch in body:                                   # split on top-level commas
+            if ch == '"' and not cur.endswith("\\"):
+                in_str = not in_str
+            if not in_str:
+                if ch in "[{":
+                    depth += 1
+                elif ch in "]}":
+                    depth -= 1
+                elif ch == "," and depth == 0:
+                    parts.append(cur)
+                    cur = ""
+                    continue
+            cur += ch
+        if cur.strip():
+            parts.append(cur)
+        for part in parts:
+            if ":" not in part:
+                ok = False
+                break
+            k, v = part.split(":", 1)
+            args[k.strip().strip('"')] = _loose_value(v)
+        if ok:
+            keep.append(text[pos:m.start()])
+            pos = m.end()
+            calls.append(_call(m.group(1), args))
+    keep.append(text[pos:])
+    return "".join(keep).strip(), calls
+
+
+_DSML = "\uff5cDSML\uff5c"
+
+
+def parse_deepseek_dsml(text: str) -> Tuple[str, List[dict]]:
+    """``<|DSML|tool_calls> <|DSML|invoke name="f"> <|DSML|parameter name="k" string="true|false">v
+    </|DSML|parameter> </|DSML|invoke> </|DSML|tool_calls>`` (full-width bars). An invoke with a
+    repeated key or an unparsable non-string parameter is dropped whole."""
+    o, c = f"<{_DSML}tool_calls>", f"</{_DSML}tool_calls>"
+    i = text.find(o)
+    if i < 0:
+        return text, []
+    j = text.find(c, i)
+    block = text[i + len(o): j if j >= 0 else len(text)]
+    calls = []
+    for inv in re.finditer(rf'<{_DSML}invoke name="([^"]+)">(.*?)</{_DSML}invoke>', block, re.S):
+        args, ok = {}, True
+        for k, is_str, v in re.findall(rf'<{_DSML}parameter name="([^"]+)"(?: string="(true|false)")?>(.*?)</{_DSML}parameter>',
+                                       inv.group(2), re.S):
+            if k in args:
+                ok = False
+                break
+            if is_str == "false":
+                try:
+                    args[k] = json.loads(v)
+                except Exception:
+                    ok = False
+                    break
+            else:
+                args[k] = v
+        if ok:
+            calls.append(_call(inv.group(1), args))
+    rest = (text[:i] + (text[j + len(c):] if j >= 0 else "")).strip()
+    return (rest, calls) if calls else (text, [])
+
+
+def parse_poolside_v1(text: str) -> Tuple[str, List[dict]]:
+    """``<tool_call>NAME<arg_key>K</arg_key><arg_value>V</arg_value>...</tool_call>``; a bare NAME is a
+    zero-argument call. Repeated keys or names that are not plain identifiers drop the call."""
+    calls, keep, pos = [], [], 0
+    for m in re.finditer(r"<tool_call>\s*([A-Za-z_][\w.\-]*)\s*((?:<arg_key>.*?</arg_key>\s*<arg_value>.*?</arg_value>\s*)*)</tool_call>",
+                         text, re.S):
+        args, ok = {}, True
+        for k, v in re.findall(r"<arg_key>(.*?)</arg_key>\s*<arg_value>(.*?)</arg_value>", m.group(2), re.S):
+            k = k.strip()
+            if k in args or not re.fullmatch(r"[A-Za-z_][\w.\-]*", k):
+                ok = False
+                break
+            args[k] = _loose_value(v)
+        if ok:
+            keep.append(text[pos:m.start()])
+            pos = m.end()
+            calls.append(_call(m.group(1), args))
+    keep.append(text[pos:])
+    return "".join(keep).strip(), calls
+
+
 PARSERS = {"hermes": parse_hermes, "qwen3_xml": parse_qwen3_xml, "qwen3_coder": parse_qwen3_xml,
-           "mistral": parse_mistral, "bare_json": parse_bare_json}
+           "mistral": parse_mistral, "bare_json": parse_bare_json, "json": parse_bare_json,
+           "minimax_xml": parse_minimax_xml, "gemma4": parse_gemma4, "deepseek_v4_dsml": parse_deepseek_dsml,
+           "poolside_v1": parse_poolside_v1}
 PIPELINE = {"hermes": ["hermes", "qwen3_xml", "bare_json"], "qwen3_xml": ["qwen3_xml", "hermes", "bare_json"],
             "qwen3_coder": ["qwen3_xml", "hermes", "bare_json"], "mistral": ["mistral", "bare_json"],
-            "bare_json": ["bare_json"]}
+            "bare_json": ["bare_json"], "json": ["bare_json"],
+            "minimax_xml": ["minimax_xml", "qwen3_xml", "hermes", "bare_json"], "gemma4": ["gemma4", "bare_json"],
+            "deepseek_v4_dsml": ["deepseek_v4_dsml", "bare_json"],
+            "poolside_v1": ["poolside_v1", "hermes", "bare_json"]}
 
 
 def _coerce(value, schema: dict):
@@ -149,7 +271,7 @@ def parse_tool_calls(text: str, fmt: str = "hermes", tools: Optional[List[dict]]
 class StreamingToolDetector:
     """Holds back streamed text from the first tool-call opener on, so clients never see raw
     call markup; the held text is parsed when the stream ends."""
-    OPENERS = ("<tool_call>", "[TOOL_CALLS]")
+    OPENERS = ("<tool_call>", "[TOOL_CALLS]", "<minimax:tool_call>", "<|tool_call>", "<\uff5cDSML\uff5ctool_calls>")
 
     def __init__(self):
         self.held = ""

@@ -83,3 +83,30 @@ def test_penalties_and_logit_bias_path():
     rep = eng.generate([[9, 8, 7, 6]], SamplingParams(max_tokens=6, repetition_penalty=1.5,
                                                       frequency_penalty=0.5))[0].output_ids
     assert len(rep) == 6 and isinstance(base, list)
+
+
+def test_swap_preemption_resumes_without_recompute_and_matches_recompute_mode(tmp_path):
+    """Under KV pressure the swap mode copies a victim's blocks out and back; tokens must equal
+    both the roomy run and the recompute mode, and no prompt token is prefetched twice."""
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    prompts = [[(7 * i + j) % 200 + 1 for j in range(40)] for i in range(4)]
+    sp = SamplingParams(max_tokens=40)
+
+    def run(**kw):
+        eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=128,
+                                   enable_prefix_caching=False, use_cuda_graphs=False, **kw))
+        eng.sched_cfg.decode_reserve_tokens = 0
+        outs = eng.generate(prompts, sp)
+        return [o.output_ids for o in outs], eng
+    roomy, _ = run(num_kv_blocks=64)
+    swap, e1 = run(num_kv_blocks=14, preempt_mode="swap", swap_space_bytes=1 << 20, swap_dir=str(tmp_path))
+    rec, e2 = run(num_kv_blocks=14)
+    assert swap == roomy == rec
+    assert e1.scheduler.stats["preempted"] > 0 and e1.spill.stats["saved"] > 0
+    assert e1.spill.stats["saved"] == e1.spill.stats["restored"]
+    assert e1.scheduler.stats["prefill_tokens"] == 4 * 40            # nothing was prefetched again
+    assert e2.scheduler.stats["prefill_tokens"] > 4 * 40             # recompute mode re-ran prompts
+    # a tiny host budget pushes victims to swap files
+    disk, e3 = run(num_kv_blocks=14, preempt_mode="swap", swap_space_bytes=1, swap_dir=str(tmp_path))
+    assert disk == roomy and e3.spill.stats["to_disk"] > 0 and not list(tmp_path.glob("*.pt"))

@@ -169,3 +169,62 @@ def test_mla_attention_matches_fp32_oracle(H, q_lens, ctx_lens, part_tokens):
     ops.check_status(DEV)
     err = (got.cpu() - want).abs().max().item()
     assert err < 2e-2 * max(1.0, want.abs().max().item()), err
+
+
+# ---------------------------------------------------------------------------- LoRA shrink / expand
+def test_lora_kernels_match_cpu_manager():
+    from metrale_inference_alpha_b200.lora import LoraAdapter, LoraManager
+    g = torch.Generator().manual_seed(4)
+    dims = {"o": (1024, 520), "k": (1024, 256)}
+    cpu = LoraManager(2, dims, max_adapters=4, max_rank=16)
+    gpu = LoraManager(2, dims, max_adapters=4, max_rank=16, device=DEV)
+    for i, r in enumerate((8, 16, 4)):
+        w = {(l, t): ((torch.randn(r, dims[t][0], generator=g) * 0.1).bfloat16(),
+                      (torch.randn(dims[t][1], r, generator=g) * 0.1).bfloat16()) for l in range(2) for t in dims}
+        for m in (cpu, gpu):
+            m.load(LoraAdapter(f"a{i}", r, alpha=2.0 * r, weights=w))
+    M = 37
+    x = torch.randn(M, 1024, generator=g).bfloat16()
+    rows = torch.tensor([(-1, 0, 1, 2)[i % 4] for i in range(64)], dtype=torch.int32)
+    for layer, target, col0, width in ((0, "o", 0, 520), (1, "k", 128, 640)):
+        base = torch.randn(M, width, generator=g).bfloat16()
+        want = base.clone()
+        cpu.apply(want, x.float(), layer, target, rows, col0)
+        got = base.to(DEV)
+        gpu.apply(got, x.to(DEV), layer, target, rows.to(DEV), col0)
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+        assert torch.allclose(got.float().cpu(), want.float(), rtol=2e-2, atol=2e-2)
+        untouched = [m for m in range(M) if rows[m] < 0]
+        assert torch.equal(got.cpu()[untouched], base[untouched])
+
+
+def test_engine_with_adapter_on_gpu_matches_cpu_engine():
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.lora import LoraAdapter
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    cfg = preset("tiny-dense")
+    g = torch.Generator().manual_seed(9)
+    D = cfg.head_dim
+    t = {}
+    for l in range(cfg.num_layers):
+        for tg, (K, N) in {"q": (cfg.hidden_size, cfg.num_heads * D), "o": (cfg.num_heads * D, cfg.hidden_size),
+                           "down": (cfg.intermediate_size, cfg.hidden_size)}.items():
+            grp = "mlp" if tg == "down" else "self_attn"
+            t[f"base_model.model.model.layers.{l}.{grp}.{tg}_proj.lora_A.weight"] = torch.randn(4, K, generator=g) * 0.3
+            t[f"base_model.model.model.layers.{l}.{grp}.{tg}_proj.lora_B.weight"] = torch.randn(N, 4, generator=g) * 0.3
+    outs = {}
+    for dev in ("cpu", DEV):
+        eng = LLMEngine(EngineArgs(model=cfg, device=dev, max_num_seqs=4, max_model_len=128))
+        eng.load_adapter("ad", LoraAdapter.from_tensors("ad", t, 4, 8.0))
+        rid_a = eng.add_request([3, 4, 5, 6, 7, 8], SamplingParams(max_tokens=6), adapter="ad")
+        rid_b = eng.add_request([3, 4, 5, 6, 7, 8], SamplingParams(max_tokens=6))
+        res = {}
+        while eng.has_work():
+            for o in eng.step():
+                if o.finished:
+                    res[o.request_id] = o.output_ids
+        outs[dev] = (res[rid_a], res[rid_b])
+    assert outs[DEV][1] == outs["cpu"][1]
+    assert outs[DEV][0] != outs[DEV][1]          # the adapter changes the continuation
+    assert outs[DEV][0][:2] == outs["cpu"][0][:2]

@@ -327,3 +327,34 @@ def test_gpu_fault_latch_turns_routes_into_503(client):
         eng.fault._reason = None if hasattr(eng.fault, "_reason") else None
         eng.fault.__init__()
     assert client.get("/health").status_code == 200
+
+
+def test_more_tool_call_formats():
+    d = "｜DSML｜"
+    cases = {
+        "minimax_xml": 'ok <minimax:tool_call>\n<invoke name="get_weather">\n<parameter name="city">Oslo</parameter>\n'
+                       '<parameter name="days">3</parameter>\n</invoke>\n</minimax:tool_call>',
+        "gemma4": '<|tool_call>call:get_weather{city:"Oslo",days:3}<tool_call|>',
+        "deepseek_v4_dsml": f'<{d}tool_calls>\n<{d}invoke name="get_weather">\n<{d}parameter name="city" string="true">Oslo'
+                            f'</{d}parameter>\n<{d}parameter name="days" string="false">3</{d}parameter>\n</{d}invoke>\n</{d}tool_calls>',
+        "poolside_v1": '<tool_call>get_weather<arg_key>city</arg_key><arg_value>Oslo</arg_value>'
+                       '<arg_key>days</arg_key><arg_value>3</arg_value></tool_call>',
+    }
+    for fmt, text in cases.items():
+        rest, calls = parse_tool_calls(text, fmt, TOOLS)
+        assert len(calls) == 1 and calls[0]["function"]["name"] == "get_weather", fmt
+        assert json.loads(calls[0]["function"]["arguments"]) == {"city": "Oslo", "days": 3}, fmt
+        assert "tool_call" not in rest and "DSML" not in rest
+    # poolside: bare name = zero-argument call; a repeated key drops the call
+    assert parse_tool_calls("<tool_call>get_weather</tool_call>", "poolside_v1", TOOLS)[1][0]["function"]["arguments"] == "{}"
+    dup = '<tool_call>get_weather<arg_key>a</arg_key><arg_value>1</arg_value><arg_key>a</arg_key><arg_value>2</arg_value></tool_call>'
+    assert parse_tool_calls(dup, "poolside_v1", TOOLS)[1] == []
+    # DSML: a repeated key drops the invoke whole
+    bad = (f'<{d}tool_calls><{d}invoke name="get_weather"><{d}parameter name="city" string="true">a</{d}parameter>'
+           f'<{d}parameter name="city" string="true">b</{d}parameter></{d}invoke></{d}tool_calls>')
+    assert parse_tool_calls(bad, "deepseek_v4_dsml", TOOLS)[1] == []
+
+
+def test_reasoning_formats_mistral_and_gemma():
+    assert split_reasoning("[THINK]plan[/THINK]answer", "mistral") == ("plan", "answer")
+    assert split_reasoning("<|channel>plan<channel|>answer", "gemma4") == ("plan", "answer")
