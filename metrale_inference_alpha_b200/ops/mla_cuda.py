@@ -25,6 +25,7 @@ class MlaArgs(C.Structure):
 _native.register_optional("mb_mla_attention", [C.POINTER(MlaArgs), c_void_p])
 
 LATENT, ROW = 512, 576
+_CNT_BYTES = 64 * 1024
 
 
 def supported(q: torch.Tensor, cache: torch.Tensor) -> bool:
@@ -47,7 +48,9 @@ def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_table, q_start, q_
     out = torch.empty(T, H, LATENT, dtype=torch.float32, device=q.device)
     need = L.mb_mla_ws_bytes(T, H, max_ctx, part_tokens)
     if need:
-        rt.ensure_attn_ws(need)
+        # the head of the shared attention workspace holds the split-KV kernel's arrival counters,
+        # which must stay zero between its launches: the MLA partials live behind them
+        rt.ensure_attn_ws(need + _CNT_BYTES)
         if row_seq is None:                       # row -> sequence map for the merge pass
             row_seq = torch.repeat_interleave(torch.arange(q_len.numel(), device=q.device, dtype=torch.int32),
                                               q_len.clamp(min=0).long(), output_size=None)
@@ -60,7 +63,7 @@ def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_table, q_start, q_
     a.num_seqs, a.max_q_len, a.max_ctx, a.total_rows = q_len.numel(), max_q_len, max_ctx, T
     a.H, a.block_size, a.num_blocks, a.scale = H, cache.shape[1], cache.shape[0], scale
     a.out, a.part_tokens, a.status = _ptr(out), part_tokens, _ptr(rt.status)
-    a.ws, a.ws_bytes = (_ptr(rt.attn_ws), rt.attn_ws.numel()) if need else (None, 0)
+    a.ws, a.ws_bytes = (_ptr(rt.attn_ws) + _CNT_BYTES, rt.attn_ws.numel() - _CNT_BYTES) if need else (None, 0)
     _native.check(L.mb_mla_attention(C.byref(a), _stream()), "mla_attention")
     _count()
     return out

@@ -199,32 +199,40 @@ def test_lora_kernels_match_cpu_manager():
         assert torch.equal(got.cpu()[untouched], base[untouched])
 
 
-def test_engine_with_adapter_on_gpu_matches_cpu_engine():
+def test_engine_with_adapters_on_gpu_isolates_rows():
     from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
     from metrale_inference_alpha_b200.lora import LoraAdapter
     from metrale_inference_alpha_b200.sampling.params import SamplingParams
     cfg = preset("tiny-dense")
-    g = torch.Generator().manual_seed(9)
     D = cfg.head_dim
-    t = {}
-    for l in range(cfg.num_layers):
-        for tg, (K, N) in {"q": (cfg.hidden_size, cfg.num_heads * D), "o": (cfg.num_heads * D, cfg.hidden_size),
-                           "down": (cfg.intermediate_size, cfg.hidden_size)}.items():
-            grp = "mlp" if tg == "down" else "self_attn"
-            t[f"base_model.model.model.layers.{l}.{grp}.{tg}_proj.lora_A.weight"] = torch.randn(4, K, generator=g) * 0.3
-            t[f"base_model.model.model.layers.{l}.{grp}.{tg}_proj.lora_B.weight"] = torch.randn(N, 4, generator=g) * 0.3
-    outs = {}
-    for dev in ("cpu", DEV):
-        eng = LLMEngine(EngineArgs(model=cfg, device=dev, max_num_seqs=4, max_model_len=128))
-        eng.load_adapter("ad", LoraAdapter.from_tensors("ad", t, 4, 8.0))
-        rid_a = eng.add_request([3, 4, 5, 6, 7, 8], SamplingParams(max_tokens=6), adapter="ad")
-        rid_b = eng.add_request([3, 4, 5, 6, 7, 8], SamplingParams(max_tokens=6))
+
+    def tensors(seed, zero_b):
+        g = torch.Generator().manual_seed(seed)
+        t = {}
+        for l in range(cfg.num_layers):
+            for tg, (K, N) in {"q": (cfg.hidden_size, cfg.num_heads * D), "v": (cfg.hidden_size, cfg.num_kv_heads * D),
+                               "o": (cfg.num_heads * D, cfg.hidden_size), "down": (cfg.intermediate_size, cfg.hidden_size)}.items():
+                grp = "mlp" if tg == "down" else "self_attn"
+                t[f"base_model.model.model.layers.{l}.{grp}.{tg}_proj.lora_A.weight"] = torch.randn(4, K, generator=g) * 0.5
+                t[f"base_model.model.model.layers.{l}.{grp}.{tg}_proj.lora_B.weight"] = (
+                    torch.zeros(N, 4) if zero_b else torch.randn(N, 4, generator=g) * 0.5)
+        return t
+    eng = LLMEngine(EngineArgs(model=cfg, device=DEV, max_num_seqs=4, max_model_len=128))
+    eng.load_adapter("noop", LoraAdapter.from_tensors("noop", tensors(1, True), 4, 8.0))
+    eng.load_adapter("strong", LoraAdapter.from_tensors("strong", tensors(2, False), 4, 8.0))
+    prompt, sp = [3, 4, 5, 6, 7, 8, 9, 10], SamplingParams(max_tokens=6)
+
+    def run(adapters):
+        ids = [eng.add_request(prompt, sp, adapter=a) for a in adapters]
         res = {}
         while eng.has_work():
             for o in eng.step():
                 if o.finished:
                     res[o.request_id] = o.output_ids
-        outs[dev] = (res[rid_a], res[rid_b])
-    assert outs[DEV][1] == outs["cpu"][1]
-    assert outs[DEV][0] != outs[DEV][1]          # the adapter changes the continuation
-    assert outs[DEV][0][:2] == outs["cpu"][0][:2]
+        return [res[i] for i in ids]
+    base = run([None])[0]                          # CUDA-graph decode path
+    assert run(["noop"])[0] == base                # eager path with a zero delta: same tokens
+    mixed = run([None, "strong", "noop"])
+    assert mixed[0] == base and mixed[2] == base and mixed[1] != base
+    assert run(["strong"])[0] == mixed[1]          # the adapted row does not depend on its neighbours
+    ops.check_status(DEV)
