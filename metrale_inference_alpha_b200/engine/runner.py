@@ -145,8 +145,38 @@ class ModelRunner:
         self.logit_processor = None    # fn(seq, row_logits fp32 [V]) -> row_logits, host-logits path
 
     # ------------------------------------------------------------------ batch staging
+    def _stage_decode_incremental(self, plan: StepPlan, pad_seqs: int) -> bool:
+        """Plain decode of the same sequences as the previous staged decode step: the pinned
+        staging arrays still hold that step, so advance them in place (vectorised: positions and
+        context + 1, slots recomputed from the block table, block-table entries only for the
+        sequences that crossed into a new block) instead of rebuilding every row in Python."""
+        st, bs, items = self.stage, self.block_size, plan.items
+        S = len(items)
+        sig = (pad_seqs, tuple(it.seq.seq_id for it in items))
+        if sig != self._fast_sig:
+            self._fast_sig_next = sig
+            return False
+        npv = lambda name: st.view(st.np, name)
+        pos, ctx, tokens = npv("pos"), npv("ctx"), npv("tokens")
+        if items[0].start_pos != pos[0] + 1 or items[-1].start_pos != pos[S - 1] + 1:
+            self._fast_sig_next = sig
+            return False
+        tokens[:S] = [it.tokens[0] for it in items]
+        pos[:S] += 1
+        ctx[:S] += 1
+        p = pos[:S]
+        bt2 = npv("bt").reshape(st.S_cap, st.max_blocks)
+        for s in np.nonzero(p % bs == 0)[0]:
+            bt2[s, p[s] // bs] = items[s].seq.blocks[p[s] // bs]
+        slots = npv("slots").view(np.int64)
+        slots[:S] = bt2[np.arange(S), p // bs].astype(np.int64) * bs + p % bs
+        st.upload()
+        self.h2d_bytes += st.bytes_per_copy
+        return True
+
     def _stage(self, plan: StepPlan, pad_seqs: int = 0, logits_all_verify: bool = True) -> ForwardBatch:
         st, bs = self.stage, self.block_size
+        self._fast_sig, self._fast_sig_next = None, None      # any full staging invalidates the fast path
         n_rows = sum(len(i.tokens) for i in plan.items)
         n_seqs = max(len(plan.items), pad_seqs)
         pad_rows = max(0, pad_seqs - len(plan.items))
@@ -201,6 +231,9 @@ class ModelRunner:
             logit_rows=dv("lrows", 2 * nl).view(torch.int64),
             max_q_len=max_q, max_ctx=max_ctx, state_slots=dv("state", S), num_tokens=row, num_seqs=S)
         return b
+
+    _fast_sig = None
+    _fast_sig_next = None
 
     def _adapter_rows(self, plan: StepPlan) -> Optional[torch.Tensor]:
         """Adapter slot of every token row of the step, or None when no sequence uses an adapter."""
@@ -281,7 +314,10 @@ class ModelRunner:
             with torch.cuda.graph(g):
                 self._forward_select(null, greedy, want_lp, rung)
             self.graphs[key] = (g, ops.launch_count - count0, self.last_hidden)
-        self._stage(plan, pad_seqs=rung)
+        if not self._stage_decode_incremental(plan, rung):
+            sig = self._fast_sig_next
+            self._stage(plan, pad_seqs=rung)
+            self._fast_sig = sig                              # the arrays now hold this decode step
         g, launches, hidden = self.graphs[key]
         g.replay()
         ops.launch_count += launches

@@ -347,13 +347,15 @@ class SchedulerCore:
                 self._finish(seq, FinishReason.TIMEOUT, publish=False)
 
     def _output(self, seq: Sequence) -> RequestOutput:
-        new = seq.output_ids[seq.emitted:]
+        new = seq.tokens[seq.prompt_len + seq.emitted:]
         seq.emitted = seq.num_output
+        done = seq.is_finished()
         ttft = None if seq.first_token_time is None else (seq.first_token_time - seq.req.arrival) * 1e3
         dec = None
         if seq.finish_time is not None and seq.first_token_time is not None:
             dec = (seq.finish_time - seq.first_token_time) * 1e3
-        return RequestOutput(seq.req.request_id, new, seq.output_ids, seq.is_finished(),
+        # the cumulative ids travel with the final output only (a per-step copy would be quadratic)
+        return RequestOutput(seq.req.request_id, new, seq.output_ids if done else new, done,
                              seq.finish.value if seq.finish else None, seq.prompt_len, seq.cached_tokens,
                              ttft, dec, seq.logprobs if seq.req.params.logprobs else None,
                              seq.accepted_draft_tokens, seq.rejected_draft_tokens)

@@ -124,7 +124,7 @@ class FatalDeviceError(RuntimeError):
 class RequestOutput:
     request_id: str
     new_token_ids: List[int]
-    output_ids: List[int]
+    output_ids: List[int]              # all generated ids once `finished`; the new ids of this step before
     finished: bool
     finish_reason: Optional[str] = None
     prompt_tokens: int = 0
