@@ -367,13 +367,14 @@ __global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_split
   const int ntiles = empty ? 0 : (tok_end - tok_begin + kTile - 1) / kTile;
 
   // block ids of this partition, staged once (bounds-checked here, not per chunk)
-  __shared__ int s_blk[64];
+  constexpr int kMaxBlk = 160;                                 // 2496 tokens per partition at block 16
+  __shared__ int s_blk[kMaxBlk];
   const int bs = p.block_size;
-  const bool fast_blocks = (bs == 16 || bs == 32 || bs == 64) && (p.part_tokens + 64) / bs <= 64;
+  const bool fast_blocks = (bs == 16 || bs == 32 || bs == 64) && (p.part_tokens + 64) / bs <= kMaxBlk;
   const int bs_shift = 31 - __clz(bs);
   if (!empty) {
     const int first_blk = tok_begin / bs, nblk = (tok_end - 1) / bs - first_blk + 1;
-    for (int i = tid; i < nblk && i < 64; i += 128) {
+    for (int i = tid; i < nblk && i < kMaxBlk; i += 128) {
       int b = bt[first_blk + i];
       if (b < 0 || b >= p.num_blocks) {
         if (p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
@@ -386,11 +387,35 @@ __global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_split
   // per-thread constants of the copy pattern: chunk i of a tile is row r_i, 16-byte column c_i
   constexpr int kCopies = (64 * kChunks) / 128;
   const size_t row_pitch = (size_t)p.Hkv * kRowB;              // bytes between consecutive tokens
+  // When the rows a thread copies are a whole number of cache blocks apart, everything but the
+  // block id is the same for every tile: one shared-memory read and one multiply-add per copy.
+  constexpr int kStep = (kChunks <= 128 && 128 % kChunks == 0) ? 128 / kChunks : 0;   // rows between copies
+  const bool lin = fast_blocks && kStep > 0 && (kStep % bs) == 0 && kCopies <= 8;
+  const int r0 = tid / kChunks, c0 = tid % kChunks;
+  const uint32_t soff0 = raw_off<kRowB>(r0, c0);               // kStep % 8 == 0: the swizzle term is fixed
+  const size_t gbase = (size_t)(r0 & (bs - 1)) * row_pitch + (size_t)kvh * kRowB + (size_t)c0 * 16;
+  const size_t blk_pitch = (size_t)bs * row_pitch;
+  const int bsel0 = r0 >> bs_shift, bstep = kStep >> bs_shift;
   auto issue_tile = [&](int it) {
     const int stage = it % kStages;
     const uint32_t sK = sbase + stage * 2 * kTileB, sV = sK + kTileB;
     const int tok0 = tok_begin + it * kTile;
     const int blk0 = (tok0 - tok_begin) >> bs_shift;
+    if (lin) {
+#pragma unroll
+      for (int i = 0; i < kCopies; ++i) {
+        const bool valid = tok0 + r0 + i * kStep < tok_end;
+        const int blk = valid ? s_blk[blk0 + bsel0 + i * bstep] : 0;
+        const size_t off = (size_t)blk * blk_pitch + gbase;
+        const int sz = valid ? 16 : 0;
+        const uint32_t so = soff0 + (uint32_t)(i * kStep * kRowB);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sK + so),
+                     "l"(reinterpret_cast<const uint8_t*>(p.k_cache) + off), "r"(sz) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sV + so),
+                     "l"(reinterpret_cast<const uint8_t*>(p.v_cache) + off), "r"(sz) : "memory");
+      }
+      return;
+    }
 #pragma unroll
     for (int i = 0; i < kCopies; ++i) {
       const int idx = tid + i * 128;
