@@ -53,6 +53,7 @@ class EngineArgs:
     request_timeout_s: float = 300.0
     eos_token_id: Optional[int] = None
     fused_collectives: bool = True
+    static_act_scales: bool = True                     # NVFP4: calibrate down-projection input scales at start-up
     preempt_mode: str = "recompute"                    # recompute | swap (KV + state to host memory / swap files)
     swap_space_bytes: int = 8 << 30
     swap_dir: Optional[str] = None
@@ -93,6 +94,9 @@ class LLMEngine:
         ops.configure(attn_part_tokens=1024 if args.max_num_seqs >= 64 else 512)
         self.runner = ModelRunner(cfg, self.weights, args.device, blocks, self.sched_cfg, self.tp,
                                   use_graphs=args.use_cuda_graphs, kv_poison=args.kv_poison)
+        self.calibrated_layers = 0
+        if args.static_act_scales and cfg.weight_format == "nvfp4" and self.device.type == "cuda":
+            self.calibrated_layers = self.runner.calibrate_static_scales()
         needs_snap = self.runner.pool is not None
         self.prefix = None
         if args.enable_prefix_caching:

@@ -235,6 +235,46 @@ class ModelRunner:
     _fast_sig = None
     _fast_sig_next = None
 
+    # ------------------------------------------------------------------ static activation scales
+    def calibrate_static_scales(self, tokens: int = 256, margin: float = 2.0, seed: int = 1234) -> int:
+        """NVFP4 models: fix the global scale of the down projection's input per layer (what a
+        ModelOpt checkpoint calls `input_scale`), so that the quantiser becomes row-local and can
+        run inside the producing GEMM's epilogue. One prefill of random tokens through temporary
+        KV blocks records max |SwiGLU output| per layer; scale = margin * amax / (6 * 448).
+        Checkpoint-provided scales (already > 0) are kept. Returns the number of layers set."""
+        ffns = [lw.ffn for lw in self.w.layers
+                if lw.ffn_kind == "dense" and getattr(lw.ffn, "interleaved", False) and lw.ffn.down.fmt == "nvfp4"]
+        todo = [f for f in ffns if f.down_in_scale <= 0.0]
+        if not todo:
+            for f in ffns:
+                ops.static_scale_vec(self.device, f.down_in_scale, 256)
+            return 0
+        tokens = min(tokens, self.sched.max_prefill_tokens, self.sched.max_model_len - 1)
+        g = torch.Generator().manual_seed(seed)
+        ids = torch.randint(1, self.cfg.vocab_size, (tokens,), generator=g).tolist()
+        nblk = (tokens + self.block_size - 1) // self.block_size
+        blocks = self.kv.allocator.alloc(nblk)
+        try:
+            batch = ForwardBatch.build([dict(tokens=ids, start_pos=0, blocks=blocks, state_slot=0, logits="none")],
+                                       self.block_size, device=self.device, max_blocks=self.max_blocks)
+            self.decoder.calib = {}
+            self.decoder.backbone(batch, self.caches)
+            calib = self.decoder.calib
+        finally:
+            self.decoder.calib = None
+            self.kv.allocator.free(blocks)
+        n = 0
+        for f in todo:
+            if id(f) in calib:
+                amax = float(calib[id(f)])
+                if amax > 0.0:
+                    f.down_in_scale = margin * amax / (6.0 * 448.0)
+                    n += 1
+        for f in ffns:
+            if f.down_in_scale > 0.0:
+                ops.static_scale_vec(self.device, f.down_in_scale, 256)
+        return n
+
     def _adapter_rows(self, plan: StepPlan) -> Optional[torch.Tensor]:
         """Adapter slot of every token row of the step, or None when no sequence uses an adapter."""
         lora = self.decoder.lora

@@ -67,6 +67,7 @@ class Decoder:
             self.cos, self.sin = ref.rope_tables(cfg.max_position, rot, cfg.rope_theta, device=self.device)
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         self.lora = None                   # lora.LoraManager when adapters are served
+        self.calib = None                  # dict while calibrating static activation scales (engine/runner.py)
 
     # ------------------------------------------------------------------ helpers
     def _norm_act(self, x, w, fmt: str, also_bf16: bool = False) -> Act:
@@ -126,11 +127,20 @@ class Decoder:
             up = ops.linear(a, w.gate_up)
             h = ops.row_op(up, fmt_d, ops.IN_RELU2, also_bf16=lora is not None)[0]
         elif w.interleaved:
-            hb = ops.linear(a, w.gate_up, swiglu=True)
-            h = self._as_act(hb, fmt_d)
+            static = w.down_in_scale if (fmt_d == "nvfp4" and self.calib is None) else 0.0
+            if static > 0.0 and lora is None:
+                # SwiGLU output quantised inside the GEMM epilogue with the calibrated scale
+                h = ops.linear(a, w.gate_up, swiglu=True, quant_out=static)
+            else:
+                hb = ops.linear(a, w.gate_up, swiglu=True)
+                if self.calib is not None:
+                    m = hb.float().abs().max()
+                    self.calib[id(w)] = torch.maximum(self.calib[id(w)], m) if id(w) in self.calib else m
+                h = ops.quantize_act(hb, fmt_d, static_scale=static) if fmt_d == "nvfp4" else self._as_act(hb, fmt_d)
         else:
             gu = ops.linear(a, w.gate_up)
-            h = ops.row_op(gu, fmt_d, ops.IN_SILU_MUL, also_bf16=lora is not None)[0]
+            static = w.down_in_scale if (fmt_d == "nvfp4" and self.calib is None) else 0.0
+            h = ops.row_op(gu, fmt_d, ops.IN_SILU_MUL, also_bf16=lora is not None, static_scale=static)[0]
         y = self.tp.linear_reduce(h, w.down, residual=residual)
         if lora is not None:
             if hb is None:

@@ -184,18 +184,20 @@ def _count(n: int = 1):
 def row_op(x: torch.Tensor, out_fmt: str = "bf16", mode: int = IN_COPY, *, K: Optional[int] = None,
            residual=None, write_residual: bool = False, w=None, plus_one: bool = False,
            eps: float = 1e-6, gate=None, head_dim: int = 0, gate_head_stride: int = 0,
-           gate_head_off: int = 0, group: int = 0, also_bf16: bool = False):
-    """Fused producer: builds y = recipe(x) per row and encodes it as `out_fmt`.
+           gate_head_off: int = 0, group: int = 0, also_bf16: bool = False, static_scale: float = 0.0):
+    """Fused producer: builds y = recipe(x) per row and encodes it as `out_fmt`. `static_scale`
+    (nvfp4 only): calibrated global scale used instead of the row's amax / (6 * 448).
     Returns (Act, residual_out or None). x is bf16 (or fp32 for IN_GATED_RMSNORM inputs)."""
     M = x.shape[0]
     if K is None:
         K = x.shape[1] // 2 if mode == IN_SILU_MUL else x.shape[1]
     if not x.is_cuda:
         return _row_op_ref(x, out_fmt, mode, K, residual, write_residual, w, plus_one, eps, gate,
-                           head_dim, gate_head_stride, gate_head_off, group, also_bf16)
+                           head_dim, gate_head_stride, gate_head_off, group, also_bf16, static_scale)
     L = _native.lib()
     dev = x.device
     a = _native.RowArgs()
+    a.static_gs = float(static_scale) if out_fmt == "nvfp4" else 0.0
     a.M, a.K, a.in_mode, a.out_mode = M, K, mode, OUT_MODE[out_fmt]
     if x.dtype == torch.float32:
         a.xf32 = _ptr(x)
@@ -255,7 +257,7 @@ def row_op(x: torch.Tensor, out_fmt: str = "bf16", mode: int = IN_COPY, *, K: Op
 
 
 def _row_op_ref(x, out_fmt, mode, K, residual, write_residual, w, plus_one, eps, gate, head_dim,
-                gate_head_stride, gate_head_off, group, also_bf16):
+                gate_head_stride, gate_head_off, group, also_bf16, static_scale=0.0):
     xf = x.float()
     res_out = None
     if mode == IN_RMSNORM:
@@ -278,13 +280,13 @@ def _row_op_ref(x, out_fmt, mode, K, residual, write_residual, w, plus_one, eps,
         y = xf * torch.sigmoid(g.float().reshape(x.shape[0], K))
     else:
         y = xf[:, :K]
-    act = encode_act_ref(y, out_fmt)
+    act = encode_act_ref(y, out_fmt, static_scale)
     if also_bf16 or out_fmt == "bf16":
         act.bf16 = y.to(torch.bfloat16)
     return act, res_out
 
 
-def encode_act_ref(y: torch.Tensor, fmt: str) -> Act:
+def encode_act_ref(y: torch.Tensor, fmt: str, static_scale: float = 0.0) -> Act:
     """CPU encoding: quantise exactly like the kernels, then keep the dequantised fp32 matrix."""
     M, K = y.shape
     if fmt == "bf16":
@@ -296,24 +298,34 @@ def encode_act_ref(y: torch.Tensor, fmt: str) -> Act:
         q, s = ref.quantize_fp8_group128(y)
         d = ref.from_e4m3(q) * s.t().repeat_interleave(128, 1)[:, :K]
     else:
-        q, sf, g = ref.quantize_nvfp4(y, per_row_global=True)
+        q, sf, g = ref.quantize_nvfp4(y, per_row_global=True, static_scale=static_scale)
         d = ref.dequantize_nvfp4(q, sf, g)
     return Act(fmt, M, K, d)
 
 
-def quantize_act(x: torch.Tensor, fmt: str) -> Act:
-    return row_op(x, fmt, IN_COPY)[0]
+def quantize_act(x: torch.Tensor, fmt: str, static_scale: float = 0.0) -> Act:
+    return row_op(x, fmt, IN_COPY, static_scale=static_scale)[0]
 
 
 # ----------------------------------------------------------------------------- linear
 def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
            swiglu: bool = False, out_f32: bool = False, out: Optional[torch.Tensor] = None,
-           force_tn: int = 0, force_splits: int = 0, dbg: int = 0, grouped=None, trace=None, no_cluster: bool = False, tp=None) -> torch.Tensor:
+           force_tn: int = 0, force_splits: int = 0, dbg: int = 0, grouped=None, trace=None, no_cluster: bool = False, tp=None,
+           quant_out: float = 0.0):
     """out[m, n] = sum_k act[m, k] * w[n, k] (+ residual); with `swiglu`, w holds gate/up rows
-    interleaved (2j, 2j+1) and the result is silu(gate) * up of width N/2."""
+    interleaved (2j, 2j+1) and the result is silu(gate) * up of width N/2. `quant_out` > 0 (with
+    `swiglu`): return the result as an NVFP4 `Act` quantised with that calibrated global scale --
+    inside the GEMM epilogue when the persistent kernel serves the shape, else by a row kernel."""
     assert act.K == w.K, (act.K, w.K)
     assert act.fmt == ACT_FOR_WEIGHT[w.fmt], (act.fmt, w.fmt)
     M, N = act.M, w.N
+    if quant_out > 0.0:
+        assert swiglu and residual is None and not out_f32 and grouped is None and tp is None
+        fused = (act.data.is_cuda and M <= 128 and (N + 127) // 128 > runtime(act.data.device).sm_count
+                 and w.fmt in ("nvfp4", "fp8_row", "bf16") and (N // 2) % 256 == 0 and not (dbg & 16))
+        if not fused:
+            y = linear(act, w, swiglu=True, out_f32=not act.data.is_cuda, force_tn=force_tn, force_splits=force_splits, dbg=dbg)
+            return quantize_act(y, "nvfp4", static_scale=quant_out)
     if not act.data.is_cuda:
         y = act.data.float() @ w.dequant().t()
         if swiglu:
@@ -326,11 +338,11 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
     n_out = N // 2 if swiglu else N
     if grouped is not None:
         n_out = grouped[3] // 2 if swiglu else grouped[3]
-    if out is None:
+    if out is None and quant_out <= 0.0:
         out = torch.empty(M, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16,
                           device=act.data.device)
     a = _native.GemmArgs()
-    a.kind, a.M, a.N, a.K, a.ldo = KIND[w.fmt], M, N, w.K, out.stride(0)
+    a.kind, a.M, a.N, a.K, a.ldo = KIND[w.fmt], M, N, w.K, (out.stride(0) if out is not None else n_out)
     a.W, a.X, a.out = _ptr(w.data), _ptr(act.data), _ptr(out)
     a.residual = _ptr(residual)
     a.alpha = 1.0
@@ -351,6 +363,15 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
     a.force_tn, a.force_splits, a.sm_count, a.dbg = force_tn, force_splits, rt.sm_count, dbg
     a.trace = _ptr(trace)
     a.no_cluster = int(no_cluster)
+    qact = None
+    if quant_out > 0.0:
+        Kq, dev = N // 2, act.data.device
+        qact = Act("nvfp4", M, Kq, torch.empty(M, Kq // 2, dtype=torch.uint8, device=dev))
+        qact.sf_k64 = Kq // 64
+        qact.sf = torch.empty(((M + 127) // 128) * qact.sf_k64 * 512, dtype=torch.uint8, device=dev)
+        qact.scale = static_scale_vec(dev, quant_out, M)
+        a.out = _ptr(qact.data)                              # the bf16 output does not exist in this mode
+        a.outq, a.ldq, a.outq_sf, a.outq_sf_k64, a.outq_gs = _ptr(qact.data), Kq // 2, _ptr(qact.sf), qact.sf_k64, quant_out
     if tp is not None:
         # fused all-reduce: tp = dict(size, rank, m_cap, u_cap, recv[], out[], flags[], done[], par)
         a.tp_size, a.tp_rank, a.tp_m_cap, a.tp_u_cap = tp["size"], tp["rank"], tp["m_cap"], tp["u_cap"]
@@ -364,7 +385,25 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
         a.n_per_expert, a.max_tiles, a.force_tn = grouped[3], grouped[4], grouped[5]
     _native.check(L.mb_gemm(C.byref(a), _stream()), f"gemm[{w.fmt} M={M} N={N} K={w.K}]")
     _count()
-    return out
+    return qact if qact is not None else out
+
+
+_SCALE_VECS: dict = {}
+
+
+def static_scale_vec(device, gs: float, M: int) -> torch.Tensor:
+    """[M] fp32 filled with a static activation scale (the per-token scale array the W4A4 GEMM
+    epilogue reads). Vectors are created once per (device, scale), outside any stream capture:
+    the engine calls this at calibration time; a miss during capture allocates without caching."""
+    key = (str(device), float(gs))
+    t = _SCALE_VECS.get(key)
+    if t is None or t.numel() < M:
+        n = max(256, M)
+        t = torch.full((n,), float(gs), dtype=torch.float32, device=device)
+        if torch.device(device).type == "cuda" and torch.cuda.is_current_stream_capturing():
+            return t[:M]
+        _SCALE_VECS[key] = t
+    return t[:M]
 
 
 def concat_weights(ws) -> QuantWeight:

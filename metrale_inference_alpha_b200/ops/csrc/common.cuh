@@ -375,6 +375,19 @@ __device__ __forceinline__ uint32_t e2m1_code(float x) {
   else c = 7;
   return c | (x < 0.f ? 8u : 0u);
 }
+// Two fp32 -> one byte of packed e2m1 (lo in bits 0..3, hi in bits 4..7) with the hardware
+// converter: round-to-nearest-even on the e2m1 grid, saturating at +-6 (same results as e2m1_code).
+__device__ __forceinline__ uint32_t e2m1x2_pack(float lo, float hi) {
+  uint32_t r;
+  asm("{\n"
+      ".reg .b8 b0;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+      "cvt.u32.u8 %0, b0;\n"
+      "}"
+      : "=r"(r)
+      : "f"(lo), "f"(hi));
+  return r;
+}
 __device__ __forceinline__ float e2m1_value(uint32_t code) {
   const float lut[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
   const float m = lut[code & 7];

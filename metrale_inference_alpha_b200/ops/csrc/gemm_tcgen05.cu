@@ -69,6 +69,13 @@ struct GemmParams {
   uint32_t* tp_flags[8];        // per rank: [2 parity][u_cap] arrivals per unit
   uint32_t* tp_done[8];         // per rank: CTA completion counter of the running call
   const uint32_t* tp_par;       // this rank's current parity (flipped by the last CTA of a call)
+  // quantised output of the SwiGLU epilogue (persistent kernel): packed e2m1 + tiled ue4m3 scale
+  // factors for the consuming W4A4 GEMM, with a calibrated (static) global scale
+  uint8_t* outq;      // [M, ldq] bytes, two values per byte; null = bf16 / fp32 output
+  int ldq;
+  uint8_t* outq_sf;   // [ceil(M / 128)][outq_sf_k64][512]
+  int outq_sf_k64;
+  float outq_gs;
   int cluster;        // splits form a thread-block cluster; partial tiles are reduced over DSMEM
   long long* trace;   // optional per-phase cycle stamps of CTA (0,0,0) and the last CTA in x
   int dbg;   // timing experiments only: 1 skip SF copies, 2 skip epilogue stores, 4 skip MMAs, 8 skip SF loads
@@ -619,7 +626,8 @@ struct PCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
 };
 
-constexpr int kPersistThreads = 320;   // producer warp + MMA warp + 8 epilogue warps
+constexpr int kPersistThreads = 576;   // producer warp + MMA warp + 16 epilogue warps
+constexpr int kEpiGroups = (kPersistThreads - 64) / 128;   // warps per TMEM lane quadrant
 
 template <int KIND, int TN>
 __global__ void __launch_bounds__(kPersistThreads, 1)
@@ -751,9 +759,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue: TMEM -> registers -> global
-    // eight warps: two per TMEM lane quadrant (a warp may only read the quadrant warp_id % 4),
-    // each taking every other 16-token chunk, so that the exposed epilogue of a CTA's last tile
-    // is half as long
+    // kEpiGroups warps per TMEM lane quadrant (a warp may only read the quadrant warp_id % 4),
+    // each taking every kEpiGroups-th 16-token chunk, which shortens the exposed epilogue of a
+    // CTA's last tile accordingly
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     const int lane = threadIdx.x & 31;
@@ -771,6 +779,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kPersistThreads - 64) : "memory");
     const int f = q * 32 + lane;                          // weight row of this thread inside a tile
+    const float outq_inv6gs = p.outq ? 1.f / (6.f * p.outq_gs) : 0.f;
     bool ok = true;
     for (int it = 0; it < my_tiles && ok; ++it) {
       const int tile = (int)blockIdx.x + it * (int)gridDim.x;
@@ -783,7 +792,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
         if (p.w_scale && n < p.N) wsc *= __ldg(&p.w_scale[n]);
       }
-      for (int c = half; c * 16 < m_valid && !(p.dbg & 2); c += 2) {   // dbg 2: timing experiments, no epilogue
+      for (int c = half; c * 16 < m_valid && !(p.dbg & 2); c += kEpiGroups) {   // dbg 2: timing experiments, no epilogue
         float v[16];
         mb::tmem_ld16(lane_addr + buf * TN + c * 16, v);
         if (swiglu) {
@@ -802,7 +811,32 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const float gate = odd ? other : x0, up = odd ? x1 : other;
             const float y = mb::silu(gate) * up;
             const int m = m0 + (odd ? 1 : 0);
-            if (n_ok && m < m_valid) outp[(size_t)m * p.ldo] = __float2bfloat16(y);
+            if (p.outq) {
+              // This warp's 16 even lanes hold one 16-wide quantisation block of token m0, its odd
+              // lanes the same block of token m0 + 1 (block index along the consumer's K: tile * 4 + q).
+              const float yv = n_ok ? y : 0.f;
+              float bmax = fabsf(yv);
+              bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
+              bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 4));
+              bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 8));
+              bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 16));
+              const uint8_t sfc = mb::float_to_e4m3(bmax * outq_inv6gs);
+              const float sff = mb::e4m3_to_float(sfc);
+              const float qi = sff > 0.f ? __fdividef(1.f, sff * p.outq_gs) : 0.f;
+              const float scaled = yv * qi;
+              // outputs 2i and 2i + 1 of the block sit two lanes apart: the lower one packs the byte
+              const float upper = __shfl_down_sync(0xffffffffu, scaled, 2);
+              const uint32_t byte = mb::e2m1x2_pack(scaled, upper);
+              const int i = lane >> 1;                      // output index inside the block
+              if (m < m_valid && !(i & 1) && n < p.N)
+                p.outq[(size_t)m * p.ldq + ((tile * 64 + q * 16 + i) >> 1)] = (uint8_t)byte;
+              if (m < m_valid && i == 0 && n < p.N) {
+                const int kb = tile * 4 + q;
+                p.outq_sf[((size_t)(m >> 7) * p.outq_sf_k64 + (kb >> 2)) * 512 + mb::sf_tile_offset(m & 127, kb & 3)] = sfc;
+              }
+            } else if (n_ok && m < m_valid) {
+              outp[(size_t)m * p.ldo] = __float2bfloat16(y);
+            }
           }
         } else {
 #pragma unroll
@@ -928,6 +962,12 @@ struct MbGemmArgs {
   int dbg;
   long long* trace;
   int no_cluster;           // keep split-K on the workspace path
+  // quantised SwiGLU output (served by the persistent kernel only; MB_ERR_UNSUPPORTED otherwise)
+  void* outq;
+  int ldq;
+  void* outq_sf;
+  int outq_sf_k64;
+  float outq_gs;
   // fused tensor-parallel all-reduce (0 = off)
   int tp_size, tp_rank, tp_m_cap, tp_u_cap;
   void* tp_recv[8];
@@ -1014,6 +1054,13 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   p.tile_expert = a->tile_expert; p.tile_row0 = a->tile_row0; p.tile_nrows = a->tile_nrows;
   p.n_per_expert = grouped ? a->n_per_expert : 0;
   p.cluster = (splits > 1 && splits <= 8 && !a->no_cluster) ? 1 : 0;
+  if (a->outq) {
+    if (a->epilogue != EPI_SWIGLU || !a->outq_sf || a->outq_gs <= 0.f || (a->N / 2) % 16 || a->outq_sf_k64 * 64 < a->N / 2)
+      return MB_ERR_BAD_ARG;
+    p.outq = reinterpret_cast<uint8_t*>(a->outq); p.ldq = a->ldq;
+    p.outq_sf = reinterpret_cast<uint8_t*>(a->outq_sf); p.outq_sf_k64 = a->outq_sf_k64;
+    p.outq_gs = a->outq_gs;
+  }
   if (a->tp_size > 1) {
     if (a->tp_size > 8 || a->epilogue != EPI_PLAIN || a->out_f32 || grouped || a->N % kTileN || a->ldo % 8 ||
         a->M > a->tp_m_cap || (splits > 1 && !p.cluster) || !a->tp_par)
@@ -1057,6 +1104,7 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
       default: return dispatch_persistent<KIND_NVFP4>(tn, tmA, tmB, p, grid_x, stream);
     }
   }
+  if (a->outq) return MB_ERR_UNSUPPORTED;      // only the persistent epilogue quantises
   switch (kind) {
     case KIND_BF16: rc = dispatch_tn<KIND_BF16>(tn, tmA, tmB, p, grid, stream); break;
     case KIND_FP8: rc = dispatch_tn<KIND_FP8>(tn, tmA, tmB, p, grid, stream); break;

@@ -56,6 +56,7 @@ struct RowParams {
   int scale_ld;                       // OUT_FP8_G128: tokens stride
   uint8_t* sf;                        // OUT_NVFP4 tiled scale factors
   int sf_k64;
+  float static_gs;                    // OUT_NVFP4: > 0 = calibrated global scale instead of the row's amax / (6 * 448)
 };
 
 __device__ __forceinline__ float load_x(const RowParams& p, int m, int k) {
@@ -177,7 +178,7 @@ __global__ void __launch_bounds__(512) row_kernel(const RowParams p) {
     float amax = 0.f;
     for (int k = tid; k < K; k += nt) amax = fmaxf(amax, fabsf(row[k]));
     amax = mb::block_max(amax, red);
-    const float gs = amax > 0.f ? amax / (6.f * 448.f) : 1.f;
+    const float gs = p.static_gs > 0.f ? p.static_gs : (amax > 0.f ? amax / (6.f * 448.f) : 1.f);
     if (tid == 0) p.scale[m] = gs;
     uint8_t* o = reinterpret_cast<uint8_t*>(p.out) + (size_t)m * p.out_ld;
     uint8_t* sf_blk = p.sf + (size_t)(m >> 7) * p.sf_k64 * 512;
@@ -298,7 +299,7 @@ __global__ void __launch_bounds__(1024) row_kernel_v2(const RowParams p) {
     row_inv = 1.f / gs;
     if (tid == 0) p.scale[m] = gs;
   } else if (p.out_mode == OUT_NVFP4) {
-    gs = amax > 0.f ? amax / (6.f * 448.f) : 1.f;
+    gs = p.static_gs > 0.f ? p.static_gs : (amax > 0.f ? amax / (6.f * 448.f) : 1.f);
     if (tid == 0) p.scale[m] = gs;
   }
 #pragma unroll
@@ -450,6 +451,7 @@ struct MbRowArgs {
   int scale_ld;
   void* sf;
   int sf_k64;
+  float static_gs;
 };
 
 int mb_row_op(const MbRowArgs* a, cudaStream_t stream) {
@@ -475,6 +477,7 @@ int mb_row_op(const MbRowArgs* a, cudaStream_t stream) {
   p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(a->out_bf16); p.out_bf16_ld = a->out_bf16_ld;
   p.scale = a->scale; p.scale_ld = a->scale_ld;
   p.sf = reinterpret_cast<uint8_t*>(a->sf); p.sf_k64 = a->sf_k64;
+  p.static_gs = a->static_gs;
   {
     // fast path eligibility: bf16 input, whole 16-element blocks, 16-byte aligned vectors
     const bool modes = p.in_mode == IN_COPY || p.in_mode == IN_RMSNORM || p.in_mode == IN_SILU_MUL;

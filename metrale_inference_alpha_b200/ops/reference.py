@@ -51,7 +51,7 @@ def unpack_fp4(packed: torch.Tensor) -> torch.Tensor:
     return torch.stack([lo, hi], dim=-1).flatten(-2)
 
 
-def quantize_nvfp4(x: torch.Tensor, per_row_global: bool = True):
+def quantize_nvfp4(x: torch.Tensor, per_row_global: bool = True, static_scale: float = 0.0):
     """x [R, K] -> (packed [R, K/2] u8, sf [R, K/16] u8 e4m3, global [R] or scalar fp32).
 
     global = amax / (6 * 448); block scale = e4m3(blockmax / (6 * global))
@@ -61,6 +61,8 @@ def quantize_nvfp4(x: torch.Tensor, per_row_global: bool = True):
     assert K % 16 == 0
     amax = x.abs().amax(dim=1) if per_row_global else x.abs().amax().expand(R)
     gs = torch.where(amax > 0, amax / (6.0 * 448.0), torch.ones_like(amax))
+    if static_scale > 0:                       # calibrated global scale (ModelOpt `input_scale` semantics)
+        gs = torch.full_like(gs, float(static_scale))
     xb = x.view(R, K // 16, 16)
     bmax = xb.abs().amax(dim=2)
     sf = to_e4m3(bmax / (6.0 * gs[:, None]))

@@ -103,6 +103,7 @@ class AttnW:
     o: QuantWeight = None
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
+    o_in_scale: float = 0.0   # NVFP4: calibrated global scale of o_proj's input (0 = per-token dynamic)
     heads: int = 0            # local q heads
     kv_heads: int = 0         # local kv heads
 
@@ -112,6 +113,7 @@ class FfnW:
     gate_up: QuantWeight = None      # swiglu: rows interleaved (gate_j, up_j) or gate | up halves; relu2: up only
     down: QuantWeight = None
     interleaved: bool = False        # True -> the GEMM epilogue applies SwiGLU
+    down_in_scale: float = 0.0       # NVFP4: calibrated global scale of down's input (0 = per-token dynamic)
 
 
 @dataclass

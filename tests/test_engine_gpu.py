@@ -53,3 +53,24 @@ def test_flagship_shape_smoke_nvfp4_fp8kv_many_steps():
                                    use_cuda_graphs=graphs))
         outs[graphs] = _drive(eng, _arrivals())
     assert outs[True] == outs[False]
+
+
+def test_static_activation_scales_are_calibrated_and_keep_graph_equals_eager():
+    """NVFP4 engines fix the down projection's input scale at start-up; decode then quantises
+    inside the GEMM epilogue (persistent kernel) and prefill through the row kernel with the same
+    scale. Tokens must not depend on graphs vs eager, and stay close to the dynamic-scale engine."""
+    cfg = preset("dense-27b-nvfp4", num_layers=2, hidden_size=1024, num_heads=8, num_kv_heads=2,
+                 intermediate_size=64 * 160, vocab_size=8192, mtp_layers=0, max_position=1024)
+    outs = {}
+    for name, kw in (("eager", dict(use_cuda_graphs=False)), ("graph", dict(use_cuda_graphs=True)),
+                     ("dynamic", dict(use_cuda_graphs=True, static_act_scales=False))):
+        eng = LLMEngine(EngineArgs(model=cfg, device="cuda", max_num_seqs=8, max_model_len=512, num_kv_blocks=256, **kw))
+        if name != "dynamic":
+            assert eng.calibrated_layers == 2
+            assert all(lw.ffn.down_in_scale > 0 for lw in eng.weights.layers)
+        else:
+            assert eng.calibrated_layers == 0
+        outs[name] = _drive(eng, _arrivals())
+    assert outs["graph"] == outs["eager"]
+    agree = sum(a == b for x, y in zip(outs["graph"], outs["dynamic"]) for a, b in zip(x[:4], y[:4]))
+    assert agree >= 12                       # first tokens of 6 requests: the scale policy barely moves logits

@@ -148,6 +148,48 @@ def test_gemm_persistent_swiglu_and_residual():
     ops.check_status(DEV)
 
 
+def _dequant_act(act):
+    """NVFP4 activation on the device -> fp32 matrix on the CPU."""
+    nb = (act.M + 127) // 128
+    sf = ref.tiled_to_sf(act.sf.cpu().view(nb, act.sf_k64, 512), act.M, act.K // 16)
+    return ref.dequantize_nvfp4(act.data.cpu(), sf, act.scale.cpu())
+
+
+@pytest.mark.parametrize("M", [1, 16, 77, 128])
+def test_gemm_swiglu_epilogue_quantises_to_nvfp4_with_a_static_scale(M):
+    """The persistent kernel's SwiGLU epilogue writes packed e2m1 + tiled ue4m3 scale factors for
+    the down projection. Checked against (a) the row kernel quantising the kernel's own bf16
+    SwiGLU output with the same static scale and (b) the down projection fed with either."""
+    I, K = 64 * 160, 512                                # 160 tiles -> persistent path; I % 256 == 0
+    x, wg = _mk(M, I, K, 1)
+    _, wu = _mk(M, I, K, 2)
+    _, wd = _mk(M, 384, I, 3)
+    w = ops.make_weight(ops.interleave_gate_up(wg, wu), "nvfp4").to(DEV)
+    down = ops.make_weight(wd, "nvfp4").to(DEV)
+    a = ops.quantize_act(x.to(DEV).to(torch.bfloat16), "nvfp4")
+    y = ops.linear(a, w, swiglu=True)                   # bf16, unfused
+    gs = float(y.float().abs().max()) * 1.5 / (6 * 448)
+    fused = ops.linear(a, w, swiglu=True, quant_out=gs)
+    unfused = ops.quantize_act(y, "nvfp4", static_scale=gs)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    assert fused.fmt == "nvfp4" and fused.K == I and torch.all(fused.scale == gs)
+    df, du = _dequant_act(fused), _dequant_act(unfused)
+    # the fused path quantises the fp32 value, the unfused one its bf16 rounding: a few codes flip
+    same = (df == du).float().mean().item()
+    assert same > 0.97, same
+    assert (df - du).abs().max().item() <= 0.51 * du.abs().max().item()
+    assert torch.allclose(df, y.float().cpu(), rtol=0.3, atol=0.1 * y.float().abs().max().item())
+    o_f = ops.linear(fused, down, out_f32=True)
+    o_u = ops.linear(unfused, down, out_f32=True)
+    _close(o_f, o_u, rtol=5e-2, atol=6e-2 * o_u.abs().max().item())   # a few flipped e2m1 codes over K = 10240
+    # shapes the persistent kernel does not serve fall back to GEMM + row kernel, same result type
+    small = ops.make_weight(ops.interleave_gate_up(wg[:256], wu[:256]), "nvfp4").to(DEV)
+    fb = ops.linear(a, small, swiglu=True, quant_out=gs)
+    assert fb.fmt == "nvfp4" and fb.K == 256
+    ops.check_status(DEV)
+
+
 def test_sf_repack_matches_reference_layout():
     sf = torch.randint(0, 120, (300, 40), dtype=torch.uint8)
     w = ops.QuantWeight("nvfp4", 300, 640, torch.zeros(300, 320, dtype=torch.uint8), sf, 1.0).to(DEV)
