@@ -237,17 +237,22 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ static activation scales
     def calibrate_static_scales(self, tokens: int = 256, margin: float = 2.0, seed: int = 1234) -> int:
-        """NVFP4 models: fix the global scale of the down projection's input per layer (what a
+        """NVFP4 models: fix the global scale of the down projection's and o projection's input per layer (what a
         ModelOpt checkpoint calls `input_scale`), so that the quantiser becomes row-local and can
         run inside the producing GEMM's epilogue. One prefill of random tokens through temporary
         KV blocks records max |SwiGLU output| per layer; scale = margin * amax / (6 * 448).
         Checkpoint-provided scales (already > 0) are kept. Returns the number of layers set."""
         ffns = [lw.ffn for lw in self.w.layers
                 if lw.ffn_kind == "dense" and getattr(lw.ffn, "interleaved", False) and lw.ffn.down.fmt == "nvfp4"]
+        attns = [lw.mixer for lw in self.w.layers
+                 if lw.kind == "attention" and lw.mixer.o.fmt == "nvfp4" and not self.cfg.attn_output_gate]
         todo = [f for f in ffns if f.down_in_scale <= 0.0]
-        if not todo:
+        todo_a = [m for m in attns if m.o_in_scale <= 0.0]
+        if not todo and not todo_a:
             for f in ffns:
                 ops.static_scale_vec(self.device, f.down_in_scale, 256)
+            for m in attns:
+                ops.static_scale_vec(self.device, m.o_in_scale, 256)
             return 0
         tokens = min(tokens, self.sched.max_prefill_tokens, self.sched.max_model_len - 1)
         g = torch.Generator().manual_seed(seed)
@@ -270,9 +275,17 @@ class ModelRunner:
                 if amax > 0.0:
                     f.down_in_scale = margin * amax / (6.0 * 448.0)
                     n += 1
+        for m in todo_a:
+            if id(m) in calib:
+                amax = float(calib[id(m)])
+                if amax > 0.0:
+                    m.o_in_scale = margin * amax / (6.0 * 448.0)
         for f in ffns:
             if f.down_in_scale > 0.0:
                 ops.static_scale_vec(self.device, f.down_in_scale, 256)
+        for m in attns:
+            if m.o_in_scale > 0.0:
+                ops.static_scale_vec(self.device, m.o_in_scale, 256)
         return n
 
     def _adapter_rows(self, plan: StepPlan) -> Optional[torch.Tensor]:

@@ -104,16 +104,26 @@ class Decoder:
             qkv, Hq=w.heads, Hkv=w.kv_heads, D=D, positions=batch.positions, slots=batch.slot_mapping,
             k_cache=kc, v_cache=vc, q_norm_w=w.q_norm, k_norm_w=w.k_norm, plus_one=c.norm_plus_one,
             eps=c.rms_eps, cos=self.cos, sin=self.sin, q_head_stride=qhs, k_scale=ks, v_scale=vs)
+        fmt = ACT_FOR_WEIGHT[w.o.fmt]
+        static = w.o_in_scale if (fmt == "nvfp4" and self.calib is None and not c.attn_output_gate) else 0.0
+        if static > 0.0 and lora is None:
+            # the attention kernel's final store quantises for o_proj with the calibrated scale
+            oa = ops.paged_attention(q, kc, vc, batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
+                                     max_q_len=batch.max_q_len, max_ctx=batch.max_ctx, scale=self.scale,
+                                     k_scale=ks, v_scale=vs, window=c.sliding_window, quant_out=static)
+            return self.tp.linear_reduce(oa, w.o, residual=x)
         o = ops.paged_attention(q, kc, vc, batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
                                 max_q_len=batch.max_q_len, max_ctx=batch.max_ctx, scale=self.scale,
                                 k_scale=ks, v_scale=vs, window=c.sliding_window)
         o = o.view(o.shape[0], w.heads * D)
-        fmt = ACT_FOR_WEIGHT[w.o.fmt]
+        if self.calib is not None:
+            m = o.float().abs().max()
+            self.calib[id(w)] = torch.maximum(self.calib[id(w)], m) if id(w) in self.calib else m
         if c.attn_output_gate:
             oa = ops.row_op(o, fmt, ops.IN_SIGMOID_GATE, gate=qkv, head_dim=D, gate_head_stride=2 * D,
                             gate_head_off=D)[0]
         else:
-            oa = self._as_act(o, fmt)
+            oa = ops.quantize_act(o, fmt, static_scale=static) if fmt == "nvfp4" else self._as_act(o, fmt)
         y = self.tp.linear_reduce(oa, w.o, residual=x)
         if lora is not None and not c.attn_output_gate:
             lora.apply(y, o, li, "o", batch.adapter_rows)

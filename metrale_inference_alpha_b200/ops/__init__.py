@@ -649,9 +649,19 @@ def configure(attn_part_tokens: Optional[int] = None) -> None:
 
 def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_len, ctx_len, *,
                     max_q_len: int, max_ctx: int, scale: float, k_scale=None, v_scale=None,
-                    window: int = 0, force_mode: int = 0, part_tokens: int = 0) -> torch.Tensor:
-    """q [T, Hq, D] bf16 -> [T, Hq, D] bf16. Caches [num_blocks, block, Hkv, D] bf16 or e4m3 bytes."""
+                    window: int = 0, force_mode: int = 0, part_tokens: int = 0, quant_out: float = 0.0):
+    """q [T, Hq, D] bf16 -> [T, Hq, D] bf16. Caches [num_blocks, block, Hkv, D] bf16 or e4m3 bytes.
+    `quant_out` > 0: return the output as an NVFP4 `Act` [T, Hq * D] quantised with that calibrated
+    global scale (inside the split-KV kernel for decode-sized steps, else by a row kernel)."""
     T, Hq, D = q.shape
+    if quant_out > 0.0:
+        Hkv_ = k_cache.shape[2]
+        fused = q.is_cuda and force_mode == 0 and (Hq // Hkv_) * max_q_len <= 16 and D % 128 == 0 and (Hq * D) % 256 == 0
+        if not fused:
+            o = paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, ctx_len, max_q_len=max_q_len,
+                                max_ctx=max_ctx, scale=scale, k_scale=k_scale, v_scale=v_scale, window=window,
+                                force_mode=force_mode, part_tokens=part_tokens)
+            return quantize_act(o.view(T, Hq * D), "nvfp4", static_scale=quant_out)
     if not q.is_cuda:
         return ref.paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, ctx_len, scale,
                                    k_scale, v_scale, window).to(torch.bfloat16)
@@ -681,9 +691,17 @@ def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_l
     rt.ensure_attn_ws(need)
     a.ws, a.ws_bytes, a.total_rows = _ptr(rt.attn_ws), rt.attn_ws.numel(), T
     a.part_tokens, a.window, a.force_mode, a.status = part_tokens, window, force_mode, _ptr(rt.status)
+    qact = None
+    if quant_out > 0.0:
+        Kq = Hq * D
+        qact = Act("nvfp4", T, Kq, torch.empty(T, Kq // 2, dtype=torch.uint8, device=q.device))
+        qact.sf_k64 = Kq // 64
+        qact.sf = torch.empty(((T + 127) // 128) * qact.sf_k64 * 512, dtype=torch.uint8, device=q.device)
+        qact.scale = static_scale_vec(q.device, quant_out, T)
+        a.outq, a.ldq, a.outq_sf, a.outq_sf_k64, a.outq_gs = _ptr(qact.data), Kq // 2, _ptr(qact.sf), qact.sf_k64, quant_out
     _native.check(L.mb_paged_attention(C.byref(a), _stream()), "paged_attention")
     _count()
-    return out
+    return qact if qact is not None else out
 
 
 def _attention_rowwise(q, k_cache, v_cache, block_table, q_start, q_len, ctx_len, **kw):

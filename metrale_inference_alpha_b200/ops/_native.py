@@ -72,6 +72,7 @@ class AttnArgs(C.Structure):
         ("k_scale", c_void_p), ("v_scale", c_void_p), ("out", c_void_p),
         ("ws", c_void_p), ("ws_bytes", c_size_t), ("total_rows", c_int),
         ("part_tokens", c_int), ("window", c_int), ("force_mode", c_int), ("status", c_void_p),
+        ("outq", c_void_p), ("ldq", c_int), ("outq_sf", c_void_p), ("outq_sf_k64", c_int), ("outq_gs", c_float),
     ]
 
 

@@ -215,7 +215,41 @@ struct AttnParams {
   uint32_t* part_cnt;       // [num_seqs * Hkv] arrival counters (zero between launches)
   int window;               // sliding window (0 = none)
   uint32_t* status;
+  // optional NVFP4 output for the o projection (split-KV kernel, head_dim % 128 == 0): packed e2m1
+  // [rows, ldq] + tiled ue4m3 scale factors, quantised with a calibrated global scale
+  uint8_t* outq;
+  int ldq;
+  uint8_t* outq_sf;
+  int outq_sf_k64;
+  float outq_gs;
 };
+
+// Final store of four consecutive dims (c4 * 4 ..) of output row `orow` = token * Hq + head. In the
+// quantised mode the four lanes that share a 16-dim block agree on its scale with two shuffles;
+// every lane of the warp must call this (the callers' loops run whole warps when D % 128 == 0).
+template <int D>
+__device__ __forceinline__ void store_out4(const AttnParams& p, size_t orow, int c4, float a, float b, float c, float d) {
+  if (p.outq) {
+    float bmax = fmaxf(fmaxf(fabsf(a), fabsf(b)), fmaxf(fabsf(c), fabsf(d)));
+    bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+    bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
+    const uint8_t sfc = mb::float_to_e4m3(bmax / (6.f * p.outq_gs));
+    const float sff = mb::e4m3_to_float(sfc);
+    const float qi = sff > 0.f ? __fdividef(1.f, sff * p.outq_gs) : 0.f;
+    const uint32_t w = mb::e2m1x2_pack(a * qi, b * qi) | (mb::e2m1x2_pack(c * qi, d * qi) << 8);
+    const size_t m = orow / p.Hq;
+    const int col = (int)(orow - m * p.Hq) * D + c4 * 4;             // index along the consumer's K
+    *reinterpret_cast<uint16_t*>(p.outq + m * p.ldq + (col >> 1)) = (uint16_t)w;
+    if ((c4 & 3) == 0) {
+      const int kb = col >> 4;
+      p.outq_sf[((m >> 7) * p.outq_sf_k64 + (kb >> 2)) * 512 + mb::sf_tile_offset((uint32_t)(m & 127), kb & 3)] = sfc;
+    }
+    return;
+  }
+  __nv_bfloat16* dst = p.out + orow * D + c4 * 4;
+  *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a, b);
+  *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(c, d);
+}
 
 // Stage a [64 x D] tile of cache rows for one kv head into shared memory.
 //   e4m3 cache: fetch() issues the global loads into registers, commit() widens to f16
@@ -717,9 +751,7 @@ __global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_split
     const int tq = r / G, hh = r - tq * G;
     const size_t orow = (size_t)(qs + tq) * p.Hq + kvh * G + hh;
     if (nparts == 1) {
-      __nv_bfloat16* dst = p.out + orow * D + c4 * 4;
-      *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x, acc.y);
-      *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z, acc.w);
+      store_out4<D>(p, orow, c4, acc.x, acc.y, acc.z, acc.w);
     } else {
       *reinterpret_cast<float4*>(p.part_o + (orow * p.parts + part) * D + c4 * 4) = acc;
       if (c4 == 0) {
@@ -760,9 +792,7 @@ __global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_split
       acc.x += ov.x * wgt; acc.y += ov.y * wgt; acc.z += ov.z * wgt; acc.w += ov.w * wgt;
     }
     const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    __nv_bfloat16* dst = p.out + orow * D + c4 * 4;
-    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-    *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    store_out4<D>(p, orow, c4, acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
   }
 }
 
@@ -1066,6 +1096,11 @@ struct MbAttnArgs {
   int window;
   int force_mode;          // 0 auto, 1 split-KV, 2 split-Q
   uint32_t* status;
+  void* outq;              // optional NVFP4 output (split-KV path only; MB_ERR_UNSUPPORTED otherwise)
+  int ldq;
+  void* outq_sf;
+  int outq_sf_k64;
+  float outq_gs;
 };
 
 // workspace bytes for the split-KV path
@@ -1094,6 +1129,13 @@ int mb_paged_attention(const MbAttnArgs* a, cudaStream_t stream) {
   int mode = a->force_mode;
   if (mode == 0) mode = rows <= 32 ? 1 : 2;
   const bool fp8 = a->cache_fp8 != 0;
+  if (a->outq) {
+    if (mode != 1 || a->D % 128 || !a->outq_sf || a->outq_gs <= 0.f || a->outq_sf_k64 * 64 < a->Hq * a->D)
+      return MB_ERR_UNSUPPORTED;
+    p.outq = reinterpret_cast<uint8_t*>(a->outq); p.ldq = a->ldq;
+    p.outq_sf = reinterpret_cast<uint8_t*>(a->outq_sf); p.outq_sf_k64 = a->outq_sf_k64;
+    p.outq_gs = a->outq_gs;
+  }
   if (mode == 1) {
     if (rows > 32) return MB_ERR_UNSUPPORTED;
     const int mt = rows <= 16 ? 1 : 2;

@@ -190,6 +190,25 @@ def test_gemm_swiglu_epilogue_quantises_to_nvfp4_with_a_static_scale(M):
     ops.check_status(DEV)
 
 
+@pytest.mark.parametrize("ctx_lens,part_tokens", [([5, 130, 64, 700], 0), ([300, 1025], 256)])
+def test_attention_epilogue_quantises_to_nvfp4_with_a_static_scale(ctx_lens, part_tokens):
+    """Decode attention writing packed e2m1 + tiled scale factors for o_proj (direct store and the
+    last-arriver merge of several partitions) against the row kernel applied to its bf16 output."""
+    fp8, D, Hq, Hkv = True, 128, 40, 8
+    q_lens = [1] * len(ctx_lens)
+    args, want = _attn_case(fp8, D, Hq, Hkv, q_lens, ctx_lens, build_only=True)
+    o = ops.paged_attention(*args["pos"], **args["kw"], part_tokens=part_tokens)
+    gs = float(o.float().abs().max()) * 1.5 / (6 * 448)
+    fused = ops.paged_attention(*args["pos"], **args["kw"], part_tokens=part_tokens, quant_out=gs)
+    unfused = ops.quantize_act(o.view(o.shape[0], Hq * D), "nvfp4", static_scale=gs)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    assert fused.fmt == "nvfp4" and fused.K == Hq * D
+    df, du = _dequant_act(fused), _dequant_act(unfused)
+    assert (df == du).float().mean().item() > 0.97
+    assert torch.allclose(df, o.float().cpu().view(len(q_lens), -1), rtol=0.3, atol=0.1 * o.float().abs().max().item())
+
+
 def test_sf_repack_matches_reference_layout():
     sf = torch.randint(0, 120, (300, 40), dtype=torch.uint8)
     w = ops.QuantWeight("nvfp4", 300, 640, torch.zeros(300, 320, dtype=torch.uint8), sf, 1.0).to(DEV)
@@ -300,7 +319,7 @@ def test_rope_kvwrite(fp8, D, rot):
     ops.check_status(DEV)
 
 
-def _attn_case(fp8, D, Hq, Hkv, q_lens, ctx_lens, window=0, force_mode=0, seed=6):
+def _attn_case(fp8, D, Hq, Hkv, q_lens, ctx_lens, window=0, force_mode=0, seed=6, build_only=False):
     bs = 16
     g = torch.Generator().manual_seed(seed)
     S = len(q_lens)
@@ -333,6 +352,10 @@ def _attn_case(fp8, D, Hq, Hkv, q_lens, ctx_lens, window=0, force_mode=0, seed=6
     scale = 1.0 / math.sqrt(D)
     want = ref.paged_attention(q, kc, vc, bt.clamp(min=0), q_start, q_len, ctx, scale, ks, vs, window)
     dv = lambda t: None if t is None else t.to(DEV)
+    if build_only:
+        return dict(pos=(dv(q), dv(kc), dv(vc), dv(bt.clamp(min=0)), dv(q_start), dv(q_len), dv(ctx)),
+                    kw=dict(max_q_len=max(q_lens), max_ctx=max(ctx_lens), scale=scale, k_scale=dv(ks), v_scale=dv(vs),
+                            window=window, force_mode=force_mode)), want
     got = ops.paged_attention(dv(q), dv(kc), dv(vc), dv(bt.clamp(min=0)), dv(q_start), dv(q_len), dv(ctx),
                               max_q_len=max(q_lens), max_ctx=max(ctx_lens), scale=scale, k_scale=dv(ks),
                               v_scale=dv(vs), window=window, force_mode=force_mode)
