@@ -32,6 +32,51 @@ def _penalty_tables(items, device):
     return mk(0, -1), mk(1, 0), mk(2, 0)
 
 
+def dry_penalties(tokens: List[int], multiplier: float, base: float, allowed: int, window: int) -> dict:
+    """DRY: for every earlier occurrence of the last token, measure how long the text before it
+    matches the text before the end; the token that followed that occurrence would extend a repeat
+    of that length. Returns {token: penalty} (the largest repeat per token wins).
+    Role of ``crates/sampling/src/penalties.rs`` (DRY)."""
+    n = len(tokens)
+    if n < 2 or multiplier <= 0:
+        return {}
+    lo = max(0, n - window)
+    last = tokens[-1]
+    out: dict = {}
+    for i in range(n - 2, lo - 1, -1):
+        if tokens[i] != last:
+            continue
+        k = 1
+        while i - k >= lo and tokens[i - k] == tokens[n - 1 - k] and k < 64:
+            k += 1
+        if k >= allowed:
+            nxt = tokens[i + 1]
+            pen = multiplier * base ** (k - allowed)
+            if pen > out.get(nxt, 0.0):
+                out[nxt] = pen
+    return out
+
+
+def lz_penalty(tokens: List[int], strength: float, window: int = 2048) -> dict:
+    """Loop guard: the longest earlier match of the current suffix (length L >= 4) predicts its
+    continuation; that token is penalised by strength * L. Role of the LZ penalty of
+    ``crates/sampling/src/penalties.rs``."""
+    n = len(tokens)
+    if strength <= 0 or n < 8:
+        return {}
+    lo = max(0, n - window)
+    best_len, best_next = 0, None
+    for i in range(n - 2, lo - 1, -1):
+        if tokens[i] != tokens[-1]:
+            continue
+        k = 1
+        while i - k >= lo and tokens[i - k] == tokens[n - 1 - k] and k < 256:
+            k += 1
+        if k > best_len:
+            best_len, best_next = k, tokens[i + 1]
+    return {best_next: strength * best_len} if best_len >= 4 else {}
+
+
 def sample_rows(runner, plan, logits: torch.Tensor) -> Tuple[List[List[int]], List[List[float]]]:
     """logits: fp32 [R, V], one row per sampled position in plan order."""
     items = [it for it in plan.items if it.sample]
@@ -42,6 +87,9 @@ def sample_rows(runner, plan, logits: torch.Tensor) -> Tuple[List[List[int]], Li
         row_item += [it] * (it.verify + 1)
     R = len(row_item)
     assert logits.shape[0] == R
+    row_first = {}
+    for r0, it0 in enumerate(row_item):
+        row_first.setdefault(id(it0), r0)
     P = [it.seq.req.params for it in row_item]
     if any(p.has_penalties for p in P):
         tok, cnt, inp = _penalty_tables(row_item, dev)
@@ -53,6 +101,16 @@ def sample_rows(runner, plan, logits: torch.Tensor) -> Tuple[List[List[int]], Li
         if p.logit_bias:
             idx = torch.tensor(list(p.logit_bias.keys()), device=dev)
             logits[r, idx] += torch.tensor(list(p.logit_bias.values()), dtype=torch.float32, device=dev)
+        if p.dry_multiplier > 0 or p.lz_penalty > 0:
+            # verify rows of one item see the sequence as of their own position
+            upto = len(it.seq.tokens) - (it.verify - (r - row_first[id(it)]))
+            hist = it.seq.tokens[:upto]
+            pens = dry_penalties(hist, p.dry_multiplier, p.dry_base, p.dry_allowed_length, p.dry_window)
+            for tkn, v in lz_penalty(hist, p.lz_penalty).items():
+                pens[tkn] = pens.get(tkn, 0.0) + v
+            if pens:
+                idx = torch.tensor(list(pens.keys()), device=dev)
+                logits[r, idx] -= torch.tensor(list(pens.values()), dtype=torch.float32, device=dev)
         if p.grammar is not None:
             mask = p.grammar.allowed_mask(logits.shape[1]).to(dev)
             logits[r].masked_fill_(~mask, float("-inf"))

@@ -18,6 +18,15 @@ class SamplingParams:
     repetition_penalty: float = 1.0
     presence_penalty: float = 0.0
     frequency_penalty: float = 0.0
+    # DRY ("don't repeat yourself"): a token that would extend a repeat of length n >= allowed_length
+    # is penalised by multiplier * base ** (n - allowed_length); 0 multiplier = off
+    dry_multiplier: float = 0.0
+    dry_base: float = 1.75
+    dry_allowed_length: int = 2
+    dry_window: int = 1024
+    # LZ-style loop guard: penalise the continuation of the longest earlier match of the current
+    # suffix by lz_penalty * match_length (0 = off)
+    lz_penalty: float = 0.0
     logit_bias: Dict[int, float] = field(default_factory=dict)
     seed: Optional[int] = None
     stop: List[str] = field(default_factory=list)
@@ -37,7 +46,8 @@ class SamplingParams:
     @property
     def needs_host_logits(self) -> bool:
         """True when plain device argmax / device sampling cannot serve the request."""
-        return bool(self.logit_bias) or self.top_n_sigma > 0 or self.grammar is not None or self.top_logprobs > 0
+        return (bool(self.logit_bias) or self.top_n_sigma > 0 or self.grammar is not None or self.top_logprobs > 0
+                or self.dry_multiplier > 0 or self.lz_penalty > 0)
 
     @property
     def has_penalties(self) -> bool:

@@ -26,6 +26,7 @@ from .engine_loop import AsyncEngine
 from .grammar import grammar_for_response_format
 from .ratelimit import RateLimiter
 from .reasoning_parser import ReasoningParser
+from .response_store import ResponseStore
 from .tool_parser import StreamingToolDetector, parse_tool_calls
 
 
@@ -68,6 +69,10 @@ def _sampling_from(body: Dict[str, Any], cfg: ServerConfig, max_key="max_tokens"
         repetition_penalty=float(body.get("repetition_penalty") or 1.0),
         presence_penalty=float(body.get("presence_penalty") or 0.0),
         frequency_penalty=float(body.get("frequency_penalty") or 0.0),
+        dry_multiplier=float(body.get("dry_multiplier") or 0.0), dry_base=float(body.get("dry_base") or 1.75),
+        dry_allowed_length=int(body.get("dry_allowed_length") or 2),
+        lz_penalty=float((body.get("repetition_detection") or {}).get("penalty", 0.0)
+                         if isinstance(body.get("repetition_detection"), dict) else 0.0),
         logit_bias={int(k): float(v) for k, v in (body.get("logit_bias") or {}).items()},
         seed=body.get("seed"), stop=list(stop), logprobs=bool(body.get("logprobs")),
         top_logprobs=int(body.get("top_logprobs") or 0),
@@ -87,6 +92,7 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
     app = FastAPI(title="metrale b200 engine", lifespan=lifespan)
     tel = Telemetry(cfg.telemetry)
     limiter = RateLimiter(cfg.rate_per_s)
+    store = ResponseStore()
     renderer = ChatRenderer(getattr(tokenizer, "chat_template", None))
     app.state.engine, app.state.async_engine, app.state.telemetry = engine, aeng, tel
     eos = getattr(tokenizer, "eos_token_id", None)
@@ -279,12 +285,35 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
             yield "data: [DONE]\n\n"
         return StreamingResponse(gen(), media_type="text/event-stream")
 
+    @app.get("/v1/responses/{response_id}")
+    async def get_response(response_id: str):
+        r = store.get(response_id)
+        if r is None:
+            raise HTTPException(404, "unknown response id")
+        return {"id": response_id, "object": "response", "status": "completed", "previous_response_id": r["previous"],
+                "output": [{"type": "message", "role": "assistant",
+                            "content": [{"type": "output_text", "text": r["output"], "annotations": []}]}]}
+
+    @app.delete("/v1/responses/{response_id}")
+    async def delete_response(response_id: str):
+        if not store.delete(response_id):
+            raise HTTPException(404, "unknown response id")
+        return {"id": response_id, "object": "response.deleted", "deleted": True}
+
     @app.post("/v1/responses")
     async def responses(request: Request):
         body = await request.json()
         inp = body.get("input")
-        messages = [{"role": "user", "content": inp}] if isinstance(inp, str) else [
+        new_msgs = [{"role": "user", "content": inp}] if isinstance(inp, str) else [
             {"role": m.get("role", "user"), "content": m.get("content")} for m in (inp or [])]
+        prev = body.get("previous_response_id")
+        history = []
+        if prev:
+            try:
+                history = store.thread(prev)
+            except KeyError:
+                raise HTTPException(404, f"unknown previous_response_id {prev!r}")
+        messages = history + new_msgs
         job = _job_from_chat(body, messages, system=body.get("instructions"), tools=body.get("tools"))
         text, ids, usage, reason, _ = await _collect(job)
         reasoning, content, calls = _split_outputs(job, text)
@@ -297,7 +326,10 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
             out.append({"type": "function_call", "call_id": c["id"], "name": c["function"]["name"],
                         "arguments": c["function"]["arguments"]})
         u = usage or {}
-        return {"id": "resp_" + uuid.uuid4().hex[:24], "object": "response", "created_at": int(time.time()),
+        rid = "resp_" + uuid.uuid4().hex[:24]
+        if body.get("store", True):
+            store.put(rid, new_msgs, content, prev)
+        return {"id": rid, "object": "response", "created_at": int(time.time()), "previous_response_id": prev,
                 "model": cfg.model_name, "status": "completed", "output": out,
                 "usage": {"input_tokens": u.get("prompt_tokens"), "output_tokens": u.get("completion_tokens"),
                           "total_tokens": u.get("total_tokens")}}

@@ -79,6 +79,13 @@ def build_parser() -> argparse.ArgumentParser:
     d.add_argument("--json", action="store_true")
 
     o = sub.add_parser("dump-serve-options", help="print every serve option and its default")
+
+    pl = sub.add_parser("plan", help="roofline estimate of a decode step (bytes, FLOPs, time per op)")
+    pl.add_argument("--model", default="dense-27b-nvfp4")
+    pl.add_argument("--batch", type=int, default=128)
+    pl.add_argument("--ctx", type=int, default=640)
+    pl.add_argument("--tp", type=int, default=1)
+    pl.add_argument("--json", action="store_true")
     return ap
 
 
@@ -163,6 +170,25 @@ def main(argv: Optional[List[str]] = None) -> int:
         rep = doctor()
         print(json.dumps(rep, indent=None if ns.json else 2))
         return 0 if rep["ok"] else 1
+    elif ns.cmd == "plan":
+        from ..config.model_config import preset
+        from ..planner import estimate
+        if os.path.isdir(ns.model):
+            from ..weights.checkpoint import open_checkpoint
+            cfg = open_checkpoint(ns.model)[0]
+        else:
+            cfg = preset(ns.model)
+        e = estimate(cfg, ns.batch, ns.ctx, ns.tp)
+        if ns.json:
+            print(json.dumps(e))
+        else:
+            print(f"{e['model']}  batch {e['batch']}  ctx {e['ctx']}  tp {e['tp']}  peaks: {e['peaks']}")
+            print(f"{'op':28s} {'count':>5} {'us each':>9} {'us total':>10} {'MB each':>10}  bound")
+            for r in e["ops"]:
+                print(f"{r['op']:28s} {r['count']:>5} {r['us_each']:>9.2f} {r['us_total']:>10.1f} {r['mbytes_each']:>10.3f}  {r['bound']}")
+            print(f"step: {e['step_ms_roofline_per_op']} ms per-op roofline, {e['step_ms_bytes_only']} ms bytes only "
+                  f"({e['gbytes_per_step']} GB, {e['tflop_per_step']} TFLOP, {e['launches']} launches); "
+                  f"upper bound {e['tok_s_upper_bound']} tok/s")
     elif ns.cmd == "dump-serve-options":
         print(json.dumps(dump_serve_options(), indent=2, default=str))
     return 0

@@ -110,3 +110,34 @@ def test_swap_preemption_resumes_without_recompute_and_matches_recompute_mode(tm
     # a tiny host budget pushes victims to swap files
     disk, e3 = run(num_kv_blocks=14, preempt_mode="swap", swap_space_bytes=1, swap_dir=str(tmp_path))
     assert disk == roomy and e3.spill.stats["to_disk"] > 0 and not list(tmp_path.glob("*.pt"))
+
+
+def test_dry_and_lz_penalties_tables_and_effect_on_generation():
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.host import dry_penalties, lz_penalty
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    toks = [1, 2, 3, 4, 9, 1, 2, 3]                     # "... 1 2 3" seen before, followed by 4
+    pen = dry_penalties(toks, multiplier=0.8, base=2.0, allowed=2, window=64)
+    assert pen == {4: 0.8 * 2.0 ** (3 - 2)}              # repeat of length 3 would be extended by token 4
+    assert dry_penalties(toks, 0.8, 2.0, allowed=4, window=64) == {}
+    assert dry_penalties(toks, 0.0, 2.0, 2, 64) == {}
+    loop = [5, 6, 7, 8] * 3
+    assert lz_penalty(loop, 0.5) == {5: 0.5 * 8}         # suffix of length 8 matched; next would be 5
+    assert lz_penalty([1, 2, 3], 0.5) == {}
+    # a greedy random model falls into a loop quickly; DRY must break exact repetition
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_model_len=256))
+    prompt = [3, 4, 5, 6]
+    plain = eng.generate([prompt], SamplingParams(max_tokens=60))[0].output_ids
+    dry = eng.generate([prompt], SamplingParams(max_tokens=60, dry_multiplier=4.0, dry_base=2.0))[0].output_ids
+
+    def longest_repeat(x):
+        best = 0
+        for i in range(len(x)):
+            for j in range(i + 1, len(x)):
+                k = 0
+                while j + k < len(x) and x[i + k] == x[j + k]:
+                    k += 1
+                best = max(best, k)
+        return best
+    assert longest_repeat(dry) <= longest_repeat(plain)
+    assert longest_repeat(dry) < 12

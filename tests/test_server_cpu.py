@@ -358,3 +358,41 @@ def test_more_tool_call_formats():
 def test_reasoning_formats_mistral_and_gemma():
     assert split_reasoning("[THINK]plan[/THINK]answer", "mistral") == ("plan", "answer")
     assert split_reasoning("<|channel>plan<channel|>answer", "gemma4") == ("plan", "answer")
+
+
+def test_responses_store_and_previous_response_id(client):
+    a = client.post("/v1/responses", json={"input": "first question", "max_output_tokens": 3}).json()
+    b = client.post("/v1/responses", json={"input": "follow up", "previous_response_id": a["id"], "max_output_tokens": 3}).json()
+    assert b["previous_response_id"] == a["id"]
+    assert b["usage"]["input_tokens"] > a["usage"]["input_tokens"]        # the thread was prepended
+    assert client.get(f"/v1/responses/{a['id']}").json()["id"] == a["id"]
+    assert client.post("/v1/responses", json={"input": "x", "previous_response_id": "resp_nope"}).status_code == 404
+    assert client.delete(f"/v1/responses/{b['id']}").json()["deleted"] is True
+    assert client.get(f"/v1/responses/{b['id']}").status_code == 404
+    c = client.post("/v1/responses", json={"input": "not stored", "store": False, "max_output_tokens": 2}).json()
+    assert client.get(f"/v1/responses/{c['id']}").status_code == 404
+
+
+def test_nvml_sampler_against_a_fake_binding():
+    from types import SimpleNamespace
+    from metrale_inference_alpha_b200.utils.nvml import DeviceSampler, decode_reasons
+    power = iter([400_000, 600_000, 800_000])
+
+    class Fake:
+        NVML_CLOCK_SM, NVML_CLOCK_MEM, NVML_TEMPERATURE_GPU = 1, 2, 0
+        nvmlInit = staticmethod(lambda: None)
+        nvmlDeviceGetHandleByIndex = staticmethod(lambda i: "h")
+        nvmlDeviceGetClockInfo = staticmethod(lambda h, k: 1965 if k == 1 else 3996)
+        nvmlDeviceGetPowerUsage = staticmethod(lambda h: next(power))
+        nvmlDeviceGetTemperature = staticmethod(lambda h, k: 55)
+        nvmlDeviceGetUtilizationRates = staticmethod(lambda h: SimpleNamespace(gpu=97))
+        nvmlDeviceGetMemoryInfo = staticmethod(lambda h: SimpleNamespace(used=10 << 30))
+        nvmlDeviceGetCurrentClocksThrottleReasons = staticmethod(lambda h: 0x4)
+    t = iter([0.0, 1.0, 2.0])
+    s = DeviceSampler(nvml=Fake, clock=lambda: next(t))
+    for _ in range(3):
+        s.sample_once()
+    out = s.summary(tokens=100)
+    assert out["energy_j"] == pytest.approx(500.0 + 700.0) and out["joules_per_token"] == pytest.approx(12.0)
+    assert out["reasons"] == ["sw_power_cap"] and out["rejected"] is False and out["sm_mhz_median"] == 1965
+    assert decode_reasons(0x8 | 0x40) == ["hw_slowdown", "hw_thermal_slowdown"]
