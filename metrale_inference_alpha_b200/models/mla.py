@@ -38,8 +38,9 @@ def mla_block(dec, x, lw, batch, kv, j: int):
     q_rope = ref.apply_rope_neox(q[..., nope:], batch.positions, dec.cos, dec.sin)
     row = torch.cat([lat, k_rope], -1).to(kv.k[j].dtype)               # cache row
     flat = kv.k[j].view(-1, L + rope)
-    ok = batch.slot_mapping >= 0
-    flat[batch.slot_mapping[ok]] = row[ok]
+    # rows without a slot (-1: padding of a CUDA-graph rung) land in the reserved null block 0, which
+    # no sequence reads; a fixed-shape scatter keeps the step capturable
+    flat.index_copy_(0, batch.slot_mapping.clamp(min=0), row)
     q_lat = torch.einsum("thn,hnl->thl", q[..., :nope], w.w_uk.float())   # absorb W_uk
     qq = torch.cat([q_lat, q_rope], -1).to(torch.bfloat16)             # [T, H, L + rope]
     scale = 1.0 / math.sqrt(nope + rope)

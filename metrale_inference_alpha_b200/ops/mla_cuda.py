@@ -52,11 +52,9 @@ def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_table, q_start, q_
         # which must stay zero between its launches: the MLA partials live behind them
         rt.ensure_attn_ws(need + _CNT_BYTES)
         if row_seq is None:                       # row -> sequence map for the merge pass
-            row_seq = torch.repeat_interleave(torch.arange(q_len.numel(), device=q.device, dtype=torch.int32),
-                                              q_len.clamp(min=0).long(), output_size=None)
-            if row_seq.numel() < T:
-                row_seq = torch.cat([row_seq, row_seq.new_zeros(T - row_seq.numel())])
-            row_seq = row_seq.to(torch.int32).contiguous()
+            # fixed-shape (capturable): the sequence of row t is the last one whose first row is <= t
+            rows = torch.arange(T, device=q.device, dtype=q_start.dtype)
+            row_seq = (torch.bucketize(rows, q_start, right=True) - 1).clamp(min=0).to(torch.int32).contiguous()
     a = MlaArgs()
     a.q, a.cache, a.block_table, a.max_blocks = _ptr(q), _ptr(cache), _ptr(block_table), block_table.stride(0)
     a.q_start, a.q_len, a.ctx_len, a.row_seq = _ptr(q_start), _ptr(q_len), _ptr(ctx_len), _ptr(row_seq)

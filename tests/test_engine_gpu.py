@@ -75,3 +75,34 @@ def test_static_activation_scales_are_calibrated_and_keep_graph_equals_eager():
     # (a random-weight model has near-flat logits, so token agreement with the dynamic-scale engine
     # is not a stable measure; the kernels' numerics are compared directly in test_kernels_gpu.py)
     assert [len(o) for o in outs["dynamic"]] == [len(o) for o in outs["graph"]]
+
+
+def _tiny_family(name):
+    if name == "hybrid-moe":
+        return preset("qwen-hybrid-moe-35b-fp8", num_layers=4, hidden_size=512, num_heads=4, num_kv_heads=2,
+                      gdn_k_heads=4, gdn_v_heads=4, num_experts=8, experts_per_token=2, moe_intermediate_size=256,
+                      intermediate_size=256, vocab_size=4096, max_position=1024)
+    if name == "nemotron-h":
+        return preset("nemotron-h-8b-fp8", num_layers=4, hidden_size=512, num_heads=8, num_kv_heads=2,
+                      intermediate_size=1024, mamba_heads=16, mamba_groups=2, vocab_size=4096, max_position=1024)
+    if name == "deepseek-mla":
+        return preset("deepseek-v3-671b-fp8", num_layers=3, first_dense_layers=1, hidden_size=512, num_heads=8,
+                      num_kv_heads=8, q_lora_rank=256, dense_intermediate_size=1024, intermediate_size=1024,
+                      num_experts=8, experts_per_token=2, moe_intermediate_size=256, router_n_group=2,
+                      router_topk_group=1, vocab_size=4096, mtp_layers=0, max_position=1024)
+    raise KeyError(name)
+
+
+@pytest.mark.parametrize("family", ["hybrid-moe", "nemotron-h", "deepseek-mla"])
+def test_other_architecture_families_run_on_the_gpu_and_graphs_equal_eager(family):
+    """Tiny instances of the hybrid GDN + MoE, Mamba2 hybrid and MLA + MoE families: prefill, ragged
+    decode with CUDA graphs and eager must give the same tokens, and the first token of every
+    request must equal the CPU oracle engine's (same synthetic checkpoint)."""
+    cfg = _tiny_family(family)
+    outs = {}
+    for graphs in (False, True):
+        eng = LLMEngine(EngineArgs(model=cfg, device="cuda", max_num_seqs=8, max_model_len=256,
+                                   use_cuda_graphs=graphs, enable_prefix_caching=False))
+        outs[graphs] = _drive(eng, _arrivals())
+    assert outs[True] == outs[False]
+    assert [len(o) for o in outs[True]] == [70, 45, 12, 50, 40, 3]
