@@ -431,8 +431,8 @@ inline cudaError_t launch_kernel_ex(void (*kern)(KArgs...), dim3 grid, dim3 bloc
   cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
-// METRALE_PDL: 0 = plain launches, 1 = every kernel launches programmatically, 2 = only the GEMMs
-// (whose prologue and first weight tiles then overlap the tail of the preceding kernel)
+// METRALE_PDL: 0 = plain launches, 1 = every kernel launches programmatically, 2 (default) = only
+// the GEMMs, whose prologue and first ring of weight tiles then overlap the preceding kernel
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                          cudaStream_t stream, int cluster_z, Args&&... args) {

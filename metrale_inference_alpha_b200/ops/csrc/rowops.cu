@@ -424,7 +424,7 @@ static int g_pdl = -1;
 int mb_pdl_enabled() {
   if (g_pdl < 0) {
     const char* e = getenv("METRALE_PDL");
-    g_pdl = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0;   // opt-in: measured slower than plain launches here
+    g_pdl = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2;   // default: GEMMs launch programmatically   
   }
   return g_pdl;
 }

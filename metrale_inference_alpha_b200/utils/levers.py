@@ -7,7 +7,7 @@ import os
 from typing import Dict, List
 
 LEVERS: Dict[str, str] = {
-    "METRALE_PDL": "programmatic dependent launch: 0 = off (default), 1 = every kernel, 2 = GEMMs only",
+    "METRALE_PDL": "programmatic dependent launch: 0 = off, 1 = every kernel, 2 = GEMMs only (default)",
     "METRALE_B200_AUTOBUILD": "0 = never build the kernel library on import (default 1)",
     "METRALE_COMM_DIAGNOSTICS": "1 = log every collective submission with a sequence number",
     "METRALE_MTP_K_LADDER": "draft-width ladder 'width:k,...' (default 4:3,8:3,16:1,32:1)",
