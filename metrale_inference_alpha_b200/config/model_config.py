@@ -32,6 +32,7 @@ class ModelConfig:
     num_kv_heads: int = 2
     head_dim: int = 64
     rope_theta: float = 1e6
+    rope_scaling: Optional[dict] = None     # HF `rope_scaling` (linear / llama3 / yarn); None = plain RoPE
     rotary_dim: int = 0                 # 0 -> head_dim; -1 -> no RoPE (Nemotron-H attention)
     qk_norm: bool = False
     attn_output_gate: bool = False      # q_proj emits [Q_h | G_h] per head, o = attn * sigmoid(G)
@@ -309,7 +310,7 @@ def from_hf_config(cfg: dict, name: str = "model") -> ModelConfig:
     heads = cfg.get("num_attention_heads", 1)
     kw = dict(name=name, arch=arch, vocab_size=cfg["vocab_size"], hidden_size=h, num_layers=L,
               num_heads=heads, num_kv_heads=cfg.get("num_key_value_heads", heads),
-              head_dim=cfg.get("head_dim", h // heads), rope_theta=float(cfg.get("rope_theta", 1e4)),
+              head_dim=cfg.get("head_dim", h // heads), rope_theta=float(cfg.get("rope_theta", 1e4)), rope_scaling=cfg.get("rope_scaling"),
               rms_eps=float(cfg.get("rms_norm_eps", cfg.get("layer_norm_epsilon", 1e-6))),
               intermediate_size=cfg.get("intermediate_size", 0),
               tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),

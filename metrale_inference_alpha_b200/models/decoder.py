@@ -64,7 +64,8 @@ class Decoder:
         rot = cfg.rotary_dim
         self.cos = self.sin = None
         if rot > 0:
-            self.cos, self.sin = ref.rope_tables(cfg.max_position, rot, cfg.rope_theta, device=self.device)
+            self.cos, self.sin = ref.rope_tables(cfg.max_position, rot, cfg.rope_theta, device=self.device,
+                                                 scaling=cfg.rope_scaling)
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         self.lora = None                   # lora.LoraManager when adapters are served
         self.calib = None                  # dict while calibrating static activation scales (engine/runner.py)

@@ -44,6 +44,11 @@ def mla_block(dec, x, lw, batch, kv, j: int):
     q_lat = torch.einsum("thn,hnl->thl", q[..., :nope], w.w_uk.float())   # absorb W_uk
     qq = torch.cat([q_lat, q_rope], -1).to(torch.bfloat16)             # [T, H, L + rope]
     scale = 1.0 / math.sqrt(nope + rope)
+    sc = c.rope_scaling or {}
+    if sc.get("rope_type", sc.get("type")) == "yarn" and sc.get("mscale_all_dim"):
+        # DeepSeek long-context checkpoints fold the YaRN magnitude correction into the softmax scale
+        m = 0.1 * float(sc["mscale_all_dim"]) * math.log(float(sc.get("factor", 1.0))) + 1.0
+        scale *= m * m
     if mla_cuda.supported(qq, kv.k[j]) and L == mla_cuda.LATENT:
         o_lat = mla_cuda.mla_attention(qq, kv.k[j], batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
                                        max_q_len=batch.max_q_len, max_ctx=max(batch.max_ctx, 1), scale=scale)

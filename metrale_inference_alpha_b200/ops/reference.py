@@ -185,11 +185,62 @@ def relu2(x: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- rope
-def rope_tables(max_pos: int, rot: int, theta: float, device="cpu") -> Tuple[torch.Tensor, torch.Tensor]:
-    """cos/sin [max_pos, rot/2] with freq_i = theta^(-2i/rot) (kernels/gb10/common/rope.cu:11-21)."""
+def rope_inv_freq(rot: int, theta: float, scaling: Optional[dict] = None) -> Tuple[torch.Tensor, float]:
+    """Inverse frequencies [rot/2] (float64) and the attention factor that multiplies cos / sin, for
+    the plain table and the long-context rescalings of HF `rope_scaling` configs: linear (position
+    interpolation), llama3 (low / high frequency bands), yarn (NTK-by-parts + mscale). The kernels
+    only ever see the finished tables, so every variant costs nothing at run time
+    (kernels/gb10/common/rope.cu: rope_forward, rope_yarn, rope_proportional)."""
+    import math
     inv = theta ** (-torch.arange(0, rot, 2, dtype=torch.float64) / rot)
+    if not scaling:
+        return inv, 1.0
+    kind = scaling.get("rope_type", scaling.get("type", "default"))
+    factor = float(scaling.get("factor", 1.0))
+    if kind in ("default", None):
+        return inv, 1.0
+    if kind == "linear":
+        return inv / factor, 1.0
+    if kind == "llama3":
+        lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        old = float(scaling["original_max_position_embeddings"])
+        wavelen = 2 * math.pi / inv
+        smooth = ((old / wavelen) - lo) / (hi - lo)
+        mid = (1 - smooth) * inv / factor + smooth * inv
+        out = torch.where(wavelen > old / lo, inv / factor, torch.where(wavelen < old / hi, inv, mid))
+        return out, 1.0
+    if kind == "yarn":
+        old = float(scaling.get("original_max_position_embeddings", 4096))
+        beta_fast, beta_slow = float(scaling.get("beta_fast", 32)), float(scaling.get("beta_slow", 1))
+
+        def get_mscale(scale, m=1.0):
+            return 1.0 if scale <= 1 else 0.1 * m * math.log(scale) + 1.0
+        ms, ms_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+        att = scaling.get("attention_factor")
+        if att is None:
+            att = get_mscale(factor, ms) / get_mscale(factor, ms_all) if (ms and ms_all) else get_mscale(factor)
+
+        def corr_dim(n_rot):
+            return (rot * math.log(old / (n_rot * 2 * math.pi))) / (2 * math.log(theta))
+        low, high = corr_dim(beta_fast), corr_dim(beta_slow)
+        if scaling.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, rot - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(rot // 2, dtype=torch.float64) - low) / (high - low)).clamp(0, 1)
+        extrap_w = 1 - ramp                                      # 1 = keep the original frequency
+        return (inv / factor) * (1 - extrap_w) + inv * extrap_w, float(att)
+    raise ValueError(f"unsupported rope_scaling type {kind!r}")
+
+
+def rope_tables(max_pos: int, rot: int, theta: float, device="cpu", scaling: Optional[dict] = None
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin [max_pos, rot/2] with freq_i = theta^(-2i/rot) (kernels/gb10/common/rope.cu:11-21),
+    optionally rescaled for long context (see rope_inv_freq)."""
+    inv, att = rope_inv_freq(rot, theta, scaling)
     ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
-    return ang.cos().float().to(device), ang.sin().float().to(device)
+    return (ang.cos() * att).float().to(device), (ang.sin() * att).float().to(device)
 
 
 def apply_rope_neox(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):

@@ -144,3 +144,36 @@ def test_sampler_reference_greedy_and_topk():
     for s in range(20):
         ids, _ = ops.sample(x, one(1.0), one(2, torch.int32), one(1.0), one(0.0), one(s, torch.int64), one(0, torch.int64))
         assert ids.item() in (1, 3)
+
+
+def test_rope_scaling_tables_match_transformers():
+    """linear / llama3 / yarn inverse frequencies and attention factor against the HF oracle."""
+    from types import SimpleNamespace
+    import torch
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+    from metrale_inference_alpha_b200.ops import reference as ref
+    cases = [
+        {"rope_type": "linear", "factor": 4.0},
+        {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+         "original_max_position_embeddings": 8192},
+        {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32768},
+        {"rope_type": "yarn", "factor": 40.0, "original_max_position_embeddings": 4096, "beta_fast": 32, "beta_slow": 1,
+         "mscale": 1.0, "mscale_all_dim": 1.0},
+    ]
+    for sc in cases:
+        theta, D = 1e6, 128
+        cfg = SimpleNamespace(rope_theta=theta, head_dim=D, hidden_size=D * 8, num_attention_heads=8,
+                              partial_rotary_factor=1.0, max_position_embeddings=131072, rope_scaling=dict(sc),
+                              rope_parameters=dict(sc, rope_theta=theta))
+        cfg.standardize_rope_params = lambda: None
+        try:
+            want, att = ROPE_INIT_FUNCTIONS[sc["rope_type"]](cfg, device="cpu")
+        except Exception as e:                      # signature drift between transformers versions
+            import pytest
+            pytest.skip(f"transformers oracle unavailable: {e}")
+        got, att_got = ref.rope_inv_freq(D, theta, sc)
+        assert torch.allclose(got.float(), want.float(), rtol=1e-5, atol=1e-9), sc
+        assert abs(att_got - float(att)) < 1e-6, sc
+    cos, sin = ref.rope_tables(64, 128, 1e6, scaling={"rope_type": "linear", "factor": 2.0})
+    c0, s0 = ref.rope_tables(64, 128, 1e6)
+    assert torch.allclose(cos[2 * 7], c0[7], atol=1e-6) and torch.allclose(sin[2 * 7], s0[7], atol=1e-6)
