@@ -53,6 +53,7 @@ class EngineArgs:
     request_timeout_s: float = 300.0
     eos_token_id: Optional[int] = None
     fused_collectives: bool = True
+    ep_dispatch: str = "allreduce"                     # expert parallelism: allreduce (masked-local experts) | a2a (token dispatch over peer memory)
     static_act_scales: bool = True                     # NVFP4: calibrate down-projection input scales at start-up
     preempt_mode: str = "recompute"                    # recompute | swap (KV + state to host memory / swap files)
     swap_space_bytes: int = 8 << 30
@@ -94,6 +95,14 @@ class LLMEngine:
         ops.configure(attn_part_tokens=1024 if args.max_num_seqs >= 64 else 512)
         self.runner = ModelRunner(cfg, self.weights, args.device, blocks, self.sched_cfg, self.tp,
                                   use_graphs=args.use_cuda_graphs, kv_poison=args.kv_poison)
+        if args.ep_dispatch == "a2a" and args.ep_size > 1 and self.tp.size > 1 and self.device.type == "cuda" \
+                and cfg.num_experts > 0:
+            from ..parallel.ep import EpAllToAll
+            per_rank = (max(self.sched_cfg.max_prefill_tokens, args.max_num_seqs * 8) + self.tp.size - 1) // self.tp.size
+            self.tp.ep = EpAllToAll(self.tp.rank, self.tp.size, self.device, cfg.hidden_size, per_rank,
+                                    cfg.experts_per_token)
+            # the exchange's sequence numbers are launch arguments: steps run eagerly on this path
+            self.runner.use_graphs = False
         self.calibrated_layers = 0
         if args.static_act_scales and cfg.weight_format == "nvfp4" and self.device.type == "cuda":
             self.calibrated_layers = self.runner.calibrate_static_scales()

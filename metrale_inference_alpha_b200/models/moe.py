@@ -29,13 +29,20 @@ def moe_block(dec, x, lw):
     else:
         routed = routed_experts(dec, a, weights, idx, w)
     y = routed
+    sh = None
     if w.shared is not None:
         sh = shared_expert(dec, a, w)
         if w.shared_gate is not None:
             g = ops.linear(dec._as_act(hb, "bf16"), w.shared_gate, out_f32=True)
             sh = sh.float() * torch.sigmoid(g)
+    # a width-sharded shared expert is a partial sum like the routed part; a replicated one (expert
+    # parallelism) is added once, after the sum over ranks
+    replicated = sh is not None and getattr(w, "shared_replicated", False) and dec.tp.size > 1
+    if sh is not None and not replicated:
         y = y.float() + sh.float()
     y = dec.tp.all_reduce(y.to(torch.bfloat16)) if (dec.tp.size > 1) else y
+    if replicated:
+        y = y.float() + sh.float()
     return (x.float() + y.float()).to(torch.bfloat16)
 
 

@@ -124,6 +124,7 @@ class MoeW:
     expert_lo: int = 0
     shared: Optional[FfnW] = None
     shared_gate: Optional[QuantWeight] = None
+    shared_replicated: bool = False                        # expert parallelism keeps the whole shared expert on every rank
     grouped: Optional[object] = None                       # stacked device layout for the grouped GEMM
 
 

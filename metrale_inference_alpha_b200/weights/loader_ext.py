@@ -90,6 +90,7 @@ def moe(ld, p: str) -> MoeW:
         sp = "shared_expert" if ld.src.has(f"{p}.shared_expert.up_proj.weight") or \
             ld.src.has(f"{p}.shared_expert.up_proj.weight_packed") else "shared_experts"
         w.shared = ld.ffn(f"{p}.{sp}", shard=shard_width)
+        w.shared_replicated = not shard_width
         if ld.src.has(f"{p}.shared_expert_gate.weight"):
             w.shared_gate = ld.lin(f"{p}.shared_expert_gate", quant=False)
     if ld.dev.type == "cuda":

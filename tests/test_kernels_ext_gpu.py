@@ -236,3 +236,37 @@ def test_engine_with_adapters_on_gpu_isolates_rows():
     assert mixed[0] == base and mixed[2] == base and mixed[1] != base
     assert run(["strong"])[0] == mixed[1]          # the adapted row does not depend on its neighbours
     ops.check_status(DEV)
+
+
+# ---------------------------------------------------------------------------- EP all-to-all (one rank = loopback)
+def test_ep_all_to_all_loopback_matches_local_experts():
+    """World size 1: the dispatch / return kernels run against the rank's own landing zone, so the
+    whole protocol (slots, counts, flags, parity double buffering) is exercised on one GPU and the
+    result must equal the local routed-expert path."""
+    from metrale_inference_alpha_b200.parallel.ep import EpAllToAll
+    torch.manual_seed(0)
+    T, K, H, E = 23, 2, 256, 8
+    x = torch.randn(T, H, device=DEV).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, device=DEV)[:K] for _ in range(T)]).to(torch.int32)
+    wts = torch.rand(T, K, device=DEV)
+    mats = torch.randn(E, H, H, device=DEV) * 0.05
+
+    def expert_fn(rows, eids):
+        e = eids.view(-1).long()
+        out = torch.zeros(rows.shape[0], H, device=DEV)
+        ok = e >= 0
+        out[ok] = torch.einsum("nh,nhk->nk", rows[ok].float(), mats[e[ok]])
+        return out
+    ep = EpAllToAll(0, 1, DEV, hidden=H, max_tokens=32, top_k=K)
+    want = torch.zeros(T, H, device=DEV)
+    for j in range(K):
+        want += wts[:, j:j + 1] * torch.einsum("nh,nhk->nk", x.float(), mats[idx[:, j].long()])
+    for step in range(3):                                  # alternating parities, stale zones from earlier steps
+        got = ep.moe(x, wts, idx, E, expert_fn)
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+        assert torch.allclose(got, want, rtol=3e-2, atol=3e-2 * want.abs().max().item()), step
+        x = x.flip(0).contiguous()
+        idx = idx.flip(0).contiguous()
+        wts = wts.flip(0).contiguous()
+        want = want.flip(0)

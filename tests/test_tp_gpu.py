@@ -17,3 +17,12 @@ def test_fused_gemm_allreduce_matches_nccl_on_two_gpus():
            "--master-port", "29533", os.path.join(ROOT, "tests", "multi_gpu", "tp_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert "TP_CHECK PASS" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ep_all_to_all_matches_masked_local_allreduce_on_two_gpus():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29534", os.path.join(ROOT, "tests", "multi_gpu", "ep_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert "EP_CHECK PASS" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
