@@ -796,30 +796,6 @@ __global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_split
   }
 }
 
-// Merge partitions: out = sum_p w_p * o_p, w_p = l_p 2^(m_p - m) / sum(...)
-__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                  __nv_bfloat16* __restrict__ out, int parts, int D) {
-  const size_t row = blockIdx.x;  // (query row, head)
-  mb::pdl_wait();
-  mb::pdl_launch_dependents();
-  float mx = -INFINITY;
-  for (int s = 0; s < parts; ++s) mx = fmaxf(mx, part_ml[(row * parts + s) * 2]);
-  float denom = 0.f;
-  for (int s = 0; s < parts; ++s) {
-    const float m = part_ml[(row * parts + s) * 2], l = part_ml[(row * parts + s) * 2 + 1];
-    denom += (m == -INFINITY) ? 0.f : l * exp2f(m - mx);
-  }
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < parts; ++s) {
-      const float m = part_ml[(row * parts + s) * 2], l = part_ml[(row * parts + s) * 2 + 1];
-      if (m == -INFINITY || l <= 0.f) continue;
-      acc += part_o[(row * parts + s) * D + d] * (l * exp2f(m - mx));
-    }
-    out[row * D + d] = __float2bfloat16(denom > 0.f ? acc / denom : 0.f);
-  }
-}
-
 // ------------------------------------------------------------------ split-Q (prefill) kernel
 // grid (ceil(max_q_len / 64), Hq, num_seqs), 128 threads; warp w owns query rows 16w..16w+15.
 template <int D, bool FP8>
@@ -1160,12 +1136,7 @@ int mb_paged_attention(const MbAttnArgs* a, cudaStream_t stream) {
     else if (a->D == 256) rc = fp8 ? dispatch_mt<256, true>(mt, p, a->num_seqs, stream)
                                    : dispatch_mt<256, false>(mt, p, a->num_seqs, stream);
     else return MB_ERR_UNSUPPORTED;
-    return rc;
-    if (p.parts > 1) {
-      return (int)mb::launch_kernel(attn_merge_kernel, dim3(a->total_rows * a->Hq), dim3(128), 0, stream,
-                                    (const float*)p.part_o, (const float*)p.part_ml, p.out, p.parts, a->D);
-    }
-    return 0;
+    return rc;                    // partitions are merged inside the kernel by the last arriver
   }
   p.parts = 1;
   if (a->D == 128) return fp8 ? launch_prefill<128, true>(p, a->num_seqs, a->max_q_len, stream)

@@ -890,17 +890,6 @@ int dispatch_persistent(int tn, const CUtensorMap& tmA, const CUtensorMap& tmB, 
   }
 }
 
-// Waits (bounded) until every unit of the fused all-reduce has been finished by its owner,
-// re-arms the counter and flips this rank's parity for the next call.
-__global__ void tp_finish_kernel(uint32_t* done, uint32_t* par, uint32_t units, uint32_t* status) {
-  if (threadIdx.x != 0) return;
-  const uint32_t pcur = *par & 1u;
-  mb::wait_flag_sys(done + pcur, units, status);
-  done[pcur] = 0;
-  *par = pcur ^ 1u;
-  __threadfence_system();
-}
-
 template <int KIND, int TN>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, dim3 grid,
            cudaStream_t stream) {

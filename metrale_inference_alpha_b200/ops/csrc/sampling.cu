@@ -51,10 +51,32 @@ argmax_kernel(const T* __restrict__ logits, long long ld, int V, int* __restrict
   const T* x = logits + (size_t)row * ld;
   float best = -INFINITY;
   int bidx = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    if (i == mask_a || i == mask_b) continue;
-    const float v = ld_logit<T>(x, i);
-    if (v > best || (v == best && i < bidx)) { best = v; bidx = i; }
+  if (sizeof(T) == 4 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    // 16-byte loads: four logits per thread per step (ascending index order inside a thread keeps
+    // the first-maximum rule)
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    const int V4 = V >> 2;
+    for (int i4 = threadIdx.x; i4 < V4; i4 += blockDim.x) {
+      const float4 q = x4[i4];
+      const float vv[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = i4 * 4 + k;
+        if (i == mask_a || i == mask_b) continue;
+        if (vv[k] > best || (vv[k] == best && i < bidx)) { best = vv[k]; bidx = i; }
+      }
+    }
+    for (int i = (V4 << 2) + threadIdx.x; i < V; i += blockDim.x) {
+      if (i == mask_a || i == mask_b) continue;
+      const float v = ld_logit<T>(x, i);
+      if (v > best || (v == best && i < bidx)) { best = v; bidx = i; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      if (i == mask_a || i == mask_b) continue;
+      const float v = ld_logit<T>(x, i);
+      if (v > best || (v == best && i < bidx)) { best = v; bidx = i; }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
