@@ -150,7 +150,41 @@ _CODES = {-1: "bad argument", -2: "unsupported shape/format", -3: "workspace too
           -4: "CUDA driver entry point unavailable"}
 
 
+# Launch trace: while a recorder list is installed, every launcher call appends its name, so two
+# runs (or a graph capture and an eager step) can be compared launch by launch. Role of the
+# reference's launch trace diff and kernel-resolution audit (crates/telemetry/src/launch_trace.rs).
+_trace = None
+
+
+class launch_trace:
+    """``with launch_trace() as names: ...`` collects the name of every kernel launcher called."""
+
+    def __enter__(self):
+        global _trace
+        self._prev, self.names = _trace, []
+        _trace = self.names
+        return self.names
+
+    def __exit__(self, *exc):
+        global _trace
+        _trace = self._prev
+        return False
+
+
+def diff_traces(a, b):
+    """First position at which two launch traces differ, as (index, name_a, name_b), or None."""
+    for i, (x, y) in enumerate(zip(a, b)):
+        if x != y:
+            return i, x, y
+    if len(a) != len(b):
+        i = min(len(a), len(b))
+        return i, a[i] if i < len(a) else None, b[i] if i < len(b) else None
+    return None
+
+
 def check(rc: int, what: str) -> None:
+    if _trace is not None:
+        _trace.append(what.split("[", 1)[0])
     if rc != 0:
         msg = _CODES.get(rc, f"CUDA error {rc}")
         raise KernelError(f"{what}: {msg}")

@@ -64,6 +64,31 @@ class NcclTpContext(TpContext):
     def is_healthy(self) -> bool:
         return self.poisoned is None
 
+    def attempt_reconnect(self, timeout_s: float = 60.0) -> bool:
+        """Replace a poisoned communicator: every rank must call this. A fresh process group over
+        the same ranks is created (new communicator, new rendezvous keys under the same store),
+        verified with one all-reduce, and swapped in; the poisoned flag is cleared only when that
+        succeeds on this rank. The fused peer-memory path stays off afterwards (its symmetric
+        buffers belonged to the old group). Role of ``NcclBackend::attempt_reconnect``
+        (``crates/comm/src/nccl_backend.rs:254-346``: abort + re-bootstrap on master_port + 1)."""
+        from datetime import timedelta
+        if self.size == 1:
+            self.poisoned = None
+            return True
+        try:
+            backend = dist.get_backend(self.group) if self.group is not None else dist.get_backend()
+            new_group = dist.new_group(ranks=list(range(self.size)), backend=backend,
+                                       timeout=timedelta(seconds=timeout_s))
+            probe = torch.ones(1, device=self.device if backend == "nccl" else "cpu")
+            dist.all_reduce(probe, group=new_group)
+            if int(probe.item()) != self.size:
+                return False
+        except RuntimeError as e:
+            self.poisoned = f"reconnect failed: {e}"
+            return False
+        self.group, self.poisoned, self.fused, self.reconnects = new_group, None, False, getattr(self, "reconnects", 0) + 1
+        return True
+
     # ------------------------------------------------------------------ collectives
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.size == 1:

@@ -49,6 +49,7 @@ def build_parser() -> argparse.ArgumentParser:
 
     s = sub.add_parser("serve", help="start the HTTP server")
     _add_engine_args(s)
+    s.add_argument("--recipe", default=None, help="YAML file with the model and its serve options (command line wins)")
     s.add_argument("--host", default="127.0.0.1")
     s.add_argument("--port", type=int, default=8888)
     s.add_argument("--served-model-name", default=None)
@@ -154,7 +155,23 @@ def serve(ns) -> None:
     uvicorn.run(app, host=ns.host, port=ns.port, log_level="info", timeout_graceful_shutdown=20)
 
 
+def _apply_recipe(argv: List[str]) -> List[str]:
+    """`serve --recipe file.yaml ...`: recipe options first, then the command line (which wins)."""
+    if not argv or argv[0] != "serve" or "--recipe" not in argv:
+        return argv
+    import os as _os
+    from ..config.recipes import load_recipe, recipe_to_argv
+    path = argv[argv.index("--recipe") + 1]
+    recipe = load_recipe(path)
+    serve = build_parser()._subparsers._group_actions[0].choices["serve"]          # noqa: SLF001
+    options = [o for a in serve._actions for o in a.option_strings if o.startswith("--")]
+    for k, v in (recipe.get("env") or {}).items():
+        _os.environ.setdefault(k, str(v))
+    return ["serve"] + recipe_to_argv(recipe, options) + argv[1:]
+
+
 def main(argv: Optional[List[str]] = None) -> int:
+    argv = _apply_recipe(list(sys.argv[1:] if argv is None else argv))
     ns = build_parser().parse_args(argv)
     if ns.cmd == "serve":
         serve(ns)

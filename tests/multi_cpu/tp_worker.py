@@ -82,6 +82,24 @@ def main():
             eng.fault.set(str(e))
         result["steps"] = steps
         result["fault"] = eng.fault.reason()
+    elif scenario == "reconnect":
+        # a collective fails on the host (injected), the context is poisoned and refuses work; all
+        # ranks reconnect and the next collective runs on the fresh group
+        from metrale_inference_alpha_b200.parallel.tp import CommPoisoned
+        t = torch.ones(4)
+        tp.all_reduce(t)
+        result["before"] = t.tolist()
+        tp.poison("injected: collective timed out")
+        try:
+            tp.all_reduce(torch.ones(4))
+            result["refused"] = False
+        except CommPoisoned:
+            result["refused"] = True
+        result["reconnected"] = tp.attempt_reconnect(timeout_s=20.0)
+        t = torch.full((4,), float(rank + 1))
+        tp.all_reduce(t)
+        result["after"] = t.tolist()
+        result["healthy"] = tp.is_healthy()
     with open(f"{out_path}.{rank}", "w") as f:
         json.dump(result, f)
     os._exit(0)                                      # no collective teardown: a peer may be gone

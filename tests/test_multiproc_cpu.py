@@ -71,3 +71,12 @@ def test_rank_leaving_between_steps_is_detected_on_the_host(tmp_path):
     assert res[1]["left_at"] == 3
     assert "peer_lost" in res[0] and res[0]["fault"]
     assert res[0]["steps"] <= 4                      # it stopped before launching further work
+
+
+def test_poisoned_communicator_refuses_then_reconnects(tmp_path):
+    p, res = _run("reconnect", tmp_path)
+    assert p.returncode == 0, p.stderr[-2000:]
+    for r in (0, 1):
+        assert res[r]["before"] == [2.0] * 4 and res[r]["refused"] is True
+        assert res[r]["reconnected"] is True and res[r]["healthy"] is True
+        assert res[r]["after"] == [3.0] * 4

@@ -51,3 +51,35 @@ def test_gate_record_signing_tamper_detection_and_regression(tmp_path):
     assert "0.877x" in slower.regression_vs(rec)
     assert GateRecord("c128", rec.metric, 13500.0, rec.unit).regression_vs(rec) is None
     assert "not comparable" in GateRecord("x", "ttft", 1.0, "ms", False).regression_vs(rec)
+
+
+def test_recipe_yaml_to_serve_arguments(tmp_path):
+    from metrale_inference_alpha_b200.config.recipes import load_recipe, recipe_to_argv
+    from metrale_inference_alpha_b200.server import cli
+    p = tmp_path / "r.yaml"
+    p.write_text("model: tiny-dense\nmax-num-seqs: 16\nuse_cuda_graphs: false\ntool_call_parser: mistral\n"
+                 "lora_adapters: {sql: /a/sql}\napi_key: [k1, k2]\nenv: {METRALE_PDL: '0'}\n")
+    argv = cli._apply_recipe(["serve", "--recipe", str(p), "--port", "9001", "--max-num-seqs", "4"])
+    ns = cli.build_parser().parse_args(argv)
+    assert ns.model == "tiny-dense" and ns.max_num_seqs == 4 and ns.port == 9001        # command line wins
+    assert ns.use_cuda_graphs is False and ns.tool_call_parser == "mistral"
+    assert ns.lora_adapter == ["sql=/a/sql"] and ns.api_key == ["k1", "k2"]
+    p.write_text("model: x\nnot_an_option: 1\n")
+    with pytest.raises(ValueError, match="not a serve option"):
+        recipe_to_argv(load_recipe(str(p)), ["--model"])
+    p.write_text("model: x\nenv: {METRALE_TYPO: 1}\n")
+    with pytest.raises(ValueError, match="undeclared levers"):
+        recipe_to_argv(load_recipe(str(p)), ["--model"])
+
+
+def test_launch_trace_records_and_diffs():
+    from metrale_inference_alpha_b200.ops import _native
+    with _native.launch_trace() as a:
+        _native.check(0, "gemm[nvfp4 M=1 N=2 K=3]")
+        _native.check(0, "row_op")
+    with _native.launch_trace() as b:
+        _native.check(0, "gemm[bf16 M=9]")
+        _native.check(0, "paged_attention")
+    assert a == ["gemm", "row_op"] and _native.diff_traces(a, b) == (1, "row_op", "paged_attention")
+    assert _native.diff_traces(a, a) is None and _native.diff_traces(a, a[:1]) == (1, "row_op", None)
+    _native.check(0, "not recorded")
