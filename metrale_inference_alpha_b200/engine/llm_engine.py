@@ -68,7 +68,7 @@ class LLMEngine:
         cfg = args.model
         if isinstance(cfg, str):
             import os
-            if os.path.isdir(cfg):
+            if os.path.isdir(cfg) or (os.path.isfile(cfg) and cfg.endswith(".gguf")):
                 from ..weights.checkpoint import open_checkpoint
                 cfg, source = open_checkpoint(cfg, device=args.device)
             else:

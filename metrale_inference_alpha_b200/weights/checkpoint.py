@@ -11,6 +11,11 @@ from .fast_source import open_source
 
 def open_checkpoint(path, device="cpu"):
     p = Path(path)
+    ggufs = [p] if p.is_file() and p.suffix == ".gguf" else (sorted(p.glob("*.gguf")) if p.is_dir() else [])
+    if ggufs and not list(p.glob("*.safetensors") if p.is_dir() else []):
+        from .gguf import GgufSource
+        src = GgufSource(ggufs[0])
+        return src.cfg, src
     src = open_source(p, device=device)
     eng = p / "engine_config.json"
     if eng.exists():
