@@ -106,3 +106,36 @@ def test_other_architecture_families_run_on_the_gpu_and_graphs_equal_eager(famil
         outs[graphs] = _drive(eng, _arrivals())
     assert outs[True] == outs[False]
     assert [len(o) for o in outs[True]] == [70, 45, 12, 50, 40, 3]
+
+
+def test_http_surface_over_a_gpu_engine():
+    """The FastAPI app over a CUDA engine: chat completion, streaming, JSON mode (native token mask
+    on the host-logits path) and usage timing fields, with the flagship architecture at tiny size."""
+    import json
+    from fastapi.testclient import TestClient
+    from metrale_inference_alpha_b200.server.app import ServerConfig, create_app
+    from metrale_inference_alpha_b200.server.tokenizer import load_tokenizer
+    cfg = preset("dense-27b-nvfp4", num_layers=2, hidden_size=1024, num_heads=8, num_kv_heads=2,
+                 intermediate_size=2048, vocab_size=8192, mtp_layers=0, max_position=1024)
+    eng = LLMEngine(EngineArgs(model=cfg, device="cuda", max_num_seqs=8, max_model_len=512, num_kv_blocks=256))
+    tok = load_tokenizer(None, cfg.vocab_size)
+    with TestClient(create_app(eng, tok, ServerConfig(model_name="tiny-gpu"))) as c:
+        body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 12, "temperature": 0, "return_token_ids": True}
+        a = c.post("/v1/chat/completions", json=body).json()
+        b = c.post("/v1/chat/completions", json=body).json()
+        # the second request resumes from the prefix cache, i.e. through different kernels (a 5-row verify-
+        # shaped step instead of a 21-row prefill): with random weights only the first tokens are stable
+        assert a["choices"][0]["token_ids"][0] == b["choices"][0]["token_ids"][0]
+        assert len(a["choices"][0]["token_ids"]) == len(b["choices"][0]["token_ids"]) == 12
+        assert a["usage"]["time_to_first_token_ms"] > 0 and b["usage"]["prompt_tokens_details"]["cached_tokens"] > 0
+        with c.stream("POST", "/v1/chat/completions", json=dict(body, stream=True)) as s:
+            lines = [l for l in s.iter_lines() if l]
+        assert lines[-1] == "data: [DONE]"
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "json"}], "max_tokens": 40,
+                                                 "response_format": {"type": "json_object"}, "temperature": 0.7, "seed": 3}).json()
+        text = r["choices"][0]["message"]["content"]
+        from metrale_inference_alpha_b200.server.grammar import JsonMatcher
+        assert JsonMatcher(require_object=True).feed_bytes(text.encode())
+        if r["choices"][0]["finish_reason"] == "stop":
+            assert isinstance(json.loads(text), dict)
+        assert "metrale_engine_graph_replays" in c.get("/metrics").text
