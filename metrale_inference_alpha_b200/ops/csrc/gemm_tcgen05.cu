@@ -76,6 +76,7 @@ struct GemmParams {
   uint8_t* outq_sf;   // [ceil(M / 128)][outq_sf_k64][512]
   int outq_sf_k64;
   float outq_gs;
+  int m_fastest;      // token tiles in blockIdx.x (prefill): see the kernel's launch-order note
   int cluster;        // splits form a thread-block cluster; partial tiles are reduced over DSMEM
   long long* trace;   // optional per-phase cycle stamps of CTA (0,0,0) and the last CTA in x
   int dbg;   // timing experiments only: 1 skip SF copies, 2 skip epilogue stores, 4 skip MMAs, 8 skip SF loads
@@ -128,7 +129,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __shared__ float s_ascale[TN];
 
   const int warp = threadIdx.x >> 5;
-  const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
+  // Launch order: blockIdx.x runs fastest. Decode (one token tile) walks the weight tiles in x. With
+  // many token tiles (prefill) the token tiles go in x instead, so the CTAs that are resident together
+  // share a few weight tiles (each read from DRAM once and re-served from L2) rather than streaming
+  // the whole weight matrix once per token tile.
+  const int tile_n = p.m_fastest ? blockIdx.y : blockIdx.x;
+  const int tile_m = p.m_fastest ? blockIdx.x : blockIdx.y;
+  const int split = blockIdx.z;
+  const int tiles_n_grid = p.m_fastest ? gridDim.y : gridDim.x;
   int m_row0 = tile_m * TN, m_end = p.M, expert = 0, n_limit = p.N;
   if (p.tile_expert) {
     mb::pdl_wait();                               // the work list is written by the preceding sort kernel
@@ -316,7 +324,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       wcol[i] = wsc;
     }
-    const size_t tile_lin = (size_t)tile_m * gridDim.x + tile_n;
+    const size_t tile_lin = (size_t)tile_m * tiles_n_grid + tile_n;
     float* wsp = (p.splits > 1 && !p.cluster) ? p.ws + (tile_lin * p.splits + split) * (size_t)(TN * kTileN) : s_tile;
 
     if constexpr (KIND == KIND_FP8_BLOCK) {
@@ -1080,7 +1088,9 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   rc = mbh::encode_2d(&tmB, dt, a->X, inner, (uint64_t)a->M, row_bytes, box_inner, (uint32_t)tn);
   if (rc) return rc;
 
-  dim3 grid(tiles_n, tiles_m, splits);
+  // prefill-sized plain GEMMs put the token tiles in x (dbg bit 64 keeps the decode order, for A/B timing)
+  p.m_fastest = (!grouped && tiles_m >= 8 && tiles_m <= 65535 && tiles_n <= 65535 && !(a->dbg & 64)) ? 1 : 0;
+  dim3 grid(p.m_fastest ? tiles_m : tiles_n, p.m_fastest ? tiles_n : tiles_m, splits);
   rc = MB_ERR_UNSUPPORTED;
   // more weight-row tiles than SMs and a single token tile: persistent CTAs, balanced tile counts
   if (!grouped && a->tp_size <= 1 && splits == 1 && tiles_m == 1 && tn <= 128 && kind != KIND_FP8_BLOCK &&

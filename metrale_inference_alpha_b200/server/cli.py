@@ -132,6 +132,30 @@ def run_benchmark(ns) -> List[dict]:
     return run_ladder(_engine_args(ns), [int(c) for c in ns.concurrency.split(",")], ns.isl, ns.osl)
 
 
+def _init_ranks(eargs):
+    """Process group + tensor-parallel context + control plane for a multi-rank launch."""
+    import torch
+    import torch.distributed as dist
+    from ..parallel.control import ControlPlane
+    rank, world, local = (int(os.environ.get(k, "0")) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if str(eargs.device).startswith("cuda"):
+        from ..parallel.tp import NcclTpContext
+        torch.cuda.set_device(local)
+        eargs.device = f"cuda:{local}"
+        dist.init_process_group("nccl", device_id=torch.device(eargs.device))
+        tp = NcclTpContext(rank, world, eargs.device, fused=eargs.fused_collectives)
+    else:
+        from ..parallel.tp import GlooTpContext
+        dist.init_process_group("gloo")
+        tp = GlooTpContext(rank, world)
+    if eargs.ep_size > 1:
+        tp.ep_rank = rank
+    else:
+        eargs.tp_size = world
+    return tp, ControlPlane.create()
+
+
 def serve(ns) -> None:
     import uvicorn
     from ..engine.llm_engine import LLMEngine
@@ -140,7 +164,17 @@ def serve(ns) -> None:
     eargs = _engine_args(ns)
     if ns.swap_space_gb > 0:
         eargs.preempt_mode, eargs.swap_space_bytes = "swap", int(ns.swap_space_gb * (1 << 30))
-    engine = LLMEngine(eargs)
+    tp, control = None, None
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        # launched by torch.distributed.run: every rank builds its shard; rank 0 owns HTTP and
+        # publishes each tick's operations, the others replay them (parallel/control.py)
+        tp, control = _init_ranks(eargs)
+    engine = LLMEngine(eargs, tp=tp)
+    if control is not None and control.rank != 0:
+        from ..parallel.control import follower_loop
+        print(f"[rank {control.rank}] follower ended: {follower_loop(engine, control)}", flush=True)
+        return
     for spec in ns.lora_adapter:
         name, _, path = spec.partition("=")
         engine.load_adapter(name, path, ns.max_loras, ns.max_lora_rank)
@@ -151,7 +185,7 @@ def serve(ns) -> None:
                        reasoning_format=ns.reasoning_format, default_max_tokens=ns.default_max_tokens,
                        tool_max_tokens=ns.tool_max_tokens,
                        telemetry=ns.telemetry, disable_thinking=ns.disable_thinking)
-    app = create_app(engine, tokenizer, cfg)
+    app = create_app(engine, tokenizer, cfg, control=control)
     uvicorn.run(app, host=ns.host, port=ns.port, log_level="info", timeout_graceful_shutdown=20)
 
 

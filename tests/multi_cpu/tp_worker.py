@@ -82,6 +82,22 @@ def main():
             eng.fault.set(str(e))
         result["steps"] = steps
         result["fault"] = eng.fault.reason()
+    elif scenario == "serve":
+        # rank 0 owns the HTTP app (driven in-process), followers replay its operations; the chat
+        # answer must equal a single-rank engine's and the followers must stop on shutdown
+        cp = ControlPlane.create(timeout_s=20.0)
+        if rank == 0:
+            from fastapi.testclient import TestClient
+            from metrale_inference_alpha_b200.server.app import ServerConfig, create_app
+            from metrale_inference_alpha_b200.server.tokenizer import load_tokenizer
+            tok = load_tokenizer(None, eng.cfg.vocab_size)
+            with TestClient(create_app(eng, tok, ServerConfig(model_name="tp"), control=cp)) as c:
+                r = c.post("/v1/completions", json={"prompt": prompts()[0], "max_tokens": 6, "temperature": 0,
+                                                    "return_token_ids": True})
+                result["status"] = r.status_code
+                result["ids"] = r.json()["choices"][0]["token_ids"]
+        else:
+            result["ended"] = follower_loop(eng, cp)
     elif scenario == "reconnect":
         # a collective fails on the host (injected), the context is poisoned and refuses work; all
         # ranks reconnect and the next collective runs on the fresh group

@@ -80,3 +80,10 @@ def test_poisoned_communicator_refuses_then_reconnects(tmp_path):
         assert res[r]["before"] == [2.0] * 4 and res[r]["refused"] is True
         assert res[r]["reconnected"] is True and res[r]["healthy"] is True
         assert res[r]["after"] == [3.0] * 4
+
+
+def test_rank0_http_app_drives_follower_ranks(tmp_path):
+    p, res = _run("serve", tmp_path)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert res[0]["status"] == 200 and res[0]["ids"] == _single_rank_ids()[0]
+    assert res[1]["ended"] == "shutdown"
