@@ -230,6 +230,15 @@ class Loader:
     def lin(self, prefix, quant=True) -> QuantWeight:
         return read_linear(self.src, prefix, self.dev, self.fmt if quant else None)
 
+    def input_scale(self, prefix: str) -> float:
+        """Calibrated global scale of an NVFP4 linear's input (ModelOpt's `<linear>.input_scale`,
+        amax / (6 * 448)); 0.0 when the checkpoint carries none."""
+        name = f"{prefix}.input_scale"
+        if self.fmt != "nvfp4" or not self.src.has(name):
+            return 0.0
+        v = float(self.src.get(name).float().reshape(-1)[0])
+        return v if v > 0.0 and v == v and v != float("inf") else 0.0
+
     def _shard(self, n: int):
         assert n % self.tp_size == 0, f"{n} not divisible by tp {self.tp_size}"
         per = n // self.tp_size
@@ -257,6 +266,7 @@ class Loader:
         else:
             hkv = c.num_kv_heads
         w = AttnW(finalize(ops.concat_weights([q, k, v])), finalize(o), heads=hq, kv_heads=hkv)
+        w.o_in_scale = self.input_scale(f"{p}.o_proj")
         if self.src.has(f"{p}.q_norm.weight"):
             w.q_norm, w.k_norm = self.vec(f"{p}.q_norm.weight"), self.vec(f"{p}.k_norm.weight")
         return w
@@ -272,15 +282,16 @@ class Loader:
             up, down = slice_rows(up, lo, hi), slice_cols(down, lo, hi)
             if gate is not None:
                 gate = slice_rows(gate, lo, hi)
+        gs = self.input_scale(f"{p}.{names[2]}")
         if gate is None:
-            return FfnW(finalize(up), finalize(down))
+            return FfnW(finalize(up), finalize(down), down_in_scale=gs)
         gu = ops.concat_weights([gate, up])
         if gu.fmt == "fp8_block":
             # 128x128 scale blocks forbid a row-interleave: keep gate | up halves
-            return FfnW(finalize(gu), finalize(down))
+            return FfnW(finalize(gu), finalize(down), down_in_scale=gs)
         I = up.N
         perm = torch.stack([torch.arange(I), torch.arange(I) + I], 1).reshape(-1).to(gu.data.device)
-        return FfnW(finalize(ops.permute_rows(gu, perm)), finalize(down), interleaved=True)
+        return FfnW(finalize(ops.permute_rows(gu, perm)), finalize(down), interleaved=True, down_in_scale=gs)
 
     # ---- layers
     def layer(self, p: str, lt: str, ft: str, names=None) -> LayerW:

@@ -221,3 +221,22 @@ def test_engine_loads_a_checkpoint_directory_through_the_fast_reader(tmp_path):
     p = [[1, 2, 3, 4, 5]]
     sp = SamplingParams(max_tokens=6)
     assert a.generate(p, sp)[0].output_ids == b.generate(p, sp)[0].output_ids
+
+
+def test_loader_reads_modelopt_input_scale():
+    """A ModelOpt NVFP4 checkpoint's `<linear>.input_scale` becomes the static activation scale of
+    the down and o projections; linears without one stay on dynamic scales (0)."""
+    import torch
+    from metrale_inference_alpha_b200.config.model_config import tiny_dense
+    from metrale_inference_alpha_b200.weights.loader import load_weights
+    from metrale_inference_alpha_b200.weights.source import DictSource, SyntheticSource
+    cfg = tiny_dense(weight_format="nvfp4")
+    syn = SyntheticSource(cfg, seed=0)
+    t = {n: syn.get(n) for n in syn.names()}
+    t["model.layers.0.mlp.down_proj.input_scale"] = torch.tensor(0.00125)
+    t["model.layers.0.self_attn.o_proj.input_scale"] = torch.tensor([0.0025])
+    t["model.layers.1.mlp.down_proj.input_scale"] = torch.tensor(float("nan"))
+    w = load_weights(cfg, DictSource(t, syn.quant_config))
+    assert abs(w.layers[0].ffn.down_in_scale - 0.00125) < 1e-9
+    assert abs(w.layers[0].mixer.o_in_scale - 0.0025) < 1e-9
+    assert w.layers[1].ffn.down_in_scale == 0.0 and w.layers[1].mixer.o_in_scale == 0.0
