@@ -5,6 +5,8 @@
   Python classes stay as the behavioural oracle of the differential tests).
 * ``NativeJsonGrammar``: byte-level JSON pushdown recogniser with a whole-vocabulary token mask
   fill (constrained decoding for ``response_format``).
+* ``NativePda``: pushdown matcher for grammars compiled by the ``grammar`` package (EBNF, regex,
+  JSON Schema, structural tags) with an exact, memoised whole-vocabulary mask and rollback.
 * ``read_ranges``: multi-threaded ``pread`` (optionally O_DIRECT) of byte ranges of a file into
   caller-owned memory (pinned staging of the checkpoint loader).
 
@@ -74,6 +76,18 @@ def _load():
         "mrt_json_feed": (C.c_int32, [C.c_void_p, _U8P, C.c_int32]),
         "mrt_json_fill_mask": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, _U8P, C.c_int32]),
         "mrt_json_advance": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32]),
+        "mrt_pda_grammar_create": (C.c_void_p, [C.c_int32, _I32P, C.c_int32, _I32P, _I32P, _I32P, _I32P, _I32P,
+                                                C.c_int32, _I32P, C.c_int32]),
+        "mrt_pda_grammar_destroy": (None, [C.c_void_p]),
+        "mrt_pda_create": (C.c_void_p, [C.c_void_p]),
+        "mrt_pda_destroy": (None, [C.c_void_p]),
+        "mrt_pda_reset": (None, [C.c_void_p]),
+        "mrt_pda_complete": (C.c_int32, [C.c_void_p]),
+        "mrt_pda_feed": (C.c_int32, [C.c_void_p, _U8P, C.c_int32]),
+        "mrt_pda_advance": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32]),
+        "mrt_pda_rollback": (C.c_int32, [C.c_void_p, C.c_int32]),
+        "mrt_pda_stats": (None, [C.c_void_p, _I64P]),
+        "mrt_pda_fill_mask": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, _U8P, C.c_int32]),
         "mrt_read_ranges": (C.c_int64, [C.c_char_p, C.c_int32, _I64P, _I64P, C.POINTER(C.c_void_p), C.c_int32, C.c_int32]),
     }
     for name, (res, args) in sig.items():
@@ -287,12 +301,90 @@ class NativeJsonGrammar:
             _lib.mrt_json_advance(self._h, self.vocab.h, int(tid))
             self._history.append(int(tid))
 
+    def rollback(self, n: int) -> None:
+        """Forgets the last n accepted tokens (rebuilds the recogniser by replaying the rest)."""
+        keep = self._history[:max(0, len(self._history) - n)]
+        _lib.mrt_json_destroy(self._h)
+        self._h = C.c_void_p(_lib.mrt_json_create(int(self.require_object)))
+        self._history = []
+        for t in keep:
+            self.advance(t)
+
     def is_complete(self) -> bool:
         return bool(_lib.mrt_json_complete(self._h))
 
     def feed_bytes(self, bs: bytes) -> bool:
         buf = (C.c_uint8 * max(1, len(bs))).from_buffer_copy(bs or b"\0")
         return _lib.mrt_json_feed(self._h, buf, len(bs)) == len(bs)
+
+
+# ---------------------------------------------------------------------------- pushdown grammar
+def has_pda() -> bool:
+    return _load() is not None and hasattr(_lib, "mrt_pda_create")
+
+
+class _NativeGrammar:
+    """The compiled tables of a ``grammar.CompiledGrammar`` in native memory (shared by matchers)."""
+
+    def __init__(self, g):
+        def arr(xs):
+            return (C.c_int32 * max(1, len(xs)))(*xs)
+        self.h = C.c_void_p(_lib.mrt_pda_grammar_create(
+            g.n_nodes, arr(g.edge_begin), len(g.edge_kind), arr(g.edge_kind), arr(g.edge_a), arr(g.edge_b),
+            arr(g.edge_to), arr(g.final), len(g.rule_start), arr(g.rule_start), g.root))
+        if not self.h:
+            raise ValueError("malformed compiled grammar")
+
+    def __del__(self):
+        if _lib is not None and getattr(self, "h", None):
+            _lib.mrt_pda_grammar_destroy(self.h)
+            self.h = None
+
+
+class NativePda:
+    """Pushdown matcher over a compiled grammar with an exact whole-vocabulary mask and rollback
+    (``grammar.TokenMatcher`` wraps it)."""
+
+    def __init__(self, grammar, tokenizer=None, vocab_size: Optional[int] = None):
+        if not has_pda():
+            raise RuntimeError("native host runtime is not built")
+        if grammar._native is None:
+            grammar._native = _NativeGrammar(grammar)
+        self._g = grammar._native                     # keeps the tables alive
+        self.vocab = _Vocab.of(tokenizer, vocab_size or tokenizer.vocab_size) if tokenizer is not None else None
+        self._h = C.c_void_p(_lib.mrt_pda_create(self._g.h))
+
+    def __del__(self):
+        if _lib is not None and getattr(self, "_h", None):
+            _lib.mrt_pda_destroy(self._h)
+            self._h = None
+
+    def fill_mask(self, vocab: int, eos: Optional[int]) -> torch.Tensor:
+        mask = torch.zeros(vocab, dtype=torch.uint8)
+        _lib.mrt_pda_fill_mask(self._h, self.vocab.h, -1 if eos is None else eos,
+                               C.cast(mask.data_ptr(), _U8P), vocab)
+        return mask.bool()
+
+    def advance(self, tid: int) -> bool:
+        return bool(_lib.mrt_pda_advance(self._h, self.vocab.h, int(tid)))
+
+    def rollback(self, n: int) -> int:
+        return int(_lib.mrt_pda_rollback(self._h, int(n)))
+
+    def is_complete(self) -> bool:
+        return bool(_lib.mrt_pda_complete(self._h))
+
+    def feed(self, bs: bytes) -> bool:
+        buf = (C.c_uint8 * max(1, len(bs))).from_buffer_copy(bs or b"\0")
+        return bool(_lib.mrt_pda_feed(self._h, buf, len(bs)))
+
+    def reset(self) -> None:
+        _lib.mrt_pda_reset(self._h)
+
+    def stats(self) -> Dict[str, int]:
+        out = (C.c_int64 * 4)()
+        _lib.mrt_pda_stats(self._h, out)
+        return {"items": out[0], "frames": out[1], "mask_cache_hits": out[2], "mask_cache_misses": out[3]}
 
 
 # ---------------------------------------------------------------------------- file reader

@@ -14,7 +14,7 @@ def build(force: bool = False) -> Path:
     srcs = sorted(HERE.glob("*.cpp"))
     if not srcs:
         return LIB
-    h = hashlib.sha256(b"".join(p.read_bytes() for p in srcs)).hexdigest()
+    h = hashlib.sha256(b"".join(p.read_bytes() for p in srcs + sorted(HERE.glob("*.h")))).hexdigest()
     stamp = HERE / "build" / "stamp.txt"
     if not force and LIB.exists() and stamp.exists() and stamp.read_text() == h:
         return LIB

@@ -9,6 +9,8 @@
 #include <cstring>
 #include <vector>
 
+#include "vocab.h"
+
 namespace {
 
 enum State : uint8_t {
@@ -135,11 +137,7 @@ struct Json {
   }
 };
 
-struct Vocab {
-  std::vector<uint8_t> bytes;
-  std::vector<int64_t> offsets;     // n + 1 entries
-  int32_t n = 0;
-};
+using Vocab = MrtVocab;
 
 }  // namespace
 

@@ -96,6 +96,7 @@ def sample_rows(runner, plan, logits: torch.Tensor) -> Tuple[List[List[int]], Li
         f = lambda name: torch.tensor([getattr(p, name) for p in P], dtype=torch.float32, device=dev)
         ops.apply_penalties(logits, tok, cnt, inp, f("repetition_penalty"), f("presence_penalty"),
                             f("frequency_penalty"))
+    spec_ahead: dict = {}            # item -> draft tokens its grammar was advanced over while masking
     for r, it in enumerate(row_item):
         p = it.seq.req.params
         if p.logit_bias:
@@ -112,8 +113,16 @@ def sample_rows(runner, plan, logits: torch.Tensor) -> Tuple[List[List[int]], Li
                 idx = torch.tensor(list(pens.keys()), device=dev)
                 logits[r, idx] -= torch.tensor(list(pens.values()), dtype=torch.float32, device=dev)
         if p.grammar is not None:
-            mask = p.grammar.allowed_mask(logits.shape[1]).to(dev)
-            logits[r].masked_fill_(~mask, float("-inf"))
+            # row j of a verify item is masked from the state after drafts 1..j; the matcher is
+            # rewound to the accepted prefix once the targets are known
+            j = r - row_first[id(it)]
+            mask = p.grammar.allowed_mask(logits.shape[1])
+            if j < it.verify and hasattr(p.grammar, "rollback"):
+                d = it.tokens[1 + j]
+                if spec_ahead.get(id(it), 0) == j and d < mask.shape[0] and bool(mask[d]):
+                    p.grammar.advance(d)
+                    spec_ahead[id(it)] = j + 1
+            logits[r].masked_fill_(~mask.to(dev), float("-inf"))
         if runner.logit_processor is not None:
             logits[r] = runner.logit_processor(it.seq, logits[r])
         if p.top_n_sigma > 0 and p.temperature > 0:
@@ -136,8 +145,15 @@ def sample_rows(runner, plan, logits: torch.Tensor) -> Tuple[List[List[int]], Li
             continue
         k = it.verify + 1
         toks.append(ids[r:r + k]); lps.append(lp[r:r + k])
-        if it.seq.req.params.grammar is not None:
-            it.seq.req.params.grammar.advance(ids[r + k - 1])
+        gm = it.seq.req.params.grammar
+        if gm is not None:
+            if spec_ahead.get(id(it)):
+                gm.rollback(spec_ahead[id(it)])
+            n_acc = 0
+            while n_acc < it.verify and it.tokens[1 + n_acc] == ids[r + n_acc]:
+                n_acc += 1
+            for tkn in list(it.tokens[1:1 + n_acc]) + [ids[r + n_acc]]:
+                gm.advance(tkn)
         if it.seq.req.params.top_logprobs:
             top = torch.log_softmax(logits[r + k - 1], -1).topk(it.seq.req.params.top_logprobs)
             it.seq.top_logprobs = getattr(it.seq, "top_logprobs", []) + [

@@ -23,7 +23,7 @@ from ..sampling.params import SamplingParams
 from ..utils.telemetry import Telemetry
 from .chat_template import ChatRenderer
 from .engine_loop import AsyncEngine
-from .grammar import grammar_for_response_format
+from .grammar import grammar_for_response_format, tool_call_grammar
 from .ratelimit import RateLimiter
 from .reasoning_parser import ReasoningParser
 from .response_store import ResponseStore
@@ -42,6 +42,7 @@ class ServerConfig:
     request_timeout_s: float = 300.0
     telemetry: str = "basic"
     disable_thinking: bool = False
+    tool_grammar: bool = False          # constrain tool calls with a grammar even under tool_choice "auto"
 
 
 @dataclass
@@ -141,7 +142,16 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         text = renderer.render(msgs, tools=tools, add_generation_prompt=True, enable_thinking=thinking, **kw)
         ids = tokenizer.encode(text)
         sp = _sampling_from(body, cfg)
-        sp.grammar = grammar_for_response_format(body.get("response_format"), tokenizer, eos)
+        try:
+            sp.grammar = grammar_for_response_format(body.get("response_format"), tokenizer, eos)
+            forced = choice == "required" or (isinstance(choice, dict) and choice.get("type") not in ("auto", "none"))
+            if sp.grammar is None and tools and (forced or cfg.tool_grammar) and hasattr(tokenizer, "token_bytes"):
+                tg = tool_call_grammar(tools, cfg.tool_call_parser, "required" if forced else "auto")
+                if tg is not None:
+                    from ..grammar import TokenMatcher
+                    sp.grammar = TokenMatcher(tg, tokenizer, eos)
+        except ValueError as e:             # GrammarError: the schema / pattern / grammar does not compile
+            raise HTTPException(400, f"invalid grammar: {e}")
         sp.adapter = body.get("adapter")
         return _ChatJob(ids, sp, tools, thinking, bool(body.get("logprobs")), bool(body.get("return_token_ids")))
 

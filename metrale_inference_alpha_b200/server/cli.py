@@ -56,6 +56,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--tokenizer", default=None, help="directory with tokenizer.json (default: the checkpoint)")
     s.add_argument("--api-key", action="append", default=[])
     s.add_argument("--rate-limit", type=float, default=0.0, help="requests per second per key; 0 = off")
+    s.add_argument("--tool-grammar", action="store_true", help="constrain tool calls with a grammar also under tool_choice=auto")
     s.add_argument("--tool-call-parser", default="hermes", choices=["hermes", "qwen3_xml", "qwen3_coder", "mistral", "gemma4", "minimax_xml", "deepseek_v4_dsml",
                             "poolside_v1", "bare_json", "json"])
     s.add_argument("--reasoning-format", default="think")
@@ -181,7 +182,7 @@ def serve(ns) -> None:
     tok_dir = ns.tokenizer or (eargs.model if isinstance(eargs.model, str) and os.path.isdir(eargs.model) else None)
     tokenizer = load_tokenizer(tok_dir, engine.cfg.vocab_size)
     cfg = ServerConfig(model_name=ns.served_model_name or str(ns.model), auth_tokens=ns.api_key,
-                       rate_per_s=ns.rate_limit, tool_call_parser=ns.tool_call_parser,
+                       rate_per_s=ns.rate_limit, tool_call_parser=ns.tool_call_parser, tool_grammar=getattr(ns, "tool_grammar", False),
                        reasoning_format=ns.reasoning_format, default_max_tokens=ns.default_max_tokens,
                        tool_max_tokens=ns.tool_max_tokens,
                        telemetry=ns.telemetry, disable_thinking=ns.disable_thinking)

@@ -1,9 +1,9 @@
 """Constrained decoding: an incremental matcher decides which tokens may come next.
 
-``JsonMatcher`` accepts exactly the prefixes of JSON values (optionally restricted to a top-level
-object, and checked against a JSON-schema subset: type, properties, required, enum, items);
-``RegexMatcher`` accepts prefixes of a regular expression via a derivative-free NFA over the
-pattern's byte alphabet. ``TokenGrammar`` lifts a byte matcher to the token vocabulary: the
+The general engine is the ``grammar`` package (EBNF / regex / JSON Schema / structural tags ->
+pushdown matcher, native mask fill); this module is the server-side glue that maps request fields
+to it, plus ``JsonMatcher``, the stand-alone JSON recogniser used when the native runtime is not
+built. ``TokenGrammar`` lifts a byte matcher to the token vocabulary: the
 allowed mask is computed by simulating each candidate token's bytes from the current state
 (candidates are limited to the highest logits first, widening until a legal token is found,
 so the cost per step is independent of vocabulary size).
@@ -241,6 +241,7 @@ class TokenGrammar:
     def __init__(self, tokenizer, matcher, eos_token_id: Optional[int] = None, probe: int = 64):
         self.tk, self.m, self.eos, self.probe = tokenizer, matcher, eos_token_id, probe
         self._last_logits: Optional[torch.Tensor] = None
+        self._snaps: list = []              # matcher before each accepted token (speculative rewind)
 
     def observe_logits(self, row: torch.Tensor) -> None:
         self._last_logits = row
@@ -276,16 +277,83 @@ class TokenGrammar:
 
     def advance(self, tid: int) -> None:
         if tid != self.eos:
+            self._snaps.append(self.m.clone())
             self.m.feed_bytes(self.tk.token_bytes(tid))
 
+    def rollback(self, n: int) -> None:
+        for _ in range(min(n, len(self._snaps))):
+            self.m = self._snaps.pop()
 
-def grammar_for_response_format(fmt: Optional[dict], tokenizer, eos_token_id=None) -> Optional[TokenGrammar]:
+
+def _native_ok(tokenizer) -> bool:
+    return hasattr(tokenizer, "token_bytes") and hasattr(tokenizer, "vocab_size")
+
+
+def grammar_for_response_format(fmt: Optional[dict], tokenizer, eos_token_id=None):
+    """``response_format`` -> a token matcher (None = unconstrained). ``json_object`` is any JSON
+    object; ``json_schema`` is compiled by the grammar package (``json_schema.schema`` or a
+    top-level ``schema``); ``regex`` (``pattern``) and ``grammar`` / ``ebnf`` (``grammar``) are
+    extensions that reach the same engine. A source that does not compile raises GrammarError."""
     if not fmt:
         return None
+    from .. import grammar as G
     t = fmt.get("type")
-    if t in ("json_object", "json_schema"):
+    if t == "json_schema":
+        js = fmt.get("json_schema") or {}
+        schema = js.get("schema", fmt.get("schema"))
+        if schema is not None and _native_ok(tokenizer):
+            return G.TokenMatcher(G.compile_json_schema(schema), tokenizer, eos_token_id)
+        t = "json_object"
+    if t == "json_object":
         from .. import native
-        if native.available() and hasattr(tokenizer, "token_bytes") and hasattr(tokenizer, "vocab_size"):
+        if native.available() and _native_ok(tokenizer):
             return native.NativeJsonGrammar(tokenizer, eos_token_id, require_object=True)
         return TokenGrammar(tokenizer, JsonMatcher(require_object=True), eos_token_id)
+    if t == "regex" and _native_ok(tokenizer):
+        return G.TokenMatcher(G.compile_regex(fmt.get("pattern") or fmt.get("regex") or ""), tokenizer, eos_token_id)
+    if t in ("grammar", "ebnf") and _native_ok(tokenizer):
+        return G.TokenMatcher(G.compile_ebnf(fmt.get("grammar") or fmt.get("ebnf") or ""), tokenizer, eos_token_id)
     return None
+
+
+def tool_call_grammar(tools: Optional[List[dict]], parser: str, mode: str = "auto"):
+    """Compiled grammar that keeps tool calls well-formed for the call syntax `parser` scans
+    (reference: ``GrammarSpec::ToolCall``, compiled by the parser that reads the response).
+    `mode`: "auto" = free text where a trigger must continue as a valid call; "required" = nothing
+    but calls (the forced tool call of ``tool_choice: required`` or a named function). None when the format has no grammar here (the parser's salvage passes still
+    apply)."""
+    if not tools:
+        return None
+    from .. import grammar as G
+    fns = []
+    for t in tools:
+        f = t.get("function") or t
+        if f.get("name"):
+            fns.append((f["name"], f.get("parameters") or f.get("input_schema") or {"type": "object"}))
+    if not fns:
+        return None
+    required = mode == "required"
+    if parser in ("hermes", "qwen3", "qwen"):
+        tags = [{"begin": '<tool_call>\n{"name": ' + json.dumps(n) + ', "arguments": ', "schema": p,
+                 "end": "}\n</tool_call>"} for n, p in fns]
+        return G.compile_structural_tag(tags, ["<tool_call>"], calls_only=required)
+    call = {"anyOf": [{"type": "object", "properties": {"name": {"const": n}, "arguments": p},
+                       "required": ["name", "arguments"]} for n, p in fns]}
+    if parser == "mistral":
+        tags = [{"begin": "[TOOL_CALLS]", "schema": {"type": "array", "items": call, "minItems": 1}, "end": ""}]
+        return G.compile_structural_tag(tags, ["[TOOL_CALLS]"], calls_only=required, stop_after_first=required)
+    if parser == "bare_json" and required:
+        return G.compile_json_schema(call)
+    return None
+
+
+def prewarm(tools: Optional[List[dict]], parser: str) -> int:
+    """Compiles (into the shared cache) the grammars a request with these tools may need, so that
+    the first constrained step does not pay for it. Returns how many compiled."""
+    n = 0
+    for mode in ("auto", "required"):
+        try:
+            n += tool_call_grammar(tools, parser, mode) is not None
+        except ValueError:
+            pass
+    return n

@@ -285,6 +285,41 @@ def test_json_mode_returns_a_json_object(client):
         assert isinstance(json.loads(text), dict)
 
 
+def test_json_schema_regex_and_tool_grammar_constrain_the_output(client):
+    from metrale_inference_alpha_b200 import grammar as G
+    schema = {"type": "object", "properties": {"n": {"type": "integer", "minimum": 0}, "k": {"enum": ["a", "b"]}},
+              "required": ["n", "k"]}
+    msgs = [{"role": "user", "content": "go"}]
+    r = client.post("/v1/chat/completions", json={
+        "messages": msgs, "max_tokens": 40, "temperature": 0,
+        "response_format": {"type": "json_schema", "json_schema": {"name": "x", "schema": schema}}}).json()
+    text = r["choices"][0]["message"]["content"]
+    m = G.GrammarMatcher(G.compile_json_schema(schema))
+    assert m.feed_bytes(text.encode())                       # a legal prefix of a document of this schema
+    if r["choices"][0]["finish_reason"] == "stop":
+        v = json.loads(text)
+        assert v["n"] >= 0 and v["k"] in ("a", "b")
+    r = client.post("/v1/chat/completions", json={
+        "messages": msgs, "max_tokens": 24, "temperature": 0.8, "seed": 5,
+        "response_format": {"type": "regex", "pattern": r"(yes|no)( [a-z]{1,3}){0,2}\."}}).json()
+    text = r["choices"][0]["message"]["content"]
+    assert G.GrammarMatcher(G.compile_regex(r"(yes|no)( [a-z]{1,3}){0,2}\.")).feed_bytes(text.encode())
+    assert r["choices"][0]["finish_reason"] == "stop"         # the pattern is finite: the mask ends it
+    import re as _re
+    assert _re.fullmatch(r"(yes|no)( [a-z]{1,3}){0,2}\.", text)
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {
+        "type": "object", "properties": {"x": {"type": "boolean"}}, "required": ["x"]}}}]
+    r = client.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 64, "temperature": 0,
+                                                  "tools": tools, "tool_choice": "required"}).json()
+    ch = r["choices"][0]
+    if ch["finish_reason"] == "tool_calls":
+        call = ch["message"]["tool_calls"][0]["function"]
+        assert call["name"] == "f" and isinstance(json.loads(call["arguments"])["x"], bool)
+    r = client.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 4,
+                                                  "response_format": {"type": "regex", "pattern": "(a"}})
+    assert r.status_code == 400 and "invalid grammar" in r.text
+
+
 def test_anthropic_messages_and_count_tokens(client):
     body = {"model": "tiny", "max_tokens": 5, "system": "be brief", "messages": [{"role": "user", "content": "hi"}]}
     r = client.post("/v1/messages", json=body).json()
