@@ -37,6 +37,7 @@ class ModelConfig:
     qk_norm: bool = False
     attn_output_gate: bool = False      # q_proj emits [Q_h | G_h] per head, o = attn * sigmoid(G)
     sliding_window: int = 0
+    attn_bias: bool = False             # q / k / v projections carry a bias (Qwen2 family)
     # norms
     rms_eps: float = 1e-6
     norm_plus_one: bool = False         # (1 + w) scaling (Qwen3.5 family)
@@ -65,6 +66,7 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     num_shared_experts: int = 0
     shared_expert_gate: bool = False
+    shared_expert_name: str = ""        # "" = by architecture ("shared_expert" for the Qwen families)
     router: str = "softmax"             # softmax | sigmoid
     router_n_group: int = 1
     router_topk_group: int = 1
@@ -270,6 +272,7 @@ def preset(name: str, **kw) -> ModelConfig:
 # ----------------------------------------------------------------------------- HF config.json
 _HF_ARCH = {
     "llama": "dense_gqa", "qwen2": "dense_gqa", "qwen3": "dense_gqa", "mistral": "dense_gqa",
+    "phi3": "dense_gqa", "qwen3_moe": "dense_gqa", "qwen2_moe": "dense_gqa", "mixtral": "dense_gqa",
     "qwen3_5": "qwen_hybrid", "qwen3_5_moe": "qwen_hybrid", "qwen3_next": "qwen_hybrid",
     "qwen3_5_text": "qwen_hybrid", "qwen3_5_moe_text": "qwen_hybrid",
     "nemotron_h": "nemotron_h", "deepseek_v3": "deepseek_mla", "deepseek_v2": "deepseek_mla",
@@ -318,8 +321,34 @@ def from_hf_config(cfg: dict, name: str = "model") -> ModelConfig:
               weight_format=detect_weight_format(cfg.get("quantization_config")),
               mtp_layers=int(cfg.get("mtp_num_hidden_layers", cfg.get("num_nextn_predict_layers", 0)) or 0))
     if arch == "dense_gqa":
-        kw["qk_norm"] = mt == "qwen3"
+        kw["qk_norm"] = mt in ("qwen3", "qwen3_moe")
+        kw["attn_bias"] = bool(cfg.get("attention_bias", cfg.get("qkv_bias", mt in ("qwen2", "qwen2_moe"))))
         kw["sliding_window"] = int(cfg.get("sliding_window") or 0) if cfg.get("use_sliding_window") else 0
+        if mt == "phi3":
+            rs = cfg.get("rope_scaling")
+            if rs and str(rs.get("type", rs.get("rope_type", ""))).lower() in ("longrope", "su"):
+                raise ValueError("phi3 longrope scaling is not supported")
+            prf = float(cfg.get("partial_rotary_factor", 1.0))
+            if prf < 1.0:
+                kw["rotary_dim"] = int(kw["head_dim"] * prf)
+        if mt in ("qwen3_moe", "qwen2_moe"):
+            step = int(cfg.get("decoder_sparse_step", 1) or 1)
+            only = set(cfg.get("mlp_only_layers") or [])
+            ne = int(cfg.get("num_experts", 0))
+            kw.update(ffn_types=["moe" if ne and i not in only and (i + 1) % step == 0 else "dense" for i in range(L)],
+                      num_experts=ne, experts_per_token=cfg.get("num_experts_per_tok", 8),
+                      moe_intermediate_size=cfg.get("moe_intermediate_size", 768), router="softmax",
+                      router_renormalize=bool(cfg.get("norm_topk_prob", mt == "qwen3_moe")))
+            if mt == "qwen2_moe" and cfg.get("shared_expert_intermediate_size", 0):
+                mi = kw["moe_intermediate_size"]
+                sh = int(cfg["shared_expert_intermediate_size"])
+                if sh % mi:
+                    raise ValueError("shared expert width must be a multiple of the routed expert width")
+                kw.update(num_shared_experts=sh // mi, shared_expert_gate=True, shared_expert_name="shared_expert")
+        if mt == "mixtral":
+            kw.update(ffn_types=["moe"] * L, num_experts=int(cfg.get("num_local_experts", 8)),
+                      experts_per_token=int(cfg.get("num_experts_per_tok", 2)),
+                      moe_intermediate_size=cfg.get("intermediate_size", 0), router="softmax", router_renormalize=True)
     elif arch == "qwen_hybrid":
         lt = cfg.get("layer_types")
         interval = cfg.get("full_attention_interval", 4)

@@ -93,6 +93,8 @@ class Decoder:
         lora = self._lora_for(batch, li)
         a = self._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.qkv.fmt], also_bf16=lora is not None)
         qkv = ops.linear(a, w.qkv)
+        if w.qkv_bias is not None:
+            qkv.add_(w.qkv_bias)
         qhs = 2 * D if c.attn_output_gate else D
         if lora is not None:
             # adapter deltas go straight into the fused q|k|v output, before norm / rope / cache write

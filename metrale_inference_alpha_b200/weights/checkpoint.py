@@ -21,5 +21,8 @@ def open_checkpoint(path, device="cpu"):
     if eng.exists():
         cfg = ModelConfig.from_json(eng.read_text())
     else:
-        cfg = from_hf_config(json.loads((p / "config.json").read_text()), name=p.name)
+        hf = json.loads((p / "config.json").read_text())
+        cfg = from_hf_config(hf, name=p.name)
+        from .remap import family_source
+        src = family_source(src, hf)          # Mixtral / fused-projection / wrapped-text-stack naming
     return cfg, src

@@ -103,6 +103,7 @@ class AttnW:
     o: QuantWeight = None
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
+    qkv_bias: Optional[torch.Tensor] = None   # bf16 [q | k | v rows of this rank]
     o_in_scale: float = 0.0   # NVFP4: calibrated global scale of o_proj's input (0 = per-token dynamic)
     heads: int = 0            # local q heads
     kv_heads: int = 0         # local kv heads
@@ -267,6 +268,12 @@ class Loader:
             hkv = c.num_kv_heads
         w = AttnW(finalize(ops.concat_weights([q, k, v])), finalize(o), heads=hq, kv_heads=hkv)
         w.o_in_scale = self.input_scale(f"{p}.o_proj")
+        if c.attn_bias and self.src.has(f"{p}.q_proj.bias"):
+            qb, kb, vb = (self.src.get(f"{p}.{n}_proj.bias").to(self.dev).to(torch.bfloat16) for n in "qkv")
+            if self.tp_size > 1:
+                qb = qb[lo * per_q:hi * per_q]
+                kb, vb = kb[klo * c.head_dim:khi * c.head_dim], vb[klo * c.head_dim:khi * c.head_dim]
+            w.qkv_bias = torch.cat([qb, kb, vb]).contiguous()
         if self.src.has(f"{p}.q_norm.weight"):
             w.q_norm, w.k_norm = self.vec(f"{p}.q_norm.weight"), self.vec(f"{p}.k_norm.weight")
         return w

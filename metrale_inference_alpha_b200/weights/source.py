@@ -142,6 +142,10 @@ class SyntheticSource(TensorSource):
         if c.qk_norm:
             self._vec(f"{p}.q_norm.weight", c.head_dim)
             self._vec(f"{p}.k_norm.weight", c.head_dim)
+        if c.attn_bias:
+            self._vec(f"{p}.q_proj.bias", c.q_size, "bias")
+            self._vec(f"{p}.k_proj.bias", c.kv_size, "bias")
+            self._vec(f"{p}.v_proj.bias", c.kv_size, "bias")
 
     def _ffn(self, p: str, inter: int, names=("gate_proj", "up_proj", "down_proj")):
         c = self.cfg
@@ -210,7 +214,7 @@ class SyntheticSource(TensorSource):
             for e in range(c.num_experts):
                 self._ffn(f"{p}.mlp.experts.{e}", c.moe_intermediate_size)
             if c.num_shared_experts:
-                sp = "shared_expert" if c.arch == "qwen_hybrid" else "shared_experts"
+                sp = c.shared_expert_name or ("shared_expert" if c.arch == "qwen_hybrid" else "shared_experts")
                 self._ffn(f"{p}.mlp.{sp}", c.moe_intermediate_size * c.num_shared_experts)
                 if c.shared_expert_gate:
                     self._lin(f"{p}.mlp.shared_expert_gate", 1, c.hidden_size, quant=False)

@@ -1,0 +1,183 @@
+"""Model families reached through config mapping and checkpoint-name dialects: Qwen2 (q/k/v bias),
+Qwen3-MoE, Qwen2-MoE (shared expert + gate), Mixtral (block_sparse_moe / w1 w3 w2), Phi-3 (fused
+qkv_proj / gate_up_proj), and text stacks wrapped under ``model.language_model.``. Each is checked
+against a straight-line fp32 restatement of the HF forward pass written here from the tensors of
+the checkpoint, not from the engine's decoder."""
+import json
+import math
+
+import pytest
+import torch
+from safetensors.torch import save_file
+
+from metrale_inference_alpha_b200.cache import KvCacheConfig, PagedKvCache
+from metrale_inference_alpha_b200.config.model_config import from_hf_config
+from metrale_inference_alpha_b200.engine.batch import ForwardBatch
+from metrale_inference_alpha_b200.models.decoder import Decoder, LayerCaches
+from metrale_inference_alpha_b200.weights.checkpoint import open_checkpoint
+from metrale_inference_alpha_b200.weights.loader import load_weights
+from metrale_inference_alpha_b200.weights.source import SyntheticSource
+
+BASE = dict(vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+            head_dim=32, intermediate_size=256, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=512,
+            tie_word_embeddings=False)
+
+FAMILIES = {
+    "qwen2": dict(BASE, model_type="qwen2"),
+    "qwen3_moe": dict(BASE, model_type="qwen3_moe", num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                      norm_topk_prob=True, decoder_sparse_step=1),
+    "qwen2_moe": dict(BASE, model_type="qwen2_moe", num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                      shared_expert_intermediate_size=128, norm_topk_prob=False, decoder_sparse_step=1),
+    "mixtral": dict(BASE, model_type="mixtral", num_local_experts=4, num_experts_per_tok=2, intermediate_size=64),
+    "phi3": dict(BASE, model_type="phi3"),
+}
+
+
+def _rms(x, w, eps):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+
+
+def _rope(x, pos, theta):
+    # x [T, H, D], rotate-half convention
+    D = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = pos[:, None].float() * inv[None, :]
+    cos, sin = torch.cat([ang.cos(), ang.cos()], -1)[:, None, :], torch.cat([ang.sin(), ang.sin()], -1)[:, None, :]
+    x1, x2 = x[..., :D // 2], x[..., D // 2:]
+    return x * cos + torch.cat([-x2, x1], -1) * sin
+
+
+def _oracle_logits(hf, get, has, toks):
+    """fp32 forward of the whole sequence, HF semantics; `get(name)` returns a canonical tensor."""
+    f = lambda n: get(n).float()
+    T = len(toks)
+    H, KV, D, eps = hf["num_attention_heads"], hf["num_key_value_heads"], hf["head_dim"], hf["rms_norm_eps"]
+    mt = hf["model_type"]
+    x = f("model.embed_tokens.weight")[torch.tensor(toks)]
+    pos = torch.arange(T)
+    for i in range(hf["num_hidden_layers"]):
+        p = f"model.layers.{i}"
+        a = _rms(x, f(f"{p}.input_layernorm.weight"), eps)
+        q, k, v = (a @ f(f"{p}.self_attn.{n}_proj.weight").T for n in "qkv")
+        if has(f"{p}.self_attn.q_proj.bias"):
+            q, k, v = (t + f(f"{p}.self_attn.{n}_proj.bias") for t, n in zip((q, k, v), "qkv"))
+        q, k, v = q.view(T, H, D), k.view(T, KV, D), v.view(T, KV, D)
+        if has(f"{p}.self_attn.q_norm.weight"):
+            q, k = _rms(q, f(f"{p}.self_attn.q_norm.weight"), eps), _rms(k, f(f"{p}.self_attn.k_norm.weight"), eps)
+        q, k = _rope(q, pos, hf["rope_theta"]), _rope(k, pos, hf["rope_theta"])
+        k, v = k.repeat_interleave(H // KV, 1), v.repeat_interleave(H // KV, 1)
+        s = torch.einsum("thd,shd->hts", q, k) / math.sqrt(D)
+        s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        o = torch.einsum("hts,shd->thd", s.softmax(-1), v).reshape(T, H * D)
+        x = x + o @ f(f"{p}.self_attn.o_proj.weight").T
+        a = _rms(x, f(f"{p}.post_attention_layernorm.weight"), eps)
+
+        def mlp(q_, inp):
+            g, u = inp @ f(f"{q_}.gate_proj.weight").T, inp @ f(f"{q_}.up_proj.weight").T
+            return (torch.nn.functional.silu(g) * u) @ f(f"{q_}.down_proj.weight").T
+        if has(f"{p}.mlp.gate.weight"):
+            probs = (a @ f(f"{p}.mlp.gate.weight").T).softmax(-1)
+            kx = hf["num_experts_per_tok"]
+            w, idx = probs.topk(kx, -1)
+            if mt == "mixtral" or hf.get("norm_topk_prob"):
+                w = w / w.sum(-1, keepdim=True)
+            y = torch.zeros_like(a)
+            for t in range(T):
+                for j in range(kx):
+                    y[t] += w[t, j] * mlp(f"{p}.mlp.experts.{int(idx[t, j])}", a[t:t + 1])[0]
+            if has(f"{p}.mlp.shared_expert.up_proj.weight"):
+                sh = mlp(f"{p}.mlp.shared_expert", a)
+                y = y + torch.sigmoid(a @ f(f"{p}.mlp.shared_expert_gate.weight").T) * sh
+            x = x + y
+        else:
+            x = x + mlp(f"{p}.mlp", a)
+    x = _rms(x, f("model.norm.weight"), eps)
+    return x[-1] @ f("lm_head.weight").T
+
+
+def _engine_logits(cfg, weights, toks):
+    dec = Decoder(cfg, weights)
+    kv = PagedKvCache(KvCacheConfig(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim), 16)
+    nb = (len(toks) + 15) // 16
+    b = ForwardBatch.build([dict(tokens=toks, start_pos=0, blocks=list(range(1, nb + 1)))], 16)
+    lg, _ = dec.forward(b, LayerCaches(cfg, kv=kv))
+    return lg[0].float()
+
+
+def _dialect(name: str, hf: dict, t: dict) -> dict:
+    """Canonical tensors -> the spelling a real checkpoint of the family uses."""
+    out = {}
+    if name == "mixtral":
+        ren = {"gate_proj": "w1", "up_proj": "w3", "down_proj": "w2"}
+        for n, v in t.items():
+            n = n.replace(".mlp.gate.", ".block_sparse_moe.gate.")
+            if ".mlp.experts." in n:
+                n = n.replace(".mlp.experts.", ".block_sparse_moe.experts.")
+                for a, b in ren.items():
+                    n = n.replace(a, b)
+            out[n] = v
+        return out
+    if name == "phi3":
+        for n, v in t.items():
+            if any(f".{x}_proj." in n for x in ("q", "k", "v", "gate", "up")):
+                continue
+            out[n] = v
+        for i in range(hf["num_hidden_layers"]):
+            p = f"model.layers.{i}"
+            out[f"{p}.self_attn.qkv_proj.weight"] = torch.cat([t[f"{p}.self_attn.{x}_proj.weight"] for x in "qkv"])
+            out[f"{p}.mlp.gate_up_proj.weight"] = torch.cat([t[f"{p}.mlp.{x}_proj.weight"] for x in ("gate", "up")])
+        return out
+    return dict(t)
+
+
+@pytest.mark.parametrize("name", list(FAMILIES))
+def test_family_matches_fp32_oracle_through_its_checkpoint_dialect(name, tmp_path):
+    hf = FAMILIES[name]
+    cfg = from_hf_config(hf, name=name)
+    syn = SyntheticSource(cfg, seed=11, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    if name in ("qwen2", "qwen2_moe"):
+        assert cfg.attn_bias and "model.layers.0.self_attn.q_proj.bias" in canon
+    tensors = {k: v.contiguous() for k, v in _dialect(name, hf, canon).items()}
+    if name == "qwen3_moe":                      # a text stack wrapped by a multimodal checkpoint
+        tensors = {(("model.language_model." + k[len("model."):]) if k.startswith("model.") else k): v
+                   for k, v in tensors.items()}
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    cfg2, src = open_checkpoint(tmp_path)
+    assert cfg2.arch == "dense_gqa" and cfg2.ffn_types == cfg.ffn_types
+    w = load_weights(cfg2, src)
+    toks = torch.randint(1, 512, (21,), generator=torch.Generator().manual_seed(5)).tolist()
+    got = _engine_logits(cfg2, w, toks)
+    want = _oracle_logits(hf, lambda n: canon[n], lambda n: n in canon, toks)
+    err = (got - want).abs().max().item()
+    assert err < 0.05 * want.abs().max().item() + 1e-3, err
+    assert int(got.argmax()) == int(want.argmax())
+
+
+def test_bias_is_not_silently_dropped():
+    hf = FAMILIES["qwen2"]
+    cfg = from_hf_config(hf)
+    syn = SyntheticSource(cfg, seed=3, std=0.05)
+    t = {n: syn.get(n) for n in syn.names()}
+    from metrale_inference_alpha_b200.weights.source import DictSource
+    toks = list(range(5, 20))
+    a = _engine_logits(cfg, load_weights(cfg, DictSource(dict(t))), toks)
+    for k in list(t):
+        if k.endswith("_proj.bias"):
+            t[k] = t[k] * 0 + 1.0
+    b = _engine_logits(cfg, load_weights(cfg, DictSource(t)), toks)
+    assert (a - b).abs().max() > 1e-3
+
+
+def test_config_mapping_of_the_new_families():
+    c = from_hf_config(dict(FAMILIES["qwen3_moe"], decoder_sparse_step=2, mlp_only_layers=[1]))
+    assert c.ffn_types == ["dense", "dense"] and c.qk_norm and not c.attn_bias
+    c = from_hf_config(FAMILIES["qwen2_moe"])
+    assert c.num_shared_experts == 2 and c.shared_expert_gate and not c.router_renormalize and c.attn_bias
+    c = from_hf_config(FAMILIES["mixtral"])
+    assert c.num_experts == 4 and c.experts_per_token == 2 and c.moe_intermediate_size == 64 and c.router_renormalize
+    with pytest.raises(ValueError):
+        from_hf_config(dict(FAMILIES["phi3"], rope_scaling={"type": "longrope"}))
+    c = from_hf_config(dict(FAMILIES["phi3"], partial_rotary_factor=0.5))
+    assert c.rotary_dim == 16
