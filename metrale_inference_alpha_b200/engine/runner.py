@@ -17,6 +17,7 @@ import numpy as np
 import torch
 
 from .. import ops
+from ..utils import nvtx
 from ..cache import KvCacheConfig, PagedKvCache, StatePool
 from ..config.model_config import ModelConfig
 from ..models.decoder import Decoder, LayerCaches, TpContext
@@ -380,6 +381,12 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ entry point
     def execute(self, plan: StepPlan) -> StepResult:
+        if nvtx.enabled():
+            with nvtx.range(f"step:{plan.kind}:{len(plan.items)}"):
+                return self._execute(plan)
+        return self._execute(plan)
+
+    def _execute(self, plan: StepPlan) -> StepResult:
         dev_cuda = self.device.type == "cuda"
         t0 = time.perf_counter()
         host_logits = any(i.seq.req.params.needs_host_logits or i.seq.req.params.has_penalties

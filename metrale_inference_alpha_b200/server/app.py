@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import contextlib
 import json
+import os
 import time
 import uuid
 from dataclasses import dataclass, field
@@ -42,6 +43,7 @@ class ServerConfig:
     request_timeout_s: float = 300.0
     telemetry: str = "basic"
     disable_thinking: bool = False
+    otlp_endpoint: str = ""             # OTLP/HTTP collector (also METRALE_OTLP_ENDPOINT)
     tool_grammar: bool = False          # constrain tool calls with a grammar even under tool_choice "auto"
 
 
@@ -87,8 +89,18 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
     @contextlib.asynccontextmanager
     async def lifespan(_app):
         aeng.start()
+        exporter = None
+        endpoint = cfg.otlp_endpoint or os.environ.get("METRALE_OTLP_ENDPOINT", "")
+        if endpoint and tel.enabled:
+            from ..utils.otlp import OtlpExporter
+            period = float(os.environ.get("METRALE_OTLP_PERIOD_S", "10"))
+            exporter = OtlpExporter(tel, endpoint, period, gauges=lambda: {
+                k: v for k, v in engine.stats().items() if isinstance(v, (int, float))}, service=cfg.model_name).start()
+            _app.state.otlp = exporter
         yield
         aeng.shutdown(drain_s=15.0)        # drain in-flight requests, then stop the scheduler thread
+        if exporter is not None:
+            exporter.stop()
 
     app = FastAPI(title="metrale b200 engine", lifespan=lifespan)
     tel = Telemetry(cfg.telemetry)

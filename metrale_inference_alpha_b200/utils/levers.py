@@ -16,6 +16,9 @@ LEVERS: Dict[str, str] = {
     "METRALE_DEBUG_SYNC_KERNELS": "1 = synchronise and check the status word after every step",
     "METRALE_KV_POISON": "1 = fill fresh KV blocks with NaN bytes",
     "METRALE_TELEMETRY": "off | basic | kernel",
+    "METRALE_NVTX": "1 = NVTX ranges around engine steps (for Nsight timelines)",
+    "METRALE_OTLP_ENDPOINT": "OTLP/HTTP collector base URL; set = push metrics every METRALE_OTLP_PERIOD_S (default 10)",
+    "METRALE_OTLP_PERIOD_S": "seconds between OTLP pushes",
     "METRALE_NATIVE_RUNTIME": "0 = keep allocator / prefix index / JSON grammar on the Python implementations",
     "METRALE_NO_FUSED_COLLECTIVES": "1 = NCCL collectives after plain GEMMs",
 }

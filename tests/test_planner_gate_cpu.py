@@ -83,3 +83,110 @@ def test_launch_trace_records_and_diffs():
     assert a == ["gemm", "row_op"] and _native.diff_traces(a, b) == (1, "row_op", "paged_attention")
     assert _native.diff_traces(a, a) is None and _native.diff_traces(a, a[:1]) == (1, "row_op", None)
     _native.check(0, "not recorded")
+
+
+# ----------------------------------------------------------------------------- OTLP export
+def test_otlp_body_and_push_to_a_local_collector():
+    import http.server
+    import json as _json
+    import threading
+
+    from metrale_inference_alpha_b200.utils.otlp import OtlpExporter, metrics_body
+    from metrale_inference_alpha_b200.utils.telemetry import Telemetry
+    tel = Telemetry("basic")
+    tel.inc("decode_tokens", 41)
+    tel.inc("decode_tokens")
+    tel.inc("energy_joules", 0.5)
+    tel.set("kv_blocks_free", 17)
+    for ms in (0.5, 3, 3, 40000):
+        tel.observe_ms("step", ms)
+    body = metrics_body(tel, {"running": 2, "name": "skip-me"}, now_ns=123)
+    ms = {m["name"]: m for m in body["resourceMetrics"][0]["scopeMetrics"][0]["metrics"]}
+    assert ms["metrale.decode_tokens"]["sum"]["dataPoints"][0]["asInt"] == "42"
+    assert ms["metrale.decode_tokens"]["sum"]["isMonotonic"] and ms["metrale.decode_tokens"]["unit"] == "{token}"
+    assert ms["metrale.energy_joules"]["sum"]["dataPoints"][0]["asDouble"] == 0.5
+    assert ms["metrale.kv_blocks_free"]["gauge"]["dataPoints"][0]["asDouble"] == 17.0
+    assert ms["metrale.running"]["gauge"]["dataPoints"][0]["timeUnixNano"] == "123" and "metrale.name" not in ms
+    h = ms["metrale.step"]["histogram"]["dataPoints"][0]
+    assert h["count"] == "4" and len(h["bucketCounts"]) == len(h["explicitBounds"]) + 1
+    assert h["bucketCounts"][0] == "1" and h["bucketCounts"][-1] == "1" and abs(h["sum"] - 40006.5) < 1e-6
+
+    got = []
+
+    class H(http.server.BaseHTTPRequestHandler):
+        def do_POST(self):
+            got.append((self.path, _json.loads(self.rfile.read(int(self.headers["Content-Length"])))))
+            self.send_response(200)
+            self.end_headers()
+
+        def log_message(self, *a):
+            pass
+    srv = http.server.HTTPServer(("127.0.0.1", 0), H)
+    t = threading.Thread(target=srv.serve_forever, daemon=True)
+    t.start()
+    try:
+        ex = OtlpExporter(tel, f"http://127.0.0.1:{srv.server_port}", period_s=0.05).start()
+        import time as _t
+        end = _t.time() + 5
+        while not got and _t.time() < end:
+            _t.sleep(0.02)
+        ex.stop()
+        assert got and got[0][0] == "/v1/metrics" and ex.pushed >= 2 and ex.failed == 0
+        assert got[-1][1]["resourceMetrics"][0]["resource"]["attributes"][0]["value"]["stringValue"] == "metrale-b200"
+    finally:
+        srv.shutdown()
+    dead = OtlpExporter(tel, "http://127.0.0.1:9", period_s=60)
+    assert dead.export_once() is False and dead.failed == 1          # a dead collector never raises
+
+
+# ----------------------------------------------------------------------------- change ledger
+def test_ledger_journey_dedup_graph_and_mergeability(tmp_path):
+    from metrale_inference_alpha_b200.bench import ledger as L
+    p = L.path_for(tmp_path, 42)
+    ev = [
+        L.Event.state(42, "aaa", "open", at=1),
+        L.Event.gate(42, "aaa", "unit-tests", "pass", run_id="r1", at=2),
+        L.Event.gate(42, "aaa", "bench-gate", "fail", invalidated_by=["kernel-closure"], detail="-7% tok/s", run_id="r1", at=3),
+        L.Event.gate(42, "aaa", "unit-tests", "pass", run_id="r1", at=2),           # CI retry replays the line
+        L.Event.measurement(42, "bbb", "decode_c128", {"tok_s": 14240.0, "ttft_ms": 506.0}, run_id="r2", at=5),
+        L.Event.gate(42, "bbb", "unit-tests", "pass", run_id="r2", at=6),
+        L.Event.gate(42, "bbb", "bench-gate", "pass", invalidated_by=["kernel-closure"], run_id="r2", at=7),
+        L.Event.category(42, "bbb", "perf", "confirmed", at=8),
+    ]
+    for e in ev:
+        L.append(p, e)
+    j = L.read_all(p)
+    assert len(j.events) == 8 and j.events[4].payload["metrics"]["tok_s"] == 14240.0
+    assert L.Event.from_json(ev[2].to_json()).identity() == ev[2].identity()
+    d = j.deduplicated()
+    assert len(d.events) == 7
+    assert [e.payload["verdict"] for e in d.gate_history("bench-gate")] == ["fail", "pass"]
+    ok, why = d.mergeable(["unit-tests", "bench-gate"])
+    assert ok and not why
+    ok, why = d.mergeable(["unit-tests", "bench-gate", "signed-record"])
+    assert not ok and "signed-record" in why[0]
+    # a later kernel-closure event invalidates the bench gate that named it
+    L.append(p, L.Event.gate(42, "bbb", "kernel-closure", "pass", run_id="r3", at=9))
+    ok, why = L.read_all(p).deduplicated().mergeable(["unit-tests", "bench-gate"])
+    assert not ok and "invalidated" in why[0]
+    g = L.materialize(d)
+    commits = [n for n in g.nodes if n["label"] == "commit"]
+    assert [c["sha"] for c in commits] == ["aaa", "bbb"]
+    assert len(g.out(0, "observed")) == 3 and len(g.out(1, "observed")) == 4
+    assert sum(1 for e in g.edges if e[2] == "precedes") == 6
+    with pytest.raises(ValueError):
+        L.Event.gate(1, "x", "g", "maybe")
+    p.write_text(p.read_text() + "{not json\n")
+    with pytest.raises(ValueError, match="line"):
+        L.read_all(p)
+
+
+def test_nvtx_ranges_are_noops_without_cuda(monkeypatch):
+    from metrale_inference_alpha_b200.utils import nvtx
+    monkeypatch.setattr(nvtx, "_enabled", None)
+    monkeypatch.setenv("METRALE_NVTX", "1")
+    with nvtx.range("x"):
+        nvtx.mark("y")
+    import torch
+    assert nvtx.enabled() == torch.cuda.is_available()
+    monkeypatch.setattr(nvtx, "_enabled", None)
