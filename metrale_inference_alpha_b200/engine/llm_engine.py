@@ -58,6 +58,8 @@ class EngineArgs:
     preempt_mode: str = "recompute"                    # recompute | swap (KV + state to host memory / swap files)
     swap_space_bytes: int = 8 << 30
     swap_dir: Optional[str] = None
+    kv_cache_dtype: str = "auto"                       # auto (the model config's) | bf16 | fp8
+    oom_guard_mb: int = 4096                           # device memory left unclaimed when sizing the KV pool
 
 
 class LLMEngine:
@@ -73,6 +75,11 @@ class LLMEngine:
                 cfg, source = open_checkpoint(cfg, device=args.device)
             else:
                 cfg = cfg_preset(cfg)
+        if args.kv_cache_dtype not in ("auto", cfg.kv_dtype):
+            import dataclasses
+            if args.kv_cache_dtype not in ("bf16", "fp8"):
+                raise ValueError(f"kv_cache_dtype must be auto | bf16 | fp8, not {args.kv_cache_dtype!r}")
+            cfg = dataclasses.replace(cfg, kv_dtype=args.kv_cache_dtype)
         self.cfg: ModelConfig = cfg
         self.fault = FaultLatch()
         t0 = time.time()
@@ -86,7 +93,8 @@ class LLMEngine:
             policy=args.scheduler, tbt_deadline_ms=args.tbt_deadline_ms,
             enable_prefix_caching=args.enable_prefix_caching, request_timeout_s=args.request_timeout_s)
         blocks = args.num_kv_blocks or plan_kv_blocks(cfg, self.weights, args.device, args.block_size,
-                                                      args.gpu_memory_utilization)
+                                                      args.gpu_memory_utilization,
+                                                      reserve_bytes=(2 << 30) + (args.oom_guard_mb << 20))
         # never more than every sequence at full length needs (plus headroom for the prefix cache)
         cap = (self.sched_cfg.max_model_len // args.block_size + 1) * args.max_num_seqs * 2 + 64
         blocks = min(blocks, cap)

@@ -58,8 +58,10 @@ class TpContext:
 
 
 class Decoder:
-    def __init__(self, cfg: ModelConfig, weights: ModelW, tp: Optional[TpContext] = None, device="cpu"):
+    def __init__(self, cfg: ModelConfig, weights: ModelW, tp: Optional[TpContext] = None, device=None):
         self.cfg, self.w, self.tp = cfg, weights, tp or TpContext()
+        if device is None:                 # tables live where the weights live
+            device = weights.embed.device if getattr(weights, "embed", None) is not None else "cpu"
         self.device = torch.device(device)
         rot = cfg.rotary_dim
         self.cos = self.sin = None

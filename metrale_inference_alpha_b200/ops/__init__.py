@@ -28,7 +28,13 @@ launch_count = 0  # kernels launched through this module (bench.py reports it)
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
-    return None if t is None else t.data_ptr()
+    """Device address for a kernel argument. Every caller is a CUDA launch, so a host tensor here
+    is a wiring error (it would fault on the device): refuse it on the host instead."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError(f"CUDA kernel argument lives on {t.device} (shape {tuple(t.shape)}, {t.dtype})")
+    return t.data_ptr()
 
 
 def _stream() -> int:

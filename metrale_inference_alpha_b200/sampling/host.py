@@ -77,6 +77,22 @@ def lz_penalty(tokens: List[int], strength: float, window: int = 2048) -> dict:
     return {best_next: strength * best_len} if best_len >= 4 else {}
 
 
+def forced_think_close(out_tokens: List[int], budget: int, end_ids: List[int]):
+    """Token to force so that the reasoning block closes, or None: nothing is forced before
+    `budget` output tokens, nor once the closing marker has appeared; after the budget the
+    marker is emitted token by token (resuming a partly written marker)."""
+    n = len(end_ids)
+    if budget <= 0 or n == 0 or len(out_tokens) < budget:
+        return None
+    for i in range(len(out_tokens) - n + 1):
+        if out_tokens[i:i + n] == end_ids:
+            return None
+    k = min(n - 1, len(out_tokens) - budget)
+    while k > 0 and out_tokens[-k:] != end_ids[:k]:
+        k -= 1
+    return end_ids[k]
+
+
 def sample_rows(runner, plan, logits: torch.Tensor) -> Tuple[List[List[int]], List[List[float]]]:
     """logits: fp32 [R, V], one row per sampled position in plan order."""
     items = [it for it in plan.items if it.sample]
@@ -123,6 +139,12 @@ def sample_rows(runner, plan, logits: torch.Tensor) -> Tuple[List[List[int]], Li
                     p.grammar.advance(d)
                     spec_ahead[id(it)] = j + 1
             logits[r].masked_fill_(~mask.to(dev), float("-inf"))
+        if p.thinking_budget > 0 and p.think_end_ids and it.verify == 0:
+            force = forced_think_close(it.seq.tokens[it.seq.prompt_len:], p.thinking_budget, p.think_end_ids)
+            if force is not None and force < logits.shape[1] and torch.isfinite(logits[r, force]):
+                keep = logits[r, force].clone()
+                logits[r].fill_(float("-inf"))
+                logits[r, force] = keep
         if runner.logit_processor is not None:
             logits[r] = runner.logit_processor(it.seq, logits[r])
         if p.top_n_sigma > 0 and p.temperature > 0:

@@ -38,6 +38,10 @@ class SamplingParams:
     timeout_s: float = 0.0
     grammar: Optional[object] = None    # constrained decoding matcher (server/grammar.py)
     adapter: Optional[str] = None       # LoRA adapter name (engine.load_adapter)
+    # reasoning budget: once `thinking_budget` output tokens passed without the closing marker
+    # `think_end_ids`, the sampler forces that marker token by token (0 = no limit)
+    thinking_budget: int = 0
+    think_end_ids: List[int] = field(default_factory=list)
 
     @property
     def greedy(self) -> bool:
@@ -47,7 +51,8 @@ class SamplingParams:
     def needs_host_logits(self) -> bool:
         """True when plain device argmax / device sampling cannot serve the request."""
         return (bool(self.logit_bias) or self.top_n_sigma > 0 or self.grammar is not None or self.top_logprobs > 0
-                or self.dry_multiplier > 0 or self.lz_penalty > 0)
+                or self.dry_multiplier > 0 or self.lz_penalty > 0
+                or (self.thinking_budget > 0 and bool(self.think_end_ids)))
 
     @property
     def has_penalties(self) -> bool:

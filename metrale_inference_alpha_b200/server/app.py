@@ -43,6 +43,11 @@ class ServerConfig:
     request_timeout_s: float = 300.0
     telemetry: str = "basic"
     disable_thinking: bool = False
+    default_top_n_sigma: float = 0.0    # sampling defaults for requests that do not set the field
+    default_min_p: float = 0.0
+    max_thinking_budget: int = 0        # cap (and default) of a request's thinking_token_budget; 0 = none
+    content_loop_watchdog: float = 0.0  # > 0: LZ loop penalty applied when the request sets none
+    dump_dir: str = ""                  # write every request / response pair as JSON files here
     otlp_endpoint: str = ""             # OTLP/HTTP collector (also METRALE_OTLP_ENDPOINT)
     tool_grammar: bool = False          # constrain tool calls with a grammar even under tool_choice "auto"
 
@@ -68,14 +73,15 @@ def _sampling_from(body: Dict[str, Any], cfg: ServerConfig, max_key="max_tokens"
         max_tokens=int(mt), min_tokens=int(body.get("min_tokens") or 0),
         temperature=float(body.get("temperature", 1.0) if body.get("temperature") is not None else 1.0),
         top_k=int(body.get("top_k") or 0), top_p=float(body.get("top_p") or 1.0),
-        min_p=float(body.get("min_p") or 0.0), top_n_sigma=float(body.get("top_n_sigma") or 0.0),
+        min_p=float(body["min_p"] if body.get("min_p") is not None else cfg.default_min_p),
+        top_n_sigma=float(body["top_n_sigma"] if body.get("top_n_sigma") is not None else cfg.default_top_n_sigma),
         repetition_penalty=float(body.get("repetition_penalty") or 1.0),
         presence_penalty=float(body.get("presence_penalty") or 0.0),
         frequency_penalty=float(body.get("frequency_penalty") or 0.0),
         dry_multiplier=float(body.get("dry_multiplier") or 0.0), dry_base=float(body.get("dry_base") or 1.75),
         dry_allowed_length=int(body.get("dry_allowed_length") or 2),
         lz_penalty=float((body.get("repetition_detection") or {}).get("penalty", 0.0)
-                         if isinstance(body.get("repetition_detection"), dict) else 0.0),
+                         if isinstance(body.get("repetition_detection"), dict) else cfg.content_loop_watchdog),
         logit_bias={int(k): float(v) for k, v in (body.get("logit_bias") or {}).items()},
         seed=body.get("seed"), stop=list(stop), logprobs=bool(body.get("logprobs")),
         top_logprobs=int(body.get("top_logprobs") or 0),
@@ -109,6 +115,11 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
     renderer = ChatRenderer(getattr(tokenizer, "chat_template", None))
     app.state.engine, app.state.async_engine, app.state.telemetry = engine, aeng, tel
     eos = getattr(tokenizer, "eos_token_id", None)
+    _close = {"think": "</think>", "mistral": "[/THINK]", "gemma4": "<channel|>"}.get(cfg.reasoning_format, "</think>")
+    try:
+        think_end_ids = list(tokenizer.encode(_close))
+    except Exception:
+        think_end_ids = []
     engine.args.eos_token_id = engine.args.eos_token_id if engine.args.eos_token_id is not None else eos
 
     @app.middleware("http")
@@ -125,6 +136,9 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
                 return JSONResponse({"error": {"message": "invalid API key", "type": "authentication_error"}}, 401)
             if not limiter.allow(key or (request.client.host if request.client else "anon")):
                 return JSONResponse({"error": {"message": "rate limit exceeded", "type": "rate_limit_error"}}, 429)
+        dump_body = None
+        if cfg.dump_dir and request.method == "POST":
+            dump_body = await request.body()         # cached by the request: the handler reads it again
         try:
             resp = await call_next(request)
         except Exception as e:                      # handler panic -> 500, server stays up
@@ -132,7 +146,26 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
             return JSONResponse({"error": {"message": f"{type(e).__name__}: {e}", "type": "internal_error"}}, 500)
         tel.inc("http_requests")
         tel.observe_ms("http_latency", (time.perf_counter() - t0) * 1e3)
+        if dump_body is not None:
+            _dump_request(path, dump_body, resp.status_code, (time.perf_counter() - t0) * 1e3)
         return resp
+
+    _dump_seq = [0]
+
+    def _dump_request(path: str, body: bytes, status: int, ms: float) -> None:
+        """One JSON file per POST: path, status, latency and the request body as sent."""
+        try:
+            os.makedirs(cfg.dump_dir, exist_ok=True)
+            _dump_seq[0] += 1
+            try:
+                parsed = json.loads(body)
+            except ValueError:
+                parsed = body.decode("utf-8", "replace")
+            name = f"{int(time.time() * 1e3):013d}-{_dump_seq[0]:06d}{path.replace('/', '_')}.json"
+            with open(os.path.join(cfg.dump_dir, name), "w") as f:
+                json.dump({"path": path, "status": status, "latency_ms": round(ms, 3), "request": parsed}, f)
+        except OSError:
+            tel.inc("dump_errors")
 
     # ------------------------------------------------------------------ plumbing
     def _job_from_chat(body: Dict[str, Any], messages, system=None, tools=None) -> _ChatJob:
@@ -165,6 +198,13 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         except ValueError as e:             # GrammarError: the schema / pattern / grammar does not compile
             raise HTTPException(400, f"invalid grammar: {e}")
         sp.adapter = body.get("adapter")
+        if thinking and think_end_ids:
+            th = body.get("thinking") if isinstance(body.get("thinking"), dict) else {}
+            want = body.get("thinking_token_budget") or th.get("budget_tokens") or 0
+            budget = int(want or cfg.max_thinking_budget)
+            if cfg.max_thinking_budget:
+                budget = min(budget, cfg.max_thinking_budget)
+            sp.thinking_budget, sp.think_end_ids = budget, list(think_end_ids)
         return _ChatJob(ids, sp, tools, thinking, bool(body.get("logprobs")), bool(body.get("return_token_ids")))
 
     async def _collect(job: _ChatJob):

@@ -67,6 +67,28 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--lora-adapter", action="append", default=[], metavar="NAME=DIR", help="PEFT adapter to serve")
     s.add_argument("--max-loras", type=int, default=8)
     s.add_argument("--max-lora-rank", type=int, default=16)
+    s.add_argument("--bind", default=None, metavar="HOST:PORT", help="listen address (overrides --host / --port)")
+    s.add_argument("--model-name", default=None, help="alias of --served-model-name")
+    s.add_argument("--max-seq-len", type=int, default=None, help="alias of --max-model-len")
+    s.add_argument("--max-batch-size", type=int, default=None, help="alias of --max-num-seqs")
+    s.add_argument("--request-timeout", type=float, default=None, help="alias of --request-timeout-s (seconds)")
+    s.add_argument("--auth-token", action="append", default=[], help="accepted bearer token (repeatable; same as --api-key)")
+    s.add_argument("--auth-tokens-file", default=None, help="file with one accepted token per line")
+    s.add_argument("--require-auth", action="store_true", help="refuse to start without at least one token")
+    s.add_argument("--default-top-n-sigma", type=float, default=0.0)
+    s.add_argument("--default-min-p", type=float, default=0.0)
+    s.add_argument("--max-thinking-budget", type=int, default=0, help="cap and default of thinking_token_budget (0 = none)")
+    s.add_argument("--content-loop-watchdog", type=float, default=0.0, metavar="PENALTY",
+                   help="> 0: loop penalty for requests that set no repetition_detection")
+    s.add_argument("--dump", default="", metavar="DIR", help="write every POST request as a JSON file into DIR")
+    s.add_argument("--otlp-endpoint", default="", help="OTLP/HTTP collector base URL for metric pushes")
+    s.add_argument("--warmup-prompt", default=None, help="generate from this prompt once before listening")
+    s.add_argument("--ngram-speculative", action="store_true", help="same as --speculative ngram")
+    s.add_argument("--self-speculative", action="store_true", help="same as --speculative mtp")
+    s.add_argument("--master-addr", default=None, help="rendezvous address when ranks are started by hand")
+    s.add_argument("--master-port", type=int, default=None)
+    s.add_argument("--rank", type=int, default=None)
+    s.add_argument("--world-size", type=int, default=None)
     s.add_argument("--swap-space-gb", type=float, default=0.0,
                    help="> 0: preempted sequences are swapped to host memory (then swap files) instead of recomputed")
 
@@ -157,11 +179,46 @@ def _init_ranks(eargs):
     return tp, ControlPlane.create()
 
 
+def apply_aliases(ns) -> None:
+    """Folds the alias flags into the fields the engine and the server read, and checks the
+    authentication options."""
+    if ns.bind:
+        host, _, port = ns.bind.rpartition(":")
+        ns.host, ns.port = (host or ns.host), int(port)
+    if ns.model_name and not ns.served_model_name:
+        ns.served_model_name = ns.model_name
+    if ns.max_seq_len:
+        ns.max_model_len = ns.max_seq_len
+    if ns.max_batch_size:
+        ns.max_num_seqs = ns.max_batch_size
+    if ns.request_timeout:
+        ns.request_timeout_s = ns.request_timeout
+    if ns.ngram_speculative:
+        ns.speculative = "ngram"
+    if ns.self_speculative:
+        ns.speculative = "mtp"
+    tokens = list(ns.api_key) + list(ns.auth_token)
+    if ns.auth_tokens_file:
+        with open(ns.auth_tokens_file) as f:
+            tokens += [ln.strip() for ln in f if ln.strip() and not ln.startswith("#")]
+    ns.api_key = tokens
+    if ns.require_auth and not tokens:
+        raise SystemExit("--require-auth: no token given (--auth-token / --auth-tokens-file / --api-key)")
+    for flag, env in (("master_addr", "MASTER_ADDR"), ("master_port", "MASTER_PORT"), ("rank", "RANK"),
+                      ("world_size", "WORLD_SIZE")):
+        v = getattr(ns, flag)
+        if v is not None:
+            os.environ[env] = str(v)
+    if ns.rank is not None:
+        os.environ.setdefault("LOCAL_RANK", str(ns.rank))
+
+
 def serve(ns) -> None:
     import uvicorn
     from ..engine.llm_engine import LLMEngine
     from .app import ServerConfig, create_app
     from .tokenizer import load_tokenizer
+    apply_aliases(ns)
     eargs = _engine_args(ns)
     if ns.swap_space_gb > 0:
         eargs.preempt_mode, eargs.swap_space_bytes = "swap", int(ns.swap_space_gb * (1 << 30))
@@ -181,7 +238,13 @@ def serve(ns) -> None:
         engine.load_adapter(name, path, ns.max_loras, ns.max_lora_rank)
     tok_dir = ns.tokenizer or (eargs.model if isinstance(eargs.model, str) and os.path.isdir(eargs.model) else None)
     tokenizer = load_tokenizer(tok_dir, engine.cfg.vocab_size)
+    if ns.warmup_prompt:
+        from ..sampling.params import SamplingParams
+        engine.generate([tokenizer.encode(ns.warmup_prompt)], SamplingParams(max_tokens=8, temperature=0.0))
     cfg = ServerConfig(model_name=ns.served_model_name or str(ns.model), auth_tokens=ns.api_key,
+                       default_top_n_sigma=ns.default_top_n_sigma, default_min_p=ns.default_min_p,
+                       max_thinking_budget=ns.max_thinking_budget, content_loop_watchdog=ns.content_loop_watchdog,
+                       dump_dir=ns.dump, otlp_endpoint=ns.otlp_endpoint,
                        rate_per_s=ns.rate_limit, tool_call_parser=ns.tool_call_parser, tool_grammar=getattr(ns, "tool_grammar", False),
                        reasoning_format=ns.reasoning_format, default_max_tokens=ns.default_max_tokens,
                        tool_max_tokens=ns.tool_max_tokens,

@@ -181,3 +181,33 @@ def test_config_mapping_of_the_new_families():
         from_hf_config(dict(FAMILIES["phi3"], rope_scaling={"type": "longrope"}))
     c = from_hf_config(dict(FAMILIES["phi3"], partial_rotary_factor=0.5))
     assert c.rotary_dim == 16
+
+
+GPU_BASE = dict(BASE, hidden_size=256, head_dim=64, intermediate_size=512, vocab_size=1024)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,extra", [
+    ("qwen2", {}),
+    ("qwen2_moe", dict(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+                       shared_expert_intermediate_size=256, norm_topk_prob=False, decoder_sparse_step=1)),
+    ("mixtral", dict(num_local_experts=4, num_experts_per_tok=2, intermediate_size=128)),
+])
+def test_family_on_gpu_matches_fp32_oracle(name, extra):
+    """The same oracle against the CUDA decoder (bf16 weights through the tcgen05 GEMMs, the
+    grouped expert GEMMs and the paged attention kernel)."""
+    hf = dict(GPU_BASE, model_type=name, **extra)
+    cfg = from_hf_config(hf, name=name)
+    syn = SyntheticSource(cfg, seed=11, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    w = load_weights(cfg, syn, device="cuda:0")
+    toks = torch.randint(1, 1024, (37,), generator=torch.Generator().manual_seed(5)).tolist()
+    dec = Decoder(cfg, w)
+    kv = PagedKvCache(KvCacheConfig(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim), 16, device="cuda:0")
+    nb = (len(toks) + 15) // 16
+    b = ForwardBatch.build([dict(tokens=toks, start_pos=0, blocks=list(range(1, nb + 1)))], 16, device="cuda:0")
+    lg, _ = dec.forward(b, LayerCaches(cfg, kv=kv))
+    got = lg[0].float().cpu()
+    want = _oracle_logits(hf, lambda n: canon[n], lambda n: n in canon, toks)
+    err = (got - want).abs().max().item()
+    assert err < 0.06 * want.abs().max().item() + 1e-2, err

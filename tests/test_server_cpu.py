@@ -431,3 +431,54 @@ def test_nvml_sampler_against_a_fake_binding():
     assert out["energy_j"] == pytest.approx(500.0 + 700.0) and out["joules_per_token"] == pytest.approx(12.0)
     assert out["reasons"] == ["sw_power_cap"] and out["rejected"] is False and out["sm_mhz_median"] == 1965
     assert decode_reasons(0x8 | 0x40) == ["hw_slowdown", "hw_thermal_slowdown"]
+
+
+def test_forced_think_close_and_budget_over_http(tmp_path):
+    from metrale_inference_alpha_b200.sampling.host import forced_think_close
+    end = [7, 8, 9]
+    assert forced_think_close([1, 2], 4, end) is None                     # under budget
+    assert forced_think_close([1, 2, 3, 4], 4, end) == 7
+    assert forced_think_close([1, 2, 3, 4, 7], 4, end) == 8               # resumes a partly written marker
+    assert forced_think_close([1, 2, 3, 4, 7, 8], 4, end) == 9
+    assert forced_think_close([1, 2, 3, 4, 7, 8, 9, 5, 5], 4, end) is None  # closed: free again
+    assert forced_think_close([7, 8, 9, 1, 2, 3], 4, end) is None
+    assert forced_think_close([1, 2, 3, 7], 4, end) == 7                  # a 7 before the budget is not progress
+    from fastapi.testclient import TestClient
+    from metrale_inference_alpha_b200.server.app import ServerConfig, create_app
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=512))
+    tok = load_tokenizer(None, eng.cfg.vocab_size)
+    cfg = ServerConfig(model_name="tiny", max_thinking_budget=6, dump_dir=str(tmp_path / "dump"),
+                       default_min_p=0.05, content_loop_watchdog=0.5)
+    with TestClient(create_app(eng, tok, cfg)) as c:
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "think"}], "max_tokens": 40,
+                                                 "temperature": 0, "enable_thinking": True,
+                                                 "thinking_token_budget": 1000, "return_token_ids": True}).json()
+        ids = r["choices"][0]["token_ids"]
+        close = tok.encode("</think>")
+        assert ids[6:6 + len(close)] == close                             # the server cap (6) beat the request's 1000
+        assert "</think>" not in r["choices"][0]["message"].get("content", "")
+        assert r["choices"][0]["message"].get("reasoning_content")
+    dumps = sorted((tmp_path / "dump").glob("*.json"))
+    assert len(dumps) == 1
+    d = json.loads(dumps[0].read_text())
+    assert d["path"] == "/v1/chat/completions" and d["status"] == 200 and d["request"]["thinking_token_budget"] == 1000
+
+
+def test_serve_alias_flags(tmp_path):
+    from metrale_inference_alpha_b200.server.cli import apply_aliases, build_parser
+    tf = tmp_path / "tokens.txt"
+    tf.write_text("# comment\nalpha\n\nbeta\n")
+    ns = build_parser().parse_args(["serve", "--bind", "0.0.0.0:9001", "--model-name", "m", "--max-seq-len", "777",
+                                    "--max-batch-size", "9", "--request-timeout", "12", "--auth-token", "gamma",
+                                    "--auth-tokens-file", str(tf), "--require-auth", "--ngram-speculative",
+                                    "--kv-cache-dtype", "fp8", "--oom-guard-mb", "1024"])
+    apply_aliases(ns)
+    assert (ns.host, ns.port, ns.served_model_name) == ("0.0.0.0", 9001, "m")
+    assert (ns.max_model_len, ns.max_num_seqs, ns.request_timeout_s, ns.speculative) == (777, 9, 12.0, "ngram")
+    assert ns.api_key == ["gamma", "alpha", "beta"] and ns.kv_cache_dtype == "fp8" and ns.oom_guard_mb == 1024
+    ns = build_parser().parse_args(["serve", "--require-auth"])
+    with pytest.raises(SystemExit):
+        apply_aliases(ns)
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=2, max_model_len=128, kv_cache_dtype="fp8"))
+    assert eng.cfg.kv_dtype == "fp8"
+    assert len(eng.generate([[1, 2, 3]], __import__("metrale_inference_alpha_b200").sampling.params.SamplingParams(max_tokens=3))[0].output_ids) == 3
