@@ -96,6 +96,9 @@ class LoraManager:
     def bytes(self) -> int:
         return sum(t.numel() * 2 for t in self.A.values()) + sum(t.numel() * 2 for t in self.B.values())
 
+    def names(self) -> List[str]:
+        return sorted(self.slots)
+
     def slot_of(self, name: Optional[str]) -> int:
         return -1 if not name else self.slots[name]
 

@@ -9,11 +9,13 @@ shared IR (``crates/server/src/main_modules/serve_router.rs:44-141``, ``api/chat
 """
 from __future__ import annotations
 
+import asyncio
 import contextlib
 import json
 import os
 import time
 import uuid
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
 
@@ -27,6 +29,7 @@ from .engine_loop import AsyncEngine
 from .grammar import grammar_for_response_format, tool_call_grammar
 from .ratelimit import RateLimiter
 from .reasoning_parser import ReasoningParser
+from .conversation_store import ConversationStore
 from .response_store import ResponseStore
 from .tool_parser import StreamingToolDetector, parse_tool_calls
 
@@ -112,6 +115,9 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
     tel = Telemetry(cfg.telemetry)
     limiter = RateLimiter(cfg.rate_per_s)
     store = ResponseStore()
+    conversations = ConversationStore()
+    stored_completions: "OrderedDict[str, dict]" = OrderedDict()
+    running_responses: Dict[str, Any] = {}
     renderer = ChatRenderer(getattr(tokenizer, "chat_template", None))
     app.state.engine, app.state.async_engine, app.state.telemetry = engine, aeng, tel
     eos = getattr(tokenizer, "eos_token_id", None)
@@ -136,6 +142,10 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
                 return JSONResponse({"error": {"message": "invalid API key", "type": "authentication_error"}}, 401)
             if not limiter.allow(key or (request.client.host if request.client else "anon")):
                 return JSONResponse({"error": {"message": "rate limit exceeded", "type": "rate_limit_error"}}, 429)
+        limit = int(os.environ.get("METRALE_MAX_BODY_BYTES", "") or 32 << 20)
+        clen = request.headers.get("content-length")
+        if clen and clen.isdigit() and int(clen) > limit:
+            return JSONResponse({"error": {"message": f"request body exceeds {limit} bytes", "type": "invalid_request_error"}}, 413)
         dump_body = None
         if cfg.dump_dir and request.method == "POST":
             dump_body = await request.body()         # cached by the request: the handler reads it again
@@ -197,7 +207,7 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
                     sp.grammar = TokenMatcher(tg, tokenizer, eos)
         except ValueError as e:             # GrammarError: the schema / pattern / grammar does not compile
             raise HTTPException(400, f"invalid grammar: {e}")
-        sp.adapter = body.get("adapter")
+        sp.adapter = body.get("adapter") or getattr(app.state, "active_adapter", None)
         if thinking and think_end_ids:
             th = body.get("thinking") if isinstance(body.get("thinking"), dict) else {}
             want = body.get("thinking_token_budget") or th.get("budget_tokens") or 0
@@ -259,8 +269,13 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
             choice = {"index": 0, "message": msg, "finish_reason": reason, "logprobs": _lp_block(ids, lps)}
             if job.return_token_ids:
                 choice["token_ids"] = ids
-            return {"id": rid, "object": "chat.completion", "created": created, "model": cfg.model_name,
-                    "choices": [choice], "usage": usage}
+            out = {"id": rid, "object": "chat.completion", "created": created, "model": cfg.model_name,
+                   "choices": [choice], "usage": usage}
+            if body.get("store"):
+                stored_completions[rid] = dict(out, metadata=body.get("metadata") or {})
+                while len(stored_completions) > 1024:
+                    stored_completions.popitem(last=False)
+            return out
 
         include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
 
@@ -362,6 +377,27 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
             raise HTTPException(404, "unknown response id")
         return {"id": response_id, "object": "response.deleted", "deleted": True}
 
+    @app.get("/v1/responses/{response_id}/input_items")
+    async def response_input_items(response_id: str):
+        r = store.get(response_id)
+        if r is None:
+            raise HTTPException(404, "unknown response id")
+        data = [{"type": "message", "id": f"msg_{response_id[5:]}_{i}", "role": m.get("role", "user"),
+                 "content": [{"type": "input_text", "text": m.get("content") if isinstance(m.get("content"), str) else ""}]}
+                for i, m in enumerate(r["messages"])]
+        return {"object": "list", "data": data, "first_id": data[0]["id"] if data else None,
+                "last_id": data[-1]["id"] if data else None, "has_more": False}
+
+    @app.post("/v1/responses/{response_id}/cancel")
+    async def cancel_response(response_id: str):
+        t = running_responses.get(response_id)
+        if t is None:
+            if store.get(response_id) is not None:
+                raise HTTPException(400, "the response has already completed")
+            raise HTTPException(404, "unknown response id")
+        t.cancel()
+        return {"id": response_id, "object": "response", "status": "cancelled"}
+
     @app.post("/v1/responses")
     async def responses(request: Request):
         body = await request.json()
@@ -375,9 +411,26 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
                 history = store.thread(prev)
             except KeyError:
                 raise HTTPException(404, f"unknown previous_response_id {prev!r}")
+        conv = body.get("conversation")
+        conv_id = conv.get("id") if isinstance(conv, dict) else conv
+        if conv_id:
+            if prev:
+                raise HTTPException(400, "`conversation` and `previous_response_id` are mutually exclusive")
+            try:
+                history = conversations.messages(conv_id)
+            except KeyError:
+                raise HTTPException(404, f"unknown conversation {conv_id!r}")
         messages = history + new_msgs
         job = _job_from_chat(body, messages, system=body.get("instructions"), tools=body.get("tools"))
-        text, ids, usage, reason, _ = await _collect(job)
+        rid = "resp_" + uuid.uuid4().hex[:24]
+        task = asyncio.ensure_future(_collect(job))
+        running_responses[rid] = task
+        try:
+            text, ids, usage, reason, _ = await task
+        except asyncio.CancelledError:
+            return {"id": rid, "object": "response", "status": "cancelled", "model": cfg.model_name, "output": []}
+        finally:
+            running_responses.pop(rid, None)
         reasoning, content, calls = _split_outputs(job, text)
         out = []
         if reasoning:
@@ -388,9 +441,15 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
             out.append({"type": "function_call", "call_id": c["id"], "name": c["function"]["name"],
                         "arguments": c["function"]["arguments"]})
         u = usage or {}
-        rid = "resp_" + uuid.uuid4().hex[:24]
         if body.get("store", True):
             store.put(rid, new_msgs, content, prev)
+        if conv_id:
+            items = [dict(m, type="message") for m in new_msgs if isinstance(m.get("content"), str)]
+            items.append({"type": "message", "role": "assistant", "content": content})
+            try:
+                conversations.add_items(conv_id, items[-20:])
+            except (KeyError, ValueError):
+                pass                           # deleted or full meanwhile: the response itself stands
         return {"id": rid, "object": "response", "created_at": int(time.time()), "previous_response_id": prev,
                 "model": cfg.model_name, "status": "completed", "output": out,
                 "usage": {"input_tokens": u.get("prompt_tokens"), "output_tokens": u.get("completion_tokens"),
@@ -501,4 +560,7 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         return {"weights_bytes": st.get("weights_bytes"), "kv_bytes": engine.runner.kv_bytes(),
                 "kv_blocks": st.get("kv_blocks"), "free_blocks": st.get("free_blocks")}
 
+    from .extra_routes import install as _install_extra
+    _install_extra(app, engine=engine, tokenizer=tokenizer, cfg=cfg, telemetry=tel, conversations=conversations,
+                   completions=stored_completions)
     return app

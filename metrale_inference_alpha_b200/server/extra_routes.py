@@ -8,6 +8,7 @@ telemetry_events,lora}.rs`` as routed by ``main_modules/serve_router.rs``.
 from __future__ import annotations
 
 import asyncio
+import functools
 import json
 import time
 from typing import Any, Dict, Optional
@@ -52,6 +53,7 @@ def install(app: FastAPI, *, engine, tokenizer, cfg, telemetry, conversations: C
 
     # ------------------------------------------------------------------ conversations
     def guarded(fn):
+        @functools.wraps(fn)               # FastAPI reads the handler's signature through __wrapped__
         async def run(*a, **kw):
             try:
                 return await fn(*a, **kw)
@@ -59,7 +61,6 @@ def install(app: FastAPI, *, engine, tokenizer, cfg, telemetry, conversations: C
                 return openai_error(400, str(e), e.param, e.code)
             except KeyError as e:
                 return openai_error(404, f"not found: {e.args[0]}", code="not_found")
-        run.__name__ = fn.__name__
         return run
 
     async def _body(request: Request) -> dict:

@@ -16,6 +16,7 @@ LEVERS: Dict[str, str] = {
     "METRALE_DEBUG_SYNC_KERNELS": "1 = synchronise and check the status word after every step",
     "METRALE_KV_POISON": "1 = fill fresh KV blocks with NaN bytes",
     "METRALE_TELEMETRY": "off | basic | kernel",
+    "METRALE_MAX_BODY_BYTES": "HTTP request body limit in bytes (default 32 MiB)",
     "METRALE_NVTX": "1 = NVTX ranges around engine steps (for Nsight timelines)",
     "METRALE_OTLP_ENDPOINT": "OTLP/HTTP collector base URL; set = push metrics every METRALE_OTLP_PERIOD_S (default 10)",
     "METRALE_OTLP_PERIOD_S": "seconds between OTLP pushes",

@@ -482,3 +482,66 @@ def test_serve_alias_flags(tmp_path):
     eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=2, max_model_len=128, kv_cache_dtype="fp8"))
     assert eng.cfg.kv_dtype == "fp8"
     assert len(eng.generate([[1, 2, 3]], __import__("metrale_inference_alpha_b200").sampling.params.SamplingParams(max_tokens=3))[0].output_ids) == 3
+
+
+def test_conversations_stored_completions_stubs_and_introspection(client):
+    # 501 stubs carry an OpenAI-shaped error, not a 404
+    for method, path in [("post", "/v1/embeddings"), ("post", "/v1/audio/speech"), ("get", "/v1/files"),
+                         ("post", "/v1/images/generations"), ("post", "/v1/moderations"), ("get", "/v1/batches/b1")]:
+        r = getattr(client, method)(path)
+        assert r.status_code == 501 and r.json()["error"]["code"] == "not_implemented", path
+    # conversations: create, add, list (desc by default), get / delete items, metadata rules
+    c = client.post("/v1/conversations", json={"metadata": {"topic": "x"},
+                                               "items": [{"type": "message", "role": "user", "content": "hello"}]}).json()
+    cid = c["id"]
+    assert cid.startswith("conv_") and c["metadata"] == {"topic": "x"} and "items" not in c
+    new = client.post(f"/v1/conversations/{cid}/items", json={"items": [
+        {"role": "assistant", "content": "hi there"}, {"type": "function_call", "name": "f", "arguments": "{}", "call_id": "c1"},
+        {"type": "function_call_output", "call_id": "c1", "output": "42"}]}).json()
+    assert len(new["data"]) == 3 and new["data"][0]["content"][0]["type"] == "output_text"
+    lst = client.get(f"/v1/conversations/{cid}/items?limit=2").json()
+    assert len(lst["data"]) == 2 and lst["has_more"] and lst["data"][0]["type"] == "function_call_output"
+    asc = client.get(f"/v1/conversations/{cid}/items?order=asc&limit=100").json()["data"]
+    assert [i["type"] for i in asc] == ["message", "message", "function_call", "function_call_output"]
+    iid = asc[1]["id"]
+    assert client.get(f"/v1/conversations/{cid}/items/{iid}").json()["role"] == "assistant"
+    assert client.delete(f"/v1/conversations/{cid}/items/{iid}").status_code == 200
+    assert client.get(f"/v1/conversations/{cid}/items/{iid}").status_code == 404
+    r = client.post("/v1/conversations", json={"items": [{"role": "user", "content": "x"}] * 21})
+    assert r.status_code == 400 and r.json()["error"]["code"] == "items_too_many"
+    assert client.post(f"/v1/conversations/{cid}", json={"metadata": {"k": 1}}).status_code == 400
+    assert client.post(f"/v1/conversations/{cid}", json={"metadata": {"k": "v"}}).json()["metadata"] == {"k": "v"}
+    # /v1/responses continues a conversation and appends to it
+    before = len(client.get(f"/v1/conversations/{cid}/items?order=asc&limit=100").json()["data"])
+    r = client.post("/v1/responses", json={"input": "and now?", "conversation": cid, "max_output_tokens": 4}).json()
+    assert r["status"] == "completed"
+    after = client.get(f"/v1/conversations/{cid}/items?order=asc&limit=100").json()["data"]
+    assert len(after) == before + 2 and after[-2]["role"] == "user" and after[-1]["role"] == "assistant"
+    items = client.get(f"/v1/responses/{r['id']}/input_items").json()
+    assert items["data"][0]["content"][0]["text"] == "and now?"
+    assert client.post(f"/v1/responses/{r['id']}/cancel").status_code == 400        # already completed
+    assert client.post("/v1/responses/resp_nope/cancel").status_code == 404
+    assert client.post("/v1/responses", json={"input": "x", "conversation": cid, "previous_response_id": r["id"]}).status_code == 400
+    assert client.delete(f"/v1/conversations/{cid}").json()["deleted"] and client.get(f"/v1/conversations/{cid}").status_code == 404
+    # stored chat completions
+    a = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3,
+                                                  "store": True, "metadata": {"run": "7"}}).json()
+    got = client.get(f"/v1/chat/completions/{a['id']}").json()
+    assert got["choices"] == a["choices"] and got["metadata"] == {"run": "7"}
+    assert client.get("/v1/chat/completions/chatcmpl-unknown").status_code == 404
+    # model lookup, LoRA control, introspection
+    assert client.get("/v1/models/tiny").json()["id"] == "tiny"
+    assert client.get("/v1/models/org/other-model").json()["error"]["code"] == "model_not_found"
+    assert client.post("/v1/lora/active", json={"name": "nope"}).status_code == 404
+    assert client.post("/v1/lora/active", json={"name": None}).json() == {"active": None}
+    assert client.post("/v1/lora/load", json={"name": "x"}).status_code == 400
+    assert client.post("/v1/lora/load", json={"name": "x", "path": "/nonexistent/adapter"}).status_code == 400
+    fw = client.get("/forward").json()
+    assert fw["arch"] == "dense_gqa" and fw["kv_dtype"] in ("bf16", "fp8") and fw["max_num_seqs"] == 8
+    hw = client.get("/hardware").json()
+    assert "devices" in hw and "torch" in hw
+    with client.stream("GET", "/v1/events?limit=2") as s:
+        frames = [json.loads(l[6:]) for l in s.iter_lines() if l.startswith("data: ")]
+    assert [f["seq"] for f in frames] == [0, 1] and "counters" in frames[0] and "engine" in frames[0]
+    big = client.post("/v1/chat/completions", content=b"x", headers={"content-length": str(64 << 20)})
+    assert big.status_code in (400, 413)
