@@ -67,6 +67,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--lora-adapter", action="append", default=[], metavar="NAME=DIR", help="PEFT adapter to serve")
     s.add_argument("--max-loras", type=int, default=8)
     s.add_argument("--max-lora-rank", type=int, default=16)
+    s.add_argument("--cache-dir", default=None, help="model cache root (default: the Hugging Face hub cache)")
     s.add_argument("--bind", default=None, metavar="HOST:PORT", help="listen address (overrides --host / --port)")
     s.add_argument("--model-name", default=None, help="alias of --served-model-name")
     s.add_argument("--max-seq-len", type=int, default=None, help="alias of --max-model-len")
@@ -98,6 +99,15 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--isl", type=int, default=128)
     b.add_argument("--osl", type=int, default=1024)
     b.add_argument("--json", action="store_true")
+
+    dl = sub.add_parser("download", help="fetch a model repository into the cache")
+    dl.add_argument("repo")
+    dl.add_argument("--cache-dir", default=None)
+    dl.add_argument("--endpoint", default=None, help="Hub-compatible endpoint (default: HF_ENDPOINT or huggingface.co)")
+    dl.add_argument("--revision", default="main")
+    ml = sub.add_parser("models", help="list the models in the cache")
+    ml.add_argument("--cache-dir", default=None)
+    ml.add_argument("--json", action="store_true")
 
     d = sub.add_parser("doctor", help="report device, driver and library state")
     d.add_argument("--json", action="store_true")
@@ -219,6 +229,10 @@ def serve(ns) -> None:
     from .app import ServerConfig, create_app
     from .tokenizer import load_tokenizer
     apply_aliases(ns)
+    if isinstance(ns.model, str):
+        from ..config.model_config import PRESETS
+        from .model_library import resolve_model_dir
+        ns.model = resolve_model_dir(ns.model, ns.cache_dir, presets=tuple(PRESETS))
     eargs = _engine_args(ns)
     if ns.swap_space_gb > 0:
         eargs.preempt_mode, eargs.swap_space_bytes = "swap", int(ns.swap_space_gb * (1 << 30))
@@ -281,6 +295,30 @@ def main(argv: Optional[List[str]] = None) -> int:
             print(f"{'C':>4} {'tok/s':>10} {'p50 TTFT ms':>12} {'p99 TTFT ms':>12} {'ms/step':>9}")
             for r in rows:
                 print(f"{r['concurrency']:>4} {r['tok_s']:>10.1f} {r['ttft_p50_ms']:>12.1f} {r['ttft_p99_ms']:>12.1f} {r['ms_per_step']:>9.2f}")
+    elif ns.cmd == "download":
+        from .model_library import DownloadError, download
+        last = [0]
+
+        def show(name, done, total):
+            pct = int(100 * done / total) if total else 0
+            if pct != last[0]:
+                last[0] = pct
+                print(f"\r{pct:3d}%  {done / 2**20:10.1f} / {total / 2**20:.1f} MiB  {name[:40]:40s}", end="", flush=True)
+        try:
+            path = download(ns.repo, ns.cache_dir, ns.endpoint, ns.revision, progress=show)
+        except DownloadError as e:
+            print(f"\ndownload failed: {e}", file=sys.stderr)
+            return 1
+        print(f"\n{path}")
+    elif ns.cmd == "models":
+        from .model_library import list_models
+        rows = list_models(ns.cache_dir)
+        if ns.json:
+            print(json.dumps(rows))
+        else:
+            for r in rows:
+                print(f"{r['repo']:50s} {(r['revision'] or '-')[:12]:12s} {r['bytes'] / 2**30:8.2f} GiB  "
+                      f"{'ok' if r['complete'] else 'incomplete'}")
     elif ns.cmd == "doctor":
         rep = doctor()
         print(json.dumps(rep, indent=None if ns.json else 2))

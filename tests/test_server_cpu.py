@@ -545,3 +545,85 @@ def test_conversations_stored_completions_stubs_and_introspection(client):
     assert [f["seq"] for f in frames] == [0, 1] and "counters" in frames[0] and "engine" in frames[0]
     big = client.post("/v1/chat/completions", content=b"x", headers={"content-length": str(64 << 20)})
     assert big.status_code in (400, 413)
+
+
+def test_model_library_resolve_plan_and_download_with_resume(tmp_path):
+    import http.server
+    import threading
+
+    from metrale_inference_alpha_b200.server import model_library as ML
+    # ---- plan: only contained metadata / safetensors names, small first, weights last
+    files = [ML.RemoteFile(n, s) for n, s in [
+        ("model-00002.safetensors", 300), ("model-00001.safetensors", 500), ("config.json", 40), ("pytorch_model.bin", 999),
+        ("../evil.safetensors", 1), ("onnx/model.safetensors", 5), ("README.md", 10), ("tokenizer.json", 80),
+        ("sub/config.json", 1), ("model.safetensors.index.json", 20), ("C:evil.safetensors", 1), ("a//b.safetensors", 1)]]
+    assert [f.name for f in ML.select(files)] == ["config.json", "tokenizer.json", "model.safetensors.index.json",
+                                                   "model-00002.safetensors", "model-00001.safetensors"]
+    # ---- a Hub-shaped server over a directory
+    repo, sha = "org/tiny-model", "abc123"
+    content = {"config.json": b'{"model_type":"llama"}', "tokenizer.json": b"{}", "model.safetensors": bytes(range(256)) * 4096,
+               "pytorch_model.bin": b"zzz"}
+    ranges = []
+
+    class H(http.server.BaseHTTPRequestHandler):
+        def do_GET(self):
+            if self.path.startswith(f"/api/models/{repo}/revision/main"):
+                body = json.dumps({"sha": sha, "siblings": [{"rfilename": n, "size": len(b)} for n, b in content.items()]}).encode()
+                self.send_response(200)
+            elif self.path.startswith(f"/{repo}/resolve/{sha}/"):
+                data = content.get(self.path.split(f"/resolve/{sha}/", 1)[1])
+                if data is None:
+                    self.send_response(404)
+                    self.end_headers()
+                    return
+                rng = self.headers.get("Range")
+                if rng:
+                    start = int(rng.split("=")[1].split("-")[0])
+                    ranges.append(start)
+                    body = data[start:]
+                    self.send_response(206)
+                else:
+                    body = data
+                    self.send_response(200)
+            else:
+                self.send_response(404)
+                self.end_headers()
+                return
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def log_message(self, *a):
+            pass
+    srv = http.server.HTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    ep = f"http://127.0.0.1:{srv.server_port}"
+    cache = tmp_path / "hub"
+    try:
+        with pytest.raises(ML.ModelNotFound, match="download it first"):
+            ML.resolve_model_dir(repo, str(cache))
+        # a previous attempt left half of the weights behind: the download resumes it
+        snap = ML.repo_dir(cache, repo) / "snapshots" / sha
+        snap.mkdir(parents=True)
+        (snap / "model.safetensors.part").write_bytes(content["model.safetensors"][:300000])
+        with pytest.raises(ML.ModelNotFound, match="no default revision"):
+            ML.resolve_model_dir(repo, str(cache))                 # refs/main is not published yet
+        seen = []
+        path = ML.download(repo, str(cache), ep, progress=lambda n, d, t: seen.append((n, d, t)))
+        assert path == str(snap) and ranges == [300000]
+        assert (snap / "model.safetensors").read_bytes() == content["model.safetensors"]
+        assert not (snap / "pytorch_model.bin").exists() and not (snap / "model.safetensors.part").exists()
+        assert seen[-1][1] == seen[-1][2] - 300000 or seen[-1][1] <= seen[-1][2]
+        assert ML.resolve_model_dir(repo, str(cache)) == str(snap)
+        assert ML.resolve_model_dir("tiny-dense", str(cache), presets=("tiny-dense",)) == "tiny-dense"
+        assert ML.resolve_model_dir(str(snap)) == str(snap)
+        rows = ML.list_models(str(cache))
+        assert rows == [{"repo": repo, "revision": sha, "bytes": rows[0]["bytes"], "complete": True}] and rows[0]["bytes"] > 1 << 20
+        ML.download(repo, str(cache), ep)                          # second run: nothing to fetch
+        assert ranges == [300000]
+        with pytest.raises(ML.DownloadError, match="HTTP 404"):
+            ML.download("org/missing", str(cache), ep)
+    finally:
+        srv.shutdown()
+    with pytest.raises(ML.DownloadError, match="cannot reach"):
+        ML.download(repo, str(tmp_path / "c2"), "http://127.0.0.1:9")
