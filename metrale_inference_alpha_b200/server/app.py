@@ -217,6 +217,16 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
             sp.thinking_budget, sp.think_end_ids = budget, list(think_end_ids)
         return _ChatJob(ids, sp, tools, thinking, bool(body.get("logprobs")), bool(body.get("return_token_ids")))
 
+    def _account(usage) -> None:
+        """Per-request telemetry from the usage block (what the dashboard and /metrics show)."""
+        if not usage or not tel.enabled:
+            return
+        tel.inc("requests_finished")
+        tel.inc("decode_tokens", float(usage.get("completion_tokens") or 0))
+        tel.inc("prefill_tokens", float(usage.get("prompt_tokens") or 0))
+        if usage.get("time_to_first_token_ms") is not None:
+            tel.observe_ms("ttft", float(usage["time_to_first_token_ms"]))
+
     async def _collect(job: _ChatJob):
         text, ids, usage, reason, lps = "", [], None, None, None
         async for ev in aeng.submit(job.prompt_ids, job.params):
@@ -226,6 +236,7 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
             ids += ev.token_ids
             if ev.finished:
                 usage, reason, lps = ev.usage, ev.finish_reason, ev.logprobs
+                _account(usage)
         return text, ids, usage, reason, lps
 
     def _split_outputs(job: _ChatJob, text: str):
@@ -306,6 +317,7 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
                     yield chunk({"content": c})
                 if ev.finished:
                     final_usage, reason = ev.usage, ev.finish_reason
+                    _account(final_usage)
             if td is not None:
                 held = td.finish()
                 if held:
@@ -358,6 +370,7 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
                      "choices": [{"index": 0, "text": ev.text, "finish_reason": ev.finish_reason if ev.finished else None}]}
                 if ev.finished:
                     d["usage"] = ev.usage
+                    _account(ev.usage)
                 yield f"data: {json.dumps(d)}\n\n"
             yield "data: [DONE]\n\n"
         return StreamingResponse(gen(), media_type="text/event-stream")
@@ -506,6 +519,7 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
                                                       "delta": {"type": "text_delta", "text": ev.text}})
                 if ev.finished:
                     usage, reason = ev.usage, ev.finish_reason
+                    _account(usage)
             yield sse("content_block_stop", {"type": "content_block_stop", "index": 0})
             yield sse("message_delta", {"type": "message_delta",
                                         "delta": {"stop_reason": stop_map.get(reason, reason), "stop_sequence": None},

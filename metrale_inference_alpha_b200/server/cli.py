@@ -100,6 +100,13 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--osl", type=int, default=1024)
     b.add_argument("--json", action="store_true")
 
+    for name, helptext in (("tui", "live dashboard of a running server"), ("chat", "terminal chat with a running server")):
+        t = sub.add_parser(name, help=helptext)
+        t.add_argument("--url", default="http://127.0.0.1:8888")
+        t.add_argument("--api-key", default=None)
+        t.add_argument("--period", type=float, default=1.0)
+        t.add_argument("--model", default="default")
+        t.add_argument("--system", default=None)
     dl = sub.add_parser("download", help="fetch a model repository into the cache")
     dl.add_argument("repo")
     dl.add_argument("--cache-dir", default=None)
@@ -295,6 +302,16 @@ def main(argv: Optional[List[str]] = None) -> int:
             print(f"{'C':>4} {'tok/s':>10} {'p50 TTFT ms':>12} {'p99 TTFT ms':>12} {'ms/step':>9}")
             for r in rows:
                 print(f"{r['concurrency']:>4} {r['tok_s']:>10.1f} {r['ttft_p50_ms']:>12.1f} {r['ttft_p99_ms']:>12.1f} {r['ms_per_step']:>9.2f}")
+    elif ns.cmd in ("tui", "chat"):
+        from .tui import ChatSession, Dashboard, HttpTransport
+        tr = HttpTransport(ns.url, ns.api_key)
+        if ns.cmd == "tui":
+            try:
+                Dashboard(tr).run(ns.period)
+            except KeyboardInterrupt:
+                pass
+        else:
+            ChatSession(tr, model=ns.model, system=ns.system).repl()
     elif ns.cmd == "download":
         from .model_library import DownloadError, download
         last = [0]

@@ -627,3 +627,85 @@ def test_model_library_resolve_plan_and_download_with_resume(tmp_path):
         srv.shutdown()
     with pytest.raises(ML.DownloadError, match="cannot reach"):
         ML.download(repo, str(tmp_path / "c2"), "http://127.0.0.1:9")
+
+
+class _ClientTransport:
+    """The TUI's transport over an in-process TestClient."""
+
+    def __init__(self, client):
+        self.c = client
+
+    def get_text(self, path):
+        r = self.c.get(path)
+        if r.status_code != 200:
+            raise RuntimeError(f"HTTP {r.status_code}")
+        return r.text
+
+    def post_stream(self, path, body):
+        with self.c.stream("POST", path, json=body) as s:
+            yield from s.iter_lines()
+
+
+def test_tui_dashboard_and_chat_against_the_app(client, tmp_path):
+    from rich.console import Console
+
+    from metrale_inference_alpha_b200.server import tui
+    m = tui.parse_prometheus('# c\nmetrale_x_total 5\nmetrale_h_ms_bucket{le="10"} 2\nmetrale_h_ms_bucket{le="20"} 6\n'
+                             'metrale_h_ms_bucket{le="+Inf"} 8\nbroken line here\nmetrale_y 1e3\n')
+    assert m["metrale_x_total"] == 5 and m["metrale_y"] == 1000 and len(m) == 5
+    assert abs(tui.histogram_quantile(m, "metrale_h_ms", 0.5) - 15.0) < 1e-6         # 4th of 8: halfway through (10, 20]
+    assert tui.histogram_quantile(m, "metrale_h_ms", 0.99) == 20.0                    # lands in +Inf: last finite bound
+    assert tui.histogram_quantile(m, "metrale_nope", 0.5) is None
+    assert tui.sparkline([]) == "(no samples yet)" and tui.sparkline([0, 5, 10]).startswith("▁▄█")
+    tr = _ClientTransport(client)
+    now = [100.0]
+    dash = tui.Dashboard(tr, clock=lambda: now[0])
+    dash.poll()
+    sess = tui.ChatSession(tr, model="tiny", temperature=0.0, max_tokens=6)
+    seen = []
+    emit = lambda k, t: seen.append((k, t))
+    ans = sess.ask("hello", emit)
+    assert ans == "".join(t for k, t in seen if k == "content") and sess.messages[-1] == {"role": "assistant", "content": ans}
+    assert sess.last_usage and sess.last_usage["completion_tokens"] == 6
+    now[0] = 102.0
+    dash.poll()
+    s = dash.summary()
+    assert s["arch"] == "dense_gqa" and s["decode_tok_s"] == 3.0 and s["error"] is None        # 6 tokens over 2 s
+    assert s["ttft_p50_ms"] is not None and s["http_p50_ms"] is not None and s["free_blocks"] > 0
+    con = Console(record=True, width=140)
+    con.print(dash.render())
+    out = con.export_text()
+    assert "decode tok/s" in out and "TTFT p50" in out and "dense_gqa" in out
+    # slash commands
+    assert sess.command("/system be brief", emit) and sess.system == "be brief"
+    assert sess.command("/thinking on", emit) and sess.thinking
+    assert sess.command("/temp 0.3", emit) and sess.temperature == 0.3
+    assert sess.command("/max 4", emit) and sess.max_tokens == 4
+    assert sess.command("/temp x", emit) and sess.temperature == 0.3
+    assert sess.command("/stats", emit) and "tok/s" in seen[-1][1]
+    f = tmp_path / "conv.json"
+    assert sess.command(f"/save {f}", emit) and len(json.loads(f.read_text())["messages"]) == 2
+    sess.ask("again", emit)
+    assert len(sess.messages) == 4
+    assert sess.command("/clear", emit) and sess.messages == []
+    assert sess.command("/bogus", emit) and "unknown command" in seen[-1][1]
+    assert sess.command("/quit", emit) is False
+    # scripted REPL: two inputs then EOF
+    lines = iter(["/help", "hi"])
+
+    def read(_prompt):
+        try:
+            return next(lines)
+        except StopIteration:
+            raise EOFError
+    con2 = Console(record=True, width=100)
+    tui.ChatSession(tr, model="tiny", max_tokens=3, temperature=0.0).repl(read, con2)
+    assert "/thinking on|off" in con2.export_text()
+
+    class Dead:
+        def get_text(self, path):
+            raise ConnectionError("refused")
+    d2 = tui.Dashboard(Dead())
+    d2.poll()
+    assert "refused" in d2.summary()["error"]
+    con.print(d2.render())
