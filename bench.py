@@ -112,7 +112,9 @@ def main() -> int:
     ap.add_argument("--isl", type=int, default=128)
     ap.add_argument("--osl", type=int, default=1024)
     ap.add_argument("--no-fast-forward", action="store_true")
-    ap.add_argument("--no-fused", action="store_true", help="NCCL(+library-free GEMM) baseline collectives")
+    ap.add_argument("--fused", action="store_true",
+                    help="--parallelism tp: fused GEMM + all-reduce kernel over NVLink peer memory (default: NCCL after the GEMM, the faster of the two as measured)")
+    ap.add_argument("--no-fused", action="store_true", help="accepted for compatibility: NCCL collectives are the default")
     ap.add_argument("--ladder", action="store_true", help="also print one line per concurrency rung")
     ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
                     help="N>1: dp = one engine replica per GPU, each serving C requests (weak scaling, the "
@@ -141,7 +143,7 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=torch.device(dev))
         if use_tp:
             from metrale_inference_alpha_b200.parallel.tp import NcclTpContext
-            tp = NcclTpContext(rank, world, dev, fused=not args.no_fused)
+            tp = NcclTpContext(rank, world, dev, fused=args.fused and not args.no_fused)
 
     from metrale_inference_alpha_b200 import ops
     from metrale_inference_alpha_b200.config.model_config import preset

@@ -52,7 +52,8 @@ class EngineArgs:
     ep_size: int = 1
     request_timeout_s: float = 300.0
     eos_token_id: Optional[int] = None
-    fused_collectives: bool = True
+    fused_collectives: bool = False                    # tensor parallel: GEMM + all-reduce in one kernel over NVLink peer memory
+                                                       # instead of NCCL after the GEMM (measured slower so far: off by default)
     ep_dispatch: str = "allreduce"                     # expert parallelism: allreduce (masked-local experts) | a2a (token dispatch over peer memory)
     static_act_scales: bool = True                     # NVFP4: calibrate down-projection input scales at start-up
     preempt_mode: str = "recompute"                    # recompute | swap (KV + state to host memory / swap files)

@@ -295,6 +295,24 @@ __device__ __forceinline__ float4 dsmem_ld_f4(uint32_t addr) {
 }
 
 // ---------------------------------------------------------------- system-scope signalling (peer GPUs)
+// In-switch reduction (NVLS): one load from a multicast address returns the sum over the mapped
+// buffers of every GPU of the group, 8 bf16 values accumulated in fp32 inside the switch.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+// One 16-byte store to an NVLink multicast address: the switch writes it into the mapped buffer of
+// every GPU of the group (NVLS), so a broadcast costs this GPU one store instead of one per peer.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
 __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

@@ -65,7 +65,8 @@ struct GemmParams {
   // tensor-parallel fused all-reduce (row-parallel GEMM): see the epilogue
   int tp_size, tp_rank, tp_m_cap, tp_u_cap;
   __nv_bfloat16* tp_recv[8];    // per rank: [2 parity][tp source][m_cap][ldo] bf16 landing zones
-  __nv_bfloat16* tp_out[8];     // unused by the one-hop protocol (kept for layout stability)
+  __nv_bfloat16* tp_out[8];     // [0]: NVLink multicast address of the landing zones (null = one peer store per rank);
+                                // [1] non-null with [0]: two-shot protocol with the reduction done inside the switch
   uint32_t* tp_flags[8];        // per rank: [2 parity][u_cap] arrivals per unit
   uint32_t* tp_done[8];         // per rank: CTA completion counter of the running call
   const uint32_t* tp_par;       // this rank's current parity (flipped by the last CTA of a call)
@@ -438,8 +439,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
           for (int i = 0; i < 4; ++i) pb[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
           const size_t slot = (((size_t)tp_par * p.tp_size + p.tp_rank) * p.tp_m_cap + m) * p.ldo + n_out0;
+          if (p.tp_out[0] && p.tp_out[1]) {
+            // two-shot: the partial stays in this rank's own zone (slot of source 0); the unit's
+            // owner sums all ranks' copies with one in-switch multimem.ld_reduce per 16 bytes
+            const size_t own = (((size_t)tp_par * p.tp_size) * p.tp_m_cap + m) * p.ldo + n_out0;
+            *reinterpret_cast<uint4*>(p.tp_recv[p.tp_rank] + own) = pk;
+          } else if (p.tp_out[0]) {
+            // NVLS: one multicast store, replicated into every rank's zone by the switch
+            mb::multimem_st_v4(p.tp_out[0] + slot, pk);
+          } else {
 #pragma unroll 1
-          for (int r = 0; r < p.tp_size; ++r) *reinterpret_cast<uint4*>(p.tp_recv[r] + slot) = pk;
+            for (int r = 0; r < p.tp_size; ++r) *reinterpret_cast<uint4*>(p.tp_recv[r] + slot) = pk;
+          }
           return;
         }
         if (vec_ok) {
@@ -540,14 +551,91 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // double-buffered by a per-rank parity that the last CTA of the kernel flips.
         __threadfence_system();
         epi_bar_sync();
-        if (threadIdx.x == 64) {
-          for (int r = 0; r < p.tp_size; ++r)
-            mb::red_add_release_sys(p.tp_flags[r] + (size_t)tp_par * p.tp_u_cap + tp_unit, 1u);
-        }
         uint32_t* my_flag = p.tp_flags[p.tp_rank] + (size_t)tp_par * p.tp_u_cap + tp_unit;
-        if (threadIdx.x == 64) is_last_s = mb::wait_flag_sys(my_flag, (uint32_t)p.tp_size, p.status) ? 1 : 0;
+        const bool two_shot = p.tp_out[0] && p.tp_out[1];
+        if (two_shot) {
+          // ---- in-switch variant. Unit u is owned by rank u % size. Every rank tells the owner
+          // that its partial is in place; the owner sums the copies of all ranks with
+          // multimem.ld_reduce (fp32 accumulation in the switch), adds the residual, broadcasts
+          // the bf16 result into every rank's result zone (slot of source 1) with multimem.st and
+          // raises bit 16 of the unit's flag on every rank; every rank then copies its rows out.
+          // Each GPU moves about two copies of the output over NVLink instead of `size` copies.
+          constexpr uint32_t kDoneBit = 1u << 16;
+          const int owner = tp_unit % p.tp_size;
+          if (threadIdx.x == 64)
+            mb::red_add_release_sys(p.tp_flags[owner] + (size_t)tp_par * p.tp_u_cap + tp_unit, 1u);
+          const size_t zone0 = ((size_t)tp_par * p.tp_size) * p.tp_m_cap * p.ldo;         // partials (source slot 0)
+          const size_t zone1 = zone0 + (size_t)p.tp_m_cap * p.ldo;                        // results (source slot 1)
+          if (p.tp_rank == owner) {
+            if (threadIdx.x == 64) is_last_s = mb::wait_flag_sys(my_flag, (uint32_t)p.tp_size, p.status) ? 1 : 0;
+            epi_bar_sync();
+            if (is_last_s) {
+              // four in-switch loads in flight per thread: their latency (a round trip through
+              // the switch to every rank) would otherwise add up row after row
+              constexpr int kBatch = 4;
+              for (int mr0 = row_lo + et / tpr; mr0 < rows_valid; mr0 += rpp * kBatch) {
+                uint4 sum[kBatch];
+#pragma unroll
+                for (int b = 0; b < kBatch; ++b) {
+                  const int mr = mr0 + b * rpp;
+                  if (mr < rows_valid)
+                    sum[b] = mb::multimem_ld_reduce_bf16x8(p.tp_out[0] + zone0 + (size_t)(m0 + mr) * p.ldo + n_out0);
+                }
+#pragma unroll
+                for (int b = 0; b < kBatch; ++b) {
+                  const int mr = mr0 + b * rpp;
+                  if (mr >= rows_valid) continue;
+                  const size_t zo = (size_t)(m0 + mr) * p.ldo + n_out0;
+                  const __nv_bfloat162* sb = reinterpret_cast<const __nv_bfloat162*>(&sum[b]);
+                  float acc[8];
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(sb[i]);
+                    acc[2 * i] = f.x; acc[2 * i + 1] = f.y;
+                  }
+                  if (p.residual) {
+                    const uint4 rr = __ldg(reinterpret_cast<const uint4*>(p.residual + zo));
+                    const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      const float2 f = __bfloat1622float2(rb[i]);
+                      acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+                    }
+                  }
+                  uint4 pk;
+                  __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) pb[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                  mb::multimem_st_v4(p.tp_out[0] + zone1 + zo, pk);
+                }
+              }
+            }
+            __threadfence_system();
+            epi_bar_sync();
+            if (threadIdx.x == 64 && is_last_s) {
+              for (int r = 0; r < p.tp_size; ++r)
+                mb::red_add_release_sys(p.tp_flags[r] + (size_t)tp_par * p.tp_u_cap + tp_unit, kDoneBit);
+            }
+          }
+          if (threadIdx.x == 64) is_last_s = mb::wait_flag_sys(my_flag, kDoneBit, p.status) ? 1 : 0;
+          epi_bar_sync();
+          if (is_last_s) {
+            const __nv_bfloat16* res = p.tp_recv[p.tp_rank] + zone1;
+            for (int mr = row_lo + et / tpr; mr < rows_valid; mr += rpp) {
+              const size_t zo = (size_t)(m0 + mr) * p.ldo + n_out0;
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + zo) =
+                  __ldcg(reinterpret_cast<const uint4*>(res + zo));
+            }
+          }
+        } else {
+          if (threadIdx.x == 64) {
+            for (int r = 0; r < p.tp_size; ++r)
+              mb::red_add_release_sys(p.tp_flags[r] + (size_t)tp_par * p.tp_u_cap + tp_unit, 1u);
+          }
+          if (threadIdx.x == 64) is_last_s = mb::wait_flag_sys(my_flag, (uint32_t)p.tp_size, p.status) ? 1 : 0;
+        }
         epi_bar_sync();
-        if (is_last_s) {
+        if (is_last_s && !two_shot) {
           const __nv_bfloat16* zone = p.tp_recv[p.tp_rank] + (size_t)tp_par * p.tp_size * p.tp_m_cap * p.ldo;
           for (int mr = row_lo + et / tpr; mr < rows_valid; mr += rpp) {
             const int m = m0 + mr;

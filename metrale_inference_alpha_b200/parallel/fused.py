@@ -2,7 +2,9 @@
 
 ``FusedCollectives.gemm_allreduce`` runs a row-parallel projection whose tcgen05 GEMM kernel
 also performs the all-reduce in one NVLink hop: the epilogue pushes each finished bf16 partial
-tile-share into every rank's landing zone (peer stores, overlapping the rest of the GEMM), then
+tile-share into every rank's landing zone (one ``multimem.st`` through the NVSwitch multicast
+mapping when the group has one, else one peer store per rank; either way overlapping the rest of
+the GEMM), then
 each rank sums the shares in rank order, adds the residual and stores the result into its own
 rank's output buffer. Buffers live in one
 symmetric allocation (``torch.distributed._symmetric_memory``: same layout on every rank, peer
@@ -15,6 +17,7 @@ The reference only ever calls ``ncclAllReduce`` after the local GEMM
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -43,6 +46,15 @@ class FusedCollectives:
         self.done = [p + 2 * U_CAP * 4 for p in ptrs]
         self.par = ptrs[rank] + 2 * U_CAP * 4 + 256
         self.recv = [p + self.ctrl_bytes for p in ptrs]
+        # NVLS: when the group has an NVLink multicast mapping of the allocation, the epilogue
+        # broadcasts each partial with one multimem.st instead of one peer store per rank
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        mode = os.environ.get("METRALE_NVLS", "1")
+        self.nvls = bool(mc) and mode != "0"
+        # 2: the owner of each tile share sums all ranks' partials inside the switch
+        # (multimem.ld_reduce) and broadcasts the result; 1: every rank receives every partial
+        self.in_switch = self.nvls and mode == "2" and size >= 2
+        self.mc_recv = (mc + self.ctrl_bytes) if self.nvls else 0
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)
         self.calls = 0
@@ -57,7 +69,7 @@ class FusedCollectives:
             dist.all_reduce(y)
             return y
         tp = dict(size=self.size, rank=self.rank, m_cap=M_CAP, u_cap=U_CAP, recv=self.recv,
-                  out=self.recv, flags=self.flags, done=self.done, par=self.par)
+                  out=[self.mc_recv, 1 if self.in_switch else 0] + [0] * (self.size - 2), flags=self.flags, done=self.done, par=self.par)
         out = ops.linear(act, w, residual=residual, tp=tp)
         self.calls += 1
         return out

@@ -40,6 +40,8 @@ class NcclTpContext(TpContext):
         self.diagnostics = (os.environ.get("METRALE_COMM_DIAGNOSTICS") == "1") if diagnostics is None else diagnostics
         self.bytes_reduced = 0
         self.fused_impl = None
+        if os.environ.get("METRALE_NO_FUSED_COLLECTIVES") == "1":
+            fused = False
         if fused and size > 1 and self.device.type == "cuda":
             try:
                 from .fused import FusedCollectives

@@ -21,6 +21,7 @@ LEVERS: Dict[str, str] = {
     "METRALE_OTLP_ENDPOINT": "OTLP/HTTP collector base URL; set = push metrics every METRALE_OTLP_PERIOD_S (default 10)",
     "METRALE_OTLP_PERIOD_S": "seconds between OTLP pushes",
     "METRALE_NATIVE_RUNTIME": "0 = keep allocator / prefix index / JSON grammar on the Python implementations",
+    "METRALE_NVLS": "fused collectives: 0 = one peer store per rank, 1 = NVLink multicast stores, 2 = reduction inside the switch (multimem.ld_reduce)",
     "METRALE_NO_FUSED_COLLECTIVES": "1 = NCCL collectives after plain GEMMs",
 }
 
