@@ -74,6 +74,11 @@ class LLMEngine:
             if os.path.isdir(cfg) or (os.path.isfile(cfg) and cfg.endswith(".gguf")):
                 from ..weights.checkpoint import open_checkpoint
                 cfg, source = open_checkpoint(cfg, device=args.device)
+                if type(source).__name__ != "GgufSource":        # GGUF names are mapped (and checked) by its own source
+                    from ..weights.preflight import preflight
+                    rep = preflight(cfg, source, check_shapes=False)      # names only: cheap, and fails before any load
+                    if not rep.ok:
+                        raise ValueError(rep.summary())
             else:
                 cfg = cfg_preset(cfg)
         if args.kv_cache_dtype not in ("auto", cfg.kv_dtype):

@@ -80,6 +80,19 @@ def available() -> bool:
     return LIB_PATH.exists()
 
 
+def check_arch(capability=None) -> None:
+    """The library holds sm_100a code only (tcgen05 / TMEM have no forward-compatible PTX): refuse
+    any other device up front instead of failing in the first launch with "no kernel image"."""
+    if capability is None:
+        import torch
+        if not torch.cuda.is_available():
+            return
+        capability = torch.cuda.get_device_capability()
+    if tuple(capability) != (10, 0):
+        raise RuntimeError(f"this build targets NVIDIA B200 (sm_100a); the current device reports sm_{capability[0]}{capability[1]}. "
+                           "Architecture-specific sm_100a code does not run on other architectures.")
+
+
 def lib():
     """Load (once) and return the kernel library; raises when it has not been built."""
     global _lib
@@ -92,6 +105,7 @@ def lib():
         if not LIB_PATH.exists():
             raise RuntimeError(
                 f"{LIB_PATH} is missing: run `python -m metrale_inference_alpha_b200.ops.build`")
+    check_arch()
     L = C.CDLL(str(LIB_PATH))
     P = C.POINTER
     L.mb_gemm.argtypes = [P(GemmArgs), c_void_p]

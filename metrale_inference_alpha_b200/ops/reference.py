@@ -398,3 +398,23 @@ def _topk_stable(x: torch.Tensor, k: int):
     """top-k with ties resolved toward the lower index."""
     order = torch.sort(x, dim=-1, descending=True, stable=True)
     return order.values[..., :k], order.indices[..., :k]
+
+
+# ----------------------------------------------------------------------------- MXFP4 (OCP microscaling)
+def e8m0_to_float(b: torch.Tensor) -> torch.Tensor:
+    """E8M0 block scales: 2 ** (byte - 127); byte 255 is NaN."""
+    e = b.to(torch.int32)
+    out = torch.pow(2.0, (e - 127).float())
+    return torch.where(e == 255, torch.full_like(out, float("nan")), out)
+
+
+def dequantize_mxfp4(packed: torch.Tensor, scales_e8m0: torch.Tensor) -> torch.Tensor:
+    """MXFP4 weights (e2m1 values, two per byte with the low nibble first, one E8M0 scale per 32
+    values along K) -> fp32 [N, K]. Host-side unpack used to convert MXFP4 checkpoints to a serving
+    format (role of the reference's crates/core/src/mxfp4_e8m0.rs)."""
+    N, kb = packed.shape
+    K = kb * 2
+    assert scales_e8m0.shape == (N, K // 32), "one E8M0 scale per 32 values"
+    vals = e2m1_decode(unpack_fp4(packed))                     # [N, K] fp32
+    s = e8m0_to_float(scales_e8m0).repeat_interleave(32, dim=1)
+    return vals * s

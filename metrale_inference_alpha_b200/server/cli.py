@@ -112,6 +112,9 @@ def build_parser() -> argparse.ArgumentParser:
     dl.add_argument("--cache-dir", default=None)
     dl.add_argument("--endpoint", default=None, help="Hub-compatible endpoint (default: HF_ENDPOINT or huggingface.co)")
     dl.add_argument("--revision", default="main")
+    pf = sub.add_parser("preflight", help="check a checkpoint directory against its configuration without loading it")
+    pf.add_argument("model")
+    pf.add_argument("--cache-dir", default=None)
     ml = sub.add_parser("models", help="list the models in the cache")
     ml.add_argument("--cache-dir", default=None)
     ml.add_argument("--json", action="store_true")
@@ -327,6 +330,14 @@ def main(argv: Optional[List[str]] = None) -> int:
             print(f"\ndownload failed: {e}", file=sys.stderr)
             return 1
         print(f"\n{path}")
+    elif ns.cmd == "preflight":
+        from ..weights.checkpoint import open_checkpoint
+        from ..weights.preflight import preflight
+        from .model_library import resolve_model_dir
+        cfg, src = open_checkpoint(resolve_model_dir(ns.model, ns.cache_dir))
+        rep = preflight(cfg, src)
+        print(rep.summary(limit=50))
+        return 0 if rep.ok else 1
     elif ns.cmd == "models":
         from .model_library import list_models
         rows = list_models(ns.cache_dir)

@@ -211,3 +211,53 @@ def test_family_on_gpu_matches_fp32_oracle(name, extra):
     want = _oracle_logits(hf, lambda n: canon[n], lambda n: n in canon, toks)
     err = (got - want).abs().max().item()
     assert err < 0.06 * want.abs().max().item() + 1e-2, err
+
+
+def test_checkpoint_preflight_reports_everything_at_once(tmp_path):
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.weights.preflight import preflight
+    hf = FAMILIES["mixtral"]
+    cfg = from_hf_config(hf, name="mixtral")
+    syn = SyntheticSource(cfg, seed=1, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    tensors = {k: v.contiguous() for k, v in _dialect("mixtral", hf, canon).items()}
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    cfg2, src = open_checkpoint(tmp_path)
+    rep = preflight(cfg2, src)
+    assert rep.ok and rep.checked > 40 and "present" in rep.summary()
+    # break it: drop one expert projection and a norm, give another tensor the wrong shape
+    bad = dict(tensors)
+    del bad["model.layers.1.block_sparse_moe.experts.2.w3.weight"]
+    del bad["model.layers.0.post_attention_layernorm.weight"]
+    bad["model.layers.0.self_attn.o_proj.weight"] = torch.zeros(7, 9, dtype=torch.bfloat16)
+    d2 = tmp_path / "broken"
+    d2.mkdir()
+    save_file(bad, str(d2 / "model.safetensors"))
+    (d2 / "config.json").write_text(json.dumps(hf))
+    cfg3, src3 = open_checkpoint(d2)
+    rep = preflight(cfg3, src3)
+    assert not rep.ok and len(rep.missing) == 2 and len(rep.bad_shape) == 1
+    text = rep.summary()
+    assert "experts.2.up_proj" in text and "post_attention_layernorm" in text and "found (7, 9)" in text
+    with pytest.raises(ValueError, match="preflight failed: 2 missing"):
+        LLMEngine(EngineArgs(model=str(d2), device="cpu", max_num_seqs=2, max_model_len=64))
+    from metrale_inference_alpha_b200.server.cli import main
+    assert main(["preflight", str(tmp_path)]) == 0 and main(["preflight", str(d2)]) == 1
+
+
+def test_arch_preflight_and_mxfp4_unpack():
+    from metrale_inference_alpha_b200.ops import _native, reference as ref
+    _native.check_arch((10, 0))
+    with pytest.raises(RuntimeError, match="sm_100a"):
+        _native.check_arch((9, 0))
+    with pytest.raises(RuntimeError, match="sm_120"):
+        _native.check_arch((12, 0))
+    # e2m1 nibbles (low first) x 2^(e - 127) per 32 values
+    codes = torch.arange(64, dtype=torch.uint8).remainder(16).view(1, 64)
+    packed = ref.pack_fp4(codes)
+    scales = torch.tensor([[127, 130]], dtype=torch.uint8)
+    w = ref.dequantize_mxfp4(packed, scales)
+    want = ref.e2m1_decode(codes).float() * torch.tensor([1.0] * 32 + [8.0] * 32)
+    assert torch.equal(w, want) and w[0, 7] == 6.0 and w[0, 32 + 15] == -48.0
+    assert torch.isnan(ref.e8m0_to_float(torch.tensor([255], dtype=torch.uint8)))[0]
