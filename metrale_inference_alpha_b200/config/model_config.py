@@ -37,13 +37,19 @@ class ModelConfig:
     qk_norm: bool = False
     attn_output_gate: bool = False      # q_proj emits [Q_h | G_h] per head, o = attn * sigmoid(G)
     sliding_window: int = 0
+    attn_scale: float = 0.0             # softmax scale; 0 -> head_dim ** -0.5 (Gemma: query_pre_attn_scalar ** -0.5)
+    window_layers: List[int] = field(default_factory=list)   # per-layer window (0 = full); empty -> sliding_window everywhere
+    rope_local_theta: float = 0.0       # RoPE base of the windowed layers when it differs (Gemma 3); 0 = rope_theta
     attn_bias: bool = False             # q / k / v projections carry a bias (Qwen2 family)
     # norms
     rms_eps: float = 1e-6
     norm_plus_one: bool = False         # (1 + w) scaling (Qwen3.5 family)
     # ffn
     intermediate_size: int = 688
-    ffn_act: str = "swiglu"             # swiglu | relu2
+    ffn_act: str = "swiglu"             # swiglu | relu2 | geglu (tanh-approximated GELU gate)
+    post_norms: bool = False            # Gemma: RMSNorm on the attention / FFN output before the residual add
+    embed_scale: float = 1.0            # embeddings are multiplied by this (Gemma: sqrt(hidden))
+    final_logit_softcap: float = 0.0    # logits = cap * tanh(logits / cap); 0 = off
     tie_embeddings: bool = False
     # per-layer structure
     layer_types: List[str] = field(default_factory=list)   # mixer per layer
@@ -272,6 +278,7 @@ def preset(name: str, **kw) -> ModelConfig:
 # ----------------------------------------------------------------------------- HF config.json
 _HF_ARCH = {
     "llama": "dense_gqa", "qwen2": "dense_gqa", "qwen3": "dense_gqa", "mistral": "dense_gqa",
+    "gemma3_text": "dense_gqa", "gemma3": "dense_gqa", "gemma2": "dense_gqa",
     "phi3": "dense_gqa", "qwen3_moe": "dense_gqa", "qwen2_moe": "dense_gqa", "mixtral": "dense_gqa",
     "qwen3_5": "qwen_hybrid", "qwen3_5_moe": "qwen_hybrid", "qwen3_next": "qwen_hybrid",
     "qwen3_5_text": "qwen_hybrid", "qwen3_5_moe_text": "qwen_hybrid",
@@ -324,6 +331,23 @@ def from_hf_config(cfg: dict, name: str = "model") -> ModelConfig:
         kw["qk_norm"] = mt in ("qwen3", "qwen3_moe")
         kw["attn_bias"] = bool(cfg.get("attention_bias", cfg.get("qkv_bias", mt in ("qwen2", "qwen2_moe"))))
         kw["sliding_window"] = int(cfg.get("sliding_window") or 0) if cfg.get("use_sliding_window") else 0
+        if mt in ("gemma3_text", "gemma3", "gemma2"):
+            if cfg.get("attn_logit_softcapping"):
+                raise ValueError("attention logit soft-capping (Gemma 2) is not supported")
+            act = cfg.get("hidden_activation", cfg.get("hidden_act", "gelu_pytorch_tanh"))
+            if act not in ("gelu_pytorch_tanh", "gelu_tanh"):
+                raise ValueError(f"unsupported Gemma activation {act!r}")
+            win = int(cfg.get("sliding_window") or 0)
+            lt = cfg.get("layer_types")
+            if lt is None:
+                pat = int(cfg.get("sliding_window_pattern", 6) or 6)
+                lt = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention" for i in range(L)]
+            kw.update(norm_plus_one=True, post_norms=True, ffn_act="geglu", qk_norm=mt != "gemma2",
+                      embed_scale=float(h) ** 0.5, tie_embeddings=bool(cfg.get("tie_word_embeddings", True)),
+                      attn_scale=float(cfg.get("query_pre_attn_scalar", kw["head_dim"])) ** -0.5,
+                      window_layers=[win if t == "sliding_attention" else 0 for t in lt], sliding_window=0,
+                      rope_local_theta=float(cfg.get("rope_local_base_freq", 0.0) or 0.0),
+                      final_logit_softcap=float(cfg.get("final_logit_softcapping") or 0.0))
         if mt == "phi3":
             rs = cfg.get("rope_scaling")
             if rs and str(rs.get("type", rs.get("rope_type", ""))).lower() in ("longrope", "su"):

@@ -68,7 +68,10 @@ class Decoder:
         if rot > 0:
             self.cos, self.sin = ref.rope_tables(cfg.max_position, rot, cfg.rope_theta, device=self.device,
                                                  scaling=cfg.rope_scaling)
-        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.cos_local = self.sin_local = None
+        if rot > 0 and cfg.rope_local_theta > 0:          # windowed layers rotate with their own, unscaled base
+            self.cos_local, self.sin_local = ref.rope_tables(cfg.max_position, rot, cfg.rope_local_theta, device=self.device)
+        self.scale = cfg.attn_scale if cfg.attn_scale > 0 else 1.0 / math.sqrt(cfg.head_dim)
         self.lora = None                   # lora.LoraManager when adapters are served
         self.calib = None                  # dict while calibrating static activation scales (engine/runner.py)
 
@@ -76,6 +79,12 @@ class Decoder:
     def _norm_act(self, x, w, fmt: str, also_bf16: bool = False) -> Act:
         return ops.row_op(x, fmt, ops.IN_RMSNORM, w=w, plus_one=self.cfg.norm_plus_one,
                           eps=self.cfg.rms_eps, also_bf16=also_bf16)[0]
+
+    def _add_normed(self, x: torch.Tensor, y: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """x + RMSNorm(y): the sandwich norm of the Gemma family (the block's output is normalised
+        before it joins the residual stream)."""
+        n = self._norm_act(y.to(x.dtype) if y.dtype != x.dtype else y, w, "bf16").data
+        return x + n.to(x.dtype)
 
     @staticmethod
     def _as_act(t: torch.Tensor, fmt: str) -> Act:
@@ -89,9 +98,14 @@ class Decoder:
             return None
         return self.lora
 
-    def attention_block(self, x, lw: LayerW, batch: ForwardBatch, kc, vc, ks, vs, li: int = -1):
+    def attention_block(self, x, lw: LayerW, batch: ForwardBatch, kc, vc, ks, vs, li: int = -1,
+                        add_residual: bool = True):
         c, w = self.cfg, lw.mixer
         D = c.head_dim
+        window = c.window_layers[li] if (c.window_layers and 0 <= li < len(c.window_layers)) else c.sliding_window
+        local = window > 0 and self.cos_local is not None
+        cos, sin = (self.cos_local, self.sin_local) if local else (self.cos, self.sin)
+        res = x if add_residual else None
         lora = self._lora_for(batch, li)
         a = self._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.qkv.fmt], also_bf16=lora is not None)
         qkv = ops.linear(a, w.qkv)
@@ -108,18 +122,18 @@ class Decoder:
         q = ops.qk_norm_rope_kvwrite(
             qkv, Hq=w.heads, Hkv=w.kv_heads, D=D, positions=batch.positions, slots=batch.slot_mapping,
             k_cache=kc, v_cache=vc, q_norm_w=w.q_norm, k_norm_w=w.k_norm, plus_one=c.norm_plus_one,
-            eps=c.rms_eps, cos=self.cos, sin=self.sin, q_head_stride=qhs, k_scale=ks, v_scale=vs)
+            eps=c.rms_eps, cos=cos, sin=sin, q_head_stride=qhs, k_scale=ks, v_scale=vs)
         fmt = ACT_FOR_WEIGHT[w.o.fmt]
         static = w.o_in_scale if (fmt == "nvfp4" and self.calib is None and not c.attn_output_gate) else 0.0
         if static > 0.0 and lora is None:
             # the attention kernel's final store quantises for o_proj with the calibrated scale
             oa = ops.paged_attention(q, kc, vc, batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
                                      max_q_len=batch.max_q_len, max_ctx=batch.max_ctx, scale=self.scale,
-                                     k_scale=ks, v_scale=vs, window=c.sliding_window, quant_out=static)
-            return self.tp.linear_reduce(oa, w.o, residual=x)
+                                     k_scale=ks, v_scale=vs, window=window, quant_out=static)
+            return self.tp.linear_reduce(oa, w.o, residual=res)
         o = ops.paged_attention(q, kc, vc, batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
                                 max_q_len=batch.max_q_len, max_ctx=batch.max_ctx, scale=self.scale,
-                                k_scale=ks, v_scale=vs, window=c.sliding_window)
+                                k_scale=ks, v_scale=vs, window=window)
         o = o.view(o.shape[0], w.heads * D)
         if self.calib is not None:
             m = o.float().abs().max()
@@ -129,7 +143,7 @@ class Decoder:
                             gate_head_off=D)[0]
         else:
             oa = ops.quantize_act(o, fmt, static_scale=static) if fmt == "nvfp4" else self._as_act(o, fmt)
-        y = self.tp.linear_reduce(oa, w.o, residual=x)
+        y = self.tp.linear_reduce(oa, w.o, residual=res)
         if lora is not None and not c.attn_output_gate:
             lora.apply(y, o, li, "o", batch.adapter_rows)
         return y
@@ -141,6 +155,12 @@ class Decoder:
         if c.ffn_act == "relu2":
             up = ops.linear(a, w.gate_up)
             h = ops.row_op(up, fmt_d, ops.IN_RELU2, also_bf16=lora is not None)[0]
+        elif c.ffn_act == "geglu":
+            gu = ops.linear(a, w.gate_up)                     # gate | up halves
+            inter = gu.shape[1] // 2
+            hb = (torch.nn.functional.gelu(gu[:, :inter].float(), approximate="tanh") * gu[:, inter:].float()
+                  ).to(torch.bfloat16)
+            h = self._as_act(hb, fmt_d)
         elif w.interleaved:
             static = w.down_in_scale if (fmt_d == "nvfp4" and self.calib is None) else 0.0
             if static > 0.0 and lora is None:
@@ -169,7 +189,11 @@ class Decoder:
         if lw.ffn_kind == "dense":
             a = self._norm_act(x, lw.ln2, ACT_FOR_WEIGHT[lw.ffn.gate_up.fmt])
             lora = self._lora_for(batch, li) if batch is not None else None
-            return self.dense_ffn(a, lw.ffn, x, lora, li, batch.adapter_rows if lora is not None else None)
+            rows = batch.adapter_rows if lora is not None else None
+            if lw.post_ffn is not None:
+                y = self.dense_ffn(a, lw.ffn, None, lora, li, rows)
+                return self._add_normed(x, y, lw.post_ffn)
+            return self.dense_ffn(a, lw.ffn, x, lora, li, rows)
         from .moe import moe_block
         return moe_block(self, x, lw)
 
@@ -177,7 +201,12 @@ class Decoder:
         if lw.kind == "attention":
             kv = kv or caches.kv
             j = caches.kv_index[i] if kv_idx is None else kv_idx
-            x = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i)
+            if lw.post_attn is not None:
+                y = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i,
+                                         add_residual=False)
+                x = self._add_normed(x, y, lw.post_attn)
+            else:
+                x = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i)
         elif lw.kind == "gdn":
             from .recurrent import gdn_block
             x = gdn_block(self, x, lw, batch, caches.state, caches.state_index[i])
@@ -193,7 +222,10 @@ class Decoder:
 
     # ------------------------------------------------------------------ full forward
     def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return ops.embed(token_ids, self.w.embed)
+        x = ops.embed(token_ids, self.w.embed)
+        if self.cfg.embed_scale != 1.0:
+            x = x * torch.tensor(self.cfg.embed_scale, dtype=torch.bfloat16).to(x.dtype)
+        return x
 
     def backbone(self, batch: ForwardBatch, caches: LayerCaches) -> torch.Tensor:
         """Token ids -> final residual stream [T, hidden] (before the final norm)."""
@@ -206,6 +238,9 @@ class Decoder:
         """Final norm + (vocab-parallel) lm_head on the selected rows."""
         a = self._norm_act(hidden_rows, self.w.final_norm if final_norm is None else final_norm, "bf16")
         lg = ops.linear(a, self.w.lm_head, out_f32=out_f32)
+        cap = self.cfg.final_logit_softcap
+        if cap > 0:
+            lg = (torch.tanh(lg.float() / cap) * cap).to(lg.dtype)
         return self.tp.all_gather_last(lg)
 
     def forward(self, batch: ForwardBatch, caches: LayerCaches, out_f32: bool = False

@@ -175,6 +175,8 @@ class LayerW:
     ffn_kind: str = "dense"
     ln1: torch.Tensor = None
     ln2: Optional[torch.Tensor] = None
+    post_attn: Optional[torch.Tensor] = None     # Gemma sandwich norms: applied to the block's output
+    post_ffn: Optional[torch.Tensor] = None
     mixer: object = None
     ffn: object = None
 
@@ -283,7 +285,7 @@ class Loader:
         c = self.cfg
         up = self.lin(f"{p}.{names[1]}")
         down = self.lin(f"{p}.{names[2]}")
-        gate = self.lin(f"{p}.{names[0]}") if c.ffn_act == "swiglu" else None
+        gate = self.lin(f"{p}.{names[0]}") if c.ffn_act in ("swiglu", "geglu") else None
         if shard and self.tp_size > 1:
             lo, hi = self._shard(up.N)
             up, down = slice_rows(up, lo, hi), slice_cols(down, lo, hi)
@@ -293,8 +295,9 @@ class Loader:
         if gate is None:
             return FfnW(finalize(up), finalize(down), down_in_scale=gs)
         gu = ops.concat_weights([gate, up])
-        if gu.fmt == "fp8_block":
-            # 128x128 scale blocks forbid a row-interleave: keep gate | up halves
+        if gu.fmt == "fp8_block" or c.ffn_act == "geglu":
+            # 128x128 scale blocks forbid a row-interleave, and the GEMM epilogue knows SwiGLU only:
+            # keep gate | up halves
             return FfnW(finalize(gu), finalize(down), down_in_scale=gs)
         I = up.N
         perm = torch.stack([torch.arange(I), torch.arange(I) + I], 1).reshape(-1).to(gu.data.device)
@@ -313,7 +316,12 @@ class Loader:
         elif lt == "mla":
             L.mixer = loader_ext.mla(self, f"{p}.self_attn")
         if ft != "none":
-            L.ln2 = self.vec(f"{p}.post_attention_layernorm.weight")
+            if c.post_norms:          # Gemma: the norm named post_attention acts on the attention output
+                L.post_attn = self.vec(f"{p}.post_attention_layernorm.weight")
+                L.ln2 = self.vec(f"{p}.pre_feedforward_layernorm.weight")
+                L.post_ffn = self.vec(f"{p}.post_feedforward_layernorm.weight")
+            else:
+                L.ln2 = self.vec(f"{p}.post_attention_layernorm.weight")
         if ft == "dense":
             L.ffn = self.ffn(f"{p}.mlp")
         elif ft == "moe":

@@ -149,7 +149,7 @@ class SyntheticSource(TensorSource):
 
     def _ffn(self, p: str, inter: int, names=("gate_proj", "up_proj", "down_proj")):
         c = self.cfg
-        if c.ffn_act == "swiglu":
+        if c.ffn_act in ("swiglu", "geglu"):
             self._lin(f"{p}.{names[0]}", inter, c.hidden_size)
         self._lin(f"{p}.{names[1]}", inter, c.hidden_size)
         self._lin(f"{p}.{names[2]}", c.hidden_size, inter)
@@ -204,6 +204,9 @@ class SyntheticSource(TensorSource):
             self._lin(f"{q}.o_proj", c.hidden_size, c.num_heads * c.v_head_dim)
         if ft != "none":
             self._vec(f"{p}.post_attention_layernorm.weight", c.hidden_size)
+            if c.post_norms:
+                self._vec(f"{p}.pre_feedforward_layernorm.weight", c.hidden_size)
+                self._vec(f"{p}.post_feedforward_layernorm.weight", c.hidden_size)
         if ft == "dense":
             inter = c.dense_intermediate_size if (c.dense_intermediate_size and idx < c.first_dense_layers) else c.intermediate_size
             self._ffn(f"{p}.mlp", inter)

@@ -261,3 +261,91 @@ def test_arch_preflight_and_mxfp4_unpack():
     want = ref.e2m1_decode(codes).float() * torch.tensor([1.0] * 32 + [8.0] * 32)
     assert torch.equal(w, want) and w[0, 7] == 6.0 and w[0, 32 + 15] == -48.0
     assert torch.isnan(ref.e8m0_to_float(torch.tensor([255], dtype=torch.uint8)))[0]
+
+
+GEMMA = dict(model_type="gemma3_text", vocab_size=512, hidden_size=128, num_hidden_layers=3, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=32, intermediate_size=256, rms_norm_eps=1e-6, rope_theta=1e6,
+             rope_local_base_freq=1e4, sliding_window=8, sliding_window_pattern=3, query_pre_attn_scalar=64,
+             max_position_embeddings=512, rope_scaling={"rope_type": "linear", "factor": 8.0},
+             hidden_activation="gelu_pytorch_tanh", final_logit_softcapping=None, attn_logit_softcapping=None)
+
+
+def _oracle_gemma(hf, get, toks):
+    """fp32 Gemma 3 text forward: (1 + w) RMSNorm, scaled embeddings, sandwich norms, GeGLU, windowed
+    layers with their own RoPE base, linearly scaled RoPE on the global layers, tied lm_head."""
+    f = lambda n: get(n).float()
+    T = len(toks)
+    H, KV, D, eps = hf["num_attention_heads"], hf["num_key_value_heads"], hf["head_dim"], hf["rms_norm_eps"]
+    rms = lambda x, w: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (1.0 + w)
+
+    def rope(x, pos, theta, factor):
+        inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D)) / factor
+        ang = pos[:, None].float() * inv[None, :]
+        cos, sin = torch.cat([ang.cos()] * 2, -1)[:, None, :], torch.cat([ang.sin()] * 2, -1)[:, None, :]
+        return x * cos + torch.cat([-x[..., D // 2:], x[..., :D // 2]], -1) * sin
+    x = f("model.embed_tokens.weight")[torch.tensor(toks)] * torch.tensor(hf["hidden_size"] ** 0.5, dtype=torch.bfloat16).float()
+    pos = torch.arange(T)
+    for i in range(hf["num_hidden_layers"]):
+        p = f"model.layers.{i}"
+        local = (i + 1) % hf["sliding_window_pattern"] != 0
+        a = rms(x, f(f"{p}.input_layernorm.weight"))
+        q, k, v = ((a @ f(f"{p}.self_attn.{n}_proj.weight").T) for n in "qkv")
+        q, k, v = q.view(T, H, D), k.view(T, KV, D), v.view(T, KV, D)
+        q, k = rms(q, f(f"{p}.self_attn.q_norm.weight")), rms(k, f(f"{p}.self_attn.k_norm.weight"))
+        theta, factor = (hf["rope_local_base_freq"], 1.0) if local else (hf["rope_theta"], hf["rope_scaling"]["factor"])
+        q, k = rope(q, pos, theta, factor), rope(k, pos, theta, factor)
+        k, v = k.repeat_interleave(H // KV, 1), v.repeat_interleave(H // KV, 1)
+        s = torch.einsum("thd,shd->hts", q, k) * hf["query_pre_attn_scalar"] ** -0.5
+        mask = torch.triu(torch.ones(T, T, dtype=torch.bool), 1)
+        if local:
+            mask |= (pos[:, None] - pos[None, :]) >= hf["sliding_window"]
+        o = torch.einsum("hts,shd->thd", s.masked_fill(mask, float("-inf")).softmax(-1), v).reshape(T, H * D)
+        x = x + rms(o @ f(f"{p}.self_attn.o_proj.weight").T, f(f"{p}.post_attention_layernorm.weight"))
+        a = rms(x, f(f"{p}.pre_feedforward_layernorm.weight"))
+        g, u = a @ f(f"{p}.mlp.gate_proj.weight").T, a @ f(f"{p}.mlp.up_proj.weight").T
+        y = (torch.nn.functional.gelu(g, approximate="tanh") * u) @ f(f"{p}.mlp.down_proj.weight").T
+        x = x + rms(y, f(f"{p}.post_feedforward_layernorm.weight"))
+    return rms(x, f("model.norm.weight"))[-1] @ f("model.embed_tokens.weight").T
+
+
+def test_gemma3_text_matches_fp32_oracle(tmp_path):
+    cfg = from_hf_config(GEMMA, name="gemma")
+    assert cfg.window_layers == [8, 8, 0] and cfg.post_norms and cfg.ffn_act == "geglu" and cfg.tie_embeddings
+    assert abs(cfg.attn_scale - 0.125) < 1e-9 and abs(cfg.embed_scale - 128 ** 0.5) < 1e-9 and cfg.rope_local_theta == 1e4
+    syn = SyntheticSource(cfg, seed=4, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    assert "model.layers.0.pre_feedforward_layernorm.weight" in canon and "lm_head.weight" not in canon
+    save_file({k: v.contiguous() for k, v in canon.items()}, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "gemma3", "text_config": GEMMA}))   # multimodal wrapper
+    cfg2, src = open_checkpoint(tmp_path)
+    w = load_weights(cfg2, src)
+    toks = torch.randint(1, 512, (29,), generator=torch.Generator().manual_seed(2)).tolist()     # longer than the window
+    got = _engine_logits(cfg2, w, toks)
+    want = _oracle_gemma(GEMMA, lambda n: canon[n], toks)
+    err = (got - want).abs().max().item()
+    assert err < 0.05 * want.abs().max().item() + 1e-3, err
+    assert int(got.argmax()) == int(want.argmax())
+    with pytest.raises(ValueError, match="soft-capping"):
+        from_hf_config(dict(GEMMA, model_type="gemma2", attn_logit_softcapping=50.0))
+    capped = from_hf_config(dict(GEMMA, final_logit_softcapping=30.0))
+    lg = _engine_logits(capped, load_weights(capped, src), toks)
+    assert lg.abs().max() <= 30.0 and (lg - 30.0 * torch.tanh(got / 30.0)).abs().max() < 0.05
+
+
+@pytest.mark.gpu
+def test_gemma3_text_on_gpu_matches_fp32_oracle():
+    hf = dict(GEMMA, hidden_size=256, head_dim=64, intermediate_size=512, vocab_size=1024, query_pre_attn_scalar=64)
+    cfg = from_hf_config(hf, name="gemma")
+    syn = SyntheticSource(cfg, seed=4, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    w = load_weights(cfg, syn, device="cuda:0")
+    toks = torch.randint(1, 1024, (37,), generator=torch.Generator().manual_seed(2)).tolist()
+    dec = Decoder(cfg, w)
+    kv = PagedKvCache(KvCacheConfig(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim), 16, device="cuda:0")
+    nb = (len(toks) + 15) // 16
+    b = ForwardBatch.build([dict(tokens=toks, start_pos=0, blocks=list(range(1, nb + 1)))], 16, device="cuda:0")
+    lg, _ = dec.forward(b, LayerCaches(cfg, kv=kv))
+    got = lg[0].float().cpu()
+    want = _oracle_gemma(hf, lambda n: canon[n], toks)
+    err = (got - want).abs().max().item()
+    assert err < 0.06 * want.abs().max().item() + 1e-2, err
