@@ -252,6 +252,15 @@ class Loader:
         c = self.cfg
         q, k, v, o = (self.lin(f"{p}.{n}_proj") for n in "qkvo")
         per_q = c.head_dim * (2 if c.attn_output_gate else 1)
+        rope_perm_q = rope_perm_k = None
+        if c.rope_interleaved and c.rotary_dim > 0:
+            # the checkpoint rotates neighbouring pairs (2i, 2i + 1); the kernels rotate (i, i + r/2):
+            # re-order the rotary rows of every q / k head (q.k is invariant under a shared permutation)
+            r, D = c.rotary_dim, c.head_dim
+            head = list(range(0, r, 2)) + list(range(1, r, 2)) + list(range(r, D))
+            mk = lambda n: torch.tensor([h * D + j for h in range(n) for j in head], device=q.data.device)
+            rope_perm_q, rope_perm_k = mk(c.num_heads), mk(c.num_kv_heads)
+            q, k = ops.permute_rows(q, rope_perm_q), ops.permute_rows(k, rope_perm_k)
         hq = c.num_heads // self.tp_size
         if self.tp_size > 1:
             lo, hi = self._shard(c.num_heads)
@@ -272,6 +281,8 @@ class Loader:
         w.o_in_scale = self.input_scale(f"{p}.o_proj")
         if c.attn_bias and self.src.has(f"{p}.q_proj.bias"):
             qb, kb, vb = (self.src.get(f"{p}.{n}_proj.bias").to(self.dev).to(torch.bfloat16) for n in "qkv")
+            if rope_perm_q is not None:
+                qb, kb = qb[rope_perm_q.to(qb.device)], kb[rope_perm_k.to(kb.device)]
             if self.tp_size > 1:
                 qb = qb[lo * per_q:hi * per_q]
                 kb, vb = kb[klo * c.head_dim:khi * c.head_dim], vb[klo * c.head_dim:khi * c.head_dim]
@@ -316,7 +327,11 @@ class Loader:
         elif lt == "mla":
             L.mixer = loader_ext.mla(self, f"{p}.self_attn")
         if ft != "none":
-            if c.post_norms:          # Gemma: the norm named post_attention acts on the attention output
+            if c.post_norms and c.post_norm_names == "glm":
+                L.post_attn = self.vec(f"{p}.post_self_attn_layernorm.weight")
+                L.ln2 = self.vec(f"{p}.post_attention_layernorm.weight")
+                L.post_ffn = self.vec(f"{p}.post_mlp_layernorm.weight")
+            elif c.post_norms:        # Gemma: the norm named post_attention acts on the attention output
                 L.post_attn = self.vec(f"{p}.post_attention_layernorm.weight")
                 L.ln2 = self.vec(f"{p}.pre_feedforward_layernorm.weight")
                 L.post_ffn = self.vec(f"{p}.post_feedforward_layernorm.weight")

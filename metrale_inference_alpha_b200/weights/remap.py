@@ -120,7 +120,8 @@ def family_source(src: TensorSource, hf_cfg: Optional[dict]) -> TensorSource:
     resolvers: List[Resolve] = []
     if mt == "mixtral":
         resolvers.append(_mixtral)
-    if mt in ("phi3", "phi4") or src.has("model.layers.0.self_attn.qkv_proj.weight"):
+    if mt in ("phi3", "phi4", "glm4") or src.has("model.layers.0.self_attn.qkv_proj.weight") \
+            or src.has("model.layers.0.mlp.gate_up_proj.weight"):
         h = cfg.get("hidden_size", 0)
         heads = cfg.get("num_attention_heads", 1)
         hd = cfg.get("head_dim", h // max(1, heads))

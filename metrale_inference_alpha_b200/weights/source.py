@@ -204,7 +204,10 @@ class SyntheticSource(TensorSource):
             self._lin(f"{q}.o_proj", c.hidden_size, c.num_heads * c.v_head_dim)
         if ft != "none":
             self._vec(f"{p}.post_attention_layernorm.weight", c.hidden_size)
-            if c.post_norms:
+            if c.post_norms and c.post_norm_names == "glm":
+                self._vec(f"{p}.post_self_attn_layernorm.weight", c.hidden_size)
+                self._vec(f"{p}.post_mlp_layernorm.weight", c.hidden_size)
+            elif c.post_norms:
                 self._vec(f"{p}.pre_feedforward_layernorm.weight", c.hidden_size)
                 self._vec(f"{p}.post_feedforward_layernorm.weight", c.hidden_size)
         if ft == "dense":

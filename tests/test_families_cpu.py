@@ -349,3 +349,66 @@ def test_gemma3_text_on_gpu_matches_fp32_oracle():
     want = _oracle_gemma(hf, lambda n: canon[n], toks)
     err = (got - want).abs().max().item()
     assert err < 0.06 * want.abs().max().item() + 1e-2, err
+
+
+GLM4 = dict(BASE, model_type="glm4", partial_rotary_factor=0.5, attention_bias=True)
+
+
+def _oracle_glm4(hf, get, toks):
+    """fp32 GLM-4 forward: q/k/v bias, interleaved rotary on the first half of each head, sandwich
+    norms (no +1), SwiGLU from a fused gate_up projection."""
+    f = lambda n: get(n).float()
+    T = len(toks)
+    H, KV, D, eps = hf["num_attention_heads"], hf["num_key_value_heads"], hf["head_dim"], hf["rms_norm_eps"]
+    r = int(D * hf["partial_rotary_factor"])
+    pos = torch.arange(T)
+    inv = 1.0 / (hf["rope_theta"] ** (torch.arange(0, r, 2, dtype=torch.float32) / r))
+    ang = pos[:, None].float() * inv[None, :]
+    cos, sin = ang.cos().repeat_interleave(2, -1)[:, None, :], ang.sin().repeat_interleave(2, -1)[:, None, :]
+
+    def rope(x):
+        xr, xp = x[..., :r], x[..., r:]
+        x1, x2 = xr[..., 0::2], xr[..., 1::2]
+        rot = torch.stack([-x2, x1], -1).flatten(-2)
+        return torch.cat([xr * cos + rot * sin, xp], -1)
+    x = f("model.embed_tokens.weight")[torch.tensor(toks)]
+    for i in range(hf["num_hidden_layers"]):
+        p = f"model.layers.{i}"
+        a = _rms(x, f(f"{p}.input_layernorm.weight"), eps)
+        q, k, v = ((a @ f(f"{p}.self_attn.{n}_proj.weight").T + f(f"{p}.self_attn.{n}_proj.bias")) for n in "qkv")
+        q, k, v = rope(q.view(T, H, D)), rope(k.view(T, KV, D)), v.view(T, KV, D)
+        k, v = k.repeat_interleave(H // KV, 1), v.repeat_interleave(H // KV, 1)
+        s = torch.einsum("thd,shd->hts", q, k) / math.sqrt(D)
+        s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        o = torch.einsum("hts,shd->thd", s.softmax(-1), v).reshape(T, H * D)
+        x = x + _rms(o @ f(f"{p}.self_attn.o_proj.weight").T, f(f"{p}.post_self_attn_layernorm.weight"), eps)
+        a = _rms(x, f(f"{p}.post_attention_layernorm.weight"), eps)
+        g, u = a @ f(f"{p}.mlp.gate_proj.weight").T, a @ f(f"{p}.mlp.up_proj.weight").T
+        y = (torch.nn.functional.silu(g) * u) @ f(f"{p}.mlp.down_proj.weight").T
+        x = x + _rms(y, f(f"{p}.post_mlp_layernorm.weight"), eps)
+    return _rms(x, f("model.norm.weight"), eps)[-1] @ f("lm_head.weight").T
+
+
+def test_glm4_matches_fp32_oracle(tmp_path):
+    cfg = from_hf_config(GLM4, name="glm4")
+    assert cfg.rope_interleaved and cfg.rotary_dim == 16 and cfg.post_norms and cfg.attn_bias and cfg.ffn_act == "swiglu"
+    syn = SyntheticSource(cfg, seed=6, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    tensors = {}
+    for n, v in canon.items():                      # the checkpoint stores gate and up as one gate_up_proj
+        if ".mlp.gate_proj." in n or ".mlp.up_proj." in n:
+            continue
+        tensors[n] = v.contiguous()
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}.mlp"
+        tensors[f"{p}.gate_up_proj.weight"] = torch.cat([canon[f"{p}.gate_proj.weight"], canon[f"{p}.up_proj.weight"]])
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(GLM4))
+    cfg2, src = open_checkpoint(tmp_path)
+    w = load_weights(cfg2, src)
+    toks = torch.randint(1, 512, (23,), generator=torch.Generator().manual_seed(8)).tolist()
+    got = _engine_logits(cfg2, w, toks)
+    want = _oracle_glm4(GLM4, lambda n: canon[n], toks)
+    err = (got - want).abs().max().item()
+    assert err < 0.05 * want.abs().max().item() + 1e-3, err
+    assert int(got.argmax()) == int(want.argmax())
