@@ -99,6 +99,9 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--isl", type=int, default=128)
     b.add_argument("--osl", type=int, default=1024)
     b.add_argument("--json", action="store_true")
+    b.add_argument("--url", default=None, help="sweep a running server over HTTP (streaming chat requests) instead of an in-process engine")
+    b.add_argument("--api-key", default=None)
+    b.add_argument("--served-model-name", default="default")
 
     for name, helptext in (("tui", "live dashboard of a running server"), ("chat", "terminal chat with a running server")):
         t = sub.add_parser(name, help=helptext)
@@ -171,6 +174,15 @@ def doctor() -> dict:
 
 
 def run_benchmark(ns) -> List[dict]:
+    if getattr(ns, "url", None):
+        from ..bench.http_sweep import run_sweep
+        rows = run_sweep(ns.url, [int(c) for c in ns.concurrency.split(",")], ns.isl, ns.osl,
+                         model=ns.served_model_name, api_key=ns.api_key)
+        for r in rows:          # same columns as the in-process ladder
+            r.setdefault("ms_per_step", float("nan"))
+            r["ttft_p50_ms"] = r["ttft_p50_ms"] if r["ttft_p50_ms"] is not None else float("nan")
+            r["ttft_p99_ms"] = r["ttft_p99_ms"] if r["ttft_p99_ms"] is not None else float("nan")
+        return rows
     from ..bench.ladder import run_ladder
     return run_ladder(_engine_args(ns), [int(c) for c in ns.concurrency.split(",")], ns.isl, ns.osl)
 

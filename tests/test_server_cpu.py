@@ -4,6 +4,7 @@ grammar, rate limiter, levers, telemetry, CLI, and every route of the app driven
 FastAPI's test client over the tiny dense model. Mirrors the reference's server test
 strategy (``crates/server/tests``: golden request / response shapes, SSE framing, auth)."""
 import json
+import time
 
 import pytest
 import torch
@@ -709,3 +710,39 @@ def test_tui_dashboard_and_chat_against_the_app(client, tmp_path):
     d2.poll()
     assert "refused" in d2.summary()["error"]
     con.print(d2.render())
+
+
+def test_http_sweep_against_a_real_listening_server():
+    """uvicorn on a loopback port + the aiohttp SSE client of the benchmark: real sockets, real
+    streaming, concurrent requests batched by the engine."""
+    import socket
+    import threading
+
+    import uvicorn
+
+    from metrale_inference_alpha_b200.bench.http_sweep import run_sweep
+    from metrale_inference_alpha_b200.server.app import ServerConfig, create_app
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=8, max_model_len=512))
+    tok = load_tokenizer(None, eng.cfg.vocab_size)
+    app = create_app(eng, tok, ServerConfig(model_name="tiny", auth_tokens=["k"]))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    try:
+        end = time.time() + 20
+        while not server.started and time.time() < end:
+            time.sleep(0.05)
+        assert server.started
+        rows = run_sweep(f"http://127.0.0.1:{port}", [1, 4], isl_words=12, osl=5, model="tiny", api_key="k")
+        assert [r["concurrency"] for r in rows] == [1, 4]
+        for r in rows:
+            assert r["errors"] == 0 and r["completion_tokens"] == 5 * r["concurrency"], r
+            assert r["tok_s"] > 0 and r["ttft_p50_ms"] is not None and r["server_ttft_p50_ms"] is not None
+        bad = run_sweep(f"http://127.0.0.1:{port}", [2], isl_words=4, osl=2, model="tiny", api_key="wrong")[0]
+        assert bad["errors"] == 2 and "401" in bad["first_error"]
+    finally:
+        server.should_exit = True
+        th.join(timeout=20)
