@@ -152,10 +152,15 @@ def sample_rows(runner, plan, logits: torch.Tensor) -> Tuple[List[List[int]], Li
             fin = torch.isfinite(x)
             thr = x[fin].max() - p.top_n_sigma * x[fin].std()
             x.masked_fill_(x < thr, float("-inf"))
+    temps = [p.temperature for p in P]
+    for r, it in enumerate(row_item):
+        ad = it.seq.req.params.adaptive
+        if ad is not None and it.verify == 0:
+            temps[r] = ad.step(logits[r], it.seq.tokens[it.seq.prompt_len:], it.seq.req.params.grammar is not None)
     t = lambda vals, dt: torch.tensor(vals, dtype=dt, device=dev)
     seeds = [(p.seed if p.seed is not None else it.seq.seq_id * 1000003) & ((1 << 62) - 1)
              for p, it in zip(P, row_item)]
-    ids, lp = ops.sample(logits, t([p.temperature for p in P], torch.float32),
+    ids, lp = ops.sample(logits, t(temps, torch.float32),
                          t([p.top_k for p in P], torch.int32), t([p.top_p for p in P], torch.float32),
                          t([p.min_p for p in P], torch.float32), t(seeds, torch.int64),
                          t([it.seq.sample_step for it in row_item], torch.int64))

@@ -40,6 +40,7 @@ class SamplingParams:
     adapter: Optional[str] = None       # LoRA adapter name (engine.load_adapter)
     # reasoning budget: once `thinking_budget` output tokens passed without the closing marker
     # `think_end_ids`, the sampler forces that marker token by token (0 = no limit)
+    adaptive: Optional[object] = None   # sampling.adaptive.AdaptiveSampling: per-token temperature
     thinking_budget: int = 0
     think_end_ids: List[int] = field(default_factory=list)
 
@@ -52,7 +53,7 @@ class SamplingParams:
         """True when plain device argmax / device sampling cannot serve the request."""
         return (bool(self.logit_bias) or self.top_n_sigma > 0 or self.grammar is not None or self.top_logprobs > 0
                 or self.dry_multiplier > 0 or self.lz_penalty > 0
-                or (self.thinking_budget > 0 and bool(self.think_end_ids)))
+                or (self.thinking_budget > 0 and bool(self.think_end_ids)) or self.adaptive is not None)
 
     @property
     def has_penalties(self) -> bool:

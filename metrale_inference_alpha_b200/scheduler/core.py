@@ -101,6 +101,9 @@ class SchedulerCore:
             self.spill.restore(seq, self)
             (self.running if seq.num_computed >= len(seq.tokens) - 1 else self.prefilling).append(seq)
             seq.status = SeqStatus.DECODE if seq in self.running else SeqStatus.PREFILL
+        order = getattr(self.policy, "order_waiting", None)
+        if order is not None:
+            order(self.waiting)
         while self.waiting and self.num_active < cfg.max_num_seqs:
             seq = self.waiting[0]
             if seq.is_finished():

@@ -13,7 +13,7 @@ class SchedulerConfig:
     max_prefill_tokens: int = 8192       # per-step prefill token budget (chunked prefill)
     max_model_len: int = 32768
     block_size: int = 16
-    policy: str = "fifo"                 # fifo | tbt
+    policy: str = "fifo"                 # fifo | tbt | slai
     tbt_deadline_ms: float = 100.0
     decode_reserve_tokens: int = 256     # admission watermark: prompt + min(max_tokens, this)
     enable_prefix_caching: bool = True
@@ -56,5 +56,47 @@ class TbtDeadlinePolicy:
         self.last_decode = now
 
 
+class SlaiPolicy:
+    """Deadline-aware scheduling (the reference's `--scheduler slai`,
+    ``crates/server/src/scheduling_policy.rs:69-153``): no prefill is started while the running
+    decodes have waited 80 % of the time-between-tokens deadline since their last token; prefill
+    chunks are never shrunk (a smaller slice does not shorten the step, it only slows the prefill);
+    admission takes the front of the queue first, then the shortest prompts, so that short requests
+    overtake long ones but the head of the line can never starve."""
+
+    def __init__(self, deadline_ms: float):
+        self.deadline = deadline_ms / 1e3
+        self.last_decode = time.monotonic()
+
+    def should_prefill(self, have_prefill: bool, have_decode: bool, now: float) -> bool:
+        if not have_prefill:
+            return False
+        if not have_decode:
+            return True
+        return (now - self.last_decode) < 0.8 * self.deadline
+
+    def prefill_budget(self, cfg: SchedulerConfig, have_decode: bool) -> int:
+        return cfg.max_prefill_tokens
+
+    def note_decode(self, now: float) -> None:
+        self.last_decode = now
+
+    @staticmethod
+    def order_waiting(waiting) -> None:
+        """In place: seat 0 stays, the rest are ordered by prompt length (stable)."""
+        if len(waiting) > 2:
+            head = waiting.popleft()
+            rest = sorted(waiting, key=lambda s: len(s.tokens))
+            waiting.clear()
+            waiting.append(head)
+            waiting.extend(rest)
+
+
 def make_policy(cfg: SchedulerConfig):
-    return TbtDeadlinePolicy(cfg.tbt_deadline_ms) if cfg.policy == "tbt" else FifoPolicy()
+    if cfg.policy == "tbt":
+        return TbtDeadlinePolicy(cfg.tbt_deadline_ms)
+    if cfg.policy == "slai":
+        return SlaiPolicy(cfg.tbt_deadline_ms)
+    if cfg.policy != "fifo":
+        raise ValueError(f"unknown scheduler policy {cfg.policy!r} (fifo | tbt | slai)")
+    return FifoPolicy()

@@ -50,6 +50,7 @@ class ServerConfig:
     default_min_p: float = 0.0
     max_thinking_budget: int = 0        # cap (and default) of a request's thinking_token_budget; 0 = none
     content_loop_watchdog: float = 0.0  # > 0: LZ loop penalty applied when the request sets none
+    adaptive_sampling: bool = False     # per-token temperature by zone, confidence, entropy run and repetition
     dump_dir: str = ""                  # write every request / response pair as JSON files here
     otlp_endpoint: str = ""             # OTLP/HTTP collector (also METRALE_OTLP_ENDPOINT)
     tool_grammar: bool = False          # constrain tool calls with a grammar even under tool_choice "auto"
@@ -208,6 +209,11 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         except ValueError as e:             # GrammarError: the schema / pattern / grammar does not compile
             raise HTTPException(400, f"invalid grammar: {e}")
         sp.adapter = body.get("adapter") or getattr(app.state, "active_adapter", None)
+        if cfg.adaptive_sampling and sp.temperature > 0:
+            from ..sampling.adaptive import AdaptiveSampling
+            opened = tokenizer.encode("<tool_call>") if tools and cfg.tool_call_parser in ("hermes", "qwen3", "qwen") else []
+            closed = tokenizer.encode("</tool_call>") if opened else []
+            sp.adaptive = AdaptiveSampling(sp.temperature, list(think_end_ids), bool(thinking), list(opened), list(closed))
         if thinking and think_end_ids:
             th = body.get("thinking") if isinstance(body.get("thinking"), dict) else {}
             want = body.get("thinking_token_budget") or th.get("budget_tokens") or 0

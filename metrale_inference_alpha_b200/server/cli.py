@@ -81,6 +81,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--max-thinking-budget", type=int, default=0, help="cap and default of thinking_token_budget (0 = none)")
     s.add_argument("--content-loop-watchdog", type=float, default=0.0, metavar="PENALTY",
                    help="> 0: loop penalty for requests that set no repetition_detection")
+    s.add_argument("--adaptive-sampling", action="store_true",
+                   help="per-token temperature from the generation zone, top-1 confidence, low-entropy runs and repetition")
     s.add_argument("--dump", default="", metavar="DIR", help="write every POST request as a JSON file into DIR")
     s.add_argument("--otlp-endpoint", default="", help="OTLP/HTTP collector base URL for metric pushes")
     s.add_argument("--warmup-prompt", default=None, help="generate from this prompt once before listening")
@@ -280,7 +282,7 @@ def serve(ns) -> None:
     cfg = ServerConfig(model_name=ns.served_model_name or str(ns.model), auth_tokens=ns.api_key,
                        default_top_n_sigma=ns.default_top_n_sigma, default_min_p=ns.default_min_p,
                        max_thinking_budget=ns.max_thinking_budget, content_loop_watchdog=ns.content_loop_watchdog,
-                       dump_dir=ns.dump, otlp_endpoint=ns.otlp_endpoint,
+                       dump_dir=ns.dump, otlp_endpoint=ns.otlp_endpoint, adaptive_sampling=ns.adaptive_sampling,
                        rate_per_s=ns.rate_limit, tool_call_parser=ns.tool_call_parser, tool_grammar=getattr(ns, "tool_grammar", False),
                        reasoning_format=ns.reasoning_format, default_max_tokens=ns.default_max_tokens,
                        tool_max_tokens=ns.tool_max_tokens,

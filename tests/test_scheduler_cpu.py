@@ -234,3 +234,37 @@ def test_snapshot_reports_counts():
     sch.add_request(req(0))
     s = sch.snapshot()
     assert s["waiting"] + s["prefilling"] + s["running"] == 1
+
+
+def test_slai_policy_orders_admission_and_protects_decodes():
+    from collections import deque
+
+    from metrale_inference_alpha_b200.scheduler.policy import SchedulerConfig, SlaiPolicy, make_policy
+    p = make_policy(SchedulerConfig(policy="slai", tbt_deadline_ms=100.0))
+    assert isinstance(p, SlaiPolicy)
+    p.note_decode(10.0)
+    assert p.should_prefill(True, True, 10.05)                     # 50 ms waited: prefill may start
+    assert not p.should_prefill(True, True, 10.081)                # 81 ms = past 80 % of the deadline: decode first
+    assert p.should_prefill(True, False, 99.0)                     # nothing is decoding: always prefill
+    assert not p.should_prefill(False, True, 10.0)
+    cfg = SchedulerConfig(max_prefill_tokens=4096)
+    assert p.prefill_budget(cfg, True) == 4096                     # chunks are never shrunk
+
+    class S:
+        def __init__(self, n):
+            self.tokens = [0] * n
+    q = deque(S(n) for n in (900, 50, 400, 10, 400))
+    first_400 = q[2]
+    SlaiPolicy.order_waiting(q)
+    assert [len(s.tokens) for s in q] == [900, 10, 50, 400, 400] and q[3] is first_400     # head kept, rest shortest first, stable
+    import pytest as _pt
+    with _pt.raises(ValueError):
+        make_policy(SchedulerConfig(policy="nope"))
+    # through the scheduler with two seats: the head of the queue and the shortest of the rest go first
+    sch, _ = make(policy="slai", max_num_seqs=2, blocks=256)
+    for i, n in enumerate((60, 40, 20, 50)):
+        sch.add_request(req(i, n_prompt=n, max_tokens=2))
+    plan = sch.plan()
+    assert sorted(len(it.seq.tokens) for it in plan.items) == [20, 60]
+    outs, _ = drive(sch, ScriptedExecutor())
+    assert len(outs) == 4                                       # every request still finishes

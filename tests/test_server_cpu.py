@@ -746,3 +746,54 @@ def test_http_sweep_against_a_real_listening_server():
     finally:
         server.should_exit = True
         th.join(timeout=20)
+
+
+def test_adaptive_sampling_rules_and_http_path():
+    from metrale_inference_alpha_b200.sampling.adaptive import FREE, STRUCTURED, THINKING, TOOL_CALL, AdaptiveSampling
+    a = AdaptiveSampling(0.0)
+    assert a.temperature() == 0.0 and a.greedy(torch.zeros(8))                   # temperature 0 stays 0
+    a = AdaptiveSampling(1.0, think_end_ids=[9], thinking_open=True, tool_open_ids=[5, 6], tool_close_ids=[7])
+    assert a.update_zone([1, 2], False) == THINKING and a.temperature() == 1.0
+    assert a.update_zone([1, 9, 2], False) == FREE
+    assert a.update_zone([1, 9, 2], True) == STRUCTURED and abs(a.temperature() - 0.6) < 1e-9
+    assert a.update_zone([1, 5, 6, 3], True) == TOOL_CALL and a.temperature() == 0.3   # capped; wins over grammar
+    assert a.update_zone([1, 5, 6, 3, 7, 4], False) == THINKING                   # call closed, marker 9 not seen yet
+    # greedy gate: thresholds per zone
+    conf = torch.tensor([5.0, 0.0, 0.0, 0.0])                                     # top-1 = 0.98
+    mid = torch.tensor([2.5, 0.0, 0.0, 0.0])                                      # top-1 = 0.80
+    a.zone = FREE
+    assert a.greedy(conf) and not a.greedy(mid)
+    a.zone = TOOL_CALL
+    assert a.greedy(mid)
+    assert not a.greedy(torch.full((4,), float("-inf")))
+    # entropy run: boosts after 8 / 16 / 32 confident tokens, reset by one uncertain token
+    a = AdaptiveSampling(0.5)
+    for n, want in ((7, 0.5), (1, 0.6), (8, 0.7), (16, 0.8)):
+        for _ in range(n):
+            a.observe(conf)
+        assert abs(a.temperature() - want) < 1e-6, (n, a.temperature())
+    a.observe(torch.zeros(16))
+    assert a.low_entropy_run == 0 and a.temperature() == 0.5
+    # repetition: a looping tail multiplies the temperature, varied output does not
+    a.update_repetition([3, 4] * 40)
+    assert a.lz_ratio < 0.15 and abs(a.temperature() - 0.9) < 1e-6
+    b = AdaptiveSampling(0.5)
+    b.update_repetition(list(range(1000, 1100)))
+    assert b.lz_ratio > 0.35 and b.temperature() == 0.5
+    b.update_repetition(list(range(1000, 1105)))                                  # fewer than 16 new tokens: not recomputed
+    assert b._lz_checked_at == 100
+    a.zone = TOOL_CALL
+    assert a.temperature() == 0.3                                                 # no boost, no multiplier in a tool call
+    # through the server: the flag attaches the state, seeded sampling stays reproducible
+    from fastapi.testclient import TestClient
+    from metrale_inference_alpha_b200.server.app import ServerConfig, create_app
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=256))
+    tok = load_tokenizer(None, eng.cfg.vocab_size)
+    with TestClient(create_app(eng, tok, ServerConfig(model_name="tiny", adaptive_sampling=True))) as c:
+        body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 12, "temperature": 0.9, "seed": 3,
+                "return_token_ids": True}
+        x = c.post("/v1/chat/completions", json=body).json()["choices"][0]["token_ids"]
+        y = c.post("/v1/chat/completions", json=body).json()["choices"][0]["token_ids"]
+        assert x == y and len(x) == 12
+        z = c.post("/v1/chat/completions", json=dict(body, temperature=0)).json()["choices"][0]["token_ids"]
+        assert len(z) == 12
