@@ -50,6 +50,7 @@ class ServerConfig:
     default_min_p: float = 0.0
     max_thinking_budget: int = 0        # cap (and default) of a request's thinking_token_budget; 0 = none
     content_loop_watchdog: float = 0.0  # > 0: LZ loop penalty applied when the request sets none
+    loop_detector: bool = True          # cross-turn repetition: bias / mask the tool-call opener when an agent loops
     adaptive_sampling: bool = False     # per-token temperature by zone, confidence, entropy run and repetition
     dump_dir: str = ""                  # write every request / response pair as JSON files here
     otlp_endpoint: str = ""             # OTLP/HTTP collector (also METRALE_OTLP_ENDPOINT)
@@ -127,6 +128,12 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         think_end_ids = list(tokenizer.encode(_close))
     except Exception:
         think_end_ids = []
+    _opener = {"hermes": "<tool_call>", "qwen3": "<tool_call>", "qwen": "<tool_call>", "qwen3_xml": "<tool_call>",
+               "qwen3_coder": "<tool_call>", "mistral": "[TOOL_CALLS]", "minimax_xml": "<minimax:tool_call>"}.get(cfg.tool_call_parser)
+    try:
+        tool_open_first = tokenizer.encode(_opener)[0] if _opener else None
+    except Exception:
+        tool_open_first = None
     engine.args.eos_token_id = engine.args.eos_token_id if engine.args.eos_token_id is not None else eos
 
     @app.middleware("http")
@@ -198,6 +205,13 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         text = renderer.render(msgs, tools=tools, add_generation_prompt=True, enable_thinking=thinking, **kw)
         ids = tokenizer.encode(text)
         sp = _sampling_from(body, cfg)
+        if tools and cfg.loop_detector and tool_open_first is not None:
+            from .loop_detector import check_loops
+            verdict = check_loops(msgs, True)
+            if verdict.state.kind != "none":
+                tel.inc(f"loop_{verdict.state.kind}")
+                sp.logit_bias = dict(sp.logit_bias)
+                sp.logit_bias[tool_open_first] = -1e4 if verdict.mask else sp.logit_bias.get(tool_open_first, 0.0) + verdict.bias
         try:
             sp.grammar = grammar_for_response_format(body.get("response_format"), tokenizer, eos)
             forced = choice == "required" or (isinstance(choice, dict) and choice.get("type") not in ("auto", "none"))

@@ -797,3 +797,50 @@ def test_adaptive_sampling_rules_and_http_path():
         assert x == y and len(x) == 12
         z = c.post("/v1/chat/completions", json=dict(body, temperature=0)).json()["choices"][0]["token_ids"]
         assert len(z) == 12
+
+
+def test_cross_turn_loop_detector():
+    from metrale_inference_alpha_b200.server import loop_detector as LD
+    call = lambda q: {"role": "assistant", "content": "Let me search the index for that file again to be sure.",
+                      "tool_calls": [{"id": "c", "type": "function",
+                                      "function": {"name": "search_files", "arguments": json.dumps({"query": q, "path": "/src", "limit": 20})}}]}
+    tool = lambda text: {"role": "tool", "tool_call_id": "c", "content": text}
+    user = {"role": "user", "content": "find the config loader"}
+    assert LD.detect([LD.signature(call("a")), LD.signature(call("a"))]).kind == "none"        # fewer than 3 signatures
+    same3 = [user, call("config loader"), tool("no results"), call("config loader"), tool("no results"),
+             call("config loader"), tool("no results")]
+    v = LD.check_loops(same3, tools_active=True)
+    assert v.state.kind == "suppress" and v.state.run_length == 3 and v.state.score >= 0.65 and v.mask and v.bias == -4.0
+    assert LD.check_loops(same3, tools_active=False).mask is False
+    failing = [user] + [m for _ in range(3) for m in (call("config loader"), tool("Error: index not found"))]
+    v = LD.check_loops(failing, True)
+    assert v.state.kind == "suppress" and not v.mask and "failed" in v.reason
+    moving = [user, call("config loader"), tool("3 results: a b c"), call("config loader"), tool("5 results: a b c d e"),
+              call("config loader"), tool("9 results")]
+    v = LD.check_loops(moving, True)
+    assert v.state.kind == "suppress" and not v.mask and "change" in v.reason
+    varied = [user, call("config loader"), tool("x"),
+              {"role": "assistant", "content": "The loader lives in settings.py; I will open it and read the parse function now."},
+              {"role": "assistant", "content": "Done: the function reads YAML first and falls back to environment variables when a key is missing."}]
+    assert LD.check_loops(varied, True).state.kind == "none"
+    os_env = __import__("os").environ
+    os_env["METRALE_LOOP_NO_SUPPRESS"] = "1"
+    try:
+        assert LD.check_loops(same3, True).mask is False
+    finally:
+        del os_env["METRALE_LOOP_NO_SUPPRESS"]
+    assert LD.jaccard(set(), {1}) == 0.0 and LD.jaccard({1, 2}, {2, 3}) == 1 / 3
+
+
+def test_loop_detector_reaches_the_sampler_over_http(client):
+    call = lambda: {"role": "assistant", "content": "search it again now ok go on pls",
+                    "tool_calls": [{"id": "c", "type": "function", "function": {"name": "s", "arguments": json.dumps({"q": "x", "n": 2})}}]}
+    msgs = [{"role": "user", "content": "find it"}]
+    for _ in range(3):
+        msgs += [call(), {"role": "tool", "tool_call_id": "c", "content": "none"}]
+    tools = [{"type": "function", "function": {"name": "s", "parameters": {"type": "object"}}}]
+    before = client.get("/metrics").text
+    r = client.post("/v1/chat/completions", json={"messages": msgs, "tools": tools, "max_tokens": 4, "temperature": 0})
+    assert r.status_code == 200
+    after = client.get("/metrics").text
+    assert "metrale_loop_suppress_total" in after and "metrale_loop_suppress_total" not in before
