@@ -28,16 +28,19 @@ class KvCacheConfig:
     dtype: str = "bf16"             # bf16 | fp8
     v_head_dim: Optional[int] = None
     has_v: bool = True              # False for MLA latent caches
+    high_precision_layers: tuple = ()   # cache layers kept in bf16 although dtype is fp8
 
     @property
     def elem_bytes(self) -> int:
         return 1 if self.dtype == "fp8" else 2
 
+    def layer_dtype(self, i: int) -> str:
+        return "bf16" if (self.dtype == "fp8" and i in self.high_precision_layers) else self.dtype
+
     def block_bytes(self) -> int:
         """Bytes one block occupies across all layers (K and V)."""
-        k = self.block_size * self.kv_heads * self.head_dim * self.elem_bytes
-        v = self.block_size * self.kv_heads * (self.v_head_dim or self.head_dim) * self.elem_bytes
-        return self.num_layers * (k + (v if self.has_v else 0))
+        per_elem = self.block_size * self.kv_heads * (self.head_dim + ((self.v_head_dim or self.head_dim) if self.has_v else 0))
+        return sum(per_elem * (1 if self.layer_dtype(i) == "fp8" else 2) for i in range(self.num_layers))
 
     def blocks_for_budget(self, nbytes: int) -> int:
         return max(0, nbytes // max(1, self.block_bytes()))
@@ -102,13 +105,13 @@ class PagedKvCache:
         self.device = torch.device(device)
         from . import make_allocator
         self.allocator = make_allocator(num_blocks)
-        dt = torch.uint8 if cfg.dtype == "fp8" else torch.bfloat16
         shape_k = (num_blocks, cfg.block_size, cfg.kv_heads, cfg.head_dim)
         shape_v = (num_blocks, cfg.block_size, cfg.kv_heads, cfg.v_head_dim or cfg.head_dim)
         fill = torch.full if poison else None
         self.k: List[torch.Tensor] = []
         self.v: List[Optional[torch.Tensor]] = []
-        for _ in range(cfg.num_layers):
+        for li in range(cfg.num_layers):
+            dt = torch.uint8 if cfg.layer_dtype(li) == "fp8" else torch.bfloat16
             if poison:
                 # new blocks start as 0xFF bytes (NaN in bf16 / e4m3) so a read of a never
                 # written slot shows up in the output (kv_poison in the reference)

@@ -93,6 +93,7 @@ class ModelConfig:
     # precision
     weight_format: str = "bf16"
     kv_dtype: str = "bf16"
+    kv_high_precision_layers: tuple = ()    # model layers whose KV stays bf16 when kv_dtype is fp8
     max_position: int = 32768
 
     def __post_init__(self):

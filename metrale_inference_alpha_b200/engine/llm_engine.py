@@ -60,7 +60,24 @@ class EngineArgs:
     swap_space_bytes: int = 8 << 30
     swap_dir: Optional[str] = None
     kv_cache_dtype: str = "auto"                       # auto (the model config's) | bf16 | fp8
+    kv_high_precision_layers: str = ""                 # e.g. "0,1,63" or "first:2,last:2": these layers keep bf16 KV under fp8
     oom_guard_mb: int = 4096                           # device memory left unclaimed when sizing the KV pool
+
+
+def parse_layer_list(spec: str, num_layers: int) -> tuple:
+    """"0,5,63", "first:2", "last:3" and combinations -> sorted layer indices."""
+    out = set()
+    for part in (p.strip() for p in spec.split(",") if p.strip()):
+        if part.startswith("first:"):
+            out.update(range(min(num_layers, int(part[6:]))))
+        elif part.startswith("last:"):
+            out.update(range(max(0, num_layers - int(part[5:])), num_layers))
+        else:
+            i = int(part)
+            if not 0 <= i < num_layers:
+                raise ValueError(f"layer {i} out of range (0..{num_layers - 1})")
+            out.add(i)
+    return tuple(sorted(out))
 
 
 class LLMEngine:
@@ -86,6 +103,10 @@ class LLMEngine:
             if args.kv_cache_dtype not in ("bf16", "fp8"):
                 raise ValueError(f"kv_cache_dtype must be auto | bf16 | fp8, not {args.kv_cache_dtype!r}")
             cfg = dataclasses.replace(cfg, kv_dtype=args.kv_cache_dtype)
+        if args.kv_high_precision_layers:
+            import dataclasses
+            cfg = dataclasses.replace(cfg, kv_high_precision_layers=parse_layer_list(args.kv_high_precision_layers,
+                                                                                       cfg.num_layers))
         self.cfg: ModelConfig = cfg
         self.fault = FaultLatch()
         t0 = time.time()

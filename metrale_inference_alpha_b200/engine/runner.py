@@ -51,8 +51,10 @@ def kv_config(cfg: ModelConfig, w: ModelW, block_size: int, mtp: bool = False) -
         if lw.kind == "attention":
             kvh = lw.mixer.kv_heads
             break
-    return KvCacheConfig(1 if mtp else max(1, len(cfg.attention_layers())), kvh, cfg.head_dim, block_size,
-                         cfg.kv_dtype)
+    att = cfg.attention_layers()
+    hp = () if mtp else tuple(i for i, layer in enumerate(att) if layer in set(cfg.kv_high_precision_layers))
+    return KvCacheConfig(1 if mtp else max(1, len(att)), kvh, cfg.head_dim, block_size, cfg.kv_dtype,
+                         high_precision_layers=hp)
 
 
 class _Stager:

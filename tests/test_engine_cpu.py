@@ -141,3 +141,25 @@ def test_dry_and_lz_penalties_tables_and_effect_on_generation():
         return best
     assert longest_repeat(dry) <= longest_repeat(plain)
     assert longest_repeat(dry) < 12
+
+
+def test_kv_high_precision_layers_mix_dtypes_per_layer():
+    from metrale_inference_alpha_b200.cache import KvCacheConfig
+    from metrale_inference_alpha_b200.engine.llm_engine import parse_layer_list
+    assert parse_layer_list("first:2,last:1,5", 8) == (0, 1, 5, 7)
+    import pytest as _pt
+    with _pt.raises(ValueError):
+        parse_layer_list("9", 8)
+    plain = KvCacheConfig(4, 2, 64, 16, "fp8")
+    mixed = KvCacheConfig(4, 2, 64, 16, "fp8", high_precision_layers=(0, 3))
+    assert mixed.block_bytes() == plain.block_bytes() * 6 // 4             # two of four layers at 2 bytes
+    assert KvCacheConfig(4, 2, 64, 16, "bf16", high_precision_layers=(0,)).block_bytes() == 2 * plain.block_bytes()
+    eng = LLMEngine(EngineArgs(model="tiny-dense", max_model_len=128, num_kv_blocks=32, kv_cache_dtype="fp8",
+                               kv_high_precision_layers="first:1"))
+    kv = eng.runner.kv
+    assert kv.k[0].dtype == torch.bfloat16 and kv.k[1].dtype == torch.uint8 and kv.v[0].dtype == torch.bfloat16
+    prompts = [list(range(5, 40))]
+    hp = eng.generate(prompts, SamplingParams(max_tokens=8, temperature=0.0))[0].output_ids
+    all_bf16 = LLMEngine(EngineArgs(model="tiny-dense", max_model_len=128, num_kv_blocks=32)).generate(
+        prompts, SamplingParams(max_tokens=8, temperature=0.0))[0].output_ids
+    assert len(hp) == 8 and len(all_bf16) == 8

@@ -139,3 +139,18 @@ def test_http_surface_over_a_gpu_engine():
         if r["choices"][0]["finish_reason"] == "stop":
             assert isinstance(json.loads(text), dict)
         assert "metrale_engine_graph_replays" in c.get("/metrics").text
+
+
+def test_mixed_kv_precision_per_layer_graph_equals_eager():
+    """fp8 KV with the first layer kept in bf16: both cache kernels' instantiations run in one
+    forward pass, under CUDA graphs as well as eagerly."""
+    outs = {}
+    for graphs in (False, True):
+        eng = LLMEngine(EngineArgs(model=preset("tiny-dense"), device="cuda", max_num_seqs=8, max_model_len=256,
+                                   use_cuda_graphs=graphs, enable_prefix_caching=False, kv_cache_dtype="fp8",
+                                   kv_high_precision_layers="first:1"))
+        kv = eng.runner.kv
+        assert kv.k[0].dtype == torch.bfloat16 and kv.k[1].dtype == torch.uint8
+        outs[graphs] = _drive(eng, _arrivals())
+    assert outs[True] == outs[False]
+    assert [len(o) for o in outs[True]] == [70, 45, 12, 50, 40, 3]
