@@ -5,6 +5,7 @@
     python benchmarks/ncu_case.py --op attn   [--m 128 --ctx 640]
     python benchmarks/ncu_case.py --op gemm   [--m 128 --n 5120 --k 17408 --fmt nvfp4]
     python benchmarks/ncu_case.py --op rowop  [--m 128 --k 5120]
+    python benchmarks/ncu_case.py --op mla    [--m 64 --ctx 2048]
 """
 import argparse
 import math
@@ -47,6 +48,20 @@ def main():
         for _ in range(a.iters):
             ops.paged_attention(q, kc, vc, bt, qs, ql, cl, max_q_len=1, max_ctx=2048, scale=1 / math.sqrt(D),
                                 k_scale=sc, v_scale=sc)
+    elif a.op == "mla":
+        # absorbed MLA decode: 128 heads of 576-wide latent queries against a [blocks, 16, 1, 576] latent cache
+        from metrale_inference_alpha_b200.ops import mla_cuda
+        H, ROW, bs = 128, 576, 16
+        nblk = (a.ctx + bs - 1) // bs
+        cache = (torch.randn(M * nblk + 1, bs, 1, ROW, device=DEV) * 0.3).to(torch.bfloat16)
+        bt = torch.zeros(M, max(nblk, 128), dtype=torch.int32, device=DEV)
+        bt[:, :nblk] = (torch.arange(M * nblk, device=DEV, dtype=torch.int32) + 1).view(M, nblk)
+        q = (torch.randn(M, H, ROW, device=DEV) * 0.3).to(torch.bfloat16)
+        qs = torch.arange(M, device=DEV, dtype=torch.int32)
+        ql = torch.ones(M, device=DEV, dtype=torch.int32)
+        cl = torch.full((M,), a.ctx, device=DEV, dtype=torch.int32)
+        for _ in range(a.iters):
+            mla_cuda.mla_attention(q, cache, bt, qs, ql, cl, max_q_len=1, max_ctx=max(nblk, 128) * bs, scale=1 / math.sqrt(192))
     elif a.op == "gemm":
         ws = rand_weight(a.n, a.k, a.fmt, 3)
         act = ops.quantize_act(torch.randn(M, a.k, device=DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[a.fmt])
