@@ -25,6 +25,9 @@ IN_COPY, IN_RMSNORM, IN_SILU_MUL, IN_RELU2, IN_SIGMOID_GATE, IN_GATED_RMSNORM = 
 OUT_MODE = {"bf16": 0, "fp8_row": 1, "fp8_g128": 2, "nvfp4": 3}
 
 launch_count = 0  # kernels launched through this module (bench.py reports it)
+# bit 128 of the GEMM's dbg word: prefill GEMMs (several 128-token tiles) also run on the persistent kernel
+# (NVFP4 prefill GEMMs measure 1.5x faster there; METRALE_PERSISTENT_PREFILL=0 keeps one tile per CTA)
+_PERSIST_PREFILL = 128 if os.environ.get("METRALE_PERSISTENT_PREFILL", "1") != "0" else 0
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -366,7 +369,7 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
         a.alpha = w.gscale
     a.epilogue, a.out_f32 = int(swiglu), int(out_f32)
     a.ws, a.ws_bytes, a.status = _ptr(rt.ws), rt.ws_bytes, _ptr(rt.status)
-    a.force_tn, a.force_splits, a.sm_count, a.dbg = force_tn, force_splits, rt.sm_count, dbg
+    a.force_tn, a.force_splits, a.sm_count, a.dbg = force_tn, force_splits, rt.sm_count, dbg | _PERSIST_PREFILL
     a.trace = _ptr(trace)
     a.no_cluster = int(no_cluster)
     qact = None

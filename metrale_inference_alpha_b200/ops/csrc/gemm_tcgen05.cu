@@ -739,12 +739,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(8) float s_ascale[TN];
+  __shared__ __align__(8) float s_ascale[2][TN];
 
   const int warp = threadIdx.x >> 5;
   const int n_tiles = (p.N + kTileN - 1) / kTileN;
+  const int m_tiles = (p.M + TN - 1) / TN;               // 1 for decode; prefill walks token tiles fastest
   const int nkb = p.num_kb;
-  const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // grid <= n_tiles
+  // work item t = blockIdx.x + i * gridDim.x covers weight tile t / m_tiles and token tile t % m_tiles
+  const int my_tiles = (n_tiles * m_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // grid <= tiles
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -776,16 +778,23 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     // ------------------------------------------------------------ producer
     if (mb::elect_one()) {
       const int total = my_tiles * nkb;                   // k blocks this CTA streams, over all its tiles
+      // both streams are issued in increasing g: the (work item, k block) cursors advance
+      // incrementally, with one division per work item instead of several per k block
+      int w_kb = 0, w_item = (int)blockIdx.x, w_tile = w_item / m_tiles;
       auto load_w = [&](int g) {
-        const int tile = (int)blockIdx.x + (g / nkb) * (int)gridDim.x, kb = g % nkb, s = g % kStages;
-        mb::tma_load_2d(sA(s), &tmA, &full_bar[s], kb * kCoordStep, tile * kTileN);
+        const int s = g % kStages;
+        mb::tma_load_2d(sA(s), &tmA, &full_bar[s], w_kb * kCoordStep, w_tile * kTileN);
         if constexpr (KIND == KIND_NVFP4)
-          mb::bulk_load(sSFA(s), p.sfa + ((size_t)tile * p.sf_k64 + (size_t)kb * 4) * 512, 2048, &full_bar[s]);
+          mb::bulk_load(sSFA(s), p.sfa + ((size_t)w_tile * p.sf_k64 + (size_t)w_kb * 4) * 512, 2048, &full_bar[s]);
+        if (++w_kb == nkb) { w_kb = 0; w_item += (int)gridDim.x; w_tile = w_item / m_tiles; }
       };
+      int x_kb = 0, x_item = (int)blockIdx.x, x_mt = x_item % m_tiles;
       auto load_x = [&](int g) {
-        const int kb = g % nkb, s = g % kStages;
-        mb::tma_load_2d(sB(s), &tmB, &full_bar[s], kb * kCoordStep, 0);
-        if constexpr (KIND == KIND_NVFP4) mb::bulk_load(sSFB(s), p.sfb + (size_t)kb * 4 * 512, 2048, &full_bar[s]);
+        const int s = g % kStages;
+        mb::tma_load_2d(sB(s), &tmB, &full_bar[s], x_kb * kCoordStep, x_mt * TN);
+        if constexpr (KIND == KIND_NVFP4)
+          mb::bulk_load(sSFB(s), p.sfb + ((size_t)((x_mt * TN) / 128) * p.sf_k64 + (size_t)x_kb * 4) * 512, 2048, &full_bar[s]);
+        if (++x_kb == nkb) { x_kb = 0; x_item += (int)gridDim.x; x_mt = x_item % m_tiles; }
       };
       const int pre = min(total, kStages);
       for (int g = 0; g < pre; ++g) {                     // weights do not depend on the preceding kernel
@@ -864,22 +873,29 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const int et = threadIdx.x - 64;
     const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
     const bool swiglu = p.epilogue == EPI_SWIGLU;
-    const int m_valid = min(p.M, TN);
     mb::pdl_wait();
-    for (int j = et; j < TN; j += kPersistThreads - 64) {
-      float sc = 1.f;
-      if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
-        if (p.a_scale && j < m_valid) sc = __ldg(&p.a_scale[j]);
-      }
-      s_ascale[j] = sc;
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kPersistThreads - 64) : "memory");
     const int f = q * 32 + lane;                          // weight row of this thread inside a tile
     const float outq_inv6gs = p.outq ? 1.f / (6.f * p.outq_gs) : 0.f;
     bool ok = true;
     for (int it = 0; it < my_tiles && ok; ++it) {
-      const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+      const int t_lin = (int)blockIdx.x + it * (int)gridDim.x;
+      const int tile = t_lin / m_tiles;
+      const int m_base = (t_lin % m_tiles) * TN;           // first token row of this tile
+      const int m_valid = min(p.M - m_base, TN);
       const int buf = it & 1;
+      if (it == 0 || m_tiles > 1) {
+        // per-token activation scales of this token tile. Two buffers and one barrier per tile:
+        // nobody can be two tiles ahead of a thread that has not passed the barrier in between.
+        for (int j = et; j < TN; j += kPersistThreads - 64) {
+          float sc = 1.f;
+          if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
+            if (p.a_scale && j < m_valid) sc = __ldg(&p.a_scale[m_base + j]);
+          }
+          s_ascale[buf][j] = sc;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kPersistThreads - 64) : "memory");
+      }
+      const float* asc = s_ascale[m_tiles > 1 ? buf : 0];
       ok = mb::mbar_wait(&acc_full[buf], (it >> 1) & 1, p.status, MB_ST_TIMEOUT_EPI);
       if (!ok) break;
       mb::tc_fence_after();
@@ -901,12 +917,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
             const int m0 = c * 16 + j;
-            const float2 as = *reinterpret_cast<const float2*>(&s_ascale[m0]);
+            const float2 as = *reinterpret_cast<const float2*>(&asc[m0]);
             const float x0 = v[j] * (wsc * as.x), x1 = v[j + 1] * (wsc * as.y);
             const float other = __shfl_xor_sync(0xffffffffu, odd ? x0 : x1, 1);
             const float gate = odd ? other : x0, up = odd ? x1 : other;
             const float y = mb::silu(gate) * up;
-            const int m = m0 + (odd ? 1 : 0);
+            const int ml = m0 + (odd ? 1 : 0);                 // row inside the tile
+            const int m = m_base + ml;
             if (p.outq) {
               // This warp's 16 even lanes hold one 16-wide quantisation block of token m0, its odd
               // lanes the same block of token m0 + 1 (block index along the consumer's K: tile * 4 + q).
@@ -924,23 +941,23 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
               const float upper = __shfl_down_sync(0xffffffffu, scaled, 2);
               const uint32_t byte = mb::e2m1x2_pack(scaled, upper);
               const int i = lane >> 1;                      // output index inside the block
-              if (m < m_valid && !(i & 1) && n < p.N)
+              if (ml < m_valid && !(i & 1) && n < p.N)
                 p.outq[(size_t)m * p.ldq + ((tile * 64 + q * 16 + i) >> 1)] = (uint8_t)byte;
-              if (m < m_valid && i == 0 && n < p.N) {
+              if (ml < m_valid && i == 0 && n < p.N) {
                 const int kb = tile * 4 + q;
                 p.outq_sf[((size_t)(m >> 7) * p.outq_sf_k64 + (kb >> 2)) * 512 + mb::sf_tile_offset(m & 127, kb & 3)] = sfc;
               }
-            } else if (n_ok && m < m_valid) {
+            } else if (n_ok && ml < m_valid) {
               outp[(size_t)m * p.ldo] = __float2bfloat16(y);
             }
           }
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int m = c * 16 + j;
-            if (m < m_valid && n < p.N) {
-              float y = v[j] * wsc * s_ascale[m];
-              const size_t o = (size_t)m * p.ldo + n;
+            const int ml = c * 16 + j;
+            if (ml < m_valid && n < p.N) {
+              float y = v[j] * wsc * asc[ml];
+              const size_t o = (size_t)(m_base + ml) * p.ldo + n;
               if (p.residual) y += __bfloat162float(p.residual[o]);
               if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = y;
               else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16(y);
@@ -1180,11 +1197,13 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   p.m_fastest = (!grouped && tiles_m >= 8 && tiles_m <= 65535 && tiles_n <= 65535 && !(a->dbg & 64)) ? 1 : 0;
   dim3 grid(p.m_fastest ? tiles_m : tiles_n, p.m_fastest ? tiles_n : tiles_m, splits);
   rc = MB_ERR_UNSUPPORTED;
-  // more weight-row tiles than SMs and a single token tile: persistent CTAs, balanced tile counts
-  if (!grouped && a->tp_size <= 1 && splits == 1 && tiles_m == 1 && tn <= 128 && kind != KIND_FP8_BLOCK &&
-      tiles_n > sms && !a->trace && !(a->dbg & 16)) {
-    const int waves = (tiles_n + sms - 1) / sms;
-    const int grid_x = (tiles_n + waves - 1) / waves;
+  // more tiles than SMs: persistent CTAs, balanced tile counts. One token tile (decode) always;
+  // several token tiles (prefill, 128-token tiles) when bit 128 of dbg asks for it.
+  const bool multi_m_ok = tiles_m > 1 && tn == 128 && (a->dbg & 128) && !a->outq;
+  if (!grouped && a->tp_size <= 1 && splits == 1 && (tiles_m == 1 || multi_m_ok) && tn <= 128 && kind != KIND_FP8_BLOCK &&
+      tiles > sms && (tiles_m > 1 || tiles_n > sms) && !a->trace && !(a->dbg & 16)) {
+    const int waves = (tiles + sms - 1) / sms;
+    const int grid_x = (tiles + waves - 1) / waves;
     switch (kind) {
       case KIND_BF16: return dispatch_persistent<KIND_BF16>(tn, tmA, tmB, p, grid_x, stream);
       case KIND_FP8: return dispatch_persistent<KIND_FP8>(tn, tmA, tmB, p, grid_x, stream);

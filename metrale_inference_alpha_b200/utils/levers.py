@@ -18,6 +18,7 @@ LEVERS: Dict[str, str] = {
     "METRALE_TELEMETRY": "off | basic | kernel",
     "METRALE_MAX_BODY_BYTES": "HTTP request body limit in bytes (default 32 MiB)",
     "METRALE_LOOP_NO_SUPPRESS": "1 = the cross-turn loop detector never masks the tool-call opener (soft bias only)",
+    "METRALE_PERSISTENT_PREFILL": "0 = prefill GEMMs (several token tiles) keep one tile per CTA instead of the persistent two-accumulator kernel",
     "METRALE_NVTX": "1 = NVTX ranges around engine steps (for Nsight timelines)",
     "METRALE_OTLP_ENDPOINT": "OTLP/HTTP collector base URL; set = push metrics every METRALE_OTLP_PERIOD_S (default 10)",
     "METRALE_OTLP_PERIOD_S": "seconds between OTLP pushes",

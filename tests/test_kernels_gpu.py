@@ -148,6 +148,39 @@ def test_gemm_persistent_swiglu_and_residual():
     ops.check_status(DEV)
 
 
+@pytest.mark.parametrize("M", [129, 300, 512])
+def test_gemm_persistent_prefill_tiles_match_the_one_tile_per_cta_kernel(M, monkeypatch):
+    """Several 128-token tiles on the persistent kernel (work items walk token tiles fastest, the
+    activation scales are reloaded per tile): bit-identical to the one-tile-per-CTA kernel, plain,
+    with a residual and through the SwiGLU epilogue; ragged last token tile and ragged last weight tile."""
+    monkeypatch.setattr(ops, "_PERSIST_PREFILL", 128)
+    N, K = 128 * 80 + 64, 768
+    x, w = _mk(M, N, K, 11)
+    res = torch.randn(M, N, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).to(DEV)
+    for fmt in ("nvfp4", "fp8_row", "bf16"):
+        if fmt == "nvfp4":
+            qw = ops.make_weight(w[:128 * 80], fmt).to(DEV)       # NVFP4 scale tiles want whole 128-row weight tiles
+            r = res[:, :128 * 80].contiguous()
+        else:
+            qw, r = ops.make_weight(w, fmt).to(DEV), res
+        act = ops.quantize_act(x.to(DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[fmt])
+        a = ops.linear(act, qw, residual=r)
+        b = ops.linear(act, qw, residual=r, dbg=16)               # dbg bit 16: one tile per CTA
+        assert torch.equal(a, b), fmt
+        assert torch.equal(ops.linear(act, qw), ops.linear(act, qw, dbg=16)), fmt
+    I = 64 * 160
+    _, wg = _mk(M, I, K, 1)
+    _, wu = _mk(M, I, K, 2)
+    wi = ops.interleave_gate_up(wg, wu)
+    for fmt in ("nvfp4", "bf16"):
+        qw = ops.make_weight(wi, fmt).to(DEV)
+        act = ops.quantize_act(x.to(DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[fmt])
+        got, want = ops.linear(act, qw, swiglu=True), ops.linear(act, qw, swiglu=True, dbg=16)
+        # the two epilogues multiply the scales in a different order: equal to a bf16 rounding step
+        _close(got, want.float().cpu(), rtol=1e-2, atol=1e-2 * want.float().abs().max().item())
+    ops.check_status(DEV)
+
+
 def _dequant_act(act):
     """NVFP4 activation on the device -> fp32 matrix on the CPU."""
     nb = (act.M + 127) // 128
