@@ -42,7 +42,8 @@ SMI_FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.act
 
 def reference_arm(args) -> int:
     """The reference is a Rust workspace (no setup.py / pyproject, needs cargo + crates.io +
-    CUDA 13.0): `pip install --no-index ... /root/reference` reports "not installable"."""
+    CUDA 13.0): an offline `pip install --no-index --target baseline/_ref <reference checkout>`
+    reports "not installable"."""
     line = {"impl": "reference",
             "unavailable": "reference is a Cargo workspace (Rust 1.93.1 + CUDA 13.0 + ~400 crates); "
                            "pip reports 'neither setup.py nor pyproject.toml found'; no cargo/rustc offline"}
