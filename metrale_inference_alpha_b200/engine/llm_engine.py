@@ -136,8 +136,6 @@ class LLMEngine:
             per_rank = (max(self.sched_cfg.max_prefill_tokens, args.max_num_seqs * 8) + self.tp.size - 1) // self.tp.size
             self.tp.ep = EpAllToAll(self.tp.rank, self.tp.size, self.device, cfg.hidden_size, per_rank,
                                     cfg.experts_per_token)
-            # the exchange's sequence numbers are launch arguments: steps run eagerly on this path
-            self.runner.use_graphs = False
         self.calibrated_layers = 0
         if args.static_act_scales and cfg.weight_format == "nvfp4" and self.device.type == "cuda":
             self.calibrated_layers = self.runner.calibrate_static_scales()

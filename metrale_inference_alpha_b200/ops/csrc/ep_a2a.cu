@@ -30,6 +30,8 @@ struct A2aParams {
   int* zone_count[8];          // per destination rank: [world] rows received from each source
   uint32_t* flag[8];           // per destination rank: [world] sequence numbers
   uint32_t seq;
+  const uint32_t* seq_ptr;     // when set, the sequence number is read from device memory at run time
+                               // (a replayed CUDA graph then sees the counter of the current step)
   uint32_t* done;              // local: CTA completion counter (self-resetting)
   uint32_t* status;
 };
@@ -67,14 +69,17 @@ __global__ void a2a_scatter_kernel(const A2aParams p) {
     const int d = threadIdx.x;
     p.zone_count[d][p.rank] = p.send_count[d];
     __threadfence_system();
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[d] + p.rank), "r"(p.seq) : "memory");
+    const uint32_t seq = p.seq_ptr ? *reinterpret_cast<const volatile uint32_t*>(p.seq_ptr) : p.seq;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[d] + p.rank), "r"(seq) : "memory");
   }
 }
 
 // one CTA: thread s waits (bounded) until source s has raised its flag to `seq`
-__global__ void a2a_wait_kernel(const uint32_t* flags, int world, uint32_t seq, uint32_t* status) {
+__global__ void a2a_wait_kernel(const uint32_t* flags, int world, uint32_t seq, const uint32_t* seq_ptr,
+                                uint32_t* status) {
   mb::pdl_wait();
   if ((int)threadIdx.x >= world) return;
+  if (seq_ptr) seq = *reinterpret_cast<const volatile uint32_t*>(seq_ptr);
   const uint32_t* f = flags + threadIdx.x;
   const long long t0 = clock64();
   while (mb::ld_acquire_sys(f) != seq) {
@@ -106,6 +111,7 @@ struct MbA2aArgs {
   unsigned int seq;
   void* done;
   void* status;
+  const void* seq_ptr;   // optional device-resident sequence number (overrides `seq`)
 };
 
 int mb_a2a_scatter(const MbA2aArgs* a, cudaStream_t stream) {
@@ -124,6 +130,7 @@ int mb_a2a_scatter(const MbA2aArgs* a, cudaStream_t stream) {
     p.flag[r] = reinterpret_cast<uint32_t*>(a->flag[r]);
   }
   p.seq = a->seq;
+  p.seq_ptr = reinterpret_cast<const uint32_t*>(a->seq_ptr);
   p.done = reinterpret_cast<uint32_t*>(a->done);
   p.status = reinterpret_cast<uint32_t*>(a->status);
   return (int)mb::launch_kernel(a2a_scatter_kernel, dim3(a->n), dim3(128), (size_t)0, stream, p);
@@ -133,7 +140,15 @@ int mb_a2a_wait(const void* flags, int world, unsigned int seq, void* status, cu
   if (!flags || world < 1 || world > 8) return MB_ERR_BAD_ARG;
   return (int)mb::launch_kernel(a2a_wait_kernel, dim3(1), dim3(32), (size_t)0, stream,
                                 reinterpret_cast<const uint32_t*>(flags), world, (uint32_t)seq,
-                                reinterpret_cast<uint32_t*>(status));
+                                static_cast<const uint32_t*>(nullptr), reinterpret_cast<uint32_t*>(status));
+}
+
+// same wait with the sequence number read from device memory (graph-capturable)
+int mb_a2a_wait_dev(const void* flags, int world, const void* seq_ptr, void* status, cudaStream_t stream) {
+  if (!flags || !seq_ptr || world < 1 || world > 8) return MB_ERR_BAD_ARG;
+  return (int)mb::launch_kernel(a2a_wait_kernel, dim3(1), dim3(32), (size_t)0, stream,
+                                reinterpret_cast<const uint32_t*>(flags), world, 0u,
+                                reinterpret_cast<const uint32_t*>(seq_ptr), reinterpret_cast<uint32_t*>(status));
 }
 
 }  // extern "C"

@@ -5,7 +5,8 @@ the rank that owns the expert, is processed there by the grouped tcgen05 expert 
 output travels back into the slot it was sent from, where the source rank applies the routing
 weights. Both directions are ``ops/csrc/ep_a2a.cu``: 16-byte peer stores into symmetric-memory
 landing zones, per-source counts and sequence-numbered flags (release / bounded acquire), double
-buffered by parity; no NCCL call and no host synchronisation, so the layer stays inside CUDA graphs.
+buffered by parity; no NCCL call and no host synchronisation, and the sequence number is read
+from device memory, so the layer stays inside CUDA graphs.
 
 World size 1 runs the same kernels against the rank's own zone (the single-GPU test).
 """
@@ -26,11 +27,12 @@ class A2aArgs(C.Structure):
                 ("dst_rank", C.c_void_p), ("dst_slot", C.c_void_p), ("meta", C.c_void_p), ("send_count", C.c_void_p),
                 ("world", C.c_int), ("rank", C.c_int), ("capacity", C.c_int),
                 ("zone", _VP8), ("zone_meta", _VP8), ("zone_count", _VP8), ("flag", _VP8),
-                ("seq", C.c_uint), ("done", C.c_void_p), ("status", C.c_void_p)]
+                ("seq", C.c_uint), ("done", C.c_void_p), ("status", C.c_void_p), ("seq_ptr", C.c_void_p)]
 
 
 _native.register_optional("mb_a2a_scatter", [C.POINTER(A2aArgs), C.c_void_p])
 _native.register_optional("mb_a2a_wait", [C.c_void_p, C.c_int, C.c_uint, C.c_void_p, C.c_void_p])
+_native.register_optional("mb_a2a_wait_dev", [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p])
 
 
 class EpAllToAll:
@@ -63,6 +65,10 @@ class EpAllToAll:
             self.ptrs = [self.buf.data_ptr()]
         self.done = torch.zeros(2, dtype=torch.int32, device=self.device)
         self.seq = 0
+        # the sequence number the kernels publish and wait for lives on the device and is advanced
+        # by a device op, so that a replayed CUDA graph sees the current step's value; the host
+        # copy only chooses the parity of the landing zones at launch (fixed per call site in a graph)
+        self.seq_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     # ------------------------------------------------------------------ layout helpers
     def _off(self, parity: int, what: str) -> int:
@@ -83,6 +89,7 @@ class EpAllToAll:
         a.rows, a.row_ld, a.n, a.row_bytes = _ptr(rows), rows.stride(0) * rows.element_size(), rows.shape[0], self.H * 2
         a.dst_rank, a.dst_slot, a.meta, a.send_count = _ptr(dst_rank), _ptr(dst_slot), _ptr(meta), _ptr(send_count)
         a.world, a.rank, a.capacity, a.seq = self.world, self.rank, self.capacity, self.seq
+        a.seq_ptr = _ptr(self.seq_dev)
         zone, cnt, flag = ("x", "xcnt", "xflag") if which == "x" else ("y", "ycnt", "yflag")
         for r in range(self.world):
             a.zone[r] = self.ptrs[r] + self._off(parity, zone)
@@ -97,8 +104,8 @@ class EpAllToAll:
     def _wait(self, parity: int, which: str) -> None:
         from ..ops import _count, _ptr, _stream, runtime
         flags = self.ptrs[self.rank] + self._off(parity, "xflag" if which == "x" else "yflag")
-        _native.check(_native.lib().mb_a2a_wait(flags, self.world, self.seq, _ptr(runtime(self.device).status), _stream()),
-                      "a2a_wait")
+        _native.check(_native.lib().mb_a2a_wait_dev(flags, self.world, _ptr(self.seq_dev),
+                                                    _ptr(runtime(self.device).status), _stream()), "a2a_wait")
         _count()
 
     # ------------------------------------------------------------------ the MoE exchange
@@ -109,6 +116,7 @@ class EpAllToAll:
         T, K, W, Cp = x.shape[0], idx.shape[1], self.world, self.capacity
         assert T * K <= Cp and x.dtype == torch.bfloat16 and x.shape[1] == self.H
         self.seq += 1
+        self.seq_dev.add_(1)
         parity = self.seq & 1
         dev = x.device
         # ---- where every (token, k) pair goes: destination rank and its slot in my region there

@@ -47,6 +47,31 @@ def main():
         ok = ok and good
         if rank == 0:
             print(f"T={T:4d} max err {err:.4g} (ref {ref:.3g}) {'ok' if good else 'MISMATCH'}", flush=True)
+    # the same exchange inside a CUDA graph, replayed: the sequence number comes from device memory,
+    # so every replay publishes and waits for a fresh value
+    tp.ep = ep
+    xs = (torch.randn(16, cfg.hidden_size, generator=torch.Generator().manual_seed(9)) * 0.5).to(torch.bfloat16).to(dev)
+    for _ in range(2):
+        moe_block(dec, xs, lw)                                    # warm-up outside the capture
+    torch.cuda.synchronize()
+    dist.barrier()
+    gph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gph):
+        y1 = moe_block(dec, xs, lw)
+        y2 = moe_block(dec, y1.to(torch.bfloat16), lw)               # two exchanges per replay (both parities)
+    tp.ep = None
+    want1 = moe_block(dec, xs, lw)
+    want2 = moe_block(dec, want1.to(torch.bfloat16), lw)
+    for rep in range(3):
+        gph.replay()
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        err = (y2.float() - want2.float()).abs().max().item()
+        ref = want2.float().abs().max().item()
+        good = err <= 3e-2 * max(1.0, ref)
+        ok = ok and good
+        if rank == 0:
+            print(f"graph replay {rep}: max err {err:.4g} (ref {ref:.3g}) {'ok' if good else 'MISMATCH'}", flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
