@@ -71,6 +71,27 @@ argmax_kernel(const T* __restrict__ logits, long long ld, int V, int* __restrict
       const float v = ld_logit<T>(x, i);
       if (v > best || (v == best && i < bidx)) { best = v; bidx = i; }
     }
+  } else if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    // bf16 logits: eight per 16-byte load (the decode step's lm_head writes bf16)
+    const uint4* x8 = reinterpret_cast<const uint4*>(x);
+    const int V8 = V >> 3;
+    for (int i8 = threadIdx.x; i8 < V8; i8 += blockDim.x) {
+      const uint4 q = x8[i8];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int i = i8 * 8 + k;
+        // a bf16 is the upper half of the fp32 with the same value
+        const float v = __uint_as_float((k & 1) ? (w[k >> 1] & 0xFFFF0000u) : (w[k >> 1] << 16));
+        if (i == mask_a || i == mask_b) continue;
+        if (v > best || (v == best && i < bidx)) { best = v; bidx = i; }
+      }
+    }
+    for (int i = (V8 << 3) + threadIdx.x; i < V; i += blockDim.x) {
+      if (i == mask_a || i == mask_b) continue;
+      const float v = ld_logit<T>(x, i);
+      if (v > best || (v == best && i < bidx)) { best = v; bidx = i; }
+    }
   } else {
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
       if (i == mask_a || i == mask_b) continue;

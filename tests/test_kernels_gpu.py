@@ -436,6 +436,17 @@ def test_argmax_and_logprob():
     _close(lp, lp_ref, 1e-3, 1e-3)
     xf = torch.randn(4, 4096, generator=g)
     assert torch.equal(ops.argmax(xf.to(DEV)).cpu(), ops.argmax(xf))
+    # bf16 rows read with 16-byte loads: ragged tail (V % 8 != 0), maxima in the last lanes and in
+    # the tail, negative-only rows, a masked maximum, an odd row pitch (the scalar path)
+    xb = (torch.randn(6, 1003, generator=g) - 4.0).to(torch.bfloat16)
+    xb[0, 1002] = 9.0
+    xb[1, 999] = 9.0
+    xb[2, 7] = xb[2, 8] = 9.0
+    xb[3, 500] = 9.0
+    assert torch.equal(ops.argmax(xb.to(DEV)).cpu(), ops.argmax(xb))
+    assert torch.equal(ops.argmax(xb.to(DEV), mask_ids=(500, 1002)).cpu(), ops.argmax(xb, mask_ids=(500, 1002)))
+    wide = torch.randn(5, 1024, generator=g).to(torch.bfloat16)
+    assert torch.equal(ops.argmax(wide.to(DEV)).cpu(), ops.argmax(wide))
 
 
 def test_sample_matches_reference_draws():
