@@ -234,7 +234,8 @@ class LLMEngine:
                 self.fault.set(str(e))
                 raise FatalDeviceError(str(e)) from e
             raise
-        before = {it.seq.seq_id: len(it.seq.tokens) for it in plan.items}
+        track = self.spec_mode != "none"                   # the gate / ladder bookkeeping is only read when speculating
+        before = {it.seq.seq_id: len(it.seq.tokens) for it in plan.items} if track else None
         drafts = None
         outs = sch.apply(plan, result, None)
         if speculate:
@@ -251,7 +252,7 @@ class LLMEngine:
                         room = it.seq.req.params.max_tokens - it.seq.num_output - 1
                         it.seq.drafts = list(d[:max(0, room)])
         dt = time.perf_counter() - t0
-        if plan.kind in ("decode", "verify"):
+        if track and plan.kind in ("decode", "verify"):
             emitted = sum(len(it.seq.tokens) - before[it.seq.seq_id] for it in plan.items)
             self.gate.record(emitted, dt)
             self.spec_stats.steps += 1

@@ -213,8 +213,9 @@ class SchedulerCore:
 
     def _decode_items(self) -> List[SeqStep]:
         items = []
+        preempted = False                                   # membership is re-checked only after a preemption
         for seq in list(self.running):
-            if seq not in self.running:
+            if preempted and seq not in self.running:
                 continue                                    # preempted while planning
             drafts = seq.drafts
             feed = [seq.tokens[-1]] + drafts
@@ -229,6 +230,7 @@ class SchedulerCore:
                         self._finish(seq, FinishReason.LENGTH)
                         feed = None
                         break
+                    preempted = True
                     items = [i for i in items if i.seq is not victim]
             if feed is None:
                 continue
