@@ -34,3 +34,31 @@ def test_speculative_modes_are_lossless_on_gpu(mode):
     spec, eng = _run("cuda", speculative=mode, num_drafts=3)
     assert spec == base
     assert eng.spec_stats.drafted > 0
+
+
+def test_grammar_masks_follow_draft_rows_and_rewind_to_the_accepted_prefix():
+    """Speculative verify rows with a grammar: row j is masked from the matcher state after drafts
+    1..j, and the matcher is rewound to what was accepted. Output must be a legal prefix of the
+    grammar and identical to the non-speculative run."""
+    from metrale_inference_alpha_b200 import grammar as G
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    from metrale_inference_alpha_b200.server.tokenizer import load_tokenizer
+    outs = {}
+    for spec in ("none", "ngram"):
+        eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=256,
+                                   speculative=spec, num_drafts=3, mtp_gate=False))
+        tok = load_tokenizer(None, eng.cfg.vocab_size)
+        g = G.compile_regex(r"(ab|abc|abab| )+\.")
+        prompt = tok.encode("abab abab abab abab abab abab ")          # gives the n-gram proposer something to repeat
+        res = []
+        for _ in range(2):
+            sp = SamplingParams(max_tokens=24, temperature=0.0, grammar=G.TokenMatcher(g, tok, None))
+            res.append(eng.generate([prompt], sp)[0])
+        outs[spec] = [r.output_ids for r in res]
+        for r in res:
+            text = b"".join(tok.token_bytes(t) for t in r.output_ids)
+            assert G.GrammarMatcher(g).feed_bytes(text), text
+        if spec == "ngram":
+            assert eng.spec_stats.drafted > 0                       # the verify path really ran
+    assert outs["ngram"] == outs["none"]
