@@ -35,6 +35,7 @@ class ModelConfig:
     rope_scaling: Optional[dict] = None     # HF `rope_scaling` (linear / llama3 / yarn); None = plain RoPE
     rotary_dim: int = 0                 # 0 -> head_dim; -1 -> no RoPE (Nemotron-H attention)
     qk_norm: bool = False
+    qk_norm_full: bool = False          # the q / k RMSNorm spans all heads of the projection (MiniMax-M2), not one head
     attn_output_gate: bool = False      # q_proj emits [Q_h | G_h] per head, o = attn * sigmoid(G)
     sliding_window: int = 0
     attn_scale: float = 0.0             # softmax scale; 0 -> head_dim ** -0.5 (Gemma: query_pre_attn_scalar ** -0.5)
@@ -281,7 +282,7 @@ def preset(name: str, **kw) -> ModelConfig:
 # ----------------------------------------------------------------------------- HF config.json
 _HF_ARCH = {
     "llama": "dense_gqa", "qwen2": "dense_gqa", "qwen3": "dense_gqa", "mistral": "dense_gqa",
-    "glm4": "dense_gqa", "gemma3_text": "dense_gqa", "gemma3": "dense_gqa", "gemma2": "dense_gqa",
+    "minimax_m2": "dense_gqa", "glm4": "dense_gqa", "gemma3_text": "dense_gqa", "gemma3": "dense_gqa", "gemma2": "dense_gqa",
     "phi3": "dense_gqa", "qwen3_moe": "dense_gqa", "qwen2_moe": "dense_gqa", "mixtral": "dense_gqa",
     "qwen3_5": "qwen_hybrid", "qwen3_5_moe": "qwen_hybrid", "qwen3_next": "qwen_hybrid",
     "qwen3_5_text": "qwen_hybrid", "qwen3_5_moe_text": "qwen_hybrid",
@@ -351,6 +352,15 @@ def from_hf_config(cfg: dict, name: str = "model") -> ModelConfig:
                       window_layers=[win if t == "sliding_attention" else 0 for t in lt], sliding_window=0,
                       rope_local_theta=float(cfg.get("rope_local_base_freq", 0.0) or 0.0),
                       final_logit_softcap=float(cfg.get("final_logit_softcapping") or 0.0))
+        if mt == "minimax_m2":
+            if cfg.get("shared_intermediate_size"):
+                raise ValueError("MiniMax shared experts are not supported")
+            kw.update(qk_norm=bool(cfg.get("use_qk_norm", True)), qk_norm_full=cfg.get("qk_norm_type", "per_layer") == "per_layer",
+                      rotary_dim=int(cfg.get("rotary_dim", kw["head_dim"])), ffn_types=["moe"] * L,
+                      num_experts=int(cfg.get("num_local_experts", 0)), experts_per_token=int(cfg.get("num_experts_per_tok", 8)),
+                      moe_intermediate_size=cfg.get("intermediate_size", 0),
+                      router="sigmoid" if cfg.get("scoring_func", "sigmoid") == "sigmoid" else "softmax",
+                      router_renormalize=True, router_scaling=float(cfg.get("routed_scaling_factor", 1.0)))
         if mt == "glm4":
             kw.update(post_norms=True, post_norm_names="glm", rope_interleaved=True,
                       attn_bias=bool(cfg.get("attention_bias", True)),

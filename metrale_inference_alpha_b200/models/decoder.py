@@ -119,9 +119,19 @@ class Decoder:
                 lora.apply(qkv, xb, li, "q", batch.adapter_rows, 0)
             lora.apply(qkv, xb, li, "k", batch.adapter_rows, w.heads * qhs)
             lora.apply(qkv, xb, li, "v", batch.adapter_rows, w.heads * qhs + w.kv_heads * D)
+        qn, kn = w.q_norm, w.k_norm
+        if c.qk_norm_full and qn is not None:
+            # the norm spans the whole projection (all heads): normalised in place here, then the
+            # fused kernel only rotates and writes the cache
+            nq, nk = w.heads * qhs, w.kv_heads * D
+            for lo, n, wt in ((0, nq, qn), (nq, nk, kn)):
+                part = qkv[:, lo:lo + n].float()
+                part = part * torch.rsqrt(part.pow(2).mean(-1, keepdim=True) + c.rms_eps) * wt.float()
+                qkv[:, lo:lo + n] = part.to(qkv.dtype)
+            qn = kn = None
         q = ops.qk_norm_rope_kvwrite(
             qkv, Hq=w.heads, Hkv=w.kv_heads, D=D, positions=batch.positions, slots=batch.slot_mapping,
-            k_cache=kc, v_cache=vc, q_norm_w=w.q_norm, k_norm_w=w.k_norm, plus_one=c.norm_plus_one,
+            k_cache=kc, v_cache=vc, q_norm_w=qn, k_norm_w=kn, plus_one=c.norm_plus_one,
             eps=c.rms_eps, cos=cos, sin=sin, q_head_stride=qhs, k_scale=ks, v_scale=vs)
         fmt = ACT_FOR_WEIGHT[w.o.fmt]
         static = w.o_in_scale if (fmt == "nvfp4" and self.calib is None and not c.attn_output_gate) else 0.0

@@ -289,6 +289,8 @@ class Loader:
             w.qkv_bias = torch.cat([qb, kb, vb]).contiguous()
         if self.src.has(f"{p}.q_norm.weight"):
             w.q_norm, w.k_norm = self.vec(f"{p}.q_norm.weight"), self.vec(f"{p}.k_norm.weight")
+            if c.qk_norm_full and self.tp_size > 1:
+                raise NotImplementedError("a q / k norm that spans all heads is served on single-rank engines")
         return w
 
     # ---- dense ffn

@@ -76,6 +76,8 @@ class MappedSource(TensorSource):
 
 
 def _mixtral(name: str):
+    if name.endswith(".mlp.gate.e_score_correction_bias"):        # MiniMax keeps the routing bias beside the gate
+        return name[:-len("mlp.gate.e_score_correction_bias")] + "block_sparse_moe.e_score_correction_bias", None
     m = re.match(r"(.*\.)mlp\.(gate\.weight|experts\.(\d+)\.(gate|up|down)_proj\.(.+))$", name)
     if not m:
         return None
@@ -118,7 +120,7 @@ def family_source(src: TensorSource, hf_cfg: Optional[dict]) -> TensorSource:
         cfg = dict(cfg["text_config"])
     mt = cfg.get("model_type", "")
     resolvers: List[Resolve] = []
-    if mt == "mixtral":
+    if mt in ("mixtral", "minimax_m2"):
         resolvers.append(_mixtral)
     if mt in ("phi3", "phi4", "glm4") or src.has("model.layers.0.self_attn.qkv_proj.weight") \
             or src.has("model.layers.0.mlp.gate_up_proj.weight"):

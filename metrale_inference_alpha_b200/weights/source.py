@@ -140,8 +140,8 @@ class SyntheticSource(TensorSource):
         self._lin(f"{p}.v_proj", c.kv_size, c.hidden_size)
         self._lin(f"{p}.o_proj", c.hidden_size, c.num_heads * c.head_dim)
         if c.qk_norm:
-            self._vec(f"{p}.q_norm.weight", c.head_dim)
-            self._vec(f"{p}.k_norm.weight", c.head_dim)
+            self._vec(f"{p}.q_norm.weight", c.q_size if c.qk_norm_full else c.head_dim)
+            self._vec(f"{p}.k_norm.weight", c.kv_size if c.qk_norm_full else c.head_dim)
         if c.attn_bias:
             self._vec(f"{p}.q_proj.bias", c.q_size, "bias")
             self._vec(f"{p}.k_proj.bias", c.kv_size, "bias")

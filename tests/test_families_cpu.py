@@ -412,3 +412,71 @@ def test_glm4_matches_fp32_oracle(tmp_path):
     err = (got - want).abs().max().item()
     assert err < 0.05 * want.abs().max().item() + 1e-3, err
     assert int(got.argmax()) == int(want.argmax())
+
+
+MINIMAX = dict(BASE, model_type="minimax_m2", num_local_experts=8, num_experts_per_tok=2, intermediate_size=64,
+               scoring_func="sigmoid", use_routing_bias=True, use_qk_norm=True, qk_norm_type="per_layer", rotary_dim=16)
+
+
+def _oracle_minimax(hf, get, toks):
+    """fp32 MiniMax-M2 forward: q / k RMSNorm over all heads jointly, partial NeoX rotary, MoE in every
+    layer with sigmoid scores, selection by score + bias, weights = selected scores renormalised."""
+    f = lambda n: get(n).float()
+    T = len(toks)
+    H, KV, D, eps, r = hf["num_attention_heads"], hf["num_key_value_heads"], hf["head_dim"], hf["rms_norm_eps"], hf["rotary_dim"]
+    pos = torch.arange(T)
+    inv = 1.0 / (hf["rope_theta"] ** (torch.arange(0, r, 2, dtype=torch.float32) / r))
+    ang = pos[:, None].float() * inv[None, :]
+    cos, sin = torch.cat([ang.cos()] * 2, -1)[:, None, :], torch.cat([ang.sin()] * 2, -1)[:, None, :]
+
+    def rope(x):
+        xr, xp = x[..., :r], x[..., r:]
+        rot = torch.cat([-xr[..., r // 2:], xr[..., :r // 2]], -1)
+        return torch.cat([xr * cos + rot * sin, xp], -1)
+    x = f("model.embed_tokens.weight")[torch.tensor(toks)]
+    for i in range(hf["num_hidden_layers"]):
+        p = f"model.layers.{i}"
+        a = _rms(x, f(f"{p}.input_layernorm.weight"), eps)
+        q, k, v = ((a @ f(f"{p}.self_attn.{n}_proj.weight").T) for n in "qkv")
+        q, k = _rms(q, f(f"{p}.self_attn.q_norm.weight"), eps), _rms(k, f(f"{p}.self_attn.k_norm.weight"), eps)
+        q, k, v = rope(q.view(T, H, D)), rope(k.view(T, KV, D)), v.view(T, KV, D)
+        k, v = k.repeat_interleave(H // KV, 1), v.repeat_interleave(H // KV, 1)
+        s = torch.einsum("thd,shd->hts", q, k) / math.sqrt(D)
+        s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        x = x + torch.einsum("hts,shd->thd", s.softmax(-1), v).reshape(T, H * D) @ f(f"{p}.self_attn.o_proj.weight").T
+        a = _rms(x, f(f"{p}.post_attention_layernorm.weight"), eps)
+        scores = torch.sigmoid(a @ f(f"{p}.mlp.gate.weight").T)
+        _, idx = (scores + f(f"{p}.mlp.gate.e_score_correction_bias")).topk(hf["num_experts_per_tok"], -1)
+        w = scores.gather(1, idx)
+        w = w / w.sum(-1, keepdim=True)
+        y = torch.zeros_like(a)
+        for t in range(T):
+            for j in range(idx.shape[1]):
+                e = f"{p}.mlp.experts.{int(idx[t, j])}"
+                g, u = a[t] @ f(f"{e}.gate_proj.weight").T, a[t] @ f(f"{e}.up_proj.weight").T
+                y[t] += w[t, j] * ((torch.nn.functional.silu(g) * u) @ f(f"{e}.down_proj.weight").T)
+        x = x + y
+    return _rms(x, f("model.norm.weight"), eps)[-1] @ f("lm_head.weight").T
+
+
+def test_minimax_m2_matches_fp32_oracle(tmp_path):
+    cfg = from_hf_config(MINIMAX, name="minimax")
+    assert cfg.qk_norm_full and cfg.router == "sigmoid" and cfg.rotary_dim == 16 and cfg.ffn_types == ["moe", "moe"]
+    syn = SyntheticSource(cfg, seed=9, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    assert canon["model.layers.0.self_attn.q_norm.weight"].shape == (128,) and canon["model.layers.0.self_attn.k_norm.weight"].shape == (64,)
+    tensors = {}
+    for n, v in _dialect("mixtral", MINIMAX, canon).items():       # same expert spelling as Mixtral ...
+        n = n.replace(".block_sparse_moe.gate.e_score_correction_bias", ".block_sparse_moe.e_score_correction_bias")
+        tensors[n] = v.contiguous()                                # ... and the routing bias beside the gate
+    assert "model.layers.0.block_sparse_moe.e_score_correction_bias" in tensors
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(MINIMAX))
+    cfg2, src = open_checkpoint(tmp_path)
+    w = load_weights(cfg2, src)
+    toks = torch.randint(1, 512, (19,), generator=torch.Generator().manual_seed(4)).tolist()
+    got = _engine_logits(cfg2, w, toks)
+    want = _oracle_minimax(MINIMAX, lambda n: canon[n], toks)
+    err = (got - want).abs().max().item()
+    assert err < 0.05 * want.abs().max().item() + 1e-3, err
+    assert int(got.argmax()) == int(want.argmax())
