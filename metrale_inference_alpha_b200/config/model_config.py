@@ -287,6 +287,7 @@ _HF_ARCH = {
     "qwen3_5": "qwen_hybrid", "qwen3_5_moe": "qwen_hybrid", "qwen3_next": "qwen_hybrid",
     "qwen3_5_text": "qwen_hybrid", "qwen3_5_moe_text": "qwen_hybrid",
     "nemotron_h": "nemotron_h", "deepseek_v3": "deepseek_mla", "deepseek_v2": "deepseek_mla",
+    "kimi_k2": "deepseek_mla",          # Kimi K2 checkpoints use the DeepSeek-V3 architecture and tensor names
 }
 
 

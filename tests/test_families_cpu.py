@@ -480,3 +480,13 @@ def test_minimax_m2_matches_fp32_oracle(tmp_path):
     err = (got - want).abs().max().item()
     assert err < 0.05 * want.abs().max().item() + 1e-3, err
     assert int(got.argmax()) == int(want.argmax())
+
+
+def test_kimi_k2_maps_onto_the_deepseek_architecture():
+    c = from_hf_config(dict(model_type="kimi_k2", vocab_size=1024, hidden_size=256, num_hidden_layers=3, num_attention_heads=4,
+                            num_key_value_heads=4, intermediate_size=512, moe_intermediate_size=128, n_routed_experts=8,
+                            num_experts_per_tok=2, n_shared_experts=1, first_k_dense_replace=1, kv_lora_rank=64, q_lora_rank=96,
+                            qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, scoring_func="sigmoid", n_group=1,
+                            topk_group=1, routed_scaling_factor=2.8, norm_topk_prob=True, rms_norm_eps=1e-6, rope_theta=5e4))
+    assert c.arch == "deepseek_mla" and c.layer_types == ["mla"] * 3 and c.ffn_types == ["dense", "moe", "moe"]
+    assert c.router == "sigmoid" and c.router_scaling == 2.8 and c.kv_lora_rank == 64 and c.head_dim == 48
