@@ -490,3 +490,41 @@ def test_kimi_k2_maps_onto_the_deepseek_architecture():
                             topk_group=1, routed_scaling_factor=2.8, norm_topk_prob=True, rms_norm_eps=1e-6, rope_theta=5e4))
     assert c.arch == "deepseek_mla" and c.layer_types == ["mla"] * 3 and c.ffn_types == ["dense", "moe", "moe"]
     assert c.router == "sigmoid" and c.router_scaling == 2.8 and c.kv_lora_rank == 64 and c.head_dim == 48
+
+
+@pytest.mark.gpu
+def test_minimax_m2_on_gpu_matches_fp32_oracle():
+    hf = dict(MINIMAX, hidden_size=256, head_dim=64, intermediate_size=128, vocab_size=1024, rotary_dim=32)
+    cfg = from_hf_config(hf, name="minimax")
+    syn = SyntheticSource(cfg, seed=9, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    w = load_weights(cfg, syn, device="cuda:0")
+    toks = torch.randint(1, 1024, (33,), generator=torch.Generator().manual_seed(4)).tolist()
+    dec = Decoder(cfg, w)
+    kv = PagedKvCache(KvCacheConfig(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim), 16, device="cuda:0")
+    nb = (len(toks) + 15) // 16
+    b = ForwardBatch.build([dict(tokens=toks, start_pos=0, blocks=list(range(1, nb + 1)))], 16, device="cuda:0")
+    lg, _ = dec.forward(b, LayerCaches(cfg, kv=kv))
+    got = lg[0].float().cpu()
+    want = _oracle_minimax(hf, lambda n: canon[n], toks)
+    err = (got - want).abs().max().item()
+    assert err < 0.06 * want.abs().max().item() + 1e-2, err
+
+
+@pytest.mark.gpu
+def test_glm4_on_gpu_matches_fp32_oracle():
+    hf = dict(GLM4, hidden_size=256, head_dim=64, intermediate_size=512, vocab_size=1024)
+    cfg = from_hf_config(hf, name="glm4")
+    syn = SyntheticSource(cfg, seed=6, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    w = load_weights(cfg, syn, device="cuda:0")
+    toks = torch.randint(1, 1024, (35,), generator=torch.Generator().manual_seed(8)).tolist()
+    dec = Decoder(cfg, w)
+    kv = PagedKvCache(KvCacheConfig(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim), 16, device="cuda:0")
+    nb = (len(toks) + 15) // 16
+    b = ForwardBatch.build([dict(tokens=toks, start_pos=0, blocks=list(range(1, nb + 1)))], 16, device="cuda:0")
+    lg, _ = dec.forward(b, LayerCaches(cfg, kv=kv))
+    got = lg[0].float().cpu()
+    want = _oracle_glm4(hf, lambda n: canon[n], toks)
+    err = (got - want).abs().max().item()
+    assert err < 0.06 * want.abs().max().item() + 1e-2, err
