@@ -494,7 +494,7 @@ def test_kimi_k2_maps_onto_the_deepseek_architecture():
 
 @pytest.mark.gpu
 def test_minimax_m2_on_gpu_matches_fp32_oracle():
-    hf = dict(MINIMAX, hidden_size=256, head_dim=64, intermediate_size=128, vocab_size=1024, rotary_dim=32)
+    hf = dict(MINIMAX, hidden_size=512, head_dim=128, intermediate_size=128, vocab_size=1024, rotary_dim=64)   # the real head shape: 64 of 128 rotated
     cfg = from_hf_config(hf, name="minimax")
     syn = SyntheticSource(cfg, seed=9, std=0.05)
     canon = {n: syn.get(n) for n in syn.names()}
@@ -513,7 +513,7 @@ def test_minimax_m2_on_gpu_matches_fp32_oracle():
 
 @pytest.mark.gpu
 def test_glm4_on_gpu_matches_fp32_oracle():
-    hf = dict(GLM4, hidden_size=256, head_dim=64, intermediate_size=512, vocab_size=1024)
+    hf = dict(GLM4, hidden_size=512, head_dim=128, intermediate_size=512, vocab_size=1024)      # rotary 64 of 128, as in the real model
     cfg = from_hf_config(hf, name="glm4")
     syn = SyntheticSource(cfg, seed=6, std=0.05)
     canon = {n: syn.get(n) for n in syn.names()}
