@@ -98,10 +98,17 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKvParams p) {
         if (lane == 0 && p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
         pos = 0;
       }
-      const int half = p.rot / 2;       // multiple of 32
+      const int half = p.rot / 2;       // a multiple of 32, or 16 (32 rotated dims)
       const int hj = half / 32;         // register distance between pair members
       const float* c = p.cos_tab + (size_t)pos * half;
       const float* s = p.sin_tab + (size_t)pos * half;
+      if (half == 16) {
+        // both members of a pair sit in register 0, sixteen lanes apart
+        const float other = __shfl_xor_sync(0xffffffffu, v[0], 16);
+        const int i = lane & 15;
+        const float cs = c[i], sn = s[i];
+        v[0] = lane < 16 ? v[0] * cs - other * sn : v[0] * cs + other * sn;
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         if (j < hj) {
@@ -1029,7 +1036,7 @@ struct MbRopeKvArgs {
 int mb_qk_norm_rope_kvwrite(const MbRopeKvArgs* a, cudaStream_t stream) {
   if (!a || a->M <= 0 || !a->qkv || !a->q_out || !a->slots) return MB_ERR_BAD_ARG;
   if (a->D % 32 || a->D > 256) return MB_ERR_UNSUPPORTED;
-  if (a->cos_tab && (a->rot % 64 || a->rot > a->D || !a->positions)) return MB_ERR_UNSUPPORTED;
+  if (a->cos_tab && ((a->rot % 64 && a->rot != 32) || a->rot > a->D || !a->positions)) return MB_ERR_UNSUPPORTED;
   if (a->cache_fp8 && (!a->k_scale || !a->v_scale)) return MB_ERR_BAD_ARG;
   RopeKvParams p{};
   p.M = a->M; p.Hq = a->Hq; p.Hkv = a->Hkv; p.D = a->D; p.rot = a->rot;

@@ -319,7 +319,7 @@ def _cache(nb, bs, Hkv, D, fp8):
 
 
 @pytest.mark.parametrize("fp8", [False, True])
-@pytest.mark.parametrize("D,rot", [(128, 128), (64, 64), (256, 64)])
+@pytest.mark.parametrize("D,rot", [(128, 128), (64, 64), (256, 64), (64, 32), (128, 32)])
 def test_rope_kvwrite(fp8, D, rot):
     M, Hq, Hkv, bs, nb = 23, 8, 2, 16, 12
     g = torch.Generator().manual_seed(5)
