@@ -49,7 +49,8 @@ class ModelConfig:
     intermediate_size: int = 688
     ffn_act: str = "swiglu"             # swiglu | relu2 | geglu (tanh-approximated GELU gate)
     post_norms: bool = False            # Gemma / GLM-4: RMSNorm on the attention / FFN output before the residual add
-    post_norm_names: str = "gemma"      # checkpoint spelling of the four norms: gemma | glm
+    post_norm_names: str = "gemma"      # checkpoint spelling of the norms: gemma | glm | olmo2
+    pre_norms: bool = True              # False: blocks read the residual stream un-normalised (OLMo 2: post-norm only)
     rope_interleaved: bool = False      # checkpoint rotates (2i, 2i+1) pairs; q / k rows are re-ordered at load
     embed_scale: float = 1.0            # embeddings are multiplied by this (Gemma: sqrt(hidden))
     final_logit_softcap: float = 0.0    # logits = cap * tanh(logits / cap); 0 = off
@@ -282,7 +283,7 @@ def preset(name: str, **kw) -> ModelConfig:
 # ----------------------------------------------------------------------------- HF config.json
 _HF_ARCH = {
     "llama": "dense_gqa", "qwen2": "dense_gqa", "qwen3": "dense_gqa", "mistral": "dense_gqa",
-    "minimax_m2": "dense_gqa", "glm4": "dense_gqa", "gemma3_text": "dense_gqa", "gemma3": "dense_gqa", "gemma2": "dense_gqa",
+    "olmo2": "dense_gqa", "minimax_m2": "dense_gqa", "glm4": "dense_gqa", "gemma3_text": "dense_gqa", "gemma3": "dense_gqa", "gemma2": "dense_gqa",
     "phi3": "dense_gqa", "qwen3_moe": "dense_gqa", "qwen2_moe": "dense_gqa", "mixtral": "dense_gqa",
     "qwen3_5": "qwen_hybrid", "qwen3_5_moe": "qwen_hybrid", "qwen3_next": "qwen_hybrid",
     "qwen3_5_text": "qwen_hybrid", "qwen3_5_moe_text": "qwen_hybrid",
@@ -353,6 +354,9 @@ def from_hf_config(cfg: dict, name: str = "model") -> ModelConfig:
                       window_layers=[win if t == "sliding_attention" else 0 for t in lt], sliding_window=0,
                       rope_local_theta=float(cfg.get("rope_local_base_freq", 0.0) or 0.0),
                       final_logit_softcap=float(cfg.get("final_logit_softcapping") or 0.0))
+        if mt == "olmo2":
+            kw.update(post_norms=True, post_norm_names="olmo2", pre_norms=False, qk_norm=True, qk_norm_full=True,
+                      attn_bias=bool(cfg.get("attention_bias", False)))
         if mt == "minimax_m2":
             if cfg.get("shared_intermediate_size"):
                 raise ValueError("MiniMax shared experts are not supported")

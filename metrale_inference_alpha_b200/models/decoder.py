@@ -77,6 +77,11 @@ class Decoder:
 
     # ------------------------------------------------------------------ helpers
     def _norm_act(self, x, w, fmt: str, also_bf16: bool = False) -> Act:
+        if w is None:                      # post-norm-only models: the block reads the stream as it is
+            a = self._as_act(x if x.dtype == torch.bfloat16 or not x.is_cuda else x.to(torch.bfloat16), fmt)
+            if also_bf16 and getattr(a, "bf16", None) is None:
+                a.bf16 = x
+            return a
         return ops.row_op(x, fmt, ops.IN_RMSNORM, w=w, plus_one=self.cfg.norm_plus_one,
                           eps=self.cfg.rms_eps, also_bf16=also_bf16)[0]
 

@@ -321,7 +321,7 @@ class Loader:
         from . import loader_ext
         c = self.cfg
         L = LayerW(kind=lt, ffn_kind=ft)
-        L.ln1 = self.vec(f"{p}.input_layernorm.weight")
+        L.ln1 = self.vec(f"{p}.input_layernorm.weight") if c.pre_norms else None
         if lt == "attention":
             L.mixer = self.attention(f"{p}.self_attn")
         elif lt == "gdn":
@@ -329,7 +329,10 @@ class Loader:
         elif lt == "mla":
             L.mixer = loader_ext.mla(self, f"{p}.self_attn")
         if ft != "none":
-            if c.post_norms and c.post_norm_names == "glm":
+            if c.post_norms and c.post_norm_names == "olmo2":     # post-norm only: no norm in front of the blocks
+                L.post_attn = self.vec(f"{p}.post_attention_layernorm.weight")
+                L.post_ffn = self.vec(f"{p}.post_feedforward_layernorm.weight")
+            elif c.post_norms and c.post_norm_names == "glm":
                 L.post_attn = self.vec(f"{p}.post_self_attn_layernorm.weight")
                 L.ln2 = self.vec(f"{p}.post_attention_layernorm.weight")
                 L.post_ffn = self.vec(f"{p}.post_mlp_layernorm.weight")

@@ -175,7 +175,8 @@ class SyntheticSource(TensorSource):
 
     def _layer(self, p: str, lt: str, ft: str, idx: int):
         c = self.cfg
-        self._vec(f"{p}.input_layernorm.weight", c.hidden_size)
+        if c.pre_norms:
+            self._vec(f"{p}.input_layernorm.weight", c.hidden_size)
         if lt == "attention":
             self._attn(f"{p}.self_attn")
         elif lt == "gdn":
@@ -204,7 +205,9 @@ class SyntheticSource(TensorSource):
             self._lin(f"{q}.o_proj", c.hidden_size, c.num_heads * c.v_head_dim)
         if ft != "none":
             self._vec(f"{p}.post_attention_layernorm.weight", c.hidden_size)
-            if c.post_norms and c.post_norm_names == "glm":
+            if c.post_norms and c.post_norm_names == "olmo2":
+                self._vec(f"{p}.post_feedforward_layernorm.weight", c.hidden_size)
+            elif c.post_norms and c.post_norm_names == "glm":
                 self._vec(f"{p}.post_self_attn_layernorm.weight", c.hidden_size)
                 self._vec(f"{p}.post_mlp_layernorm.weight", c.hidden_size)
             elif c.post_norms:

@@ -528,3 +528,36 @@ def test_glm4_on_gpu_matches_fp32_oracle():
     want = _oracle_glm4(hf, lambda n: canon[n], toks)
     err = (got - want).abs().max().item()
     assert err < 0.06 * want.abs().max().item() + 1e-2, err
+
+
+def test_olmo2_post_norm_only_matches_fp32_oracle():
+    hf = dict(BASE, model_type="olmo2")
+    cfg = from_hf_config(hf, name="olmo2")
+    assert not cfg.pre_norms and cfg.post_norms and cfg.qk_norm_full
+    syn = SyntheticSource(cfg, seed=12, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    assert "model.layers.0.input_layernorm.weight" not in canon and "model.layers.0.post_feedforward_layernorm.weight" in canon
+    w = load_weights(cfg, syn)
+    toks = torch.randint(1, 512, (17,), generator=torch.Generator().manual_seed(6)).tolist()
+    got = _engine_logits(cfg, w, toks)
+    f = lambda n: canon[n].float()
+    T, H, KV, D, eps = len(toks), 4, 2, 32, hf["rms_norm_eps"]
+    x = f("model.embed_tokens.weight")[torch.tensor(toks)]
+    pos = torch.arange(T)
+    for i in range(2):
+        p = f"model.layers.{i}"
+        q, k, v = ((x @ f(f"{p}.self_attn.{n}_proj.weight").T) for n in "qkv")
+        q, k = _rms(q, f(f"{p}.self_attn.q_norm.weight"), eps), _rms(k, f(f"{p}.self_attn.k_norm.weight"), eps)
+        q, k, v = _rope(q.view(T, H, D), pos, hf["rope_theta"]), _rope(k.view(T, KV, D), pos, hf["rope_theta"]), v.view(T, KV, D)
+        k, v = k.repeat_interleave(H // KV, 1), v.repeat_interleave(H // KV, 1)
+        s = torch.einsum("thd,shd->hts", q, k) / math.sqrt(D)
+        s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        o = torch.einsum("hts,shd->thd", s.softmax(-1), v).reshape(T, H * D) @ f(f"{p}.self_attn.o_proj.weight").T
+        x = x + _rms(o, f(f"{p}.post_attention_layernorm.weight"), eps)
+        g, u = x @ f(f"{p}.mlp.gate_proj.weight").T, x @ f(f"{p}.mlp.up_proj.weight").T
+        y = (torch.nn.functional.silu(g) * u) @ f(f"{p}.mlp.down_proj.weight").T
+        x = x + _rms(y, f(f"{p}.post_feedforward_layernorm.weight"), eps)
+    want = _rms(x, f("model.norm.weight"), eps)[-1] @ f("lm_head.weight").T
+    err = (got - want).abs().max().item()
+    assert err < 0.05 * want.abs().max().item() + 1e-3, err
+    assert int(got.argmax()) == int(want.argmax())
