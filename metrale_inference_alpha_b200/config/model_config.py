@@ -54,6 +54,8 @@ class ModelConfig:
     rope_interleaved: bool = False      # checkpoint rotates (2i, 2i+1) pairs; q / k rows are re-ordered at load
     embed_scale: float = 1.0            # embeddings are multiplied by this (Gemma: sqrt(hidden))
     final_logit_softcap: float = 0.0    # logits = cap * tanh(logits / cap); 0 = off
+    residual_multiplier: float = 1.0    # Granite: a block's output is scaled by this before it joins the stream
+    logits_divisor: float = 1.0         # Granite: logits are divided by this
     tie_embeddings: bool = False
     # per-layer structure
     layer_types: List[str] = field(default_factory=list)   # mixer per layer
@@ -283,7 +285,7 @@ def preset(name: str, **kw) -> ModelConfig:
 # ----------------------------------------------------------------------------- HF config.json
 _HF_ARCH = {
     "llama": "dense_gqa", "qwen2": "dense_gqa", "qwen3": "dense_gqa", "mistral": "dense_gqa",
-    "olmo2": "dense_gqa", "minimax_m2": "dense_gqa", "glm4": "dense_gqa", "gemma3_text": "dense_gqa", "gemma3": "dense_gqa", "gemma2": "dense_gqa",
+    "granite": "dense_gqa", "olmo2": "dense_gqa", "minimax_m2": "dense_gqa", "glm4": "dense_gqa", "gemma3_text": "dense_gqa", "gemma3": "dense_gqa", "gemma2": "dense_gqa",
     "phi3": "dense_gqa", "qwen3_moe": "dense_gqa", "qwen2_moe": "dense_gqa", "mixtral": "dense_gqa",
     "qwen3_5": "qwen_hybrid", "qwen3_5_moe": "qwen_hybrid", "qwen3_next": "qwen_hybrid",
     "qwen3_5_text": "qwen_hybrid", "qwen3_5_moe_text": "qwen_hybrid",
@@ -354,6 +356,11 @@ def from_hf_config(cfg: dict, name: str = "model") -> ModelConfig:
                       window_layers=[win if t == "sliding_attention" else 0 for t in lt], sliding_window=0,
                       rope_local_theta=float(cfg.get("rope_local_base_freq", 0.0) or 0.0),
                       final_logit_softcap=float(cfg.get("final_logit_softcapping") or 0.0))
+        if mt == "granite":
+            kw.update(embed_scale=float(cfg.get("embedding_multiplier", 1.0)), attn_scale=float(cfg.get("attention_multiplier", 0.0) or 0.0),
+                      residual_multiplier=float(cfg.get("residual_multiplier", 1.0)),
+                      logits_divisor=float(cfg.get("logits_scaling", 1.0) or 1.0),
+                      attn_bias=bool(cfg.get("attention_bias", False)))
         if mt == "olmo2":
             kw.update(post_norms=True, post_norm_names="olmo2", pre_norms=False, qk_norm=True, qk_norm_full=True,
                       attn_bias=bool(cfg.get("attention_bias", False)))

@@ -208,6 +208,9 @@ class Decoder:
             if lw.post_ffn is not None:
                 y = self.dense_ffn(a, lw.ffn, None, lora, li, rows)
                 return self._add_normed(x, y, lw.post_ffn)
+            if self.cfg.residual_multiplier != 1.0:
+                y = self.dense_ffn(a, lw.ffn, None, lora, li, rows)
+                return x + (y.float() * self.cfg.residual_multiplier).to(x.dtype)
             return self.dense_ffn(a, lw.ffn, x, lora, li, rows)
         from .moe import moe_block
         return moe_block(self, x, lw)
@@ -220,6 +223,10 @@ class Decoder:
                 y = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i,
                                          add_residual=False)
                 x = self._add_normed(x, y, lw.post_attn)
+            elif self.cfg.residual_multiplier != 1.0:
+                y = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i,
+                                         add_residual=False)
+                x = x + (y.float() * self.cfg.residual_multiplier).to(x.dtype)
             else:
                 x = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i)
         elif lw.kind == "gdn":
@@ -253,6 +260,8 @@ class Decoder:
         """Final norm + (vocab-parallel) lm_head on the selected rows."""
         a = self._norm_act(hidden_rows, self.w.final_norm if final_norm is None else final_norm, "bf16")
         lg = ops.linear(a, self.w.lm_head, out_f32=out_f32)
+        if self.cfg.logits_divisor != 1.0:
+            lg = (lg.float() / self.cfg.logits_divisor).to(lg.dtype)
         cap = self.cfg.final_logit_softcap
         if cap > 0:
             lg = (torch.tanh(lg.float() / cap) * cap).to(lg.dtype)

@@ -561,3 +561,35 @@ def test_olmo2_post_norm_only_matches_fp32_oracle():
     err = (got - want).abs().max().item()
     assert err < 0.05 * want.abs().max().item() + 1e-3, err
     assert int(got.argmax()) == int(want.argmax())
+
+
+def test_granite_multipliers_match_fp32_oracle():
+    hf = dict(BASE, model_type="granite", embedding_multiplier=12.0, attention_multiplier=0.0625, residual_multiplier=0.22,
+              logits_scaling=8.0)
+    cfg = from_hf_config(hf, name="granite")
+    assert cfg.embed_scale == 12.0 and cfg.attn_scale == 0.0625 and cfg.residual_multiplier == 0.22 and cfg.logits_divisor == 8.0
+    syn = SyntheticSource(cfg, seed=13, std=0.05)
+    canon = {n: syn.get(n) for n in syn.names()}
+    toks = torch.randint(1, 512, (18,), generator=torch.Generator().manual_seed(7)).tolist()
+    got = _engine_logits(cfg, load_weights(cfg, syn), toks)
+    f = lambda n: canon[n].float()
+    T, H, KV, D, eps = len(toks), 4, 2, 32, hf["rms_norm_eps"]
+    x = f("model.embed_tokens.weight")[torch.tensor(toks)] * 12.0
+    pos = torch.arange(T)
+    for i in range(2):
+        p = f"model.layers.{i}"
+        a = _rms(x, f(f"{p}.input_layernorm.weight"), eps)
+        q, k, v = ((a @ f(f"{p}.self_attn.{n}_proj.weight").T) for n in "qkv")
+        q, k, v = _rope(q.view(T, H, D), pos, hf["rope_theta"]), _rope(k.view(T, KV, D), pos, hf["rope_theta"]), v.view(T, KV, D)
+        k, v = k.repeat_interleave(H // KV, 1), v.repeat_interleave(H // KV, 1)
+        s = torch.einsum("thd,shd->hts", q, k) * 0.0625
+        s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        o = torch.einsum("hts,shd->thd", s.softmax(-1), v).reshape(T, H * D) @ f(f"{p}.self_attn.o_proj.weight").T
+        x = x + 0.22 * o
+        a = _rms(x, f(f"{p}.post_attention_layernorm.weight"), eps)
+        g, u = a @ f(f"{p}.mlp.gate_proj.weight").T, a @ f(f"{p}.mlp.up_proj.weight").T
+        x = x + 0.22 * ((torch.nn.functional.silu(g) * u) @ f(f"{p}.mlp.down_proj.weight").T)
+    want = (_rms(x, f("model.norm.weight"), eps)[-1] @ f("lm_head.weight").T) / 8.0
+    err = (got - want).abs().max().item()
+    assert err < 0.05 * want.abs().max().item() + 1e-3, err
+    assert int(got.argmax()) == int(want.argmax())
