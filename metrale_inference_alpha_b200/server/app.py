@@ -286,22 +286,41 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         body = await request.json()
         if not body.get("messages"):
             raise HTTPException(400, "messages is required")
+        n = int(body.get("n") or 1)
+        if n < 1 or n > 16:
+            raise HTTPException(400, "n must be between 1 and 16")
+        if n > 1 and body.get("stream"):
+            raise HTTPException(400, "n > 1 is supported for non-streaming requests")
         job = _job_from_chat(body, body["messages"], tools=body.get("tools"))
         rid, created = "chatcmpl-" + uuid.uuid4().hex[:24], int(time.time())
         if not body.get("stream"):
-            text, ids, usage, reason, lps = await _collect(job)
-            reasoning, content, calls = _split_outputs(job, text)
-            msg: Dict[str, Any] = {"role": "assistant", "content": content or (None if calls else "")}
-            if reasoning:
-                msg["reasoning_content"] = reasoning
-            if calls:
-                msg["tool_calls"] = calls
-                reason = "tool_calls"
-            choice = {"index": 0, "message": msg, "finish_reason": reason, "logprobs": _lp_block(ids, lps)}
-            if job.return_token_ids:
-                choice["token_ids"] = ids
+            # n choices = n independent samples of the same prompt (the prefix cache shares its KV);
+            # a seeded request gives choice i the seed + i
+            jobs = [job]
+            for i in range(1, n):
+                b_i = dict(body, seed=body["seed"] + i) if body.get("seed") is not None else body
+                jobs.append(_job_from_chat(b_i, body["messages"], tools=body.get("tools")))
+            results = await asyncio.gather(*(_collect(j) for j in jobs))
+            choices, usage = [], None
+            for i, (j, (text, ids, u, reason, lps)) in enumerate(zip(jobs, results)):
+                reasoning, content, calls = _split_outputs(j, text)
+                msg: Dict[str, Any] = {"role": "assistant", "content": content or (None if calls else "")}
+                if reasoning:
+                    msg["reasoning_content"] = reasoning
+                if calls:
+                    msg["tool_calls"] = calls
+                    reason = "tool_calls"
+                choice = {"index": i, "message": msg, "finish_reason": reason, "logprobs": _lp_block(ids, lps)}
+                if j.return_token_ids:
+                    choice["token_ids"] = ids
+                choices.append(choice)
+                if usage is None:
+                    usage = dict(u or {})
+                elif u:
+                    usage["completion_tokens"] = (usage.get("completion_tokens") or 0) + (u.get("completion_tokens") or 0)
+                    usage["total_tokens"] = (usage.get("prompt_tokens") or 0) + usage["completion_tokens"]
             out = {"id": rid, "object": "chat.completion", "created": created, "model": cfg.model_name,
-                   "choices": [choice], "usage": usage}
+                   "choices": choices, "usage": usage}
             if body.get("store"):
                 stored_completions[rid] = dict(out, metadata=body.get("metadata") or {})
                 while len(stored_completions) > 1024:

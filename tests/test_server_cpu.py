@@ -844,3 +844,19 @@ def test_loop_detector_reaches_the_sampler_over_http(client):
     assert r.status_code == 200
     after = client.get("/metrics").text
     assert "metrale_loop_suppress_total" in after and "metrale_loop_suppress_total" not in before
+
+
+def test_n_choices_are_independent_samples(client):
+    body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "temperature": 1.2, "seed": 5, "n": 3,
+            "return_token_ids": True}
+    r = client.post("/v1/chat/completions", json=body).json()
+    assert [c["index"] for c in r["choices"]] == [0, 1, 2]
+    ids = [tuple(c["token_ids"]) for c in r["choices"]]
+    assert all(len(i) == 6 for i in ids) and len(set(ids)) > 1                 # different seeds, different samples
+    assert r["usage"]["completion_tokens"] == 18 and r["usage"]["total_tokens"] == r["usage"]["prompt_tokens"] + 18
+    again = client.post("/v1/chat/completions", json=body).json()
+    assert [tuple(c["token_ids"]) for c in again["choices"]] == ids             # reproducible per choice
+    one = client.post("/v1/chat/completions", json=dict(body, n=1)).json()
+    assert tuple(one["choices"][0]["token_ids"]) == ids[0]
+    assert client.post("/v1/chat/completions", json=dict(body, n=2, stream=True)).status_code == 400
+    assert client.post("/v1/chat/completions", json=dict(body, n=99)).status_code == 400
