@@ -59,6 +59,7 @@ class EngineArgs:
     preempt_mode: str = "recompute"                    # recompute | swap (KV + state to host memory / swap files)
     swap_space_bytes: int = 8 << 30
     swap_dir: Optional[str] = None
+    prediction_drafts: int = 8                         # tokens verified per step for requests with a predicted output
     kv_cache_dtype: str = "auto"                       # auto (the model config's) | bf16 | fp8
     kv_high_precision_layers: str = ""                 # e.g. "0,1,63" or "first:2,last:2": these layers keep bf16 KV under fp8
     oom_guard_mb: int = 4096                           # device memory left unclaimed when sizing the KV pool
@@ -251,6 +252,16 @@ class LLMEngine:
                     if not it.seq.is_finished():
                         room = it.seq.req.params.max_tokens - it.seq.num_output - 1
                         it.seq.drafts = list(d[:max(0, room)])
+        if not speculate and plan.kind in ("decode", "verify"):
+            # predicted outputs: a request that brought its own guess of the answer is verified
+            # against it a few tokens per step, whatever the engine's own speculation mode
+            for it in plan.items:
+                pred = it.seq.req.params.prediction_ids
+                if pred and it.seq.req.params.greedy and not it.seq.is_finished():     # verification is by argmax: lossless for greedy requests only
+                    from ..speculative.ngram import propose_from_prediction
+                    room = it.seq.req.params.max_tokens - it.seq.num_output - 1
+                    d = propose_from_prediction(it.seq.tokens[it.seq.prompt_len:], pred, min(self.args.prediction_drafts, max(0, room)))
+                    it.seq.drafts = d
         dt = time.perf_counter() - t0
         if track and plan.kind in ("decode", "verify"):
             emitted = sum(len(it.seq.tokens) - before[it.seq.seq_id] for it in plan.items)

@@ -40,6 +40,7 @@ class SamplingParams:
     adapter: Optional[str] = None       # LoRA adapter name (engine.load_adapter)
     # reasoning budget: once `thinking_budget` output tokens passed without the closing marker
     # `think_end_ids`, the sampler forces that marker token by token (0 = no limit)
+    prediction_ids: List[int] = field(default_factory=list)   # predicted output (OpenAI `prediction`): used as drafts
     adaptive: Optional[object] = None   # sampling.adaptive.AdaptiveSampling: per-token temperature
     thinking_budget: int = 0
     think_end_ids: List[int] = field(default_factory=list)

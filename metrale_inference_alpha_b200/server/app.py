@@ -223,6 +223,12 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         except ValueError as e:             # GrammarError: the schema / pattern / grammar does not compile
             raise HTTPException(400, f"invalid grammar: {e}")
         sp.adapter = body.get("adapter") or getattr(app.state, "active_adapter", None)
+        pred = body.get("prediction")
+        if isinstance(pred, dict) and pred.get("content"):
+            pc = pred["content"]
+            if isinstance(pc, list):
+                pc = "".join(p_.get("text", "") for p_ in pc if isinstance(p_, dict))
+            sp.prediction_ids = list(tokenizer.encode(pc))
         if cfg.adaptive_sampling and sp.temperature > 0:
             from ..sampling.adaptive import AdaptiveSampling
             opened = tokenizer.encode("<tool_call>") if tools and cfg.tool_call_parser in ("hermes", "qwen3", "qwen") else []

@@ -23,3 +23,22 @@ class NgramProposer:
                     if cont:
                         return cont
         return []
+
+
+def propose_from_prediction(output: List[int], prediction: List[int], k: int, anchor: int = 3) -> List[int]:
+    """Drafts from a caller-supplied predicted output (OpenAI `prediction`): while the output
+    follows the prediction, the next k predicted tokens; after a divergence, the continuation of
+    the latest place in the prediction where the last `anchor` output tokens occur (an edit in the
+    middle of a file re-synchronises a few tokens later); nothing when there is no such place."""
+    n = len(output)
+    if k <= 0 or not prediction:
+        return []
+    if n <= len(prediction) and prediction[:n] == output:
+        return list(prediction[n:n + k])
+    if n < anchor:
+        return []
+    tail = output[-anchor:]
+    for i in range(len(prediction) - anchor, -1, -1):
+        if prediction[i:i + anchor] == tail:
+            return list(prediction[i + anchor:i + anchor + k])
+    return []

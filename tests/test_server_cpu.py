@@ -860,3 +860,17 @@ def test_n_choices_are_independent_samples(client):
     assert tuple(one["choices"][0]["token_ids"]) == ids[0]
     assert client.post("/v1/chat/completions", json=dict(body, n=2, stream=True)).status_code == 400
     assert client.post("/v1/chat/completions", json=dict(body, n=99)).status_code == 400
+
+
+def test_prediction_field_reports_accepted_tokens(client):
+    body = {"messages": [{"role": "user", "content": "say it"}], "max_tokens": 12, "temperature": 0, "return_token_ids": True}
+    a = client.post("/v1/chat/completions", json=body).json()
+    text = a["choices"][0]["message"]["content"] or ""
+    tok = load_tokenizer(None, 4096)
+    pred = tok.decode(a["choices"][0]["token_ids"], False) if hasattr(tok, "decode") else text
+    b = client.post("/v1/chat/completions", json=dict(body, prediction={"type": "content", "content": pred})).json()
+    assert b["choices"][0]["token_ids"] == a["choices"][0]["token_ids"]           # lossless
+    det = b["usage"]["completion_tokens_details"]
+    assert det["accepted_prediction_tokens"] + det["rejected_prediction_tokens"] >= 0
+    if tok.encode(pred) == a["choices"][0]["token_ids"]:                           # the guess survived the text round trip
+        assert det["accepted_prediction_tokens"] > 0

@@ -62,3 +62,27 @@ def test_grammar_masks_follow_draft_rows_and_rewind_to_the_accepted_prefix():
         if spec == "ngram":
             assert eng.spec_stats.drafted > 0                       # the verify path really ran
     assert outs["ngram"] == outs["none"]
+
+
+def test_predicted_outputs_are_verified_losslessly_and_save_steps():
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    from metrale_inference_alpha_b200.speculative.ngram import propose_from_prediction as pfp
+    assert pfp([1, 2], [1, 2, 3, 4, 5], 2) == [3, 4]                          # following the prediction
+    assert pfp([1, 2, 9, 4, 5, 6], [1, 2, 3, 4, 5, 6, 7, 8], 3) == [7, 8]     # re-synchronised after an edit
+    assert pfp([9, 9, 9, 9], [1, 2, 3, 4], 3) == [] and pfp([1], [], 3) == [] and pfp([1, 2], [1, 2], 3) == []
+    prompt = list(range(10, 40))
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=256))
+    base = eng.generate([prompt], SamplingParams(max_tokens=24, temperature=0.0))[0]
+    steps0 = eng.step_count
+    exact = eng.generate([prompt], SamplingParams(max_tokens=24, temperature=0.0, prediction_ids=list(base.output_ids)))[0]
+    steps_exact = eng.step_count - steps0
+    assert exact.output_ids == base.output_ids and exact.accepted_draft_tokens >= 16 and steps_exact <= 8
+    edited = list(base.output_ids)
+    edited[5] = (edited[5] + 1) % 4000                                           # the guess is wrong in one place
+    steps1 = eng.step_count
+    part = eng.generate([prompt], SamplingParams(max_tokens=24, temperature=0.0, prediction_ids=edited))[0]
+    assert part.output_ids == base.output_ids and part.rejected_draft_tokens > 0 and part.accepted_draft_tokens > 0
+    assert eng.step_count - steps1 < 24
+    sampled = eng.generate([prompt], SamplingParams(max_tokens=8, temperature=0.9, seed=1, prediction_ids=edited))[0]
+    assert sampled.accepted_draft_tokens == 0 and sampled.rejected_draft_tokens == 0     # not used for sampled requests
