@@ -86,3 +86,18 @@ def test_predicted_outputs_are_verified_losslessly_and_save_steps():
     assert eng.step_count - steps1 < 24
     sampled = eng.generate([prompt], SamplingParams(max_tokens=8, temperature=0.9, seed=1, prediction_ids=edited))[0]
     assert sampled.accepted_draft_tokens == 0 and sampled.rejected_draft_tokens == 0     # not used for sampled requests
+
+
+@pytest.mark.gpu
+def test_predicted_outputs_on_gpu_are_lossless():
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    prompt = list(range(10, 40))
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cuda", max_num_seqs=4, max_model_len=256))
+    base = eng.generate([prompt], SamplingParams(max_tokens=40, temperature=0.0))[0]
+    edited = list(base.output_ids)
+    edited[7] = (edited[7] + 1) % 4000
+    s0 = eng.step_count
+    out = eng.generate([prompt], SamplingParams(max_tokens=40, temperature=0.0, prediction_ids=edited))[0]
+    assert out.output_ids == base.output_ids
+    assert out.accepted_draft_tokens >= 20 and out.rejected_draft_tokens > 0 and eng.step_count - s0 < 20
