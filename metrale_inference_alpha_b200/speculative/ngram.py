@@ -28,8 +28,9 @@ class NgramProposer:
 def propose_from_prediction(output: List[int], prediction: List[int], k: int, anchor: int = 3) -> List[int]:
     """Drafts from a caller-supplied predicted output (OpenAI `prediction`): while the output
     follows the prediction, the next k predicted tokens; after a divergence, the continuation of
-    the latest place in the prediction where the last `anchor` output tokens occur (an edit in the
-    middle of a file re-synchronises a few tokens later); nothing when there is no such place."""
+    the place in the prediction where the last `anchor` output tokens occur that lies closest to
+    the current output length (an edit in the middle of a file re-synchronises a few tokens later,
+    and repetitive text stays aligned); nothing when there is no such place."""
     n = len(output)
     if k <= 0 or not prediction:
         return []
@@ -38,7 +39,8 @@ def propose_from_prediction(output: List[int], prediction: List[int], k: int, an
     if n < anchor:
         return []
     tail = output[-anchor:]
-    for i in range(len(prediction) - anchor, -1, -1):
-        if prediction[i:i + anchor] == tail:
-            return list(prediction[i + anchor:i + anchor + k])
-    return []
+    best = -1
+    for i in range(len(prediction) - anchor + 1):
+        if prediction[i:i + anchor] == tail and (best < 0 or abs(i + anchor - n) <= abs(best + anchor - n)):   # ties: the later place
+            best = i
+    return list(prediction[best + anchor:best + anchor + k]) if best >= 0 else []
