@@ -26,7 +26,7 @@ from ..sampling.params import SamplingParams
 from ..utils.telemetry import Telemetry
 from .chat_template import ChatRenderer
 from .engine_loop import AsyncEngine
-from .grammar import grammar_for_response_format, tool_call_grammar
+from .grammar import grammar_for_response_format, response_format_from_guided, tool_call_grammar
 from .ratelimit import RateLimiter
 from .reasoning_parser import ReasoningParser
 from .conversation_store import ConversationStore
@@ -213,7 +213,8 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
                 sp.logit_bias = dict(sp.logit_bias)
                 sp.logit_bias[tool_open_first] = -1e4 if verdict.mask else sp.logit_bias.get(tool_open_first, 0.0) + verdict.bias
         try:
-            sp.grammar = grammar_for_response_format(body.get("response_format"), tokenizer, eos)
+            sp.grammar = grammar_for_response_format(body.get("response_format") or response_format_from_guided(body),
+                                                     tokenizer, eos)
             forced = choice == "required" or (isinstance(choice, dict) and choice.get("type") not in ("auto", "none"))
             if sp.grammar is None and tools and (forced or cfg.tool_grammar) and hasattr(tokenizer, "token_bytes"):
                 tg = tool_call_grammar(tools, cfg.tool_call_parser, "required" if forced else "auto")
@@ -393,6 +394,11 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         sp.adapter = body.get("adapter")
         if body.get("ignore_eos"):
             sp.ignore_eos = True
+        try:
+            sp.grammar = grammar_for_response_format(body.get("response_format") or response_format_from_guided(body),
+                                                     tokenizer, eos)
+        except ValueError as e:
+            raise HTTPException(400, f"invalid grammar: {e}")
         job = _ChatJob(ids, sp)
         rid, created = "cmpl-" + uuid.uuid4().hex[:24], int(time.time())
         if not body.get("stream"):

@@ -316,6 +316,25 @@ def grammar_for_response_format(fmt: Optional[dict], tokenizer, eos_token_id=Non
     return None
 
 
+def response_format_from_guided(body: dict) -> Optional[dict]:
+    """vLLM-style request fields (`guided_json`, `guided_regex`, `guided_grammar`, `guided_choice`, or
+    the same keys inside `structured_outputs`) as an equivalent `response_format`."""
+    so = body.get("structured_outputs") if isinstance(body.get("structured_outputs"), dict) else {}
+    pick = lambda k: body.get("guided_" + k) if body.get("guided_" + k) is not None else so.get(k)
+    js = pick("json")
+    if js is not None:
+        return {"type": "json_schema", "json_schema": {"schema": json.loads(js) if isinstance(js, str) else js}}
+    if pick("regex"):
+        return {"type": "regex", "pattern": pick("regex")}
+    if pick("grammar"):
+        return {"type": "ebnf", "grammar": pick("grammar")}
+    choice = pick("choice")
+    if choice:
+        alts = " | ".join(json.dumps(str(c)) for c in choice)      # JSON string quoting is valid EBNF literal quoting
+        return {"type": "ebnf", "grammar": f"root ::= {alts}"}
+    return None
+
+
 def tool_call_grammar(tools: Optional[List[dict]], parser: str, mode: str = "auto"):
     """Compiled grammar that keeps tool calls well-formed for the call syntax `parser` scans
     (reference: ``GrammarSpec::ToolCall``, compiled by the parser that reads the response).

@@ -4,6 +4,7 @@ grammar, rate limiter, levers, telemetry, CLI, and every route of the app driven
 FastAPI's test client over the tiny dense model. Mirrors the reference's server test
 strategy (``crates/server/tests``: golden request / response shapes, SSE framing, auth)."""
 import json
+import re
 import time
 
 import pytest
@@ -874,3 +875,19 @@ def test_prediction_field_reports_accepted_tokens(client):
     assert det["accepted_prediction_tokens"] + det["rejected_prediction_tokens"] >= 0
     if tok.encode(pred) == a["choices"][0]["token_ids"]:                           # the guess survived the text round trip
         assert det["accepted_prediction_tokens"] > 0
+
+
+def test_guided_fields_map_onto_the_grammar_engine(client):
+    from metrale_inference_alpha_b200.server.grammar import response_format_from_guided as rf
+    assert rf({"guided_regex": "a+"}) == {"type": "regex", "pattern": "a+"}
+    assert rf({"structured_outputs": {"json": {"type": "object"}}})["json_schema"]["schema"] == {"type": "object"}
+    assert rf({"guided_json": '{"type": "integer"}'})["json_schema"]["schema"] == {"type": "integer"}
+    assert rf({"guided_choice": ["yes", 'say "no"']})["grammar"] == 'root ::= "yes" | "say \\"no\\""'
+    assert rf({"temperature": 0}) is None
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "pick"}], "max_tokens": 16,
+                                                  "temperature": 0.7, "seed": 2, "guided_choice": ["alpha", "beta", "gamma delta"]}).json()
+    assert r["choices"][0]["message"]["content"] in ("alpha", "beta", "gamma delta") and r["choices"][0]["finish_reason"] == "stop"
+    r = client.post("/v1/completions", json={"prompt": "n=", "max_tokens": 8, "temperature": 0.8, "seed": 1,
+                                              "guided_regex": r"[1-9]\d{2}"}).json()
+    assert re.fullmatch(r"[1-9]\d{2}", r["choices"][0]["text"]) and r["choices"][0]["finish_reason"] == "stop"
+    assert client.post("/v1/completions", json={"prompt": "x", "guided_regex": "(a"}).status_code == 400
