@@ -3,8 +3,10 @@
 concurrency C (default 128, the top rung of the reference's ISL128/OSL1024 ladder) on N GPUs
 of one node. For N > 1 the default is one engine replica per GPU, each serving its own C
 requests (the model fits one GPU, so replicas are the throughput deployment; the job's value is
-the sum over replicas, weak scaling); `--parallelism tp` shards one engine over the N GPUs with
-the fused GEMM + all-reduce kernels over NVLink peer memory (C requests in total, strong scaling).
+the sum over replicas, weak scaling); `--parallelism tp` shards one engine over the N GPUs, the
+tensor-parallel sweep of the same configuration (C requests in total, strong scaling; NCCL
+all-reduce after the row-parallel GEMMs, or with `--fused` the GEMM + all-reduce kernels over
+NVLink peer memory).
 
     python bench.py --gpus 1 --steps 64 --warmup 8
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
