@@ -201,7 +201,13 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
             th = body.get("thinking")
             thinking = bool(th and (th is True or th.get("type") == "enabled"))
         thinking = bool(thinking) and not cfg.disable_thinking
-        kw = body.get("chat_template_kwargs") or {}
+        kw = dict(body.get("chat_template_kwargs") or {})
+        # the template variable `reasoning_effort`: the request's value (also as `reasoning.effort`)
+        # while thinking is on, "medium" when it says nothing, "none" when thinking is off
+        eff = body.get("reasoning_effort") or ((body.get("reasoning") or {}).get("effort") if isinstance(body.get("reasoning"), dict) else None)
+        if eff is not None and eff not in ("none", "minimal", "low", "medium", "high", "max"):
+            raise HTTPException(400, "reasoning_effort must be one of none, minimal, low, medium, high, max")
+        kw.setdefault("reasoning_effort", (eff or "medium") if thinking else "none")
         text = renderer.render(msgs, tools=tools, add_generation_prompt=True, enable_thinking=thinking, **kw)
         ids = tokenizer.encode(text)
         sp = _sampling_from(body, cfg)

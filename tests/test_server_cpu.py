@@ -891,3 +891,25 @@ def test_guided_fields_map_onto_the_grammar_engine(client):
                                               "guided_regex": r"[1-9]\d{2}"}).json()
     assert re.fullmatch(r"[1-9]\d{2}", r["choices"][0]["text"]) and r["choices"][0]["finish_reason"] == "stop"
     assert client.post("/v1/completions", json={"prompt": "x", "guided_regex": "(a"}).status_code == 400
+
+
+def test_reasoning_effort_reaches_the_chat_template():
+    from fastapi.testclient import TestClient
+    from metrale_inference_alpha_b200.server.app import ServerConfig, create_app
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=2, max_model_len=256))
+    tok = load_tokenizer(None, eng.cfg.vocab_size)
+    tok.chat_template = "{% for m in messages %}{{ m.content }}{% endfor %}|effort={{ reasoning_effort }}|"
+    with TestClient(create_app(eng, tok, ServerConfig(model_name="tiny"))) as c:
+        def n_prompt(**kw):
+            r = c.post("/v1/chat/completions", json=dict({"messages": [{"role": "user", "content": "q"}], "max_tokens": 1}, **kw))
+            assert r.status_code == 200, r.text
+            return r.json()["usage"]["prompt_tokens"]
+        base = len("q|effort=|")
+        assert n_prompt() == base + len("none")                                           # thinking off
+        assert n_prompt(enable_thinking=True) == base + len("medium")                     # on, nothing said
+        assert n_prompt(enable_thinking=True, reasoning_effort="minimal") == base + len("minimal")
+        assert n_prompt(enable_thinking=True, reasoning={"effort": "max"}) == base + len("max")
+        assert n_prompt(reasoning_effort="high") == base + len("none")                    # ignored while thinking is off
+        assert n_prompt(enable_thinking=True, chat_template_kwargs={"reasoning_effort": "low"}) == base + len("low")
+        assert c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "q"}],
+                                                    "reasoning_effort": "extreme"}).status_code == 400
