@@ -468,6 +468,64 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         t.cancel()
         return {"id": response_id, "object": "response", "status": "cancelled"}
 
+    async def _responses_stream(body, job, rid, new_msgs, prev, conv_id):
+        """Responses API event stream: response.created, output_item.added, content_part.added,
+        output_text.delta ..., output_text.done, output_item.done, response.completed (with usage)."""
+        seq = [0]
+
+        def ev(kind: str, **fields) -> str:
+            d = {"type": kind, "sequence_number": seq[0], **fields}
+            seq[0] += 1
+            return f"event: {kind}\ndata: {json.dumps(d)}\n\n"
+        shell = {"id": rid, "object": "response", "created_at": int(time.time()), "model": cfg.model_name,
+                 "previous_response_id": prev, "status": "in_progress", "output": []}
+        yield ev("response.created", response=shell)
+        mid = "msg_" + uuid.uuid4().hex[:16]
+        item = {"type": "message", "id": mid, "role": "assistant", "status": "in_progress", "content": []}
+        yield ev("response.output_item.added", output_index=0, item=item)
+        yield ev("response.content_part.added", item_id=mid, output_index=0, content_index=0,
+                 part={"type": "output_text", "text": "", "annotations": []})
+        rp = ReasoningParser(cfg.reasoning_format, starts_open=job.thinking_open)
+        text, reasoning, usage, status = "", "", None, "completed"
+        async for e in aeng.submit(job.prompt_ids, job.params):
+            if e.error:
+                status = "failed"
+                yield ev("error", message=e.error)
+                break
+            r, c = rp.push(e.text)
+            if e.finished:
+                r2, c2 = rp.flush()
+                r, c = r + r2, c + c2
+                usage = e.usage
+                _account(usage)
+            reasoning += r
+            if c:
+                text += c
+                yield ev("response.output_text.delta", item_id=mid, output_index=0, content_index=0, delta=c)
+        content, calls = (parse_tool_calls(text, cfg.tool_call_parser, job.tools) if job.tools else (text, []))
+        yield ev("response.output_text.done", item_id=mid, output_index=0, content_index=0, text=content)
+        done_item = dict(item, status="completed", content=[{"type": "output_text", "text": content, "annotations": []}])
+        yield ev("response.output_item.done", output_index=0, item=done_item)
+        out = ([{"type": "reasoning", "id": "rs_" + uuid.uuid4().hex[:16], "summary": [{"type": "summary_text", "text": reasoning}]}]
+               if reasoning else []) + [done_item]
+        for cl in calls:
+            out.append({"type": "function_call", "call_id": cl["id"], "name": cl["function"]["name"],
+                        "arguments": cl["function"]["arguments"]})
+        u = usage or {}
+        if status == "completed" and body.get("store", True):
+            store.put(rid, new_msgs, content, prev)
+        if status == "completed" and conv_id:
+            items = [dict(m, type="message") for m in new_msgs if isinstance(m.get("content"), str)]
+            items.append({"type": "message", "role": "assistant", "content": content})
+            try:
+                conversations.add_items(conv_id, items[-20:])
+            except (KeyError, ValueError):
+                pass
+        yield ev("response.completed" if status == "completed" else "response.failed",
+                 response=dict(shell, status=status, output=out,
+                               usage={"input_tokens": u.get("prompt_tokens"), "output_tokens": u.get("completion_tokens"),
+                                      "total_tokens": u.get("total_tokens")}))
+
     @app.post("/v1/responses")
     async def responses(request: Request):
         body = await request.json()
@@ -493,6 +551,8 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         messages = history + new_msgs
         job = _job_from_chat(body, messages, system=body.get("instructions"), tools=body.get("tools"))
         rid = "resp_" + uuid.uuid4().hex[:24]
+        if body.get("stream"):
+            return StreamingResponse(_responses_stream(body, job, rid, new_msgs, prev, conv_id), media_type="text/event-stream")
         task = asyncio.ensure_future(_collect(job))
         running_responses[rid] = task
         try:

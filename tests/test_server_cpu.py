@@ -913,3 +913,22 @@ def test_reasoning_effort_reaches_the_chat_template():
         assert n_prompt(enable_thinking=True, chat_template_kwargs={"reasoning_effort": "low"}) == base + len("low")
         assert c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "q"}],
                                                     "reasoning_effort": "extreme"}).status_code == 400
+
+
+def test_responses_api_streams_typed_events(client):
+    with client.stream("POST", "/v1/responses", json={"input": "hello", "max_output_tokens": 5, "stream": True,
+                                                       "temperature": 0}) as s:
+        lines = [l for l in s.iter_lines() if l]
+    kinds = [l[7:] for l in lines if l.startswith("event: ")]
+    datas = [json.loads(l[6:]) for l in lines if l.startswith("data: ")]
+    assert kinds[0] == "response.created" and kinds[-1] == "response.completed"
+    assert kinds[1:3] == ["response.output_item.added", "response.content_part.added"]
+    assert "response.output_text.done" in kinds and "response.output_item.done" in kinds
+    assert [d["sequence_number"] for d in datas] == list(range(len(datas)))
+    final = datas[-1]["response"]
+    assert final["status"] == "completed" and final["usage"]["output_tokens"] == 5
+    text = final["output"][-1]["content"][0]["text"]
+    assert text == "".join(d["delta"] for d in datas if d["type"] == "response.output_text.delta")
+    # the streamed response was stored: a follow-up continues it
+    r = client.post("/v1/responses", json={"input": "more", "previous_response_id": final["id"], "max_output_tokens": 2}).json()
+    assert r["status"] == "completed" and r["previous_response_id"] == final["id"]
