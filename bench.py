@@ -146,7 +146,7 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=torch.device(dev))
         if use_tp:
             from metrale_inference_alpha_b200.parallel.tp import NcclTpContext
-            tp = NcclTpContext(rank, world, dev, fused=args.fused and not args.no_fused)
+            tp = NcclTpContext(rank, world, dev, fused=not args.no_fused)
 
     from metrale_inference_alpha_b200 import ops
     from metrale_inference_alpha_b200.config.model_config import preset

@@ -124,6 +124,8 @@ class ModelRunner:
         self.max_seqs = max(self.sched.batch_rungs[-1], self.sched.max_num_seqs)
         max_tokens = max(self.sched.max_prefill_tokens + self.max_seqs, self.max_seqs * 8)
         self.stage = _Stager(max_tokens, self.max_seqs, self.max_blocks, device)
+        if hasattr(self.tp, "setup_fused") and self.device.type == "cuda":
+            self.tp.setup_fused(cfg.hidden_size, max_tokens)         # collective: symmetric buffers of the fused reduction
         self.use_graphs = use_graphs and self.device.type == "cuda"
         self.graphs: Dict[Tuple, object] = {}
         self.mtp_drafts = mtp_drafts if weights.mtp is not None else 0
@@ -267,6 +269,7 @@ class ModelRunner:
                                        self.block_size, device=self.device, max_blocks=self.max_blocks)
             self.decoder.calib = {}
             self.decoder.backbone(batch, self.caches)
+            self.tp.end_forward()
             calib = self.decoder.calib
         finally:
             self.decoder.calib = None
@@ -332,9 +335,13 @@ class ModelRunner:
     # ------------------------------------------------------------------ forward variants
     def _forward_select(self, batch: ForwardBatch, greedy: bool, want_lp: bool, n_rows: int):
         """decoder forward + on-device token selection into self.out_ids[:n_rows]."""
-        logits, hidden = self.decoder.forward(batch, self.caches, out_f32=not greedy)
+        merge = greedy and not want_lp and getattr(self.tp, "reduce", None) is not None
+        logits, hidden = self.decoder.forward(batch, self.caches, out_f32=not greedy, gather_logits=not merge)
         self.last_hidden = hidden
-        if greedy:
+        if merge:
+            # vocabulary-parallel greedy selection: one (max, index) pair per rank and row crosses NVLink
+            self.tp.reduce.argmax_merge(logits, self.w.vocab_lo, self.out_ids[:n_rows])
+        elif greedy:
             if want_lp:
                 _, lp = ops.argmax(logits, logprob=True, out=self.out_ids[:n_rows])
                 self.out_lp[:n_rows].copy_(lp)
@@ -345,6 +352,7 @@ class ModelRunner:
                                  self.s_minp[:n_rows], self.s_seed[:n_rows], self.s_step[:n_rows])
             self.out_ids[:n_rows].copy_(ids)
             self.out_lp[:n_rows].copy_(lp)
+        self.tp.end_forward()
         return logits
 
     def _rung(self, n: int) -> int:
@@ -399,6 +407,7 @@ class ModelRunner:
         if n_sample_rows == 0:
             batch = self._stage_with_adapters(plan)
             self.decoder.backbone(batch, self.caches)
+            self.tp.end_forward()
             return StepResult([[] for _ in plan.items], device_ms=(time.perf_counter() - t0) * 1e3)
         if host_logits:
             return self._execute_host_logits(plan, t0)
@@ -438,6 +447,7 @@ class ModelRunner:
         from ..sampling.host import sample_rows
         batch = self._stage_with_adapters(plan)
         logits, hidden = self.decoder.forward(batch, self.caches, out_f32=True)
+        self.tp.end_forward()
         self.last_hidden = hidden
         toks, lps = sample_rows(self, plan, logits)
         self.d2h_bytes += logits.numel() * 4

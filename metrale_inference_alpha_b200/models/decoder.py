@@ -52,9 +52,16 @@ class TpContext:
     def all_gather_last(self, t: torch.Tensor) -> torch.Tensor:
         return t
 
-    def linear_reduce(self, act: Act, w, residual=None) -> torch.Tensor:
-        """Row-parallel projection + sum over ranks + residual."""
+    def linear_reduce(self, act: Act, w, residual=None, defer: bool = False):
+        """Row-parallel projection + sum over ranks + residual. `defer`: the caller's next step
+        is a norm that can perform the sum itself (see parallel.tp.NcclTpContext)."""
         return ops.linear(act, w, residual=residual)
+
+    def sum_deferred(self, y: torch.Tensor, residual=None):
+        return y if residual is None else (residual.float() + y.float()).to(torch.bfloat16)
+
+    def end_forward(self) -> None:
+        pass
 
 
 class Decoder:
@@ -76,7 +83,17 @@ class Decoder:
         self.calib = None                  # dict while calibrating static activation scales (engine/runner.py)
 
     # ------------------------------------------------------------------ helpers
-    def _norm_act(self, x, w, fmt: str, also_bf16: bool = False) -> Act:
+    def _norm_act(self, x, w, fmt: str, also_bf16: bool = False, res_only: bool = False) -> Act:
+        """RMSNorm(x) encoded for the GEMM that consumes it. When x is a pending cross-rank sum
+        the norm kernel performs the sum (+ residual) itself; afterwards ``self.res(x)`` is the
+        summed stream. `res_only`: the caller uses that stream only as the residual of the next
+        row-parallel projection, so each rank may keep just its own row share."""
+        if hasattr(x, "resolve"):
+            if w is None:
+                x = x.resolve()
+            else:
+                return x.owner.reduce_norm(x, w, fmt, plus_one=self.cfg.norm_plus_one, eps=self.cfg.rms_eps,
+                                           also_bf16=also_bf16, gather_residual=not res_only)
         if w is None:                      # post-norm-only models: the block reads the stream as it is
             a = self._as_act(x if x.dtype == torch.bfloat16 or not x.is_cuda else x.to(torch.bfloat16), fmt)
             if also_bf16 and getattr(a, "bf16", None) is None:
@@ -85,10 +102,24 @@ class Decoder:
         return ops.row_op(x, fmt, ops.IN_RMSNORM, w=w, plus_one=self.cfg.norm_plus_one,
                           eps=self.cfg.rms_eps, also_bf16=also_bf16)[0]
 
+    @staticmethod
+    def res(x):
+        """The residual-stream tensor behind x (x itself, or the value of a reduced PendingSum)."""
+        if hasattr(x, "resolve"):
+            return x.value if x.value is not None else x.resolve()
+        return x
+
+    @staticmethod
+    def full(x):
+        """x as a tensor that is complete on every rank."""
+        return x.resolve() if hasattr(x, "resolve") else x
+
     def _add_normed(self, x: torch.Tensor, y: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """x + RMSNorm(y): the sandwich norm of the Gemma family (the block's output is normalised
         before it joins the residual stream)."""
-        n = self._norm_act(y.to(x.dtype) if y.dtype != x.dtype else y, w, "bf16").data
+        if not hasattr(y, "resolve") and y.dtype != x.dtype:
+            y = y.to(x.dtype)
+        n = self._norm_act(y, w, "bf16").data
         return x + n.to(x.dtype)
 
     @staticmethod
@@ -110,9 +141,11 @@ class Decoder:
         window = c.window_layers[li] if (c.window_layers and 0 <= li < len(c.window_layers)) else c.sliding_window
         local = window > 0 and self.cos_local is not None
         cos, sin = (self.cos_local, self.sin_local) if local else (self.cos, self.sin)
-        res = x if add_residual else None
         lora = self._lora_for(batch, li)
-        a = self._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.qkv.fmt], also_bf16=lora is not None)
+        a = self._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.qkv.fmt], also_bf16=lora is not None, res_only=add_residual)
+        x = self.res(x)
+        res = x if add_residual else None
+        defer = add_residual and lora is None
         qkv = ops.linear(a, w.qkv)
         if w.qkv_bias is not None:
             qkv.add_(w.qkv_bias)
@@ -145,7 +178,7 @@ class Decoder:
             oa = ops.paged_attention(q, kc, vc, batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
                                      max_q_len=batch.max_q_len, max_ctx=batch.max_ctx, scale=self.scale,
                                      k_scale=ks, v_scale=vs, window=window, quant_out=static)
-            return self.tp.linear_reduce(oa, w.o, residual=res)
+            return self.tp.linear_reduce(oa, w.o, residual=res, defer=defer)
         o = ops.paged_attention(q, kc, vc, batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
                                 max_q_len=batch.max_q_len, max_ctx=batch.max_ctx, scale=self.scale,
                                 k_scale=ks, v_scale=vs, window=window)
@@ -158,7 +191,7 @@ class Decoder:
                             gate_head_off=D)[0]
         else:
             oa = ops.quantize_act(o, fmt, static_scale=static) if fmt == "nvfp4" else self._as_act(o, fmt)
-        y = self.tp.linear_reduce(oa, w.o, residual=res)
+        y = self.tp.linear_reduce(oa, w.o, residual=res, defer=defer)
         if lora is not None and not c.attn_output_gate:
             lora.apply(y, o, li, "o", batch.adapter_rows)
         return y
@@ -191,7 +224,7 @@ class Decoder:
             gu = ops.linear(a, w.gate_up)
             static = w.down_in_scale if (fmt_d == "nvfp4" and self.calib is None) else 0.0
             h = ops.row_op(gu, fmt_d, ops.IN_SILU_MUL, also_bf16=lora is not None, static_scale=static)[0]
-        y = self.tp.linear_reduce(h, w.down, residual=residual)
+        y = self.tp.linear_reduce(h, w.down, residual=residual, defer=residual is not None and lora is None)
         if lora is not None:
             if hb is None:
                 hb = h.bf16 if getattr(h, "bf16", None) is not None else h.data
@@ -202,7 +235,9 @@ class Decoder:
         if lw.ffn_kind == "none":
             return x
         if lw.ffn_kind == "dense":
-            a = self._norm_act(x, lw.ln2, ACT_FOR_WEIGHT[lw.ffn.gate_up.fmt])
+            plain = lw.post_ffn is None and self.cfg.residual_multiplier == 1.0
+            a = self._norm_act(x, lw.ln2, ACT_FOR_WEIGHT[lw.ffn.gate_up.fmt], res_only=plain)
+            x = self.res(x)
             lora = self._lora_for(batch, li) if batch is not None else None
             rows = batch.adapter_rows if lora is not None else None
             if lw.post_ffn is not None:
@@ -210,7 +245,7 @@ class Decoder:
                 return self._add_normed(x, y, lw.post_ffn)
             if self.cfg.residual_multiplier != 1.0:
                 y = self.dense_ffn(a, lw.ffn, None, lora, li, rows)
-                return x + (y.float() * self.cfg.residual_multiplier).to(x.dtype)
+                return x + (self.full(y).float() * self.cfg.residual_multiplier).to(x.dtype)
             return self.dense_ffn(a, lw.ffn, x, lora, li, rows)
         from .moe import moe_block
         return moe_block(self, x, lw)
@@ -219,6 +254,8 @@ class Decoder:
         if lw.kind == "attention":
             kv = kv or caches.kv
             j = caches.kv_index[i] if kv_idx is None else kv_idx
+            if lw.post_attn is not None or self.cfg.residual_multiplier != 1.0:
+                x = self.full(x)
             if lw.post_attn is not None:
                 y = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i,
                                          add_residual=False)
@@ -226,7 +263,7 @@ class Decoder:
             elif self.cfg.residual_multiplier != 1.0:
                 y = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i,
                                          add_residual=False)
-                x = x + (y.float() * self.cfg.residual_multiplier).to(x.dtype)
+                x = x + (self.full(y).float() * self.cfg.residual_multiplier).to(x.dtype)
             else:
                 x = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i)
         elif lw.kind == "gdn":
@@ -256,7 +293,7 @@ class Decoder:
             x = self.layer(i, x, lw, batch, caches)
         return x
 
-    def logits(self, hidden_rows: torch.Tensor, final_norm=None, out_f32: bool = False) -> torch.Tensor:
+    def logits(self, hidden_rows, final_norm=None, out_f32: bool = False, gather: bool = True) -> torch.Tensor:
         """Final norm + (vocab-parallel) lm_head on the selected rows."""
         a = self._norm_act(hidden_rows, self.w.final_norm if final_norm is None else final_norm, "bf16")
         lg = ops.linear(a, self.w.lm_head, out_f32=out_f32)
@@ -265,14 +302,20 @@ class Decoder:
         cap = self.cfg.final_logit_softcap
         if cap > 0:
             lg = (torch.tanh(lg.float() / cap) * cap).to(lg.dtype)
-        return self.tp.all_gather_last(lg)
+        return self.tp.all_gather_last(lg) if gather else lg
 
-    def forward(self, batch: ForwardBatch, caches: LayerCaches, out_f32: bool = False
-                ) -> Tuple[torch.Tensor, torch.Tensor]:
-        """Returns (logits [R, vocab], hidden [R, hidden]) for batch.logit_rows."""
+    def forward(self, batch: ForwardBatch, caches: LayerCaches, out_f32: bool = False,
+                gather_logits: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Returns (logits [R, vocab], hidden [R, hidden]) for batch.logit_rows. With
+        `gather_logits` off a tensor-parallel rank returns its own vocabulary shard
+        [R, vocab / size] (greedy selection then merges per-rank maxima instead)."""
         x = self.backbone(batch, caches)
-        rows = x.index_select(0, batch.logit_rows) if batch.logit_rows.numel() != x.shape[0] else x
-        return self.logits(rows, out_f32=out_f32), rows
+        if batch.logit_rows.numel() != x.shape[0]:
+            rows = self.full(x).index_select(0, batch.logit_rows)
+        else:
+            rows = x
+        lg = self.logits(rows, out_f32=out_f32, gather=gather_logits)
+        return lg, self.res(rows)
 
     # ------------------------------------------------------------------ MTP draft head
     def mtp_forward(self, token_ids, hidden, batch: ForwardBatch, caches: LayerCaches) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -285,5 +328,6 @@ class Decoder:
         cat = torch.cat([e, h], dim=-1).contiguous()
         x = ops.linear(self._as_act(cat, "bf16"), m.fc)
         x = self.layer(c.num_layers, x, m.layer, batch, caches, kv=caches.mtp_kv, kv_idx=0)
-        rows = x.index_select(0, batch.logit_rows) if batch.logit_rows.numel() != x.shape[0] else x
-        return self.logits(rows, final_norm=m.final_norm), rows
+        rows = self.full(x).index_select(0, batch.logit_rows) if batch.logit_rows.numel() != x.shape[0] else x
+        lg = self.logits(rows, final_norm=m.final_norm)
+        return lg, self.res(rows)

@@ -24,7 +24,8 @@ def mla_block(dec, x, lw, batch, kv, j: int):
     c, w = dec.cfg, lw.mixer
     H, nope, rope, vd, L = w.heads, c.qk_nope_dim, c.qk_rope_dim, c.v_head_dim, c.kv_lora_rank
     T = x.shape[0]
-    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.kv_a.fmt])
+    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.kv_a.fmt], res_only=True)
+    x = dec.res(x)
     if w.q_a is not None:
         qa = ops.linear(a, w.q_a)
         qn = ops.row_op(qa, ACT_FOR_WEIGHT[w.q_b.fmt], ops.IN_RMSNORM, w=w.q_a_norm, eps=c.rms_eps)[0]
@@ -56,7 +57,7 @@ def mla_block(dec, x, lw, batch, kv, j: int):
         o_lat = mla_attention(qq, kv.k[j], batch, scale, L)            # [T, H, L] fp32
     o = torch.einsum("thl,hvl->thv", o_lat, w.w_uv.float()).reshape(T, H * vd)
     oa = ops.quantize_act(o.to(torch.bfloat16), ACT_FOR_WEIGHT[w.o.fmt])
-    return dec.tp.linear_reduce(oa, w.o, residual=x)
+    return dec.tp.linear_reduce(oa, w.o, residual=x, defer=True)
 
 
 def mla_attention(q, cache, batch, scale: float, L: int) -> torch.Tensor:

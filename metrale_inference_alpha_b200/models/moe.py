@@ -18,7 +18,8 @@ from ..ops import ACT_FOR_WEIGHT, moe as moe_ops
 def moe_block(dec, x, lw):
     c, w = dec.cfg, lw.ffn
     fmt = ACT_FOR_WEIGHT[(w.experts[0].gate_up if w.experts else w.shared.gate_up).fmt]
-    a = dec._norm_act(x, lw.ln2, fmt, also_bf16=True)
+    a = dec._norm_act(x, lw.ln2, fmt, also_bf16=True, res_only=dec.tp.size > 1)
+    x = dec.res(x)
     hb = a.bf16
     logits = ops.linear(dec._as_act(hb, "bf16"), w.router, out_f32=True)
     weights, idx = moe_ops.route(logits, c, w.bias)
@@ -40,9 +41,10 @@ def moe_block(dec, x, lw):
     replicated = sh is not None and getattr(w, "shared_replicated", False) and dec.tp.size > 1
     if sh is not None and not replicated:
         y = y.float() + sh.float()
-    y = dec.tp.all_reduce(y.to(torch.bfloat16)) if (dec.tp.size > 1) else y
-    if replicated:
-        y = y.float() + sh.float()
+    if dec.tp.size > 1:
+        # the sum over ranks (+ residual) is left to the next norm when the fused reduction is on
+        res = (x.float() + sh.float()).to(torch.bfloat16) if replicated else x
+        return dec.tp.sum_deferred(y.to(torch.bfloat16), residual=res)
     return (x.float() + y.float()).to(torch.bfloat16)
 
 

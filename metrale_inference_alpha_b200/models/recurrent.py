@@ -20,7 +20,8 @@ def gdn_block(dec, x, lw, batch, pool, sidx: int):
     c, w = dec.cfg, lw.mixer
     kd, vd, kh, vh = c.gdn_k_dim, c.gdn_v_dim, w.k_heads, w.v_heads
     QK, V = kh * kd, vh * vd
-    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.in_qkvz.fmt], also_bf16=True)
+    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.in_qkvz.fmt], also_bf16=True, res_only=True)
+    x = dec.res(x)
     qkvz = ops.linear(a, w.in_qkvz)                                   # [T, 2QK + 2V]
     ba = ops.linear(dec._as_act(a.bf16, "bf16"), w.in_ba, out_f32=True)   # [T, 2 vh] = b | a
     conv_out = rops.causal_conv1d(qkvz, 2 * QK + V, w.conv_w, None, pool.conv[sidx], batch, activation=True)
@@ -29,7 +30,7 @@ def gdn_block(dec, x, lw, batch, pool, sidx: int):
     z = qkvz[:, 2 * QK + V:]
     y = ops.row_op(core, ACT_FOR_WEIGHT[w.out.fmt], ops.IN_GATED_RMSNORM, gate=z, w=_tile(w.norm_w, vh),
                    group=vd, eps=c.rms_eps)[0]
-    return dec.tp.linear_reduce(y, w.out, residual=x)
+    return dec.tp.linear_reduce(y, w.out, residual=x, defer=True)
 
 
 _tile_cache = {}
@@ -46,7 +47,8 @@ def mamba2_block(dec, x, lw, batch, pool, sidx: int):
     c, w = dec.cfg, lw.mixer
     H, G, P, N = w.heads, w.groups, c.mamba_head_dim, c.mamba_state
     inner, GN = H * P, G * N
-    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.in_proj.fmt])
+    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.in_proj.fmt], res_only=True)
+    x = dec.res(x)
     zxbcdt = ops.linear(a, w.in_proj)                                 # [T, 2 inner + 2GN + H]
     xbc = rops.causal_conv1d(zxbcdt[:, inner:], inner + 2 * GN, w.conv_w, w.conv_b, pool.conv[sidx], batch,
                              activation=True)
@@ -56,4 +58,4 @@ def mamba2_block(dec, x, lw, batch, pool, sidx: int):
     z = zxbcdt[:, :inner]
     ya = ops.row_op(y, ACT_FOR_WEIGHT[w.out.fmt], ops.IN_GATED_RMSNORM, gate=z, w=w.norm_w,
                     group=inner // max(1, G), eps=c.rms_eps)[0]
-    return dec.tp.linear_reduce(ya, w.out, residual=x)
+    return dec.tp.linear_reduce(ya, w.out, residual=x, defer=True)

@@ -41,7 +41,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 argmax_kernel(const T* __restrict__ logits, long long ld, int V, int* __restrict__ out_ids,
               float* __restrict__ out_logprob, int mask_a, int mask_b, int* __restrict__ feed,
-              const int* __restrict__ row_map) {
+              const int* __restrict__ row_map, uint2* __restrict__ pair_out, int idx_offset) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ float s_red[32];
@@ -123,10 +123,15 @@ argmax_kernel(const T* __restrict__ logits, long long ld, int V, int* __restrict
   best = s_val[0];
   bidx = s_idx[0];
   if (threadIdx.x == 0) {
-    if (bidx == 0x7fffffff) bidx = 0;
-    const int orow = row_map ? row_map[row] : row;
-    out_ids[orow] = bidx;
-    if (feed) feed[orow] = bidx;
+    if (pair_out) {
+      // vocabulary shard: publish (max logit, global index); the cross-rank merge picks the winner
+      pair_out[row] = make_uint2(__float_as_uint(best), (uint32_t)(bidx == 0x7fffffff ? 0x7fffffff : bidx + idx_offset));
+    } else {
+      if (bidx == 0x7fffffff) bidx = 0;
+      const int orow = row_map ? row_map[row] : row;
+      out_ids[orow] = bidx;
+      if (feed) feed[orow] = bidx;
+    }
   }
   if (out_logprob) {
     float se = 0.f;
@@ -325,11 +330,28 @@ int mb_argmax(const void* logits, int is_f32, long long ld, int M, int V, int* o
   if (!logits || !out_ids || M <= 0 || V <= 0) return MB_ERR_BAD_ARG;
   if (is_f32)
     argmax_kernel<float><<<M, 1024, 0, stream>>>(reinterpret_cast<const float*>(logits), ld, V,
-                                                 out_ids, out_logprob, mask_a, mask_b, feed, row_map);
+                                                 out_ids, out_logprob, mask_a, mask_b, feed, row_map,
+                                                 nullptr, 0);
   else
     argmax_kernel<__nv_bfloat16><<<M, 1024, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(logits), ld, V, out_ids, out_logprob, mask_a, mask_b,
-        feed, row_map);
+        feed, row_map, nullptr, 0);
+  return (int)cudaGetLastError();
+}
+
+// Argmax over one rank's shard of the vocabulary: writes (max logit bits, idx_offset + local
+// index) per row into `pairs` (8 bytes per row) for mb_tp_argmax_merge.
+int mb_argmax_shard(const void* logits, int is_f32, long long ld, int M, int V, void* pairs,
+                    int idx_offset, cudaStream_t stream) {
+  if (!logits || !pairs || M <= 0 || V <= 0) return MB_ERR_BAD_ARG;
+  if (is_f32)
+    argmax_kernel<float><<<M, 1024, 0, stream>>>(reinterpret_cast<const float*>(logits), ld, V, nullptr,
+                                                 nullptr, -1, -1, nullptr, nullptr,
+                                                 reinterpret_cast<uint2*>(pairs), idx_offset);
+  else
+    argmax_kernel<__nv_bfloat16><<<M, 1024, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(logits), ld, V, nullptr, nullptr, -1, -1, nullptr, nullptr,
+        reinterpret_cast<uint2*>(pairs), idx_offset);
   return (int)cudaGetLastError();
 }
 

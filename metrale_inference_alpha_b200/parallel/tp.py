@@ -3,9 +3,14 @@
 ``NcclTpContext`` is both the baseline (plain NCCL all-reduce / all-gather after the local
 GEMM, the reference's scheme: one bf16 all-reduce after o_proj, after the FFN / MoE output and
 on the vocab-parallel logits, ``crates/comm/src/nccl_backend.rs``) and the home of the fused
-paths: when ``fused`` is on, row-parallel projections run ``parallel.fused.gemm_allreduce``
-(GEMM whose epilogue reduces through NVLink peer memory / NVLS multimem), and the lm_head
-exchanges per-rank (max, argmax) pairs instead of all-reducing logits.
+paths. With ``fused`` on (and symmetric memory available) a row-parallel projection writes its
+bf16 partial into a symmetric buffer and returns a ``PendingSum``; the RMSNorm that consumes it
+runs ``parallel.fused.FusedReduce.reduce_norm``: sum over ranks through NVLink (in-switch
+``multimem.ld_reduce`` or peer loads) + residual + norm + quantiser, and for larger batches the
+all-gather of the quantised rows (``multimem.st``), in one kernel. Greedy selection over the
+vocab-parallel lm_head exchanges one (max, index) pair per rank and row
+(``FusedReduce.argmax_merge``) instead of gathering logits. ``fused_gemm`` selects the older
+variant that reduces inside the GEMM epilogue (``FusedCollectives``).
 
 Health: every collective is followed by an async-error check when ``check_health`` is set;
 a failed or timed-out collective poisons the context (all later calls raise) and the engine
@@ -30,7 +35,7 @@ class CommPoisoned(RuntimeError):
 
 class NcclTpContext(TpContext):
     def __init__(self, rank: int, size: int, device, fused: bool = True, group=None,
-                 diagnostics: Optional[bool] = None):
+                 diagnostics: Optional[bool] = None, fused_gemm: bool = False):
         self.rank, self.size = rank, size
         self.device = torch.device(device)
         self.group = group
@@ -40,9 +45,11 @@ class NcclTpContext(TpContext):
         self.diagnostics = (os.environ.get("METRALE_COMM_DIAGNOSTICS") == "1") if diagnostics is None else diagnostics
         self.bytes_reduced = 0
         self.fused_impl = None
+        self.reduce = None               # parallel.fused.FusedReduce once setup_fused() has run
         if os.environ.get("METRALE_NO_FUSED_COLLECTIVES") == "1":
             fused = False
-        if fused and size > 1 and self.device.type == "cuda":
+        self.want_fused = bool(fused) and not fused_gemm and size > 1 and self.device.type == "cuda"
+        if fused and fused_gemm and size > 1 and self.device.type == "cuda":
             try:
                 from .fused import FusedCollectives
                 self.fused_impl = FusedCollectives(rank, size, self.device, group)
@@ -50,6 +57,25 @@ class NcclTpContext(TpContext):
             except Exception as e:                      # symmetric memory unavailable: keep NCCL
                 if rank == 0:
                     print(f"[tp] fused collectives unavailable ({type(e).__name__}: {e}); using NCCL", flush=True)
+
+    def setup_fused(self, hidden: int, m_cap: int) -> bool:
+        """Allocate the symmetric buffers of the consumer-fused reduction (collective: every rank
+        calls it with the same sizes). Returns whether the fused path is on."""
+        if not self.want_fused or self.reduce is not None:
+            return self.reduce is not None
+        try:
+            from .fused import FusedReduce
+            self.reduce = FusedReduce(self.rank, self.size, self.device, hidden, m_cap, self.group)
+            self.fused = True
+        except Exception as e:                          # symmetric memory unavailable: keep NCCL
+            if self.rank == 0:
+                print(f"[tp] fused reduction unavailable ({type(e).__name__}: {e}); using NCCL", flush=True)
+            self.want_fused = False
+        return self.reduce is not None
+
+    def end_forward(self) -> None:
+        if self.reduce is not None:
+            self.reduce.end_forward()
 
     # ------------------------------------------------------------------ plumbing
     def _pre(self, what: str, t: torch.Tensor) -> None:
@@ -89,6 +115,7 @@ class NcclTpContext(TpContext):
             self.poisoned = f"reconnect failed: {e}"
             return False
         self.group, self.poisoned, self.fused, self.reconnects = new_group, None, False, getattr(self, "reconnects", 0) + 1
+        self.reduce = self.fused_impl = None
         return True
 
     # ------------------------------------------------------------------ collectives
@@ -127,14 +154,38 @@ class NcclTpContext(TpContext):
         if self.size > 1:
             dist.barrier(group=self.group)
 
-    def linear_reduce(self, act: Act, w, residual=None) -> torch.Tensor:
-        """Row-parallel projection: sum of the ranks' partial products, plus the residual once."""
+    def linear_reduce(self, act: Act, w, residual=None, defer: bool = False):
+        """Row-parallel projection: sum of the ranks' partial products, plus the residual once.
+        With `defer` (and the fused reduction on) the sum is left to the norm that consumes the
+        result: a ``PendingSum`` is returned instead of a tensor."""
+        residual = getattr(residual, "value", residual)          # a reduced PendingSum stands for its value
         if self.size == 1:
             return ops.linear(act, w, residual=residual)
-        if self.fused and act.data.is_cuda:
+        if self.reduce is not None and act.data.is_cuda and self.reduce.supports(act.M, w.N):
+            if self.poisoned:
+                raise CommPoisoned(self.poisoned)
+            from .fused import PendingSum
+            part = self.reduce.partial_view(act.M)
+            ops.linear(act, w, out=part)
+            pend = PendingSum(self.reduce, part, residual)
+            return pend if defer else pend.resolve()
+        if self.fused_impl is not None and act.data.is_cuda:
             return self.fused_impl.gemm_allreduce(act, w, residual)
         y = ops.linear(act, w, residual=residual if self.rank == 0 else None)
         return self.all_reduce(y)
+
+    def sum_deferred(self, y: torch.Tensor, residual=None):
+        """Sum a bf16 partial result that some other op produced (MoE experts of this rank) over
+        ranks, plus the residual; deferred to the consuming norm when the fused reduction is on."""
+        residual = getattr(residual, "value", residual)
+        if self.size > 1 and self.reduce is not None and y.is_cuda and self.reduce.supports(y.shape[0], y.shape[1]):
+            from .fused import PendingSum
+            part = self.reduce.partial_view(y.shape[0])
+            part.copy_(y)
+            ops._count()
+            return PendingSum(self.reduce, part, residual)
+        y = self.all_reduce(y.to(torch.bfloat16).contiguous()) if self.size > 1 else y
+        return y if residual is None else (residual.float() + y.float()).to(torch.bfloat16)
 
 
 class GlooTpContext(NcclTpContext):

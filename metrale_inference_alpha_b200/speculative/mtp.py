@@ -51,6 +51,7 @@ def mtp_propose(runner, plan, result, accepted: List[int], k: int) -> List[List[
         b = ForwardBatch.build(items, bs, device=dev, max_blocks=runner.max_blocks)
         b.token_ids = toks
         logits, hidden = dec.mtp_forward(toks, hidden, b, runner.caches)
+        runner.tp.end_forward()
         toks = ops.argmax(logits)
         for s, t in zip(seqs, toks.tolist()):
             drafts[s.seq_id].append(int(t))
