@@ -267,8 +267,27 @@ def deepseek_v3_671b(**kw) -> ModelConfig:
     return ModelConfig(**base)
 
 
+def tiny_hybrid_moe(**kw) -> ModelConfig:
+    """Four-layer instance of the hybrid GDN + gated-attention MoE family (tests, smoke runs)."""
+    base = dict(num_layers=4, hidden_size=512, num_heads=4, num_kv_heads=2, gdn_k_heads=4, gdn_v_heads=4,
+                num_experts=8, experts_per_token=2, moe_intermediate_size=256, intermediate_size=256,
+                vocab_size=4096, max_position=1024, name="tiny-hybrid-moe")
+    base.update(kw)
+    return qwen_hybrid_moe_35b(**base)
+
+
+def tiny_nemotron_h(**kw) -> ModelConfig:
+    """Four-mixer instance of the Mamba2 + attention hybrid family (tests, smoke runs)."""
+    base = dict(num_layers=4, hidden_size=512, num_heads=8, num_kv_heads=2, intermediate_size=1024,
+                mamba_heads=16, mamba_groups=2, vocab_size=4096, max_position=1024, name="tiny-nemotron-h")
+    base.update(kw)
+    return nemotron_h_8b(**base)
+
+
 PRESETS = {
     "tiny-dense": tiny_dense,
+    "tiny-hybrid-moe": tiny_hybrid_moe,
+    "tiny-nemotron-h": tiny_nemotron_h,
     "dense-27b-nvfp4": dense_27b_nvfp4,
     "qwen-hybrid-moe-35b-fp8": qwen_hybrid_moe_35b,
     "nemotron-h-8b-fp8": nemotron_h_8b,

@@ -16,6 +16,19 @@ from typing import List, Optional
 import torch
 
 
+class SpecStash:
+    """Inputs of every recurrent op of one speculative verify step. During such a step the
+    recurrent layers read their state but do not advance it; once the scheduler knows how many
+    tokens each sequence accepted, ``ModelRunner.commit_recurrent`` replays exactly that many
+    rows of these inputs through the same ops, state-only (write-on-accept; role of the
+    reference's GDN carry / verify kernels, ``crates/model-engine/src/model/gdn_carry.rs:1-25``,
+    rollback invariants ``book/src/deep-dives/mtp.md:294-300``)."""
+
+    def __init__(self, batch: "ForwardBatch"):
+        self.batch = batch
+        self.layers = {}                 # recurrent layer index -> tuple of retained tensors
+
+
 @dataclass
 class ForwardBatch:
     token_ids: torch.Tensor            # [T] int32
@@ -37,6 +50,8 @@ class ForwardBatch:
     want_hidden: bool = False
     # LoRA: adapter slot of every token row (-1 = base model); None when no row has an adapter
     adapter_rows: Optional[torch.Tensor] = None
+    # speculative verify over recurrent layers: state is left untouched and inputs are retained here
+    spec_stash: Optional[SpecStash] = None
 
     @property
     def device(self):

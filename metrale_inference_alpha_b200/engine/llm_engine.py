@@ -239,6 +239,7 @@ class LLMEngine:
         before = {it.seq.seq_id: len(it.seq.tokens) for it in plan.items} if track else None
         drafts = None
         outs = sch.apply(plan, result, None)
+        self.runner.commit_recurrent(plan)                 # verify steps on recurrent models: write-on-accept
         if speculate:
             k = self.ladder.drafts_for(len(plan.items))
             if k > 0:
@@ -249,7 +250,9 @@ class LLMEngine:
                     drafts = [self.ngram.propose(it.seq.tokens, k) if not it.seq.is_finished() else []
                               for it in plan.items]
                 for it, d in zip(plan.items, drafts):
-                    if not it.seq.is_finished():
+                    # verification is by argmax: only greedy requests speculate (a sampled request
+                    # batched in the same step keeps its sampler)
+                    if not it.seq.is_finished() and it.seq.req.params.greedy:
                         room = it.seq.req.params.max_tokens - it.seq.num_output - 1
                         it.seq.drafts = list(d[:max(0, room)])
         if not speculate and plan.kind in ("decode", "verify"):

@@ -75,6 +75,10 @@ class _Stager:
         self.bytes_per_copy = 0
         self.off = {}
         self.used = 0
+        # the async H2D copy reads the pinned buffer when the stream gets to it, not when it is
+        # enqueued: the event marks that point, and nothing rewrites the buffer before it
+        self.copied = torch.cuda.Event() if pin else None
+        self.in_flight = False
 
     def _layout(self, T: int, S: int):
         off, o = {}, 0
@@ -85,8 +89,15 @@ class _Stager:
             o += n + (n & 1)
         return off, o
 
+    def wait_copied(self) -> None:
+        """Block until the last upload has read the pinned buffer (call before rewriting it)."""
+        if self.in_flight:
+            self.copied.synchronize()
+            self.in_flight = False
+
     def begin(self, T_cap: int, S_cap: int) -> None:
         assert T_cap <= self.max_tokens and S_cap <= self.max_seqs, (T_cap, S_cap)
+        self.wait_copied()
         self.off, self.used = self._layout(T_cap, S_cap)
         self.S_cap = S_cap
 
@@ -97,6 +108,9 @@ class _Stager:
     def upload(self) -> None:
         self.dev[:self.used].copy_(self.host[:self.used], non_blocking=True)
         self.bytes_per_copy = self.used * 4
+        if self.copied is not None:
+            self.copied.record()
+            self.in_flight = True
 
 
 class ModelRunner:
@@ -129,7 +143,7 @@ class ModelRunner:
         self.use_graphs = use_graphs and self.device.type == "cuda"
         self.graphs: Dict[Tuple, object] = {}
         self.mtp_drafts = mtp_drafts if weights.mtp is not None else 0
-        S = self.max_seqs
+        S = max_tokens                   # one entry per sampled row (verify rows included)
         dev = self.device
         # sampling parameters, fixed addresses
         self.s_temp = torch.zeros(S, dtype=torch.float32, device=dev)
@@ -145,6 +159,10 @@ class ModelRunner:
         self.host_lp = torch.zeros(max_tokens, dtype=torch.float32, pin_memory=pin)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        # the kernels' status word (expired bounded waits, out-of-range indices that skipped an
+        # access) rides back with the sampled ids: no extra synchronisation
+        self.host_status = torch.zeros(4, dtype=torch.int32, pin_memory=pin)
+        self.status_pending = False
         self.last_hidden = None
         self.graph_replays = 0
         self.logit_processor = None    # fn(seq, row_logits fp32 [V]) -> row_logits, host-logits path
@@ -166,6 +184,7 @@ class ModelRunner:
         if items[0].start_pos != pos[0] + 1 or items[-1].start_pos != pos[S - 1] + 1:
             self._fast_sig_next = sig
             return False
+        st.wait_copied()
         tokens[:S] = [it.tokens[0] for it in items]
         pos[:S] += 1
         ctx[:S] += 1
@@ -311,26 +330,77 @@ class ModelRunner:
     def _stage_with_adapters(self, plan: StepPlan) -> ForwardBatch:
         batch = self._stage(plan)
         batch.adapter_rows = self._adapter_rows(plan)
+        self.pending_stash = None
+        if self.pool is not None and any(i.verify for i in plan.items):
+            from .batch import SpecStash
+            batch.spec_stash = self.pending_stash = SpecStash(batch)
         return batch
 
+    pending_stash = None
+
+    def commit_recurrent(self, plan: StepPlan) -> None:
+        """After the scheduler has applied a verify step: advance the recurrent state of every
+        sequence by the rows it accepted (the verify forward left the state untouched)."""
+        stash, self.pending_stash = self.pending_stash, None
+        if stash is None:
+            return
+        import dataclasses
+        from ..models.recurrent import commit_recurrent
+        b = stash.batch
+        n = [0] * b.q_len.numel()
+        for s, it in enumerate(plan.items):
+            if it.seq.is_finished():
+                continue
+            n[s] = (getattr(it.seq, "last_accept", 0) + 1) if it.verify else len(it.tokens)
+        ql = torch.tensor(n, dtype=torch.int32)
+        self.h2d_bytes += ql.numel() * 4
+        cb = dataclasses.replace(b, q_len=ql.to(self.device, non_blocking=True), spec_stash=None)
+        commit_recurrent(self.cfg, self.pool, stash, cb)
+
     def _set_sampling(self, plan: StepPlan) -> bool:
-        """Upload per-row sampling parameters; returns True when every row is greedy."""
+        """Upload per-row sampling parameters (one entry per sampled row: a sequence that verifies
+        k drafts contributes k + 1 rows; drafts are only ever given to greedy sequences, whose rows
+        carry temperature 0 and are selected by argmax inside the sampler). Returns True when every
+        row is greedy."""
         all_greedy = all(i.seq.req.params.greedy for i in plan.items)
         if all_greedy:
             return True
-        n = len(plan.items)
-        P = [i.seq.req.params for i in plan.items]
+        items = [i for i in plan.items if i.sample for _ in range(i.verify + 1)]
+        n = len(items)
+        P = [i.seq.req.params for i in items]
         dev = self.device
         self.s_temp[:n] = torch.tensor([p.temperature for p in P], dtype=torch.float32).to(dev, non_blocking=True)
         self.s_topk[:n] = torch.tensor([p.top_k for p in P], dtype=torch.int32).to(dev, non_blocking=True)
         self.s_topp[:n] = torch.tensor([p.top_p for p in P], dtype=torch.float32).to(dev, non_blocking=True)
         self.s_minp[:n] = torch.tensor([p.min_p for p in P], dtype=torch.float32).to(dev, non_blocking=True)
         seeds = [(p.seed if p.seed is not None else i.seq.seq_id * 1000003) & ((1 << 62) - 1)
-                 for p, i in zip(P, plan.items)]
+                 for p, i in zip(P, items)]
         self.s_seed[:n] = torch.tensor(seeds, dtype=torch.int64).to(dev, non_blocking=True)
-        self.s_step[:n] = torch.tensor([i.seq.sample_step for i in plan.items], dtype=torch.int64).to(dev, non_blocking=True)
+        self.s_step[:n] = torch.tensor([i.seq.sample_step for i in items], dtype=torch.int64).to(dev, non_blocking=True)
         self.h2d_bytes += n * 32
         return False
+
+    # ------------------------------------------------------------------ device status
+    def _post_status(self) -> None:
+        """Queue a copy of the status word behind the step's kernels."""
+        if self.device.type == "cuda":
+            self.host_status.copy_(ops.runtime(self.device).status, non_blocking=True)
+            self.status_pending = True
+            self.d2h_bytes += 16
+
+    def _check_status(self) -> None:
+        """After a stream synchronisation: raise if any kernel since the last check reported."""
+        if not self.status_pending:
+            return
+        self.status_pending = False
+        code = int(self.host_status[0])
+        if code:
+            if self.device.type == "cuda":
+                ops.runtime(self.device).status.zero_()
+            from ..ops._native import KernelError
+            what = {0x400: "a peer wait expired", 0x500: "an out-of-range index skipped an access"}.get(
+                code, "a bounded wait expired")
+            raise KernelError(f"device status 0x{code:x}: {what}")
 
     # ------------------------------------------------------------------ forward variants
     def _forward_select(self, batch: ForwardBatch, greedy: bool, want_lp: bool, n_rows: int):
@@ -408,6 +478,7 @@ class ModelRunner:
             batch = self._stage_with_adapters(plan)
             self.decoder.backbone(batch, self.caches)
             self.tp.end_forward()
+            self._post_status()                       # read at the next synchronisation point
             return StepResult([[] for _ in plan.items], device_ms=(time.perf_counter() - t0) * 1e3)
         if host_logits:
             return self._execute_host_logits(plan, t0)
@@ -417,16 +488,16 @@ class ModelRunner:
             self._decode_graph(plan, greedy, want_lp)
         else:
             batch = self._stage_with_adapters(plan)     # steps with adapter rows run eagerly
-            if not greedy and n_sample_rows != len(plan.items):
-                greedy = True                                   # verify rows are always argmax
             self._forward_select(batch, greedy, want_lp, n_sample_rows)
         self.host_ids[:n_sample_rows].copy_(self.out_ids[:n_sample_rows], non_blocking=True)
         if want_lp or not greedy:
             self.host_lp[:n_sample_rows].copy_(self.out_lp[:n_sample_rows], non_blocking=True)
             self.d2h_bytes += 4 * n_sample_rows
         self.d2h_bytes += 4 * n_sample_rows
+        self._post_status()
         if dev_cuda:
             torch.cuda.current_stream(self.device).synchronize()
+        self._check_status()
         ids = self.host_ids[:n_sample_rows].tolist()
         lps = self.host_lp[:n_sample_rows].tolist() if (want_lp or not greedy) else None
         toks, lpo, r = [], [], 0
@@ -449,7 +520,11 @@ class ModelRunner:
         logits, hidden = self.decoder.forward(batch, self.caches, out_f32=True)
         self.tp.end_forward()
         self.last_hidden = hidden
+        self._post_status()
         toks, lps = sample_rows(self, plan, logits)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()
+        self._check_status()
         self.d2h_bytes += logits.numel() * 4
         return StepResult(toks, lps, hidden=hidden, device_ms=(time.perf_counter() - t0) * 1e3)
 

@@ -24,9 +24,14 @@ def gdn_block(dec, x, lw, batch, pool, sidx: int):
     x = dec.res(x)
     qkvz = ops.linear(a, w.in_qkvz)                                   # [T, 2QK + 2V]
     ba = ops.linear(dec._as_act(a.bf16, "bf16"), w.in_ba, out_f32=True)   # [T, 2 vh] = b | a
-    conv_out = rops.causal_conv1d(qkvz, 2 * QK + V, w.conv_w, None, pool.conv[sidx], batch, activation=True)
+    stash = getattr(batch, "spec_stash", None)
+    ws = stash is None                                               # verify steps commit the state afterwards
+    conv_out = rops.causal_conv1d(qkvz, 2 * QK + V, w.conv_w, None, pool.conv[sidx], batch, activation=True,
+                                  write_state=ws)
     core = rops.gdn_recurrence(conv_out, ba, w.A_log, w.dt_bias, pool.ssm[sidx], batch,
-                               k_heads=kh, v_heads=vh, k_dim=kd, v_dim=vd)          # [T, V] fp32
+                               k_heads=kh, v_heads=vh, k_dim=kd, v_dim=vd, write_state=ws)   # [T, V] fp32
+    if stash is not None:
+        stash.layers[sidx] = ("gdn", lw, qkvz, conv_out, ba)
     z = qkvz[:, 2 * QK + V:]
     y = ops.row_op(core, ACT_FOR_WEIGHT[w.out.fmt], ops.IN_GATED_RMSNORM, gate=z, w=_tile(w.norm_w, vh),
                    group=vd, eps=c.rms_eps)[0]
@@ -50,12 +55,37 @@ def mamba2_block(dec, x, lw, batch, pool, sidx: int):
     a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.in_proj.fmt], res_only=True)
     x = dec.res(x)
     zxbcdt = ops.linear(a, w.in_proj)                                 # [T, 2 inner + 2GN + H]
+    stash = getattr(batch, "spec_stash", None)
+    ws = stash is None
     xbc = rops.causal_conv1d(zxbcdt[:, inner:], inner + 2 * GN, w.conv_w, w.conv_b, pool.conv[sidx], batch,
-                             activation=True)
+                             activation=True, write_state=ws)
     dt = zxbcdt[:, 2 * inner + 2 * GN:]
     y = rops.mamba2_scan(xbc, dt, w.A_log, w.D, w.dt_bias, pool.ssm[sidx], batch, heads=H, groups=G,
-                         head_dim=P, state=N)                          # [T, inner] fp32
+                         head_dim=P, state=N, write_state=ws)          # [T, inner] fp32
+    if stash is not None:
+        stash.layers[sidx] = ("mamba2", lw, zxbcdt, xbc, dt)
     z = zxbcdt[:, :inner]
     ya = ops.row_op(y, ACT_FOR_WEIGHT[w.out.fmt], ops.IN_GATED_RMSNORM, gate=z, w=w.norm_w,
                     group=inner // max(1, G), eps=c.rms_eps)[0]
     return dec.tp.linear_reduce(ya, w.out, residual=x, defer=True)
+
+
+def commit_recurrent(cfg, pool, stash, commit_batch) -> None:
+    """Advance the state of every recurrent layer by the accepted rows of a verify step:
+    `commit_batch` is that step's batch with q_len replaced by the number of rows to commit per
+    sequence (0 = leave the sequence's state as it was)."""
+    for sidx, (kind, lw, x_in, conv_out, gate) in stash.layers.items():
+        w = lw.mixer
+        if kind == "gdn":
+            kd, vd, kh, vh = cfg.gdn_k_dim, cfg.gdn_v_dim, w.k_heads, w.v_heads
+            rops.causal_conv1d(x_in, 2 * kh * kd + vh * vd, w.conv_w, None, pool.conv[sidx], commit_batch,
+                               activation=True, write_out=False)
+            rops.gdn_recurrence(conv_out, gate, w.A_log, w.dt_bias, pool.ssm[sidx], commit_batch,
+                                k_heads=kh, v_heads=vh, k_dim=kd, v_dim=vd, write_out=False)
+        else:
+            H, G, P, N = w.heads, w.groups, cfg.mamba_head_dim, cfg.mamba_state
+            inner, GN = H * P, G * N
+            rops.causal_conv1d(x_in[:, inner:], inner + 2 * GN, w.conv_w, w.conv_b, pool.conv[sidx], commit_batch,
+                               activation=True, write_out=False)
+            rops.mamba2_scan(conv_out, gate, w.A_log, w.D, w.dt_bias, pool.ssm[sidx], commit_batch, heads=H,
+                             groups=G, head_dim=P, state=N, write_out=False)

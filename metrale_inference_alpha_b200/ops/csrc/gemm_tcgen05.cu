@@ -33,6 +33,8 @@
 // w8a16_gemm*,w8a8_gemv,fp8_gemm_t_blockscaled}.cu and the W4A4 path of
 // kernels/gb10/qwen3.6-27b/nvfp4/nvfp4_mmq.cu (compiled out for sm_100a there).
 #include "common.cuh"
+#include "gemm_args.h"
+#include <mutex>
 #include "tensormap.h"
 #include "noalloc.h"
 
@@ -79,8 +81,12 @@ struct GemmParams {
   float outq_gs;
   int m_fastest;      // token tiles in blockIdx.x (prefill): see the kernel's launch-order note
   int cluster;        // splits form a thread-block cluster; partial tiles are reduced over DSMEM
-  long long* trace;   // optional per-phase cycle stamps of CTA (0,0,0) and the last CTA in x
-  int dbg;   // timing experiments only: 1 skip SF copies, 2 skip epilogue stores, 4 skip MMAs, 8 skip SF loads
+#ifdef MB_GEMM_TIMING_EXPERIMENTS
+  // kernel-development builds only (never the shipped library): per-phase cycle stamps of CTA
+  // (0,0,0) and the last CTA in x, and switches that skip parts of the work to time the rest
+  long long* trace;
+  int dbg;   // 1 skip SF copies, 2 skip epilogue stores, 4 skip MMAs, 8 skip SF loads, 32 stale activation tiles
+#endif
 };
 
 constexpr int kTileN = 128;  // output features per CTA (UMMA M)
@@ -104,11 +110,17 @@ struct Cfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
 };
 
+#ifdef MB_GEMM_TIMING_EXPERIMENTS
 #define MB_STAMP(i)                                                                              \
   do {                                                                                           \
     if (p.trace && blockIdx.y == 0 && blockIdx.x == 0 && (blockIdx.z == 0 || blockIdx.z == gridDim.z - 1)) \
       p.trace[(blockIdx.z == 0 ? 0 : 12) + (i)] = clock64();                                     \
   } while (0)
+#define MB_DBG(bit) (p.dbg & (bit))
+#else
+#define MB_STAMP(i) do { } while (0)
+#define MB_DBG(bit) 0
+#endif
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -190,7 +202,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (mb::elect_one()) {
-      const bool sf_load = (KIND == KIND_NVFP4) && !(p.dbg & 8);
+      const bool sf_load = (KIND == KIND_NVFP4) && !MB_DBG(8);
       const uint32_t stage_tx = C::kStageBytes - (KIND == KIND_NVFP4 && !sf_load ? 4096 : 0);
       auto load_w = [&](int i) {                   // weight tile + its scale factors
         const int s = i % kStages, kb = kb0 + i;
@@ -255,7 +267,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const uint32_t a_base = mb::smem_u32(sA(s)), b_base = mb::smem_u32(sB(s));
         const uint32_t kSfaCol = kSfBase + (i & 1) * 32, kSfbCol = kSfaCol + 16;
         if constexpr (KIND == KIND_NVFP4) {
-          if (!(p.dbg & 1)) {
+          if (!MB_DBG(1)) {
             const uint32_t sfa = mb::smem_u32(sSFA(s)), sfb = mb::smem_u32(sSFB(s));
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -264,7 +276,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
         }
-        if (!(p.dbg & 4)) {
+        if (!MB_DBG(4)) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const uint64_t da = mb::umma_desc_sw128(a_base + j * 32);
@@ -408,7 +420,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     } else {
       epi_bar_sync();
     }
-    if (do_store && !(p.dbg & 2)) {
+    if (do_store && !MB_DBG(2)) {
       const int rpp = 128 / tpr;                           // rows per pass
       const int n_out0 = swiglu ? (tile_n * kTileN + col0) / 2 : tile_n * kTileN + col0;
       const int n_out_limit = swiglu ? n_limit / 2 : n_limit;
@@ -803,7 +815,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       }
       mb::pdl_wait();
       for (int g = 0; g < pre; ++g) load_x(g);
-      const bool skip_x = p.dbg & 32;                     // timing experiments: stale activation tiles
+      const bool skip_x = MB_DBG(32);                     // timing experiments: stale activation tiles
       for (int g = pre; g < total; ++g) {
         const int s = g % kStages;
         const uint32_t ph = (g / kStages) & 1;
@@ -846,7 +858,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
               mb::tmem_cp_sf(tmem + sfb_col + j * 4, mb::umma_desc_sf(sfb + j * 512));
             }
           }
-          if (!(p.dbg & 4)) {                             // timing experiments: no MMAs
+          if (!MB_DBG(4)) {                             // timing experiments: no MMAs
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint64_t da = mb::umma_desc_sw128(a_base + j * 32);
@@ -904,7 +916,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       if constexpr (KIND == KIND_FP8 || KIND == KIND_NVFP4) {
         if (p.w_scale && n < p.N) wsc *= __ldg(&p.w_scale[n]);
       }
-      for (int c = half; c * 16 < m_valid && !(p.dbg & 2); c += kEpiGroups) {   // dbg 2: timing experiments, no epilogue
+      for (int c = half; c * 16 < m_valid && !MB_DBG(2); c += kEpiGroups) {   // dbg 2: timing experiments, no epilogue
         float v[16];
         mb::tmem_ld16(lane_addr + buf * TN + c * 16, v);
         if (swiglu) {
@@ -1044,44 +1056,6 @@ extern "C" {
 // per-tile arrival counters and must be zero before the first launch.
 size_t mb_gemm_counter_bytes() { return 64 * 1024; }
 
-struct MbGemmArgs {
-  int kind, M, N, K, ldo, a_ld;
-  const void* W;
-  const void* X;
-  void* out;
-  const void* residual;
-  const float* w_scale;
-  const float* a_scale;
-  float alpha;
-  const void* sfa;
-  const void* sfb;
-  int sf_k64;
-  int epilogue, out_f32;
-  void* ws;
-  size_t ws_bytes;
-  uint32_t* status;
-  int force_tn, force_splits, sm_count;
-  int dbg;
-  long long* trace;
-  int no_cluster;           // keep split-K on the workspace path
-  // quantised SwiGLU output (served by the persistent kernel only; MB_ERR_UNSUPPORTED otherwise)
-  void* outq;
-  int ldq;
-  void* outq_sf;
-  int outq_sf_k64;
-  float outq_gs;
-  // fused tensor-parallel all-reduce (0 = off)
-  int tp_size, tp_rank, tp_m_cap, tp_u_cap;
-  void* tp_recv[8];
-  void* tp_out[8];
-  void* tp_flags[8];
-  void* tp_done[8];
-  void* tp_par;
-  const int* tile_expert;   // grouped mode (all four set together)
-  const int* tile_row0;
-  const int* tile_nrows;
-  int n_per_expert, max_tiles;
-};
 
 int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   if (!a || !a->W || !a->X || !a->out || a->M <= 0 || a->N <= 0 || a->K <= 0) return MB_ERR_BAD_ARG;
@@ -1151,8 +1125,10 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   p.splits = splits; p.kb_per_split = kb_per; p.num_kb = num_kb;
   p.epilogue = a->epilogue; p.out_f32 = a->out_f32;
   p.status = a->status;
-  p.dbg = a->dbg;
-  p.trace = a->trace;
+#ifdef MB_GEMM_TIMING_EXPERIMENTS
+  p.dbg = a->flags & 47;
+  p.trace = a->timing_trace;
+#endif
   p.tile_expert = a->tile_expert; p.tile_row0 = a->tile_row0; p.tile_nrows = a->tile_nrows;
   p.n_per_expert = grouped ? a->n_per_expert : 0;
   p.cluster = (splits > 1 && splits <= 8 && !a->no_cluster) ? 1 : 0;
@@ -1193,15 +1169,15 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   rc = mbh::encode_2d(&tmB, dt, a->X, inner, (uint64_t)a->M, row_bytes, box_inner, (uint32_t)tn);
   if (rc) return rc;
 
-  // prefill-sized plain GEMMs put the token tiles in x (dbg bit 64 keeps the decode order, for A/B timing)
-  p.m_fastest = (!grouped && tiles_m >= 8 && tiles_m <= 65535 && tiles_n <= 65535 && !(a->dbg & 64)) ? 1 : 0;
+  // prefill-sized plain GEMMs put the token tiles in x (MB_GEMM_DECODE_TILE_ORDER keeps the decode order)
+  p.m_fastest = (!grouped && tiles_m >= 8 && tiles_m <= 65535 && tiles_n <= 65535 && !(a->flags & MB_GEMM_DECODE_TILE_ORDER)) ? 1 : 0;
   dim3 grid(p.m_fastest ? tiles_m : tiles_n, p.m_fastest ? tiles_n : tiles_m, splits);
   rc = MB_ERR_UNSUPPORTED;
   // more tiles than SMs: persistent CTAs, balanced tile counts. One token tile (decode) always;
-  // several token tiles (prefill, 128-token tiles) when bit 128 of dbg asks for it.
-  const bool multi_m_ok = tiles_m > 1 && tn == 128 && (a->dbg & 128) && !a->outq;
+  // several token tiles (prefill, 128-token tiles) when MB_GEMM_PERSISTENT_PREFILL asks for it.
+  const bool multi_m_ok = tiles_m > 1 && tn == 128 && (a->flags & MB_GEMM_PERSISTENT_PREFILL) && !a->outq;
   if (!grouped && a->tp_size <= 1 && splits == 1 && (tiles_m == 1 || multi_m_ok) && tn <= 128 && kind != KIND_FP8_BLOCK &&
-      tiles > sms && (tiles_m > 1 || tiles_n > sms) && !a->trace && !(a->dbg & 16)) {
+      tiles > sms && (tiles_m > 1 || tiles_n > sms) && !(a->flags & MB_GEMM_ONE_TILE_PER_CTA)) {
     const int waves = (tiles + sms - 1) / sms;
     const int grid_x = (tiles + waves - 1) / waves;
     switch (kind) {
@@ -1252,17 +1228,25 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[MB_NOALLOC_SCRA
 extern "C" int mb_gemm_noalloc(const MbGemmArgs* a, cudaStream_t stream) {
   if (!a) return MB_ERR_BAD_ARG;
   static void* dev_ptr[64] = {nullptr};
+  static std::mutex setup_lock;          // first calls from several threads set a device up once
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= 64) return MB_ERR_UNSUPPORTED;
-  if (!dev_ptr[dev]) {
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaMemsetAsync(ptr, 0, mb_gemm_counter_bytes(), stream);   // arrival counters start at zero
-    if (e != cudaSuccess) return (int)e;
-    dev_ptr[dev] = ptr;
+  {
+    std::lock_guard<std::mutex> guard(setup_lock);
+    if (!dev_ptr[dev]) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+      if (e != cudaSuccess) return (int)e;
+      // arrival counters start at zero; the set-up call waits for this, so that a first pair of
+      // calls on two different streams cannot see the second one run ahead of the clearing
+      e = cudaMemsetAsync(ptr, 0, mb_gemm_counter_bytes(), stream);
+      if (e != cudaSuccess) return (int)e;
+      e = cudaStreamSynchronize(stream);
+      if (e != cudaSuccess) return (int)e;
+      dev_ptr[dev] = ptr;
+    }
   }
   MbGemmArgs b = *a;
   b.ws = dev_ptr[dev];

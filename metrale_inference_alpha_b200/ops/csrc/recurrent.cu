@@ -11,6 +11,13 @@
 //   mb_mamba2_scan     per (head, sequence): dt = softplus(dt + bias); dA = exp(-exp(A_log) dt);
 //                      h = dA h + dt x (x) B; y = h C + D x. Two threads own one row h[p, :].
 //
+// Speculative verification: with `write_state` = 0 a kernel computes its outputs from the stored
+// state and leaves the state untouched; once the number of accepted tokens is known the same
+// kernel is run again over the retained inputs with q_len = accepted count and `write_out` = 0,
+// which advances the state by exactly the accepted tokens with bit-identical arithmetic
+// (write-on-accept; role of kernels/gb10/common/gated_delta_rule_wy4_woa.cu and
+// gated_delta_rule_carry.cu, crates/model-engine/src/model/gdn_carry.rs).
+//
 // Reference behaviour covered: kernels/gb10/common/causal_conv1d.cu (update / fwd / prefill
 // state), ssm_preprocess.cu (compute_gdn_gates), gated_delta_rule.cu (decode_f32_strided and
 // the persistent prefill variants), mamba2_ssm_decode.cu (decode / prefill).
@@ -31,7 +38,7 @@ template <int TAPS>
 __global__ void __launch_bounds__(128)
 conv1d_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int C, const float* __restrict__ w,
               const float* __restrict__ bias, float* __restrict__ state, float* __restrict__ out,
-              SeqMeta sm, int activation, uint32_t* status) {
+              SeqMeta sm, int activation, int write_state, int write_out, uint32_t* status) {
   const int c = blockIdx.x * 128 + threadIdx.x;
   const int seq = blockIdx.y;
   if (c >= C) return;
@@ -58,12 +65,14 @@ conv1d_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int C, const 
 #pragma unroll
     for (int k = 0; k < TAPS; ++k) y += win[k] * wk[k];
     if (activation) y = mb::silu(y);
-    out[(size_t)(q0 + t) * C + c] = y;
+    if (write_out) out[(size_t)(q0 + t) * C + c] = y;
 #pragma unroll
     for (int k = 0; k < TAPS - 1; ++k) win[k] = win[k + 1];
   }
+  if (write_state) {
 #pragma unroll
-  for (int k = 0; k < TAPS - 1; ++k) st[k] = win[k];
+    for (int k = 0; k < TAPS - 1; ++k) st[k] = win[k];
+  }
 }
 
 // ------------------------------------------------------------------ gated delta net
@@ -73,7 +82,7 @@ template <int DK, int DV>
 __global__ void __launch_bounds__(DV)
 gdn_kernel(const float* __restrict__ conv, const float* __restrict__ ba, const float* __restrict__ A_log,
            const float* __restrict__ dt_bias, float* __restrict__ state, float* __restrict__ out,
-           int k_heads, int v_heads, SeqMeta sm, uint32_t* status) {
+           int k_heads, int v_heads, SeqMeta sm, int write_state, int write_out, uint32_t* status) {
   __shared__ float s_q[DK], s_k[DK];
   __shared__ float s_red[8];
   const int vh = blockIdx.x, seq = blockIdx.y, v = threadIdx.x;
@@ -134,10 +143,12 @@ gdn_kernel(const float* __restrict__ conv, const float* __restrict__ ba, const f
       h[k] = gdec * h[k] + (s_k[k] * nk) * vp;
       o += h[k] * s_q[k];
     }
-    out[(size_t)(q0 + t) * V + vh * DV + v] = o * nq;
+    if (write_out) out[(size_t)(q0 + t) * V + vh * DV + v] = o * nq;
   }
+  if (write_state) {
 #pragma unroll
-  for (int k = 0; k < DK; ++k) hs[(size_t)k * DV] = h[k];
+    for (int k = 0; k < DK; ++k) hs[(size_t)k * DV] = h[k];
+  }
 }
 
 // ------------------------------------------------------------------ mamba2
@@ -148,7 +159,7 @@ __global__ void __launch_bounds__(256)
 mamba2_kernel(const float* __restrict__ xbc, const __nv_bfloat16* __restrict__ dt, long long dt_ld,
               const float* __restrict__ A_log, const float* __restrict__ Dp, const float* __restrict__ dt_bias,
               float* __restrict__ state, float* __restrict__ out, int H, int G, int P, SeqMeta sm,
-              uint32_t* status) {
+              int write_state, int write_out, uint32_t* status) {
   constexpr int N = 2 * NH;
   __shared__ float s_B[N], s_C[N];
   const int hd = blockIdx.x, seq = blockIdx.y;
@@ -191,10 +202,12 @@ mamba2_kernel(const float* __restrict__ xbc, const __nv_bfloat16* __restrict__ d
       y += h[j] * s_C[half * NH + j];
     }
     y += __shfl_xor_sync(0xffffffffu, y, 1);
-    if (half == 0) out[(size_t)(q0 + t) * inner + hd * P + p] = y + dcoef * xv;
+    if (half == 0 && write_out) out[(size_t)(q0 + t) * inner + hd * P + p] = y + dcoef * xv;
   }
+  if (write_state) {
 #pragma unroll
-  for (int j = 0; j < NH; ++j) hs[j] = h[j];
+    for (int j = 0; j < NH; ++j) hs[j] = h[j];
+  }
 }
 
 }  // namespace
@@ -203,16 +216,16 @@ extern "C" {
 
 int mb_causal_conv1d(const void* x, long long x_ld, int C, int taps, const float* w, const float* bias,
                      float* state, float* out, const int* q_start, const int* q_len, const int* positions,
-                     const int* state_slots, int num_seqs, int num_slots, int activation, uint32_t* status,
-                     cudaStream_t stream) {
+                     const int* state_slots, int num_seqs, int num_slots, int activation, int write_state,
+                     int write_out, uint32_t* status, cudaStream_t stream) {
   if (!x || !w || !state || !out || C <= 0 || num_seqs <= 0) return MB_ERR_BAD_ARG;
   SeqMeta sm{q_start, q_len, positions, state_slots, num_slots};
   dim3 grid((C + 127) / 128, num_seqs);
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
   switch (taps) {
-    case 2: conv1d_kernel<2><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, status); break;
-    case 3: conv1d_kernel<3><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, status); break;
-    case 4: conv1d_kernel<4><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, status); break;
+    case 2: conv1d_kernel<2><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, write_state, write_out, status); break;
+    case 3: conv1d_kernel<3><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, write_state, write_out, status); break;
+    case 4: conv1d_kernel<4><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, write_state, write_out, status); break;
     default: return MB_ERR_UNSUPPORTED;
   }
   return (int)cudaGetLastError();
@@ -221,16 +234,17 @@ int mb_causal_conv1d(const void* x, long long x_ld, int C, int taps, const float
 int mb_gdn_recurrence(const float* conv, const float* ba, const float* A_log, const float* dt_bias,
                       float* state, float* out, int k_heads, int v_heads, int k_dim, int v_dim,
                       const int* q_start, const int* q_len, const int* positions, const int* state_slots,
-                      int num_seqs, int num_slots, uint32_t* status, cudaStream_t stream) {
+                      int num_seqs, int num_slots, int write_state, int write_out, uint32_t* status,
+                      cudaStream_t stream) {
   if (!conv || !ba || !state || !out || num_seqs <= 0 || v_heads % k_heads) return MB_ERR_BAD_ARG;
   SeqMeta sm{q_start, q_len, positions, state_slots, num_slots};
   dim3 grid(v_heads, num_seqs);
   if (k_dim == 128 && v_dim == 128)
-    gdn_kernel<128, 128><<<grid, 128, 0, stream>>>(conv, ba, A_log, dt_bias, state, out, k_heads, v_heads, sm, status);
+    gdn_kernel<128, 128><<<grid, 128, 0, stream>>>(conv, ba, A_log, dt_bias, state, out, k_heads, v_heads, sm, write_state, write_out, status);
   else if (k_dim == 64 && v_dim == 64)
-    gdn_kernel<64, 64><<<grid, 64, 0, stream>>>(conv, ba, A_log, dt_bias, state, out, k_heads, v_heads, sm, status);
+    gdn_kernel<64, 64><<<grid, 64, 0, stream>>>(conv, ba, A_log, dt_bias, state, out, k_heads, v_heads, sm, write_state, write_out, status);
   else if (k_dim == 32 && v_dim == 32)
-    gdn_kernel<32, 32><<<grid, 32, 0, stream>>>(conv, ba, A_log, dt_bias, state, out, k_heads, v_heads, sm, status);
+    gdn_kernel<32, 32><<<grid, 32, 0, stream>>>(conv, ba, A_log, dt_bias, state, out, k_heads, v_heads, sm, write_state, write_out, status);
   else
     return MB_ERR_UNSUPPORTED;
   return (int)cudaGetLastError();
@@ -239,18 +253,19 @@ int mb_gdn_recurrence(const float* conv, const float* ba, const float* A_log, co
 int mb_mamba2_scan(const float* xbc, const void* dt, long long dt_ld, const float* A_log, const float* D,
                    const float* dt_bias, float* state, float* out, int H, int G, int P, int N,
                    const int* q_start, const int* q_len, const int* positions, const int* state_slots,
-                   int num_seqs, int num_slots, uint32_t* status, cudaStream_t stream) {
+                   int num_seqs, int num_slots, int write_state, int write_out, uint32_t* status,
+                   cudaStream_t stream) {
   if (!xbc || !dt || !state || !out || num_seqs <= 0 || H % G || P > 128 || P <= 0) return MB_ERR_BAD_ARG;
   SeqMeta sm{q_start, q_len, positions, state_slots, num_slots};
   dim3 grid(H, num_seqs);
   const __nv_bfloat16* dtb = reinterpret_cast<const __nv_bfloat16*>(dt);
   const int threads = 2 * P;
   if (N == 128)
-    mamba2_kernel<64><<<grid, threads, 0, stream>>>(xbc, dtb, dt_ld, A_log, D, dt_bias, state, out, H, G, P, sm, status);
+    mamba2_kernel<64><<<grid, threads, 0, stream>>>(xbc, dtb, dt_ld, A_log, D, dt_bias, state, out, H, G, P, sm, write_state, write_out, status);
   else if (N == 64)
-    mamba2_kernel<32><<<grid, threads, 0, stream>>>(xbc, dtb, dt_ld, A_log, D, dt_bias, state, out, H, G, P, sm, status);
+    mamba2_kernel<32><<<grid, threads, 0, stream>>>(xbc, dtb, dt_ld, A_log, D, dt_bias, state, out, H, G, P, sm, write_state, write_out, status);
   else if (N == 16)
-    mamba2_kernel<8><<<grid, threads, 0, stream>>>(xbc, dtb, dt_ld, A_log, D, dt_bias, state, out, H, G, P, sm, status);
+    mamba2_kernel<8><<<grid, threads, 0, stream>>>(xbc, dtb, dt_ld, A_log, D, dt_bias, state, out, H, G, P, sm, write_state, write_out, status);
   else
     return MB_ERR_UNSUPPORTED;
   return (int)cudaGetLastError();

@@ -23,11 +23,14 @@ def _seq_rows(batch):
 
 
 def causal_conv1d(x: torch.Tensor, channels: int, w: torch.Tensor, bias, state: torch.Tensor, batch,
-                  activation: bool = True) -> torch.Tensor:
+                  activation: bool = True, write_state: bool = True, write_out: bool = True) -> torch.Tensor:
     """x [T, >=channels] (first `channels` columns are convolved), w [C, taps] (tap 0 oldest),
-    state [slots, C, taps-1] fp32. Returns fp32 [T, C]; updates the window in place."""
+    state [slots, C, taps-1] fp32. Returns fp32 [T, C]; updates the window in place.
+    `write_state=False` leaves the state untouched (speculative verification);
+    `write_out=False` only advances the state (the commit pass over the accepted tokens).
+    The same two switches exist on the two recurrences below."""
     if x.is_cuda and _native.available() and hasattr(_native.lib(), "mb_causal_conv1d"):
-        return _conv_cuda(x, channels, w, bias, state, batch, activation)
+        return _conv_cuda(x, channels, w, bias, state, batch, activation, write_state, write_out)
     T = x.shape[0]
     out = torch.empty(T, channels, dtype=torch.float32, device=x.device)
     qs, ql, slots, pos0 = _seq_rows(batch)
@@ -40,16 +43,18 @@ def causal_conv1d(x: torch.Tensor, channels: int, w: torch.Tensor, bias, state: 
         for t in range(qs[s], qs[s] + ql[s]):
             y, st = ref.causal_conv1d_update(st, x[t:t + 1, :channels], w, bias, activation)
             out[t] = y[0]
-        state[slots[s]] = st[0]
+        if write_state and ql[s] > 0:
+            state[slots[s]] = st[0]
     return out
 
 
-def gdn_recurrence(conv_out, ba, A_log, dt_bias, state, batch, *, k_heads, v_heads, k_dim, v_dim):
+def gdn_recurrence(conv_out, ba, A_log, dt_bias, state, batch, *, k_heads, v_heads, k_dim, v_dim,
+                   write_state: bool = True, write_out: bool = True):
     """conv_out [T, 2 QK + V] fp32 (q | k | v after conv + SiLU), ba [T, 2 v_heads] fp32
     (b | a). Applies l2-norm to q and k per head, computes decay/beta, runs the delta rule.
     state [slots, v_heads, k_dim, v_dim] fp32. Returns fp32 [T, v_heads * v_dim]."""
     if conv_out.is_cuda and _native.available() and hasattr(_native.lib(), "mb_gdn_recurrence"):
-        return _gdn_cuda(conv_out, ba, A_log, dt_bias, state, batch, k_heads, v_heads, k_dim, v_dim)
+        return _gdn_cuda(conv_out, ba, A_log, dt_bias, state, batch, k_heads, v_heads, k_dim, v_dim, write_state, write_out)
     T = conv_out.shape[0]
     QK, V = k_heads * k_dim, v_heads * v_dim
     out = torch.empty(T, V, dtype=torch.float32, device=conv_out.device)
@@ -65,15 +70,17 @@ def gdn_recurrence(conv_out, ba, A_log, dt_bias, state, batch, *, k_heads, v_hea
             v = conv_out[t, 2 * QK:2 * QK + V].view(1, v_heads, v_dim)
             o, h = ref.gdn_recurrence_step(h, q, k, v, decay[t:t + 1], beta[t:t + 1])
             out[t] = o.reshape(-1)
-        state[slots[s]] = h[0]
+        if write_state and ql[s] > 0:
+            state[slots[s]] = h[0]
     return out
 
 
-def mamba2_scan(xbc, dt, A_log, D, dt_bias, ssm_state, batch, *, heads, groups, head_dim, state):
+def mamba2_scan(xbc, dt, A_log, D, dt_bias, ssm_state, batch, *, heads, groups, head_dim, state,
+                write_state: bool = True, write_out: bool = True):
     """xbc [T, inner + 2 G N] fp32 (x | B | C after conv + SiLU), dt [T, heads] (raw).
     ssm_state [slots, heads, head_dim, state] fp32. Returns fp32 [T, heads * head_dim]."""
     if xbc.is_cuda and _native.available() and hasattr(_native.lib(), "mb_mamba2_scan"):
-        return _mamba_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups, head_dim, state)
+        return _mamba_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups, head_dim, state, write_state, write_out)
     T = xbc.shape[0]
     inner, GN = heads * head_dim, groups * state
     out = torch.empty(T, inner, dtype=torch.float32, device=xbc.device)
@@ -88,7 +95,8 @@ def mamba2_scan(xbc, dt, A_log, D, dt_bias, ssm_state, batch, *, heads, groups, 
             Cm = xbc[t, inner + GN:inner + 2 * GN].view(1, groups, state)
             y, h = ref.mamba2_step(h, x, dt[t:t + 1].float(), A_log, B, Cm, D, dt_bias)
             out[t] = y.reshape(-1)
-        ssm_state[slots[s]] = h[0]
+        if write_state and ql[s] > 0:
+            ssm_state[slots[s]] = h[0]
     return out
 
 
@@ -96,12 +104,12 @@ def mamba2_scan(xbc, dt, A_log, D, dt_bias, ssm_state, batch, *, heads, groups, 
 _c = C
 _native.register_optional("mb_causal_conv1d", [_c.c_void_p, _c.c_longlong, _c.c_int, _c.c_int, _c.c_void_p,
                                               _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
-                                              _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
+                                              _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                               _c.c_void_p, _c.c_void_p])
 _native.register_optional("mb_gdn_recurrence", [_c.c_void_p] * 6 + [_c.c_int] * 4 + [_c.c_void_p] * 4 +
-                          [_c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p])
+                          [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p])
 _native.register_optional("mb_mamba2_scan", [_c.c_void_p, _c.c_void_p, _c.c_longlong] + [_c.c_void_p] * 5 +
-                          [_c.c_int] * 4 + [_c.c_void_p] * 4 + [_c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p])
+                          [_c.c_int] * 4 + [_c.c_void_p] * 4 + [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p])
 
 
 def _status(dev):
@@ -109,38 +117,41 @@ def _status(dev):
     return runtime(dev).status
 
 
-def _conv_cuda(x, channels, w, bias, state, batch, activation):
+def _conv_cuda(x, channels, w, bias, state, batch, activation, write_state=True, write_out=True):
     T = x.shape[0]
     out = torch.empty(T, channels, dtype=torch.float32, device=x.device)
     rc = _native.lib().mb_causal_conv1d(
         _ptr(x), x.stride(0), channels, w.shape[1], _ptr(w), _ptr(bias), _ptr(state), _ptr(out),
         _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions), _ptr(batch.state_slots),
-        batch.q_len.numel(), state.shape[0], int(activation), _ptr(_status(x.device)), _stream())
+        batch.q_len.numel(), state.shape[0], int(activation), int(write_state), int(write_out),
+        _ptr(_status(x.device)), _stream())
     _native.check(rc, "causal_conv1d")
     _count()
     return out
 
 
-def _gdn_cuda(conv_out, ba, A_log, dt_bias, state, batch, k_heads, v_heads, k_dim, v_dim):
+def _gdn_cuda(conv_out, ba, A_log, dt_bias, state, batch, k_heads, v_heads, k_dim, v_dim, write_state=True, write_out=True):
     T = conv_out.shape[0]
     out = torch.empty(T, v_heads * v_dim, dtype=torch.float32, device=conv_out.device)
     rc = _native.lib().mb_gdn_recurrence(
         _ptr(conv_out), _ptr(ba), _ptr(A_log), _ptr(dt_bias), _ptr(state), _ptr(out), k_heads, v_heads,
         k_dim, v_dim, _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions),
-        _ptr(batch.state_slots), batch.q_len.numel(), state.shape[0], _ptr(_status(conv_out.device)), _stream())
+        _ptr(batch.state_slots), batch.q_len.numel(), state.shape[0], int(write_state), int(write_out),
+        _ptr(_status(conv_out.device)), _stream())
     _native.check(rc, "gdn_recurrence")
     _count()
     return out
 
 
-def _mamba_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups, head_dim, state):
+def _mamba_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups, head_dim, state, write_state=True, write_out=True):
     T = xbc.shape[0]
     out = torch.empty(T, heads * head_dim, dtype=torch.float32, device=xbc.device)
     assert dt.dtype == torch.bfloat16
     rc = _native.lib().mb_mamba2_scan(
         _ptr(xbc), _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(D), _ptr(dt_bias), _ptr(ssm_state), _ptr(out),
         heads, groups, head_dim, state, _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions),
-        _ptr(batch.state_slots), batch.q_len.numel(), ssm_state.shape[0], _ptr(_status(xbc.device)), _stream())
+        _ptr(batch.state_slots), batch.q_len.numel(), ssm_state.shape[0], int(write_state), int(write_out),
+        _ptr(_status(xbc.device)), _stream())
     _native.check(rc, "mamba2_scan")
     _count()
     return out

@@ -187,7 +187,10 @@ class SchedulerCore:
         if self.policy.should_prefill(have_prefill, have_decode, now):
             items = self._prefill_items(self.policy.prefill_budget(self.cfg, have_decode))
             if self.cfg.mixed_prefill_decode and have_decode:
-                items = self._decode_items() + items
+                dec = self._decode_items()
+                # growing a decode sequence can preempt a prefilling one when the pool is
+                # exhausted: its blocks are gone, so its chunk leaves the plan too
+                items = dec + [i for i in items if i.seq in self.prefilling]
                 return StepPlan("mixed", items) if items else None
             if items:
                 return StepPlan("prefill", items)

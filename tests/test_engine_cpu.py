@@ -1,6 +1,7 @@
 """Config-1 plumbing check on CPU: the engine (scheduler + paged KV + prefix cache + sampler)
 must reproduce, token for token and logit for logit, a straight-line oracle that re-runs the
 whole sequence through the decoder without any cache reuse."""
+import pytest
 import torch
 
 from metrale_inference_alpha_b200.cache import KvCacheConfig, PagedKvCache
@@ -163,3 +164,53 @@ def test_kv_high_precision_layers_mix_dtypes_per_layer():
     all_bf16 = LLMEngine(EngineArgs(model="tiny-dense", max_model_len=128, num_kv_blocks=32)).generate(
         prompts, SamplingParams(max_tokens=8, temperature=0.0))[0].output_ids
     assert len(hp) == 8 and len(all_bf16) == 8
+
+
+def test_seeded_temperature_request_is_unchanged_by_speculation():
+    """Drafts are verified by argmax, so only greedy requests get them: a seeded temperature
+    request decodes the same tokens with speculation on and off, also when it shares steps with
+    greedy requests that do speculate."""
+    prompts = [[3, 4, 5, 6, 3, 4, 5, 6, 3, 4, 5, 6, 3, 4], [9, 8, 7, 9, 8, 7, 9, 8, 7, 9, 8]]
+    params = [SamplingParams(max_tokens=16, temperature=0.9, top_p=0.95, seed=1234),
+              SamplingParams(max_tokens=16, temperature=0.0)]
+    outs = {}
+    for spec in ("none", "ngram"):
+        eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=256,
+                                   speculative=spec, num_drafts=3, mtp_gate=False))
+        outs[spec] = [o.output_ids for o in eng.generate(prompts, params)]
+    assert outs["ngram"] == outs["none"]
+
+
+def test_a_reported_device_status_latches_the_engine_fault():
+    """The status word comes back with the sampled ids; a non-zero value (an expired bounded
+    wait, a skipped out-of-range access) raises, and step() turns it into a latched fault."""
+    from metrale_inference_alpha_b200.ops._native import KernelError
+    from metrale_inference_alpha_b200.scheduler.types import FatalDeviceError
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_model_len=128, num_kv_blocks=32))
+    r = eng.runner
+    r.host_status[0] = 0x400                               # what MB_ST_TIMEOUT_PEER looks like on the host
+    r.status_pending = True
+    with pytest.raises(KernelError, match="device status 0x400"):
+        r._check_status()
+    assert not r.status_pending
+    eng.add_request([1, 2, 3], SamplingParams(max_tokens=4))
+    real = r._check_status
+
+    def reported():
+        r.host_status[0] = 0x500
+        r.status_pending = True
+        real()
+    r._check_status = reported
+    r._post_status = lambda: None
+    execute = r._execute
+
+    def execute_and_check(plan):
+        out = execute(plan)
+        r._check_status()
+        return out
+    r._execute = execute_and_check
+    with pytest.raises(FatalDeviceError):
+        eng.step()
+    assert eng.fault.is_set()
+    with pytest.raises(FatalDeviceError):
+        eng.add_request([1], SamplingParams(max_tokens=1))

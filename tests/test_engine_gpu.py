@@ -154,3 +154,20 @@ def test_mixed_kv_precision_per_layer_graph_equals_eager():
         outs[graphs] = _drive(eng, _arrivals())
     assert outs[True] == outs[False]
     assert [len(o) for o in outs[True]] == [70, 45, 12, 50, 40, 3]
+
+
+def test_many_chunk_prefill_equals_single_chunk_prefill():
+    """A prompt split into many prefill chunks (none but the last samples, so the runner never
+    synchronises in between) must leave the same KV cache as one chunk: each chunk's metadata is
+    staged in the one pinned buffer, which may only be rewritten once the previous upload has
+    read it. Compared token for token with an engine that prefills the prompt in one piece."""
+    cfg = preset("tiny-dense")
+    prompt = [(7 * j) % 300 + 1 for j in range(300)]
+    outs = {}
+    for budget in (512, 32):
+        eng = LLMEngine(EngineArgs(model=cfg, device="cuda", max_num_seqs=4, max_model_len=512,
+                                   max_prefill_tokens=budget, enable_prefix_caching=False))
+        outs[budget] = eng.generate([prompt, prompt[:150]], SamplingParams(max_tokens=12))
+        if budget == 32:
+            assert eng.scheduler.stats["steps"] >= 10 + 12          # at least ten prefill chunks
+    assert [o.output_ids for o in outs[32]] == [o.output_ids for o in outs[512]]

@@ -124,7 +124,7 @@ def test_gemm_persistent_matches_one_tile_per_cta_kernel_bitwise():
         qw = ops.make_weight(w, fmt).to(DEV)
         act = ops.quantize_act(x.to(DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[fmt])
         a = ops.linear(act, qw)
-        b = ops.linear(act, qw, dbg=16)                   # dbg bit 16: keep the one-tile-per-CTA kernel
+        b = ops.linear(act, qw, one_tile_per_cta=True)
         assert torch.equal(a, b)
     ops.check_status(DEV)
 
@@ -165,9 +165,9 @@ def test_gemm_persistent_prefill_tiles_match_the_one_tile_per_cta_kernel(M, monk
             qw, r = ops.make_weight(w, fmt).to(DEV), res
         act = ops.quantize_act(x.to(DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[fmt])
         a = ops.linear(act, qw, residual=r)
-        b = ops.linear(act, qw, residual=r, dbg=16)               # dbg bit 16: one tile per CTA
+        b = ops.linear(act, qw, residual=r, one_tile_per_cta=True)
         assert torch.equal(a, b), fmt
-        assert torch.equal(ops.linear(act, qw), ops.linear(act, qw, dbg=16)), fmt
+        assert torch.equal(ops.linear(act, qw), ops.linear(act, qw, one_tile_per_cta=True)), fmt
     I = 64 * 160
     _, wg = _mk(M, I, K, 1)
     _, wu = _mk(M, I, K, 2)
@@ -175,7 +175,7 @@ def test_gemm_persistent_prefill_tiles_match_the_one_tile_per_cta_kernel(M, monk
     for fmt in ("nvfp4", "bf16"):
         qw = ops.make_weight(wi, fmt).to(DEV)
         act = ops.quantize_act(x.to(DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[fmt])
-        got, want = ops.linear(act, qw, swiglu=True), ops.linear(act, qw, swiglu=True, dbg=16)
+        got, want = ops.linear(act, qw, swiglu=True), ops.linear(act, qw, swiglu=True, one_tile_per_cta=True)
         # the two epilogues multiply the scales in a different order: equal to a bf16 rounding step
         _close(got, want.float().cpu(), rtol=1e-2, atol=1e-2 * want.float().abs().max().item())
     ops.check_status(DEV)

@@ -268,3 +268,62 @@ def test_slai_policy_orders_admission_and_protects_decodes():
     assert sorted(len(it.seq.tokens) for it in plan.items) == [20, 60]
     outs, _ = drive(sch, ScriptedExecutor())
     assert len(outs) == 4                                       # every request still finishes
+
+
+def test_mixed_lane_never_plans_a_sequence_it_just_preempted():
+    """Mixed prefill + decode with a pool so small that growing the decode rows preempts the
+    prefilling sequence: its chunk must leave the plan (its blocks were freed), every plan item
+    still owns the blocks it addresses, and all requests finish with the scripted tokens."""
+    ex = ScriptedExecutor()
+    sch, alloc = make(blocks=7, mixed_prefill_decode=True, max_prefill_tokens=16)
+    sch.add_request(req(0, n_prompt=30, max_tokens=40))
+    outs = {}
+    steps = 0
+    added = False
+    while sch.has_work() and steps < 2000:
+        plan = sch.plan()
+        if plan is None:
+            continue
+        for it in plan.items:
+            assert it.seq.status in (SeqStatus.PREFILL, SeqStatus.DECODE), it.seq.status
+            need = (it.start_pos + len(it.tokens) + 15) // 16
+            assert len(it.seq.blocks) >= need, (it.seq.req.request_id, len(it.seq.blocks), need)
+        res = ex.execute(plan)
+        for o in sch.apply(plan, res):
+            outs[o.request_id] = o
+        steps += 1
+        if not added and sch.running and len(sch.running[0].tokens) >= 45:
+            sch.add_request(req(1, n_prompt=40, max_tokens=6))     # r0 needs its next block while r1 is prefilling
+            added = True
+    for o in sch.drain_finished():
+        outs[o.request_id] = o
+    assert sch.stats["preempted"] >= 1
+    assert outs["r0"].finished and outs["r1"].finished
+    assert len(outs["r0"].output_ids) == 40 and len(outs["r1"].output_ids) == 6
+
+
+def test_mixed_plan_drops_the_chunk_of_a_sequence_preempted_while_building_it():
+    sch, _ = make(blocks=64, mixed_prefill_decode=True, max_prefill_tokens=16)
+    ex = ScriptedExecutor()
+    sch.add_request(req(0, n_prompt=10, max_tokens=30))
+    while not sch.running:                                   # r0 reaches decode
+        plan = sch.plan()
+        sch.apply(plan, ex.execute(plan))
+    sch.add_request(req(1, n_prompt=40, max_tokens=4))       # r1 will be mid-prefill
+    real = sch._decode_items
+
+    def decode_items_under_pressure():
+        victim = sch.prefilling[0] if sch.prefilling else None
+        items = real()
+        if victim is not None:
+            assert sch.preempt_one(exclude=sch.running[0]) is victim     # what KV exhaustion does
+        return items
+    sch._decode_items = decode_items_under_pressure
+    plan = sch.plan()
+    sch._decode_items = real
+    assert plan is not None and plan.kind == "mixed"
+    assert [it.seq.req.request_id for it in plan.items] == ["r0"]
+    assert all(it.seq.blocks for it in plan.items)
+    sch.apply(plan, ex.execute(plan))
+    outs, _ = drive(sch, ex)
+    assert outs["r1"].finished and len(outs["r1"].output_ids) == 4

@@ -101,3 +101,64 @@ def test_predicted_outputs_on_gpu_are_lossless():
     out = eng.generate([prompt], SamplingParams(max_tokens=40, temperature=0.0, prediction_ids=edited))[0]
     assert out.output_ids == base.output_ids
     assert out.accepted_draft_tokens >= 20 and out.rejected_draft_tokens > 0 and eng.step_count - s0 < 20
+
+
+# ---------------------------------------------------------------- recurrent models: write-on-accept
+def _hybrid_run(device, model, prompts, max_tokens=20, params=None, **kw):
+    cfg = preset(model)
+    eng = LLMEngine(EngineArgs(model=cfg, device=device, max_num_seqs=4, max_model_len=256, mtp_gate=False, **kw))
+    if params is None:
+        params = SamplingParams(max_tokens=max_tokens)
+    outs = eng.generate(prompts, params)
+    eng.last_outputs = outs
+    return [o.output_ids for o in outs], eng
+
+
+def _wrong_predictions(base):
+    """The plain-decode output with every fifth token changed: predictions that are partly
+    accepted and partly rejected, so the verify rows advance the recurrent state past what is
+    finally committed."""
+    preds = []
+    for ids in base:
+        p = list(ids)
+        for j in range(4, len(p), 5):
+            p[j] = (p[j] + 7) % 250 + 1
+        preds.append(p)
+    return preds
+
+
+def _check_recurrent_speculation(device, model):
+    prompts = [[3, 4, 5, 6, 3, 4, 5, 6, 3, 4, 5], [9, 8, 7, 9, 8, 7, 9, 8]]
+    base, _ = _hybrid_run(device, model, prompts)
+    # (1) predicted outputs with forced rejections
+    params = [SamplingParams(max_tokens=20, prediction_ids=p) for p in _wrong_predictions(base)]
+    got, eng = _hybrid_run(device, model, prompts, params=params)
+    assert got == base
+    assert sum(o.rejected_draft_tokens for o in eng.last_outputs) > 0       # rows past the accepted prefix were run
+    assert sum(o.accepted_draft_tokens for o in eng.last_outputs) > 0
+    # (2) n-gram drafts, whatever they are
+    got, eng = _hybrid_run(device, model, prompts, speculative="ngram", num_drafts=3)
+    assert got == base
+
+
+@pytest.mark.parametrize("model", ["tiny-hybrid-moe", "tiny-nemotron-h"])
+def test_speculation_on_recurrent_models_is_lossless_on_cpu(model):
+    _check_recurrent_speculation("cpu", model)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("model", ["tiny-hybrid-moe", "tiny-nemotron-h"])
+def test_speculation_on_recurrent_models_is_lossless_on_gpu(model):
+    _check_recurrent_speculation("cuda", model)
+
+
+def test_mtp_k3_on_a_hybrid_model_is_lossless_on_cpu():
+    prompts = [[3, 4, 5, 6, 3, 4, 5, 6, 3, 4, 5], [9, 8, 7, 9, 8, 7, 9, 8]]
+    cfg = preset("tiny-hybrid-moe", mtp_layers=1)
+    base = [o.output_ids for o in LLMEngine(EngineArgs(model=cfg, device="cpu", max_num_seqs=4, max_model_len=256,
+                                                       mtp_gate=False)).generate(prompts, SamplingParams(max_tokens=16))]
+    eng = LLMEngine(EngineArgs(model=cfg, device="cpu", max_num_seqs=4, max_model_len=256, mtp_gate=False,
+                               speculative="mtp", num_drafts=3))
+    got = [o.output_ids for o in eng.generate(prompts, SamplingParams(max_tokens=16))]
+    assert got == base
+    assert eng.spec_stats.drafted > 0
