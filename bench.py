@@ -1,30 +1,32 @@
 #!/usr/bin/env python
-"""Headline benchmark: aggregate decode tokens/s of the dense ~27B NVFP4 model (fp8 KV) at
-concurrency C (default 128, the top rung of the reference's ISL128/OSL1024 ladder) on N GPUs
-of one node. For N > 1 the default is one engine replica per GPU, each serving its own C
-requests (the model fits one GPU, so replicas are the throughput deployment; the job's value is
-the sum over replicas, weak scaling); `--parallelism tp` shards one engine over the N GPUs, the
-tensor-parallel sweep of the same configuration (C requests in total, strong scaling; NCCL
-all-reduce after the row-parallel GEMMs, or with `--fused` the GEMM + all-reduce kernels over
-NVLink peer memory).
+"""Headline benchmark: aggregate decode tokens/s of the dense ~27B NVFP4 model (fp8 KV) on the
+reference's ISL128 / OSL1024 concurrency ladder, on N GPUs of one node. N > 1 shards ONE engine
+over the N GPUs with tensor parallelism (the configuration's TP = 1/2/4/8 sweep; C requests in
+total, strong scaling): row-parallel GEMMs leave their partial sums in NVLink peer memory and
+the all-reduce runs inside the RMSNorm + quantiser kernel that consumes it (`--no-fused`: NCCL
+all-reduce after the GEMM, the reference's scheme). `--parallelism dp` runs one replica per GPU
+instead (weak scaling).
 
     python bench.py --gpus 1 --steps 64 --warmup 8
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29511 bench.py --gpus 8 --steps 64 --warmup 8
 
 Workload (reference ladder semantics): C requests arrive at once, prompts are 128 uniform
-random token ids (seed 42), temperature 0, context 2048, batch cap 128, OSL 1024. Weights are
-random N(0, 0.02) quantised to NVFP4 (e2m1 + per-16 e4m3 scales + fp32 global scale), bf16
-embeddings / lm_head; there is no network for a real checkpoint.
+random token ids (seed 42), temperature 0, context 2048, batch cap 128, OSL 1024, EOS ignored.
+Weights are random N(0, 0.02) quantised to NVFP4 (e2m1 + per-16 e4m3 scales + fp32 global
+scale), bf16 embeddings / lm_head; there is no network for a real checkpoint.
 
-Two numbers are measured on the same sequences around the middle of the 1024-token
-generation (context ~640, reached by untimed fast-forward decode steps):
-  value  K decode steps replayed as CUDA graphs from device-resident metadata, timed with
-         CUDA events (kernel-only view).
-  e2e    K ticks of the public engine API (`LLMEngine.step()`): scheduler planning, metadata
-         staged in pinned host memory and copied host->device every step, graph replay,
-         on-device token selection, device->host read of the new token ids.
-Both are the max over ranks. One JSON line is printed by rank 0.
+What is measured (all as the max over ranks; rank 0 prints ONE JSON line):
+  value    K decode steps at concurrency C around the middle of the generation (context ~640,
+           reached by untimed fast-forward steps), replayed as CUDA graphs from device-resident
+           metadata and timed with CUDA events: the kernel-only view of a step.
+  e2e      the ladder rung itself through the public API (`LLMEngine.add_request` / `step`):
+           C requests arrive at once, every one generates OSL tokens; value = sum of completion
+           tokens / wall time of the batch, prefill included; p50 TTFT from the same run. Every
+           step stages its metadata in pinned host memory, copies it host -> device, and reads
+           the sampled ids (and the kernels' status word) device -> host. `e2e.k_steps` is the
+           same K steps as `value`, driven through `step()`.
+  config.ladder   the same end-to-end measurement for every rung 1..128 (`--no-ladder` skips it).
 """
 from __future__ import annotations
 
@@ -115,14 +117,16 @@ def main() -> int:
     ap.add_argument("--isl", type=int, default=128)
     ap.add_argument("--osl", type=int, default=1024)
     ap.add_argument("--no-fast-forward", action="store_true")
-    ap.add_argument("--fused", action="store_true",
-                    help="--parallelism tp: fused GEMM + all-reduce kernel over NVLink peer memory (default: NCCL after the GEMM, the faster of the two as measured)")
-    ap.add_argument("--no-fused", action="store_true", help="accepted for compatibility: NCCL collectives are the default")
-    ap.add_argument("--ladder", action="store_true", help="also print one line per concurrency rung")
-    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
-                    help="N>1: dp = one engine replica per GPU, each serving C requests (weak scaling, the "
-                         "throughput deployment of a model that fits one GPU); tp = one engine sharded over "
-                         "N GPUs with the fused GEMM+all-reduce kernels, C requests in total (strong scaling)")
+    ap.add_argument("--fused", action="store_true", help="accepted for compatibility: the fused reduction is the default")
+    ap.add_argument("--no-fused", action="store_true",
+                    help="tensor parallel: NCCL all-reduce after the row-parallel GEMMs + separate norm kernel "
+                         "(the reference's scheme) instead of the reduction fused into its consumer")
+    ap.add_argument("--no-ladder", action="store_true", help="skip the full-OSL ladder (e2e then covers rung C only)")
+    ap.add_argument("--ladder", action="store_true", help="accepted for compatibility: the ladder runs by default")
+    ap.add_argument("--rungs", default="1,2,4,8,16,32,64,128")
+    ap.add_argument("--parallelism", default="tp", choices=["dp", "tp"],
+                    help="N>1: tp = one engine sharded over N GPUs, C requests in total (strong scaling, the "
+                         "configuration's TP sweep); dp = one engine replica per GPU, each serving C requests")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -217,6 +221,7 @@ def main() -> int:
         h2d = (eng.runner.h2d_bytes - h0) / steps
         d2h = (eng.runner.d2h_bytes - d0) / steps
         # ---- kernel-only: replay the decode graph of this rung from device-resident metadata
+        eng.flush()                                       # a step launched ahead is applied first
         plan = eng.scheduler.plan()
         rung = eng.runner._rung(len(plan.items))
         key = (rung, True, False)
@@ -250,39 +255,57 @@ def main() -> int:
     C = args.concurrency
     r = run_rung(C, args.steps, args.warmup)
     eng = r.pop("eng")
+
+    # ---- the ladder: every rung end to end through the public API, full OSL, prefill included
+    from metrale_inference_alpha_b200.bench.ladder import run_rung as ladder_rung
+    rungs = [C] if args.no_ladder else sorted({int(x) for x in args.rungs.split(",") if x} | {C})
+    ladder = {}
+    for c in rungs:
+        ladder_rung(eng, c, min(args.isl, 16), 4, seed=7)          # graph capture / allocator warm-up of the rung
+        h0, d0, s0 = eng.runner.h2d_bytes, eng.runner.d2h_bytes, eng.step_count
+        barrier()
+        row = ladder_rung(eng, c, args.isl, args.osl)
+        barrier()
+        wall = max_over_ranks(row["wall_s"])
+        n_steps = max(1, eng.step_count - s0)
+        ladder[c] = {"tok_s": round(replicas * row["tokens"] / wall, 2), "ttft_p50_ms": round(max_over_ranks(row["ttft_p50_ms"]), 1),
+                     "decode_ms_per_step": round(row["ms_per_step"], 4), "wall_s": round(wall, 3), "steps": n_steps,
+                     "completion_tokens": row["tokens"] * replicas,
+                     "h2d_bytes_per_step": int((eng.runner.h2d_bytes - h0) / n_steps) * replicas,
+                     "d2h_bytes_per_step": int((eng.runner.d2h_bytes - d0) / n_steps) * replicas,
+                     "vs_gb10_published": round(replicas * row["tokens"] / wall / BASELINE_TOKS[c], 2) if c in BASELINE_TOKS else None}
+    top = ladder[C]
     line = {
         "metric": "aggregate decode tok/s at C=%d (ISL128/OSL1024), dense 27B NVFP4, fp8 KV" % C,
         "value": round(r["tok_s"], 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True,
-        "scaling": "strong" if use_tp else "weak", "vs_baseline": round(r["tok_s"] / BASELINE_TOKS.get(C, BASELINE_TOKS[128]), 3),
+        "scaling": "strong" if (use_tp or world == 1) else "weak", "vs_baseline": round(r["tok_s"] / BASELINE_TOKS.get(C, BASELINE_TOKS[128]), 3),
         "dtype": "nvfp4 weights x nvfp4 activations (fp32 accumulate), bf16 lm_head, fp8 KV",
         "data": "synthetic: random-init N(0,0.02) weights in NVFP4 checkpoint layout, uniform-random prompts (seed 42)",
         "config": {"model": cfg.name, "layers": cfg.num_layers, "hidden": cfg.hidden_size,
                    "global_batch": C * replicas, "per_gpu_batch": C if not use_tp else None, "seq_len": args.isl, "osl": args.osl, "context": ctx_len,
                    "mean_ctx_in_timed_window": r["ctx"], "fast_forward_steps": r["ff"],
-                   "parallelism": (f"tp{world}" if use_tp else f"dp{world}"), "l2": "inputs larger than L2 (weights %.1f GB + KV per step)" % (eng.weights.nbytes() / 1e9),
-                   "fused_collectives": bool(tp is not None and getattr(tp, "fused", False)),
-                   "speculative": "off (MTP gate: random-init drafts never accepted)"},
-        "e2e": {"value": round(r["e2e_tok_s"], 2), "unit": "tokens/s", "ms_per_step": round(r["e2e_ms_per_step"], 4),
-                "h2d_bytes_per_step": int(r["h2d"]) * replicas, "d2h_bytes_per_step": int(r["d2h"]) * replicas},
+                   "parallelism": (f"tp{world}" if (use_tp or world == 1) else f"dp{world}"),
+                   "l2": "inputs larger than L2 (weights %.1f GB per GPU + KV per step)" % (eng.weights.nbytes() / 1e9),
+                   "fused_collectives": bool(tp is not None and getattr(tp, "reduce", None) is not None),
+                   "speculative": "off (MTP gate: random-init drafts never accepted)",
+                   "value_is": "K graph-replayed decode steps at C, CUDA events, max over ranks",
+                   "ladder": {str(c): v for c, v in ladder.items()}},
+        "e2e": {"value": top["tok_s"], "unit": "tokens/s",
+                "is": "ladder rung C end to end: C requests at once, OSL tokens each, completion tokens / batch wall, prefill included",
+                "steps": top["steps"], "wall_s": top["wall_s"], "ttft_p50_ms": top["ttft_p50_ms"],
+                "h2d_bytes_per_step": top["h2d_bytes_per_step"], "d2h_bytes_per_step": top["d2h_bytes_per_step"],
+                "k_steps": {"value": round(r["e2e_tok_s"], 2), "ms_per_step": round(r["e2e_ms_per_step"], 4),
+                            "h2d_bytes_per_step": int(r["h2d"]) * replicas, "d2h_bytes_per_step": int(r["d2h"]) * replicas}},
         "gpu_launches": int(r["launches"]),
         "clocks": r["clocks"],
-        "ttft_p50_ms": None if r["ttft_p50_ms"] is None else round(r["ttft_p50_ms"], 1),
+        "ttft_p50_ms": top["ttft_p50_ms"],
         "impl": "ours",
     }
     if args.layers:
         line["invalid"] = "debug run with fewer layers"
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if args.ladder:
-        for c in (1, 2, 4, 8, 16, 32, 64):
-            rr = run_rung(c, max(16, args.steps // 2), args.warmup, eng)
-            rr.pop("eng")
-            if rank == 0:
-                print(json.dumps({"ladder_rung": c, "tok_s": round(rr["tok_s"], 2),
-                                  "e2e_tok_s": round(rr["e2e_tok_s"], 2), "ms_per_step": round(rr["ms_per_step"], 4),
-                                  "ttft_p50_ms": rr["ttft_p50_ms"], "vs_baseline": round(rr["tok_s"] / BASELINE_TOKS[c], 2)}),
-                      flush=True)
     if world > 1:
         # NCCL communicators captured into CUDA graphs do not tear down reliably at interpreter
         # exit; every rank has printed / reduced what it needs, so leave without destructors

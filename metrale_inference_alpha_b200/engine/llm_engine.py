@@ -63,6 +63,7 @@ class EngineArgs:
     kv_cache_dtype: str = "auto"                       # auto (the model config's) | bf16 | fp8
     kv_high_precision_layers: str = ""                 # e.g. "0,1,63" or "first:2,last:2": these layers keep bf16 KV under fp8
     oom_guard_mb: int = 4096                           # device memory left unclaimed when sizing the KV pool
+    pipeline_decode: bool = True                       # launch decode step t + 1 from the device-fed tokens while step t is read back
 
 
 def parse_layer_list(spec: str, num_layers: int) -> tuple:
@@ -161,6 +162,8 @@ class LLMEngine:
         self.ngram = NgramProposer()
         self.spec_stats = SpecStats()
         self.step_count = 0
+        self._inflight = None            # (plan, handle) of a decode step launched ahead and not yet applied
+        self.pipeline = bool(args.pipeline_decode and self.device.type == "cuda" and args.use_cuda_graphs)
         self.tokenizer = None
         self.stop_strings_active = False
 
@@ -206,16 +209,53 @@ class LLMEngine:
         return self.scheduler.abort(request_id)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self._inflight is not None or self.scheduler.has_work()
+
+    def flush(self) -> List[RequestOutput]:
+        """Complete (read back and apply) a decode step that was launched ahead, if any."""
+        if self._inflight is None:
+            return []
+        plan, handle = self._inflight
+        self._inflight = None
+        return self._finish_pipelined(plan, handle, launch_next=False)
+
+    def _finish_pipelined(self, plan: StepPlan, handle, launch_next: bool = True) -> List[RequestOutput]:
+        """Step t is on the device. Launch step t + 1 from the device-fed tokens when the scheduler
+        can plan it blind, then wait for step t's ids and apply them."""
+        nxt = None
+        if launch_next:
+            ahead = self.scheduler.plan_ahead(plan)
+            if ahead is not None:
+                h2 = self.runner.launch_decode(ahead, ahead=True)
+                if h2 is not None:
+                    nxt = (ahead, h2)
+        try:
+            result = self.runner.finish_decode(handle)
+        except RuntimeError as e:
+            if isinstance(e, FatalDeviceError) or "CUDA" in str(e) or "device status" in str(e):
+                self.fault.set(str(e))
+                raise FatalDeviceError(str(e)) from e
+            raise
+        outs = self.scheduler.apply(plan, result, None)
+        self._inflight = nxt
+        self.step_count += 1
+        return outs
 
     # ------------------------------------------------------------------ one tick
     def step(self) -> List[RequestOutput]:
         if self.fault.is_set():
             raise FatalDeviceError(self.fault.reason())
         sch = self.scheduler
+        if self._inflight is not None:
+            plan, handle = self._inflight
+            self._inflight = None
+            return self._finish_pipelined(plan, handle)
         plan = sch.plan()
         if plan is None:
             return sch.drain_finished()
+        if self.pipeline and self.spec_mode == "none" and self.runner.can_pipeline(plan):
+            handle = self.runner.launch_decode(plan)
+            return self._finish_pipelined(plan, handle)
         speculate = False
         if self.spec_mode != "none" and plan.kind in ("decode", "verify"):
             speculate = self.gate.next_step() == MtpGate.MEASURE_VERIFY or not self.gate.enabled

@@ -82,8 +82,10 @@ class _Stager:
 
     def _layout(self, T: int, S: int):
         off, o = {}, 0
-        # slot_mapping and logit rows are int64: they come first / stay 8-byte aligned
-        for name, n in (("slots", 2 * T), ("lrows", 2 * T), ("tokens", T), ("pos", T), ("q_start", S),
+        # token ids come first so that an upload can leave them out (look-ahead decode: the device
+        # wrote them itself); every field starts on an even offset, which keeps the int64 fields
+        # (slot_mapping, logit rows) 8-byte aligned
+        for name, n in (("tokens", T), ("slots", 2 * T), ("lrows", 2 * T), ("pos", T), ("q_start", S),
                         ("q_len", S), ("ctx", S), ("state", S), ("bt", S * self.max_blocks)):
             off[name] = (o, n)
             o += n + (n & 1)
@@ -105,9 +107,10 @@ class _Stager:
         o, cap = self.off[name]
         return buf[o:o + (cap if n is None else n)]
 
-    def upload(self) -> None:
-        self.dev[:self.used].copy_(self.host[:self.used], non_blocking=True)
-        self.bytes_per_copy = self.used * 4
+    def upload(self, skip_tokens: bool = False) -> None:
+        lo = self.off["slots"][0] if skip_tokens else 0
+        self.dev[lo:self.used].copy_(self.host[lo:self.used], non_blocking=True)
+        self.bytes_per_copy = (self.used - lo) * 4
         if self.copied is not None:
             self.copied.record()
             self.in_flight = True
@@ -168,7 +171,7 @@ class ModelRunner:
         self.logit_processor = None    # fn(seq, row_logits fp32 [V]) -> row_logits, host-logits path
 
     # ------------------------------------------------------------------ batch staging
-    def _stage_decode_incremental(self, plan: StepPlan, pad_seqs: int) -> bool:
+    def _stage_decode_incremental(self, plan: StepPlan, pad_seqs: int, ahead: bool = False) -> bool:
         """Plain decode of the same sequences as the previous staged decode step: the pinned
         staging arrays still hold that step, so advance them in place (vectorised: positions and
         context + 1, slots recomputed from the block table, block-table entries only for the
@@ -185,7 +188,8 @@ class ModelRunner:
             self._fast_sig_next = sig
             return False
         st.wait_copied()
-        tokens[:S] = [it.tokens[0] for it in items]
+        if not ahead:                                         # look-ahead: the previous step's argmax fed them on the device
+            tokens[:S] = [it.tokens[0] for it in items]
         pos[:S] += 1
         ctx[:S] += 1
         p = pos[:S]
@@ -194,7 +198,7 @@ class ModelRunner:
             bt2[s, p[s] // bs] = items[s].seq.blocks[p[s] // bs]
         slots = npv("slots").view(np.int64)
         slots[:S] = bt2[np.arange(S), p // bs].astype(np.int64) * bs + p % bs
-        st.upload()
+        st.upload(skip_tokens=ahead)
         self.h2d_bytes += st.bytes_per_copy
         return True
 
@@ -403,20 +407,23 @@ class ModelRunner:
             raise KernelError(f"device status 0x{code:x}: {what}")
 
     # ------------------------------------------------------------------ forward variants
-    def _forward_select(self, batch: ForwardBatch, greedy: bool, want_lp: bool, n_rows: int):
-        """decoder forward + on-device token selection into self.out_ids[:n_rows]."""
+    def _forward_select(self, batch: ForwardBatch, greedy: bool, want_lp: bool, n_rows: int, feed: bool = False):
+        """decoder forward + on-device token selection into self.out_ids[:n_rows]. `feed`: greedy
+        selection also writes each id into the batch's own token buffer, the next decode step's
+        input (look-ahead decode)."""
+        feed_t = batch.token_ids[:n_rows] if (feed and greedy and not want_lp) else None
         merge = greedy and not want_lp and getattr(self.tp, "reduce", None) is not None
         logits, hidden = self.decoder.forward(batch, self.caches, out_f32=not greedy, gather_logits=not merge)
         self.last_hidden = hidden
         if merge:
             # vocabulary-parallel greedy selection: one (max, index) pair per rank and row crosses NVLink
-            self.tp.reduce.argmax_merge(logits, self.w.vocab_lo, self.out_ids[:n_rows])
+            self.tp.reduce.argmax_merge(logits, self.w.vocab_lo, self.out_ids[:n_rows], feed_t)
         elif greedy:
             if want_lp:
                 _, lp = ops.argmax(logits, logprob=True, out=self.out_ids[:n_rows])
                 self.out_lp[:n_rows].copy_(lp)
             else:
-                ops.argmax(logits, out=self.out_ids[:n_rows])
+                ops.argmax(logits, out=self.out_ids[:n_rows], feed=feed_t)
         else:
             ids, lp = ops.sample(logits, self.s_temp[:n_rows], self.s_topk[:n_rows], self.s_topp[:n_rows],
                                  self.s_minp[:n_rows], self.s_seed[:n_rows], self.s_step[:n_rows])
@@ -431,8 +438,10 @@ class ModelRunner:
                 return r
         return n
 
-    def _decode_graph(self, plan: StepPlan, greedy: bool, want_lp: bool):
-        """Replay (capturing on first use) the CUDA graph for this batch rung."""
+    def _decode_graph(self, plan: StepPlan, greedy: bool, want_lp: bool, ahead: bool = False):
+        """Replay (capturing on first use) the CUDA graph for this batch rung. `ahead`: the step's
+        tokens are already in the device buffer (fed by the previous step); returns None when such
+        a step cannot be staged incrementally."""
         n = len(plan.items)
         rung = self._rung(n)
         key = (rung, greedy, want_lp)
@@ -441,14 +450,16 @@ class ModelRunner:
             # the scratch state slot), so capturing never advances a live sequence
             null = self._stage(StepPlan("decode", []), pad_seqs=rung)
             null.max_ctx, null.max_q_len = self.sched.max_model_len, 1   # fixed launch geometry
-            self._forward_select(null, greedy, want_lp, rung)
+            self._forward_select(null, greedy, want_lp, rung, feed=True)
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             count0 = ops.launch_count
             with torch.cuda.graph(g):
-                self._forward_select(null, greedy, want_lp, rung)
+                self._forward_select(null, greedy, want_lp, rung, feed=True)
             self.graphs[key] = (g, ops.launch_count - count0, self.last_hidden)
-        if not self._stage_decode_incremental(plan, rung):
+        if not self._stage_decode_incremental(plan, rung, ahead):
+            if ahead:
+                return None
             sig = self._fast_sig_next
             self._stage(plan, pad_seqs=rung)
             self._fast_sig = sig                              # the arrays now hold this decode step
@@ -458,6 +469,57 @@ class ModelRunner:
         self.graph_replays += 1
         self.last_hidden = hidden
         return rung
+
+    # ------------------------------------------------------------------ pipelined decode
+    def can_pipeline(self, plan: StepPlan) -> bool:
+        """Plain greedy graph-replayed decode: the only step kind that is launched without waiting."""
+        if not (self.use_graphs and plan.kind == "decode" and plan.items):
+            return False
+        if self.decoder.lora is not None and any(i.seq.req.adapter for i in plan.items):
+            return False
+        for it in plan.items:
+            p = it.seq.req.params
+            if len(it.tokens) != 1 or not it.sample or not p.greedy or p.logprobs or p.needs_host_logits \
+                    or p.has_penalties or p.prediction_ids:
+                return False
+        return True
+
+    def launch_decode(self, plan: StepPlan, ahead: bool = False):
+        """Enqueue one decode step (stage, replay, queue the read-back of ids and status) and
+        return a handle for ``finish_decode`` without waiting for the device."""
+        t0 = time.perf_counter()
+        n = len(plan.items)
+        if self._decode_graph(plan, True, False, ahead=ahead) is None:
+            return None
+        par = self._ids_par = self._ids_par ^ 1
+        if self._pipe_host is None:
+            pin = self.device.type == "cuda"
+            self._pipe_host = [torch.zeros(self.max_seqs + 4, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+            self._pipe_ev = [torch.cuda.Event() for _ in range(2)]
+        host = self._pipe_host[par]
+        host[:n].copy_(self.out_ids[:n], non_blocking=True)
+        host[self.max_seqs:self.max_seqs + 4].copy_(ops.runtime(self.device).status, non_blocking=True)
+        self._pipe_ev[par].record()
+        self.d2h_bytes += 4 * n + 16
+        return (plan, par, n, t0)
+
+    def finish_decode(self, handle) -> StepResult:
+        plan, par, n, t0 = handle
+        self._pipe_ev[par].synchronize()
+        host = self._pipe_host[par]
+        code = int(host[self.max_seqs])
+        if code:
+            self.host_status[0] = code
+            self.status_pending = True
+            self._check_status()
+        ids = host[:n].tolist()
+        for it in plan.items:
+            it.seq.sample_step += 1
+        return StepResult([[t] for t in ids], None, hidden=None, device_ms=(time.perf_counter() - t0) * 1e3)
+
+    _ids_par = 0
+    _pipe_host = None
+    _pipe_ev = None
 
     # ------------------------------------------------------------------ entry point
     def execute(self, plan: StepPlan) -> StepResult:

@@ -200,6 +200,37 @@ class SchedulerCore:
         self.policy.note_decode(now)
         return StepPlan("verify" if any(i.verify for i in items) else "decode", items)
 
+    def plan_ahead(self, plan: StepPlan) -> Optional[StepPlan]:
+        """The decode step that follows `plan`, planned before `plan`'s tokens are known (one step
+        of look-ahead: the device feeds each sampled token straight into the next step, so the
+        engine can launch step t + 1 while it reads back step t). Every sequence advances by one
+        position; the token values are placeholders (-1). Returns None whenever the next step is
+        not simply "the same sequences, one position later": something waits for admission, a
+        sequence reaches its length limit at `plan`, or a block is missing (no preemption here).
+        A sequence that ends at `plan` by a stop token still occupies its row in the look-ahead
+        step; `apply` skips finished sequences, so that row's token is discarded.
+        Role of the reference's one-step-ahead decode (``crates/server/src/scheduler/core/pipeline.rs:1-22,124-149``)."""
+        if plan.kind != "decode" or self.waiting or self.prefilling or self.swapped:
+            return None
+        if len(plan.items) != len(self.running):
+            return None
+        items = []
+        for it, seq in zip(plan.items, self.running):
+            if it.seq is not seq or seq.is_finished() or seq.drafts or it.verify or len(it.tokens) != 1:
+                return None
+            L = len(seq.tokens)
+            if seq.num_output + 2 > seq.req.params.max_tokens or L + 2 > self.cfg.max_model_len:
+                return None
+            if self._blocks_for(L + 1) > len(seq.blocks) and self._free_capacity() < 1:
+                return None
+            items.append(SeqStep(seq, [-1], L, sample=True))
+        try:
+            for it in items:
+                self._ensure_blocks(it.seq, it.start_pos + 1)
+        except NoFreeBlocks:
+            return None
+        return StepPlan("decode", items)
+
     def _prefill_items(self, budget: int) -> List[SeqStep]:
         items = []
         for seq in self.prefilling:

@@ -171,3 +171,34 @@ def test_many_chunk_prefill_equals_single_chunk_prefill():
         if budget == 32:
             assert eng.scheduler.stats["steps"] >= 10 + 12          # at least ten prefill chunks
     assert [o.output_ids for o in outs[32]] == [o.output_ids for o in outs[512]]
+
+
+@pytest.mark.parametrize("model", ["tiny-dense", "tiny-hybrid-moe"])
+def test_look_ahead_decode_equals_synchronous_decode(model):
+    """With one step of look-ahead the engine launches decode step t + 1 from the device-fed
+    tokens before it has read step t back. Tokens must equal the synchronous engine's, including
+    a request that stops on a stop token (its in-flight row is discarded), late arrivals (the
+    pipeline drains for their prefill) and ragged finishes."""
+    def run(pipeline, stop=None):
+        eng = LLMEngine(EngineArgs(model=preset(model), device="cuda", max_num_seqs=8, max_model_len=256,
+                                   pipeline_decode=pipeline, enable_prefix_caching=False))
+        arr = _arrivals()
+        ids, res, step = [], {}, 0
+        while arr or eng.has_work():
+            for j, (prompt, n) in enumerate(arr.pop(step, [])):
+                sp = SamplingParams(max_tokens=n, stop_token_ids=[stop] if (stop is not None and step == 0 and j == 0) else [])
+                ids.append(eng.add_request(prompt, sp))
+            if eng.has_work():
+                for o in eng.step():
+                    if o.finished:
+                        res[o.request_id] = (o.output_ids, o.finish_reason)
+            step += 1
+        return [res[i] for i in ids], eng
+    base, _ = run(False)
+    first = base[0][0]
+    stop = next(t for j, t in enumerate(first) if j >= 25 and t not in first[:j])
+    want, _ = run(False, stop)
+    got, eng = run(True, stop)
+    assert got == want
+    assert want[0][1] == "stop" and len(want[0][0]) < 70
+    assert eng.runner.graph_replays > 50

@@ -327,3 +327,73 @@ def test_mixed_plan_drops_the_chunk_of_a_sequence_preempted_while_building_it():
     sch.apply(plan, ex.execute(plan))
     outs, _ = drive(sch, ex)
     assert outs["r1"].finished and len(outs["r1"].output_ids) == 4
+
+
+def _drive_look_ahead(sch, ex, arrivals):
+    """The engine's pipelined loop on the scripted executor: step t + 1 is planned (and 'launched')
+    before step t's tokens are applied."""
+    outs, inflight, step, ahead_steps = {}, None, 0, 0
+    while arrivals or sch.has_work() or inflight:
+        for r in arrivals.pop(step, []):
+            sch.add_request(r)
+        step += 1
+        if inflight is not None:
+            plan, res = inflight
+            inflight = None
+        else:
+            plan = sch.plan()
+            if plan is None:
+                for o in sch.drain_finished():
+                    outs[o.request_id] = o
+                continue
+            res = ex.execute(plan)
+        nxt = sch.plan_ahead(plan) if plan.kind == "decode" else None
+        if nxt is not None:
+            inflight = (nxt, ex.execute(nxt))          # results exist before plan's tokens are applied
+            ahead_steps += 1
+        for o in sch.apply(plan, res):
+            outs[o.request_id] = o
+    for o in sch.drain_finished():
+        outs[o.request_id] = o
+    return outs, ahead_steps
+
+
+def test_look_ahead_decode_equals_synchronous_decode_including_overrun_discard():
+    """One step of look-ahead must not change any request's tokens: sequences that stop on a
+    stop token while their next row is already in flight have that row discarded; arrivals,
+    length limits and block boundaries interrupt the pipeline and it resumes afterwards."""
+    probe, _ = make(blocks=64)
+    for r in (req(0, n_prompt=20, max_tokens=40), req(1, n_prompt=33, max_tokens=17), req(2, n_prompt=9, max_tokens=60)):
+        probe.add_request(r)
+    seq_ids = drive(probe, ScriptedExecutor())[0]["r2"].output_ids
+    stop = next(t for j, t in enumerate(seq_ids) if j >= 20 and t not in seq_ids[:j])   # first seen at step >= 20
+
+    def arrivals():
+        return {0: [req(0, n_prompt=20, max_tokens=40), req(1, n_prompt=33, max_tokens=17),
+                    req(2, n_prompt=9, max_tokens=60, stop_token_ids=[stop])],
+                12: [req(3, n_prompt=50, max_tokens=25)], 13: [req(4, n_prompt=5, max_tokens=3)]}
+    sch, alloc = make(blocks=64)
+    sync_outs = {}
+    arr = arrivals()
+    step = 0
+    ex = ScriptedExecutor()
+    while arr or sch.has_work():
+        for r in arr.pop(step, []):
+            sch.add_request(r)
+        step += 1
+        plan = sch.plan()
+        if plan is None:
+            for o in sch.drain_finished():
+                sync_outs[o.request_id] = o
+            continue
+        for o in sch.apply(plan, ex.execute(plan)):
+            sync_outs[o.request_id] = o
+    sch2, alloc2 = make(blocks=64)
+    outs, ahead_steps = _drive_look_ahead(sch2, ScriptedExecutor(), arrivals())
+    assert ahead_steps > 30
+    assert set(outs) == set(sync_outs) == {f"r{i}" for i in range(5)}
+    for k in outs:
+        assert outs[k].finished and outs[k].output_ids == sync_outs[k].output_ids, k
+        assert outs[k].finish_reason == sync_outs[k].finish_reason
+    assert outs["r2"].finish_reason == "stop" and len(outs["r2"].output_ids) < 60
+    assert alloc2.num_free == alloc.num_free
