@@ -15,6 +15,13 @@
 //                                   activation buffer, so the GEMM that follows reads the
 //                                   gathered operand from local memory (all-gather fused into
 //                                   the producer of the operand): two barriers per call.
+//                         packets   for the smallest batches there is no barrier at all: every rank
+//                                   broadcasts its partial rows as 8-byte packets (two bf16 values
+//                                   + a 4-byte tag that changes every call) with `multimem.st`, and
+//                                   every rank polls its own landing zone until all `size` packets
+//                                   of a position carry the current tag, then sums them in rank
+//                                   order. One NVLink hop per call instead of a signal hop plus a
+//                                   load round trip; twice the bytes, so only below ~1.5 MB.
 //   mb_tp_argmax_merge  vocab-parallel greedy selection: every rank publishes one
 //                       (max logit, global index) pair per row; all ranks pull the pairs of
 //                       their peers and keep the best (8 bytes per rank per row instead of an
@@ -50,7 +57,7 @@ struct TpSync {
   uint32_t* done;              // same three for the completion counter (two-shot)
   uint32_t* done_mc;
   uint32_t* done_peer[8];
-  uint32_t* epoch;             // local: [0] calls completed on this barrier, [1] two-shot calls completed
+  uint32_t* epoch;             // local: [0] calls completed on this barrier, [1] two-shot calls, [2] packet-protocol calls
   uint32_t* cta_done;          // local: CTAs of the running call that have finished
   uint32_t* status;
   long long wait_cycles;
@@ -79,6 +86,12 @@ struct TpNormParams {
   uint8_t* sf;
   int sf_k64;
   float static_gs;
+  // packet protocol: landing zones [2 parity][size][ll_rows][K / 2] of 8-byte packets
+  uint2* ll;                   // this rank's zones
+  uint2* ll_mc;                // multicast alias, or null
+  uint2* ll_peer[8];           // every rank's zones (no-multicast path)
+  int ll_rows;
+  const __nv_bfloat16* partial_local;   // this rank's partial [M, K]
 };
 
 __device__ __forceinline__ void multimem_red_add_release(uint32_t* mc, uint32_t v) {
@@ -187,10 +200,73 @@ __device__ __forceinline__ void pack16(const float* y, uint4& o0, uint4& o1) {
   }
 }
 
+__device__ __forceinline__ void multimem_st_v2(void* mc, uint32_t a, uint32_t b) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc), "f"(__uint_as_float(a)),
+               "f"(__uint_as_float(b))
+               : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys_v2(void* p, uint32_t a, uint32_t b) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+
+// Packet protocol, one row: broadcast this rank's 16 values per thread as 8 packets, then poll
+// the local landing zones of all ranks until every packet carries `tag`; x = bf16(sum in rank
+// order). Returns false when the bounded wait ran out.
+__device__ __forceinline__ bool ll_exchange_row(const TpNormParams& p, int m, int tid, uint32_t tag,
+                                                uint32_t parity, float* x) {
+  const int K = p.K, size = p.s.size;
+  const size_t row_pk = (size_t)(K >> 1);                              // packets per row
+  const size_t zone = (size_t)p.ll_rows * row_pk;                      // packets per (parity, rank)
+  const size_t mine = ((size_t)parity * size + p.s.rank) * zone + (size_t)m * row_pk + (size_t)tid * 8;
+  const uint4 v0 = *reinterpret_cast<const uint4*>(p.partial_local + (size_t)m * K + tid * 16);
+  const uint4 v1 = *reinterpret_cast<const uint4*>(p.partial_local + (size_t)m * K + tid * 16 + 8);
+  const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  if (p.ll_mc) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) multimem_st_v2(p.ll_mc + mine + j, w[j], tag);
+  } else {
+    for (int r = 0; r < size; ++r) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) st_relaxed_sys_v2(p.ll_peer[r] + mine + j, w[j], tag);
+    }
+  }
+  float acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+  const long long t0 = clock64();
+  for (int r = 0; r < size; ++r) {
+    const uint2* src = p.ll + ((size_t)parity * size + r) * zone + (size_t)m * row_pk + (size_t)tid * 8;
+    uint4 q[4];
+    bool ready;
+    do {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) q[j] = ld_relaxed_sys_v4(src + 2 * j);
+      ready = true;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ready = ready && q[j].y == tag && q[j].w == tag;
+      if (!ready && clock64() - t0 > p.s.wait_cycles) {
+        if (p.s.status) atomicCAS(p.s.status, 0u, MB_ST_TIMEOUT_PEER);
+        return false;
+      }
+    } while (!ready);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q[j].x));
+      const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q[j].z));
+      acc[4 * j] += a.x; acc[4 * j + 1] += a.y; acc[4 * j + 2] += c.x; acc[4 * j + 3] += c.y;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) x[i] = __bfloat162float(__float2bfloat16(acc[i]));
+  return true;
+}
+
 // One CTA per row at a time; thread t owns the 16 channels [16 t, 16 t + 16). K % 64 == 0,
-// K <= 8192. TWO = two-shot protocol (outputs are multicast aliases).
-template <bool TWO>
+// K <= 8192. PROTO: 0 one-shot behind a barrier, 1 two-shot (outputs are multicast aliases),
+// 2 packets (no barrier; epoch word [2] counts these calls and gives the tag and the parity).
+template <int PROTO>
 __global__ void __launch_bounds__(512) tp_reduce_norm_kernel(const TpNormParams p) {
+  constexpr bool TWO = PROTO == 1;
   __shared__ float red[64];
   __shared__ uint32_t sh[3];
   const int tid = threadIdx.x, nt = blockDim.x;
@@ -198,15 +274,29 @@ __global__ void __launch_bounds__(512) tp_reduce_norm_kernel(const TpNormParams 
   const bool active = tid < nblk;
   mb::pdl_wait();
   mb::pdl_launch_dependents();
-  uint2 e;
-  const bool ok = sync_enter(p.s, sh, e);
+  uint2 e = make_uint2(0u, 0u);
+  bool ok = true;
+  uint32_t ll_epoch = 0;
+  if (PROTO == 2) {
+    ll_epoch = *reinterpret_cast<volatile uint32_t*>(p.s.epoch + 2);
+  } else {
+    ok = sync_enter(p.s, sh, e);
+  }
   if (ok) {
     for (int m = p.row_lo + blockIdx.x; m < p.row_hi; m += gridDim.x) {
       float x[16];
       float ss = 0.f, mx = 0.f;
+      if (PROTO == 2) {
+        // every thread takes part (a thread beyond the row has no packets and no work)
+        bool got = true;
+        if (active) got = ll_exchange_row(p, m, tid, ll_epoch + 1u, ll_epoch & 1u, x);
+        if (__syncthreads_count(got ? 0 : 1) > 0) { ok = false; break; }
+      }
       if (active) {
         const size_t off = (size_t)m * K + (size_t)tid * 16;
-        if (p.partial_mc) {
+        if (PROTO == 2) {
+          // x already holds the sum
+        } else if (p.partial_mc) {
           const uint4 v0 = mb::multimem_ld_reduce_bf16x8(p.partial_mc + off);
           const uint4 v1 = mb::multimem_ld_reduce_bf16x8(p.partial_mc + off + 8);
           unpack16(v0, v1, x);
@@ -353,7 +443,18 @@ __global__ void __launch_bounds__(512) tp_reduce_norm_kernel(const TpNormParams 
       }
     }
   }
-  sync_exit(p.s, e, TWO, ok);
+  if (PROTO == 2) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t prev = atomicAdd(p.s.cta_done, 1u);
+      if (prev == gridDim.x - 1) {
+        *reinterpret_cast<volatile uint32_t*>(p.s.cta_done) = 0u;
+        *reinterpret_cast<volatile uint32_t*>(p.s.epoch + 2) = ll_epoch + 1u;
+      }
+    }
+  } else {
+    sync_exit(p.s, e, TWO, ok);
+  }
 }
 
 // Greedy selection over a vocabulary sharded across ranks: `pairs[r]` is rank r's array of
@@ -432,6 +533,11 @@ struct MbTpNormArgs {
   int sf_k64;
   float static_gs;
   int max_ctas;
+  // packet protocol (two_shot == 2)
+  void* ll;
+  void* ll_mc;
+  void* ll_peer[8];
+  int ll_rows;
 };
 
 static int fill_sync(const MbTpSync& a, TpSync& s) {
@@ -462,17 +568,23 @@ int mb_tp_reduce_norm(const MbTpNormArgs* a, cudaStream_t stream) {
   int rc = fill_sync(a->sync, p.s);
   if (rc) return rc;
   const int size = p.s.size;
-  if (a->two_shot && (!a->sync.done || (!a->sync.done_mc && !a->sync.done_peer[0]))) return MB_ERR_BAD_ARG;
-  if (!a->partial_mc)
+  if (a->two_shot == 1 && (!a->sync.done || (!a->sync.done_mc && !a->sync.done_peer[0]))) return MB_ERR_BAD_ARG;
+  if (a->two_shot == 2) {
+    if (!a->ll || a->ll_rows < a->M || !a->partial[p.s.rank]) return MB_ERR_BAD_ARG;
+    if (!a->ll_mc)
+      for (int r = 0; r < size; ++r)
+        if (!a->ll_peer[r]) return MB_ERR_BAD_ARG;
+  } else if (!a->partial_mc) {
     for (int r = 0; r < size; ++r)
       if (!a->partial[r]) return MB_ERR_BAD_ARG;
+  }
   if (a->out_mode < OUT_BF16 || a->out_mode > OUT_NONE) return MB_ERR_BAD_ARG;
   if (a->out_mode != OUT_NONE && !a->out) return MB_ERR_BAD_ARG;
   if (a->out_mode == OUT_NVFP4 && (!a->sf || !a->scale || a->sf_k64 * 64 < a->K)) return MB_ERR_BAD_ARG;
   if ((a->out_mode == OUT_FP8_ROW || a->out_mode == OUT_FP8_G128) && !a->scale) return MB_ERR_BAD_ARG;
   if (a->out_mode == OUT_FP8_G128 && a->K % 128) return MB_ERR_UNSUPPORTED;
   p.M = a->M; p.K = a->K; p.out_mode = a->out_mode;
-  if (a->two_shot) {
+  if (a->two_shot == 1) {
     const int per = (a->M + size - 1) / size;
     p.row_lo = per * p.s.rank < a->M ? per * p.s.rank : a->M;
     p.row_hi = p.row_lo + per < a->M ? p.row_lo + per : a->M;
@@ -491,14 +603,21 @@ int mb_tp_reduce_norm(const MbTpNormArgs* a, cudaStream_t stream) {
   p.scale = reinterpret_cast<float*>(a->scale); p.scale_ld = a->scale_ld;
   p.sf = reinterpret_cast<uint8_t*>(a->sf); p.sf_k64 = a->sf_k64;
   p.static_gs = a->static_gs;
+  p.ll = reinterpret_cast<uint2*>(a->ll);
+  p.ll_mc = reinterpret_cast<uint2*>(a->ll_mc);
+  for (int r = 0; r < 8; ++r) p.ll_peer[r] = reinterpret_cast<uint2*>(a->ll_peer[r]);
+  p.ll_rows = a->ll_rows;
+  p.partial_local = p.partial[p.s.rank];
   const int rows = p.row_hi - p.row_lo;
   const int cap = a->max_ctas > 0 ? a->max_ctas : 128;        // every CTA must be resident: they wait on one another
   const int grid = rows < 1 ? 1 : (rows < cap ? rows : cap);
   const int threads = ((a->K / 16) + 31) / 32 * 32;
   const bool pdl = mb_pdl_enabled() >= 1;
-  if (a->two_shot)
-    return (int)mb::launch_kernel_ex(tp_reduce_norm_kernel<true>, dim3(grid), dim3(threads), 0, stream, 1, pdl, p);
-  return (int)mb::launch_kernel_ex(tp_reduce_norm_kernel<false>, dim3(grid), dim3(threads), 0, stream, 1, pdl, p);
+  if (a->two_shot == 2)
+    return (int)mb::launch_kernel_ex(tp_reduce_norm_kernel<2>, dim3(grid), dim3(threads), 0, stream, 1, pdl, p);
+  if (a->two_shot == 1)
+    return (int)mb::launch_kernel_ex(tp_reduce_norm_kernel<1>, dim3(grid), dim3(threads), 0, stream, 1, pdl, p);
+  return (int)mb::launch_kernel_ex(tp_reduce_norm_kernel<0>, dim3(grid), dim3(threads), 0, stream, 1, pdl, p);
 }
 
 struct MbTpMergeArgs {

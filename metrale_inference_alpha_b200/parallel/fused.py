@@ -99,7 +99,8 @@ class TpNormArgs(C.Structure):
                 ("do_norm", C.c_int), ("w_plus_one", C.c_int), ("eps", C.c_float),
                 ("out", C.c_void_p), ("out_ld", C.c_longlong), ("out_bf16", C.c_void_p), ("out_bf16_ld", C.c_longlong),
                 ("scale", C.c_void_p), ("scale_ld", C.c_int), ("sf", C.c_void_p), ("sf_k64", C.c_int),
-                ("static_gs", C.c_float), ("max_ctas", C.c_int)]
+                ("static_gs", C.c_float), ("max_ctas", C.c_int),
+                ("ll", C.c_void_p), ("ll_mc", C.c_void_p), ("ll_peer", _VP8), ("ll_rows", C.c_int)]
 
 
 class TpMergeArgs(C.Structure):
@@ -155,8 +156,10 @@ class FusedReduce:
         n_ranks = max(size, emulate, 1)
         al = lambda n: (n + 255) // 256 * 256
         self.scale_ld = (m_cap + 63) // 64 * 64
+        self.ll_rows = min(m_cap, 64)
         lay, o = {}, 0
         for name, n in (("sync", 1024), ("pairs", 2 * m_cap * 8),
+                        ("ll", 2 * max(size, 1) * self.ll_rows * (K // 2) * 8),
                         ("partial", 2 * m_cap * K * 2 * (emulate if emulate > 1 else 1)),
                         ("data", m_cap * K * 2), ("bf16", m_cap * K * 2), ("resid", m_cap * K * 2),
                         ("sf", ((m_cap + 127) // 128) * self.sf_k64 * 512),
@@ -186,6 +189,10 @@ class FusedReduce:
         # one-shot while the partials every GPU must serve to all readers stay small (size x M x K x 2
         # bytes leave each GPU per call); above that the row-owner protocol moves 1 / size of it
         self.one_shot_bytes = int(os.environ.get("METRALE_TP_ONESHOT_BYTES", str(2816 << 10)))
+        # packet protocol (no barrier, one NVLink hop, twice the bytes) below this many bytes
+        # received per GPU and call (size x M x K x 4)
+        self.packet_bytes = int(os.environ.get("METRALE_TP_PACKET_BYTES", str(1536 << 10)))
+        self.force_proto: Optional[int] = None            # tests: 0 one-shot, 1 two-shot, 2 packets
         torch.cuda.synchronize(self.device)
         if size > 1:
             dist.barrier(group=group)
@@ -228,6 +235,17 @@ class FusedReduce:
         v = self._view("partial", torch.bfloat16, par * (nb // 2) + slot, nb)
         return v[:M * self.hidden].view(M, self.hidden)
 
+    def protocol(self, M: int, K: int) -> int:
+        """0 one-shot behind a barrier, 1 two-shot (row owners + multicast gather), 2 packets."""
+        if self.force_proto is not None:
+            return self.force_proto
+        n = max(self.size, 1)
+        if self.emulate <= 1 and M <= self.ll_rows and n * M * K * 4 <= self.packet_bytes:
+            return 2
+        if self.size > 1 and self.mc and self.size * M * K * 2 > self.one_shot_bytes:
+            return 1
+        return 0
+
     # ------------------------------------------------------------------ consumer side
     def reduce_norm(self, pend: PendingSum, w: Optional[torch.Tensor], fmt: str, *, plus_one: bool = False,
                     eps: float = 1e-6, also_bf16: bool = False, gather_residual: bool = False,
@@ -237,10 +255,18 @@ class FusedReduce:
         M, K = pend.partial.shape
         rt = ops.runtime(self.device)
         n = max(self.size, self.emulate, 1)
-        two = self.size > 1 and bool(self.mc) and self.size * M * K * 2 > self.one_shot_bytes
+        proto = self.protocol(M, K)
+        two = proto == 1
         a = TpNormArgs()
         a.sync = self._sync(rt.status.data_ptr())
-        a.M, a.K, a.two_shot = M, K, int(two)
+        a.M, a.K, a.two_shot = M, K, proto
+        if proto == 2:
+            me = self.ptrs[self.rank if self.size > 1 else 0]
+            a.ll, a.ll_rows = self._addr(me, "ll"), self.ll_rows
+            if self.mc:
+                a.ll_mc = self._addr(self.mc, "ll")
+            for r in range(max(self.size, 1)):
+                a.ll_peer[r] = self._addr(self.ptrs[r], "ll")
         par = self.calls & 1
         nb = 2 * (self.emulate if self.emulate > 1 else 1)
         if self.mc:
@@ -297,7 +323,7 @@ class FusedReduce:
         _native.check(_native.lib().mb_tp_reduce_norm(C.byref(a), ops._stream()), "tp_reduce_norm")
         ops._count()
         self.calls += 1
-        self.dirty = not two
+        self.dirty = proto == 0                 # only the barrier one-shot leaves peers reading this rank's partial
         pend.value, pend.full = value, full
         return act
 

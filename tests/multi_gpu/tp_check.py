@@ -43,7 +43,7 @@ def main():
     gw = torch.Generator().manual_seed(3)
     wn = (torch.randn(N, generator=gw) * 0.1).to(torch.bfloat16).to(dev)
     for fmt in ("nvfp4",):
-        for (M, Kfull) in ((1, 5120), (16, 17408), (32, 17408), (128, 17408), (300, 5120)):
+        for (M, Kfull) in ((1, 5120), (8, 17408), (16, 17408), (32, 17408), (64, 17408), (128, 17408), (300, 5120)):
             K = Kfull // world
             K -= K % 256
             g = torch.Generator().manual_seed(100 + rank)
@@ -63,8 +63,11 @@ def main():
 
             a0, y0 = baseline()
             want_bf16, want_res, want_deq = a0.bf16.float().cpu(), y0.float().cpu(), deq_nvfp4(a0, M, N)
-            for it in range(3):
+            protos = [0] + ([1] if fr.mc else []) + ([2] if M <= fr.ll_rows else [])
+            for it in range(3 * len(protos)):
+                fr.force_proto = protos[it % len(protos)]
                 a1, y1 = fused()
+                fr.force_proto = None
                 torch.cuda.synchronize()
                 e_res = (y1.float().cpu() - want_res).abs().max().item()
                 e_n = (a1.bf16.float().cpu() - want_bf16).abs().max().item()
@@ -75,7 +78,7 @@ def main():
                 # the residual stream may differ by one bf16 rounding of the cross-rank sum
                 if e_res > 0.05 * max(1.0, want_res.abs().max().item()) or e_n > 0.08 or bad or frac > 0.1:
                     ok = False
-                    print(f"[r{rank}] MISMATCH M={M} K={K} it={it} e_res={e_res:.4f} e_norm={e_n:.4f} "
+                    print(f"[r{rank}] MISMATCH proto={protos[it % len(protos)]} M={M} K={K} it={it} e_res={e_res:.4f} e_norm={e_n:.4f} "
                           f"quant_bad={bad} frac={frac:.3f}", flush=True)
             tp.end_forward()
             ops.check_status(dev)
@@ -103,18 +106,19 @@ def main():
                 t = torch.tensor([a.elapsed_time(b) / 50 * 1e3], device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 return t.item()
-            auto = fr.one_shot_bytes
-            fr.one_shot_bytes = 1 << 40
+            fr.force_proto = 0
             t_one = timed(lambda: fused(True))
-            fr.one_shot_bytes = 0
+            fr.force_proto = 1
             t_two = timed(lambda: fused(True)) if fr.mc else float("nan")
-            fr.one_shot_bytes = auto
+            fr.force_proto = 2
+            t_pkt = timed(lambda: fused(True)) if M <= fr.ll_rows else float("nan")
+            fr.force_proto = None
             t_fused = timed(lambda: fused(True))
             t_nccl = timed(baseline)
             t_gemm = timed(lambda: ops.linear(act, w, residual=res))
             ops.check_status(dev)
             if rank == 0:
-                print(f"{fmt} M={M} N={N} K/rank={K}: gemm+fused(reduce,residual,norm,quant,gather) {t_fused:.2f} us (one-shot {t_one:.2f}, two-shot {t_two:.2f})   "
+                print(f"{fmt} M={M} N={N} K/rank={K}: gemm+fused(reduce,residual,norm,quant,gather) {t_fused:.2f} us (protocol {fr.protocol(M, N)}: one-shot {t_one:.2f}, two-shot {t_two:.2f}, packets {t_pkt:.2f})   "
                       f"gemm+nccl+norm-quant {t_nccl:.2f} us   gemm alone {t_gemm:.2f} us   speedup {t_nccl / t_fused:.2f}x",
                       flush=True)
     # vocabulary-parallel greedy selection

@@ -79,6 +79,75 @@ def test_mamba2_scan_matches_reference(N, P):
     _close(st_dev, st_ref, 5e-3, 5e-3)
 
 
+def _commit_batch(b, n_rows):
+    import dataclasses
+    return dataclasses.replace(b, q_len=torch.tensor(n_rows, dtype=torch.int32, device=b.q_len.device))
+
+
+@pytest.mark.parametrize("dev", ["cpu", DEV])
+def test_write_on_accept_equals_feeding_only_the_accepted_rows(dev):
+    """Speculative verify over the recurrent kernels: a pass with write_state=False leaves the
+    state untouched and gives the same outputs; the commit pass (q_len = accepted rows,
+    write_out=False) leaves exactly the state that feeding only those rows would have left,
+    bit for bit (same kernel, same order of operations)."""
+    g = torch.Generator().manual_seed(4)
+    b = _batch(dev)                                     # q_len 7 (fresh), 1, 3
+    accept = [4, 1, 0]                                  # rows committed per sequence (0: nothing accepted yet)
+    T = 11
+    # conv
+    C, taps = 200, 4
+    x = torch.randn(T, C, generator=g).to(torch.bfloat16).to(dev)
+    w, bias = torch.randn(C, taps, generator=g).to(dev), torch.randn(C, generator=g).to(dev)
+    st0 = torch.randn(5, C, taps - 1, generator=g).to(dev)
+    full_state = st0.clone()
+    full = rops.causal_conv1d(x, C, w, bias, full_state, b)
+    st = st0.clone()
+    ver = rops.causal_conv1d(x, C, w, bias, st, b, write_state=False)
+    assert torch.equal(st, st0) and torch.equal(ver, full)
+    rops.causal_conv1d(x, C, w, bias, st, _commit_batch(b, accept), write_out=False)
+    want = st0.clone()
+    rops.causal_conv1d(x, C, w, bias, want, _commit_batch(b, accept))
+    assert torch.equal(st, want)
+    assert torch.equal(st[3], st0[3]) and not torch.equal(st[1], st0[1])
+    # gated delta net
+    kh, vh, dk = 2, 4, 32
+    QK, V = kh * dk, vh * dk
+    conv = torch.randn(T, 2 * QK + V, generator=g).to(dev)
+    ba = torch.randn(T, 2 * vh, generator=g).to(dev)
+    A_log, dtb = (torch.randn(vh, generator=g) * 0.3).to(dev), (torch.randn(vh, generator=g) * 0.1).to(dev)
+    s0 = (torch.randn(5, vh, dk, dk, generator=g) * 0.1).to(dev)
+    kw = dict(k_heads=kh, v_heads=vh, k_dim=dk, v_dim=dk)
+    fs = s0.clone()
+    full = rops.gdn_recurrence(conv, ba, A_log, dtb, fs, b, **kw)
+    st = s0.clone()
+    ver = rops.gdn_recurrence(conv, ba, A_log, dtb, st, b, write_state=False, **kw)
+    assert torch.equal(st, s0) and torch.equal(ver, full)
+    rops.gdn_recurrence(conv, ba, A_log, dtb, st, _commit_batch(b, accept), write_out=False, **kw)
+    want = s0.clone()
+    rops.gdn_recurrence(conv, ba, A_log, dtb, want, _commit_batch(b, accept), **kw)
+    assert torch.equal(st, want) and torch.equal(st[3], s0[3])
+    # Mamba2
+    H, G, P, N = 8, 2, 32, 16
+    inner, GN = H * P, G * N
+    xbc = torch.randn(T, inner + 2 * GN, generator=g).to(dev)
+    dt = torch.randn(T, H + 8, generator=g).to(torch.bfloat16).to(dev)[:, :H]
+    A_log, D, dtb = (torch.randn(H, generator=g) * 0.3).to(dev), torch.randn(H, generator=g).to(dev), (torch.randn(H, generator=g) * 0.1).to(dev)
+    s0 = (torch.randn(5, H, P, N, generator=g) * 0.1).to(dev)
+    kw = dict(heads=H, groups=G, head_dim=P, state=N)
+    fs = s0.clone()
+    full = rops.mamba2_scan(xbc, dt, A_log, D, dtb, fs, b, **kw)
+    st = s0.clone()
+    ver = rops.mamba2_scan(xbc, dt, A_log, D, dtb, st, b, write_state=False, **kw)
+    assert torch.equal(st, s0) and torch.equal(ver, full)
+    rops.mamba2_scan(xbc, dt, A_log, D, dtb, st, _commit_batch(b, accept), write_out=False, **kw)
+    want = s0.clone()
+    rops.mamba2_scan(xbc, dt, A_log, D, dtb, want, _commit_batch(b, accept), **kw)
+    assert torch.equal(st, want) and torch.equal(st[3], s0[3])
+    if dev != "cpu":
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+
+
 def test_router_softmax_and_group_limited():
     g = torch.Generator().manual_seed(3)
     T, E = 37, 256

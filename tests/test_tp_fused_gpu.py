@@ -57,6 +57,31 @@ def test_reduce_norm_matches_reference(fmt, ranks, M, K):
     fr.end_forward()
 
 
+@pytest.mark.parametrize("M,K", [(1, 5120), (9, 2048), (64, 1024)])
+def test_packet_protocol_loopback_matches_reference(M, K):
+    """World size 1: the rank broadcasts its packets into its own landing zone and polls them
+    back; repeated calls alternate the zone parity and change the tag."""
+    g = torch.Generator().manual_seed(21)
+    fr = FusedReduce(0, 1, DEV, K, 64)
+    assert fr.protocol(M, K) == 2
+    w = (torch.randn(K, generator=g) * 0.1).to(torch.bfloat16)
+    for it in range(4):
+        part = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+        res = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        fr.partial_view(M).copy_(part.to(DEV))
+        pend = PendingSum(fr, fr.partial_view(M), res.to(DEV))
+        a = fr.reduce_norm(pend, w.to(DEV), "nvfp4", eps=1e-6, also_bf16=True)
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+        h = ref.bf16_round(part.float() + res.float())
+        assert torch.equal(pend.value.cpu().float(), h)
+        a_ref = ops.row_op(h.to(torch.bfloat16), "nvfp4", ops.IN_RMSNORM, w=w, eps=1e-6, also_bf16=True)[0]
+        deq = _deq(a, M, K)
+        step = a_ref.data.abs().amax(dim=1, keepdim=True) * 0.3
+        assert ((deq - a_ref.data).abs() <= step + 1e-3).all()
+        assert ((deq - a_ref.data).abs() > 1e-3).float().mean() < 0.02
+
+
 def test_reduce_without_norm_and_feeds_a_gemm():
     """resolve(): sum + residual only; and the NVFP4 rows the kernel wrote are a valid GEMM operand."""
     g = torch.Generator().manual_seed(5)
