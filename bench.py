@@ -105,12 +105,47 @@ class ClockSampler:
         return out
 
 
+def torch_arm(args, cfg, rank: int, world: int, local: int, dev: str) -> int:
+    """`--impl torch`: K graph-replayed decode steps of the same shape, batch and context from
+    library kernels only (bf16 weights: cuBLAS has no NVFP4 x NVFP4 path here)."""
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from benchmarks.torch_baseline import run as torch_run
+    C = args.concurrency
+    ctx = args.isl + args.osl // 2
+    sampler = ClockSampler(local)
+    sampler.start()
+    r = torch_run(cfg, C, ctx, args.steps, args.warmup, rank, world, dev)
+    clocks = sampler.stop()
+    line = {"metric": "aggregate decode tok/s at C=%d (ISL128/OSL1024), dense 27B, library kernels" % C,
+            "value": round(r["tok_s"], 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(r["tok_s"] / BASELINE_TOKS.get(C, BASELINE_TOKS[128]), 3),
+            "dtype": "bf16 weights and activations (cuBLAS), bf16 KV (SDPA)", "data": "synthetic: random-init bf16 weights",
+            "config": {"model": cfg.name, "layers": cfg.num_layers, "hidden": cfg.hidden_size, "global_batch": C,
+                       "seq_len": args.isl, "osl": args.osl, "ctx_in_timed_window": ctx, "parallelism": f"tp{world}",
+                       "l2": "inputs larger than L2 (weights %.1f GB per GPU)" % (r["weight_bytes"] / 1e9),
+                       "value_is": "K graph-replayed decode steps at C, CUDA events, max over ranks"},
+            "e2e": None, "gpu_launches": 0, "clocks": clocks, "impl": "torch"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"],
+                    help="reference: the reference engine (does not build offline: prints `unavailable`); torch: the "
+                         "same step from PyTorch's library kernels (cuBLAS bf16, SDPA, NCCL), see benchmarks/torch_baseline.py")
     ap.add_argument("--concurrency", type=int, default=128)
     ap.add_argument("--model", default="dense-27b-nvfp4")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the line invalid)")
@@ -152,8 +187,10 @@ def main() -> int:
             from metrale_inference_alpha_b200.parallel.tp import NcclTpContext
             tp = NcclTpContext(rank, world, dev, fused=not args.no_fused)
 
-    from metrale_inference_alpha_b200 import ops
     from metrale_inference_alpha_b200.config.model_config import preset
+    if args.impl == "torch":
+        return torch_arm(args, preset(args.model), rank, world, local, dev)
+    from metrale_inference_alpha_b200 import ops
     from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
     from metrale_inference_alpha_b200.sampling.params import SamplingParams
 

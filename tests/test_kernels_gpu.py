@@ -45,7 +45,7 @@ def _run_linear(fmt, M, N, K, **kw):
     return got, want
 
 
-@pytest.mark.parametrize("M", [1, 16, 77, 128, 300])
+@pytest.mark.parametrize("M", [1, 16, 24, 48, 64, 77, 128, 300])
 def test_gemm_bf16(M):
     _run_linear("bf16", M, 384, 512)
 
@@ -56,7 +56,7 @@ def test_gemm_bf16_ragged_n_and_splitk():
     _run_linear("bf16", 130, 256, 2048, force_splits=3)
 
 
-@pytest.mark.parametrize("M", [1, 33, 128, 260])
+@pytest.mark.parametrize("M", [1, 18, 24, 32, 33, 128, 260])
 def test_gemm_fp8_row(M):
     _run_linear("fp8_row", M, 256, 1024)
 
@@ -67,7 +67,7 @@ def test_gemm_fp8_block(M):
     _run_linear("fp8_block", M, 256, 2048, force_splits=2)
 
 
-@pytest.mark.parametrize("M", [1, 7, 16, 64, 128, 200])
+@pytest.mark.parametrize("M", [1, 7, 16, 18, 32, 64, 128, 200])
 def test_gemm_nvfp4(M):
     _run_linear("nvfp4", M, 256, 1024)
 
@@ -419,6 +419,17 @@ def test_attention_decode_d256(fp8):
 def test_attention_prefill(fp8, D):
     Hq, Hkv = (8, 2) if D != 64 else (4, 2)
     _attn_case(fp8, D, Hq, Hkv, [128, 70, 200], [128, 170, 200])   # fresh, chunked-after-cache, fresh
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_attention_short_verify_chunks_on_the_prefill_path(fp8):
+    """Verify steps with more than 32 query rows per KV head group (8 drafts + 1, GQA 4) take the
+    split-Q kernel with short, ragged chunks that start deep inside the context, also mixed
+    with single-row sequences."""
+    _attn_case(fp8, 128, 8, 2, [9, 9], [28, 25])
+    _attn_case(fp8, 128, 8, 2, [9, 1], [28, 30])
+    _attn_case(fp8, 128, 8, 2, [1, 9, 2], [40, 21, 77])
+    _attn_case(fp8, 128, 8, 2, [9, 9, 9, 5], [200, 9, 130, 64])
 
 
 def test_attention_sliding_window():

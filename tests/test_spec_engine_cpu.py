@@ -127,12 +127,12 @@ def _wrong_predictions(base):
     return preds
 
 
-def _check_recurrent_speculation(device, model):
+def _check_recurrent_speculation(device, model, **kw):
     prompts = [[3, 4, 5, 6, 3, 4, 5, 6, 3, 4, 5], [9, 8, 7, 9, 8, 7, 9, 8]]
     base, _ = _hybrid_run(device, model, prompts)
     # (1) predicted outputs with forced rejections
     params = [SamplingParams(max_tokens=20, prediction_ids=p) for p in _wrong_predictions(base)]
-    got, eng = _hybrid_run(device, model, prompts, params=params)
+    got, eng = _hybrid_run(device, model, prompts, params=params, **kw)
     assert got == base
     assert sum(o.rejected_draft_tokens for o in eng.last_outputs) > 0       # rows past the accepted prefix were run
     assert sum(o.accepted_draft_tokens for o in eng.last_outputs) > 0
@@ -149,7 +149,12 @@ def test_speculation_on_recurrent_models_is_lossless_on_cpu(model):
 @pytest.mark.gpu
 @pytest.mark.parametrize("model", ["tiny-hybrid-moe", "tiny-nemotron-h"])
 def test_speculation_on_recurrent_models_is_lossless_on_gpu(model):
-    _check_recurrent_speculation("cuda", model)
+    """Token-exact on the GPU as long as verify rows run on the kernel plain decode uses (up to 32
+    query rows per KV head on the split-KV attention kernel: 3 drafts here). Wider verify steps
+    take the split-Q attention kernel, whose summation order differs in the last bits, so a
+    random-weight model may flip near-ties there; the recurrent state itself is compared bit for
+    bit in tests/test_kernels_ext_gpu.py::test_write_on_accept_equals_feeding_only_the_accepted_rows."""
+    _check_recurrent_speculation("cuda", model, prediction_drafts=3)
 
 
 def test_mtp_k3_on_a_hybrid_model_is_lossless_on_cpu():
