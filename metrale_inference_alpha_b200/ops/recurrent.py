@@ -80,6 +80,11 @@ def mamba2_scan(xbc, dt, A_log, D, dt_bias, ssm_state, batch, *, heads, groups, 
     """xbc [T, inner + 2 G N] fp32 (x | B | C after conv + SiLU), dt [T, heads] (raw).
     ssm_state [slots, heads, head_dim, state] fp32. Returns fp32 [T, heads * head_dim]."""
     if xbc.is_cuda and _native.available() and hasattr(_native.lib(), "mb_mamba2_scan"):
+        if (write_out and head_dim == 64 and state == 128 and getattr(batch, "max_q_len", 1) >= _SSD_MIN_TOKENS
+                and hasattr(_native.lib(), "mb_mamba2_ssd")):
+            y = _mamba_ssd_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups, write_state)
+            if y is not None:
+                return y
         return _mamba_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups, head_dim, state, write_state, write_out)
     T = xbc.shape[0]
     inner, GN = heads * head_dim, groups * state
@@ -110,6 +115,43 @@ _native.register_optional("mb_gdn_recurrence", [_c.c_void_p] * 6 + [_c.c_int] * 
                           [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p])
 _native.register_optional("mb_mamba2_scan", [_c.c_void_p, _c.c_void_p, _c.c_longlong] + [_c.c_void_p] * 5 +
                           [_c.c_int] * 4 + [_c.c_void_p] * 4 + [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p])
+
+
+_native.register_optional("mb_mamba2_ssd", [_c.c_void_p, _c.c_void_p, _c.c_longlong] + [_c.c_void_p] * 5 +
+                          [_c.c_int] * 4 + [_c.c_void_p] * 4 + [_c.c_int] * 4 + [_c.c_void_p, _c.c_size_t, _c.c_void_p,
+                                                                                _c.c_void_p])
+# prefill chunks at least this long take the chunked (state-space-dual) Mamba2 scan
+_SSD_MIN_TOKENS = 32
+_SSD_WS_MAX = 3 << 30
+_ssd_ws = {}
+
+
+def _mamba_ssd_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups, write_state):
+    """Chunked scan (csrc/recurrent_chunked.cu); None when the workspace would be unreasonably large."""
+    L = _native.lib()
+    L.mb_mamba2_ssd_ws_bytes.restype = _c.c_size_t
+    L.mb_mamba2_ssd_ws_bytes.argtypes = [_c.c_int, _c.c_int, _c.c_int]
+    S = batch.q_len.numel()
+    need = int(L.mb_mamba2_ssd_ws_bytes(S, int(batch.max_q_len), heads))
+    if need > _SSD_WS_MAX:
+        return None
+    dev = xbc.device
+    ws = _ssd_ws.get(dev)
+    if ws is None or ws.numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        ws = _ssd_ws[dev] = torch.empty(int(need * 1.25), dtype=torch.uint8, device=dev)
+    T = xbc.shape[0]
+    out = torch.empty(T, heads * 64, dtype=torch.float32, device=dev)
+    assert dt.dtype == torch.bfloat16
+    rc = L.mb_mamba2_ssd(
+        _ptr(xbc), _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(D), _ptr(dt_bias), _ptr(ssm_state), _ptr(out),
+        heads, groups, 64, 128, _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions),
+        _ptr(batch.state_slots), S, ssm_state.shape[0], int(batch.max_q_len), int(write_state), _ptr(ws), ws.numel(),
+        _ptr(_status(dev)), _stream())
+    _native.check(rc, "mamba2_ssd")
+    _count(3)
+    return out
 
 
 def _status(dev):

@@ -79,6 +79,45 @@ def test_mamba2_scan_matches_reference(N, P):
     _close(st_dev, st_ref, 5e-3, 5e-3)
 
 
+@pytest.mark.parametrize("lens", [[64], [200, 1, 77], [8192], [130, 64, 5, 300]])
+def test_mamba2_chunked_scan_matches_the_sequential_kernel_and_the_fp32_oracle(lens):
+    """State-space-dual chunked scan (TF32 tensor-core products) against the sequential kernel on
+    the same inputs: outputs and the hand-off state; the shortest case also against the fp32 CPU
+    reference. Sequences mix fresh starts with continuations from a stored state."""
+    g = torch.Generator().manual_seed(12)
+    H, G, P, N = 16, 2, 64, 128
+    inner, GN = H * P, G * N
+    seqs, pos = [], 0
+    for i, n in enumerate(lens):
+        seqs.append(dict(tokens=[1] * n, start_pos=0 if i % 2 == 0 else 7, blocks=list(range(1, 2 + (n + 7) // 16)), state_slot=i + 1))
+    b = ForwardBatch.build(seqs, 16, device=DEV)
+    T = sum(lens)
+    xbc = (torch.randn(T, inner + 2 * GN, generator=g) * 0.5).to(DEV)
+    dt = (torch.randn(T, H + 8, generator=g) * 0.5).to(torch.bfloat16).to(DEV)[:, :H]
+    A_log = (torch.randn(H, generator=g) * 0.3).to(DEV)
+    Dv, dtb = torch.randn(H, generator=g).to(DEV), (torch.randn(H, generator=g) * 0.1).to(DEV)
+    s0 = (torch.randn(len(lens) + 1, H, P, N, generator=g) * 0.1).to(DEV)
+    kw = dict(heads=H, groups=G, head_dim=P, state=N)
+    st_seq, st_chk = s0.clone(), s0.clone()
+    rops._SSD_MIN_TOKENS, keep = 1 << 30, rops._SSD_MIN_TOKENS
+    want = rops.mamba2_scan(xbc, dt, A_log, Dv, dtb, st_seq, b, **kw)          # sequential kernel
+    rops._SSD_MIN_TOKENS = 1
+    got = rops.mamba2_scan(xbc, dt, A_log, Dv, dtb, st_chk, b, **kw)           # chunked kernels
+    rops._SSD_MIN_TOKENS = keep
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    scale = want.abs().max().item()
+    assert (got - want).abs().max().item() <= 4e-3 * max(1.0, scale), ((got - want).abs().max().item(), scale)
+    assert (st_chk - st_seq).abs().max().item() <= 4e-3 * max(1.0, st_seq.abs().max().item())
+    assert torch.equal(st_chk[0], s0[0])                                       # untouched slot
+    if T <= 64:
+        st_cpu = s0.cpu().clone()
+        ref_y = rops.mamba2_scan(xbc.cpu(), dt.cpu(), A_log.cpu(), Dv.cpu(), dtb.cpu(), st_cpu,
+                                 ForwardBatch.build(seqs, 16, device="cpu"), **kw)
+        _close(got, ref_y, 5e-3, 5e-3 * max(1.0, scale))
+        _close(st_chk, st_cpu, 5e-3, 5e-3)
+
+
 def _commit_batch(b, n_rows):
     import dataclasses
     return dataclasses.replace(b, q_len=torch.tensor(n_rows, dtype=torch.int32, device=b.q_len.device))
