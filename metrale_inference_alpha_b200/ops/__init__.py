@@ -186,6 +186,29 @@ class Act:
     bf16: Optional[torch.Tensor] = None     # extra bf16 copy when requested
 
 
+_SF_ZERO: dict = {}
+
+
+def _sf_buffer(dev, M: int, K: int):
+    """Tiled scale-factor buffer of an NVFP4 activation [M, K] and its row length in 64-channel
+    groups. When K fills whole 256-channel stages every byte is written by the producing kernel
+    (fresh memory); otherwise the padding groups must read as zero, and a small ring of
+    persistent pre-zeroed buffers per shape is used instead of a memset per call (a producer's
+    buffer is consumed by the GEMM right behind it, long before the ring comes round)."""
+    sf_k64 = ((K + 255) // 256) * 4
+    n = ((M + 127) // 128) * sf_k64 * 512
+    if K % 256 == 0:
+        return torch.empty(n, dtype=torch.uint8, device=dev), sf_k64
+    key = (str(dev), (M + 127) // 128, K)
+    ring = _SF_ZERO.get(key)
+    if ring is None:
+        if torch.cuda.is_current_stream_capturing():        # first use inside a capture: pay the memset once
+            return torch.zeros(n, dtype=torch.uint8, device=dev), sf_k64
+        ring = _SF_ZERO[key] = [[torch.zeros(n, dtype=torch.uint8, device=dev) for _ in range(4)], 0]
+    ring[1] = (ring[1] + 1) % len(ring[0])
+    return ring[0][ring[1]], sf_k64
+
+
 def _count(n: int = 1):
     global launch_count
     launch_count += n
@@ -246,11 +269,7 @@ def row_op(x: torch.Tensor, out_fmt: str = "bf16", mode: int = IN_COPY, *, K: Op
     else:
         act.data = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
         act.scale = torch.empty(M, dtype=torch.float32, device=dev)
-        act.sf_k64 = ((K + 255) // 256) * 4
-        # every 64-wide k group of every row is written by the kernel when K fills the padded
-        # layout; otherwise the padding groups must read as zero scale factors
-        sf_alloc = torch.empty if K % 256 == 0 else torch.zeros
-        act.sf = sf_alloc(((M + 127) // 128) * act.sf_k64 * 512, dtype=torch.uint8, device=dev)
+        act.sf, act.sf_k64 = _sf_buffer(dev, M, K)
         a.out_ld = K // 2
         a.sf = _ptr(act.sf)
         a.sf_k64 = act.sf_k64
@@ -263,7 +282,7 @@ def row_op(x: torch.Tensor, out_fmt: str = "bf16", mode: int = IN_COPY, *, K: Op
     elif out_fmt == "bf16":
         act.bf16 = act.data
     _native.check(L.mb_row_op(C.byref(a), _stream()), "row_op")
-    _count(2 if (out_fmt == "nvfp4" and K % 256) else 1)  # + the zero fill of padded scale-factor groups
+    _count()
     return act, res_out
 
 
@@ -671,7 +690,7 @@ def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_l
     T, Hq, D = q.shape
     if quant_out > 0.0:
         Hkv_ = k_cache.shape[2]
-        fused = q.is_cuda and force_mode == 0 and (Hq // Hkv_) * max_q_len <= 16 and D % 128 == 0 and (Hq * D) % 256 == 0
+        fused = q.is_cuda and force_mode == 0 and (Hq // Hkv_) * max_q_len <= 16 and D % 128 == 0 and (Hq * D) % 64 == 0
         if not fused:
             o = paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, ctx_len, max_q_len=max_q_len,
                                 max_ctx=max_ctx, scale=scale, k_scale=k_scale, v_scale=v_scale, window=window,
@@ -710,8 +729,7 @@ def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_l
     if quant_out > 0.0:
         Kq = Hq * D
         qact = Act("nvfp4", T, Kq, torch.empty(T, Kq // 2, dtype=torch.uint8, device=q.device))
-        qact.sf_k64 = Kq // 64
-        qact.sf = torch.empty(((T + 127) // 128) * qact.sf_k64 * 512, dtype=torch.uint8, device=q.device)
+        qact.sf, qact.sf_k64 = _sf_buffer(q.device, T, Kq)
         qact.scale = static_scale_vec(q.device, quant_out, T)
         a.outq, a.ldq, a.outq_sf, a.outq_sf_k64, a.outq_gs = _ptr(qact.data), Kq // 2, _ptr(qact.sf), qact.sf_k64, quant_out
     _native.check(L.mb_paged_attention(C.byref(a), _stream()), "paged_attention")

@@ -188,10 +188,11 @@ class FusedReduce:
         self.dirty = False               # a one-shot reduction has run since the last full barrier
         # one-shot while the partials every GPU must serve to all readers stay small (size x M x K x 2
         # bytes leave each GPU per call); above that the row-owner protocol moves 1 / size of it
-        self.one_shot_bytes = int(os.environ.get("METRALE_TP_ONESHOT_BYTES", str(2816 << 10)))
-        # packet protocol (no barrier, one NVLink hop, twice the bytes) below this many bytes
-        # received per GPU and call (size x M x K x 4)
-        self.packet_bytes = int(os.environ.get("METRALE_TP_PACKET_BYTES", str(1536 << 10)))
+        # (measured crossovers: ~3.7 MB on 8 GPUs, above 6 MB on 2)
+        self.one_shot_bytes = int(os.environ.get("METRALE_TP_ONESHOT_BYTES", str((8 << 20) if size <= 2 else (3584 << 10))))
+        # packet protocol (no barrier, one NVLink hop, twice the bytes): measured faster than the
+        # barrier one-shot only between two ranks and below ~400 KB received per call
+        self.packet_bytes = int(os.environ.get("METRALE_TP_PACKET_BYTES", str((400 << 10) if size <= 2 else 0)))
         self.force_proto: Optional[int] = None            # tests: 0 one-shot, 1 two-shot, 2 packets
         torch.cuda.synchronize(self.device)
         if size > 1:

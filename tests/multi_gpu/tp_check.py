@@ -72,11 +72,13 @@ def main():
                 e_res = (y1.float().cpu() - want_res).abs().max().item()
                 e_n = (a1.bf16.float().cpu() - want_bf16).abs().max().item()
                 dq = deq_nvfp4(a1, M, N)
-                step = want_deq.abs().amax(dim=1, keepdim=True) * 0.3
+                # one e2m1 step at the top of the range is a third of the row maximum
+                step = want_deq.abs().amax(dim=1, keepdim=True) * 0.35
                 frac = ((dq - want_deq).abs() > 1e-3).float().mean().item()
                 bad = not ((dq - want_deq).abs() <= step + 1e-3).all().item()
-                # the residual stream may differ by one bf16 rounding of the cross-rank sum
-                if e_res > 0.05 * max(1.0, want_res.abs().max().item()) or e_n > 0.08 or bad or frac > 0.1:
+                # the residual stream may differ by bf16 roundings of the cross-rank sum (NCCL and the
+                # switch add the ranks' bf16 partials in different orders): two ulps of the largest value
+                if e_res > 2 ** -6 * max(1.0, want_res.abs().max().item()) or e_n > 0.08 or bad or frac > 0.2:
                     ok = False
                     print(f"[r{rank}] MISMATCH proto={protos[it % len(protos)]} M={M} K={K} it={it} e_res={e_res:.4f} e_norm={e_n:.4f} "
                           f"quant_bad={bad} frac={frac:.3f}", flush=True)

@@ -223,11 +223,15 @@ def test_gemm_swiglu_epilogue_quantises_to_nvfp4_with_a_static_scale(M):
     ops.check_status(DEV)
 
 
+@pytest.mark.parametrize("heads", [(40, 8), (5, 1)])
 @pytest.mark.parametrize("ctx_lens,part_tokens", [([5, 130, 64, 700], 0), ([300, 1025], 256)])
-def test_attention_epilogue_quantises_to_nvfp4_with_a_static_scale(ctx_lens, part_tokens):
+def test_attention_epilogue_quantises_to_nvfp4_with_a_static_scale(ctx_lens, part_tokens, heads):
     """Decode attention writing packed e2m1 + tiled scale factors for o_proj (direct store and the
-    last-arriver merge of several partitions) against the row kernel applied to its bf16 output."""
-    fp8, D, Hq, Hkv = True, 128, 40, 8
+    last-arriver merge of several partitions) against the row kernel applied to its bf16 output.
+    (5, 1) is one rank's share under 8-way tensor parallelism: 640 channels do not fill a
+    256-channel scale-factor stage, so the padding groups come from a pre-zeroed buffer."""
+    fp8, D = True, 128
+    Hq, Hkv = heads
     q_lens = [1] * len(ctx_lens)
     args, want = _attn_case(fp8, D, Hq, Hkv, q_lens, ctx_lens, build_only=True)
     o = ops.paged_attention(*args["pos"], **args["kw"], part_tokens=part_tokens)
