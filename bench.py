@@ -39,6 +39,10 @@ import sys
 import time
 
 BASELINE_TOKS = {1: 23.59, 2: 41.02, 4: 74.21, 8: 125.95, 16: 203.36, 32: 291.01, 64: 386.63, 128: 478.11}
+# published GB10 ladders of the other configurations' closest reference models (tok/s by concurrency)
+BASELINE_OTHER = {"qwen-hybrid-moe-35b-fp8": {1: 84.99, 2: 127.12, 4: 180.24, 8: 235.82, 16: 311.18}}
+WEIGHT_DESC = {"nvfp4": "nvfp4 weights x nvfp4 activations (fp32 accumulate)", "fp8_block": "fp8 e4m3 128x128-block weights x fp8 activations",
+               "fp8_row": "fp8 e4m3 per-row weights x fp8 activations", "bf16": "bf16"}
 SMI_FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -159,7 +163,11 @@ def main() -> int:
     ap.add_argument("--no-ladder", action="store_true", help="skip the full-OSL ladder (e2e then covers rung C only)")
     ap.add_argument("--ladder", action="store_true", help="accepted for compatibility: the ladder runs by default")
     ap.add_argument("--rungs", default="1,2,4,8,16,32,64,128")
-    ap.add_argument("--parallelism", default="tp", choices=["dp", "tp"],
+    ap.add_argument("--ttft-reps", type=int, default=0,
+                    help="also measure p50 time to first token of single requests of --isl tokens, cold and prefix-warm")
+    ap.add_argument("--ep-dispatch", default="allreduce", choices=["allreduce", "a2a"],
+                    help="--parallelism ep: masked-local experts + all-reduce, or token dispatch over NVLink peer memory")
+    ap.add_argument("--parallelism", default="tp", choices=["dp", "tp", "ep"],
                     help="N>1: tp = one engine sharded over N GPUs, C requests in total (strong scaling, the "
                          "configuration's TP sweep); dp = one engine replica per GPU, each serving C requests")
     args = ap.parse_args()
@@ -178,7 +186,8 @@ def main() -> int:
     torch.cuda.set_device(local)
     dev = f"cuda:{local}"
     tp = None
-    use_tp = world > 1 and args.parallelism == "tp"
+    use_ep = world > 1 and args.parallelism == "ep"        # attention tensor-parallel, experts expert-parallel
+    use_tp = world > 1 and args.parallelism in ("tp", "ep")
     replicas = world if not use_tp else 1
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -186,6 +195,8 @@ def main() -> int:
         if use_tp:
             from metrale_inference_alpha_b200.parallel.tp import NcclTpContext
             tp = NcclTpContext(rank, world, dev, fused=not args.no_fused)
+            if use_ep:
+                tp.ep_rank = rank
 
     from metrale_inference_alpha_b200.config.model_config import preset
     if args.impl == "torch":
@@ -198,7 +209,8 @@ def main() -> int:
     if args.layers:
         cfg = cfg.scaled(num_layers=args.layers, layer_types=cfg.layer_types[:args.layers],
                          ffn_types=cfg.ffn_types[:args.layers])
-    ctx_len = 2048
+    ctx_len = max(2048, args.isl + args.osl + 16)
+    base_toks = BASELINE_TOKS if args.model == "dense-27b-nvfp4" else BASELINE_OTHER.get(args.model, {})
 
     def barrier():
         if world > 1:
@@ -216,7 +228,8 @@ def main() -> int:
         if eng is None:
             eng = LLMEngine(EngineArgs(model=cfg, device=dev, max_num_seqs=128, max_model_len=ctx_len,
                                        max_prefill_tokens=8192, enable_prefix_caching=True,
-                                       gpu_memory_utilization=0.85, tp_size=world if use_tp else 1, seed=0), tp=tp)
+                                       gpu_memory_utilization=0.85, tp_size=world if use_tp else 1,
+                                       ep_size=world if use_ep else 1, ep_dispatch=args.ep_dispatch, seed=0), tp=tp)
         g = torch.Generator().manual_seed(42 + (0 if use_tp else rank))
         prompts = [torch.randint(0, cfg.vocab_size, (args.isl,), generator=g).tolist() for _ in range(C)]
         sp = SamplingParams(max_tokens=args.osl, temperature=0.0, ignore_eos=True)
@@ -310,19 +323,40 @@ def main() -> int:
                      "completion_tokens": row["tokens"] * replicas,
                      "h2d_bytes_per_step": int((eng.runner.h2d_bytes - h0) / n_steps) * replicas,
                      "d2h_bytes_per_step": int((eng.runner.d2h_bytes - d0) / n_steps) * replicas,
-                     "vs_gb10_published": round(replicas * row["tokens"] / wall / BASELINE_TOKS[c], 2) if c in BASELINE_TOKS else None}
+                     "vs_gb10_published": round(replicas * row["tokens"] / wall / base_toks[c], 2) if c in base_toks else None}
     top = ladder[C]
+    ttft = None
+    if args.ttft_reps > 0:
+        # single requests of ISL tokens: cold (new prompt), then the same prompt again (prefix cache warm)
+        cold, warm = [], []
+        g2 = torch.Generator().manual_seed(4242)
+        for _ in range(args.ttft_reps):
+            prompt = torch.randint(0, cfg.vocab_size, (args.isl,), generator=g2).tolist()
+            for bucket in (cold, warm):
+                barrier()
+                t0 = time.perf_counter()
+                rid = eng.add_request(prompt, SamplingParams(max_tokens=2, temperature=0.0, ignore_eos=True))
+                first = None
+                while eng.has_work():
+                    for o in eng.step():
+                        if o.request_id == rid and o.new_token_ids and first is None:
+                            torch.cuda.synchronize()
+                            first = (time.perf_counter() - t0) * 1e3
+                bucket.append(max_over_ranks(first if first is not None else float("nan")))
+        med = lambda xs: sorted(xs)[len(xs) // 2]
+        ttft = {"isl": args.isl, "reps": args.ttft_reps, "cold_p50_ms": round(med(cold), 2), "prefix_warm_p50_ms": round(med(warm), 2)}
+    par = f"ep{world}" if use_ep else (f"tp{world}" if (use_tp or world == 1) else f"dp{world}")
     line = {
-        "metric": "aggregate decode tok/s at C=%d (ISL128/OSL1024), dense 27B NVFP4, fp8 KV" % C,
+        "metric": "aggregate decode tok/s at C=%d (ISL%d/OSL%d), %s, %s KV" % (C, args.isl, args.osl, cfg.name, cfg.kv_dtype),
         "value": round(r["tok_s"], 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True,
-        "scaling": "strong" if (use_tp or world == 1) else "weak", "vs_baseline": round(r["tok_s"] / BASELINE_TOKS.get(C, BASELINE_TOKS[128]), 3),
-        "dtype": "nvfp4 weights x nvfp4 activations (fp32 accumulate), bf16 lm_head, fp8 KV",
-        "data": "synthetic: random-init N(0,0.02) weights in NVFP4 checkpoint layout, uniform-random prompts (seed 42)",
+        "scaling": "strong" if (use_tp or world == 1) else "weak", "vs_baseline": round(r["tok_s"] / base_toks[C], 3) if C in base_toks else None,
+        "dtype": "%s, bf16 lm_head, %s KV" % (WEIGHT_DESC.get(cfg.weight_format, cfg.weight_format), cfg.kv_dtype),
+        "data": "synthetic: random-init N(0,0.02) weights in the %s checkpoint layout, uniform-random prompts (seed 42)" % cfg.weight_format,
         "config": {"model": cfg.name, "layers": cfg.num_layers, "hidden": cfg.hidden_size,
                    "global_batch": C * replicas, "per_gpu_batch": C if not use_tp else None, "seq_len": args.isl, "osl": args.osl, "context": ctx_len,
                    "mean_ctx_in_timed_window": r["ctx"], "fast_forward_steps": r["ff"],
-                   "parallelism": (f"tp{world}" if (use_tp or world == 1) else f"dp{world}"),
+                   "parallelism": par, "ep_dispatch": args.ep_dispatch if use_ep else None,
                    "l2": "inputs larger than L2 (weights %.1f GB per GPU + KV per step)" % (eng.weights.nbytes() / 1e9),
                    "fused_collectives": bool(tp is not None and getattr(tp, "reduce", None) is not None),
                    "speculative": "off (MTP gate: random-init drafts never accepted)",
@@ -339,6 +373,8 @@ def main() -> int:
         "ttft_p50_ms": top["ttft_p50_ms"],
         "impl": "ours",
     }
+    if ttft is not None:
+        line["ttft"] = ttft
     if args.layers:
         line["invalid"] = "debug run with fewer layers"
     if rank == 0:

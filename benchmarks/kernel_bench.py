@@ -6,7 +6,7 @@ copies so each timed launch streams its weights from HBM (inputs larger than L2)
 figures are reported against the measured copy bandwidth and cuBLAS bf16 throughput in
 MEASURED_PEAKS.json ("of measured") or the fallback peaks ("of fallback").
 
-    python benchmarks/kernel_bench.py [--m 1,16,128] [--ctx 640] [--json out.json]
+    python benchmarks/kernel_bench.py [--m 1,16,128] [--ctx 640] [--tp 8] [--json out.json]
 """
 from __future__ import annotations
 
@@ -84,9 +84,10 @@ def main():
     ap.add_argument("--fmt", default="nvfp4")
     ap.add_argument("--json", default="")
     ap.add_argument("--splits", default="")
+    ap.add_argument("--tp", type=int, default=1, help="time one rank's share of the shapes under N-way tensor parallelism")
     args = ap.parse_args()
     hbm, tflops, tag = peaks()
-    H, I, V, Hq, Hkv, D = 5120, 17408, 151936, 40, 8, 128
+    H, I, V, Hq, Hkv, D = 5120, 17408 // args.tp, (151936 + args.tp - 1) // args.tp, 40 // args.tp, max(1, 8 // args.tp), 128
     rows = []
     fmt = args.fmt
     afmt = ops.ACT_FOR_WEIGHT[fmt]

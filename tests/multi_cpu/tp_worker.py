@@ -31,7 +31,11 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     torch.set_num_threads(1)
     tp = GlooTpContext(rank, world)
-    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=128, tp_size=world,
+    model = "tiny-dense"
+    if scenario.startswith("parity:"):                 # parity:<preset>: another family, in bf16 (sharding only, no per-shard quantisation noise)
+        from metrale_inference_alpha_b200.config.model_config import preset
+        model, scenario = preset(scenario.split(":", 1)[1], weight_format="bf16"), "parity"
+    eng = LLMEngine(EngineArgs(model=model, device="cpu", max_num_seqs=4, max_model_len=128, tp_size=world,
                                use_cuda_graphs=False), tp=tp)
     sp = SamplingParams(max_tokens=6, temperature=0.0)
     result = {"rank": rank}
