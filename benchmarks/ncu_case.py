@@ -30,6 +30,8 @@ def main():
     ap.add_argument("--k", type=int, default=17408)
     ap.add_argument("--fmt", default="nvfp4")
     ap.add_argument("--iters", type=int, default=6)
+    ap.add_argument("--swiglu", action="store_true", help="--op gemm: SwiGLU epilogue (gate / up rows interleaved)")
+    ap.add_argument("--ranks", type=int, default=8, help="--op tpfused: emulated ranks (partials summed by one kernel)")
     a = ap.parse_args()
     M = a.m
     if a.op == "attn":
@@ -65,9 +67,21 @@ def main():
     elif a.op == "gemm":
         ws = rand_weight(a.n, a.k, a.fmt, 3)
         act = ops.quantize_act(torch.randn(M, a.k, device=DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[a.fmt])
-        out = torch.empty(M, a.n, device=DEV, dtype=torch.bfloat16)
+        out = torch.empty(M, a.n // 2 if a.swiglu else a.n, device=DEV, dtype=torch.bfloat16)
         for i in range(a.iters):
-            ops.linear(act, ws[i % 3], out=out)
+            ops.linear(act, ws[i % 3], out=out, swiglu=a.swiglu)
+    elif a.op == "tpfused":
+        # the consumer-fused tensor-parallel reduction with the ranks emulated on one GPU: one launch sums
+        # `ranks` local partial buffers through the peer-load path, adds the residual, normalises, quantises
+        from metrale_inference_alpha_b200.parallel.fused import FusedReduce, PendingSum
+        fr = FusedReduce(0, 1, DEV, a.n, max(M, 16), emulate=a.ranks)
+        w = torch.ones(a.n, device=DEV, dtype=torch.bfloat16)
+        res = torch.randn(M, a.n, device=DEV).to(torch.bfloat16)
+        for i in range(a.iters):
+            for r in range(a.ranks):
+                fr.partial_view(M, r).normal_()
+            pend = PendingSum(fr, fr.partial_view(M, 0), res)
+            fr.reduce_norm(pend, w, "nvfp4", eps=1e-6)
     elif a.op == "rowop":
         x = torch.randn(M, a.k, device=DEV).to(torch.bfloat16)
         w = torch.ones(a.k, device=DEV, dtype=torch.bfloat16)

@@ -26,7 +26,7 @@ OUT_MODE = {"bf16": 0, "fp8_row": 1, "fp8_g128": 2, "nvfp4": 3}
 
 launch_count = 0  # kernels launched through this module (bench.py reports it)
 # kernel-selection bits of the GEMM launcher (csrc/gemm_args.h)
-GEMM_ONE_TILE_PER_CTA, GEMM_DECODE_TILE_ORDER, GEMM_PERSISTENT_PREFILL = 16, 64, 128
+GEMM_ONE_TILE_PER_CTA, GEMM_DECODE_TILE_ORDER, GEMM_PERSISTENT_PREFILL, GEMM_DSMEM_SPLITK = 16, 64, 128, 256
 # prefill GEMMs (several 128-token tiles) also run on the persistent kernel (NVFP4 prefill GEMMs
 # measure 1.5x faster there; METRALE_PERSISTENT_PREFILL=0 keeps one tile per CTA)
 _PERSIST_PREFILL = GEMM_PERSISTENT_PREFILL if os.environ.get("METRALE_PERSISTENT_PREFILL", "1") != "0" else 0
@@ -341,13 +341,15 @@ def quantize_act(x: torch.Tensor, fmt: str, static_scale: float = 0.0) -> Act:
 def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
            swiglu: bool = False, out_f32: bool = False, out: Optional[torch.Tensor] = None,
            force_tn: int = 0, force_splits: int = 0, one_tile_per_cta: bool = False, decode_tile_order: bool = False,
-           grouped=None, no_cluster: bool = False, tp=None, quant_out: float = 0.0):
+           dsmem_splitk: bool = False, grouped=None, no_cluster: bool = False, tp=None, quant_out: float = 0.0):
     """out[m, n] = sum_k act[m, k] * w[n, k] (+ residual); with `swiglu`, w holds gate/up rows
     interleaved (2j, 2j+1) and the result is silu(gate) * up of width N/2. `quant_out` > 0 (with
     `swiglu`): return the result as an NVFP4 `Act` quantised with that calibrated global scale --
     inside the GEMM epilogue when the persistent kernel serves the shape, else by a row kernel.
     `one_tile_per_cta` keeps the shape off the persistent kernel and `decode_tile_order` keeps
-    prefill-sized GEMMs on the decode launch order (both for A/B comparisons and tests)."""
+    prefill-sized GEMMs on the decode launch order; `dsmem_splitk` makes a split-K cluster exchange
+    its partial tiles over distributed shared memory instead of the L2-resident workspace (all
+    three for A/B comparisons and tests)."""
     assert act.K == w.K, (act.K, w.K)
     assert act.fmt == ACT_FOR_WEIGHT[w.fmt], (act.fmt, w.fmt)
     M, N = act.M, w.N
@@ -395,7 +397,7 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
     a.ws, a.ws_bytes, a.status = _ptr(rt.ws), rt.ws_bytes, _ptr(rt.status)
     a.force_tn, a.force_splits, a.sm_count = force_tn, force_splits, rt.sm_count
     a.flags = (_PERSIST_PREFILL | (GEMM_ONE_TILE_PER_CTA if one_tile_per_cta else 0)
-               | (GEMM_DECODE_TILE_ORDER if decode_tile_order else 0))
+               | (GEMM_DECODE_TILE_ORDER if decode_tile_order else 0) | (GEMM_DSMEM_SPLITK if dsmem_splitk else 0))
     a.no_cluster = int(no_cluster)
     qact = None
     if quant_out > 0.0:

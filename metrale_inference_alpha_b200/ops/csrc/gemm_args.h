@@ -10,6 +10,8 @@
 #define MB_GEMM_ONE_TILE_PER_CTA 16     // never use the persistent kernel
 #define MB_GEMM_DECODE_TILE_ORDER 64    // prefill-sized GEMMs keep the decode launch order (weight tiles in x)
 #define MB_GEMM_PERSISTENT_PREFILL 128  // several 128-token tiles may run on the persistent kernel
+#define MB_GEMM_DSMEM_SPLITK 256        // cluster split-K exchanges partial tiles over distributed shared memory
+                                        // (default: through the L2-resident workspace)
 
 struct MbGemmArgs {
   int kind, M, N, K, ldo, a_ld;

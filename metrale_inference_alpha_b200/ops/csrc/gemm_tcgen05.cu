@@ -80,7 +80,9 @@ struct GemmParams {
   int outq_sf_k64;
   float outq_gs;
   int m_fastest;      // token tiles in blockIdx.x (prefill): see the kernel's launch-order note
-  int cluster;        // splits form a thread-block cluster; partial tiles are reduced over DSMEM
+  int cluster;        // splits form a thread-block cluster (co-resident, one cluster barrier instead of counters)
+  int cluster_ws;     // with `cluster`: partial tiles are exchanged through the global workspace (L2), which
+                      // measures ~4x faster than distributed shared memory for 64 KB tiles; 0 = over DSMEM
 #ifdef MB_GEMM_TIMING_EXPERIMENTS
   // kernel-development builds only (never the shipped library): per-phase cycle stamps of CTA
   // (0,0,0) and the last CTA in x, and switches that skip parts of the work to time the rest
@@ -237,7 +239,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
     __syncwarp();
-    if (p.cluster) { mb::cluster_sync_all(); mb::cluster_sync_all(); }
+    if (p.cluster) { mb::cluster_sync_all(); if (!p.cluster_ws) mb::cluster_sync_all(); }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (mb::elect_one()) {
@@ -300,7 +302,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       MB_STAMP(4);
     }
     __syncwarp();
-    if (p.cluster) { mb::cluster_sync_all(); mb::cluster_sync_all(); }
+    if (p.cluster) { mb::cluster_sync_all(); if (!p.cluster_ws) mb::cluster_sync_all(); }
   } else {
     // ------------------------------------------------------------ epilogue
     // (a) TMEM -> registers -> fp32 staging tile [m][n] in the (by then idle) pipeline
@@ -338,7 +340,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       wcol[i] = wsc;
     }
     const size_t tile_lin = (size_t)tile_m * tiles_n_grid + tile_n;
-    float* wsp = (p.splits > 1 && !p.cluster) ? p.ws + (tile_lin * p.splits + split) * (size_t)(TN * kTileN) : s_tile;
+    float* wsp = (p.splits > 1 && (!p.cluster || p.cluster_ws)) ? p.ws + (tile_lin * p.splits + split) * (size_t)(TN * kTileN) : s_tile;
 
     if constexpr (KIND == KIND_FP8_BLOCK) {
       float accr[TN];
@@ -392,9 +394,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       // every CTA of the cluster holds its partial tile in shared memory at the same offset;
       // each one finishes a contiguous share of the rows, summing the peers' tiles in split
       // order through distributed shared memory
+      if (threadIdx.x == 64) MB_STAMP(8);
+      if (p.cluster_ws) __threadfence();                   // partial tile in global memory: visible to the cluster's other SMs
       epi_bar_sync();
       mb::cluster_sync_all();
+      if (threadIdx.x == 64) MB_STAMP(9);
       nsrc = p.splits;
+      if (p.cluster_ws) src = p.ws + tile_lin * p.splits * (size_t)(TN * kTileN);
       const int share = (((TN + p.splits - 1) / p.splits) + 7) & ~7;
       row_lo = split * share;
       row_hi = min(TN, row_lo + share);
@@ -431,7 +437,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int tp_unit = (int)tile_lin * (p.cluster ? p.splits : 1) + (p.cluster ? split : 0);
       const uint32_t tp_par = p.tp_size > 1 ? (*reinterpret_cast<const volatile uint32_t*>(p.tp_par) & 1u) : 0u;
       // scale + (SwiGLU) + residual + store of one row held in x[]
-      auto emit = [&](int mr, const float* x) {
+      // `rpre`: the residual vector of this row, loaded by the caller ahead of the partial tiles so
+      // that its latency overlaps theirs (null: load it here)
+      auto emit = [&](int mr, const float* x, const uint4* rpre = nullptr) {
         const int m = m0 + mr;
         const float as = s_ascale[mr];
         float y[8];
@@ -467,7 +475,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         if (vec_ok) {
           if (p.residual) {
-            const uint4 r = __ldg(reinterpret_cast<const uint4*>(p.residual + o));
+            const uint4 r = rpre ? *rpre : __ldg(reinterpret_cast<const uint4*>(p.residual + o));
             const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&r);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -502,13 +510,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // staged tile in shared memory
         for (int mr = row_lo + et / tpr; mr < rows_valid; mr += rpp) {
           float x[16];
+          uint4 rv = make_uint4(0, 0, 0, 0);
+          const bool pre = vec_ok && p.residual && p.tp_size <= 1;
+          if (pre) rv = __ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)(m0 + mr) * p.ldo + n_out0));
           const float4* row = reinterpret_cast<const float4*>(s_tile + mr * kTileN + col0);
 #pragma unroll
           for (int i4 = 0; i4 < 4; ++i4) {
             const float4 f = i4 < nf4 ? row[i4] : make_float4(0.f, 0.f, 0.f, 0.f);
             x[i4 * 4] = f.x; x[i4 * 4 + 1] = f.y; x[i4 * 4 + 2] = f.z; x[i4 * 4 + 3] = f.w;
           }
-          emit(mr, x);
+          emit(mr, x, pre ? &rv : nullptr);
         }
       } else {
         // split-K: partial tiles in the workspace (L2). Two rows x all splits are requested
@@ -517,6 +528,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         for (int mr = row_lo + et / tpr; mr < rows_valid; mr += 2 * rpp) {
           const int mr1 = mr + rpp;
           const bool has1 = mr1 < rows_valid;
+          // residual first: an independent load whose latency then runs under the partial tiles'
+          const bool pre = vec_ok && p.residual && p.tp_size <= 1;
+          uint4 rv0 = make_uint4(0, 0, 0, 0), rv1 = rv0;
+          if (pre) {
+            rv0 = __ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)(m0 + mr) * p.ldo + n_out0));
+            if (has1) rv1 = __ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)(m0 + mr1) * p.ldo + n_out0));
+          }
           float x0[16], x1[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) { x0[i] = 0.f; x1[i] = 0.f; }
@@ -526,12 +544,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int sb = 0; sb < kMaxBatch; ++sb) {
               const bool on = s0 + sb < nsrc;
               const float* base = src + (size_t)(on ? s0 + sb : 0) * (TN * kTileN) + col0;
-              const uint32_t peer = p.cluster ? mb::dsmem_addr(mb::smem_u32(s_tile + col0), on ? s0 + sb : 0) : 0u;
+              const bool dsm = p.cluster && !p.cluster_ws;
+              const uint32_t peer = dsm ? mb::dsmem_addr(mb::smem_u32(s_tile + col0), on ? s0 + sb : 0) : 0u;
 #pragma unroll
               for (int i4 = 0; i4 < 4; ++i4) {
                 const bool ld = on && i4 < nf4;
                 const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (p.cluster) {
+                if (dsm) {
                   f0[sb][i4] = ld ? mb::dsmem_ld_f4(peer + (mr * kTileN + i4 * 4) * 4) : z4;
                   f1[sb][i4] = (ld && has1) ? mb::dsmem_ld_f4(peer + (mr1 * kTileN + i4 * 4) * 4) : z4;
                 } else {
@@ -550,8 +569,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 x1[i4 * 4 + 2] += f1[sb][i4].z; x1[i4 * 4 + 3] += f1[sb][i4].w;
               }
           }
-          emit(mr, x0);
-          if (has1) emit(mr1, x1);
+          if (threadIdx.x == 64 && mr == row_lo) MB_STAMP(11);
+          emit(mr, x0, pre ? &rv0 : nullptr);
+          if (has1) emit(mr1, x1, pre ? &rv1 : nullptr);
         }
       }
       if (p.tp_size > 1) {
@@ -701,7 +721,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       }
     }
-    if (p.splits > 1 && p.cluster) mb::cluster_sync_all();   // peers may still be reading this CTA's tile
+    if (threadIdx.x == 64 && p.cluster) MB_STAMP(10);
+    if (p.splits > 1 && p.cluster && !p.cluster_ws) mb::cluster_sync_all();   // peers may still be reading this CTA's tile
     if (threadIdx.x == 64) MB_STAMP(6);
     mb::tc_fence_before();
   }
@@ -1132,6 +1153,10 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   p.tile_expert = a->tile_expert; p.tile_row0 = a->tile_row0; p.tile_nrows = a->tile_nrows;
   p.n_per_expert = grouped ? a->n_per_expert : 0;
   p.cluster = (splits > 1 && splits <= 8 && !a->no_cluster) ? 1 : 0;
+  // exchange through the workspace when it is there and large enough (the fused tensor-parallel
+  // epilogue keeps its tiles in shared memory)
+  p.cluster_ws = (p.cluster && a->ws && a->tp_size <= 1 && !(a->flags & MB_GEMM_DSMEM_SPLITK) &&
+                  a->ws_bytes >= mb_gemm_counter_bytes() + (size_t)tiles * splits * tn * kTileN * sizeof(float)) ? 1 : 0;
   if (a->outq) {
     if (a->epilogue != EPI_SWIGLU || !a->outq_sf || a->outq_gs <= 0.f || (a->N / 2) % 16 || a->outq_sf_k64 * 64 < a->N / 2)
       return MB_ERR_BAD_ARG;
@@ -1153,10 +1178,10 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
     }
     p.tp_par = reinterpret_cast<const uint32_t*>(a->tp_par);
   }
-  if (splits > 1 && !p.cluster) {
+  if (splits > 1 && (!p.cluster || p.cluster_ws)) {
     const size_t cbytes = mb_gemm_counter_bytes();
     const size_t need = cbytes + (size_t)tiles * splits * tn * kTileN * sizeof(float);
-    if (!a->ws || a->ws_bytes < need || (size_t)tiles * 4 > cbytes) return MB_ERR_TOO_LARGE;
+    if (!a->ws || a->ws_bytes < need || (!p.cluster && (size_t)tiles * 4 > cbytes)) return MB_ERR_TOO_LARGE;
     p.cnt = reinterpret_cast<uint32_t*>(a->ws);
     p.ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a->ws) + cbytes);
   }

@@ -80,6 +80,27 @@ def test_gemm_splitk_workspace_path_matches_cluster_path():
         _run_linear(fmt, 128, 512, 4096, force_splits=8)
 
 
+@pytest.mark.parametrize("fmt", ["nvfp4", "bf16", "fp8_row"])
+@pytest.mark.parametrize("M", [1, 16, 100, 128])
+def test_gemm_cluster_splitk_exchange_paths_agree_bitwise(fmt, M):
+    """A split-K cluster exchanges its fp32 partial tiles through the L2-resident workspace by
+    default and over distributed shared memory on request; both sum in split order, so the
+    results are identical, with and without a residual."""
+    g = torch.Generator().manual_seed(31)
+    N, K = 640, 4096
+    qw = ops.make_weight(torch.randn(N, K, generator=g) * 0.05, fmt).to(DEV)
+    act = ops.quantize_act(torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV), ops.ACT_FOR_WEIGHT[fmt])
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16).to(DEV)
+    for splits in (2, 4, 8):
+        a = ops.linear(act, qw, residual=res, force_splits=splits)
+        b = ops.linear(act, qw, residual=res, force_splits=splits, dsmem_splitk=True)
+        c = ops.linear(act, qw, residual=res, force_splits=splits, no_cluster=True)
+        torch.cuda.synchronize()
+        assert torch.equal(a, b) and torch.equal(a, c), (fmt, M, splits)
+    ops.check_status(DEV)
+    _run_linear(fmt, M, 384, 2048, force_splits=4)
+
+
 def test_gemm_nvfp4_splitk_and_tn():
     _run_linear("nvfp4", 24, 384, 2048, force_splits=4)
     _run_linear("nvfp4", 24, 128, 512, force_tn=128)
