@@ -25,6 +25,18 @@ def moe_block(dec, x, lw):
     weights, idx = moe_ops.route(logits, c, w.bias)
     T = x.shape[0]
     ep = getattr(dec.tp, "ep", None)
+    replicated = w.shared is not None and getattr(w, "shared_replicated", False) and dec.tp.size > 1
+    if (x.is_cuda and ep is None and w.grouped is not None and not replicated
+            and (w.shared is None or w.shared_gate is None or w.shared_gate.N == 1)):
+        # CUDA fast path: the combine kernel also applies the shared expert's sigmoid gate and adds
+        # the residual, so the block's tail is one launch instead of a chain of elementwise ops
+        from ..ops.moe_cuda import grouped_ffn
+        sh = shared_expert(dec, a, w) if w.shared is not None else None
+        g = ops.linear(dec._as_act(hb, "bf16"), w.shared_gate, out_f32=True) if (sh is not None and w.shared_gate is not None) else None
+        if dec.tp.size > 1:
+            y = grouped_ffn(c, a, weights, idx, w, finish=(sh, g, None))
+            return dec.tp.sum_deferred(y, residual=x)
+        return grouped_ffn(c, a, weights, idx, w, finish=(sh, g, x))
     if ep is not None and x.is_cuda:
         routed = ep.dispatch_compute_combine(dec, a, weights, idx, w)
     else:
@@ -38,7 +50,6 @@ def moe_block(dec, x, lw):
             sh = sh.float() * torch.sigmoid(g)
     # a width-sharded shared expert is a partial sum like the routed part; a replicated one (expert
     # parallelism) is added once, after the sum over ranks
-    replicated = sh is not None and getattr(w, "shared_replicated", False) and dec.tp.size > 1
     if sh is not None and not replicated:
         y = y.float() + sh.float()
     if dec.tp.size > 1:

@@ -218,10 +218,13 @@ def _count(n: int = 1):
 def row_op(x: torch.Tensor, out_fmt: str = "bf16", mode: int = IN_COPY, *, K: Optional[int] = None,
            residual=None, write_residual: bool = False, w=None, plus_one: bool = False,
            eps: float = 1e-6, gate=None, head_dim: int = 0, gate_head_stride: int = 0,
-           gate_head_off: int = 0, group: int = 0, also_bf16: bool = False, static_scale: float = 0.0):
+           gate_head_off: int = 0, group: int = 0, also_bf16: bool = False, static_scale: float = 0.0,
+           scale_pad: int = 0):
     """Fused producer: builds y = recipe(x) per row and encodes it as `out_fmt`. `static_scale`
     (nvfp4 only): calibrated global scale used instead of the row's amax / (6 * 448).
-    Returns (Act, residual_out or None). x is bf16 (or fp32 for IN_GATED_RMSNORM inputs)."""
+    `scale_pad` (fp8_g128): extra token columns in the per-group scale matrix (grouped expert GEMMs
+    read whole row tiles past the last row). Returns (Act, residual_out or None). x is bf16 (or
+    fp32 for IN_GATED_RMSNORM inputs)."""
     M = x.shape[0]
     if K is None:
         K = x.shape[1] // 2 if mode == IN_SILU_MUL else x.shape[1]
@@ -261,9 +264,10 @@ def row_op(x: torch.Tensor, out_fmt: str = "bf16", mode: int = IN_COPY, *, K: Op
         act.scale = torch.empty(M, dtype=torch.float32, device=dev)
         a.out_ld = K
     elif out_fmt == "fp8_g128":
-        ld = ((M + 63) // 64) * 64
+        ld = ((M + scale_pad + 63) // 64) * 64
         act.data = torch.empty(M, K, dtype=torch.uint8, device=dev)
-        act.scale = torch.ones((K + 127) // 128, ld, dtype=torch.float32, device=dev)
+        # columns past M only scale token rows past M, whose outputs are never stored
+        act.scale = torch.empty((K + 127) // 128, ld, dtype=torch.float32, device=dev)
         a.out_ld = K
         a.scale_ld = ld
     else:

@@ -239,9 +239,62 @@ __global__ void combine_kernel(const float* __restrict__ y, long long y_ld, cons
   }
 }
 
+// The whole tail of a MoE block in one pass over the token's hidden row:
+//   out = bf16( residual + sum_j w_j y[pair_row_j] + sigmoid(gate_logit) * shared )
+// (shared expert, its sigmoid gate and the residual are each optional).
+__global__ void moe_finish_kernel(const float* __restrict__ y, long long y_ld, const int* __restrict__ pair_row,
+                                  const float* __restrict__ w, int K, int H,
+                                  const __nv_bfloat16* __restrict__ shared, long long shared_ld,
+                                  const float* __restrict__ gate_logit, long long gate_ld,
+                                  const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out) {
+  const int tok = blockIdx.x;
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
+  float sg = 1.f;
+  if (gate_logit) sg = 1.f / (1.f + __expf(-gate_logit[(size_t)tok * gate_ld]));
+  int rows[32];
+  float ws[32];
+  for (int j = 0; j < K; ++j) {
+    rows[j] = pair_row[(size_t)tok * K + j];
+    ws[j] = w[(size_t)tok * K + j];
+  }
+  for (int h = threadIdx.x * 2; h < H; h += blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int j = 0; j < K; ++j) {
+      if (rows[j] >= 0) {
+        const float2 v = *reinterpret_cast<const float2*>(y + (size_t)rows[j] * y_ld + h);
+        a0 += ws[j] * v.x;
+        a1 += ws[j] * v.y;
+      }
+    }
+    if (shared) {
+      const float2 sv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(shared + (size_t)tok * shared_ld + h));
+      a0 += sg * sv.x;
+      a1 += sg * sv.y;
+    }
+    if (residual) {
+      const float2 rv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(residual + (size_t)tok * H + h));
+      a0 += rv.x;
+      a1 += rv.y;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)tok * H + h) = __floats2bfloat162_rn(a0, a1);
+  }
+}
+
 }  // namespace
 
 extern "C" {
+
+int mb_moe_finish(const float* y, long long y_ld, const int* pair_row, const float* w, int T, int K, int H,
+                  const void* shared, long long shared_ld, const float* gate_logit, long long gate_ld,
+                  const void* residual, void* out, cudaStream_t stream) {
+  if (!y || !pair_row || !w || !out || T <= 0 || K <= 0 || K > 32 || H % 2 || y_ld % 2 || shared_ld % 2)
+    return MB_ERR_BAD_ARG;
+  return (int)mb::launch_kernel(moe_finish_kernel, dim3(T), dim3(256), 0, stream, y, y_ld, pair_row, w, K, H,
+                                reinterpret_cast<const __nv_bfloat16*>(shared), shared_ld, gate_logit, gate_ld,
+                                reinterpret_cast<const __nv_bfloat16*>(residual),
+                                reinterpret_cast<__nv_bfloat16*>(out));
+}
 
 int mb_moe_route(const float* logits, long long ld, int T, int E, int K, int mode, const float* bias,
                  int n_group, int topk_group, int renorm, float scaling, float* out_w, int* out_id,

@@ -21,6 +21,11 @@ _native.register_optional("mb_moe_combine", [c.c_void_p, c.c_longlong, c.c_void_
                                             c.c_int, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p])
 
 
+_native.register_optional("mb_moe_finish", [c.c_void_p, c.c_longlong, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int,
+                                           c.c_void_p, c.c_longlong, c.c_void_p, c.c_longlong, c.c_void_p, c.c_void_p,
+                                           c.c_void_p])
+
+
 def route_cuda(logits: torch.Tensor, cfg, bias=None):
     T, E = logits.shape
     K = cfg.experts_per_token
@@ -69,11 +74,12 @@ def gather_act(a: Act, sp: SortedPairs) -> Act:
     groups = s_ld = d_ld = 0
     if a.fmt == "fp8_g128":
         groups, s_ld, d_ld = a.scale.shape[0], a.scale.stride(0), alloc
-        out.scale = torch.ones(groups, alloc, dtype=torch.float32, device=dev)
+        # rows past the sorted pairs only feed output rows nobody reads: their scales may hold anything
+        out.scale = torch.empty(groups, alloc, dtype=torch.float32, device=dev)
         src_scale, dst_scale = a.scale, out.scale
     elif a.fmt == "fp8_row":
         groups, s_ld, d_ld = 1, a.scale.numel(), alloc
-        out.scale = torch.ones(alloc, dtype=torch.float32, device=dev)
+        out.scale = torch.empty(alloc, dtype=torch.float32, device=dev)
         src_scale, dst_scale = a.scale, out.scale
     elif a.fmt == "nvfp4":
         raise NotImplementedError("grouped NVFP4 experts need 128-row aligned scale-factor tiles")
@@ -82,12 +88,15 @@ def gather_act(a: Act, sp: SortedPairs) -> Act:
                                      sp.K, _ptr(sp.total_rows), rows, _ptr(src_scale), _ptr(dst_scale), groups,
                                      s_ld, d_ld, _stream())
     _native.check(rc, "moe_gather")
-    _count(2 if src_scale is not None else 1)
+    _count()
     return out
 
 
-def grouped_ffn(cfg, a: Act, weights: torch.Tensor, idx: torch.Tensor, w) -> torch.Tensor:
-    """Routed experts for all tokens: fp32 [T, hidden] = sum_j weight_j * expert_j(x)."""
+def grouped_ffn(cfg, a: Act, weights: torch.Tensor, idx: torch.Tensor, w, finish=None) -> torch.Tensor:
+    """Routed experts for all tokens: fp32 [T, hidden] = sum_j weight_j * expert_j(x). With
+    `finish` = (shared bf16 [T, hidden] | None, gate logit fp32 [T, 1] | None, residual bf16 | None)
+    the combine kernel also adds the (sigmoid-gated) shared expert and the residual and returns
+    the bf16 block output."""
     ge = w.grouped
     T = a.M
     per_expert = max(1, (T * cfg.experts_per_token) // max(1, ge.num))
@@ -100,14 +109,24 @@ def grouped_ffn(cfg, a: Act, weights: torch.Tensor, idx: torch.Tensor, w) -> tor
         h = row_op(linear(xa, ge.gate_up, grouped=g(ge.n_gate_up)), fmt_d, IN_RELU2)[0]
     elif ge.interleaved:
         act = linear(xa, ge.gate_up, swiglu=True, grouped=g(ge.n_gate_up))
-        h = row_op(act, fmt_d)[0]
+        h = row_op(act, fmt_d, scale_pad=64)[0]
     else:
-        h = row_op(linear(xa, ge.gate_up, grouped=g(ge.n_gate_up)), fmt_d, IN_SILU_MUL)[0]
-    if h.fmt == "fp8_g128" and h.scale.shape[1] < h.M + 64:
-        pad = torch.ones(h.scale.shape[0], h.M + 64, dtype=torch.float32, device=h.scale.device)
+        h = row_op(linear(xa, ge.gate_up, grouped=g(ge.n_gate_up)), fmt_d, IN_SILU_MUL, scale_pad=64)[0]
+    if cfg.ffn_act == "relu2" and h.fmt == "fp8_g128" and h.scale.shape[1] < h.M + 64:
+        pad = torch.empty(h.scale.shape[0], h.M + 64, dtype=torch.float32, device=h.scale.device)
         pad[:, :h.scale.shape[1]] = h.scale
         h.scale = pad
     y = linear(h, ge.down, out_f32=True, grouped=g(ge.n_down))
+    if finish is not None:
+        shared, gate, residual = finish
+        out = torch.empty(T, ge.n_down, dtype=torch.bfloat16, device=y.device)
+        rc = _native.lib().mb_moe_finish(_ptr(y), y.stride(0), _ptr(sp.pair_row), _ptr(weights), T, sp.K, ge.n_down,
+                                         _ptr(shared), shared.stride(0) if shared is not None else 0,
+                                         _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(residual),
+                                         _ptr(out), _stream())
+        _native.check(rc, "moe_finish")
+        _count()
+        return out
     out = torch.empty(T, ge.n_down, dtype=torch.float32, device=y.device)
     rc = _native.lib().mb_moe_combine(_ptr(y), y.stride(0), _ptr(sp.pair_row), _ptr(weights), T, sp.K, ge.n_down,
                                       None, _ptr(out), None, _stream())
