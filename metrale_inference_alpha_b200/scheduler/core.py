@@ -241,6 +241,15 @@ class SchedulerCore:
             if n <= 0:
                 continue
             start = seq.num_computed
+            if (n == remaining and self.pool is not None and self.prefix is not None
+                    and getattr(self.prefix, "needs_snapshot", False)):
+                # recurrent models: a later request with the same prompt can only resume from a state
+                # snapshot, and the longest reusable prefix ends at the last block boundary below the
+                # prompt's end: stop this chunk there, so that the snapshot exists (the remaining
+                # < one block of tokens runs as the next step)
+                boundary = ((len(seq.tokens) - 1) // self.cfg.block_size) * self.cfg.block_size
+                if start < boundary and boundary >= self.snapshot_interval:
+                    n = boundary - start
             items.append(SeqStep(seq, seq.tokens[start:start + n], start, sample=(start + n == len(seq.tokens))))
             budget -= n
         return items

@@ -214,3 +214,18 @@ def test_a_reported_device_status_latches_the_engine_fault():
     assert eng.fault.is_set()
     with pytest.raises(FatalDeviceError):
         eng.add_request([1], SamplingParams(max_tokens=1))
+
+
+@pytest.mark.parametrize("model", ["tiny-nemotron-h", "tiny-hybrid-moe"])
+def test_recurrent_models_reuse_a_prompt_prefix_through_a_state_snapshot(model):
+    """A prompt seen before resumes from the state snapshot taken at its last full block
+    (prefill stops there once, so that the snapshot exists): the second request computes less
+    than one block of prompt tokens and produces the same tokens."""
+    eng = LLMEngine(EngineArgs(model=preset(model), device="cpu", max_num_seqs=4, max_model_len=512))
+    prompt = [(7 * j) % 300 + 1 for j in range(300)]
+    cold = eng.generate([prompt], SamplingParams(max_tokens=6))[0]
+    warm = eng.generate([prompt], SamplingParams(max_tokens=6))[0]
+    longer = eng.generate([prompt + [5, 6, 7]], SamplingParams(max_tokens=4))[0]
+    assert cold.cached_tokens == 0
+    assert warm.cached_tokens == 288 and warm.output_ids == cold.output_ids
+    assert longer.cached_tokens == 288
