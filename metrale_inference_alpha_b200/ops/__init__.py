@@ -345,7 +345,7 @@ def quantize_act(x: torch.Tensor, fmt: str, static_scale: float = 0.0) -> Act:
 def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
            swiglu: bool = False, out_f32: bool = False, out: Optional[torch.Tensor] = None,
            force_tn: int = 0, force_splits: int = 0, one_tile_per_cta: bool = False, decode_tile_order: bool = False,
-           dsmem_splitk: bool = False, grouped=None, no_cluster: bool = False, tp=None, quant_out: float = 0.0):
+           dsmem_splitk: bool = False, grouped=None, no_cluster: bool = False, quant_out: float = 0.0):
     """out[m, n] = sum_k act[m, k] * w[n, k] (+ residual); with `swiglu`, w holds gate/up rows
     interleaved (2j, 2j+1) and the result is silu(gate) * up of width N/2. `quant_out` > 0 (with
     `swiglu`): return the result as an NVFP4 `Act` quantised with that calibrated global scale --
@@ -358,7 +358,7 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
     assert act.fmt == ACT_FOR_WEIGHT[w.fmt], (act.fmt, w.fmt)
     M, N = act.M, w.N
     if quant_out > 0.0:
-        assert swiglu and residual is None and not out_f32 and grouped is None and tp is None
+        assert swiglu and residual is None and not out_f32 and grouped is None
         fused = (act.data.is_cuda and M <= 128 and (N + 127) // 128 > runtime(act.data.device).sm_count
                  and w.fmt in ("nvfp4", "fp8_row", "bf16") and (N // 2) % 256 == 0 and not one_tile_per_cta)
         if not fused:
@@ -412,13 +412,6 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
         qact.scale = static_scale_vec(dev, quant_out, M)
         a.out = _ptr(qact.data)                              # the bf16 output does not exist in this mode
         a.outq, a.ldq, a.outq_sf, a.outq_sf_k64, a.outq_gs = _ptr(qact.data), Kq // 2, _ptr(qact.sf), qact.sf_k64, quant_out
-    if tp is not None:
-        # fused all-reduce: tp = dict(size, rank, m_cap, u_cap, recv[], out[], flags[], done[], par)
-        a.tp_size, a.tp_rank, a.tp_m_cap, a.tp_u_cap = tp["size"], tp["rank"], tp["m_cap"], tp["u_cap"]
-        for r in range(tp["size"]):
-            a.tp_recv[r], a.tp_out[r] = tp["recv"][r], tp["out"][r]
-            a.tp_flags[r], a.tp_done[r] = tp["flags"][r], tp["done"][r]
-        a.tp_par = tp["par"]
     if grouped is not None:
         # (tile_expert, tile_row0, tile_nrows, n_per_expert, max_tiles, tile_rows)
         a.tile_expert, a.tile_row0, a.tile_nrows = _ptr(grouped[0]), _ptr(grouped[1]), _ptr(grouped[2])

@@ -27,9 +27,6 @@ class GemmArgs(C.Structure):
         ("ws", c_void_p), ("ws_bytes", c_size_t), ("status", c_void_p),
         ("force_tn", c_int), ("force_splits", c_int), ("sm_count", c_int), ("flags", c_int), ("timing_trace", c_void_p), ("no_cluster", c_int),
         ("outq", c_void_p), ("ldq", c_int), ("outq_sf", c_void_p), ("outq_sf_k64", c_int), ("outq_gs", c_float),
-        ("tp_size", c_int), ("tp_rank", c_int), ("tp_m_cap", c_int), ("tp_u_cap", c_int),
-        ("tp_recv", c_void_p * 8), ("tp_out", c_void_p * 8), ("tp_flags", c_void_p * 8), ("tp_done", c_void_p * 8),
-        ("tp_par", c_void_p),
         ("tile_expert", c_void_p), ("tile_row0", c_void_p), ("tile_nrows", c_void_p),
         ("n_per_expert", c_int), ("max_tiles", c_int),
     ]

@@ -39,13 +39,6 @@ struct MbGemmArgs {
   void* outq_sf;
   int outq_sf_k64;
   float outq_gs;
-  // fused tensor-parallel all-reduce (0 = off)
-  int tp_size, tp_rank, tp_m_cap, tp_u_cap;
-  void* tp_recv[8];
-  void* tp_out[8];
-  void* tp_flags[8];
-  void* tp_done[8];
-  void* tp_par;
   const int* tile_expert;   // grouped mode (all four set together)
   const int* tile_row0;
   const int* tile_nrows;

@@ -64,14 +64,6 @@ struct GemmParams {
   const int* tile_row0;
   const int* tile_nrows;
   int n_per_expert;
-  // tensor-parallel fused all-reduce (row-parallel GEMM): see the epilogue
-  int tp_size, tp_rank, tp_m_cap, tp_u_cap;
-  __nv_bfloat16* tp_recv[8];    // per rank: [2 parity][tp source][m_cap][ldo] bf16 landing zones
-  __nv_bfloat16* tp_out[8];     // [0]: NVLink multicast address of the landing zones (null = one peer store per rank);
-                                // [1] non-null with [0]: two-shot protocol with the reduction done inside the switch
-  uint32_t* tp_flags[8];        // per rank: [2 parity][u_cap] arrivals per unit
-  uint32_t* tp_done[8];         // per rank: CTA completion counter of the running call
-  const uint32_t* tp_par;       // this rank's current parity (flipped by the last CTA of a call)
   // quantised output of the SwiGLU epilogue (persistent kernel): packed e2m1 + tiled ue4m3 scale
   // factors for the consuming W4A4 GEMM, with a calibrated (static) global scale
   uint8_t* outq;      // [M, ldq] bytes, two values per byte; null = bf16 / fp32 output
@@ -434,8 +426,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                           ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.residual)) & 15) == 0;
       const int rows_valid = min(row_hi, m_end - m0);
       const int nf4 = cpt / 4;                             // float4 per row for this thread
-      const int tp_unit = (int)tile_lin * (p.cluster ? p.splits : 1) + (p.cluster ? split : 0);
-      const uint32_t tp_par = p.tp_size > 1 ? (*reinterpret_cast<const volatile uint32_t*>(p.tp_par) & 1u) : 0u;
       // scale + (SwiGLU) + residual + store of one row held in x[]
       // `rpre`: the residual vector of this row, loaded by the caller ahead of the partial tiles so
       // that its latency overlaps theirs (null: load it here)
@@ -451,28 +441,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           for (int i = 0; i < 8; ++i) y[i] = x[i] * wcol[i] * as;
         }
         const size_t o = (size_t)m * p.ldo + n_out0;
-        if (p.tp_size > 1) {
-          // stage 1 of the fused all-reduce: this rank's bf16 partial goes straight into every
-          // rank's landing zone [parity][source rank] (peer stores over NVLink)
-          uint4 pk;
-          __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) pb[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
-          const size_t slot = (((size_t)tp_par * p.tp_size + p.tp_rank) * p.tp_m_cap + m) * p.ldo + n_out0;
-          if (p.tp_out[0] && p.tp_out[1]) {
-            // two-shot: the partial stays in this rank's own zone (slot of source 0); the unit's
-            // owner sums all ranks' copies with one in-switch multimem.ld_reduce per 16 bytes
-            const size_t own = (((size_t)tp_par * p.tp_size) * p.tp_m_cap + m) * p.ldo + n_out0;
-            *reinterpret_cast<uint4*>(p.tp_recv[p.tp_rank] + own) = pk;
-          } else if (p.tp_out[0]) {
-            // NVLS: one multicast store, replicated into every rank's zone by the switch
-            mb::multimem_st_v4(p.tp_out[0] + slot, pk);
-          } else {
-#pragma unroll 1
-            for (int r = 0; r < p.tp_size; ++r) *reinterpret_cast<uint4*>(p.tp_recv[r] + slot) = pk;
-          }
-          return;
-        }
         if (vec_ok) {
           if (p.residual) {
             const uint4 r = rpre ? *rpre : __ldg(reinterpret_cast<const uint4*>(p.residual + o));
@@ -511,13 +479,55 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         for (int mr = row_lo + et / tpr; mr < rows_valid; mr += rpp) {
           float x[16];
           uint4 rv = make_uint4(0, 0, 0, 0);
-          const bool pre = vec_ok && p.residual && p.tp_size <= 1;
+          const bool pre = vec_ok && p.residual;
           if (pre) rv = __ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)(m0 + mr) * p.ldo + n_out0));
           const float4* row = reinterpret_cast<const float4*>(s_tile + mr * kTileN + col0);
 #pragma unroll
           for (int i4 = 0; i4 < 4; ++i4) {
             const float4 f = i4 < nf4 ? row[i4] : make_float4(0.f, 0.f, 0.f, 0.f);
             x[i4 * 4] = f.x; x[i4 * 4 + 1] = f.y; x[i4 * 4 + 2] = f.z; x[i4 * 4 + 3] = f.w;
+          }
+          emit(mr, x, pre ? &rv : nullptr);
+        }
+      } else if (p.cluster && p.cluster_ws) {
+        // split-K cluster, partial tiles in the L2-resident workspace: this CTA's row share of
+        // every split's tile is brought into the (idle) stage buffers with asynchronous 16-byte
+        // copies that are all in flight together, so the ~1.3 us first-touch latency of lines
+        // another SM has just written is paid once, not once per batch of register loads; the
+        // rows are then summed from shared memory in split order.
+        const int my_rows = rows_valid - row_lo;                       // may be <= 0
+        if (my_rows > 0) {
+          const int chunks_per_row = kTileN / 4;                       // 16-byte chunks
+          const int per_split = my_rows * chunks_per_row;
+          for (int i = et; i < nsrc * per_split; i += 128) {
+            const int sI = i / per_split, rem = i - sI * per_split;
+            const float* g = src + (size_t)sI * (TN * kTileN) + (size_t)row_lo * kTileN + rem * 4;
+            const uint32_t d = mb::smem_u32(s_tile + (size_t)sI * per_split * 4 + rem * 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(g) : "memory");
+          }
+        }
+        // residual vectors of this thread's first two rows: independent loads, issued under the copies
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        epi_bar_sync();
+        if (threadIdx.x == 64) MB_STAMP(11);
+        const int per_split_f = (my_rows > 0 ? my_rows : 0) * kTileN;
+        for (int mr = row_lo + et / tpr; mr < rows_valid; mr += rpp) {
+          const bool pre = vec_ok && p.residual;
+          uint4 rv = make_uint4(0, 0, 0, 0);
+          if (pre) rv = __ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)(m0 + mr) * p.ldo + n_out0));
+          float x[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) x[i] = 0.f;
+          for (int sI = 0; sI < nsrc; ++sI) {
+            const float4* row = reinterpret_cast<const float4*>(s_tile + (size_t)sI * per_split_f + (mr - row_lo) * kTileN + col0);
+#pragma unroll
+            for (int i4 = 0; i4 < 4; ++i4) {
+              if (i4 < nf4) {
+                const float4 f = row[i4];
+                x[i4 * 4] += f.x; x[i4 * 4 + 1] += f.y; x[i4 * 4 + 2] += f.z; x[i4 * 4 + 3] += f.w;
+              }
+            }
           }
           emit(mr, x, pre ? &rv : nullptr);
         }
@@ -529,7 +539,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int mr1 = mr + rpp;
           const bool has1 = mr1 < rows_valid;
           // residual first: an independent load whose latency then runs under the partial tiles'
-          const bool pre = vec_ok && p.residual && p.tp_size <= 1;
+          const bool pre = vec_ok && p.residual;
           uint4 rv0 = make_uint4(0, 0, 0, 0), rv1 = rv0;
           if (pre) {
             rv0 = __ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)(m0 + mr) * p.ldo + n_out0));
@@ -572,152 +582,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (threadIdx.x == 64 && mr == row_lo) MB_STAMP(11);
           emit(mr, x0, pre ? &rv0 : nullptr);
           if (has1) emit(mr1, x1, pre ? &rv1 : nullptr);
-        }
-      }
-      if (p.tp_size > 1) {
-        // ---- fused all-reduce, one NVLink hop. Every rank runs the same grid, so unit u (an
-        // output tile share) exists on every rank. Publish: system-scope fence, then a release
-        // increment of unit u's arrival flag on every rank. Consume: wait (bounded) until all
-        // ranks have arrived here, sum the landing-zone rows in rank order, add the residual,
-        // store the bf16 result locally, re-arm the flag. Landing zones and flags are
-        // double-buffered by a per-rank parity that the last CTA of the kernel flips.
-        __threadfence_system();
-        epi_bar_sync();
-        uint32_t* my_flag = p.tp_flags[p.tp_rank] + (size_t)tp_par * p.tp_u_cap + tp_unit;
-        const bool two_shot = p.tp_out[0] && p.tp_out[1];
-        if (two_shot) {
-          // ---- in-switch variant. Unit u is owned by rank u % size. Every rank tells the owner
-          // that its partial is in place; the owner sums the copies of all ranks with
-          // multimem.ld_reduce (fp32 accumulation in the switch), adds the residual, broadcasts
-          // the bf16 result into every rank's result zone (slot of source 1) with multimem.st and
-          // raises bit 16 of the unit's flag on every rank; every rank then copies its rows out.
-          // Each GPU moves about two copies of the output over NVLink instead of `size` copies.
-          constexpr uint32_t kDoneBit = 1u << 16;
-          const int owner = tp_unit % p.tp_size;
-          if (threadIdx.x == 64)
-            mb::red_add_release_sys(p.tp_flags[owner] + (size_t)tp_par * p.tp_u_cap + tp_unit, 1u);
-          const size_t zone0 = ((size_t)tp_par * p.tp_size) * p.tp_m_cap * p.ldo;         // partials (source slot 0)
-          const size_t zone1 = zone0 + (size_t)p.tp_m_cap * p.ldo;                        // results (source slot 1)
-          if (p.tp_rank == owner) {
-            if (threadIdx.x == 64) is_last_s = mb::wait_flag_sys(my_flag, (uint32_t)p.tp_size, p.status) ? 1 : 0;
-            epi_bar_sync();
-            if (is_last_s) {
-              // four in-switch loads in flight per thread: their latency (a round trip through
-              // the switch to every rank) would otherwise add up row after row
-              constexpr int kBatch = 4;
-              for (int mr0 = row_lo + et / tpr; mr0 < rows_valid; mr0 += rpp * kBatch) {
-                uint4 sum[kBatch];
-#pragma unroll
-                for (int b = 0; b < kBatch; ++b) {
-                  const int mr = mr0 + b * rpp;
-                  if (mr < rows_valid)
-                    sum[b] = mb::multimem_ld_reduce_bf16x8(p.tp_out[0] + zone0 + (size_t)(m0 + mr) * p.ldo + n_out0);
-                }
-#pragma unroll
-                for (int b = 0; b < kBatch; ++b) {
-                  const int mr = mr0 + b * rpp;
-                  if (mr >= rows_valid) continue;
-                  const size_t zo = (size_t)(m0 + mr) * p.ldo + n_out0;
-                  const __nv_bfloat162* sb = reinterpret_cast<const __nv_bfloat162*>(&sum[b]);
-                  float acc[8];
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(sb[i]);
-                    acc[2 * i] = f.x; acc[2 * i + 1] = f.y;
-                  }
-                  if (p.residual) {
-                    const uint4 rr = __ldg(reinterpret_cast<const uint4*>(p.residual + zo));
-                    const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rr);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                      const float2 f = __bfloat1622float2(rb[i]);
-                      acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
-                    }
-                  }
-                  uint4 pk;
-                  __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) pb[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-                  mb::multimem_st_v4(p.tp_out[0] + zone1 + zo, pk);
-                }
-              }
-            }
-            __threadfence_system();
-            epi_bar_sync();
-            if (threadIdx.x == 64 && is_last_s) {
-              for (int r = 0; r < p.tp_size; ++r)
-                mb::red_add_release_sys(p.tp_flags[r] + (size_t)tp_par * p.tp_u_cap + tp_unit, kDoneBit);
-            }
-          }
-          if (threadIdx.x == 64) is_last_s = mb::wait_flag_sys(my_flag, kDoneBit, p.status) ? 1 : 0;
-          epi_bar_sync();
-          if (is_last_s) {
-            const __nv_bfloat16* res = p.tp_recv[p.tp_rank] + zone1;
-            for (int mr = row_lo + et / tpr; mr < rows_valid; mr += rpp) {
-              const size_t zo = (size_t)(m0 + mr) * p.ldo + n_out0;
-              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + zo) =
-                  __ldcg(reinterpret_cast<const uint4*>(res + zo));
-            }
-          }
-        } else {
-          if (threadIdx.x == 64) {
-            for (int r = 0; r < p.tp_size; ++r)
-              mb::red_add_release_sys(p.tp_flags[r] + (size_t)tp_par * p.tp_u_cap + tp_unit, 1u);
-          }
-          if (threadIdx.x == 64) is_last_s = mb::wait_flag_sys(my_flag, (uint32_t)p.tp_size, p.status) ? 1 : 0;
-        }
-        epi_bar_sync();
-        if (is_last_s && !two_shot) {
-          const __nv_bfloat16* zone = p.tp_recv[p.tp_rank] + (size_t)tp_par * p.tp_size * p.tp_m_cap * p.ldo;
-          for (int mr = row_lo + et / tpr; mr < rows_valid; mr += rpp) {
-            const int m = m0 + mr;
-            const size_t o = (size_t)m * p.ldo + n_out0;
-            uint4 v[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-              if (r < p.tp_size)
-                v[r] = __ldcg(reinterpret_cast<const uint4*>(zone + ((size_t)r * p.tp_m_cap + m) * p.ldo + n_out0));
-            float acc[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              if (r < p.tp_size) {
-                const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&v[r]);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const float2 f = __bfloat1622float2(vb[i]);
-                  acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
-                }
-              }
-            }
-            if (p.residual) {
-              const uint4 rr = __ldg(reinterpret_cast<const uint4*>(p.residual + o));
-              const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rr);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(rb[i]);
-                acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
-              }
-            }
-            uint4 pk;
-            __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) pb[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
-          }
-        }
-        epi_bar_sync();
-        if (threadIdx.x == 64) {
-          *my_flag = 0;
-          __threadfence();
-          // the last CTA of the grid to get here flips the parity for the next call
-          const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
-          const uint32_t prev = atomicAdd(p.tp_done[p.tp_rank], 1u);
-          if (prev == total - 1) {
-            *p.tp_done[p.tp_rank] = 0;
-            *const_cast<uint32_t*>(p.tp_par) = tp_par ^ 1u;
-          }
         }
       }
     }
@@ -1155,7 +1019,7 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   p.cluster = (splits > 1 && splits <= 8 && !a->no_cluster) ? 1 : 0;
   // exchange through the workspace when it is there and large enough (the fused tensor-parallel
   // epilogue keeps its tiles in shared memory)
-  p.cluster_ws = (p.cluster && a->ws && a->tp_size <= 1 && !(a->flags & MB_GEMM_DSMEM_SPLITK) &&
+  p.cluster_ws = (p.cluster && a->ws && !(a->flags & MB_GEMM_DSMEM_SPLITK) &&
                   a->ws_bytes >= mb_gemm_counter_bytes() + (size_t)tiles * splits * tn * kTileN * sizeof(float)) ? 1 : 0;
   if (a->outq) {
     if (a->epilogue != EPI_SWIGLU || !a->outq_sf || a->outq_gs <= 0.f || (a->N / 2) % 16 || a->outq_sf_k64 * 64 < a->N / 2)
@@ -1163,20 +1027,6 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
     p.outq = reinterpret_cast<uint8_t*>(a->outq); p.ldq = a->ldq;
     p.outq_sf = reinterpret_cast<uint8_t*>(a->outq_sf); p.outq_sf_k64 = a->outq_sf_k64;
     p.outq_gs = a->outq_gs;
-  }
-  if (a->tp_size > 1) {
-    if (a->tp_size > 8 || a->epilogue != EPI_PLAIN || a->out_f32 || grouped || a->N % kTileN || a->ldo % 8 ||
-        a->M > a->tp_m_cap || (splits > 1 && !p.cluster) || !a->tp_par)
-      return MB_ERR_UNSUPPORTED;
-    if (tiles * splits > a->tp_u_cap) return MB_ERR_TOO_LARGE;
-    p.tp_size = a->tp_size; p.tp_rank = a->tp_rank; p.tp_m_cap = a->tp_m_cap; p.tp_u_cap = a->tp_u_cap;
-    for (int r = 0; r < a->tp_size; ++r) {
-      p.tp_recv[r] = reinterpret_cast<__nv_bfloat16*>(a->tp_recv[r]);
-      p.tp_out[r] = reinterpret_cast<__nv_bfloat16*>(a->tp_out[r]);
-      p.tp_flags[r] = reinterpret_cast<uint32_t*>(a->tp_flags[r]);
-      p.tp_done[r] = reinterpret_cast<uint32_t*>(a->tp_done[r]);
-    }
-    p.tp_par = reinterpret_cast<const uint32_t*>(a->tp_par);
   }
   if (splits > 1 && (!p.cluster || p.cluster_ws)) {
     const size_t cbytes = mb_gemm_counter_bytes();
@@ -1201,7 +1051,7 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   // more tiles than SMs: persistent CTAs, balanced tile counts. One token tile (decode) always;
   // several token tiles (prefill, 128-token tiles) when MB_GEMM_PERSISTENT_PREFILL asks for it.
   const bool multi_m_ok = tiles_m > 1 && tn == 128 && (a->flags & MB_GEMM_PERSISTENT_PREFILL) && !a->outq;
-  if (!grouped && a->tp_size <= 1 && splits == 1 && (tiles_m == 1 || multi_m_ok) && tn <= 128 && kind != KIND_FP8_BLOCK &&
+  if (!grouped && splits == 1 && (tiles_m == 1 || multi_m_ok) && tn <= 128 && kind != KIND_FP8_BLOCK &&
       tiles > sms && (tiles_m > 1 || tiles_n > sms) && !(a->flags & MB_GEMM_ONE_TILE_PER_CTA)) {
     const int waves = (tiles + sms - 1) / sms;
     const int grid_x = (tiles + waves - 1) / waves;
@@ -1277,6 +1127,5 @@ extern "C" int mb_gemm_noalloc(const MbGemmArgs* a, cudaStream_t stream) {
   b.ws = dev_ptr[dev];
   b.ws_bytes = MB_NOALLOC_SCRATCH_BYTES;
   b.no_cluster = 1;            // this variant is the workspace path by definition
-  b.tp_size = 0;
   return mb_gemm(&b, stream);  // refuses with MB_ERR_TOO_LARGE when the workspace would not fit
 }

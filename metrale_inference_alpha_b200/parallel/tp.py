@@ -9,8 +9,7 @@ runs ``parallel.fused.FusedReduce.reduce_norm``: sum over ranks through NVLink (
 ``multimem.ld_reduce`` or peer loads) + residual + norm + quantiser, and for larger batches the
 all-gather of the quantised rows (``multimem.st``), in one kernel. Greedy selection over the
 vocab-parallel lm_head exchanges one (max, index) pair per rank and row
-(``FusedReduce.argmax_merge``) instead of gathering logits. ``fused_gemm`` selects the older
-variant that reduces inside the GEMM epilogue (``FusedCollectives``).
+(``FusedReduce.argmax_merge``) instead of gathering logits.
 
 Health: every collective is followed by an async-error check when ``check_health`` is set;
 a failed or timed-out collective poisons the context (all later calls raise) and the engine
@@ -35,7 +34,7 @@ class CommPoisoned(RuntimeError):
 
 class NcclTpContext(TpContext):
     def __init__(self, rank: int, size: int, device, fused: bool = True, group=None,
-                 diagnostics: Optional[bool] = None, fused_gemm: bool = False):
+                 diagnostics: Optional[bool] = None):
         self.rank, self.size = rank, size
         self.device = torch.device(device)
         self.group = group
@@ -44,19 +43,10 @@ class NcclTpContext(TpContext):
         self.seq = 0
         self.diagnostics = (os.environ.get("METRALE_COMM_DIAGNOSTICS") == "1") if diagnostics is None else diagnostics
         self.bytes_reduced = 0
-        self.fused_impl = None
         self.reduce = None               # parallel.fused.FusedReduce once setup_fused() has run
         if os.environ.get("METRALE_NO_FUSED_COLLECTIVES") == "1":
             fused = False
-        self.want_fused = bool(fused) and not fused_gemm and size > 1 and self.device.type == "cuda"
-        if fused and fused_gemm and size > 1 and self.device.type == "cuda":
-            try:
-                from .fused import FusedCollectives
-                self.fused_impl = FusedCollectives(rank, size, self.device, group)
-                self.fused = True
-            except Exception as e:                      # symmetric memory unavailable: keep NCCL
-                if rank == 0:
-                    print(f"[tp] fused collectives unavailable ({type(e).__name__}: {e}); using NCCL", flush=True)
+        self.want_fused = bool(fused) and size > 1 and self.device.type == "cuda"
 
     def setup_fused(self, hidden: int, m_cap: int) -> bool:
         """Allocate the symmetric buffers of the consumer-fused reduction (collective: every rank
@@ -115,7 +105,7 @@ class NcclTpContext(TpContext):
             self.poisoned = f"reconnect failed: {e}"
             return False
         self.group, self.poisoned, self.fused, self.reconnects = new_group, None, False, getattr(self, "reconnects", 0) + 1
-        self.reduce = self.fused_impl = None
+        self.reduce = None
         return True
 
     # ------------------------------------------------------------------ collectives
@@ -169,8 +159,6 @@ class NcclTpContext(TpContext):
             ops.linear(act, w, out=part)
             pend = PendingSum(self.reduce, part, residual)
             return pend if defer else pend.resolve()
-        if self.fused_impl is not None and act.data.is_cuda:
-            return self.fused_impl.gemm_allreduce(act, w, residual)
         y = ops.linear(act, w, residual=residual if self.rank == 0 else None)
         return self.all_reduce(y)
 

@@ -1,4 +1,4 @@
-"""Multi-GPU checks (skipped with fewer than 2 GPUs): fused GEMM + all-reduce vs the NCCL baseline."""
+"""Multi-GPU checks (skipped with fewer than 2 GPUs): the consumer-fused tensor-parallel reduction and the EP all-to-all vs their NCCL baselines."""
 import os
 import subprocess
 import sys
@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_gemm_allreduce_matches_nccl_on_two_gpus():
+def test_fused_tensor_parallel_reduction_matches_nccl_on_two_gpus():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", "29533", os.path.join(ROOT, "tests", "multi_gpu", "tp_check.py")]
