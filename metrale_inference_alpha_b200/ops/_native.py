@@ -193,9 +193,20 @@ def diff_traces(a, b):
     return None
 
 
+_launch_hook = None
+
+
+def set_launch_hook(fn) -> None:
+    """fn(kernel launcher name) is called after every launch (telemetry level "kernel")."""
+    global _launch_hook
+    _launch_hook = fn
+
+
 def check(rc: int, what: str) -> None:
     if _trace is not None:
         _trace.append(what.split("[", 1)[0])
+    if _launch_hook is not None and rc == 0:
+        _launch_hook(what.split("[", 1)[0])
     if rc != 0:
         msg = _CODES.get(rc, f"CUDA error {rc}")
         raise KernelError(f"{what}: {msg}")

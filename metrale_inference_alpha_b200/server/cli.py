@@ -61,7 +61,8 @@ def build_parser() -> argparse.ArgumentParser:
                             "poolside_v1", "bare_json", "json"])
     s.add_argument("--reasoning-format", default="think")
     s.add_argument("--default-max-tokens", type=int, default=1024)
-    s.add_argument("--telemetry", default="basic", choices=["off", "basic", "full"])
+    s.add_argument("--telemetry", default="basic", choices=["off", "basic", "kernel", "full"],
+                   help="off | basic (counters, host-timed lanes) | kernel (CUDA-event lanes + per-kernel device time; `full` is an alias)")
     s.add_argument("--disable-thinking", action="store_true")
     s.add_argument("--tool-max-tokens", type=int, default=8192)
     s.add_argument("--lora-adapter", action="append", default=[], metavar="NAME=DIR", help="PEFT adapter to serve")

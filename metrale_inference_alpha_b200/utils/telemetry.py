@@ -1,6 +1,10 @@
 """Level-gated telemetry hub: counters, histograms and lane spans, exported as Prometheus text.
-At level "off" every hook is one attribute test. Level "kernel" additionally times scheduler
-lanes with CUDA events. Role of ``crates/telemetry`` (``level.rs``, ``hub.rs``,
+At level "off" every hook is one attribute test. At level "basic" spans are host timers. At
+level "kernel" (on a CUDA device) spans are pairs of CUDA events recorded on the launching
+stream and resolved later without synchronising, and every kernel launcher of ``ops`` leaves
+an event behind it, so consecutive events give per-kernel device time (``kernel_<name>_us``
+histograms; launches inside a replayed CUDA graph are one span, the graph's). Role of
+``crates/telemetry`` (``level.rs``, ``hub.rs``, ``kernel.rs:3-15`` per-kernel spans,
 ``export/prometheus*.rs``) and ``server/src/metrics.rs``."""
 from __future__ import annotations
 
@@ -16,6 +20,7 @@ _BUCKETS = [1, 2, 5, 10, 20, 50, 100, 200, 500, 1000, 2000, 5000, 10000, 30000]
 
 class Telemetry:
     def __init__(self, level: str = "off"):
+        level = "kernel" if level == "full" else level
         assert level in LEVELS
         self.level = level
         self.enabled = level != "off"
@@ -25,6 +30,53 @@ class Telemetry:
         self.hist: Dict[str, List[int]] = {}
         self.hist_sum: Dict[str, float] = defaultdict(float)
         self.start = time.time()
+        self._pending = []               # (name, start event, end event) not yet resolved
+        self._launches = []              # (kernel name, event recorded after its launch)
+        self._cuda = False
+        if level == "kernel":
+            try:
+                import torch
+                self._cuda = torch.cuda.is_available()
+            except Exception:
+                self._cuda = False
+            if self._cuda:
+                from ..ops import _native
+                _native.set_launch_hook(self._on_launch)
+
+    def close(self) -> None:
+        """Detach the per-kernel hook (tests; a second hub in the same process)."""
+        if self._cuda:
+            from ..ops import _native
+            _native.set_launch_hook(None)
+            self._cuda = False
+
+    # ------------------------------------------------------------------ CUDA-event timing
+    def _on_launch(self, name: str) -> None:
+        import torch
+        if torch.cuda.is_current_stream_capturing():
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._launches.append((name, ev))
+        if len(self._launches) > 2048:
+            self.resolve()
+
+    def resolve(self) -> None:
+        """Turn finished event pairs into observations; never blocks."""
+        keep = []
+        for name, a, b in self._pending:
+            if b.query():
+                self.observe_ms(name, a.elapsed_time(b))
+            else:
+                keep.append((name, a, b))
+        self._pending = keep
+        ls = self._launches
+        i = 1
+        while i < len(ls) and ls[i][1].query():
+            self.observe_ms(f"kernel_{ls[i][0]}", ls[i - 1][1].elapsed_time(ls[i][1]), unit_us=True)
+            i += 1
+        if i > 1:
+            self._launches = ls[i - 1:]
 
     def inc(self, name: str, v: float = 1.0) -> None:
         if self.enabled:
@@ -35,9 +87,12 @@ class Telemetry:
         if self.enabled:
             self.gauges[name] = v
 
-    def observe_ms(self, name: str, ms: float) -> None:
+    def observe_ms(self, name: str, ms: float, unit_us: bool = False) -> None:
+        """One observation in milliseconds (`unit_us`: stored and bucketed in microseconds under <name>_us)."""
         if not self.enabled:
             return
+        if unit_us:
+            name, ms = name + "_us", ms * 1e3
         with self._lock:
             h = self.hist.setdefault(name, [0] * (len(_BUCKETS) + 1))
             h[bisect.bisect_left(_BUCKETS, ms)] += 1
@@ -47,6 +102,8 @@ class Telemetry:
         return _Span(self, name)
 
     def prometheus(self, extra: Dict[str, float] = None) -> str:
+        if self._cuda:
+            self.resolve()
         lines = [f"# metrale b200 engine, telemetry level {self.level}",
                  f"metrale_uptime_seconds {time.time() - self.start:.1f}"]
         for k, v in sorted(self.counters.items()):
@@ -70,10 +127,25 @@ class _Span:
         self.t, self.name = t, name
 
     def __enter__(self):
-        self.t0 = time.perf_counter() if self.t.enabled else 0.0
+        t = self.t
+        self.ev = None
+        if t._cuda:
+            import torch
+            if not torch.cuda.is_current_stream_capturing():
+                self.ev = torch.cuda.Event(enable_timing=True)
+                self.ev.record()
+        self.t0 = time.perf_counter() if t.enabled else 0.0
         return self
 
     def __exit__(self, *exc):
-        if self.t.enabled:
-            self.t.observe_ms(self.name, (time.perf_counter() - self.t0) * 1e3)
+        t = self.t
+        if self.ev is not None:
+            import torch
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            t._pending.append((self.name, self.ev, end))      # device time of the lane, resolved later
+            if len(t._pending) > 256:
+                t.resolve()
+        elif t.enabled:
+            t.observe_ms(self.name, (time.perf_counter() - self.t0) * 1e3)
         return False

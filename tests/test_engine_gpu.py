@@ -202,3 +202,23 @@ def test_look_ahead_decode_equals_synchronous_decode(model):
     assert got == want
     assert want[0][1] == "stop" and len(want[0][0]) == first.index(stop) + 1
     assert eng.runner.graph_replays > 50
+
+
+def test_telemetry_kernel_level_records_per_kernel_device_time():
+    """At level "kernel" every launcher leaves a CUDA event behind it; resolved pairs become
+    kernel_<name>_us histograms and lane spans are device time, with no synchronisation added."""
+    from metrale_inference_alpha_b200 import ops
+    from metrale_inference_alpha_b200.utils.telemetry import Telemetry
+    t = Telemetry("kernel")
+    try:
+        x = torch.randn(64, 2048, device="cuda").to(torch.bfloat16)
+        w = torch.ones(2048, device="cuda", dtype=torch.bfloat16)
+        with t.span("lane_norm"):
+            for _ in range(5):
+                ops.row_op(x, "nvfp4", ops.IN_RMSNORM, w=w)
+        torch.cuda.synchronize()
+        text = t.prometheus()
+        assert "metrale_kernel_row_op_us_count 4" in text or "metrale_kernel_row_op_us_count 5" in text
+        assert "metrale_lane_norm_ms_count 1" in text
+    finally:
+        t.close()

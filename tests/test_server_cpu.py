@@ -170,6 +170,19 @@ def test_undeclared_levers_are_refused():
         levers.check_environment({"METRALE_TYPO": "1"})
 
 
+def test_telemetry_kernel_level_without_a_gpu_falls_back_to_host_timers():
+    """Level "kernel" (alias "full") installs CUDA-event spans and the per-launch hook only on a
+    CUDA device; without one it behaves like "basic" and leaves the launch hook alone."""
+    from metrale_inference_alpha_b200.ops import _native
+    t = Telemetry("full")
+    assert t.level == "kernel" and t.enabled
+    assert _native._launch_hook is None or torch.cuda.is_available()
+    with t.span("lane"):
+        pass
+    assert "metrale_lane_ms_count 1" in t.prometheus()
+    t.close()
+
+
 def test_telemetry_prometheus_text():
     t = Telemetry("basic")
     t.inc("requests")
