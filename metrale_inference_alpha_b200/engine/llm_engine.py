@@ -63,6 +63,8 @@ class EngineArgs:
     kv_cache_dtype: str = "auto"                       # auto (the model config's) | bf16 | fp8
     kv_high_precision_layers: str = ""                 # e.g. "0,1,63" or "first:2,last:2": these layers keep bf16 KV under fp8
     oom_guard_mb: int = 4096                           # device memory left unclaimed when sizing the KV pool
+    fp8_kv_calibration_tokens: int = 0                 # fp8 KV without checkpoint scales: calibrate them online over this many tokens (0 = scale 1.0)
+    fp8_kv_headroom: float = 1.0
     pipeline_decode: bool = True                       # launch decode step t + 1 from the device-fed tokens while step t is read back
 
 
@@ -131,7 +133,9 @@ class LLMEngine:
         # a sequence) still never depends on which other requests happen to be running
         ops.configure(attn_part_tokens=1024 if args.max_num_seqs >= 64 else 512)
         self.runner = ModelRunner(cfg, self.weights, args.device, blocks, self.sched_cfg, self.tp,
-                                  use_graphs=args.use_cuda_graphs, kv_poison=args.kv_poison)
+                                  use_graphs=args.use_cuda_graphs, kv_poison=args.kv_poison,
+                                  fp8_kv_calibration_tokens=args.fp8_kv_calibration_tokens,
+                                  fp8_kv_headroom=args.fp8_kv_headroom)
         if args.ep_dispatch == "a2a" and args.ep_size > 1 and self.tp.size > 1 and self.device.type == "cuda" \
                 and cfg.num_experts > 0:
             from ..parallel.ep import EpAllToAll

@@ -120,7 +120,8 @@ class ModelRunner:
     def __init__(self, cfg: ModelConfig, weights: ModelW, device="cpu", num_blocks: int = 256,
                  sched: Optional[SchedulerConfig] = None, tp: Optional[TpContext] = None,
                  use_graphs: bool = True, max_state_slots: Optional[int] = None, num_snapshots: int = 16,
-                 mtp_drafts: int = 0, kv_poison: bool = False):
+                 mtp_drafts: int = 0, kv_poison: bool = False, fp8_kv_calibration_tokens: int = 0,
+                 fp8_kv_headroom: float = 1.0):
         self.cfg, self.w, self.device = cfg, weights, torch.device(device)
         self.sched = sched or SchedulerConfig()
         self.tp = tp or TpContext()
@@ -137,6 +138,22 @@ class ModelRunner:
             self.pool = StatePool(shapes, slots, num_snapshots, device)
         self.caches = LayerCaches(cfg, kv=self.kv, state=self.pool, mtp_kv=self.mtp_kv)
         self.decoder = Decoder(cfg, weights, self.tp, device)
+        # FP8 KV scales: the checkpoint's (three key spellings, weights/kv_scales.py), else online
+        # calibration over the first tokens when asked for, else 1.0
+        self.kv_scales_loaded = 0
+        att = [lw for lw in weights.layers if lw.kind == "attention"]
+        for j, lw in enumerate(att):
+            sc = getattr(lw.mixer, "kv_scale", None)
+            if sc is not None and j < len(self.kv.k_scale) and self.kv.k[j].dtype == torch.uint8:
+                self.kv.k_scale[j].fill_(sc[0])
+                self.kv.v_scale[j].fill_(sc[1])
+                self.kv_scales_loaded += 1
+        self.kv_cal = None
+        if fp8_kv_calibration_tokens > 0 and self.kv_scales_loaded == 0 and cfg.arch != "deepseek_mla":
+            from ..cache.fp8_calibration import Fp8KvCalibration
+            cal = Fp8KvCalibration(self.kv, fp8_kv_calibration_tokens, fp8_kv_headroom)
+            if not cal.frozen:
+                self.kv_cal = self.decoder.kv_cal = cal
         self.max_blocks = (self.sched.max_model_len + bs - 1) // bs
         self.max_seqs = max(self.sched.batch_rungs[-1], self.sched.max_num_seqs)
         max_tokens = max(self.sched.max_prefill_tokens + self.max_seqs, self.max_seqs * 8)
@@ -291,11 +308,13 @@ class ModelRunner:
             batch = ForwardBatch.build([dict(tokens=ids, start_pos=0, blocks=blocks, state_slot=0, logits="none")],
                                        self.block_size, device=self.device, max_blocks=self.max_blocks)
             self.decoder.calib = {}
+            kv_cal, self.decoder.kv_cal = self.decoder.kv_cal, None      # random tokens must not count towards the KV scales
             self.decoder.backbone(batch, self.caches)
             self.tp.end_forward()
             calib = self.decoder.calib
         finally:
             self.decoder.calib = None
+            self.decoder.kv_cal = self.kv_cal
             self.kv.allocator.free(blocks)
         n = 0
         for f in todo:
@@ -384,6 +403,17 @@ class ModelRunner:
         self.h2d_bytes += n * 32
         return False
 
+    def _after_forward(self, batch: ForwardBatch) -> None:
+        """Per-forward bookkeeping that is not part of the model: the collective epilogue and the
+        FP8 KV scale calibration window."""
+        self.tp.end_forward()
+        if self.kv_cal is not None and self.kv_cal.after_step(batch.slot_mapping):
+            self.kv_cal = self.decoder.kv_cal = None          # frozen: graphs may be used from now on
+
+    def graphs_ready(self) -> bool:
+        """CUDA graphs stay off while the KV scales are still being calibrated."""
+        return self.use_graphs and self.kv_cal is None
+
     # ------------------------------------------------------------------ device status
     def _post_status(self) -> None:
         """Queue a copy of the status word behind the step's kernels."""
@@ -429,7 +459,7 @@ class ModelRunner:
                                  self.s_minp[:n_rows], self.s_seed[:n_rows], self.s_step[:n_rows])
             self.out_ids[:n_rows].copy_(ids)
             self.out_lp[:n_rows].copy_(lp)
-        self.tp.end_forward()
+        self._after_forward(batch)
         return logits
 
     def _rung(self, n: int) -> int:
@@ -473,7 +503,7 @@ class ModelRunner:
     # ------------------------------------------------------------------ pipelined decode
     def can_pipeline(self, plan: StepPlan) -> bool:
         """Plain greedy graph-replayed decode: the only step kind that is launched without waiting."""
-        if not (self.use_graphs and plan.kind == "decode" and plan.items):
+        if not (self.graphs_ready() and plan.kind == "decode" and plan.items):
             return False
         if self.decoder.lora is not None and any(i.seq.req.adapter for i in plan.items):
             return False
@@ -539,14 +569,14 @@ class ModelRunner:
         if n_sample_rows == 0:
             batch = self._stage_with_adapters(plan)
             self.decoder.backbone(batch, self.caches)
-            self.tp.end_forward()
+            self._after_forward(batch)
             self._post_status()                       # read at the next synchronisation point
             return StepResult([[] for _ in plan.items], device_ms=(time.perf_counter() - t0) * 1e3)
         if host_logits:
             return self._execute_host_logits(plan, t0)
         is_plain_decode = plan.kind == "decode" and all(len(i.tokens) == 1 for i in plan.items)
         uses_adapter = self.decoder.lora is not None and any(i.seq.req.adapter for i in plan.items)
-        if is_plain_decode and self.use_graphs and not uses_adapter:
+        if is_plain_decode and self.graphs_ready() and not uses_adapter:
             self._decode_graph(plan, greedy, want_lp)
         else:
             batch = self._stage_with_adapters(plan)     # steps with adapter rows run eagerly
@@ -580,7 +610,7 @@ class ModelRunner:
         from ..sampling.host import sample_rows
         batch = self._stage_with_adapters(plan)
         logits, hidden = self.decoder.forward(batch, self.caches, out_f32=True)
-        self.tp.end_forward()
+        self._after_forward(batch)
         self.last_hidden = hidden
         self._post_status()
         toks, lps = sample_rows(self, plan, logits)

@@ -79,6 +79,7 @@ class Decoder:
         if rot > 0 and cfg.rope_local_theta > 0:          # windowed layers rotate with their own, unscaled base
             self.cos_local, self.sin_local = ref.rope_tables(cfg.max_position, rot, cfg.rope_local_theta, device=self.device)
         self.scale = cfg.attn_scale if cfg.attn_scale > 0 else 1.0 / math.sqrt(cfg.head_dim)
+        self.kv_cal = None                 # cache.fp8_calibration.Fp8KvCalibration while FP8 KV scales are being calibrated
         self.lora = None                   # lora.LoraManager when adapters are served
         self.calib = None                  # dict while calibrating static activation scales (engine/runner.py)
 
@@ -135,7 +136,7 @@ class Decoder:
         return self.lora
 
     def attention_block(self, x, lw: LayerW, batch: ForwardBatch, kc, vc, ks, vs, li: int = -1,
-                        add_residual: bool = True):
+                        add_residual: bool = True, kv_layer: int = -1):
         c, w = self.cfg, lw.mixer
         D = c.head_dim
         window = c.window_layers[li] if (c.window_layers and 0 <= li < len(c.window_layers)) else c.sliding_window
@@ -170,7 +171,8 @@ class Decoder:
         q = ops.qk_norm_rope_kvwrite(
             qkv, Hq=w.heads, Hkv=w.kv_heads, D=D, positions=batch.positions, slots=batch.slot_mapping,
             k_cache=kc, v_cache=vc, q_norm_w=qn, k_norm_w=kn, plus_one=c.norm_plus_one,
-            eps=c.rms_eps, cos=cos, sin=sin, q_head_stride=qhs, k_scale=ks, v_scale=vs)
+            eps=c.rms_eps, cos=cos, sin=sin, q_head_stride=qhs, k_scale=ks, v_scale=vs,
+            amax=self.kv_cal.amax_for(kv_layer) if (self.kv_cal is not None and kv_layer >= 0) else None)
         fmt = ACT_FOR_WEIGHT[w.o.fmt]
         static = w.o_in_scale if (fmt == "nvfp4" and self.calib is None and not c.attn_output_gate) else 0.0
         if static > 0.0 and lora is None:
@@ -258,14 +260,15 @@ class Decoder:
                 x = self.full(x)
             if lw.post_attn is not None:
                 y = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i,
-                                         add_residual=False)
+                                         add_residual=False, kv_layer=j if kv is caches.kv else -1)
                 x = self._add_normed(x, y, lw.post_attn)
             elif self.cfg.residual_multiplier != 1.0:
                 y = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i,
-                                         add_residual=False)
+                                         add_residual=False, kv_layer=j if kv is caches.kv else -1)
                 x = x + (self.full(y).float() * self.cfg.residual_multiplier).to(x.dtype)
             else:
-                x = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i)
+                x = self.attention_block(x, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i,
+                                         kv_layer=j if kv is caches.kv else -1)
         elif lw.kind == "gdn":
             from .recurrent import gdn_block
             x = gdn_block(self, x, lw, batch, caches.state, caches.state_index[i])

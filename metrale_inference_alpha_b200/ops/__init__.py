@@ -624,9 +624,10 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, *, Hq: int, Hkv: int, D: int, positi
                          k_cache, v_cache, q_norm_w=None, k_norm_w=None, plus_one: bool = False,
                          eps: float = 1e-6, cos=None, sin=None, q_head_stride: Optional[int] = None,
                          k_off: Optional[int] = None, v_off: Optional[int] = None,
-                         k_scale=None, v_scale=None) -> torch.Tensor:
+                         k_scale=None, v_scale=None, amax=None) -> torch.Tensor:
     """Per-head q/k RMSNorm (optional) + NeoX RoPE (optional) + K/V scatter into the paged cache.
-    qkv [M, *] bf16 row = q heads | k heads | v heads. Returns q [M, Hq, D] bf16."""
+    qkv [M, *] bf16 row = q heads | k heads | v heads. Returns q [M, Hq, D] bf16. `amax`
+    (fp32 [2]): running max |k| and max |v| of the rows written, for online scale calibration."""
     M = qkv.shape[0]
     qhs = q_head_stride or D
     k_off = Hq * qhs if k_off is None else k_off
@@ -644,6 +645,11 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, *, Hq: int, Hkv: int, D: int, positi
         if cos is not None:
             q = ref.apply_rope_neox(q, positions, cos, sin)
             k = ref.apply_rope_neox(k, positions, cos, sin)
+        if amax is not None:
+            okr = slots >= 0
+            if bool(okr.any()):
+                amax[0] = torch.maximum(amax[0], k[okr].abs().max())
+                amax[1] = torch.maximum(amax[1], v[okr].abs().max())
         ref.kv_cache_write(k_cache, v_cache, ref.bf16_round(k) if k_cache.dtype != torch.uint8 else k,
                            v, slots, k_scale, v_scale)
         return q.to(torch.bfloat16)
@@ -661,9 +667,29 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, *, Hq: int, Hkv: int, D: int, positi
     a.k_scale, a.v_scale = _ptr(k_scale), _ptr(v_scale)
     a.num_slots = k_cache.shape[0] * k_cache.shape[1]
     a.status = _ptr(runtime(qkv.device).status)
+    a.amax = _ptr(amax)
     _native.check(_native.lib().mb_qk_norm_rope_kvwrite(C.byref(a), _stream()), "rope_kvwrite")
     _count()
     return q_out
+
+
+def kv_rescale(cache: torch.Tensor, slots: torch.Tensor, old_scale: float, new_scale: torch.Tensor) -> None:
+    """In place, for the listed flat slots of an e4m3 cache [blocks, block, heads, dim]: re-encode
+    value * old_scale / new_scale (a per-tensor scale changed after these rows were written)."""
+    nb, bs = cache.shape[0], cache.shape[1]
+    row = cache.shape[2] * cache.shape[3]
+    if not cache.is_cuda:
+        flat = cache.view(nb * bs, row)
+        ok = slots[(slots >= 0) & (slots < nb * bs)].long()
+        flat[ok] = ref.to_e4m3(ref.from_e4m3(flat[ok]) * (old_scale / float(new_scale)))
+        return
+    _native.check(_native.lib().mb_kv_rescale(_ptr(cache), _ptr(slots), slots.numel(), row, nb * bs, float(old_scale),
+                                              _ptr(new_scale), _stream()), "kv_rescale")
+    _count()
+
+
+_native.register_optional("mb_kv_rescale", [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_longlong, C.c_float,
+                                           C.c_void_p, C.c_void_p])
 
 
 # split-KV partition size (tokens); a function of nothing but this lever, so a sequence's

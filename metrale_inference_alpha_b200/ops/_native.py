@@ -55,6 +55,7 @@ class RopeKvArgs(C.Structure):
         ("cos_tab", c_void_p), ("sin_tab", c_void_p), ("max_pos", c_int),
         ("q_out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("cache_fp8", c_int),
         ("k_scale", c_void_p), ("v_scale", c_void_p), ("num_slots", c_ll), ("status", c_void_p),
+        ("amax", c_void_p),
     ]
 
 

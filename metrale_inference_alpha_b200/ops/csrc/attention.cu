@@ -52,7 +52,21 @@ struct RopeKvParams {
   const float* v_scale;
   long long num_slots;
   uint32_t* status;
+  float* amax;                   // optional [2]: running max |k|, max |v| of the rows written (online scale calibration)
 };
+
+// In-place change of an e4m3 cache's per-tensor scale for the listed slots: value * old / new.
+// Used once, when online calibration freezes its scale and rewrites what the window wrote.
+__global__ void kv_rescale_kernel(uint8_t* cache, const long long* __restrict__ slots, int n, int row_elems,
+                                  long long num_slots, float old_scale, const float* __restrict__ new_scale) {
+  const int i = blockIdx.x;
+  if (i >= n) return;
+  const long long slot = slots[i];
+  if (slot < 0 || slot >= num_slots) return;
+  const float f = old_scale / *new_scale;
+  uint8_t* row = cache + (size_t)slot * row_elems;
+  for (int j = threadIdx.x; j < row_elems; j += blockDim.x) row[j] = mb::float_to_e4m3(mb::e4m3_to_float(row[j]) * f);
+}
 
 __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKvParams p) {
   const int m = blockIdx.x;
@@ -135,6 +149,14 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKvParams p) {
     return;
   }
   const size_t off = ((size_t)slot * p.Hkv + h) * D;
+  if (p.amax) {
+    float mx = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(v[j]));
+    mx = mb::warp_max(mx);
+    // non-negative floats order like their bit patterns
+    if (lane == 0) atomicMax(reinterpret_cast<int*>(p.amax + (kind - 1)), __float_as_int(mx));
+  }
   if (p.cache_fp8) {
     const float sc = kind == 1 ? *p.k_scale : *p.v_scale;
     const float inv = 1.f / sc;
@@ -1031,7 +1053,17 @@ struct MbRopeKvArgs {
   const float* v_scale;
   long long num_slots;
   uint32_t* status;
+  float* amax;             // optional [2] running max |k|, |v| of the written rows
 };
+
+// value * old_scale / *new_scale for every listed slot of an e4m3 cache [num_slots, row_elems]
+int mb_kv_rescale(void* cache, const long long* slots, int n, int row_elems, long long num_slots, float old_scale,
+                  const float* new_scale, cudaStream_t stream) {
+  if (!cache || !slots || !new_scale || n <= 0 || row_elems <= 0 || !(old_scale > 0.f)) return MB_ERR_BAD_ARG;
+  kv_rescale_kernel<<<n, 256, 0, stream>>>(reinterpret_cast<uint8_t*>(cache), slots, n, row_elems, num_slots, old_scale,
+                                           new_scale);
+  return (int)cudaGetLastError();
+}
 
 int mb_qk_norm_rope_kvwrite(const MbRopeKvArgs* a, cudaStream_t stream) {
   if (!a || a->M <= 0 || !a->qkv || !a->q_out || !a->slots) return MB_ERR_BAD_ARG;
@@ -1051,6 +1083,7 @@ int mb_qk_norm_rope_kvwrite(const MbRopeKvArgs* a, cudaStream_t stream) {
   p.k_cache = a->k_cache; p.v_cache = a->v_cache; p.cache_fp8 = a->cache_fp8;
   p.k_scale = a->k_scale; p.v_scale = a->v_scale; p.num_slots = a->num_slots;
   p.status = a->status;
+  p.amax = a->amax;
   const int Htot = a->Hq + 2 * a->Hkv;
   return (int)mb::launch_kernel(rope_kv_kernel, dim3(a->M, (Htot + 3) / 4), dim3(128), 0, stream, p);
 }

@@ -107,6 +107,7 @@ class AttnW:
     o_in_scale: float = 0.0   # NVFP4: calibrated global scale of o_proj's input (0 = per-token dynamic)
     heads: int = 0            # local q heads
     kv_heads: int = 0         # local kv heads
+    kv_scale: Optional[tuple] = None   # (k_scale, v_scale) dequant multipliers from the checkpoint, or None
 
 
 @dataclass
@@ -291,6 +292,9 @@ class Loader:
             w.q_norm, w.k_norm = self.vec(f"{p}.q_norm.weight"), self.vec(f"{p}.k_norm.weight")
             if c.qk_norm_full and self.tp_size > 1:
                 raise NotImplementedError("a q / k norm that spans all heads is served on single-rank engines")
+        # per-layer FP8 KV scales, in whichever of the three spellings the exporter used
+        from .kv_scales import load_kv_scales
+        w.kv_scale = load_kv_scales(self.src, {0: p}).get(0)
         return w
 
     # ---- dense ffn

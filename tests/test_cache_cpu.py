@@ -120,3 +120,93 @@ def test_state_pool_slots_snapshots_and_export():
     p.free(s)
     p.free(s2)
     assert p.num_free == 3
+
+
+# ---------------------------------------------------------------- FP8 KV scales
+def test_kv_scale_keys_resolve_three_spellings_and_refuse_ambiguity():
+    from metrale_inference_alpha_b200.weights.kv_scales import kv_scale_census, load_kv_scales, resolve_kv_scale_keys
+    from metrale_inference_alpha_b200.weights.source import DictSource
+    import torch
+    p = "model.layers.3.self_attn"
+    for spelling, ks, vs in (("k_proj_output", "k_proj.k_scale", "v_proj.v_scale"), ("attn_module", "attn.k_scale", "attn.v_scale"),
+                             ("bare", "k_scale", "v_scale")):
+        src = DictSource({f"{p}.{ks}": torch.tensor(0.02), f"{p}.{vs}": torch.tensor([0.5])})
+        assert resolve_kv_scale_keys(src.has, p) == (spelling, f"{p}.{ks}", f"{p}.{vs}")
+        got = load_kv_scales(src, {3: p, 4: "model.layers.4.self_attn"})
+        assert set(got) == {3} and abs(got[3][0] - 0.02) < 1e-7 and got[3][1] == 0.5
+        assert kv_scale_census(src, {3: p, 4: "model.layers.4.self_attn"}) == {spelling: 1, "none": 1}
+    with pytest.raises(ValueError, match="but not"):
+        resolve_kv_scale_keys(DictSource({f"{p}.k_scale": torch.tensor(1.0)}).has, p)
+    two = DictSource({f"{p}.k_scale": torch.tensor(1.0), f"{p}.v_scale": torch.tensor(1.0),
+                      f"{p}.attn.k_scale": torch.tensor(1.0), f"{p}.attn.v_scale": torch.tensor(1.0)})
+    with pytest.raises(ValueError, match="2 ways"):
+        resolve_kv_scale_keys(two.has, p)
+    with pytest.raises(ValueError, match="non-positive"):
+        load_kv_scales(DictSource({f"{p}.k_scale": torch.tensor(0.0), f"{p}.v_scale": torch.tensor(1.0)}), {3: p})
+
+
+def test_engine_takes_fp8_kv_scales_from_the_checkpoint():
+    import torch
+    from metrale_inference_alpha_b200.config.model_config import preset
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    from metrale_inference_alpha_b200.weights.source import DictSource, SyntheticSource
+    cfg = preset("tiny-dense", kv_dtype="fp8")
+    syn = SyntheticSource(cfg, seed=0)
+    t = {n: syn.get(n) for n in syn.names()}
+    t["model.layers.0.self_attn.k_proj.k_scale"] = torch.tensor(0.03)
+    t["model.layers.0.self_attn.v_proj.v_scale"] = torch.tensor(0.01)
+    eng = LLMEngine(EngineArgs(model=cfg, device="cpu", max_model_len=128, num_kv_blocks=32), source=DictSource(t))
+    kv = eng.runner.kv
+    assert eng.runner.kv_scales_loaded == 1
+    assert abs(float(kv.k_scale[0]) - 0.03) < 1e-7 and abs(float(kv.v_scale[0]) - 0.01) < 1e-7
+    assert float(kv.k_scale[1]) == 1.0
+    out = eng.generate([[5, 6, 7, 8, 9]], SamplingParams(max_tokens=4))[0]
+    assert len(out.output_ids) == 4
+
+
+def test_online_fp8_kv_calibration_freezes_rescales_and_holds_graphs_back():
+    """Scales start provisional, the window's entries are re-encoded at the frozen scale
+    amax * headroom / 448, and CUDA graphs are reported not ready until then."""
+    import torch
+    from metrale_inference_alpha_b200.cache.fp8_calibration import PROVISIONAL_SCALE
+    from metrale_inference_alpha_b200.config.model_config import preset
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.ops import reference as ref
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    cfg = preset("tiny-dense", kv_dtype="fp8")
+    prompt = [(5 * j) % 200 + 1 for j in range(40)]
+    eng = LLMEngine(EngineArgs(model=cfg, device="cpu", max_model_len=128, num_kv_blocks=32, fp8_kv_calibration_tokens=48,
+                               fp8_kv_headroom=1.25, enable_prefix_caching=False))
+    r = eng.runner
+    assert r.kv_cal is not None and not r.kv_cal.frozen and float(r.kv.k_scale[0]) == PROVISIONAL_SCALE
+    def ready():                                           # a CPU engine never uses graphs: only the readiness rule is checked
+        r.use_graphs = True
+        try:
+            return r.graphs_ready()
+        finally:
+            r.use_graphs = False
+    assert not ready()
+    eng.add_request(prompt, SamplingParams(max_tokens=20))
+    eng.step()                                             # prefill: 40 tokens observed, window not reached
+    cal = r.kv_cal
+    assert cal is not None and cal.observed == 40
+    amax_k = float(cal.amax[0][0])
+    assert amax_k > 0
+    while eng.has_work():
+        eng.step()
+    assert r.kv_cal is None and cal.frozen and ready()
+    for i in range(cfg.num_layers):
+        ks, vs = float(r.kv.k_scale[i]), float(r.kv.v_scale[i])
+        assert abs(ks - float(cal.amax[i][0]) * 1.25 / 448) < 1e-9 and abs(vs - float(cal.amax[i][1]) * 1.25 / 448) < 1e-9
+        assert ks not in (1.0, PROVISIONAL_SCALE)
+    # the window's cached keys decode to the same values (to e4m3 rounding) as a cache written at the frozen scale from the start
+    eng2 = LLMEngine(EngineArgs(model=cfg, device="cpu", max_model_len=128, num_kv_blocks=32, enable_prefix_caching=False))
+    for i in range(cfg.num_layers):
+        eng2.runner.kv.k_scale[i].copy_(r.kv.k_scale[i])
+        eng2.runner.kv.v_scale[i].copy_(r.kv.v_scale[i])
+    eng2.add_request(prompt, SamplingParams(max_tokens=1))
+    eng2.step()
+    a = ref.from_e4m3(r.kv.k[0][1:3]) * float(r.kv.k_scale[0])          # blocks 1, 2: positions 0..31 of the first sequence
+    b = ref.from_e4m3(eng2.runner.kv.k[0][1:3]) * float(r.kv.k_scale[0])
+    assert (a - b).abs().max().item() <= 0.13 * b.abs().max().item()

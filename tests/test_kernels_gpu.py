@@ -338,6 +338,39 @@ def test_rowop_activations():
     _close(got.data, want.data, 1e-2, 1e-2)
 
 
+def test_kv_write_observes_amax_and_rescale_matches_reference():
+    """Online FP8 KV calibration support: the KV-write kernel accumulates max |k| / max |v| of the
+    rows it writes, and kv_rescale re-encodes the listed slots from one scale to another."""
+    M, Hq, Hkv, D, bs, nb = 19, 4, 2, 128, 16, 6
+    g = torch.Generator().manual_seed(8)
+    qkv = (torch.randn(M, (Hq + 2 * Hkv) * D, generator=g) * 3).to(torch.bfloat16)
+    pos = torch.arange(M, dtype=torch.int32)
+    slots = torch.randperm(nb * bs, generator=g)[:M].to(torch.int64)
+    slots[5] = -1
+    cos, sin = ref.rope_tables(64, D, 1e6)
+    two = torch.tensor([2.0])
+    kc, vc = _cache(nb, bs, Hkv, D, True)
+    am_ref = torch.zeros(2)
+    ops.qk_norm_rope_kvwrite(qkv, Hq=Hq, Hkv=Hkv, D=D, positions=pos, slots=slots, k_cache=kc, v_cache=vc, cos=cos, sin=sin,
+                             k_scale=two, v_scale=two, amax=am_ref)
+    kcg, vcg = kc.clone().zero_().to(DEV), vc.clone().zero_().to(DEV)
+    am = torch.zeros(2, device=DEV)
+    ops.qk_norm_rope_kvwrite(qkv.to(DEV), Hq=Hq, Hkv=Hkv, D=D, positions=pos.to(DEV), slots=slots.to(DEV), k_cache=kcg,
+                             v_cache=vcg, cos=cos.to(DEV), sin=sin.to(DEV), k_scale=two.to(DEV), v_scale=two.to(DEV), amax=am)
+    torch.cuda.synchronize()
+    assert (am.cpu() - am_ref).abs().max() <= 2e-2 * am_ref.max()
+    new = (am.cpu()[:1] / 448).clone()
+    want = kc.clone()
+    ops.kv_rescale(want, slots, 2.0, new)
+    ops.kv_rescale(kcg, slots.to(DEV), 2.0, new.to(DEV))
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    a, b = ref.from_e4m3(kcg.cpu()), ref.from_e4m3(want)
+    assert ((a - b).abs() <= 0.13 * b.abs() + 1e-6).all() and (kcg.cpu() != want).float().mean() < 0.02
+    live = slots[slots >= 0]
+    assert ref.from_e4m3(want).view(nb * bs, -1)[live].abs().max() > 200        # the rows now use the e4m3 range
+
+
 def _cache(nb, bs, Hkv, D, fp8):
     dt = torch.uint8 if fp8 else torch.bfloat16
     return torch.zeros(nb, bs, Hkv, D, dtype=dt), torch.zeros(nb, bs, Hkv, D, dtype=dt)
