@@ -167,6 +167,9 @@ def main() -> int:
                     help="also measure p50 time to first token of single requests of --isl tokens, cold and prefix-warm")
     ap.add_argument("--ep-dispatch", default="allreduce", choices=["allreduce", "a2a"],
                     help="--parallelism ep: masked-local experts + all-reduce, or token dispatch over NVLink peer memory")
+    ap.add_argument("--speculative", default="off", choices=["off", "mtp"],
+                    help="mtp: after the headline run, also report what a verify step (K = 1..4) and the "
+                         "draft proposal cost next to a decode step at C = 8 (1 GPU; benchmarks/spec_cost.py)")
     ap.add_argument("--parallelism", default="tp", choices=["dp", "tp", "ep"],
                     help="N>1: tp = one engine sharded over N GPUs, C requests in total (strong scaling, the "
                          "configuration's TP sweep); dp = one engine replica per GPU, each serving C requests")
@@ -375,6 +378,13 @@ def main() -> int:
     }
     if ttft is not None:
         line["ttft"] = ttft
+    if args.speculative == "mtp" and world == 1:
+        del eng
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        from benchmarks.spec_cost import run as spec_cost
+        line["speculative_cost"] = spec_cost(args.model, dev, 8, steps=32, isl=args.isl, ctx_len=ctx_len)
     if args.layers:
         line["invalid"] = "debug run with fewer layers"
     if rank == 0:

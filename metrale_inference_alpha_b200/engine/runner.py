@@ -219,12 +219,14 @@ class ModelRunner:
         self.h2d_bytes += st.bytes_per_copy
         return True
 
-    def _stage(self, plan: StepPlan, pad_seqs: int = 0, logits_all_verify: bool = True) -> ForwardBatch:
+    def _stage(self, plan: StepPlan, pad_seqs: int = 0, logits_all_verify: bool = True, pad_q: int = 1) -> ForwardBatch:
+        """`pad_seqs`: pad with null sequences (rows that write nothing) up to this many, each of
+        `pad_q` rows, so that a CUDA-graph rung always sees the same layout."""
         st, bs = self.stage, self.block_size
         self._fast_sig, self._fast_sig_next = None, None      # any full staging invalidates the fast path
         n_rows = sum(len(i.tokens) for i in plan.items)
         n_seqs = max(len(plan.items), pad_seqs)
-        pad_rows = max(0, pad_seqs - len(plan.items))
+        pad_rows = max(0, pad_seqs - len(plan.items)) * pad_q
         if pad_seqs:
             st.begin(n_rows + pad_rows, n_seqs)               # graph rung: exact, fixed layout
         else:
@@ -258,13 +260,15 @@ class ModelRunner:
             max_q, max_ctx = max(max_q, n), max(max_ctx, p0 + n)
         S = len(plan.items)
         while S < pad_seqs:                                   # null rows up to the graph rung
-            tokens[row], pos[row], slots[row] = 0, 0, -1
-            qs[S], ql[S], ctx[S], state[S] = row, 1, 1, 0
+            tokens[row:row + pad_q], slots[row:row + pad_q] = 0, -1
+            pos[row:row + pad_q] = np.arange(pad_q, dtype=np.int32)
+            qs[S], ql[S], ctx[S], state[S] = row, pad_q, pad_q, 0
             bt2[S, 0] = 0
-            lrows[nl] = row
-            nl += 1
-            row += 1
+            lrows[nl:nl + pad_q] = np.arange(row, row + pad_q)
+            nl += pad_q
+            row += pad_q
             S += 1
+            max_q = max(max_q, pad_q)
         st.upload()
         self.h2d_bytes += st.bytes_per_copy
         dv = lambda name, n: st.view(st.dev, name, n)
@@ -500,6 +504,37 @@ class ModelRunner:
         self.last_hidden = hidden
         return rung
 
+    def _verify_graph(self, plan: StepPlan, K: int) -> None:
+        """Replay (capturing on first use) the CUDA graph of a speculative verify step in which
+        every sequence feeds K drafts: one forward over rung x (K + 1) rows, argmax of every row
+        (role of the reference's batched verify with one graph per key,
+        ``crates/model-engine/src/model/trait_impl/verify_e.rs:123``). With recurrent layers the
+        graph also holds the step's write-on-accept stash (static buffers, refreshed by every
+        replay)."""
+        rung = self._rung(len(plan.items))
+        key = ("verify", rung, K)
+        rows = rung * (K + 1)
+        if key not in self.graphs:
+            from .batch import SpecStash
+            null = self._stage(StepPlan("verify", []), pad_seqs=rung, pad_q=K + 1)
+            null.max_ctx, null.max_q_len = self.sched.max_model_len, K + 1
+            if self.pool is not None:
+                null.spec_stash = SpecStash(null)
+            self._forward_select(null, True, False, rows)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            count0 = ops.launch_count
+            with torch.cuda.graph(g):
+                self._forward_select(null, True, False, rows)
+            self.graphs[key] = (g, ops.launch_count - count0, self.last_hidden, null.spec_stash)
+        self._stage(plan, pad_seqs=rung, pad_q=K + 1)
+        g, launches, hidden, stash = self.graphs[key]
+        g.replay()
+        ops.launch_count += launches
+        self.graph_replays += 1
+        self.last_hidden = hidden
+        self.pending_stash = stash
+
     # ------------------------------------------------------------------ pipelined decode
     def can_pipeline(self, plan: StepPlan) -> bool:
         """Plain greedy graph-replayed decode: the only step kind that is launched without waiting."""
@@ -576,8 +611,14 @@ class ModelRunner:
             return self._execute_host_logits(plan, t0)
         is_plain_decode = plan.kind == "decode" and all(len(i.tokens) == 1 for i in plan.items)
         uses_adapter = self.decoder.lora is not None and any(i.seq.req.adapter for i in plan.items)
+        K = plan.items[0].verify if plan.items else 0
+        uniform_verify = (plan.kind == "verify" and K > 0 and greedy and not want_lp
+                          and all(i.verify == K and len(i.tokens) == K + 1 and i.sample for i in plan.items)
+                          and self._rung(len(plan.items)) * (K + 1) <= self.stage.max_tokens)
         if is_plain_decode and self.graphs_ready() and not uses_adapter:
             self._decode_graph(plan, greedy, want_lp)
+        elif uniform_verify and self.graphs_ready() and not uses_adapter:
+            self._verify_graph(plan, K)
         else:
             batch = self._stage_with_adapters(plan)     # steps with adapter rows run eagerly
             self._forward_select(batch, greedy, want_lp, n_sample_rows)
@@ -628,6 +669,86 @@ class ModelRunner:
             return [[] for _ in plan.items]
         from ..speculative.mtp import mtp_propose
         return mtp_propose(self, plan, result, accepted, k)
+
+    def propose_graphed(self, seqs, first_tok: List[int], hid_rows: List[int], hidden_all: torch.Tensor,
+                        k: int) -> Optional[List[List[int]]]:
+        """All k draft steps of the MTP head for every sequence as ONE CUDA-graph replay per
+        (batch rung, k): one metadata upload (first token, position, block table, hidden row of
+        each sequence), one gather of the target hidden rows, the graph, one read-back of
+        [rung, k] token ids. Inside the graph, step j derives its positions, KV slots and context
+        lengths from step 0's on the device, and feeds its own argmax and hidden state to step
+        j + 1 (role of the reference's drafter graphs, one per key,
+        ``crates/server/src/scheduler/mtp_step.rs``). Returns None when some sequence has no
+        KV block for its last draft position (the caller then drafts step by step)."""
+        bs, n = self.block_size, len(seqs)
+        for s in seqs:
+            if (len(s.tokens) - 1 + k - 1) // bs >= len(s.blocks):
+                return None
+        rung = self._rung(n)
+        S, mb, H, dev = self.sched.max_num_seqs, self.max_blocks, self.cfg.hidden_size, self.device
+        if getattr(self, "_mtp_stage", None) is None:
+            tot = 4 * S + S * mb
+            host = torch.zeros(tot, dtype=torch.int32, pin_memory=True)
+            self._mtp_stage = dict(host=host, np=host.numpy(), dev=torch.zeros(tot, dtype=torch.int32, device=dev),
+                                   hidden=torch.zeros(S, H, dtype=torch.bfloat16, device=dev),
+                                   out=torch.zeros(S, 8, dtype=torch.int32, device=dev),
+                                   out_host=torch.zeros(S, 8, dtype=torch.int32, pin_memory=True),
+                                   ev=torch.cuda.Event())
+        st = self._mtp_stage
+        assert k <= st["out"].shape[1]
+        d = st["dev"]
+        tok_d, pos_d, val_d, row_d, bt_d = d[0:S], d[S:2 * S], d[2 * S:3 * S], d[3 * S:4 * S], d[4 * S:].view(S, mb)
+        key = ("mtp", rung, k)
+        if key not in self.graphs:
+            ar32 = torch.arange(rung, dtype=torch.int32, device=dev)
+            ar64 = torch.arange(rung, dtype=torch.int64, device=dev)
+            ones = torch.ones(rung, dtype=torch.int32, device=dev)
+            zeros = torch.zeros(rung, dtype=torch.int32, device=dev)
+
+            def body():
+                toks, hid = tok_d[:rung], st["hidden"][:rung]
+                valid = val_d[:rung] > 0
+                for j in range(k):
+                    pos = pos_d[:rung] + j
+                    blk = bt_d[:rung].gather(1, (pos // bs).long()[:, None]).squeeze(1).long()
+                    slot = torch.where(valid, blk * bs + (pos % bs).long(), torch.full_like(blk, -1))
+                    b = ForwardBatch(token_ids=toks, positions=pos, slot_mapping=slot, q_start=ar32, q_len=ones,
+                                     ctx_len=torch.where(valid, pos + 1, ones), block_table=bt_d[:rung],
+                                     logit_rows=ar64, max_q_len=1, max_ctx=self.sched.max_model_len,
+                                     state_slots=zeros, num_tokens=rung, num_seqs=rung)
+                    logits, hid = self.decoder.mtp_forward(toks, hid, b, self.caches)
+                    self.tp.end_forward()
+                    toks = ops.argmax(logits)
+                    st["out"][:rung, j].copy_(toks)
+            d.zero_()                                      # null rows for the warm-up and the capture
+            body()
+            torch.cuda.synchronize(dev)
+            g = torch.cuda.CUDAGraph()
+            c0 = ops.launch_count
+            with torch.cuda.graph(g):
+                body()
+            self.graphs[key] = (g, ops.launch_count - c0, None, None)
+        st["ev"].synchronize()
+        a = st["np"]
+        a[0:rung], a[S:S + rung], a[2 * S:2 * S + rung], a[3 * S:3 * S + rung] = 0, 0, 0, 0
+        a[0:n] = first_tok
+        a[S:S + n] = [len(s.tokens) - 1 for s in seqs]
+        a[2 * S:2 * S + n] = 1
+        a[3 * S:3 * S + n] = hid_rows
+        bt = a[4 * S:].reshape(S, mb)
+        for i, s in enumerate(seqs):
+            bt[i, :len(s.blocks)] = s.blocks
+        used = 4 * S + rung * mb
+        d[:used].copy_(st["host"][:used], non_blocking=True)
+        st["ev"].record()
+        torch.index_select(hidden_all, 0, row_d[:n].long(), out=st["hidden"][:n])
+        g, launches, _, _ = self.graphs[key]
+        g.replay()
+        ops.launch_count += launches + 1
+        self.graph_replays += 1
+        st["out_host"][:rung].copy_(st["out"][:rung], non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        return st["out_host"][:n, :k].tolist()
 
     # ------------------------------------------------------------------ helpers
     def kv_bytes(self) -> int:

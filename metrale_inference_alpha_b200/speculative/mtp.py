@@ -37,6 +37,12 @@ def mtp_propose(runner, plan, result, accepted: List[int], k: int) -> List[List[
     drafts = {s.seq_id: [] for s in seqs}
     if not seqs:
         return [[] for _ in plan.items]
+    if dev.type == "cuda" and runner.graphs_ready() and getattr(runner, "graph_propose", True):
+        got = runner.propose_graphed(seqs, first_tok, hid_rows, hidden_all, k)
+        if got is not None:
+            for s, d in zip(seqs, got):
+                drafts[s.seq_id] = d
+            return _collect(plan, drafts)
     hidden = hidden_all.index_select(0, torch.tensor(hid_rows, device=dev))
     toks = torch.tensor(first_tok, dtype=torch.int32, device=dev)
     for j in range(k):

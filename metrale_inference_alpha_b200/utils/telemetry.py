@@ -113,12 +113,13 @@ class Telemetry:
                 lines.append(f"metrale_{k} {v:g}")
         for k, h in sorted(self.hist.items()):
             acc = 0
-            for b, n in zip(_BUCKETS, h):
-                acc += n
-                lines.append(f'metrale_{k}_ms_bucket{{le="{b}"}} {acc}')
-            lines.append(f'metrale_{k}_ms_bucket{{le="+Inf"}} {acc + h[-1]}')
-            lines.append(f"metrale_{k}_ms_sum {self.hist_sum[k]:g}")
-            lines.append(f"metrale_{k}_ms_count {acc + h[-1]}")
+            name = k if k.endswith("_us") else k + "_ms"     # microsecond series carry their own unit suffix
+            for b, cnt in zip(_BUCKETS, h):
+                acc += cnt
+                lines.append(f'metrale_{name}_bucket{{le="{b}"}} {acc}')
+            lines.append(f'metrale_{name}_bucket{{le="+Inf"}} {acc + h[-1]}')
+            lines.append(f"metrale_{name}_sum {self.hist_sum[k]:g}")
+            lines.append(f"metrale_{name}_count {acc + h[-1]}")
         return "\n".join(lines) + "\n"
 
 

@@ -36,6 +36,27 @@ def test_speculative_modes_are_lossless_on_gpu(mode):
     assert eng.spec_stats.drafted > 0
 
 
+@pytest.mark.gpu
+def test_graphed_verify_and_mtp_propose_equal_the_eager_steps():
+    """The speculative loop on a GPU runs as CUDA graphs: one graph per (rung, K) for the verify
+    forward and one per (rung, k) for all k draft steps of the MTP head. Outputs, draft counts and
+    acceptance must equal the step-by-step (eager) drafting and plain decoding."""
+    base, _ = _run("cuda")
+    cfg = preset("tiny-dense", mtp_layers=1)
+    res = {}
+    for graphed in (False, True):
+        eng = LLMEngine(EngineArgs(model=cfg, device="cuda", max_num_seqs=4, max_model_len=256, mtp_gate=False,
+                                   speculative="mtp", num_drafts=3))
+        eng.runner.graph_propose = graphed
+        outs = eng.generate(PROMPTS, SamplingParams(max_tokens=24))
+        res[graphed] = ([o.output_ids for o in outs], eng.spec_stats.drafted, eng.spec_stats.accepted)
+        keys = [k for k in eng.runner.graphs if isinstance(k, tuple) and k[0] in ("mtp", "verify")]
+        assert any(k[0] == "verify" and k[2] == 3 for k in keys)
+        assert any(k[0] == "mtp" for k in keys) == graphed
+    assert res[True][0] == base == res[False][0]
+    assert res[True][1:] == res[False][1:]
+
+
 def test_grammar_masks_follow_draft_rows_and_rewind_to_the_accepted_prefix():
     """Speculative verify rows with a grammar: row j is masked from the matcher state after drafts
     1..j, and the matcher is rewound to what was accepted. Output must be a legal prefix of the
