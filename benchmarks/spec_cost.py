@@ -76,6 +76,8 @@ def run(model: str, device: str, C: int = 8, ks=(1, 2, 3, 4), steps: int = 32, i
         rows.append({"K": K, "step_ms": round(ms, 3), "verify_ms": round(acc["verify"] / steps * 1e3, 3),
                      "propose_ms": round(acc["propose"] / steps * 1e3, 3),
                      "verify_over_decode": round(acc["verify"] / steps * 1e3 / out["decode_ms"], 3),
+                     # tokens a sequence must commit per speculative step (accepted drafts + 1) to match plain decode
+                     "break_even_accept_len": round(ms / out["decode_ms"], 3),
                      "tokens_per_step": round(toks, 2), "graph_replays_per_step": (runner.graph_replays - l0) / steps})
     runner.execute, runner.propose = real_execute, real_propose
     out["decode_ms"] = round(out["decode_ms"], 3)

@@ -55,6 +55,7 @@ class EngineArgs:
     fused_collectives: bool = False                    # tensor parallel: GEMM + all-reduce in one kernel over NVLink peer memory
                                                        # instead of NCCL after the GEMM (measured slower so far: off by default)
     ep_dispatch: str = "allreduce"                     # expert parallelism: allreduce (masked-local experts) | a2a (token dispatch over peer memory)
+    activation_precision: str = "native"               # native (W4A4 / W8A8) | a16 (bf16 activations, weight-only quantisation)
     static_act_scales: bool = True                     # NVFP4: calibrate down-projection input scales at start-up
     preempt_mode: str = "recompute"                    # recompute | swap (KV + state to host memory / swap files)
     swap_space_bytes: int = 8 << 30
@@ -114,6 +115,8 @@ class LLMEngine:
         self.cfg: ModelConfig = cfg
         self.fault = FaultLatch()
         t0 = time.time()
+        from .. import ops as _ops
+        _ops.set_activation_precision(args.activation_precision)
         self.weights = load_weights(cfg, source, device=args.device, tp_rank=self.tp.rank,
                                     tp_size=self.tp.size if args.ep_size == 1 or args.tp_size > 1 else 1,
                                     ep_rank=getattr(self.tp, "ep_rank", 0), ep_size=args.ep_size, seed=args.seed)
@@ -143,7 +146,8 @@ class LLMEngine:
             self.tp.ep = EpAllToAll(self.tp.rank, self.tp.size, self.device, cfg.hidden_size, per_rank,
                                     cfg.experts_per_token)
         self.calibrated_layers = 0
-        if args.static_act_scales and cfg.weight_format == "nvfp4" and self.device.type == "cuda":
+        if (args.static_act_scales and cfg.weight_format == "nvfp4" and self.device.type == "cuda"
+                and args.activation_precision == "native"):
             self.calibrated_layers = self.runner.calibrate_static_scales()
         needs_snap = self.runner.pool is not None
         self.prefix = None

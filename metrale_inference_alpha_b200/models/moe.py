@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..ops import ACT_FOR_WEIGHT, moe as moe_ops
+from ..ops import NATIVE_ACT_FOR_WEIGHT as ACT_FOR_WEIGHT, moe as moe_ops   # experts keep the weight's own activation format
 
 
 def moe_block(dec, x, lw):

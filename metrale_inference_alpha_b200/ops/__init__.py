@@ -20,7 +20,9 @@ import torch
 from . import _native, reference as ref
 
 KIND = {"bf16": 0, "fp8_row": 1, "nvfp4": 2, "fp8_block": 3}
-ACT_FOR_WEIGHT = {"bf16": "bf16", "fp8_row": "fp8_row", "fp8_block": "fp8_g128", "nvfp4": "nvfp4"}
+NATIVE_ACT_FOR_WEIGHT = {"bf16": "bf16", "fp8_row": "fp8_row", "fp8_block": "fp8_g128", "nvfp4": "nvfp4"}
+# the activation encoding each weight format is fed with; `set_activation_precision` rewrites it in place
+ACT_FOR_WEIGHT = dict(NATIVE_ACT_FOR_WEIGHT)
 IN_COPY, IN_RMSNORM, IN_SILU_MUL, IN_RELU2, IN_SIGMOID_GATE, IN_GATED_RMSNORM = range(6)
 OUT_MODE = {"bf16": 0, "fp8_row": 1, "fp8_g128": 2, "nvfp4": 3}
 
@@ -342,6 +344,61 @@ def quantize_act(x: torch.Tensor, fmt: str, static_scale: float = 0.0) -> Act:
 
 
 # ----------------------------------------------------------------------------- linear
+def set_activation_precision(mode: str) -> None:
+    """"native": activations are quantised to the weight's own format (W4A4 / W8A8, the tensor-core
+    block-scaled GEMMs). "a16": activations stay bf16 and only the weights are low precision
+    (W4A16 / W8A16, `_linear_a16`); the accuracy option for checkpoints whose activations have
+    outliers that 4- or 8-bit rows cannot hold. Process-wide. Expert GEMMs keep the native format."""
+    assert mode in ("native", "a16"), mode
+    for k, v in NATIVE_ACT_FOR_WEIGHT.items():
+        ACT_FOR_WEIGHT[k] = v if mode == "native" else "bf16"
+
+
+_A16_GEMV_MAX_M = 32           # up to this many rows: passes of the streaming kernel, 8 rows each
+_A16_WS_BYTES = 256 << 20      # bf16 staging band for the tensor-core path
+
+
+def _linear_a16(act: Act, w: QuantWeight, residual, swiglu: bool, out_f32: bool, out):
+    """bf16 activations x quantised weight. M <= 32: the streaming kernel reads the packed weight
+    once per 8 rows. Larger M: row bands of the weight are widened to bf16 (at most 256 MB at a
+    time) and go through the bf16 tensor-core GEMM, one band per launch pair."""
+    M, N, K, dev = act.M, w.N, w.K, act.data.device
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty(M, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
+    L = _native.lib()
+    a = _native.A16Args()
+    a.kind, a.N, a.K, a.ldx, a.swiglu = KIND[w.fmt], N, K, act.data.stride(0), int(swiglu)
+    a.W, a.scale, a.row_gscale, a.gscale = _ptr(w.data), _ptr(w.scale), _ptr(w.row_gscale), float(w.gscale)
+    a.scale_ld = w.scale.stride(0) if w.fmt == "fp8_block" else 0
+    if M <= _A16_GEMV_MAX_M:
+        a.ldo = out.stride(0)
+        for m0 in range(0, M, 8):
+            a.M = min(8, M - m0)
+            a.x = act.data.data_ptr() + m0 * act.data.stride(0) * 2
+            a.residual = None if residual is None else residual.data_ptr() + m0 * residual.stride(0) * 2
+            assert residual is None or residual.stride(0) == out.stride(0)
+            o = out.data_ptr() + m0 * out.stride(0) * out.element_size()
+            a.out, a.out_f32 = (None, o) if out_f32 else (o, None)
+            _native.check(L.mb_a16_gemv(C.byref(a), _stream()), f"a16_gemv[{w.fmt} M={M} N={N} K={K}]")
+            _count()
+        return out
+    band = max(256, min(N, (_A16_WS_BYTES // (2 * K)) // 256 * 256))
+    rt = runtime(dev)
+    if getattr(rt, "a16_ws", None) is None or rt.a16_ws.numel() < band * K:
+        rt.a16_ws = torch.empty(band * K, dtype=torch.bfloat16, device=dev)
+    for n_lo in range(0, N, band):
+        rows = min(band, N - n_lo)
+        wb = rt.a16_ws[:rows * K].view(rows, K)
+        a.n_lo, a.rows, a.out = n_lo, rows, _ptr(wb)
+        _native.check(L.mb_a16_dequant(C.byref(a), _stream()), f"a16_dequant[{w.fmt} N={N} K={K}]")
+        _count()
+        lo, hi = (n_lo // 2, (n_lo + rows) // 2) if swiglu else (n_lo, n_lo + rows)
+        linear(act, QuantWeight("bf16", rows, K, wb), residual=None if residual is None else residual[:, lo:hi],
+               swiglu=swiglu, out_f32=out_f32, out=out[:, lo:hi])
+    return out
+
+
 def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
            swiglu: bool = False, out_f32: bool = False, out: Optional[torch.Tensor] = None,
            force_tn: int = 0, force_splits: int = 0, one_tile_per_cta: bool = False, decode_tile_order: bool = False,
@@ -355,8 +412,13 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
     its partial tiles over distributed shared memory instead of the L2-resident workspace (all
     three for A/B comparisons and tests)."""
     assert act.K == w.K, (act.K, w.K)
-    assert act.fmt == ACT_FOR_WEIGHT[w.fmt], (act.fmt, w.fmt)
+    a16 = act.fmt == "bf16" and w.fmt != "bf16"
+    assert a16 or act.fmt == NATIVE_ACT_FOR_WEIGHT[w.fmt], (act.fmt, w.fmt)
     M, N = act.M, w.N
+    if a16 and act.data.is_cuda:
+        assert grouped is None, "expert GEMMs take activations in the weight's own format"
+        y = _linear_a16(act, w, residual, swiglu, out_f32 or quant_out > 0.0, out)
+        return quantize_act(y, "nvfp4", static_scale=quant_out) if quant_out > 0.0 else y
     if quant_out > 0.0:
         assert swiglu and residual is None and not out_f32 and grouped is None
         fused = (act.data.is_cuda and M <= 128 and (N + 127) // 128 > runtime(act.data.device).sm_count

@@ -45,6 +45,16 @@ class RowArgs(C.Structure):
     ]
 
 
+class A16Args(C.Structure):
+    _fields_ = [
+        ("kind", c_int), ("M", c_int), ("N", c_int), ("K", c_int), ("ldx", c_int), ("ldo", c_int),
+        ("swiglu", c_int), ("scale_ld", c_int),
+        ("W", c_void_p), ("scale", c_void_p), ("row_gscale", c_void_p), ("x", c_void_p),
+        ("residual", c_void_p), ("out", c_void_p), ("out_f32", c_void_p),
+        ("gscale", c_float), ("n_lo", c_int), ("rows", c_int),
+    ]
+
+
 class RopeKvArgs(C.Structure):
     _fields_ = [
         ("M", c_int), ("Hq", c_int), ("Hkv", c_int), ("D", c_int), ("rot", c_int),
@@ -108,6 +118,9 @@ def lib():
     P = C.POINTER
     L.mb_gemm.argtypes = [P(GemmArgs), c_void_p]
     L.mb_gemm.restype = c_int
+    for fn in (L.mb_a16_gemv, L.mb_a16_dequant):
+        fn.argtypes = [P(A16Args), c_void_p]
+        fn.restype = c_int
     L.mb_gemm_counter_bytes.argtypes = []
     L.mb_gemm_counter_bytes.restype = c_size_t
     L.mb_row_op.argtypes = [P(RowArgs), c_void_p]

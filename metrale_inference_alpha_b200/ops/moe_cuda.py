@@ -7,7 +7,7 @@ import ctypes as C
 
 import torch
 
-from . import Act, ACT_FOR_WEIGHT, IN_RELU2, IN_SILU_MUL, _count, _native, _ptr, _stream, linear, row_op
+from . import Act, NATIVE_ACT_FOR_WEIGHT as ACT_FOR_WEIGHT, IN_RELU2, IN_SILU_MUL, _count, _native, _ptr, _stream, linear, row_op
 
 c = C
 _native.register_optional("mb_moe_route", [c.c_void_p, c.c_longlong, c.c_int, c.c_int, c.c_int, c.c_int, c.c_void_p,
