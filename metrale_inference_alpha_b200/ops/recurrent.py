@@ -54,6 +54,11 @@ def gdn_recurrence(conv_out, ba, A_log, dt_bias, state, batch, *, k_heads, v_hea
     (b | a). Applies l2-norm to q and k per head, computes decay/beta, runs the delta rule.
     state [slots, v_heads, k_dim, v_dim] fp32. Returns fp32 [T, v_heads * v_dim]."""
     if conv_out.is_cuda and _native.available() and hasattr(_native.lib(), "mb_gdn_recurrence"):
+        if (write_out and k_dim == 128 and v_dim == 128 and getattr(batch, "max_q_len", 1) >= _GDN_CHUNK_MIN_TOKENS
+                and hasattr(_native.lib(), "mb_gdn_chunked")):
+            y = _gdn_chunked_cuda(conv_out, ba, A_log, dt_bias, state, batch, k_heads, v_heads, write_state)
+            if y is not None:
+                return y
         return _gdn_cuda(conv_out, ba, A_log, dt_bias, state, batch, k_heads, v_heads, k_dim, v_dim, write_state, write_out)
     T = conv_out.shape[0]
     QK, V = k_heads * k_dim, v_heads * v_dim
@@ -151,6 +156,39 @@ def _mamba_ssd_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups,
         _ptr(_status(dev)), _stream())
     _native.check(rc, "mamba2_ssd")
     _count(3)
+    return out
+
+
+_native.register_optional("mb_gdn_chunked", [_c.c_void_p] * 6 + [_c.c_int] * 4 + [_c.c_void_p] * 4 + [_c.c_int] * 4 +
+                          [_c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p])
+# prefill chunks at least this long take the chunked gated delta rule
+_GDN_CHUNK_MIN_TOKENS = 64
+_gdn_ws = {}
+
+
+def _gdn_chunked_cuda(conv_out, ba, A_log, dt_bias, state, batch, k_heads, v_heads, write_state):
+    """Chunked delta rule (csrc/gdn_chunked.cu); None when the workspace would be unreasonably large."""
+    L = _native.lib()
+    L.mb_gdn_chunked_ws_bytes.restype = _c.c_size_t
+    L.mb_gdn_chunked_ws_bytes.argtypes = [_c.c_int, _c.c_int, _c.c_int]
+    S = batch.q_len.numel()
+    need = int(L.mb_gdn_chunked_ws_bytes(S, int(batch.max_q_len), v_heads))
+    if need > _SSD_WS_MAX:
+        return None
+    dev = conv_out.device
+    ws = _gdn_ws.get(dev)
+    if ws is None or ws.numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        ws = _gdn_ws[dev] = torch.empty(int(need * 1.25), dtype=torch.uint8, device=dev)
+    T = conv_out.shape[0]
+    out = torch.empty(T, v_heads * 128, dtype=torch.float32, device=dev)
+    rc = L.mb_gdn_chunked(
+        _ptr(conv_out), _ptr(ba), _ptr(A_log), _ptr(dt_bias), _ptr(state), _ptr(out), k_heads, v_heads, 128, 128,
+        _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions), _ptr(batch.state_slots), S, state.shape[0],
+        int(batch.max_q_len), int(write_state), _ptr(ws), ws.numel(), _ptr(_status(dev)), _stream())
+    _native.check(rc, "gdn_chunked")
+    _count(2)
     return out
 
 

@@ -118,6 +118,48 @@ def test_mamba2_chunked_scan_matches_the_sequential_kernel_and_the_fp32_oracle(l
         _close(st_chk, st_cpu, 5e-3, 5e-3)
 
 
+@pytest.mark.parametrize("lens", [[64], [200, 1, 77], [8192], [130, 64, 5, 300]])
+def test_gdn_chunked_prefill_matches_the_sequential_kernel_and_the_fp32_oracle(lens):
+    """Chunked gated delta rule (WY form, TF32 tensor-core products) against the sequential kernel
+    on the same inputs: outputs and the hand-off state; the shortest case also against the fp32
+    CPU reference. Sequences mix fresh starts with continuations from a stored state, and the
+    decay / beta gates cover both strong forgetting and near-1 retention."""
+    g = torch.Generator().manual_seed(14)
+    kh, vh, dk = 2, 4, 128
+    QK, V = kh * dk, vh * dk
+    seqs = []
+    for i, n in enumerate(lens):
+        seqs.append(dict(tokens=[1] * n, start_pos=0 if i % 2 == 0 else 7, blocks=list(range(1, 2 + (n + 7) // 16)), state_slot=i + 1))
+    b = ForwardBatch.build(seqs, 16, device=DEV)
+    T = sum(lens)
+    conv = torch.randn(T, 2 * QK + V, generator=g).to(DEV)
+    ba = (torch.randn(T, 2 * vh, generator=g) * 1.5).to(DEV)
+    A_log = (torch.randn(vh, generator=g) * 0.5).to(DEV)
+    dtb = (torch.randn(vh, generator=g) * 0.3).to(DEV)
+    s0 = (torch.randn(len(lens) + 1, vh, dk, dk, generator=g) * 0.1).to(DEV)
+    kw = dict(k_heads=kh, v_heads=vh, k_dim=dk, v_dim=dk)
+    st_seq, st_chk = s0.clone(), s0.clone()
+    rops._GDN_CHUNK_MIN_TOKENS, keep = 1 << 30, rops._GDN_CHUNK_MIN_TOKENS
+    want = rops.gdn_recurrence(conv, ba, A_log, dtb, st_seq, b, **kw)           # sequential kernel
+    rops._GDN_CHUNK_MIN_TOKENS = 1
+    n0 = ops.launch_count
+    got = rops.gdn_recurrence(conv, ba, A_log, dtb, st_chk, b, **kw)            # chunked kernels
+    assert ops.launch_count - n0 == 2
+    rops._GDN_CHUNK_MIN_TOKENS = keep
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    scale = want.abs().max().item()
+    assert (got - want).abs().max().item() <= 5e-3 * max(1.0, scale), ((got - want).abs().max().item(), scale)
+    assert (st_chk - st_seq).abs().max().item() <= 5e-3 * max(1.0, st_seq.abs().max().item())
+    assert torch.equal(st_chk[0], s0[0])                                       # untouched slot
+    if T <= 64:
+        st_cpu = s0.cpu().clone()
+        ref_y = rops.gdn_recurrence(conv.cpu(), ba.cpu(), A_log.cpu(), dtb.cpu(), st_cpu,
+                                    ForwardBatch.build(seqs, 16, device="cpu"), **kw)
+        _close(got, ref_y, 5e-3, 5e-3 * max(1.0, scale))
+        _close(st_chk, st_cpu, 5e-3, 5e-3)
+
+
 def _commit_batch(b, n_rows):
     import dataclasses
     return dataclasses.replace(b, q_len=torch.tensor(n_rows, dtype=torch.int32, device=b.q_len.device))
