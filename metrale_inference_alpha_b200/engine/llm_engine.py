@@ -44,8 +44,10 @@ class EngineArgs:
     scheduler: str = "fifo"
     tbt_deadline_ms: float = 100.0
     use_cuda_graphs: bool = True
-    speculative: str = "none"                          # none | mtp | ngram
+    speculative: str = "none"                          # none | mtp | ngram | dflash
     num_drafts: int = 3
+    dflash_layers: int = 2                             # block drafter depth (random weights unless a drafter checkpoint is attached)
+    dflash_gamma: int = 0                              # block drafter: drafts per proposal; 0 = the width policy (4 at C >= 2; 5 / 8 at C = 1)
     mtp_gate: bool = True
     kv_poison: bool = False
     tp_size: int = 1
@@ -166,6 +168,13 @@ class LLMEngine:
         if self.spec_mode == "mtp" and self.weights.mtp is None:
             self.spec_mode = "none"
         self.ladder = KLadder(max_k=args.num_drafts)
+        self.dflash_rung = None
+        if self.spec_mode == "dflash":
+            from ..speculative.dflash import DflashConfig
+            from ..speculative.ladder import DflashRung
+            self.dflash_rung = DflashRung()
+            self.runner.enable_dflash(DflashConfig(num_layers=args.dflash_layers,
+                                                   gamma=max(args.dflash_gamma, self.dflash_rung.wide)))
         self.gate = MtpGate(enabled=(self.spec_mode != "none" and args.mtp_gate))
         self.ngram = NgramProposer()
         self.spec_stats = SpecStats()
@@ -290,9 +299,13 @@ class LLMEngine:
         self.runner.commit_recurrent(plan)                 # verify steps on recurrent models: write-on-accept
         if speculate:
             k = self.ladder.drafts_for(len(plan.items))
+            if self.dflash_rung is not None:
+                if plan.kind == "verify" and len(plan.items) == 1:
+                    self.dflash_rung.observe(getattr(plan.items[0].seq, "last_accept", 0) > 0)
+                k = self.args.dflash_gamma or self.dflash_rung.gamma(len(plan.items))
             if k > 0:
                 accepted = [len(it.seq.tokens) - before[it.seq.seq_id] for it in plan.items]
-                if self.spec_mode == "mtp":
+                if self.spec_mode in ("mtp", "dflash"):
                     drafts = self.runner.propose(plan, result, accepted, k)
                 else:
                     drafts = [self.ngram.propose(it.seq.tokens, k) if not it.seq.is_finished() else []

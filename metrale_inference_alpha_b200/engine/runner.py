@@ -138,6 +138,7 @@ class ModelRunner:
             self.pool = StatePool(shapes, slots, num_snapshots, device)
         self.caches = LayerCaches(cfg, kv=self.kv, state=self.pool, mtp_kv=self.mtp_kv)
         self.decoder = Decoder(cfg, weights, self.tp, device)
+        self.dflash = None
         # FP8 KV scales: the checkpoint's (three key spellings, weights/kv_scales.py), else online
         # calibration over the first tokens when asked for, else 1.0
         self.kv_scales_loaded = 0
@@ -662,11 +663,28 @@ class ModelRunner:
         return StepResult(toks, lps, hidden=hidden, device_ms=(time.perf_counter() - t0) * 1e3)
 
     # ------------------------------------------------------------------ MTP drafting
+    def enable_dflash(self, dc, weights=None, seed: int = 1) -> None:
+        """Attach a block drafter (speculative/dflash.py): from now on every target forward also
+        writes the drafter's context K/V, and `propose` drafts with it."""
+        from ..speculative.dflash import DflashDrafter
+        assert not self.graphs, "attach the drafter before the first decode graph is captured"
+        self.dflash = DflashDrafter(self, dc, weights, seed)
+        self.decoder.side_head = self.dflash
+
     def propose(self, plan: StepPlan, result: StepResult, accepted: List[int], k: int) -> List[List[int]]:
         """Draft k tokens per sequence with the MTP head, autoregressively: step j feeds the
         previous token and the previous hidden state (target hidden for j = 0)."""
-        if self.w.mtp is None or k <= 0:
+        if k <= 0 or (self.w.mtp is None and self.dflash is None):
             return [[] for _ in plan.items]
+        if self.dflash is not None:
+            live = [(i, it.seq) for i, it in enumerate(plan.items)
+                    if it.sample and accepted[i] > 0 and not it.seq.is_finished()]
+            out = [[] for _ in plan.items]
+            if live:
+                for (i, _), d in zip(live, self.dflash.propose([s for _, s in live], k)):
+                    out[i] = d
+            self.tp.end_forward()
+            return out
         from ..speculative.mtp import mtp_propose
         return mtp_propose(self, plan, result, accepted, k)
 

@@ -82,6 +82,7 @@ class Decoder:
         self.kv_cal = None                 # cache.fp8_calibration.Fp8KvCalibration while FP8 KV scales are being calibrated
         self.lora = None                   # lora.LoraManager when adapters are served
         self.calib = None                  # dict while calibrating static activation scales (engine/runner.py)
+        self.side_head = None              # speculative.dflash.DflashDrafter: sees chosen layers' hidden states of every forward
 
     # ------------------------------------------------------------------ helpers
     def _norm_act(self, x, w, fmt: str, also_bf16: bool = False, res_only: bool = False) -> Act:
@@ -292,8 +293,16 @@ class Decoder:
     def backbone(self, batch: ForwardBatch, caches: LayerCaches) -> torch.Tensor:
         """Token ids -> final residual stream [T, hidden] (before the final norm)."""
         x = self.embed(batch.token_ids)
+        side = self.side_head
+        if side is not None:
+            side.begin(x.shape[0])
         for i, lw in enumerate(self.w.layers):
             x = self.layer(i, x, lw, batch, caches)
+            if side is not None and i in side.capture_ids:
+                x = self.full(x)
+                side.capture(i, x)
+        if side is not None:
+            side.absorb(batch)
         return x
 
     def logits(self, hidden_rows, final_norm=None, out_f32: bool = False, gather: bool = True) -> torch.Tensor:

@@ -383,6 +383,10 @@ def _linear_a16(act: Act, w: QuantWeight, residual, swiglu: bool, out_f32: bool,
             _native.check(L.mb_a16_gemv(C.byref(a), _stream()), f"a16_gemv[{w.fmt} M={M} N={N} K={K}]")
             _count()
         return out
+    if swiglu and out_f32:                                 # the tensor-core SwiGLU epilogue writes bf16
+        y = _linear_a16(act, w, residual, True, False, None)
+        out.copy_(y)
+        return out
     band = max(256, min(N, (_A16_WS_BYTES // (2 * K)) // 256 * 256))
     rt = runtime(dev)
     if getattr(rt, "a16_ws", None) is None or rt.a16_ws.numel() < band * K:

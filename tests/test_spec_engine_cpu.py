@@ -188,3 +188,60 @@ def test_mtp_k3_on_a_hybrid_model_is_lossless_on_cpu():
     got = [o.output_ids for o in eng.generate(prompts, SamplingParams(max_tokens=16))]
     assert got == base
     assert eng.spec_stats.drafted > 0
+
+
+def _dflash_run(device, model="tiny-dense", **kw):
+    eng = LLMEngine(EngineArgs(model=preset(model), device=device, max_num_seqs=4, max_model_len=256, mtp_gate=False,
+                               speculative="dflash", **kw))
+    outs = eng.generate(PROMPTS, SamplingParams(max_tokens=24))
+    return [o.output_ids for o in outs], eng
+
+
+@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)])
+def test_block_drafter_is_lossless_and_drafts_a_whole_block_per_forward(device):
+    """DFlash-style drafter: every proposal is one drafter forward for all drafts of all
+    sequences; whatever it drafts (random weights here), greedy output equals plain decoding."""
+    base, _ = _run(device)
+    got, eng = _dflash_run(device, dflash_gamma=4)
+    assert got == base
+    d = eng.runner.dflash
+    assert eng.spec_stats.drafted > 0 and d.proposals > 0
+    # several drafts per sequence per drafter forward (a step drafts for up to 3 sequences x 4)
+    assert eng.spec_stats.drafted / d.proposals > 4
+
+
+def test_block_drafter_context_follows_the_committed_tokens():
+    """The drafter's context K/V of a position is a function of the committed prefix only: after
+    speculative steps with rejected drafts it equals what a plain prefill of the same tokens writes
+    (slots rewritten by the target are rewritten by the drafter in the same forward)."""
+    import torch
+
+    def run(prompt, n):
+        eng = LLMEngine(EngineArgs(model=preset("tiny-dense"), device="cpu", max_num_seqs=4, max_model_len=256,
+                                   mtp_gate=False, speculative="dflash", dflash_gamma=3, enable_prefix_caching=False))
+        eng.add_request(prompt, SamplingParams(max_tokens=n))
+        blocks, out = None, None
+        while eng.has_work():
+            for o in eng.step():
+                if o.finished:
+                    out = o.output_ids
+            live = list(eng.scheduler.running) + list(eng.scheduler.prefilling)
+            if live:
+                blocks = list(live[0].blocks)
+        return eng, blocks, out
+
+    prompt = PROMPTS[0]
+    eng_a, blocks_a, out = run(prompt, 12)                    # prefill + speculative decode steps
+    assert eng_a.spec_stats.drafted > eng_a.spec_stats.accepted   # some drafts were rejected on the way
+    full = prompt + out[:-1]
+    eng_b, blocks_b, _ = run(full, 2)                         # the same tokens as one prefill (+ one decode step)
+    bs = eng_a.runner.block_size
+    for li in range(len(eng_a.runner.dflash.kv.k)):
+        for name in ("k", "v"):
+            a = getattr(eng_a.runner.dflash.kv, name)[li]
+            b = getattr(eng_b.runner.dflash.kv, name)[li]
+            a, b = a.reshape(-1, *a.shape[2:]), b.reshape(-1, *b.shape[2:])
+            for p in range(len(full)):
+                ra = a[blocks_a[p // bs] * bs + p % bs].float()
+                rb = b[blocks_b[p // bs] * bs + p % bs].float()
+                assert torch.allclose(ra, rb, atol=2e-2, rtol=2e-2), (li, name, p)
