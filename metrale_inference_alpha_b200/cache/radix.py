@@ -43,6 +43,7 @@ class RadixTree:
         self.block_size = block_size
         self.needs_snapshot = needs_snapshot
         self.on_snapshot_evict = on_snapshot_evict
+        self.snapshot_ok = None              # optional predicate: is this snapshot handle still restorable (tiered pools)
         self._roots: Dict[Hashable, _Node] = {}
         self._clock = itertools.count(1)
         self.num_nodes = 0
@@ -79,7 +80,8 @@ class RadixTree:
             node = nxt
         snap = None
         if self.needs_snapshot:
-            while path and path[-1].snapshot is None:
+            while path and (path[-1].snapshot is None
+                            or (self.snapshot_ok is not None and not self.snapshot_ok(path[-1].snapshot))):
                 path.pop()
             snap = path[-1].snapshot if path else None
         now = next(self._clock)

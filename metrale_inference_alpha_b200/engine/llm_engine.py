@@ -62,6 +62,11 @@ class EngineArgs:
     preempt_mode: str = "recompute"                    # recompute | swap (KV + state to host memory / swap files)
     swap_space_bytes: int = 8 << 30
     swap_dir: Optional[str] = None
+    decode_rollback_ring: int = 0                      # recurrent models: state snapshots per decoding sequence for rollback_request (0 = off)
+    decode_rollback_interval: int = 16                 # a ring snapshot every this many generated tokens
+    state_snapshots: int = 0                           # device-resident state snapshots (0 = 16 + ring slots x max_num_seqs)
+    state_tier_host_bytes: int = 0                     # > 0: resident snapshots overflow into this much host memory ...
+    state_tier_dir: Optional[str] = None               # ... and from there (or directly) into files in this directory
     prediction_drafts: int = 8                         # tokens verified per step for requests with a predicted output
     kv_cache_dtype: str = "auto"                       # auto (the model config's) | bf16 | fp8
     kv_high_precision_layers: str = ""                 # e.g. "0,1,63" or "first:2,last:2": these layers keep bf16 KV under fp8
@@ -127,7 +132,8 @@ class LLMEngine:
             max_num_seqs=args.max_num_seqs, max_prefill_tokens=args.max_prefill_tokens,
             max_model_len=min(args.max_model_len, cfg.max_position), block_size=args.block_size,
             policy=args.scheduler, tbt_deadline_ms=args.tbt_deadline_ms,
-            enable_prefix_caching=args.enable_prefix_caching, request_timeout_s=args.request_timeout_s)
+            enable_prefix_caching=args.enable_prefix_caching, request_timeout_s=args.request_timeout_s,
+            decode_ring_slots=args.decode_rollback_ring, decode_ring_interval=args.decode_rollback_interval)
         blocks = args.num_kv_blocks or plan_kv_blocks(cfg, self.weights, args.device, args.block_size,
                                                       args.gpu_memory_utilization,
                                                       reserve_bytes=(2 << 30) + (args.oom_guard_mb << 20))
@@ -140,7 +146,10 @@ class LLMEngine:
         self.runner = ModelRunner(cfg, self.weights, args.device, blocks, self.sched_cfg, self.tp,
                                   use_graphs=args.use_cuda_graphs, kv_poison=args.kv_poison,
                                   fp8_kv_calibration_tokens=args.fp8_kv_calibration_tokens,
-                                  fp8_kv_headroom=args.fp8_kv_headroom)
+                                  fp8_kv_headroom=args.fp8_kv_headroom,
+                                  num_snapshots=args.state_snapshots or 16 + args.decode_rollback_ring * args.max_num_seqs)
+        if self.runner.pool is not None and (args.state_tier_host_bytes > 0 or args.state_tier_dir):
+            self.runner.pool.configure_tiers(args.state_tier_host_bytes, args.state_tier_dir)
         if args.ep_dispatch == "a2a" and args.ep_size > 1 and self.tp.size > 1 and self.device.type == "cuda" \
                 and cfg.num_experts > 0:
             from ..parallel.ep import EpAllToAll
@@ -156,6 +165,8 @@ class LLMEngine:
         if args.enable_prefix_caching:
             self.prefix = make_radix(self.runner.kv.allocator, args.block_size, needs_snapshot=needs_snap,
                                     on_snapshot_evict=(self.runner.pool.release_snapshot if needs_snap else None))
+            if needs_snap and hasattr(self.prefix, "snapshot_ok"):
+                self.prefix.snapshot_ok = self.runner.pool.available
         self.spill = None
         if args.preempt_mode == "swap":
             from ..cache.kv_spill import KvSpillManager
@@ -181,6 +192,8 @@ class LLMEngine:
         self.step_count = 0
         self._inflight = None            # (plan, handle) of a decode step launched ahead and not yet applied
         self.pipeline = bool(args.pipeline_decode and self.device.type == "cuda" and args.use_cuda_graphs)
+        if args.decode_rollback_ring > 0 and self.runner.pool is not None:
+            self.pipeline = False          # a ring snapshot must see the state of exactly the applied step
         self.tokenizer = None
         self.stop_strings_active = False
 
@@ -336,6 +349,18 @@ class LLMEngine:
             self.spec_stats.accepted += sum(getattr(it.seq, "last_accept", 0) for it in plan.items)
         self.step_count += 1
         return outs
+
+    # ------------------------------------------------------------------ rollback
+    def rollback_request(self, request_id: str, keep_output_tokens: int) -> bool:
+        """Rewind a decoding request to its first `keep_output_tokens` generated tokens (a loop
+        detector or a tool-call parser decides where). Returns False when the request is not
+        decoding or, on a recurrent model, no state snapshot exists at that length
+        (`scheduler.rollback_positions` lists the reachable lengths)."""
+        self.flush()
+        for seq in self.scheduler.running:
+            if seq.req.request_id == request_id:
+                return self.scheduler.rollback(seq, keep_output_tokens)
+        return False
 
     # ------------------------------------------------------------------ offline loop
     def generate(self, prompts: Iterable[Seq[int]], params: Union[SamplingParams, Seq[SamplingParams], None] = None

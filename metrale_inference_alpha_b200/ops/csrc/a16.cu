@@ -4,8 +4,8 @@
 //
 //   a16_gemv_kernel   out[m, n] = sum_k x[m, k] * dequant(W[n, k]) for up to 8 rows of x. It is a
 //                     streaming kernel: each warp owns two weight rows (a gate / up pair when the
-//                     SwiGLU epilogue is on), every lane reads 8 weights per step with one 4- or
-//                     8-byte coalesced load, widens them in registers and accumulates in fp32
+//                     SwiGLU epilogue is on), every lane reads 32 NVFP4 or 16 FP8 weights per step with
+//                     one 16-byte load, widens them in registers and accumulates in fp32
 //                     against the activation rows staged in shared memory. One pass over the
 //                     packed weights; the host loops row blocks of 8 for a few more rows.
 //   a16_dequant_kernel  widens a row band of the weight to bf16 so that the tensor-core bf16 GEMM
@@ -64,8 +64,15 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t b) {
   return __half2float(*reinterpret_cast<const __half*>(&h));
 }
 
+// Values of one weight row a lane consumes per step: one 16-byte load (32 NVFP4 nibbles or 16 FP8
+// bytes). A warp step then covers 32 * kVpl consecutive k. The staged activations are stored
+// lane-interleaved, [step][8-value group j][lane][8], so that the 16-byte shared-memory reads of a
+// warp are consecutive (no bank conflicts) although each lane's k range is contiguous in global memory.
+template <int KIND> struct Vpl { static constexpr int v = KIND == kKindNvfp4 ? 32 : 16; };
+
 template <int KIND, int MT>
 __global__ void __launch_bounds__(kWarps * 32) a16_gemv_kernel(const A16Params p) {
+  constexpr int kVpl = Vpl<KIND>::v, kJ = kVpl / 8, kStepK = 32 * kVpl;
   __shared__ __align__(16) __nv_bfloat16 xs[MT][kChunk];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = (blockIdx.x * kWarps + warp) * 2;
@@ -79,48 +86,62 @@ __global__ void __launch_bounds__(kWarps * 32) a16_gemv_kernel(const A16Params p
   for (int k0 = 0; k0 < p.K; k0 += kChunk) {
     __syncthreads();
     for (int i = threadIdx.x; i < MT * (kChunk / 8); i += kWarps * 32) {
-      const int m = i / (kChunk / 8), c = (i % (kChunk / 8)) * 8;
+      const int m = i / (kChunk / 8), c = (i % (kChunk / 8)) * 8;          // c: offset of an 8-value group in the chunk
       uint4 v = make_uint4(0, 0, 0, 0);
       if (m < p.M && k0 + c < p.K) v = *reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + k0 + c);
-      *reinterpret_cast<uint4*>(&xs[m][c]) = v;
+      const int step = c / kStepK, in = c % kStepK, ln = in / kVpl, jj = (in % kVpl) / 8;
+      *reinterpret_cast<uint4*>(&xs[m][step * kStepK + jj * 256 + ln * 8]) = v;
     }
     __syncthreads();
     if (n0 >= p.N) continue;
-#pragma unroll 4
-    for (int s = 0; s < kChunk / 256; ++s) {
-      const int c = s * 256 + lane * 8, k = k0 + c;
+#pragma unroll 2
+    for (int s = 0; s < kChunk / kStepK; ++s) {
+      const int k = k0 + s * kStepK + lane * kVpl;
       if (k >= p.K) break;
-      float wv[2][8], ws[2];
+      uint4 wq[2];
+      float ws[2][2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int n = min(n0 + r, p.N - 1);
         if (KIND == kKindNvfp4) {
-          widen8_fp4(*reinterpret_cast<const uint32_t*>(p.W + n * wld + k / 2), wv[r]);
-          ws[r] = e4m3_to_float(reinterpret_cast<const uint8_t*>(p.scale)[(size_t)n * (p.K / 16) + k / 16]);
+          wq[r] = *reinterpret_cast<const uint4*>(p.W + n * wld + k / 2);
+          const uint16_t sf2 = *reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(p.scale) + (size_t)n * (p.K / 16) + k / 16);
+          ws[r][0] = e4m3_to_float((uint8_t)(sf2 & 0xFF));
+          ws[r][1] = e4m3_to_float((uint8_t)(sf2 >> 8));
         } else {
-          widen8_fp8(*reinterpret_cast<const uint2*>(p.W + n * wld + k), wv[r]);
-          ws[r] = KIND == kKindFp8Block
-                      ? reinterpret_cast<const float*>(p.scale)[(size_t)(n / 128) * p.scale_ld + k / 128]
-                      : 1.f;
+          wq[r] = *reinterpret_cast<const uint4*>(p.W + n * wld + k);
+          ws[r][0] = ws[r][1] = KIND == kKindFp8Block
+                                    ? reinterpret_cast<const float*>(p.scale)[(size_t)(n / 128) * p.scale_ld + k / 128]
+                                    : 1.f;
         }
       }
 #pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(&xs[m][c]);
-        const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
-        float xf[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __bfloat1622float2(xb[i]);
-          xf[2 * i] = f.x;
-          xf[2 * i + 1] = f.y;
-        }
+      for (int jj = 0; jj < kJ; ++jj) {
+        float wv[2][8];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          float d = 0.f;
+          const uint32_t* w32 = reinterpret_cast<const uint32_t*>(&wq[r]);
+          if (KIND == kKindNvfp4) widen8_fp4(w32[jj], wv[r]);
+          else widen8_fp8(make_uint2(w32[2 * jj], w32[2 * jj + 1]), wv[r]);
+        }
 #pragma unroll
-          for (int i = 0; i < 8; ++i) d = fmaf(wv[r][i], xf[i], d);
-          acc[r][m] = fmaf(d, ws[r], acc[r][m]);
+        for (int m = 0; m < MT; ++m) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(&xs[m][s * kStepK + jj * 256 + lane * 8]);
+          const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
+          float xf[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(xb[i]);
+            xf[2 * i] = f.x;
+            xf[2 * i + 1] = f.y;
+          }
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) d = fmaf(wv[r][i], xf[i], d);
+            acc[r][m] = fmaf(d, ws[r][KIND == kKindNvfp4 ? jj / 2 : 0], acc[r][m]);
+          }
         }
       }
     }
@@ -212,7 +233,7 @@ struct MbA16Args {
 };
 
 static int fill(const MbA16Args* a, A16Params& p) {
-  if (a->K % 16 != 0 || a->ldx % 8 != 0 || (a->swiglu && (a->N & 1))) return 1;
+  if (a->K % 32 != 0 || a->ldx % 8 != 0 || (a->swiglu && (a->N & 1))) return 1;
   if (a->kind != kKindFp8Row && a->kind != kKindNvfp4 && a->kind != kKindFp8Block) return 1;
   p.W = (const uint8_t*)a->W; p.scale = a->scale; p.row_gscale = (const float*)a->row_gscale;
   p.gscale = a->gscale; p.x = (const __nv_bfloat16*)a->x; p.residual = (const __nv_bfloat16*)a->residual;

@@ -172,6 +172,10 @@ class SchedulerCore:
     def _release(self, seq: Sequence) -> None:
         self.alloc.free(seq.blocks)
         seq.blocks = []
+        ring = getattr(seq, "decode_ring", None)
+        if ring is not None and self.pool is not None:
+            for sid in ring.clear():
+                self.pool.release_snapshot(sid)
         if self.pool is not None and seq.state_slot:
             self.pool.free(seq.state_slot)
             seq.state_slot = 0
@@ -316,6 +320,7 @@ class SchedulerCore:
                 new = result.tokens[i][:1]
                 seq.num_computed = item.start_pos + 1
                 seq.last_accept = 0
+                self._ring_record(seq, new)
             seq.drafts = []
             if drafts is not None and i < len(drafts) and drafts[i]:
                 seq.drafts = list(drafts[i])
@@ -350,6 +355,60 @@ class SchedulerCore:
         del seq.tokens[seq.prompt_len + keep_output_tokens:]
         seq.stop_hit = stop
         self._finish(seq, FinishReason.STOP)
+
+    # ------------------------------------------------------------------ decode rollback
+    def _ring_record(self, seq: Sequence, new: List[int]) -> None:
+        """After a plain decode step: the recurrent state now covers every token but the one just
+        sampled, which is exactly what a rollback keeping `num_output + 1` tokens must resume from."""
+        c = self.cfg
+        if self.pool is None or c.decode_ring_slots <= 0 or not new:
+            return
+        pos = seq.num_output + 1                            # generated tokens once `new` is appended
+        if pos % max(1, c.decode_ring_interval) != 0 and new[0] not in c.decode_ring_boundary_tokens:
+            return
+        ring = getattr(seq, "decode_ring", None)
+        if ring is None:
+            from .decode_ring import StateDecodeRing
+            ring = seq.decode_ring = StateDecodeRing(c.decode_ring_slots)
+        sid = self.pool.snapshot(seq.state_slot)
+        if sid is None:
+            return
+        drop = ring.record(pos, sid)
+        if drop is not None:
+            self.pool.release_snapshot(drop)
+
+    def rollback_positions(self, seq: Sequence) -> List[int]:
+        """Output lengths this sequence can be rolled back to right now."""
+        if self.pool is None:
+            return list(range(1, seq.num_output + 1))
+        ring = getattr(seq, "decode_ring", None)
+        return [p for p in (ring.positions() if ring else []) if p <= seq.num_output]
+
+    def rollback(self, seq: Sequence, keep_output_tokens: int) -> bool:
+        """Truncate a decoding sequence to its first `keep_output_tokens` generated tokens and
+        continue from there. Attention KV needs nothing (later slots are rewritten); a recurrent
+        model needs the ring snapshot taken at exactly that length, else the rollback is declined
+        (role of the reference's boundary rollback, ``crates/server/src/scheduler/rollback.rs`` with
+        ``ssm_decode_ring.rs``)."""
+        if seq.is_finished() or seq not in self.running or not (0 < keep_output_tokens <= seq.num_output):
+            return False
+        if keep_output_tokens == seq.num_output:
+            return True
+        if self.pool is not None:
+            ring = getattr(seq, "decode_ring", None)
+            e = ring.find(keep_output_tokens) if ring else None
+            if e is None or not self.pool.available(e.snapshot):
+                return False
+            self.pool.restore(e.snapshot, seq.state_slot)
+            for sid in ring.truncate_after(keep_output_tokens):
+                self.pool.release_snapshot(sid)
+        del seq.tokens[seq.prompt_len + keep_output_tokens:]
+        if seq.logprobs:
+            del seq.logprobs[keep_output_tokens:]
+        seq.drafts = []
+        seq.num_computed = len(seq.tokens) - 1
+        self.stats["rollbacks"] = self.stats.get("rollbacks", 0) + 1
+        return True
 
     def _maybe_snapshot(self, seq: Sequence) -> None:
         if self.pool is None or self.prefix is None or not self.prefix.needs_snapshot:

@@ -21,6 +21,9 @@ class SchedulerConfig:
     request_timeout_s: float = 300.0
     preempt_mode: str = "recompute"      # recompute | swap
     batch_rungs: tuple = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128)
+    decode_ring_slots: int = 0           # recurrent models: state snapshots kept per decoding sequence for rollback (0 = off)
+    decode_ring_interval: int = 16       # a snapshot every this many generated tokens ...
+    decode_ring_boundary_tokens: tuple = ()   # ... and whenever one of these token ids is generated
 
 
 class FifoPolicy:

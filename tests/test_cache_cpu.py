@@ -210,3 +210,46 @@ def test_online_fp8_kv_calibration_freezes_rescales_and_holds_graphs_back():
     a = ref.from_e4m3(r.kv.k[0][1:3]) * float(r.kv.k_scale[0])          # blocks 1, 2: positions 0..31 of the first sequence
     b = ref.from_e4m3(eng2.runner.kv.k[0][1:3]) * float(r.kv.k_scale[0])
     assert (a - b).abs().max().item() <= 0.13 * b.abs().max().item()
+
+
+def test_state_snapshots_overflow_into_host_and_file_tiers(tmp_path):
+    """Resident snapshot area of 2: further snapshots demote the least recently used resident one
+    to host memory, and the host tier (budget of one slot) demotes its oldest to a file; every
+    handle restores the exact state it captured, from whichever tier, and release cleans up."""
+    import os
+    import torch
+    from metrale_inference_alpha_b200.cache.state_pool import StatePool
+    pool = StatePool([((6, 3), (2, 4, 5))], num_slots=3, num_snapshots=2)
+    pool.configure_tiers(host_tier_bytes=pool.bytes_per_slot(), tier_dir=str(tmp_path))
+    handles, want = [], []
+    for n in range(5):
+        pool.conv[0][1].fill_(float(n))
+        pool.ssm[0][1].fill_(float(10 + n))
+        handles.append(pool.snapshot(1))
+        want.append((float(n), float(10 + n)))
+    assert None not in handles and len(set(handles)) == 5
+    tiers = [pool._where[h][0] for h in handles]
+    assert tiers.count("dev") == 2 and tiers.count("host") == 1 and tiers.count("file") == 2
+    assert len(os.listdir(tmp_path)) == 2
+    for h, (c, s) in zip(handles, want):
+        pool.restore(h, 2)
+        assert float(pool.conv[0][2].mean()) == c and float(pool.ssm[0][2].mean()) == s
+    assert pool.tier_stats["restored_file"] == 2 and pool.tier_stats["restored_host"] == 1
+    for h in handles:
+        pool.release_snapshot(h)
+    assert os.listdir(tmp_path) == [] and len(pool._snap_free) == 2 and pool._host_bytes == 0
+    # without tiers a full area refuses, as before
+    plain = StatePool([((6, 3), (2, 4, 5))], num_slots=3, num_snapshots=1)
+    assert plain.snapshot(1) is not None and plain.snapshot(1) is None
+
+
+def test_decode_ring_keeps_the_newest_entries_and_needs_an_exact_position():
+    from metrale_inference_alpha_b200.scheduler.decode_ring import StateDecodeRing
+    r = StateDecodeRing(3)
+    dropped = [r.record(p, 100 + p) for p in (4, 8, 12, 16)]
+    assert dropped == [None, None, None, 104] and r.positions() == [8, 12, 16]
+    assert r.find(12).snapshot == 112 and r.find(10) is None
+    assert r.last_at_or_before(15).token_position == 12
+    assert r.record(12, 999) == 112                       # a re-generated position replaces its entry
+    assert r.truncate_after(8) == [999, 116] and r.positions() == [8]
+    assert StateDecodeRing(0).record(4, 7) == 7            # a disabled ring hands the snapshot straight back

@@ -284,3 +284,31 @@ def test_config1_tiny_dense_64_tokens_per_step_logits_against_an_independent_res
             break                                           # 16 full decode steps of logits (the rest by tokens)
     assert checked >= 4 * 16
     assert flips <= 4                                       # of 256 tokens
+
+
+@pytest.mark.parametrize("model", ["tiny-hybrid-moe", "tiny-nemotron-h", "tiny-dense"])
+def test_rollback_to_a_ring_snapshot_resumes_exactly(model):
+    """Generate, roll the request back to an earlier length, continue: greedy decoding must
+    reproduce the tokens it produced the first time (recurrent state restored from the decode
+    ring, attention KV simply rewritten). A length with no ring snapshot is declined on recurrent
+    models and the sequence is left untouched."""
+    eng = LLMEngine(EngineArgs(model=preset(model), device="cpu", max_num_seqs=2, max_model_len=256,
+                               decode_rollback_ring=3, decode_rollback_interval=4, enable_prefix_caching=False))
+    rid = eng.add_request([5, 6, 7, 8, 9, 10, 11], SamplingParams(max_tokens=24))
+    first = None
+    while eng.has_work():
+        outs = eng.step()
+        seq = next((s for s in eng.scheduler.running if s.req.request_id == rid), None)
+        if seq is not None and seq.num_output == 14 and first is None:
+            first = list(seq.tokens[seq.prompt_len:])
+            recurrent = eng.runner.pool is not None
+            if recurrent:
+                assert eng.scheduler.rollback_positions(seq) == [4, 8, 12]
+                assert not eng.rollback_request(rid, 7)          # no snapshot at 7
+                assert list(seq.tokens[seq.prompt_len:]) == first
+            assert eng.rollback_request(rid, 8)
+            assert seq.num_output == 8
+        final = [o for o in outs if o.finished]
+    assert first is not None and final
+    assert final[0].output_ids[:14] == first
+    assert len(final[0].output_ids) == 24
