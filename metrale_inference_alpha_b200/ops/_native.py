@@ -121,6 +121,8 @@ def lib():
     for fn in (L.mb_a16_gemv, L.mb_a16_dequant):
         fn.argtypes = [P(A16Args), c_void_p]
         fn.restype = c_int
+    L.mb_gguf_dequant.argtypes = [c_int, c_void_p, c_ll, c_void_p, c_void_p]
+    L.mb_gguf_dequant.restype = c_int
     L.mb_gemm_counter_bytes.argtypes = []
     L.mb_gemm_counter_bytes.restype = c_size_t
     L.mb_row_op.argtypes = [P(RowArgs), c_void_p]

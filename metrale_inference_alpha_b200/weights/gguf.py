@@ -95,6 +95,21 @@ class GgufFile:
         shape, typ, _ = self.tensors[name]
         return dequantize(self.read_raw(name), typ, int(np.prod(shape))).reshape(shape)
 
+    def dequant_device(self, name: str, device) -> torch.Tensor:
+        """The tensor as bf16 on `device`. Block-quantised types are uploaded packed and widened
+        by the device kernels (ops/csrc/gguf_dequant.cu); other types take the host path."""
+        shape, typ, _ = self.tensors[name]
+        dev = torch.device(device)
+        if dev.type != "cuda" or typ not in (Q8_0, Q4_0, Q4_K, Q6_K):
+            return self.dequant(name).to(torch.bfloat16).to(dev)
+        from ..ops import _native, _ptr, _stream
+        n = int(np.prod(shape))
+        raw = torch.from_numpy(self.read_raw(name).copy()).to(dev)
+        out = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        _native.check(_native.lib().mb_gguf_dequant(typ, _ptr(raw), n // BLOCK[typ][0], _ptr(out), _stream()),
+                      f"gguf_dequant[type {typ}]")
+        return out.view(shape)
+
 
 # ----------------------------------------------------------------------------- block formats
 def _f16(b: np.ndarray) -> np.ndarray:
@@ -254,7 +269,8 @@ def config_from_gguf(g: GgufFile) -> ModelConfig:
 class GgufSource(TensorSource):
     """Serves HF-named bf16 tensors out of a GGUF file (dequantised on demand)."""
 
-    def __init__(self, path, cfg: Optional[ModelConfig] = None):
+    def __init__(self, path, cfg: Optional[ModelConfig] = None, device="cpu"):
+        self.device = torch.device(device)     # "cuda": block formats are widened on the device
         self.g = GgufFile(path)
         self.cfg = cfg or config_from_gguf(self.g)
         self.arch = self.g.meta.get("general.architecture", "llama")
@@ -274,7 +290,8 @@ class GgufSource(TensorSource):
         return w.view(heads, d // 2, 2, *w.shape[1:]).transpose(1, 2).reshape(w.shape)
 
     def get(self, name):
-        w = self.g.dequant(self._names[name])
+        w = (self.g.dequant_device(self._names[name], self.device) if self.device.type == "cuda"
+             else self.g.dequant(self._names[name]))
         if self.arch == "llama" and name.endswith(("q_proj.weight", "k_proj.weight")):
             w = self._unpermute(w, self.cfg.num_heads if "q_proj" in name else self.cfg.num_kv_heads)
         return w.to(torch.bfloat16)

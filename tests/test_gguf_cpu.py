@@ -117,3 +117,29 @@ def test_engine_runs_from_a_gguf_export_of_the_tiny_model(tmp_path):
     assert len(a) == 4 and a[0] == b[0]                 # Q8_0 weights: the first greedy token survives
     assert gguf.hf_name("blk.3.attn_k_norm.weight") == "model.layers.3.self_attn.k_norm.weight"
     assert gguf.hf_name("rope_freqs.weight") is None
+
+
+@pytest.mark.gpu
+def test_device_dequantisers_match_the_host_ones(tmp_path):
+    """Q8_0 / Q4_0 / Q4_K / Q6_K blocks widened by the device kernels equal the host dequantisation
+    rounded to bf16, through the file path a loader takes (`GgufFile.dequant_device`)."""
+    import torch
+    rng = np.random.default_rng(5)
+    sizes = {gguf.Q8_0: (32, 34), gguf.Q4_0: (32, 18), gguf.Q4_K: (256, 144), gguf.Q6_K: (256, 210)}
+    for typ, (vals, size) in sizes.items():
+        nb = 517
+        raw = rng.integers(0, 256, size=(nb, size), dtype=np.uint8)
+        for r in raw:                                   # finite, small f16 scale fields
+            if typ in (gguf.Q8_0, gguf.Q4_0):
+                r[0:2] = np.array([0.02], np.float16).view(np.uint8)
+            elif typ == gguf.Q4_K:
+                r[0:4] = np.array([0.01, 0.02], np.float16).view(np.uint8)
+            else:
+                r[208:210] = np.array([0.015], np.float16).view(np.uint8)
+        want = gguf.dequantize(raw.reshape(-1), typ, nb * vals).to(torch.bfloat16)
+        from metrale_inference_alpha_b200.ops import _native, _ptr, _stream
+        dev_raw = torch.from_numpy(raw.reshape(-1).copy()).cuda()
+        out = torch.empty(nb * vals, dtype=torch.bfloat16, device="cuda")
+        _native.check(_native.lib().mb_gguf_dequant(typ, _ptr(dev_raw), nb, _ptr(out), _stream()), "gguf_dequant")
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), want), typ
