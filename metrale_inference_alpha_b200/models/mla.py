@@ -4,8 +4,11 @@ The paged cache stores one row per token: ``[kv_lora latent (RMS-normed) | rope 
 (kv_lora + rope dims, a single "kv head"). Queries are projected into latent space with
 W_uk, attention runs as multi-query attention over the latent rows, and W_uv maps the
 latent-space output back to per-head values before o_proj.
-On a GPU the attention itself runs in ``ops/csrc/mla.cu`` (one CTA per 16 query rows, the cached
-tile feeding both products); this file keeps the fp32 restatement used on CPU and as the oracle.
+On a GPU the block is: projections (tcgen05 GEMMs), the two absorption products as bf16 batched
+GEMMs over heads, one assembly kernel (latent RMSNorm, both rotations, cache row write, absorbed
+query rows: ``mla.cu::mla_prepare_kernel``) and the paged attention kernel (one CTA per 16 query
+rows, the cached tile feeding both products); this file keeps the fp32 restatement used on CPU
+and as the oracle.
 Reference behaviour: ``kernels/gb10/deepseek-v4-flash/nvfp4/mla_absorbed.cu``
 (``mla_batched_gemv``, ``mla_cache_assemble``), ``paged_decode_attn_mla.cu``.
 """
@@ -32,6 +35,29 @@ def mla_block(dec, x, lw, batch, kv, j: int):
         q = ops.linear(qn, w.q_b)
     else:
         q = ops.linear(a, w.q_b)
+    scale = 1.0 / math.sqrt(nope + rope)
+    sc = c.rope_scaling or {}
+    if sc.get("rope_type", sc.get("type")) == "yarn" and sc.get("mscale_all_dim"):
+        # DeepSeek long-context checkpoints fold the YaRN magnitude correction into the softmax scale
+        m = 0.1 * float(sc["mscale_all_dim"]) * math.log(float(sc.get("factor", 1.0))) + 1.0
+        scale *= m * m
+    if (x.is_cuda and L == mla_cuda.LATENT and kv.k[j].dtype == torch.bfloat16 and kv.k[j].shape[-1] == mla_cuda.ROW
+            and dec.cos.shape[1] * 2 == rope and w.kv_a_norm.dtype == torch.bfloat16):
+        # GPU: bf16 absorption products on the tensor cores (batched over heads), one kernel for the
+        # latent norm + both rotations + the cache write + the query assembly, the paged MLA kernel
+        q = q.view(T, H, nope + rope)
+        ckv = ops.linear(a, w.kv_a)                                    # [T, L + rope] bf16
+        uk = _bf16(w, "w_uk")                                          # [H, nope, L]
+        q_lat = torch.bmm(q[..., :nope].transpose(0, 1), uk)           # [H, T, L]
+        qq = mla_cuda.prepare(q, q_lat, ckv, w.kv_a_norm, dec.cos, dec.sin, batch.positions, batch.slot_mapping,
+                              kv.k[j], nope, c.rms_eps)
+        o_lat = mla_cuda.mla_attention(qq, kv.k[j], batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
+                                       max_q_len=batch.max_q_len, max_ctx=max(batch.max_ctx, 1), scale=scale)
+        uv = _bf16(w, "w_uv")                                          # [H, vd, L]
+        o = torch.bmm(o_lat.to(torch.bfloat16).transpose(0, 1), uv.transpose(1, 2))      # [H, T, vd]
+        o = o.transpose(0, 1).reshape(T, H * vd)
+        oa = ops.quantize_act(o, ACT_FOR_WEIGHT[w.o.fmt])
+        return dec.tp.linear_reduce(oa, w.o, residual=x, defer=True)
     q = q.view(T, H, nope + rope).float()
     ckv = ops.linear(a, w.kv_a).float()                                # [T, L + rope]
     lat = ref.rms_norm(ckv[:, :L], w.kv_a_norm, c.rms_eps)
@@ -44,12 +70,6 @@ def mla_block(dec, x, lw, batch, kv, j: int):
     flat.index_copy_(0, batch.slot_mapping.clamp(min=0), row)
     q_lat = torch.einsum("thn,hnl->thl", q[..., :nope], w.w_uk.float())   # absorb W_uk
     qq = torch.cat([q_lat, q_rope], -1).to(torch.bfloat16)             # [T, H, L + rope]
-    scale = 1.0 / math.sqrt(nope + rope)
-    sc = c.rope_scaling or {}
-    if sc.get("rope_type", sc.get("type")) == "yarn" and sc.get("mscale_all_dim"):
-        # DeepSeek long-context checkpoints fold the YaRN magnitude correction into the softmax scale
-        m = 0.1 * float(sc["mscale_all_dim"]) * math.log(float(sc.get("factor", 1.0))) + 1.0
-        scale *= m * m
     if mla_cuda.supported(qq, kv.k[j]) and L == mla_cuda.LATENT:
         o_lat = mla_cuda.mla_attention(qq, kv.k[j], batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
                                        max_q_len=batch.max_q_len, max_ctx=max(batch.max_ctx, 1), scale=scale)
@@ -58,6 +78,16 @@ def mla_block(dec, x, lw, batch, kv, j: int):
     o = torch.einsum("thl,hvl->thv", o_lat, w.w_uv.float()).reshape(T, H * vd)
     oa = ops.quantize_act(o.to(torch.bfloat16), ACT_FOR_WEIGHT[w.o.fmt])
     return dec.tp.linear_reduce(oa, w.o, residual=x, defer=True)
+
+
+def _bf16(w, name: str) -> torch.Tensor:
+    """The absorption matrix as a bf16 tensor, converted once and kept beside the weights."""
+    key = "_" + name + "_bf16"
+    t = getattr(w, key, None)
+    if t is None:
+        t = getattr(w, name).to(torch.bfloat16).contiguous()
+        setattr(w, key, t)
+    return t
 
 
 def mla_attention(q, cache, batch, scale: float, L: int) -> torch.Tensor:

@@ -368,3 +368,104 @@ int mb_mla_attention(const MbMlaArgs* a, cudaStream_t stream) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ absorbed-MLA operand assembly
+// One launch between the projections and the attention kernel, replacing a chain of elementwise
+// tensor ops: per token
+//   * the compressed KV row [latent (L) | rope key (R)] from the kv_a projection: RMSNorm of the
+//     latent with its weight, NeoX rotation of the rope key at the token's position, both written
+//     as one bf16 cache row at the token's slot (rows without a slot write nothing);
+//   * the absorbed query row of every head, [q_lat (L) | rotated q_rope (R)]: q_lat comes from the
+//     batched absorption product q_nope W_uk (laid out [H, T, L]), q_rope from the q projection.
+// grid = T tokens, 256 threads. Reference behaviour: mla_cache_assemble and the rope half of
+// mla_batched_gemv (kernels/gb10/deepseek-v4-flash/nvfp4/mla_absorbed.cu).
+namespace {
+struct MlaPrepParams {
+  const __nv_bfloat16* q;        // [T, H, nope + R]
+  const __nv_bfloat16* q_lat;    // [H, T, L]
+  const __nv_bfloat16* ckv;      // [T, L + R]
+  const __nv_bfloat16* norm_w;   // [L]
+  const float* cos_tab;          // [max_pos, R / 2]
+  const float* sin_tab;
+  const int* positions;
+  const long long* slots;
+  __nv_bfloat16* cache;          // [num_slots, L + R]
+  __nv_bfloat16* qq;             // [T, H, L + R]
+  int T, H, nope, R, L, max_pos;
+  long long num_slots;
+  float eps;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(256) mla_prepare_kernel(const MlaPrepParams p) {
+  __shared__ float s_red[8];
+  __shared__ float s_cs[2][64];                      // cos | sin of this position (R / 2 <= 64)
+  const int t = blockIdx.x, tid = threadIdx.x;
+  mb::pdl_wait();
+  mb::pdl_launch_dependents();
+  const int pos = min(max(p.positions[t], 0), p.max_pos - 1);
+  const int half = p.R / 2;
+  if (tid < half) {
+    s_cs[0][tid] = p.cos_tab[(size_t)pos * half + tid];
+    s_cs[1][tid] = p.sin_tab[(size_t)pos * half + tid];
+  }
+  // latent RMSNorm (fp32 statistics over L)
+  const __nv_bfloat16* row = p.ckv + (size_t)t * (p.L + p.R);
+  float ss = 0.f;
+  for (int i = tid; i < p.L; i += 256) {
+    const float v = __bfloat162float(row[i]);
+    ss += v * v;
+  }
+  ss = mb::warp_sum(ss);
+  if ((tid & 31) == 0) s_red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += s_red[w];
+  const float rinv = rsqrtf(tot / (float)p.L + p.eps);
+  const long long slot = p.slots[t];
+  if (slot >= p.num_slots) {
+    if (p.status && tid == 0) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
+  } else if (slot >= 0) {
+    __nv_bfloat16* dst = p.cache + (size_t)slot * (p.L + p.R);
+    for (int i = tid; i < p.L; i += 256)
+      dst[i] = __float2bfloat16(__bfloat162float(row[i]) * rinv * __bfloat162float(p.norm_w[i]));
+    if (tid < half) {
+      const float x1 = __bfloat162float(row[p.L + tid]), x2 = __bfloat162float(row[p.L + half + tid]);
+      dst[p.L + tid] = __float2bfloat16(x1 * s_cs[0][tid] - x2 * s_cs[1][tid]);
+      dst[p.L + half + tid] = __float2bfloat16(x2 * s_cs[0][tid] + x1 * s_cs[1][tid]);
+    }
+  }
+  // absorbed query rows: 16-byte copies of q_lat, then the rotated rope part
+  const int W = p.L + p.R;
+  const int chunks = p.L / 8;
+  for (int i = tid; i < p.H * chunks; i += 256) {
+    const int h = i / chunks, c = i - h * chunks;
+    *reinterpret_cast<uint4*>(p.qq + ((size_t)t * p.H + h) * W + c * 8) =
+        *reinterpret_cast<const uint4*>(p.q_lat + ((size_t)h * p.T + t) * p.L + c * 8);
+  }
+  for (int i = tid; i < p.H * half; i += 256) {
+    const int h = i / half, j = i - h * half;
+    const __nv_bfloat16* qr = p.q + ((size_t)t * p.H + h) * (p.nope + p.R) + p.nope;
+    const float x1 = __bfloat162float(qr[j]), x2 = __bfloat162float(qr[half + j]);
+    __nv_bfloat16* dst = p.qq + ((size_t)t * p.H + h) * W + p.L;
+    dst[j] = __float2bfloat16(x1 * s_cs[0][j] - x2 * s_cs[1][j]);
+    dst[half + j] = __float2bfloat16(x2 * s_cs[0][j] + x1 * s_cs[1][j]);
+  }
+}
+}  // namespace
+
+extern "C" int mb_mla_prepare(const void* q, const void* q_lat, const void* ckv, const void* norm_w,
+                              const float* cos_tab, const float* sin_tab, const int* positions, const long long* slots,
+                              void* cache, void* qq, int T, int H, int nope, int R, int L, int max_pos,
+                              long long num_slots, float eps, uint32_t* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (R > 128 || (R & 1) || L % 8 != 0 || H <= 0) return MB_ERR_BAD_ARG;
+  MlaPrepParams p;
+  p.q = (const __nv_bfloat16*)q; p.q_lat = (const __nv_bfloat16*)q_lat; p.ckv = (const __nv_bfloat16*)ckv;
+  p.norm_w = (const __nv_bfloat16*)norm_w; p.cos_tab = cos_tab; p.sin_tab = sin_tab;
+  p.positions = positions; p.slots = slots; p.cache = (__nv_bfloat16*)cache; p.qq = (__nv_bfloat16*)qq;
+  p.T = T; p.H = H; p.nope = nope; p.R = R; p.L = L; p.max_pos = max_pos; p.num_slots = num_slots;
+  p.eps = eps; p.status = status;
+  return (int)mb::launch_kernel(mla_prepare_kernel, dim3(T), dim3(256), (size_t)0, stream, p);
+}

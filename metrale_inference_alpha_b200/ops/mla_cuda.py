@@ -24,6 +24,8 @@ class MlaArgs(C.Structure):
 
 _native.register_optional("mb_mla_attention", [C.POINTER(MlaArgs), c_void_p])
 
+_native.register_optional("mb_mla_prepare", [c_void_p] * 10 + [c_int] * 6 + [c_ll, c_float, c_void_p, c_void_p])
+
 LATENT, ROW = 512, 576
 _CNT_BYTES = 64 * 1024
 
@@ -65,3 +67,20 @@ def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_table, q_start, q_
     _native.check(L.mb_mla_attention(C.byref(a), _stream()), "mla_attention")
     _count()
     return out
+
+
+def prepare(q: torch.Tensor, q_lat: torch.Tensor, ckv: torch.Tensor, norm_w: torch.Tensor, cos, sin, positions,
+            slots, cache: torch.Tensor, nope: int, eps: float) -> torch.Tensor:
+    """One launch: latent RMSNorm + key RoPE + cache row write, and the absorbed query rows
+    [T, H, L + R] assembled from q_lat [H, T, L] and the rotated rope part of q [T, H, nope + R]."""
+    from . import _count, _ptr, _stream, runtime
+    T, H, qd = q.shape
+    L, R = q_lat.shape[-1], qd - nope
+    qq = torch.empty(T, H, L + R, dtype=torch.bfloat16, device=q.device)
+    rc = _native.lib().mb_mla_prepare(
+        _ptr(q), _ptr(q_lat), _ptr(ckv), _ptr(norm_w), _ptr(cos), _ptr(sin), _ptr(positions), _ptr(slots),
+        _ptr(cache), _ptr(qq), T, H, nope, R, L, cos.shape[0], cache.shape[0] * cache.shape[1], eps,
+        _ptr(runtime(q.device).status), _stream())
+    _native.check(rc, "mla_prepare")
+    _count()
+    return qq

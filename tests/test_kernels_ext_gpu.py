@@ -420,3 +420,43 @@ def test_ep_all_to_all_loopback_matches_local_experts():
         idx = idx.flip(0).contiguous()
         wts = wts.flip(0).contiguous()
         want = want.flip(0)
+
+
+def test_mla_block_on_gpu_matches_the_cpu_restatement():
+    """A two-layer DeepSeek-shaped model with the real latent geometry (512 + 64) through the
+    engine on both devices: the GPU block (bf16 absorption products, the operand-assembly kernel,
+    the paged MLA kernel) must give the logits of the fp32 restatement on CPU, for a prefill
+    and for decode steps over the cache rows the assembly kernel wrote."""
+    from metrale_inference_alpha_b200.config.model_config import from_hf_config
+    from metrale_inference_alpha_b200.engine.runner import ModelRunner
+    from metrale_inference_alpha_b200.scheduler.policy import SchedulerConfig
+    from metrale_inference_alpha_b200.weights.loader import load_weights
+    cfg = from_hf_config(dict(model_type="deepseek_v3", vocab_size=1024, hidden_size=512, num_hidden_layers=2,
+                              num_attention_heads=16, num_key_value_heads=16, intermediate_size=512, moe_intermediate_size=128,
+                              n_routed_experts=0, first_k_dense_replace=2, kv_lora_rank=512, q_lora_rank=192,
+                              qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, rms_norm_eps=1e-6, rope_theta=1e4,
+                              max_position_embeddings=512), name="tiny-mla")
+    toks = torch.randint(1, 1024, (37,), generator=torch.Generator().manual_seed(8)).tolist()
+    logits = {}
+    for dev in ("cpu", DEV):
+        w = load_weights(cfg, None, device=dev, seed=3)
+        r = ModelRunner(cfg, w, dev, num_blocks=16, sched=SchedulerConfig(max_num_seqs=2, max_model_len=256), use_graphs=False)
+        blocks = [1, 2, 3, 4]
+        out = []
+        b = ForwardBatch.build([dict(tokens=toks, start_pos=0, blocks=blocks, state_slot=0)], 16, device=dev, max_blocks=r.max_blocks)
+        lg, _ = r.decoder.forward(b, r.caches, out_f32=True)
+        out.append(lg.float().cpu())
+        nxt = int(lg.argmax())
+        for step in range(3):                                   # decode rows read what the prefill wrote
+            b = ForwardBatch.build([dict(tokens=[nxt], start_pos=len(toks) + step, blocks=blocks, state_slot=0)], 16,
+                                   device=dev, max_blocks=r.max_blocks)
+            lg, _ = r.decoder.forward(b, r.caches, out_f32=True)
+            out.append(lg.float().cpu())
+            nxt = int(out[0].argmax()) if step < 0 else 7 + step   # fixed tokens: both devices see the same inputs
+        logits[dev] = out
+    if DEV == "cuda":
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+    for a, bb in zip(logits["cpu"], logits[DEV]):
+        assert (a - bb).abs().max() <= 0.04 * a.abs().max() + 2e-3, ((a - bb).abs().max(), a.abs().max())
+        assert int(a.argmax()) == int(bb.argmax())
