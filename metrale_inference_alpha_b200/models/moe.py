@@ -21,10 +21,22 @@ def moe_block(dec, x, lw):
     a = dec._norm_act(x, lw.ln2, fmt, also_bf16=True, res_only=dec.tp.size > 1)
     x = dec.res(x)
     hb = a.bf16
-    logits = ops.linear(dec._as_act(hb, "bf16"), w.router, out_f32=True)
-    weights, idx = moe_ops.route(logits, c, w.bias)
     T = x.shape[0]
     ep = getattr(dec.tp, "ep", None)
+    ge = w.grouped
+    if x.is_cuda and ep is None and ge is not None and ge.shared_slot is not None:
+        # the shared expert is stacked behind the routed ones and the router weight carries its gate
+        # row: one routing launch hands every token k + 1 (expert, weight) pairs, and the grouped
+        # GEMMs, the sort and the combine serve the shared expert at no extra launch
+        from ..ops.moe_cuda import grouped_ffn, route_shared_cuda
+        logits = ops.linear(dec._as_act(hb, "bf16"), w.router_ext, out_f32=True)
+        weights, idx = route_shared_cuda(logits, c, w.bias, w.expert_lo + ge.shared_slot,
+                                         c.num_experts if w.shared_gate is not None else -1)
+        if dec.tp.size > 1:
+            return dec.tp.sum_deferred(grouped_ffn(c, a, weights, idx, w, finish=(None, None, None)), residual=x)
+        return grouped_ffn(c, a, weights, idx, w, finish=(None, None, x))
+    logits = ops.linear(dec._as_act(hb, "bf16"), w.router, out_f32=True)
+    weights, idx = moe_ops.route(logits, c, w.bias)
     replicated = w.shared is not None and getattr(w, "shared_replicated", False) and dec.tp.size > 1
     if (x.is_cuda and ep is None and w.grouped is not None and not replicated
             and (w.shared is None or w.shared_gate is None or w.shared_gate.N == 1)):

@@ -189,27 +189,6 @@ __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
 }
-// e4m3 x e4m3 -> f32, k = 32: A row-major bytes (a0: row g, k 4t..4t+3; a1: row g + 8; a2 / a3: k + 16),
-// B bytes (b0: k 4t..4t+3 of column g; b1: k + 16)
-__device__ __forceinline__ void mma16832_e4m3(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// four floats -> four e4m3 bytes (a in the lowest byte), and back
-__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
-  uint16_t lo, hi;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
-  return (uint32_t)lo | ((uint32_t)hi << 16);
-}
-__device__ __forceinline__ float2 unpack2_e4m3(uint16_t v) {
-  uint32_t r;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
-  return __half22float2(*reinterpret_cast<const __half2*>(&r));
-}
 __device__ __forceinline__ void ldsm4(uint32_t* r, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -534,14 +513,7 @@ __global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_split
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
 
-  // Q fragments, kept in registers for the whole kernel. For an e4m3 cache Q.K^T runs as an
-  // e4m3 x e4m3 product straight on the cached bytes (no widening of K): every query row is split
-  // into two e4m3 terms, q = s (hi + lo) with s = amax / 448, hi = e4m3(q / s) and
-  // lo = e4m3(q / s - hi), which keeps about 7 bits of mantissa, as the bf16 row had (e4m3 reaches
-  // 2^-9, so the remainder of every element that matters next to the row maximum is representable).
-  // qf[mt][j][0..3] = hi and qf[mt][D / 32 + j][0..3] = lo of the 32-dim group j.
   uint32_t qf[MT][D / 16][4];
-  float q_mul[MT][2];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -552,46 +524,23 @@ __global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_split
         const int tq = r / G, hh = r - tq * G;
         qrow = p.q + ((size_t)(qs + tq) * p.Hq + kvh * G + hh) * D;
       }
-      q_mul[mt][hr] = 1.f;
-      if constexpr (FP8) {
-        float amax = 0.f;
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          uint2 v = make_uint2(0, 0);
-          if (qrow) v = *reinterpret_cast<const uint2*>(qrow + ks * 16 + 4 * t);
-          const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
-          const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
-          amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y))));
-        }
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        const float sq = amax > 0.f ? amax * (1.f / 448.f) : 1.f, inv = 1.f / sq;
-        q_mul[mt][hr] = sq * p.scale * (*p.k_scale) * 1.44269504088896f;   // row scale x softmax scale x K scale x log2(e)
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {            // second pass over the row (it is in L1 now)
-          uint2 v = make_uint2(0, 0);
-          if (qrow) v = *reinterpret_cast<const uint2*>(qrow + ks * 16 + 4 * t);
-          const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
-          const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
-          const float a = f0.x * inv, b = f0.y * inv, c = f1.x * inv, d = f1.y * inv;
-          const uint32_t hi = pack4_e4m3(a, b, c, d);
-          const float2 h0 = unpack2_e4m3((uint16_t)(hi & 0xFFFFu)), h1 = unpack2_e4m3((uint16_t)(hi >> 16));
-          const uint32_t lo = pack4_e4m3(a - h0.x, b - h0.y, c - h1.x, d - h1.y);
-          // k step ks is the low (ks even) or high (ks odd) 16 dims of 32-dim group ks / 2: a0 / a1 or a2 / a3
-          qf[mt][ks >> 1][(ks & 1) * 2 + hr] = hi;
-          qf[mt][D / 32 + (ks >> 1)][(ks & 1) * 2 + hr] = lo;
-        }
-      } else {
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          uint32_t lo = 0, hi = 0;
-          if (qrow) {
+      for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t lo = 0, hi = 0;
+        if (qrow) {
+          if constexpr (FP8) {
+            const uint2 v = *reinterpret_cast<const uint2*>(qrow + ks * 16 + 4 * t);
+            const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+            const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+            lo = pack2<true>(f0.x, f0.y);
+            hi = pack2<true>(f1.x, f1.y);
+          } else {
             lo = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t);
             hi = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t + 8);
           }
-          qf[mt][ks][hr] = lo;          // a0 (row g) / a1 (row g + 8)
-          qf[mt][ks][2 + hr] = hi;      // a2 / a3
         }
+        qf[mt][ks][hr] = lo;          // a0 (row g) / a1 (row g + 8)
+        qf[mt][ks][2 + hr] = hi;      // a2 / a3
       }
     }
   }
@@ -643,18 +592,20 @@ __global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_split
         for (int i = 0; i < 4; ++i) s[mt][n][i] = 0.f;
     if constexpr (FP8) {
 #pragma unroll
-      for (int kg = 0; kg < D / 32; ++kg) {              // 32 dims = one e4m3 k step per ldmatrix.x4
+      for (int kg = 0; kg < D / 32; ++kg) {              // 32 dims = 2 k steps per ldmatrix.x4
         uint32_t r[4];
-        // matrices: (tok 0-7, dims 0-15) (tok 0-7, dims 16-31) (tok 8-15, 0-15) (tok 8-15, 16-31): thread
-        // (g, t) gets bytes 4t..4t+3 of token g from each, which is the B fragment as it is
+        // matrices: (tok 0-7, bytes lo) (tok 0-7, bytes hi) (tok 8-15, lo) (tok 8-15, hi)
         const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
         ldsm4(r, kT + raw_off<kRowB>(row, kg * 2 + ((lane >> 3) & 1)));
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          mma16832_e4m3(s[mt][0], qf[mt][kg], r[0], r[1]);
-          mma16832_e4m3(s[mt][1], qf[mt][kg], r[2], r[3]);
-          mma16832_e4m3(s[mt][0], qf[mt][D / 32 + kg], r[0], r[1]);
-          mma16832_e4m3(s[mt][1], qf[mt][D / 32 + kg], r[2], r[3]);
+        for (int h = 0; h < 2; ++h) {                     // k step 2 kg + h
+          const uint32_t b00 = e4m3_lo16(r[h]), b01 = e4m3_hi16(r[h]);
+          const uint32_t b10 = e4m3_lo16(r[2 + h]), b11 = e4m3_hi16(r[2 + h]);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma16816<true>(s[mt][0], qf[mt][kg * 2 + h], b00, b01);
+            mma16816<true>(s[mt][1], qf[mt][kg * 2 + h], b10, b11);
+          }
         }
       }
     } else {
@@ -687,7 +638,7 @@ __global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_split
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
               const int tok = tok0 + n * 8 + t * 2 + i;
-              float v = s[mt][n][hr * 2 + i] * (FP8 ? q_mul[mt][hr] : sc_log2);
+              float v = s[mt][n][hr * 2 + i] * sc_log2;
               if (tok >= limit || tok < wlo) v = -INFINITY;
               s[mt][n][hr * 2 + i] = v;
               mx = fmaxf(mx, v);
@@ -697,7 +648,7 @@ __global__ void __launch_bounds__(128, (D <= 128 && MT == 1) ? 4 : 1) attn_split
           for (int n = 0; n < 2; ++n)
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-              const float v = s[mt][n][hr * 2 + i] * (FP8 ? q_mul[mt][hr] : sc_log2);
+              const float v = s[mt][n][hr * 2 + i] * sc_log2;
               s[mt][n][hr * 2 + i] = v;
               mx = fmaxf(mx, v);
             }

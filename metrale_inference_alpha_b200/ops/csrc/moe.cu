@@ -25,7 +25,7 @@ constexpr int kMaxPerLane = 16;  // 512 experts / 32 lanes
 __global__ void __launch_bounds__(128)
 route_kernel(const float* __restrict__ logits, long long ld, int T, int E, int K, int mode,
              const float* __restrict__ bias, int n_group, int topk_group, int renorm, float scaling,
-             float* __restrict__ out_w, int* __restrict__ out_id) {
+             float* __restrict__ out_w, int* __restrict__ out_id, int out_ld, int shared_id, int gate_col) {
   const int tok = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (tok >= T) return;
@@ -141,8 +141,14 @@ route_kernel(const float* __restrict__ logits, long long ld, int T, int E, int K
   if (lane < K) {
     float w = my_w;
     if (renorm) w = w / (wsum + (mode == 0 ? 0.f : 1e-20f));
-    out_w[(size_t)tok * K + lane] = w * scaling;
-    out_id[(size_t)tok * K + lane] = my_id;
+    out_w[(size_t)tok * out_ld + lane] = w * scaling;
+    out_id[(size_t)tok * out_ld + lane] = my_id;
+  }
+  // an always-selected shared expert rides along as slot K: its weight is 1 or the sigmoid of an
+  // extra logit column (the shared-expert gate row appended to the router weight)
+  if (shared_id >= 0 && lane == K) {
+    out_w[(size_t)tok * out_ld + K] = gate_col >= 0 ? 1.f / (1.f + __expf(-x[gate_col])) : 1.f;
+    out_id[(size_t)tok * out_ld + K] = shared_id;
   }
 }
 
@@ -303,7 +309,20 @@ int mb_moe_route(const float* logits, long long ld, int T, int E, int K, int mod
     return MB_ERR_BAD_ARG;
   if (n_group > 1 && (E % n_group || n_group > 32 || topk_group > n_group)) return MB_ERR_BAD_ARG;
   route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(logits, ld, T, E, K, mode, bias, n_group, topk_group,
-                                               renorm, scaling, out_w, out_id);
+                                               renorm, scaling, out_w, out_id, K, -1, -1);
+  return (int)cudaGetLastError();
+}
+
+// As mb_moe_route, with the outputs [T, K + 1]: slot K of every token is expert `shared_id` with
+// weight sigmoid(logits[gate_col]) (or 1 when gate_col < 0). Top-k runs over the first E columns.
+int mb_moe_route_shared(const float* logits, long long ld, int T, int E, int K, int mode, const float* bias,
+                        int n_group, int topk_group, int renorm, float scaling, float* out_w, int* out_id,
+                        int shared_id, int gate_col, cudaStream_t stream) {
+  if (!logits || !out_w || !out_id || T <= 0 || E <= 0 || E > 512 || K <= 0 || K >= 32 || K > E || shared_id < 0)
+    return MB_ERR_BAD_ARG;
+  if (n_group > 1 && (E % n_group || n_group > 32 || topk_group > n_group)) return MB_ERR_BAD_ARG;
+  route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(logits, ld, T, E, K, mode, bias, n_group, topk_group,
+                                               renorm, scaling, out_w, out_id, K + 1, shared_id, gate_col);
   return (int)cudaGetLastError();
 }
 

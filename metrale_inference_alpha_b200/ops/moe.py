@@ -27,6 +27,7 @@ class GroupedExperts:
     n_gate_up: int
     n_down: int
     interleaved: bool
+    shared_slot: Optional[int] = None     # local expert index of a folded-in shared expert (every token routes to it)
 
 
 def stack_experts(experts) -> Optional[GroupedExperts]:

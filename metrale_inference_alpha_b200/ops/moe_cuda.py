@@ -26,6 +26,28 @@ _native.register_optional("mb_moe_finish", [c.c_void_p, c.c_longlong, c.c_void_p
                                            c.c_void_p])
 
 
+_native.register_optional("mb_moe_route_shared", [c.c_void_p, c.c_longlong, c.c_int, c.c_int, c.c_int, c.c_int, c.c_void_p,
+                                                 c.c_int, c.c_int, c.c_int, c.c_float, c.c_void_p, c.c_void_p,
+                                                 c.c_int, c.c_int, c.c_void_p])
+
+
+def route_shared_cuda(logits: torch.Tensor, cfg, bias, shared_id: int, gate_col: int):
+    """Routing over the first `num_experts` logit columns plus an always-on slot for the shared
+    expert: returns weights / ids [T, k + 1]."""
+    T = logits.shape[0]
+    E, K = cfg.num_experts, cfg.experts_per_token
+    w = torch.empty(T, K + 1, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(T, K + 1, dtype=torch.int32, device=logits.device)
+    mode = 0 if cfg.router == "softmax" else 1
+    rc = _native.lib().mb_moe_route_shared(_ptr(logits), logits.stride(0), T, E, K, mode, _ptr(bias),
+                                           cfg.router_n_group if mode else 1, cfg.router_topk_group if mode else 1,
+                                           int(cfg.router_renormalize), float(cfg.router_scaling if mode else 1.0),
+                                           _ptr(w), _ptr(idx), shared_id, gate_col, _stream())
+    _native.check(rc, "moe_route_shared")
+    _count()
+    return w, idx
+
+
 def route_cuda(logits: torch.Tensor, cfg, bias=None):
     T, E = logits.shape
     K = cfg.experts_per_token

@@ -128,6 +128,7 @@ class MoeW:
     shared_gate: Optional[QuantWeight] = None
     shared_replicated: bool = False                        # expert parallelism keeps the whole shared expert on every rank
     grouped: Optional[object] = None                       # stacked device layout for the grouped GEMM
+    router_ext: Optional[QuantWeight] = None               # router rows + the shared expert's gate row (shared expert folded into `grouped`)
 
 
 @dataclass

@@ -94,8 +94,19 @@ def moe(ld, p: str) -> MoeW:
         if ld.src.has(f"{p}.shared_expert_gate.weight"):
             w.shared_gate = ld.lin(f"{p}.shared_expert_gate", quant=False)
     if ld.dev.type == "cuda":
-        from ..ops import moe as moe_ops
-        w.grouped = moe_ops.stack_experts(w.experts)
+        from ..ops import concat_weights, moe as moe_ops
+        sh = w.shared
+        fold = (sh is not None and w.experts and not w.shared_replicated and lo == 0 and hi == c.num_experts
+                and c.num_experts < 512 and c.experts_per_token < 31
+                and sh.gate_up.N == w.experts[0].gate_up.N and sh.down.K == w.experts[0].down.K
+                and sh.gate_up.fmt == w.experts[0].gate_up.fmt and sh.interleaved == w.experts[0].interleaved
+                and (w.shared_gate is None or w.shared_gate.N == 1))
+        w.grouped = moe_ops.stack_experts(w.experts + ([sh] if fold else []))
+        if fold:
+            # the shared expert becomes expert `num_experts` of the stack (every token routes to it),
+            # and its sigmoid gate row is appended to the router weight
+            w.grouped.shared_slot = len(w.experts)
+            w.router_ext = concat_weights([w.router] + ([w.shared_gate] if w.shared_gate is not None else []))
     return w
 
 
