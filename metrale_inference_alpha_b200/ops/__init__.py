@@ -772,6 +772,10 @@ def configure(attn_part_tokens: Optional[int] = None) -> None:
         _ATTN_PART_TOKENS = int(attn_part_tokens)
 
 
+# prefill chunks of >= 128 query rows at head_dim 128 take the tcgen05 / TMEM kernel
+_ATTN_TC = os.environ.get("METRALE_ATTN_TC", "0") == "1"
+
+
 def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_len, ctx_len, *,
                     max_q_len: int, max_ctx: int, scale: float, k_scale=None, v_scale=None,
                     window: int = 0, force_mode: int = 0, part_tokens: int = 0, quant_out: float = 0.0):
@@ -804,6 +808,17 @@ def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_l
         return _attention_rowwise(q, k_cache, v_cache, block_table, q_start, q_len, ctx_len,
                                   max_ctx=max_ctx, scale=scale, k_scale=k_scale, v_scale=v_scale,
                                   window=window)
+    if force_mode == 3 or (force_mode == 0 and _ATTN_TC and D == 128 and window == 0 and max_q_len >= 128):
+        # prefill chunks: both products on tcgen05 with TMEM accumulators (csrc/attention_tc.cu)
+        t = _native.AttnTcArgs()
+        t.q, t.k_cache, t.v_cache, t.block_table = _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table)
+        t.q_start, t.q_len, t.ctx_len = _ptr(q_start), _ptr(q_len), _ptr(ctx_len)
+        t.k_scale, t.v_scale, t.out, t.status = _ptr(k_scale), _ptr(v_scale), _ptr(out), _ptr(rt.status)
+        t.num_blocks, t.max_blocks, t.num_seqs, t.max_q_len = nb, block_table.stride(0), S, max_q_len
+        t.Hq, t.Hkv, t.D, t.block_size, t.cache_fp8, t.scale = Hq, Hkv, D, bs, int(k_cache.dtype == torch.uint8), scale
+        _native.check(L.mb_attn_prefill_tc(C.byref(t), _stream()), "attn_prefill_tc")
+        _count()
+        return out
     a = _native.AttnArgs()
     a.q, a.k_cache, a.v_cache = _ptr(q), _ptr(k_cache), _ptr(v_cache)
     a.block_table, a.max_blocks = _ptr(block_table), block_table.stride(0)

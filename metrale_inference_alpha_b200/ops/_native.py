@@ -45,6 +45,16 @@ class RowArgs(C.Structure):
     ]
 
 
+class AttnTcArgs(C.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("block_table", c_void_p),
+        ("q_start", c_void_p), ("q_len", c_void_p), ("ctx_len", c_void_p), ("k_scale", c_void_p), ("v_scale", c_void_p),
+        ("out", c_void_p), ("status", c_void_p), ("num_blocks", c_ll),
+        ("max_blocks", c_int), ("num_seqs", c_int), ("max_q_len", c_int), ("Hq", c_int), ("Hkv", c_int), ("D", c_int),
+        ("block_size", c_int), ("cache_fp8", c_int), ("scale", c_float),
+    ]
+
+
 class A16Args(C.Structure):
     _fields_ = [
         ("kind", c_int), ("M", c_int), ("N", c_int), ("K", c_int), ("ldx", c_int), ("ldo", c_int),
@@ -121,6 +131,8 @@ def lib():
     for fn in (L.mb_a16_gemv, L.mb_a16_dequant):
         fn.argtypes = [P(A16Args), c_void_p]
         fn.restype = c_int
+    L.mb_attn_prefill_tc.argtypes = [P(AttnTcArgs), c_void_p]
+    L.mb_attn_prefill_tc.restype = c_int
     L.mb_gguf_dequant.argtypes = [c_int, c_void_p, c_ll, c_void_p, c_void_p]
     L.mb_gguf_dequant.restype = c_int
     L.mb_gemm_counter_bytes.argtypes = []

@@ -25,6 +25,8 @@ LEVERS: Dict[str, str] = {
     "METRALE_NATIVE_RUNTIME": "0 = keep allocator / prefix index / JSON grammar on the Python implementations",
     "METRALE_NVLS": "fused collectives: 0 = one peer store per rank, 1 = NVLink multicast stores, 2 = reduction inside the switch (multimem.ld_reduce)",
     "METRALE_NO_FUSED_COLLECTIVES": "1 = NCCL collectives after plain GEMMs",
+    "METRALE_MOE_FOLD_SHARED": "0 = the shared expert keeps its own dense GEMMs instead of riding in the grouped expert stack",
+    "METRALE_ATTN_TC": "0 = prefill attention stays on the mma.sync kernel instead of the tcgen05 / TMEM kernel",
 }
 
 

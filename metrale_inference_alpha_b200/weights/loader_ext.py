@@ -96,7 +96,9 @@ def moe(ld, p: str) -> MoeW:
     if ld.dev.type == "cuda":
         from ..ops import concat_weights, moe as moe_ops
         sh = w.shared
-        fold = (sh is not None and w.experts and not w.shared_replicated and lo == 0 and hi == c.num_experts
+        import os
+        fold = (os.environ.get("METRALE_MOE_FOLD_SHARED", "1") != "0"
+                and sh is not None and w.experts and not w.shared_replicated and lo == 0 and hi == c.num_experts
                 and c.num_experts < 512 and c.experts_per_token < 31
                 and sh.gate_up.N == w.experts[0].gate_up.N and sh.down.K == w.experts[0].down.K
                 and sh.gate_up.fmt == w.experts[0].gate_up.fmt and sh.interleaved == w.experts[0].interleaved
@@ -106,7 +108,13 @@ def moe(ld, p: str) -> MoeW:
             # the shared expert becomes expert `num_experts` of the stack (every token routes to it),
             # and its sigmoid gate row is appended to the router weight
             w.grouped.shared_slot = len(w.experts)
-            w.router_ext = concat_weights([w.router] + ([w.shared_gate] if w.shared_gate is not None else []))
+            parts = [w.router] + ([w.shared_gate] if w.shared_gate is not None else [])
+            n = sum(p_.N for p_ in parts)
+            if n % 8:                                       # logit rows stay 32-byte aligned
+                from ..ops import QuantWeight
+                z = torch.zeros(8 - n % 8, w.router.K, dtype=w.router.data.dtype, device=w.router.data.device)
+                parts.append(QuantWeight("bf16", z.shape[0], w.router.K, z))
+            w.router_ext = concat_weights(parts)
     return w
 
 

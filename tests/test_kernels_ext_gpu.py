@@ -438,8 +438,9 @@ def test_mla_block_on_gpu_matches_the_cpu_restatement():
                               max_position_embeddings=512), name="tiny-mla")
     toks = torch.randint(1, 1024, (37,), generator=torch.Generator().manual_seed(8)).tolist()
     logits = {}
+    from metrale_inference_alpha_b200.weights.source import SyntheticSource
     for dev in ("cpu", DEV):
-        w = load_weights(cfg, None, device=dev, seed=3)
+        w = load_weights(cfg, SyntheticSource(cfg, seed=3, device="cpu"), device=dev)      # the same checkpoint on both devices
         r = ModelRunner(cfg, w, dev, num_blocks=16, sched=SchedulerConfig(max_num_seqs=2, max_model_len=256), use_graphs=False)
         blocks = [1, 2, 3, 4]
         out = []

@@ -377,6 +377,16 @@ def _cache(nb, bs, Hkv, D, fp8):
 
 
 @pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("q_lens,ctx_lens", [([128], [128]), ([200, 130], [200, 391]), ([384, 5, 131], [384, 70, 400]),
+                                             ([1024], [1024])])
+def test_prefill_attention_on_tcgen05_matches_fp32_oracle(fp8, q_lens, ctx_lens):
+    """Both products of a 128-row query tile as tcgen05.mma with TMEM accumulators
+    (csrc/attention_tc.cu): fresh prefills, chunks that continue a cached prefix, ragged tails,
+    short sequences in the same launch, GQA (8 query heads per 2 KV heads), bf16 and e4m3 caches."""
+    _attn_case(fp8, 128, 8, 2, q_lens, ctx_lens, force_mode=3)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
 @pytest.mark.parametrize("D,rot", [(128, 128), (64, 64), (256, 64), (64, 32), (128, 32)])
 def test_rope_kvwrite(fp8, D, rot):
     M, Hq, Hkv, bs, nb = 23, 8, 2, 16, 12
