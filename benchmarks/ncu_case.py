@@ -50,6 +50,26 @@ def main():
         for _ in range(a.iters):
             ops.paged_attention(q, kc, vc, bt, qs, ql, cl, max_q_len=1, max_ctx=2048, scale=1 / math.sqrt(D),
                                 k_scale=sc, v_scale=sc)
+    elif a.op == "prefill_attn":
+        # one sequence of --ctx query tokens over its own keys (fresh prefill), 40 / 8 heads of 128, e4m3 cache:
+        # the tcgen05 / TMEM kernel (csrc/attention_tc.cu); --fmt bf16 for a bf16 cache
+        Hq, Hkv, D, bs, q = 40, 8, 128, 16, a.ctx
+        nblk = (q + bs - 1) // bs
+        if a.fmt == "bf16":
+            kc = torch.randn(nblk + 1, bs, Hkv, D, device=DEV).to(torch.bfloat16)
+            vc = torch.randn(nblk + 1, bs, Hkv, D, device=DEV).to(torch.bfloat16)
+            sc = None
+        else:
+            kc = torch.randint(32, 100, (nblk + 1, bs, Hkv, D), dtype=torch.uint8, device=DEV)
+            vc = torch.randint(32, 100, (nblk + 1, bs, Hkv, D), dtype=torch.uint8, device=DEV)
+            sc = torch.tensor([0.05], device=DEV)
+        bt = (torch.arange(nblk, device=DEV, dtype=torch.int32) + 1).view(1, nblk).contiguous()
+        qq = torch.randn(q, Hq, D, device=DEV).to(torch.bfloat16)
+        ql = torch.tensor([q], dtype=torch.int32, device=DEV)
+        qs = torch.zeros(1, dtype=torch.int32, device=DEV)
+        for _ in range(a.iters):
+            ops.paged_attention(qq, kc, vc, bt, qs, ql, ql, max_q_len=q, max_ctx=q, scale=1 / math.sqrt(D),
+                                k_scale=sc, v_scale=sc, force_mode=3)
     elif a.op == "mla":
         # absorbed MLA decode: 128 heads of 576-wide latent queries against a [blocks, 16, 1, 576] latent cache
         from metrale_inference_alpha_b200.ops import mla_cuda

@@ -773,7 +773,7 @@ def configure(attn_part_tokens: Optional[int] = None) -> None:
 
 
 # prefill chunks of >= 128 query rows at head_dim 128 take the tcgen05 / TMEM kernel
-_ATTN_TC = os.environ.get("METRALE_ATTN_TC", "0") == "1"
+_ATTN_TC = os.environ.get("METRALE_ATTN_TC", "1") != "0"
 
 
 def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_len, ctx_len, *,

@@ -86,7 +86,6 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
   const int qt = blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5;
   mb::pdl_wait();
-  mb::pdl_launch_dependents();
   const int qlen = p.q_len[seq], ctx = p.ctx_len[seq], qs = p.q_start[seq];
   const int q0 = qt * kQ;
   if (q0 >= qlen) return;
@@ -111,6 +110,9 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
   mb::tc_fence_before();
   __syncthreads();
   mb::tc_fence_after();
+  // only now may a dependent kernel start early on this SM: it would allocate TMEM before its own
+  // dependency wait, and must not do so while this CTA still has to get its columns
+  mb::pdl_launch_dependents();
   const uint32_t tmem = s_tmem;
   const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 TMEM lanes
   constexpr uint32_t kIdescS = mb::umma_idesc(1, 1, kQ, kT);
@@ -124,60 +126,66 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
   const int tiles = (ctx - qlen + last_row + 1 + kT - 1) / kT;        // up to the last row's limit
   const float kmul = FP8 ? (*p.k_scale) * 256.f : 1.f;
   const float sc_log2 = p.scale * kmul * 1.44269504088896f;
-  float o[kD];
-#pragma unroll
-  for (int i = 0; i < kD; ++i) o[i] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
   uint32_t ph_s = 0, ph_o = 0;
   bool ok = true;
   const size_t esz = FP8 ? 1 : 2;
   const size_t row_pitch = (size_t)p.Hkv * kD * esz;
   const int s_tok = tid & 63, s_half = tid >> 6;                      // staging: one token, one 64-dim half
+  // raw cache bytes of this thread's (token, half) of the next tile, fetched one tile ahead
+  constexpr int kRaw = FP8 ? 4 : 8;
+  uint4 kraw[kRaw], vraw[kRaw];
+  auto fetch = [&](int jt) {
+    const int tok = jt * kT + s_tok;
+    if (jt < tiles && tok < ctx) {
+      long long blk = bt[tok / p.block_size];
+      if (blk < 0 || blk >= p.num_blocks) {
+        if (p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
+        blk = 0;
+      }
+      const size_t off = ((size_t)blk * p.block_size + (tok % p.block_size)) * row_pitch + (size_t)kvh * kD * esz +
+                         (size_t)s_half * 64 * esz;
+      const uint4* ks = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.k_cache) + off);
+      const uint4* vs = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.v_cache) + off);
+#pragma unroll
+      for (int c = 0; c < kRaw; ++c) {
+        kraw[c] = __ldg(ks + c);
+        vraw[c] = __ldg(vs + c);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < kRaw; ++c) kraw[c] = vraw[c] = make_uint4(0, 0, 0, 0);
+    }
+  };
+  fetch(0);
 
   for (int j = 0; j < tiles; ++j) {
-    // ---- stage K (K-major) and V (transposed) of tokens [j * 64, j * 64 + 64)
-    {
-      const int tok = j * kT + s_tok;
-      uint4 kv[8], vv[8];
-      if (tok < ctx) {
-        long long blk = bt[tok / p.block_size];
-        if (blk < 0 || blk >= p.num_blocks) {
-          if (p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
-          blk = 0;
-        }
-        const size_t off = ((size_t)blk * p.block_size + (tok % p.block_size)) * row_pitch + (size_t)kvh * kD * esz +
-                           (size_t)s_half * 64 * esz;
-        const uint8_t* ks = reinterpret_cast<const uint8_t*>(p.k_cache) + off;
-        const uint8_t* vs = reinterpret_cast<const uint8_t*>(p.v_cache) + off;
-        if constexpr (FP8) {
+    // ---- the previous tile's P V has to be done before its operands are overwritten (and O read)
+    if (j > 0) {
+      ok = mb::mbar_wait(&bar_o, ph_o, p.status, MB_ST_TIMEOUT_MMA) && ok;
+      ph_o ^= 1;
+      mb::tc_fence_after();
+    }
+    // ---- stage K (K-major) and V (transposed) of tokens [j * 64, j * 64 + 64) from the registers
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            kv[c] = widen8(*reinterpret_cast<const uint2*>(ks + c * 8));
-            vv[c] = widen8(*reinterpret_cast<const uint2*>(vs + c * 8));
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            kv[c] = *reinterpret_cast<const uint4*>(ks + c * 16);
-            vv[c] = *reinterpret_cast<const uint4*>(vs + c * 16);
-          }
-        }
+    for (int c = 0; c < 8; ++c) {
+      uint4 kv, vv;
+      if constexpr (FP8) {
+        const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kraw[c >> 1]);
+        const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vraw[c >> 1]);
+        kv = widen8(make_uint2(kw[(c & 1) * 2], kw[(c & 1) * 2 + 1]));
+        vv = widen8(make_uint2(vw[(c & 1) * 2], vw[(c & 1) * 2 + 1]));
       } else {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) kv[c] = vv[c] = make_uint4(0, 0, 0, 0);
+        kv = kraw[c];
+        vv = vraw[c];
       }
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(sK + s_half * (kT * 128) + sw_off(s_tok, c)) = kv[c];
+      *reinterpret_cast<uint4*>(sK + s_half * (kT * 128) + sw_off(s_tok, c)) = kv;
       // V^T: element (dim d, token t) at row d, byte 2 t (chunk t / 8)
+      const uint16_t* e = reinterpret_cast<const uint16_t*>(&vv);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint16_t* e = reinterpret_cast<const uint16_t*>(&vv[c]);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int d = s_half * 64 + c * 8 + i;
-          *reinterpret_cast<uint16_t*>(sV + sw_off(d, s_tok >> 3) + (s_tok & 7) * 2) = e[i];
-        }
+      for (int i = 0; i < 8; ++i) {
+        const int d = s_half * 64 + c * 8 + i;
+        *reinterpret_cast<uint16_t*>(sV + sw_off(d, s_tok >> 3) + (s_tok & 7) * 2) = e[i];
       }
     }
     fence_async_smem();
@@ -194,11 +202,13 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
                        mb::umma_desc_sw128(aK + h * (kT * 128) + s * 32), kIdescS, (h | s) != 0);
       mb::tc_commit(&bar_s);
     }
+    fetch(j + 1);                                       // its latency hides behind both products and the softmax
     ok = mb::mbar_wait(&bar_s, ph_s, p.status, MB_ST_TIMEOUT_MMA) && ok;
     ph_s ^= 1;
     mb::tc_fence_after();
-    // ---- online softmax on this thread's row
-    float alpha = 1.f;
+    // ---- online softmax on this thread's row. The running maximum only moves when the new one is
+    // more than 2^8 above it (probabilities then stay below 256, exact enough in bf16 / fp32), so the
+    // O accumulator in TMEM is rescaled on few tiles.
     {
       float sv[kT];
 #pragma unroll
@@ -211,9 +221,24 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
         sv[i] = v;
         mx = fmaxf(mx, v);
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      alpha = exp2f(m_run - m_use);
+      float alpha = 1.f;
+      const bool move = mx > m_run + 8.f;                // also true on a row's first finite tile
+      if (move) {
+        alpha = exp2f(m_run - mx);                       // 0 when the row had seen nothing yet
+        m_run = mx;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, move)) {
+#pragma unroll
+        for (int c = 0; c < kD / 16; ++c) {
+          float ov[16];
+          mb::tmem_ld16(t_row + 64 + c * 16, ov);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) ov[i] *= alpha;
+          mb::tmem_st16(t_row + 64 + c * 16, ov);
+        }
+        mb::tmem_st_wait();
+      }
+      const float m_use = m_run == -INFINITY ? 0.f : m_run;
       float rs = 0.f;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -230,46 +255,42 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
         *reinterpret_cast<uint4*>(sP + sw_off(tid, c)) = pk;
       }
       l_run = l_run * alpha + rs;
-      m_run = m_new;
     }
     fence_async_smem();
     mb::tc_fence_before();
-    __syncthreads();
-    // ---- O_j = P V
+    // a wait that ran out in any thread (the status word says so) ends the loop for the whole CTA
+    ok = __syncthreads_and(ok) != 0;
+    if (!ok) break;
+    // ---- O += P V (accumulated in TMEM across tiles)
     if (tid == 0) {
       mb::tc_fence_after();
 #pragma unroll
       for (int s = 0; s < 4; ++s)
-        mb::umma_f16(tmem + 64, mb::umma_desc_sw128(aP + s * 32), mb::umma_desc_sw128(aV + s * 32), kIdescO, s != 0);
+        mb::umma_f16(tmem + 64, mb::umma_desc_sw128(aP + s * 32), mb::umma_desc_sw128(aV + s * 32), kIdescO,
+                     (j | s) != 0);
       mb::tc_commit(&bar_o);
     }
+  }
+  if (ok && tiles > 0) {
     ok = mb::mbar_wait(&bar_o, ph_o, p.status, MB_ST_TIMEOUT_MMA) && ok;
-    ph_o ^= 1;
     mb::tc_fence_after();
+  }
+  if (ok) {                                               // uniform: tcgen05.ld is a whole-warp instruction
+    const float vmul = FP8 ? (*p.v_scale) * 256.f : 1.f;
+    const float inv = l_run > 0.f ? vmul / l_run : 0.f;
+    uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)(qs + (row_ok ? qi : 0)) * p.Hq + head) * kD);
 #pragma unroll
     for (int c = 0; c < kD / 16; ++c) {
       float ov[16];
-      mb::tmem_ld16(t_row + 64 + c * 16, ov);
+      mb::tmem_ld16(t_row + 64 + c * 16, ov);             // every lane reads; only rows of the sequence store
 #pragma unroll
-      for (int i = 0; i < 16; ++i) o[c * 16 + i] = o[c * 16 + i] * alpha + ov[i];
-    }
-    mb::tc_fence_before();
-    // the tiles and both accumulators are free for the next iteration; a wait that ran out in any
-    // thread (the status word says so) ends the loop for the whole CTA
-    ok = __syncthreads_and(ok) != 0;
-    if (!ok) break;
-  }
-  if (row_ok && ok) {
-    const float vmul = FP8 ? (*p.v_scale) * 256.f : 1.f;
-    const float inv = l_run > 0.f ? vmul / l_run : 0.f;
-    uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)(qs + qi) * p.Hq + head) * kD);
+      for (int h2 = 0; h2 < 2; ++h2) {
+        uint4 w;
+        __nv_bfloat162* wb = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      uint4 w;
-      __nv_bfloat162* wb = reinterpret_cast<__nv_bfloat162*>(&w);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) wb[i] = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
-      dst[c] = w;
+        for (int i = 0; i < 4; ++i) wb[i] = __floats2bfloat162_rn(ov[h2 * 8 + 2 * i] * inv, ov[h2 * 8 + 2 * i + 1] * inv);
+        if (row_ok) dst[c * 2 + h2] = w;
+      }
     }
   }
   mb::tc_fence_before();
