@@ -33,19 +33,20 @@ def gdn_block(dec, x, lw, batch, pool, sidx: int):
     if stash is not None:
         stash.layers[sidx] = ("gdn", lw, qkvz, conv_out, ba)
     z = qkvz[:, 2 * QK + V:]
-    y = ops.row_op(core, ACT_FOR_WEIGHT[w.out.fmt], ops.IN_GATED_RMSNORM, gate=z, w=_tile(w.norm_w, vh),
+    y = ops.row_op(core, ACT_FOR_WEIGHT[w.out.fmt], ops.IN_GATED_RMSNORM, gate=z, w=_tile(w, w.norm_w, vh),
                    group=vd, eps=c.rms_eps)[0]
     return dec.tp.linear_reduce(y, w.out, residual=x, defer=True)
 
 
-_tile_cache = {}
-
-
-def _tile(w: torch.Tensor, n: int) -> torch.Tensor:
-    key = (w.data_ptr(), n)
-    if key not in _tile_cache:
-        _tile_cache[key] = w.repeat(n).contiguous()
-    return _tile_cache[key]
+def _tile(owner, w: torch.Tensor, n: int) -> torch.Tensor:
+    """`w` repeated n times (the per-head norm weight laid out for all heads of a row), built once
+    and kept on the layer's own weight object: a cache keyed by anything else (a device address,
+    say) would outlive the weights and hand a later model another layer's values."""
+    t = getattr(owner, "_norm_w_tiled", None)
+    if t is None or t.numel() != w.numel() * n or t.device != w.device:
+        t = w.repeat(n).contiguous()
+        owner._norm_w_tiled = t
+    return t
 
 
 def mamba2_block(dec, x, lw, batch, pool, sidx: int):
