@@ -95,6 +95,11 @@ def _sampling_from(body: Dict[str, Any], cfg: ServerConfig, max_key="max_tokens"
 
 def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=None) -> FastAPI:
     cfg = cfg or ServerConfig()
+    # routes and the scheduler thread hold proxies, so `/v1/models/swap` can replace the engine (and
+    # its tokenizer) behind a listener that stays up (server/model_swap.py)
+    from .model_swap import Proxy
+    engine = engine if isinstance(engine, Proxy) else Proxy(engine)
+    tokenizer = tokenizer if isinstance(tokenizer, Proxy) else Proxy(tokenizer)
     aeng = AsyncEngine(engine, tokenizer, control)
 
     @contextlib.asynccontextmanager

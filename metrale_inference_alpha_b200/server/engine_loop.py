@@ -139,10 +139,61 @@ class AsyncEngine:
         if finished:
             self._live.pop(o.request_id, None)
 
+    def request_swap(self, build, timeout_s: float = 600.0):
+        """Replace the engine without closing the listener: `build()` returns the new engine (and
+        optionally a tokenizer) and runs on the scheduler thread once nothing is in flight, so no
+        step ever sees two models. New requests queue behind the swap. Returns the new engine or
+        raises what `build` raised (the old engine then keeps serving). Role of the reference's
+        model hot-swap (``crates/server/src/main_modules/model_swap.rs``)."""
+        done = threading.Event()
+        box = {}
+        self._in.put(("swap", None, (build, box, done), None))
+        if not done.wait(timeout_s):
+            raise TimeoutError("model swap did not finish in time")
+        if "error" in box:
+            raise box["error"]
+        return box["engine"]
+
+    def _swap(self, payload) -> None:
+        build, box, done = payload
+        try:
+            old = self.engine.target() if hasattr(self.engine, "target") else self.engine
+            old.flush() if hasattr(old, "flush") else None
+            res = build()
+            new, tok = res if isinstance(res, tuple) else (res, None)
+            if hasattr(self.engine, "swap"):
+                self.engine.swap(new)
+            else:
+                self.engine = new
+            if tok is not None:
+                if hasattr(self.tokenizer, "swap"):
+                    self.tokenizer.swap(tok)
+                else:
+                    self.tokenizer = tok
+            box["engine"] = new
+            del old
+            import gc
+            gc.collect()
+            try:
+                import torch
+                if torch.cuda.is_available():
+                    torch.cuda.empty_cache()
+            except Exception:
+                pass
+        except Exception as e:
+            box["error"] = e
+        finally:
+            done.set()
+
     def _run(self) -> None:
         eng = self.engine
+        pending_swap = None
         while not self._stop.is_set():
             try:
+                if pending_swap is not None and not eng.has_work():
+                    self._swap(pending_swap)
+                    pending_swap = None
+                    eng = self.engine
                 block = not eng.has_work()
                 ops = []
                 while True:
@@ -154,7 +205,18 @@ class AsyncEngine:
                 if self.control is not None:
                     self.control.check_peers()
                     ops = self.control.exchange(ops)
+                if pending_swap is not None:
+                    # requests that arrive while the old engine drains wait for the new one
+                    held = [o for o in ops if o[0] == "add"]
+                    ops = [o for o in ops if o[0] != "add"]
+                    for o in held:
+                        self._in.put(o)
+                    if held and not eng.has_work():
+                        continue
                 for kind, rid, ids, params in ops:
+                    if kind == "swap":
+                        pending_swap = ids
+                        continue
                     if kind == "add":
                         try:
                             eng.add_request(ids, params, request_id=rid)

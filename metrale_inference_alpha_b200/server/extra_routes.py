@@ -133,6 +133,27 @@ def install(app: FastAPI, *, engine, tokenizer, cfg, telemetry, conversations: C
             return openai_error(404, f"The model '{model_id}' does not exist", "model", "model_not_found")
         return {"id": model_id, "object": "model", "owned_by": "metrale-b200", "max_model_len": engine.sched_cfg.max_model_len}
 
+    @app.post("/v1/models/swap")
+    async def model_swap(request: Request):
+        """Load another model (preset name or checkpoint directory) behind the running listener.
+        In-flight requests finish on the old model, later ones are answered by the new one."""
+        b = await _body(request)
+        model = b.get("model")
+        if not model:
+            return openai_error(400, "`model` is required", "model")
+        aeng = app.state.async_engine
+        if aeng.control is not None:
+            return openai_error(501, "model swap is not available on a multi-rank engine", code="not_implemented")
+        from .model_swap import build_like
+        try:
+            new = await asyncio.get_running_loop().run_in_executor(
+                None, lambda: aeng.request_swap(lambda: build_like(engine.target(), model, b.get("tokenizer"))))
+        except (OSError, ValueError, KeyError, RuntimeError, TimeoutError) as e:
+            return openai_error(400, f"cannot load model: {e}", "model", "model_swap_failed")
+        if b.get("served_model_name"):
+            cfg.model_name = b["served_model_name"]
+        return {"status": "swapped", "model": new.cfg.name, "served_model_name": cfg.model_name, "swaps": engine.swaps}
+
     @app.post("/v1/lora/load")
     async def lora_load(request: Request):
         b = await _body(request)

@@ -945,3 +945,26 @@ def test_responses_api_streams_typed_events(client):
     # the streamed response was stored: a follow-up continues it
     r = client.post("/v1/responses", json={"input": "more", "previous_response_id": final["id"], "max_output_tokens": 2}).json()
     assert r["status"] == "completed" and r["previous_response_id"] == final["id"]
+
+
+def test_model_swap_keeps_the_listener_and_answers_with_the_new_model():
+    """POST /v1/models/swap: the app, its routes and the scheduler thread stay; requests before the
+    swap are answered by the old model, requests after it by the new one (a different preset gives
+    different greedy tokens for the same prompt), and a bad model name leaves the old one serving."""
+    from fastapi.testclient import TestClient
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.server.app import ServerConfig, create_app
+    from metrale_inference_alpha_b200.server.tokenizer import load_tokenizer
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=128))
+    tok = load_tokenizer(None, eng.cfg.vocab_size)
+    body = {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 8, "temperature": 0, "return_token_ids": True}
+    with TestClient(create_app(eng, tok, ServerConfig(model_name="m"))) as c:
+        a = c.post("/v1/chat/completions", json=body).json()["choices"][0]["token_ids"]
+        assert c.post("/v1/models/swap", json={"model": "no-such-model"}).status_code == 400
+        assert c.post("/v1/chat/completions", json=body).json()["choices"][0]["token_ids"] == a
+        r = c.post("/v1/models/swap", json={"model": "tiny-hybrid-moe", "served_model_name": "m2"})
+        assert r.status_code == 200 and r.json()["swaps"] == 1 and r.json()["served_model_name"] == "m2"
+        b = c.post("/v1/chat/completions", json=body).json()["choices"][0]["token_ids"]
+        assert len(b) == 8 and b != a
+        assert c.get("/serve-config").json()["model_config"]["arch"] == "qwen_hybrid"
+        assert c.get("/health").status_code == 200
