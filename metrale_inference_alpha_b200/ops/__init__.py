@@ -774,6 +774,8 @@ def configure(attn_part_tokens: Optional[int] = None) -> None:
 
 # prefill chunks of >= 128 query rows at head_dim 128 take the tcgen05 / TMEM kernel
 _ATTN_TC = os.environ.get("METRALE_ATTN_TC", "1") != "0"
+# 1: the V tile is staged as stored and read as an MN-major operand; 0: transposed on the way into shared memory
+_ATTN_TC_VMN = int(os.environ.get("METRALE_ATTN_TC_VMN", "0"))
 
 
 def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_len, ctx_len, *,
@@ -816,6 +818,7 @@ def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_l
         t.k_scale, t.v_scale, t.out, t.status = _ptr(k_scale), _ptr(v_scale), _ptr(out), _ptr(rt.status)
         t.num_blocks, t.max_blocks, t.num_seqs, t.max_q_len = nb, block_table.stride(0), S, max_q_len
         t.Hq, t.Hkv, t.D, t.block_size, t.cache_fp8, t.scale = Hq, Hkv, D, bs, int(k_cache.dtype == torch.uint8), scale
+        t.v_mn = _ATTN_TC_VMN
         _native.check(L.mb_attn_prefill_tc(C.byref(t), _stream()), "attn_prefill_tc")
         _count()
         return out

@@ -51,7 +51,7 @@ class AttnTcArgs(C.Structure):
         ("q_start", c_void_p), ("q_len", c_void_p), ("ctx_len", c_void_p), ("k_scale", c_void_p), ("v_scale", c_void_p),
         ("out", c_void_p), ("status", c_void_p), ("num_blocks", c_ll),
         ("max_blocks", c_int), ("num_seqs", c_int), ("max_q_len", c_int), ("Hq", c_int), ("Hkv", c_int), ("D", c_int),
-        ("block_size", c_int), ("cache_fp8", c_int), ("scale", c_float),
+        ("block_size", c_int), ("cache_fp8", c_int), ("scale", c_float), ("v_mn", c_int),
     ]
 
 

@@ -79,7 +79,7 @@ __device__ __forceinline__ uint4 widen8(uint2 v) {
   return o;
 }
 
-template <bool FP8>
+template <bool FP8, bool VMN>
 __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   // the swizzled tiles need 1024-byte alignment in the shared window (the launch reserves the slack)
@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
   const uint32_t tmem = s_tmem;
   const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 TMEM lanes
   constexpr uint32_t kIdescS = mb::umma_idesc(1, 1, kQ, kT);
-  constexpr uint32_t kIdescO = mb::umma_idesc(1, 1, kQ, kD);
+  constexpr uint32_t kIdescO = mb::umma_idesc(1, 1, kQ, kD, 0, VMN ? 1 : 0);
   const uint32_t aQ = mb::smem_u32(sQ), aK = mb::smem_u32(sK), aV = mb::smem_u32(sV), aP = mb::smem_u32(sP);
 
   const int qi = q0 + tid;
@@ -187,12 +187,17 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
         vv = vraw[c];
       }
       *reinterpret_cast<uint4*>(sK + s_half * (kT * 128) + sw_off(s_tok, c)) = kv;
-      // V^T: element (dim d, token t) at row d, byte 2 t (chunk t / 8)
-      const uint16_t* e = reinterpret_cast<const uint16_t*>(&vv);
+      if constexpr (VMN) {
+        // V as stored, [token][dim] in two 64-dim halves: read by the second product as an MN-major operand
+        *reinterpret_cast<uint4*>(sV + s_half * (kT * 128) + sw_off(s_tok, c)) = vv;
+      } else {
+        // V^T: element (dim d, token t) at row d, byte 2 t (chunk t / 8)
+        const uint16_t* e = reinterpret_cast<const uint16_t*>(&vv);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int d = s_half * 64 + c * 8 + i;
-        *reinterpret_cast<uint16_t*>(sV + sw_off(d, s_tok >> 3) + (s_tok & 7) * 2) = e[i];
+        for (int i = 0; i < 8; ++i) {
+          const int d = s_half * 64 + c * 8 + i;
+          *reinterpret_cast<uint16_t*>(sV + sw_off(d, s_tok >> 3) + (s_tok & 7) * 2) = e[i];
+        }
       }
     }
     fence_async_smem();
@@ -280,8 +285,10 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
       mb::tc_fence_after();
 #pragma unroll
       for (int s = 0; s < 4; ++s)
-        mb::umma_f16(tmem + 64, mb::umma_desc_sw128(aP + s * 32), mb::umma_desc_sw128(aV + s * 32), kIdescO,
-                     (j | s) != 0);
+        mb::umma_f16(tmem + 64, mb::umma_desc_sw128(aP + s * 32),
+                     VMN ? mb::umma_desc_sw128_mn(aV + s * 2048, kT * 128, 1024)   // 16 tokens = two 8-row groups on
+                         : mb::umma_desc_sw128(aV + s * 32),
+                     kIdescO, (j | s) != 0);
       mb::tc_commit(&bar_o);
     }
   }
@@ -329,6 +336,7 @@ struct MbAttnTcArgs {
   long long num_blocks;
   int max_blocks, num_seqs, max_q_len, Hq, Hkv, D, block_size, cache_fp8;
   float scale;
+  int v_mn;      // 1: V staged as stored and read as an MN-major operand (no transposition)
 };
 
 // Causal paged attention for prefill chunks (head dim 128). Returns 0, MB_ERR_* or a CUDA error.
@@ -346,13 +354,18 @@ extern "C" int mb_attn_prefill_tc(const MbAttnTcArgs* a, cudaStream_t stream) {
   constexpr size_t smem = 2 * kQ * 128 + 2 * kT * 128 + kD * 128 + kQ * 128 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const dim3 grid((a->max_q_len + kQ - 1) / kQ, a->Hq, a->num_seqs);
-  if (a->cache_fp8) return (int)mb::launch_kernel(attn_prefill_tc_kernel<true>, grid, dim3(128), smem, stream, p);
-  return (int)mb::launch_kernel(attn_prefill_tc_kernel<false>, grid, dim3(128), smem, stream, p);
+  if (a->v_mn) {
+    if (a->cache_fp8) return (int)mb::launch_kernel(attn_prefill_tc_kernel<true, true>, grid, dim3(128), smem, stream, p);
+    return (int)mb::launch_kernel(attn_prefill_tc_kernel<false, true>, grid, dim3(128), smem, stream, p);
+  }
+  if (a->cache_fp8) return (int)mb::launch_kernel(attn_prefill_tc_kernel<true, false>, grid, dim3(128), smem, stream, p);
+  return (int)mb::launch_kernel(attn_prefill_tc_kernel<false, false>, grid, dim3(128), smem, stream, p);
 }

@@ -83,12 +83,13 @@ class EpAllToAll:
         o = self._off(parity, what)
         return self.buf[o:o + numel * torch.tensor([], dtype=dtype).element_size()].view(dtype)
 
-    def _scatter(self, rows: torch.Tensor, dst_rank, dst_slot, meta, send_count, parity: int, which: str) -> None:
+    def _scatter(self, rows: torch.Tensor, dst_rank, dst_slot, meta, send_count, parity: int, which: str,
+                 capacity: Optional[int] = None) -> None:
         from ..ops import _count, _ptr, _stream, runtime
         a = A2aArgs()
         a.rows, a.row_ld, a.n, a.row_bytes = _ptr(rows), rows.stride(0) * rows.element_size(), rows.shape[0], self.H * 2
         a.dst_rank, a.dst_slot, a.meta, a.send_count = _ptr(dst_rank), _ptr(dst_slot), _ptr(meta), _ptr(send_count)
-        a.world, a.rank, a.capacity, a.seq = self.world, self.rank, self.capacity, self.seq
+        a.world, a.rank, a.capacity, a.seq = self.world, self.rank, capacity or self.capacity, self.seq
         a.seq_ptr = _ptr(self.seq_dev)
         zone, cnt, flag = ("x", "xcnt", "xflag") if which == "x" else ("y", "ycnt", "yflag")
         for r in range(self.world):
@@ -109,11 +110,18 @@ class EpAllToAll:
         _count()
 
     # ------------------------------------------------------------------ the MoE exchange
-    def moe(self, x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor, experts_per_rank: int, expert_fn):
+    def moe(self, x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor, experts_per_rank: int, expert_fn,
+            cap: Optional[int] = None):
         """x [T, H] bf16, routing weights / expert ids [T, K]. `expert_fn(rows bf16 [N, H], expert ids
         int32 [N, 1] (-1 = empty slot)) -> fp32 [N, H]` runs the local experts on received rows.
-        Returns fp32 [T, H] = sum_j weights[t, j] * expert_{idx[t, j]}(x[t])."""
-        T, K, W, Cp = x.shape[0], idx.shape[1], self.world, self.capacity
+        Returns fp32 [T, H] = sum_j weights[t, j] * expert_{idx[t, j]}(x[t]).
+        `cap`: rows each source may send in THIS call (the same number on every rank: the step's token
+        count is known to all of them). The landing zones are then strided by it instead of by the
+        allocation-time capacity, so the local experts run over about as many rows as were routed
+        here, not over the whole capacity (a decode step sends tens of rows, the capacity is
+        sized for a prefill chunk)."""
+        T, K, W = x.shape[0], idx.shape[1], self.world
+        Cp = self.capacity if cap is None else max(1, min(int(cap), self.capacity))
         assert T * K <= Cp and x.dtype == torch.bfloat16 and x.shape[1] == self.H
         self.seq += 1
         self.seq_dev.add_(1)
@@ -128,7 +136,7 @@ class EpAllToAll:
         send_count = onehot.sum(0).to(torch.int32)
         dest32 = torch.where(live, dest, torch.full_like(dest, -1)).to(torch.int32)
         rows = x.repeat_interleave(K, 0) if K > 1 else x                              # pair p = token p // K
-        self._scatter(rows, dest32, slot, flat.to(torch.int32), send_count, parity, "x")
+        self._scatter(rows, dest32, slot, flat.to(torch.int32), send_count, parity, "x", Cp)
         self._wait(parity, "x")
         # ---- local experts over everything that landed here
         n_cap = W * Cp
@@ -142,7 +150,7 @@ class EpAllToAll:
         back_rank = torch.where(valid, torch.arange(W, device=dev, dtype=torch.int32)[:, None].expand(W, Cp),
                                 torch.full_like(meta, -1)).reshape(-1).contiguous()
         back_slot = torch.arange(Cp, device=dev, dtype=torch.int32).repeat(W)
-        self._scatter(y.to(torch.bfloat16), back_rank, back_slot, None, rcnt, parity, "y")
+        self._scatter(y.to(torch.bfloat16), back_rank, back_slot, None, rcnt, parity, "y", Cp)
         self._wait(parity, "y")
         yz = self._local(parity, "y", torch.bfloat16, n_cap * self.H).view(n_cap, self.H)
         # ---- combine: pair p's result sits in my y zone at (dest[p], slot[p])
@@ -169,12 +177,13 @@ class EpAllToAll:
             ones = torch.ones(rows.shape[0], 1, dtype=torch.float32, device=rows.device)
             return routed_experts(dec, ar, ones, eids, w)
         out = torch.zeros(T, self.H, dtype=torch.float32, device=xb.device)
+        cap = per * idx.shape[1]                      # every rank derives the same bound from the step's token count
         if hi > lo:
             out[lo:hi] = self.moe(xb[lo:hi].contiguous(), weights[lo:hi].contiguous(), idx[lo:hi].contiguous(),
-                                  E_local, expert_fn)
+                                  E_local, expert_fn, cap=cap)
         else:
             # nothing to send, but the peers still wait for this rank's flags and rows for its experts
             dummy_x = torch.zeros(1, self.H, dtype=torch.bfloat16, device=xb.device)
             self.moe(dummy_x, torch.zeros(1, idx.shape[1], device=xb.device),
-                     torch.full((1, idx.shape[1]), -1, dtype=idx.dtype, device=xb.device), E_local, expert_fn)
+                     torch.full((1, idx.shape[1]), -1, dtype=idx.dtype, device=xb.device), E_local, expert_fn, cap=cap)
         return out

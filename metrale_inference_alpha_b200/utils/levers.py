@@ -26,6 +26,7 @@ LEVERS: Dict[str, str] = {
     "METRALE_NVLS": "fused collectives: 0 = one peer store per rank, 1 = NVLink multicast stores, 2 = reduction inside the switch (multimem.ld_reduce)",
     "METRALE_NO_FUSED_COLLECTIVES": "1 = NCCL collectives after plain GEMMs",
     "METRALE_MOE_FOLD_SHARED": "0 = the shared expert keeps its own dense GEMMs instead of riding in the grouped expert stack",
+    "METRALE_ATTN_TC_VMN": "tcgen05 prefill attention: 1 = V read as an MN-major operand (no transposition while staging), 0 = transposed",
     "METRALE_ATTN_TC": "0 = prefill attention stays on the mma.sync kernel instead of the tcgen05 / TMEM kernel",
 }
 
