@@ -775,7 +775,7 @@ def configure(attn_part_tokens: Optional[int] = None) -> None:
 # prefill chunks of >= 128 query rows at head_dim 128 take the tcgen05 / TMEM kernel
 _ATTN_TC = os.environ.get("METRALE_ATTN_TC", "1") != "0"
 # 1: the V tile is staged as stored and read as an MN-major operand; 0: transposed on the way into shared memory
-_ATTN_TC_VMN = int(os.environ.get("METRALE_ATTN_TC_VMN", "0"))
+_ATTN_TC_VMN = int(os.environ.get("METRALE_ATTN_TC_VMN", "1"))
 
 
 def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_len, ctx_len, *,

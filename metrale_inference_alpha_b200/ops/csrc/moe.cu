@@ -153,8 +153,8 @@ route_kernel(const float* __restrict__ logits, long long ld, int T, int E, int K
 }
 
 // ------------------------------------------------------------------ sort (single CTA)
-// pairs = T * K. counts/offsets in shared memory; stable order is not required (rows of one
-// expert are independent), determinism is: positions are assigned by pair index order.
+// pairs = T * K. counts / offsets in shared memory; rows of one expert are independent, so their
+// order inside the expert's range is free.
 __global__ void __launch_bounds__(1024)
 sort_kernel(const int* __restrict__ ids, int pairs, int expert_lo, int num_local, int tile_rows,
             int* __restrict__ pair_row, int* __restrict__ row_pair, int* __restrict__ expert_off,
@@ -190,18 +190,18 @@ sort_kernel(const int* __restrict__ ids, int pairs, int expert_lo, int num_local
   }
   __syncthreads();
   for (int e = tid; e <= num_local; e += nt) expert_off[e] = off[e];
-  // deterministic placement: each expert's pairs keep their pair-index order. One thread per
-  // expert walks the pair list (pairs <= a few thousand at decode; prefill uses more CTAs of
-  // the same kernel on token ranges through the host wrapper).
-  for (int e = tid; e < num_local; e += nt) {
-    int pos = off[e];
-    if (cnt[e] == 0) continue;
-    for (int i = 0; i < pairs; ++i) {
-      if (ids[i] - expert_lo == e) {
-        pair_row[i] = pos;
-        row_pair[pos] = i;
-        ++pos;
-      }
+  // placement: every thread takes pairs tid, tid + nt, ... and claims the next free row of its pair's
+  // expert with a shared-memory counter. Which row of an expert a pair lands on therefore varies from
+  // run to run, the result does not: a row's GEMM output is independent of its place in the tile and
+  // the combine reads rows through pair_row in slot order.
+  for (int e = tid; e < num_local; e += nt) cnt[e] = 0;         // reused as the running fill of each expert
+  __syncthreads();
+  for (int i = tid; i < pairs; i += nt) {
+    const int e = ids[i] - expert_lo;
+    if (e >= 0 && e < num_local) {
+      const int pos = off[e] + atomicAdd(&cnt[e], 1);
+      pair_row[i] = pos;
+      row_pair[pos] = i;
     }
   }
   for (int i = tid; i < pairs; i += nt) {

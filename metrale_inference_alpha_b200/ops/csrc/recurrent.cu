@@ -75,6 +75,79 @@ conv1d_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int C, const 
   }
 }
 
+// Time-parallel form for prefill chunks: grid (channel blocks, time blocks of kConvTb tokens, sequences).
+// A thread owns one channel of one time block: it primes its window from the three inputs in front
+// of the block (the stored state for the first block of a continued sequence, zeros for a fresh one)
+// and slides over its tokens, so every input is read once (plus the halo). The state is advanced by
+// conv1d_state_kernel afterwards (stream order keeps it from racing with the first block's reads).
+constexpr int kConvTb = 64;
+template <int TAPS>
+__global__ void __launch_bounds__(128)
+conv1d_par_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int C, const float* __restrict__ w,
+                  const float* __restrict__ bias, const float* __restrict__ state, float* __restrict__ out,
+                  SeqMeta sm, int activation, uint32_t* status) {
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  const int seq = blockIdx.z;
+  if (c >= C) return;
+  const int n = sm.q_len[seq];
+  const int t0 = blockIdx.y * kConvTb;
+  if (t0 >= n) return;
+  const int q0 = sm.q_start[seq];
+  const int slot = sm.state_slots[seq];
+  if (slot < 0 || slot >= sm.num_slots) {
+    if (status) atomicCAS(status, 0u, MB_ST_BOUNDS);
+    return;
+  }
+  float win[TAPS], wk[TAPS];
+#pragma unroll
+  for (int k = 0; k < TAPS; ++k) wk[k] = w[(size_t)c * TAPS + k];
+  const float* st = state + ((size_t)slot * C + c) * (TAPS - 1);
+  const bool fresh = sm.positions[q0] == 0;
+#pragma unroll
+  for (int k = 0; k < TAPS - 1; ++k) {
+    const int t = t0 - (TAPS - 1) + k;                   // input index of window slot k
+    if (t >= 0) win[k] = __bfloat162float(x[(size_t)(q0 + t) * x_ld + c]);
+    else win[k] = fresh ? 0.f : st[(TAPS - 1) + t];       // t in [-(TAPS-1), -1] -> stored input TAPS-1+t
+  }
+  const float b = bias ? bias[c] : 0.f;
+  const int t1 = min(n, t0 + kConvTb);
+  for (int t = t0; t < t1; ++t) {
+    win[TAPS - 1] = __bfloat162float(x[(size_t)(q0 + t) * x_ld + c]);
+    float y = b;
+#pragma unroll
+    for (int k = 0; k < TAPS; ++k) y += win[k] * wk[k];
+    if (activation) y = mb::silu(y);
+    out[(size_t)(q0 + t) * C + c] = y;
+#pragma unroll
+    for (int k = 0; k < TAPS - 1; ++k) win[k] = win[k + 1];
+  }
+}
+
+// new state = the last TAPS - 1 inputs of (old state | this step's inputs); one thread per channel
+template <int TAPS>
+__global__ void __launch_bounds__(128)
+conv1d_state_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int C, float* __restrict__ state, SeqMeta sm) {
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  const int seq = blockIdx.y;
+  if (c >= C) return;
+  const int n = sm.q_len[seq];
+  if (n <= 0) return;
+  const int q0 = sm.q_start[seq];
+  const int slot = sm.state_slots[seq];
+  if (slot < 0 || slot >= sm.num_slots) return;
+  float* st = state + ((size_t)slot * C + c) * (TAPS - 1);
+  const bool fresh = sm.positions[q0] == 0;
+  float nw[TAPS - 1];
+#pragma unroll
+  for (int k = 0; k < TAPS - 1; ++k) {
+    const int t = n - (TAPS - 1) + k;                    // input index of new state slot k
+    if (t >= 0) nw[k] = __bfloat162float(x[(size_t)(q0 + t) * x_ld + c]);
+    else nw[k] = fresh ? 0.f : st[(TAPS - 1) + t];
+  }
+#pragma unroll
+  for (int k = 0; k < TAPS - 1; ++k) st[k] = nw[k];
+}
+
 // ------------------------------------------------------------------ gated delta net
 // grid (v_heads, num_seqs), block = DV threads. conv [T, 2 QK + V] fp32 (q | k | v),
 // ba [T, 2 v_heads] fp32 (b | a), state [slots, v_heads, DK, DV] fp32, out [T, v_heads * DV].
@@ -226,6 +299,34 @@ int mb_causal_conv1d(const void* x, long long x_ld, int C, int taps, const float
     case 2: conv1d_kernel<2><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, write_state, write_out, status); break;
     case 3: conv1d_kernel<3><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, write_state, write_out, status); break;
     case 4: conv1d_kernel<4><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, write_state, write_out, status); break;
+    default: return MB_ERR_UNSUPPORTED;
+  }
+  return (int)cudaGetLastError();
+}
+
+// Prefill form of mb_causal_conv1d: time-parallel output, then the state update (two launches).
+int mb_causal_conv1d_par(const void* x, long long x_ld, int C, int taps, const float* w, const float* bias,
+                         float* state, float* out, const int* q_start, const int* q_len, const int* positions,
+                         const int* state_slots, int num_seqs, int num_slots, int max_q_len, int activation,
+                         int write_state, uint32_t* status, cudaStream_t stream) {
+  if (!x || !w || !state || !out || C <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_ERR_BAD_ARG;
+  SeqMeta sm{q_start, q_len, positions, state_slots, num_slots};
+  const dim3 grid((C + 127) / 128, (max_q_len + kConvTb - 1) / kConvTb, num_seqs), sgrid((C + 127) / 128, num_seqs);
+  if (grid.y > 65535 || num_seqs > 65535) return MB_ERR_TOO_LARGE;
+  const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  switch (taps) {
+    case 2:
+      conv1d_par_kernel<2><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, status);
+      if (write_state) conv1d_state_kernel<2><<<sgrid, 128, 0, stream>>>(xb, x_ld, C, state, sm);
+      break;
+    case 3:
+      conv1d_par_kernel<3><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, status);
+      if (write_state) conv1d_state_kernel<3><<<sgrid, 128, 0, stream>>>(xb, x_ld, C, state, sm);
+      break;
+    case 4:
+      conv1d_par_kernel<4><<<grid, 128, 0, stream>>>(xb, x_ld, C, w, bias, state, out, sm, activation, status);
+      if (write_state) conv1d_state_kernel<4><<<sgrid, 128, 0, stream>>>(xb, x_ld, C, state, sm);
+      break;
     default: return MB_ERR_UNSUPPORTED;
   }
   return (int)cudaGetLastError();

@@ -197,9 +197,26 @@ def _status(dev):
     return runtime(dev).status
 
 
+_native.register_optional("mb_causal_conv1d_par", [_c.c_void_p, _c.c_longlong, _c.c_int, _c.c_int, _c.c_void_p,
+                                                  _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                                  _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                                  _c.c_void_p, _c.c_void_p])
+# prefill chunks at least this long take the time-parallel convolution
+_CONV_PAR_MIN_TOKENS = 64
+
+
 def _conv_cuda(x, channels, w, bias, state, batch, activation, write_state=True, write_out=True):
     T = x.shape[0]
     out = torch.empty(T, channels, dtype=torch.float32, device=x.device)
+    mq = int(getattr(batch, "max_q_len", 1))
+    if write_out and mq >= _CONV_PAR_MIN_TOKENS and hasattr(_native.lib(), "mb_causal_conv1d_par"):
+        rc = _native.lib().mb_causal_conv1d_par(
+            _ptr(x), x.stride(0), channels, w.shape[1], _ptr(w), _ptr(bias), _ptr(state), _ptr(out),
+            _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions), _ptr(batch.state_slots),
+            batch.q_len.numel(), state.shape[0], mq, int(activation), int(write_state), _ptr(_status(x.device)), _stream())
+        _native.check(rc, "causal_conv1d_par")
+        _count(2 if write_state else 1)
+        return out
     rc = _native.lib().mb_causal_conv1d(
         _ptr(x), x.stride(0), channels, w.shape[1], _ptr(w), _ptr(bias), _ptr(state), _ptr(out),
         _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions), _ptr(batch.state_slots),

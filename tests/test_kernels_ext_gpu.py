@@ -42,6 +42,31 @@ def test_causal_conv1d_matches_reference():
     _close(st_dev, st_ref)
 
 
+@pytest.mark.parametrize("taps", [2, 4])
+def test_time_parallel_conv1d_matches_the_sequential_reference(taps):
+    """Prefill chunks (>= 64 tokens) take the time-parallel kernel + the state kernel: outputs and the
+    stored window must equal the CPU reference for fresh sequences, continuations from a stored
+    window, sequences shorter than the window and a one-token sequence in the same launch."""
+    g = torch.Generator().manual_seed(3)
+    C = 200
+    lens = [200, 1, 77, 64, 2]
+    seqs = [dict(tokens=[1] * n, start_pos=0 if i % 2 == 0 else 9, blocks=list(range(1, 3 + n // 16)), state_slot=i + 1)
+            for i, n in enumerate(lens)]
+    T = sum(lens)
+    x = torch.randn(T, C + 24, generator=g).to(torch.bfloat16)
+    w, b = torch.randn(C, taps, generator=g), torch.randn(C, generator=g)
+    st = torch.randn(len(lens) + 1, C, taps - 1, generator=g)
+    st_ref = st.clone()
+    want = rops.causal_conv1d(x, C, w, b, st_ref, ForwardBatch.build(seqs, 16, device="cpu"))
+    st_dev = st.to(DEV)
+    n0 = ops.launch_count
+    got = rops.causal_conv1d(x.to(DEV), C, w.to(DEV), b.to(DEV), st_dev, ForwardBatch.build(seqs, 16, device=DEV))
+    assert ops.launch_count - n0 == 2                       # the parallel kernel and the state kernel
+    _close(got, want)
+    _close(st_dev, st_ref)
+    assert torch.equal(st_dev[0].cpu(), st[0])              # untouched slot
+
+
 @pytest.mark.parametrize("dk", [32, 128])
 def test_gdn_recurrence_matches_reference(dk):
     g = torch.Generator().manual_seed(1)
