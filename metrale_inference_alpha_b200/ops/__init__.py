@@ -810,7 +810,7 @@ def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_l
         return _attention_rowwise(q, k_cache, v_cache, block_table, q_start, q_len, ctx_len,
                                   max_ctx=max_ctx, scale=scale, k_scale=k_scale, v_scale=v_scale,
                                   window=window)
-    if force_mode == 3 or (force_mode == 0 and _ATTN_TC and D == 128 and window == 0 and max_q_len >= 128):
+    if force_mode == 3 or (force_mode == 0 and _ATTN_TC and D in (128, 256) and window == 0 and max_q_len >= 128):
         # prefill chunks: both products on tcgen05 with TMEM accumulators (csrc/attention_tc.cu)
         t = _native.AttnTcArgs()
         t.q, t.k_cache, t.v_cache, t.block_table = _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table)
@@ -818,7 +818,7 @@ def paged_attention(q: torch.Tensor, k_cache, v_cache, block_table, q_start, q_l
         t.k_scale, t.v_scale, t.out, t.status = _ptr(k_scale), _ptr(v_scale), _ptr(out), _ptr(rt.status)
         t.num_blocks, t.max_blocks, t.num_seqs, t.max_q_len = nb, block_table.stride(0), S, max_q_len
         t.Hq, t.Hkv, t.D, t.block_size, t.cache_fp8, t.scale = Hq, Hkv, D, bs, int(k_cache.dtype == torch.uint8), scale
-        t.v_mn = _ATTN_TC_VMN
+        t.v_mn = 1 if D == 256 else _ATTN_TC_VMN
         _native.check(L.mb_attn_prefill_tc(C.byref(t), _stream()), "attn_prefill_tc")
         _count()
         return out

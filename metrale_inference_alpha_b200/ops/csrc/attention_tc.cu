@@ -28,7 +28,6 @@
 
 namespace {
 
-constexpr int kD = 128;          // head dim
 constexpr int kQ = 128;          // query rows per CTA
 constexpr int kT = 64;           // cached tokens per tile
 constexpr int kHalfB = 64 * 2;   // bytes of a 64-element bf16 swizzle row
@@ -79,13 +78,18 @@ __device__ __forceinline__ uint4 widen8(uint2 v) {
   return o;
 }
 
-template <bool FP8, bool VMN>
-__global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams p) {
+// kD = head dim (128 or 256; 256 needs the MN-major V path). kNH = 64-dim blocks per row; a staging
+// thread owns one token and the blocks sub, sub + 2, ... (sub = tid / 64).
+template <int kD, bool FP8, bool VMN>
+__global__ void __launch_bounds__(128, kD == 128 ? 2 : 1) attn_prefill_tc_kernel(const TcParams p) {
+  static_assert(kD == 128 || (kD == 256 && VMN), "head dim 256 stages V as stored");
+  constexpr int kNH = kD / 64, kNHT = kNH / 2;
+  constexpr uint32_t kTmemCols = kD == 128 ? 256 : 512;    // S (64) + O (kD), rounded to a power of two
   extern __shared__ __align__(16) uint8_t smem[];
   // the swizzled tiles need 1024-byte alignment in the shared window (the launch reserves the slack)
-  uint8_t* sQ = smem + ((1024u - (mb::smem_u32(smem) & 1023u)) & 1023u);   // 2 halves x [128 rows x 128 B]
-  uint8_t* sK = sQ + 2 * kQ * 128;          // 2 halves x [64 rows x 128 B]
-  uint8_t* sV = sK + 2 * kT * 128;          // [128 dims x 128 B (64 tokens)]
+  uint8_t* sQ = smem + ((1024u - (mb::smem_u32(smem) & 1023u)) & 1023u);   // kNH blocks x [128 rows x 128 B]
+  uint8_t* sK = sQ + kNH * kQ * 128;        // kNH blocks x [64 rows x 128 B]
+  uint8_t* sV = sK + kNH * kT * 128;        // as stored: kNH blocks x [64 tokens x 128 B]; transposed: [kD dims x 128 B]
   uint8_t* sP = sV + kD * 128;              // [128 rows x 128 B (64 tokens)]
   __shared__ uint64_t bar_s, bar_o;
   __shared__ uint32_t s_tmem;
@@ -102,13 +106,13 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
     mb::mbar_init(&bar_o, 1);
     mb::mbar_fence_init();
   }
-  if (warp == 0) mb::tmem_alloc(&s_tmem, 256);
+  if (warp == 0) mb::tmem_alloc(&s_tmem, kTmemCols);
   // Q tile: thread = row
   {
     const int qi = q0 + tid;
     const uint4* src = qi < qlen ? reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + qi) * p.Hq + head) * kD) : nullptr;
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
+    for (int c = 0; c < kD / 8; ++c) {
       const uint4 v = src ? src[c] : make_uint4(0, 0, 0, 0);
       *reinterpret_cast<uint4*>(sQ + (c >> 3) * (kQ * 128) + sw_off(tid, c & 7)) = v;
     }
@@ -139,9 +143,9 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
   const size_t esz = FP8 ? 1 : 2;
   const size_t row_pitch = (size_t)p.Hkv * kD * esz;
   const int s_tok = tid & 63, s_half = tid >> 6;                      // staging: one token, one 64-dim half
-  // raw cache bytes of this thread's (token, half) of the next tile, fetched one tile ahead
+  // raw cache bytes of this thread's token (blocks sub, sub + 2, ...) of the next tile, fetched one tile ahead
   constexpr int kRaw = FP8 ? 4 : 8;
-  uint4 kraw[kRaw], vraw[kRaw];
+  uint4 kraw[kNHT][kRaw], vraw[kNHT][kRaw];
   auto fetch = [&](int jt) {
     const int tok = jt * kT + s_tok;
     if (jt < tiles && tok < ctx) {
@@ -150,18 +154,23 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
         if (p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
         blk = 0;
       }
-      const size_t off = ((size_t)blk * p.block_size + (tok % p.block_size)) * row_pitch + (size_t)kvh * kD * esz +
-                         (size_t)s_half * 64 * esz;
-      const uint4* ks = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.k_cache) + off);
-      const uint4* vs = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.v_cache) + off);
+      const size_t off = ((size_t)blk * p.block_size + (tok % p.block_size)) * row_pitch + (size_t)kvh * kD * esz;
 #pragma unroll
-      for (int c = 0; c < kRaw; ++c) {
-        kraw[c] = __ldg(ks + c);
-        vraw[c] = __ldg(vs + c);
+      for (int hh = 0; hh < kNHT; ++hh) {
+        const size_t o2 = off + (size_t)(s_half + 2 * hh) * 64 * esz;
+        const uint4* ks = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.k_cache) + o2);
+        const uint4* vs = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.v_cache) + o2);
+#pragma unroll
+        for (int c = 0; c < kRaw; ++c) {
+          kraw[hh][c] = __ldg(ks + c);
+          vraw[hh][c] = __ldg(vs + c);
+        }
       }
     } else {
 #pragma unroll
-      for (int c = 0; c < kRaw; ++c) kraw[c] = vraw[c] = make_uint4(0, 0, 0, 0);
+      for (int hh = 0; hh < kNHT; ++hh)
+#pragma unroll
+        for (int c = 0; c < kRaw; ++c) kraw[hh][c] = vraw[hh][c] = make_uint4(0, 0, 0, 0);
     }
   };
   fetch(0);
@@ -175,28 +184,32 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
     }
     // ---- stage K (K-major) and V (transposed) of tokens [j * 64, j * 64 + 64) from the registers
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      uint4 kv, vv;
-      if constexpr (FP8) {
-        const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kraw[c >> 1]);
-        const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vraw[c >> 1]);
-        kv = widen8(make_uint2(kw[(c & 1) * 2], kw[(c & 1) * 2 + 1]));
-        vv = widen8(make_uint2(vw[(c & 1) * 2], vw[(c & 1) * 2 + 1]));
-      } else {
-        kv = kraw[c];
-        vv = vraw[c];
-      }
-      *reinterpret_cast<uint4*>(sK + s_half * (kT * 128) + sw_off(s_tok, c)) = kv;
-      if constexpr (VMN) {
-        // V as stored, [token][dim] in two 64-dim halves: read by the second product as an MN-major operand
-        *reinterpret_cast<uint4*>(sV + s_half * (kT * 128) + sw_off(s_tok, c)) = vv;
-      } else {
-        // V^T: element (dim d, token t) at row d, byte 2 t (chunk t / 8)
-        const uint16_t* e = reinterpret_cast<const uint16_t*>(&vv);
+    for (int hh = 0; hh < kNHT; ++hh) {
+      const int blk64 = s_half + 2 * hh;                 // which 64-dim block of the row
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int d = s_half * 64 + c * 8 + i;
-          *reinterpret_cast<uint16_t*>(sV + sw_off(d, s_tok >> 3) + (s_tok & 7) * 2) = e[i];
+      for (int c = 0; c < 8; ++c) {
+        uint4 kv, vv;
+        if constexpr (FP8) {
+          const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kraw[hh][c >> 1]);
+          const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vraw[hh][c >> 1]);
+          kv = widen8(make_uint2(kw[(c & 1) * 2], kw[(c & 1) * 2 + 1]));
+          vv = widen8(make_uint2(vw[(c & 1) * 2], vw[(c & 1) * 2 + 1]));
+        } else {
+          kv = kraw[hh][c];
+          vv = vraw[hh][c];
+        }
+        *reinterpret_cast<uint4*>(sK + blk64 * (kT * 128) + sw_off(s_tok, c)) = kv;
+        if constexpr (VMN) {
+          // V as stored, [token][dim] in 64-dim blocks: read by the second product as an MN-major operand
+          *reinterpret_cast<uint4*>(sV + blk64 * (kT * 128) + sw_off(s_tok, c)) = vv;
+        } else {
+          // V^T: element (dim d, token t) at row d, byte 2 t (chunk t / 8)
+          const uint16_t* e = reinterpret_cast<const uint16_t*>(&vv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int d = blk64 * 64 + c * 8 + i;
+            *reinterpret_cast<uint16_t*>(sV + sw_off(d, s_tok >> 3) + (s_tok & 7) * 2) = e[i];
+          }
         }
       }
     }
@@ -207,7 +220,7 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
     if (tid == 0) {
       mb::tc_fence_after();
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
+      for (int h = 0; h < kNH; ++h)
 #pragma unroll
         for (int s = 0; s < 4; ++s)
           mb::umma_f16(tmem, mb::umma_desc_sw128(aQ + h * (kQ * 128) + s * 32),
@@ -316,7 +329,7 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(const TcParams 
   }
   mb::tc_fence_before();
   __syncthreads();
-  if (warp == 0) mb::tmem_dealloc(tmem, 256);
+  if (warp == 0) mb::tmem_dealloc(tmem, kTmemCols);
 }
 
 }  // namespace
@@ -342,7 +355,7 @@ struct MbAttnTcArgs {
 // Causal paged attention for prefill chunks (head dim 128). Returns 0, MB_ERR_* or a CUDA error.
 extern "C" int mb_attn_prefill_tc(const MbAttnTcArgs* a, cudaStream_t stream) {
   if (!a || !a->q || !a->k_cache || !a->v_cache || !a->block_table || !a->out) return MB_ERR_BAD_ARG;
-  if (a->D != kD || a->num_seqs <= 0 || a->Hkv <= 0 || a->Hq % a->Hkv || a->max_q_len <= 0) return MB_ERR_UNSUPPORTED;
+  if ((a->D != 128 && a->D != 256) || a->num_seqs <= 0 || a->Hkv <= 0 || a->Hq % a->Hkv || a->max_q_len <= 0) return MB_ERR_UNSUPPORTED;
   if (a->cache_fp8 && (!a->k_scale || !a->v_scale)) return MB_ERR_BAD_ARG;
   TcParams p;
   p.q = (const __nv_bfloat16*)a->q; p.k_cache = a->k_cache; p.v_cache = a->v_cache;
@@ -351,21 +364,28 @@ extern "C" int mb_attn_prefill_tc(const MbAttnTcArgs* a, cudaStream_t stream) {
   p.Hq = a->Hq; p.Hkv = a->Hkv; p.block_size = a->block_size; p.num_blocks = a->num_blocks;
   p.scale = a->scale; p.k_scale = a->k_scale; p.v_scale = a->v_scale;
   p.out = (__nv_bfloat16*)a->out; p.status = a->status;
-  constexpr size_t smem = 2 * kQ * 128 + 2 * kT * 128 + kD * 128 + kQ * 128 + 1024;
+  const size_t smem = (size_t)(a->D / 64) * (kQ + 2 * kT) * 128 + kQ * 128 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int s128 = 2 * (kQ + 2 * kT) * 128 + kQ * 128 + 1024, s256 = 4 * (kQ + 2 * kT) * 128 + kQ * 128 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, s128);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, s128);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, s128);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, s128);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<256, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, s256);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc_kernel<256, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, s256);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const dim3 grid((a->max_q_len + kQ - 1) / kQ, a->Hq, a->num_seqs);
-  if (a->v_mn) {
-    if (a->cache_fp8) return (int)mb::launch_kernel(attn_prefill_tc_kernel<true, true>, grid, dim3(128), smem, stream, p);
-    return (int)mb::launch_kernel(attn_prefill_tc_kernel<false, true>, grid, dim3(128), smem, stream, p);
+  if (a->D == 256) {
+    if (a->cache_fp8) return (int)mb::launch_kernel(attn_prefill_tc_kernel<256, true, true>, grid, dim3(128), smem, stream, p);
+    return (int)mb::launch_kernel(attn_prefill_tc_kernel<256, false, true>, grid, dim3(128), smem, stream, p);
   }
-  if (a->cache_fp8) return (int)mb::launch_kernel(attn_prefill_tc_kernel<true, false>, grid, dim3(128), smem, stream, p);
-  return (int)mb::launch_kernel(attn_prefill_tc_kernel<false, false>, grid, dim3(128), smem, stream, p);
+  if (a->v_mn) {
+    if (a->cache_fp8) return (int)mb::launch_kernel(attn_prefill_tc_kernel<128, true, true>, grid, dim3(128), smem, stream, p);
+    return (int)mb::launch_kernel(attn_prefill_tc_kernel<128, false, true>, grid, dim3(128), smem, stream, p);
+  }
+  if (a->cache_fp8) return (int)mb::launch_kernel(attn_prefill_tc_kernel<128, true, false>, grid, dim3(128), smem, stream, p);
+  return (int)mb::launch_kernel(attn_prefill_tc_kernel<128, false, false>, grid, dim3(128), smem, stream, p);
 }

@@ -387,6 +387,14 @@ def test_prefill_attention_on_tcgen05_matches_fp32_oracle(fp8, q_lens, ctx_lens)
 
 
 @pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("q_lens,ctx_lens", [([200, 130], [200, 391]), ([512], [512])])
+def test_prefill_attention_on_tcgen05_head_dim_256(fp8, q_lens, ctx_lens):
+    """The same kernel at head_dim 256 (four 64-dim blocks per row, O in 256 TMEM columns, V read
+    as an MN-major operand): the attention layers of the Qwen3-Next style hybrids."""
+    _attn_case(fp8, 256, 4, 2, q_lens, ctx_lens, force_mode=3)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
 @pytest.mark.parametrize("D,rot", [(128, 128), (64, 64), (256, 64), (64, 32), (128, 32)])
 def test_rope_kvwrite(fp8, D, rot):
     M, Hq, Hkv, bs, nb = 23, 8, 2, 16, 12
