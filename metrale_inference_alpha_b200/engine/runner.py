@@ -9,6 +9,8 @@ metadata, graph cache; ``prefill_b.rs``: chunked prefill; ``verify_e.rs``: batch
 """
 from __future__ import annotations
 
+import contextlib
+import gc
 import time
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
@@ -55,6 +57,24 @@ def kv_config(cfg: ModelConfig, w: ModelW, block_size: int, mtp: bool = False) -
     hp = () if mtp else tuple(i for i, layer in enumerate(att) if layer in set(cfg.kv_high_precision_layers))
     return KvCacheConfig(1 if mtp else max(1, len(att)), kvh, cfg.head_dim, block_size, cfg.kv_dtype,
                          high_precision_layers=hp)
+
+
+@contextlib.contextmanager
+def _capture(g: "torch.cuda.CUDAGraph"):
+    """Stream capture that other activity in the process cannot invalidate: the capture-error mode is
+    thread-local (HTTP handler threads, samplers and exporters may call into CUDA while the scheduler
+    thread captures), and Python's cyclic collector is held off for the duration (a collection inside
+    the capture could free pinned staging buffers of retired engines, which is not a capturable
+    operation)."""
+    was = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            yield
+    finally:
+        if was:
+            gc.enable()
 
 
 class _Stager:
@@ -489,7 +509,7 @@ class ModelRunner:
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             count0 = ops.launch_count
-            with torch.cuda.graph(g):
+            with _capture(g):
                 self._forward_select(null, greedy, want_lp, rung, feed=True)
             self.graphs[key] = (g, ops.launch_count - count0, self.last_hidden)
         if not self._stage_decode_incremental(plan, rung, ahead):
@@ -525,7 +545,7 @@ class ModelRunner:
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             count0 = ops.launch_count
-            with torch.cuda.graph(g):
+            with _capture(g):
                 self._forward_select(null, True, False, rows)
             self.graphs[key] = (g, ops.launch_count - count0, self.last_hidden, null.spec_stash)
         self._stage(plan, pad_seqs=rung, pad_q=K + 1)
@@ -743,7 +763,7 @@ class ModelRunner:
             torch.cuda.synchronize(dev)
             g = torch.cuda.CUDAGraph()
             c0 = ops.launch_count
-            with torch.cuda.graph(g):
+            with _capture(g):
                 body()
             self.graphs[key] = (g, ops.launch_count - c0, None, None)
         st["ev"].synchronize()
