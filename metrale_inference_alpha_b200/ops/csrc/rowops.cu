@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(1024) row_kernel_v2(const RowParams p) {
       if (valid)
         *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.out) + (size_t)m * p.out_ld + b * 16) =
             make_uint4(w4[0], w4[1], w4[2], w4[3]);
-    } else if (valid && p.out_mode == OUT_NVFP4) {
+    } else if (p.out_mode == OUT_NVFP4) {
       float bmax = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(y[i]));
@@ -359,12 +359,24 @@ __global__ void __launch_bounds__(1024) row_kernel_v2(const RowParams p) {
       const float qi = sff > 0.f ? 1.f / (sff * gs) : 0.f;
       uint32_t lo = 0, hi = 0;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) lo |= mb::e2m1_code(y[i] * qi) << (4 * i);
+      for (int i = 0; i < 4; ++i) lo |= mb::e2m1x2_pack(y[2 * i] * qi, y[2 * i + 1] * qi) << (8 * i);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) hi |= mb::e2m1_code(y[8 + i] * qi) << (4 * i);
-      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(p.out) + (size_t)m * p.out_ld + b * 8) = make_uint2(lo, hi);
+      for (int i = 0; i < 4; ++i) hi |= mb::e2m1x2_pack(y[8 + 2 * i] * qi, y[8 + 2 * i + 1] * qi) << (8 * i);
+      if (valid)
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(p.out) + (size_t)m * p.out_ld + b * 8) = make_uint2(lo, hi);
       uint8_t* sf_blk = p.sf + (size_t)(m >> 7) * p.sf_k64 * 512;
-      sf_blk[(size_t)(b >> 2) * 512 + mb::sf_tile_offset(m & 127, b & 3)] = sfc;
+      if ((nblk & 3) == 0) {
+        // four consecutive blocks sit on four consecutive lanes and fill one 4-byte group of the tiled
+        // scale-factor layout: one 32-bit store per group instead of four byte stores
+        const uint32_t s1 = __shfl_down_sync(0xffffffffu, (uint32_t)sfc, 1);
+        const uint32_t s2 = __shfl_down_sync(0xffffffffu, (uint32_t)sfc, 2);
+        const uint32_t s3 = __shfl_down_sync(0xffffffffu, (uint32_t)sfc, 3);
+        if (valid && (b & 3) == 0)
+          *reinterpret_cast<uint32_t*>(sf_blk + (size_t)(b >> 2) * 512 + mb::sf_tile_offset(m & 127, 0)) =
+              (uint32_t)sfc | (s1 << 8) | (s2 << 16) | (s3 << 24);
+      } else if (valid) {
+        sf_blk[(size_t)(b >> 2) * 512 + mb::sf_tile_offset(m & 127, b & 3)] = sfc;
+      }
     }
   }
 }
