@@ -31,6 +31,7 @@ def main():
     ap.add_argument("--fmt", default="nvfp4")
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--swiglu", action="store_true", help="--op gemm: SwiGLU epilogue (gate / up rows interleaved)")
+    ap.add_argument("--impl", type=int, default=0, help="--op mla: 1 = mma.sync kernel, 2 = tcgen05 kernel, 0 = the engine's choice")
     ap.add_argument("--ranks", type=int, default=8, help="--op tpfused: emulated ranks (partials summed by one kernel)")
     a = ap.parse_args()
     M = a.m
@@ -83,7 +84,7 @@ def main():
         ql = torch.ones(M, device=DEV, dtype=torch.int32)
         cl = torch.full((M,), a.ctx, device=DEV, dtype=torch.int32)
         for _ in range(a.iters):
-            mla_cuda.mla_attention(q, cache, bt, qs, ql, cl, max_q_len=1, max_ctx=max(nblk, 128) * bs, scale=1 / math.sqrt(192))
+            mla_cuda.mla_attention(q, cache, bt, qs, ql, cl, max_q_len=1, max_ctx=max(nblk, 128) * bs, scale=1 / math.sqrt(192), impl=a.impl)
     elif a.op == "gemm":
         ws = rand_weight(a.n, a.k, a.fmt, 3)
         act = ops.quantize_act(torch.randn(M, a.k, device=DEV).to(torch.bfloat16), ops.ACT_FOR_WEIGHT[a.fmt])

@@ -20,6 +20,7 @@
 // Reference behaviour: kernels/gb10/deepseek-v4-flash/nvfp4/{paged_decode_attn_mla.cu,
 // mla_paged_decode_fp8.cu, mla_absorbed.cu} (CUDA-core per-head loops there).
 #include "common.cuh"
+#include "mla_args.h"
 
 namespace {
 
@@ -303,29 +304,220 @@ __global__ void mla_merge_kernel(const MlaParams p, const int* row_seq) {
   }
 }
 
+// ------------------------------------------------------------------ decode on tcgen05 / TMEM
+// One query token per sequence, all heads of it as the 128 rows of one UMMA tile: thread r owns head r.
+// grid (2 halves of the 512 value dims, partitions of the context, sequences), 128 threads. Per tile of
+// 32 cached tokens the latent rows [32 x 576] are staged ONCE (nine 64-dim blocks, 128-byte swizzle) and
+// feed both products: S = Q K^T (M 128, N 32, 36 k steps over the 576 dims, K-major) and, for this CTA's
+// half, O += P V (M 128, N 256, 2 k steps) with V = four of the same blocks read as an MN-major operand.
+// S (32 columns) and O (256 columns) live in TMEM; O is rescaled only when a row maximum moves by more
+// than 2^8; the next tile's rows are fetched into registers while the products run. Both halves compute
+// the same S (the second one's tile reads hit L2). Partitions are merged by mla_merge_kernel.
+constexpr int kTcT = 32;                       // cached tokens per tile
+constexpr int kTcBlocks = kD / 64;             // 9 blocks of 64 dims
+constexpr int kTcQB = 128 * 128;               // one Q block: 128 rows x 128 B
+constexpr int kTcKB = kTcT * 128;              // one cache block of a tile: 32 rows x 128 B
+constexpr int kTcSmem = kTcBlocks * (kTcQB + kTcKB) + 128 * 128 /*P*/ + 1024 /*alignment*/;
+
+__device__ __forceinline__ uint32_t tc_sw(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+__device__ __forceinline__ float tc_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(128, 1) mla_decode_tc_kernel(const MlaParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  uint8_t* sQ = smem_raw + ((1024u - (mb::smem_u32(smem_raw) & 1023u)) & 1023u);   // 9 x [128 rows x 128 B]
+  uint8_t* sK = sQ + kTcBlocks * kTcQB;                                             // 9 x [32 tokens x 128 B]
+  uint8_t* sP = sK + kTcBlocks * kTcKB;                                             // [128 rows x 128 B], 32 tokens used
+  __shared__ uint64_t bar_s, bar_o;
+  __shared__ uint32_t s_tmem;
+  const int hv = blockIdx.x, part = blockIdx.y, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  mb::pdl_wait();
+  const int ctx = p.ctx_len[seq];
+  if (p.q_len[seq] <= 0) return;
+  const int nparts = max(1, (ctx + p.part_tokens - 1) / p.part_tokens);
+  if (part >= nparts) return;
+  const int tok_begin = part * p.part_tokens, tok_end = min(ctx, tok_begin + p.part_tokens);
+  const int tiles = (tok_end - tok_begin + kTcT - 1) / kTcT;
+  const int row = p.q_start[seq];                       // the sequence's single query row
+  const int* bt = p.block_table + (size_t)seq * p.max_blocks;
+  if (tid == 0) {
+    mb::mbar_init(&bar_s, 1);
+    mb::mbar_init(&bar_o, 1);
+    mb::mbar_fence_init();
+  }
+  if (warp == 0) mb::tmem_alloc(&s_tmem, 512);
+  {
+    const uint4* src = tid < p.H ? reinterpret_cast<const uint4*>(p.q + ((size_t)row * p.H + tid) * kD) : nullptr;
+#pragma unroll 8
+    for (int c = 0; c < kChunks; ++c) {
+      const uint4 v = src ? src[c] : make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(sQ + (c >> 3) * kTcQB + tc_sw(tid, c & 7)) = v;
+    }
+    // the upper half of every P row is never written again: the second product only reads 32 tokens
+#pragma unroll
+    for (int c = 4; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tc_sw(tid, c)) = make_uint4(0, 0, 0, 0);
+  }
+  mb::tc_fence_before();
+  __syncthreads();
+  mb::tc_fence_after();
+  mb::pdl_launch_dependents();                          // only once this CTA holds its TMEM columns
+  const uint32_t tmem = s_tmem;
+  const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);
+  constexpr uint32_t kIdescS = mb::umma_idesc(1, 1, 128, kTcT);
+  constexpr uint32_t kIdescO = mb::umma_idesc(1, 1, 128, 256, 0, 1);
+  const uint32_t aQ = mb::smem_u32(sQ), aK = mb::smem_u32(sK), aP = mb::smem_u32(sP);
+  const float sc_log2 = p.scale * 1.44269504088896f;
+  float m_run = -INFINITY, l_run = 0.f;
+  uint32_t ph_s = 0, ph_o = 0;
+  bool ok = true;
+  // staging: thread = (token tid / 4 of the tile, quarter tid % 4 of its row): 18 consecutive 16-byte chunks,
+  // one block-table lookup per tile
+  constexpr int kPer = kChunks / 4;
+  const int s_tok = tid >> 2, s_c0 = (tid & 3) * kPer;
+  uint4 raw[kPer];
+  auto fetch = [&](int jt) {
+    const int tok = tok_begin + jt * kTcT + s_tok;
+    if (jt < tiles && tok < tok_end) {
+      long long blk = bt[tok / p.block_size];
+      if (blk < 0 || blk >= p.num_blocks) {
+        if (p.status) atomicCAS(p.status, 0u, MB_ST_BOUNDS);
+        blk = 0;
+      }
+      const uint4* src = reinterpret_cast<const uint4*>(p.cache + ((size_t)blk * p.block_size + (tok % p.block_size)) * kD) + s_c0;
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) raw[i] = __ldg(src + i);
+    } else {
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) raw[i] = make_uint4(0, 0, 0, 0);
+    }
+  };
+  fetch(0);
+  for (int j = 0; j < tiles; ++j) {
+    if (j > 0) {                                        // the previous tile's second product read sK and sP
+      ok = mb::mbar_wait(&bar_o, ph_o, p.status, MB_ST_TIMEOUT_MMA) && ok;
+      ph_o ^= 1;
+      mb::tc_fence_after();
+    }
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int c = s_c0 + i;
+      *reinterpret_cast<uint4*>(sK + (c >> 3) * kTcKB + tc_sw(s_tok, c & 7)) = raw[i];
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mb::tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      mb::tc_fence_after();
+#pragma unroll
+      for (int b = 0; b < kTcBlocks; ++b)
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+          mb::umma_f16(tmem, mb::umma_desc_sw128(aQ + b * kTcQB + s * 32), mb::umma_desc_sw128(aK + b * kTcKB + s * 32),
+                       kIdescS, (b | s) != 0);
+      mb::tc_commit(&bar_s);
+    }
+    fetch(j + 1);
+    ok = mb::mbar_wait(&bar_s, ph_s, p.status, MB_ST_TIMEOUT_MMA) && ok;
+    ph_s ^= 1;
+    mb::tc_fence_after();
+    {
+      float sv[kTcT];
+      mb::tmem_ld16(t_row, sv);
+      mb::tmem_ld16(t_row + 16, sv + 16);
+      float mx = -INFINITY;
+      const int tok0 = tok_begin + j * kTcT;
+#pragma unroll
+      for (int i = 0; i < kTcT; ++i) {
+        const float v = (tok0 + i < tok_end) ? sv[i] * sc_log2 : -INFINITY;
+        sv[i] = v;
+        mx = fmaxf(mx, v);
+      }
+      float alpha = 1.f;
+      const bool move = mx > m_run + 8.f;
+      if (move) {
+        alpha = tc_ex2(m_run - mx);
+        m_run = mx;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, move)) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float ov[16];
+          mb::tmem_ld16(t_row + 32 + c * 16, ov);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) ov[i] *= alpha;
+          mb::tmem_st16(t_row + 32 + c * 16, ov);
+        }
+        mb::tmem_st_wait();
+      }
+      const float m_use = m_run == -INFINITY ? 0.f : m_run;
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint4 pk;
+        uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float a = tc_ex2(sv[c * 8 + 2 * i] - m_use), b = tc_ex2(sv[c * 8 + 2 * i + 1] - m_use);
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(a, b);
+          rs += a + b;
+          pw[i] = *reinterpret_cast<const uint32_t*>(&pb);
+        }
+        *reinterpret_cast<uint4*>(sP + tc_sw(tid, c)) = pk;
+      }
+      l_run = l_run * alpha + rs;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mb::tc_fence_before();
+    ok = __syncthreads_and(ok) != 0;
+    if (!ok) break;
+    if (tid == 0) {
+      mb::tc_fence_after();
+#pragma unroll
+      for (int s = 0; s < 2; ++s)                         // 16 tokens per step = two 8-row groups of the tile
+        mb::umma_f16(tmem + 32, mb::umma_desc_sw128(aP + s * 32),
+                     mb::umma_desc_sw128_mn(aK + (4 * hv) * kTcKB + s * 2048, kTcKB, 1024), kIdescO, (j | s) != 0);
+      mb::tc_commit(&bar_o);
+    }
+  }
+  if (ok && tiles > 0) {
+    ok = mb::mbar_wait(&bar_o, ph_o, p.status, MB_ST_TIMEOUT_MMA) && ok;
+    mb::tc_fence_after();
+  }
+  if (ok) {                                               // uniform: tcgen05.ld is a whole-warp instruction
+    const bool row_ok = tid < p.H;
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    const size_t grow = (size_t)row * p.H + (row_ok ? tid : 0);
+    float* dst = (nparts == 1 ? p.out + grow * kL : p.part_o + (grow * p.parts + part) * kL) + hv * 256;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      float ov[16];
+      mb::tmem_ld16(t_row + 32 + c * 16, ov);
+      if (row_ok) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<float4*>(dst + c * 16 + i * 4) =
+              make_float4(ov[4 * i] * inv, ov[4 * i + 1] * inv, ov[4 * i + 2] * inv, ov[4 * i + 3] * inv);
+      }
+    }
+    if (row_ok && nparts > 1 && hv == 0) {
+      p.part_ml[(grow * p.parts + part) * 2] = m_run;
+      p.part_ml[(grow * p.parts + part) * 2 + 1] = l_run;
+    }
+  }
+  mb::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) mb::tmem_dealloc(tmem, 512);
+}
+
 }  // namespace
 
 extern "C" {
 
-struct MbMlaArgs {
-  const void* q;
-  const void* cache;
-  const int* block_table;
-  int max_blocks;
-  const int* q_start;
-  const int* q_len;
-  const int* ctx_len;
-  const int* row_seq;        // [total_rows] sequence index of every query row (merge kernel)
-  int num_seqs, max_q_len, max_ctx, total_rows;
-  int H, block_size;
-  long long num_blocks;
-  float scale;
-  float* out;
-  void* ws;
-  size_t ws_bytes;
-  int part_tokens;           // 0 = default 1024
-  uint32_t* status;
-};
+// (MbMlaArgs: mla_args.h)
 
 size_t mb_mla_ws_bytes(int total_rows, int H, int max_ctx, int part_tokens) {
   const int pt = part_tokens > 0 ? part_tokens : 1024;
@@ -333,8 +525,46 @@ size_t mb_mla_ws_bytes(int total_rows, int H, int max_ctx, int part_tokens) {
   return parts <= 1 ? 0 : (size_t)total_rows * H * parts * (kL + 2) * sizeof(float);
 }
 
+// Decode rows (one query token per sequence, H <= 128 heads) on the tcgen05 kernel; same arguments,
+// workspace and results as mb_mla_attention.
+int mb_mla_decode_tc(const MbMlaArgs* a, cudaStream_t stream) {
+  if (!a || !a->q || !a->cache || !a->out || a->num_seqs <= 0 || a->H <= 0 || a->H > 128 || a->max_q_len != 1)
+    return MB_ERR_BAD_ARG;
+  MlaParams p{};
+  p.q = reinterpret_cast<const __nv_bfloat16*>(a->q);
+  p.cache = reinterpret_cast<const __nv_bfloat16*>(a->cache);
+  p.block_table = a->block_table; p.max_blocks = a->max_blocks;
+  p.q_start = a->q_start; p.q_len = a->q_len; p.ctx_len = a->ctx_len;
+  p.H = a->H; p.block_size = a->block_size; p.num_blocks = a->num_blocks;
+  p.scale = a->scale; p.out = a->out; p.status = a->status;
+  p.part_tokens = a->part_tokens > 0 ? a->part_tokens : 1024;
+  p.parts = (a->max_ctx + p.part_tokens - 1) / p.part_tokens;
+  if (p.parts < 1) p.parts = 1;
+  if (p.parts > 1) {
+    const size_t need = mb_mla_ws_bytes(a->total_rows, a->H, a->max_ctx, p.part_tokens);
+    if (!a->ws || a->ws_bytes < need || !a->row_seq) return MB_ERR_TOO_LARGE;
+    p.part_o = reinterpret_cast<float*>(a->ws);
+    p.part_ml = p.part_o + (size_t)a->total_rows * a->H * p.parts * kL;
+  }
+  if (p.parts > 65535) return MB_ERR_TOO_LARGE;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(mla_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  cudaError_t e = mb::launch_kernel(mla_decode_tc_kernel, dim3(2, p.parts, a->num_seqs), dim3(128), (size_t)kTcSmem, stream, p);
+  if (e != cudaSuccess) return (int)e;
+  if (p.parts > 1) {
+    e = mb::launch_kernel(mla_merge_kernel, dim3(a->total_rows * a->H), dim3(128), (size_t)0, stream, p, a->row_seq);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
 int mb_mla_attention(const MbMlaArgs* a, cudaStream_t stream) {
   if (!a || !a->q || !a->cache || !a->out || a->num_seqs <= 0 || a->H <= 0 || a->max_q_len <= 0) return MB_ERR_BAD_ARG;
+  if (a->impl == 2 || (a->impl == 0 && a->max_q_len == 1 && a->H <= 128 && a->H >= 16)) return mb_mla_decode_tc(a, stream);
   MlaParams p{};
   p.q = reinterpret_cast<const __nv_bfloat16*>(a->q);
   p.cache = reinterpret_cast<const __nv_bfloat16*>(a->cache);

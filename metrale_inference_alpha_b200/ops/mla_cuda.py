@@ -19,6 +19,7 @@ class MlaArgs(C.Structure):
         ("num_seqs", c_int), ("max_q_len", c_int), ("max_ctx", c_int), ("total_rows", c_int),
         ("H", c_int), ("block_size", c_int), ("num_blocks", c_ll), ("scale", c_float),
         ("out", c_void_p), ("ws", c_void_p), ("ws_bytes", c_size_t), ("part_tokens", c_int), ("status", c_void_p),
+        ("impl", c_int),
     ]
 
 
@@ -27,6 +28,7 @@ _native.register_optional("mb_mla_attention", [C.POINTER(MlaArgs), c_void_p])
 _native.register_optional("mb_mla_prepare", [c_void_p] * 10 + [c_int] * 6 + [c_ll, c_float, c_void_p, c_void_p])
 
 LATENT, ROW = 512, 576
+TC_PART_TOKENS = 256
 _CNT_BYTES = 64 * 1024
 
 
@@ -36,8 +38,9 @@ def supported(q: torch.Tensor, cache: torch.Tensor) -> bool:
 
 
 def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_table, q_start, q_len, ctx_len, *, max_q_len: int,
-                  max_ctx: int, scale: float, row_seq=None, part_tokens: int = 0) -> torch.Tensor:
-    """q [T, H, 576] bf16 -> [T, H, 512] fp32."""
+                  max_ctx: int, scale: float, row_seq=None, part_tokens: int = 0, impl: int = 0) -> torch.Tensor:
+    """q [T, H, 576] bf16 -> [T, H, 512] fp32. `impl`: 0 = decode steps (one query row per sequence,
+    16 <= H <= 128) take the tcgen05 / TMEM kernel, everything else the mma.sync kernel; 1 / 2 force one."""
     from . import _count, _ptr, _stream, runtime
     L = _native.lib()
     if not hasattr(L, "mb_mla_attention"):
@@ -46,6 +49,10 @@ def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_table, q_start, q_
     L.mb_mla_ws_bytes.restype = c_size_t
     T, H, _ = q.shape
     q = q.contiguous()
+    if part_tokens == 0 and impl != 1 and max_q_len == 1 and 16 <= H <= 128:
+        # the tcgen05 decode kernel runs one CTA per SM: shorter partitions than the mma.sync kernel's 1024
+        # keep the SMs busy at small batch (a constant, so a sequence's split never depends on the batch)
+        part_tokens = TC_PART_TOKENS
     rt = runtime(q.device)
     out = torch.empty(T, H, LATENT, dtype=torch.float32, device=q.device)
     need = L.mb_mla_ws_bytes(T, H, max_ctx, part_tokens)
@@ -62,7 +69,7 @@ def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_table, q_start, q_
     a.q_start, a.q_len, a.ctx_len, a.row_seq = _ptr(q_start), _ptr(q_len), _ptr(ctx_len), _ptr(row_seq)
     a.num_seqs, a.max_q_len, a.max_ctx, a.total_rows = q_len.numel(), max_q_len, max_ctx, T
     a.H, a.block_size, a.num_blocks, a.scale = H, cache.shape[1], cache.shape[0], scale
-    a.out, a.part_tokens, a.status = _ptr(out), part_tokens, _ptr(rt.status)
+    a.out, a.part_tokens, a.status, a.impl = _ptr(out), part_tokens, _ptr(rt.status), impl
     a.ws, a.ws_bytes = (_ptr(rt.attn_ws) + _CNT_BYTES, rt.attn_ws.numel() - _CNT_BYTES) if need else (None, 0)
     _native.check(L.mb_mla_attention(C.byref(a), _stream()), "mla_attention")
     _count()

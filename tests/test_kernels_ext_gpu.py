@@ -308,13 +308,20 @@ def test_grouped_expert_ffn_matches_loop(fmt):
 
 
 # ---------------------------------------------------------------------------- absorbed MLA attention
+@pytest.mark.parametrize("impl", [1, 2])
 @pytest.mark.parametrize("H,q_lens,ctx_lens,part_tokens", [
     (16, [1, 1, 1], [5, 130, 64], 0),             # decode, ragged contexts, one row group per sequence
     (128, [1, 1], [700, 33], 0),                  # DeepSeek-V3 head count: 8 row groups
     (8, [4, 1, 7], [40, 9, 200], 0),              # verify / chunked rows: causal limits inside a group
     (16, [1, 2], [300, 257], 128),                # three partitions + merge kernel
+    (128, [1, 1, 1], [1000, 31, 257], 256),       # decode with partitions (the tcgen05 kernel + merge)
+    (40, [1], [97], 0),                           # a head count that does not fill the 128-row tile
 ])
-def test_mla_attention_matches_fp32_oracle(H, q_lens, ctx_lens, part_tokens):
+def test_mla_attention_matches_fp32_oracle(H, q_lens, ctx_lens, part_tokens, impl):
+    """impl 1 = the mma.sync kernel, 2 = the tcgen05 / TMEM decode kernel (one query row per sequence,
+    16 <= H <= 128; other cases are skipped for it)."""
+    if impl == 2 and (max(q_lens) != 1 or H < 16):
+        pytest.skip("the tcgen05 kernel serves decode rows")
     from types import SimpleNamespace
     from metrale_inference_alpha_b200.models.mla import mla_attention as mla_ref
     from metrale_inference_alpha_b200.ops import mla_cuda
@@ -339,7 +346,8 @@ def test_mla_attention_matches_fp32_oracle(H, q_lens, ctx_lens, part_tokens):
     scale = 1.0 / (192 ** 0.5)
     want = mla_ref(q, cache, batch, scale, L)
     got = mla_cuda.mla_attention(q.to(DEV), cache.to(DEV), bt.to(DEV), qs.to(DEV), ql.to(DEV), cl.to(DEV),
-                                 max_q_len=max(q_lens), max_ctx=max(ctx_lens), scale=scale, part_tokens=part_tokens)
+                                 max_q_len=max(q_lens), max_ctx=max(ctx_lens), scale=scale, part_tokens=part_tokens,
+                                 impl=impl)
     torch.cuda.synchronize()
     ops.check_status(DEV)
     err = (got.cpu() - want).abs().max().item()
