@@ -67,6 +67,8 @@ class EngineArgs:
     state_snapshots: int = 0                           # device-resident state snapshots (0 = 16 + ring slots x max_num_seqs)
     state_tier_host_bytes: int = 0                     # > 0: resident snapshots overflow into this much host memory ...
     state_tier_dir: Optional[str] = None               # ... and from there (or directly) into files in this directory
+    expert_arena_slots: int = 0                        # MoE: > 0 pages the routed experts from an expert store into a device arena of this many experts
+    expert_store_dir: Optional[str] = None             # ... the store's directory (written from the loaded weights when it has no manifest yet)
     prediction_drafts: int = 8                         # tokens verified per step for requests with a predicted output
     kv_cache_dtype: str = "auto"                       # auto (the model config's) | bf16 | fp8
     kv_high_precision_layers: str = ""                 # e.g. "0,1,63" or "first:2,last:2": these layers keep bf16 KV under fp8
@@ -128,6 +130,15 @@ class LLMEngine:
                                     tp_size=self.tp.size if args.ep_size == 1 or args.tp_size > 1 else 1,
                                     ep_rank=getattr(self.tp, "ep_rank", 0), ep_size=args.ep_size, seed=args.seed)
         self.load_seconds = time.time() - t0
+        self.paged_experts = None
+        if args.expert_arena_slots > 0:
+            if not args.expert_store_dir:
+                raise ValueError("expert_arena_slots needs expert_store_dir")
+            from ..storage.expert_store import enable_expert_paging
+            self.paged_experts = enable_expert_paging(self.weights, args.expert_store_dir, args.expert_arena_slots,
+                                                      args.device)
+            # residency is decided on the host from each step's routing: no graph replay over it
+            args.use_cuda_graphs = False
         self.sched_cfg = SchedulerConfig(
             max_num_seqs=args.max_num_seqs, max_prefill_tokens=args.max_prefill_tokens,
             max_model_len=min(args.max_model_len, cfg.max_position), block_size=args.block_size,

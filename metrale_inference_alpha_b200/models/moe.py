@@ -17,7 +17,10 @@ from ..ops import NATIVE_ACT_FOR_WEIGHT as ACT_FOR_WEIGHT, moe as moe_ops   # ex
 
 def moe_block(dec, x, lw):
     c, w = dec.cfg, lw.ffn
-    fmt = ACT_FOR_WEIGHT[(w.experts[0].gate_up if w.experts else w.shared.gate_up).fmt]
+    if getattr(w, "paged", None) is not None:
+        fmt = ACT_FOR_WEIGHT[w.paged.spec.fmt[0]]
+    else:
+        fmt = ACT_FOR_WEIGHT[(w.experts[0].gate_up if w.experts else w.shared.gate_up).fmt]
     a = dec._norm_act(x, lw.ln2, fmt, also_bf16=True, res_only=dec.tp.size > 1)
     x = dec.res(x)
     hb = a.bf16
@@ -85,6 +88,8 @@ def shared_expert(dec, a, w):
 
 def routed_experts(dec, a, weights, idx, w):
     """Sum over the local experts of weight * expert(x); fp32 [T, hidden]."""
+    if getattr(w, "paged", None) is not None:
+        return _routed_paged(dec, a, weights, idx, w)
     if a.data.is_cuda and w.grouped is not None:
         from ..ops.moe_cuda import grouped_ffn
         return grouped_ffn(dec.cfg, a, weights, idx, w)
@@ -95,6 +100,52 @@ def routed_experts(dec, a, weights, idx, w):
     for j, f in enumerate(w.experts):
         e = lo + j
         tok, slot = torch.nonzero(idx == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        sub = ops.Act(a.fmt, tok.numel(), a.K, a.data[tok])
+        fmt_d = ACT_FOR_WEIGHT[f.down.fmt]
+        if dec.cfg.ffn_act == "relu2":
+            h = ops.row_op(ops.linear(sub, f.gate_up), fmt_d, ops.IN_RELU2)[0]
+        elif f.interleaved:
+            h = ops.quantize_act(ops.linear(sub, f.gate_up, swiglu=True), fmt_d)
+        else:
+            h = ops.row_op(ops.linear(sub, f.gate_up), fmt_d, ops.IN_SILU_MUL)[0]
+        y = ops.linear(h, f.down, out_f32=True)
+        out.index_add_(0, tok, y * weights[tok, slot][:, None])
+    return out
+
+
+def _routed_paged(dec, a, weights, idx, w):
+    """Routed experts whose weights are paged from an expert store: every wave of resident experts is
+    one pass of the grouped (CUDA) or per-expert (CPU) path over the routing ids rewritten to arena
+    slots; experts outside the wave carry id -1 and are dropped, and the waves' outputs add up."""
+    import copy
+    paged = w.paged
+    out = None
+    for slot_idx in paged.waves(w.paged_layer, idx):
+        view = copy.copy(w)
+        view.paged, view.expert_lo = None, 0
+        if a.data.is_cuda:
+            view.grouped, view.experts = paged.grouped, []
+        else:
+            view.grouped = None
+            view.experts = [paged.slot_ffn(s) if paged.resident[s] is not None else None for s in range(paged.slots)]
+        y = _routed_slots(dec, a, weights, slot_idx, view)
+        out = y if out is None else out + y
+    if out is None:
+        out = torch.zeros(a.M, dec.cfg.hidden_size, dtype=torch.float32, device=a.data.device)
+    return out
+
+
+def _routed_slots(dec, a, weights, idx, view):
+    if view.grouped is not None:
+        from ..ops.moe_cuda import grouped_ffn
+        return grouped_ffn(dec.cfg, a, weights, idx, view)
+    live = [(j, f) for j, f in enumerate(view.experts) if f is not None]
+    T, H = a.M, dec.cfg.hidden_size
+    out = torch.zeros(T, H, dtype=torch.float32, device=a.data.device)
+    for j, f in live:
+        tok, slot = torch.nonzero(idx == j, as_tuple=True)
         if tok.numel() == 0:
             continue
         sub = ops.Act(a.fmt, tok.numel(), a.K, a.data[tok])

@@ -129,6 +129,8 @@ class MoeW:
     shared_replicated: bool = False                        # expert parallelism keeps the whole shared expert on every rank
     grouped: Optional[object] = None                       # stacked device layout for the grouped GEMM
     router_ext: Optional[QuantWeight] = None               # router rows + the shared expert's gate row (shared expert folded into `grouped`)
+    paged: Optional[object] = None                         # storage.expert_store.PagedExperts: the experts live in a store and are paged into an arena
+    paged_layer: int = 0                                   # this layer's index in that store
 
 
 @dataclass

@@ -494,3 +494,115 @@ def test_mla_block_on_gpu_matches_the_cpu_restatement():
     for a, bb in zip(logits["cpu"], logits[DEV]):
         assert (a - bb).abs().max() <= 0.04 * a.abs().max() + 2e-3, ((a - bb).abs().max(), a.abs().max())
         assert int(a.argmax()) == int(bb.argmax())
+
+
+# ----------------------------------------------------------------------------- storage tier kernels
+@pytest.mark.parametrize("D,fp8", [(128, False), (128, True), (256, False), (256, True)])
+def test_kv_tile_attention_folds_tiles_like_the_restatement(D, fp8):
+    from metrale_inference_alpha_b200.storage import kernels as SK
+    g = torch.Generator().manual_seed(3)
+    S, Hq, Hkv, bs, nblk = 3, 8, 2, 16, 12
+    k = torch.randn(nblk, bs, Hkv, D, generator=g) * 0.5
+    v = torch.randn(nblk, bs, Hkv, D, generator=g)
+    if fp8:
+        pk, pv = k.to(torch.float8_e4m3fn).view(torch.uint8), v.to(torch.float8_e4m3fn).view(torch.uint8)
+        ks, vs = 0.5, 2.0
+    else:
+        pk, pv, ks, vs = k.to(torch.bfloat16), v.to(torch.bfloat16), 1.0, 1.0
+    q = torch.randn(S, Hq, D, generator=g).to(torch.bfloat16)
+    tiles = [(torch.tensor([[0, 5, 2, 7], [1, 3, 0, 0], [4, 6, 8, 9]], dtype=torch.int32), torch.tensor([4, 2, 4], dtype=torch.int32),
+              torch.tensor([16, 9, 16], dtype=torch.int32)),
+             (torch.tensor([[10, 11, 0, 0], [0, 0, 0, 0], [3, 0, 0, 0]], dtype=torch.int32), torch.tensor([2, 0, 1], dtype=torch.int32),
+              torch.tensor([3, 16, 1], dtype=torch.int32))]
+    strides = SK.paged_strides(bs, Hkv, D)
+    outs = {}
+    for dev in ("cpu", DEV):
+        st = SK.attn_state(S, Hq, D, dev)
+        fused = torch.zeros(S, Hq, D, dtype=torch.bfloat16, device=dev)
+        for i, (tb, tc, lv) in enumerate(tiles):
+            SK.kv_tile_attn(q.to(dev), pk.to(dev), pv.to(dev), tb.to(dev), tc.to(dev), st, Hkv=Hkv, block_size=bs,
+                            strides=strides, last_valid=lv.to(dev), k_scale=ks, v_scale=vs,
+                            out=fused if i == len(tiles) - 1 else None)
+        outs[dev] = (SK.attn_finalize(st[1], st[2]), fused, st)
+    _close(outs[DEV][0], outs["cpu"][0], 2e-2, 2e-2)
+    _close(outs[DEV][1], outs["cpu"][0], 2e-2, 2e-2)            # the last tile's fused output = finalize
+    _close(outs[DEV][2][0], outs["cpu"][2][0], 1e-3, 1e-3)      # running maxima
+
+
+def test_lowrank_projection_and_predictor_score_match_the_restatement():
+    from metrale_inference_alpha_b200.storage import kernels as SK
+    g = torch.Generator().manual_seed(4)
+    Hq, Hkv, D, bs, r, nblk = 8, 2, 128, 16, 32, 10
+    P = (torch.randn(D, r, generator=g) / D ** 0.5).to(torch.bfloat16)
+    q = torch.randn(3, Hq, D, generator=g).to(torch.bfloat16)
+    _close(SK.project_rows(q.to(DEV), P.to(DEV)), SK.project_rows(q, P), 2e-2, 2e-2)
+    for fp8 in (False, True):
+        k = torch.randn(nblk, bs, Hkv, D, generator=g)
+        pool = k.to(torch.float8_e4m3fn).view(torch.uint8) if fp8 else k.to(torch.bfloat16)
+        src = torch.tensor([7, 2, 9], dtype=torch.int32)
+        dst = torch.tensor([1, 4, 0], dtype=torch.int32)
+        lr = {}
+        for dev in ("cpu", DEV):
+            out = torch.zeros(6, Hkv, bs, r, dtype=torch.bfloat16, device=dev)
+            SK.project_blocks(pool.to(dev), P.to(dev), out, src.to(dev), dst.to(dev), Hkv=Hkv, block_size=bs,
+                              strides=SK.paged_strides(bs, Hkv, D), k_scale=0.5 if fp8 else 1.0)
+            lr[dev] = out
+        _close(lr[DEV], lr["cpu"], 2e-2, 2e-2)
+    k_lr = lr["cpu"]
+    q_lr = SK.project_rows(q, P)
+    blocks = torch.tensor([[1, 4, 0, 0], [0, 1, 4, 0], [4, 0, 0, 0]], dtype=torch.int32)
+    counts = torch.tensor([2, 3, 1], dtype=torch.int32)
+    last = torch.tensor([5, 16, 1], dtype=torch.int32)
+    want = SK.predictor_score(q_lr, k_lr, blocks, counts, last)
+    got = SK.predictor_score(q_lr.to(DEV), k_lr.to(DEV), blocks.to(DEV), counts.to(DEV), last.to(DEV)).cpu()
+    assert torch.equal(torch.isinf(got), torch.isinf(want))
+    fin = ~torch.isinf(want)
+    _close(got[fin], want[fin], 1e-2, 1e-2)
+
+
+def test_streamed_attention_through_files_on_the_device(tmp_path):
+    import math
+    from metrale_inference_alpha_b200.storage import HighSpeedSwap, HighSpeedSwapConfig, ModelDims
+    g = torch.Generator().manual_seed(5)
+    md = ModelDims(1, 8, 2, 128)
+    hss = HighSpeedSwap(HighSpeedSwapConfig(dir=str(tmp_path / "kv"), block_size=16, max_blocks_per_layer=64,
+                                            resident_blocks=12, tile_capacity=4, rank=32, max_seqs=2), md, device=DEV)
+    lens, ids, kv = [200, 96], [], []
+    for n in lens:
+        k = (torch.randn(n, 2, 128, generator=g) * 0.5).to(torch.bfloat16)
+        v = torch.randn(n, 2, 128, generator=g).to(torch.bfloat16)
+        nb = (n + 15) // 16
+        d = [hss.alloc_disk_block() for _ in range(nb)]
+        for j, blk in enumerate(d):
+            kb, vb = torch.zeros(16, 2, 128, dtype=torch.bfloat16), torch.zeros(16, 2, 128, dtype=torch.bfloat16)
+            m = min(16, n - j * 16)
+            kb[:m], vb[:m] = k[j * 16:j * 16 + m], v[j * 16:j * 16 + m]
+            hss.offload_block(0, blk, kb.to(DEV), vb.to(DEV))
+        ids.append(d)
+        kv.append((k, v))
+    q = torch.randn(2, 8, 128, generator=g).to(torch.bfloat16)
+    last = [n - (len(d) - 1) * 16 for n, d in zip(lens, ids)]
+    for _ in range(2):
+        out = hss.attend_layer(0, q.to(DEV), ids, last_valid=last).float().cpu()
+        for s, (k, v) in enumerate(kv):
+            for h in range(8):
+                sc = (k[:, h // 4].float() @ q[s, h].float()) / math.sqrt(128)
+                ref_o = torch.softmax(sc, 0) @ v[:, h // 4].float()
+                _close(out[s, h], ref_o, 2e-2, 2e-2)
+    assert hss.stats["evictions"] > 0 and hss.stats["slot_hits"] > 0
+    ops.check_status(torch.device(DEV))
+    hss.close()
+
+
+def test_paged_experts_grouped_path_matches_resident_experts(tmp_path):
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    prompts = [list(range(5, 45)), list(range(40, 52))]
+    sp = SamplingParams(max_tokens=6, temperature=0.0)
+    base = LLMEngine(EngineArgs(model="tiny-hybrid-moe", device=DEV, num_kv_blocks=64, max_num_seqs=4))
+    want = [o.output_ids for o in base.generate(prompts, sp)]
+    eng = LLMEngine(EngineArgs(model="tiny-hybrid-moe", device=DEV, num_kv_blocks=64, max_num_seqs=4,
+                               expert_arena_slots=3, expert_store_dir=str(tmp_path / "experts")))
+    got = [o.output_ids for o in eng.generate(prompts, sp)]
+    assert got == want
+    assert eng.paged_experts.stats["evictions"] > 0
