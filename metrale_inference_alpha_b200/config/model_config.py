@@ -16,7 +16,7 @@ from typing import List, Optional
 
 WEIGHT_FORMATS = ("bf16", "nvfp4", "fp8_block", "fp8_row")
 KV_DTYPES = ("bf16", "fp8")
-LAYER_KINDS = ("attention", "gdn", "mamba2", "mla")
+LAYER_KINDS = ("attention", "gdn", "mamba2", "mla", "kda")
 FFN_KINDS = ("dense", "moe", "none")
 
 
@@ -34,6 +34,7 @@ class ModelConfig:
     rope_theta: float = 1e6
     rope_scaling: Optional[dict] = None     # HF `rope_scaling` (linear / llama3 / yarn); None = plain RoPE
     rotary_dim: int = 0                 # 0 -> head_dim; -1 -> no RoPE (Nemotron-H attention)
+    rope_identity: bool = False         # keep the rotary slots of the layout but rotate by nothing (Kimi-Linear's NoPE MLA layers)
     qk_norm: bool = False
     qk_norm_full: bool = False          # the q / k RMSNorm spans all heads of the projection (MiniMax-M2), not one head
     attn_output_gate: bool = False      # q_proj emits [Q_h | G_h] per head, o = attn * sigmoid(G)
@@ -66,6 +67,11 @@ class ModelConfig:
     gdn_k_dim: int = 128
     gdn_v_dim: int = 128
     conv_kernel: int = 4
+    # Kimi delta attention (per-channel gated delta rule)
+    kda_heads: int = 0
+    kda_head_dim: int = 128
+    kda_gate_rank: int = 0              # inner width of the low-rank decay (f_a / f_b) and output-gate (g_a / g_b) projections; 0 = head_dim
+    kda_gate_lower_bound: float = -5.0
     # mamba2
     mamba_heads: int = 0
     mamba_head_dim: int = 64
@@ -160,6 +166,9 @@ class ModelConfig:
                 n += h * (self.q_size + 2 * self.kv_size) + self.num_heads * self.head_dim * h
             elif lt == "gdn":
                 n += h * (2 * self.gdn_qk_size + 2 * self.gdn_v_size + 2 * self.gdn_v_heads) + self.gdn_v_size * h
+            elif lt == "kda":
+                hd, r = self.kda_heads * self.kda_head_dim, self.kda_gate_rank or self.kda_head_dim
+                n += 4 * h * hd + 2 * (h * r + r * hd) + h * self.kda_heads
             elif lt == "mamba2":
                 n += h * (2 * self.mamba_inner + 2 * self.mamba_groups * self.mamba_state + self.mamba_heads)
                 n += self.mamba_inner * h
@@ -284,8 +293,21 @@ def tiny_nemotron_h(**kw) -> ModelConfig:
     return nemotron_h_8b(**base)
 
 
+def tiny_kimi_linear(**kw) -> ModelConfig:
+    """Four-layer instance of the Kimi-Linear family: three Kimi-delta-attention layers per full-attention
+    layer, MoE feed-forward (tests, smoke runs)."""
+    base = dict(num_layers=4, hidden_size=512, num_heads=4, num_kv_heads=2, gdn_k_heads=0, gdn_v_heads=0,
+                kda_heads=4, kda_head_dim=128, kda_gate_rank=64,
+                layer_types=["kda", "kda", "kda", "attention"],
+                num_experts=8, experts_per_token=2, moe_intermediate_size=256, intermediate_size=256,
+                vocab_size=4096, max_position=1024, name="tiny-kimi-linear")
+    base.update(kw)
+    return qwen_hybrid_moe_35b(**base)
+
+
 PRESETS = {
     "tiny-dense": tiny_dense,
+    "tiny-kimi-linear": tiny_kimi_linear,
     "tiny-hybrid-moe": tiny_hybrid_moe,
     "tiny-nemotron-h": tiny_nemotron_h,
     "dense-27b-nvfp4": dense_27b_nvfp4,
@@ -310,6 +332,7 @@ _HF_ARCH = {
     "qwen3_5_text": "qwen_hybrid", "qwen3_5_moe_text": "qwen_hybrid",
     "nemotron_h": "nemotron_h", "deepseek_v3": "deepseek_mla", "deepseek_v2": "deepseek_mla",
     "kimi_k2": "deepseek_mla",          # Kimi K2 checkpoints use the DeepSeek-V3 architecture and tensor names
+    "kimi_linear": "deepseek_mla",      # Kimi-Linear: Kimi-delta-attention layers + (NoPE) MLA layers, DeepSeek-style MoE
 }
 
 
@@ -472,6 +495,24 @@ def from_hf_config(cfg: dict, name: str = "model") -> ModelConfig:
                   router_n_group=cfg.get("n_group", 1), router_topk_group=cfg.get("topk_group", 1),
                   router_scaling=float(cfg.get("routed_scaling_factor", 1.0)),
                   router_renormalize=bool(cfg.get("norm_topk_prob", True)))
+        if mt == "kimi_linear":
+            la = cfg.get("linear_attn_config") or {}
+            kda_layers = {int(i) - 1 for i in la.get("kda_layers", [])}            # the checkpoint counts layers from 1
+            if not kda_layers:
+                raise ValueError("kimi_linear needs linear_attn_config.kda_layers")
+            conv = int(la.get("short_conv_kernel_size", 4))
+            kw.update(layer_types=["kda" if i in kda_layers else "mla" for i in range(L)],
+                      kda_heads=int(la.get("num_heads", heads)), kda_head_dim=int(la.get("head_dim", 128)),
+                      kda_gate_rank=int(la.get("gate_rank", 0) or 0), conv_kernel=conv,
+                      kda_gate_lower_bound=float(la.get("gate_lower_bound", -5.0)),
+                      rope_identity=bool(cfg.get("mla_use_nope", False)),
+                      num_experts=cfg.get("num_experts", cfg.get("n_routed_experts", 0)),
+                      experts_per_token=cfg.get("num_experts_per_token", cfg.get("num_experts_per_tok", 8)),
+                      num_shared_experts=cfg.get("num_shared_experts", cfg.get("n_shared_experts", 0)),
+                      router="sigmoid" if cfg.get("moe_router_activation_func", cfg.get("scoring_func", "sigmoid")) == "sigmoid" else "softmax",
+                      router_n_group=cfg.get("num_expert_group", cfg.get("n_group", 1)),
+                      router_topk_group=cfg.get("topk_group", 1),
+                      router_renormalize=bool(cfg.get("moe_renormalize", cfg.get("norm_topk_prob", True))))
     return ModelConfig(**kw)
 
 

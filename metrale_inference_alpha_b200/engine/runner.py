@@ -37,6 +37,9 @@ def state_shapes(cfg: ModelConfig, w: ModelW):
             m = lw.mixer
             C = 2 * m.k_heads * cfg.gdn_k_dim + m.v_heads * cfg.gdn_v_dim
             out.append(((C, cfg.conv_kernel - 1), (m.v_heads, cfg.gdn_k_dim, cfg.gdn_v_dim)))
+        elif lw.kind == "kda":
+            m = lw.mixer
+            out.append(((3 * m.heads * cfg.kda_head_dim, cfg.conv_kernel - 1), (m.heads, cfg.kda_head_dim, cfg.kda_head_dim)))
         elif lw.kind == "mamba2":
             m = lw.mixer
             C = m.heads * cfg.mamba_head_dim + 2 * m.groups * cfg.mamba_state

@@ -75,6 +75,8 @@ class Decoder:
         if rot > 0:
             self.cos, self.sin = ref.rope_tables(cfg.max_position, rot, cfg.rope_theta, device=self.device,
                                                  scaling=cfg.rope_scaling)
+            if cfg.rope_identity:          # position-free attention in a rotary layout: cos = 1, sin = 0
+                self.cos, self.sin = torch.ones_like(self.cos), torch.zeros_like(self.sin)
         self.cos_local = self.sin_local = None
         if rot > 0 and cfg.rope_local_theta > 0:          # windowed layers rotate with their own, unscaled base
             self.cos_local, self.sin_local = ref.rope_tables(cfg.max_position, rot, cfg.rope_local_theta, device=self.device)
@@ -273,6 +275,9 @@ class Decoder:
         elif lw.kind == "gdn":
             from .recurrent import gdn_block
             x = gdn_block(self, x, lw, batch, caches.state, caches.state_index[i])
+        elif lw.kind == "kda":
+            from .recurrent import kda_block
+            x = kda_block(self, x, lw, batch, caches.state, caches.state_index[i])
         elif lw.kind == "mamba2":
             from .recurrent import mamba2_block
             x = mamba2_block(self, x, lw, batch, caches.state, caches.state_index[i])

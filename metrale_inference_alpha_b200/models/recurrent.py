@@ -38,6 +38,32 @@ def gdn_block(dec, x, lw, batch, pool, sidx: int):
     return dec.tp.linear_reduce(y, w.out, residual=x, defer=True)
 
 
+def kda_block(dec, x, lw, batch, pool, sidx: int):
+    """Kimi delta attention: q|k|v projection -> short convolution + SiLU -> (inside the recurrence
+    kernel) l2 norm of q and k, bounded per-channel decay from the low-rank f projection, beta =
+    sigmoid(b), per-channel gated delta rule, sigmoid-gated output RMSNorm with the low-rank g
+    projection -> output projection. Reference op graph: crates/model-arch/src/glm5next_kda/mod.rs."""
+    c, w = dec.cfg, lw.mixer
+    H, D = w.heads, c.kda_head_dim
+    HD = H * D
+    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.in_qkv.fmt], also_bf16=True, res_only=True)
+    x = dec.res(x)
+    hb = dec._as_act(a.bf16, "bf16")
+    qkv = ops.linear(a, w.in_qkv)                                                    # [T, 3 HD]
+    g_raw = ops.linear(dec._as_act(ops.linear(hb, w.f_a), "bf16"), w.f_b, out_f32=True)   # [T, HD]
+    b_raw = ops.linear(hb, w.b_proj, out_f32=True)                                   # [T, H]
+    o_gate = ops.linear(dec._as_act(ops.linear(hb, w.g_a), "bf16"), w.g_b)           # [T, HD] bf16
+    stash = getattr(batch, "spec_stash", None)
+    ws = stash is None
+    conv_out = rops.causal_conv1d(qkv, 3 * HD, w.conv_w, None, pool.conv[sidx], batch, activation=True, write_state=ws)
+    y = rops.kda_recurrence(conv_out, g_raw, b_raw, w.A_log, w.dt_bias, c.kda_gate_lower_bound, pool.ssm[sidx], batch,
+                            heads=H, dim=D, write_state=ws, norm=(w.norm_w, o_gate, c.rms_eps))   # bf16 [T, HD]
+    if stash is not None:
+        stash.layers[sidx] = ("kda", lw, qkv, conv_out, (g_raw, b_raw))
+    ya = dec._as_act(y, ACT_FOR_WEIGHT[w.out.fmt])
+    return dec.tp.linear_reduce(ya, w.out, residual=x, defer=True)
+
+
 def _tile(owner, w: torch.Tensor, n: int) -> torch.Tensor:
     """`w` repeated n times (the per-head norm weight laid out for all heads of a row), built once
     and kept on the layer's own weight object: a cache keyed by anything else (a device address,
@@ -83,6 +109,12 @@ def commit_recurrent(cfg, pool, stash, commit_batch) -> None:
                                activation=True, write_out=False)
             rops.gdn_recurrence(conv_out, gate, w.A_log, w.dt_bias, pool.ssm[sidx], commit_batch,
                                 k_heads=kh, v_heads=vh, k_dim=kd, v_dim=vd, write_out=False)
+        elif kind == "kda":
+            H, D = w.heads, cfg.kda_head_dim
+            rops.causal_conv1d(x_in, 3 * H * D, w.conv_w, None, pool.conv[sidx], commit_batch, activation=True,
+                               write_out=False)
+            rops.kda_recurrence(conv_out, gate[0], gate[1], w.A_log, w.dt_bias, cfg.kda_gate_lower_bound, pool.ssm[sidx],
+                                commit_batch, heads=H, dim=D, write_out=False)
         else:
             H, G, P, N = w.heads, w.groups, cfg.mamba_head_dim, cfg.mamba_state
             inner, GN = H * P, G * N

@@ -252,3 +252,70 @@ def _mamba_cuda(xbc, dt, A_log, D, dt_bias, ssm_state, batch, heads, groups, hea
     _native.check(rc, "mamba2_scan")
     _count()
     return out
+
+
+# ----------------------------------------------------------------------------- Kimi delta attention
+import ctypes as _C
+
+
+class _KdaArgs(_C.Structure):
+    _fields_ = [("conv", _C.c_void_p), ("g_raw", _C.c_void_p), ("b_raw", _C.c_void_p), ("b_ld", _C.c_int),
+                ("A_log", _C.c_void_p), ("dt_bias", _C.c_void_p), ("lower_bound", _C.c_float), ("state", _C.c_void_p),
+                ("out", _C.c_void_p), ("out_norm", _C.c_void_p), ("out_gate", _C.c_void_p), ("gate_ld", _C.c_longlong),
+                ("norm_w", _C.c_void_p), ("eps", _C.c_float), ("H", _C.c_int), ("D", _C.c_int),
+                ("q_start", _C.c_void_p), ("q_len", _C.c_void_p), ("positions", _C.c_void_p),
+                ("state_slots", _C.c_void_p), ("num_seqs", _C.c_int), ("num_slots", _C.c_int),
+                ("write_state", _C.c_int), ("write_out", _C.c_int), ("status", _C.c_void_p)]
+
+
+_native.register_optional("mb_kda_recurrence", [_C.POINTER(_KdaArgs), _C.c_void_p])
+
+
+def kda_recurrence(conv_out, g_raw, b_raw, A_log, dt_bias, lower_bound: float, state, batch, *, heads: int, dim: int,
+                   write_state: bool = True, write_out: bool = True, norm=None):
+    """Kimi delta attention over a ragged batch. conv_out [T, 3 H D] fp32 (q | k | v after conv + SiLU),
+    g_raw [T, H D] fp32 (the decay projection), b_raw [T, >= H] fp32 (beta logits), A_log [H], dt_bias
+    [H D], state [slots, H, D, D] fp32. l2-normalises q and k per head, applies the bounded gate law and
+    the beta sigmoid, runs the per-channel gated delta rule. With ``norm = (w [D] fp32, gate [T, H D]
+    bf16, eps)`` the sigmoid-gated output RMSNorm is applied too and the result is bf16; otherwise fp32
+    [T, H D]."""
+    T = conv_out.shape[0]
+    H, D = heads, dim
+    if conv_out.is_cuda and _native.available() and hasattr(_native.lib(), "mb_kda_recurrence"):
+        dev = conv_out.device
+        out = out_n = gate = w = None
+        eps = 0.0
+        if norm is not None:
+            w, gate, eps = norm
+            out_n = torch.empty(T, H * D, dtype=torch.bfloat16, device=dev)
+        else:
+            out = torch.empty(T, H * D, dtype=torch.float32, device=dev)
+        a = _KdaArgs(_ptr(conv_out), _ptr(g_raw), _ptr(b_raw), b_raw.stride(0), _ptr(A_log), _ptr(dt_bias),
+                     float(lower_bound), _ptr(state), _ptr(out), _ptr(out_n), _ptr(gate),
+                     gate.stride(0) if gate is not None else 0, _ptr(w), float(eps), H, D,
+                     _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions), _ptr(batch.state_slots),
+                     batch.q_len.numel(), state.shape[0], int(write_state), int(write_out), _ptr(_status(dev)))
+        _native.check(_native.lib().mb_kda_recurrence(_C.byref(a), _stream()), "kda_recurrence")
+        _count()
+        return out_n if norm is not None else out
+    HD = H * D
+    out = torch.zeros(T, H, D, dtype=torch.float32, device=conv_out.device)
+    qs, ql, slots, pos0 = _seq_rows(batch)
+    gate_all = ref.kda_gate(g_raw.view(T, H, D), A_log, dt_bias.view(H, D), lower_bound)
+    beta_all = torch.sigmoid(b_raw[:, :H].float())
+    for s in range(len(ql)):
+        S = state[slots[s]:slots[s] + 1].clone()
+        if pos0[s] == 0:
+            S.zero_()
+        for t in range(qs[s], qs[s] + ql[s]):
+            q = ref.l2_norm(conv_out[t, :HD].view(1, H, D))
+            k = ref.l2_norm(conv_out[t, HD:2 * HD].view(1, H, D))
+            v = conv_out[t, 2 * HD:3 * HD].view(1, H, D)
+            o, S = ref.kda_recurrence_step(S, q, k, v, gate_all[t:t + 1], beta_all[t:t + 1])
+            out[t] = o[0]
+        if write_state and ql[s] > 0:
+            state[slots[s]] = S[0]
+    if norm is not None:
+        w, gate, eps = norm
+        return ref.sigmoid_gated_rmsnorm(out, gate.view(T, H, D), w, eps).reshape(T, HD).to(torch.bfloat16)
+    return out.reshape(T, HD)

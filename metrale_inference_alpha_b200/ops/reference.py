@@ -418,3 +418,57 @@ def dequantize_mxfp4(packed: torch.Tensor, scales_e8m0: torch.Tensor) -> torch.T
     vals = e2m1_decode(unpack_fp4(packed))                     # [N, K] fp32
     s = e8m0_to_float(scales_e8m0).repeat_interleave(32, dim=1)
     return vals * s
+
+
+# ----------------------------------------------------------------------------- Kimi delta attention
+def kda_gate(g_raw, A_log, dt_bias, lower_bound: float):
+    """Bounded per-channel log-decay: lower_bound * sigmoid(exp(A_log[h]) * (g_raw[t,h,d] + dt_bias[h,d]))
+    (kernels/gb10/common/kda_gate.cu). g_raw [T, H, D] -> fp32 [T, H, D] in (lower_bound, 0)."""
+    a = torch.exp(torch.clamp(A_log.float(), max=20.0))[None, :, None]
+    return lower_bound * torch.sigmoid(a * (g_raw.float() + dt_bias.float().view(1, *g_raw.shape[1:])))
+
+
+def kda_recurrence_step(S, q, k, v, gate, beta):
+    """One token of the per-channel gated delta rule (kernels/gb10/common/kda_recurrent.cu). S [B, H, D, D]
+    fp32 indexed [k][v]; q, k already l2-normalised, v, gate (log-decay) [B, H, D]; beta [B, H] already
+    sigmoided. Returns (out [B, H, D], S)."""
+    D = S.shape[-1]
+    S = S * torch.exp(gate.float())[..., None]
+    delta = (v.float() - torch.einsum("bhkv,bhk->bhv", S, k.float())) * beta.float()[..., None]
+    S = S + torch.einsum("bhk,bhv->bhkv", k.float(), delta)
+    return torch.einsum("bhkv,bhk->bhv", S, q.float()) / math.sqrt(D), S
+
+
+def kda_chunk(S, q, k, v, gate, beta, chunk: int = 32):
+    """The same recurrence over T tokens of one sequence in chunks (the WY / UT-transform form of
+    kernels/gb10/common/kda_chunk.cu): q, k, v, gate [T, H, D], beta [T, H], S [H, D, D]. Used as a
+    second oracle: it must agree with T applications of `kda_recurrence_step`."""
+    T, H, D = q.shape
+    scale = 1.0 / math.sqrt(D)
+    out = torch.zeros(T, H, D)
+    S = S.clone().float()
+    for c0 in range(0, T, chunk):
+        C = min(chunk, T - c0)
+        qc, kc, vc = (x[c0:c0 + C].float().transpose(0, 1) for x in (q, k, v))           # [H, C, D]
+        gc = gate[c0:c0 + C].float().transpose(0, 1).cumsum(1)                             # [H, C, D]
+        bc = beta[c0:c0 + C].float().transpose(0, 1)                                        # [H, C]
+        kd = kc[:, :, None, :] * kc[:, None, :, :] * torch.exp(gc[:, :, None, :] - gc[:, None, :, :])
+        A = -(bc[:, :, None] * kd.sum(-1)).tril(-1)                                         # [H, C, C]
+        for i in range(1, C):
+            A[:, i, :i] = A[:, i, :i] + torch.einsum("hj,hjm->hm", A[:, i, :i], A[:, :i, :i])
+        A = A + torch.eye(C)
+        u = A @ (vc * bc[..., None])
+        w = A @ (kc * bc[..., None] * torch.exp(gc))
+        v_new = u - w @ S
+        intra = ((qc[:, :, None, :] * kc[:, None, :, :] * torch.exp(gc[:, :, None, :] - gc[:, None, :, :])).sum(-1) * scale).tril(0)
+        o = scale * (qc * torch.exp(gc)) @ S + intra @ v_new
+        last = gc[:, -1:, :]
+        S = S * torch.exp(last).transpose(1, 2) + (kc * torch.exp(last - gc)).transpose(1, 2) @ v_new
+        out[c0:c0 + C] = o.transpose(0, 1)
+    return out, S
+
+
+def sigmoid_gated_rmsnorm(x, gate, w, eps: float):
+    """x [.., D] fp32: x * rsqrt(mean(x^2) + eps) * w * sigmoid(gate) (kda_layer_ops.cu::kda_o_norm_gated)."""
+    x = x.float()
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.float() * torch.sigmoid(gate.float())

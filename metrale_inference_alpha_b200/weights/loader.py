@@ -134,6 +134,22 @@ class MoeW:
 
 
 @dataclass
+class KdaW:
+    in_qkv: QuantWeight = None       # rows q | k | v, heads contiguous
+    f_a: QuantWeight = None          # hidden -> rank (decay projection, first half)
+    f_b: QuantWeight = None          # rank -> H D
+    b_proj: QuantWeight = None       # hidden -> H (beta logits), bf16
+    g_a: QuantWeight = None          # hidden -> rank (output gate)
+    g_b: QuantWeight = None          # rank -> H D
+    conv_w: torch.Tensor = None      # [3 H D, taps] fp32, q | k | v
+    A_log: torch.Tensor = None       # [H]
+    dt_bias: torch.Tensor = None     # [H D]
+    norm_w: torch.Tensor = None      # [D] fp32
+    out: QuantWeight = None
+    heads: int = 0
+
+
+@dataclass
 class GdnW:
     in_qkvz: QuantWeight = None
     in_ba: QuantWeight = None
@@ -335,6 +351,8 @@ class Loader:
             L.mixer = loader_ext.gdn(self, f"{p}.linear_attn")
         elif lt == "mla":
             L.mixer = loader_ext.mla(self, f"{p}.self_attn")
+        elif lt == "kda":
+            L.mixer = loader_ext.kda(self, f"{p}.self_attn")
         if ft != "none":
             if c.post_norms and c.post_norm_names == "olmo2":     # post-norm only: no norm in front of the blocks
                 L.post_attn = self.vec(f"{p}.post_attention_layernorm.weight")

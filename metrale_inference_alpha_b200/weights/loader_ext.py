@@ -42,6 +42,37 @@ def gdn(ld, p: str) -> GdnW:
                 A_log, dt_bias, ld.vec(f"{p}.norm.weight"), finalize(out), kh, vh)
 
 
+def kda(ld, p: str):
+    """Kimi delta attention block: q / k / v projections fused to one GEMM, their three short
+    convolutions concatenated in the same q | k | v order, the low-rank decay (f_a, f_b) and output-gate
+    (g_a, g_b) projections, per-channel dt_bias and per-head A_log in fp32. Tensor parallelism splits
+    every per-head tensor by head and leaves the rank-sized inner projections replicated
+    (crates/model-arch/src/glm5next_kda/{binding,tp}.rs)."""
+    from .loader import KdaW
+    c = ld.cfg
+    H, D = c.kda_heads, c.kda_head_dim
+    q, k, v = (ld.lin(f"{p}.{n}_proj") for n in "qkv")
+    conv = [ld.src.get(f"{p}.{n}_conv1d.weight").to(ld.dev).float().reshape(-1, c.conv_kernel) for n in "qkv"]
+    f_a, f_b = ld.lin(f"{p}.f_a_proj", quant=False), ld.lin(f"{p}.f_b_proj", quant=False)
+    g_a, g_b = ld.lin(f"{p}.g_a_proj", quant=False), ld.lin(f"{p}.g_b_proj", quant=False)
+    b = ld.lin(f"{p}.b_proj", quant=False)
+    out = ld.lin(f"{p}.o_proj")
+    A_log = ld.vec(f"{p}.A_log", torch.float32).reshape(-1)
+    dt_bias = ld.vec(f"{p}.dt_bias", torch.float32).reshape(-1)
+    if ld.tp_size > 1:
+        lo, hi = ld._shard(H)
+        rows = (lo * D, hi * D)
+        q, k, v = (slice_rows(w, *rows) for w in (q, k, v))
+        conv = [cw[rows[0]:rows[1]] for cw in conv]
+        f_b, g_b = slice_rows(f_b, *rows), slice_rows(g_b, *rows)
+        b = slice_rows(b, lo, hi)
+        out = slice_cols(out, *rows)
+        A_log, dt_bias = A_log[lo:hi].contiguous(), dt_bias[rows[0]:rows[1]].contiguous()
+        H = hi - lo
+    return KdaW(finalize(ops.concat_weights([q, k, v])), f_a, f_b, b, g_a, g_b, torch.cat(conv, 0).contiguous(),
+                A_log, dt_bias, ld.vec(f"{p}.o_norm.weight", torch.float32), finalize(out), H)
+
+
 def mamba2(ld, p: str) -> MambaW:
     """in_proj rows are [z | x | B | C | dt]; tensor parallelism splits heads (z, x, dt) and
     state groups (B, C) together."""

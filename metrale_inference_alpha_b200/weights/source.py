@@ -190,6 +190,21 @@ class SyntheticSource(TensorSource):
             self._vec(f"{q}.dt_bias", c.gdn_v_heads, "bias")
             self._vec(f"{q}.norm.weight", c.gdn_v_dim, "ones")
             self._lin(f"{q}.out_proj", c.hidden_size, c.gdn_v_size)
+        elif lt == "kda":
+            q = f"{p}.self_attn"
+            hd, r = c.kda_heads * c.kda_head_dim, c.kda_gate_rank or c.kda_head_dim
+            for n in "qkv":
+                self._lin(f"{q}.{n}_proj", hd, c.hidden_size)
+                self._vec(f"{q}.{n}_conv1d.weight", (hd, 1, c.conv_kernel), "conv")
+            self._lin(f"{q}.f_a_proj", r, c.hidden_size, quant=False)
+            self._lin(f"{q}.f_b_proj", hd, r, quant=False)
+            self._lin(f"{q}.g_a_proj", r, c.hidden_size, quant=False)
+            self._lin(f"{q}.g_b_proj", hd, r, quant=False)
+            self._lin(f"{q}.b_proj", c.kda_heads, c.hidden_size, quant=False)
+            self._vec(f"{q}.A_log", c.kda_heads, "alog")
+            self._vec(f"{q}.dt_bias", hd, "bias")
+            self._vec(f"{q}.o_norm.weight", c.kda_head_dim, "ones")
+            self._lin(f"{q}.o_proj", c.hidden_size, hd)
         elif lt == "mla":
             q = f"{p}.self_attn"
             qh = c.qk_nope_dim + c.qk_rope_dim

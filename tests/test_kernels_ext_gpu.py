@@ -606,3 +606,47 @@ def test_paged_experts_grouped_path_matches_resident_experts(tmp_path):
     got = [o.output_ids for o in eng.generate(prompts, sp)]
     assert got == want
     assert eng.paged_experts.stats["evictions"] > 0
+
+
+# ----------------------------------------------------------------------------- Kimi delta attention
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("fused_norm", [False, True])
+def test_kda_recurrence_matches_reference(D, fused_norm):
+    g = torch.Generator().manual_seed(6)
+    H, T = 3, 11
+    conv = torch.randn(T, 3 * H * D, generator=g)
+    g_raw = torch.randn(T, H * D, generator=g)
+    b_raw = torch.randn(T, H, generator=g)
+    A_log, dtb = torch.randn(H, generator=g) * 0.3, torch.randn(H * D, generator=g) * 0.3
+    st = torch.randn(5, H, D, D, generator=g) * 0.1
+    gate = torch.randn(T, H * D, generator=g).to(torch.bfloat16)
+    w = torch.rand(D, generator=g) + 0.5
+    outs = {}
+    for dev in ("cpu", DEV):
+        s = st.clone().to(dev)
+        norm = (w.to(dev), gate.to(dev), 1e-6) if fused_norm else None
+        y = rops.kda_recurrence(conv.to(dev), g_raw.to(dev), b_raw.to(dev), A_log.to(dev), dtb.to(dev), -5.0, s,
+                                _batch(dev), heads=H, dim=D, norm=norm)
+        outs[dev] = (y, s)
+    tol = 2e-2 if fused_norm else 2e-3
+    _close(outs[DEV][0], outs["cpu"][0], tol, tol)
+    _close(outs[DEV][1], outs["cpu"][1], 2e-3, 2e-3)
+    # a pass that writes no state leaves it untouched
+    s2 = st.clone().to(DEV)
+    rops.kda_recurrence(conv.to(DEV), g_raw.to(DEV), b_raw.to(DEV), A_log.to(DEV), dtb.to(DEV), -5.0, s2, _batch(DEV),
+                        heads=H, dim=D, write_state=False)
+    assert torch.equal(s2.cpu(), st)
+    ops.check_status(torch.device(DEV))
+
+
+def test_kimi_linear_model_runs_on_the_device_and_chunked_prefill_agrees():
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    prompts = [list(range(5, 75)), list(range(40, 59))]
+    sp = SamplingParams(max_tokens=6, temperature=0.0)
+    whole = LLMEngine(EngineArgs(model="tiny-kimi-linear", device=DEV, num_kv_blocks=64, max_num_seqs=4))
+    want = [o.output_ids for o in whole.generate(prompts, sp)]
+    assert all(len(w) == 6 for w in want)
+    graphs_off = LLMEngine(EngineArgs(model="tiny-kimi-linear", device=DEV, num_kv_blocks=64, max_num_seqs=4,
+                                      use_cuda_graphs=False))
+    assert [o.output_ids for o in graphs_off.generate(prompts, sp)] == want

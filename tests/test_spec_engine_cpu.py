@@ -162,13 +162,13 @@ def _check_recurrent_speculation(device, model, **kw):
     assert got == base
 
 
-@pytest.mark.parametrize("model", ["tiny-hybrid-moe", "tiny-nemotron-h"])
+@pytest.mark.parametrize("model", ["tiny-hybrid-moe", "tiny-nemotron-h", "tiny-kimi-linear"])
 def test_speculation_on_recurrent_models_is_lossless_on_cpu(model):
     _check_recurrent_speculation("cpu", model)
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("model", ["tiny-hybrid-moe", "tiny-nemotron-h"])
+@pytest.mark.parametrize("model", ["tiny-hybrid-moe", "tiny-nemotron-h", "tiny-kimi-linear"])
 def test_speculation_on_recurrent_models_is_lossless_on_gpu(model):
     """Token-exact on the GPU as long as verify rows run on the kernel plain decode uses (up to 32
     query rows per KV head on the split-KV attention kernel: 3 drafts here). Wider verify steps
