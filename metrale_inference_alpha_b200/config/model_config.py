@@ -67,6 +67,10 @@ class ModelConfig:
     gdn_k_dim: int = 128
     gdn_v_dim: int = 128
     conv_kernel: int = 4
+    # sparse attention over MLA (DeepSeek sparse attention): a light indexer picks index_topk tokens per query
+    index_topk: int = 0                 # 0 = dense attention
+    index_n_heads: int = 64
+    index_head_dim: int = 128
     # Kimi delta attention (per-channel gated delta rule)
     kda_heads: int = 0
     kda_head_dim: int = 128
@@ -332,6 +336,7 @@ _HF_ARCH = {
     "qwen3_5_text": "qwen_hybrid", "qwen3_5_moe_text": "qwen_hybrid",
     "nemotron_h": "nemotron_h", "deepseek_v3": "deepseek_mla", "deepseek_v2": "deepseek_mla",
     "kimi_k2": "deepseek_mla",          # Kimi K2 checkpoints use the DeepSeek-V3 architecture and tensor names
+    "deepseek_v32": "deepseek_mla",     # DeepSeek-V3.2: V3 + the sparse-attention indexer
     "kimi_linear": "deepseek_mla",      # Kimi-Linear: Kimi-delta-attention layers + (NoPE) MLA layers, DeepSeek-style MoE
 }
 
@@ -495,6 +500,9 @@ def from_hf_config(cfg: dict, name: str = "model") -> ModelConfig:
                   router_n_group=cfg.get("n_group", 1), router_topk_group=cfg.get("topk_group", 1),
                   router_scaling=float(cfg.get("routed_scaling_factor", 1.0)),
                   router_renormalize=bool(cfg.get("norm_topk_prob", True)))
+        if cfg.get("index_topk"):
+            kw.update(index_topk=int(cfg["index_topk"]), index_n_heads=int(cfg.get("index_n_heads", 64)),
+                      index_head_dim=int(cfg.get("index_head_dim", 128)))
         if mt == "kimi_linear":
             la = cfg.get("linear_attn_config") or {}
             kda_layers = {int(i) - 1 for i in la.get("kda_layers", [])}            # the checkpoint counts layers from 1

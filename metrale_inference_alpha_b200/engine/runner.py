@@ -49,8 +49,10 @@ def state_shapes(cfg: ModelConfig, w: ModelW):
 
 def kv_config(cfg: ModelConfig, w: ModelW, block_size: int, mtp: bool = False) -> KvCacheConfig:
     if cfg.arch == "deepseek_mla":
+        # with a sparse-attention indexer, the pool's second tensor holds the indexer key of every token
         return KvCacheConfig(1 if mtp else len(cfg.attention_layers()), 1, cfg.kv_lora_rank + cfg.qk_rope_dim,
-                             block_size, cfg.kv_dtype if cfg.kv_dtype == "bf16" else "bf16", has_v=False)
+                             block_size, cfg.kv_dtype if cfg.kv_dtype == "bf16" else "bf16",
+                             v_head_dim=cfg.index_head_dim if cfg.index_topk > 0 else None, has_v=cfg.index_topk > 0)
     kvh = cfg.num_kv_heads
     for lw in ([w.mtp.layer] if (mtp and w.mtp) else w.layers):
         if lw.kind == "attention":

@@ -19,7 +19,7 @@ import math
 import torch
 
 from .. import ops
-from ..ops import ACT_FOR_WEIGHT, mla_cuda
+from ..ops import ACT_FOR_WEIGHT, mla_cuda, sparse_attn
 from ..ops import reference as ref
 
 
@@ -27,14 +27,20 @@ def mla_block(dec, x, lw, batch, kv, j: int):
     c, w = dec.cfg, lw.mixer
     H, nope, rope, vd, L = w.heads, c.qk_nope_dim, c.qk_rope_dim, c.v_head_dim, c.kv_lora_rank
     T = x.shape[0]
-    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.kv_a.fmt], res_only=True)
+    a = dec._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.kv_a.fmt], also_bf16=w.idx_q is not None, res_only=True)
     x = dec.res(x)
+    sel = None
     if w.q_a is not None:
         qa = ops.linear(a, w.q_a)
-        qn = ops.row_op(qa, ACT_FOR_WEIGHT[w.q_b.fmt], ops.IN_RMSNORM, w=w.q_a_norm, eps=c.rms_eps)[0]
+        want_lat = w.idx_q is not None
+        qn = ops.row_op(qa, ACT_FOR_WEIGHT[w.q_b.fmt], ops.IN_RMSNORM, w=w.q_a_norm, eps=c.rms_eps,
+                        **({"also_bf16": True} if want_lat and ACT_FOR_WEIGHT[w.q_b.fmt] != "bf16" else {}))[0]
         q = ops.linear(qn, w.q_b)
     else:
+        qn = None
         q = ops.linear(a, w.q_b)
+    if w.idx_q is not None:
+        sel = _index_select(dec, x, a, qn, w, batch, kv, j)
     scale = 1.0 / math.sqrt(nope + rope)
     sc = c.rope_scaling or {}
     if sc.get("rope_type", sc.get("type")) == "yarn" and sc.get("mscale_all_dim"):
@@ -51,8 +57,11 @@ def mla_block(dec, x, lw, batch, kv, j: int):
         q_lat = torch.bmm(q[..., :nope].transpose(0, 1), uk)           # [H, T, L]
         qq = mla_cuda.prepare(q, q_lat, ckv, w.kv_a_norm, dec.cos, dec.sin, batch.positions, batch.slot_mapping,
                               kv.k[j], nope, c.rms_eps)
-        o_lat = mla_cuda.mla_attention(qq, kv.k[j], batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
-                                       max_q_len=batch.max_q_len, max_ctx=max(batch.max_ctx, 1), scale=scale)
+        if sel is not None:
+            o_lat = sparse_attn.selected_latent_attention(qq, kv.k[j], batch.block_table, sel[0], sel[1], sel[2], scale, L)
+        else:
+            o_lat = mla_cuda.mla_attention(qq, kv.k[j], batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
+                                           max_q_len=batch.max_q_len, max_ctx=max(batch.max_ctx, 1), scale=scale)
         uv = _bf16(w, "w_uv")                                          # [H, vd, L]
         o = torch.bmm(o_lat.to(torch.bfloat16).transpose(0, 1), uv.transpose(1, 2))      # [H, T, vd]
         o = o.transpose(0, 1).reshape(T, H * vd)
@@ -70,7 +79,9 @@ def mla_block(dec, x, lw, batch, kv, j: int):
     flat.index_copy_(0, batch.slot_mapping.clamp(min=0), row)
     q_lat = torch.einsum("thn,hnl->thl", q[..., :nope], w.w_uk.float())   # absorb W_uk
     qq = torch.cat([q_lat, q_rope], -1).to(torch.bfloat16)             # [T, H, L + rope]
-    if mla_cuda.supported(qq, kv.k[j]) and L == mla_cuda.LATENT:
+    if sel is not None:
+        o_lat = sparse_attn.selected_latent_attention(qq, kv.k[j], batch.block_table, sel[0], sel[1], sel[2], scale, L)
+    elif mla_cuda.supported(qq, kv.k[j]) and L == mla_cuda.LATENT:
         o_lat = mla_cuda.mla_attention(qq, kv.k[j], batch.block_table, batch.q_start, batch.q_len, batch.ctx_len,
                                        max_q_len=batch.max_q_len, max_ctx=max(batch.max_ctx, 1), scale=scale)
     else:
@@ -78,6 +89,45 @@ def mla_block(dec, x, lw, batch, kv, j: int):
     o = torch.einsum("thl,hvl->thv", o_lat, w.w_uv.float()).reshape(T, H * vd)
     oa = ops.quantize_act(o.to(torch.bfloat16), ACT_FOR_WEIGHT[w.o.fmt])
     return dec.tp.linear_reduce(oa, w.o, residual=x, defer=True)
+
+
+def _index_select(dec, x, a, qn, w, batch, kv, j: int):
+    """The sparse-attention indexer of one layer: writes this step's indexer keys into the pool's second
+    tensor and, when some row sees more than ``index_topk`` tokens, returns (row -> sequence, selected
+    positions [T, k], count [T]); None means every row attends to its whole context (dense attention is
+    then exactly what the selection would give). Indexer queries come from the query latent, keys and
+    head weights from the block input; q / k are rotated on their first ``qk_rope_dim`` dims; the key goes
+    through a LayerNorm. score = sum_h w_h relu(q_h . k), with w scaled by Hi^-1/2 Di^-1/2."""
+    c = dec.cfg
+    Hi, Di = c.index_n_heads, c.index_head_dim
+    T = x.shape[0]
+    hb = _plain(a)
+    src = hb if qn is None else _plain(qn)
+    iq = ops.linear(dec._as_act(src, "bf16"), w.idx_q, out_f32=True).view(T, Hi, Di)
+    ik = ops.linear(dec._as_act(hb, "bf16"), w.idx_k, out_f32=True)                       # [T, Di]
+    ik = torch.nn.functional.layer_norm(ik, (Di,), w.idx_k_norm[0], w.idx_k_norm[1], 1e-6)
+    iw = ops.linear(dec._as_act(hb, "bf16"), w.idx_w, out_f32=True) * (Hi ** -0.5 * Di ** -0.5)
+    iq = ref.apply_rope_neox(iq, batch.positions, dec.cos, dec.sin)          # the first qk_rope_dim channels rotate
+    ik = ref.apply_rope_neox(ik[:, None], batch.positions, dec.cos, dec.sin)[:, 0]
+    kc = kv.v[j]
+    kc.view(-1, Di).index_copy_(0, batch.slot_mapping.clamp(min=0), ik.to(kc.dtype))
+    if batch.max_ctx <= c.index_topk:
+        return None
+    row_seq, row_ctx = sparse_attn.row_meta(batch)
+    scores = sparse_attn.index_scores(iq.to(torch.bfloat16), iw.float(), kc, batch.block_table, row_seq, row_ctx,
+                                      batch.max_ctx)
+    idx, cnt = sparse_attn.topk_indices(scores, row_ctx, c.index_topk)
+    return row_seq, idx, cnt
+
+
+def _plain(act) -> torch.Tensor:
+    """The unquantised values of an activation: its bf16 side copy, or its data when that is already
+    plain (bf16 activations; every activation on the CPU path)."""
+    if getattr(act, "bf16", None) is not None:
+        return act.bf16
+    if act.fmt == "bf16" or not act.data.is_cuda:
+        return act.data
+    raise ValueError("the indexer needs the unquantised activation (request also_bf16)")
 
 
 def _bf16(w, name: str) -> torch.Tensor:

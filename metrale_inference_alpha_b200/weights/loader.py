@@ -187,6 +187,11 @@ class MlaW:
     w_uv: torch.Tensor = None        # [H, v, kv_lora] bf16
     o: QuantWeight = None
     heads: int = 0
+    # sparse-attention indexer (replicated across tensor-parallel ranks so that every rank selects the same tokens)
+    idx_q: Optional[QuantWeight] = None          # query latent (or hidden) -> Hi * Di
+    idx_k: Optional[QuantWeight] = None          # hidden -> Di
+    idx_k_norm: Optional[torch.Tensor] = None    # LayerNorm weight | bias, fp32 [2, Di]
+    idx_w: Optional[QuantWeight] = None          # hidden -> Hi (head weights), bf16
 
 
 @dataclass

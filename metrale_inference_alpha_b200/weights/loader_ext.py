@@ -176,6 +176,12 @@ def mla(ld, p: str) -> MlaW:
     w.q_b, w.o, w.heads = finalize(q_b), finalize(o), H
     w.w_uk = kv_b[:, :c.qk_nope_dim].to(torch.bfloat16).contiguous()
     w.w_uv = kv_b[:, c.qk_nope_dim:].to(torch.bfloat16).contiguous()
+    if c.index_topk > 0:
+        q = f"{p}.indexer"
+        w.idx_q = ld.lin(f"{q}.wq_b", quant=False)
+        w.idx_k = ld.lin(f"{q}.wk", quant=False)
+        w.idx_w = ld.lin(f"{q}.weights_proj", quant=False)
+        w.idx_k_norm = torch.stack([ld.vec(f"{q}.k_norm.weight", torch.float32), ld.vec(f"{q}.k_norm.bias", torch.float32)])
     return w
 
 

@@ -218,6 +218,12 @@ class SyntheticSource(TensorSource):
             self._vec(f"{q}.kv_a_layernorm.weight", c.kv_lora_rank)
             self._lin(f"{q}.kv_b_proj", c.num_heads * (c.qk_nope_dim + c.v_head_dim), c.kv_lora_rank)
             self._lin(f"{q}.o_proj", c.hidden_size, c.num_heads * c.v_head_dim)
+            if c.index_topk > 0:
+                self._lin(f"{q}.indexer.wq_b", c.index_n_heads * c.index_head_dim, c.q_lora_rank or c.hidden_size, quant=False)
+                self._lin(f"{q}.indexer.wk", c.index_head_dim, c.hidden_size, quant=False)
+                self._lin(f"{q}.indexer.weights_proj", c.index_n_heads, c.hidden_size, quant=False)
+                self._vec(f"{q}.indexer.k_norm.weight", c.index_head_dim, "ones")
+                self._vec(f"{q}.indexer.k_norm.bias", c.index_head_dim, "bias")
         if ft != "none":
             self._vec(f"{p}.post_attention_layernorm.weight", c.hidden_size)
             if c.post_norms and c.post_norm_names == "olmo2":

@@ -594,18 +594,29 @@ def test_streamed_attention_through_files_on_the_device(tmp_path):
     hss.close()
 
 
-def test_paged_experts_grouped_path_matches_resident_experts(tmp_path):
+def test_paged_experts_grouped_path_matches_resident_experts(tmp_path, monkeypatch):
+    """One MoE block on the device: experts paged through an arena smaller than the expert count (several
+    waves per call, evictions between calls) against the same block with every expert resident."""
     from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.models.moe import moe_block
     from metrale_inference_alpha_b200.sampling.params import SamplingParams
-    prompts = [list(range(5, 45)), list(range(40, 52))]
-    sp = SamplingParams(max_tokens=6, temperature=0.0)
-    base = LLMEngine(EngineArgs(model="tiny-hybrid-moe", device=DEV, num_kv_blocks=64, max_num_seqs=4))
-    want = [o.output_ids for o in base.generate(prompts, sp)]
-    eng = LLMEngine(EngineArgs(model="tiny-hybrid-moe", device=DEV, num_kv_blocks=64, max_num_seqs=4,
-                               expert_arena_slots=3, expert_store_dir=str(tmp_path / "experts")))
-    got = [o.output_ids for o in eng.generate(prompts, sp)]
-    assert got == want
-    assert eng.paged_experts.stats["evictions"] > 0
+    from metrale_inference_alpha_b200.storage.expert_store import enable_expert_paging
+    monkeypatch.setenv("METRALE_MOE_FOLD_SHARED", "0")          # the same block structure on both sides
+    eng = LLMEngine(EngineArgs(model="tiny-hybrid-moe", device=DEV, num_kv_blocks=64, max_num_seqs=4, use_cuda_graphs=False))
+    dec = eng.runner.decoder
+    lw = next(L for L in eng.weights.layers if L.ffn_kind == "moe")
+    g = torch.Generator().manual_seed(7)
+    xs = [torch.randn(n, eng.cfg.hidden_size, generator=g).to(torch.bfloat16).to(DEV) for n in (52, 3, 1)]
+    want = [moe_block(dec, x, lw).float() for x in xs]
+    paged = enable_expert_paging(eng.weights, str(tmp_path / "experts"), 3, DEV)
+    got = [moe_block(dec, x, lw).float() for x in xs]
+    for gy, wy in zip(got, want):
+        _close(gy, wy, 2e-2, 2e-2)
+    assert paged.stats["waves"] >= 4 and paged.stats["evictions"] > 0
+    # and the engine serves with it
+    out = eng.generate([list(range(5, 45))], SamplingParams(max_tokens=4, temperature=0.0))[0].output_ids
+    assert len(out) == 4
+    ops.check_status(torch.device(DEV))
 
 
 # ----------------------------------------------------------------------------- Kimi delta attention
@@ -650,3 +661,83 @@ def test_kimi_linear_model_runs_on_the_device_and_chunked_prefill_agrees():
     graphs_off = LLMEngine(EngineArgs(model="tiny-kimi-linear", device=DEV, num_kv_blocks=64, max_num_seqs=4,
                                       use_cuda_graphs=False))
     assert [o.output_ids for o in graphs_off.generate(prompts, sp)] == want
+
+
+# ----------------------------------------------------------------------------- sparse (indexed) attention
+@pytest.mark.parametrize("Di,Hi", [(128, 64), (64, 4)])
+def test_index_scores_match_the_restatement(Di, Hi):
+    from metrale_inference_alpha_b200.ops import sparse_attn as SA
+    g = torch.Generator().manual_seed(8)
+    bs, nb = 16, 40
+    kc = torch.randn(nb, bs, 1, Di, generator=g).to(torch.bfloat16)
+    table = torch.randint(1, nb, (2, 24), generator=g, dtype=torch.int32)
+    row_seq = torch.tensor([0, 0, 0, 1], dtype=torch.int32)
+    row_ctx = torch.tensor([298, 299, 300, 77], dtype=torch.int32)
+    iq = torch.randn(4, Hi, Di, generator=g).to(torch.bfloat16)
+    iw = torch.rand(4, Hi, generator=g)
+    want = SA.index_scores(iq, iw, kc, table, row_seq, row_ctx, 300)
+    got = SA.index_scores(iq.to(DEV), iw.to(DEV), kc.to(DEV), table.to(DEV), row_seq.to(DEV), row_ctx.to(DEV), 300).cpu()
+    assert got.shape == want.shape and torch.equal(torch.isinf(got), torch.isinf(want))
+    fin = ~torch.isinf(want)
+    _close(got[fin], want[fin], 2e-3, 2e-3)
+    ops.check_status(torch.device(DEV))
+
+
+def test_topk_selection_equals_a_stable_sort():
+    from metrale_inference_alpha_b200.ops import sparse_attn as SA
+    g = torch.Generator().manual_seed(9)
+    T, n = 5, 5000
+    sc = torch.randn(T, 5056, generator=g)
+    sc[1] = torch.randint(0, 20, (5056,), generator=g).float()            # heavy ties
+    sc[2, :] = 1.0                                                         # everything equal
+    sc[3] = -sc[3].abs()                                                   # all negative
+    ctx = torch.tensor([n, n, 4000, 3000, 37], dtype=torch.int32)
+    for k in (64, 2048):
+        want_i, want_c = SA.topk_indices(sc, ctx, k)
+        got_i, got_c = SA.topk_indices(sc.to(DEV), ctx.to(DEV), k)
+        assert torch.equal(got_c.cpu(), want_c)
+        assert torch.equal(got_i.cpu(), want_i)
+
+
+def test_selected_latent_attention_matches_the_restatement():
+    from metrale_inference_alpha_b200.ops import sparse_attn as SA
+    g = torch.Generator().manual_seed(10)
+    bs, nb, H, W, L = 16, 64, 16, 576, 512
+    cache = (torch.randn(nb, bs, 1, W, generator=g) * 0.3).to(torch.bfloat16)
+    table = torch.randint(1, nb, (2, 40), generator=g, dtype=torch.int32)
+    row_seq = torch.tensor([0, 1, 1], dtype=torch.int32)
+    row_ctx = torch.tensor([600, 333, 334], dtype=torch.int32)
+    sc = torch.randn(3, 640, generator=g)
+    idx, cnt = SA.topk_indices(sc, row_ctx, 128)
+    qq = (torch.randn(3, H, W, generator=g) * 0.3).to(torch.bfloat16)
+    want = SA.selected_latent_attention(qq, cache, table, row_seq, idx, cnt, 0.05, L)
+    got = SA.selected_latent_attention(qq.to(DEV), cache.to(DEV), table.to(DEV), row_seq.to(DEV), idx.to(DEV), cnt.to(DEV),
+                                       0.05, L)
+    _close(got, want, 2e-2, 2e-2)
+    rows_d = SA.gather_rows(cache.to(DEV), table.to(DEV), row_seq.to(DEV), idx.to(DEV), cnt.to(DEV)).cpu()
+    rows_h = SA.gather_rows(cache, table, row_seq, idx, cnt)
+    n = int(cnt[0])
+    assert torch.equal(rows_d.view(3, -1, W)[:, :n], rows_h.view(3, -1, W)[:, :n])
+    ops.check_status(torch.device(DEV))
+
+
+def test_sparse_mla_model_runs_on_the_device():
+    import dataclasses
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    cfg = preset("deepseek-v3-671b-fp8", num_layers=3, first_dense_layers=1, hidden_size=512, num_heads=16,
+                 num_kv_heads=16, q_lora_rank=256, dense_intermediate_size=1024, intermediate_size=1024,
+                 num_experts=8, experts_per_token=2, moe_intermediate_size=256, router_n_group=2,
+                 router_topk_group=1, vocab_size=4096, mtp_layers=0, max_position=1024,
+                 index_topk=32, index_n_heads=4, index_head_dim=64)
+    prompts = [list(range(5, 105)), list(range(200, 230))]
+    sp = SamplingParams(max_tokens=6, temperature=0.0)
+    eager = LLMEngine(EngineArgs(model=cfg, device=DEV, num_kv_blocks=64, max_num_seqs=4, use_cuda_graphs=False))
+    want = [o.output_ids for o in eager.generate(prompts, sp)]
+    graphs = LLMEngine(EngineArgs(model=cfg, device=DEV, num_kv_blocks=64, max_num_seqs=4))
+    assert [o.output_ids for o in graphs.generate(prompts, sp)] == want
+    # the selection covers the whole context: the dense kernel and the gather path see the same tokens
+    wide = dataclasses.replace(cfg, index_topk=512)
+    dense = LLMEngine(EngineArgs(model=wide, device=DEV, num_kv_blocks=64, max_num_seqs=4, use_cuda_graphs=False))
+    assert all(len(o.output_ids) == 6 for o in dense.generate(prompts, sp))
+    ops.check_status(torch.device(DEV))
