@@ -67,6 +67,10 @@ class ModelConfig:
     gdn_k_dim: int = 128
     gdn_v_dim: int = 128
     conv_kernel: int = 4
+    # hyper-connections: the residual stream is hc_mult fp32 copies mixed in and out of every block
+    hc_mult: int = 0                    # 0 / 1 = a single residual stream
+    hc_sinkhorn_iters: int = 20
+    hc_eps: float = 1e-6
     # sparse attention over MLA (DeepSeek sparse attention): a light indexer picks index_topk tokens per query
     index_topk: int = 0                 # 0 = dense attention
     index_n_heads: int = 64
@@ -297,6 +301,13 @@ def tiny_nemotron_h(**kw) -> ModelConfig:
     return nemotron_h_8b(**base)
 
 
+def tiny_dense_hc(**kw) -> ModelConfig:
+    """The tiny dense model with a four-stream hyper-connection highway (tests, smoke runs)."""
+    base = dict(hc_mult=4, hc_sinkhorn_iters=4, name="tiny-dense-hc")
+    base.update(kw)
+    return tiny_dense(**base)
+
+
 def tiny_kimi_linear(**kw) -> ModelConfig:
     """Four-layer instance of the Kimi-Linear family: three Kimi-delta-attention layers per full-attention
     layer, MoE feed-forward (tests, smoke runs)."""
@@ -312,6 +323,7 @@ def tiny_kimi_linear(**kw) -> ModelConfig:
 PRESETS = {
     "tiny-dense": tiny_dense,
     "tiny-kimi-linear": tiny_kimi_linear,
+    "tiny-dense-hc": tiny_dense_hc,
     "tiny-hybrid-moe": tiny_hybrid_moe,
     "tiny-nemotron-h": tiny_nemotron_h,
     "dense-27b-nvfp4": dense_27b_nvfp4,

@@ -301,6 +301,8 @@ class Decoder:
         side = self.side_head
         if side is not None:
             side.begin(x.shape[0])
+        if self.cfg.hc_mult > 1:
+            return self._backbone_highway(x, batch, caches)
         for i, lw in enumerate(self.w.layers):
             x = self.layer(i, x, lw, batch, caches)
             if side is not None and i in side.capture_ids:
@@ -309,6 +311,33 @@ class Decoder:
         if side is not None:
             side.absorb(batch)
         return x
+
+    def _backbone_highway(self, x, batch: ForwardBatch, caches: LayerCaches) -> torch.Tensor:
+        """Hyper-connection models: the residual stream is hc fp32 copies per token. Each block reads a
+        learned mixture of the copies (``hc_pre``: one fused kernel for the statistics, the mixing
+        projection, the gates and the Sinkhorn-normalised combination matrix) and its output is
+        written back into every copy (``hc_post``); the final norm sees the mean of the copies.
+        Dense GQA blocks only (the block output is taken without its residual add). Reference:
+        kernels/gb10/common/glm5next_mhc.cu, deepseek-v4-flash/nvfp4/hyper_connection.cu."""
+        from ..ops import highway as hw
+        c = self.cfg
+        if self.tp.size > 1:
+            raise NotImplementedError("hyper-connections are served on one rank")
+        kw = dict(norm_eps=c.rms_eps, hc_eps=c.hc_eps, iters=c.hc_sinkhorn_iters)
+        streams = hw.hc_expand(x, c.hc_mult)
+        for i, lw in enumerate(self.w.layers):
+            if lw.kind != "attention" or lw.ffn_kind != "dense":
+                raise NotImplementedError("hyper-connections: attention + dense feed-forward layers only")
+            kv, j = caches.kv, caches.kv_index[i]
+            y, post, comb = hw.hc_pre(streams, *lw.hc_attn, **kw)
+            f = self.attention_block(y, lw, batch, kv.k[j], kv.v[j], kv.k_scale[j], kv.v_scale[j], li=i,
+                                     add_residual=False, kv_layer=j)
+            streams = hw.hc_post(self.full(f), streams, post, comb)
+            y, post, comb = hw.hc_pre(streams, *lw.hc_ffn, **kw)
+            a = self._norm_act(y, lw.ln2, ACT_FOR_WEIGHT[lw.ffn.gate_up.fmt])
+            f = self.dense_ffn(a, lw.ffn, None, None, i, None)
+            streams = hw.hc_post(self.full(f), streams, post, comb)
+        return hw.hc_head_mean(streams)
 
     def logits(self, hidden_rows, final_norm=None, out_f32: bool = False, gather: bool = True) -> torch.Tensor:
         """Final norm + (vocab-parallel) lm_head on the selected rows."""

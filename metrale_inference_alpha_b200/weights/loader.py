@@ -204,6 +204,8 @@ class LayerW:
     post_ffn: Optional[torch.Tensor] = None
     mixer: object = None
     ffn: object = None
+    hc_attn: Optional[tuple] = None              # hyper-connection site in front of the mixer: (fn bf16, scale fp32 [3], base fp32)
+    hc_ffn: Optional[tuple] = None               # ... and in front of the feed-forward block
 
 
 @dataclass
@@ -376,6 +378,10 @@ class Loader:
             L.ffn = self.ffn(f"{p}.mlp")
         elif ft == "moe":
             L.ffn = loader_ext.moe(self, f"{p}.mlp")
+        if c.hc_mult > 1:
+            site = lambda q: (self.src.get(f"{q}.fn").to(self.dev).to(torch.bfloat16).contiguous(),
+                              self.vec(f"{q}.scale", torch.float32), self.vec(f"{q}.base", torch.float32))
+            L.hc_attn, L.hc_ffn = site(f"{p}.attn_hc"), site(f"{p}.ffn_hc")
         return L
 
     def load(self) -> ModelW:

@@ -224,6 +224,12 @@ class SyntheticSource(TensorSource):
                 self._lin(f"{q}.indexer.weights_proj", c.index_n_heads, c.hidden_size, quant=False)
                 self._vec(f"{q}.indexer.k_norm.weight", c.index_head_dim, "ones")
                 self._vec(f"{q}.indexer.k_norm.bias", c.index_head_dim, "bias")
+        if c.hc_mult > 1:
+            mix = (2 + c.hc_mult) * c.hc_mult
+            for site in ("attn_hc", "ffn_hc"):
+                self._vec(f"{p}.{site}.fn", (mix, c.hc_mult * c.hidden_size), "small")
+                self._vec(f"{p}.{site}.scale", 3, "ones")
+                self._vec(f"{p}.{site}.base", mix, "bias")
         if ft != "none":
             self._vec(f"{p}.post_attention_layernorm.weight", c.hidden_size)
             if c.post_norms and c.post_norm_names == "olmo2":
@@ -354,6 +360,8 @@ class SyntheticSource(TensorSource):
                 return (self._rand(name, shape, 0.3)).float()
             if kind == "bias":
                 return self._rand(name, shape, 0.1).float()
+            if kind == "small":
+                return self._rand(name, shape, 0.02).to(torch.bfloat16)
         prefix, suffix = self._split(name)
         if prefix is None or not self.has(name):
             raise KeyError(name)

@@ -741,3 +741,58 @@ def test_sparse_mla_model_runs_on_the_device():
     dense = LLMEngine(EngineArgs(model=wide, device=DEV, num_kv_blocks=64, max_num_seqs=4, use_cuda_graphs=False))
     assert all(len(o.output_ids) == 6 for o in dense.generate(prompts, sp))
     ops.check_status(torch.device(DEV))
+
+
+# ----------------------------------------------------------------------------- residual highway
+def test_hyper_connection_kernels_match_the_restatement():
+    from metrale_inference_alpha_b200.ops import highway as hw
+    g = torch.Generator().manual_seed(11)
+    for hc, H in ((4, 1024), (2, 512)):
+        T = 7
+        streams = torch.randn(T, hc, H, generator=g)
+        fn = (torch.randn((2 + hc) * hc, hc * H, generator=g) * 0.03).to(torch.bfloat16)
+        scale, base = torch.tensor([1.0, 0.5, 2.0]), torch.randn((2 + hc) * hc, generator=g) * 0.1
+        want = hw.hc_pre(streams, fn, scale, base, iters=6)
+        got = hw.hc_pre(streams.to(DEV), fn.to(DEV), scale.to(DEV), base.to(DEV), iters=6)
+        for a, b in zip(got, want):
+            _close(a, b, 1e-2, 1e-2)
+        out = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        s_d = hw.hc_post(out.to(DEV), streams.clone().to(DEV), want[1].to(DEV), want[2].to(DEV))
+        _close(s_d, hw.hc_post(out, streams.clone(), want[1], want[2]), 1e-4, 1e-4)
+
+
+def test_engram_ple_and_dilated_conv_kernels_match_the_restatement():
+    from metrale_inference_alpha_b200.ops import highway as hw
+    g = torch.Generator().manual_seed(12)
+    T, hc, H = 11, 4, 512
+    streams = torch.randn(T, hc, H, generator=g)
+    kv = torch.randn(T, (hc + 1) * H, generator=g).to(torch.bfloat16)
+    qk = torch.rand(hc, H, generator=g)
+    _close(hw.engram_gate_add(streams.clone().to(DEV), kv.to(DEV), qk.to(DEV)), hw.engram_gate_add(streams.clone(), kv, qk),
+           1e-3, 1e-3)
+    key, value = torch.randn(T, hc * H, generator=g).to(torch.bfloat16), torch.randn(T, H, generator=g).to(torch.bfloat16)
+    ws = [torch.randn(hc, H, generator=g) * 0.1 for _ in range(3)]
+    want = hw.ple_gate(streams, key, value, *ws)
+    got = hw.ple_gate(streams.to(DEV), key.to(DEV), value.to(DEV), *[w.to(DEV) for w in ws])
+    _close(got[0], want[0], 1e-3, 1e-3)
+    _close(got[1], want[1], 2e-3, 2e-3)
+    C, taps, dil = hc * H, 4, 3
+    w = torch.randn(C, taps, generator=g) * 0.3
+    st = torch.randn(5, C, (taps - 1) * dil, generator=g)
+    s_h, s_d = st.clone(), st.clone().to(DEV)
+    o_h = hw.dilated_conv(want[1], want[0], w, s_h, _batch("cpu"), dil)
+    o_d = hw.dilated_conv(want[1].to(DEV), want[0].to(DEV), w.to(DEV), s_d, _batch(DEV), dil)
+    _close(o_d, o_h, 1e-3, 1e-3)
+    _close(s_d, s_h, 1e-5, 1e-5)
+    ops.check_status(torch.device(DEV))
+
+
+def test_dense_model_on_a_highway_runs_on_the_device():
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    prompts = [list(range(5, 60)), list(range(40, 52))]
+    sp = SamplingParams(max_tokens=6, temperature=0.0)
+    eager = LLMEngine(EngineArgs(model="tiny-dense-hc", device=DEV, num_kv_blocks=64, max_num_seqs=4, use_cuda_graphs=False))
+    want = [o.output_ids for o in eager.generate(prompts, sp)]
+    graphs = LLMEngine(EngineArgs(model="tiny-dense-hc", device=DEV, num_kv_blocks=64, max_num_seqs=4))
+    assert [o.output_ids for o in graphs.generate(prompts, sp)] == want
