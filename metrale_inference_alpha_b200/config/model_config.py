@@ -67,6 +67,11 @@ class ModelConfig:
     gdn_k_dim: int = 128
     gdn_v_dim: int = 128
     conv_kernel: int = 4
+    # vision input (Qwen-VL family): the tower's configuration, the placeholder token and the rotary sections
+    vision: Optional[dict] = None       # HF vision_config of the checkpoint (vision.VisionConfig.from_hf)
+    image_token_id: int = -1
+    vision_start_token_id: int = -1
+    mrope_sections: Optional[List[int]] = None      # rotary frequencies per (time, height, width) axis
     # hyper-connections: the residual stream is hc_mult fp32 copies mixed in and out of every block
     hc_mult: int = 0                    # 0 / 1 = a single residual stream
     hc_sinkhorn_iters: int = 20
@@ -353,6 +358,12 @@ _HF_ARCH = {
 }
 
 
+# vision-language wrappers -> the text stack they carry (tensor names under model.language_model. are
+# unwrapped by weights/remap.py)
+_HF_VISION = {"qwen2_vl": "qwen2", "qwen2_5_vl": "qwen2", "qwen2_vl_text": "qwen2", "qwen2_5_vl_text": "qwen2",
+              "qwen3_vl": "qwen3", "qwen3_vl_text": "qwen3"}
+
+
 def detect_weight_format(qc: Optional[dict]) -> str:
     """quantization_config -> serving weight format
     (crates/model-layers/src/quant_format/mod.rs:61-138, weight_map/nvfp4_detect.rs:23-38)."""
@@ -374,11 +385,23 @@ def detect_weight_format(qc: Optional[dict]) -> str:
 
 def from_hf_config(cfg: dict, name: str = "model") -> ModelConfig:
     """Map a HF ``config.json`` dict (text stack) to ModelConfig; refuses unknown model types."""
+    outer = cfg
     if "text_config" in cfg:
         inner = dict(cfg["text_config"])
         inner.setdefault("quantization_config", cfg.get("quantization_config"))
         cfg = inner
     mt = cfg.get("model_type", "")
+    vision_kw = {}
+    if outer.get("vision_config") and (outer.get("model_type", "") in _HF_VISION or mt in _HF_VISION):
+        rs = cfg.get("rope_scaling") or outer.get("rope_scaling") or {}
+        vision_kw = dict(vision=dict(outer["vision_config"]), image_token_id=int(outer.get("image_token_id", -1)),
+                         vision_start_token_id=int(outer.get("vision_start_token_id", -1)),
+                         mrope_sections=list(rs["mrope_section"]) if rs.get("mrope_section") else None)
+        if mt in _HF_VISION:
+            mt = _HF_VISION[mt]
+        if (rs.get("type") or rs.get("rope_type")) in ("mrope", "default"):
+            cfg = dict(cfg)
+            cfg["rope_scaling"] = None                     # the sections only say which axis a frequency follows
     if mt not in _HF_ARCH:
         raise ValueError(f"unsupported model_type {mt!r}")
     arch = _HF_ARCH[mt]
@@ -533,6 +556,7 @@ def from_hf_config(cfg: dict, name: str = "model") -> ModelConfig:
                       router_n_group=cfg.get("num_expert_group", cfg.get("n_group", 1)),
                       router_topk_group=cfg.get("topk_group", 1),
                       router_renormalize=bool(cfg.get("moe_renormalize", cfg.get("norm_topk_prob", True))))
+    kw.update(vision_kw)
     return ModelConfig(**kw)
 
 

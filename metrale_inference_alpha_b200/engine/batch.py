@@ -50,6 +50,11 @@ class ForwardBatch:
     want_hidden: bool = False
     # LoRA: adapter slot of every token row (-1 = base model); None when no row has an adapter
     adapter_rows: Optional[torch.Tensor] = None
+    # multimodal rows: (row indices int64 [n], embeddings bf16 [n, hidden]) that replace token embeddings
+    embed_override: Optional[tuple] = None
+    # per-row rotary tables (cos, sin) [T, rot / 2] when some row's rotary position is not its sequence index
+    rope_tables: Optional[tuple] = None
+    rope_rows: Optional[torch.Tensor] = None     # arange(T) int32: row -> its rotary row
     # speculative verify over recurrent layers: state is left untouched and inputs are retained here
     spec_stash: Optional[SpecStash] = None
 

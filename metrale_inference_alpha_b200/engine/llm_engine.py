@@ -232,17 +232,57 @@ class LLMEngine:
             self.runner.decoder.lora.unload(name)
 
     # ------------------------------------------------------------------ requests
+    # ------------------------------------------------------------------ vision input
+    vision = None
+
+    def attach_vision(self, encoder=None, preprocessor=None, seed: int = 0) -> None:
+        """Enable ``add_request(..., images=[...])``. Without an encoder the tower of the model
+        configuration is built with random weights (synthetic checkpoints); ``open_vision`` loads it
+        from a checkpoint's ``visual.`` tensors."""
+        from ..vision import ImagePreprocessor, VisionConfig, VisionEncoder
+        c = self.cfg
+        if c.image_token_id < 0:
+            raise ValueError("the model configuration names no image placeholder token")
+        if self.args.speculative != "none":
+            raise NotImplementedError("image inputs and speculative decoding are not combined")
+        if encoder is None:
+            vc = VisionConfig.from_hf(dict(c.vision or {}, hidden_size=c.hidden_size))
+            encoder = VisionEncoder(vc, VisionEncoder.random_tensors(vc, seed), device=self.device)
+        if encoder.cfg.hidden_size != c.hidden_size:
+            raise ValueError("the vision tower's output width differs from the model's hidden size")
+        vc = encoder.cfg
+        self.vision = (encoder, preprocessor or ImagePreprocessor(vc.patch_size, vc.spatial_merge_size, vc.temporal_patch_size))
+
+    def open_vision(self, source) -> None:
+        """Load the vision tower from a checkpoint source (tensor names ``visual.*`` or ``model.visual.*``)."""
+        from ..vision import VisionConfig, VisionEncoder
+        vc = VisionConfig.from_hf(dict(self.cfg.vision or {}, hidden_size=self.cfg.hidden_size))
+        names = [n for n in source.names() if n.startswith(("visual.", "model.visual."))]
+        if not names:
+            raise ValueError("the checkpoint holds no visual.* tensors")
+        tensors = {n.split("visual.", 1)[1]: source.get(n) for n in names}
+        self.attach_vision(VisionEncoder(vc, tensors, device=self.device))
+
     def add_request(self, prompt_ids: Seq[int], params: Optional[SamplingParams] = None,
-                    request_id: Optional[str] = None, adapter: Optional[str] = None) -> str:
+                    request_id: Optional[str] = None, adapter: Optional[str] = None, images=None) -> str:
         if self.fault.is_set():
             raise FatalDeviceError(self.fault.reason())
         rid = request_id or f"req-{next(self._ids)}"
         params = params or SamplingParams()
+        mm = None
+        if images:
+            if self.vision is None:
+                raise ValueError("this engine serves no image inputs (attach_vision was not called)")
+            from .multimodal import build_inputs
+            enc, pre = self.vision
+            prompt_ids, mm = build_inputs(prompt_ids, images, encoder=enc, preprocessor=pre,
+                                          image_token_id=self.cfg.image_token_id, merge=enc.cfg.spatial_merge_size,
+                                          device=self.device)
         adapter = adapter or params.adapter
         if adapter and (self.runner.decoder.lora is None or adapter not in self.runner.decoder.lora.slots):
             raise ValueError(f"unknown LoRA adapter {adapter!r}")
         req = Request(rid, list(prompt_ids), params, adapter=adapter,
-                      eos_token_id=self.args.eos_token_id)
+                      eos_token_id=self.args.eos_token_id, mm=mm)
         self.scheduler.add_request(req)
         return rid
 
@@ -374,12 +414,14 @@ class LLMEngine:
         return False
 
     # ------------------------------------------------------------------ offline loop
-    def generate(self, prompts: Iterable[Seq[int]], params: Union[SamplingParams, Seq[SamplingParams], None] = None
-                 ) -> List[RequestOutput]:
+    def generate(self, prompts: Iterable[Seq[int]], params: Union[SamplingParams, Seq[SamplingParams], None] = None,
+                 images: Optional[Seq] = None) -> List[RequestOutput]:
+        """``images``: per prompt, the list of images its placeholder tokens stand for (or None)."""
         prompts = list(prompts)
         if params is None or isinstance(params, SamplingParams):
             params = [params or SamplingParams()] * len(prompts)
-        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        images = list(images) if images is not None else [None] * len(prompts)
+        ids = [self.add_request(p, sp, images=im) for p, sp, im in zip(prompts, params, images)]
         done: Dict[str, RequestOutput] = {}
         while len(done) < len(ids):
             outs = self.step()

@@ -383,6 +383,8 @@ class ModelRunner:
     def _stage_with_adapters(self, plan: StepPlan) -> ForwardBatch:
         batch = self._stage(plan)
         batch.adapter_rows = self._adapter_rows(plan)
+        if any(i.seq.req.mm is not None for i in plan.items):
+            self._attach_multimodal(plan, batch)
         self.pending_stash = None
         if self.pool is not None and any(i.verify for i in plan.items):
             from .batch import SpecStash
@@ -390,6 +392,61 @@ class ModelRunner:
         return batch
 
     pending_stash = None
+
+    def _attach_multimodal(self, plan: StepPlan, batch: ForwardBatch) -> None:
+        """Steps that hold a sequence with images: rows on placeholder tokens take the vision tower's
+        embeddings, and every row gets its rotary row from three-axis positions (prompt rows from the
+        request's index, generated rows from sequence index + the request's offset on all axes)."""
+        from ..vision.mrope import gather_tables
+        dec = self.decoder
+        T = batch.num_tokens
+        pos3 = torch.zeros(3, T, dtype=torch.int64)
+        rows, embs = [], []
+        r = 0
+        for it in plan.items:
+            n, p0, mm = len(it.tokens), it.start_pos, it.seq.req.mm
+            idx = torch.arange(p0, p0 + n)
+            if mm is None:
+                pos3[:, r:r + n] = idx
+            else:
+                L = mm.positions.shape[1]
+                inside = idx < L
+                pos3[:, r:r + n] = torch.where(inside, mm.positions[:, idx.clamp(max=L - 1)], idx + mm.delta)
+                for j in range(n):
+                    e = mm.row_of_token.get(p0 + j)
+                    if e is not None:
+                        rows.append(r + j)
+                        embs.append(e)
+            r += n
+        half = dec.cos.shape[1]
+        sections = self.cfg.mrope_sections or [half - 2 * (half // 3), half // 3, half // 3]
+        cos, sin = gather_tables(dec.cos, dec.sin, pos3[:, :T].to(self.device), sections)
+        pad = batch.token_ids.shape[0] - T
+        if pad > 0:
+            cos = torch.cat([cos, cos.new_ones(pad, half)])
+            sin = torch.cat([sin, sin.new_zeros(pad, half)])
+        batch.rope_tables = (cos.contiguous(), sin.contiguous())
+        batch.rope_rows = torch.arange(batch.token_ids.shape[0], dtype=torch.int32, device=self.device)
+        if rows:
+            mmv = [it.seq.req.mm for it in plan.items if it.seq.req.mm is not None]
+            table = torch.cat([m.embeds for m in mmv], 0)
+            base, off = {}, 0
+            for m in mmv:
+                base[id(m)] = off
+                off += m.embeds.shape[0]
+            sel = []
+            r = 0
+            for it in plan.items:
+                mm = it.seq.req.mm
+                if mm is not None:
+                    for j in range(len(it.tokens)):
+                        e = mm.row_of_token.get(it.start_pos + j)
+                        if e is not None:
+                            sel.append(base[id(mm)] + e)
+                r += len(it.tokens)
+            batch.embed_override = (torch.tensor(rows, dtype=torch.int64, device=self.device),
+                                    table[torch.tensor(sel, dtype=torch.int64, device=self.device)])
+            self.h2d_bytes += 16 * len(rows)
 
     def commit_recurrent(self, plan: StepPlan) -> None:
         """After the scheduler has applied a verify step: advance the recurrent state of every
@@ -568,6 +625,8 @@ class ModelRunner:
             return False
         if self.decoder.lora is not None and any(i.seq.req.adapter for i in plan.items):
             return False
+        if any(i.seq.req.mm is not None for i in plan.items):
+            return False
         for it in plan.items:
             p = it.seq.req.params
             if len(it.tokens) != 1 or not it.sample or not p.greedy or p.logprobs or p.needs_host_logits \
@@ -636,7 +695,8 @@ class ModelRunner:
         if host_logits:
             return self._execute_host_logits(plan, t0)
         is_plain_decode = plan.kind == "decode" and all(len(i.tokens) == 1 for i in plan.items)
-        uses_adapter = self.decoder.lora is not None and any(i.seq.req.adapter for i in plan.items)
+        uses_adapter = (self.decoder.lora is not None and any(i.seq.req.adapter for i in plan.items)) \
+            or any(i.seq.req.mm is not None for i in plan.items)          # rows with their own rotary rows run eagerly too
         K = plan.items[0].verify if plan.items else 0
         uniform_verify = (plan.kind == "verify" and K > 0 and greedy and not want_lp
                           and all(i.verify == K and len(i.tokens) == K + 1 and i.sample for i in plan.items)

@@ -145,6 +145,14 @@ class Decoder:
         window = c.window_layers[li] if (c.window_layers and 0 <= li < len(c.window_layers)) else c.sliding_window
         local = window > 0 and self.cos_local is not None
         cos, sin = (self.cos_local, self.sin_local) if local else (self.cos, self.sin)
+        rope_pos = batch.positions
+        if getattr(batch, "rope_tables", None) is not None:
+            # multimodal batch: every row brings its own rotary row (three-axis positions gathered per
+            # frequency section), addressed by the row's index
+            if local:
+                raise NotImplementedError("multimodal rotary positions with per-layer local rotary bases")
+            cos, sin = batch.rope_tables
+            rope_pos = batch.rope_rows
         lora = self._lora_for(batch, li)
         a = self._norm_act(x, lw.ln1, ACT_FOR_WEIGHT[w.qkv.fmt], also_bf16=lora is not None, res_only=add_residual)
         x = self.res(x)
@@ -172,7 +180,7 @@ class Decoder:
                 qkv[:, lo:lo + n] = part.to(qkv.dtype)
             qn = kn = None
         q = ops.qk_norm_rope_kvwrite(
-            qkv, Hq=w.heads, Hkv=w.kv_heads, D=D, positions=batch.positions, slots=batch.slot_mapping,
+            qkv, Hq=w.heads, Hkv=w.kv_heads, D=D, positions=rope_pos, slots=batch.slot_mapping,
             k_cache=kc, v_cache=vc, q_norm_w=qn, k_norm_w=kn, plus_one=c.norm_plus_one,
             eps=c.rms_eps, cos=cos, sin=sin, q_head_stride=qhs, k_scale=ks, v_scale=vs,
             amax=self.kv_cal.amax_for(kv_layer) if (self.kv_cal is not None and kv_layer >= 0) else None)
@@ -298,6 +306,9 @@ class Decoder:
     def backbone(self, batch: ForwardBatch, caches: LayerCaches) -> torch.Tensor:
         """Token ids -> final residual stream [T, hidden] (before the final norm)."""
         x = self.embed(batch.token_ids)
+        if getattr(batch, "embed_override", None) is not None:
+            rows, emb = batch.embed_override
+            x = x.index_copy(0, rows, emb.to(x.dtype))
         side = self.side_head
         if side is not None:
             side.begin(x.shape[0])

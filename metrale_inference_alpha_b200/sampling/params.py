@@ -33,6 +33,7 @@ class SamplingParams:
     stop_token_ids: List[int] = field(default_factory=list)
     ignore_eos: bool = False
     logprobs: bool = False
+    images: Optional[list] = None              # images of the request (data: URLs, bytes, arrays) for engines with a vision tower
     top_logprobs: int = 0
     n: int = 1
     timeout_s: float = 0.0

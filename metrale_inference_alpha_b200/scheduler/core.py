@@ -111,7 +111,7 @@ class SchedulerCore:
                 continue
             matched, snap = [], None
             if self.prefix is not None and seq.num_computed == 0:
-                m = self.prefix.match(seq.tokens, seq.req.adapter)
+                m = self.prefix.match(seq.tokens, seq.req.cache_ns)
                 matched, snap = m.blocks, m.snapshot
             reserve = min(seq.req.params.max_tokens, cfg.decode_reserve_tokens)
             need = self._blocks_for(len(seq.tokens) + reserve) - len(matched)
@@ -126,7 +126,7 @@ class SchedulerCore:
                 if self.num_active == 0 and self._blocks_for(len(seq.tokens) + 1) <= self._free_capacity():
                     # forced-oversize liveness: admit with a smaller reserve when alone
                     if self.prefix is not None and seq.num_computed == 0:
-                        m = self.prefix.match(seq.tokens, seq.req.adapter)
+                        m = self.prefix.match(seq.tokens, seq.req.cache_ns)
                         matched, snap = m.blocks, m.snapshot
                 else:
                     break                                   # stop at the first misfit (FIFO)
@@ -437,7 +437,7 @@ class SchedulerCore:
             n_full = min(seq.num_computed, len(seq.tokens)) // self.cfg.block_size
             if n_full:
                 self.prefix.insert(seq.tokens[:n_full * self.cfg.block_size], seq.blocks[:n_full],
-                                   seq.req.adapter, getattr(seq, "snapshots", None))
+                                   seq.req.cache_ns, getattr(seq, "snapshots", None))
         self._release(seq)
         seq.status = SeqStatus.FINISHED
         seq.finish = reason

@@ -40,6 +40,13 @@ class Request:
     arrival: float = field(default_factory=time.monotonic)
     adapter: Optional[str] = None
     eos_token_id: Optional[int] = None
+    mm: Optional[object] = None          # engine.multimodal.MultiModalInputs of a request with images
+
+    @property
+    def cache_ns(self):
+        """Namespace of this request in the prefix cache: placeholder tokens of different images are the
+        same ids, so cached blocks are only shared between requests that carry the same images."""
+        return self.adapter if self.mm is None else (self.adapter, self.mm.digest)
 
 
 class Sequence:

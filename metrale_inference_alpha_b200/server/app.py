@@ -216,6 +216,14 @@ def create_app(engine, tokenizer, cfg: Optional[ServerConfig] = None, control=No
         text = renderer.render(msgs, tools=tools, add_generation_prompt=True, enable_thinking=thinking, **kw)
         ids = tokenizer.encode(text)
         sp = _sampling_from(body, cfg)
+        from .chat_template import collect_images
+        imgs = collect_images(msgs)
+        if imgs:
+            if getattr(engine, "vision", None) is None:
+                raise HTTPException(400, "this model takes no image input")
+            if any(not str(u).startswith("data:") for u in imgs):
+                raise HTTPException(400, "images must be sent inline as data: URLs (the server fetches nothing)")
+            sp.images = imgs
         if tools and cfg.loop_detector and tool_open_first is not None:
             from .loop_detector import check_loops
             verdict = check_loops(msgs, True)

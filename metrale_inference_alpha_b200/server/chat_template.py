@@ -14,6 +14,34 @@ CHATML = (
 )
 
 
+IMAGE_PLACEHOLDER = "<|vision_start|><|image_pad|><|vision_end|>"
+_IMAGE_PARTS = ("image_url", "input_image", "image")
+
+
+def image_of_part(p) -> Optional[str]:
+    """The image a content part carries, as a data: URL (OpenAI ``image_url`` / ``input_image`` parts,
+    Anthropic ``image`` blocks with a base64 source), or None for any other part."""
+    if not isinstance(p, dict) or p.get("type") not in _IMAGE_PARTS:
+        return None
+    if p["type"] == "image":
+        src = p.get("source") or {}
+        if src.get("type") == "base64":
+            return f"data:{src.get('media_type', 'image/png')};base64,{src.get('data', '')}"
+        return src.get("url")
+    u = p.get("image_url")
+    return u.get("url") if isinstance(u, dict) else u
+
+
+def collect_images(messages) -> List[str]:
+    """Images of a conversation in the order their placeholders appear in the rendered prompt."""
+    out = []
+    for m in messages:
+        c = m.get("content")
+        if isinstance(c, list):
+            out += [u for u in (image_of_part(p) for p in c) if u]
+    return out
+
+
 def _content_to_text(content) -> str:
     if content is None:
         return ""
@@ -25,6 +53,8 @@ def _content_to_text(content) -> str:
             parts.append(p)
         elif p.get("type") in ("text", "input_text", "output_text"):
             parts.append(p.get("text", ""))
+        elif p.get("type") in _IMAGE_PARTS:
+            parts.append(IMAGE_PLACEHOLDER)
         elif p.get("type") == "tool_result":
             parts.append(_content_to_text(p.get("content")))
         elif p.get("type") == "tool_use":

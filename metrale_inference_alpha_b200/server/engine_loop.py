@@ -219,7 +219,7 @@ class AsyncEngine:
                         continue
                     if kind == "add":
                         try:
-                            eng.add_request(ids, params, request_id=rid)
+                            eng.add_request(ids, params, request_id=rid, **({"images": params.images} if getattr(params, "images", None) else {}))
                         except Exception as e:          # bad request: answer it, keep serving
                             self._emit(rid, StreamEvent(finished=True, finish_reason="error", error=str(e)))
                             self._live.pop(rid, None)

@@ -12,7 +12,7 @@ from typing import List, Optional
 class ByteTokenizer:
     """ids 0..255 = raw bytes; 256 = <bos>, 257 = <eos>, 258.. = chat markers."""
     SPECIALS = ["<|bos|>", "<|eos|>", "<|im_start|>", "<|im_end|>", "<think>", "</think>",
-                "<tool_call>", "</tool_call>"]
+                "<tool_call>", "</tool_call>", "<|vision_start|>", "<|image_pad|>", "<|vision_end|>"]
 
     def __init__(self, vocab_size: int = 4096):
         self.vocab_size = vocab_size

@@ -796,3 +796,30 @@ def test_dense_model_on_a_highway_runs_on_the_device():
     want = [o.output_ids for o in eager.generate(prompts, sp)]
     graphs = LLMEngine(EngineArgs(model="tiny-dense-hc", device=DEV, num_kv_blocks=64, max_num_seqs=4))
     assert [o.output_ids for o in graphs.generate(prompts, sp)] == want
+
+
+# ----------------------------------------------------------------------------- vision input
+def test_vision_tower_on_the_device_matches_the_host_and_images_reach_the_model():
+    import dataclasses
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    from metrale_inference_alpha_b200.vision import VisionConfig, VisionEncoder
+    vc = VisionConfig(depth=2, embed_dim=128, hidden_size=256, num_heads=4, mlp_ratio=2)
+    t = VisionEncoder.random_tensors(vc, 3)
+    g = torch.Generator().manual_seed(13)
+    patches, grid = torch.randn(24 + 16, vc.patch_dim, generator=g), torch.tensor([[1, 4, 6], [2, 2, 4]])
+    want = VisionEncoder(vc, t)(patches, grid)
+    got = VisionEncoder(vc, t, device=DEV)(patches, grid)
+    _close(got, want, 3e-2, 3e-2)
+    cfg = dataclasses.replace(preset("tiny-dense"), image_token_id=4000, vision=dict(depth=1, embed_dim=64, num_heads=2, mlp_ratio=2),
+                              name="tiny-vl")
+    eng = LLMEngine(EngineArgs(model=cfg, device=DEV, num_kv_blocks=128, max_num_seqs=4, max_model_len=512))
+    eng.attach_vision()
+    img = torch.randint(0, 255, (56, 84, 3), generator=g, dtype=torch.uint8)
+    sp = SamplingParams(max_tokens=6, temperature=0.0)
+    prompt = list(range(5, 19)) + [4000, 7, 8, 9]
+    out = eng.generate([prompt, [5, 6, 7, 8]], sp, images=[[img], None])
+    assert len(out[0].output_ids) == 6 and out[0].prompt_tokens == len(prompt) + 5
+    again = eng.generate([prompt], sp, images=[[img]])[0]
+    assert again.output_ids == out[0].output_ids and again.cached_tokens > 0
+    ops.check_status(torch.device(DEV))
