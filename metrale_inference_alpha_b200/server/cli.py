@@ -43,6 +43,19 @@ def _engine_args(ns) -> "EngineArgs":
     return EngineArgs(**kw)
 
 
+def _serve_translation(ns):
+    """An m2m_100 / nllb checkpoint: the translation app instead of the decoder-only engine."""
+    import uvicorn
+    from transformers import AutoTokenizer
+    from .translate import Translator, create_translation_app, open_translation_model
+    if not (ns.nllb_src_lang and ns.nllb_tgt_lang):
+        raise SystemExit("--nllb-src-lang and --nllb-tgt-lang are required for an NLLB / M2M-100 checkpoint")
+    model, _ = open_translation_model(ns.model, ns.device)
+    tok = AutoTokenizer.from_pretrained(ns.tokenizer or ns.model, local_files_only=True)
+    tr = Translator(model, tok, ns.nllb_src_lang, ns.nllb_tgt_lang)
+    uvicorn.run(create_translation_app(tr, ns.served_model_name or os.path.basename(ns.model.rstrip("/"))), host=ns.host, port=ns.port)
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="metrale-b200")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -93,6 +106,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--master-port", type=int, default=None)
     s.add_argument("--rank", type=int, default=None)
     s.add_argument("--world-size", type=int, default=None)
+    s.add_argument("--nllb-src-lang", default=None, help="NLLB / M2M-100 checkpoints: source language code, e.g. eng_Latn")
+    s.add_argument("--nllb-tgt-lang", default=None, help="NLLB / M2M-100 checkpoints: target language code, e.g. fra_Latn")
     s.add_argument("--swap-space-gb", type=float, default=0.0,
                    help="> 0: preempted sequences are swapped to host memory (then swap files) instead of recomputed")
 
@@ -263,6 +278,10 @@ def serve(ns) -> None:
         from ..config.model_config import PRESETS
         from .model_library import resolve_model_dir
         ns.model = resolve_model_dir(ns.model, ns.cache_dir, presets=tuple(PRESETS))
+    if isinstance(ns.model, str) and os.path.isdir(ns.model):
+        from .translate import is_translation_checkpoint
+        if is_translation_checkpoint(ns.model):
+            return _serve_translation(ns)
     eargs = _engine_args(ns)
     if ns.swap_space_gb > 0:
         eargs.preempt_mode, eargs.swap_space_bytes = "swap", int(ns.swap_space_gb * (1 << 30))

@@ -823,3 +823,31 @@ def test_vision_tower_on_the_device_matches_the_host_and_images_reach_the_model(
     again = eng.generate([prompt], sp, images=[[img]])[0]
     assert again.output_ids == out[0].output_ids and again.cached_tokens > 0
     ops.check_status(torch.device(DEV))
+
+
+def test_nllb_on_the_device_matches_the_host():
+    from metrale_inference_alpha_b200.models.nllb import NllbConfig, NllbModel
+    g = torch.Generator().manual_seed(14)
+    cfg = NllbConfig(vocab_size=512, d_model=128, encoder_layers=2, decoder_layers=2, encoder_attention_heads=4,
+                     decoder_attention_heads=4, encoder_ffn_dim=256, decoder_ffn_dim=256, max_position_embeddings=64)
+    r = lambda *s: torch.randn(*s, generator=g) * 0.08
+    t = {"shared.weight": r(512, 128)}
+    for side, n in (("encoder", 2), ("decoder", 2)):
+        for i in range(n):
+            p = f"{side}.layers.{i}"
+            atts = ["self_attn"] + (["encoder_attn"] if side == "decoder" else [])
+            for a in atts:
+                for proj in ("q_proj", "k_proj", "v_proj", "out_proj"):
+                    t[f"{p}.{a}.{proj}.weight"], t[f"{p}.{a}.{proj}.bias"] = r(128, 128), r(128)
+                t[f"{p}.{a}_layer_norm.weight"], t[f"{p}.{a}_layer_norm.bias"] = 1 + r(128), r(128)
+            t[f"{p}.fc1.weight"], t[f"{p}.fc1.bias"], t[f"{p}.fc2.weight"], t[f"{p}.fc2.bias"] = r(256, 128), r(256), r(128, 256), r(128)
+            t[f"{p}.final_layer_norm.weight"], t[f"{p}.final_layer_norm.bias"] = 1 + r(128), r(128)
+        t[f"{side}.layer_norm.weight"], t[f"{side}.layer_norm.bias"] = 1 + r(128), r(128)
+    host, dev = NllbModel(cfg, t), NllbModel(cfg, t, device=DEV)
+    src = torch.tensor([[10, 11, 12, 13, 2], [10, 44, 2, 1, 1]])
+    dec = torch.tensor([[2, 20, 31, 32], [2, 20, 41, 42]])
+    want = host.decode_step(dec, host.encode(src), host.new_cache(), 0)
+    got = dev.decode_step(dec, dev.encode(src), dev.new_cache(), 0)
+    _close(got, want, 5e-2, 5e-2)
+    out = dev.translate([10, 11, 12, 13, 2], 20, num_beams=3, max_new_tokens=8)
+    assert len(out) <= 8 and all(0 <= x < 512 for x in out)
