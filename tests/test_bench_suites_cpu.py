@@ -1,0 +1,131 @@
+"""Benchmark suites: function calling (draw, checker, aggregation, run through the HTTP app), the agentic
+tool loop on a virtual workspace, request isolation and scheduler equivalence."""
+import json
+
+import pytest
+
+from metrale_inference_alpha_b200.bench import agentic as AG
+from metrale_inference_alpha_b200.bench import function_calling as FC
+from metrale_inference_alpha_b200.bench.isolation import contamination, scheduler_equivalence
+from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+
+
+def _call(name, **args):
+    return {"tool_calls": [{"id": "c1", "type": "function", "function": {"name": name, "arguments": json.dumps(args)}}]}
+
+
+def test_checker_accepts_equivalent_values_and_names_the_first_mismatch():
+    s = {x.id: x for x in FC.load_dataset()}
+    ok = FC.check_sample(s["simple_0"], FC.calls_of_message(_call("get_weather", city=" paris ", unit="celsius")))
+    assert ok.ok
+    assert FC.check_sample(s["simple_0"], FC.calls_of_message(_call("get_weather", city="Paris"))).ok        # optional unit
+    assert FC.check_sample(s["simple_1"], FC.calls_of_message(_call("triangle_area", base=10.0, height=5))).ok
+    assert not FC.check_sample(s["simple_1"], FC.calls_of_message(_call("triangle_area", base=10.0, height="5"))).ok     # a string is not a number
+    bad = FC.check_sample(s["simple_0"], FC.calls_of_message(_call("get_weather", city="Lyon")))
+    assert not bad.ok and "city" in bad.reason
+    assert "unexpected" in FC.check_sample(s["simple_0"], FC.calls_of_message(_call("get_weather", city="Paris", day=1))).reason
+    assert "missing" in FC.check_sample(s["simple_1"], FC.calls_of_message(_call("triangle_area", base=10))).reason
+    assert "expected" in FC.check_sample(s["multiple_0"], FC.calls_of_message(_call("get_stock_price", symbol="X"))).reason
+    # parallel: order-free, each expected call claims its own produced call
+    two = {"tool_calls": _call("get_weather", city="Oslo")["tool_calls"] + _call("get_weather", city="Rome")["tool_calls"]}
+    assert FC.check_sample(s["parallel_0"], FC.calls_of_message(two)).ok
+    dup = {"tool_calls": _call("get_weather", city="Oslo")["tool_calls"] * 2}
+    assert not FC.check_sample(s["parallel_0"], FC.calls_of_message(dup)).ok
+    assert FC.check_sample(s["irrelevance_0"], []).ok and not FC.check_sample(s["irrelevance_0"], FC.calls_of_message(_call("get_weather", city="x"))).ok
+
+
+def test_draw_is_deterministic_stratified_and_shards_partition(tmp_path):
+    rows = [dict(FC.SMOKE_SET[i % 5], id=f"{FC.SMOKE_SET[i % 5]['category']}_{i}") for i in range(40)]
+    p = tmp_path / "d.jsonl"
+    p.write_text("\n".join(json.dumps(r) for r in rows))
+    data = FC.load_dataset(str(p))
+    a, b = FC.draw(data, 20, seed=3), FC.draw(data, 20, seed=3)
+    assert [s.id for s in a] == [s.id for s in b] and len(a) == 20
+    assert [s.id for s in FC.draw(data, 20, seed=4)] != [s.id for s in a]
+    cats = {}
+    for s in a:
+        cats[s.category] = cats.get(s.category, 0) + 1
+    assert cats == {"simple": 8, "multiple": 4, "parallel": 4, "irrelevance": 4}       # half of every category
+    shards = [FC.draw(data, None, seed=1, shard=i, shards=3) for i in range(3)]
+    ids = sorted(s.id for sh in shards for s in sh)
+    assert ids == sorted(s.id for s in data)
+    with pytest.raises(ValueError):
+        FC.draw(data, 5, shard=3, shards=3)
+    with pytest.raises(ValueError):
+        p.write_text('{"id": "x"}')
+        FC.load_dataset(str(p))
+
+
+def test_run_and_aggregate_with_a_scripted_model():
+    answers = {"simple_0": _call("get_weather", city="Paris"), "simple_1": _call("triangle_area", base=10, height=6),
+               "multiple_0": _call("convert_currency", **{"amount": 100, "from": "usd", "to": "eur"}), "irrelevance_0": {"content": "why did..."}}
+    data = FC.load_dataset()
+    by_q = {s.question[0]["content"]: s.id for s in data}
+
+    def ask(messages, tools):
+        sid = by_q[messages[-1]["content"]]
+        if sid == "parallel_0":
+            raise RuntimeError("boom")
+        assert tools and tools[0]["type"] == "function"
+        return answers[sid]
+    seen = []
+    agg = FC.aggregate(FC.run(data, ask, on_progress=lambda i, n: seen.append((i, n))))
+    assert seen[-1] == (5, 5) and agg["n"] == 5 and agg["correct"] == 3
+    assert agg["categories"]["simple"] == {"n": 2, "correct": 1, "accuracy": 0.5} and agg["categories"]["parallel"]["correct"] == 0
+    assert any("request failed" in f["reason"] for f in agg["failures"]) and "3 / 5" in FC.report(agg)
+    assert len(FC.run(data, ask, should_stop=lambda: True)) == 0
+
+
+def test_function_calling_through_the_http_app():
+    from fastapi.testclient import TestClient
+    from metrale_inference_alpha_b200.server.app import ServerConfig, create_app
+    from metrale_inference_alpha_b200.server.tokenizer import load_tokenizer
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=1024))
+    with TestClient(create_app(eng, load_tokenizer(None, eng.cfg.vocab_size), ServerConfig(model_name="tiny"))) as c:
+        agg = FC.aggregate(FC.run(FC.load_dataset()[:2], FC.app_asker(c, "tiny", max_tokens=8)))
+    assert agg["n"] == 2 and not any("request failed" in f["reason"] for f in agg["failures"])     # a random model answers wrongly, but it answers
+
+
+def test_agent_loop_tools_sandbox_and_scoring():
+    assert AG.norm_path("a/../b.txt") == "b.txt" and AG.norm_path("/x/y") == "x/y"
+    for bad in ("../etc/passwd", "", "a/../../b"):
+        with pytest.raises(ValueError):
+            AG.norm_path(bad)
+    script = {
+        "sum_numbers": [_call("read_file", path="numbers.txt"), _call("write_file", path="total.txt", content="108\n"), _call("finish")],
+        "rename_constant": [_call("read_file", path="config.py"), _call("read_file", path="config.py"), _call("read_file", path="nope.py"),
+                            {"content": "I give up"}],
+        "create_readme": [_call("write_file", path="../README.md", content="x")] * 20,
+    }
+    state = {}
+
+    def ask(messages, tools):
+        goal = messages[1]["content"]
+        tid = next(t.id for t in AG.builtin_tasks() if t.goal == goal)
+        i = state.get(tid, 0)
+        state[tid] = i + 1
+        assert [m["role"] for m in messages[:2]] == ["system", "user"]
+        if i > 0 and messages[-1]["role"] == "tool":
+            assert messages[-1]["tool_call_id"]
+        return script[tid][i]
+    res = AG.run_suite(ask)
+    tasks = res["tasks"]
+    assert tasks["sum_numbers"] == {"passed": True, "turns": 3, "reason": "finish"}
+    assert not tasks["rename_constant"]["passed"] and tasks["rename_constant"]["reason"] == "the model stopped calling tools"
+    assert tasks["create_readme"]["reason"] == "turn budget exhausted" and not tasks["create_readme"]["passed"]
+    assert res["passed"] == 1 and res["repeated_calls"] >= 1 and res["tool_errors"] >= 2
+    tr = next(t for t in res["traces"] if t.task == "rename_constant")
+    assert tr.turns[2]["calls"][0]["error"] and "no such file" in tr.turns[2]["calls"][0]["result"]
+    big = AG.Task("big", "read", {"big.txt": "x" * 10000}, lambda f: True, max_turns=1)
+    t = AG.run_task(big, lambda m, tools: _call("read_file", path="big.txt"))
+    assert t.truncated_results == 1 and t.turns[0]["calls"][0]["result"].endswith("[truncated]")
+
+
+def test_requests_do_not_leak_into_each_other_and_scheduling_does_not_change_tokens():
+    eng = LLMEngine(EngineArgs(model="tiny-hybrid-moe", device="cpu", max_num_seqs=4, max_model_len=256, num_kv_blocks=96))
+    rep = contamination(eng, n_requests=6, rounds=2, max_tokens=10)
+    assert rep["ok"] and rep["requests"] == 12
+    make = lambda **kw: LLMEngine(EngineArgs(**{**dict(model="tiny-dense", device="cpu", max_num_seqs=8, max_model_len=256, num_kv_blocks=128), **kw}))
+    eq = scheduler_equivalence(make, n=4, max_tokens=8)
+    assert eq["ok"], eq
+    assert set(eq["variants"]) == {"small_prefill_chunks", "batch_cap_2", "tbt_policy", "no_prefix_cache"}
