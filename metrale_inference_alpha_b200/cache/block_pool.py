@@ -122,8 +122,9 @@ class PagedKvCache:
                               (torch.full(shape_v, 255, dtype=torch.uint8, device=device)
                                if dt == torch.uint8 else torch.full(shape_v, float("nan"), dtype=dt, device=device)))
             else:
-                self.k.append(torch.zeros(shape_k, dtype=dt, device=device))
-                self.v.append(torch.zeros(shape_v, dtype=dt, device=device) if cfg.has_v else None)
+                from ..utils.alloc_ledger import ledger
+                self.k.append(ledger().alloc(shape_k, dt, device, "kv pool (k)"))
+                self.v.append(ledger().alloc(shape_v, dt, device, "kv pool (v)") if cfg.has_v else None)
         del fill
         # dequant multipliers (stored value = amax / 448); 1.0 until calibrated or loaded
         self.k_scale = [torch.ones(1, dtype=torch.float32, device=device) for _ in range(cfg.num_layers)]

@@ -20,12 +20,14 @@ class StatePool:
         """layer_shapes[i] = (conv_state_shape, ssm_state_shape) of recurrent layer i."""
         self.num_slots = num_slots
         self.device = torch.device(device)
-        self.conv = [torch.zeros((num_slots, *c), dtype=torch.float32, device=device) for c, _ in layer_shapes]
-        self.ssm = [torch.zeros((num_slots, *s), dtype=torch.float32, device=device) for _, s in layer_shapes]
+        from ..utils.alloc_ledger import ledger
+        z = lambda shape, name: ledger().alloc(shape, torch.float32, device, name)
+        self.conv = [z((num_slots, *c), "state pool (conv)") for c, _ in layer_shapes]
+        self.ssm = [z((num_slots, *s), "state pool (ssm)") for _, s in layer_shapes]
         self._free = list(range(num_slots - 1, 0, -1))
         self.num_snapshots = num_snapshots
-        self.snap_conv = [torch.zeros((num_snapshots, *c), dtype=torch.float32, device=device) for c, _ in layer_shapes]
-        self.snap_ssm = [torch.zeros((num_snapshots, *s), dtype=torch.float32, device=device) for _, s in layer_shapes]
+        self.snap_conv = [z((num_snapshots, *c), "state snapshots (conv)") for c, _ in layer_shapes]
+        self.snap_ssm = [z((num_snapshots, *s), "state snapshots (ssm)") for _, s in layer_shapes]
         self._snap_free = list(range(num_snapshots - 1, -1, -1))
         self._snap_ref: Dict[int, int] = {}
 

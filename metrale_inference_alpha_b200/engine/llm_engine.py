@@ -130,6 +130,8 @@ class LLMEngine:
                                     tp_size=self.tp.size if args.ep_size == 1 or args.tp_size > 1 else 1,
                                     ep_rank=getattr(self.tp, "ep_rank", 0), ep_size=args.ep_size, seed=args.seed)
         self.load_seconds = time.time() - t0
+        import os as _os
+        self._redzone_every = int(_os.environ.get("METRALE_REDZONE_EVERY", "0") or 0)
         self.paged_experts = None
         if args.expert_arena_slots > 0:
             if not args.expert_store_dir:
@@ -399,6 +401,8 @@ class LLMEngine:
             self.spec_stats.drafted += sum(it.verify for it in plan.items)
             self.spec_stats.accepted += sum(getattr(it.seq, "last_accept", 0) for it in plan.items)
         self.step_count += 1
+        if self._redzone_every and self.step_count % self._redzone_every == 0:
+            self.check_red_zones()
         return outs
 
     # ------------------------------------------------------------------ rollback
@@ -431,6 +435,23 @@ class LLMEngine:
             if not outs and not self.has_work():
                 break
         return [done[i] for i in ids if i in done]
+
+    def check_red_zones(self) -> list:
+        """Compare the guard bands behind the engine's pools (``METRALE_REDZONE``); a damaged band
+        latches the fault with the name of the buffer that was overrun."""
+        from ..utils.alloc_ledger import ledger
+        bad = ledger().check()
+        if bad:
+            self.fault.set("red zone overwritten behind " + ", ".join(f"{b['name']} ({b['site']}, {b['bytes_overwritten']} bytes)" for b in bad))
+        return bad
+
+    def memory_report(self) -> dict:
+        """The allocation ledger: long-lived device allocations by name and call site, and what the
+        caching allocator holds beyond them."""
+        from ..utils.alloc_ledger import ledger
+        led = ledger()
+        return {"allocations": led.report(), "ledger_bytes": led.total_bytes(), "slack_bytes": led.slack(self.device),
+                "redzone_bytes": led.redzone}
 
     def stats(self) -> dict:
         s = self.scheduler.snapshot()

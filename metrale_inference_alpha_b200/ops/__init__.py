@@ -58,9 +58,10 @@ class _Runtime:
         self.device = device
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self.ws_bytes = 96 << 20
-        self.ws = torch.zeros(self.ws_bytes, dtype=torch.uint8, device=device)
-        self.attn_ws = torch.zeros(32 << 20, dtype=torch.uint8, device=device)
-        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        from ..utils.alloc_ledger import ledger
+        self.ws = ledger().alloc(self.ws_bytes, torch.uint8, device, "gemm workspace")
+        self.attn_ws = ledger().alloc(32 << 20, torch.uint8, device, "attention workspace")
+        self.status = ledger().alloc(4, torch.int32, device, "status word")
 
     @classmethod
     def get(cls, device) -> "_Runtime":
@@ -72,7 +73,8 @@ class _Runtime:
 
     def ensure_attn_ws(self, nbytes: int):
         if nbytes > self.attn_ws.numel():
-            self.attn_ws = torch.zeros(int(nbytes * 1.25), dtype=torch.uint8, device=self.device)
+            from ..utils.alloc_ledger import ledger
+            self.attn_ws = ledger().alloc(int(nbytes * 1.25), torch.uint8, self.device, "attention workspace")
 
 
 def runtime(device) -> _Runtime:

@@ -151,6 +151,7 @@ def build_parser() -> argparse.ArgumentParser:
     pl.add_argument("--ctx", type=int, default=640)
     pl.add_argument("--tp", type=int, default=1)
     pl.add_argument("--json", action="store_true")
+    pl.add_argument("--circuit", default=None, help="also summarise this circuit file (name under planner/circuits or a path): ops, launches after fusion, planned activation bytes")
 
     sp = sub.add_parser("storage-probe", help="what a scratch directory can do for the KV / expert tiers (O_DIRECT, GDS, read and write rates)")
     sp.add_argument("--dir", default=None)
@@ -409,6 +410,9 @@ def main(argv: Optional[List[str]] = None) -> int:
             print(f"step: {e['step_ms_roofline_per_op']} ms per-op roofline, {e['step_ms_bytes_only']} ms bytes only "
                   f"({e['gbytes_per_step']} GB, {e['tflop_per_step']} TFLOP, {e['launches']} launches); "
                   f"upper bound {e['tok_s_upper_bound']} tok/s")
+        if ns.circuit:
+            from ..planner import circuit as _c
+            print(json.dumps(_c.summary(_c.load(ns.circuit), cfg, ns.batch)))
     elif ns.cmd == "storage-probe":
         from ..storage.probe import run_probe
         print(json.dumps(run_probe(ns.dir, blocks=ns.blocks, block_kib=ns.block_kib), indent=2))

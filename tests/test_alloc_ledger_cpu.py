@@ -1,0 +1,61 @@
+"""Allocation ledger and red zones."""
+import gc
+
+import pytest
+import torch
+
+from metrale_inference_alpha_b200.utils import alloc_ledger as AL
+
+
+def test_ledger_records_sizes_sites_and_forgets_dead_tensors():
+    led = AL.AllocLedger(0)
+    a = led.alloc((4, 8), torch.float32, "cpu", "pool a")
+    b = led.alloc(100, torch.uint8, "cpu", "pool b")
+    c = led.alloc(28, torch.uint8, "cpu", "pool b")
+    led.track(torch.zeros(10), "foreign")
+    keep = led.report()
+    assert keep[0] == {"name": "pool a", "site": keep[0]["site"], "device": "cpu", "count": 1, "bytes": 128}
+    assert keep[1]["name"] == "pool b" and keep[1]["count"] == 2 and keep[1]["bytes"] == 128
+    assert "test_alloc_ledger_cpu.py" in keep[0]["site"] and led.total_bytes() == 128 + 128          # `foreign` died at once
+    assert float(a.sum()) == 0 and led.slack("cpu") is None
+    del b, c
+    gc.collect()
+    assert [r["name"] for r in led.report()] == ["pool a"]
+
+
+def test_red_zone_names_the_overrun_buffer():
+    led = AL.AllocLedger(64)
+    a = led.alloc((3, 5), torch.float32, "cpu", "victim")              # 60 bytes: padded to 64 before the band
+    b = led.alloc(32, torch.uint8, "cpu", "bystander")
+    assert led.check() == [] and float(a.sum()) == 0 and a.shape == (3, 5)
+    # a write past the end of `victim`, through its own storage
+    raw = torch.empty(0, dtype=torch.uint8).set_(a.untyped_storage())
+    raw[64 + 3] = 7
+    raw[64 + 10] = 9
+    bad = led.check()
+    assert len(bad) == 1 and bad[0]["name"] == "victim" and bad[0]["bytes_overwritten"] == 2 and bad[0]["first_offset"] == 3
+    led.refill()
+    assert led.check() == [] and int(b.sum()) == 0
+    with pytest.raises(ValueError):
+        AL.AllocLedger(10)
+
+
+def test_engine_pools_are_in_the_ledger_and_a_damaged_band_latches_the_fault(monkeypatch):
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    led = AL.reset_for_tests(256)
+    try:
+        monkeypatch.setenv("METRALE_REDZONE_EVERY", "2")
+        eng = LLMEngine(EngineArgs(model="tiny-hybrid-moe", device="cpu", num_kv_blocks=32, max_num_seqs=2))
+        rep = eng.memory_report()
+        names = {r["name"] for r in rep["allocations"]}
+        assert {"kv pool (k)", "kv pool (v)", "state pool (ssm)", "state pool (conv)"} <= names and rep["redzone_bytes"] == 256
+        out = eng.generate([[5, 6, 7, 8, 9]], SamplingParams(max_tokens=5, temperature=0.0))
+        assert len(out[0].output_ids) == 5 and eng.check_red_zones() == [] and not eng.fault.is_set()
+        k0 = eng.runner.kv.k[0]
+        raw = torch.empty(0, dtype=torch.uint8).set_(k0.untyped_storage())
+        raw[k0.numel() * k0.element_size() + 5] = 1                 # one byte past the pool
+        bad = eng.check_red_zones()
+        assert bad and bad[0]["name"] == "kv pool (k)" and eng.fault.is_set() and "kv pool (k)" in eng.fault.reason()
+    finally:
+        AL.reset_for_tests(0)
