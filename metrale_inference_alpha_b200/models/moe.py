@@ -102,7 +102,12 @@ def routed_experts(dec, a, weights, idx, w):
         tok, slot = torch.nonzero(idx == e, as_tuple=True)
         if tok.numel() == 0:
             continue
-        sub = ops.Act(a.fmt, tok.numel(), a.K, a.data[tok])
+        if a.data.is_cuda and a.fmt != "bf16":
+            # a quantised activation keeps its scales in a layout tied to the row order: the expert's rows
+            # are re-encoded from the bf16 copy
+            sub = dec._as_act(a.bf16[tok].contiguous(), ACT_FOR_WEIGHT[f.gate_up.fmt])
+        else:
+            sub = ops.Act(a.fmt, tok.numel(), a.K, a.data[tok])
         fmt_d = ACT_FOR_WEIGHT[f.down.fmt]
         if dec.cfg.ffn_act == "relu2":
             h = ops.row_op(ops.linear(sub, f.gate_up), fmt_d, ops.IN_RELU2)[0]

@@ -51,7 +51,6 @@ __global__ void __launch_bounds__(kHcThreads)
 hc_pre_kernel(const float* __restrict__ streams, const __nv_bfloat16* __restrict__ fn, const float* __restrict__ scale,
               const float* __restrict__ base, __nv_bfloat16* __restrict__ y, float* __restrict__ post_out,
               float* __restrict__ comb_out, int hc, int H, float norm_eps, float hc_eps, int iters) {
-  __shared__ float red[kHcThreads / 32];
   __shared__ float mix[kMaxMix];
   __shared__ float pre_s[kMaxHc];
   const int t = blockIdx.x;
@@ -60,21 +59,53 @@ hc_pre_kernel(const float* __restrict__ streams, const __nv_bfloat16* __restrict
   float ss = 0.f, acc[kMaxMix];
 #pragma unroll
   for (int r = 0; r < kMaxMix; ++r) acc[r] = 0.f;
-  for (int i = threadIdx.x; i < n; i += kHcThreads) {
+  // eight consecutive stream values per step: two 16-byte loads of the stream, one of every mixing row
+  const int n8 = (n % 8 == 0) ? n / 8 : 0;
+  for (int i8 = threadIdx.x; i8 < n8; i8 += kHcThreads) {
+    const float4 x0 = reinterpret_cast<const float4*>(x)[2 * i8], x1 = reinterpret_cast<const float4*>(x)[2 * i8 + 1];
+    const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss = fmaf(xv[j], xv[j], ss);
+#pragma unroll
+    for (int r = 0; r < kMaxMix; ++r) {
+      if (r < mix_hc) {
+        const uint4 w = reinterpret_cast<const uint4*>(fn + (size_t)r * n)[i8];
+        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(w2[j]);
+          acc[r] = fmaf(f.x, xv[2 * j], acc[r]);
+          acc[r] = fmaf(f.y, xv[2 * j + 1], acc[r]);
+        }
+      }
+    }
+  }
+  for (int i = n8 * 8 + threadIdx.x; i < n; i += kHcThreads) {
     const float v = x[i];
     ss = fmaf(v, v, ss);
 #pragma unroll
     for (int r = 0; r < kMaxMix; ++r)
       if (r < mix_hc) acc[r] = fmaf(__bfloat162float(fn[(size_t)r * n + i]), v, acc[r]);
   }
-  const float rstd = rsqrtf(block_sum(ss, red) / n + norm_eps);
+  // one reduction for the statistic and all mixing rows: warp sums, then kMaxMix + 1 threads add the warps' partials
+  __shared__ float part[kMaxMix + 1][kHcThreads / 32];
+  ss = mb::warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) part[kMaxMix][threadIdx.x >> 5] = ss;
 #pragma unroll
   for (int r = 0; r < kMaxMix; ++r) {
     if (r < mix_hc) {
-      const float s = block_sum(acc[r], red);
-      if (threadIdx.x == 0) mix[r] = s * rstd;
+      const float v = mb::warp_sum(acc[r]);
+      if ((threadIdx.x & 31) == 0) part[r][threadIdx.x >> 5] = v;
     }
   }
+  __syncthreads();
+  if (threadIdx.x <= kMaxMix && (threadIdx.x < mix_hc || threadIdx.x == kMaxMix)) {
+    float v = 0.f;
+    for (int w = 0; w < kHcThreads / 32; ++w) v += part[threadIdx.x][w];
+    part[threadIdx.x][0] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < mix_hc) mix[threadIdx.x] = part[threadIdx.x][0] * rsqrtf(part[kMaxMix][0] / n + norm_eps);
   __syncthreads();
   if (threadIdx.x == 0) {
     float c[kMaxHc][kMaxHc];

@@ -50,7 +50,7 @@ struct KdaArgs {
 
 template <int D>
 __global__ void __launch_bounds__(D) kda_kernel(const KdaArgs a) {
-  __shared__ float s_q[D], s_k[D], s_g[D];
+  __shared__ __align__(16) float s_q[D], s_k[D], s_g[D];
   __shared__ float s_red[3][4];
   const int hd = blockIdx.x, seq = blockIdx.y, v = threadIdx.x;
   const int n = a.sm.q_len[seq];
@@ -72,12 +72,26 @@ __global__ void __launch_bounds__(D) kda_kernel(const KdaArgs a) {
   const float dtb = a.dt_bias[hd * D + v];
   const float scale = rsqrtf((float)D);
   const float nw = a.norm_w ? a.norm_w[v] : 1.f;
-  for (int t = 0; t < n; ++t) {
+  // the next token's inputs are fetched while the current token is computed (a prefill walks thousands of
+  // tokens with one warp per scheduler: a global load in the dependent chain of every token would set the pace)
+  float n_q, n_k, n_v, n_g, n_b, n_og = 0.f;
+  auto fetch = [&](int t) {
     const size_t row = (size_t)(q0 + t);
     const float* cr = a.conv + row * 3 * HD;
+    n_q = cr[hd * D + v];
+    n_k = cr[HD + hd * D + v];
+    n_v = cr[2 * HD + hd * D + v];
+    n_g = a.g_raw[row * HD + hd * D + v];
+    n_b = a.b_raw[row * a.b_ld + hd];
+    if (a.out_norm && a.write_out) n_og = __bfloat162float(a.out_gate[row * a.gate_ld + hd * D + v]);
+  };
+  fetch(0);
+  for (int t = 0; t < n; ++t) {
+    const size_t row = (size_t)(q0 + t);
     __syncthreads();                                    // the last token's shared values are consumed
-    const float qv = cr[hd * D + v], kv = cr[HD + hd * D + v];
-    const float gate = a.lower_bound / (1.f + __expf(-a_exp * (a.g_raw[row * HD + hd * D + v] + dtb)));
+    const float qv = n_q, kv = n_k, vv = n_v, braw = n_b, og = n_og;
+    const float gate = a.lower_bound / (1.f + __expf(-a_exp * (n_g + dtb)));
+    if (t + 1 < n) fetch(t + 1);
     s_q[v] = qv;
     s_k[v] = kv;
     s_g[v] = __expf(gate);
@@ -94,21 +108,39 @@ __global__ void __launch_bounds__(D) kda_kernel(const KdaArgs a) {
       tk += s_red[1][w];
     }
     const float nq = rsqrtf(tq + 1e-6f) * scale, nk = rsqrtf(tk + 1e-6f);
-    const float beta = 1.f / (1.f + __expf(-a.b_raw[row * a.b_ld + hd]));
-    const float vv = cr[2 * HD + hd * D + v];
-    float hk = 0.f;
+    const float beta = 1.f / (1.f + __expf(-braw));
+    // four partial sums per reduction: with one warp per scheduler the dependent fma chain is the limit
+    float hk4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int k = 0; k < D; ++k) {
-      h[k] *= s_g[k];
-      hk = fmaf(h[k], s_k[k], hk);
+    for (int k = 0; k < D; k += 4) {
+      const float4 g4 = *reinterpret_cast<const float4*>(&s_g[k]);
+      const float4 k4 = *reinterpret_cast<const float4*>(&s_k[k]);
+      h[k] *= g4.x;
+      h[k + 1] *= g4.y;
+      h[k + 2] *= g4.z;
+      h[k + 3] *= g4.w;
+      hk4[0] = fmaf(h[k], k4.x, hk4[0]);
+      hk4[1] = fmaf(h[k + 1], k4.y, hk4[1]);
+      hk4[2] = fmaf(h[k + 2], k4.z, hk4[2]);
+      hk4[3] = fmaf(h[k + 3], k4.w, hk4[3]);
     }
+    const float hk = (hk4[0] + hk4[1]) + (hk4[2] + hk4[3]);
     const float delta = (vv - hk * nk) * beta * nk;      // the second nk belongs to k^ in the update
-    float o = 0.f;
+    float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int k = 0; k < D; ++k) {
-      h[k] = fmaf(s_k[k], delta, h[k]);
-      o = fmaf(h[k], s_q[k], o);
+    for (int k = 0; k < D; k += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(&s_k[k]);
+      const float4 q4 = *reinterpret_cast<const float4*>(&s_q[k]);
+      h[k] = fmaf(k4.x, delta, h[k]);
+      h[k + 1] = fmaf(k4.y, delta, h[k + 1]);
+      h[k + 2] = fmaf(k4.z, delta, h[k + 2]);
+      h[k + 3] = fmaf(k4.w, delta, h[k + 3]);
+      o4[0] = fmaf(h[k], q4.x, o4[0]);
+      o4[1] = fmaf(h[k + 1], q4.y, o4[1]);
+      o4[2] = fmaf(h[k + 2], q4.z, o4[2]);
+      o4[3] = fmaf(h[k + 3], q4.w, o4[3]);
     }
+    float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     o *= nq;
     if (a.write_out) {
       if (a.out) a.out[row * HD + hd * D + v] = o;
@@ -119,9 +151,8 @@ __global__ void __launch_bounds__(D) kda_kernel(const KdaArgs a) {
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w) tot += s_red[2][w];
-        const float g = __bfloat162float(a.out_gate[row * a.gate_ld + hd * D + v]);
         a.out_norm[row * HD + hd * D + v] =
-            __float2bfloat16(o * rsqrtf(tot / D + a.eps) * nw / (1.f + __expf(-g)));
+            __float2bfloat16(o * rsqrtf(tot / D + a.eps) * nw / (1.f + __expf(-og)));
       }
     }
   }

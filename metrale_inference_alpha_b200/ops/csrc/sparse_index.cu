@@ -17,55 +17,95 @@
 
 namespace {
 
-constexpr int kKeysPerCta = 64;
+constexpr int kKeysPerCta = 128;     // two keys per thread, four threads per key
 
+// Four threads share a key: each keeps a quarter of the key's channels in registers as fp32 and walks all
+// indexer heads, reading the matching quarter of the head's query from shared memory (fp32, rows padded so
+// that the four quarters fall on different banks); the four partial dot products meet through two shuffles
+// before the ReLU. Per (key, head) that is DI / 4 FMAs per thread and nothing else in the inner loop.
 template <int DI>
 __global__ void __launch_bounds__(256)
 index_score_kernel(const __nv_bfloat16* __restrict__ iq, const float* __restrict__ iw,
                    const __nv_bfloat16* __restrict__ kc, const int* __restrict__ block_table, int max_blocks,
                    const int* __restrict__ row_seq, const int* __restrict__ row_ctx, float* __restrict__ scores,
                    long long ld, int Hi, int block_size, long long num_blocks, uint32_t* status) {
+  constexpr int Q = DI / 4;                 // channels per thread
+  constexpr int QS = Q + 4;                 // padded quarter: quarter p starts at bank 4p
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat162* qs = reinterpret_cast<__nv_bfloat162*>(smem_raw);                  // [Hi][DI / 2]
-  float* ws = reinterpret_cast<float*>(smem_raw + (size_t)Hi * DI * 2);               // [Hi]
+  float* qs = reinterpret_cast<float*>(smem_raw);                                      // [Hi][4][QS]
+  float* ws = qs + (size_t)Hi * 4 * QS;                                                // [Hi]
   const int t = blockIdx.y, s0 = blockIdx.x * kKeysPerCta;
   const int ctx = row_ctx[t];
-  const int key = threadIdx.x >> 2, hg = threadIdx.x & 3;
-  const int pos = s0 + key;
+  const int part = threadIdx.x & 3;
+  const int pos0 = s0 + (threadIdx.x >> 2), pos1 = pos0 + kKeysPerCta / 2;
   if (s0 >= ctx) {                                          // the whole tile is past this row's context
-    if (hg == 0 && pos < ld) scores[(size_t)t * ld + pos] = -INFINITY;
+    if (part == 0) {
+      if (pos0 < ld) scores[(size_t)t * ld + pos0] = -INFINITY;
+      if (pos1 < ld) scores[(size_t)t * ld + pos1] = -INFINITY;
+    }
     return;
   }
-  const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(iq + (size_t)t * Hi * DI);
-  for (int i = threadIdx.x; i < Hi * DI / 2; i += blockDim.x) qs[i] = q2[i];
+  const __nv_bfloat16* q = iq + (size_t)t * Hi * DI;
+  for (int i = threadIdx.x; i < Hi * DI; i += blockDim.x) {
+    const int h = i / DI, d = i - h * DI;
+    qs[((size_t)h * 4 + d / Q) * QS + d % Q] = __bfloat162float(q[i]);
+  }
   for (int i = threadIdx.x; i < Hi; i += blockDim.x) ws[i] = iw[(size_t)t * Hi + i];
   __syncthreads();
-  float acc = 0.f;
-  if (pos < ctx) {
-    const int blk = block_table[(size_t)row_seq[t] * max_blocks + pos / block_size];
-    if (blk < 0 || blk >= num_blocks) {
-      if (status) atomicCAS(status, 0u, MB_ST_BOUNDS);
-    } else {
-      const uint4* kr = reinterpret_cast<const uint4*>(kc + ((size_t)blk * block_size + pos % block_size) * DI);
-      __nv_bfloat162 k2[DI / 2];
+  float k[2][Q];
 #pragma unroll
-      for (int i = 0; i < DI / 8; ++i) *reinterpret_cast<uint4*>(&k2[4 * i]) = kr[i];
-      for (int h = hg; h < Hi; h += 4) {
-        const __nv_bfloat162* qh = qs + (size_t)h * (DI / 2);
-        float dot = 0.f;
+  for (int u = 0; u < 2; ++u) {
+    const int pos = u ? pos1 : pos0;
 #pragma unroll
-        for (int i = 0; i < DI / 2; ++i) {
-          const float2 a = __bfloat1622float2(qh[i]), b = __bfloat1622float2(k2[i]);
-          dot = fmaf(a.x, b.x, dot);
-          dot = fmaf(a.y, b.y, dot);
+    for (int i = 0; i < Q; ++i) k[u][i] = 0.f;
+    if (pos < ctx) {
+      const int blk = block_table[(size_t)row_seq[t] * max_blocks + pos / block_size];
+      if (blk < 0 || blk >= num_blocks) {
+        if (status) atomicCAS(status, 0u, MB_ST_BOUNDS);
+      } else {
+        const uint4* kr = reinterpret_cast<const uint4*>(kc + ((size_t)blk * block_size + pos % block_size) * DI + part * Q);
+#pragma unroll
+        for (int i = 0; i < Q / 8; ++i) {
+          const uint4 v = kr[i];
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h2[j]);
+            k[u][8 * i + 2 * j] = f.x;
+            k[u][8 * i + 2 * j + 1] = f.y;
+          }
         }
-        acc = fmaf(ws[h], fmaxf(dot, 0.f), acc);
       }
     }
   }
-  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-  if (hg == 0 && pos < ld) scores[(size_t)t * ld + pos] = pos < ctx ? acc : -INFINITY;
+  float acc0 = 0.f, acc1 = 0.f;
+  for (int h = 0; h < Hi; ++h) {
+    const float4* qh = reinterpret_cast<const float4*>(qs + ((size_t)h * 4 + part) * QS);
+    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < Q / 4; ++i) {
+      const float4 a = qh[i];                     // one shared-memory read feeds both keys
+      d0 = fmaf(a.x, k[0][4 * i], d0);
+      d1 = fmaf(a.x, k[1][4 * i], d1);
+      d0 = fmaf(a.y, k[0][4 * i + 1], d0);
+      d1 = fmaf(a.y, k[1][4 * i + 1], d1);
+      d0 = fmaf(a.z, k[0][4 * i + 2], d0);
+      d1 = fmaf(a.z, k[1][4 * i + 2], d1);
+      d0 = fmaf(a.w, k[0][4 * i + 3], d0);
+      d1 = fmaf(a.w, k[1][4 * i + 3], d1);
+    }
+    d0 += __shfl_xor_sync(0xffffffffu, d0, 1);
+    d1 += __shfl_xor_sync(0xffffffffu, d1, 1);
+    d0 += __shfl_xor_sync(0xffffffffu, d0, 2);
+    d1 += __shfl_xor_sync(0xffffffffu, d1, 2);
+    const float w = ws[h];
+    acc0 = fmaf(w, fmaxf(d0, 0.f), acc0);
+    acc1 = fmaf(w, fmaxf(d1, 0.f), acc1);
+  }
+  if (part == 0) {
+    if (pos0 < ld) scores[(size_t)t * ld + pos0] = pos0 < ctx ? acc0 : -INFINITY;
+    if (pos1 < ld) scores[(size_t)t * ld + pos1] = pos1 < ctx ? acc1 : -INFINITY;
+  }
 }
 
 // order-preserving map float -> uint32 (larger float = larger integer)
@@ -74,13 +114,17 @@ __device__ __forceinline__ uint32_t f2key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-// exclusive prefix of `flag` over the block (1024 threads), and the block total
-__device__ __forceinline__ int block_excl_scan(int flag, int* warp_tot, int& total) {
+// exclusive prefix of `v` over the block (1024 threads), and the block total
+__device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int& total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const unsigned m = __ballot_sync(0xffffffffu, flag);
-  const int in_warp = __popc(m & ((1u << lane) - 1u));
+  int inc = v;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, inc, off);
+    if (lane >= off) inc += n;
+  }
   __syncthreads();                                          // warp_tot is free again
-  if (lane == 0) warp_tot[warp] = __popc(m);
+  if (lane == 31) warp_tot[warp] = inc;
   __syncthreads();
   int before = 0, tot = 0;
   for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
@@ -89,7 +133,7 @@ __device__ __forceinline__ int block_excl_scan(int flag, int* warp_tot, int& tot
     tot += c;
   }
   total = tot;
-  return before + in_warp;
+  return before + inc - v;
 }
 
 __global__ void __launch_bounds__(1024)
@@ -109,25 +153,37 @@ topk_select_kernel(const float* __restrict__ scores, long long ld, const int* __
     return;
   }
   // radix select: after the four passes `prefix` is the key of the k-th largest score and `need`
-  // the number of entries equal to it that still belong to the selection
+  // the number of entries equal to it that still belong to the selection. Lanes that hit the same
+  // bin are counted by one atomic (scores cluster on few exponents, so the first pass would
+  // otherwise serialise on a handful of counters).
   uint32_t prefix = 0, mask = 0;
   int need = k;
+  const int n_up = (n + 31) / 32 * 32;
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const uint32_t key = f2key(sc[i]);
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+    for (int i = threadIdx.x; i < n_up; i += blockDim.x) {
+      const uint32_t key = i < n ? f2key(sc[i]) : 0u;
+      const bool in = i < n && (key & mask) == prefix;
+      const unsigned part = __ballot_sync(0xffffffffu, in);
+      if (in) {
+        const int bin = (key >> shift) & 255;
+        const unsigned peers = __match_any_sync(part, bin);
+        if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
+      }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int rem = need, b = 255;
-      for (; b > 0; --b) {
-        if (hist[b] >= rem) break;
-        rem -= hist[b];
+    {
+      // bins in descending order: thread i looks at bin 255 - i; the entries above it are the exclusive
+      // prefix, and the bin that takes the count across `need` holds the k-th largest key
+      const int b = 255 - (int)threadIdx.x;
+      const int c = threadIdx.x < 256 ? hist[b] : 0;
+      int tot;
+      const int above = block_excl_scan(c, warp_tot, tot);
+      if (threadIdx.x < 256 && above < need && need <= above + c) {
+        s_prefix = prefix | ((uint32_t)b << shift);
+        s_need = need - above;
       }
-      s_prefix = prefix | ((uint32_t)b << shift);
-      s_need = rem;
     }
     __syncthreads();
     prefix = s_prefix;
@@ -135,19 +191,58 @@ topk_select_kernel(const float* __restrict__ scores, long long ld, const int* __
     mask |= 255u << shift;
     __syncthreads();
   }
-  // ordered compaction: everything above the threshold, and the first `need` entries equal to it
-  int base = 0, eq_seen = 0;
-  for (int c0 = 0; c0 < n; c0 += blockDim.x) {
-    const int i = c0 + threadIdx.x;
-    const uint32_t key = i < n ? f2key(sc[i]) : 0u;
-    const int gt = i < n && key > prefix, eq = i < n && key == prefix;
-    int eq_tot, sel_tot;
-    const int eq_rank = eq_seen + block_excl_scan(eq, warp_tot, eq_tot);
-    const int sel = gt || (eq && eq_rank < need);
-    const int p = base + block_excl_scan(sel, warp_tot, sel_tot);
-    if (sel && p < k) out[p] = i;
-    base += sel_tot;
-    eq_seen += eq_tot;
+  // ordered compaction: warp w owns the contiguous segment [w * seg, (w + 1) * seg) and walks it 32 entries
+  // at a time (coalesced); a counting pass gives every warp its base in the output and the number of
+  // threshold-equal entries before it, a second pass places the selected entries with ballots
+  __shared__ int gt_w[32], eq_w[32], base_w[32], eqb_w[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int seg = ((n + 31) / 32 + 31) / 32 * 32;
+  const int lo = warp * seg, hi = min(n, lo + seg);
+  int gt = 0, eq = 0;
+  for (int c0 = lo; c0 < hi; c0 += 32) {
+    const int i = c0 + lane;
+    const uint32_t key = i < hi ? f2key(sc[i]) : 0u;
+    gt += __popc(__ballot_sync(0xffffffffu, i < hi && key > prefix));
+    eq += __popc(__ballot_sync(0xffffffffu, i < hi && key == prefix));
+  }
+  if (lane == 0) {
+    gt_w[warp] = gt;
+    eq_w[warp] = eq;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int g = gt_w[lane], e = eq_w[lane];
+    int inc = e;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc, off);
+      if (lane >= off) inc += v;
+    }
+    const int eq_before = inc - e;
+    const int sel = g + max(0, min(e, need - eq_before));
+    int inc2 = sel;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc2, off);
+      if (lane >= off) inc2 += v;
+    }
+    base_w[lane] = inc2 - sel;
+    eqb_w[lane] = eq_before;
+  }
+  __syncthreads();
+  int p = base_w[warp], eq_run = eqb_w[warp];
+  const unsigned lt = (1u << lane) - 1u;
+  for (int c0 = lo; c0 < hi; c0 += 32) {
+    const int i = c0 + lane;
+    const uint32_t key = i < hi ? f2key(sc[i]) : 0u;
+    const bool is_eq = i < hi && key == prefix;
+    const unsigned eqm = __ballot_sync(0xffffffffu, is_eq);
+    const bool sel = (i < hi && key > prefix) || (is_eq && eq_run + __popc(eqm & lt) < need);
+    const unsigned sm = __ballot_sync(0xffffffffu, sel);
+    const int at = p + __popc(sm & lt);
+    if (sel && at < k) out[at] = i;
+    p += __popc(sm);
+    eq_run += __popc(eqm);
   }
   if (threadIdx.x == 0) count[t] = k;
 }
@@ -181,8 +276,12 @@ extern "C" int mb_index_score(const void* iq, const void* iw, const void* kc, co
                               int Di, int block_size, long long num_blocks, void* status, cudaStream_t stream) {
   if (!iq || !iw || !kc || !scores || T <= 0 || Hi <= 0 || Hi > 128 || ld <= 0) return MB_ERR_BAD_ARG;
   const dim3 grid((unsigned)((ld + kKeysPerCta - 1) / kKeysPerCta), T);
-  const size_t smem = (size_t)Hi * Di * 2 + (size_t)Hi * 4;
-  if (smem > 48 * 1024) return MB_ERR_TOO_LARGE;
+  const size_t smem = (size_t)Hi * 4 * (Di / 4 + 4) * 4 + (size_t)Hi * 4;
+  if (smem > 200 * 1024 || Di % 32) return MB_ERR_TOO_LARGE;
+  if (smem > 48 * 1024) {
+    cudaFuncSetAttribute(index_score_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(index_score_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
 #define MB_IDX_LAUNCH(DI)                                                                                        \
   index_score_kernel<DI><<<grid, 256, smem, stream>>>(                                                           \
       static_cast<const __nv_bfloat16*>(iq), static_cast<const float*>(iw), static_cast<const __nv_bfloat16*>(kc), \

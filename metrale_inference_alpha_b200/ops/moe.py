@@ -34,11 +34,13 @@ def stack_experts(experts) -> Optional[GroupedExperts]:
     if not experts:
         return None
     from . import concat_weights
+    if experts[0].gate_up.fmt == "nvfp4":
+        # the grouped GEMM takes token tiles of 16 - 64 rows at arbitrary row offsets, while the scale
+        # factors of an NVFP4 operand are tiled by 128 rows: NVFP4 experts run one GEMM per active expert
+        # (models/moe.py::routed_experts) instead of the grouped path
+        return None
     gu = concat_weights([e.gate_up for e in experts])
     dn = concat_weights([e.down for e in experts])
-    if gu.fmt == "nvfp4":
-        gu.prepare_cuda()
-        dn.prepare_cuda()
     return GroupedExperts(gu, dn, len(experts), experts[0].gate_up.N, experts[0].down.N,
                           experts[0].interleaved)
 

@@ -135,7 +135,7 @@ def moe(ld, p: str) -> MoeW:
                 and sh.gate_up.fmt == w.experts[0].gate_up.fmt and sh.interleaved == w.experts[0].interleaved
                 and (w.shared_gate is None or w.shared_gate.N == 1))
         w.grouped = moe_ops.stack_experts(w.experts + ([sh] if fold else []))
-        if fold:
+        if fold and w.grouped is not None:
             # the shared expert becomes expert `num_experts` of the stack (every token routes to it),
             # and its sigmoid gate row is appended to the router weight
             w.grouped.shared_slot = len(w.experts)

@@ -851,3 +851,45 @@ def test_nllb_on_the_device_matches_the_host():
     _close(got, want, 5e-2, 5e-2)
     out = dev.translate([10, 11, 12, 13, 2], 20, num_beams=3, max_new_tokens=8)
     assert len(out) <= 8 and all(0 <= x < 512 for x in out)
+
+
+def test_nvfp4_experts_run_one_gemm_per_active_expert():
+    """NVFP4 MoE checkpoints: the grouped GEMM does not take NVFP4 operands, so the experts run one W4A4 GEMM
+    per active expert; the block must agree with the CPU restatement of the same synthetic checkpoint."""
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.models.moe import moe_block
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    from metrale_inference_alpha_b200.models.decoder import Decoder
+    from metrale_inference_alpha_b200.weights.loader import load_weights
+    from metrale_inference_alpha_b200.weights.source import SyntheticSource
+    cfg = preset("tiny-hybrid-moe", weight_format="nvfp4")
+    eng = LLMEngine(EngineArgs(model=cfg, device=DEV, num_kv_blocks=64, max_num_seqs=4))
+    assert not eng.args.use_cuda_graphs
+    # the same synthetic checkpoint on both devices
+    w_h = load_weights(cfg, SyntheticSource(cfg, seed=3, device="cpu"), device="cpu")
+    w_d = load_weights(cfg, SyntheticSource(cfg, seed=3, device="cpu"), device=DEV)
+    lw_d = next(L for L in w_d.layers if L.ffn_kind == "moe")
+    lw_h = next(L for L in w_h.layers if L.ffn_kind == "moe")
+    assert lw_d.ffn.grouped is None and lw_d.ffn.experts[0].gate_up.fmt == "nvfp4"
+    from metrale_inference_alpha_b200.models.moe import routed_experts
+    from metrale_inference_alpha_b200.ops import ACT_FOR_WEIGHT
+    g = torch.Generator().manual_seed(15)
+    x = (torch.randn(24, cfg.hidden_size, generator=g)).to(torch.bfloat16)
+    # the same routing on both sides (a near-tie in the router would send a token to different experts)
+    E, K = cfg.num_experts, cfg.experts_per_token
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(24)]).to(torch.int32)
+    wts = torch.rand(24, K, generator=g)
+    fmt = ACT_FOR_WEIGHT["nvfp4"]
+    dh, dd = Decoder(cfg, w_h, device="cpu"), Decoder(cfg, w_d, device=DEV)
+    a_h = dh._norm_act(x, lw_h.ln2, fmt, also_bf16=True)
+    a_d = dd._norm_act(x.to(DEV), lw_d.ln2, fmt, also_bf16=True)
+    want = routed_experts(dh, a_h, wts, idx, lw_h.ffn).float()
+    got = routed_experts(dd, a_d, wts.to(DEV), idx.to(DEV), lw_d.ffn).float().cpu()
+    err = (got - want).abs()
+    # both sides quantise activations to 4 bits, the device from the bf16 copy of the normed rows: the roundings
+    # decorrelate, so agreement is within the format's noise (a wrong expert or scale would be off by ~100 %)
+    assert float(err.mean()) < 0.15 * float(want.abs().mean()), (float(err.mean()), float(want.abs().mean()))
+    assert moe_block(dd, x.to(DEV), lw_d).shape == x.shape
+    out = eng.generate([list(range(5, 40))], SamplingParams(max_tokens=4, temperature=0.0))[0]
+    assert len(out.output_ids) == 4
+    ops.check_status(torch.device(DEV))
