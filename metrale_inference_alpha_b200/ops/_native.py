@@ -222,6 +222,7 @@ def diff_traces(a, b):
 
 
 _launch_hook = None
+_audit = None          # dict name -> launches while a kernel audit is on (utils/kernel_audit.py)
 
 
 def set_launch_hook(fn) -> None:
@@ -231,6 +232,9 @@ def set_launch_hook(fn) -> None:
 
 
 def check(rc: int, what: str) -> None:
+    if _audit is not None and rc == 0:
+        name = what.split("[", 1)[0]
+        _audit[name] = _audit.get(name, 0) + 1
     if _trace is not None:
         _trace.append(what.split("[", 1)[0])
     if _launch_hook is not None and rc == 0:

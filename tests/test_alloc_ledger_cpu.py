@@ -59,3 +59,23 @@ def test_engine_pools_are_in_the_ledger_and_a_damaged_band_latches_the_fault(mon
         assert bad and bad[0]["name"] == "kv pool (k)" and eng.fault.is_set() and "kv pool (k)" in eng.fault.reason()
     finally:
         AL.reset_for_tests(0)
+
+
+def test_kernel_audit_counts_and_classifies_launchers():
+    from metrale_inference_alpha_b200.ops import _native
+    from metrale_inference_alpha_b200.utils.kernel_audit import KernelAudit
+    with KernelAudit() as a:
+        _native.check(0, "gemm[nvfp4 M=1 N=8 K=8]")
+        _native.check(0, "gemm[bf16 M=2 N=8 K=8]")
+        _native.check(0, "attn_prefill_tc")
+        _native.check(0, "brand_new_kernel")
+        with pytest.raises(_native.KernelError):
+            _native.check(-1, "row_op")                      # a refused launch is not counted
+    assert a.counts == {"gemm": 2, "attn_prefill_tc": 1, "brand_new_kernel": 1}
+    res = a.resolve()
+    assert res["gemm"] == {"gemm": 2} and res["prefill attention"] == {"attn_prefill_tc": 1} and res["unclassified"] == {"brand_new_kernel": 1}
+    a.require("attn_prefill_tc", never=["paged_attention"])
+    with pytest.raises(AssertionError):
+        a.require("paged_attention")
+    _native.check(0, "gemm")                                  # outside the audit: not counted
+    assert a.counts["gemm"] == 2

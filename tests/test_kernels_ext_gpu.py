@@ -893,3 +893,23 @@ def test_nvfp4_experts_run_one_gemm_per_active_expert():
     out = eng.generate([list(range(5, 40))], SamplingParams(max_tokens=4, temperature=0.0))[0]
     assert len(out.output_ids) == 4
     ops.check_status(torch.device(DEV))
+
+
+def test_kernel_audit_shows_which_kernels_served_a_long_prefill_and_a_decode_step():
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    from metrale_inference_alpha_b200.utils.kernel_audit import KernelAudit
+    eng = LLMEngine(EngineArgs(model="tiny-hybrid-moe", device=DEV, num_kv_blocks=64, max_num_seqs=2, use_cuda_graphs=False))
+    with KernelAudit() as audit:
+        eng.generate([list(range(5, 5 + 200))], SamplingParams(max_tokens=3, temperature=0.0))
+    res = audit.resolve()
+    # a 200-token prefill takes the chunked gated-delta-rule scan, the time-parallel conv and the tcgen05 attention
+    audit.require("gdn_chunked")
+    audit.require("causal_conv1d_par")
+    audit.require("attn_prefill_tc")
+    assert res["gemm"]["gemm"] > 10 and "moe routing" in res and "sampling" in res
+    assert res["gated delta rule"].get("gdn_recurrence", 0) > 0          # the decode steps
+    with pytest.raises(AssertionError):
+        audit.require("kda_recurrence")
+    with pytest.raises(AssertionError):
+        audit.require("gemm", never=["row_op"])

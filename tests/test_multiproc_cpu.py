@@ -54,7 +54,7 @@ def test_two_rank_tp_matches_single_rank(tmp_path):
     assert res[0]["ids"] == _single_rank_ids()
 
 
-@pytest.mark.parametrize("family", ["tiny-hybrid-moe", "tiny-nemotron-h"])
+@pytest.mark.parametrize("family", ["tiny-hybrid-moe", "tiny-nemotron-h", "tiny-kimi-linear"])
 def test_two_rank_tp_matches_single_rank_for_hybrid_families(tmp_path, family):
     """Gated-delta-net + MoE and Mamba2 hybrids sharded over two ranks (heads, groups, conv
     channels, expert widths; the MoE output joins the residual through the deferred sum) give the
