@@ -271,6 +271,57 @@ class _KdaArgs(_C.Structure):
 _native.register_optional("mb_kda_recurrence", [_C.POINTER(_KdaArgs), _C.c_void_p])
 
 
+_KDA_CHUNK_MIN_TOKENS = 64
+_kda_ws: dict = {}
+
+
+class _KdaChunkedArgs(_C.Structure):
+    _fields_ = [("conv", _C.c_void_p), ("g_raw", _C.c_void_p), ("b_raw", _C.c_void_p), ("b_ld", _C.c_int),
+                ("A_log", _C.c_void_p), ("dt_bias", _C.c_void_p), ("lower_bound", _C.c_float), ("state", _C.c_void_p),
+                ("out", _C.c_void_p), ("out_norm", _C.c_void_p), ("out_gate", _C.c_void_p), ("gate_ld", _C.c_longlong),
+                ("norm_w", _C.c_void_p), ("eps", _C.c_float), ("H", _C.c_int), ("D", _C.c_int),
+                ("q_start", _C.c_void_p), ("q_len", _C.c_void_p), ("positions", _C.c_void_p),
+                ("state_slots", _C.c_void_p), ("num_seqs", _C.c_int), ("num_slots", _C.c_int), ("max_q_len", _C.c_int),
+                ("total_rows", _C.c_int), ("write_state", _C.c_int), ("ws", _C.c_void_p), ("ws_bytes", _C.c_size_t),
+                ("status", _C.c_void_p)]
+
+
+_native.register_optional("mb_kda_chunked", [_C.POINTER(_KdaChunkedArgs), _C.c_void_p])
+
+
+def _kda_chunked_cuda(conv_out, g_raw, b_raw, A_log, dt_bias, lower_bound, state, batch, H, write_state, norm):
+    """Chunked prefill (csrc/kda_chunked.cu); None when the workspace would be unreasonably large."""
+    L = _native.lib()
+    L.mb_kda_chunked_ws_bytes.restype = _C.c_size_t
+    L.mb_kda_chunked_ws_bytes.argtypes = [_C.c_int, _C.c_int, _C.c_int]
+    S = batch.q_len.numel()
+    need = int(L.mb_kda_chunked_ws_bytes(S, int(batch.max_q_len), H))
+    if need > _SSD_WS_MAX:
+        return None
+    dev = conv_out.device
+    ws = _kda_ws.get(dev)
+    if ws is None or ws.numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        ws = _kda_ws[dev] = torch.empty(int(need * 1.25), dtype=torch.uint8, device=dev)
+    T = conv_out.shape[0]
+    out = torch.empty(T, H * 128, dtype=torch.float32, device=dev)
+    out_n = gate = w = None
+    eps = 0.0
+    if norm is not None:
+        w, gate, eps = norm
+        out_n = torch.empty(T, H * 128, dtype=torch.bfloat16, device=dev)
+    a = _KdaChunkedArgs(_ptr(conv_out), _ptr(g_raw), _ptr(b_raw), b_raw.stride(0), _ptr(A_log), _ptr(dt_bias),
+                        float(lower_bound), _ptr(state), _ptr(out), _ptr(out_n), _ptr(gate),
+                        gate.stride(0) if gate is not None else 0, _ptr(w), float(eps), H, 128,
+                        _ptr(batch.q_start), _ptr(batch.q_len), _ptr(batch.positions), _ptr(batch.state_slots), S,
+                        state.shape[0], int(batch.max_q_len), T, int(write_state), _ptr(ws), ws.numel(),
+                        _ptr(_status(dev)))
+    _native.check(L.mb_kda_chunked(_C.byref(a), _stream()), "kda_chunked")
+    _count(3 if norm is not None else 2)
+    return out_n if norm is not None else out
+
+
 def kda_recurrence(conv_out, g_raw, b_raw, A_log, dt_bias, lower_bound: float, state, batch, *, heads: int, dim: int,
                    write_state: bool = True, write_out: bool = True, norm=None):
     """Kimi delta attention over a ragged batch. conv_out [T, 3 H D] fp32 (q | k | v after conv + SiLU),
@@ -282,6 +333,11 @@ def kda_recurrence(conv_out, g_raw, b_raw, A_log, dt_bias, lower_bound: float, s
     T = conv_out.shape[0]
     H, D = heads, dim
     if conv_out.is_cuda and _native.available() and hasattr(_native.lib(), "mb_kda_recurrence"):
+        if (write_out and D == 128 and getattr(batch, "max_q_len", 1) >= _KDA_CHUNK_MIN_TOKENS
+                and hasattr(_native.lib(), "mb_kda_chunked")):
+            y = _kda_chunked_cuda(conv_out, g_raw, b_raw, A_log, dt_bias, lower_bound, state, batch, H, write_state, norm)
+            if y is not None:
+                return y
         dev = conv_out.device
         out = out_n = gate = w = None
         eps = 0.0

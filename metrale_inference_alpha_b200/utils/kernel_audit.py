@@ -26,7 +26,7 @@ DEFAULT_RULES: Dict[str, List[str]] = {
     "moe routing": ["moe_route", "moe_route_shared"],
     "moe sort / gather / combine": ["moe_sort", "moe_gather", "moe_combine", "moe_finish"],
     "gated delta rule": ["gdn_chunked", "gdn_recurrence"],
-    "kimi delta attention": ["kda_recurrence"],
+    "kimi delta attention": ["kda_chunked", "kda_recurrence"],
     "mamba2 scan": ["mamba2_ssd", "mamba2_scan"],
     "causal conv": ["causal_conv1d_par", "causal_conv1d"],
     "sparse attention select": ["index_score", "topk_select", "gather_rows"],

@@ -913,3 +913,38 @@ def test_kernel_audit_shows_which_kernels_served_a_long_prefill_and_a_decode_ste
         audit.require("kda_recurrence")
     with pytest.raises(AssertionError):
         audit.require("gemm", never=["row_op"])
+
+
+@pytest.mark.parametrize("fused_norm", [False, True])
+def test_kda_chunked_prefill_matches_the_token_recurrence(fused_norm, monkeypatch):
+    """Long rows take the chunked kernels; forcing the token-by-token kernel on the same inputs must give the
+    same outputs and the same final state: a fresh 200-token sequence, a 130-token continuation of an existing
+    state and a 7-token sequence in one ragged batch."""
+    g = torch.Generator().manual_seed(16)
+    H, D = 3, 128
+    lens, starts = [200, 130, 7], [0, 40, 0]
+    T = sum(lens)
+    conv = torch.randn(T, 3 * H * D, generator=g)
+    g_raw = torch.randn(T, H * D, generator=g) * 2
+    b_raw = torch.randn(T, H + 2, generator=g)[:, :H]                  # a strided beta view
+    A_log, dtb = torch.randn(H, generator=g) * 0.3, torch.randn(H * D, generator=g) * 0.3
+    st = torch.randn(5, H, D, D, generator=g) * 0.1
+    gate = torch.randn(T, H * D, generator=g).to(torch.bfloat16)
+    w = torch.rand(D, generator=g) + 0.5
+    seqs = [dict(tokens=[1] * n, start_pos=s, blocks=list(range(1, 20)), state_slot=i + 1) for i, (n, s) in enumerate(zip(lens, starts))]
+    b = ForwardBatch.build(seqs, 16, device=DEV)
+    outs = {}
+    for name, thresh in (("chunked", 64), ("sequential", 1 << 30)):
+        monkeypatch.setattr(rops, "_KDA_CHUNK_MIN_TOKENS", thresh)
+        s = st.clone().to(DEV)
+        norm = (w.to(DEV), gate.to(DEV), 1e-6) if fused_norm else None
+        with ops._native.launch_trace() as names:
+            y = rops.kda_recurrence(conv.to(DEV), g_raw.to(DEV), b_raw.to(DEV), A_log.to(DEV), dtb.to(DEV), -5.0, s, b,
+                                    heads=H, dim=D, norm=norm)
+        assert ("kda_chunked" in names) == (name == "chunked")
+        outs[name] = (y.float().cpu(), s.cpu())
+    tol = 2e-2 if fused_norm else 2e-3
+    _close(outs["chunked"][0], outs["sequential"][0], tol, tol)
+    _close(outs["chunked"][1], outs["sequential"][1], 2e-3, 2e-3)
+    assert torch.equal(outs["chunked"][1][0], st[0]) and torch.equal(outs["chunked"][1][4], st[4])       # untouched slots
+    ops.check_status(torch.device(DEV))
