@@ -6,6 +6,7 @@
     python benchmarks/ncu_case.py --op gemm   [--m 128 --n 5120 --k 17408 --fmt nvfp4]
     python benchmarks/ncu_case.py --op rowop  [--m 128 --k 5120]
     python benchmarks/ncu_case.py --op mla    [--m 64 --ctx 2048]
+    python benchmarks/ncu_case.py --op kda_prefill [--ctx 4096]
 """
 import argparse
 import math
@@ -103,6 +104,21 @@ def main():
                 fr.partial_view(M, r).normal_()
             pend = PendingSum(fr, fr.partial_view(M, 0), res)
             fr.reduce_norm(pend, w, "nvfp4", eps=1e-6)
+    elif a.op == "kda_prefill":
+        # one sequence of --ctx tokens through the chunked Kimi-delta-attention kernels, 32 heads x 128
+        # (workspace 70 KB per chunk and head: 0.3 GB at 4096 tokens)
+        from metrale_inference_alpha_b200.engine.batch import ForwardBatch
+        from metrale_inference_alpha_b200.ops import recurrent as rops
+        H, D, T = 32, 128, a.ctx
+        conv = torch.randn(T, 3 * H * D, device=DEV)
+        g_raw, b_raw = torch.randn(T, H * D, device=DEV), torch.randn(T, H, device=DEV)
+        A, dtb = torch.zeros(H, device=DEV), torch.zeros(H * D, device=DEV)
+        st = torch.zeros(2, H, D, D, device=DEV)
+        gate = torch.randn(T, H * D, device=DEV).to(torch.bfloat16)
+        wn = torch.ones(D, device=DEV)
+        b = ForwardBatch.build([dict(tokens=[1] * T, start_pos=0, blocks=list(range(1, T // 16 + 2)), state_slot=1)], 16, device=DEV)
+        for _ in range(a.iters):
+            rops.kda_recurrence(conv, g_raw, b_raw, A, dtb, -5.0, st, b, heads=H, dim=D, norm=(wn, gate, 1e-6))
     elif a.op == "rowop":
         x = torch.randn(M, a.k, device=DEV).to(torch.bfloat16)
         w = torch.ones(a.k, device=DEV, dtype=torch.bfloat16)

@@ -31,6 +31,7 @@ constexpr int kD = 128;           // head dim (key and value)
 constexpr int kLd = kD + 1;       // padded row: rows i and j fall on different banks for the same channel
 constexpr int kVs = 4;            // value-dimension splits of the scan
 constexpr int kCols = kD / kVs;   // 32 state columns per scan CTA
+constexpr int kScanThreads = 512, kWarps = kScanThreads / 32, kRw = kC / kWarps, kSr = kD / kWarps;   // rows per warp: chunk, state
 // one stage of the scan's operands in shared memory, in floats
 constexpr int kStW = 0, kStQg = kC * kD, kStKd = 2 * kC * kD, kStU = 3 * kC * kD, kStIn = kStU + kC * kCols,
               kStGl = kStIn + kC * kC, kStage = kStGl + kD;
@@ -200,9 +201,10 @@ struct ScanArgs {
   uint32_t* status;
 };
 
-// grid (H * kVs, sequences); 256 threads: warp r owns output rows r, r + 8, r + 16, r + 24 of the chunk and
-// state rows [16 r, 16 r + 16); lane = state column
-__global__ void __launch_bounds__(256) kda_chunk_scan_kernel(const ScanArgs a) {
+// grid (H * kVs, sequences); 512 threads (one CTA per SM: four warps per scheduler hide the shared-memory
+// latency of the small products): warp r owns output rows r and r + 16 of the chunk and state rows
+// [8 r, 8 r + 8); lane = state column
+__global__ void __launch_bounds__(kScanThreads) kda_chunk_scan_kernel(const ScanArgs a) {
   extern __shared__ __align__(16) float smem[];
   float* S = smem;                      // [D][kCols]
   float* stage0 = S + kD * kCols;       // two stages of a chunk's operands: the next chunk streams in (cp.async)
@@ -220,22 +222,22 @@ __global__ void __launch_bounds__(256) kda_chunk_scan_kernel(const ScanArgs a) {
   const int HD = a.H * kD;
   float* st = a.state + (((size_t)slot * a.H + hd) * kD) * kD + vs * kCols + col;
   const bool fresh = a.sm.positions[q0] == 0;
-  for (int k = r * 16; k < r * 16 + 16; ++k) S[k * kCols + col] = fresh ? 0.f : st[(size_t)k * kD];
+  for (int k = r * kSr; k < r * kSr + kSr; ++k) S[k * kCols + col] = fresh ? 0.f : st[(size_t)k * kD];
   const int nchunks = (n + kC - 1) / kC;
   float* vn_s = stage0 + 2 * kStage;    // [C][kCols]
   auto issue = [&](int c) {
     const float* wsb = a.ws + ((size_t)((size_t)seq * a.max_chunks + c) * a.H + hd) * kWsStride;
     float* st_ = stage0 + (c & 1) * kStage;
-    for (int p = threadIdx.x; p < kC * kD / 4; p += 256) {
+    for (int p = threadIdx.x; p < kC * kD / 4; p += kScanThreads) {
       cp16(st_ + kStW + 4 * p, wsb + kOffW + 4 * p);
       cp16(st_ + kStQg + 4 * p, wsb + kOffQg + 4 * p);
       cp16(st_ + kStKd + 4 * p, wsb + kOffKd + 4 * p);
     }
-    for (int p = threadIdx.x; p < kC * kCols / 4; p += 256) {
+    for (int p = threadIdx.x; p < kC * kCols / 4; p += kScanThreads) {
       const int i = p >> 3, q4 = p & 7;
       cp16(st_ + kStU + i * kCols + 4 * q4, wsb + kOffU + i * kD + vs * kCols + 4 * q4);
     }
-    for (int p = threadIdx.x; p < kC * kC / 4; p += 256) cp16(st_ + kStIn + 4 * p, wsb + kOffIntra + 4 * p);
+    for (int p = threadIdx.x; p < kC * kC / 4; p += kScanThreads) cp16(st_ + kStIn + 4 * p, wsb + kOffIntra + 4 * p);
     if (threadIdx.x < kD / 4) cp16(st_ + kStGl + 4 * threadIdx.x, wsb + kOffGlast + 4 * threadIdx.x);
     cp_commit();
   };
@@ -254,15 +256,16 @@ __global__ void __launch_bounds__(256) kda_chunk_scan_kernel(const ScanArgs a) {
                 *gl_s = st_ + kStGl;
     // v_new = u - w S, and the part of the output that reads the old state: four state rows per step, the
     // w / q operands as 16-byte broadcast reads shared by the chunk rows this warp owns
-    float o[4], sv[4] = {0.f, 0.f, 0.f, 0.f};
+    float o[kRw], sv[kRw];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) o[e] = 0.f;
+    for (int e = 0; e < kRw; ++e) o[e] = sv[e] = 0.f;
+#pragma unroll 2
     for (int k = 0; k < kD; k += 4) {
       const float s0 = S[k * kCols + col], s1 = S[(k + 1) * kCols + col], s2 = S[(k + 2) * kCols + col],
                   s3 = S[(k + 3) * kCols + col];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = r + 8 * e;
+      for (int e = 0; e < kRw; ++e) {
+        const int i = r + kWarps * e;
         const float4 w4 = *reinterpret_cast<const float4*>(&w_s[i * kD + k]);
         const float4 q4 = *reinterpret_cast<const float4*>(&qg_s[i * kD + k]);
         sv[e] = fmaf(w4.x, s0, sv[e]);
@@ -276,15 +279,15 @@ __global__ void __launch_bounds__(256) kda_chunk_scan_kernel(const ScanArgs a) {
       }
     }
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = r + 8 * e;
+    for (int e = 0; e < kRw; ++e) {
+      const int i = r + kWarps * e;
       vn_s[i * kCols + col] = u_s[i * kCols + col] - sv[e];
     }
     __syncthreads();
     const int rows = min(kC, n - c * kC);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = r + 8 * e;
+    for (int e = 0; e < kRw; ++e) {
+      const int i = r + kWarps * e;
       float so = o[e];
       for (int j = 0; j <= i; ++j) so = fmaf(in_s[i * kC + j], vn_s[j * kCols + col], so);
       if (i < rows) a.out[(size_t)(q0 + c * kC + i) * HD + hd * kD + vs * kCols + col] = so;
@@ -294,7 +297,7 @@ __global__ void __launch_bounds__(256) kda_chunk_scan_kernel(const ScanArgs a) {
       float vn[kC];
 #pragma unroll
       for (int i = 0; i < kC; ++i) vn[i] = vn_s[i * kCols + col];
-      for (int k = r * 16; k < r * 16 + 16; k += 4) {
+      for (int k = r * kSr; k < r * kSr + kSr; k += 4) {
         float s0 = S[k * kCols + col] * __expf(gl_s[k]), s1 = S[(k + 1) * kCols + col] * __expf(gl_s[k + 1]),
               s2 = S[(k + 2) * kCols + col] * __expf(gl_s[k + 2]), s3 = S[(k + 3) * kCols + col] * __expf(gl_s[k + 3]);
 #pragma unroll
@@ -313,7 +316,7 @@ __global__ void __launch_bounds__(256) kda_chunk_scan_kernel(const ScanArgs a) {
     }
   }
   if (a.write_state)
-    for (int k = r * 16; k < r * 16 + 16; ++k) st[(size_t)k * kD] = S[k * kCols + col];
+    for (int k = r * kSr; k < r * kSr + kSr; ++k) st[(size_t)k * kD] = S[k * kCols + col];
 }
 
 // y = o * rsqrt(mean(o^2) + eps) * w * sigmoid(gate), one CTA per (row, head)
@@ -389,7 +392,7 @@ extern "C" int mb_kda_chunked(const MbKdaChunkedArgs* p, cudaStream_t stream) {
   kda_chunk_prep_kernel<<<dim3(max_chunks, p->H, p->num_seqs), 256, prep_smem, stream>>>(pa);
   ScanArgs sa{static_cast<const float*>(p->ws), static_cast<float*>(p->state), static_cast<float*>(p->out), p->H, max_chunks,
               sm, p->write_state, static_cast<uint32_t*>(p->status)};
-  kda_chunk_scan_kernel<<<dim3(p->H * kVs, p->num_seqs), 256, scan_smem, stream>>>(sa);
+  kda_chunk_scan_kernel<<<dim3(p->H * kVs, p->num_seqs), kScanThreads, scan_smem, stream>>>(sa);
   if (p->out_norm && p->total_rows > 0)
     kda_out_norm_kernel<<<dim3(p->total_rows, p->H), kD, 0, stream>>>(
         static_cast<const float*>(p->out), static_cast<const __nv_bfloat16*>(p->out_gate), p->gate_ld,
