@@ -67,6 +67,9 @@ class EngineArgs:
     state_snapshots: int = 0                           # device-resident state snapshots (0 = 16 + ring slots x max_num_seqs)
     state_tier_host_bytes: int = 0                     # > 0: resident snapshots overflow into this much host memory ...
     state_tier_dir: Optional[str] = None               # ... and from there (or directly) into files in this directory
+    kv_tier_blocks: int = 0                            # > 0: KV blocks the prefix cache evicts are kept in a second tier of this many blocks ...
+    kv_tier_dir: Optional[str] = None                  # ... in files under this directory (default: host memory)
+    kv_tier_host_blocks: int = 0                       # with kv_tier_dir: a pinned write-back host cache of this many blocks in front of the files
     expert_arena_slots: int = 0                        # MoE: > 0 pages the routed experts from an expert store into a device arena of this many experts
     expert_store_dir: Optional[str] = None             # ... the store's directory (written from the loaded weights when it has no manifest yet)
     prediction_drafts: int = 8                         # tokens verified per step for requests with a predicted output
@@ -185,6 +188,13 @@ class LLMEngine:
                                     on_snapshot_evict=(self.runner.pool.release_snapshot if needs_snap else None))
             if needs_snap and hasattr(self.prefix, "snapshot_ok"):
                 self.prefix.snapshot_ok = self.runner.pool.available
+            if args.kv_tier_blocks > 0:
+                if needs_snap:
+                    raise ValueError("kv_tier_blocks: models with recurrent state keep their prefix hits through state "
+                                     "snapshots (state_tier_host_bytes / state_tier_dir), not through KV tiering")
+                from ..cache.kv_tier import KvTierStore, TieredRadixTree
+                self.kv_tier = KvTierStore(self.runner.kv, args.kv_tier_blocks, args.kv_tier_dir, args.kv_tier_host_blocks)
+                self.prefix = TieredRadixTree(self.runner.kv.allocator, args.block_size, self.kv_tier)
         self.spill = None
         if args.preempt_mode == "swap":
             from ..cache.kv_spill import KvSpillManager

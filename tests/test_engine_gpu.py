@@ -223,3 +223,19 @@ def test_telemetry_kernel_level_records_per_kernel_device_time():
         assert "metrale_lane_norm_ms_count 1" in text
     finally:
         t.close()
+
+
+def test_kv_tier_restores_evicted_prefix_blocks_on_the_device():
+    """Blocks the prefix cache evicts are kept in host memory and copied back on the next hit."""
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    sp = SamplingParams(max_tokens=4, temperature=0.0)
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cuda", max_num_seqs=2, max_model_len=256, num_kv_blocks=14,
+                               kv_tier_blocks=64))
+    a = list(range(10, 110))
+    first = eng.generate([a], sp)[0]
+    for i in range(3):
+        eng.generate([list(range(300 + 150 * i, 420 + 150 * i))], sp)
+    again = eng.generate([a], sp)[0]
+    assert again.output_ids == first.output_ids and again.cached_tokens >= 80
+    assert eng.prefix.stats()["tier_restored"] >= 5

@@ -362,3 +362,60 @@ def test_probe_reports_and_recommends(tmp_path):
     assert decide({"dir_writable": False}) == "memory"
     assert decide({"dir_writable": True, "buffered": {"read_gbs": 2.0}, "direct": {"error": "x"}}) == "file"
     assert decide({"dir_writable": True, "buffered": {"read_gbs": 2.0}, "direct": {"read_gbs": 3.0}}) == "file-direct"
+
+
+# ----------------------------------------------------------------------------- KV tier under the prefix cache
+@pytest.mark.parametrize("use_files", [False, True])
+def test_evicted_prefix_blocks_come_back_from_the_tier(tmp_path, use_files):
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    sp = SamplingParams(max_tokens=4, temperature=0.0)
+    common = dict(model="tiny-dense", device="cpu", max_num_seqs=2, max_model_len=256, num_kv_blocks=14)
+    plain = LLMEngine(EngineArgs(**common))
+    tiered = LLMEngine(EngineArgs(**common, kv_tier_blocks=64, kv_tier_dir=str(tmp_path / "tier") if use_files else None,
+                                  kv_tier_host_blocks=4 if use_files else 0))
+    a = list(range(10, 10 + 100))                              # 6 full blocks of 16
+    others = [list(range(300 + 150 * i, 300 + 150 * i + 120)) for i in range(3)]
+    want_a = plain.generate([a], sp)[0].output_ids
+    first = tiered.generate([a], sp)[0]
+    assert first.output_ids == want_a and first.cached_tokens == 0
+    for o in others:                                           # push a's blocks out of the 13-block pool
+        tiered.generate([o], sp)
+    st = tiered.prefix.stats()
+    assert st["tier_stored"] >= 6
+    again = tiered.generate([a], sp)[0]
+    assert again.output_ids == want_a
+    assert again.cached_tokens >= 80                           # restored from the tier, not recomputed
+    st = tiered.prefix.stats()
+    assert st["tier_hits"] >= 1 and st["tier_restored"] >= 5 and st["tier_hit_tokens"] >= 80
+    # the plain engine recomputes the same prompt from scratch after the same churn
+    for o in others:
+        plain.generate([o], sp)
+    assert plain.generate([a], sp)[0].cached_tokens < again.cached_tokens
+    # a different namespace (adapter) never sees these records
+    from metrale_inference_alpha_b200.cache.kv_tier import chain_digest
+    assert chain_digest(b"", a[:16], None) != chain_digest(b"", a[:16], "adapter-x")
+
+
+def test_tier_capacity_overwrites_the_least_recently_used_record():
+    from metrale_inference_alpha_b200.cache import KvCacheConfig, PagedKvCache
+    from metrale_inference_alpha_b200.cache.kv_tier import KvTierStore
+    kv = PagedKvCache(KvCacheConfig(2, 2, 16, block_size=4), 8)
+    for i in range(8):
+        for L in range(2):
+            kv.k[L][i].fill_(i + L)
+            kv.v[L][i].fill_(-(i + L))
+    st = KvTierStore(kv, capacity_blocks=2)
+    st.put(b"a", 1)
+    st.put(b"b", 2)
+    st.put(b"a", 1)                                            # refresh: b is now the oldest
+    st.put(b"c", 3)
+    assert st.has(b"a") and st.has(b"c") and not st.has(b"b") and st.stats["overwritten"] == 1
+    assert st.restore(b"c", 5) and not st.restore(b"b", 6)
+    assert torch.equal(kv.k[1][5], kv.k[1][3]) and torch.equal(kv.v[0][5], kv.v[0][3])
+
+
+def test_kv_tier_is_refused_for_recurrent_models():
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    with pytest.raises(ValueError):
+        LLMEngine(EngineArgs(model="tiny-hybrid-moe", device="cpu", num_kv_blocks=32, kv_tier_blocks=8))
