@@ -47,6 +47,41 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
 __device__ __forceinline__ float ssqrt(float x) { return copysignf(sqrtf(fmaxf(fabsf(x), 1e-6f)), x); }
 
+// The gates and the combination matrix of one token from its (rms-scaled) mixes, by warp 0: lane = element
+// (i, j) = (lane / 4, lane % 4) of the 4 x 4 grid (elements outside hc x hc carry zeros). Row sums meet through
+// shuffles over the lanes of a row (xor 1, 2), column sums over xor 4, 8; every normalisation is one reciprocal
+// and one multiply per lane, so the Sinkhorn iterations cost a few hundred cycles instead of a serial chain of
+// divisions.
+__device__ __forceinline__ void hc_gates_warp(const float* mix, float rstd, const float* __restrict__ scale,
+                                              const float* __restrict__ base, int hc, float hc_eps, int iters,
+                                              float* pre_s, float* post_out, float* comb_out) {
+  const int lane = threadIdx.x & 31;
+  const int i = (lane >> 2) & 3, j = lane & 3;
+  const bool in = lane < 16 && i < hc && j < hc;
+  if (lane < hc) {
+    pre_s[lane] = sigmoidf_(mix[lane] * rstd * scale[0] + base[lane]) + hc_eps;
+    post_out[lane] = 2.f * sigmoidf_(mix[hc + lane] * rstd * scale[1] + base[hc + lane]);
+  }
+  float c = in ? mix[2 * hc + i * hc + j] * rstd * scale[2] + base[2 * hc + i * hc + j] : -INFINITY;
+  float m = fmaxf(c, __shfl_xor_sync(0xffffffffu, c, 1));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+  c = in ? __expf(c - m) : 0.f;
+  float rs = c + __shfl_xor_sync(0xffffffffu, c, 1);
+  rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+  c = in ? c / rs + hc_eps : 0.f;
+  for (int it = 0; it < iters; ++it) {
+    if (it > 0) {                                                   // row normalisation
+      float r = c + __shfl_xor_sync(0xffffffffu, c, 1);
+      r += __shfl_xor_sync(0xffffffffu, r, 2);
+      c *= 1.f / (r + hc_eps);
+    }
+    float cs = c + __shfl_xor_sync(0xffffffffu, c, 4);              // column normalisation
+    cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+    c *= 1.f / (cs + hc_eps);
+  }
+  if (in) comb_out[i * hc + j] = c;
+}
+
 __global__ void __launch_bounds__(kHcThreads)
 hc_pre_kernel(const float* __restrict__ streams, const __nv_bfloat16* __restrict__ fn, const float* __restrict__ scale,
               const float* __restrict__ base, __nv_bfloat16* __restrict__ y, float* __restrict__ post_out,
@@ -107,41 +142,114 @@ hc_pre_kernel(const float* __restrict__ streams, const __nv_bfloat16* __restrict
   __syncthreads();
   if (threadIdx.x < mix_hc) mix[threadIdx.x] = part[threadIdx.x][0] * rsqrtf(part[kMaxMix][0] / n + norm_eps);
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float c[kMaxHc][kMaxHc];
-    for (int i = 0; i < hc; ++i) {
-      pre_s[i] = sigmoidf_(mix[i] * scale[0] + base[i]) + hc_eps;
-      post_out[(size_t)t * hc + i] = 2.f * sigmoidf_(mix[hc + i] * scale[1] + base[hc + i]);
-    }
-    for (int i = 0; i < hc; ++i) {                                  // softmax over j
-      float m = -INFINITY, s = 0.f;
-      for (int j = 0; j < hc; ++j) {
-        c[i][j] = mix[2 * hc + i * hc + j] * scale[2] + base[2 * hc + i * hc + j];
-        m = fmaxf(m, c[i][j]);
-      }
-      for (int j = 0; j < hc; ++j) {
-        c[i][j] = __expf(c[i][j] - m);
-        s += c[i][j];
-      }
-      for (int j = 0; j < hc; ++j) c[i][j] = c[i][j] / s + hc_eps;
-    }
-    for (int it = 0; it < iters; ++it) {
-      if (it > 0) {                                                 // row normalisation
-        for (int i = 0; i < hc; ++i) {
-          float s = hc_eps;
-          for (int j = 0; j < hc; ++j) s += c[i][j];
-          for (int j = 0; j < hc; ++j) c[i][j] /= s;
-        }
-      }
-      for (int j = 0; j < hc; ++j) {                                // column normalisation
-        float s = hc_eps;
-        for (int i = 0; i < hc; ++i) s += c[i][j];
-        for (int i = 0; i < hc; ++i) c[i][j] /= s;
-      }
-    }
-    for (int i = 0; i < hc; ++i)
-      for (int j = 0; j < hc; ++j) comb_out[((size_t)t * hc + i) * hc + j] = c[i][j];
+  if (threadIdx.x < 32)
+    hc_gates_warp(mix, 1.f, scale, base, hc, hc_eps, iters, pre_s, post_out + (size_t)t * hc, comb_out + (size_t)t * hc * hc);
+  __syncthreads();
+  for (int d = threadIdx.x; d < H; d += kHcThreads) {
+    float v = 0.f;
+    for (int i = 0; i < hc; ++i) v = fmaf(pre_s[i], x[(size_t)i * H + d], v);
+    y[(size_t)t * H + d] = __float2bfloat16(v);
   }
+}
+
+// ---- the same computation split for many rows: `hc_mix` walks (4-token tile, slice of the hc*H axis) so that a
+// slice of the mixing matrix is read once per four tokens and the grid fills the machine whatever the row count;
+// it leaves per-slice partial sums, which `hc_finish` adds in slice order (no atomics: the result does not
+// depend on scheduling) before the gates, the Sinkhorn iterations and the collapse.
+constexpr int kMixTok = 4, kMixThreads = 64;
+
+__global__ void __launch_bounds__(kMixThreads)
+hc_mix_kernel(const float* __restrict__ streams, const __nv_bfloat16* __restrict__ fn, float* __restrict__ part,
+              int T, int hc, int H, int slices) {
+  __shared__ float red[kMixThreads / 32][kMixTok][kMaxMix + 1];
+  const int n = hc * H, mix_hc = (2 + hc) * hc;
+  const int t0 = blockIdx.x * kMixTok, sl = blockIdx.y;
+  const int n8 = n / 8, per = (n8 + slices - 1) / slices;
+  const int lo = sl * per, hi = min(n8, lo + per);
+  float acc[kMixTok][kMaxMix], ss[kMixTok];
+#pragma unroll
+  for (int m = 0; m < kMixTok; ++m) {
+    ss[m] = 0.f;
+#pragma unroll
+    for (int r = 0; r < kMaxMix; ++r) acc[m][r] = 0.f;
+  }
+  for (int i8 = lo + threadIdx.x; i8 < hi; i8 += kMixThreads) {
+    float xv[kMixTok][8];
+#pragma unroll
+    for (int m = 0; m < kMixTok; ++m) {
+      if (t0 + m < T) {
+        const float4* xp = reinterpret_cast<const float4*>(streams + (size_t)(t0 + m) * n) + 2 * i8;
+        const float4 a = xp[0], b = xp[1];
+        xv[m][0] = a.x; xv[m][1] = a.y; xv[m][2] = a.z; xv[m][3] = a.w;
+        xv[m][4] = b.x; xv[m][5] = b.y; xv[m][6] = b.z; xv[m][7] = b.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xv[m][j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss[m] = fmaf(xv[m][j], xv[m][j], ss[m]);
+    }
+#pragma unroll
+    for (int r = 0; r < kMaxMix; ++r) {
+      if (r < mix_hc) {
+        const uint4 w = reinterpret_cast<const uint4*>(fn + (size_t)r * n)[i8];
+        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+        float wf[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(w2[j]);
+          wf[2 * j] = f.x;
+          wf[2 * j + 1] = f.y;
+        }
+#pragma unroll
+        for (int m = 0; m < kMixTok; ++m)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[m][r] = fmaf(wf[j], xv[m][j], acc[m][r]);
+      }
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int m = 0; m < kMixTok; ++m) {
+    const float s = mb::warp_sum(ss[m]);
+    if (lane == 0) red[warp][m][kMaxMix] = s;
+#pragma unroll
+    for (int r = 0; r < kMaxMix; ++r) {
+      if (r < mix_hc) {
+        const float v = mb::warp_sum(acc[m][r]);
+        if (lane == 0) red[warp][m][r] = v;
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kMixTok * (kMaxMix + 1); i += kMixThreads) {
+    const int m = i / (kMaxMix + 1), r = i - m * (kMaxMix + 1);
+    if (t0 + m < T && (r < mix_hc || r == kMaxMix)) {
+      float v = 0.f;
+      for (int w = 0; w < kMixThreads / 32; ++w) v += red[w][m][r];
+      part[((size_t)sl * T + t0 + m) * (kMaxMix + 1) + r] = v;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kHcThreads)
+hc_finish_kernel(const float* __restrict__ streams, const float* __restrict__ part, const float* __restrict__ scale,
+                 const float* __restrict__ base, __nv_bfloat16* __restrict__ y, float* __restrict__ post_out,
+                 float* __restrict__ comb_out, int T, int hc, int H, int slices, float norm_eps, float hc_eps, int iters) {
+  __shared__ float mix[kMaxMix + 1];
+  __shared__ float pre_s[kMaxHc];
+  const int t = blockIdx.x;
+  const int n = hc * H, mix_hc = (2 + hc) * hc;
+  const float* x = streams + (size_t)t * n;
+  if (threadIdx.x <= kMaxMix && (threadIdx.x < mix_hc || threadIdx.x == kMaxMix)) {
+    float v = 0.f;
+    for (int s = 0; s < slices; ++s) v += part[((size_t)s * T + t) * (kMaxMix + 1) + threadIdx.x];
+    mix[threadIdx.x] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32)
+    hc_gates_warp(mix, rsqrtf(mix[kMaxMix] / n + norm_eps), scale, base, hc, hc_eps, iters, pre_s,
+                  post_out + (size_t)t * hc, comb_out + (size_t)t * hc * hc);
   __syncthreads();
   for (int d = threadIdx.x; d < H; d += kHcThreads) {
     float v = 0.f;
@@ -284,6 +392,34 @@ dilated_conv_kernel(const float* __restrict__ x, const float* __restrict__ basep
 }
 
 }  // namespace
+
+extern "C" int mb_hc_pre_ws_floats(int T, int hc, int H) {
+  // slices chosen so that (token tiles x slices) covers the machine about twice
+  const int tiles = (T + kMixTok - 1) / kMixTok;
+  int slices = (296 + tiles - 1) / tiles;
+  const int n8 = hc * H / 8;
+  if (slices > n8 / kMixThreads) slices = n8 / kMixThreads;
+  if (slices < 1) slices = 1;
+  if (slices > 32) slices = 32;
+  return slices * T * (kMaxMix + 1);
+}
+
+extern "C" int mb_hc_pre_split(const void* streams, const void* fn, const void* scale, const void* base, void* y,
+                               void* post, void* comb, void* ws, int ws_floats, int T, int hc, int H, float norm_eps,
+                               float hc_eps, int iters, cudaStream_t stream) {
+  if (!streams || !fn || !y || !ws || T <= 0 || hc <= 0 || hc > kMaxHc || H <= 0 || iters < 1 || (hc * H) % 8)
+    return MB_ERR_BAD_ARG;
+  const int need = mb_hc_pre_ws_floats(T, hc, H);
+  if (ws_floats < need) return MB_ERR_TOO_LARGE;
+  const int slices = need / (T * (kMaxMix + 1));
+  hc_mix_kernel<<<dim3((T + kMixTok - 1) / kMixTok, slices), kMixThreads, 0, stream>>>(
+      static_cast<const float*>(streams), static_cast<const __nv_bfloat16*>(fn), static_cast<float*>(ws), T, hc, H, slices);
+  hc_finish_kernel<<<T, kHcThreads, 0, stream>>>(
+      static_cast<const float*>(streams), static_cast<const float*>(ws), static_cast<const float*>(scale),
+      static_cast<const float*>(base), static_cast<__nv_bfloat16*>(y), static_cast<float*>(post),
+      static_cast<float*>(comb), T, hc, H, slices, norm_eps, hc_eps, iters);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int mb_hc_pre(const void* streams, const void* fn, const void* scale, const void* base, void* y, void* post,
                          void* comb, int T, int hc, int H, float norm_eps, float hc_eps, int iters, cudaStream_t stream) {

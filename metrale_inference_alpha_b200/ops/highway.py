@@ -18,11 +18,15 @@ from . import _native
 c_void_p, c_int, c_float = C.c_void_p, C.c_int, C.c_float
 
 _native.register_optional("mb_hc_pre", [c_void_p] * 7 + [c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+_native.register_optional("mb_hc_pre_split", [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
 _native.register_optional("mb_hc_post", [c_void_p] * 4 + [c_int, c_int, c_int, c_void_p])
 _native.register_optional("mb_engram_gate_add", [c_void_p] * 3 + [c_int, c_int, c_int, c_float, c_void_p])
 _native.register_optional("mb_ple_gate", [c_void_p] * 8 + [c_int, c_int, c_int, c_float, c_void_p])
 _native.register_optional("mb_dilated_conv", [c_void_p] * 5 + [c_int, c_int, c_int] + [c_void_p] * 4 +
                           [c_int, c_int, c_int, c_void_p, c_void_p])
+
+
+_HC_SPLIT_MIN_ROWS = 8
 
 
 def _cuda(t: torch.Tensor) -> bool:
@@ -54,6 +58,18 @@ def hc_pre(streams: torch.Tensor, fn: torch.Tensor, scale: torch.Tensor, base: t
         y = torch.empty(T, H, dtype=torch.bfloat16, device=streams.device)
         post = torch.empty(T, hc, dtype=torch.float32, device=streams.device)
         comb = torch.empty(T, hc, hc, dtype=torch.float32, device=streams.device)
+        L = _native.lib()
+        if T >= _HC_SPLIT_MIN_ROWS and (hc * H) % 8 == 0 and hasattr(L, "mb_hc_pre_split"):
+            # several rows: token tiles x slices of the stream axis, partial sums added in slice order
+            L.mb_hc_pre_ws_floats.restype = c_int
+            L.mb_hc_pre_ws_floats.argtypes = [c_int, c_int, c_int]
+            need = int(L.mb_hc_pre_ws_floats(T, hc, H))
+            ws = torch.empty(need, dtype=torch.float32, device=streams.device)
+            rc = L.mb_hc_pre_split(_ptr(streams), _ptr(fn), _ptr(scale), _ptr(base), _ptr(y), _ptr(post), _ptr(comb), _ptr(ws),
+                                   need, T, hc, H, norm_eps, hc_eps, iters, _stream())
+            _native.check(rc, f"hc_pre_split[T={T}]")
+            _count(2)
+            return y, post, comb
         rc = _native.lib().mb_hc_pre(_ptr(streams), _ptr(fn), _ptr(scale), _ptr(base), _ptr(y), _ptr(post), _ptr(comb),
                                      T, hc, H, norm_eps, hc_eps, iters, _stream())
         _native.check(rc, f"hc_pre[T={T}]")

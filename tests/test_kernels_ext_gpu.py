@@ -747,8 +747,7 @@ def test_sparse_mla_model_runs_on_the_device():
 def test_hyper_connection_kernels_match_the_restatement():
     from metrale_inference_alpha_b200.ops import highway as hw
     g = torch.Generator().manual_seed(11)
-    for hc, H in ((4, 1024), (2, 512)):
-        T = 7
+    for hc, H, T in ((4, 1024, 7), (2, 512, 7), (4, 1024, 37), (4, 5120, 130)):           # few rows: one kernel; many: mix + finish
         streams = torch.randn(T, hc, H, generator=g)
         fn = (torch.randn((2 + hc) * hc, hc * H, generator=g) * 0.03).to(torch.bfloat16)
         scale, base = torch.tensor([1.0, 0.5, 2.0]), torch.randn((2 + hc) * hc, generator=g) * 0.1
