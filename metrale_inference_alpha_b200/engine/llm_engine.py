@@ -451,6 +451,28 @@ class LLMEngine:
                 break
         return [done[i] for i in ids if i in done]
 
+    def close(self) -> None:
+        """Ordered teardown: finish the step in flight, abort what is queued, drop the CUDA graphs (they hold
+        the static buffers), then close what owns files or threads — swap files, state and KV tiers, the expert
+        store — and finally the pools. Safe to call twice; the engine takes no requests afterwards.
+        Role of the reference's scoped teardown (crates/core/src/scope.rs)."""
+        if getattr(self, "_closed", False):
+            return
+        self._closed = True
+        try:
+            self.flush()
+        except Exception:
+            pass
+        for seq in list(self.scheduler.waiting) + list(self.scheduler.prefilling) + list(self.scheduler.running):
+            self.scheduler.abort(seq.req.request_id)
+        self.runner.graphs.clear()
+        for owner in (getattr(self, "kv_tier", None), getattr(getattr(self, "paged_experts", None), "reader", None)):
+            if owner is not None:
+                owner.close()
+        if self.prefix is not None:
+            self.prefix.clear()
+        self.fault.set("engine closed")
+
     def check_red_zones(self) -> list:
         """Compare the guard bands behind the engine's pools (``METRALE_REDZONE``); a damaged band
         latches the fault with the name of the buffer that was overrun."""

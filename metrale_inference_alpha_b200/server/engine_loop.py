@@ -62,6 +62,12 @@ class AsyncEngine:
             time.sleep(0.05)
         self._stop.set()
         self._thread.join(timeout=5)
+        close = getattr(self.engine, "close", None)
+        if close is not None and not self._thread.is_alive():      # the scheduler thread is gone: tear the engine down in order
+            try:
+                close()
+            except Exception:
+                pass
         if self.control is not None and not self.fatal:
             try:
                 self.control.exchange([("shutdown", None, None, None)])

@@ -312,3 +312,18 @@ def test_rollback_to_a_ring_snapshot_resumes_exactly(model):
     assert first is not None and final
     assert final[0].output_ids[:14] == first
     assert len(final[0].output_ids) == 24
+
+
+def test_close_is_ordered_idempotent_and_final(tmp_path):
+    from metrale_inference_alpha_b200.scheduler.types import FatalDeviceError
+    eng = LLMEngine(EngineArgs(model="tiny-dense", max_model_len=256, num_kv_blocks=32, kv_tier_blocks=8, kv_tier_dir=str(tmp_path / "t")))
+    eng.generate([[5, 6, 7, 8] * 6], SamplingParams(max_tokens=3, temperature=0.0))
+    rid = eng.add_request([1, 2, 3], SamplingParams(max_tokens=50))
+    used = eng.runner.kv.allocator.num_free
+    eng.close()
+    eng.close()
+    assert not eng.scheduler.has_work() and eng.kv_tier.backend._fds == []
+    assert eng.runner.kv.allocator.num_free >= used            # the prefix tree gave its blocks back
+    with pytest.raises(FatalDeviceError):
+        eng.add_request([1, 2, 3])
+    assert rid
