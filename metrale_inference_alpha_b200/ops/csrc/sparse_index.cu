@@ -14,6 +14,7 @@
 // selection expansion, compaction) and the sparse decode of glm5next_dsa_mla_decode.cu; there the
 // candidates are pools of tokens, here single tokens (the DeepSeek sparse-attention form).
 #include "common.cuh"
+#include <cstdlib>
 
 namespace {
 
@@ -105,6 +106,100 @@ index_score_kernel(const __nv_bfloat16* __restrict__ iq, const float* __restrict
   if (part == 0) {
     if (pos0 < ld) scores[(size_t)t * ld + pos0] = pos0 < ctx ? acc0 : -INFINITY;
     if (pos1 < ld) scores[(size_t)t * ld + pos1] = pos1 < ctx ? acc1 : -INFINITY;
+  }
+}
+
+// Tensor-core form for the common indexer shape (a multiple of 16 heads, up to 64; 128 channels): the score is
+// a [heads x 128] by [128 x keys] product followed by ReLU, the head weights and a sum over heads. One warp keeps
+// the whole query as m16n8k16 A fragments in registers (loaded once, straight from global memory) and walks
+// tiles of eight keys; the B fragments are the keys' own rows, read from the paged cache as 32-bit pairs in the
+// fragment layout (lane = (key, channel pair)), so nothing is staged in shared memory. The epilogue applies
+// ReLU and the head weights on the accumulators and reduces over heads with three shuffles.
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kTcWarps = 4;          // keys per CTA = 4 warps x tiles per warp (launcher's choice) x 8
+
+template <int MT>                                          // MT head tiles of 16
+__global__ void __launch_bounds__(kTcWarps * 32)
+index_score_tc_kernel(const __nv_bfloat16* __restrict__ iq, const float* __restrict__ iw,
+                      const __nv_bfloat16* __restrict__ kc, const int* __restrict__ block_table, int max_blocks,
+                      const int* __restrict__ row_seq, const int* __restrict__ row_ctx, float* __restrict__ scores,
+                      long long ld, int block_size, long long num_blocks, int tiles_per_warp, uint32_t* status) {
+  constexpr int DI = 128, KS = DI / 16, Hi = MT * 16;
+  const int t = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = lane >> 2, c = lane & 3;
+  const int ctx = row_ctx[t];
+  const int key0 = (blockIdx.x * kTcWarps + warp) * tiles_per_warp * 8;
+  if (key0 >= ld) return;
+  if (key0 >= ctx) {                                         // nothing of this warp's span is visible
+    for (int i = lane; i < tiles_per_warp * 8; i += 32)
+      if (key0 + i < ld) scores[(size_t)t * ld + key0 + i] = -INFINITY;
+    return;
+  }
+  // A fragments of the whole query: a[mt][ks] = rows (mt*16 + r, + 8), channel pairs (ks*16 + 2c, + 8)
+  uint32_t a[MT][KS][4];
+  const uint32_t* q32 = reinterpret_cast<const uint32_t*>(iq + (size_t)t * Hi * DI);
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int row = mt * 16 + r, col = ks * 16 + 2 * c;
+      a[mt][ks][0] = q32[(row * DI + col) >> 1];
+      a[mt][ks][1] = q32[((row + 8) * DI + col) >> 1];
+      a[mt][ks][2] = q32[(row * DI + col + 8) >> 1];
+      a[mt][ks][3] = q32[((row + 8) * DI + col + 8) >> 1];
+    }
+  float w_lo[MT], w_hi[MT];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    w_lo[mt] = iw[(size_t)t * Hi + mt * 16 + r];
+    w_hi[mt] = iw[(size_t)t * Hi + mt * 16 + r + 8];
+  }
+  const int seq = row_seq[t];
+  for (int nt = 0; nt < tiles_per_warp; ++nt) {
+    const int base = key0 + nt * 8;
+    if (base >= ld) break;
+    const int pos = base + r;                                // this lane's key (the fragment's column)
+    const uint32_t* krow = nullptr;
+    if (pos < ctx) {
+      const int blk = block_table[(size_t)seq * max_blocks + pos / block_size];
+      if (blk < 0 || blk >= num_blocks) {
+        if (status) atomicCAS(status, 0u, MB_ST_BOUNDS);
+      } else {
+        krow = reinterpret_cast<const uint32_t*>(kc + ((size_t)blk * block_size + pos % block_size) * DI);
+      }
+    }
+    uint32_t b[KS][2];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      b[ks][0] = krow ? krow[(ks * 16 + 2 * c) >> 1] : 0u;
+      b[ks][1] = krow ? krow[(ks * 16 + 2 * c + 8) >> 1] : 0u;
+    }
+    float s0 = 0.f, s1 = 0.f;                                // keys base + 2c and base + 2c + 1, this lane's head rows
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) mma_bf16_16816(acc, a[mt][ks], b[ks][0], b[ks][1]);
+      s0 += w_lo[mt] * fmaxf(acc[0], 0.f) + w_hi[mt] * fmaxf(acc[2], 0.f);
+      s1 += w_lo[mt] * fmaxf(acc[1], 0.f) + w_hi[mt] * fmaxf(acc[3], 0.f);
+    }
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {                 // over the eight head rows a lane group holds
+      s0 += __shfl_xor_sync(0xffffffffu, s0, off);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, off);
+    }
+    if (r == 0) {
+      const int p0 = base + 2 * c, p1 = p0 + 1;
+      if (p0 < ld) scores[(size_t)t * ld + p0] = p0 < ctx ? s0 : -INFINITY;
+      if (p1 < ld) scores[(size_t)t * ld + p1] = p1 < ctx ? s1 : -INFINITY;
+    }
   }
 }
 
@@ -271,6 +366,14 @@ gather_rows_kernel(const uint4* __restrict__ cache, const int* __restrict__ bloc
 
 }  // namespace
 
+static bool tc_off() {
+  static const bool off = [] {
+    const char* e = getenv("METRALE_INDEX_TC");
+    return e && e[0] == '0';
+  }();
+  return off;
+}
+
 extern "C" int mb_index_score(const void* iq, const void* iw, const void* kc, const void* block_table, int max_blocks,
                               const void* row_seq, const void* row_ctx, void* scores, long long ld, int T, int Hi,
                               int Di, int block_size, long long num_blocks, void* status, cudaStream_t stream) {
@@ -288,6 +391,26 @@ extern "C" int mb_index_score(const void* iq, const void* iw, const void* kc, co
       static_cast<const int*>(block_table), max_blocks, static_cast<const int*>(row_seq),                        \
       static_cast<const int*>(row_ctx), static_cast<float*>(scores), ld, Hi, block_size, num_blocks,             \
       static_cast<uint32_t*>(status))
+  if (Di == 128 && Hi % 16 == 0 && Hi <= 64 && !(tc_off())) {
+    // 16 key tiles per warp amortise the query fragments best; fewer when that would leave SMs idle
+    int tpw = 16;
+    while (tpw > 2 && (long long)T * ((ld + kTcWarps * tpw * 8 - 1) / (kTcWarps * tpw * 8)) < 2 * 148) tpw >>= 1;
+    const dim3 g2((unsigned)((ld + kTcWarps * tpw * 8 - 1) / (kTcWarps * tpw * 8)), T);
+#define MB_IDX_TC(MT)                                                                                              \
+  index_score_tc_kernel<MT><<<g2, kTcWarps * 32, 0, stream>>>(                                                     \
+      static_cast<const __nv_bfloat16*>(iq), static_cast<const float*>(iw), static_cast<const __nv_bfloat16*>(kc), \
+      static_cast<const int*>(block_table), max_blocks, static_cast<const int*>(row_seq),                          \
+      static_cast<const int*>(row_ctx), static_cast<float*>(scores), ld, block_size, num_blocks, tpw,              \
+      static_cast<uint32_t*>(status))
+    switch (Hi / 16) {
+      case 1: MB_IDX_TC(1); break;
+      case 2: MB_IDX_TC(2); break;
+      case 3: MB_IDX_TC(3); break;
+      default: MB_IDX_TC(4); break;
+    }
+#undef MB_IDX_TC
+    return (int)cudaGetLastError();
+  }
   if (Di == 128) MB_IDX_LAUNCH(128);
   else if (Di == 64) MB_IDX_LAUNCH(64);
   else return MB_ERR_UNSUPPORTED;

@@ -24,7 +24,6 @@
 namespace {
 
 constexpr int kMaxG = 8;          // query heads per kv head
-constexpr int kTileWarps = 4;
 
 __device__ __forceinline__ float e4m3_to_f(uint8_t b) {
   __nv_fp8_e4m3 v;
@@ -89,9 +88,13 @@ struct TileArgs {
   float scale, k_scale, v_scale;
 };
 
+template <int D>
+constexpr int tile_warps() { return D == 128 ? 8 : 4; }        // the merge buffer o_s must stay under 48 KB
+
 template <int D, bool FP8>
-__global__ void __launch_bounds__(kTileWarps * 32) kv_tile_attn_kernel(const TileArgs a) {
+__global__ void __launch_bounds__(tile_warps<D>() * 32) kv_tile_attn_kernel(const TileArgs a) {
   constexpr int EPL = D / 32;
+  constexpr int kTileWarps = tile_warps<D>();
   const int kh = blockIdx.x, seq = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = a.Hq / a.Hkv;
@@ -125,13 +128,25 @@ __global__ void __launch_bounds__(kTileWarps * 32) kv_tile_attn_kernel(const Til
     lv = lv < a.block_size ? (lv < 0 ? 0 : lv) : a.block_size;
     ntok = (nblk - 1) * a.block_size + lv;
   }
-  for (int t = warp; t < ntok; t += kTileWarps) {
+  // the next token's K / V rows are fetched before the current token is folded in, so the global-load latency
+  // overlaps the dot products and shuffles of the previous token
+  auto fetch = [&](int t, float (&kv)[EPL], float (&vv)[EPL]) {
     const int b = t / a.block_size, slot = t - b * a.block_size;
     const long long blk = a.tile_blocks[(size_t)seq * a.cap + b];
     const size_t at = (size_t)(blk * a.blk_stride + slot * a.tok_stride + kh * a.kvh_stride) + lane * EPL;
-    float kv[EPL], vv[EPL];
     load_row<EPL, FP8>(a.k_pool, at, a.k_scale, kv);
     load_row<EPL, FP8>(a.v_pool, at, a.v_scale, vv);
+  };
+  float kn[EPL], vn[EPL];
+  if (warp < ntok) fetch(warp, kn, vn);
+  for (int t = warp; t < ntok; t += kTileWarps) {
+    float kv[EPL], vv[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      kv[e] = kn[e];
+      vv[e] = vn[e];
+    }
+    if (t + kTileWarps < ntok) fetch(t + kTileWarps, kn, vn);
 #pragma unroll
     for (int g = 0; g < kMaxG; ++g) {
       if (g < G) {
@@ -343,13 +358,13 @@ extern "C" int mb_kv_tile_attn(const MbKvTileArgs* p, cudaStream_t stream) {
              static_cast<float*>(p->l_state), static_cast<float*>(p->o_state),
              static_cast<__nv_bfloat16*>(p->out), p->Hq, p->Hkv, p->block_size, p->cap,
              p->blk_stride, p->tok_stride, p->kvh_stride, p->scale, p->k_scale, p->v_scale};
-  const dim3 grid(p->Hkv, p->num_seqs), block(kTileWarps * 32);
+  const dim3 grid(p->Hkv, p->num_seqs);
   if (p->D == 128) {
-    if (p->kv_fp8) kv_tile_attn_kernel<128, true><<<grid, block, 0, stream>>>(a);
-    else kv_tile_attn_kernel<128, false><<<grid, block, 0, stream>>>(a);
+    if (p->kv_fp8) kv_tile_attn_kernel<128, true><<<grid, tile_warps<128>() * 32, 0, stream>>>(a);
+    else kv_tile_attn_kernel<128, false><<<grid, tile_warps<128>() * 32, 0, stream>>>(a);
   } else {
-    if (p->kv_fp8) kv_tile_attn_kernel<256, true><<<grid, block, 0, stream>>>(a);
-    else kv_tile_attn_kernel<256, false><<<grid, block, 0, stream>>>(a);
+    if (p->kv_fp8) kv_tile_attn_kernel<256, true><<<grid, tile_warps<256>() * 32, 0, stream>>>(a);
+    else kv_tile_attn_kernel<256, false><<<grid, tile_warps<256>() * 32, 0, stream>>>(a);
   }
   return (int)cudaGetLastError();
 }
