@@ -105,14 +105,62 @@ def storage(rows):
         rows.append({"op": f"kv_tile_attn (8 seqs x 4096 tokens, 40 / 8 heads, {'e4m3' if fp8 else 'bf16'})", "us": t * 1e6, "gbs": byt / t / 1e9})
 
 
+def moe_nvfp4(rows):
+    """Routed NVFP4 (W4A4) experts of a 128-expert, top-8 block (hidden 2048, expert width 768): the grouped
+    tcgen05 GEMM over 128-row aligned expert segments against one GEMM per active expert."""
+    from types import SimpleNamespace
+
+    from kernel_bench import rand_weight
+    from metrale_inference_alpha_b200 import ops
+    from metrale_inference_alpha_b200.models.decoder import Decoder
+    from metrale_inference_alpha_b200.models.moe import routed_experts
+    from metrale_inference_alpha_b200.ops.moe import stack_experts
+    from metrale_inference_alpha_b200.weights.loader import FfnW, MoeW
+    E, K, H, I = 128, 8, 2048, 768
+    experts = [FfnW(rand_weight(2 * I, H, "nvfp4", 1)[0], rand_weight(H, I, "nvfp4", 1)[0], interleaved=True) for _ in range(E)]
+    w = MoeW(experts=experts, expert_lo=0)
+    w.grouped = stack_experts(experts)
+    cfg = SimpleNamespace(experts_per_token=K, ffn_act="swiglu", hidden_size=H, num_experts=E)
+    dec = SimpleNamespace(cfg=cfg, _as_act=Decoder._as_act)
+    g = torch.Generator(device=DEV).manual_seed(5)
+    wbytes = sum(e.gate_up.nbytes() + e.down.nbytes() for e in experts) / E
+    for T in (64, 2048):
+        x = torch.randn(T, H, device=DEV, generator=g).to(torch.bfloat16)
+        a = ops.row_op(x, "nvfp4", also_bf16=True)[0]
+        idx = torch.stack([torch.randperm(E, device=DEV, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+        wts = torch.rand(T, K, device=DEV, generator=g)
+        active = int(idx.unique().numel())
+        flops = 2.0 * T * K * (2 * I * H + H * I)
+        t_g = timeit(lambda i: routed_experts(dec, a, wts, idx, w), iters=10)
+        grouped, w.grouped = w.grouped, None
+        try:
+            for _ in range(2):
+                routed_experts(dec, a, wts, idx, w)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                routed_experts(dec, a, wts, idx, w)
+            e1.record()
+            torch.cuda.synchronize()
+            t_e = e0.elapsed_time(e1) / 3 * 1e-3
+        finally:
+            w.grouped = grouped
+        for name, t in (("grouped GEMM, graph replay", t_g), ("one GEMM per active expert, eager", t_e)):
+            rows.append({"op": f"nvfp4 experts ({T} tokens x top-8 of 128, {active} active; {name})", "us": t * 1e6,
+                         "gbs": active * wbytes / t / 1e9, "tflops": flops / t / 1e12})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
+    ap.add_argument("--only", default=None, help="run one section: kda | sparse | highway | storage | moe_nvfp4")
     ns = ap.parse_args()
     hbm, _, tag = peaks()
     rows = []
-    for f in (kda, sparse, highway, storage):
-        f(rows)
+    for f in (kda, sparse, highway, storage, moe_nvfp4):
+        if ns.only in (None, f.__name__):
+            f(rows)
     for r in rows:
         r["frac_hbm"] = r["gbs"] / hbm
         extra = f", {r['tflops']:.1f} TFLOP/s" if "tflops" in r else ""

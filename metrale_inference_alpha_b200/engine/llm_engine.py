@@ -136,9 +136,10 @@ class LLMEngine:
         import os as _os
         self._redzone_every = int(_os.environ.get("METRALE_REDZONE_EVERY", "0") or 0)
         if (cfg.num_experts > 0 and cfg.weight_format == "nvfp4" and torch.device(args.device).type == "cuda"
-                and args.use_cuda_graphs):
-            # NVFP4 experts run one GEMM per active expert, chosen on the host from the step's routing:
-            # such a step cannot be replayed from a graph
+                and args.use_cuda_graphs
+                and any(getattr(getattr(L, "ffn", None), "experts", None) and L.ffn.grouped is None for L in self.weights.layers)):
+            # NVFP4 experts whose row count is not a multiple of the 128-row scale-factor tile run one GEMM per
+            # active expert, chosen on the host from the step's routing: such a step cannot be replayed from a graph
             args.use_cuda_graphs = False
         self.paged_experts = None
         if args.expert_arena_slots > 0:

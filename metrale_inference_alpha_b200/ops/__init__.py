@@ -231,12 +231,14 @@ def row_op(x: torch.Tensor, out_fmt: str = "bf16", mode: int = IN_COPY, *, K: Op
            residual=None, write_residual: bool = False, w=None, plus_one: bool = False,
            eps: float = 1e-6, gate=None, head_dim: int = 0, gate_head_stride: int = 0,
            gate_head_off: int = 0, group: int = 0, also_bf16: bool = False, static_scale: float = 0.0,
-           scale_pad: int = 0):
+           scale_pad: int = 0, row_index: Optional[torch.Tensor] = None):
     """Fused producer: builds y = recipe(x) per row and encodes it as `out_fmt`. `static_scale`
     (nvfp4 only): calibrated global scale used instead of the row's amax / (6 * 448).
     `scale_pad` (fp8_g128): extra token columns in the per-group scale matrix (grouped expert GEMMs
-    read whole row tiles past the last row). Returns (Act, residual_out or None). x is bf16 (or
-    fp32 for IN_GATED_RMSNORM inputs)."""
+    read whole row tiles past the last row). `row_index` (CUDA): int32 list of the rows to work on
+    (negative entries are skipped); the other rows' outputs stay unwritten (an expert-sorted layout with
+    aligned tiles is mostly padding). Returns (Act,
+    residual_out or None). x is bf16 (or fp32 for IN_GATED_RMSNORM inputs)."""
     M = x.shape[0]
     if K is None:
         K = x.shape[1] // 2 if mode == IN_SILU_MUL else x.shape[1]
@@ -247,7 +249,8 @@ def row_op(x: torch.Tensor, out_fmt: str = "bf16", mode: int = IN_COPY, *, K: Op
     dev = x.device
     a = _native.RowArgs()
     a.static_gs = float(static_scale) if out_fmt == "nvfp4" else 0.0
-    a.M, a.K, a.in_mode, a.out_mode = M, K, mode, OUT_MODE[out_fmt]
+    a.row_index = _ptr(row_index)
+    a.M, a.K, a.in_mode, a.out_mode = (M if row_index is None else row_index.numel()), K, mode, OUT_MODE[out_fmt]
     if x.dtype == torch.float32:
         a.xf32 = _ptr(x)
     else:

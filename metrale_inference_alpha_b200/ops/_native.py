@@ -42,6 +42,7 @@ class RowArgs(C.Structure):
         ("xf32", c_void_p), ("out", c_void_p), ("out_ld", c_ll),
         ("out_bf16", c_void_p), ("out_bf16_ld", c_ll),
         ("scale", c_void_p), ("scale_ld", c_int), ("sf", c_void_p), ("sf_k64", c_int), ("static_gs", c_float),
+        ("row_index", c_void_p),
     ]
 
 

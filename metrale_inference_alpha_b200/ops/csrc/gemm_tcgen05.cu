@@ -202,13 +202,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int s = i % kStages, kb = kb0 + i;
         mb::tma_load_2d(sA(s), &tmA, &full_bar[s], kb * kCoordStep, w_row0);
         if (sf_load)
-          mb::bulk_load(sSFA(s), p.sfa + ((size_t)tile_n * p.sf_k64 + (size_t)kb * 4) * 512, 2048, &full_bar[s]);
+          mb::bulk_load(sSFA(s), p.sfa + ((size_t)(w_row0 / kTileN) * p.sf_k64 + (size_t)kb * 4) * 512, 2048, &full_bar[s]);
       };
       auto load_x = [&](int i) {                   // activation tile + its scale factors
         const int s = i % kStages, kb = kb0 + i;
         mb::tma_load_2d(sB(s), &tmB, &full_bar[s], kb * kCoordStep, m_row0);
         if (sf_load)
-          mb::bulk_load(sSFB(s), p.sfb + ((size_t)((tile_m * TN) / 128) * p.sf_k64 + (size_t)kb * 4) * 512, 2048,
+          mb::bulk_load(sSFB(s), p.sfb + ((size_t)(m_row0 / 128) * p.sf_k64 + (size_t)kb * 4) * 512, 2048,
                         &full_bar[s]);
       };
       const int pre = min(nkb, kStages);           // the first round needs no empty-slot wait
@@ -972,16 +972,23 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
   const bool grouped = a->tile_expert != nullptr;
   if (grouped) {
     if (!a->tile_row0 || !a->tile_nrows || a->n_per_expert <= 0 || a->n_per_expert % kTileN ||
-        a->max_tiles <= 0 || kind == KIND_NVFP4)
+        a->max_tiles <= 0)
       return MB_ERR_UNSUPPORTED;
-    if (tn > 64) tn = 64;
+    // NVFP4 scale factors come in blocks of 128 rows: every tile of the work list must start at a multiple
+    // of 128 rows (the sort lays the tiles out that way) and takes the first force_tn rows of its block
+    if (kind == KIND_NVFP4) {
+      if ((a->force_tn != 16 && a->force_tn != 32 && a->force_tn != 64 && a->force_tn != 128) || a->M % 128)
+        return MB_ERR_UNSUPPORTED;
+    } else if (tn > 64) {
+      tn = 64;
+    }
   }
   const int tiles_n = grouped ? a->n_per_expert / kTileN : (a->N + kTileN - 1) / kTileN;
   const int tiles_m = grouped ? a->max_tiles : (a->M + tn - 1) / tn;
   if (kind == KIND_FP8_BLOCK && !grouped && a->a_ld < tiles_m * tn) return MB_ERR_BAD_ARG;
   if (kind == KIND_FP8_BLOCK && grouped && a->a_ld < a->M + tn) return MB_ERR_BAD_ARG;
   // scale-factor tiles are 128 rows: several token tiles only line up at TN = 128
-  if (kind == KIND_NVFP4 && tiles_m > 1 && tn != 128) return MB_ERR_BAD_ARG;
+  if (kind == KIND_NVFP4 && !grouped && tiles_m > 1 && tn != 128) return MB_ERR_BAD_ARG;
   const int tiles = tiles_n * tiles_m;
   const int sms = a->sm_count > 0 ? a->sm_count : 148;
   int splits = a->force_splits;

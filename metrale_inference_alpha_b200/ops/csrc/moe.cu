@@ -154,9 +154,13 @@ route_kernel(const float* __restrict__ logits, long long ld, int T, int E, int K
 
 // ------------------------------------------------------------------ sort (single CTA)
 // pairs = T * K. counts / offsets in shared memory; rows of one expert are independent, so their
-// order inside the expert's range is free.
+// order inside the expert's range is free. With align > 1 every *tile* starts at a multiple of `align`
+// rows and holds at most tile_rows (<= align) pairs in its first rows (NVFP4 operands carry their scale
+// factors in blocks of 128 rows, and a token tile must start on such a block): pair i of an expert sits at
+// row off[e] + (i / tile_rows) * align + i % tile_rows. Every row of [0, row_cap) that holds no pair gets
+// row_pair = -1 (nothing is gathered or computed for it); *total_rows is the end of the last tile's slot.
 __global__ void __launch_bounds__(1024)
-sort_kernel(const int* __restrict__ ids, int pairs, int expert_lo, int num_local, int tile_rows,
+sort_kernel(const int* __restrict__ ids, int pairs, int expert_lo, int num_local, int tile_rows, int align, int row_cap,
             int* __restrict__ pair_row, int* __restrict__ row_pair, int* __restrict__ expert_off,
             int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ tile_nrows,
             int max_tiles, int* __restrict__ total_rows) {
@@ -171,22 +175,51 @@ sort_kernel(const int* __restrict__ ids, int pairs, int expert_lo, int num_local
     if (e >= 0 && e < num_local) atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
-  if (tid == 0) {
-    int acc = 0, tiles = 0;
-    for (int e = 0; e < num_local; ++e) {
-      off[e] = acc;
-      const int c = cnt[e];
-      for (int r = 0; r < c && tiles < max_tiles; r += tile_rows) {
-        tile_expert[tiles] = e;
-        tile_row0[tiles] = acc + r;
-        tile_nrows[tiles] = min(tile_rows, c - r);
-        ++tiles;
-      }
-      acc += c;
+  // offsets and the tile work-list: thread e owns expert e (num_local <= blockDim.x = 1024); an exclusive block
+  // scan over (rows, tiles) of the experts replaces a walk over the experts by one thread
+  __shared__ int wsum[2][32];
+  __shared__ int tot[2];
+  {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int c = tid < num_local ? cnt[tid] : 0;
+    const int my_tiles = (c + tile_rows - 1) / tile_rows;
+    const int my_rows = align > 1 ? my_tiles * align : c;
+    int sr = my_rows, st = my_tiles;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int ur = __shfl_up_sync(0xffffffffu, sr, d), ut = __shfl_up_sync(0xffffffffu, st, d);
+      if (lane >= d) { sr += ur; st += ut; }
     }
-    off[num_local] = acc;
-    for (int i = tiles; i < max_tiles; ++i) { tile_expert[i] = -1; tile_row0[i] = 0; tile_nrows[i] = 0; }
-    *total_rows = acc;
+    if (lane == 31) { wsum[0][warp] = sr; wsum[1][warp] = st; }
+    __syncthreads();
+    if (warp == 0) {
+      const int wr = wsum[0][lane], wt = wsum[1][lane];
+      int ir = wr, it = wt;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int ur = __shfl_up_sync(0xffffffffu, ir, d), ut = __shfl_up_sync(0xffffffffu, it, d);
+        if (lane >= d) { ir += ur; it += ut; }
+      }
+      wsum[0][lane] = ir - wr;                                   // rows / tiles in front of this warp
+      wsum[1][lane] = it - wt;
+      if (lane == 31) { tot[0] = ir; tot[1] = it; }
+    }
+    __syncthreads();
+    const int row_base = wsum[0][warp] + sr - my_rows, tile_base = wsum[1][warp] + st - my_tiles;
+    if (tid < num_local) {
+      off[tid] = row_base;
+      const int stride = align > 1 ? align : tile_rows;
+      for (int j = 0; j < my_tiles && tile_base + j < max_tiles; ++j) {
+        tile_expert[tile_base + j] = tid;
+        tile_row0[tile_base + j] = row_base + j * stride;
+        tile_nrows[tile_base + j] = min(tile_rows, c - j * tile_rows);
+      }
+    }
+    if (tid == 0) { off[num_local] = tot[0]; *total_rows = tot[0]; }
+    for (int i = tot[1] + tid; i < max_tiles; i += nt) { tile_expert[i] = -1; tile_row0[i] = 0; tile_nrows[i] = 0; }
+    // rows that end up without a pair keep this -1 (the placement below overwrites the others)
+    if (align > 1)
+      for (int r = tid; r < row_cap; r += nt) row_pair[r] = -1;
   }
   __syncthreads();
   for (int e = tid; e <= num_local; e += nt) expert_off[e] = off[e];
@@ -199,7 +232,8 @@ sort_kernel(const int* __restrict__ ids, int pairs, int expert_lo, int num_local
   for (int i = tid; i < pairs; i += nt) {
     const int e = ids[i] - expert_lo;
     if (e >= 0 && e < num_local) {
-      const int pos = off[e] + atomicAdd(&cnt[e], 1);
+      const int k = atomicAdd(&cnt[e], 1);
+      const int pos = off[e] + (align > 1 ? (k / tile_rows) * align + k % tile_rows : k);
       pair_row[i] = pos;
       row_pair[pos] = i;
     }
@@ -219,15 +253,39 @@ __global__ void gather_kernel(const uint8_t* __restrict__ src, long long src_ld,
                               int scale_groups, int src_scale_ld, int dst_scale_ld) {
   const int r = blockIdx.x;
   if (r >= *total_rows || r >= max_rows) return;
-  const int tok = row_pair[r] / K;
-  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)tok * src_ld);
+  const int pr = row_pair[r];
   uint4* d = reinterpret_cast<uint4*>(dst + (size_t)r * dst_ld);
+  if (pr < 0) return;                             // padding up to the next expert's aligned first row
+  const int tok = pr / K;
+  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)tok * src_ld);
   for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) d[i] = s[i];
   if (src_scale) {
     // scales stored [group][row]
     for (int gI = threadIdx.x; gI < scale_groups; gI += blockDim.x)
       dst_scale[(size_t)gI * dst_scale_ld + r] = src_scale[(size_t)gI * src_scale_ld + tok];
   }
+}
+
+// NVFP4 activations, one CTA per (token, slot) pair: the pair's sorted row takes the token's packed e2m1
+// row, its per-token scale and its scale-factor bytes. The scale factors live in 512-byte tiles of 128 rows x
+// 4 groups of 16 channels (the layout tcgen05.cp consumes); the four bytes of one row and one 64-channel
+// group are one aligned word, moved from the token's tile to the sorted row's tile. Rows that hold no pair
+// are left as they are: the GEMM computes their output columns from whatever they hold and stores none.
+__global__ void gather_nvfp4_kernel(const uint8_t* __restrict__ src, long long src_ld, uint8_t* __restrict__ dst,
+                                    long long dst_ld, int row_bytes, const int* __restrict__ pair_row, int K,
+                                    int max_rows, const float* __restrict__ src_scale, float* __restrict__ dst_scale,
+                                    const uint8_t* __restrict__ src_sf, uint8_t* __restrict__ dst_sf, int sf_k64) {
+  const int r = pair_row[blockIdx.x];
+  if (r < 0 || r >= max_rows) return;
+  const int tok = blockIdx.x / K;
+  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)tok * src_ld);
+  uint4* d = reinterpret_cast<uint4*>(dst + (size_t)r * dst_ld);
+  for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) d[i] = s[i];
+  if (threadIdx.x == 0) dst_scale[r] = src_scale[tok];
+  const uint8_t* sfs = src_sf + (size_t)(tok >> 7) * sf_k64 * 512 + mb::sf_tile_offset(tok & 127, 0);
+  uint8_t* sfd = dst_sf + (size_t)(r >> 7) * sf_k64 * 512 + mb::sf_tile_offset(r & 127, 0);
+  for (int g = threadIdx.x; g < sf_k64; g += blockDim.x)
+    *reinterpret_cast<uint32_t*>(sfd + (size_t)g * 512) = *reinterpret_cast<const uint32_t*>(sfs + (size_t)g * 512);
 }
 
 __global__ void combine_kernel(const float* __restrict__ y, long long y_ld, const int* __restrict__ pair_row,
@@ -326,14 +384,24 @@ int mb_moe_route_shared(const float* logits, long long ld, int T, int E, int K, 
   return (int)cudaGetLastError();
 }
 
+// `align` > 1: every tile starts at a multiple of `align` rows; row_pair has `row_cap` entries
+// (>= max_tiles * align covers every routing); tile_rows must divide `align`.
+int mb_moe_sort_aligned(const int* ids, int pairs, int expert_lo, int num_local, int tile_rows, int align, int row_cap,
+                        int* pair_row, int* row_pair, int* expert_off, int* tile_expert, int* tile_row0,
+                        int* tile_nrows, int max_tiles, int* total_rows, cudaStream_t stream) {
+  if (!ids || pairs <= 0 || num_local <= 0 || num_local > 1024 || tile_rows <= 0 || align <= 0 || (align > 1 && (align % tile_rows || row_cap < pairs)))
+    return MB_ERR_BAD_ARG;
+  const size_t smem = (2 * (size_t)num_local + 1) * sizeof(int);
+  sort_kernel<<<1, 1024, smem, stream>>>(ids, pairs, expert_lo, num_local, tile_rows, align, row_cap, pair_row, row_pair,
+                                         expert_off, tile_expert, tile_row0, tile_nrows, max_tiles, total_rows);
+  return (int)cudaGetLastError();
+}
+
 int mb_moe_sort(const int* ids, int pairs, int expert_lo, int num_local, int tile_rows, int* pair_row,
                 int* row_pair, int* expert_off, int* tile_expert, int* tile_row0, int* tile_nrows,
                 int max_tiles, int* total_rows, cudaStream_t stream) {
-  if (!ids || pairs <= 0 || num_local <= 0 || num_local > 1024 || tile_rows <= 0) return MB_ERR_BAD_ARG;
-  const size_t smem = (2 * (size_t)num_local + 1) * sizeof(int);
-  sort_kernel<<<1, 1024, smem, stream>>>(ids, pairs, expert_lo, num_local, tile_rows, pair_row, row_pair,
-                                         expert_off, tile_expert, tile_row0, tile_nrows, max_tiles, total_rows);
-  return (int)cudaGetLastError();
+  return mb_moe_sort_aligned(ids, pairs, expert_lo, num_local, tile_rows, 1, pairs, pair_row, row_pair, expert_off,
+                             tile_expert, tile_row0, tile_nrows, max_tiles, total_rows, stream);
 }
 
 int mb_moe_gather(const void* src, long long src_ld, void* dst, long long dst_ld, int row_bytes,
@@ -345,6 +413,20 @@ int mb_moe_gather(const void* src, long long src_ld, void* dst, long long dst_ld
                                               reinterpret_cast<uint8_t*>(dst), dst_ld, row_bytes, row_pair, K,
                                               total_rows, max_rows, src_scale, dst_scale, scale_groups,
                                               src_scale_ld, dst_scale_ld);
+  return (int)cudaGetLastError();
+}
+
+int mb_moe_gather_nvfp4(const void* src, long long src_ld, void* dst, long long dst_ld, int row_bytes,
+                        const int* pair_row, int pairs, int K, int max_rows, const float* src_scale,
+                        float* dst_scale, const void* src_sf, void* dst_sf, int sf_k64, cudaStream_t stream) {
+  if (!src || !dst || !pair_row || !src_scale || !dst_scale || !src_sf || !dst_sf || sf_k64 <= 0 || row_bytes % 16 ||
+      pairs <= 0 || K <= 0 || max_rows <= 0)
+    return MB_ERR_BAD_ARG;
+  gather_nvfp4_kernel<<<pairs, 64, 0, stream>>>(reinterpret_cast<const uint8_t*>(src), src_ld,
+                                                reinterpret_cast<uint8_t*>(dst), dst_ld, row_bytes, pair_row, K,
+                                                max_rows, src_scale, dst_scale,
+                                                reinterpret_cast<const uint8_t*>(src_sf),
+                                                reinterpret_cast<uint8_t*>(dst_sf), sf_k64);
   return (int)cudaGetLastError();
 }
 

@@ -57,6 +57,7 @@ struct RowParams {
   uint8_t* sf;                        // OUT_NVFP4 tiled scale factors
   int sf_k64;
   float static_gs;                    // OUT_NVFP4: > 0 = calibrated global scale instead of the row's amax / (6 * 448)
+  const int* row_index;               // optional [M]: CTA i works on row row_index[i] (negative: none) instead of row i
 };
 
 __device__ __forceinline__ float load_x(const RowParams& p, int m, int k) {
@@ -67,11 +68,12 @@ __device__ __forceinline__ float load_x(const RowParams& p, int m, int k) {
 __global__ void __launch_bounds__(512) row_kernel(const RowParams p) {
   extern __shared__ float row[];
   __shared__ float red[32];
-  const int m = blockIdx.x;
   const int K = p.K;
   const int tid = threadIdx.x, nt = blockDim.x;
   mb::pdl_wait();
   mb::pdl_launch_dependents();
+  const int m = p.row_index ? p.row_index[blockIdx.x] : (int)blockIdx.x;
+  if (m < 0) return;
 
   // ---- stage 1: build the fp32 row
   if (p.in_mode == IN_RMSNORM) {
@@ -215,10 +217,12 @@ __global__ void __launch_bounds__(512) row_kernel(const RowParams p) {
 template <int BPT>
 __global__ void __launch_bounds__(1024) row_kernel_v2(const RowParams p) {
   __shared__ float red[64];
-  const int m = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+  const int tid = threadIdx.x, nt = blockDim.x;
   const int K = p.K, nblk = K >> 4;
   mb::pdl_wait();
   mb::pdl_launch_dependents();
+  const int m = p.row_index ? p.row_index[blockIdx.x] : (int)blockIdx.x;
+  if (m < 0) return;
   float x[BPT][16];
   float ss = 0.f, mx = 0.f;
   const bool norm = p.in_mode == IN_RMSNORM;
@@ -464,6 +468,7 @@ struct MbRowArgs {
   void* sf;
   int sf_k64;
   float static_gs;
+  const int* row_index;
 };
 
 int mb_row_op(const MbRowArgs* a, cudaStream_t stream) {
@@ -490,6 +495,7 @@ int mb_row_op(const MbRowArgs* a, cudaStream_t stream) {
   p.scale = a->scale; p.scale_ld = a->scale_ld;
   p.sf = reinterpret_cast<uint8_t*>(a->sf); p.sf_k64 = a->sf_k64;
   p.static_gs = a->static_gs;
+  p.row_index = a->row_index;
   {
     // fast path eligibility: bf16 input, whole 16-element blocks, 16-byte aligned vectors
     const bool modes = p.in_mode == IN_COPY || p.in_mode == IN_RMSNORM || p.in_mode == IN_SILU_MUL;

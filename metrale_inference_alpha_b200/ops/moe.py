@@ -34,13 +34,17 @@ def stack_experts(experts) -> Optional[GroupedExperts]:
     if not experts:
         return None
     from . import concat_weights
-    if experts[0].gate_up.fmt == "nvfp4":
-        # the grouped GEMM takes token tiles of 16 - 64 rows at arbitrary row offsets, while the scale
-        # factors of an NVFP4 operand are tiled by 128 rows: NVFP4 experts run one GEMM per active expert
+    nvfp4 = experts[0].gate_up.fmt == "nvfp4"
+    if nvfp4 and (experts[0].gate_up.N % 128 or experts[0].down.N % 128):
+        # the scale factors of an NVFP4 operand are tiled by 128 rows: an expert whose row count is not a
+        # multiple of that shares a tile with its neighbour, and such experts run one GEMM per active expert
         # (models/moe.py::routed_experts) instead of the grouped path
         return None
     gu = concat_weights([e.gate_up for e in experts])
     dn = concat_weights([e.down for e in experts])
+    if nvfp4 and gu.data.is_cuda:
+        gu.prepare_cuda()                                  # tiled scale factors, built once at load
+        dn.prepare_cuda()
     return GroupedExperts(gu, dn, len(experts), experts[0].gate_up.N, experts[0].down.N,
                           experts[0].interleaved)
 

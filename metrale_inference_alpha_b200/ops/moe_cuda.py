@@ -14,6 +14,11 @@ _native.register_optional("mb_moe_route", [c.c_void_p, c.c_longlong, c.c_int, c.
                                           c.c_int, c.c_int, c.c_int, c.c_float, c.c_void_p, c.c_void_p, c.c_void_p])
 _native.register_optional("mb_moe_sort", [c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int] + [c.c_void_p] * 6 +
                           [c.c_int, c.c_void_p, c.c_void_p])
+_native.register_optional("mb_moe_sort_aligned", [c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int] +
+                          [c.c_void_p] * 6 + [c.c_int, c.c_void_p, c.c_void_p])
+_native.register_optional("mb_moe_gather_nvfp4", [c.c_void_p, c.c_longlong, c.c_void_p, c.c_longlong, c.c_int, c.c_void_p,
+                                                 c.c_int, c.c_int, c.c_int, c.c_void_p, c.c_void_p, c.c_void_p,
+                                                 c.c_void_p, c.c_int, c.c_void_p])
 _native.register_optional("mb_moe_gather", [c.c_void_p, c.c_longlong, c.c_void_p, c.c_longlong, c.c_int, c.c_void_p,
                                            c.c_int, c.c_void_p, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int,
                                            c.c_int, c.c_void_p])
@@ -64,23 +69,26 @@ def route_cuda(logits: torch.Tensor, cfg, bias=None):
 
 
 class SortedPairs:
-    """Device-side result of sorting (token, slot) pairs by local expert."""
+    """Device-side result of sorting (token, slot) pairs by local expert. With `align` > 1 every tile starts at
+    a multiple of `align` rows and holds up to `tile_rows` pairs; `rows_cap` is the number of rows the sorted
+    layout can then take, and every row of it that holds no pair has row_pair = -1."""
 
-    def __init__(self, idx: torch.Tensor, expert_lo: int, num_local: int, tile_rows: int):
+    def __init__(self, idx: torch.Tensor, expert_lo: int, num_local: int, tile_rows: int, align: int = 1):
         dev = idx.device
         T, K = idx.shape
         self.T, self.K, self.pairs = T, K, T * K
         self.tile_rows = tile_rows
         self.max_tiles = (self.pairs + tile_rows - 1) // tile_rows + num_local
+        self.rows_cap = self.pairs if align == 1 else self.max_tiles * align
         i32 = lambda n: torch.empty(n, dtype=torch.int32, device=dev)
-        self.pair_row, self.row_pair = i32(self.pairs), i32(self.pairs)
+        self.pair_row, self.row_pair = i32(self.pairs), i32(self.rows_cap)
         self.expert_off = i32(num_local + 1)
         self.tile_expert, self.tile_row0, self.tile_nrows = i32(self.max_tiles), i32(self.max_tiles), i32(self.max_tiles)
         self.total_rows = i32(1)
-        rc = _native.lib().mb_moe_sort(_ptr(idx), self.pairs, expert_lo, num_local, tile_rows, _ptr(self.pair_row),
-                                       _ptr(self.row_pair), _ptr(self.expert_off), _ptr(self.tile_expert),
-                                       _ptr(self.tile_row0), _ptr(self.tile_nrows), self.max_tiles,
-                                       _ptr(self.total_rows), _stream())
+        rc = _native.lib().mb_moe_sort_aligned(_ptr(idx), self.pairs, expert_lo, num_local, tile_rows, align, self.rows_cap,
+                                               _ptr(self.pair_row), _ptr(self.row_pair), _ptr(self.expert_off),
+                                               _ptr(self.tile_expert), _ptr(self.tile_row0), _ptr(self.tile_nrows),
+                                               self.max_tiles, _ptr(self.total_rows), _stream())
         _native.check(rc, "moe_sort")
         _count()
 
@@ -88,6 +96,21 @@ class SortedPairs:
 def gather_act(a: Act, sp: SortedPairs) -> Act:
     """Expert-sorted copy of the activation rows (and their scales)."""
     dev = a.data.device
+    if a.fmt == "nvfp4":
+        # one CTA per pair: packed row, per-token scale and the scale-factor words, the latter moved between the
+        # 128-row tiles of the two layouts; rows without a pair are left unwritten (the GEMM stores nothing for them)
+        rows = sp.rows_cap
+        out = Act("nvfp4", rows, a.K, torch.empty(rows, a.data.shape[1], dtype=torch.uint8, device=dev))
+        out.scale = torch.empty(rows, dtype=torch.float32, device=dev)
+        out.sf_k64 = a.sf_k64
+        out.sf = torch.empty((rows // 128) * a.sf_k64 * 512, dtype=torch.uint8, device=dev)
+        rc = _native.lib().mb_moe_gather_nvfp4(_ptr(a.data), a.data.stride(0), _ptr(out.data), out.data.stride(0),
+                                               a.data.shape[1], _ptr(sp.pair_row), sp.pairs, sp.K, rows,
+                                               _ptr(a.scale), _ptr(out.scale), _ptr(a.sf), _ptr(out.sf), a.sf_k64,
+                                               _stream())
+        _native.check(rc, "moe_gather_nvfp4")
+        _count()
+        return out
     rows = sp.pairs
     alloc = rows + 64                                   # the last tile may read past the end
     row_bytes = a.data.shape[1] * a.data.element_size()
@@ -103,8 +126,6 @@ def gather_act(a: Act, sp: SortedPairs) -> Act:
         groups, s_ld, d_ld = 1, a.scale.numel(), alloc
         out.scale = torch.empty(alloc, dtype=torch.float32, device=dev)
         src_scale, dst_scale = a.scale, out.scale
-    elif a.fmt == "nvfp4":
-        raise NotImplementedError("grouped NVFP4 experts need 128-row aligned scale-factor tiles")
     rc = _native.lib().mb_moe_gather(_ptr(a.data), a.data.stride(0) * a.data.element_size(), _ptr(out.data),
                                      out.data.stride(0) * out.data.element_size(), row_bytes, _ptr(sp.row_pair),
                                      sp.K, _ptr(sp.total_rows), rows, _ptr(src_scale), _ptr(dst_scale), groups,
@@ -122,18 +143,21 @@ def grouped_ffn(cfg, a: Act, weights: torch.Tensor, idx: torch.Tensor, w, finish
     ge = w.grouped
     T = a.M
     per_expert = max(1, (T * cfg.experts_per_token) // max(1, ge.num))
-    tile_rows = 16 if per_expert <= 16 else (32 if per_expert <= 32 else 64)
-    sp = SortedPairs(idx, w.expert_lo, ge.num, tile_rows)
+    nvfp4 = ge.gate_up.fmt == "nvfp4"
+    # NVFP4: every token tile starts on a 128-row block of scale factors and takes its first tile_rows rows
+    tile_rows = 16 if per_expert <= 16 else (32 if per_expert <= 32 else (64 if per_expert <= 64 or not nvfp4 else 128))
+    sp = SortedPairs(idx, w.expert_lo, ge.num, tile_rows, align=128 if nvfp4 else 1)
     xa = gather_act(a, sp)
     g = lambda n: (sp.tile_expert, sp.tile_row0, sp.tile_nrows, n, sp.max_tiles, tile_rows)
+    live = sp.pair_row if nvfp4 else None       # the aligned layout is mostly padding at decode sizes: one CTA per pair
     fmt_d = ACT_FOR_WEIGHT[ge.down.fmt]
     if cfg.ffn_act == "relu2":
-        h = row_op(linear(xa, ge.gate_up, grouped=g(ge.n_gate_up)), fmt_d, IN_RELU2)[0]
+        h = row_op(linear(xa, ge.gate_up, grouped=g(ge.n_gate_up)), fmt_d, IN_RELU2, row_index=live)[0]
     elif ge.interleaved:
         act = linear(xa, ge.gate_up, swiglu=True, grouped=g(ge.n_gate_up))
-        h = row_op(act, fmt_d, scale_pad=64)[0]
+        h = row_op(act, fmt_d, scale_pad=64, row_index=live)[0]
     else:
-        h = row_op(linear(xa, ge.gate_up, grouped=g(ge.n_gate_up)), fmt_d, IN_SILU_MUL, scale_pad=64)[0]
+        h = row_op(linear(xa, ge.gate_up, grouped=g(ge.n_gate_up)), fmt_d, IN_SILU_MUL, scale_pad=64, row_index=live)[0]
     if cfg.ffn_act == "relu2" and h.fmt == "fp8_g128" and h.scale.shape[1] < h.M + 64:
         pad = torch.empty(h.scale.shape[0], h.M + 64, dtype=torch.float32, device=h.scale.device)
         pad[:, :h.scale.shape[1]] = h.scale

@@ -852,46 +852,92 @@ def test_nllb_on_the_device_matches_the_host():
     assert len(out) <= 8 and all(0 <= x < 512 for x in out)
 
 
-def test_nvfp4_experts_run_one_gemm_per_active_expert():
-    """NVFP4 MoE checkpoints: the grouped GEMM does not take NVFP4 operands, so the experts run one W4A4 GEMM
-    per active expert; the block must agree with the CPU restatement of the same synthetic checkpoint."""
+def test_nvfp4_experts_take_the_grouped_gemm_on_128_row_aligned_segments():
+    """NVFP4 MoE checkpoints: the expert sort pads every expert's rows to the 128-row tile of the scale factors and
+    the grouped tcgen05 GEMM takes the W4A4 operands. Checked three ways: against one GEMM per active expert on the
+    same device (same quantisation, so the two agree closely), against the CPU restatement of the same synthetic
+    checkpoint, and end to end with CUDA graphs on."""
     from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
-    from metrale_inference_alpha_b200.models.moe import moe_block
+    from metrale_inference_alpha_b200.models.moe import moe_block, routed_experts
     from metrale_inference_alpha_b200.sampling.params import SamplingParams
     from metrale_inference_alpha_b200.models.decoder import Decoder
+    from metrale_inference_alpha_b200.ops import ACT_FOR_WEIGHT
     from metrale_inference_alpha_b200.weights.loader import load_weights
     from metrale_inference_alpha_b200.weights.source import SyntheticSource
     cfg = preset("tiny-hybrid-moe", weight_format="nvfp4")
-    eng = LLMEngine(EngineArgs(model=cfg, device=DEV, num_kv_blocks=64, max_num_seqs=4))
-    assert not eng.args.use_cuda_graphs
     # the same synthetic checkpoint on both devices
     w_h = load_weights(cfg, SyntheticSource(cfg, seed=3, device="cpu"), device="cpu")
     w_d = load_weights(cfg, SyntheticSource(cfg, seed=3, device="cpu"), device=DEV)
     lw_d = next(L for L in w_d.layers if L.ffn_kind == "moe")
     lw_h = next(L for L in w_h.layers if L.ffn_kind == "moe")
-    assert lw_d.ffn.grouped is None and lw_d.ffn.experts[0].gate_up.fmt == "nvfp4"
-    from metrale_inference_alpha_b200.models.moe import routed_experts
-    from metrale_inference_alpha_b200.ops import ACT_FOR_WEIGHT
-    g = torch.Generator().manual_seed(15)
-    x = (torch.randn(24, cfg.hidden_size, generator=g)).to(torch.bfloat16)
-    # the same routing on both sides (a near-tie in the router would send a token to different experts)
-    E, K = cfg.num_experts, cfg.experts_per_token
-    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(24)]).to(torch.int32)
-    wts = torch.rand(24, K, generator=g)
+    assert lw_d.ffn.grouped is not None and lw_d.ffn.grouped.gate_up.fmt == "nvfp4"
     fmt = ACT_FOR_WEIGHT["nvfp4"]
     dh, dd = Decoder(cfg, w_h, device="cpu"), Decoder(cfg, w_d, device=DEV)
-    a_h = dh._norm_act(x, lw_h.ln2, fmt, also_bf16=True)
-    a_d = dd._norm_act(x.to(DEV), lw_d.ln2, fmt, also_bf16=True)
-    want = routed_experts(dh, a_h, wts, idx, lw_h.ffn).float()
-    got = routed_experts(dd, a_d, wts.to(DEV), idx.to(DEV), lw_d.ffn).float().cpu()
-    err = (got - want).abs()
-    # both sides quantise activations to 4 bits, the device from the bf16 copy of the normed rows: the roundings
-    # decorrelate, so agreement is within the format's noise (a wrong expert or scale would be off by ~100 %)
-    assert float(err.mean()) < 0.15 * float(want.abs().mean()), (float(err.mean()), float(want.abs().mean()))
+    E, K = cfg.num_experts, cfg.experts_per_token
+    for T in (3, 24, 300):                     # 300 x 2 pairs over 8 experts: some experts span several 128-row tiles
+        g = torch.Generator().manual_seed(15 + T)
+        x = (torch.randn(T, cfg.hidden_size, generator=g)).to(torch.bfloat16)
+        # the same routing on every side (a near-tie in the router would send a token to different experts)
+        idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+        if T == 3:
+            idx[:, 0] = 5                      # most experts empty
+        wts = torch.rand(T, K, generator=g)
+        a_d = dd._norm_act(x.to(DEV), lw_d.ln2, fmt, also_bf16=True)
+        got = routed_experts(dd, a_d, wts.to(DEV), idx.to(DEV), lw_d.ffn).float().cpu()
+        grouped, lw_d.ffn.grouped = lw_d.ffn.grouped, None
+        try:
+            each = routed_experts(dd, a_d, wts.to(DEV), idx.to(DEV), lw_d.ffn).float().cpu()
+        finally:
+            lw_d.ffn.grouped = grouped
+        assert torch.isfinite(got).all()
+        scale = float(each.abs().mean())
+        # the grouped path gathers the 4-bit rows the norm produced, the per-expert path re-quantises their bf16
+        # copy with scales of its own: the two agree within the format's noise
+        assert float((got - each).abs().mean()) < 0.15 * scale, (T, float((got - each).abs().mean()), scale)
+        a_h = dh._norm_act(x, lw_h.ln2, fmt, also_bf16=True)
+        want = routed_experts(dh, a_h, wts, idx, lw_h.ffn).float()
+        err = (got - want).abs()
+        # host and device round the 4-bit activations independently, so they agree within the format's noise
+        # (a wrong expert or scale would be off by ~100 %)
+        assert float(err.mean()) < 0.15 * float(want.abs().mean()), (T, float(err.mean()), float(want.abs().mean()))
     assert moe_block(dd, x.to(DEV), lw_d).shape == x.shape
+    eng = LLMEngine(EngineArgs(model=cfg, device=DEV, num_kv_blocks=64, max_num_seqs=4))
+    assert eng.args.use_cuda_graphs
     out = eng.generate([list(range(5, 40))], SamplingParams(max_tokens=4, temperature=0.0))[0]
     assert len(out.output_ids) == 4
     ops.check_status(torch.device(DEV))
+
+
+def test_expert_sort_with_aligned_tiles_marks_every_empty_row():
+    from metrale_inference_alpha_b200.ops.moe_cuda import SortedPairs
+    g = torch.Generator().manual_seed(4)
+    T, K, E = 77, 3, 6
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    idx[idx == 4] = 5                                     # expert 4 gets nothing (and 5 may repeat in a row)
+    flat = idx.view(-1)
+    for tr in (128, 32):                                  # every tile starts a 128-row slot and fills its first `tr` rows
+        sp = SortedPairs(idx.to(DEV), 1, 5, tr, align=128)    # local experts 1..5; expert 0's pairs are not local
+        torch.cuda.synchronize()
+        off = sp.expert_off.cpu().tolist()
+        total = int(sp.total_rows.item())
+        row_pair = sp.row_pair.cpu()
+        pair_row = sp.pair_row.cpu().view(-1)
+        assert all(o % 128 == 0 for o in off) and off[-1] == total and total <= sp.rows_cap == row_pair.numel()
+        live_rows = []
+        for e in range(5):
+            n = int((flat == e + 1).sum())
+            assert off[e + 1] - off[e] == (n + tr - 1) // tr * 128
+            live_rows += [off[e] + (i // tr) * 128 + i % tr for i in range(n)]
+            assert (flat[row_pair[live_rows[len(live_rows) - n:]].long()] == e + 1).all()
+        mask = torch.zeros(sp.rows_cap, dtype=torch.bool)
+        mask[live_rows] = True
+        assert (row_pair[mask] >= 0).all() and (row_pair[~mask] == -1).all()
+        assert (pair_row[flat == 0] == -1).all()
+        live = pair_row[flat != 0].long()
+        assert (row_pair[live] == torch.nonzero(flat != 0).view(-1)).all()
+        tiles = [(int(e), int(r0), int(n)) for e, r0, n in zip(sp.tile_expert.cpu(), sp.tile_row0.cpu(), sp.tile_nrows.cpu()) if e >= 0]
+        assert all(r0 % 128 == 0 and 0 < n <= tr for _, r0, n in tiles)
+        assert sum(n for _, _, n in tiles) == int((flat != 0).sum())
 
 
 def test_kernel_audit_shows_which_kernels_served_a_long_prefill_and_a_decode_step():
