@@ -32,6 +32,8 @@ GEMM_ONE_TILE_PER_CTA, GEMM_DECODE_TILE_ORDER, GEMM_PERSISTENT_PREFILL, GEMM_DSM
 # prefill GEMMs (several 128-token tiles) also run on the persistent kernel (NVFP4 prefill GEMMs
 # measure 1.5x faster there; METRALE_PERSISTENT_PREFILL=0 keeps one tile per CTA)
 _PERSIST_PREFILL = GEMM_PERSISTENT_PREFILL if os.environ.get("METRALE_PERSISTENT_PREFILL", "1") != "0" else 0
+GEMM_GROUPED_ONE_CTA = 512
+_GROUPED_CTAS = GEMM_GROUPED_ONE_CTA if os.environ.get("METRALE_GROUPED_CTAS", "2") == "1" else 0
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -482,7 +484,7 @@ def linear(act: Act, w: QuantWeight, *, residual: Optional[torch.Tensor] = None,
     a.epilogue, a.out_f32 = int(swiglu), int(out_f32)
     a.ws, a.ws_bytes, a.status = _ptr(rt.ws), rt.ws_bytes, _ptr(rt.status)
     a.force_tn, a.force_splits, a.sm_count = force_tn, force_splits, rt.sm_count
-    a.flags = (_PERSIST_PREFILL | (GEMM_ONE_TILE_PER_CTA if one_tile_per_cta else 0)
+    a.flags = (_PERSIST_PREFILL | _GROUPED_CTAS | (GEMM_ONE_TILE_PER_CTA if one_tile_per_cta else 0)
                | (GEMM_DECODE_TILE_ORDER if decode_tile_order else 0) | (GEMM_DSMEM_SPLITK if dsmem_splitk else 0))
     a.no_cluster = int(no_cluster)
     qact = None

@@ -10,6 +10,7 @@
 #define MB_GEMM_ONE_TILE_PER_CTA 16     // never use the persistent kernel
 #define MB_GEMM_DECODE_TILE_ORDER 64    // prefill-sized GEMMs keep the decode launch order (weight tiles in x)
 #define MB_GEMM_PERSISTENT_PREFILL 128  // several 128-token tiles may run on the persistent kernel
+#define MB_GEMM_GROUPED_ONE_CTA 512     // grouped GEMMs of small token tiles keep one CTA per SM (default: two)
 #define MB_GEMM_DSMEM_SPLITK 256        // cluster split-K exchanges partial tiles over distributed shared memory
                                         // (default: through the L2-resident workspace)
 

@@ -85,16 +85,18 @@ struct GemmParams {
 
 constexpr int kTileN = 128;  // output features per CTA (UMMA M)
 
-template <int KIND, int TN>
+template <int KIND, int TN, int CTAS = 1>
 struct Cfg {
   static constexpr int kABytes = kTileN * 128;
   static constexpr int kBBytes = TN * 128;
   static constexpr int kSfBytes = (KIND == KIND_NVFP4) ? 2048 : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;
   // one CTA per SM with a deep pipeline: two co-resident CTAs with half the stages measured
-  // slower on the decode shapes (fewer bytes in flight per CTA on the split-K GEMMs)
-  static constexpr int kCtasPerSm = 1;
-  static constexpr int kBudget = 200 * 1024;
+  // slower on the decode shapes (fewer bytes in flight per CTA on the split-K GEMMs). CTAS = 2 is
+  // for the grouped (MoE) work lists of small token tiles: thousands of CTAs of 3 - 8 k blocks each,
+  // where a second resident CTA runs its main loop under the first one's prologue and epilogue.
+  static constexpr int kCtasPerSm = CTAS;
+  static constexpr int kBudget = (CTAS == 2 ? 100 : 200) * 1024;
   static constexpr int kStagesRaw = kBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = (KIND == KIND_FP8_BLOCK) ? 2 * TN : TN;
@@ -118,11 +120,11 @@ struct Cfg {
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <int KIND, int TN>
-__global__ void __launch_bounds__(192, Cfg<KIND, TN>::kCtasPerSm)
+template <int KIND, int TN, int CTAS = 1>
+__global__ void __launch_bounds__(192, CTAS)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const GemmParams p) {
-  using C = Cfg<KIND, TN>;
+  using C = Cfg<KIND, TN, CTAS>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -900,13 +902,13 @@ int dispatch_persistent(int tn, const CUtensorMap& tmA, const CUtensorMap& tmB, 
   }
 }
 
-template <int KIND, int TN>
+template <int KIND, int TN, int CTAS = 1>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, dim3 grid,
            cudaStream_t stream) {
   const int cluster_z = p.cluster ? p.splits : 1;
-  using C = Cfg<KIND, TN>;
+  using C = Cfg<KIND, TN, CTAS>;
   static bool configured = false;
-  auto kern = gemm_kernel<KIND, TN>;
+  auto kern = gemm_kernel<KIND, TN, CTAS>;
   if (!configured) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
@@ -1069,6 +1071,16 @@ int mb_gemm(const MbGemmArgs* a, cudaStream_t stream) {
     }
   }
   if (a->outq) return MB_ERR_UNSUPPORTED;      // only the persistent epilogue quantises
+  if (grouped && tn <= 32 && !(a->flags & MB_GEMM_GROUPED_ONE_CTA)) {
+    // small token tiles of a MoE work list: two CTAs per SM with half the stages each
+    const bool t16 = tn == 16;
+    switch (kind) {
+      case KIND_BF16: return t16 ? launch<KIND_BF16, 16, 2>(tmA, tmB, p, grid, stream) : launch<KIND_BF16, 32, 2>(tmA, tmB, p, grid, stream);
+      case KIND_FP8: return t16 ? launch<KIND_FP8, 16, 2>(tmA, tmB, p, grid, stream) : launch<KIND_FP8, 32, 2>(tmA, tmB, p, grid, stream);
+      case KIND_NVFP4: return t16 ? launch<KIND_NVFP4, 16, 2>(tmA, tmB, p, grid, stream) : launch<KIND_NVFP4, 32, 2>(tmA, tmB, p, grid, stream);
+      default: return t16 ? launch<KIND_FP8_BLOCK, 16, 2>(tmA, tmB, p, grid, stream) : launch<KIND_FP8_BLOCK, 32, 2>(tmA, tmB, p, grid, stream);
+    }
+  }
   switch (kind) {
     case KIND_BF16: rc = dispatch_tn<KIND_BF16>(tn, tmA, tmB, p, grid, stream); break;
     case KIND_FP8: rc = dispatch_tn<KIND_FP8>(tn, tmA, tmB, p, grid, stream); break;

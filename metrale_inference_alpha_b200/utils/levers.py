@@ -27,6 +27,7 @@ LEVERS: Dict[str, str] = {
     "METRALE_NO_FUSED_COLLECTIVES": "1 = NCCL collectives after plain GEMMs",
     "METRALE_MOE_FOLD_SHARED": "0 = the shared expert keeps its own dense GEMMs instead of riding in the grouped expert stack",
     "METRALE_ATTN_TC_VMN": "tcgen05 prefill attention: 1 = V read as an MN-major operand (no transposition while staging), 0 = transposed",
+    "METRALE_GROUPED_CTAS": "1 = grouped expert GEMMs of 16- / 32-row token tiles keep one CTA per SM (default 2: two co-resident CTAs, half the stages each)",
     "METRALE_INDEX_TC": "0 = the sparse-attention indexer score stays on the CUDA-core kernel instead of the mma.sync kernel",
     "METRALE_REDZONE": "bytes of guard band behind every ledger allocation (multiple of 16; default 0 = off)",
     "METRALE_REDZONE_EVERY": "with METRALE_REDZONE: check the guard bands every n-th engine step (default 0 = only on request)",
