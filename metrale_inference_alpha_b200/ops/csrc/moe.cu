@@ -292,7 +292,8 @@ __global__ void combine_kernel(const float* __restrict__ y, long long y_ld, cons
                                const float* __restrict__ w, int K, int H, const float* __restrict__ addend,
                                float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16) {
   const int tok = blockIdx.x;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+  // the hidden row is split over blockIdx.y: at decode sizes one CTA per token leaves most SMs idle
+  for (int h = blockIdx.y * blockDim.x + threadIdx.x; h < H; h += gridDim.y * blockDim.x) {
     float acc = addend ? addend[(size_t)tok * H + h] : 0.f;
     for (int j = 0; j < K; ++j) {
       const int r = pair_row[(size_t)tok * K + j];
@@ -322,7 +323,7 @@ __global__ void moe_finish_kernel(const float* __restrict__ y, long long y_ld, c
     rows[j] = pair_row[(size_t)tok * K + j];
     ws[j] = w[(size_t)tok * K + j];
   }
-  for (int h = threadIdx.x * 2; h < H; h += blockDim.x * 2) {
+  for (int h = (blockIdx.y * blockDim.x + threadIdx.x) * 2; h < H; h += gridDim.y * blockDim.x * 2) {
     float a0 = 0.f, a1 = 0.f;
     for (int j = 0; j < K; ++j) {
       if (rows[j] >= 0) {
@@ -354,7 +355,8 @@ int mb_moe_finish(const float* y, long long y_ld, const int* pair_row, const flo
                   const void* residual, void* out, cudaStream_t stream) {
   if (!y || !pair_row || !w || !out || T <= 0 || K <= 0 || K > 32 || H % 2 || y_ld % 2 || shared_ld % 2)
     return MB_ERR_BAD_ARG;
-  return (int)mb::launch_kernel(moe_finish_kernel, dim3(T), dim3(256), 0, stream, y, y_ld, pair_row, w, K, H,
+  const int gy = T >= 2048 ? 1 : min(8, (H + 511) / 512);
+  return (int)mb::launch_kernel(moe_finish_kernel, dim3(T, gy), dim3(256), 0, stream, y, y_ld, pair_row, w, K, H,
                                 reinterpret_cast<const __nv_bfloat16*>(shared), shared_ld, gate_logit, gate_ld,
                                 reinterpret_cast<const __nv_bfloat16*>(residual),
                                 reinterpret_cast<__nv_bfloat16*>(out));
@@ -433,7 +435,8 @@ int mb_moe_gather_nvfp4(const void* src, long long src_ld, void* dst, long long 
 int mb_moe_combine(const float* y, long long y_ld, const int* pair_row, const float* w, int T, int K, int H,
                    const float* addend, float* out_f32, void* out_bf16, cudaStream_t stream) {
   if (!y || !pair_row || !w || T <= 0) return MB_ERR_BAD_ARG;
-  combine_kernel<<<T, 256, 0, stream>>>(y, y_ld, pair_row, w, K, H, addend, out_f32,
+  const int gy = T >= 2048 ? 1 : min(8, (H + 255) / 256);
+  combine_kernel<<<dim3(T, gy), 256, 0, stream>>>(y, y_ld, pair_row, w, K, H, addend, out_f32,
                                         reinterpret_cast<__nv_bfloat16*>(out_bf16));
   return (int)cudaGetLastError();
 }
