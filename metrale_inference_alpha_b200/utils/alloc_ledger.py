@@ -21,6 +21,7 @@ import os
 import sys
 import threading
 import weakref
+from collections import deque
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -53,6 +54,7 @@ class AllocLedger:
         self._live: Dict[int, Entry] = {}
         self._next = 0
         self._lock = threading.Lock()
+        self._dead: "deque[int]" = deque()           # keys of tensors that died; taken out of _live under the lock
 
     # ------------------------------------------------------------------ allocation
     def alloc(self, shape, dtype=torch.uint8, device="cpu", name: str = "", fill: Optional[float] = 0, site: Optional[str] = None
@@ -78,6 +80,7 @@ class AllocLedger:
         if fill is not None:
             t.fill_(fill) if fill else t.zero_()
         with self._lock:
+            self._reap()
             key = self._next
             self._next += 1
             self._live[key] = Entry(name or site, site, nbytes, str(t.device), guard)
@@ -87,6 +90,7 @@ class AllocLedger:
     def track(self, t: torch.Tensor, name: str, site: Optional[str] = None) -> torch.Tensor:
         """Record an allocation made elsewhere (no red zone can be added after the fact)."""
         with self._lock:
+            self._reap()
             key = self._next
             self._next += 1
             self._live[key] = Entry(name, site or _call_site(), t.numel() * t.element_size(), str(t.device))
@@ -94,12 +98,20 @@ class AllocLedger:
         return t
 
     def _drop(self, key: int) -> None:
-        with self._lock:
-            self._live.pop(key, None)
+        # A tensor's finalizer runs wherever the garbage collector happens to run: that can be inside one of this
+        # ledger's own locked sections (creating an Entry allocates), on the very thread that holds the lock. It
+        # therefore takes no lock and touches no dict: it leaves the key in a queue that the locked sections drain.
+        self._dead.append(key)
+
+    def _reap(self) -> None:
+        """Forget the entries of dead tensors. The caller holds the lock."""
+        while self._dead:
+            self._live.pop(self._dead.popleft(), None)
 
     # ------------------------------------------------------------------ reports
     def total_bytes(self, device: Optional[str] = None) -> int:
         with self._lock:
+            self._reap()
             return sum(e.nbytes + (e.guard.numel() if e.guard is not None else 0) for e in self._live.values()
                        if device is None or e.device == device)
 
@@ -108,6 +120,7 @@ class AllocLedger:
         groups: Dict[Tuple[str, str], List[int]] = {}
         sites: Dict[Tuple[str, str], str] = {}
         with self._lock:
+            self._reap()
             for e in self._live.values():
                 groups.setdefault((e.name, e.device), []).append(e.nbytes)
                 sites.setdefault((e.name, e.device), e.site)
@@ -128,6 +141,7 @@ class AllocLedger:
         """The allocations whose guard band no longer holds the pattern: name, site and how many band
         bytes changed. Empty when red zones are off or all bands are intact."""
         with self._lock:
+            self._reap()
             bands = [(e.name, e.site, e.guard) for e in self._live.values() if e.guard is not None]
         bad = []
         for name, site, g in bands:
@@ -139,6 +153,7 @@ class AllocLedger:
 
     def refill(self) -> None:
         with self._lock:
+            self._reap()
             for e in self._live.values():
                 if e.guard is not None:
                     e.guard.fill_(PATTERN)

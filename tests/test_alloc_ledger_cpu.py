@@ -79,3 +79,24 @@ def test_kernel_audit_counts_and_classifies_launchers():
         a.require("paged_attention")
     _native.check(0, "gemm")                                  # outside the audit: not counted
     assert a.counts["gemm"] == 2
+
+
+def test_a_finalizer_that_runs_inside_a_locked_section_does_not_deadlock():
+    """Garbage collection can run a dead tensor's finalizer on the thread that is inside the ledger's lock."""
+    import threading
+
+    from metrale_inference_alpha_b200.utils.alloc_ledger import AllocLedger
+    led = AllocLedger()
+    t = led.alloc((4,), torch.float32, "cpu", name="a")
+    done = []
+
+    def inside():
+        with led._lock:                       # what alloc() holds when the collector fires
+            led._drop(0)                      # the finalizer's body
+        done.append(1)
+    th = threading.Thread(target=inside, daemon=True)
+    th.start()
+    th.join(5)
+    assert done, "the finalizer blocked on the ledger's own lock"
+    del t
+    assert led.total_bytes() == 0
