@@ -70,6 +70,7 @@ class EngineArgs:
     kv_tier_blocks: int = 0                            # > 0: KV blocks the prefix cache evicts are kept in a second tier of this many blocks ...
     kv_tier_dir: Optional[str] = None                  # ... in files under this directory (default: host memory)
     kv_tier_host_blocks: int = 0                       # with kv_tier_dir: a pinned write-back host cache of this many blocks in front of the files
+    kv_tier_codec: str = "raw"                         # raw | nvfp4 (tier records hold e2m1 values + e4m3 block scales: 3.4 x fewer bytes than bf16, lossy)
     expert_arena_slots: int = 0                        # MoE: > 0 pages the routed experts from an expert store into a device arena of this many experts
     expert_store_dir: Optional[str] = None             # ... the store's directory (written from the loaded weights when it has no manifest yet)
     prediction_drafts: int = 8                         # tokens verified per step for requests with a predicted output
@@ -194,7 +195,8 @@ class LLMEngine:
                     raise ValueError("kv_tier_blocks: models with recurrent state keep their prefix hits through state "
                                      "snapshots (state_tier_host_bytes / state_tier_dir), not through KV tiering")
                 from ..cache.kv_tier import KvTierStore, TieredRadixTree
-                self.kv_tier = KvTierStore(self.runner.kv, args.kv_tier_blocks, args.kv_tier_dir, args.kv_tier_host_blocks)
+                self.kv_tier = KvTierStore(self.runner.kv, args.kv_tier_blocks, args.kv_tier_dir, args.kv_tier_host_blocks,
+                                           codec=args.kv_tier_codec)
                 self.prefix = TieredRadixTree(self.runner.kv.allocator, args.block_size, self.kv_tier)
         self.spill = None
         if args.preempt_mode == "swap":

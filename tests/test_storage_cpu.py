@@ -419,3 +419,42 @@ def test_kv_tier_is_refused_for_recurrent_models():
     from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
     with pytest.raises(ValueError):
         LLMEngine(EngineArgs(model="tiny-hybrid-moe", device="cpu", num_kv_blocks=32, kv_tier_blocks=8))
+
+
+def test_nvfp4_tier_records_are_a_third_of_the_bytes_and_restore_within_the_formats_noise():
+    from metrale_inference_alpha_b200.cache import KvCacheConfig, PagedKvCache
+    from metrale_inference_alpha_b200.cache.kv_tier import KvTierStore
+    kv = PagedKvCache(KvCacheConfig(2, 2, 64, block_size=4), 8)
+    g = torch.Generator().manual_seed(0)
+    for L in range(2):
+        kv.k[L].copy_(torch.randn(kv.k[L].shape, generator=g).to(kv.k[L].dtype))
+        kv.v[L].copy_(torch.randn(kv.v[L].shape, generator=g).to(kv.v[L].dtype))
+    st = KvTierStore(kv, capacity_blocks=4, codec="nvfp4")
+    elem = kv.k[0].element_size()
+    rows = 2 * 2 * 4 * 2                                       # layers x (k, v) x tokens x kv heads
+    assert st.record_bytes == rows * (32 + 4 + 4) and st.raw_bytes == rows * 64 * elem
+    want_k, want_v = kv.k[1][3].clone().float(), kv.v[0][3].clone().float()
+    st.put(b"x", 3)
+    assert st.restore(b"x", 6)
+    for got, want in ((kv.k[1][6].float(), want_k), (kv.v[0][6].float(), want_v)):
+        rel = float((got - want).norm() / want.norm())
+        assert 0.0 < rel < 0.15, rel                           # 4-bit values with a scale per 16 channels
+    with pytest.raises(ValueError):
+        KvTierStore(kv, capacity_blocks=4, codec="int3")
+
+
+def test_engine_serves_prefix_hits_from_an_nvfp4_tier(tmp_path):
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    sp = SamplingParams(max_tokens=4, temperature=0.0)
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=2, max_model_len=256, num_kv_blocks=14,
+                               kv_tier_blocks=64, kv_tier_codec="nvfp4"))
+    a = list(range(10, 10 + 100))
+    eng.generate([a], sp)
+    for i in range(3):
+        eng.generate([list(range(300 + 150 * i, 300 + 150 * i + 120))], sp)
+    again = eng.generate([a], sp)[0]
+    st = eng.prefix.stats()
+    assert again.cached_tokens >= 80 and len(again.output_ids) == 4 and st["tier_restored"] >= 5
+    assert eng.kv_tier.record_bytes * 3 < eng.kv_tier.raw_bytes            # 76 bytes per 128 channels against 256 (bf16) or 512
+    eng.close()
