@@ -4,11 +4,10 @@ of being lost, and a later request with the same prefix gets them back by a copy
 ``KvTierStore`` keeps fixed-size records (one record = one block of every cache layer, K and V) in a byte
 store of the storage package (files with an optional pinned write-back host tier, or host memory), indexed
 by the *chain digest* of the block: a hash over the namespace, every token of the prefix up to and including
-the block. Capacity is bounded; the least recently used record is overwritten. With ``codec="nvfp4"`` the floating-point
-fields of a record are stored as e2m1 values with one e4m3 scale per 16 channels and one fp32 scale per row
-(the weight format of the checkpoints, applied to cached keys and values): 76 bytes per 128-channel row
-instead of 256 for bf16. The encoding is lossy; it is applied on the way into the tier and undone on the way
-back, the device pool keeps its own dtype.
+the block. Capacity is bounded; the least recently used record is overwritten. The floating-point fields of a
+record can go through a codec of ``cache/kv_codec.py`` (``nvfp4``: 76 bytes per 128-channel row; ``turbo4`` /
+``turbo3`` / ``turbo2``: 68 / 52 / 36, against 256 for bf16). These encodings are lossy; they are applied on the way
+into the tier and undone on the way back, the device pool keeps its own dtype.
 
 ``TieredRadixTree`` is the prefix tree with two hooks: ``evict`` writes a leaf's block to the store before the
 block goes back to the allocator, and ``match`` continues past the last resident block while the store holds
@@ -44,20 +43,17 @@ class KvTierStore:
         from ..storage.backend import CascadeBackend, FileBackend, KvLayout, MemoryBackend, pinned_bytes
         if capacity_blocks <= 0:
             raise ValueError("the KV tier needs a positive capacity")
-        if codec not in ("raw", "nvfp4"):
-            raise ValueError(f"kv tier codec must be raw | nvfp4, not {codec!r}")
-        self.kv, self.codec = kv, codec
+        from .kv_codec import make_codec
+        self.kv, self.codec = kv, make_codec(codec)
         sample = kv.gather_blocks([0])
         self.fields = []                      # (name, dtype, shape, bytes in the record, packed as nvfp4)
         self.raw_bytes = 0
         for name, t in sorted(sample.items()):
             raw = t[0].numel() * t.element_size()
             self.raw_bytes += raw
-            packed = codec == "nvfp4" and t.dtype in (torch.bfloat16, torch.float16, torch.float32) and t.shape[-1] % 16 == 0
-            n = raw
-            if packed:
-                K = t.shape[-1]
-                n = (t[0].numel() // K) * (K // 2 + K // 16 + 4)
+            K = t.shape[-1]
+            packed = self.codec.applies(t.dtype, K)
+            n = (t[0].numel() // K) * self.codec.row_bytes(K, t.element_size()) if packed else raw
             self.fields.append((name, t.dtype, tuple(t.shape[1:]), n, packed))
         self.record_bytes = sum(f[3] for f in self.fields)
         layout = KvLayout(1, capacity_blocks, 1, 1, (self.record_bytes + 1) // 2, elem_bytes=1)
@@ -88,9 +84,7 @@ class KvTierStore:
         for name, _, _, n, packed in self.fields:
             src = data[name][0].contiguous()
             if packed:
-                from ..ops import reference as ref
-                q, sf, g = ref.quantize_nvfp4(src.reshape(-1, src.shape[-1]).float())
-                src = torch.cat([q.reshape(-1), sf.reshape(-1), g.float().contiguous().view(torch.uint8).reshape(-1)])
+                src = self.codec.encode(src.reshape(-1, src.shape[-1])).contiguous()
             self._buf[off:off + n].copy_(src.view(torch.uint8).reshape(-1))
             off += n
         self.backend.write_block(0, slot, self._buf)
@@ -108,11 +102,9 @@ class KvTierStore:
         for name, dt, shape, n, packed in self.fields:
             rec = self._buf[off:off + n].clone()
             if packed:
-                from ..ops import reference as ref
                 K = shape[-1]
-                rows = n // (K // 2 + K // 16 + 4)
-                q, sf, g = rec[:rows * K // 2], rec[rows * K // 2:rows * (K // 2 + K // 16)], rec[rows * (K // 2 + K // 16):]
-                data[name] = ref.dequantize_nvfp4(q.view(rows, K // 2), sf.view(rows, K // 16), g.view(torch.float32)).to(dt).view(1, *shape)
+                per_row = self.codec.row_bytes(K, 0)
+                data[name] = self.codec.decode(rec.view(n // per_row, per_row), K).to(dt).view(1, *shape)
             else:
                 data[name] = rec.view(dt).view(1, *shape)
             off += n

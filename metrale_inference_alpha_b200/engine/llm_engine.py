@@ -70,7 +70,7 @@ class EngineArgs:
     kv_tier_blocks: int = 0                            # > 0: KV blocks the prefix cache evicts are kept in a second tier of this many blocks ...
     kv_tier_dir: Optional[str] = None                  # ... in files under this directory (default: host memory)
     kv_tier_host_blocks: int = 0                       # with kv_tier_dir: a pinned write-back host cache of this many blocks in front of the files
-    kv_tier_codec: str = "raw"                         # raw | nvfp4 (tier records hold e2m1 values + e4m3 block scales: 3.4 x fewer bytes than bf16, lossy)
+    kv_tier_codec: str = "raw"                         # raw | nvfp4 | turbo4 | turbo3 | turbo2: lossy record formats of the tier (76 / 68 / 52 / 36 bytes per 128 channels against 256 for bf16)
     expert_arena_slots: int = 0                        # MoE: > 0 pages the routed experts from an expert store into a device arena of this many experts
     expert_store_dir: Optional[str] = None             # ... the store's directory (written from the loaded weights when it has no manifest yet)
     prediction_drafts: int = 8                         # tokens verified per step for requests with a predicted output

@@ -443,6 +443,44 @@ def test_nvfp4_tier_records_are_a_third_of_the_bytes_and_restore_within_the_form
         KvTierStore(kv, capacity_blocks=4, codec="int3")
 
 
+@pytest.mark.parametrize("name,row_bytes,bound", [("nvfp4", 76, 0.12), ("turbo4", 68, 0.12), ("turbo3", 52, 0.22), ("turbo2", 36, 0.40)])
+def test_tier_codecs_meet_their_sizes_and_distortion_with_an_outlier_channel(name, row_bytes, bound):
+    """The Lloyd-Max distortion of a unit Gaussian is 0.0095 / 0.0345 / 0.1175 at 4 / 3 / 2 bits (relative rms error
+    0.097 / 0.186 / 0.343); the Walsh-Hadamard rotation is what makes a row with one channel 20 x the rest meet it."""
+    from metrale_inference_alpha_b200.cache.kv_codec import fwht, make_codec, roundtrip
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(64, 128, generator=g)
+    x[:, 5] *= 20
+    assert torch.allclose(fwht(fwht(x, 128), 128), x, atol=1e-4)
+    y, b = roundtrip(make_codec(name), x)
+    assert b == row_bytes and float((y - x).norm() / x.norm()) < bound
+    # a latent row of 576 channels (not a power of two): the rotation runs over blocks of 64
+    z = torch.randn(8, 576, generator=g)
+    y, b = roundtrip(make_codec(name), z)
+    assert float((y - z).norm() / z.norm()) < bound
+    # an all-zero row stays zero
+    y, _ = roundtrip(make_codec(name), torch.zeros(2, 64))
+    assert float(y.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("codec", ["turbo4", "turbo2"])
+def test_tier_store_round_trips_blocks_through_a_turbo_codec(codec):
+    from metrale_inference_alpha_b200.cache import KvCacheConfig, PagedKvCache
+    from metrale_inference_alpha_b200.cache.kv_tier import KvTierStore
+    kv = PagedKvCache(KvCacheConfig(2, 2, 64, block_size=4), 8)
+    g = torch.Generator().manual_seed(1)
+    for L in range(2):
+        kv.k[L].copy_(torch.randn(kv.k[L].shape, generator=g).to(kv.k[L].dtype))
+        kv.v[L].copy_(torch.randn(kv.v[L].shape, generator=g).to(kv.v[L].dtype))
+    st = KvTierStore(kv, capacity_blocks=2, codec=codec)
+    want = kv.v[1][2].clone().float()
+    st.put(b"k", 2)
+    assert st.restore(b"k", 7)
+    rel = float((kv.v[1][7].float() - want).norm() / want.norm())
+    assert 0.0 < rel < (0.12 if codec == "turbo4" else 0.40)
+    assert st.record_bytes == 2 * 2 * 4 * 2 * (64 * int(codec[-1]) // 8 + 4)
+
+
 def test_engine_serves_prefix_hits_from_an_nvfp4_tier(tmp_path):
     from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
     from metrale_inference_alpha_b200.sampling.params import SamplingParams
