@@ -893,13 +893,13 @@ def test_nvfp4_experts_take_the_grouped_gemm_on_128_row_aligned_segments():
         scale = float(each.abs().mean())
         # the grouped path gathers the 4-bit rows the norm produced, the per-expert path re-quantises their bf16
         # copy with scales of its own: the two agree within the format's noise
-        assert float((got - each).abs().mean()) < 0.15 * scale, (T, float((got - each).abs().mean()), scale)
+        assert float((got - each).abs().mean()) < 0.2 * scale, (T, float((got - each).abs().mean()), scale)
         a_h = dh._norm_act(x, lw_h.ln2, fmt, also_bf16=True)
         want = routed_experts(dh, a_h, wts, idx, lw_h.ffn).float()
         err = (got - want).abs()
         # host and device round the 4-bit activations independently, so they agree within the format's noise
         # (a wrong expert or scale would be off by ~100 %)
-        assert float(err.mean()) < 0.15 * float(want.abs().mean()), (T, float(err.mean()), float(want.abs().mean()))
+        assert float(err.mean()) < 0.2 * float(want.abs().mean()), (T, float(err.mean()), float(want.abs().mean()))
     assert moe_block(dd, x.to(DEV), lw_d).shape == x.shape
     eng = LLMEngine(EngineArgs(model=cfg, device=DEV, num_kv_blocks=64, max_num_seqs=4))
     assert eng.args.use_cuda_graphs
