@@ -121,6 +121,13 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--api-key", default=None)
     b.add_argument("--served-model-name", default="default")
 
+    gt = sub.add_parser("gates", help="correctness gates over an in-process engine: order equality, conversation replay, "
+                                      "history independence, state poisoning, cross-request contamination, decode floor")
+    _add_engine_args(gt)
+    gt.add_argument("--only", default=None, help="comma list of: order, replay, kat, poison, contamination, floor")
+    gt.add_argument("--rounds", type=int, default=12, help="replays of the conversation / of the probe request")
+    gt.add_argument("--decode-floor", type=float, default=0.0, help="tokens/s the single-user decode rate must reach (0: recorded only)")
+
     for name, helptext in (("tui", "live dashboard of a running server"), ("chat", "terminal chat with a running server")):
         t = sub.add_parser(name, help=helptext)
         t.add_argument("--url", default="http://127.0.0.1:8888")
@@ -209,6 +216,49 @@ def run_benchmark(ns) -> List[dict]:
         return rows
     from ..bench.ladder import run_ladder
     return run_ladder(_engine_args(ns), [int(c) for c in ns.concurrency.split(",")], ns.isl, ns.osl)
+
+
+def run_gates(ns) -> list:
+    """The correctness gates of ``bench/`` against one in-process engine built from the serve options."""
+    import torch
+
+    from ..bench import determinism, isolation, replay_gates
+    from ..engine.llm_engine import LLMEngine
+    from ..sampling.params import SamplingParams
+    eargs = _engine_args(ns)
+    eargs.enable_prefix_caching = True
+    want = set((ns.only or "order,replay,kat,poison,contamination,floor").split(","))
+    make = lambda: LLMEngine(eargs)
+    eng = make()
+    vocab = eng.cfg.vocab_size
+    g = torch.Generator().manual_seed(5)
+    draw = lambda n, length: [torch.randint(1, vocab, (length + 3 * i,), generator=g).tolist() for i in range(n)]
+    dev = str(eargs.device)
+    recs = []
+    if "order" in want:
+        recs.append(replay_gates.order_equality(eng, draw(8, 40), orders=3, max_tokens=24, device=dev))
+    if "replay" in want:
+        noise_prompts = draw(4, 64)
+        first = max(48, eng.scheduler.snapshot_interval + eargs.block_size + 8) if eng.runner.pool is not None else 48
+        script = [draw(1, first)[0]] + draw(3, 24)
+        recs.append(replay_gates.conversation_replay(
+            eng, script, rounds=ns.rounds, max_tokens=16, device=dev,
+            noise=lambda r: eng.generate([noise_prompts[r % 4]], SamplingParams(max_tokens=8, temperature=0.0))))
+    if "floor" in want:
+        rec = replay_gates.decode_floor(eng, draw(1, 64)[0], ns.decode_floor, runs=5, max_tokens=64, device=dev)
+        recs.append(rec)
+    if "contamination" in want:
+        rep = isolation.contamination(eng, n_requests=min(8, eargs.max_num_seqs), rounds=2)
+        from ..bench.gate import GateRecord, kernel_closure_hash
+        recs.append(GateRecord("contamination", "requests whose reply holds another request's secret", float(len(rep["leaks"])), "leaks",
+                               higher_is_better=False, config={"pass": rep["ok"], "requests": rep["requests"], "leaks": rep["leaks"][:8]},
+                               closure=kernel_closure_hash(), device=dev))
+    eng.close()
+    if "kat" in want:
+        recs.append(determinism.kat_equality(make, device=dev))
+    if "poison" in want and eng.runner.pool is not None:
+        recs.append(determinism.state_poisoning(make, replays=ns.rounds, device=dev))
+    return recs
 
 
 def _init_ranks(eargs):
@@ -345,6 +395,13 @@ def main(argv: Optional[List[str]] = None) -> int:
             print(f"{'C':>4} {'tok/s':>10} {'p50 TTFT ms':>12} {'p99 TTFT ms':>12} {'ms/step':>9}")
             for r in rows:
                 print(f"{r['concurrency']:>4} {r['tok_s']:>10.1f} {r['ttft_p50_ms']:>12.1f} {r['ttft_p99_ms']:>12.1f} {r['ms_per_step']:>9.2f}")
+    elif ns.cmd == "gates":
+        recs = run_gates(ns)
+        for r in recs:
+            ok = r.config.get("pass", r.value == 1.0)
+            print(f"{'PASS' if ok else 'FAIL'}  {r.name:<22} {r.metric}: {r.value:g} {r.unit}  {r.config.get('why') or r.config.get('mismatch') or ''}")
+        if not all(r.config.get("pass", r.value == 1.0) for r in recs):
+            raise SystemExit(1)
     elif ns.cmd in ("tui", "chat"):
         from .tui import ChatSession, Dashboard, HttpTransport
         tr = HttpTransport(ns.url, ns.api_key)

@@ -3,6 +3,7 @@ tool loop on a virtual workspace, request isolation and scheduler equivalence.""
 import json
 
 import pytest
+import torch
 
 from metrale_inference_alpha_b200.bench import agentic as AG
 from metrale_inference_alpha_b200.bench import function_calling as FC
@@ -129,3 +130,70 @@ def test_requests_do_not_leak_into_each_other_and_scheduling_does_not_change_tok
     eq = scheduler_equivalence(make, n=4, max_tokens=8)
     assert eq["ok"], eq
     assert set(eq["variants"]) == {"small_prefill_chunks", "batch_cap_2", "tbt_policy", "no_prefix_cache"}
+
+
+# ----------------------------------------------------------------------------- replay gates
+def test_order_comparison_names_each_way_to_fail():
+    from metrale_inference_alpha_b200.bench.replay_gates import compare_orders
+    a = {"s0": [1, 2, 3], "s1": [4, 5]}
+    assert compare_orders([a, dict(a), dict(a)])["pass"]
+    assert compare_orders([a])["why"] == "fewer than two orders"
+    assert compare_orders([{}, {}])["why"] == "no samples"
+    assert compare_orders([{"s0": []}, {"s0": []}])["why"] == "every reference reply is empty"
+    bad = compare_orders([a, {"s0": [1, 9, 3], "s1": [4, 5]}])
+    assert not bad["pass"] and bad["unequal"] == [{"sample": "s0", "order": 1, "first_difference": 1, "missing": False}]
+    assert compare_orders([a, {"s0": [1, 2, 3]}])["unequal"][0]["missing"]
+
+
+def test_turns_split_into_invariant_jittered_collapsed_and_unmeasured():
+    from metrale_inference_alpha_b200.bench.replay_gates import ReplayScore, Turn, compare_round, compare_turn
+    ref = Turn(list(range(10)), "length")
+    assert compare_turn(ref, Turn(list(range(10)), "length")) == "invariant"
+    assert compare_turn(ref, Turn(list(range(9)) + [99], "length")) == "jittered"           # reworded, same shape
+    assert compare_turn(ref, Turn([1, 2], "length")) == "collapsed"                          # a stub: ratio 0.2
+    assert compare_turn(ref, Turn(list(range(25)), "length")) == "collapsed"                 # a runaway: ratio 2.5
+    assert compare_turn(ref, Turn(list(range(10)), "stop")) == "collapsed"                   # another finish reason
+    assert compare_turn(ref, Turn([], None, error="boom")) == "unmeasured"
+    assert compare_round([ref, ref], [ref, Turn(list(range(9)) + [7], "length")]) == "jittered"
+    assert compare_round([ref, ref], [ref]) == "unmeasured"                                  # a short round
+    assert compare_round([ref, ref], [Turn([1], "length"), Turn([], None, error="x")]) == "collapsed"
+    ok = ReplayScore(3, ["invariant", "jittered", "invariant"]).decide()
+    assert ok["pass"] and ok["jittered"] == 1
+    assert "short run" in ReplayScore(3, ["invariant"]).decide()["why"]
+    assert "1 collapsed" in ReplayScore(2, ["invariant", "collapsed"]).decide()["why"]
+    assert "restored nothing" in ReplayScore(1, ["invariant"], zero_cache_rounds=[1]).decide()["why"]
+    assert "anchors" in ReplayScore(1, ["invariant"], reference_ok=False).decide()["why"]
+
+
+@pytest.mark.parametrize("model", ["tiny-dense", "tiny-hybrid-moe"])
+def test_replay_gates_pass_on_the_engine(model):
+    from metrale_inference_alpha_b200.bench.replay_gates import conversation_replay, decode_floor, judge_floor, order_equality
+    from metrale_inference_alpha_b200.engine.llm_engine import EngineArgs, LLMEngine
+    from metrale_inference_alpha_b200.sampling.params import SamplingParams
+    eng = LLMEngine(EngineArgs(model=model, device="cpu", max_num_seqs=4, max_model_len=512, num_kv_blocks=96))
+    eng.scheduler.snapshot_interval = 16          # recurrent models: state snapshots (hence prefix hits) from the first block on
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(1, eng.cfg.vocab_size, (20 + 5 * i,), generator=g).tolist() for i in range(5)]
+    rec = order_equality(eng, prompts, orders=3, max_tokens=8)
+    assert rec.value == 1.0, rec.config
+    script = [torch.randint(1, eng.cfg.vocab_size, (24,), generator=g).tolist() for _ in range(3)]
+    noise_prompts = [torch.randint(1, eng.cfg.vocab_size, (30,), generator=g).tolist() for _ in range(4)]
+
+    def noise(r):
+        eng.generate([noise_prompts[r % 4]], SamplingParams(max_tokens=4, temperature=0.0))
+    rec = conversation_replay(eng, script, rounds=3, max_tokens=6, noise=noise)
+    assert rec.value == 1.0 and rec.config["verdicts"] == ["invariant"] * 3, rec.config
+    rec = decode_floor(eng, prompts[0], floor_tok_s=0.01, runs=3, max_tokens=6)
+    assert rec.config["pass"] and rec.value > 0.01
+    assert not judge_floor([5.0, 6.0, 7.0], 10.0)["pass"] and not judge_floor([50.0], 10.0)["pass"]
+    eng.close()
+
+
+def test_gates_command_runs_the_suites_and_fails_on_an_unmet_floor(capsys):
+    from metrale_inference_alpha_b200.server import cli
+    cli.main(["gates", "--model", "tiny-dense", "--device", "cpu", "--rounds", "2", "--only", "order,replay,floor", "--max-num-seqs", "4"])
+    out = capsys.readouterr().out
+    assert out.count("PASS") == 3 and "conversation-replay" in out and "FAIL" not in out
+    with pytest.raises(SystemExit):
+        cli.main(["gates", "--model", "tiny-dense", "--device", "cpu", "--only", "floor", "--decode-floor", "1e9"])
+    assert "under the floor" in capsys.readouterr().out
