@@ -197,3 +197,44 @@ def test_gates_command_runs_the_suites_and_fails_on_an_unmet_floor(capsys):
     with pytest.raises(SystemExit):
         cli.main(["gates", "--model", "tiny-dense", "--device", "cpu", "--only", "floor", "--decode-floor", "1e9"])
     assert "under the floor" in capsys.readouterr().out
+
+
+# ----------------------------------------------------------------------------- speed gates
+def test_ttft_verdicts_and_baseline_rules(tmp_path):
+    from metrale_inference_alpha_b200.bench.speed_gates import TtftBaselines, same_host, summarise_ttft, ttft_verdict
+    assert same_host("http://localhost:8888/v1", "127.0.0.1:8888") and same_host("https://a.example", "https://A.example:443/")
+    assert not same_host("http://a.example:8888", "http://a.example:9999") and not same_host("http://a", "http://b")
+    s = summarise_ttft([10.0, 30.0, 20.0, None, 40.0, 50.0])
+    assert s == {"n": 5, "median_ms": 30.0, "p90_ms": 50.0} and summarise_ttft([])["median_ms"] is None
+    base = {"median_ms": 100.0, "p90_ms": 150.0}
+    assert ttft_verdict({"median_ms": 105.0, "p90_ms": 160.0}, base) == {"verdict": "pass", "should_store": False, "why": ""}
+    assert ttft_verdict({"median_ms": 90.0, "p90_ms": 140.0}, base)["should_store"]              # a better run becomes the baseline
+    bad = ttft_verdict({"median_ms": 100.0, "p90_ms": 200.0}, base)
+    assert bad["verdict"] == "fail" and not bad["should_store"] and "p90_ms" in bad["why"]
+    assert ttft_verdict({"median_ms": 1.0, "p90_ms": 2.0}, None)["verdict"] == "no-baseline"
+    assert ttft_verdict({"median_ms": 1.0, "p90_ms": 2.0}, {"median_ms": None, "p90_ms": 3.0})["verdict"] == "no-baseline"
+    assert ttft_verdict({"median_ms": None, "p90_ms": None}, base)["verdict"] == "fail"
+    bl = TtftBaselines(str(tmp_path / "ttft.json"))
+    bl.store("http://localhost:8888", "m", "cold", base)
+    again = TtftBaselines(str(tmp_path / "ttft.json"))
+    assert again.find("127.0.0.1:8888", "m", "cold")["p90_ms"] == 150.0 and again.find("127.0.0.1:8888", "m", "warm") is None
+
+
+def test_speed_measurements_on_the_engine(tmp_path):
+    from metrale_inference_alpha_b200.bench.speed_gates import TtftBaselines, boot_memory, quick_speed, ttft_gate
+    eng = LLMEngine(EngineArgs(model="tiny-dense", device="cpu", max_num_seqs=4, max_model_len=256, num_kv_blocks=64))
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(1, eng.cfg.vocab_size, (48,), generator=g).tolist() for _ in range(4)]
+    q = quick_speed(eng, prompts[0], runs=2, max_tokens=8)
+    assert len(q["runs"]) == 2 and q["e2e_tok_s"] > 0 and all(r["completion_tokens"] == 8 for r in q["runs"])
+    bl = TtftBaselines(str(tmp_path / "b.json"))
+    first = ttft_gate(eng, prompts[1:], bl, kind="cold")
+    assert first["verdict"] == "no-baseline" and first["n"] == 3 and bl.find("in-process", eng.cfg.name, "cold") is not None
+    second = ttft_gate(eng, prompts[1:], bl, kind="warm", tolerance=100.0)
+    assert second["verdict"] == "no-baseline" and second["kind"] == "warm"                       # warm and cold keep separate baselines
+    third = ttft_gate(eng, prompts[1:], bl, kind="warm", tolerance=100.0)
+    assert third["verdict"] == "pass"
+    m = boot_memory(eng, warmup_prompts=prompts[:2])
+    assert m["verdict"] == "info" and m["kv_blocks"] == 64 and m["weights_bytes"] > 0
+    assert boot_memory(eng, budget_bytes=1)["verdict"] == "fail"
+    eng.close()
