@@ -208,3 +208,29 @@ def test_chat_completion_with_an_inline_image():
     plain = LLMEngine(EngineArgs(model="tiny-dense", num_kv_blocks=64, max_num_seqs=2, max_model_len=256))
     with TestClient(create_app(plain, tok, ServerConfig(model_name="tiny"))) as c:
         assert c.post("/v1/chat/completions", json=dict(body, model="tiny")).status_code == 400
+
+
+def test_media_integrity_gate_and_its_failure_classes():
+    from metrale_inference_alpha_b200.bench.media_integrity import judge, media_integrity
+    ok = [{"tokens": [1, 2], "cached_tokens": 0}, {"tokens": [1, 2], "cached_tokens": 32}, {"tokens": [3, 4], "cached_tokens": 16},
+          {"tokens": [1, 2], "cached_tokens": 32}]
+    assert judge(ok, placeholder_index=20, block_size=16)["pass"]
+    crossed = [dict(r) for r in ok]
+    crossed[2]["cached_tokens"] = 32
+    assert "more than the 16" in judge(crossed, 20, 16)["why"]
+    cold = [dict(r) for r in ok]
+    cold[1]["cached_tokens"] = 0
+    assert "did not hit" in judge(cold, 20, 16)["why"]
+    drift = [dict(r) for r in ok]
+    drift[3]["tokens"] = [1, 9]
+    assert "same image differ" in judge(drift, 20, 16)["why"]
+    blind = [dict(r) for r in ok]
+    blind[2]["tokens"] = [1, 2]
+    assert "does not depend" in judge(blind, 20, 16)["why"] and judge(blind, 20, 16, expect_different=False)["pass"]
+    assert not judge(ok[:3], 20, 16)["pass"]
+    eng = _vl_engine()
+    prompt = list(range(5, 25)) + [4001, 4000] + list(range(30, 50))
+    rec = media_integrity(eng, prompt, _image(1), _image(2), max_tokens=6, expect_different=False)
+    assert rec.value == 1.0, rec.config
+    assert rec.config["cached"][1] > 0 and rec.config["cached"][2] <= 16
+    eng.close()
